@@ -1,0 +1,528 @@
+"""CPU oracle for the FP4 training hot path (TEST INFRASTRUCTURE, not product code).
+
+Plain numpy restatement of the arithmetic of the reference CUDA kernels.  Only the test
+suite, ``__graft_entry__.smoke()`` and the CPU-baseline leg of ``bench.py`` may import it;
+the product path (the CUDA library and the Python shims over it) never does.
+
+Parity status: the shared arithmetic (E2M1 round-to-nearest-even, E4M3 cast, packing,
+global scale, coefficient, dequantise, block-wise GEMM) is pinned byte-for-byte against the
+reference's own CPU emulation ``NVFP4QuantizerRef`` (golden vectors under ``tests/golden``).
+The formulas that exist only in the CUDA sources (TK encode-centric, true-division
+decode-centric, scale swizzle, RMSNorm reduction tree, MXFP4 exponent modes, Philox stream
+order) are restated from those sources and cited per function; the reference CUDA kernels
+cannot be executed in the build container, so for those "parity unpinned" beyond the
+properties the reference's GPU tests assert (amax identity, sg == amax/2688, SR axis
+isolation), which the tests here re-assert.
+
+All functions take/return numpy arrays.  bf16 tensors travel as float32 arrays whose values
+are exactly representable in bf16 (use :func:`bf16_round`).
+"""
+from __future__ import annotations
+
+import numpy as np
+
+F32 = np.float32
+FLT_MAX = np.float32(3.4028235e38)
+
+# ----------------------------------------------------------------------------------------
+# bf16 helpers
+# ----------------------------------------------------------------------------------------
+
+def bf16_round(x: np.ndarray) -> np.ndarray:
+    """float32 -> nearest-even bf16, returned as float32 (``__float2bfloat16_rn``)."""
+    x = np.ascontiguousarray(x, dtype=np.float32)
+    u = x.view(np.uint32).astype(np.uint64)
+    lsb = (u >> 16) & 1
+    r = ((u + 0x7FFF + lsb) & 0xFFFF0000).astype(np.uint32)
+    out = r.view(np.float32).copy()
+    nan = np.isnan(x)
+    if nan.any():
+        out[nan] = np.float32(np.nan)
+    return out.reshape(x.shape)
+
+
+def bf16_bits(x: np.ndarray) -> np.ndarray:
+    """bf16-exact float32 array -> uint16 bit patterns."""
+    return (np.ascontiguousarray(x, dtype=np.float32).view(np.uint32) >> 16).astype(np.uint16)
+
+
+def bf16_from_bits(b: np.ndarray) -> np.ndarray:
+    return (b.astype(np.uint32) << 16).view(np.float32)
+
+
+# ----------------------------------------------------------------------------------------
+# E4M3 (fp8e4m3fn) and E2M1 codecs
+# ----------------------------------------------------------------------------------------
+
+def _e4m3_table() -> np.ndarray:
+    t = np.zeros(256, dtype=np.float64)
+    for c in range(256):
+        s = -1.0 if c & 0x80 else 1.0
+        e = (c >> 3) & 0xF
+        m = c & 7
+        if e == 0xF and m == 7:
+            v = np.nan
+        elif e == 0:
+            v = m * 2.0 ** -9
+        else:
+            v = (1 + m / 8.0) * 2.0 ** (e - 7)
+        t[c] = s * v
+    return t.astype(np.float32)
+
+
+E4M3_TO_F32 = _e4m3_table()
+
+
+def e4m3_encode(x: np.ndarray) -> np.ndarray:
+    """float32 -> E4M3 byte, round-to-nearest-even, saturating to +-448, subnormals kept.
+
+    Models ``static_cast<__nv_fp8_e4m3>(float)`` (``__NV_SATFINITE``) used for every block
+    scale (nvfp4_v5/core.cuh:39-60).  NaN -> 0x7F.
+    """
+    x = np.asarray(x, dtype=np.float32)
+    a = np.abs(x).astype(np.float64)
+    sign = (np.signbit(x)).astype(np.uint8) << 7
+    code = np.zeros(x.shape, dtype=np.int64)
+    sub = a < 2.0 ** -6
+    q_sub = np.rint(a / 2.0 ** -9)
+    with np.errstate(divide="ignore", invalid="ignore"):
+        mant, ex = np.frexp(np.where(sub | ~np.isfinite(a), 1.0, a))  # a = mant * 2**ex, mant in [0.5,1)
+    e = ex - 1
+    q = np.rint((mant * 2.0 - 1.0) * 8.0)
+    carry = q == 8
+    e = np.where(carry, e + 1, e)
+    q = np.where(carry, 0, q)
+    norm_code = ((e + 7).astype(np.int64) << 3) | q.astype(np.int64)
+    code = np.where(sub, q_sub.astype(np.int64), norm_code)
+    # saturate: anything that would round above 448 (incl. inf) -> 0x7E
+    too_big = (~sub) & ((e > 8) | ((e == 8) & (q == 7)))
+    code = np.where(too_big | np.isinf(a), 0x7E, code)
+    code = np.where(np.isnan(a), 0x7F, code)
+    return (code.astype(np.uint8) | sign).astype(np.uint8)
+
+
+def e4m3_decode(b: np.ndarray) -> np.ndarray:
+    return E4M3_TO_F32[np.asarray(b, dtype=np.uint8)]
+
+
+E2M1_TO_F32 = np.array([0, .5, 1, 1.5, 2, 3, 4, 6, -0.0, -.5, -1, -1.5, -2, -3, -4, -6], dtype=np.float32)
+
+
+def e2m1_encode_rn(v: np.ndarray) -> np.ndarray:
+    """float32 -> 4-bit E2M1 code, round-to-nearest-even with saturation to +-6.
+
+    ``cvt.rn.satfinite.e2m1x2.f32`` (nvfp4_v5/util/ptx.cuh:783-825).  Tie rules are the
+    ones pinned by the reference's ``cast_to_fp4x2`` (quantization_nvfp4.py:58-74); unlike
+    that Python helper the hardware keeps the sign bit of zero and of values that round to
+    zero, and so does this function.
+    """
+    v = np.asarray(v, dtype=np.float32)
+    a = np.abs(v)
+    idx = np.zeros(v.shape, dtype=np.uint8)
+    idx = np.where(a > 0.25, 1, idx)
+    idx = np.where(a >= 0.75, 2, idx)
+    idx = np.where(a > 1.25, 3, idx)
+    idx = np.where(a >= 1.75, 4, idx)
+    idx = np.where(a > 2.5, 5, idx)
+    idx = np.where(a >= 3.5, 6, idx)
+    idx = np.where(a > 5.0, 7, idx)
+    idx = np.where(np.isnan(v), 7, idx)
+    return (idx.astype(np.uint8) | (np.signbit(v).astype(np.uint8) << 3)).astype(np.uint8)
+
+
+def pack_fp4(codes: np.ndarray) -> np.ndarray:
+    """[R, C] 4-bit codes -> [R, C/2] bytes, even element in the low nibble
+    (quantization_nvfp4.py:76; PTX operand order nvfp4_v5/util/ptx.cuh:811-822)."""
+    codes = np.asarray(codes, dtype=np.uint8)
+    return (codes[..., 0::2] | (codes[..., 1::2] << 4)).astype(np.uint8)
+
+
+def unpack_fp4(packed: np.ndarray) -> np.ndarray:
+    packed = np.asarray(packed, dtype=np.uint8)
+    out = np.empty(packed.shape[:-1] + (packed.shape[-1] * 2,), dtype=np.uint8)
+    out[..., 0::2] = packed & 0xF
+    out[..., 1::2] = packed >> 4
+    return out
+
+
+# ----------------------------------------------------------------------------------------
+# NVFP4 scale rules
+# ----------------------------------------------------------------------------------------
+
+def nvfp4_global_encode_scale(amax) -> np.float32:
+    """``S_enc = min(448*6/amax, FLT_MAX)``, 1 when amax == 0 or the quotient is 0
+    (nvfp4_v5/core.cuh:100-113)."""
+    amax = np.float32(amax)
+    if amax == 0:
+        return np.float32(1.0)
+    with np.errstate(over="ignore", divide="ignore"):
+        s = np.float32(np.float32(448.0 * 6.0) / amax)
+    s = np.float32(min(s, FLT_MAX))
+    if s == 0:
+        return np.float32(1.0)
+    return s
+
+
+def nvfp4_global_decode_scale(amax) -> np.float32:
+    """GEMM-side tensor scale ``sg = amax / 2688`` (fp32 division;
+    nvfp4_v5/persistent_quantize.cuh:592, tk_quantize.cu:1020-1021)."""
+    return np.float32(np.float32(amax) / np.float32(2688.0))
+
+
+def nvfp4_block_scale(block_amax: np.ndarray, s_enc, mode: str):
+    """Per-16 block: returns (stored E4M3 byte, fp32 coefficient applied before the E2M1 cast).
+
+    mode "encode": TK encode-centric (core.cuh:51-60, fused_amax_quantize.cuh:267-270):
+        m8 = e4m3(448) if b <= 1e-9 else e4m3(min(6/(b*S_enc), FLT_MAX));
+        coeff = float(m8)*S_enc; stored = e4m3(1/float(m8)).
+    mode "decode": TK decode-centric, true division (core.cuh:39-46,
+        fused_amax_quantize.cuh:271-276): s8 = e4m3(min(b/6*S_enc, FLT_MAX));
+        coeff = min(1/(float(s8)*(1/S_enc)), FLT_MAX).
+    mode "decode_te": the reference's CPU emulation (quantization_nvfp4.py:580-610):
+        s8 = e4m3(clamp(b * (S_enc * (1/6)), 448)); same coefficient formula.
+    """
+    b = np.asarray(block_amax, dtype=np.float32)
+    s_enc = np.float32(s_enc)
+    with np.errstate(over="ignore", divide="ignore", invalid="ignore"):
+        if mode == "encode":
+            m = (F32(6.0) / (b * s_enc).astype(F32)).astype(F32)
+            m = np.minimum(m, FLT_MAX)
+            m8 = e4m3_encode(m)
+            m8 = np.where(b <= F32(1.0e-9), np.uint8(0x7E), m8).astype(np.uint8)
+            mf = e4m3_decode(m8)
+            coeff = (mf * s_enc).astype(F32)
+            stored = e4m3_encode((F32(1.0) / mf).astype(F32))
+            return stored, coeff
+        if mode == "decode":
+            s = ((b / F32(6.0)).astype(F32) * s_enc).astype(F32)
+        elif mode == "decode_te":
+            s = (b * F32(s_enc * F32(F32(1.0) / F32(6.0)))).astype(F32)
+        else:
+            raise ValueError(mode)
+        s = np.minimum(s, FLT_MAX)
+        s8 = e4m3_encode(s)
+        s_dec = F32(F32(1.0) / s_enc)
+        coeff = (F32(1.0) / (e4m3_decode(s8) * s_dec).astype(F32)).astype(F32)
+        coeff = np.minimum(coeff, FLT_MAX)  # 1/0 = inf -> FLT_MAX
+        return s8, coeff
+
+
+def nvfp4_quantize_1d(x: np.ndarray, amax, mode: str = "encode"):
+    """Quantise bf16-exact ``x [R, C]`` along its last axis in 16-element blocks.
+
+    Returns (packed codes [R, C/2] u8, scale bytes [R, C/16] u8 in logical order).
+    codes = e2m1_rn(float(x) * coeff) with the product rounded to fp32 (``mul.f32x2`` then
+    cvt, nvfp4_v5/util/ptx.cuh:783-825).
+    """
+    x = np.asarray(x, dtype=np.float32)
+    R, C = x.shape
+    assert C % 16 == 0
+    xb = x.reshape(R, C // 16, 16)
+    b = np.abs(xb).max(axis=-1)
+    s_enc = nvfp4_global_encode_scale(amax)
+    stored, coeff = nvfp4_block_scale(b, s_enc, mode)
+    with np.errstate(over="ignore", invalid="ignore"):
+        scaled = (xb * coeff[..., None]).astype(F32)
+    codes = e2m1_encode_rn(scaled).reshape(R, C)
+    return pack_fp4(codes), stored
+
+
+def nvfp4_quantize_2d(w: np.ndarray, amax):
+    """16x16-block weight quantisation: one block amax shared by both orientations,
+    decode-centric (nvfp4_v5/tk_quantize.cu:2493-2538).  Returns row codes/scales and
+    column (transposed) codes/scales; the column pair is the exact transpose of the row pair.
+    """
+    w = np.asarray(w, dtype=np.float32)
+    R, C = w.shape
+    assert R % 16 == 0 and C % 16 == 0
+    t = np.abs(w).reshape(R // 16, 16, C // 16, 16).max(axis=(1, 3))  # [R/16, C/16]
+    s_enc = nvfp4_global_encode_scale(amax)
+    s8, coeff = nvfp4_block_scale(t, s_enc, "decode")
+    coeff_full = np.repeat(np.repeat(coeff, 16, axis=0), 16, axis=1)
+    with np.errstate(over="ignore", invalid="ignore"):
+        codes = e2m1_encode_rn((w * coeff_full).astype(F32))
+    row_sc = np.repeat(s8, 16, axis=0)  # [R, C/16]
+    col_sc = np.repeat(s8.T, 16, axis=0)  # [C, R/16]
+    return pack_fp4(codes), row_sc, pack_fp4(np.ascontiguousarray(codes.T)), col_sc
+
+
+# ----------------------------------------------------------------------------------------
+# Scale swizzle (128-row x 4-block tiles of 512 bytes)
+# ----------------------------------------------------------------------------------------
+
+def swizzle_scales(S: np.ndarray) -> np.ndarray:
+    """Logical ``S[rows, nb]`` -> flat bytes in ``[rows/128, nb/4, 512]`` tile order with
+    ``off = (r%32)*16 + ((r%128)/32)*4 + (kb%4)`` inside a tile
+    (nvfp4_v5/persistent_quantize.cuh:33-36, quantize_transpose_tuned.cuh:871-896)."""
+    S = np.asarray(S, dtype=np.uint8)
+    rows, nb = S.shape
+    assert rows % 128 == 0 and nb % 4 == 0
+    t = S.reshape(rows // 128, 4, 32, nb // 4, 4)      # [tm, group, j, tk, kq]
+    t = t.transpose(0, 3, 2, 1, 4)                      # [tm, tk, j, group, kq]
+    return np.ascontiguousarray(t).reshape(rows // 128, nb // 4, 512)
+
+
+def unswizzle_scales(T: np.ndarray, rows: int, nb: int) -> np.ndarray:
+    t = np.asarray(T, dtype=np.uint8).reshape(rows // 128, nb // 4, 32, 4, 4)
+    return np.ascontiguousarray(t.transpose(0, 3, 2, 1, 4)).reshape(rows, nb)
+
+
+# ----------------------------------------------------------------------------------------
+# Whole-operator restatements (NVFP4)
+# ----------------------------------------------------------------------------------------
+
+def tensor_amax(x: np.ndarray) -> np.float32:
+    return np.float32(np.abs(np.asarray(x, dtype=np.float32)).max()) if x.size else np.float32(0)
+
+
+def nvfp4_quantize_for_gemm(x: np.ndarray, return_transpose=True, encode_centric=True, amax=None):
+    """``tk_quantize_for_gemm`` (nvfp4_v5/tk_quantize.cu:2208-2412): one tensor amax for both
+    orientations.  Returns dict with row_fp4, row_sc (swizzled), col_fp4, col_sc, sg, amax."""
+    x = np.asarray(x, dtype=np.float32)
+    M, K = x.shape
+    amax = tensor_amax(x) if amax is None else np.float32(amax)
+    mode = "encode" if encode_centric else "decode"
+    row_fp4, row_s = nvfp4_quantize_1d(x, amax, mode)
+    out = dict(row_fp4=row_fp4, row_sc=swizzle_scales(row_s), row_sc_logical=row_s,
+               sg=nvfp4_global_decode_scale(amax), amax=amax)
+    if return_transpose:
+        col_fp4, col_s = nvfp4_quantize_1d(np.ascontiguousarray(x.T), amax, mode)
+        out.update(col_fp4=col_fp4, col_sc=swizzle_scales(col_s), col_sc_logical=col_s)
+    return out
+
+
+def rmsnorm_inv_rms(x: np.ndarray, eps: float) -> np.ndarray:
+    """Per-row ``rsqrt(sum(x^2)/K + eps)`` with the reduction tree of the reference's pass-1
+    kernel (nvfp4_v5/tk_quantize.cu:1041-1064): 256 lanes, lane t accumulates columns
+    2t, 2t+1, 2t+512, 2t+513, ... sequentially with fmaf (exact here: a bf16 square is exact
+    in fp32), xor-butterfly adds over masks 16..1 inside each warp, then over the 8 warp
+    partials with masks 4,2,1.  The final rsqrt is the CPU's correctly rounded value; the
+    GPU's ``rsqrtf`` may differ from it in the last bits.
+    """
+    x = np.asarray(x, dtype=np.float32)
+    M, K = x.shape
+    acc = np.zeros((M, 256), dtype=np.float32)
+    sq = (x * x).astype(np.float32)  # exact
+    for base in range(0, K, 512):
+        blk = sq[:, base:base + 512]
+        n = blk.shape[1] // 2
+        acc[:, :n] = (acc[:, :n] + blk[:, 0::2]).astype(F32)
+        acc[:, :n] = (acc[:, :n] + blk[:, 1::2]).astype(F32)
+    v = acc.reshape(M, 8, 32)
+    for mask in (16, 8, 4, 2, 1):
+        idx = np.arange(32) ^ mask
+        v = (v + v[:, :, idx]).astype(F32)
+    w = v[:, :, 0]
+    for mask in (4, 2, 1):
+        idx = np.arange(8) ^ mask
+        w = (w + w[:, idx]).astype(F32)
+    s = w[:, 0]
+    mean = ((s / F32(K)).astype(F32) + F32(eps)).astype(F32)
+    return (1.0 / np.sqrt(mean.astype(np.float64))).astype(np.float32)
+
+
+def rmsnorm_apply(x: np.ndarray, inv_rms: np.ndarray, gamma: np.ndarray) -> np.ndarray:
+    """``n = bf16_rn((float(x) * inv_rms) * float(gamma_bf16))``, left to right in fp32
+    (nvfp4_v5/tk_quantize.cu:1082-1088, quantize_transpose_tuned.cuh:769-776)."""
+    x = np.asarray(x, dtype=np.float32)
+    t = (x * np.asarray(inv_rms, dtype=F32)[:, None]).astype(F32)
+    t = (t * np.asarray(gamma, dtype=F32)[None, :]).astype(F32)
+    return bf16_round(t)
+
+
+def nvfp4_fused_norm_quantize(x, gamma, eps, inv_rms=None):
+    """``tk_fused_norm_quantize`` default (barrier-free) branch, encode-centric hard-wired
+    (nvfp4_v5/tk_quantize.cu:8048-8108).  ``inv_rms`` may be supplied
+    (``tk_fused_norm_quantize_from_inv_rms``, :8250-8259)."""
+    if inv_rms is None:
+        inv_rms = rmsnorm_inv_rms(x, eps)
+    n = rmsnorm_apply(x, inv_rms, gamma)
+    out = nvfp4_quantize_for_gemm(n, True, True)
+    out["inv_rms"] = np.asarray(inv_rms, dtype=F32)
+    out["normed"] = n
+    return out
+
+
+def silu_mul(h1: np.ndarray, h3: np.ndarray) -> np.ndarray:
+    """``h = bf16_rn((x / (1 + exp(-x))) * h3)`` (nvfp4_v5/silu_split_bf16.cuh:7-9,96-104).
+    The GPU uses ``__expf``; compare to 1 bf16 ulp, not bytes."""
+    x = np.asarray(h1, dtype=np.float32)
+    with np.errstate(over="ignore"):
+        s = (x / (F32(1.0) + np.exp(-x).astype(F32)).astype(F32)).astype(F32)
+    return bf16_round((s * np.asarray(h3, dtype=F32)).astype(F32))
+
+
+def silu_deriv(dh, h3, h1):
+    """``dh1 = bf16(dh*h3*silu'(h1))``, ``dh3 = bf16(dh*silu(h1))`` with
+    ``silu' = sig*(1 + x - x*sig)`` (nvfp4_v5/silu_split_bf16.cuh:226-249)."""
+    x = np.asarray(h1, dtype=F32)
+    dh = np.asarray(dh, dtype=F32)
+    h3 = np.asarray(h3, dtype=F32)
+    with np.errstate(over="ignore"):
+        sig = (F32(1.0) / (F32(1.0) + np.exp(-x).astype(F32)).astype(F32)).astype(F32)
+    silu = (x * sig).astype(F32)
+    dsilu = (sig * ((F32(1.0) + x).astype(F32) - silu).astype(F32)).astype(F32)
+    dh1 = bf16_round(((dh * h3).astype(F32) * dsilu).astype(F32))
+    dh3 = bf16_round((dh * silu).astype(F32))
+    return dh1, dh3
+
+
+# ----------------------------------------------------------------------------------------
+# RHT-16
+# ----------------------------------------------------------------------------------------
+
+RHT_SIGN_LITERAL = 0x2817  # bit i set => +1 at position i (mxfp4_v3_quantize.cuh:1461-1508)
+
+
+def rht_fixed_signs() -> np.ndarray:
+    return np.array([1.0 if (RHT_SIGN_LITERAL >> i) & 1 else -1.0 for i in range(16)], dtype=F32)
+
+
+def _splitmix32_sign(seed: int, subseq: int, c: np.ndarray) -> np.ndarray:
+    """+1/-1 per coordinate ``c`` along the transformed axis (nvfp4_v5/tk_quantize.cu:483-488,
+    613-633): 64-bit mix of seed ^ subseq*0xd1b54a32d192ed03 ^ c*0x9e3779b97f4a7c15, low bit."""
+    M64 = (1 << 64) - 1
+    out = np.empty(len(c), dtype=F32)
+    for i, ci in enumerate(c):
+        z = (seed ^ ((subseq * 0xD1B54A32D192ED03) & M64) ^ ((int(ci) * 0x9E3779B97F4A7C15) & M64)) & M64
+        z = (z + 0x9E3779B97F4A7C15) & M64
+        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
+        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
+        z = z ^ (z >> 31)
+        out[i] = 1.0 if (z & 1) else -1.0
+    return out
+
+
+def fwht16_bf16(x: np.ndarray, signs: np.ndarray | None = None) -> np.ndarray:
+    """Per 16 contiguous elements of the last axis: optional sign flip, unnormalised
+    Sylvester butterflies (step 1,2,4,8), x0.25, all fp32, rounded to bf16
+    (nvfp4_v5/quantize_transpose_tuned.cuh:161-179,301-321)."""
+    x = np.asarray(x, dtype=F32)
+    R, C = x.shape
+    v = x.reshape(R, C // 16, 16).copy()
+    if signs is not None:
+        v = (v * np.asarray(signs, dtype=F32).reshape(1, -1, 16) if np.size(signs) == C
+             else v * np.asarray(signs, dtype=F32).reshape(1, 1, 16)).astype(F32)
+    step = 1
+    while step < 16:
+        for base in range(0, 16, 2 * step):
+            for j in range(step):
+                a = v[..., base + j].copy()
+                b = v[..., base + j + step].copy()
+                v[..., base + j] = (a + b).astype(F32)
+                v[..., base + j + step] = (a - b).astype(F32)
+        step <<= 1
+    v = (v * F32(0.25)).astype(F32)
+    return bf16_round(v.reshape(R, C))
+
+
+# ----------------------------------------------------------------------------------------
+# Dequantise and GEMM definitions
+# ----------------------------------------------------------------------------------------
+
+def nvfp4_dequantize(fp4: np.ndarray, sc_logical: np.ndarray, sg) -> np.ndarray:
+    """value = code * float(s8) * sg (fp32) — quantization_nvfp4.py:259-288 with sg = amax/2688."""
+    vals = E2M1_TO_F32[unpack_fp4(fp4)]
+    s = e4m3_decode(sc_logical)
+    return (vals * np.repeat(s, 16, axis=1) * F32(sg)).astype(F32)
+
+
+def nvfp4_gemm_fp32(a_fp4, a_sc_logical, a_sg, b_fp4, b_sc_logical, b_sg) -> np.ndarray:
+    """``D = (sum_k codeA*sA*codeB*sB) * (sgA*sgB)`` accumulated in high precision, returned
+    fp32 (nvfp4_b200/nvfp4_gemm.cuh:735-754,911-920).  A [M,K/2], B [N,K/2]."""
+    a = (E2M1_TO_F32[unpack_fp4(a_fp4)] * np.repeat(e4m3_decode(a_sc_logical), 16, axis=1)).astype(np.float64)
+    b = (E2M1_TO_F32[unpack_fp4(b_fp4)] * np.repeat(e4m3_decode(b_sc_logical), 16, axis=1)).astype(np.float64)
+    acc = a @ b.T
+    gs = F32(F32(a_sg) * F32(b_sg))
+    return (acc.astype(F32) * gs).astype(F32)
+
+
+# ----------------------------------------------------------------------------------------
+# MXFP4 (32-blocks, E8M0 scales)
+# ----------------------------------------------------------------------------------------
+
+def mx_e8m0(block_amax: np.ndarray, mode: int = 1) -> np.ndarray:
+    """Biased exponent byte of a 32-block (mxfp4_v4/mxfp4_v3_quantize.cuh:1305-1342):
+    0 if b <= 1e-38; else fp32 exponent of b, +1 when (mode 1 / ceil) mantissa != 0,
+    (mode 0 / RTE) mantissa > half or == half with odd exponent, (mode 2 / floor) never;
+    capped at 0xFE."""
+    b = np.asarray(block_amax, dtype=np.float32)
+    bits = b.view(np.uint32) if b.flags["C_CONTIGUOUS"] else np.ascontiguousarray(b).view(np.uint32)
+    e = ((bits >> 23) & 0xFF).astype(np.int64)
+    m = (bits & 0x7FFFFF).astype(np.int64)
+    if mode == 1:
+        inc = m != 0
+    elif mode == 0:
+        inc = (m > 0x400000) | ((m == 0x400000) & ((e & 1) == 1))
+    elif mode == 2:
+        inc = np.zeros_like(m, dtype=bool)
+    else:
+        raise ValueError(mode)
+    e = np.minimum(e + inc.astype(np.int64), 0xFE)
+    e = np.where(b <= F32(1e-38), 0, e)
+    return e.astype(np.uint8)
+
+
+def mxfp4_quantize_1d(x: np.ndarray, mode: int = 1):
+    """codes = e2m1_rn(x * 6 * 2^(127-e)) per 32-block (mxfp4_v3_quantize.cuh:1601-1603,
+    util/ptx.cuh:330-338).  Returns (packed [R,C/2], e8m0 bytes [R,C/32])."""
+    x = np.asarray(x, dtype=F32)
+    R, C = x.shape
+    assert C % 32 == 0
+    xb = x.reshape(R, C // 32, 32)
+    b = np.abs(xb).max(axis=-1)
+    e = mx_e8m0(b, mode)
+    # exp2f_rcp: 2^(127-e) as an fp32 built from the exponent field (e==0 -> 2^127)
+    rcp_bits = ((254 - e.astype(np.int64)).clip(0, 254).astype(np.uint32) << 23)
+    rcp = rcp_bits.view(np.float32)
+    rcp = np.where(e == 254, F32(2.0 ** -127), rcp).astype(F32)
+    with np.errstate(over="ignore", invalid="ignore"):
+        coeff = (F32(6.0) * rcp).astype(F32)
+        scaled = (xb * coeff[..., None]).astype(F32)
+    return pack_fp4(e2m1_encode_rn(scaled).reshape(R, C)), e
+
+
+def mxfp4_quantize_row_and_col(x: np.ndarray, mode: int = 1):
+    """``mxfp4_quantize_row_and_col`` (mxfp4_v4/tk_quantize.cu:1883-2060): scales stored in
+    the same 512-byte swizzle with 4 scales per row per tile -> [rows/128, C/128, 32, 16]."""
+    x = np.asarray(x, dtype=F32)
+    r_fp4, r_e = mxfp4_quantize_1d(x, mode)
+    c_fp4, c_e = mxfp4_quantize_1d(np.ascontiguousarray(x.T), mode)
+    return dict(row_fp4=r_fp4, row_sc=swizzle_scales(r_e), row_sc_logical=r_e,
+                col_fp4=c_fp4, col_sc=swizzle_scales(c_e), col_sc_logical=c_e)
+
+
+def mxfp4_gemm_fp32(a_fp4, a_e, b_fp4, b_e) -> np.ndarray:
+    """``D = (sum code_a*2^(ea-127)*code_b*2^(eb-127)) / 36`` (mxfp4_gb200/mxfp4_gemm.cuh:557-558)."""
+    sa = np.exp2(a_e.astype(np.float64) - 127.0)
+    sb = np.exp2(b_e.astype(np.float64) - 127.0)
+    a = E2M1_TO_F32[unpack_fp4(a_fp4)].astype(np.float64) * np.repeat(sa, 32, axis=1)
+    b = E2M1_TO_F32[unpack_fp4(b_fp4)].astype(np.float64) * np.repeat(sb, 32, axis=1)
+    return ((a @ b.T).astype(F32) * F32(1.0 / 36.0)).astype(F32)
+
+
+def mxfp4_dequantize(fp4, e) -> np.ndarray:
+    s = np.exp2(e.astype(np.float64) - 127.0) / 6.0
+    return (E2M1_TO_F32[unpack_fp4(fp4)].astype(np.float64) * np.repeat(s, 32, axis=1)).astype(F32)
+
+
+# ----------------------------------------------------------------------------------------
+# Synthetic inputs shared by tests, smoke and bench (seeded, CPU generator)
+# ----------------------------------------------------------------------------------------
+
+def make_activations(M: int, K: int, seed: int, scale: float = 1.0, outlier_frac: float = 0.001,
+                     outlier_mult: float = 20.0) -> np.ndarray:
+    """bf16-exact float32 ``N(0,scale)`` with ``outlier_frac`` of the channels multiplied by
+    ``outlier_mult`` — the activation recipe of the benchmark configurations."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal((M, K), dtype=np.float32) * F32(scale)
+    n_out = int(round(K * outlier_frac))
+    if n_out:
+        cols = rng.permutation(K)[:n_out]
+        x[:, cols] *= F32(outlier_mult)
+    return bf16_round(x)
+
+
+def make_gamma(K: int, seed: int) -> np.ndarray:
+    rng = np.random.default_rng(seed)
+    return bf16_round((1.0 + 0.1 * rng.standard_normal(K)).astype(F32))

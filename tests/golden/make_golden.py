@@ -1,0 +1,137 @@
+"""Generate the golden vectors under tests/golden from the reference's own CPU emulation.
+
+Run in the build container only (it needs the reference checkout):
+
+    python tests/golden/make_golden.py --reference /root/reference
+
+It loads ``transformer_engine/pytorch/custom_recipes/quantization_nvfp4.py`` (and its two
+small helper modules) straight from the reference tree, with stub parents injected into
+``sys.modules`` because the compiled ``transformer_engine`` package is not installable here.
+Nothing from the reference is copied into this repository: only seeded inputs (as bf16 bit
+patterns) and the bytes the reference produced for them are stored.
+"""
+from __future__ import annotations
+
+import argparse
+import importlib.util
+import os
+import sys
+import types
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+
+
+def load_reference(root: str):
+    base = os.path.join(root, "TransformerEngine", "transformer_engine", "pytorch", "custom_recipes")
+    for name in ("transformer_engine", "transformer_engine.pytorch",
+                 "transformer_engine.pytorch.custom_recipes",
+                 "transformer_engine.pytorch.quantized_tensor"):
+        if name not in sys.modules:
+            m = types.ModuleType(name)
+            m.__path__ = []
+            sys.modules[name] = m
+    qt = sys.modules["transformer_engine.pytorch.quantized_tensor"]
+
+    class QuantizedTensorStorage:  # empty base, as the emulation only subclasses it
+        pass
+
+    class Quantizer:
+        def __init__(self, rowwise: bool = True, columnwise: bool = True):
+            self.rowwise_usage = rowwise
+            self.columnwise_usage = columnwise
+
+    qt.QuantizedTensorStorage = QuantizedTensorStorage
+    qt.Quantizer = Quantizer
+    mods = {}
+    for short in ("utils", "quantization", "quantization_nvfp4"):
+        full = f"transformer_engine.pytorch.custom_recipes.{short}"
+        spec = importlib.util.spec_from_file_location(full, os.path.join(base, short + ".py"))
+        mod = importlib.util.module_from_spec(spec)
+        sys.modules[full] = mod
+        setattr(sys.modules["transformer_engine.pytorch.custom_recipes"], short, mod)
+        spec.loader.exec_module(mod)
+        mods[short] = mod
+    return mods
+
+
+def bf16_bits(t: torch.Tensor) -> np.ndarray:
+    return t.contiguous().view(torch.int16).numpy().astype(np.uint16)
+
+
+def make_inputs(M, K, N, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(M, K, generator=g)
+    cols = torch.randperm(K, generator=g)[: max(1, K // 1000)]
+    x[:, cols] *= 20.0
+    w = 0.02 * torch.randn(N, K, generator=g)
+    return x.to(torch.bfloat16), w.to(torch.bfloat16)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    mods = load_reference(args.reference)
+    qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]
+
+    out = {}
+    # (1) E2M1 value table / tie rules as pinned by cast_to_fp4x2 / cast_from_fp4x2
+    probe = torch.tensor([[-7.0, -6.0, -5.0, -4.5, -3.5, -3.0, -2.5, -2.0, -1.75, -1.5, -1.25, -1.0,
+                           -0.75, -0.5, -0.25, -0.1, 0.0, 0.1, 0.25, 0.5, 0.75, 1.0, 1.25, 1.5, 1.75,
+                           2.0, 2.5, 3.0, 3.5, 4.5, 5.0, 5.01, 6.0, 7.0, 0.2500001, 0.7499999]],
+                         dtype=torch.float32)
+    out["e2m1_probe_in"] = probe.numpy()
+    out["e2m1_probe_packed"] = qn.cast_to_fp4x2(probe.clamp(-6, 6)).numpy()
+    out["e2m1_lut"] = qn.cast_from_fp4x2(torch.arange(256, dtype=torch.uint8).view(1, -1), torch.float32).numpy()
+    out["wgrad_sign_vector"] = qn.get_wgrad_sign_vector().numpy()
+
+    # (2) quantise + qgemm on seeded inputs, decode-centric (the emulation's default) and its
+    #     encode-centric branch, 1x16 tiles, plus 16x16 weight tiles.
+    for tag, (M, K, N, seed) in {"small": (128, 256, 128, 1234), "mid": (256, 512, 384, 20260903)}.items():
+        x, w = make_inputs(M, K, N, seed)
+        out[f"{tag}_x_bits"] = bf16_bits(x)
+        out[f"{tag}_w_bits"] = bf16_bits(w)
+        for ec in (False, True):
+            q = qn.NVFP4QuantizerRef(dtype=utils.Fp4Formats.E2M1, rowwise=True, columnwise=True,
+                                     quant_tile_shape=(1, 16), encode_centric=ec)
+            qx = q.quantize(x)
+            qw = q.quantize(w)
+            pre = f"{tag}_{'ec' if ec else 'dc'}"
+            out[f"{pre}_x_data"] = qx.data.numpy()
+            out[f"{pre}_x_scale"] = qx.scale.view(torch.uint8).numpy()
+            out[f"{pre}_x_data_t"] = qx.data_t.numpy()
+            out[f"{pre}_x_scale_t"] = qx.scale_t.view(torch.uint8).numpy()
+            out[f"{pre}_x_amax"] = qx.global_amax_row.numpy()
+            out[f"{pre}_w_data"] = qw.data.numpy()
+            out[f"{pre}_w_scale"] = qw.scale.view(torch.uint8).numpy()
+            out[f"{pre}_w_amax"] = qw.global_amax_row.numpy()
+            if not ec:
+                y = q.qgemm(qx.data, qw.data, quantization.MMParams(), torch.float32,
+                            qx.scale, qw.scale, qresult_x=qx, qresult_w=qw)
+                out[f"{pre}_qgemm_f32"] = y.numpy()
+                out[f"{pre}_x_deq"] = qx.dequantize(torch.float32).numpy()
+        q2 = qn.NVFP4QuantizerRef(dtype=utils.Fp4Formats.E2M1, rowwise=True, columnwise=True,
+                                  quant_tile_shape=(16, 16))
+        qw2 = q2.quantize(w)
+        out[f"{tag}_2d_w_data"] = qw2.data.numpy()
+        out[f"{tag}_2d_w_scale"] = qw2.scale.view(torch.uint8).numpy()
+        out[f"{tag}_2d_w_data_t"] = qw2.data_t.numpy()
+        out[f"{tag}_2d_w_scale_t"] = qw2.scale_t.view(torch.uint8).numpy()
+
+    # (3) exhaustive E4M3 cast table on a sweep of fp32 inputs within the clamp range
+    sweep = torch.cat([torch.linspace(0, 448, 20001), torch.logspace(-12, 2.7, 20001),
+                       torch.tensor([2.0 ** -10, 2.0 ** -9, 1.5 * 2.0 ** -9, 2.0 ** -6, 464.0, 448.0])]).float()
+    sweep = sweep.clamp(max=448.0)
+    out["e4m3_sweep_in"] = sweep.numpy()
+    out["e4m3_sweep_out"] = sweep.to(torch.float8_e4m3fn).view(torch.uint8).numpy()
+
+    path = os.path.join(HERE, "nvfp4_reference_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
+if __name__ == "__main__":
+    main()
