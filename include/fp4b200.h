@@ -1,0 +1,89 @@
+/* libfp4b200 — C ABI of the B200 (sm_100a) FP4 training hot path.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle
+ * (cudaStream_t passed as void*; NULL = the legacy default stream), enqueues its kernels on
+ * that stream and returns without synchronising.  Return value: 0 on success, -1 on a
+ * rejected argument or a CUDA launch error, with a message available from
+ * fp4b200_last_error() (thread-local).  Outputs are caller-allocated; no entry point
+ * allocates device memory unless its comment says so.
+ *
+ * Reference paths are relative to the reference repository root.
+ *
+ * Layouts (identical to the reference extensions):
+ *   packed codes   uint8 [rows, cols/2], element 2j in the low nibble of byte j
+ *   NVFP4 scales   E4M3 bytes, tiles of 128 rows x 4 blocks = 512 bytes,
+ *                  [rows/128, cols/64, 512], offset (r%32)*16 + ((r%128)/32)*4 + (kb%4)
+ *   MXFP4 scales   E8M0 bytes, same 512-byte tile, [rows/128, cols/128, 32, 16]
+ *   amax_sg        float[2]: [0] tensor amax, [1] sg = amax / 2688 (GEMM-side tensor scale)
+ */
+#ifndef FP4B200_H_
+#define FP4B200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- housekeeping --------------------------------------------------------------------- */
+
+/* Message of the last failed call on this thread ("" if none). */
+const char* fp4b200_last_error(void);
+/* ABI revision of this header. */
+int fp4b200_abi_version(void);
+/* Synchronises the current device, returns and clears the device status word: 0, or the code
+ * of a kernel that gave up a bounded wait (1 quantiser TMA, 2..5 GEMM pipeline stages).
+ * The reference has no counterpart: its kernels spin without a limit
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/fused_amax_quantize.cuh:198-206). */
+int fp4b200_device_status(void);
+
+/* ---- NVFP4 producers ------------------------------------------------------------------ */
+
+/* Tensor amax of a bf16 buffer and sg = amax/2688.
+ * Replaces pipelined_amax::fused_amax_pipelined_kernel
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/amax_pipelined.cuh:26-48,504-512). */
+int fp4b200_nvfp4_amax(const void* x_bf16, int64_t n_elems, float* amax_sg, void* stream);
+
+/* Row-wise (and, when col_* are non-NULL, column-wise) NVFP4 quantisation of bf16 [M,K]
+ * from given device-resident tensor amaxes (amax_col NULL = same as amax_row).  M, K
+ * multiples of 128.  sg_out (optional) receives amax_row/2688.
+ * Replaces tk_quantize_transpose / quantize_transpose_nvfp4_tuned_1D_kernel, RTN path
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:3807-3926,
+ *  quantize_transpose_tuned.cuh:530-1007). */
+int fp4b200_nvfp4_quantize(const void* x_bf16, int64_t M, int64_t K, const float* amax_row,
+                           const float* amax_col, int encode_centric, void* row_fp4, void* row_sc,
+                           void* col_fp4, void* col_sc, float* sg_out, void* stream);
+
+/* amax + quantise in one call: tk_quantize_for_gemm(input, return_transpose, encode_centric)
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:2208-2412). */
+int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, int return_transpose,
+                                    int encode_centric, void* row_fp4, void* row_sc, void* col_fp4,
+                                    void* col_sc, float* amax_sg, void* stream);
+
+/* RMSNorm statistics: inv_rms[M] = rsqrt(mean(x^2)+eps) (computed when compute_inv_rms != 0,
+ * else read) and amax of bf16(x*inv_rms*gamma).
+ * Replaces rmsnorm_bf16_amax_kernel (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:1025-1111). */
+int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
+                                float* inv_rms, int compute_inv_rms, float* amax_sg, void* stream);
+
+/* Fused RMSNorm + NVFP4 quantisation: tk_fused_norm_quantize (barrier-free branch) and
+ * tk_fused_norm_quantize_from_inv_rms (compute_inv_rms = 0)
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:8003-8243,8250-8259).  The reference
+ * hard-wires encode_centric = 1 on this path. */
+int fp4b200_nvfp4_fused_norm_quantize(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,
+                                      int64_t K, float* inv_rms, int compute_inv_rms, int encode_centric,
+                                      void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                      float* amax_sg, void* stream);
+
+/* Second pass of the fused producer on its own: quantise bf16(x*inv_rms*gamma) given inv_rms[M]
+ * and the device-resident tensor amax (as written by fp4b200_nvfp4_rmsnorm_stats).
+ * Replaces launch_v2_rmsnorm_kernel / quantize_transpose_nvfp4_tuned_1D_kernel<APPLY_RMSNORM>
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:1512-1582, quantize_transpose_tuned.cuh:761-779). */
+int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, const float* inv_rms,
+                                  const float* amax, int64_t M, int64_t K, int encode_centric, void* row_fp4,
+                                  void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FP4B200_H_ */

@@ -1,0 +1,66 @@
+"""ctypes binding of libfp4b200.so.  There is no fallback: if the library is missing or a
+call fails, a RuntimeError is raised."""
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libfp4b200.so")
+
+_c_void_p = ctypes.c_void_p
+_i64 = ctypes.c_int64
+_int = ctypes.c_int
+_f32 = ctypes.c_float
+
+# name -> argtypes; every function returns int (0 = ok) unless listed in _RESTYPES
+SIGNATURES = {
+    "fp4b200_last_error": [],
+    "fp4b200_abi_version": [],
+    "fp4b200_device_status": [],
+    "fp4b200_nvfp4_amax": [_c_void_p, _i64, _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_quantize": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _int, _c_void_p, _c_void_p,
+                               _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_quantize_for_gemm": [_c_void_p, _i64, _i64, _int, _int, _c_void_p, _c_void_p, _c_void_p,
+                                        _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_rmsnorm_stats": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _int, _c_void_p,
+                                    _c_void_p],
+    "fp4b200_nvfp4_fused_norm_quantize": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _int, _int,
+                                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_quantize_normed": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p,
+                                      _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+}
+_RESTYPES = {"fp4b200_last_error": ctypes.c_char_p}
+
+_lib = None
+
+
+def load() -> ctypes.CDLL:
+    """Loads the shared library (once) and declares every prototype of include/fp4b200.h."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise RuntimeError(
+            f"{LIB_PATH} is missing: build it with `python {os.path.join(HERE, 'build.py')}` "
+            "(there is no CPU or PyTorch fallback for the FP4 hot path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    for name, argtypes in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.argtypes = argtypes
+        fn.restype = _RESTYPES.get(name, _int)
+    _lib = lib
+    return lib
+
+
+def call(name: str, *args) -> None:
+    """Calls an int-returning entry point and raises RuntimeError with the library's message."""
+    lib = load()
+    rc = getattr(lib, name)(*args)
+    if rc != 0:
+        msg = lib.fp4b200_last_error()
+        raise RuntimeError(f"{name} failed: {msg.decode() if msg else rc}")
+
+
+def device_status() -> int:
+    return load().fp4b200_device_status()

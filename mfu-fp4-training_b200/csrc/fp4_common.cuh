@@ -1,0 +1,227 @@
+// Shared device helpers for the sm_100a FP4 hot-path kernels: number-format conversions,
+// mbarrier / TMA wrappers with bounded waits, and small vector utilities.
+#pragma once
+
+#include <cuda.h>
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace fp4b200 {
+
+constexpr float kFltMax = 3.4028235e+38f;
+
+// Device status words (one array per loaded library, per device).  A kernel whose bounded
+// wait runs out records a non-zero code here and returns; the host reads it with
+// fp4b200_device_status().
+enum StatusCode : int {
+  kStatusOk = 0,
+  kStatusQuantTmaTimeout = 1,
+  kStatusGemmTmaTimeout = 2,
+  kStatusGemmMmaTimeout = 3,
+  kStatusGemmEpilogueTimeout = 4,
+  kStatusGemmTmemTimeout = 5,
+};
+
+// ---------------------------------------------------------------------------------------
+// Number formats
+// ---------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float bf16lo_to_f32(uint32_t w) { return __uint_as_float(w << 16); }
+__device__ __forceinline__ float bf16hi_to_f32(uint32_t w) { return __uint_as_float(w & 0xffff0000u); }
+
+// two floats -> packed bf16x2 (round-to-nearest-even), lo in the low half
+__device__ __forceinline__ uint32_t f32x2_to_bf16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// |a| max |b| element-wise on packed bf16x2 (NaN-free inputs assumed)
+__device__ __forceinline__ uint32_t bf16x2_absmax(uint32_t acc, uint32_t v) {
+  uint32_t r;
+  asm("{.reg .b32 t; abs.bf16x2 t, %2; max.bf16x2 %0, %1, t;}" : "=r"(r) : "r"(acc), "r"(v));
+  return r;
+}
+
+__device__ __forceinline__ float bf16x2_hmax_to_f32(uint32_t absmax2) {
+  return fmaxf(bf16lo_to_f32(absmax2), bf16hi_to_f32(absmax2));
+}
+
+// fp32 -> E4M3 byte: round-to-nearest-even, saturate to +-448, subnormals kept.
+__device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
+  return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
+}
+
+__device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
+  return __half2float(__half(h));
+}
+
+// Two fp32 -> one byte of two E2M1 codes (lo in the low nibble), RN-even, saturating.
+__device__ __forceinline__ uint32_t f32x2_to_e2m1x2(float lo, float hi) {
+  uint32_t r;
+  asm("{.reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; cvt.u32.u8 %0, t;}"
+      : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// Eight fp32 (already multiplied by the block coefficient) -> 4 bytes of packed codes.
+__device__ __forceinline__ uint32_t f32x8_to_e2m1x8(float v0, float v1, float v2, float v3,
+                                                    float v4, float v5, float v6, float v7) {
+  uint32_t r;
+  asm("{.reg .b8 a, b, c, d;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 a, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 b, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 c, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 d, %8, %7;\n\t"
+      "mov.b32 %0, {a, b, c, d};}"
+      : "=r"(r)
+      : "f"(v0), "f"(v1), "f"(v2), "f"(v3), "f"(v4), "f"(v5), "f"(v6), "f"(v7));
+  return r;
+}
+
+// Stochastic rounding of four fp32 with one 32-bit random word -> 2 bytes (v0 lowest nibble).
+__device__ __forceinline__ uint32_t f32x4_to_e2m1x4_sr(float v0, float v1, float v2, float v3,
+                                                       uint32_t rbits) {
+  uint32_t r;
+  asm("{.reg .b16 t; cvt.rs.satfinite.e2m1x4.f32 t, {%4, %3, %2, %1}, %5; cvt.u32.u16 %0, t;}"
+      : "=r"(r) : "f"(v0), "f"(v1), "f"(v2), "f"(v3), "r"(rbits));
+  return r;
+}
+
+// ---------------------------------------------------------------------------------------
+// NVFP4 scale rules
+// ---------------------------------------------------------------------------------------
+
+// S_enc = min(448*6/amax, FLT_MAX); 1 when amax == 0 or the quotient underflows to 0.
+__device__ __forceinline__ float nvfp4_global_encode_scale(float amax) {
+  float s = fminf((448.0f * 6.0f) / amax, kFltMax);
+  return (amax == 0.0f || s == 0.0f) ? 1.0f : s;
+}
+
+// Per-16 block: stored decode-scale byte and the fp32 coefficient applied before the cast.
+// ENCODE_CENTRIC: m8 = e4m3(6/(b*S_enc)) (448 for b <= 1e-9), coeff = float(m8)*S_enc,
+//                 stored = e4m3(1/float(m8)).
+// decode-centric: s8 = e4m3(b/6*S_enc), coeff = min(1/(float(s8)*(1/S_enc)), FLT_MAX).
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ void nvfp4_block_scale(float b, float s_enc, uint8_t& stored, float& coeff) {
+  if constexpr (ENCODE_CENTRIC) {
+    uint8_t m8;
+    if (b <= 1.0e-9f) {
+      m8 = 0x7E;  // 448
+    } else {
+      m8 = f32_to_e4m3(fminf(6.0f / (b * s_enc), kFltMax));
+    }
+    const float mf = e4m3_to_f32(m8);
+    coeff = mf * s_enc;
+    stored = f32_to_e4m3(1.0f / mf);
+  } else {
+    stored = f32_to_e4m3(fminf(b / 6.0f * s_enc, kFltMax));
+    const float s_dec = 1.0f / s_enc;
+    coeff = fminf(1.0f / (e4m3_to_f32(stored) * s_dec), kFltMax);
+  }
+}
+
+// Byte offset of scale (row r, block kb) inside its 512-byte tile of 128 rows x 4 blocks.
+__device__ __forceinline__ int scale_tile_offset(int r_in_tile, int kb_in_tile) {
+  return (r_in_tile & 31) * 16 + (r_in_tile >> 5) * 4 + kb_in_tile;
+}
+
+// ---------------------------------------------------------------------------------------
+// mbarrier / TMA
+// ---------------------------------------------------------------------------------------
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
+               : "memory");
+}
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{.reg .pred p; mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2; selp.u32 %0, 1, 0, p;}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: gives up after ~kSpinLimit polls (each poll itself blocks for a
+// hardware-defined short time), returning false so that the caller can record a status
+// code and leave instead of spinning for ever.
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  return false;
+}
+
+__device__ __forceinline__ void fence_proxy_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+__device__ __forceinline__ void fence_mbar_init() {
+  asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+
+// 2-D tiled TMA load (no multicast): box at element coordinates (x = inner, y = outer).
+__device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, int x, int y, int z,
+                                            uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      : "memory");
+}
+
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
+}
+
+// float max via integer atomics; valid for non-negative, non-NaN values.
+__device__ __forceinline__ void atomic_max_nonneg(float* addr, float v) {
+  atomicMax(reinterpret_cast<unsigned int*>(addr), __float_as_uint(v));
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+
+// Streaming (evict-first) 8- and 16-byte stores for write-once outputs.
+__device__ __forceinline__ void st_cs_u2(void* p, uint2 v) {
+  asm volatile("st.global.cs.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_cs_u32(void* p, uint32_t v) {
+  asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ void st_cs_u4(void* p, uint4 v) {
+  asm volatile("st.global.cs.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
+
+}  // namespace fp4b200

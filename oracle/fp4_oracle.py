@@ -83,10 +83,12 @@ def e4m3_encode(x: np.ndarray) -> np.ndarray:
     a = np.abs(x).astype(np.float64)
     sign = (np.signbit(x)).astype(np.uint8) << 7
     code = np.zeros(x.shape, dtype=np.int64)
-    sub = a < 2.0 ** -6
-    q_sub = np.rint(a / 2.0 ** -9)
+    bad = ~np.isfinite(a)
+    a_f = np.where(bad, 1.0, a)
+    sub = a_f < 2.0 ** -6
+    q_sub = np.rint(np.where(sub, a_f, 0.0) / 2.0 ** -9)
     with np.errstate(divide="ignore", invalid="ignore"):
-        mant, ex = np.frexp(np.where(sub | ~np.isfinite(a), 1.0, a))  # a = mant * 2**ex, mant in [0.5,1)
+        mant, ex = np.frexp(np.where(sub, 1.0, a_f))  # a = mant * 2**ex, mant in [0.5,1)
     e = ex - 1
     q = np.rint((mant * 2.0 - 1.0) * 8.0)
     carry = q == 8

@@ -1,0 +1,132 @@
+"""GPU parity: NVFP4 producers through the reference-shaped shim (and so through the C ABI)
+against the CPU oracle on identical seeded inputs.  Codes and scale bytes must be bit-exact."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import fp4_oracle as o
+from tests.gpu_util import assert_status_ok, mod, to_dev_bf16, u8
+
+pytestmark = pytest.mark.gpu
+
+
+def _check_operands(out, ref, want_col=True):
+    assert np.array_equal(u8(out[0]), ref["row_fp4"]), "row codes differ"
+    assert np.array_equal(u8(out[1]).reshape(ref["row_sc"].shape), ref["row_sc"]), "row scales differ"
+    if want_col:
+        assert np.array_equal(u8(out[2]), ref["col_fp4"]), "column codes differ"
+        assert np.array_equal(u8(out[3]).reshape(ref["col_sc"].shape), ref["col_sc"]), "column scales differ"
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (1024, 512), (384, 4096), (2048, 4096)])
+@pytest.mark.parametrize("ec", [True, False])
+def test_quantize_for_gemm_bit_exact(shape, ec):
+    tkq = mod("tk_quant_v5")
+    x = o.make_activations(*shape, seed=shape[0] + shape[1])
+    out = tkq.tk_quantize_for_gemm(to_dev_bf16(x), True, ec)
+    torch.cuda.synchronize()
+    ref = o.nvfp4_quantize_for_gemm(x, True, ec)
+    _check_operands(out, ref)
+    assert out[4].item() == ref["sg"] and out[6][0].item() == ref["amax"]
+    assert out[0].dtype == torch.float4_e2m1fn_x2 and out[1].dtype == torch.float8_e4m3fn
+    assert tuple(out[1].shape) == (shape[0] // 128, shape[1] // 64, 512)
+    assert_status_ok()
+
+
+def test_quantize_row_only_and_golden_inputs(golden):
+    tkq = mod("tk_quant_v5")
+    x = o.bf16_from_bits(golden["mid_x_bits"])
+    out = tkq.tk_quantize_for_gemm(to_dev_bf16(x), False, False)
+    torch.cuda.synchronize()
+    assert out[2].numel() == 0 and out[3].numel() == 0
+    # decode-centric codes/scales equal the bytes the reference's CPU emulation produced
+    assert np.array_equal(u8(out[0]), golden["mid_ec_x_data"])
+    assert np.array_equal(o.unswizzle_scales(u8(out[1]), 256, 32), golden["mid_ec_x_scale"])
+    assert_status_ok()
+
+
+def test_edge_values_zero_blocks_and_negative_zero():
+    tkq = mod("tk_quant_v5")
+    x = o.make_activations(256, 256, seed=5)
+    x[:16, :32] = 0.0            # all-zero blocks in both orientations
+    x[40, 64:80] = -0.0          # negative zeros keep their sign bit in the code
+    x[100:116, 200] = 1e-30      # tiny block amax
+    x[200, 0] = 3.0e38           # huge outlier -> S_enc tiny
+    x = o.bf16_round(x)
+    for ec in (True, False):
+        out = tkq.tk_quantize_for_gemm(to_dev_bf16(x), True, ec)
+        torch.cuda.synchronize()
+        _check_operands(out, o.nvfp4_quantize_for_gemm(x, True, ec))
+    z = np.zeros((128, 128), dtype=np.float32)
+    out = tkq.tk_quantize_for_gemm(to_dev_bf16(z), True, True)
+    torch.cuda.synchronize()
+    _check_operands(out, o.nvfp4_quantize_for_gemm(z, True, True))
+    assert out[4].item() == 0.0
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 640), (512, 2048), (1024, 4096), (256, 8192)])
+def test_fused_norm_quantize(shape):
+    tkq = mod("tk_quant_v5")
+    M, K = shape
+    x = o.make_activations(M, K, seed=M * 3 + K)
+    g = o.make_gamma(K, seed=K)
+    out = tkq.tk_fused_norm_quantize(to_dev_bf16(x), to_dev_bf16(g), 1e-5, False, True)
+    torch.cuda.synchronize()
+    inv_gpu = out[5].cpu().numpy()
+    inv_ref = o.rmsnorm_inv_rms(x, 1e-5)
+    # rsqrtf is a hardware approximation: tolerance 2e-6 relative, as in the reference's own test
+    assert np.abs(inv_gpu / inv_ref - 1).max() < 2e-6
+    # bit-exact given the GPU's inverse RMS
+    ref = o.nvfp4_fused_norm_quantize(x, g, 1e-5, inv_rms=inv_gpu)
+    _check_operands(out, ref)
+    # properties the reference's GPU test pins: amax identity and sg == amax/2688
+    assert out[6].item() == ref["amax"]
+    assert out[4].item() == np.float32(ref["amax"] / np.float32(2688.0))
+    assert_status_ok()
+
+
+def test_fused_norm_from_inv_rms_bit_exact_vs_pure_oracle():
+    """With a shared inverse RMS the whole producer is reproducible on the CPU."""
+    tkq = mod("tk_quant_v5")
+    M, K = 512, 1024
+    x = o.make_activations(M, K, seed=77)
+    g = o.make_gamma(K, seed=78)
+    inv = o.rmsnorm_inv_rms(x, 1e-5)
+    out = tkq.tk_fused_norm_quantize_from_inv_rms(to_dev_bf16(x), to_dev_bf16(g),
+                                                  torch.from_numpy(inv).cuda(), False, True)
+    torch.cuda.synchronize()
+    _check_operands(out, o.nvfp4_fused_norm_quantize(x, g, 1e-5, inv_rms=inv))
+    assert out[5].data_ptr() != 0 and np.array_equal(out[5].cpu().numpy(), inv)
+    assert_status_ok()
+
+
+def test_full_size_properties_config2():
+    """Benchmark-size case (16384 x 4096): size-independent properties instead of a full oracle run —
+    determinism, a sampled-row oracle check, column codes equal to the row codes of the
+    transposed input."""
+    tkq = mod("tk_quant_v5")
+    M, K = 16384, 4096
+    gen = torch.Generator().manual_seed(2)
+    x = torch.randn(M, K, generator=gen).to(torch.bfloat16)
+    x[:, torch.randperm(K, generator=gen)[:4]] *= 20
+    g = (1 + 0.1 * torch.randn(K, generator=gen)).to(torch.bfloat16)
+    xd, gd = x.cuda(), g.cuda()
+    a = tkq.tk_fused_norm_quantize(xd, gd, 1e-5, False, True)
+    b = tkq.tk_fused_norm_quantize(xd, gd, 1e-5, False, True)
+    torch.cuda.synchronize()
+    for i in range(4):
+        assert torch.equal(a[i].view(torch.uint8), b[i].view(torch.uint8))
+    inv = a[5].cpu().numpy()
+    xf = x.float().numpy()
+    n = o.rmsnorm_apply(xf, inv, g.float().numpy())
+    assert a[6].item() == np.abs(n).max()
+    rows = np.arange(0, M, 128 * 17)[:6]
+    for r0 in rows:
+        blk = n[r0:r0 + 128]
+        codes, sc = o.nvfp4_quantize_1d(blk, a[6].item(), "encode")
+        assert np.array_equal(u8(a[0][r0:r0 + 128]), codes)
+        assert np.array_equal(u8(a[1][r0 // 128]).reshape(-1), o.swizzle_scales(sc).reshape(-1))
+        ccodes, csc = o.nvfp4_quantize_1d(np.ascontiguousarray(blk.T), a[6].item(), "encode")
+        assert np.array_equal(u8(a[2][:, r0 // 2:(r0 + 128) // 2]), ccodes)
+    assert_status_ok()

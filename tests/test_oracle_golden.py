@@ -1,0 +1,131 @@
+"""CPU: the oracle against the golden vectors produced by the reference's own CPU emulation
+(tests/golden/make_golden.py), plus internal consistency of the oracle."""
+import numpy as np
+import pytest
+
+from oracle import fp4_oracle as o
+
+
+def test_e4m3_cast_matches_reference_sweep(golden):
+    assert np.array_equal(o.e4m3_encode(golden["e4m3_sweep_in"]), golden["e4m3_sweep_out"])
+
+
+def test_e4m3_saturates_and_roundtrips():
+    assert o.e4m3_encode(np.array([1e9, 449.0, 464.0, 480.0, np.inf], dtype=np.float32)).tolist() == [0x7E] * 5
+    codes = np.arange(0, 0x7F, dtype=np.uint8)
+    assert np.array_equal(o.e4m3_encode(o.e4m3_decode(codes)), codes)
+    # ties to even between 2^-9 multiples (subnormals)
+    assert o.e4m3_encode(np.array([1.5 * 2.0 ** -9, 2.5 * 2.0 ** -9, 2.0 ** -10], dtype=np.float32)).tolist() == [2, 2, 0]
+
+
+def test_e2m1_rules_match_reference(golden):
+    p = golden["e2m1_probe_in"]
+    assert np.array_equal(o.pack_fp4(o.e2m1_encode_rn(np.clip(p, -6, 6))), golden["e2m1_probe_packed"])
+    lut = o.E2M1_TO_F32[o.unpack_fp4(np.arange(256, dtype=np.uint8).reshape(1, -1))]
+    assert np.array_equal(lut, golden["e2m1_lut"])
+    assert np.array_equal(o.rht_fixed_signs(), golden["wgrad_sign_vector"])
+    # hardware keeps the sign of zero
+    assert o.e2m1_encode_rn(np.array([-0.0, -0.1], dtype=np.float32)).tolist() == [8, 8]
+
+
+@pytest.mark.parametrize("tag", ["small", "mid"])
+@pytest.mark.parametrize("pre,mode", [("dc", "decode_te"), ("ec", "decode")])
+def test_quantize_1d_bit_exact_vs_reference(golden, tag, pre, mode):
+    """The emulation's default branch is the folded-reciprocal decode rule ("decode_te"); its
+    encode_centric branch evaluates the true-division decode rule of the CUDA kernels ("decode")."""
+    x = o.bf16_from_bits(golden[f"{tag}_x_bits"])
+    w = o.bf16_from_bits(golden[f"{tag}_w_bits"])
+    amax = o.tensor_amax(x)
+    assert amax == golden[f"{tag}_{pre}_x_amax"][0]
+    d, s = o.nvfp4_quantize_1d(x, amax, mode)
+    assert np.array_equal(d, golden[f"{tag}_{pre}_x_data"]) and np.array_equal(s, golden[f"{tag}_{pre}_x_scale"])
+    d, s = o.nvfp4_quantize_1d(np.ascontiguousarray(x.T), amax, mode)
+    assert np.array_equal(d, golden[f"{tag}_{pre}_x_data_t"]) and np.array_equal(s, golden[f"{tag}_{pre}_x_scale_t"])
+    d, s = o.nvfp4_quantize_1d(w, o.tensor_amax(w), mode)
+    assert np.array_equal(d, golden[f"{tag}_{pre}_w_data"]) and np.array_equal(s, golden[f"{tag}_{pre}_w_scale"])
+
+
+@pytest.mark.parametrize("tag", ["small", "mid"])
+def test_qgemm_and_dequantize_vs_reference(golden, tag):
+    x = o.bf16_from_bits(golden[f"{tag}_x_bits"])
+    w = o.bf16_from_bits(golden[f"{tag}_w_bits"])
+    ax, aw = o.tensor_amax(x), o.tensor_amax(w)
+    xd, xs = o.nvfp4_quantize_1d(x, ax, "decode_te")
+    wd, ws = o.nvfp4_quantize_1d(w, aw, "decode_te")
+    y = o.nvfp4_gemm_fp32(xd, xs, o.nvfp4_global_decode_scale(ax), wd, ws, o.nvfp4_global_decode_scale(aw))
+    ref = golden[f"{tag}_dc_qgemm_f32"]
+    assert np.linalg.norm(y - ref) / np.linalg.norm(ref) < 1e-6
+    deq = o.nvfp4_dequantize(xd, xs, o.nvfp4_global_decode_scale(ax))
+    assert np.abs(deq - golden[f"{tag}_dc_x_deq"]).max() <= 2e-7 * np.abs(deq).max()
+
+
+@pytest.mark.parametrize("tag", ["small", "mid"])
+def test_2d_weight_codes_transpose_consistent(golden, tag):
+    """16x16 weight tiles: one code set valid in both orientations; scales match the
+    emulation except where its folded-reciprocal rule and the kernels' true division differ."""
+    w = o.bf16_from_bits(golden[f"{tag}_w_bits"])
+    r, rs, c, cs = o.nvfp4_quantize_2d(w, o.tensor_amax(w))
+    assert np.array_equal(o.unpack_fp4(c), o.unpack_fp4(r).T)
+    same = (rs == golden[f"{tag}_2d_w_scale"]).mean()
+    assert same > 0.98
+    blocks_equal = np.repeat(rs == golden[f"{tag}_2d_w_scale"], 8, axis=1)
+    assert np.array_equal(r[blocks_equal], golden[f"{tag}_2d_w_data"][blocks_equal])
+
+
+def test_swizzle_roundtrip_and_formula():
+    rng = np.random.default_rng(0)
+    S = rng.integers(0, 255, size=(256, 24), dtype=np.uint8)
+    T = o.swizzle_scales(S)
+    assert T.shape == (2, 6, 512)
+    assert np.array_equal(o.unswizzle_scales(T, 256, 24), S)
+    flat = T.reshape(-1)
+    for r, kb in [(0, 0), (5, 3), (37, 9), (130, 23), (255, 0)]:
+        off = ((r // 128) * 6 + kb // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + (kb % 4)
+        assert flat[off] == S[r, kb]
+
+
+def test_encode_centric_edge_cases():
+    # zero block: multiplier 448, stored byte e4m3(1/448) (a subnormal), never 0
+    st, co = o.nvfp4_block_scale(np.array([0.0, 1e-10], dtype=np.float32), np.float32(100.0), "encode")
+    assert st.tolist() == [o.e4m3_encode(np.float32(1 / 448.0)).item()] * 2 and (co == np.float32(44800.0)).all()
+    # decode-centric underflow: stored 0, coefficient FLT_MAX
+    st, co = o.nvfp4_block_scale(np.array([1e-6], dtype=np.float32), np.float32(1.0), "decode")
+    assert st[0] == 0 and co[0] == o.FLT_MAX
+    assert o.nvfp4_global_encode_scale(0.0) == 1.0
+    assert o.nvfp4_global_decode_scale(2688.0) == 1.0
+
+
+def test_rmsnorm_tree_close_to_float64_and_amax_identity():
+    x = o.make_activations(256, 1024, seed=3)
+    g = o.make_gamma(1024, seed=4)
+    inv = o.rmsnorm_inv_rms(x, 1e-5)
+    ref = 1.0 / np.sqrt((x.astype(np.float64) ** 2).mean(axis=1) + 1e-5)
+    assert np.abs(inv / ref - 1).max() < 5e-7
+    out = o.nvfp4_fused_norm_quantize(x, g, 1e-5)
+    n = o.bf16_round((x * inv[:, None]).astype(np.float32) * g[None, :])
+    assert out["amax"] == np.abs(n).max()           # property pinned by the reference's GPU test
+    assert out["sg"] == np.float32(out["amax"] / np.float32(2688.0))
+
+
+def test_mx_e8m0_modes():
+    b = np.array([1.0, 1.5, 1.25, 1.75, 3.0, 0.0, 1e-39], dtype=np.float32)
+    assert o.mx_e8m0(b, 1).tolist() == [127, 128, 128, 128, 129, 0, 0]
+    assert o.mx_e8m0(b, 2).tolist() == [127, 127, 127, 127, 128, 0, 0]
+    assert o.mx_e8m0(b, 0).tolist() == [127, 128, 127, 128, 128, 0, 0]
+
+
+def test_mxfp4_roundtrip_error_small():
+    x = o.make_activations(128, 256, seed=7, outlier_frac=0)
+    q = o.mxfp4_quantize_row_and_col(x, 1)
+    deq = o.mxfp4_dequantize(q["row_fp4"], q["row_sc_logical"])
+    rel = np.linalg.norm(deq - x) / np.linalg.norm(x)
+    assert rel < 0.2
+    deq_t = o.mxfp4_dequantize(q["col_fp4"], q["col_sc_logical"])
+    assert np.linalg.norm(deq_t - x.T) / np.linalg.norm(x) < 0.2
+
+
+def test_fwht16_is_orthonormal_involution():
+    x = o.make_activations(16, 64, seed=11, outlier_frac=0)
+    y = o.fwht16_bf16(x)
+    z = o.fwht16_bf16(y)
+    assert np.abs(z - x).max() < 0.05
