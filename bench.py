@@ -172,6 +172,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--quick", action="store_true",
+                    help="timed loop only (no per-kernel, end-to-end or CPU legs): the command ncu captures")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
 
@@ -234,6 +236,14 @@ def main():
     value = alg * world / (ms_per_step * 1e-3) / 1e9
     if lib.device_status() != 0:
         raise RuntimeError("device status word is non-zero: a kernel gave up a bounded wait")
+
+    if args.quick:
+        if rank == 0:
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                              "warmup": args.warmup, "ms_per_step": ms_per_step, "quick": True}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
 
     # ---- per-kernel timing through the C ABI (pass 1: statistics, pass 2: quantise) -------
     dev = torch.device("cuda", local_rank)

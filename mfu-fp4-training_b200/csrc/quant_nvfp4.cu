@@ -62,81 +62,132 @@ __global__ void finalize_sg_kernel(float* __restrict__ amax_sg) { amax_sg[1] = a
 // virtual lanes 4L+128i+q (i = 0,1; q = 0..3) in acc[i][q], so the butterfly levels map to
 // shuffles over lane masks 4,2,1, register adds over q, a register add over i, and
 // shuffles over lane masks 16,8.
+constexpr int kStatsThreads = 128;
+
+// {a.x*b.x + c.x, a.y*b.y + c.y}, each a fused multiply-add (same rounding as fmaf)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{.reg .b64 x, y, z, w; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mov.b64 z, {%6, %7};"
+      " fma.rn.f32x2 w, x, y, z; mov.b64 {%0, %1}, w;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+__device__ __forceinline__ float2 mul2s(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mul.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ uint32_t absmax_xs_s(uint32_t acc, uint32_t v) {
+  uint32_t r;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(v));
+  return r;
+}
+
+template <int NV>
+__device__ __forceinline__ void stats_load_row(uint4 (&v)[NV], const __nv_bfloat16* x, int row, int K, int lane) {
+  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
+  const int nvec_row = K >> 3;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int q = lane + 32 * j;
+    v[j] = (q < nvec_row) ? __ldg(xr + q) : make_uint4(0, 0, 0, 0);
+  }
+}
+
+// One row held in registers: inverse RMS (reference summation tree) and |bf16(x*inv*gamma)| max.
+template <int NV, bool COMPUTE_INV_RMS>
+__device__ __forceinline__ uint32_t stats_process_row(const uint4 (&v)[NV], const float2* gamma_s, float* inv_rms,
+                                                      int row, int K, float eps, int lane, uint32_t mx) {
+  float inv;
+  if constexpr (COMPUTE_INV_RMS) {
+    // acc[i][q]: virtual lane 4*lane + 128*i + q; packed as pairs (q, q+1)
+    float2 acc[2][2] = {{{0, 0}, {0, 0}}, {{0, 0}, {0, 0}}};
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int i = j & 1;
+      const float2 lo01 = make_float2(bf16lo_to_f32(v[j].x), bf16lo_to_f32(v[j].y));
+      const float2 hi01 = make_float2(bf16hi_to_f32(v[j].x), bf16hi_to_f32(v[j].y));
+      const float2 lo23 = make_float2(bf16lo_to_f32(v[j].z), bf16lo_to_f32(v[j].w));
+      const float2 hi23 = make_float2(bf16hi_to_f32(v[j].z), bf16hi_to_f32(v[j].w));
+      acc[i][0] = fma2(lo01, lo01, acc[i][0]);
+      acc[i][0] = fma2(hi01, hi01, acc[i][0]);
+      acc[i][1] = fma2(lo23, lo23, acc[i][1]);
+      acc[i][1] = fma2(hi23, hi23, acc[i][1]);
+    }
+    float part[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      float a4[4] = {acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 4);
+        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 2);
+        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 1);
+      }
+      const float a = a4[0] + a4[2];
+      const float b = a4[1] + a4[3];
+      part[i] = a + b;
+    }
+    float s = part[0] + part[1];
+    s += __shfl_xor_sync(0xffffffffu, s, 16);
+    s += __shfl_xor_sync(0xffffffffu, s, 8);
+    inv = rsqrtf(s / static_cast<float>(K) + eps);
+    if (lane == 0) inv_rms[row] = inv;
+  } else {
+    inv = __ldg(inv_rms + row);
+  }
+  const float2 inv2 = make_float2(inv, inv);
+  const int nvec_row = K >> 3;
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const int q = lane + 32 * j;
+    if (q < nvec_row) {
+      const float4 g01 = *reinterpret_cast<const float4*>(gamma_s + 4 * q);
+      const float4 g23 = *reinterpret_cast<const float4*>(gamma_s + 4 * q + 2);
+      float2 t0 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2), make_float2(g01.x, g01.y));
+      float2 t1 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2), make_float2(g01.z, g01.w));
+      float2 t2 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2), make_float2(g23.x, g23.y));
+      float2 t3 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2), make_float2(g23.z, g23.w));
+      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t0.x, t0.y));
+      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t1.x, t1.y));
+      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t2.x, t2.y));
+      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t3.x, t3.y));
+    }
+  }
+  return mx;
+}
+
+// One warp per row, two rows in flight per warp (the next row's loads are issued before the
+// current row is reduced), so that every warp always has a row of HBM traffic outstanding.
 template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kStatsThreads, 2)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                      float* __restrict__ inv_rms, float* __restrict__ amax, float eps, int M, int K) {
-  const int lane = threadIdx.x & 31;
-  const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int n_warps = gridDim.x * (blockDim.x >> 5);
-  const int nvec_row = K >> 3;  // 16-byte vectors per row
-  float run_max = 0.0f;
-
-  for (int row = warp_global; row < M; row += n_warps) {
-    const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
-    uint4 v[NV];
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int q = lane + 32 * j;
-      v[j] = (q < nvec_row) ? __ldg(xr + q) : make_uint4(0, 0, 0, 0);
-    }
-    float inv;
-    if constexpr (COMPUTE_INV_RMS) {
-      float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
-#pragma unroll
-      for (int j = 0; j < NV; ++j) {
-        const int i = j & 1;  // vector index within a 512-column block = lane + 32*i
-        const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float lo = bf16lo_to_f32(w[q]), hi = bf16hi_to_f32(w[q]);
-          acc[i][q] = fmaf(lo, lo, acc[i][q]);
-          acc[i][q] = fmaf(hi, hi, acc[i][q]);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          acc[i][q] += __shfl_xor_sync(0xffffffffu, acc[i][q], 4);
-          acc[i][q] += __shfl_xor_sync(0xffffffffu, acc[i][q], 2);
-          acc[i][q] += __shfl_xor_sync(0xffffffffu, acc[i][q], 1);
-        }
-      }
-      float part[2];
-#pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        const float a = acc[i][0] + acc[i][2];
-        const float b = acc[i][1] + acc[i][3];
-        part[i] = a + b;
-      }
-      float s = part[0] + part[1];
-      s += __shfl_xor_sync(0xffffffffu, s, 16);
-      s += __shfl_xor_sync(0xffffffffu, s, 8);
-      inv = rsqrtf(s / static_cast<float>(K) + eps);
-      if (lane == 0) inv_rms[row] = inv;
-    } else {
-      inv = __ldg(inv_rms + row);
-    }
-
-    uint32_t mx = 0;
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int q = lane + 32 * j;
-      if (q < nvec_row) {
-        const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
-        const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
-        const uint32_t gw[4] = {g.x, g.y, g.z, g.w};
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float lo = bf16lo_to_f32(w[e]) * inv * bf16lo_to_f32(gw[e]);
-          const float hi = bf16hi_to_f32(w[e]) * inv * bf16hi_to_f32(gw[e]);
-          mx = bf16x2_absmax(mx, f32x2_to_bf16x2(lo, hi));
-        }
-      }
-    }
-    run_max = fmaxf(run_max, bf16x2_hmax_to_f32(mx));
+  extern __shared__ float2 gamma_f2[];   // gamma as fp32 pairs, one copy per CTA
+  for (int q = threadIdx.x; q < (K >> 1); q += kStatsThreads) {
+    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(gamma) + q);
+    gamma_f2[q] = make_float2(bf16lo_to_f32(w), bf16hi_to_f32(w));
   }
+  __syncthreads();
+  const int lane = threadIdx.x & 31;
+  const int warp_global = blockIdx.x * (kStatsThreads >> 5) + (threadIdx.x >> 5);
+  const int n_warps = gridDim.x * (kStatsThreads >> 5);
+  uint32_t mx = 0;
+  uint4 va[NV], vb[NV];
+  int row = warp_global;
+  if (row < M) stats_load_row<NV>(va, x, row, K, lane);
+  while (row < M) {
+    const int row_b = row + n_warps;
+    if (row_b < M) stats_load_row<NV>(vb, x, row_b, K, lane);
+    mx = stats_process_row<NV, COMPUTE_INV_RMS>(va, gamma_f2, inv_rms, row, K, eps, lane, mx);
+    if (row_b >= M) break;
+    const int row_c = row_b + n_warps;
+    if (row_c < M) stats_load_row<NV>(va, x, row_c, K, lane);
+    mx = stats_process_row<NV, COMPUTE_INV_RMS>(vb, gamma_f2, inv_rms, row_b, K, eps, lane, mx);
+    row = row_c;
+  }
+  float run_max = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
   run_max = warp_max(run_max);
   if (lane == 0 && run_max > 0.0f) atomic_max_nonneg(amax, run_max);
 }
@@ -213,20 +264,39 @@ rmsnorm_stats_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
 // ---------------------------------------------------------------------------------------
 // Row + column quantiser
 // ---------------------------------------------------------------------------------------
+//
+// Persistent CTAs (2 per SM, 256 threads) walk 128x128 chunks.  A chunk arrives as two TMA
+// boxes of 128 rows x 64 columns in the 128-byte-swizzled layout, three chunks deep.
+//   row pass   : lane = (row & 7, 32-column unit); four conflict-free 16-byte reads, optional
+//                RMSNorm (normalised bf16 written back for the column pass), two 16-blocks
+//                quantised, one 16-byte streaming store of codes per thread.
+//   column pass: warp = 16-row group, lane = column pair; sixteen conflict-free 4-byte reads,
+//                two blocks quantised, codes staged so that the write-out is 16-byte stores.
+// The decode of a block's E4M3 multiplier into (coefficient, stored byte) is a 128-entry table
+// built per CTA from S_enc, so a block costs one IEEE division and one cast.
+// The instruction stream, not HBM, is what bounds this kernel (about 12 instructions per
+// element are needed for two orientations), hence the packed mul.f32x2 and xorsign.abs forms.
 
 constexpr int kChunk = 128;            // chunk edge in elements
 constexpr int kQThreads = 256;
 constexpr int kQStages = 3;
-constexpr int kTileBytes = kChunk * kChunk * 2;  // 32 KiB of bf16
-constexpr int kColPitch = 72;          // bytes per column of staged column codes (64 + pad)
+constexpr int kHalfBytes = kChunk * 128;         // one 128-row x 64-column swizzled box
+constexpr int kTileBytes = 2 * kHalfBytes;       // 32 KiB of bf16
+
+struct ScaleLut {
+  float coeff;
+  uint32_t stored;
+};
 
 struct QuantSmem {
-  alignas(128) uint8_t in[kQStages][kTileBytes];
-  alignas(16) uint8_t col_codes[kChunk * kColPitch];
+  alignas(1024) uint8_t in[kQStages][kTileBytes];
+  alignas(16) uint2 col_codes[8][kChunk];   // [16-row group][column] -> 8 bytes of codes
   alignas(16) uint8_t row_sc[2][1024];
   alignas(16) uint8_t col_sc[1024];
   alignas(16) float inv_rms[2][kChunk];
   alignas(16) float gamma[2][kChunk];
+  alignas(8) ScaleLut lut_row[128];
+  alignas(8) ScaleLut lut_col[128];
   alignas(8) uint64_t full[kQStages];
 };
 
@@ -246,11 +316,60 @@ struct QuantArgs {
   int reverse;             // walk chunks from the last row block to the first
 };
 
+// {a.x*b.x, a.y*b.y} in one packed instruction (round-to-nearest, denormals kept)
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mul.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// running |.|-max on packed bf16x2; the sign of the result is meaningless
+__device__ __forceinline__ uint32_t absmax_xs(uint32_t acc, uint32_t v) {
+  uint32_t r;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(v));
+  return r;
+}
+
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ ScaleLut lut_entry(int code, float s_enc) {
+  ScaleLut e;
+  const float f = e4m3_to_f32((uint8_t)code);
+  if constexpr (ENCODE_CENTRIC) {
+    e.coeff = f * s_enc;
+    e.stored = f32_to_e4m3(1.0f / f);
+  } else {
+    const float s_dec = 1.0f / s_enc;
+    e.coeff = fminf(1.0f / (f * s_dec), kFltMax);
+    e.stored = (uint32_t)code;
+  }
+  return e;
+}
+
+// E4M3 code of the block's multiplier (encode-centric) or decode scale (decode-centric)
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ uint32_t block_code(float b, float s_enc) {
+  if constexpr (ENCODE_CENTRIC) {
+    return (b <= 1.0e-9f) ? 0x7Eu : (uint32_t)f32_to_e4m3(fminf(6.0f / (b * s_enc), kFltMax));
+  } else {
+    return (uint32_t)f32_to_e4m3(fminf(b / 6.0f * s_enc, kFltMax));
+  }
+}
+
+__device__ __forceinline__ uint32_t quant8(const uint32_t* w, float coeff) {
+  const float2 cc = make_float2(coeff, coeff);
+  const float2 a = mul2(make_float2(bf16lo_to_f32(w[0]), bf16hi_to_f32(w[0])), cc);
+  const float2 b = mul2(make_float2(bf16lo_to_f32(w[1]), bf16hi_to_f32(w[1])), cc);
+  const float2 c = mul2(make_float2(bf16lo_to_f32(w[2]), bf16hi_to_f32(w[2])), cc);
+  const float2 d = mul2(make_float2(bf16lo_to_f32(w[3]), bf16hi_to_f32(w[3])), cc);
+  return f32x8_to_e2m1x8(a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y);
+}
+
 template <bool ENCODE_CENTRIC, bool NORM>
 __global__ void __launch_bounds__(kQThreads, 2)
 nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArgs a) {
   extern __shared__ uint8_t smem_raw[];
-  QuantSmem& sm = *reinterpret_cast<QuantSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 127) & ~uintptr_t(127));
+  QuantSmem& sm = *reinterpret_cast<QuantSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -265,6 +384,13 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     cm = c / a.chunks_k;
     ck = c - cm * a.chunks_k;
   };
+  auto issue_load = [&](int it, int s) {
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    mbar_expect_tx(&sm.full[s], kTileBytes);
+    tma_load_2d(sm.in[s], &tmap_x, ck * kChunk, cm * kChunk, &sm.full[s]);
+    tma_load_2d(sm.in[s] + kHalfBytes, &tmap_x, ck * kChunk + 64, cm * kChunk, &sm.full[s]);
+  };
 
   if (tid == 0) {
     tma_prefetch_desc(&tmap_x);
@@ -274,17 +400,36 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
   }
   __syncthreads();
   if (tid == 0) {
-    for (int s = 0; s < kQStages && s < my_count; ++s) {
-      int cm, ck;
-      chunk_coords(s, cm, ck);
-      mbar_expect_tx(&sm.full[s], kTileBytes);
-      tma_load_2d(sm.in[s], &tmap_x, ck * kChunk, cm * kChunk, &sm.full[s]);
-    }
+    for (int s = 0; s < kQStages && s < my_count; ++s) issue_load(s, s);
   }
 
   const float s_enc_row = nvfp4_global_encode_scale(*a.amax_row);
   const float s_enc_col = nvfp4_global_encode_scale(*a.amax_col);
   const bool want_col = a.col_fp4 != nullptr;
+  if (tid < 128) sm.lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
+  else sm.lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
+  if constexpr (NORM) {
+    if (my_count > 0) {
+      int cm, ck;
+      chunk_coords(0, cm, ck);
+      if (tid < kChunk) sm.inv_rms[0][tid] = __ldg(a.inv_rms + cm * kChunk + tid);
+      else sm.gamma[0][tid - kChunk] = __bfloat162float(a.gamma[ck * kChunk + tid - kChunk]);
+    }
+  }
+  __syncthreads();
+
+  // row-pass geometry of this thread (loop invariant)
+  const int unit = lane >> 3;                    // which 32 columns of the chunk
+  const int r_lo = lane & 7;
+  const int half_off = (unit >> 1) * kHalfBytes;
+  const int cb = (unit & 1) * 4;                 // first 16-byte column group inside the half
+  int row_off[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) row_off[j] = ((cb + j) ^ r_lo) << 4;
+  // column-pass geometry
+  int col_off[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) col_off[j] = (((lane >> 2) ^ j) << 4) + (lane & 3) * 4;
 
   for (int it = 0; it < my_count; ++it) {
     const int s = it % kQStages;
@@ -294,109 +439,110 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     const int m0 = cm * kChunk, k0 = ck * kChunk;
     const int pp = it & 1;
 
+    // prefetch the next chunk's inv_rms / gamma into a register (stored after the column pass)
+    float pre = 0.0f;
     if constexpr (NORM) {
-      // stage this chunk's 128 inv_rms values and 128 gammas (as fp32)
-      if (tid < kChunk) sm.inv_rms[pp][tid] = __ldg(a.inv_rms + m0 + tid);
-      else sm.gamma[pp][tid - kChunk] = __bfloat162float(a.gamma[k0 + tid - kChunk]);
-      __syncthreads();
+      if (it + 1 < my_count) {
+        int ncm, nck;
+        chunk_coords(it + 1, ncm, nck);
+        pre = (tid < kChunk) ? __ldg(a.inv_rms + ncm * kChunk + tid)
+                             : __bfloat162float(a.gamma[nck * kChunk + tid - kChunk]);
+      }
     }
 
     if (!mbar_wait_bounded(&sm.full[s], parity)) {
       if (tid == 0) atomicExch(a.status, kStatusQuantTmaTimeout);
       return;
     }
-
     uint8_t* tile = sm.in[s];
 
-    // ---- row pass: each thread owns 16 contiguous elements of one row, 4 times -------
+    // ---- row pass ---------------------------------------------------------------------
 #pragma unroll
-    for (int rep = 0; rep < 4; ++rep) {
-      const int b = rep * kQThreads + tid;
-      const int r = b >> 3, kb = b & 7;
-      uint4* p = reinterpret_cast<uint4*>(tile + r * (kChunk * 2) + kb * 32);
-      uint4 v0 = p[0], v1 = p[1];
-      uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+    for (int rep = 0; rep < 2; ++rep) {
+      const int r = warp * 16 + rep * 8 + r_lo;
+      uint8_t* rowp = tile + half_off + r * 128;
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(rowp + row_off[j]);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
       if constexpr (NORM) {
         const float inv = sm.inv_rms[pp][r];
-        const float4* g4 = reinterpret_cast<const float4*>(&sm.gamma[pp][kb * 16]);
+        const float2 inv2 = make_float2(inv, inv);
+        const float2* g2 = reinterpret_cast<const float2*>(&sm.gamma[pp][unit * 32]);
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const float4 g = g4[q];
-          w[2 * q] = f32x2_to_bf16x2(bf16lo_to_f32(w[2 * q]) * inv * g.x, bf16hi_to_f32(w[2 * q]) * inv * g.y);
-          w[2 * q + 1] =
-              f32x2_to_bf16x2(bf16lo_to_f32(w[2 * q + 1]) * inv * g.z, bf16hi_to_f32(w[2 * q + 1]) * inv * g.w);
+        for (int q = 0; q < 16; ++q) {
+          float2 t = mul2(make_float2(bf16lo_to_f32(w[q]), bf16hi_to_f32(w[q])), inv2);
+          t = mul2(t, g2[q]);
+          w[q] = f32x2_to_bf16x2(t.x, t.y);
         }
-        if (want_col) {  // the column pass reads the normalised values
-          p[0] = make_uint4(w[0], w[1], w[2], w[3]);
-          p[1] = make_uint4(w[4], w[5], w[6], w[7]);
+        if (want_col) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(rowp + row_off[j]) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         }
       }
-      uint32_t mx = 0;
+      uint32_t mx0 = 0, mx1 = 0;
 #pragma unroll
-      for (int q = 0; q < 8; ++q) mx = bf16x2_absmax(mx, w[q]);
-      const float bmax = bf16x2_hmax_to_f32(mx);
-      uint8_t stored;
-      float coeff;
-      nvfp4_block_scale<ENCODE_CENTRIC>(bmax, s_enc_row, stored, coeff);
-      uint2 codes;
-      codes.x = f32x8_to_e2m1x8(bf16lo_to_f32(w[0]) * coeff, bf16hi_to_f32(w[0]) * coeff,
-                                bf16lo_to_f32(w[1]) * coeff, bf16hi_to_f32(w[1]) * coeff,
-                                bf16lo_to_f32(w[2]) * coeff, bf16hi_to_f32(w[2]) * coeff,
-                                bf16lo_to_f32(w[3]) * coeff, bf16hi_to_f32(w[3]) * coeff);
-      codes.y = f32x8_to_e2m1x8(bf16lo_to_f32(w[4]) * coeff, bf16hi_to_f32(w[4]) * coeff,
-                                bf16lo_to_f32(w[5]) * coeff, bf16hi_to_f32(w[5]) * coeff,
-                                bf16lo_to_f32(w[6]) * coeff, bf16hi_to_f32(w[6]) * coeff,
-                                bf16lo_to_f32(w[7]) * coeff, bf16hi_to_f32(w[7]) * coeff);
-      st_cs_u2(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + kb * 16) >> 1), codes);
-      sm.row_sc[pp][(kb >> 2) * 512 + scale_tile_offset(r, kb & 3)] = stored;
+      for (int q = 0; q < 8; ++q) { mx0 = absmax_xs(mx0, w[q]); mx1 = absmax_xs(mx1, w[8 + q]); }
+      const float b0 = fmaxf(fabsf(bf16lo_to_f32(mx0)), fabsf(bf16hi_to_f32(mx0)));
+      const float b1 = fmaxf(fabsf(bf16lo_to_f32(mx1)), fabsf(bf16hi_to_f32(mx1)));
+      const ScaleLut e0 = sm.lut_row[block_code<ENCODE_CENTRIC>(b0, s_enc_row)];
+      const ScaleLut e1 = sm.lut_row[block_code<ENCODE_CENTRIC>(b1, s_enc_row)];
+      uint4 codes;
+      codes.x = quant8(w, e0.coeff);
+      codes.y = quant8(w + 4, e0.coeff);
+      codes.z = quant8(w + 8, e1.coeff);
+      codes.w = quant8(w + 12, e1.coeff);
+      st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1), codes);
+      // blocks kb = 2*unit, 2*unit+1 of tile kb>>2 = unit>>1: two adjacent bytes
+      *reinterpret_cast<uint16_t*>(&sm.row_sc[pp][(unit >> 1) * 512 + scale_tile_offset(r, (unit & 1) * 2)]) =
+          (uint16_t)(e0.stored | (e1.stored << 8));
     }
     __syncthreads();
 
-    // ---- column pass: warp w owns rows 16w..16w+15, lane owns two adjacent columns ---
+    // ---- column pass ------------------------------------------------------------------
     if (want_col) {
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        const int c = 2 * lane + 64 * h;  // first of the two columns
+        const uint8_t* base = tile + h * kHalfBytes + (warp * 16) * 128;
         uint32_t w[16];
         uint32_t mx = 0;
-        const uint32_t* col = reinterpret_cast<const uint32_t*>(tile + (warp * 16) * (kChunk * 2) + c * 2);
 #pragma unroll
         for (int i = 0; i < 16; ++i) {
-          w[i] = col[i * (kChunk / 2)];
-          mx = bf16x2_absmax(mx, w[i]);
+          w[i] = *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]);
+          mx = absmax_xs(mx, w[i]);
         }
-        uint8_t st0, st1;
-        float c0, c1;
-        nvfp4_block_scale<ENCODE_CENTRIC>(bf16lo_to_f32(mx), s_enc_col, st0, c0);
-        nvfp4_block_scale<ENCODE_CENTRIC>(bf16hi_to_f32(mx), s_enc_col, st1, c1);
-        uint2 q0, q1;
-        q0.x = f32x8_to_e2m1x8(bf16lo_to_f32(w[0]) * c0, bf16lo_to_f32(w[1]) * c0, bf16lo_to_f32(w[2]) * c0,
-                               bf16lo_to_f32(w[3]) * c0, bf16lo_to_f32(w[4]) * c0, bf16lo_to_f32(w[5]) * c0,
-                               bf16lo_to_f32(w[6]) * c0, bf16lo_to_f32(w[7]) * c0);
-        q0.y = f32x8_to_e2m1x8(bf16lo_to_f32(w[8]) * c0, bf16lo_to_f32(w[9]) * c0, bf16lo_to_f32(w[10]) * c0,
-                               bf16lo_to_f32(w[11]) * c0, bf16lo_to_f32(w[12]) * c0, bf16lo_to_f32(w[13]) * c0,
-                               bf16lo_to_f32(w[14]) * c0, bf16lo_to_f32(w[15]) * c0);
-        q1.x = f32x8_to_e2m1x8(bf16hi_to_f32(w[0]) * c1, bf16hi_to_f32(w[1]) * c1, bf16hi_to_f32(w[2]) * c1,
-                               bf16hi_to_f32(w[3]) * c1, bf16hi_to_f32(w[4]) * c1, bf16hi_to_f32(w[5]) * c1,
-                               bf16hi_to_f32(w[6]) * c1, bf16hi_to_f32(w[7]) * c1);
-        q1.y = f32x8_to_e2m1x8(bf16hi_to_f32(w[8]) * c1, bf16hi_to_f32(w[9]) * c1, bf16hi_to_f32(w[10]) * c1,
-                               bf16hi_to_f32(w[11]) * c1, bf16hi_to_f32(w[12]) * c1, bf16hi_to_f32(w[13]) * c1,
-                               bf16hi_to_f32(w[14]) * c1, bf16hi_to_f32(w[15]) * c1);
-        *reinterpret_cast<uint2*>(&sm.col_codes[c * kColPitch + warp * 8]) = q0;
-        *reinterpret_cast<uint2*>(&sm.col_codes[(c + 1) * kColPitch + warp * 8]) = q1;
-        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c, warp & 3)] = st0;
-        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c + 1, warp & 3)] = st1;
+        const float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
+        const ScaleLut e0 = sm.lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
+        const ScaleLut e1 = sm.lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
+        const float2 cc = make_float2(e0.coeff, e1.coeff);
+        float2 v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = mul2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), cc);
+        uint4 q;
+        q.x = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+        q.y = f32x8_to_e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
+        q.z = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+        q.w = f32x8_to_e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+        const int c = 2 * lane + 64 * h;
+        *reinterpret_cast<uint4*>(&sm.col_codes[warp][c]) = q;   // columns c and c+1
+        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c, warp & 3)] = (uint8_t)e0.stored;
+        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c + 1, warp & 3)] = (uint8_t)e1.stored;
       }
+    }
+    if constexpr (NORM) {
+      // the other inv_rms/gamma buffer was last read in the previous chunk's row pass
+      if (tid < kChunk) sm.inv_rms[pp ^ 1][tid] = pre;
+      else sm.gamma[pp ^ 1][tid - kChunk] = pre;
     }
     __syncthreads();
 
     // stage s is free again: refill it with the chunk kQStages ahead
     if (tid == 0 && it + kQStages < my_count) {
-      int ncm, nck;
-      chunk_coords(it + kQStages, ncm, nck);
       fence_proxy_async_smem();
-      mbar_expect_tx(&sm.full[s], kTileBytes);
-      tma_load_2d(sm.in[s], &tmap_x, nck * kChunk, ncm * kChunk, &sm.full[s]);
+      issue_load(it + kQStages, s);
     }
 
     // ---- write-out: scales (two 512-byte tiles per orientation) and column codes -----
@@ -408,14 +554,16 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
       uint8_t* dst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)cm * 2) * 512;
       st_cs_u32(dst + tid * 4, *reinterpret_cast<const uint32_t*>(&sm.col_sc[tid * 4]));
 #pragma unroll
-      for (int rep = 0; rep < 4; ++rep) {
-        const int idx = rep * kQThreads + tid;  // 1024 pieces of 8 bytes
-        const int c = idx >> 3, part = idx & 7;
-        const uint2 v = *reinterpret_cast<const uint2*>(&sm.col_codes[c * kColPitch + part * 8]);
-        st_cs_u2(a.col_fp4 + (size_t)(k0 + c) * (a.M >> 1) + (m0 >> 1) + part * 8, v);
+      for (int rep = 0; rep < 2; ++rep) {
+        const int idx = rep * kQThreads + tid;   // 512 pieces of 16 bytes: column = idx/4, 32-row part = idx%4
+        const int c = idx >> 2, part = idx & 3;
+        const uint2 lo = sm.col_codes[2 * part][c];
+        const uint2 hi = sm.col_codes[2 * part + 1][c];
+        st_cs_u4(a.col_fp4 + (size_t)(k0 + c) * (a.M >> 1) + (m0 >> 1) + part * 16,
+                 make_uint4(lo.x, lo.y, hi.x, hi.y));
       }
-      // no barrier needed here: col_codes / col_sc are next written after the barrier that
-      // follows the next chunk's row pass, which every thread reaches only after this loop
+      // col_codes / col_sc are next written after the barrier that follows the next chunk's row
+      // pass, which every thread reaches only after this loop: no barrier needed here
     }
   }
 }
@@ -440,7 +588,7 @@ static int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStrea
 template <bool EC, bool NORM>
 static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cudaStream_t st) {
   auto kern = nvfp4_quantize_kernel<EC, NORM>;
-  const int smem = (int)sizeof(QuantSmem) + 128;
+  const int smem = (int)sizeof(QuantSmem) + 1024;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_chunks = args.chunks_m * args.chunks_k;
   const int grid = std::min(n_chunks, 2 * device_sm_count());
@@ -456,7 +604,7 @@ static int launch_quantize(const void* x, int64_t M, int64_t K, const float* ama
                            cudaStream_t st) {
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
-                            (uint64_t)K * 2, kChunk, kChunk, CU_TENSOR_MAP_SWIZZLE_NONE))
+                            (uint64_t)K * 2, 64, kChunk, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   QuantArgs a{};
   a.amax_row = amax_row;
@@ -479,18 +627,19 @@ static int launch_quantize(const void* x, int64_t M, int64_t K, const float* ama
 static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms, float* amax_sg, float eps,
                                 int64_t M, int64_t K, bool compute_inv, cudaStream_t st) {
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
-  const int warps_per_block = 8;
-  int grid = (int)std::min<int64_t>((M + warps_per_block - 1) / warps_per_block, (int64_t)device_sm_count() * 8);
+  const int warps_per_block = kStatsThreads / 32;
+  int grid = (int)std::min<int64_t>((M + warps_per_block - 1) / warps_per_block, (int64_t)device_sm_count() * 2);
   if (grid > 0) {
     auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
     auto gb = reinterpret_cast<const __nv_bfloat16*>(gamma);
     if (K <= 2048) {
-      if (compute_inv) rmsnorm_stats_kernel<8, true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-      else rmsnorm_stats_kernel<8, false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
+      if (compute_inv) rmsnorm_stats_kernel<8, true><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
+      else rmsnorm_stats_kernel<8, false><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
     } else if (K <= 4096) {
-      if (compute_inv) rmsnorm_stats_kernel<16, true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-      else rmsnorm_stats_kernel<16, false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
+      if (compute_inv) rmsnorm_stats_kernel<16, true><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
+      else rmsnorm_stats_kernel<16, false><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
     } else {
+      grid = (int)std::min<int64_t>((M + 7) / 8, (int64_t)device_sm_count() * 8);
       if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
       else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
     }
