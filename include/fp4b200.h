@@ -83,6 +83,32 @@ int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
                                   const float* amax, int64_t M, int64_t K, int encode_centric, void* row_fp4,
                                   void* row_sc, void* col_fp4, void* col_sc, void* stream);
 
+/* ---- block-scaled FP4 GEMMs ------------------------------------------------------------ */
+/* Shapes: M % 128 == 0, N % 256 == 0, K % 256 == 0.  A [M,K/2] and B [N,K/2] packed codes,
+ * scales in the 512-byte tile layout above, D row-major [M,N] written in place.
+ * out_fp32 = 0: D is bf16, = 1: D is fp32 (the accumulator times the tensor scales, unrounded).
+ * residual_bf16 (optional, bf16 [M,N]): D = bf16(bf16(acc*scale) + R). */
+
+/* D = bf16((A.B^T) * A_sg * B_sg): nvfp4_gemm / nvfp4_gemm_config / nvfp4_gemm_nopdl /
+ * nvfp4_gemm_residual (fp4_runtime/ThunderKittens/kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:648-761,
+ * 1702-1735, 1899-1920; kernel nvfp4_gemm.cuh:490-1012).  A_sg, B_sg: device scalars. */
+int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                       const float* B_sg, void* D, int out_fp32, const void* residual_bf16, int64_t M, int64_t N,
+                       int64_t K, void* stream);
+
+/* nvfp4_grouped_gemm (nvfp4_b200_gemm.cu:764-841): B is the row concatenation of n_out weights,
+ * B_sg_per_tile holds one tensor scale per 256 rows of B, output i receives D_cols[i] columns
+ * (each a multiple of 256, adding up to N) into its own bf16 [M, D_cols[i]] buffer. */
+int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                               const float* B_sg_per_tile, int n_out, void* const* D, const int64_t* D_cols,
+                               int64_t M, int64_t N, int64_t K, void* stream);
+
+/* D = bf16((A.B^T) / 36) with E8M0 scales per 32 elements: mxfp4_gemm / mxfp4_gemm_config /
+ * mxfp4_gemm_residual (fp4_runtime/ThunderKittens/kernels/gemm/mxfp4_gb200/mxfp4_gb200_gemm.cu:2704-2950;
+ * kernel mxfp4_gemm.cuh, 1/36 at :557-558). */
+int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,
+                       const void* residual_bf16, int64_t M, int64_t N, int64_t K, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -29,6 +29,12 @@ SIGNATURES = {
                                           _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_normed": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p,
                                       _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int,
+                           _c_void_p, _i64, _i64, _i64, _c_void_p],
+    "fp4b200_nvfp4_grouped_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int,
+                                   ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _i64, _i64, _i64, _c_void_p],
+    "fp4b200_mxfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p, _i64, _i64,
+                           _i64, _c_void_p],
 }
 _RESTYPES = {"fp4b200_last_error": ctypes.c_char_p}
 

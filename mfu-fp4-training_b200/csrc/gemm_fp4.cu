@@ -1,0 +1,453 @@
+// Block-scaled FP4 GEMM for sm_100a: D[M,N] = (A . B^T) * (a_sg * b_sg), A [M,K/2] and
+// B [N,K/2] packed E2M1 (K-major), block scales in 512-byte tiles (128 rows x 4 blocks),
+// fp32 accumulation in tensor memory.
+//
+//   NVFP4: 16-element blocks, E4M3 scales, tcgen05.mma kind::mxf4nvf4 scale_vec::4X
+//   MXFP4: 32-element blocks, E8M0 scales, tcgen05.mma kind::mxf4     scale_vec::2X,
+//          accumulator multiplied by 1/36 (operands were scaled to +-6 rather than +-1)
+//
+// Replaces nvfp4_gemm::kernel / mxfp4_gemm::kernel of the reference
+// (fp4_runtime/ThunderKittens/kernels/gemm/nvfp4_b200/nvfp4_gemm.cuh:490-1012,
+//  fp4_runtime/ThunderKittens/kernels/gemm/mxfp4_gb200/mxfp4_gemm.cuh).  Unlike the reference
+// there is no cluster-multicast TMA load: every CTA fetches its own operand tiles.
+//
+// One persistent CTA per SM works through 128 x 256 output tiles.  Warp roles:
+//   warp 0      TMA producer: per 256-deep K stage one A box (128 rows x 128 B), one B box
+//               (256 rows x 128 B), both 128-byte swizzled, and three bulk copies of scale tiles
+//   warp 1      owns tensor memory; one lane issues tcgen05.cp (scales -> TMEM) and tcgen05.mma
+//   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, (residual), convert, store
+// Every wait on an mbarrier is bounded in time; a wait that runs out records a status code,
+// and the CTA drains to the common exit where tensor memory is released.
+#include "fp4_common.cuh"
+#include "host_util.h"
+
+namespace fp4b200 {
+
+constexpr int kGemmBM = 128;
+constexpr int kGemmBN = 256;
+constexpr int kGemmBKBytes = 128;                  // 256 FP4 elements per stage
+constexpr int kGemmStages = 4;
+constexpr int kGemmThreads = 192;
+constexpr int kATileBytes = kGemmBM * kGemmBKBytes;   // 16 KiB
+constexpr int kBTileBytes = kGemmBN * kGemmBKBytes;   // 32 KiB
+constexpr int kASfBytes = 2048;                    // 4 scale tiles of 512 B (one per K=64 step)
+constexpr int kBSfBytes = 4096;                    // two 128-row groups x 4 scale tiles
+constexpr int kTmemCols = 512;
+constexpr int kSfTmemBase = 256;                   // accumulator occupies columns [0,256)
+constexpr int kSfSlotCols = 48;                    // per stage: 16 columns of A scales + 32 of B scales
+constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at boost clock
+
+struct GemmSmem {
+  alignas(1024) uint8_t a[kGemmStages][kATileBytes];
+  alignas(1024) uint8_t b[kGemmStages][kBTileBytes];
+  alignas(128) uint8_t sfa[kGemmStages][kASfBytes];
+  alignas(128) uint8_t sfb[kGemmStages][kBSfBytes];
+  alignas(8) uint64_t full[kGemmStages];
+  alignas(8) uint64_t empty[kGemmStages];
+  alignas(8) uint64_t acc_full;
+  alignas(8) uint64_t acc_empty;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+struct GemmArgs {
+  const uint8_t* a_sc;      // [M/128, K/(4*block), 512]
+  const uint8_t* b_sc;      // [N/128, K/(4*block), 512]
+  const float* a_sg;        // device scalar (NVFP4) or null
+  const float* b_sg;        // device scalar, or per-256-column-tile array when b_sg_per_tile != 0
+  int b_sg_per_tile;
+  float fixed_scale;        // multiplies the accumulator when a_sg is null (MXFP4: 1/36)
+  void* d[3];               // up to three outputs, split by column range
+  int d_col_end[3];         // exclusive end column (in N) of each output
+  int d_ld[3];              // leading dimension (elements) of each output
+  int n_out;
+  int out_fp32;             // 0: bf16 output, 1: fp32 output
+  const __nv_bfloat16* residual;  // optional [M, N] bf16 added after the bf16 rounding
+  int residual_ld;
+  int M, N, K;
+  int sf_tiles_k;           // scale tiles along K per row tile
+  int* status;
+};
+
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  while (!mbar_try_wait(bar, parity)) {
+    if (clock64() - t0 > kWaitLimitCycles) return false;
+  }
+  return true;
+}
+
+__device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(smem_dst)), "l"(gsrc), "r"(bytes), "r"(smem_u32(bar))
+               : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+               : "memory");
+}
+
+// shared-memory matrix descriptor (tcgen05): 14-bit address/offset fields in 16-byte units,
+// descriptor version 1 at bit 46, layout type at bits 61..63 (0 none, 2 = 128-byte swizzle)
+__device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes, uint32_t layout) {
+  return (uint64_t)((saddr & 0x3FFFF) >> 4) | ((uint64_t)((lbo_bytes & 0x3FFFF) >> 4) << 16) |
+         ((uint64_t)((sbo_bytes & 0x3FFFF) >> 4) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
+}
+
+// 32 rows x 16 bytes in shared memory -> 128 lanes x 4 columns of tensor memory (replicated per quadrant)
+__device__ __forceinline__ void tc_copy_sf(uint32_t tmem_addr, uint32_t saddr) {
+  const uint64_t desc = smem_desc(saddr, 128, 128, 0);
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
+}
+
+template <bool MX>
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
+  if constexpr (MX) {
+    asm volatile(
+        "{.reg .pred p; setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.scale_vec::2X [%0], %1, %2, %3, [%5], [%6], p;}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  } else {
+    asm volatile(
+        "{.reg .pred p; setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%5], [%6], p;}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(sfa_tmem), "r"(sfb_tmem)
+        : "memory");
+  }
+}
+
+// instruction descriptor of the block-scaled kinds: A/B format E2M1 (=1) at bits 7 and 10,
+// N>>3 at bit 17, scale type at bit 23 (0 UE4M3, 1 UE8M0), M>>4 at bit 24, scale-factor ids
+// at bits 4 (B) and 29 (A), K=64 (bit 31 = 0), both operands K-major, dense.
+__host__ __device__ constexpr uint32_t block_scaled_idesc(int M, int N, int ue8m0, int sf_id) {
+  return (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)ue8m0 << 23) |
+         ((uint32_t)(M >> 4) << 24) | ((uint32_t)sf_id << 4) | ((uint32_t)sf_id << 29);
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+template <bool MX>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                const GemmArgs g) {
+  extern __shared__ uint8_t smem_raw[];
+  GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+
+  const int tid = threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31;
+  const int tiles_m = g.M / kGemmBM, tiles_n = g.N / kGemmBN;
+  const int n_tiles = tiles_m * tiles_n;
+  const int k_stages = g.K / (2 * kGemmBKBytes);     // stages of 256 elements
+
+  if (tid == 0) {
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    mbar_init(&sm.acc_full, 1);
+    mbar_init(&sm.acc_empty, 4);   // one arrival per epilogue warp
+    sm.abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {   // tensor-memory allocation is a warp-wide operation
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
+                 "r"(kTmemCols)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sm.tmem_base;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------------------
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_a);
+      tma_prefetch_desc(&tmap_b);
+      int stage = 0;
+      uint32_t phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        const int tm = t % tiles_m, tn = t / tiles_m;
+        const uint8_t* sfa_src = g.a_sc + (size_t)tm * g.sf_tiles_k * 512;
+        const uint8_t* sfb_src0 = g.b_sc + (size_t)(2 * tn) * g.sf_tiles_k * 512;
+        const uint8_t* sfb_src1 = sfb_src0 + (size_t)g.sf_tiles_k * 512;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (!mbar_wait_timed(&sm.empty[stage], phase ^ 1)) {
+            atomicExch(g.status, kStatusGemmTmaTimeout);
+            ok = false;
+            break;
+          }
+          constexpr int kSfPerStage = MX ? 1024 : 2048;
+          mbar_expect_tx(&sm.full[stage], kATileBytes + kBTileBytes + 3 * kSfPerStage);
+          tma_load_2d(sm.a[stage], &tmap_a, ks * kGemmBKBytes, tm * kGemmBM, &sm.full[stage]);
+          tma_load_2d(sm.b[stage], &tmap_b, ks * kGemmBKBytes, tn * kGemmBN, &sm.full[stage]);
+          // scale tiles of this stage: NVFP4 4 tiles (256/64), MXFP4 2 tiles (256/128) per row tile
+          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)ks * kSfPerStage, kSfPerStage,
+                       &sm.full[stage]);
+          if (++stage == kGemmStages) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer --------------------------------------------
+    if (lane == 0) {
+      int stage = 0;
+      uint32_t phase = 0;
+      uint32_t acc_phase = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+        // the epilogue must have drained the accumulator of the previous tile
+        if (!mbar_wait_timed(&sm.acc_empty, acc_phase ^ 1)) {
+          atomicExch(g.status, kStatusGemmEpilogueTimeout);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (!mbar_wait_timed(&sm.full[stage], phase)) {
+            atomicExch(g.status, kStatusGemmMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sf_cols = tmem + kSfTmemBase + (stage & 1) * kSfSlotCols;
+          const uint32_t a_base = smem_u32(sm.a[stage]);
+          const uint32_t b_base = smem_u32(sm.b[stage]);
+          const uint32_t sfa_base = smem_u32(sm.sfa[stage]);
+          const uint32_t sfb_base = smem_u32(sm.sfb[stage]);
+          if constexpr (!MX) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {   // one 512-byte scale tile per K=64 step
+              tc_copy_sf(sf_cols + j * 4, sfa_base + j * 512);
+              tc_copy_sf(sf_cols + 16 + j * 8, sfb_base + j * 512);
+              tc_copy_sf(sf_cols + 16 + j * 8 + 4, sfb_base + 2048 + j * 512);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
+              const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+              tc_mma<false>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 0, 0), sf_cols + j * 4,
+                            sf_cols + 16 + j * 8, (ks | j) != 0);
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {   // one 512-byte scale tile per K=128 (two K=64 steps)
+              tc_copy_sf(sf_cols + j * 4, sfa_base + j * 512);
+              tc_copy_sf(sf_cols + 16 + j * 8, sfb_base + j * 512);
+              tc_copy_sf(sf_cols + 16 + j * 8 + 4, sfb_base + 1024 + j * 512);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
+              const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+              const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
+              tc_mma<true>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 1, sf_id),
+                           sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
+            }
+          }
+          tc_commit(&sm.empty[stage]);   // frees the shared-memory stage once these MMAs have read it
+          if (++stage == kGemmStages) { stage = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&sm.acc_full);
+        acc_phase ^= 1;
+      }
+    }
+  } else {
+    // ------------------------------ epilogue ----------------------------------------------
+    const int quad = warp & 3;                 // tensor-memory lane quadrant this warp may read
+    uint32_t acc_phase = 0;
+    float a_sg = g.fixed_scale;
+    if (g.a_sg != nullptr) a_sg = __ldg(g.a_sg);
+    bool ok = true;
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      const int tm = t % tiles_m, tn = t / tiles_m;
+      float gs = a_sg;
+      if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? tn : 0));
+      const int row = tm * kGemmBM + quad * 32 + lane;
+      int col0 = tn * kGemmBN;
+      // which output receives this column tile
+      int oi = 0, col_start = 0;
+      while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
+      const int ld = g.d_ld[oi];
+      const int ocol = col0 - col_start;
+      if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
+        if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+#pragma unroll 1
+      for (int c = 0; c < kGemmBN; c += 32) {
+        uint32_t r[32];
+        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+        tmem_ld_wait();
+        if (g.out_fp32) {
+          float* dst = reinterpret_cast<float*>(g.d[oi]) + (size_t)row * ld + ocol + c;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            float4 v = make_float4(__uint_as_float(r[4 * q]) * gs, __uint_as_float(r[4 * q + 1]) * gs,
+                                   __uint_as_float(r[4 * q + 2]) * gs, __uint_as_float(r[4 * q + 3]) * gs);
+            *reinterpret_cast<float4*>(dst + 4 * q) = v;
+          }
+        } else {
+          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.d[oi]) + (size_t)row * ld + ocol + c;
+          uint32_t o[16];
+#pragma unroll
+          for (int q = 0; q < 16; ++q)
+            o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs, __uint_as_float(r[2 * q + 1]) * gs);
+          if (g.residual != nullptr) {
+            const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.residual_ld + col0 + c);
+#pragma unroll
+            for (int q = 0; q < 4; ++q) {
+              const uint4 rv = __ldg(rs + q);
+              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const uint32_t d = o[4 * q + e];
+                o[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]),
+                                               bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
+              }
+            }
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+      }
+      // accumulator drained: let the MMA warp start the next tile
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.acc_empty);
+      acc_phase ^= 1;
+    }
+  }
+
+  // common exit: every role arrives here (also after a timeout); release tensor memory
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+  }
+}
+
+static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                       const float* B_sg, int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld,
+                       int n_out, int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N,
+                       int64_t K, cudaStream_t st) {
+  CUtensorMap tmap_a, tmap_b;
+  if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)M,
+                            (uint64_t)K / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_tmap_2d(&tmap_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)N,
+                            (uint64_t)K / 2, kGemmBKBytes, kGemmBN, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  GemmArgs g{};
+  g.a_sc = (const uint8_t*)A_sc; g.b_sc = (const uint8_t*)B_sc;
+  g.a_sg = A_sg; g.b_sg = B_sg; g.b_sg_per_tile = b_sg_per_tile;
+  g.fixed_scale = mx ? (1.0f / 36.0f) : 1.0f;
+  for (int i = 0; i < 3; ++i) { g.d[i] = i < n_out ? D[i] : nullptr; g.d_col_end[i] = i < n_out ? d_col_end[i] : 0; g.d_ld[i] = i < n_out ? d_ld[i] : 0; }
+  g.n_out = n_out; g.out_fp32 = out_fp32;
+  g.residual = (const __nv_bfloat16*)residual; g.residual_ld = residual_ld;
+  g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.sf_tiles_k = (int)(K / (mx ? 128 : 64));
+  g.status = device_status_ptr();
+  if (g.status == nullptr) return -1;
+  const int smem = (int)sizeof(GemmSmem) + 1024;
+  const int n_tiles = (int)((M / kGemmBM) * (N / kGemmBN));
+  const int grid = std::min(n_tiles, device_sm_count());
+  if (grid == 0) return 0;
+  if (mx) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    fp4_gemm_kernel<true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, g);
+  } else {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    fp4_gemm_kernel<false><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, g);
+  }
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace fp4b200
+
+using namespace fp4b200;
+
+static int check_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, int64_t M, int64_t N,
+                      int64_t K, const char* who) {
+  if (!A || !A_sc || !B || !B_sc) return set_error("%s: operand pointer is null", who);
+  if (M <= 0 || N <= 0 || K <= 0 || (M % kGemmBM) || (N % kGemmBN) || (K % 256))
+    return set_error("%s: needs M %% 128 == 0, N %% 256 == 0, K %% 256 == 0 (got M=%lld N=%lld K=%lld)", who,
+                     (long long)M, (long long)N, (long long)K);
+  if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return set_error("%s: dimension too large", who);
+  if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(A_sc) |
+       reinterpret_cast<uintptr_t>(B_sc)) & 15)
+    return set_error("%s: operands and scales must be 16-byte aligned", who);
+  return 0;
+}
+
+extern "C" {
+
+int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                       const float* B_sg, void* D, int out_fp32, const void* residual_bf16, int64_t M, int64_t N,
+                       int64_t K, void* stream) {
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, "nvfp4_gemm")) return rc;
+  if (!A_sg || !B_sg || !D) return set_error("nvfp4_gemm: A_sg, B_sg and D are required");
+  if (residual_bf16 && out_fp32) return set_error("nvfp4_gemm: the residual epilogue writes bf16 only");
+  void* d[1] = {D};
+  int ce[1] = {(int)N}, ld[1] = {(int)N};
+  return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg, 0, d, ce, ld, 1, out_fp32, residual_bf16, (int)N, M, N, K,
+                     (cudaStream_t)stream);
+}
+
+int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                               const float* B_sg_per_tile, int n_out, void* const* D, const int64_t* D_cols,
+                               int64_t M, int64_t N, int64_t K, void* stream) {
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, "nvfp4_grouped_gemm")) return rc;
+  if (!A_sg || !B_sg_per_tile || !D || !D_cols) return set_error("nvfp4_grouped_gemm: null argument");
+  if (n_out < 1 || n_out > 3) return set_error("nvfp4_grouped_gemm: 1 to 3 outputs are supported");
+  int ce[3] = {0, 0, 0}, ld[3] = {0, 0, 0};
+  int64_t acc = 0;
+  for (int i = 0; i < n_out; ++i) {
+    if (!D[i] || D_cols[i] <= 0 || (D_cols[i] % kGemmBN))
+      return set_error("nvfp4_grouped_gemm: every output needs a column count that is a multiple of 256");
+    acc += D_cols[i];
+    ce[i] = (int)acc;
+    ld[i] = (int)D_cols[i];
+  }
+  if (acc != N) return set_error("nvfp4_grouped_gemm: output columns must add up to N");
+  return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg_per_tile, 1, D, ce, ld, n_out, 0, nullptr, 0, M, N, K,
+                     (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,
+                       const void* residual_bf16, int64_t M, int64_t N, int64_t K, void* stream) {
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, "mxfp4_gemm")) return rc;
+  if (!D) return set_error("mxfp4_gemm: D is required");
+  if (residual_bf16 && out_fp32) return set_error("mxfp4_gemm: the residual epilogue writes bf16 only");
+  void* d[1] = {D};
+  int ce[1] = {(int)N}, ld[1] = {(int)N};
+  return launch_gemm(true, A, A_sc, nullptr, B, B_sc, nullptr, 0, d, ce, ld, 1, out_fp32, residual_bf16, (int)N, M, N,
+                     K, (cudaStream_t)stream);
+}
+
+}  // extern "C"

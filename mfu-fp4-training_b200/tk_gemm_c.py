@@ -1,0 +1,128 @@
+"""Host-side mirror of the reference's ``_C`` extension module (NVFP4 tcgen05 GEMMs).
+
+Same names and argument order as the pybind module at
+fp4_runtime/ThunderKittens/kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:2851-3034: operands are
+packed ``[rows, K/2]`` code tensors, scales ``[rows/128, K/64, 512]`` (or any contiguous view of
+the same bytes), tensor scales fp32 ``[1]`` on the device; ``D`` is pre-allocated bf16 and written
+in place; every function returns ``None``.  Kernels go to torch's current stream.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _chk_operand(t, name):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous():
+        raise RuntimeError(f"{name} must be a contiguous CUDA tensor")
+    if t.element_size() != 1:
+        raise RuntimeError(f"{name} must be a 1-byte dtype (packed fp4 / fp8 scale bytes)")
+
+
+def _shapes(A, B, D_cols_total=None):
+    if A.dim() != 2 or B.dim() != 2:
+        raise RuntimeError("A and B must be 2-D packed tensors [rows, K/2]")
+    M, Kh = A.shape
+    N, Kh2 = B.shape
+    if Kh != Kh2:
+        raise RuntimeError(f"K mismatch between A ({2 * Kh}) and B ({2 * Kh2})")
+    return M, N, 2 * Kh
+
+
+def _chk_sg(t, name, n=1):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.float32 or t.numel() < n:
+        raise RuntimeError(f"{name} must be a CUDA float32 tensor with at least {n} element(s)")
+
+
+def _chk_out(D, M, N, dtype=torch.bfloat16):
+    if not isinstance(D, torch.Tensor) or not D.is_cuda or not D.is_contiguous() or D.dtype != dtype:
+        raise RuntimeError(f"D must be a contiguous CUDA {dtype} tensor")
+    if tuple(D.shape) != (M, N):
+        raise RuntimeError(f"D must have shape ({M}, {N}), got {tuple(D.shape)}")
+
+
+def _stream(t):
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def _gemm(A, A_sc, A_sg, B, B_sc, B_sg, D, residual=None):
+    for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
+        _chk_operand(t, n)
+    _chk_sg(A_sg, "A_sc_global")
+    _chk_sg(B_sg, "B_sc_global")
+    M, N, K = _shapes(A, B)
+    out_fp32 = 1 if D.dtype == torch.float32 else 0
+    _chk_out(D, M, N, D.dtype if out_fp32 else torch.bfloat16)
+    if residual is not None:
+        _chk_out(residual, M, N)
+    with torch.cuda.device(A.device):
+        _lib.call("fp4b200_nvfp4_gemm", A.data_ptr(), A_sc.data_ptr(), A_sg.data_ptr(), B.data_ptr(),
+                  B_sc.data_ptr(), B_sg.data_ptr(), D.data_ptr(), out_fp32,
+                  None if residual is None else residual.data_ptr(), M, N, K, _stream(A))
+
+
+def nvfp4_gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D):
+    """nvfp4_b200_gemm.cu:648-761.  A float32 ``D`` selects the unrounded fp32 epilogue (an
+    addition used by the parity tests; the reference writes bf16 only)."""
+    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
+
+
+def nvfp4_gemm_config(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D, config_id):
+    """nvfp4_b200_gemm.cu:1899-1920.  ``config_id`` selects among the reference's precompiled tile
+    shapes; this library has one tile shape, so the id is accepted and ignored."""
+    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
+
+
+def nvfp4_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D):
+    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
+
+
+def nvfp4_gemm_config_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D, config_id):
+    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
+
+
+def nvfp4_gemm_residual(A, A_sc, A_sc_global, B, B_sc, B_sc_global, R, D):
+    """nvfp4_b200_gemm.cu:1702-1735: ``D = bf16(bf16(acc * sg) + R)``."""
+    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D, residual=R)
+
+
+def nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt=None, D_V_opt=None, silu_dim=0):
+    """nvfp4_b200_gemm.cu:764-841: one GEMM over concatenated weights, per-256-row tensor scales,
+    outputs routed by column range to ``D`` (and ``D_K_opt``, ``D_V_opt``)."""
+    if silu_dim:
+        raise RuntimeError("nvfp4_grouped_gemm: the SiLU epilogue (silu_dim > 0) is not built")
+    for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
+        _chk_operand(t, n)
+    M, N, K = _shapes(A, B)
+    _chk_sg(A_sc_global, "A_sc_global")
+    _chk_sg(B_sg_per_tile, "B_sg_per_tile", N // 256)
+    outs = [D] + [t for t in (D_K_opt, D_V_opt) if t is not None]
+    cols = []
+    for o in outs:
+        if not o.is_cuda or o.dtype != torch.bfloat16 or not o.is_contiguous() or o.dim() != 2 or o.shape[0] != M:
+            raise RuntimeError("grouped GEMM outputs must be contiguous CUDA bfloat16 [M, n_i]")
+        cols.append(o.shape[1])
+    if sum(cols) != N:
+        raise RuntimeError(f"grouped GEMM outputs have {sum(cols)} columns in total, B has {N} rows")
+    ptrs = (ctypes.c_void_p * len(outs))(*[o.data_ptr() for o in outs])
+    ccols = (ctypes.c_int64 * len(outs))(*cols)
+    with torch.cuda.device(A.device):
+        _lib.call("fp4b200_nvfp4_grouped_gemm", A.data_ptr(), A_sc.data_ptr(), A_sc_global.data_ptr(), B.data_ptr(),
+                  B_sc.data_ptr(), B_sg_per_tile.data_ptr(), len(outs), ptrs, ccols, M, N, K, _stream(A))
+
+
+def nvfp4_grouped_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt=None, D_V_opt=None,
+                             silu_dim=0):
+    nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt, D_V_opt, silu_dim)
+
+
+def nvfp4_batched_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_list, D_list):
+    """nvfp4_b200_gemm.cu:1946-2010: independent GEMMs ``D_i = A_i . B_i^T`` (up to four)."""
+    n = len(D_list)
+    if not (len(A_list) == len(A_sc_list) == len(A_sg_list) == len(B_list) == len(B_sc_list) == len(B_sg_list) == n):
+        raise RuntimeError("nvfp4_batched_gemm: all lists must have the same length")
+    for i in range(n):
+        _gemm(A_list[i], A_sc_list[i], A_sg_list[i], B_list[i], B_sc_list[i], B_sg_list[i], D_list[i])
