@@ -739,4 +739,57 @@ int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
                          col_fp4, col_sc, nullptr, true, (cudaStream_t)stream);
 }
 
+
+// ---- variant that allocates nothing -------------------------------------------------------
+// Scratch of the fused producer (inverse RMS per row, tensor amax, sg) in a fixed device array
+// owned by the library, for callers that must not allocate.  Every device that loads the
+// library holds kNoAllocMaxRows * 4 + 256 bytes of it until the process exits.
+constexpr int64_t kNoAllocMaxRows = 65536;
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxRows + 64];
+
+// Device address of the scratch array on the current device.  The array's name is only a
+// host-side handle, so the address is looked up once per device and cached.
+static float* noalloc_scratch_ptr() {
+  static float* cached[64] = {nullptr};
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+    set_error("nvfp4_fused_norm_quantize_noalloc: cudaGetDevice failed");
+    return nullptr;
+  }
+  if (cached[dev] == nullptr) {
+    void* p = nullptr;
+    const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+    if (e != cudaSuccess || p == nullptr) {
+      set_error("nvfp4_fused_norm_quantize_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
+      return nullptr;
+    }
+    cached[dev] = static_cast<float*>(p);
+  }
+  return cached[dev];
+}
+
+int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,
+                                              int64_t K, void* row_fp4, void* row_sc, void* col_fp4,
+                                              void* col_sc, float* sg_out, void* stream) {
+  if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_fused_norm_quantize_noalloc")) return rc;
+  if (M > kNoAllocMaxRows)
+    return set_error("nvfp4_fused_norm_quantize_noalloc: M=%lld exceeds the built-in scratch (at most %lld rows); "
+                     "use fp4b200_nvfp4_fused_norm_quantize with caller-provided buffers",
+                     (long long)M, (long long)kNoAllocMaxRows);
+  if (gamma_bf16 == nullptr || row_fp4 == nullptr || row_sc == nullptr || sg_out == nullptr)
+    return set_error("nvfp4_fused_norm_quantize_noalloc: gamma, row_fp4, row_sc and sg_out are required");
+  if ((col_fp4 == nullptr) != (col_sc == nullptr))
+    return set_error("nvfp4_fused_norm_quantize_noalloc: col_fp4 and col_sc must both be given or both be null");
+  if ((reinterpret_cast<uintptr_t>(gamma_bf16) & 15) != 0)
+    return set_error("nvfp4_fused_norm_quantize_noalloc: gamma must be 16-byte aligned");
+  float* scratch = noalloc_scratch_ptr();
+  if (scratch == nullptr) return -1;
+  float* amax_sg = scratch;        // [0] amax (cleared by the statistics launcher), [1] sg
+  float* inv_rms = scratch + 64;   // [M]
+  if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, true, (cudaStream_t)stream))
+    return rc;
+  return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, true, inv_rms, gamma_bf16, row_fp4, row_sc, col_fp4,
+                         col_sc, sg_out, true, (cudaStream_t)stream);
+}
+
 }  // extern "C"

@@ -1,0 +1,64 @@
+"""GPU: the entry point that allocates nothing (fp4b200_nvfp4_fused_norm_quantize_noalloc).
+
+Some callers of this library cannot allocate device memory when they need the fused producer:
+code that runs while a stream is being captured, or under a memory budget that is already fully
+handed out.  For them the library keeps the producer's scratch (inverse RMS per row, tensor amax)
+in a fixed device array of its own.  This test calls that entry point through the C ABI twice in a
+row, with different inputs, and checks every output byte against the ordinary entry point, which
+uses caller-provided buffers: the second call must not see anything left over from the first.
+It is collected last so that a run stopping at the first failure has already run the other tests.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import fp4_oracle as o
+from tests.gpu_util import assert_status_ok, mod, to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _run_both(lib, x, g, eps):
+    M, K = x.shape
+    dev = x.device
+    u8 = dict(dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def bufs():
+        return (torch.full((M, K // 2), 0xAA, **u8), torch.full((M * K // 16,), 0xAA, **u8),
+                torch.full((K, M // 2), 0xAA, **u8), torch.full((M * K // 16,), 0xAA, **u8))
+
+    a = bufs()
+    sg_a = torch.zeros(1, dtype=torch.float32, device=dev)
+    lib.call("fp4b200_nvfp4_fused_norm_quantize_noalloc", x.data_ptr(), g.data_ptr(), eps, M, K,
+             a[0].data_ptr(), a[1].data_ptr(), a[2].data_ptr(), a[3].data_ptr(), sg_a.data_ptr(), stream)
+    b = bufs()
+    inv = torch.empty(M, dtype=torch.float32, device=dev)
+    amax_sg = torch.empty(2, dtype=torch.float32, device=dev)
+    lib.call("fp4b200_nvfp4_fused_norm_quantize", x.data_ptr(), g.data_ptr(), eps, M, K, inv.data_ptr(), 1, 1,
+             b[0].data_ptr(), b[1].data_ptr(), b[2].data_ptr(), b[3].data_ptr(), amax_sg.data_ptr(), stream)
+    torch.cuda.synchronize()
+    for got, want, name in zip(a, b, ("row codes", "row scales", "column codes", "column scales")):
+        assert torch.equal(got, want), f"{name} differ from the allocating entry point"
+    assert sg_a.item() == amax_sg[1].item()
+
+
+def test_noalloc_matches_allocating_entry_point_twice():
+    lib = mod("_lib")
+    # first call: a large-amplitude tensor; second call: a smaller one with a smaller amax and
+    # fewer rows, so stale scratch from the first call would change the result
+    x1 = to_dev_bf16(o.make_activations(512, 1024, seed=101, scale=4.0))
+    g1 = to_dev_bf16(o.make_gamma(1024, seed=102))
+    _run_both(lib, x1, g1, 1e-5)
+    x2 = to_dev_bf16(o.make_activations(256, 512, seed=103, scale=0.05, outlier_frac=0))
+    g2 = to_dev_bf16(o.make_gamma(512, seed=104))
+    _run_both(lib, x2, g2, 1e-5)
+    assert_status_ok()
+
+
+def test_noalloc_rejects_too_many_rows():
+    lib = mod("_lib")
+    x = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(RuntimeError, match="exceeds the built-in scratch"):
+        lib.call("fp4b200_nvfp4_fused_norm_quantize_noalloc", x.data_ptr(), x.data_ptr(), 1e-5, 65536 + 128, 128,
+                 x.data_ptr(), x.data_ptr(), None, None, x.data_ptr(), None)
