@@ -98,6 +98,43 @@ int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* ga
                                               int64_t K, void* row_fp4, void* row_sc, void* col_fp4,
                                               void* col_sc, float* sg_out, void* stream);
 
+/* ---- MXFP4 producers ------------------------------------------------------------------- */
+
+/* Row (+column when col_* non-NULL) MXFP4 quantisation of bf16 [M,K]: 32-element blocks, E8M0
+ * scale = exponent of the block amax rounded by mode (0 RTE, 1 ceil, 2 floor), codes =
+ * e2m1(x * 6 * 2^(127-e)).  Replaces mxfp4_quantize_row_and_col / mxfp4_quantize_for_gemm
+ * (fp4_runtime/TK_quantisation/mxfp4_v4/tk_quantize.cu:1883-2060; kernels mxfp4_v3_quantize.cuh:1540-1790). */
+int fp4b200_mxfp4_quantize(const void* x_bf16, int64_t M, int64_t K, int mode, void* row_fp4, void* row_sc,
+                           void* col_fp4, void* col_sc, void* stream);
+
+/* Same on bf16(x * inv_rms[row] * gamma[col]): second half of
+ * mxfp4_fused_rmsnorm_quantize_row_and_col (mxfp4_v4/tk_quantize.cu:6947-6964); inv_rms comes from
+ * fp4b200_nvfp4_rmsnorm_stats. */
+int fp4b200_mxfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M,
+                                  int64_t K, int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                  void* stream);
+
+/* ---- SwiGLU producers ------------------------------------------------------------------ */
+
+/* h = bf16(silu(h1) * h3) element-wise and its tensor amax / sg; n_elems multiple of 8.
+ * Replaces tk_silu_split::silu_mul_split_kernel
+ * (fp4_runtime/TK_quantisation/nvfp4_v5/silu_split_bf16.cuh:62-140). */
+int fp4b200_silu_mul_bf16(const void* h1, const void* h3, int64_t n_elems, void* h_out, float* amax_sg,
+                          void* stream);
+
+/* tk_silu_quantize_split_for_gemm(h1_raw, h3) (tk_quantize.cu:8985-9123): h as above (materialised
+ * in h_bf16 [M,H]) then row (+column) NVFP4 quantisation of h with its own tensor amax. */
+int fp4b200_nvfp4_silu_quantize(const void* h1, const void* h3, int64_t M, int64_t H, void* h_bf16,
+                                int encode_centric, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                float* amax_sg, void* stream);
+
+/* dh1 = bf16(dh*h3*silu'(h1)), dh3 = bf16(dh*silu(h1)) and their amax/sg pairs.
+ * Replaces tk_silu_split::silu_deriv_dual_split_kernel (silu_split_bf16.cuh:181-300); the
+ * quantisation of dh1/dh3 (tk_silu_deriv_quantize_split_for_gemm[_opt], tk_quantize.cu:9418-9640,
+ * 10063-10255) is two calls of fp4b200_nvfp4_quantize with these amaxes. */
+int fp4b200_silu_deriv_bf16(const void* dh, const void* h3, const void* h1, int64_t n_elems, void* dh1_out,
+                            void* dh3_out, float* amax_sg1, float* amax_sg3, void* stream);
+
 /* ---- block-scaled FP4 GEMMs ------------------------------------------------------------ */
 /* Shapes: M % 128 == 0, N % 256 == 0, K % 256 == 0.  A [M,K/2] and B [N,K/2] packed codes,
  * scales in the 512-byte tile layout above, D row-major [M,N] written in place.

@@ -31,6 +31,14 @@ SIGNATURES = {
                                       _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_fused_norm_quantize_noalloc": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _c_void_p,
                                                   _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_mxfp4_quantize": [_c_void_p, _i64, _i64, _int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_mxfp4_quantize_normed": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p, _c_void_p,
+                                      _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_silu_mul_bf16": [_c_void_p, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_silu_quantize": [_c_void_p, _c_void_p, _i64, _i64, _c_void_p, _int, _c_void_p, _c_void_p,
+                                    _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_silu_deriv_bf16": [_c_void_p, _c_void_p, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                _c_void_p],
     "fp4b200_nvfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int,
                            _c_void_p, _i64, _i64, _i64, _c_void_p],
     "fp4b200_nvfp4_grouped_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int,

@@ -224,4 +224,42 @@ __device__ __forceinline__ void st_cs_u4(void* p, uint4 v) {
                : "memory");
 }
 
+// ---------------------------------------------------------------------------------------
+// Packed fp32x2 arithmetic (one issue slot for two lanes of fp32 work)
+// ---------------------------------------------------------------------------------------
+
+// {a.x*b.x, a.y*b.y}, round-to-nearest, denormals kept
+__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mul.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
+// {a.x*b.x + c.x, a.y*b.y + c.y}, each a fused multiply-add (same rounding as fmaf)
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  float2 d;
+  asm("{.reg .b64 x, y, z, w; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mov.b64 z, {%6, %7};"
+      " fma.rn.f32x2 w, x, y, z; mov.b64 {%0, %1}, w;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+  return d;
+}
+
+// running |.|-max on packed bf16x2; the sign of the result is meaningless
+__device__ __forceinline__ uint32_t absmax_xs(uint32_t acc, uint32_t v) {
+  uint32_t r;
+  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(v));
+  return r;
+}
+
+// four packed bf16x2 words times one coefficient -> 4 bytes of E2M1 codes
+__device__ __forceinline__ uint32_t quant8(const uint32_t* w, float coeff) {
+  const float2 cc = make_float2(coeff, coeff);
+  const float2 a = mul2(make_float2(bf16lo_to_f32(w[0]), bf16hi_to_f32(w[0])), cc);
+  const float2 b = mul2(make_float2(bf16lo_to_f32(w[1]), bf16hi_to_f32(w[1])), cc);
+  const float2 c = mul2(make_float2(bf16lo_to_f32(w[2]), bf16hi_to_f32(w[2])), cc);
+  const float2 d = mul2(make_float2(bf16lo_to_f32(w[3]), bf16hi_to_f32(w[3])), cc);
+  return f32x8_to_e2m1x8(a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y);
+}
+
 }  // namespace fp4b200

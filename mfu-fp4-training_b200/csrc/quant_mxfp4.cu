@@ -1,0 +1,287 @@
+// MXFP4 producers for sm_100a: row + column quantisation in 32-element blocks with E8M0 scales
+// (no tensor-level scale, so a single pass over the input), optional fused RMSNorm.
+//
+// Arithmetic follows the reference (fp4_runtime/TK_quantisation/mxfp4_v4/mxfp4_v3_quantize.cuh):
+//   E8M0 of the block amax, modes RTE / ceil / floor            :1295-1342
+//   coefficient 6 * 2^(127-e), codes = e2m1_rn(x * coefficient) :1601-1603 (exp2f_rcp util/ptx.cuh:330-338)
+//   scale bytes in 512-byte tiles of 128 rows x 4 blocks        :5059-5086
+// Pipeline and shared-memory geometry are those of the NVFP4 quantiser (quant_nvfp4.cu): persistent
+// CTAs, 128x128 chunks as two 128-byte-swizzled TMA boxes, three stages.
+#include "fp4_common.cuh"
+#include "host_util.h"
+
+namespace fp4b200 {
+
+constexpr int kMxChunk = 128;
+constexpr int kMxThreads = 256;
+constexpr int kMxStages = 3;
+constexpr int kMxHalfBytes = kMxChunk * 128;
+constexpr int kMxTileBytes = 2 * kMxHalfBytes;
+
+struct MxSmem {
+  alignas(1024) uint8_t in[kMxStages][kMxTileBytes];
+  alignas(16) uint4 col_codes[4][kMxChunk];   // [32-row group][column] -> 16 bytes of codes
+  alignas(16) uint8_t row_sc[2][512];
+  alignas(16) uint8_t col_sc[512];
+  alignas(16) float inv_rms[2][kMxChunk];
+  alignas(16) float gamma[2][kMxChunk];
+  alignas(8) uint64_t full[kMxStages];
+};
+
+struct MxArgs {
+  const float* inv_rms;        // [M] (NORM only)
+  const __nv_bfloat16* gamma;  // [K] (NORM only)
+  uint8_t* row_fp4;            // [M, K/2]
+  uint8_t* row_sc;             // [M/128, K/128, 512]
+  uint8_t* col_fp4;            // [K, M/2]   (may be null)
+  uint8_t* col_sc;             // [K/128, M/128, 512]
+  int* status;
+  int M, K, chunks_m, chunks_k;
+  int mode;                    // 0 RTE, 1 ceil ("encode"), 2 floor ("decode")
+};
+
+__device__ __forceinline__ uint32_t mx_e8m0(float b, int mode) {
+  if (b <= 1e-38f) return 0;
+  const uint32_t u = __float_as_uint(b);
+  uint32_t e = (u >> 23) & 0xFF;
+  const uint32_t m = u & 0x7FFFFF;
+  bool up;
+  if (mode == 1) up = m != 0;
+  else if (mode == 0) up = (m > 0x400000u) || (m == 0x400000u && (e & 1));
+  else up = false;
+  if (up && e < 0xFE) ++e;
+  return e;
+}
+
+// 6 * 2^(127-e); e = 254 needs the denormal 2^-127, e = 0 gives 2^127 (product overflows to inf)
+__device__ __forceinline__ float mx_coeff(uint32_t e) {
+  const float rcp = (e == 254) ? __uint_as_float(0x00400000u) : __uint_as_float((254u - e) << 23);
+  return 6.0f * rcp;
+}
+
+template <bool NORM>
+__global__ void __launch_bounds__(kMxThreads, 2)
+mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  MxSmem& sm = *reinterpret_cast<MxSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_chunks = a.chunks_m * a.chunks_k;
+  const int first = blockIdx.x, step = gridDim.x;
+  const int my_count = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
+  auto chunk_coords = [&](int it, int& cm, int& ck) {
+    const int c = first + it * step;
+    cm = c / a.chunks_k;
+    ck = c - cm * a.chunks_k;
+  };
+  auto issue_load = [&](int it, int s) {
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    mbar_expect_tx(&sm.full[s], kMxTileBytes);
+    tma_load_2d(sm.in[s], &tmap_x, ck * kMxChunk, cm * kMxChunk, &sm.full[s]);
+    tma_load_2d(sm.in[s] + kMxHalfBytes, &tmap_x, ck * kMxChunk + 64, cm * kMxChunk, &sm.full[s]);
+  };
+  if (tid == 0) {
+    tma_prefetch_desc(&tmap_x);
+    for (int s = 0; s < kMxStages; ++s) mbar_init(&sm.full[s], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (tid == 0)
+    for (int s = 0; s < kMxStages && s < my_count; ++s) issue_load(s, s);
+  const bool want_col = a.col_fp4 != nullptr;
+  if constexpr (NORM) {
+    if (my_count > 0) {
+      int cm, ck;
+      chunk_coords(0, cm, ck);
+      if (tid < kMxChunk) sm.inv_rms[0][tid] = __ldg(a.inv_rms + cm * kMxChunk + tid);
+      else sm.gamma[0][tid - kMxChunk] = __bfloat162float(a.gamma[ck * kMxChunk + tid - kMxChunk]);
+    }
+    __syncthreads();
+  }
+  // row pass: lane = (row & 7, 32-column unit = one MX block); column pass: warp = (32-row group, half)
+  const int unit = lane >> 3, r_lo = lane & 7;
+  const int half_off = (unit >> 1) * kMxHalfBytes, cb = (unit & 1) * 4;
+  int row_off[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) row_off[j] = ((cb + j) ^ r_lo) << 4;
+  int col_off[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) col_off[j] = (((lane >> 2) ^ j) << 4) + (lane & 3) * 4;
+  const int grp = warp >> 1, chalf = warp & 1;
+
+  for (int it = 0; it < my_count; ++it) {
+    const int s = it % kMxStages;
+    const uint32_t parity = (it / kMxStages) & 1;
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    const int m0 = cm * kMxChunk, k0 = ck * kMxChunk, pp = it & 1;
+    float pre = 0.0f;
+    if constexpr (NORM) {
+      if (it + 1 < my_count) {
+        int ncm, nck;
+        chunk_coords(it + 1, ncm, nck);
+        pre = (tid < kMxChunk) ? __ldg(a.inv_rms + ncm * kMxChunk + tid)
+                               : __bfloat162float(a.gamma[nck * kMxChunk + tid - kMxChunk]);
+      }
+    }
+    if (!mbar_wait_bounded(&sm.full[s], parity)) {
+      if (tid == 0) atomicExch(a.status, kStatusQuantTmaTimeout);
+      return;
+    }
+    uint8_t* tile = sm.in[s];
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      const int r = warp * 16 + rep * 8 + r_lo;
+      uint8_t* rowp = tile + half_off + r * 128;
+      uint32_t w[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(rowp + row_off[j]);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      if constexpr (NORM) {
+        const float inv = sm.inv_rms[pp][r];
+        const float2 inv2 = make_float2(inv, inv);
+        const float2* g2 = reinterpret_cast<const float2*>(&sm.gamma[pp][unit * 32]);
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          float2 t = mul2(make_float2(bf16lo_to_f32(w[q]), bf16hi_to_f32(w[q])), inv2);
+          t = mul2(t, g2[q]);
+          w[q] = f32x2_to_bf16x2(t.x, t.y);
+        }
+        if (want_col) {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(rowp + row_off[j]) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
+      }
+      uint32_t mx = 0;
+#pragma unroll
+      for (int q = 0; q < 16; ++q) mx = absmax_xs(mx, w[q]);
+      const float b = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+      const uint32_t e = mx_e8m0(b, a.mode);
+      const float coeff = mx_coeff(e);
+      uint4 codes;
+      codes.x = quant8(w, coeff); codes.y = quant8(w + 4, coeff);
+      codes.z = quant8(w + 8, coeff); codes.w = quant8(w + 12, coeff);
+      st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1), codes);
+      sm.row_sc[pp][scale_tile_offset(r, unit)] = (uint8_t)e;
+    }
+    __syncthreads();
+    if (want_col) {
+      const uint8_t* base = tile + chalf * kMxHalfBytes + (grp * 32) * 128;
+      uint32_t w[32];
+      uint32_t mx = 0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        w[i] = *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]);
+        mx = absmax_xs(mx, w[i]);
+      }
+      const uint32_t e0 = mx_e8m0(fabsf(bf16lo_to_f32(mx)), a.mode), e1 = mx_e8m0(fabsf(bf16hi_to_f32(mx)), a.mode);
+      const float2 cc = make_float2(mx_coeff(e0), mx_coeff(e1));
+      uint32_t q0[4], q1[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        float2 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          v[i] = mul2(make_float2(bf16lo_to_f32(w[8 * p + i]), bf16hi_to_f32(w[8 * p + i])), cc);
+        q0[p] = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+        q1[p] = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+      }
+      const int c = 2 * lane + 64 * chalf;
+      sm.col_codes[grp][c] = make_uint4(q0[0], q0[1], q0[2], q0[3]);
+      sm.col_codes[grp][c + 1] = make_uint4(q1[0], q1[1], q1[2], q1[3]);
+      sm.col_sc[scale_tile_offset(c, grp)] = (uint8_t)e0;
+      sm.col_sc[scale_tile_offset(c + 1, grp)] = (uint8_t)e1;
+    }
+    if constexpr (NORM) {
+      if (tid < kMxChunk) sm.inv_rms[pp ^ 1][tid] = pre;
+      else sm.gamma[pp ^ 1][tid - kMxChunk] = pre;
+    }
+    __syncthreads();
+    if (tid == 0 && it + kMxStages < my_count) {
+      fence_proxy_async_smem();
+      issue_load(it + kMxStages, s);
+    }
+    if (tid < 128) {
+      uint8_t* dst = a.row_sc + ((size_t)cm * a.chunks_k + ck) * 512;
+      st_cs_u32(dst + tid * 4, *reinterpret_cast<const uint32_t*>(&sm.row_sc[pp][tid * 4]));
+    } else if (want_col) {
+      uint8_t* dst = a.col_sc + ((size_t)ck * a.chunks_m + cm) * 512;
+      const int t = tid - 128;
+      st_cs_u32(dst + t * 4, *reinterpret_cast<const uint32_t*>(&sm.col_sc[t * 4]));
+    }
+    if (want_col) {
+#pragma unroll
+      for (int rep = 0; rep < 2; ++rep) {
+        const int idx = rep * kMxThreads + tid;   // 512 pieces of 16 bytes: column = idx/4, 32-row group = idx%4
+        const int c = idx >> 2, g = idx & 3;
+        st_cs_u4(a.col_fp4 + (size_t)(k0 + c) * (a.M >> 1) + (m0 >> 1) + g * 16, sm.col_codes[g][c]);
+      }
+    }
+  }
+}
+
+static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float* inv_rms, const void* gamma,
+                     void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st) {
+  CUtensorMap tmap;
+  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,
+                            64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  MxArgs a{};
+  a.inv_rms = inv_rms; a.gamma = (const __nv_bfloat16*)gamma;
+  a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc; a.col_fp4 = (uint8_t*)col_fp4; a.col_sc = (uint8_t*)col_sc;
+  a.status = device_status_ptr();
+  if (!a.status) return -1;
+  a.M = (int)M; a.K = (int)K; a.chunks_m = (int)(M / kMxChunk); a.chunks_k = (int)(K / kMxChunk); a.mode = mode;
+  const int smem = (int)sizeof(MxSmem) + 1024;
+  const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
+  if (grid == 0) return 0;
+  if (inv_rms) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_quantize_kernel<true><<<grid, kMxThreads, smem, st>>>(tmap, a);
+  } else {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_quantize_kernel<false><<<grid, kMxThreads, smem, st>>>(tmap, a);
+  }
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace fp4b200
+
+using namespace fp4b200;
+
+static int check_mx(const void* x, int64_t M, int64_t K, int mode, const char* who) {
+  if (!x) return set_error("%s: input pointer is null", who);
+  if (M <= 0 || K <= 0 || (M % 128) || (K % 128))
+    return set_error("%s: M and K must be positive multiples of 128 (got %lld x %lld)", who, (long long)M, (long long)K);
+  if (mode < 0 || mode > 2) return set_error("%s: mode must be 0 (RTE), 1 (ceil) or 2 (floor)", who);
+  if (reinterpret_cast<uintptr_t>(x) & 15) return set_error("%s: input must be 16-byte aligned", who);
+  return 0;
+}
+
+extern "C" {
+
+int fp4b200_mxfp4_quantize(const void* x_bf16, int64_t M, int64_t K, int mode, void* row_fp4, void* row_sc,
+                           void* col_fp4, void* col_sc, void* stream) {
+  if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize")) return rc;
+  if (!row_fp4 || !row_sc) return set_error("mxfp4_quantize: row_fp4 and row_sc are required");
+  if ((col_fp4 == nullptr) != (col_sc == nullptr))
+    return set_error("mxfp4_quantize: col_fp4 and col_sc must both be given or both be null");
+  return launch_mx(x_bf16, M, K, mode, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M,
+                                  int64_t K, int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                  void* stream) {
+  if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize_normed")) return rc;
+  if (!gamma_bf16 || !inv_rms || !row_fp4 || !row_sc)
+    return set_error("mxfp4_quantize_normed: gamma, inv_rms, row_fp4 and row_sc are required");
+  if ((col_fp4 == nullptr) != (col_sc == nullptr))
+    return set_error("mxfp4_quantize_normed: col_fp4 and col_sc must both be given or both be null");
+  return launch_mx(x_bf16, M, K, mode, inv_rms, gamma_bf16, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -64,26 +64,6 @@ __global__ void finalize_sg_kernel(float* __restrict__ amax_sg) { amax_sg[1] = a
 // shuffles over lane masks 16,8.
 constexpr int kStatsThreads = 128;
 
-// {a.x*b.x + c.x, a.y*b.y + c.y}, each a fused multiply-add (same rounding as fmaf)
-__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
-  float2 d;
-  asm("{.reg .b64 x, y, z, w; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mov.b64 z, {%6, %7};"
-      " fma.rn.f32x2 w, x, y, z; mov.b64 {%0, %1}, w;}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
-  return d;
-}
-__device__ __forceinline__ float2 mul2s(float2 a, float2 b) {
-  float2 d;
-  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mul.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-__device__ __forceinline__ uint32_t absmax_xs_s(uint32_t acc, uint32_t v) {
-  uint32_t r;
-  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(v));
-  return r;
-}
-
 template <int NV>
 __device__ __forceinline__ void stats_load_row(uint4 (&v)[NV], const __nv_bfloat16* x, int row, int K, int lane) {
   const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
@@ -145,14 +125,14 @@ __device__ __forceinline__ uint32_t stats_process_row(const uint4 (&v)[NV], cons
     if (q < nvec_row) {
       const float4 g01 = *reinterpret_cast<const float4*>(gamma_s + 4 * q);
       const float4 g23 = *reinterpret_cast<const float4*>(gamma_s + 4 * q + 2);
-      float2 t0 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2), make_float2(g01.x, g01.y));
-      float2 t1 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2), make_float2(g01.z, g01.w));
-      float2 t2 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2), make_float2(g23.x, g23.y));
-      float2 t3 = mul2s(mul2s(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2), make_float2(g23.z, g23.w));
-      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t0.x, t0.y));
-      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t1.x, t1.y));
-      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t2.x, t2.y));
-      mx = absmax_xs_s(mx, f32x2_to_bf16x2(t3.x, t3.y));
+      float2 t0 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2), make_float2(g01.x, g01.y));
+      float2 t1 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2), make_float2(g01.z, g01.w));
+      float2 t2 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2), make_float2(g23.x, g23.y));
+      float2 t3 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2), make_float2(g23.z, g23.w));
+      mx = absmax_xs(mx, f32x2_to_bf16x2(t0.x, t0.y));
+      mx = absmax_xs(mx, f32x2_to_bf16x2(t1.x, t1.y));
+      mx = absmax_xs(mx, f32x2_to_bf16x2(t2.x, t2.y));
+      mx = absmax_xs(mx, f32x2_to_bf16x2(t3.x, t3.y));
     }
   }
   return mx;
@@ -316,21 +296,6 @@ struct QuantArgs {
   int reverse;             // walk chunks from the last row block to the first
 };
 
-// {a.x*b.x, a.y*b.y} in one packed instruction (round-to-nearest, denormals kept)
-__device__ __forceinline__ float2 mul2(float2 a, float2 b) {
-  float2 d;
-  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; mul.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
-      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
-  return d;
-}
-
-// running |.|-max on packed bf16x2; the sign of the result is meaningless
-__device__ __forceinline__ uint32_t absmax_xs(uint32_t acc, uint32_t v) {
-  uint32_t r;
-  asm("max.xorsign.abs.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(acc), "r"(v));
-  return r;
-}
-
 template <bool ENCODE_CENTRIC>
 __device__ __forceinline__ ScaleLut lut_entry(int code, float s_enc) {
   ScaleLut e;
@@ -354,15 +319,6 @@ __device__ __forceinline__ uint32_t block_code(float b, float s_enc) {
   } else {
     return (uint32_t)f32_to_e4m3(fminf(b / 6.0f * s_enc, kFltMax));
   }
-}
-
-__device__ __forceinline__ uint32_t quant8(const uint32_t* w, float coeff) {
-  const float2 cc = make_float2(coeff, coeff);
-  const float2 a = mul2(make_float2(bf16lo_to_f32(w[0]), bf16hi_to_f32(w[0])), cc);
-  const float2 b = mul2(make_float2(bf16lo_to_f32(w[1]), bf16hi_to_f32(w[1])), cc);
-  const float2 c = mul2(make_float2(bf16lo_to_f32(w[2]), bf16hi_to_f32(w[2])), cc);
-  const float2 d = mul2(make_float2(bf16lo_to_f32(w[3]), bf16hi_to_f32(w[3])), cc);
-  return f32x8_to_e2m1x8(a.x, a.y, b.x, b.y, c.x, c.y, d.x, d.y);
 }
 
 template <bool ENCODE_CENTRIC, bool NORM>
@@ -572,7 +528,7 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
 // Host launchers
 // ---------------------------------------------------------------------------------------
 
-static int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st) {
+int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st) {
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
   const size_t n_vec = (size_t)n_elems / 8;
   if (n_vec > 0) {
@@ -598,7 +554,7 @@ static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cud
   return 0;
 }
 
-static int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
+int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
                            cudaStream_t st) {

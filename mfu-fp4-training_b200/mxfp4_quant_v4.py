@@ -1,0 +1,75 @@
+"""Host-side mirror of the reference's ``mxfp4_quant_v4`` extension module (MXFP4 producers).
+
+Names, argument order, defaults and return tuples follow the pybind module at
+fp4_runtime/TK_quantisation/mxfp4_v4/tk_quantize.cu:7281-7724: codes ``[rows, cols/2]`` as
+``float4_e2m1fn_x2``, E8M0 scale bytes ``[rows/128, cols/128, 32, 16]`` as uint8.  ``mode``: 0 RTE,
+1 ceil ("encode", the production setting), 2 floor.  Dense FFN subset only.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+from .tk_quant_v5 import _check_bf16_2d, _same_shape_bf16, _stream
+
+_FP4 = torch.float4_e2m1fn_x2
+
+
+def _alloc(M, K, device, want_col):
+    u8 = dict(dtype=torch.uint8, device=device)
+    row_fp4 = torch.empty((M, K // 2), **u8)
+    row_sc = torch.empty((M // 128, K // 128, 32, 16), **u8)
+    if not want_col:
+        return row_fp4, row_sc, None, None
+    return row_fp4, row_sc, torch.empty((K, M // 2), **u8), torch.empty((K // 128, M // 128, 32, 16), **u8)
+
+
+def _quant(x, mode, want_col):
+    M, K = _check_bf16_2d(x, "input")
+    with torch.cuda.device(x.device):
+        rf, rs, cf, cs = _alloc(M, K, x.device, want_col)
+        _lib.call("fp4b200_mxfp4_quantize", x.data_ptr(), M, K, int(mode), rf.data_ptr(), rs.data_ptr(),
+                  None if cf is None else cf.data_ptr(), None if cs is None else cs.data_ptr(), _stream(x))
+    return rf, rs, cf, cs
+
+
+def mxfp4_quantize_for_gemm(input, mode=0):
+    """tk_quantize.cu:7282 — (fp4, scales), row-wise only."""
+    rf, rs, _, _ = _quant(input, mode, False)
+    return rf.view(_FP4), rs
+
+
+def mxfp4_quantize_row_and_col(input, mode=0):
+    """tk_quantize.cu:7344 — (row_fp4, row_sc, col_fp4, col_sc)."""
+    rf, rs, cf, cs = _quant(input, mode, True)
+    return rf.view(_FP4), rs, cf.view(_FP4), cs
+
+
+def mxfp4_fused_rmsnorm_quantize_row_and_col(input, norm_weight, epsilon, mode=0):
+    """tk_quantize.cu:7701 — (row_fp4, row_sc, col_fp4, col_sc, inv_rms)."""
+    M, K = _check_bf16_2d(input, "input")
+    if (not isinstance(norm_weight, torch.Tensor) or norm_weight.dtype != torch.bfloat16 or norm_weight.numel() != K
+            or not norm_weight.is_contiguous() or norm_weight.device != input.device):
+        raise RuntimeError("norm_weight must be contiguous CUDA bfloat16 [K] on the input device")
+    with torch.cuda.device(input.device):
+        rf, rs, cf, cs = _alloc(M, K, input.device, True)
+        inv_rms = torch.empty(M, dtype=torch.float32, device=input.device)
+        amax_sg = torch.empty(2, dtype=torch.float32, device=input.device)
+        st = _stream(input)
+        _lib.call("fp4b200_nvfp4_rmsnorm_stats", input.data_ptr(), norm_weight.data_ptr(), float(epsilon), M, K,
+                  inv_rms.data_ptr(), 1, amax_sg.data_ptr(), st)
+        _lib.call("fp4b200_mxfp4_quantize_normed", input.data_ptr(), norm_weight.data_ptr(), inv_rms.data_ptr(), M, K,
+                  int(mode), rf.data_ptr(), rs.data_ptr(), cf.data_ptr(), cs.data_ptr(), st)
+    return rf.view(_FP4), rs, cf.view(_FP4), cs, inv_rms
+
+
+def mxfp4_fused_silu_mul_quantize_row_and_col(h1_raw, h3, mode=0):
+    """tk_quantize.cu:7435 — (row_fp4, row_sc, col_fp4, col_sc) of ``bf16(silu(h1_raw) * h3)``."""
+    M, H = _check_bf16_2d(h1_raw, "h1_raw")
+    _same_shape_bf16(h1_raw, h3)
+    with torch.cuda.device(h1_raw.device):
+        h = torch.empty_like(h1_raw)
+        amax_sg = torch.empty(2, dtype=torch.float32, device=h1_raw.device)
+        _lib.call("fp4b200_silu_mul_bf16", h1_raw.data_ptr(), h3.data_ptr(), h1_raw.numel(), h.data_ptr(),
+                  amax_sg.data_ptr(), _stream(h1_raw))
+    return mxfp4_quantize_row_and_col(h, mode)

@@ -128,8 +128,10 @@ def e2m1_encode_rn(v: np.ndarray) -> np.ndarray:
     idx = np.where(a > 2.5, 5, idx)
     idx = np.where(a >= 3.5, 6, idx)
     idx = np.where(a > 5.0, 7, idx)
-    idx = np.where(np.isnan(v), 7, idx)
-    return (idx.astype(np.uint8) | (np.signbit(v).astype(np.uint8) << 3)).astype(np.uint8)
+    code = (idx.astype(np.uint8) | (np.signbit(v).astype(np.uint8) << 3)).astype(np.uint8)
+    # NaN (e.g. 0 * inf from an overflowed coefficient) converts to +6: the GPU produces the
+    # canonical positive NaN and satfinite maps NaN to the positive maximum
+    return np.where(np.isnan(v), np.uint8(7), code).astype(np.uint8)
 
 
 def pack_fp4(codes: np.ndarray) -> np.ndarray:
