@@ -70,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20",
                  "-i", str(self.index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
@@ -165,17 +165,109 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5):
+    """Llama-3-8B FFN forward in NVFP4 at M=16384 per rank (config 3): fused RMSNorm+quant, grouped
+    gate/up GEMM (N=28672, K=4096), SwiGLU producer, down GEMM (N=4096, K=14336).  Weights are
+    quantised once outside the timed region.  Returns per-kernel and whole-step figures."""
+    tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
+    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    H, K, M = 14336, K_COLS, M_ROWS
+    dev = x_dev.device
+    g = torch.Generator(device="cpu").manual_seed(7)
+    def weight(n, k):
+        return (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(dev)
+    q1, q3, q2 = (tkq.tk_quantize_for_gemm(weight(H, K), False, True), tkq.tk_quantize_for_gemm(weight(H, K), False, True),
+                  tkq.tk_quantize_for_gemm(weight(K, H), False, True))
+    b13 = torch.cat([q1[0].view(torch.uint8), q3[0].view(torch.uint8)], 0)
+    b13_sc = torch.cat([q1[1].view(torch.uint8), q3[1].view(torch.uint8)], 0)
+    b13_sg = torch.cat([q1[4].expand(H // 256), q3[4].expand(H // 256)]).contiguous()
+    h1 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    h3 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    names = ["rmsnorm_quant", "gate_up_gemm", "swiglu_quant", "down_gemm"]
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(iters)]
+    for i in range(2 + iters):
+        rec = (lambda j: ev[i - 2][j].record()) if i >= 2 else (lambda j: None)
+        rec(0)
+        qx = tkq.tk_fused_norm_quantize(x_dev, gamma, EPS, False, True)
+        rec(1)
+        gemm.nvfp4_grouped_gemm(qx[0], qx[1], qx[4], b13, b13_sc, b13_sg, h1, h3)
+        rec(2)
+        qh = tkq.tk_silu_quantize_split_for_gemm(h1, h3)
+        rec(3)
+        gemm.nvfp4_gemm(qh[0], qh[1], qh[4], q2[0], q2[1], q2[4], y)
+        rec(4)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ms = [statistics.mean(e[j].elapsed_time(e[j + 1]) for e in ev) for j in range(4)]
+    total = statistics.mean(e[0].elapsed_time(e[4]) for e in ev)
+    t = torch.tensor(ms + [total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, total = t[:4].tolist(), t[4].item()
+    fl_up, fl_down = 2.0 * M * 2 * H * K, 2.0 * M * K * H
+    fp4_nominal = 9000.0
+    fp4_box = 4.0 * peaks["bf16_tflops"]
+    out = {"workload": "config3: Llama-3-8B FFN forward in NVFP4, M=16384 tokens per GPU", "ms": dict(zip(names, ms)),
+           "step_ms": total,
+           "gate_up_gemm_tflops": fl_up * world / (ms[1] * 1e-3) / 1e12,
+           "down_gemm_tflops": fl_down * world / (ms[3] * 1e-3) / 1e12,
+           "step_tflops": (fl_up + fl_down) * world / (total * 1e-3) / 1e12,
+           "swiglu_quant_gbs": M * H * 5.125 * world / (ms[2] * 1e-3) / 1e9,
+           "roofline": {"bound": "tensor", "kernel": "fp4_gemm_kernel<nvfp4> (gate/up, N=28672 K=4096)",
+                        "achieved": fl_up / (ms[1] * 1e-3) / 1e12, "unit": "TFLOP/s",
+                        "peak": fp4_nominal, "frac": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_nominal,
+                        "peak_kind": "nominal dense FP4 (no measured FP4 peak exists)",
+                        "frac_of_4x_measured_bf16": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_box, "traffic": None}}
+    return out
+
+
+def gemm_only(args):
+    """Times fp4b200_nvfp4_gemm alone at one shape on cuda:0 (random codes and scales)."""
+    import torch
+    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    lib = importlib.import_module("mfu-fp4-training_b200._lib")
+    M, N, K = (int(v) for v in args.gemm_only.lower().split("x"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev, generator=g)
+    b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
+    a_sc = torch.randint(40, 64, (M // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g)
+    b_sc = torch.randint(40, 64, (N // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g)
+    sg = torch.full((1,), 1e-3, dtype=torch.float32, device=dev)
+    d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    for _ in range(args.warmup):
+        gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(args.steps):
+        gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / args.steps
+    print(json.dumps({"gemm_only": args.gemm_only, "ms": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12,
+                      "status": lib.device_status()}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--quick", action="store_true",
                     help="timed loop only (no per-kernel, end-to-end or CPU legs): the command ncu captures")
+    ap.add_argument("--gemm-only", default=None, metavar="MxNxK",
+                    help="time only the NVFP4 GEMM at this shape (tuning / ncu capture helper)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.gemm_only:
+        gemm_only(args)
+        return
 
     if args.impl == "reference":
         run_reference(args)
@@ -226,7 +318,6 @@ def main():
     e1.record()
     barrier()
     ms = e0.elapsed_time(e1)
-    clocks = sampler.stop() if rank == 0 else None
     t = torch.tensor([ms], device="cuda")
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -241,6 +332,7 @@ def main():
         if rank == 0:
             print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps,
                               "warmup": args.warmup, "ms_per_step": ms_per_step, "quick": True}), flush=True)
+            sampler.stop()
         if world > 1:
             dist.destroy_process_group()
         return
@@ -319,6 +411,10 @@ def main():
     e2e = {"value": alg * world / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
            "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e}
 
+    del outs_host
+    ffn = ffn_forward_leg(torch, dist, world, local_rank, xs[0], gamma, peaks)
+    clocks = sampler.stop() if rank == 0 else None
+
     if rank == 0:
         cpu = None
         if world == 1 and not args.no_cpu_baseline:
@@ -330,7 +426,7 @@ def main():
                            "l2": "inputs rotate over 3 copies of X (402 MB > 126 MB L2) between steps",
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * args.steps, "roofline": roofline,
-                "cpu_baseline": cpu}
+                "cpu_baseline": cpu, "ffn_forward": ffn}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -14,20 +14,23 @@
 // One persistent CTA per SM works through 128 x 256 output tiles.  Warp roles:
 //   warp 0      TMA producer: per 256-deep K stage one A box (128 rows x 128 B), one B box
 //               (256 rows x 128 B), both 128-byte swizzled, and three bulk copies of scale tiles
-//   warp 1      owns tensor memory; one lane issues tcgen05.cp (scales -> TMEM) and tcgen05.mma
+//   warp 1      owns tensor memory; one lane issues tcgen05.mma
 //   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, (residual), convert, store
+//   warps 6..9  scale movers: shared memory -> registers -> tcgen05.st into this quadrant's scale columns
 // Every wait on an mbarrier is bounded in time; a wait that runs out records a status code,
 // and the CTA drains to the common exit where tensor memory is released.
 #include "fp4_common.cuh"
 #include "host_util.h"
+
+#include <string.h>
 
 namespace fp4b200 {
 
 constexpr int kGemmBM = 128;
 constexpr int kGemmBN = 256;
 constexpr int kGemmBKBytes = 128;                  // 256 FP4 elements per stage
-constexpr int kGemmStages = 4;
-constexpr int kGemmThreads = 192;
+constexpr int kGemmStages = 3;
+constexpr int kGemmThreads = 320;
 constexpr int kATileBytes = kGemmBM * kGemmBKBytes;   // 16 KiB
 constexpr int kBTileBytes = kGemmBN * kGemmBKBytes;   // 32 KiB
 constexpr int kASfBytes = 2048;                    // 4 scale tiles of 512 B (one per K=64 step)
@@ -40,10 +43,12 @@ constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at boost clock
 struct GemmSmem {
   alignas(1024) uint8_t a[kGemmStages][kATileBytes];
   alignas(1024) uint8_t b[kGemmStages][kBTileBytes];
+  alignas(1024) uint8_t epi[4][2][4096];             // per epilogue warp: two slabs of 32 rows x 128 B
   alignas(128) uint8_t sfa[kGemmStages][kASfBytes];
   alignas(128) uint8_t sfb[kGemmStages][kBSfBytes];
   alignas(8) uint64_t full[kGemmStages];
   alignas(8) uint64_t empty[kGemmStages];
+  alignas(8) uint64_t sf_ready[kGemmStages];
   alignas(8) uint64_t acc_full;
   alignas(8) uint64_t acc_empty;
   uint32_t tmem_base;
@@ -145,10 +150,41 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// registers -> 32 lanes x 16 / 32 columns of tensor memory (this warp's lane quadrant)
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+        "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+        "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+
+struct GemmOutMaps {
+  CUtensorMap m[3];
+};
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+
 template <bool MX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                const GemmArgs g) {
+                const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
   extern __shared__ uint8_t smem_raw[];
   GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
 
@@ -159,7 +195,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   const int k_stages = g.K / (2 * kGemmBKBytes);     // stages of 256 elements
 
   if (tid == 0) {
-    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
+    for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); mbar_init(&sm.sf_ready[s], 4); }
     mbar_init(&sm.acc_full, 1);
     mbar_init(&sm.acc_empty, 4);   // one arrival per epilogue warp
     sm.abort_flag = 0;
@@ -230,36 +266,23 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             break;
           }
           tc_fence_after();
-          const uint32_t sf_cols = tmem + kSfTmemBase + (stage & 1) * kSfSlotCols;
+          if (!mbar_wait_timed(&sm.sf_ready[stage], phase)) {   // scales of this stage are in tensor memory
+            atomicExch(g.status, kStatusGemmMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sf_cols = tmem + kSfTmemBase + stage * kSfSlotCols;
           const uint32_t a_base = smem_u32(sm.a[stage]);
           const uint32_t b_base = smem_u32(sm.b[stage]);
-          const uint32_t sfa_base = smem_u32(sm.sfa[stage]);
-          const uint32_t sfb_base = smem_u32(sm.sfb[stage]);
-          if constexpr (!MX) {
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {   // one 512-byte scale tile per K=64 step
-              tc_copy_sf(sf_cols + j * 4, sfa_base + j * 512);
-              tc_copy_sf(sf_cols + 16 + j * 8, sfb_base + j * 512);
-              tc_copy_sf(sf_cols + 16 + j * 8 + 4, sfb_base + 2048 + j * 512);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
-              const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+          for (int j = 0; j < 4; ++j) {
+            const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
+            const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+            if constexpr (!MX) {
               tc_mma<false>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 0, 0), sf_cols + j * 4,
                             sf_cols + 16 + j * 8, (ks | j) != 0);
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 2; ++j) {   // one 512-byte scale tile per K=128 (two K=64 steps)
-              tc_copy_sf(sf_cols + j * 4, sfa_base + j * 512);
-              tc_copy_sf(sf_cols + 16 + j * 8, sfb_base + j * 512);
-              tc_copy_sf(sf_cols + 16 + j * 8 + 4, sfb_base + 1024 + j * 512);
-            }
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
-              const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+            } else {
               const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
               tc_mma<true>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 1, sf_id),
                            sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
@@ -270,6 +293,50 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         if (ok) tc_commit(&sm.acc_full);
         acc_phase ^= 1;
+      }
+    }
+  } else if (warp >= 6) {
+    // ------------------------------ scale movers ------------------------------------------
+    // Four warps, one per tensor-memory lane quadrant, move each stage's scale tiles from shared
+    // memory into tensor memory through registers (tcgen05.st), which keeps the tensor pipe free
+    // for MMAs (a tcgen05.cp per 512-byte tile would serialise with them).  Every quadrant gets
+    // the same 16 bytes per lane: row l of a tile, i.e. the scales of tile rows l, 32+l, 64+l, 96+l.
+    const int quad = warp & 3;
+    int stage = 0;
+    uint32_t phase = 0;
+    bool ok = true;
+    constexpr int kTiles = MX ? 2 : 4;            // scale tiles per 128-row group per stage
+    for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+      for (int ks = 0; ks < k_stages; ++ks) {
+        if (!mbar_wait_timed(&sm.full[stage], phase)) {
+          if (lane == 0) atomicExch(g.status, kStatusGemmMmaTimeout);
+          ok = false;
+          break;
+        }
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + kSfTmemBase + stage * kSfSlotCols;
+        uint32_t ra[16], rb[32];
+#pragma unroll
+        for (int j = 0; j < kTiles; ++j) {
+          const uint4 va = *reinterpret_cast<const uint4*>(&sm.sfa[stage][j * 512 + lane * 16]);
+          ra[4 * j] = va.x; ra[4 * j + 1] = va.y; ra[4 * j + 2] = va.z; ra[4 * j + 3] = va.w;
+          const uint4 v0 = *reinterpret_cast<const uint4*>(&sm.sfb[stage][j * 512 + lane * 16]);
+          const uint4 v1 = *reinterpret_cast<const uint4*>(&sm.sfb[stage][kTiles * 512 + j * 512 + lane * 16]);
+          rb[8 * j] = v0.x; rb[8 * j + 1] = v0.y; rb[8 * j + 2] = v0.z; rb[8 * j + 3] = v0.w;
+          rb[8 * j + 4] = v1.x; rb[8 * j + 5] = v1.y; rb[8 * j + 6] = v1.z; rb[8 * j + 7] = v1.w;
+        }
+#pragma unroll
+        for (int j = kTiles; j < 4; ++j) {
+          ra[4 * j] = ra[4 * j + 1] = ra[4 * j + 2] = ra[4 * j + 3] = 0;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) rb[8 * j + e] = 0;
+        }
+        tmem_st16(taddr, ra);
+        tmem_st32(taddr + 16, rb);
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.sf_ready[stage]);
+        if (++stage == kGemmStages) { stage = 0; phase ^= 1; }
       }
     }
   } else {
@@ -288,7 +355,6 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       // which output receives this column tile
       int oi = 0, col_start = 0;
       while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
-      const int ld = g.d_ld[oi];
       const int ocol = col0 - col_start;
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
@@ -296,21 +362,31 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         break;
       }
       tc_fence_after();
+      // 32 columns per tensor-memory load; a slab of 128 bytes per row (64 bf16 or 32 fp32 columns) is
+      // staged in the 128-byte-swizzled layout and written with one TMA store per slab
+      const int chunks_per_slab = g.out_fp32 ? 1 : 2;
 #pragma unroll 1
       for (int c = 0; c < kGemmBN; c += 32) {
+        const int chunk = c >> 5;
+        const int slab = chunk / chunks_per_slab;
+        uint8_t* buf = sm.epi[warp - 2][slab & 1];
         uint32_t r[32];
         tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+        if ((chunk % chunks_per_slab) == 0) {
+          // the store issued from this buffer two slabs ago must have finished reading it
+          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+          __syncwarp();
+        }
         tmem_ld_wait();
+        uint8_t* rowp = buf + lane * 128;
         if (g.out_fp32) {
-          float* dst = reinterpret_cast<float*>(g.d[oi]) + (size_t)row * ld + ocol + c;
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            float4 v = make_float4(__uint_as_float(r[4 * q]) * gs, __uint_as_float(r[4 * q + 1]) * gs,
-                                   __uint_as_float(r[4 * q + 2]) * gs, __uint_as_float(r[4 * q + 3]) * gs);
-            *reinterpret_cast<float4*>(dst + 4 * q) = v;
+            const float4 v = make_float4(__uint_as_float(r[4 * q]) * gs, __uint_as_float(r[4 * q + 1]) * gs,
+                                         __uint_as_float(r[4 * q + 2]) * gs, __uint_as_float(r[4 * q + 3]) * gs);
+            *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) = v;
           }
         } else {
-          __nv_bfloat16* dst = reinterpret_cast<__nv_bfloat16*>(g.d[oi]) + (size_t)row * ld + ocol + c;
           uint32_t o[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q)
@@ -329,9 +405,20 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
               }
             }
           }
+          const int piece0 = (chunk & 1) * 4;
 #pragma unroll
           for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+            *reinterpret_cast<uint4*>(rowp + (((piece0 + q) ^ (lane & 7)) << 4)) =
+                make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+        }
+        if ((chunk % chunks_per_slab) == chunks_per_slab - 1) {
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            const int slab_cols = g.out_fp32 ? 32 : 64;
+            tma_store_2d(&tmap_d.m[oi], buf, ocol + slab * slab_cols, tm * kGemmBM + quad * 32);
+            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+          }
         }
       }
       // accumulator drained: let the MMA warp start the next tile
@@ -340,6 +427,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       if (lane == 0) mbar_arrive(&sm.acc_empty);
       acc_phase ^= 1;
     }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staged stores have left shared memory
   }
 
   // common exit: every role arrives here (also after a timeout); release tensor memory
@@ -362,6 +450,15 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   if (int rc = make_tmap_2d(&tmap_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)N,
                             (uint64_t)K / 2, kGemmBKBytes, kGemmBN, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
+  GemmOutMaps omaps;
+  memset(&omaps, 0, sizeof(omaps));
+  for (int i = 0; i < n_out; ++i) {
+    const uint64_t cols = (uint64_t)d_ld[i];
+    if (int rc = make_tmap_2d(&omaps.m[i], D[i], out_fp32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16,
+                              out_fp32 ? 4 : 2, cols, (uint64_t)M, cols * (out_fp32 ? 4 : 2), out_fp32 ? 32 : 64, 32,
+                              CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  }
   GemmArgs g{};
   g.a_sc = (const uint8_t*)A_sc; g.b_sc = (const uint8_t*)B_sc;
   g.a_sg = A_sg; g.b_sg = B_sg; g.b_sg_per_tile = b_sg_per_tile;
@@ -379,10 +476,10 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   if (grid == 0) return 0;
   if (mx) {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    fp4_gemm_kernel<true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, g);
+    fp4_gemm_kernel<true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
   } else {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    fp4_gemm_kernel<false><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, g);
+    fp4_gemm_kernel<false><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
   }
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
