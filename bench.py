@@ -176,11 +176,39 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
     g = torch.Generator(device="cpu").manual_seed(7)
     def weight(n, k):
         return (0.02 * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(dev)
-    q1, q3, q2 = (tkq.tk_quantize_for_gemm(weight(H, K), False, True), tkq.tk_quantize_for_gemm(weight(H, K), False, True),
-                  tkq.tk_quantize_for_gemm(weight(K, H), False, True))
-    b13 = torch.cat([q1[0].view(torch.uint8), q3[0].view(torch.uint8)], 0)
-    b13_sc = torch.cat([q1[1].view(torch.uint8), q3[1].view(torch.uint8)], 0)
-    b13_sg = torch.cat([q1[4].expand(H // 256), q3[4].expand(H // 256)]).contiguous()
+    gather = None
+    if world == 1:
+        q1, q3, q2 = (tkq.tk_quantize_for_gemm(weight(H, K), False, True),
+                      tkq.tk_quantize_for_gemm(weight(H, K), False, True),
+                      tkq.tk_quantize_for_gemm(weight(K, H), False, True))
+        ops = [(q[0].view(torch.uint8), q[1].view(torch.uint8), q[4]) for q in (q1, q3, q2)]
+    else:
+        # weights are FSDP-sharded along their rows; every rank quantises its shard and the ranks
+        # all-gather packed codes + scale tiles (plus one float amax all-reduce per weight)
+        fsdp = importlib.import_module("mfu-fp4-training_b200.fsdp_weights")
+        rank = dist.get_rank()
+        shards = []
+        for n, k in ((H, K), (H, K), (K, H)):
+            w = weight(n, k)
+            shards.append(w[rank * n // world:(rank + 1) * n // world].contiguous())
+            del w
+        ops = []
+        g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        for rep in range(3):
+            if rep == 2:
+                dist.barrier(); torch.cuda.synchronize(); g0.record()
+            ops = [fsdp.all_gather_nvfp4_weight(sh, None, False, True) for sh in shards]
+        g1.record(); torch.cuda.synchronize()
+        ag = torch.tensor([g0.elapsed_time(g1)], device=dev)
+        dist.all_reduce(ag, op=dist.ReduceOp.MAX)
+        nbytes = sum(fsdp.gathered_bytes(n, k, "nvfp4", False) for n, k in ((H, K), (H, K), (K, H)))
+        gather = {"ms": ag.item(), "bytes_received_per_rank": nbytes, "bf16_equivalent_bytes": 3 * H * K * 2,
+                  "note": "quantise own shard + amax all-reduce + all-gather of row-wise codes and scale tiles, 3 FFN weights"}
+        ops = [(o_[0], o_[1], o_[4]) for o_ in ops]
+    (w1c, w1s, w1g), (w3c, w3s, w3g), (w2c, w2s, w2g) = ops
+    b13 = torch.cat([w1c, w3c], 0)
+    b13_sc = torch.cat([w1s, w3s], 0)
+    b13_sg = torch.cat([w1g.expand(H // 256), w3g.expand(H // 256)]).contiguous()
     h1 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     h3 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     y = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
@@ -195,7 +223,7 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
         rec(2)
         qh = tkq.tk_silu_quantize_split_for_gemm(h1, h3)
         rec(3)
-        gemm.nvfp4_gemm(qh[0], qh[1], qh[4], q2[0], q2[1], q2[4], y)
+        gemm.nvfp4_gemm(qh[0], qh[1], qh[4], w2c, w2s, w2g, y)
         rec(4)
     if world > 1:
         dist.barrier()
@@ -220,6 +248,8 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
                         "peak": fp4_nominal, "frac": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_nominal,
                         "peak_kind": "nominal dense FP4 (no measured FP4 peak exists)",
                         "frac_of_4x_measured_bf16": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_box, "traffic": None}}
+    if gather is not None:
+        out["weight_all_gather"] = gather
     return out
 
 

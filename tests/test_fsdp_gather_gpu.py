@@ -1,0 +1,61 @@
+"""GPU, two ranks over NCCL (skipped on a single-GPU box): the packed-weight all-gather through the
+CUDA quantiser equals quantising the full weight locally, byte for byte, on every rank."""
+import importlib
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, q):
+    import torch.distributed as dist
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        fsdp = importlib.import_module("mfu-fp4-training_b200.fsdp_weights")
+        tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
+        mxq = importlib.import_module("mfu-fp4-training_b200.mxfp4_quant_v4")
+        N, K = 1024, 512
+        g = torch.Generator().manual_seed(3)
+        w = (0.02 * torch.randn(N, K, generator=g)).to(torch.bfloat16)
+        w[700, 3] = 0.75
+        wd = w.cuda()
+        shard = wd[rank * N // world:(rank + 1) * N // world].contiguous()
+        out = fsdp.all_gather_nvfp4_weight(shard, None, True, True)
+        ref = tkq.tk_quantize_for_gemm(wd, True, True)
+        ok = all(torch.equal(out[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
+        ok = ok and out[4].item() == ref[4].item()
+        out = fsdp.all_gather_mxfp4_weight(shard, None, True, 1)
+        ref = mxq.mxfp4_quantize_row_and_col(wd, 1)
+        ok = ok and all(torch.equal(out[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
+        torch.cuda.synchronize()
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.timeout(300)
+def test_packed_weight_all_gather_two_gpus():
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    procs = [ctx.Process(target=_worker, args=(r, 2, port, q)) for r in range(2)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=240) for _ in range(2)]
+    for p in procs:
+        p.join(30)
+    assert all(r[1] for r in res)
