@@ -60,6 +60,12 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
                                     int encode_centric, void* row_fp4, void* row_sc, void* col_fp4,
                                     void* col_sc, float* amax_sg, void* stream);
 
+/* tk_quantize_weight_2d(input) (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:2445-2555): one
+ * decode-centric scale per 16x16 tile shared by both orientations, so that the column-wise codes
+ * are the exact transpose of the row-wise codes. */
+int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
+                                     void* col_fp4, void* col_sc, float* amax_sg, void* stream);
+
 /* RMSNorm statistics: inv_rms[M] = rsqrt(mean(x^2)+eps) (computed when compute_inv_rms != 0,
  * else read) and amax of bf16(x*inv_rms*gamma).
  * Replaces rmsnorm_bf16_amax_kernel (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:1025-1111). */

@@ -39,9 +39,10 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 // amax_sg[0] = max|x|, amax_sg[1] = amax/2688 (cleared and recomputed on the stream).
 int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st);
 // Row (+ column when col_* non-null) NVFP4 quantisation from device-resident amaxes; RMSNorm is
-// applied on the fly when inv_rms/gamma are given; reverse walks the chunks back to front.
+// applied on the fly when inv_rms/gamma are given; reverse walks the chunks back to front;
+// weight_2d shares one scale per 16x16 tile between the two orientations (decode-centric).
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                     bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4, void* row_sc,
-                    void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st);
+                    void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st, bool weight_2d = false);
 
 }  // namespace fp4b200

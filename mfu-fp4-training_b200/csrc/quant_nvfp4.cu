@@ -275,6 +275,7 @@ struct QuantSmem {
   alignas(16) uint8_t col_sc[1024];
   alignas(16) float inv_rms[2][kChunk];
   alignas(16) float gamma[2][kChunk];
+  alignas(16) float tile_amax[8][8];        // W2D: amax of each 16x16 tile of the chunk
   alignas(8) ScaleLut lut_row[128];
   alignas(8) ScaleLut lut_col[128];
   alignas(8) uint64_t full[kQStages];
@@ -321,7 +322,7 @@ __device__ __forceinline__ uint32_t block_code(float b, float s_enc) {
   }
 }
 
-template <bool ENCODE_CENTRIC, bool NORM>
+template <bool ENCODE_CENTRIC, bool NORM, bool W2D>
 __global__ void __launch_bounds__(kQThreads, 2)
 nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -412,6 +413,25 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     }
     uint8_t* tile = sm.in[s];
 
+    if constexpr (W2D) {
+      // 16x16-tile amaxes (one scale shared by both orientations): column-pass geometry, then a
+      // max over the 8 lanes that hold one 16-column block
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const uint8_t* base = tile + h * kHalfBytes + (warp * 16) * 128;
+        uint32_t mx = 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          mx = absmax_xs(mx, *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]));
+        float b = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 1));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 2));
+        b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 4));
+        if ((lane & 7) == 0) sm.tile_amax[warp][h * 4 + (lane >> 3)] = b;
+      }
+      __syncthreads();
+    }
+
     // ---- row pass ---------------------------------------------------------------------
 #pragma unroll
     for (int rep = 0; rep < 2; ++rep) {
@@ -442,8 +462,12 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
       uint32_t mx0 = 0, mx1 = 0;
 #pragma unroll
       for (int q = 0; q < 8; ++q) { mx0 = absmax_xs(mx0, w[q]); mx1 = absmax_xs(mx1, w[8 + q]); }
-      const float b0 = fmaxf(fabsf(bf16lo_to_f32(mx0)), fabsf(bf16hi_to_f32(mx0)));
-      const float b1 = fmaxf(fabsf(bf16lo_to_f32(mx1)), fabsf(bf16hi_to_f32(mx1)));
+      float b0 = fmaxf(fabsf(bf16lo_to_f32(mx0)), fabsf(bf16hi_to_f32(mx0)));
+      float b1 = fmaxf(fabsf(bf16lo_to_f32(mx1)), fabsf(bf16hi_to_f32(mx1)));
+      if constexpr (W2D) {
+        b0 = sm.tile_amax[r >> 4][unit * 2];
+        b1 = sm.tile_amax[r >> 4][unit * 2 + 1];
+      }
       const ScaleLut e0 = sm.lut_row[block_code<ENCODE_CENTRIC>(b0, s_enc_row)];
       const ScaleLut e1 = sm.lut_row[block_code<ENCODE_CENTRIC>(b1, s_enc_row)];
       uint4 codes;
@@ -470,7 +494,8 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
           w[i] = *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]);
           mx = absmax_xs(mx, w[i]);
         }
-        const float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
+        float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
+        if constexpr (W2D) b0 = b1 = sm.tile_amax[warp][h * 4 + (lane >> 3)];
         const ScaleLut e0 = sm.lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
         const ScaleLut e1 = sm.lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
         const float2 cc = make_float2(e0.coeff, e1.coeff);
@@ -541,9 +566,9 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st)
   return 0;
 }
 
-template <bool EC, bool NORM>
+template <bool EC, bool NORM, bool W2D = false>
 static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cudaStream_t st) {
-  auto kern = nvfp4_quantize_kernel<EC, NORM>;
+  auto kern = nvfp4_quantize_kernel<EC, NORM, W2D>;
   const int smem = (int)sizeof(QuantSmem) + 1024;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_chunks = args.chunks_m * args.chunks_k;
@@ -557,7 +582,7 @@ static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cud
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
-                           cudaStream_t st) {
+                           cudaStream_t st, bool weight_2d) {
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                             (uint64_t)K * 2, 64, kChunk, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -576,6 +601,7 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.chunks_m = (int)(M / kChunk); a.chunks_k = (int)(K / kChunk);
   a.reverse = reverse ? 1 : 0;
   const bool norm = inv_rms != nullptr;
+  if (weight_2d) return launch_quantize_t<false, false, true>(tmap, a, st);   // decode-centric, as the reference
   if (encode_centric) return norm ? launch_quantize_t<true, true>(tmap, a, st) : launch_quantize_t<true, false>(tmap, a, st);
   return norm ? launch_quantize_t<false, true>(tmap, a, st) : launch_quantize_t<false, false>(tmap, a, st);
 }
@@ -652,6 +678,16 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
   return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
                          return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr,
                          true, (cudaStream_t)stream);
+}
+
+int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
+                                     void* col_fp4, void* col_sc, float* amax_sg, void* stream) {
+  if (int rc = check_quant_shapes(w_bf16, N, K, "nvfp4_quantize_weight_2d")) return rc;
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc || !amax_sg)
+    return set_error("nvfp4_quantize_weight_2d: all outputs are required");
+  if (int rc = launch_amax(w_bf16, N * K, amax_sg, (cudaStream_t)stream)) return rc;
+  return launch_quantize(w_bf16, N, K, amax_sg, amax_sg, false, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc,
+                         nullptr, true, (cudaStream_t)stream, true);
 }
 
 int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,

@@ -66,6 +66,19 @@ def tk_quantize_for_gemm(input, return_transpose, encode_centric=True):
             col_sc.view(_E4M3) if return_transpose else col_sc, sg, sg, amax_sg, sync_buf)
 
 
+def tk_quantize_weight_2d(input):
+    """tk_quantize.cu:2445-2555 — 16x16-tile weight quantisation, returns
+    (row_fp4, row_sc, col_fp4, col_sc, sg, sg)."""
+    N, K = _check_bf16_2d(input, "input")
+    with torch.cuda.device(input.device):
+        row_fp4, row_sc, col_fp4, col_sc = _alloc_operands(N, K, input.device, True)
+        amax_sg = torch.empty(2, dtype=torch.float32, device=input.device)
+        _lib.call("fp4b200_nvfp4_quantize_weight_2d", input.data_ptr(), N, K, row_fp4.data_ptr(), row_sc.data_ptr(),
+                  col_fp4.data_ptr(), col_sc.data_ptr(), amax_sg.data_ptr(), _stream(input))
+    sg = amax_sg.narrow(0, 1, 1)
+    return row_fp4.view(_FP4), row_sc.view(_E4M3), col_fp4.view(_FP4), col_sc.view(_E4M3), sg, sg
+
+
 def _fused_norm_impl(input, gamma, eps, with_silu, return_transpose, inv_rms):
     M, K = _check_bf16_2d(input, "input")
     if with_silu:

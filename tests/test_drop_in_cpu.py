@@ -1,0 +1,35 @@
+"""CPU: the drop-in tree — four extension modules at the paths and names the reference looks up
+under FP4_MATMUL_ROOT — loads the way the reference loads it (by file path) and exposes the symbols
+the reference dereferences (tk_gemm.py:3454-3461, tools/check_fp4_runtime_abi.py:16-47)."""
+import importlib
+import importlib.util
+import os
+
+import pytest
+
+REQUIRED = {
+    "_tk_quant_v5": ["tk_quantize_for_gemm", "tk_quantize_weight_2d", "tk_fused_norm_quantize",
+                     "tk_fused_norm_quantize_from_inv_rms", "tk_silu_quantize_split_for_gemm",
+                     "tk_silu_deriv_quantize_split_for_gemm", "tk_silu_deriv_quantize_split_for_gemm_opt"],
+    "_C": ["nvfp4_gemm", "nvfp4_gemm_config", "nvfp4_gemm_nopdl", "nvfp4_grouped_gemm", "nvfp4_gemm_residual",
+           "nvfp4_batched_gemm"],
+    "mxfp4_quant_v4": ["mxfp4_quantize_for_gemm", "mxfp4_quantize_row_and_col",
+                       "mxfp4_fused_rmsnorm_quantize_row_and_col", "mxfp4_fused_silu_mul_quantize_row_and_col"],
+    "_C_mx": ["mxfp4_gemm", "mxfp4_gemm_config", "mxfp4_batched_gemm", "mxfp4_batched_gemm_config",
+              "mxfp4_gemm_residual"],
+}
+
+
+@pytest.mark.parametrize("name", sorted(REQUIRED))
+def test_stub_loads_by_path_and_exports_symbols(name):
+    b = importlib.import_module("mfu-fp4-training_b200.build")
+    b.build_drop_in()
+    path = b.drop_in_path(name)
+    assert os.path.isfile(path)
+    rel = os.path.relpath(path, b.DROP_IN_ROOT)
+    assert rel.startswith(b.DROP_IN[name][0])
+    spec = importlib.util.spec_from_file_location(name, path)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    for sym in REQUIRED[name]:
+        assert callable(getattr(mod, sym)), f"{name}.{sym} missing"

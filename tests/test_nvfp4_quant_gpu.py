@@ -130,3 +130,22 @@ def test_full_size_properties_config2():
         ccodes, csc = o.nvfp4_quantize_1d(np.ascontiguousarray(blk.T), a[6].item(), "encode")
         assert np.array_equal(u8(a[2][:, r0 // 2:(r0 + 128) // 2]), ccodes)
     assert_status_ok()
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (512, 1024), (1792, 4096)])
+def test_quantize_weight_2d(shape):
+    tkq = mod("tk_quant_v5")
+    N, K = shape
+    w = o.bf16_round((0.02 * np.random.default_rng(N).standard_normal((N, K))).astype(np.float32))
+    w[:16, :16] = 0.0
+    out = tkq.tk_quantize_weight_2d(to_dev_bf16(w))
+    torch.cuda.synchronize()
+    amax = o.tensor_amax(w)
+    r, rs, c, cs = o.nvfp4_quantize_2d(w, amax)
+    assert np.array_equal(u8(out[0]), r) and np.array_equal(u8(out[2]), c)
+    assert np.array_equal(u8(out[1]).reshape(-1), o.swizzle_scales(rs).reshape(-1))
+    assert np.array_equal(u8(out[3]).reshape(-1), o.swizzle_scales(cs).reshape(-1))
+    # the property the reference relies on: column codes are the transpose of the row codes
+    assert np.array_equal(o.unpack_fp4(u8(out[2])), o.unpack_fp4(u8(out[0])).T)
+    assert out[4].item() == o.nvfp4_global_decode_scale(amax)
+    assert_status_ok()
