@@ -463,8 +463,8 @@ def main():
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one pass-2 launch at the bench size, from the ncu
-# capture summarised under profiles/ (None until a capture exists).
-TRAFFIC_PER_LAUNCH = None
+# capture summarised under profiles/.
+TRAFFIC_PER_LAUNCH = 134324736 + 35709184  # profiles/fused_rmsnorm_nvfp4_quant_16384x4096.md (in-kernel DRAM bytes)
 
 if __name__ == "__main__":
     main()
