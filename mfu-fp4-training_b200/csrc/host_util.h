@@ -35,6 +35,16 @@ int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
                  uint64_t dim1, uint64_t dim2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
                  uint32_t box1, uint32_t box2, CUtensorMapSwizzle swizzle);
 
+// Options of the stochastic-rounding / Hadamard variants of the NVFP4 quantiser (one launch).
+struct QuantOpt {
+  int sr;                    // data stochastic rounding on every pass of this launch
+  int rht_row, rht_col;      // 16-point Hadamard transform along K (row operand) / along M (column operand)
+  int sign;                  // seeded sign flip before the transform
+  int return_row;            // 0: skip the row-wise outputs but keep their place in the random stream
+  unsigned long long rng_seed, rng_offset;
+  unsigned long long sign_seed, sign_subseq;
+};
+
 // Launchers defined in quant_nvfp4.cu and shared with the other producers.
 // amax_sg[0] = max|x|, amax_sg[1] = amax/2688 (cleared and recomputed on the stream).
 int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st);
@@ -43,6 +53,7 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st)
 // weight_2d shares one scale per 16x16 tile between the two orientations (decode-centric).
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                     bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4, void* row_sc,
-                    void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st, bool weight_2d = false);
+                    void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st, bool weight_2d = false,
+                    const QuantOpt* opt = nullptr);
 
 }  // namespace fp4b200

@@ -295,6 +295,13 @@ struct QuantArgs {
   int M, K;
   int chunks_m, chunks_k;
   int reverse;             // walk chunks from the last row block to the first
+  // ---- OPT instantiations only (stochastic rounding / 16-point Hadamard transform) ----
+  int opt_sr;              // data stochastic rounding in this launch (row and column passes)
+  int opt_rht_row, opt_rht_col;   // per-16 Hadamard transform along K (row operand) / along M (column operand)
+  int opt_sign;            // seeded sign flip before the transform
+  int opt_return_row;      // 0: row-wise outputs are not written (their random words are still skipped)
+  unsigned long long rng_seed, rng_offset;     // Philox key and counter offset
+  unsigned long long sign_seed, sign_subseq;   // sign-mask hash inputs
 };
 
 template <bool ENCODE_CENTRIC>
@@ -322,8 +329,95 @@ __device__ __forceinline__ uint32_t block_code(float b, float s_enc) {
   }
 }
 
-template <bool ENCODE_CENTRIC, bool NORM, bool W2D>
-__global__ void __launch_bounds__(kQThreads, 2)
+
+// ---- helpers of the OPT instantiations ------------------------------------------------------
+
+// Philox4x32-10 block: key = seed, counter = {offset (64 bit), sequence (64 bit)}
+// (reference generator: nvfp4_v5/util/curanddx.hpp:20-103)
+__device__ __forceinline__ uint4 philox4x32_10(unsigned long long seed, unsigned long long sequence,
+                                               unsigned long long offset) {
+  uint32_t kx = (uint32_t)seed, ky = (uint32_t)(seed >> 32);
+  uint32_t c0 = (uint32_t)offset, c1 = (uint32_t)(offset >> 32), c2 = (uint32_t)sequence, c3 = (uint32_t)(sequence >> 32);
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    const uint32_t n0 = hi1 ^ c1 ^ kx, n2 = hi0 ^ c3 ^ ky;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    kx += 0x9E3779B9u; ky += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+
+// +1 / -1 per coordinate along the transformed axis (reference: tk_quantize.cu:483-488,620-627)
+__device__ __forceinline__ float rht_sign(unsigned long long seed, unsigned long long subseq, unsigned long long coord) {
+  unsigned long long x = seed ^ (subseq * 0xd1b54a32d192ed03ull) ^ (coord * 0x9e3779b97f4a7c15ull);
+  x += 0x9e3779b97f4a7c15ull;
+  x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+  x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+  const uint32_t h = (uint32_t)((x ^ (x >> 31)) >> 32);
+  return (h & 1u) ? 1.0f : -1.0f;
+}
+
+// unnormalised Sylvester butterflies (steps 1,2,4,8), then x0.25 (quantize_transpose_tuned.cuh:161-179)
+__device__ __forceinline__ void fwht16(float (&v)[16]) {
+#pragma unroll
+  for (int step = 1; step < 16; step <<= 1) {
+#pragma unroll
+    for (int base = 0; base < 16; base += 2 * step) {
+#pragma unroll
+      for (int j = 0; j < step; ++j) {
+        const float x = v[base + j], y = v[base + j + step];
+        v[base + j] = x + y;
+        v[base + j + step] = x - y;
+      }
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] *= 0.25f;
+}
+
+// 16 values times coeff -> 8 bytes of codes, stochastic rounding with words wsel[0..3] for the
+// four groups of four elements
+__device__ __forceinline__ uint2 quant16_sr(const float (&x)[16], float coeff, const uint32_t (&wsel)[4]) {
+  uint32_t h[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g)
+    h[g] = f32x4_to_e2m1x4_sr(x[4 * g] * coeff, x[4 * g + 1] * coeff, x[4 * g + 2] * coeff, x[4 * g + 3] * coeff, wsel[g]);
+  return make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+}
+
+__device__ __forceinline__ uint2 quant16_rn(const float (&x)[16], float coeff) {
+  return make_uint2(f32x8_to_e2m1x8(x[0] * coeff, x[1] * coeff, x[2] * coeff, x[3] * coeff, x[4] * coeff, x[5] * coeff,
+                                    x[6] * coeff, x[7] * coeff),
+                    f32x8_to_e2m1x8(x[8] * coeff, x[9] * coeff, x[10] * coeff, x[11] * coeff, x[12] * coeff,
+                                    x[13] * coeff, x[14] * coeff, x[15] * coeff));
+}
+
+// transform (optional sign flip, Hadamard, bf16 rounding), block scale, codes of one 16-element block
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, bool sign, unsigned long long sign_seed,
+                                           unsigned long long sign_subseq, unsigned long long coord0, float s_enc,
+                                           const ScaleLut* lut, bool sr, const uint32_t (&wsel)[4], uint32_t& stored) {
+  if (rht) {
+    if (sign) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) x[i] *= rht_sign(sign_seed, sign_subseq, coord0 + (unsigned long long)i);
+    }
+    fwht16(x);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) x[i] = __bfloat162float(__float2bfloat16_rn(x[i]));
+  }
+  float bm = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(x[i]));
+  const ScaleLut e = lut[block_code<ENCODE_CENTRIC>(bm, s_enc)];
+  stored = e.stored;
+  return sr ? quant16_sr(x, e.coeff, wsel) : quant16_rn(x, e.coeff);
+}
+
+template <bool ENCODE_CENTRIC, bool NORM, bool W2D, bool OPT>
+__global__ void __launch_bounds__(kQThreads, OPT ? 1 : 2)
 nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArgs a) {
   extern __shared__ uint8_t smem_raw[];
   QuantSmem& sm = *reinterpret_cast<QuantSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -459,26 +553,66 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
             *reinterpret_cast<uint4*>(rowp + row_off[j]) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
         }
       }
-      uint32_t mx0 = 0, mx1 = 0;
+      if constexpr (OPT) {
+        // The stochastic-rounding stream follows the reference kernel's thread/draw order, so that the
+        // same (seed, offset) gives the same word to the same element: 128 threads per chunk, four
+        // 64x64 stages, per stage a row pass (2 iterations x 4 words) then a column pass (2 x 4 words);
+        // a 16-element block consumes exactly one Philox block (quantize_transpose_tuned.cuh:392-528).
+        const int per_stage = want_col ? 16 : 8;
+        uint32_t st_b[2];
+        uint2 cd[2];
 #pragma unroll
-      for (int q = 0; q < 8; ++q) { mx0 = absmax_xs(mx0, w[q]); mx1 = absmax_xs(mx1, w[8 + q]); }
-      float b0 = fmaxf(fabsf(bf16lo_to_f32(mx0)), fabsf(bf16hi_to_f32(mx0)));
-      float b1 = fmaxf(fabsf(bf16lo_to_f32(mx1)), fabsf(bf16hi_to_f32(mx1)));
-      if constexpr (W2D) {
-        b0 = sm.tile_amax[r >> 4][unit * 2];
-        b1 = sm.tile_amax[r >> 4][unit * 2 + 1];
+        for (int b = 0; b < 2; ++b) {
+          float x[16];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) { x[2 * q] = bf16lo_to_f32(w[8 * b + q]); x[2 * q + 1] = bf16hi_to_f32(w[8 * b + q]); }
+          const int lc0 = unit * 32 + b * 16;           // first column of the block inside the chunk
+          uint32_t wsel[4] = {0, 0, 0, 0};
+          if (a.opt_sr) {
+            const int stage = (r >> 6) * 2 + (lc0 >> 6);
+            const int lr = r & 63, it_ref = lr >> 5;
+            const int tid_ref = (lr & 31) * 4 + ((lc0 & 63) >> 4);
+            const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
+                                           128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
+            const uint4 rw = philox4x32_10(a.rng_seed, seq,
+                                           a.rng_offset + (unsigned long long)((stage * per_stage + it_ref * 4) >> 2));
+            const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
+            const int bg = (tid_ref & 31) >> 4;
+#pragma unroll
+            for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
+          }
+          cd[b] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
+                                            (unsigned long long)(k0 + lc0), s_enc_row, sm.lut_row, a.opt_sr != 0, wsel,
+                                            st_b[b]);
+        }
+        if (a.opt_return_row) {
+          st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1),
+                   make_uint4(cd[0].x, cd[0].y, cd[1].x, cd[1].y));
+          *reinterpret_cast<uint16_t*>(&sm.row_sc[pp][(unit >> 1) * 512 + scale_tile_offset(r, (unit & 1) * 2)]) =
+              (uint16_t)(st_b[0] | (st_b[1] << 8));
+        }
+      } else {
+        uint32_t mx0 = 0, mx1 = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { mx0 = absmax_xs(mx0, w[q]); mx1 = absmax_xs(mx1, w[8 + q]); }
+        float b0 = fmaxf(fabsf(bf16lo_to_f32(mx0)), fabsf(bf16hi_to_f32(mx0)));
+        float b1 = fmaxf(fabsf(bf16lo_to_f32(mx1)), fabsf(bf16hi_to_f32(mx1)));
+        if constexpr (W2D) {
+          b0 = sm.tile_amax[r >> 4][unit * 2];
+          b1 = sm.tile_amax[r >> 4][unit * 2 + 1];
+        }
+        const ScaleLut e0 = sm.lut_row[block_code<ENCODE_CENTRIC>(b0, s_enc_row)];
+        const ScaleLut e1 = sm.lut_row[block_code<ENCODE_CENTRIC>(b1, s_enc_row)];
+        uint4 codes;
+        codes.x = quant8(w, e0.coeff);
+        codes.y = quant8(w + 4, e0.coeff);
+        codes.z = quant8(w + 8, e1.coeff);
+        codes.w = quant8(w + 12, e1.coeff);
+        st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1), codes);
+        // blocks kb = 2*unit, 2*unit+1 of tile kb>>2 = unit>>1: two adjacent bytes
+        *reinterpret_cast<uint16_t*>(&sm.row_sc[pp][(unit >> 1) * 512 + scale_tile_offset(r, (unit & 1) * 2)]) =
+            (uint16_t)(e0.stored | (e1.stored << 8));
       }
-      const ScaleLut e0 = sm.lut_row[block_code<ENCODE_CENTRIC>(b0, s_enc_row)];
-      const ScaleLut e1 = sm.lut_row[block_code<ENCODE_CENTRIC>(b1, s_enc_row)];
-      uint4 codes;
-      codes.x = quant8(w, e0.coeff);
-      codes.y = quant8(w + 4, e0.coeff);
-      codes.z = quant8(w + 8, e1.coeff);
-      codes.w = quant8(w + 12, e1.coeff);
-      st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1), codes);
-      // blocks kb = 2*unit, 2*unit+1 of tile kb>>2 = unit>>1: two adjacent bytes
-      *reinterpret_cast<uint16_t*>(&sm.row_sc[pp][(unit >> 1) * 512 + scale_tile_offset(r, (unit & 1) * 2)]) =
-          (uint16_t)(e0.stored | (e1.stored << 8));
     }
     __syncthreads();
 
@@ -494,23 +628,52 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
           w[i] = *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]);
           mx = absmax_xs(mx, w[i]);
         }
-        float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
-        if constexpr (W2D) b0 = b1 = sm.tile_amax[warp][h * 4 + (lane >> 3)];
-        const ScaleLut e0 = sm.lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
-        const ScaleLut e1 = sm.lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
-        const float2 cc = make_float2(e0.coeff, e1.coeff);
-        float2 v[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = mul2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), cc);
         uint4 q;
-        q.x = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
-        q.y = f32x8_to_e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
-        q.z = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
-        q.w = f32x8_to_e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+        uint32_t st0, st1;
+        if constexpr (OPT) {
+          uint2 cd[2];
+          uint32_t st_c[2];
+#pragma unroll
+          for (int wq = 0; wq < 2; ++wq) {
+            float x[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = wq ? bf16hi_to_f32(w[i]) : bf16lo_to_f32(w[i]);
+            uint32_t wsel[4] = {0, 0, 0, 0};
+            if (a.opt_sr) {
+              const int stage = (warp >> 2) * 2 + h;
+              const int tid_ref = (((warp & 3) - (lane & 3)) & 3) * 32 + lane;
+              const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
+                                             128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
+              const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
+              wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
+            }
+            cd[wq] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
+                                               (unsigned long long)(m0 + warp * 16), s_enc_col, sm.lut_col,
+                                               a.opt_sr != 0, wsel, st_c[wq]);
+          }
+          q = make_uint4(cd[0].x, cd[0].y, cd[1].x, cd[1].y);
+          st0 = st_c[0]; st1 = st_c[1];
+        }
+        if constexpr (!OPT) {
+          float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
+          if constexpr (W2D) b0 = b1 = sm.tile_amax[warp][h * 4 + (lane >> 3)];
+          const ScaleLut e0 = sm.lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
+          const ScaleLut e1 = sm.lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
+          const float2 cc = make_float2(e0.coeff, e1.coeff);
+          float2 v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = mul2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), cc);
+          q.x = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+          q.y = f32x8_to_e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
+          q.z = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+          q.w = f32x8_to_e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+          st0 = e0.stored;
+          st1 = e1.stored;
+        }
         const int c = 2 * lane + 64 * h;
         *reinterpret_cast<uint4*>(&sm.col_codes[warp][c]) = q;   // columns c and c+1
-        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c, warp & 3)] = (uint8_t)e0.stored;
-        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c + 1, warp & 3)] = (uint8_t)e1.stored;
+        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c, warp & 3)] = (uint8_t)st0;
+        sm.col_sc[(warp >> 2) * 512 + scale_tile_offset(c + 1, warp & 3)] = (uint8_t)st1;
       }
     }
     if constexpr (NORM) {
@@ -527,7 +690,7 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     }
 
     // ---- write-out: scales (two 512-byte tiles per orientation) and column codes -----
-    {
+    if (!OPT || a.opt_return_row) {
       uint8_t* dst = a.row_sc + ((size_t)cm * (a.K >> 6) + (size_t)ck * 2) * 512;
       st_cs_u32(dst + tid * 4, *reinterpret_cast<const uint32_t*>(&sm.row_sc[pp][tid * 4]));
     }
@@ -549,6 +712,58 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
   }
 }
 
+
+// Tensor amax of the 16-point Hadamard transform of x (per 16 contiguous elements along K when
+// along_k, else per 16 consecutive rows), taken on the fp32 transform output before its bf16
+// rounding, as the reference's scan does (tk_quantize.cu:574-664).
+__global__ void __launch_bounds__(256)
+rht16_amax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                  const float* __restrict__ inv_rms, float* __restrict__ amax, int64_t M, int64_t K, int along_k,
+                  int sign, unsigned long long sign_seed, unsigned long long sign_subseq) {
+  const int64_t groups = along_k ? M * (K / 16) : (M / 16) * K;
+  float local = 0.0f;
+  for (int64_t gidx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gidx < groups; gidx += (int64_t)gridDim.x * blockDim.x) {
+    float v[16];
+    int64_t coord0;
+    if (along_k) {
+      const int64_t bpr = K / 16, row = gidx / bpr, cb = gidx - row * bpr;
+      const uint4* p = reinterpret_cast<const uint4*>(x + row * K + cb * 16);
+      const uint4 a0 = __ldg(p), a1 = __ldg(p + 1);
+      const uint32_t w[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+      for (int q = 0; q < 8; ++q) { v[2 * q] = bf16lo_to_f32(w[q]); v[2 * q + 1] = bf16hi_to_f32(w[q]); }
+      if (gamma != nullptr) {   // transform of the RMS-normalised, bf16-rounded values
+        const float inv = __ldg(inv_rms + row);
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+          v[i] = __bfloat162float(__float2bfloat16_rn(v[i] * inv * __bfloat162float(gamma[cb * 16 + i])));
+      }
+      coord0 = cb * 16;
+    } else {
+      const int64_t rb = gidx / K, col = gidx - rb * K;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] = __bfloat162float(x[(rb * 16 + i) * K + col]);
+      coord0 = rb * 16;
+    }
+    if (sign) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) v[i] *= rht_sign(sign_seed, sign_subseq, (unsigned long long)(coord0 + i));
+    }
+    fwht16(v);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) local = fmaxf(local, fabsf(v[i]));
+  }
+  local = warp_max(local);
+  __shared__ float part[8];
+  if ((threadIdx.x & 31) == 0) part[threadIdx.x >> 5] = local;
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    local = threadIdx.x < 8 ? part[threadIdx.x] : 0.0f;
+    local = warp_max(local);
+    if (threadIdx.x == 0 && local > 0.0f) atomic_max_nonneg(amax, local);
+  }
+}
+
 // ---------------------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------------------
@@ -566,13 +781,13 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st)
   return 0;
 }
 
-template <bool EC, bool NORM, bool W2D = false>
+template <bool EC, bool NORM, bool W2D = false, bool OPT = false>
 static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cudaStream_t st) {
-  auto kern = nvfp4_quantize_kernel<EC, NORM, W2D>;
+  auto kern = nvfp4_quantize_kernel<EC, NORM, W2D, OPT>;
   const int smem = (int)sizeof(QuantSmem) + 1024;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_chunks = args.chunks_m * args.chunks_k;
-  const int grid = std::min(n_chunks, 2 * device_sm_count());
+  const int grid = std::min(n_chunks, (OPT ? 1 : 2) * device_sm_count());
   if (grid == 0) return 0;
   kern<<<grid, kQThreads, smem, st>>>(tmap, args);
   FP4_CUDA_CHECK(cudaGetLastError());
@@ -582,7 +797,7 @@ static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cud
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
-                           cudaStream_t st, bool weight_2d) {
+                           cudaStream_t st, bool weight_2d, const QuantOpt* opt) {
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                             (uint64_t)K * 2, 64, kChunk, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -601,6 +816,15 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.chunks_m = (int)(M / kChunk); a.chunks_k = (int)(K / kChunk);
   a.reverse = reverse ? 1 : 0;
   const bool norm = inv_rms != nullptr;
+  if (opt != nullptr) {
+    a.opt_sr = opt->sr; a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
+    a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
+    a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
+    if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st)
+                                    : launch_quantize_t<true, false, false, true>(tmap, a, st);
+    return norm ? launch_quantize_t<false, true, false, true>(tmap, a, st)
+                : launch_quantize_t<false, false, false, true>(tmap, a, st);
+  }
   if (weight_2d) return launch_quantize_t<false, false, true>(tmap, a, st);   // decode-centric, as the reference
   if (encode_centric) return norm ? launch_quantize_t<true, true>(tmap, a, st) : launch_quantize_t<true, false>(tmap, a, st);
   return norm ? launch_quantize_t<false, true>(tmap, a, st) : launch_quantize_t<false, false>(tmap, a, st);
@@ -678,6 +902,47 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
   return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
                          return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr,
                          true, (cudaStream_t)stream);
+}
+
+int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
+                             int along_k, int with_sign, uint64_t sign_seed, uint64_t sign_subseq, float* amax_sg,
+                             void* stream) {
+  if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_rht16_amax")) return rc;
+  if (!amax_sg) return set_error("nvfp4_rht16_amax: amax_sg is required");
+  if ((gamma_bf16 == nullptr) != (inv_rms == nullptr) || (gamma_bf16 != nullptr && !along_k))
+    return set_error("nvfp4_rht16_amax: fused RMSNorm needs gamma and inv_rms and the transform along K");
+  cudaStream_t st = (cudaStream_t)stream;
+  FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
+  const int64_t groups = M * K / 16;
+  const int grid = (int)std::min<int64_t>((groups + 255) / 256, (int64_t)device_sm_count() * 8);
+  rht16_amax_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x_bf16),
+                                          reinterpret_cast<const __nv_bfloat16*>(gamma_bf16), inv_rms, amax_sg, M, K, along_k != 0,
+                                          with_sign != 0, sign_seed, sign_subseq);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
+                               const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
+                               int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, void* row_fp4, void* row_sc,
+                               void* col_fp4, void* col_sc, void* stream) {
+  if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_quantize_opt")) return rc;
+  if (!amax_row) return set_error("nvfp4_quantize_opt: amax_row is required");
+  if ((gamma_bf16 == nullptr) != (inv_rms == nullptr))
+    return set_error("nvfp4_quantize_opt: gamma and inv_rms must both be given (fused RMSNorm) or both be null");
+  if (return_row && (!row_fp4 || !row_sc)) return set_error("nvfp4_quantize_opt: row outputs are required when return_row");
+  if ((col_fp4 == nullptr) != (col_sc == nullptr))
+    return set_error("nvfp4_quantize_opt: col_fp4 and col_sc must both be given or both be null");
+  if (!return_row && !col_fp4) return set_error("nvfp4_quantize_opt: nothing to compute");
+  QuantOpt o{};
+  o.sr = data_sr != 0; o.rht_row = rht_row != 0; o.rht_col = rht_col != 0; o.sign = with_sign != 0;
+  o.return_row = return_row != 0; o.rng_seed = rng_seed; o.rng_offset = rng_offset;
+  o.sign_seed = sign_seed; o.sign_subseq = sign_subseq;
+  return launch_quantize(x_bf16, M, K, amax_row, amax_col, encode_centric != 0, inv_rms, gamma_bf16, row_fp4, row_sc,
+                         col_fp4, col_sc, nullptr, false, (cudaStream_t)stream, false, &o);
 }
 
 int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,

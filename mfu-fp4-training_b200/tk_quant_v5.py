@@ -198,21 +198,223 @@ def tk_silu_deriv_quantize_split_for_gemm(dh, h3, h1_raw):
     return (*q1, a1.narrow(0, 1, 1), zero, *q3, a3.narrow(0, 1, 1), zero.clone(), amax_buf, sync_buf, dh1, dh3)
 
 
+# ---- stochastic rounding / Hadamard ("opt") producers -----------------------------------------
+
+_U64 = (1 << 64) - 1
+_sr_invocations = {}   # device index -> number of SR launches so far (the reference's device-global counter)
+
+
+def tk_sr_invocation_count(device=None) -> int:
+    """Number of stochastic-rounding launches issued so far on ``device`` in this process: the Philox offset
+    of launch n is ``rng_subsequence + n * 2**32`` (reference: tk_sr_invocation_offset, tk_quantize.cu:443-481)."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    return _sr_invocations.get(idx, 0)
+
+
+def tk_set_sr_invocation_count(n: int, device=None) -> None:
+    """Restores the counter (checkpoint resume, tests); no counterpart in the reference, whose counter
+    cannot be set."""
+    idx = torch.cuda.current_device() if device is None else torch.device(device).index
+    _sr_invocations[idx] = int(n)
+
+
+def _next_offset(t, rng_subsequence, use_sr):
+    idx = t.device.index
+    n = _sr_invocations.get(idx, 0)
+    if use_sr:
+        _sr_invocations[idx] = n + 1
+    return (int(rng_subsequence) + n * (1 << 32)) & _U64
+
+
+def _norm_axes(rht_axes):
+    a = str(rht_axes).lower().replace("-", "_")
+    if a not in ("none", "row", "col", "both", "rowcol", "row_col"):
+        raise RuntimeError(f"Unsupported regular TK RHT axes: {rht_axes}")
+    return a in ("row", "both", "rowcol", "row_col"), a in ("col", "both", "rowcol", "row_col")
+
+
+def _norm_sr_axes(data_sr_axes):
+    a = str(data_sr_axes).lower().replace("-", "_")
+    a = {"all": "both", "rowcol": "both", "row_col": "both", "column": "col", "columns": "col", "wgrad": "col",
+         "dgrad": "row", "off": "none", "0": "none"}.get(a, a)
+    if a not in ("none", "row", "col", "both"):
+        raise RuntimeError(f"Unsupported regular TK data SR axes: {data_sr_axes}")
+    return a
+
+
+def _amax_plain(x):
+    amax_sg = torch.empty(2, dtype=torch.float32, device=x.device)
+    _lib.call("fp4b200_nvfp4_amax", x.data_ptr(), x.numel(), amax_sg.data_ptr(), _stream(x))
+    return amax_sg
+
+
+def _amax_rht(x, along_k, sign, seed, subseq, gamma=None, inv_rms=None):
+    M, K = x.shape
+    amax_sg = torch.empty(2, dtype=torch.float32, device=x.device)
+    _lib.call("fp4b200_nvfp4_rht16_amax", x.data_ptr(), _p(gamma), _p(inv_rms), M, K, int(along_k), int(sign),
+              int(seed) & _U64, int(subseq) & _U64, amax_sg.data_ptr(), _stream(x))
+    return amax_sg
+
+
+def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row_rht, col_rht, return_row, seed, offset,
+                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None):
+    """One launch, the counterpart of tk_quantize_transpose (tk_quantize.cu:3807-3926)."""
+    M, K = x.shape
+    u8 = dict(dtype=torch.uint8, device=x.device)
+    row_fp4 = torch.empty((M, K // 2), **u8) if return_row else None
+    row_sc = torch.empty((M // 128, K // 64, 512), **u8) if return_row else None
+    col_fp4 = torch.empty((K, M // 2), **u8) if return_transpose else None
+    col_sc = torch.empty((K // 128, M // 64, 512), **u8) if return_transpose else None
+    _lib.call("fp4b200_nvfp4_quantize_opt", x.data_ptr(), _p(gamma), _p(inv_rms), M, K, amax_row.data_ptr(),
+              amax_col.data_ptr(), int(bool(encode_centric)), int(bool(sr)), int(bool(row_rht)), int(bool(col_rht)),
+              int(bool(sign)), int(sign_seed) & _U64, int(sign_subseq) & _U64, int(bool(return_row)),
+              int(seed) & _U64, int(offset) & _U64, _p(row_fp4), _p(row_sc), _p(col_fp4), _p(col_sc), _stream(x))
+    return row_fp4, row_sc, col_fp4, col_sc
+
+
+def tk_quantize_transpose(input, amax_row, amax_col, return_transpose, stochastic_rounding=False, encode_centric=True,
+                          scale_stochastic_rounding=False, row_rht=False, col_rht=False, return_row=True, rng_state=None):
+    """tk_quantize.cu:3807-3926 — quantise with pre-computed device amaxes; ``rng_state`` = int64[2] tensor
+    ``[seed, offset]``.  Returns (row_fp4, row_sc, col_fp4, col_sc) as uint8 tensors."""
+    _check_bf16_2d(input, "input")
+    if scale_stochastic_rounding:
+        raise RuntimeError("tk_quantize_transpose: scale stochastic rounding is not built")
+    seed = offset = 0
+    if stochastic_rounding:
+        if rng_state is None or rng_state.numel() < 2:
+            raise RuntimeError("rng_state [seed, offset] is required with stochastic rounding")
+        seed, offset = (int(v) & _U64 for v in rng_state.cpu().tolist()[:2])
+    with torch.cuda.device(input.device):
+        out = _launch_opt(input, amax_row, amax_col, return_transpose, stochastic_rounding, encode_centric, row_rht,
+                          col_rht, return_row, seed, offset, False, 0, 0)
+    empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
+    return tuple(empty if t is None else t for t in out)
+
+
+def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, data_stochastic_rounding=False,
+                             scale_stochastic_rounding=False, rht_axes="none", with_random_sign_mask=False, rng_seed=0,
+                             rng_subsequence=0, global_scale_target=448.0, data_sr_axes="both"):
+    """tk_quantize.cu:4299-4540 — returns (row_fp4, row_sc, col_fp4, col_sc, row_sg, col_sg).  Same choice of
+    amaxes, number of launches and Philox offsets as the reference; scale stochastic rounding is not built."""
+    M, K = _check_bf16_2d(input, "input")
+    if scale_stochastic_rounding:
+        raise RuntimeError("tk_quantize_for_gemm_opt: scale stochastic rounding is not built")
+    if not (0.0 < float(global_scale_target) <= 512.0):
+        raise RuntimeError(f"global_scale_target must be finite and in (0, 512], got {global_scale_target}")
+    row_rht, col_rht = _norm_axes(rht_axes)
+    if float(global_scale_target) != 448.0 and (row_rht or col_rht):
+        raise RuntimeError("non-default global_scale_target is currently supported only with rht_axes='none'")
+    axes = _norm_sr_axes(data_sr_axes)
+    row_sr = bool(data_stochastic_rounding) and axes in ("row", "both")
+    col_sr = bool(data_stochastic_rounding) and axes in ("col", "both")
+    if not (row_rht or col_rht or row_sr or col_sr) and float(global_scale_target) == 448.0:
+        base = tk_quantize_for_gemm(input, return_transpose, encode_centric)
+        return base[:6]
+    use_sr = row_sr or col_sr
+    sign = bool(with_random_sign_mask)
+    with torch.cuda.device(input.device):
+        plain = None
+        if row_rht:
+            row_amax = _amax_rht(input, True, sign, rng_seed, rng_subsequence)
+        else:
+            plain = row_amax = _amax_plain(input)
+            if float(global_scale_target) != 448.0:
+                row_amax.mul_(448.0 / float(global_scale_target))
+        if col_rht:
+            col_amax = _amax_rht(input, False, sign, rng_seed, rng_subsequence)
+        elif row_rht:
+            col_amax = _amax_plain(input)
+        else:
+            col_amax = row_amax
+        row_mat, col_mat = row_rht and sign, col_rht and sign     # the reference materialises these
+        if return_transpose and not row_mat and row_sr == col_sr and not col_mat:
+            off = _next_offset(input, rng_subsequence, use_sr)
+            rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr, encode_centric, row_rht, col_rht,
+                                         True, rng_seed, off, sign, rng_seed, rng_subsequence)
+        else:
+            off = _next_offset(input, rng_subsequence, use_sr)
+            rf, rs, _, _ = _launch_opt(input, row_amax, row_amax, False, row_sr, encode_centric, row_rht, False, True,
+                                       rng_seed, off, sign, rng_seed, rng_subsequence)
+            cf = cs = None
+            if return_transpose:
+                off = _next_offset(input, rng_subsequence, use_sr)
+                _, _, cf, cs = _launch_opt(input, col_amax, col_amax, True, col_sr, encode_centric, False, col_rht,
+                                           False, rng_seed, off, sign, rng_seed, rng_subsequence)
+    empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
+    row_sg = row_amax.narrow(0, 1, 1)
+    col_sg = col_amax.narrow(0, 1, 1) if return_transpose else row_sg
+    return (rf.view(_FP4), rs.view(_E4M3), cf.view(_FP4) if cf is not None else empty,
+            cs.view(_E4M3) if cs is not None else empty, row_sg, col_sg)
+
+
+def tk_fused_norm_quantize_opt(input, gamma, epsilon, return_transpose=True, encode_centric=True,
+                               data_stochastic_rounding=False, scale_stochastic_rounding=False, rht_axes="row",
+                               with_random_sign_mask=False, rng_seed=0, rng_subsequence=0):
+    """tk_quantize.cu:8465-8586 — fused RMSNorm + row-Hadamard (+ stochastic rounding) quantisation; returns
+    (row_fp4, row_sc, col_fp4, col_sc, row_sg, col_sg, inv_rms).  As in the reference only the row transform
+    without sign mask is accepted."""
+    M, K = _check_bf16_2d(input, "input")
+    row_rht, col_rht = _norm_axes(rht_axes)
+    if not row_rht or col_rht:
+        raise RuntimeError("tk_fused_norm_quantize_opt currently supports the regular-TK QKV row-RHT contract only")
+    if with_random_sign_mask:
+        raise RuntimeError("tk_fused_norm_quantize_opt does not yet fuse random-sign RHT")
+    if scale_stochastic_rounding:
+        raise RuntimeError("tk_fused_norm_quantize_opt: scale stochastic rounding is not built")
+    if gamma.dtype != torch.bfloat16 or gamma.numel() != K or not gamma.is_contiguous() or gamma.device != input.device:
+        raise RuntimeError("gamma must be contiguous CUDA bfloat16 [K] on the input device")
+    sr = bool(data_stochastic_rounding)
+    with torch.cuda.device(input.device):
+        inv_rms = torch.empty(M, dtype=torch.float32, device=input.device)
+        col_amax = torch.empty(2, dtype=torch.float32, device=input.device)
+        _lib.call("fp4b200_nvfp4_rmsnorm_stats", input.data_ptr(), gamma.data_ptr(), float(epsilon), M, K,
+                  inv_rms.data_ptr(), 1, col_amax.data_ptr(), _stream(input))
+        row_amax = _amax_rht(input, True, False, 0, 0, gamma, inv_rms)
+        off = _next_offset(input, rng_subsequence, sr)
+        rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, sr, encode_centric, True, False, True, rng_seed,
+                                     off, False, 0, 0, gamma, inv_rms)
+    return (rf.view(_FP4), rs.view(_E4M3), cf.view(_FP4), cs.view(_E4M3), row_amax.narrow(0, 1, 1),
+            col_amax.narrow(0, 1, 1), inv_rms)
+
+
 def tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1_raw, return_transpose=True, encode_centric=True,
                                               data_stochastic_rounding=False, scale_stochastic_rounding=False,
                                               rht_axes="row", with_random_sign_mask=False, rng_seed=0,
                                               rng_subsequence=0, data_sr_axes="both"):
-    """tk_quantize.cu:10063-10255 — 15-tuple: dh1 (row_fp4,row_sc,col_fp4,col_sc,row_sg,col_sg), dh3
-    likewise, amaxes[4], dh1 bf16, dh3 bf16.  Built: round-to-nearest without Hadamard transform
-    (``rht_axes="none"``); the stochastic-rounding and RHT variants raise until they are built."""
-    if data_stochastic_rounding or scale_stochastic_rounding:
-        raise RuntimeError("tk_silu_deriv_quantize_split_for_gemm_opt: stochastic rounding is not built yet")
-    if rht_axes not in ("none", "", None):
-        raise RuntimeError("tk_silu_deriv_quantize_split_for_gemm_opt: rht_axes other than 'none' is not built yet")
+    """tk_quantize.cu:10063-10255 — 15-tuple: dh1 (row_fp4,row_sc,col_fp4,col_sc,row_sg,col_sg), dh3 likewise,
+    amaxes[4], dh1 bf16, dh3 bf16.  As in the reference the row operand is Hadamard-transformed
+    (``rht_axes="row"``), there is no sign mask, and each of dh1/dh3 takes one Philox offset shared by its
+    row and column launches; ``rht_axes="none"`` is accepted as an extension (no transform)."""
+    if not return_transpose:
+        raise RuntimeError("split2 opt producer currently requires return_transpose=True")
+    row_rht, col_rht = _norm_axes(rht_axes)
+    if col_rht:
+        raise RuntimeError(f"split2 opt producer currently supports the row-RHT regular-TK contract only; got {rht_axes}")
+    if with_random_sign_mask:
+        raise RuntimeError("split2 opt producer does not support random RHT sign masks yet")
+    if scale_stochastic_rounding:
+        raise RuntimeError("split2 opt producer: scale stochastic rounding is not built")
+    axes = _norm_sr_axes(data_sr_axes)
+    row_sr = bool(data_stochastic_rounding) and axes in ("row", "both")
+    col_sr = bool(data_stochastic_rounding) and axes in ("col", "both")
+    use_sr = row_sr or col_sr
     with torch.cuda.device(dh.device):
         M, H, dh1, dh3, a1, a3 = _silu_deriv(dh, h3, h1_raw)
-        q1 = _quantize_with_amax(dh1, M, H, a1, encode_centric, return_transpose)
-        q3 = _quantize_with_amax(dh3, M, H, a3, encode_centric, return_transpose)
-        amaxes = torch.stack([a1[0], a1[0], a3[0], a3[0]])
-    sg1, sg3 = a1.narrow(0, 1, 1), a3.narrow(0, 1, 1)
-    return (*q1, sg1, sg1, *q3, sg3, sg3, amaxes, dh1, dh3)
+        outs, sgs, amax_list = [], [], []
+        for t, orig in ((dh1, a1), (dh3, a3)):
+            row_amax = _amax_rht(t, True, False, 0, 0) if row_rht else orig
+            off = _next_offset(t, rng_subsequence, use_sr)
+            if row_sr == col_sr:
+                q = _launch_opt(t, row_amax, orig, True, row_sr, encode_centric, row_rht, False, True, rng_seed, off,
+                                False, 0, 0)
+            else:
+                rf, rs, _, _ = _launch_opt(t, row_amax, orig, False, row_sr, encode_centric, row_rht, False, True,
+                                           rng_seed, off, False, 0, 0)
+                _, _, cf, cs = _launch_opt(t, row_amax, orig, True, col_sr, encode_centric, row_rht, False, False,
+                                           rng_seed, off, False, 0, 0)
+                q = (rf, rs, cf, cs)
+            outs.append((q[0].view(_FP4), q[1].view(_E4M3), q[2].view(_FP4), q[3].view(_E4M3)))
+            sgs.append((row_amax.narrow(0, 1, 1), orig.narrow(0, 1, 1)))
+            amax_list += [row_amax[0], orig[0]]
+        amaxes = torch.stack(amax_list)
+    return (*outs[0], *sgs[0], *outs[1], *sgs[1], amaxes, dh1, dh3)

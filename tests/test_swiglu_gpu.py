@@ -62,7 +62,8 @@ def test_silu_deriv_quantize_split_opt(ec):
             assert np.array_equal(u8(out[base + i]).reshape(ref[k].shape), ref[k]), (idx, k)
         assert out[base + 4].item() == ref["sg"] and out[base + 5].item() == ref["sg"]
     with pytest.raises(RuntimeError):
-        tkq.tk_silu_deriv_quantize_split_for_gemm_opt(to_dev_bf16(dh), to_dev_bf16(h3), to_dev_bf16(h1), True, ec, True)
+        tkq.tk_silu_deriv_quantize_split_for_gemm_opt(to_dev_bf16(dh), to_dev_bf16(h3), to_dev_bf16(h1), True, ec, False,
+                                                      False, "col")
     out16 = tkq.tk_silu_deriv_quantize_split_for_gemm(to_dev_bf16(dh), to_dev_bf16(h3), to_dev_bf16(h1))
     torch.cuda.synchronize()
     assert len(out16) == 16 and out16[5].item() == 0.0
