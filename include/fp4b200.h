@@ -178,6 +178,14 @@ int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const
                        const float* B_sg, void* D, int out_fp32, const void* residual_bf16, int64_t M, int64_t N,
                        int64_t K, void* stream);
 
+/* One term of nvfp4_batched_accum_gemm (nvfp4_b200_gemm.cu:2567-2635; kernel nvfp4_batched_accum_gemm.cuh):
+ * D = round(partial_f32 + acc * A_sg * B_sg), partial_f32 a caller buffer [M,N] holding the fp32 sum of the
+ * earlier terms (written by this entry point or by fp4b200_nvfp4_gemm with out_fp32 = 1).  D may alias
+ * partial_f32 when out_fp32 = 1. */
+int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                             const float* B_sg, const float* partial_f32, void* D, int out_fp32, int64_t M, int64_t N,
+                             int64_t K, void* stream);
+
 /* nvfp4_grouped_gemm (nvfp4_b200_gemm.cu:764-841): B is the row concatenation of n_out weights,
  * B_sg_per_tile holds one tensor scale per 256 rows of B, output i receives D_cols[i] columns
  * (each a multiple of 256, adding up to N) into its own bf16 [M, D_cols[i]] buffer. */

@@ -69,6 +69,7 @@ struct GemmArgs {
   int out_fp32;             // 0: bf16 output, 1: fp32 output
   const __nv_bfloat16* residual;  // optional [M, N] bf16 added after the bf16 rounding
   int residual_ld;
+  const float* accum_f32;   // optional [M, N] fp32 partial sum added to acc*scale before the output rounding
   int M, N, K;
   int sf_tiles_k;           // scale tiles along K per row tile
   int* status;
@@ -379,18 +380,31 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         tmem_ld_wait();
         uint8_t* rowp = buf + lane * 128;
+        if (g.accum_f32 != nullptr) {
+          // running fp32 sum over a batch of GEMMs: partial + acc*scale (multiply, then add)
+          const float4* ps = reinterpret_cast<const float4*>(g.accum_f32 + (size_t)row * g.N + col0 + c);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 pv = __ldg(ps + q);
+            r[4 * q] = __float_as_uint(__fadd_rn(pv.x, __fmul_rn(__uint_as_float(r[4 * q]), gs)));
+            r[4 * q + 1] = __float_as_uint(__fadd_rn(pv.y, __fmul_rn(__uint_as_float(r[4 * q + 1]), gs)));
+            r[4 * q + 2] = __float_as_uint(__fadd_rn(pv.z, __fmul_rn(__uint_as_float(r[4 * q + 2]), gs)));
+            r[4 * q + 3] = __float_as_uint(__fadd_rn(pv.w, __fmul_rn(__uint_as_float(r[4 * q + 3]), gs)));
+          }
+        }
+        const float gs_out = g.accum_f32 != nullptr ? 1.0f : gs;
         if (g.out_fp32) {
 #pragma unroll
           for (int q = 0; q < 8; ++q) {
-            const float4 v = make_float4(__uint_as_float(r[4 * q]) * gs, __uint_as_float(r[4 * q + 1]) * gs,
-                                         __uint_as_float(r[4 * q + 2]) * gs, __uint_as_float(r[4 * q + 3]) * gs);
+            const float4 v = make_float4(__uint_as_float(r[4 * q]) * gs_out, __uint_as_float(r[4 * q + 1]) * gs_out,
+                                         __uint_as_float(r[4 * q + 2]) * gs_out, __uint_as_float(r[4 * q + 3]) * gs_out);
             *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) = v;
           }
         } else {
           uint32_t o[16];
 #pragma unroll
           for (int q = 0; q < 16; ++q)
-            o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs, __uint_as_float(r[2 * q + 1]) * gs);
+            o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs_out, __uint_as_float(r[2 * q + 1]) * gs_out);
           if (g.residual != nullptr) {
             const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.residual_ld + col0 + c);
 #pragma unroll
@@ -442,7 +456,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                        const float* B_sg, int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld,
                        int n_out, int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N,
-                       int64_t K, cudaStream_t st) {
+                       int64_t K, cudaStream_t st, const float* accum_f32 = nullptr) {
   CUtensorMap tmap_a, tmap_b;
   if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)M,
                             (uint64_t)K / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -466,6 +480,7 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   for (int i = 0; i < 3; ++i) { g.d[i] = i < n_out ? D[i] : nullptr; g.d_col_end[i] = i < n_out ? d_col_end[i] : 0; g.d_ld[i] = i < n_out ? d_ld[i] : 0; }
   g.n_out = n_out; g.out_fp32 = out_fp32;
   g.residual = (const __nv_bfloat16*)residual; g.residual_ld = residual_ld;
+  g.accum_f32 = accum_f32;
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.sf_tiles_k = (int)(K / (mx ? 128 : 64));
   g.status = device_status_ptr();
@@ -514,6 +529,17 @@ int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const
   int ce[1] = {(int)N}, ld[1] = {(int)N};
   return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg, 0, d, ce, ld, 1, out_fp32, residual_bf16, (int)N, M, N, K,
                      (cudaStream_t)stream);
+}
+
+int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                             const float* B_sg, const float* partial_f32, void* D, int out_fp32, int64_t M, int64_t N,
+                             int64_t K, void* stream) {
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, "nvfp4_gemm_accum")) return rc;
+  if (!A_sg || !B_sg || !D || !partial_f32) return set_error("nvfp4_gemm_accum: A_sg, B_sg, partial_f32 and D are required");
+  void* d[1] = {D};
+  int ce[1] = {(int)N}, ld[1] = {(int)N};
+  return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg, 0, d, ce, ld, 1, out_fp32, nullptr, 0, M, N, K,
+                     (cudaStream_t)stream, partial_f32);
 }
 
 int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,

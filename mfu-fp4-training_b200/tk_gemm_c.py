@@ -126,3 +126,50 @@ def nvfp4_batched_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_lis
         raise RuntimeError("nvfp4_batched_gemm: all lists must have the same length")
     for i in range(n):
         _gemm(A_list[i], A_sc_list[i], A_sg_list[i], B_list[i], B_sc_list[i], B_sg_list[i], D_list[i])
+
+
+def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_list, D_out):
+    """nvfp4_b200_gemm.cu:2567-2635: ``D_out = bf16(sum_i (A_i . B_i^T) * A_sg_i * B_sg_i)`` with the sum kept in
+    fp32 in batch order (at most four terms in the reference; any number here)."""
+    n = len(A_list)
+    if n == 0 or not (len(A_sc_list) == len(A_sg_list) == len(B_list) == len(B_sc_list) == len(B_sg_list) == n):
+        raise RuntimeError("nvfp4_batched_accum_gemm: all lists must have the same non-zero length")
+    if n == 1:
+        return _gemm(A_list[0], A_sc_list[0], A_sg_list[0], B_list[0], B_sc_list[0], B_sg_list[0], D_out)
+    M, N, _ = _shapes(A_list[0], B_list[0])
+    _chk_out(D_out, M, N)
+    with torch.cuda.device(D_out.device):
+        partial = torch.empty((M, N), dtype=torch.float32, device=D_out.device)
+        _gemm(A_list[0], A_sc_list[0], A_sg_list[0], B_list[0], B_sc_list[0], B_sg_list[0], partial)
+        for i in range(1, n):
+            A, B = A_list[i], B_list[i]
+            for t, nm in ((A, "A"), (A_sc_list[i], "A_sc"), (B, "B"), (B_sc_list[i], "B_sc")):
+                _chk_operand(t, nm)
+            _chk_sg(A_sg_list[i], "A_sc_global")
+            _chk_sg(B_sg_list[i], "B_sc_global")
+            Mi, Ni, Ki = _shapes(A, B)
+            if (Mi, Ni) != (M, N):
+                raise RuntimeError("nvfp4_batched_accum_gemm: every term must produce the same [M, N]")
+            last = i == n - 1
+            dst = D_out if last else partial
+            _lib.call("fp4b200_nvfp4_gemm_accum", A.data_ptr(), A_sc_list[i].data_ptr(), A_sg_list[i].data_ptr(),
+                      B.data_ptr(), B_sc_list[i].data_ptr(), B_sg_list[i].data_ptr(), partial.data_ptr(),
+                      dst.data_ptr(), 0 if last else 1, M, N, Ki, _stream(A))
+
+
+def nvfp4_split_dgrad_sum(A_fp4_cat, A_sc_cat, A_sg_list, B_fp4_list, B_sc_list, B_sg_cat, split_dims, D_out):
+    """nvfp4_b200_gemm.cu:2424-2565: dgrad of a fused projection — the row-quantised gradient is the column
+    concatenation of the splits; term i multiplies columns of split i by the column-quantised weight i.
+    The slices are made contiguous here (a copy the reference avoids with strided descriptors)."""
+    offs = 0
+    A_list, A_sc_l, B_sg_l = [], [], []
+    a_u8 = A_fp4_cat.view(torch.uint8)
+    sc_u8 = A_sc_cat.view(torch.uint8)
+    for i, d in enumerate(split_dims):
+        if d % 128:
+            raise RuntimeError("nvfp4_split_dgrad_sum: split sizes must be multiples of 128")
+        A_list.append(a_u8[:, offs // 2:(offs + d) // 2].contiguous())
+        A_sc_l.append(sc_u8[:, offs // 64:(offs + d) // 64, :].contiguous())
+        B_sg_l.append(B_sg_cat.narrow(0, i, 1))
+        offs += d
+    nvfp4_batched_accum_gemm(A_list, A_sc_l, list(A_sg_list), list(B_fp4_list), list(B_sc_list), B_sg_l, D_out)

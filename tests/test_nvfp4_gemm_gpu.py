@@ -56,3 +56,69 @@ def test_nvfp4_gemm_fp32_and_bf16(shape):
     full = x.astype(np.float64) @ w.astype(np.float64).T
     rel_q = np.linalg.norm(got - full) / np.linalg.norm(full)
     assert rel_q < 0.25
+
+
+def test_backward_gemms_from_column_operands():
+    """dgrad dX = dY . W (row operand of dY x column operand of W) and wgrad dW = dY^T . X (column operands of
+    both): the column-wise packs feed the same GEMM; checked against the oracle's dequantised products."""
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    M, N, K = 512, 256, 768          # X [M,K], W [N,K], dY [M,N]
+    x = o.make_activations(M, K, seed=1)
+    w = o.bf16_round((0.02 * np.random.default_rng(2).standard_normal((N, K))).astype(np.float32))
+    dy = o.bf16_round((1e-3 * np.random.default_rng(3).standard_normal((M, N))).astype(np.float32))
+    qx, qw, qdy = (tkq.tk_quantize_for_gemm(to_dev_bf16(t), True, False) for t in (x, w, dy))
+    rx, rw, rdy = (o.nvfp4_quantize_for_gemm(t, True, False) for t in (x, w, dy))
+    # dgrad: [M,N] row operand of dY  x  column operand of W ([K, N/2])  ->  [M,K]
+    dx = torch.empty((M, K), dtype=torch.float32, device="cuda")
+    gemm.nvfp4_gemm(qdy[0], qdy[1], qdy[4], qw[2], qw[3], qw[5], dx)
+    ref = o.nvfp4_gemm_fp32(rdy["row_fp4"], rdy["row_sc_logical"], rdy["sg"], rw["col_fp4"], rw["col_sc_logical"], rw["sg"])
+    torch.cuda.synchronize()
+    assert np.linalg.norm(dx.cpu().numpy() - ref) / np.linalg.norm(ref) <= REL_FRO_TOL
+    full = dy.astype(np.float64) @ w.astype(np.float64)
+    assert np.linalg.norm(dx.cpu().numpy() - full) / np.linalg.norm(full) < 0.25
+    # wgrad: column operand of dY ([N, M/2])  x  column operand of X ([K, M/2])  ->  [N,K]
+    dw = torch.empty((N, K), dtype=torch.float32, device="cuda")
+    gemm.nvfp4_gemm(qdy[2], qdy[3], qdy[5], qx[2], qx[3], qx[5], dw)
+    ref = o.nvfp4_gemm_fp32(rdy["col_fp4"], rdy["col_sc_logical"], rdy["sg"], rx["col_fp4"], rx["col_sc_logical"], rx["sg"])
+    torch.cuda.synchronize()
+    assert np.linalg.norm(dw.cpu().numpy() - ref) / np.linalg.norm(ref) <= REL_FRO_TOL
+    assert_status_ok()
+
+
+def test_grouped_residual_and_batched_accum():
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    M, K, H = 256, 512, 512
+    x = o.make_activations(M, K, seed=4)
+    w1 = o.bf16_round((0.02 * np.random.default_rng(5).standard_normal((H, K))).astype(np.float32))
+    w3 = o.bf16_round((0.05 * np.random.default_rng(6).standard_normal((H, K))).astype(np.float32))
+    qx = tkq.tk_quantize_for_gemm(to_dev_bf16(x), False, True)
+    q1 = tkq.tk_quantize_for_gemm(to_dev_bf16(w1), False, True)
+    q3 = tkq.tk_quantize_for_gemm(to_dev_bf16(w3), False, True)
+    # grouped: concatenated weights, one tensor scale per 256 rows, two outputs
+    b = torch.cat([q1[0].view(torch.uint8), q3[0].view(torch.uint8)], 0)
+    b_sc = torch.cat([q1[1].view(torch.uint8), q3[1].view(torch.uint8)], 0)
+    b_sg = torch.cat([q1[4].expand(H // 256), q3[4].expand(H // 256)]).contiguous()
+    h1 = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    h3 = torch.empty((M, H), dtype=torch.bfloat16, device="cuda")
+    gemm.nvfp4_grouped_gemm(qx[0], qx[1], qx[4], b, b_sc, b_sg, h1, h3)
+    s1 = torch.empty_like(h1); s3 = torch.empty_like(h3)
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], q1[0], q1[1], q1[4], s1)
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], q3[0], q3[1], q3[4], s3)
+    torch.cuda.synchronize()
+    assert torch.equal(h1, s1) and torch.equal(h3, s3)
+    # residual epilogue: D = bf16(bf16(acc*sg) + R)
+    r = torch.randn((M, H), generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).cuda()
+    d = torch.empty_like(h1)
+    gemm.nvfp4_gemm_residual(qx[0], qx[1], qx[4], q1[0], q1[1], q1[4], r, d)
+    torch.cuda.synchronize()
+    assert torch.equal(d, (s1.float() + r.float()).to(torch.bfloat16))
+    # batched accumulate: sum of two products kept in fp32, rounded once
+    acc = torch.empty_like(h1)
+    gemm.nvfp4_batched_accum_gemm([qx[0], qx[0]], [qx[1], qx[1]], [qx[4], qx[4]], [q1[0], q3[0]], [q1[1], q3[1]],
+                                  [q1[4], q3[4]], acc)
+    f1 = torch.empty((M, H), dtype=torch.float32, device="cuda"); f3 = torch.empty_like(f1)
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], q1[0], q1[1], q1[4], f1)
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], q3[0], q3[1], q3[4], f3)
+    torch.cuda.synchronize()
+    assert torch.equal(acc, (f1 + f3).to(torch.bfloat16))
+    assert_status_ok()
