@@ -22,6 +22,7 @@
 #include "fp4_common.cuh"
 #include "host_util.h"
 
+#include <stdlib.h>
 #include <string.h>
 
 namespace fp4b200 {
@@ -180,6 +181,93 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
                ::"l"(tmap), "r"(x), "r"(y), "r"(smem_u32(smem_src))
                : "memory");
+}
+
+// Epilogue of one 128 x 256 accumulator tile by one warp (its 32-lane quadrant): tensor memory ->
+// registers -> scale / accumulate / residual -> swizzled staging -> TMA store.  row0 = first global
+// row of the tile, tn = column-tile index, epi = this warp's two 4 KiB staging buffers.
+__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t tmem, uint8_t* epi,
+                                              int row0, int tn, float a_sg, int quad, int lane) {
+    float gs = a_sg;
+    if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? tn : 0));
+    const int row = row0 + quad * 32 + lane;
+    int col0 = tn * kGemmBN;
+    // which output receives this column tile
+    int oi = 0, col_start = 0;
+    while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
+    const int ocol = col0 - col_start;
+    // 32 columns per tensor-memory load; a slab of 128 bytes per row (64 bf16 or 32 fp32 columns) is
+    // staged in the 128-byte-swizzled layout and written with one TMA store per slab
+    const int chunks_per_slab = g.out_fp32 ? 1 : 2;
+#pragma unroll 1
+    for (int c = 0; c < kGemmBN; c += 32) {
+      const int chunk = c >> 5;
+      const int slab = chunk / chunks_per_slab;
+      uint8_t* buf = epi + (slab & 1) * 4096;
+      uint32_t r[32];
+      tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
+      if ((chunk % chunks_per_slab) == 0) {
+        // the store issued from this buffer two slabs ago must have finished reading it
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+        __syncwarp();
+      }
+      tmem_ld_wait();
+      uint8_t* rowp = buf + lane * 128;
+      if (g.accum_f32 != nullptr) {
+        // running fp32 sum over a batch of GEMMs: partial + acc*scale (multiply, then add)
+        const float4* ps = reinterpret_cast<const float4*>(g.accum_f32 + (size_t)row * g.N + col0 + c);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 pv = __ldg(ps + q);
+          r[4 * q] = __float_as_uint(__fadd_rn(pv.x, __fmul_rn(__uint_as_float(r[4 * q]), gs)));
+          r[4 * q + 1] = __float_as_uint(__fadd_rn(pv.y, __fmul_rn(__uint_as_float(r[4 * q + 1]), gs)));
+          r[4 * q + 2] = __float_as_uint(__fadd_rn(pv.z, __fmul_rn(__uint_as_float(r[4 * q + 2]), gs)));
+          r[4 * q + 3] = __float_as_uint(__fadd_rn(pv.w, __fmul_rn(__uint_as_float(r[4 * q + 3]), gs)));
+        }
+      }
+      const float gs_out = g.accum_f32 != nullptr ? 1.0f : gs;
+      if (g.out_fp32) {
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 v = make_float4(__uint_as_float(r[4 * q]) * gs_out, __uint_as_float(r[4 * q + 1]) * gs_out,
+                                       __uint_as_float(r[4 * q + 2]) * gs_out, __uint_as_float(r[4 * q + 3]) * gs_out);
+          *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) = v;
+        }
+      } else {
+        uint32_t o[16];
+#pragma unroll
+        for (int q = 0; q < 16; ++q)
+          o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs_out, __uint_as_float(r[2 * q + 1]) * gs_out);
+        if (g.residual != nullptr) {
+          const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.residual_ld + col0 + c);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 rv = __ldg(rs + q);
+            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const uint32_t d = o[4 * q + e];
+              o[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]),
+                                             bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
+            }
+          }
+        }
+        const int piece0 = (chunk & 1) * 4;
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(rowp + (((piece0 + q) ^ (lane & 7)) << 4)) =
+              make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+      }
+      if ((chunk % chunks_per_slab) == chunks_per_slab - 1) {
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          const int slab_cols = g.out_fp32 ? 32 : 64;
+          tma_store_2d(&tmap_d.m[oi], buf, ocol + slab * slab_cols, row0 + quad * 32);
+          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        }
+      }
+    }
 }
 
 template <bool MX>
@@ -349,92 +437,13 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       const int tm = t % tiles_m, tn = t / tiles_m;
-      float gs = a_sg;
-      if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? tn : 0));
-      const int row = tm * kGemmBM + quad * 32 + lane;
-      int col0 = tn * kGemmBN;
-      // which output receives this column tile
-      int oi = 0, col_start = 0;
-      while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
-      const int ocol = col0 - col_start;
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;
         break;
       }
       tc_fence_after();
-      // 32 columns per tensor-memory load; a slab of 128 bytes per row (64 bf16 or 32 fp32 columns) is
-      // staged in the 128-byte-swizzled layout and written with one TMA store per slab
-      const int chunks_per_slab = g.out_fp32 ? 1 : 2;
-#pragma unroll 1
-      for (int c = 0; c < kGemmBN; c += 32) {
-        const int chunk = c >> 5;
-        const int slab = chunk / chunks_per_slab;
-        uint8_t* buf = sm.epi[warp - 2][slab & 1];
-        uint32_t r[32];
-        tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
-        if ((chunk % chunks_per_slab) == 0) {
-          // the store issued from this buffer two slabs ago must have finished reading it
-          if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-          __syncwarp();
-        }
-        tmem_ld_wait();
-        uint8_t* rowp = buf + lane * 128;
-        if (g.accum_f32 != nullptr) {
-          // running fp32 sum over a batch of GEMMs: partial + acc*scale (multiply, then add)
-          const float4* ps = reinterpret_cast<const float4*>(g.accum_f32 + (size_t)row * g.N + col0 + c);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 pv = __ldg(ps + q);
-            r[4 * q] = __float_as_uint(__fadd_rn(pv.x, __fmul_rn(__uint_as_float(r[4 * q]), gs)));
-            r[4 * q + 1] = __float_as_uint(__fadd_rn(pv.y, __fmul_rn(__uint_as_float(r[4 * q + 1]), gs)));
-            r[4 * q + 2] = __float_as_uint(__fadd_rn(pv.z, __fmul_rn(__uint_as_float(r[4 * q + 2]), gs)));
-            r[4 * q + 3] = __float_as_uint(__fadd_rn(pv.w, __fmul_rn(__uint_as_float(r[4 * q + 3]), gs)));
-          }
-        }
-        const float gs_out = g.accum_f32 != nullptr ? 1.0f : gs;
-        if (g.out_fp32) {
-#pragma unroll
-          for (int q = 0; q < 8; ++q) {
-            const float4 v = make_float4(__uint_as_float(r[4 * q]) * gs_out, __uint_as_float(r[4 * q + 1]) * gs_out,
-                                         __uint_as_float(r[4 * q + 2]) * gs_out, __uint_as_float(r[4 * q + 3]) * gs_out);
-            *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) = v;
-          }
-        } else {
-          uint32_t o[16];
-#pragma unroll
-          for (int q = 0; q < 16; ++q)
-            o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs_out, __uint_as_float(r[2 * q + 1]) * gs_out);
-          if (g.residual != nullptr) {
-            const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.residual_ld + col0 + c);
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              const uint4 rv = __ldg(rs + q);
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const uint32_t d = o[4 * q + e];
-                o[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]),
-                                               bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
-              }
-            }
-          }
-          const int piece0 = (chunk & 1) * 4;
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            *reinterpret_cast<uint4*>(rowp + (((piece0 + q) ^ (lane & 7)) << 4)) =
-                make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-        }
-        if ((chunk % chunks_per_slab) == chunks_per_slab - 1) {
-          fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) {
-            const int slab_cols = g.out_fp32 ? 32 : 64;
-            tma_store_2d(&tmap_d.m[oi], buf, ocol + slab * slab_cols, tm * kGemmBM + quad * 32);
-            asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-          }
-        }
-      }
+      epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
       // accumulator drained: let the MMA warp start the next tile
       tc_fence_before();
       __syncwarp();
@@ -451,6 +460,18 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     tc_fence_after();
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
   }
+}
+
+}  // namespace fp4b200
+
+#include "gemm_fp4_pair.cuh"
+
+namespace fp4b200 {
+
+// FP4B200_GEMM_PAIR=0 in the environment selects the one-CTA kernel for every shape (A/B comparisons).
+static bool gemm_pair_disabled() {
+  static const bool off = [] { const char* e = getenv("FP4B200_GEMM_PAIR"); return e != nullptr && e[0] == '0'; }();
+  return off;
 }
 
 static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
@@ -485,6 +506,33 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   g.sf_tiles_k = (int)(K / (mx ? 128 : 64));
   g.status = device_status_ptr();
   if (g.status == nullptr) return -1;
+  if ((M % 256) == 0 && !gemm_pair_disabled()) {
+    // two-CTA clusters: one 256 x 256 tile per pair of SMs
+    if (int rc = make_tmap_2d(&tmap_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)N,
+                              (uint64_t)K / 2, kGemmBKBytes, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+    const int psmem = (int)sizeof(GemmPairSmem) + 1024;
+    const int pair_tiles = (int)((M / 256) * (N / kGemmBN));
+    const int clusters = std::min(pair_tiles, device_sm_count() / 2);
+    cudaLaunchConfig_t cfg{};
+    cfg.gridDim = dim3(2 * clusters, 1, 1);
+    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.dynamicSmemBytes = psmem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    if (mx) {
+      FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+      FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<true>, tmap_a, tmap_b, omaps, g));
+    } else {
+      FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+      FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<false>, tmap_a, tmap_b, omaps, g));
+    }
+    return 0;
+  }
   const int smem = (int)sizeof(GemmSmem) + 1024;
   const int n_tiles = (int)((M / kGemmBM) * (N / kGemmBN));
   const int grid = std::min(n_tiles, device_sm_count());
