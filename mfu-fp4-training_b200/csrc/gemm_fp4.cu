@@ -138,6 +138,18 @@ __host__ __device__ constexpr uint32_t block_scaled_idesc(int M, int N, int ue8m
          ((uint32_t)(M >> 4) << 24) | ((uint32_t)sf_id << 4) | ((uint32_t)sf_id << 29);
 }
 
+// Tile order: groups of kRasterGroup row tiles are walked column by column, so that the tiles in
+// flight at one time (one per CTA or CTA pair) cover a compact block of the output and re-use a
+// small set of A and B rows out of L2.
+constexpr int kRasterGroup = 8;
+__device__ __forceinline__ void raster_tile(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_group = kRasterGroup * tiles_n;
+  const int grp = t / per_group, r = t - grp * per_group;
+  const int rows = min(kRasterGroup, tiles_m - grp * kRasterGroup);
+  tn = r / rows;
+  tm = grp * kRasterGroup + (r - tn * rows);
+}
+
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
@@ -310,7 +322,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        const int tm = t % tiles_m, tn = t / tiles_m;
+        int tm, tn;
+        raster_tile(t, tiles_m, tiles_n, tm, tn);
         const uint8_t* sfa_src = g.a_sc + (size_t)tm * g.sf_tiles_k * 512;
         const uint8_t* sfb_src0 = g.b_sc + (size_t)(2 * tn) * g.sf_tiles_k * 512;
         const uint8_t* sfb_src1 = sfb_src0 + (size_t)g.sf_tiles_k * 512;
@@ -436,7 +449,8 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     if (g.a_sg != nullptr) a_sg = __ldg(g.a_sg);
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-      const int tm = t % tiles_m, tn = t / tiles_m;
+      int tm, tn;
+        raster_tile(t, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;

@@ -115,17 +115,27 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
+      uint32_t empty_peer[kPairStages];
+#pragma unroll
+      for (int s = 0; s < kPairStages; ++s) empty_peer[s] = map_to_cta(&sm.empty[s], 1);
+      int filled = 0;
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-        const int tm = t % tiles_m, tn = t / tiles_m;
+        int tm, tn;
+        raster_tile(t, tiles_m, tiles_n, tm, tn);
         const uint8_t* sfa_src = g.a_sc + (size_t)(2 * tm + rank) * g.sf_tiles_k * 512;
         const uint8_t* sfb_src0 = g.b_sc + (size_t)(2 * tn) * g.sf_tiles_k * 512;
         const uint8_t* sfb_src1 = sfb_src0 + (size_t)g.sf_tiles_k * 512;
         for (int ks = 0; ks < k_stages; ++ks) {
+          const bool first_fill = filled < kPairStages;   // the first use of a stage waits for nothing
+          ++filled;
           if (!mbar_wait_timed(&sm.empty[stage], phase ^ 1)) {
             atomicExch(g.status, kStatusGemmTmaTimeout);
             ok = false;
             break;
           }
+          // the leader's barrier is signalled by tcgen05.commit; it passes the news on to the other CTA
+          // (one commit per stage instead of two keeps the tensor pipe's queue short)
+          if (rank == 0 && !first_fill) mbar_arrive_cluster(empty_peer[stage]);
           mbar_expect_tx(&sm.full[stage], kATileBytes + kPairBHalfBytes + 3 * kSfPerStage);
           tma_load_2d(sm.a[stage], &tmap_a, ks * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
           tma_load_2d(sm.b[stage], &tmap_b, ks * kGemmBKBytes, tn * kGemmBN + (int)rank * 128, &sm.full[stage]);
@@ -142,10 +152,6 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
-      uint32_t empty_remote[kPairStages];
-#pragma unroll
-      for (int s = 0; s < kPairStages; ++s) empty_remote[s] = map_to_cta(&sm.empty[s], 1);
-      const uint32_t acc_full_remote = map_to_cta(&sm.acc_full, 1);
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
         if (!mbar_wait_timed(&sm.acc_empty, acc_phase ^ 1)) {
           atomicExch(g.status, kStatusGemmEpilogueTimeout);
@@ -176,14 +182,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
                                 sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
             }
           }
-          tc_commit_pair(smem_u32(&sm.empty[stage]));   // own stage buffer
-          tc_commit_pair(empty_remote[stage]);          // the other CTA's stage buffer
+          tc_commit_pair(smem_u32(&sm.empty[stage]));   // the producer forwards it to the other CTA
           if (++stage == kPairStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) {
-          tc_commit_pair(smem_u32(&sm.acc_full));
-          tc_commit_pair(acc_full_remote);
-        }
+        if (ok) tc_commit_pair(smem_u32(&sm.acc_full));   // an epilogue warp forwards it to the other CTA
         acc_phase ^= 1;
       }
     }
@@ -235,14 +237,17 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     float a_sg = g.fixed_scale;
     if (g.a_sg != nullptr) a_sg = __ldg(g.a_sg);
     const uint32_t acc_empty_leader = map_to_cta(&sm.acc_empty, 0);
+    const uint32_t acc_full_peer = map_to_cta(&sm.acc_full, 1);
     bool ok = true;
     for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-      const int tm = t % tiles_m, tn = t / tiles_m;
+      int tm, tn;
+        raster_tile(t, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;
         break;
       }
+      if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(acc_full_peer);
       tc_fence_after();
       epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad, lane);
       tc_fence_before();
