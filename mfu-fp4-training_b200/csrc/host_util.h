@@ -46,14 +46,18 @@ struct QuantOpt {
 };
 
 // Launchers defined in quant_nvfp4.cu and shared with the other producers.
-// amax_sg[0] = max|x|, amax_sg[1] = amax/2688 (cleared and recomputed on the stream).
-int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st);
+// amax_sg[0] = max|x|, amax_sg[1] = amax/2688 (cleared and recomputed on the stream; with
+// finalize == false the division is left to the quantiser launched next, via its sg_out).
+int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st, bool finalize = true);
 // Row (+ column when col_* non-null) NVFP4 quantisation from device-resident amaxes; RMSNorm is
 // applied on the fly when inv_rms/gamma are given; reverse walks the chunks back to front;
 // weight_2d shares one scale per 16x16 tile between the two orientations (decode-centric).
+// behind_pass1: the kernel launched just before on st is this library's own amax / statistics
+// kernel over the same x (which it only reads), so the quantiser may be launched programmatically
+// dependent on it and fetch its first chunks while that kernel drains.
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                     bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4, void* row_sc,
                     void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st, bool weight_2d = false,
-                    const QuantOpt* opt = nullptr);
+                    const QuantOpt* opt = nullptr, bool behind_pass1 = false);
 
 }  // namespace fp4b200

@@ -19,6 +19,7 @@ namespace fp4b200 {
 
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, size_t n_vec,
                                                         float* __restrict__ amax) {
+  pdl_launch_dependents();   // a quantiser launched behind this kernel may set up and prefetch meanwhile
   uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -62,61 +63,50 @@ __global__ void finalize_sg_kernel(float* __restrict__ amax_sg) { amax_sg[1] = a
 // virtual lanes 4L+128i+q (i = 0,1; q = 0..3) in acc[i][q], so the butterfly levels map to
 // shuffles over lane masks 4,2,1, register adds over q, a register add over i, and
 // shuffles over lane masks 16,8.
-constexpr int kStatsThreads = 128;
+constexpr int kStatsMaxWarps = 12;   // warps per CTA, one CTA per SM
+constexpr int kStatsDepth = 2;       // row slots per warp
 
+// Sum of squares of the row held in v -> 1/rms, identical on all lanes.
 template <int NV>
-__device__ __forceinline__ void stats_load_row(uint4 (&v)[NV], const __nv_bfloat16* x, int row, int K, int lane) {
-  const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
-  const int nvec_row = K >> 3;
+__device__ __forceinline__ float stats_inv_rms(const uint4 (&v)[NV], int K, float eps) {
+  // acc[i][q]: virtual lane 4*lane + 128*i + q; packed as pairs (q, q+1)
+  float2 acc[2][2] = {{{0, 0}, {0, 0}}, {{0, 0}, {0, 0}}};
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
-    const int q = lane + 32 * j;
-    v[j] = (q < nvec_row) ? __ldg(xr + q) : make_uint4(0, 0, 0, 0);
+    const int i = j & 1;
+    const float2 lo01 = make_float2(bf16lo_to_f32(v[j].x), bf16lo_to_f32(v[j].y));
+    const float2 hi01 = make_float2(bf16hi_to_f32(v[j].x), bf16hi_to_f32(v[j].y));
+    const float2 lo23 = make_float2(bf16lo_to_f32(v[j].z), bf16lo_to_f32(v[j].w));
+    const float2 hi23 = make_float2(bf16hi_to_f32(v[j].z), bf16hi_to_f32(v[j].w));
+    acc[i][0] = fma2(lo01, lo01, acc[i][0]);
+    acc[i][0] = fma2(hi01, hi01, acc[i][0]);
+    acc[i][1] = fma2(lo23, lo23, acc[i][1]);
+    acc[i][1] = fma2(hi23, hi23, acc[i][1]);
   }
+  float part[2];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    float a4[4] = {acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 4);
+      a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 2);
+      a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 1);
+    }
+    const float a = a4[0] + a4[2];
+    const float b = a4[1] + a4[3];
+    part[i] = a + b;
+  }
+  float s = part[0] + part[1];
+  s += __shfl_xor_sync(0xffffffffu, s, 16);
+  s += __shfl_xor_sync(0xffffffffu, s, 8);
+  return rsqrtf(s / static_cast<float>(K) + eps);
 }
 
-// One row held in registers: inverse RMS (reference summation tree) and |bf16(x*inv*gamma)| max.
-template <int NV, bool COMPUTE_INV_RMS>
-__device__ __forceinline__ uint32_t stats_process_row(const uint4 (&v)[NV], const float2* gamma_s, float* inv_rms,
-                                                      int row, int K, float eps, int lane, uint32_t mx) {
-  float inv;
-  if constexpr (COMPUTE_INV_RMS) {
-    // acc[i][q]: virtual lane 4*lane + 128*i + q; packed as pairs (q, q+1)
-    float2 acc[2][2] = {{{0, 0}, {0, 0}}, {{0, 0}, {0, 0}}};
-#pragma unroll
-    for (int j = 0; j < NV; ++j) {
-      const int i = j & 1;
-      const float2 lo01 = make_float2(bf16lo_to_f32(v[j].x), bf16lo_to_f32(v[j].y));
-      const float2 hi01 = make_float2(bf16hi_to_f32(v[j].x), bf16hi_to_f32(v[j].y));
-      const float2 lo23 = make_float2(bf16lo_to_f32(v[j].z), bf16lo_to_f32(v[j].w));
-      const float2 hi23 = make_float2(bf16hi_to_f32(v[j].z), bf16hi_to_f32(v[j].w));
-      acc[i][0] = fma2(lo01, lo01, acc[i][0]);
-      acc[i][0] = fma2(hi01, hi01, acc[i][0]);
-      acc[i][1] = fma2(lo23, lo23, acc[i][1]);
-      acc[i][1] = fma2(hi23, hi23, acc[i][1]);
-    }
-    float part[2];
-#pragma unroll
-    for (int i = 0; i < 2; ++i) {
-      float a4[4] = {acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y};
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 4);
-        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 2);
-        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 1);
-      }
-      const float a = a4[0] + a4[2];
-      const float b = a4[1] + a4[3];
-      part[i] = a + b;
-    }
-    float s = part[0] + part[1];
-    s += __shfl_xor_sync(0xffffffffu, s, 16);
-    s += __shfl_xor_sync(0xffffffffu, s, 8);
-    inv = rsqrtf(s / static_cast<float>(K) + eps);
-    if (lane == 0) inv_rms[row] = inv;
-  } else {
-    inv = __ldg(inv_rms + row);
-  }
+// Running |bf16(x * inv * gamma)| maximum (packed bf16x2) over the row held in v.
+template <int NV>
+__device__ __forceinline__ uint32_t stats_row_amax(const uint4 (&v)[NV], const float2* gamma_s, float inv, int K,
+                                                   int lane, uint32_t mx) {
   const float2 inv2 = make_float2(inv, inv);
   const int nvec_row = K >> 3;
 #pragma unroll
@@ -138,34 +128,80 @@ __device__ __forceinline__ uint32_t stats_process_row(const uint4 (&v)[NV], cons
   return mx;
 }
 
-// One warp per row, two rows in flight per warp (the next row's loads are issued before the
-// current row is reduced), so that every warp always has a row of HBM traffic outstanding.
+// One CTA per SM; every warp is its own pipeline: rows arrive in the warp's two shared-memory slots
+// by bulk copies that its lane 0 issues (one row = one contiguous copy), are lifted into registers,
+// and the slot is refilled as soon as the row's sum of squares has been reduced (the reduction needs
+// every lane's values, so all reads of the slot are complete by then).  Bytes in flight per SM are
+// set by the slots (warps x 2 rows), not by registers, which is what a streaming reduction at HBM
+// speed needs; no CTA-wide barrier after start-up.
 template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS>
-__global__ void __launch_bounds__(kStatsThreads, 2)
+__global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
-                     float* __restrict__ inv_rms, float* __restrict__ amax, float eps, int M, int K) {
-  extern __shared__ float2 gamma_f2[];   // gamma as fp32 pairs, one copy per CTA
-  for (int q = threadIdx.x; q < (K >> 1); q += kStatsThreads) {
+                     float* __restrict__ inv_rms, float* __restrict__ amax, float eps, int M, int K,
+                     int* __restrict__ status) {
+  extern __shared__ __align__(128) uint8_t stats_smem[];
+  pdl_launch_dependents();   // the quantiser launched behind this kernel may set up and prefetch meanwhile
+  const int warps = blockDim.x >> 5;
+  const uint32_t row_bytes = (uint32_t)K * 2u;
+  float2* gamma_f2 = reinterpret_cast<float2*>(stats_smem);                 // [K/2] gamma as fp32 pairs
+  uint8_t* slots = stats_smem + (size_t)K * 4;                              // [warps][kStatsDepth][row_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t)warps * kStatsDepth * row_bytes);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < warps * kStatsDepth; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+  }
+  for (int q = threadIdx.x; q < (K >> 1); q += blockDim.x) {
     const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(gamma) + q);
     gamma_f2[q] = make_float2(bf16lo_to_f32(w), bf16hi_to_f32(w));
   }
   __syncthreads();
-  const int lane = threadIdx.x & 31;
-  const int warp_global = blockIdx.x * (kStatsThreads >> 5) + (threadIdx.x >> 5);
-  const int n_warps = gridDim.x * (kStatsThreads >> 5);
+
+  const int stride = gridDim.x * warps;
+  const int row0 = blockIdx.x * warps + warp;
+  uint8_t* my_slots = slots + (size_t)warp * kStatsDepth * row_bytes;
+  uint64_t* my_bars = bars + warp * kStatsDepth;
+  auto issue = [&](int row, int d) {
+    mbar_expect_tx(&my_bars[d], row_bytes);
+    bulk_load_1d(my_slots + (size_t)d * row_bytes, x + (size_t)row * K, row_bytes, &my_bars[d]);
+  };
+  if (lane == 0) {
+#pragma unroll
+    for (int d = 0; d < kStatsDepth; ++d)
+      if (row0 + d * stride < M) issue(row0 + d * stride, d);
+  }
   uint32_t mx = 0;
-  uint4 va[NV], vb[NV];
-  int row = warp_global;
-  if (row < M) stats_load_row<NV>(va, x, row, K, lane);
-  while (row < M) {
-    const int row_b = row + n_warps;
-    if (row_b < M) stats_load_row<NV>(vb, x, row_b, K, lane);
-    mx = stats_process_row<NV, COMPUTE_INV_RMS>(va, gamma_f2, inv_rms, row, K, eps, lane, mx);
-    if (row_b >= M) break;
-    const int row_c = row_b + n_warps;
-    if (row_c < M) stats_load_row<NV>(va, x, row_c, K, lane);
-    mx = stats_process_row<NV, COMPUTE_INV_RMS>(vb, gamma_f2, inv_rms, row_b, K, eps, lane, mx);
-    row = row_c;
+  const int nvec_row = K >> 3;
+  int it = 0;
+  for (int row = row0; row < M; row += stride, ++it) {
+    const int d = it % kStatsDepth;
+    if (!mbar_wait_bounded(&my_bars[d], (uint32_t)(it / kStatsDepth) & 1u)) {
+      if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
+      break;
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(my_slots + (size_t)d * row_bytes);
+    uint4 v[NV];
+#pragma unroll
+    for (int j = 0; j < NV; ++j) {
+      const int q = lane + 32 * j;
+      v[j] = (q < nvec_row) ? src[q] : make_uint4(0, 0, 0, 0);
+    }
+    const int next = row + kStatsDepth * stride;
+    float inv;
+    if constexpr (COMPUTE_INV_RMS) {
+      inv = stats_inv_rms<NV>(v, K, eps);
+      if (lane == 0) {
+        inv_rms[row] = inv;
+        if (next < M) issue(next, d);
+      }
+      mx = stats_row_amax<NV>(v, gamma_f2, inv, K, lane, mx);
+    } else {
+      inv = __ldg(inv_rms + row);
+      mx = stats_row_amax<NV>(v, gamma_f2, inv, K, lane, mx);
+      // every lane's copy of the row has been consumed by the arithmetic above
+      __syncwarp();
+      if (lane == 0 && next < M) issue(next, d);
+    }
   }
   float run_max = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
   run_max = warp_max(run_max);
@@ -447,12 +483,15 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     tma_prefetch_desc(&tmap_x);
     for (int s = 0; s < kQStages; ++s) mbar_init(&sm.full[s], 1);
     fence_mbar_init();
-    if (blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = *a.amax_row / 2688.0f;
   }
   __syncthreads();
   if (tid == 0) {
     for (int s = 0; s < kQStages && s < my_count; ++s) issue_load(s, s);
   }
+  // The input is never written by the pass-1 kernel this one may have been launched behind, so the
+  // first chunks are already on their way; amax / inv_rms are that kernel's results.
+  pdl_wait();
+  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = *a.amax_row / 2688.0f;
 
   const float s_enc_row = nvfp4_global_encode_scale(*a.amax_row);
   const float s_enc_col = nvfp4_global_encode_scale(*a.amax_col);
@@ -491,13 +530,14 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     const int pp = it & 1;
 
     // prefetch the next chunk's inv_rms / gamma into a register (stored after the column pass)
-    float pre = 0.0f;
+    // (raw bits: converting here would wait for the load before the chunk's work starts)
+    uint32_t pre = 0;
     if constexpr (NORM) {
       if (it + 1 < my_count) {
         int ncm, nck;
         chunk_coords(it + 1, ncm, nck);
-        pre = (tid < kChunk) ? __ldg(a.inv_rms + ncm * kChunk + tid)
-                             : __bfloat162float(a.gamma[nck * kChunk + tid - kChunk]);
+        pre = (tid < kChunk) ? __ldg(reinterpret_cast<const uint32_t*>(a.inv_rms) + ncm * kChunk + tid)
+                             : (uint32_t)__ldg(reinterpret_cast<const uint16_t*>(a.gamma) + nck * kChunk + tid - kChunk) << 16;
       }
     }
 
@@ -678,8 +718,8 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
     }
     if constexpr (NORM) {
       // the other inv_rms/gamma buffer was last read in the previous chunk's row pass
-      if (tid < kChunk) sm.inv_rms[pp ^ 1][tid] = pre;
-      else sm.gamma[pp ^ 1][tid - kChunk] = pre;
+      if (tid < kChunk) sm.inv_rms[pp ^ 1][tid] = __uint_as_float(pre);
+      else sm.gamma[pp ^ 1][tid - kChunk] = __uint_as_float(pre);
     }
     __syncthreads();
 
@@ -768,7 +808,7 @@ rht16_amax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 // Host launchers
 // ---------------------------------------------------------------------------------------
 
-int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st) {
+int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st, bool finalize) {
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
   const size_t n_vec = (size_t)n_elems / 8;
   if (n_vec > 0) {
@@ -776,28 +816,39 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st)
     amax_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(x), n_vec, amax_sg);
     FP4_CUDA_CHECK(cudaGetLastError());
   }
-  finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
-  FP4_CUDA_CHECK(cudaGetLastError());
+  if (finalize) {
+    finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
+    FP4_CUDA_CHECK(cudaGetLastError());
+  }
   return 0;
 }
 
 template <bool EC, bool NORM, bool W2D = false, bool OPT = false>
-static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cudaStream_t st) {
+static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cudaStream_t st, bool pdl) {
   auto kern = nvfp4_quantize_kernel<EC, NORM, W2D, OPT>;
   const int smem = (int)sizeof(QuantSmem) + 1024;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_chunks = args.chunks_m * args.chunks_k;
   const int grid = std::min(n_chunks, (OPT ? 1 : 2) * device_sm_count());
   if (grid == 0) return 0;
-  kern<<<grid, kQThreads, smem, st>>>(tmap, args);
-  FP4_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kQThreads);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, args));
   return 0;
 }
 
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
-                           cudaStream_t st, bool weight_2d, const QuantOpt* opt) {
+                           cudaStream_t st, bool weight_2d, const QuantOpt* opt, bool behind_pass1) {
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                             (uint64_t)K * 2, 64, kChunk, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -820,39 +871,66 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
     a.opt_sr = opt->sr; a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
     a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
-    if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st)
-                                    : launch_quantize_t<true, false, false, true>(tmap, a, st);
-    return norm ? launch_quantize_t<false, true, false, true>(tmap, a, st)
-                : launch_quantize_t<false, false, false, true>(tmap, a, st);
+    if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st, behind_pass1)
+                                    : launch_quantize_t<true, false, false, true>(tmap, a, st, behind_pass1);
+    return norm ? launch_quantize_t<false, true, false, true>(tmap, a, st, behind_pass1)
+                : launch_quantize_t<false, false, false, true>(tmap, a, st, behind_pass1);
   }
-  if (weight_2d) return launch_quantize_t<false, false, true>(tmap, a, st);   // decode-centric, as the reference
-  if (encode_centric) return norm ? launch_quantize_t<true, true>(tmap, a, st) : launch_quantize_t<true, false>(tmap, a, st);
-  return norm ? launch_quantize_t<false, true>(tmap, a, st) : launch_quantize_t<false, false>(tmap, a, st);
+  if (weight_2d) return launch_quantize_t<false, false, true>(tmap, a, st, behind_pass1);   // decode-centric, as the reference
+  if (encode_centric) return norm ? launch_quantize_t<true, true>(tmap, a, st, behind_pass1) : launch_quantize_t<true, false>(tmap, a, st, behind_pass1);
+  return norm ? launch_quantize_t<false, true>(tmap, a, st, behind_pass1) : launch_quantize_t<false, false>(tmap, a, st, behind_pass1);
+}
+
+// Warps per CTA of the pipelined statistics kernel for rows of K elements (0: rows too long for it).
+static int stats_warps_for(int64_t K) {
+  const int64_t budget = 227 * 1024 - K * 4 - 512;
+  const int64_t w = budget / (kStatsDepth * K * 2);
+  const int64_t cap = K <= 4096 ? kStatsMaxWarps : 6;
+  return (int)std::max<int64_t>(0, std::min<int64_t>(w, cap));
+}
+
+template <int NV, bool CI>
+static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* amax_sg, float eps,
+                          int64_t M, int64_t K, int warps, int* status, cudaStream_t st) {
+  auto kern = rmsnorm_stats_kernel<NV, CI>;
+  const size_t smem = (size_t)K * 4 + (size_t)warps * kStatsDepth * K * 2 + (size_t)warps * kStatsDepth * 8;
+  FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
+  kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K, status);
+  return 0;
 }
 
 static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms, float* amax_sg, float eps,
-                                int64_t M, int64_t K, bool compute_inv, cudaStream_t st) {
+                                int64_t M, int64_t K, bool compute_inv, cudaStream_t st, bool finalize = true) {
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
-  const int warps_per_block = kStatsThreads / 32;
-  int grid = (int)std::min<int64_t>((M + warps_per_block - 1) / warps_per_block, (int64_t)device_sm_count() * 2);
-  if (grid > 0) {
+  if (M > 0) {
     auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
     auto gb = reinterpret_cast<const __nv_bfloat16*>(gamma);
-    if (K <= 2048) {
-      if (compute_inv) rmsnorm_stats_kernel<8, true><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-      else rmsnorm_stats_kernel<8, false><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-    } else if (K <= 4096) {
-      if (compute_inv) rmsnorm_stats_kernel<16, true><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-      else rmsnorm_stats_kernel<16, false><<<grid, kStatsThreads, (size_t)K * 4, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
+    const int warps = stats_warps_for(K);
+    int rc = 0;
+    if (K <= 8192 && warps >= 2) {
+      int* status = device_status_ptr();
+      if (status == nullptr) return -1;
+      if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
+                                      : launch_stats_t<4, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
+      else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
+                                           : launch_stats_t<8, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
+      else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
+                                           : launch_stats_t<16, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
+      else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
+                            : launch_stats_t<32, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
+      if (rc) return rc;
     } else {
-      grid = (int)std::min<int64_t>((M + 7) / 8, (int64_t)device_sm_count() * 8);
+      const int grid = (int)std::min<int64_t>((M + 7) / 8, (int64_t)device_sm_count() * 8);
       if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
       else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
     }
     FP4_CUDA_CHECK(cudaGetLastError());
   }
-  finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
-  FP4_CUDA_CHECK(cudaGetLastError());
+  if (finalize) {
+    finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
+    FP4_CUDA_CHECK(cudaGetLastError());
+  }
   return 0;
 }
 
@@ -898,10 +976,10 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
     return set_error("nvfp4_quantize_for_gemm: row_fp4, row_sc and amax_sg are required");
   if (return_transpose && (col_fp4 == nullptr || col_sc == nullptr))
     return set_error("nvfp4_quantize_for_gemm: return_transpose needs col_fp4 and col_sc");
-  if (int rc = launch_amax(x_bf16, M * K, amax_sg, (cudaStream_t)stream)) return rc;
+  if (int rc = launch_amax(x_bf16, M * K, amax_sg, (cudaStream_t)stream, false)) return rc;
   return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
-                         return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr,
-                         true, (cudaStream_t)stream);
+                         return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, amax_sg + 1,
+                         true, (cudaStream_t)stream, false, nullptr, true);
 }
 
 int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
@@ -950,9 +1028,9 @@ int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
   if (int rc = check_quant_shapes(w_bf16, N, K, "nvfp4_quantize_weight_2d")) return rc;
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc || !amax_sg)
     return set_error("nvfp4_quantize_weight_2d: all outputs are required");
-  if (int rc = launch_amax(w_bf16, N * K, amax_sg, (cudaStream_t)stream)) return rc;
+  if (int rc = launch_amax(w_bf16, N * K, amax_sg, (cudaStream_t)stream, false)) return rc;
   return launch_quantize(w_bf16, N, K, amax_sg, amax_sg, false, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc,
-                         nullptr, true, (cudaStream_t)stream, true);
+                         amax_sg + 1, true, (cudaStream_t)stream, true, nullptr, true);
 }
 
 int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
@@ -977,10 +1055,10 @@ int fp4b200_nvfp4_fused_norm_quantize(const void* x_bf16, const void* gamma_bf16
   if ((reinterpret_cast<uintptr_t>(gamma_bf16) & 15) != 0)
     return set_error("nvfp4_fused_norm_quantize: gamma must be 16-byte aligned");
   if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, compute_inv_rms != 0,
-                                    (cudaStream_t)stream))
+                                    (cudaStream_t)stream, false))
     return rc;
   return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, encode_centric != 0, inv_rms, gamma_bf16, row_fp4,
-                         row_sc, col_fp4, col_sc, nullptr, true, (cudaStream_t)stream);
+                         row_sc, col_fp4, col_sc, amax_sg + 1, true, (cudaStream_t)stream, false, nullptr, true);
 }
 
 
@@ -1043,10 +1121,10 @@ int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* ga
   if (scratch == nullptr) return -1;
   float* amax_sg = scratch;        // [0] amax (cleared by the statistics launcher), [1] sg
   float* inv_rms = scratch + 64;   // [M]
-  if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, true, (cudaStream_t)stream))
+  if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, true, (cudaStream_t)stream, false))
     return rc;
   return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, true, inv_rms, gamma_bf16, row_fp4, row_sc, col_fp4,
-                         col_sc, sg_out, true, (cudaStream_t)stream);
+                         col_sc, sg_out, true, (cudaStream_t)stream, false, nullptr, true);
 }
 
 }  // extern "C"
