@@ -137,6 +137,13 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) {
   return (uint32_t)__cvta_generic_to_shared(p);
 }
 
+// First 1024-byte boundary at or after p inside the dynamic shared-memory array.  The pad is added to
+// the array's own pointer (no round trip through an integer), so that the compiler still knows that
+// everything derived from the result is shared memory and emits shared loads and stores, not generic ones.
+__device__ __forceinline__ uint8_t* smem_align_1024(uint8_t* p) {
+  return p + ((1024u - (smem_u32(p) & 1023u)) & 1023u);
+}
+
 __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
   asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
 }
@@ -179,6 +186,19 @@ __device__ __forceinline__ void fence_proxy_async_smem() {
 __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
+
+// 2-D tiled TMA store shared -> global of one box; completion is tracked by the thread's bulk async-group.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
+               ::"l"(tmap), "r"(x), "r"(y), "r"(smem_u32(smem_src))
+               : "memory");
+}
+
+__device__ __forceinline__ void bulk_commit_group() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// earlier bulk stores of this thread have finished READING shared memory (the source may be overwritten)
+__device__ __forceinline__ void bulk_wait_group_read0() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
+// earlier bulk stores of this thread are complete
+__device__ __forceinline__ void bulk_wait_group0() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 
 // Programmatic dependent launch: a kernel launched with the programmatic-serialisation attribute may
 // start while its predecessor in the stream still runs; everything the predecessor wrote is
@@ -228,6 +248,9 @@ __device__ __forceinline__ float warp_max(float v) {
 // Streaming (evict-first) 8- and 16-byte stores for write-once outputs.
 __device__ __forceinline__ void st_cs_u2(void* p, uint2 v) {
   asm volatile("st.global.cs.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
+}
+__device__ __forceinline__ void st_cs_u16(void* p, uint16_t v) {
+  asm volatile("st.global.cs.u16 [%0], %1;" ::"l"(p), "h"(v) : "memory");
 }
 __device__ __forceinline__ void st_cs_u32(void* p, uint32_t v) {
   asm volatile("st.global.cs.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");

@@ -183,12 +183,6 @@ struct GemmOutMaps {
   CUtensorMap m[3];
 };
 
-__device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
-               ::"l"(tmap), "r"(x), "r"(y), "r"(smem_u32(smem_src))
-               : "memory");
-}
-
 // Epilogue of one 128 x 256 accumulator tile by one warp (its 32-lane quadrant): tensor memory ->
 // registers -> scale / accumulate / residual -> swizzled staging -> TMA store.  row0 = first global
 // row of the tile, tn = column-tile index, epi = this warp's two 4 KiB staging buffers.
@@ -280,8 +274,8 @@ template <bool MX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                 const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
-  extern __shared__ uint8_t smem_raw[];
-  GemmSmem& sm = *reinterpret_cast<GemmSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  GemmSmem& sm = *reinterpret_cast<GemmSmem*>(smem_align_1024(smem_raw));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;

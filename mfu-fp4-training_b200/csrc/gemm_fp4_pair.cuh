@@ -75,8 +75,8 @@ template <bool MX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                      const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
-  extern __shared__ uint8_t smem_raw[];
-  GemmPairSmem& sm = *reinterpret_cast<GemmPairSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  GemmPairSmem& sm = *reinterpret_cast<GemmPairSmem*>(smem_align_1024(smem_raw));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs)
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;

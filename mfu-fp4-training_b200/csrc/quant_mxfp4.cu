@@ -62,8 +62,8 @@ __device__ __forceinline__ float mx_coeff(uint32_t e) {
 template <bool NORM>
 __global__ void __launch_bounds__(kMxThreads, 2)
 mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  MxSmem& sm = *reinterpret_cast<MxSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  MxSmem& sm = *reinterpret_cast<MxSmem*>(smem_align_1024(smem_raw));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int n_chunks = a.chunks_m * a.chunks_k;
   const int first = blockIdx.x, step = gridDim.x;

@@ -103,9 +103,11 @@ __device__ __forceinline__ float stats_inv_rms(const uint4 (&v)[NV], int K, floa
   return rsqrtf(s / static_cast<float>(K) + eps);
 }
 
-// Running |bf16(x * inv * gamma)| maximum (packed bf16x2) over the row held in v.
+// Running |bf16(x * inv * gamma)| maximum (packed bf16x2) over the row held in v.  gamma stays packed
+// bf16 in shared memory: one conflict-free 16-byte read per vector (an fp32 copy would cost four times
+// the shared-memory bandwidth, which is what bounded this kernel before).
 template <int NV>
-__device__ __forceinline__ uint32_t stats_row_amax(const uint4 (&v)[NV], const float2* gamma_s, float inv, int K,
+__device__ __forceinline__ uint32_t stats_row_amax(const uint4 (&v)[NV], const uint4* gamma_s, float inv, int K,
                                                    int lane, uint32_t mx) {
   const float2 inv2 = make_float2(inv, inv);
   const int nvec_row = K >> 3;
@@ -113,12 +115,15 @@ __device__ __forceinline__ uint32_t stats_row_amax(const uint4 (&v)[NV], const f
   for (int j = 0; j < NV; ++j) {
     const int q = lane + 32 * j;
     if (q < nvec_row) {
-      const float4 g01 = *reinterpret_cast<const float4*>(gamma_s + 4 * q);
-      const float4 g23 = *reinterpret_cast<const float4*>(gamma_s + 4 * q + 2);
-      float2 t0 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2), make_float2(g01.x, g01.y));
-      float2 t1 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2), make_float2(g01.z, g01.w));
-      float2 t2 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2), make_float2(g23.x, g23.y));
-      float2 t3 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2), make_float2(g23.z, g23.w));
+      const uint4 g = gamma_s[q];
+      float2 t0 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2),
+                       make_float2(bf16lo_to_f32(g.x), bf16hi_to_f32(g.x)));
+      float2 t1 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2),
+                       make_float2(bf16lo_to_f32(g.y), bf16hi_to_f32(g.y)));
+      float2 t2 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2),
+                       make_float2(bf16lo_to_f32(g.z), bf16hi_to_f32(g.z)));
+      float2 t3 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2),
+                       make_float2(bf16lo_to_f32(g.w), bf16hi_to_f32(g.w)));
       mx = absmax_xs(mx, f32x2_to_bf16x2(t0.x, t0.y));
       mx = absmax_xs(mx, f32x2_to_bf16x2(t1.x, t1.y));
       mx = absmax_xs(mx, f32x2_to_bf16x2(t2.x, t2.y));
@@ -143,18 +148,15 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   pdl_launch_dependents();   // the quantiser launched behind this kernel may set up and prefetch meanwhile
   const int warps = blockDim.x >> 5;
   const uint32_t row_bytes = (uint32_t)K * 2u;
-  float2* gamma_f2 = reinterpret_cast<float2*>(stats_smem);                 // [K/2] gamma as fp32 pairs
-  uint8_t* slots = stats_smem + (size_t)K * 4;                              // [warps][kStatsDepth][row_bytes]
+  uint4* gamma_s = reinterpret_cast<uint4*>(stats_smem);                    // [K/8] gamma, packed bf16
+  uint8_t* slots = stats_smem + (size_t)K * 2;                              // [warps][kStatsDepth][row_bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t)warps * kStatsDepth * row_bytes);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) {
     for (int i = 0; i < warps * kStatsDepth; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
   }
-  for (int q = threadIdx.x; q < (K >> 1); q += blockDim.x) {
-    const uint32_t w = __ldg(reinterpret_cast<const uint32_t*>(gamma) + q);
-    gamma_f2[q] = make_float2(bf16lo_to_f32(w), bf16hi_to_f32(w));
-  }
+  for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) gamma_s[q] = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
   __syncthreads();
 
   const int stride = gridDim.x * warps;
@@ -194,10 +196,10 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         inv_rms[row] = inv;
         if (next < M) issue(next, d);
       }
-      mx = stats_row_amax<NV>(v, gamma_f2, inv, K, lane, mx);
+      mx = stats_row_amax<NV>(v, gamma_s, inv, K, lane, mx);
     } else {
       inv = __ldg(inv_rms + row);
-      mx = stats_row_amax<NV>(v, gamma_f2, inv, K, lane, mx);
+      mx = stats_row_amax<NV>(v, gamma_s, inv, K, lane, mx);
       // every lane's copy of the row has been consumed by the arithmetic above
       __syncwarp();
       if (lane == 0 && next < M) issue(next, d);
@@ -455,8 +457,8 @@ __device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, bool sign, 
 template <bool ENCODE_CENTRIC, bool NORM, bool W2D, bool OPT>
 __global__ void __launch_bounds__(kQThreads, OPT ? 1 : 2)
 nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArgs a) {
-  extern __shared__ uint8_t smem_raw[];
-  QuantSmem& sm = *reinterpret_cast<QuantSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  QuantSmem& sm = *reinterpret_cast<QuantSmem*>(smem_align_1024(smem_raw));
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
@@ -753,6 +755,248 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
 }
 
 
+// ---------------------------------------------------------------------------------------
+// Row + column quantiser, warp-autonomous form (round-to-nearest, 1-D blocks)
+// ---------------------------------------------------------------------------------------
+//
+// One CTA of 16 warps per SM and no CTA-wide barrier after start-up.  A warp owns a strip of
+// 32 rows x 64 columns (one TMA box, 4 KiB, 128-byte swizzle), two private strip slots with one
+// mbarrier each, and 2 KiB of staging for its codes; it quantises its strip in both orientations
+// by itself:
+//   row pass   : lane = row; eight conflict-free 16-byte reads, optional RMSNorm (normalised bf16
+//                written back for the column pass), four 16-blocks -> 32 bytes of codes (staged)
+//                and one 32-bit word of scales (stored straight to global memory);
+//   column pass: lane = column pair; 32 conflict-free 4-byte reads, two 16-row blocks per column
+//                -> 16 bytes of codes per column (staged) and two scale bytes (stored directly).
+// The staged codes leave as two TMA stores per strip (32 rows x 32 B into [M, K/2], 64 rows x 16 B
+// into [K, M/2]): the L1 data path, which carries shared-memory traffic as well as global stores,
+// is the busiest unit of this kernel, and a per-lane store instruction touching 32 lines occupies
+// it 32 times longer than the same bytes staged once.
+// Eight warps (4 down x 2 across) cover the same 128 x 128 chunks, in the same order, as the
+// CTA-synchronous kernel above, so neighbouring pieces of the outputs are written within a few
+// microseconds of each other.  Warps drift freely: nothing waits at a barrier.
+
+constexpr int kStripRows = 32;
+constexpr int kStripCols = 64;
+constexpr int kStripBytes = kStripRows * kStripCols * 2;
+constexpr int kStripWarps = 16;
+constexpr int kStripDepth = 2;          // input slots per warp: one being processed, one in flight
+constexpr int kStripStageBytes = 2048;  // per warp: 1 KiB of row codes + 1 KiB of column codes awaiting their TMA store
+
+__host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm) {
+  return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes) + 2 * 128 * sizeof(ScaleLut) +
+         (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + (size_t)k_norm * sizeof(float) + 1024;
+}
+
+template <bool ENCODE_CENTRIC, bool NORM>
+__global__ void __launch_bounds__(kStripWarps * 32, 1)
+nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_row,
+                            const __grid_constant__ CUtensorMap tmap_col, const QuantArgs a) {
+  constexpr int depth = kStripDepth;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* base = smem_align_1024(smem_raw);
+  uint8_t* slots = base;                                                       // [warp][depth][4 KiB]
+  uint8_t* staging = base + (size_t)kStripWarps * depth * kStripBytes;         // [warp][2 KiB]
+  ScaleLut* lut_row = reinterpret_cast<ScaleLut*>(staging + (size_t)kStripWarps * kStripStageBytes);
+  ScaleLut* lut_col = lut_row + 128;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(lut_col + 128);                 // [warp][depth]
+  float* gamma_f = reinterpret_cast<float*>(bars + kStripWarps * depth);       // [K] (NORM)
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wv = warp & 3;          // which 32 rows of the chunk
+  const int wh = (warp >> 2) & 1;   // which 64 columns of the chunk
+  const int n_chunks = a.chunks_m * a.chunks_k;
+  const int first = blockIdx.x * 2 + (warp >> 3);
+  const int step = gridDim.x * 2;
+  const int my_count = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
+  uint8_t* my_slots = slots + (size_t)warp * depth * kStripBytes;
+  uint64_t* my_bars = bars + warp * depth;
+  uint8_t* my_stage = staging + (size_t)warp * kStripStageBytes;
+
+  auto chunk_coords = [&](int it, int& cm, int& ck) {
+    int c = first + it * step;
+    if (a.reverse) c = n_chunks - 1 - c;
+    cm = c / a.chunks_k;
+    ck = c - cm * a.chunks_k;
+  };
+  auto issue_load = [&](int it, int s) {
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    mbar_expect_tx(&my_bars[s], kStripBytes);
+    tma_load_2d(my_slots + (size_t)s * kStripBytes, &tmap_x, ck * kChunk + wh * kStripCols, cm * kChunk + wv * kStripRows,
+                &my_bars[s]);
+  };
+
+  if (tid == 0) {
+    tma_prefetch_desc(&tmap_x);
+    tma_prefetch_desc(&tmap_row);
+    if (a.col_fp4 != nullptr) tma_prefetch_desc(&tmap_col);
+    for (int i = 0; i < kStripWarps * depth; ++i) mbar_init(&bars[i], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (lane == 0) {
+    for (int s = 0; s < depth && s < my_count; ++s) issue_load(s, s);
+  }
+  // The input is never written by the pass-1 kernel this one may have been launched behind, so the
+  // first strips are already on their way; amax / inv_rms are that kernel's results.
+  pdl_wait();
+  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = *a.amax_row / 2688.0f;
+  const float s_enc_row = nvfp4_global_encode_scale(*a.amax_row);
+  const float s_enc_col = nvfp4_global_encode_scale(*a.amax_col);
+  const bool want_col = a.col_fp4 != nullptr;
+  if (tid < 128) lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
+  else if (tid < 256) lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
+  if constexpr (NORM) {
+    for (int q = tid; q < (a.K >> 1); q += kStripWarps * 32) {
+      const uint32_t g = __ldg(reinterpret_cast<const uint32_t*>(a.gamma) + q);
+      *reinterpret_cast<float2*>(gamma_f + 2 * q) = make_float2(bf16lo_to_f32(g), bf16hi_to_f32(g));
+    }
+  }
+  __syncthreads();
+
+  // loop-invariant geometry
+  const int sw = lane & 7;
+  int row_off[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) row_off[j] = lane * 128 + ((j ^ sw) << 4);
+  int col_off[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) col_off[j] = j * 128 + ((((lane >> 2) ^ j) << 4) | ((lane & 3) << 2));
+
+  float inv_next = 0.0f;
+  if constexpr (NORM) {
+    if (my_count > 0) {
+      int cm, ck;
+      chunk_coords(0, cm, ck);
+      inv_next = __ldg(a.inv_rms + cm * kChunk + wv * kStripRows + lane);
+    }
+  }
+
+  for (int it = 0; it < my_count; ++it) {
+    const int s = it % depth;
+    const uint32_t parity = (uint32_t)(it / depth) & 1u;
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    const int row0 = cm * kChunk + wv * kStripRows;      // first row of the strip
+    const int col0 = ck * kChunk + wh * kStripCols;      // first column of the strip
+    const float inv = inv_next;
+    if constexpr (NORM) {
+      if (it + 1 < my_count) {
+        int ncm, nck;
+        chunk_coords(it + 1, ncm, nck);
+        inv_next = __ldg(a.inv_rms + ncm * kChunk + wv * kStripRows + lane);
+      }
+    }
+    if (!mbar_wait_bounded(&my_bars[s], parity)) {
+      if (lane == 0) atomicExch(a.status, kStatusQuantTmaTimeout);
+      break;
+    }
+    uint8_t* tile = my_slots + (size_t)s * kStripBytes;
+
+    // ---- row pass: lane = row ----------------------------------------------------------
+    {
+      uint32_t w[32];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint4 v = *reinterpret_cast<const uint4*>(tile + row_off[j]);
+        w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+      }
+      if constexpr (NORM) {
+        const float2 inv2 = make_float2(inv, inv);
+        const float4* g4 = reinterpret_cast<const float4*>(gamma_f + col0);   // same address on all lanes
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const float4 g = g4[q];
+          float2 t0 = mul2(make_float2(bf16lo_to_f32(w[2 * q]), bf16hi_to_f32(w[2 * q])), inv2);
+          float2 t1 = mul2(make_float2(bf16lo_to_f32(w[2 * q + 1]), bf16hi_to_f32(w[2 * q + 1])), inv2);
+          t0 = mul2(t0, make_float2(g.x, g.y));
+          t1 = mul2(t1, make_float2(g.z, g.w));
+          w[2 * q] = f32x2_to_bf16x2(t0.x, t0.y);
+          w[2 * q + 1] = f32x2_to_bf16x2(t1.x, t1.y);
+        }
+        if (want_col) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(tile + row_off[j]) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
+      }
+      uint32_t codes[8];
+      uint32_t sc_word = 0;
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        uint32_t mx = 0;
+#pragma unroll
+        for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[8 * b + q]);
+        const float bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+        const ScaleLut e = lut_row[block_code<ENCODE_CENTRIC>(bm, s_enc_row)];
+        codes[2 * b] = quant8(w + 8 * b, e.coeff);
+        codes[2 * b + 1] = quant8(w + 8 * b + 4, e.coeff);
+        sc_word |= e.stored << (8 * b);
+      }
+      // codes leave through a TMA store (32 rows x 32 bytes): per-lane global stores of 32 different
+      // lines each would cost the L1 as much as all the shared-memory traffic of the strip
+      if (lane == 0) bulk_wait_group_read0();   // the previous strip's stores have left the staging buffers
+      __syncwarp();
+      *reinterpret_cast<uint4*>(my_stage + lane * 32) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+      *reinterpret_cast<uint4*>(my_stage + lane * 32 + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+      // 512-byte tile (128 rows x these 4 blocks): row wv*32 + lane, blocks 0..3 are 4 adjacent bytes
+      st_cs_u32(a.row_sc + ((size_t)cm * (a.K >> 6) + (size_t)(col0 >> 6)) * 512 + lane * 16 + wv * 4, sc_word);
+    }
+
+    // ---- column pass: lane = column pair -----------------------------------------------
+    if (want_col) {
+      if constexpr (NORM) __syncwarp();   // the normalised rows of all lanes are in the slot
+      uint32_t cc0[4], cc1[4];            // codes of columns c and c+1: rows 0..7, 8..15, 16..23, 24..31
+      uint32_t sc0 = 0, sc1 = 0;
+#pragma unroll
+      for (int g = 0; g < 2; ++g) {
+        const uint8_t* gbase = tile + g * 16 * 128;
+        uint32_t w[16];
+        uint32_t mx = 0;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          w[i] = *reinterpret_cast<const uint32_t*>(gbase + (i >> 3) * 1024 + col_off[i & 7]);
+          mx = absmax_xs(mx, w[i]);
+        }
+        const float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
+        const ScaleLut e0 = lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
+        const ScaleLut e1 = lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
+        const float2 cc = make_float2(e0.coeff, e1.coeff);
+        float2 v[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) v[i] = mul2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), cc);
+        cc0[2 * g] = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+        cc0[2 * g + 1] = f32x8_to_e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
+        cc1[2 * g] = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+        cc1[2 * g + 1] = f32x8_to_e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+        sc0 |= e0.stored << (8 * g);
+        sc1 |= e1.stored << (8 * g);
+      }
+      // 64 columns x 16 bytes (32 rows), staged for a TMA store into [K, M/2]
+      *reinterpret_cast<uint4*>(my_stage + 1024 + lane * 32) = make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]);
+      *reinterpret_cast<uint4*>(my_stage + 1024 + lane * 32 + 16) = make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]);
+      // 512-byte tile (128 columns x four 16-row groups of a 64-row band): this strip holds groups
+      // (wv & 1) * 2 and (wv & 1) * 2 + 1 of band cm * 2 + (wv >> 1): two adjacent bytes per column
+      const int cin = wh * kStripCols + 2 * lane;   // column inside the 128-column tile
+      uint8_t* sdst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)(cm * 2 + (wv >> 1))) * 512 + (wv & 1) * 2;
+      st_cs_u16(sdst + scale_tile_offset(cin, 0), (uint16_t)sc0);
+      st_cs_u16(sdst + scale_tile_offset(cin + 1, 0), (uint16_t)sc1);
+    }
+
+    // staged codes -> global memory; the slot is free again: refill it with the strip `depth` chunks ahead
+    fence_proxy_async_smem();   // this lane's generic-proxy writes (staging, normalised rows) before the TMA engine's accesses
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(&tmap_row, my_stage, col0 >> 1, row0);
+      if (want_col) tma_store_2d(&tmap_col, my_stage + 1024, row0 >> 1, col0);
+      bulk_commit_group();
+      if (it + depth < my_count) issue_load(it + depth, s);
+    }
+  }
+  if (lane == 0) bulk_wait_group0();
+}
+
 // Tensor amax of the 16-point Hadamard transform of x (per 16 contiguous elements along K when
 // along_k, else per 16 consecutive rows), taken on the fp32 transform output before its bf16
 // rounding, as the reference's scan does (tk_quantize.cu:574-664).
@@ -845,6 +1089,58 @@ static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cud
   return 0;
 }
 
+// CTA-synchronous kernel for everything when FP4B200_QUANT_STRIP=0 (A/B comparisons)
+static bool quant_strip_disabled() {
+  static const bool off = [] {
+    const char* e = getenv("FP4B200_QUANT_STRIP");
+    return e != nullptr && e[0] == '0';
+  }();
+  return off;
+}
+
+template <bool EC, bool NORM>
+static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
+  CUtensorMap tmap, tmap_row, tmap_col;
+  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)args.K, (uint64_t)args.M,
+                            (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  // packed codes as byte matrices: [M, K/2] in boxes of 32 rows x 32 bytes, [K, M/2] in boxes of 64 rows x 16 bytes
+  if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
+                            (uint64_t)args.K / 2, kStripCols / 2, kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  tmap_col = tmap_row;
+  if (args.col_fp4 != nullptr) {
+    if (int rc = make_tmap_2d(&tmap_col, args.col_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.M / 2, (uint64_t)args.K,
+                              (uint64_t)args.M / 2, kStripRows / 2, kStripCols, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+  }
+  auto kern = nvfp4_quantize_strip_kernel<EC, NORM>;
+  const int smem = (int)strip_smem_bytes(NORM ? args.K : 0);
+  FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  const int n_chunks = args.chunks_m * args.chunks_k;
+  const int grid = std::min((n_chunks + 1) / 2, device_sm_count());
+  if (grid == 0) return 0;
+  cudaLaunchConfig_t cfg{};
+  cfg.gridDim = dim3((unsigned)grid);
+  cfg.blockDim = dim3(kStripWarps * 32);
+  cfg.dynamicSmemBytes = (size_t)smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = pdl ? 1 : 0;
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, tmap_row, tmap_col, args));
+  return 0;
+}
+
+// The strip kernel stores codes by TMA (16-byte aligned outputs) and keeps gamma in shared memory.
+static bool strip_kernel_applies(const QuantArgs& a, bool norm) {
+  if (quant_strip_disabled()) return false;
+  if (((reinterpret_cast<uintptr_t>(a.row_fp4) | reinterpret_cast<uintptr_t>(a.col_fp4)) & 15) != 0) return false;
+  return strip_smem_bytes(norm ? a.K : 0) <= 227 * 1024;
+}
+
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
@@ -877,13 +1173,19 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
                 : launch_quantize_t<false, false, false, true>(tmap, a, st, behind_pass1);
   }
   if (weight_2d) return launch_quantize_t<false, false, true>(tmap, a, st, behind_pass1);   // decode-centric, as the reference
+  if (strip_kernel_applies(a, norm)) {
+    if (encode_centric) return norm ? launch_quantize_strip_t<true, true>(x, a, st, behind_pass1)
+                                    : launch_quantize_strip_t<true, false>(x, a, st, behind_pass1);
+    return norm ? launch_quantize_strip_t<false, true>(x, a, st, behind_pass1)
+                : launch_quantize_strip_t<false, false>(x, a, st, behind_pass1);
+  }
   if (encode_centric) return norm ? launch_quantize_t<true, true>(tmap, a, st, behind_pass1) : launch_quantize_t<true, false>(tmap, a, st, behind_pass1);
   return norm ? launch_quantize_t<false, true>(tmap, a, st, behind_pass1) : launch_quantize_t<false, false>(tmap, a, st, behind_pass1);
 }
 
 // Warps per CTA of the pipelined statistics kernel for rows of K elements (0: rows too long for it).
 static int stats_warps_for(int64_t K) {
-  const int64_t budget = 227 * 1024 - K * 4 - 512;
+  const int64_t budget = 227 * 1024 - K * 2 - 512;
   const int64_t w = budget / (kStatsDepth * K * 2);
   const int64_t cap = K <= 4096 ? kStatsMaxWarps : 6;
   return (int)std::max<int64_t>(0, std::min<int64_t>(w, cap));
@@ -893,7 +1195,7 @@ template <int NV, bool CI>
 static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* amax_sg, float eps,
                           int64_t M, int64_t K, int warps, int* status, cudaStream_t st) {
   auto kern = rmsnorm_stats_kernel<NV, CI>;
-  const size_t smem = (size_t)K * 4 + (size_t)warps * kStatsDepth * K * 2 + (size_t)warps * kStatsDepth * 8;
+  const size_t smem = (size_t)K * 2 + (size_t)warps * kStatsDepth * K * 2 + (size_t)warps * kStatsDepth * 8;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
   kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K, status);
@@ -902,6 +1204,7 @@ static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, floa
 
 static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms, float* amax_sg, float eps,
                                 int64_t M, int64_t K, bool compute_inv, cudaStream_t st, bool finalize = true) {
+  if ((reinterpret_cast<uintptr_t>(gamma) & 15) != 0) return set_error("rmsnorm statistics: gamma must be 16-byte aligned");
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
   if (M > 0) {
     auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
