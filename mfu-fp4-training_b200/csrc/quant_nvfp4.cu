@@ -761,17 +761,18 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
 //
 // One CTA of 16 warps per SM and no CTA-wide barrier after start-up.  A warp owns a strip of
 // 32 rows x 64 columns (one TMA box, 4 KiB, 128-byte swizzle), two private strip slots with one
-// mbarrier each, and 2 KiB of staging for its codes; it quantises its strip in both orientations
+// mbarrier each, and 1 KiB of staging for its row codes; it quantises its strip in both orientations
 // by itself:
 //   row pass   : lane = row; eight conflict-free 16-byte reads, optional RMSNorm (normalised bf16
 //                written back for the column pass), four 16-blocks -> 32 bytes of codes (staged)
 //                and one 32-bit word of scales (stored straight to global memory);
 //   column pass: lane = column pair; 32 conflict-free 4-byte reads, two 16-row blocks per column
-//                -> 16 bytes of codes per column (staged) and two scale bytes (stored directly).
-// The staged codes leave as two TMA stores per strip (32 rows x 32 B into [M, K/2], 64 rows x 16 B
-// into [K, M/2]): the L1 data path, which carries shared-memory traffic as well as global stores,
-// is the busiest unit of this kernel, and a per-lane store instruction touching 32 lines occupies
-// it 32 times longer than the same bytes staged once.
+//                -> 16 bytes of codes per column and two scale bytes, stored straight to global memory.
+// The row codes leave as one TMA store per strip (32 rows x 32 B into [M, K/2]); the column codes
+// (16 B per column) are stored per lane.  Two units set the pace besides instruction issue: the L1
+// data path, which carries shared-memory traffic as well as global stores (a per-lane store touching
+// 32 lines occupies it 32 cycles), and the TMA unit, whose cost is per box ROW (~3 cycles each,
+// whatever the row's length); splitting the outputs this way loads both about equally.
 // Eight warps (4 down x 2 across) cover the same 128 x 128 chunks, in the same order, as the
 // CTA-synchronous kernel above, so neighbouring pieces of the outputs are written within a few
 // microseconds of each other.  Warps drift freely: nothing waits at a barrier.
@@ -781,7 +782,7 @@ constexpr int kStripCols = 64;
 constexpr int kStripBytes = kStripRows * kStripCols * 2;
 constexpr int kStripWarps = 16;
 constexpr int kStripDepth = 2;          // input slots per warp: one being processed, one in flight
-constexpr int kStripStageBytes = 2048;  // per warp: 1 KiB of row codes + 1 KiB of column codes awaiting their TMA store
+constexpr int kStripStageBytes = 1024;  // per warp: row codes of one strip awaiting their TMA store
 
 __host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm) {
   return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes) + 2 * 128 * sizeof(ScaleLut) +
@@ -791,7 +792,7 @@ __host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm) {
 template <bool ENCODE_CENTRIC, bool NORM>
 __global__ void __launch_bounds__(kStripWarps * 32, 1)
 nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_row,
-                            const __grid_constant__ CUtensorMap tmap_col, const QuantArgs a) {
+                            const QuantArgs a) {
   constexpr int depth = kStripDepth;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* base = smem_align_1024(smem_raw);
@@ -830,7 +831,6 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   if (tid == 0) {
     tma_prefetch_desc(&tmap_x);
     tma_prefetch_desc(&tmap_row);
-    if (a.col_fp4 != nullptr) tma_prefetch_desc(&tmap_col);
     for (int i = 0; i < kStripWarps * depth; ++i) mbar_init(&bars[i], 1);
     fence_mbar_init();
   }
@@ -973,9 +973,11 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         sc0 |= e0.stored << (8 * g);
         sc1 |= e1.stored << (8 * g);
       }
-      // 64 columns x 16 bytes (32 rows), staged for a TMA store into [K, M/2]
-      *reinterpret_cast<uint4*>(my_stage + 1024 + lane * 32) = make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]);
-      *reinterpret_cast<uint4*>(my_stage + 1024 + lane * 32 + 16) = make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]);
+      // 16 bytes per column straight to [K, M/2]: as a TMA store this would be 64 box rows of 16 bytes,
+      // and the TMA unit's rate of box rows (not bytes) is what bounds the kernel once everything goes through it
+      uint8_t* cdst = a.col_fp4 + (size_t)(col0 + 2 * lane) * (a.M >> 1) + (row0 >> 1);
+      st_cs_u4(cdst, make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]));
+      st_cs_u4(cdst + (a.M >> 1), make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]));
       // 512-byte tile (128 columns x four 16-row groups of a 64-row band): this strip holds groups
       // (wv & 1) * 2 and (wv & 1) * 2 + 1 of band cm * 2 + (wv >> 1): two adjacent bytes per column
       const int cin = wh * kStripCols + 2 * lane;   // column inside the 128-column tile
@@ -989,7 +991,6 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     __syncwarp();
     if (lane == 0) {
       tma_store_2d(&tmap_row, my_stage, col0 >> 1, row0);
-      if (want_col) tma_store_2d(&tmap_col, my_stage + 1024, row0 >> 1, col0);
       bulk_commit_group();
       if (it + depth < my_count) issue_load(it + depth, s);
     }
@@ -1100,20 +1101,14 @@ static bool quant_strip_disabled() {
 
 template <bool EC, bool NORM>
 static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
-  CUtensorMap tmap, tmap_row, tmap_col;
+  CUtensorMap tmap, tmap_row;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)args.K, (uint64_t)args.M,
                             (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  // packed codes as byte matrices: [M, K/2] in boxes of 32 rows x 32 bytes, [K, M/2] in boxes of 64 rows x 16 bytes
+  // row-wise codes as a byte matrix [M, K/2], stored in boxes of 32 rows x 32 bytes
   if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
                             (uint64_t)args.K / 2, kStripCols / 2, kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
     return rc;
-  tmap_col = tmap_row;
-  if (args.col_fp4 != nullptr) {
-    if (int rc = make_tmap_2d(&tmap_col, args.col_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.M / 2, (uint64_t)args.K,
-                              (uint64_t)args.M / 2, kStripRows / 2, kStripCols, CU_TENSOR_MAP_SWIZZLE_NONE))
-      return rc;
-  }
   auto kern = nvfp4_quantize_strip_kernel<EC, NORM>;
   const int smem = (int)strip_smem_bytes(NORM ? args.K : 0);
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -1130,14 +1125,14 @@ static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStr
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = pdl ? 1 : 0;
-  FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, tmap_row, tmap_col, args));
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, tmap_row, args));
   return 0;
 }
 
 // The strip kernel stores codes by TMA (16-byte aligned outputs) and keeps gamma in shared memory.
 static bool strip_kernel_applies(const QuantArgs& a, bool norm) {
   if (quant_strip_disabled()) return false;
-  if (((reinterpret_cast<uintptr_t>(a.row_fp4) | reinterpret_cast<uintptr_t>(a.col_fp4)) & 15) != 0) return false;
+  if (((reinterpret_cast<uintptr_t>(a.row_fp4) | reinterpret_cast<uintptr_t>(a.col_fp4)) & 15) != 0) return false;   // TMA / 16-byte stores
   return strip_smem_bytes(norm ? a.K : 0) <= 227 * 1024;
 }
 
