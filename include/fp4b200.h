@@ -118,12 +118,12 @@ int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
  * graph capture, under a memory pool that is already full by design, or in a host thread that
  * is not allowed to touch the allocator.  It has no counterpart in the reference, whose producers
  * always allocate their scratch through torch.  The caller passes inputs and outputs only (sg_out
- * receives amax/2688); the per-row inverse RMS and the tensor amax live in a fixed array inside
- * the library (256 KiB + 256 B per device, held until the process exits), so M is limited to
- * 65536 rows and larger calls are rejected with an error.  The first call on a device looks up
- * the array's device address; make that call before any stream capture starts.  All calls share
- * the array, which keeps the previous call's contents (the amax word is cleared on the stream at
- * the start of every call): two calls that overlap on the GPU, e.g. on different streams, race. */
+ * receives amax/2688); the per-row inverse RMS and the first pass's per-CTA partial maxima live
+ * in a fixed array inside the library (264 KiB per device, held until the process exits), so M is
+ * limited to 65536 rows and larger calls are rejected with an error.  The first call on a device
+ * looks up the array's device address; make that call before any stream capture starts.  All calls
+ * share the array, which keeps the previous call's contents (every call overwrites the part it
+ * reads): two calls that overlap on the GPU, e.g. on different streams, race. */
 int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,
                                               int64_t K, void* row_fp4, void* row_sc, void* col_fp4,
                                               void* col_sc, float* sg_out, void* stream);

@@ -290,6 +290,23 @@ __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   return d;
 }
 
+// acc + lo(w)^2 and then + hi(w)^2, each one fused multiply-add of the bf16 value with itself into the
+// fp32 accumulator (mixed-precision FMA: the bf16 x bf16 product is exact in fp32, so the result is
+// bit-identical to fmaf on the converted values, without the conversion instructions).
+__device__ __forceinline__ float fma_sq_bf16x2(uint32_t w, float acc) {
+  asm("{.reg .b16 lo, hi; mov.b32 {lo, hi}, %1;\n\t"
+      "fma.rn.f32.bf16 %0, lo, lo, %0;\n\t"
+      "fma.rn.f32.bf16 %0, hi, hi, %0;}"
+      : "+f"(acc) : "r"(w));
+  return acc;
+}
+
+// max(acc, |a|, |b|) for acc >= 0 (written so that the compiler may use a three-input maximum with
+// absolute-value operand modifiers)
+__device__ __forceinline__ float absmax3(float acc, float a, float b) {
+  return fmaxf(acc, fmaxf(fabsf(a), fabsf(b)));
+}
+
 // running |.|-max on packed bf16x2; the sign of the result is meaningless
 __device__ __forceinline__ uint32_t absmax_xs(uint32_t acc, uint32_t v) {
   uint32_t r;

@@ -5,7 +5,9 @@
 #include <stdio.h>
 #include <string.h>
 
+#include <map>
 #include <mutex>
+#include <utility>
 
 namespace fp4b200 {
 
@@ -50,6 +52,30 @@ int* device_status_ptr() {
     cached[dev] = static_cast<int*>(p);
   }
   return cached[dev];
+}
+
+float* stream_scratch(cudaStream_t st) {
+  static std::mutex mu;
+  static std::map<std::pair<int, uintptr_t>, float*> table;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) {
+    set_error("stream_scratch: cudaGetDevice failed");
+    return nullptr;
+  }
+  std::lock_guard<std::mutex> lock(mu);
+  const auto key = std::make_pair(dev, reinterpret_cast<uintptr_t>(st));
+  auto it = table.find(key);
+  if (it != table.end()) return it->second;
+  void* p = nullptr;
+  const cudaError_t e = cudaMalloc(&p, kScratchFloats * sizeof(float));
+  if (e != cudaSuccess || p == nullptr) {
+    (void)cudaGetLastError();
+    set_error("stream_scratch: cudaMalloc of %zu bytes failed: %s (the first call on a stream must not be inside a "
+              "stream capture)", kScratchFloats * sizeof(float), cudaGetErrorString(e));
+    return nullptr;
+  }
+  table.emplace(key, static_cast<float*>(p));
+  return static_cast<float*>(p);
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,

@@ -25,6 +25,20 @@ int device_sm_count();
 // Device address of the per-device status word array (4 ints); nullptr + error on failure.
 int* device_status_ptr();
 
+// Device scratch of kScratchFloats floats private to (current device, stream).  Kernels of one stream
+// run in order, so consecutive launches of one entry point may hand small results to each other
+// through it (per-CTA partial maxima of a pass-1 kernel, read by the kernel launched next).  Allocated
+// with cudaMalloc on the first use of a stream and kept for the life of the process; nullptr + error
+// on failure (e.g. a first use inside a stream capture).
+constexpr int kScratchFloats = 2048;
+float* stream_scratch(cudaStream_t st);
+
+// Per-CTA partial tensor maxima left in scratch by a pass-1 kernel for the kernel launched next.
+struct AmaxPartials {
+  const float* ptr = nullptr;
+  int count = 0;
+};
+
 // Encodes a 2-D tiled tensor map: inner extent dim0 (elements), outer extent dim1, row pitch
 // in bytes, box (box0 x box1) elements.  Returns 0 or -1 (message set).
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
@@ -46,18 +60,23 @@ struct QuantOpt {
 };
 
 // Launchers defined in quant_nvfp4.cu and shared with the other producers.
-// amax_sg[0] = max|x|, amax_sg[1] = amax/2688 (cleared and recomputed on the stream; with
-// finalize == false the division is left to the quantiser launched next, via its sg_out).
-int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st, bool finalize = true);
-// Row (+ column when col_* non-null) NVFP4 quantisation from device-resident amaxes; RMSNorm is
-// applied on the fly when inv_rms/gamma are given; reverse walks the chunks back to front;
-// weight_2d shares one scale per 16x16 tile between the two orientations (decode-centric).
-// behind_pass1: the kernel launched just before on st is this library's own amax / statistics
-// kernel over the same x (which it only reads), so the quantiser may be launched programmatically
-// dependent on it and fetch its first chunks while that kernel drains.
+// Tensor amax of a bf16 buffer.  partials_out == nullptr: amax_sg[0] = max|x|, amax_sg[1] = amax/2688
+// are written on the stream (two launches).  Otherwise only the per-CTA maxima are produced, in
+// `scratch` (kScratchFloats floats), described by *partials_out, for a quantiser launched next.
+int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st, float* scratch = nullptr,
+                AmaxPartials* partials_out = nullptr);
+// Row (+ column when col_* non-null) NVFP4 quantisation; RMSNorm is applied on the fly when
+// inv_rms/gamma are given; reverse walks the chunks back to front; weight_2d shares one scale per
+// 16x16 tile between the two orientations (decode-centric).
+// The tensor amax comes either from the device scalars amax_row / amax_col, or (partials != nullptr)
+// from the partial maxima of this library's own pass-1 kernel launched just before on st over the
+// same x, which it only reads: the quantiser is then launched programmatically dependent on that
+// kernel (it fetches its first chunks while that kernel drains), reduces the partials itself and
+// writes amax_out[0] = amax, amax_out[1] = amax/2688 (when non-null).  sg_out (when non-null)
+// receives amax_row/2688 in both cases.
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                     bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4, void* row_sc,
                     void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st, bool weight_2d = false,
-                    const QuantOpt* opt = nullptr, bool behind_pass1 = false);
+                    const QuantOpt* opt = nullptr, const AmaxPartials* partials = nullptr, float* amax_out = nullptr);
 
 }  // namespace fp4b200

@@ -17,8 +17,9 @@ namespace fp4b200 {
 // Tensor amax of a bf16 buffer (pass 1 of the plain quantiser)
 // ---------------------------------------------------------------------------------------
 
+// partials[blockIdx.x] = max|x| over this CTA's share (every CTA writes, so nothing needs clearing)
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, size_t n_vec,
-                                                        float* __restrict__ amax) {
+                                                        float* __restrict__ partials) {
   pdl_launch_dependents();   // a quantiser launched behind this kernel may set up and prefetch meanwhile
   uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
@@ -45,12 +46,43 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
   if (threadIdx.x < 32) {
     v = threadIdx.x < 8 ? warp_part[threadIdx.x] : 0.0f;
     v = warp_max(v);
-    if (threadIdx.x == 0 && v > 0.0f) atomic_max_nonneg(amax, v);
+    if (threadIdx.x == 0) partials[blockIdx.x] = v;
   }
 }
 
-// amax_sg[1] = amax_sg[0] / 2688 (GEMM-side tensor scale)
+// amax_sg[0] = max of the partial maxima, amax_sg[1] = amax / 2688 (GEMM-side tensor scale); one CTA.
+__global__ void __launch_bounds__(256) reduce_partials_kernel(const float* __restrict__ partials, int n,
+                                                              float* __restrict__ amax_sg) {
+  pdl_wait();
+  float v = 0.0f;
+  for (int i = threadIdx.x; i < n; i += 256) v = fmaxf(v, partials[i]);
+  v = warp_max(v);
+  __shared__ float warp_part[8];
+  if ((threadIdx.x & 31) == 0) warp_part[threadIdx.x >> 5] = v;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+#pragma unroll
+    for (int w = 1; w < 8; ++w) v = fmaxf(v, warp_part[w]);
+    amax_sg[0] = v;
+    amax_sg[1] = v / 2688.0f;
+  }
+}
+
+// amax_sg[1] = amax_sg[0] / 2688
 __global__ void finalize_sg_kernel(float* __restrict__ amax_sg) { amax_sg[1] = amax_sg[0] / 2688.0f; }
+
+// Tensor amax of a quantiser launch behind a pass-1 kernel: maximum of that kernel's per-CTA partial
+// maxima, computed by every CTA for itself (n <= 2048 floats that sit in L2).  Contains a CTA barrier.
+__device__ __forceinline__ float amax_from_partials(const float* partials, int n, float* slot) {
+  if (threadIdx.x < 32) {
+    float v = 0.0f;
+    for (int i = threadIdx.x; i < n; i += 32) v = fmaxf(v, partials[i]);
+    v = warp_max(v);
+    if (threadIdx.x == 0) *slot = v;
+  }
+  __syncthreads();
+  return *slot;
+}
 
 // ---------------------------------------------------------------------------------------
 // RMSNorm statistics: inv_rms per row, and amax of bf16(x * inv_rms * gamma)
@@ -69,24 +101,20 @@ constexpr int kStatsDepth = 2;       // row slots per warp
 // Sum of squares of the row held in v -> 1/rms, identical on all lanes.
 template <int NV>
 __device__ __forceinline__ float stats_inv_rms(const uint4 (&v)[NV], int K, float eps) {
-  // acc[i][q]: virtual lane 4*lane + 128*i + q; packed as pairs (q, q+1)
-  float2 acc[2][2] = {{{0, 0}, {0, 0}}, {{0, 0}, {0, 0}}};
+  // acc[i][q]: virtual lane 4*lane + 128*i + q accumulates elements 2q, 2q+1 of vectors j = i, i+2, ...
+  float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int i = j & 1;
-    const float2 lo01 = make_float2(bf16lo_to_f32(v[j].x), bf16lo_to_f32(v[j].y));
-    const float2 hi01 = make_float2(bf16hi_to_f32(v[j].x), bf16hi_to_f32(v[j].y));
-    const float2 lo23 = make_float2(bf16lo_to_f32(v[j].z), bf16lo_to_f32(v[j].w));
-    const float2 hi23 = make_float2(bf16hi_to_f32(v[j].z), bf16hi_to_f32(v[j].w));
-    acc[i][0] = fma2(lo01, lo01, acc[i][0]);
-    acc[i][0] = fma2(hi01, hi01, acc[i][0]);
-    acc[i][1] = fma2(lo23, lo23, acc[i][1]);
-    acc[i][1] = fma2(hi23, hi23, acc[i][1]);
+    acc[i][0] = fma_sq_bf16x2(v[j].x, acc[i][0]);
+    acc[i][1] = fma_sq_bf16x2(v[j].y, acc[i][1]);
+    acc[i][2] = fma_sq_bf16x2(v[j].z, acc[i][2]);
+    acc[i][3] = fma_sq_bf16x2(v[j].w, acc[i][3]);
   }
   float part[2];
 #pragma unroll
   for (int i = 0; i < 2; ++i) {
-    float a4[4] = {acc[i][0].x, acc[i][0].y, acc[i][1].x, acc[i][1].y};
+    float a4[4] = {acc[i][0], acc[i][1], acc[i][2], acc[i][3]};
 #pragma unroll
     for (int q = 0; q < 4; ++q) {
       a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 4);
@@ -103,31 +131,29 @@ __device__ __forceinline__ float stats_inv_rms(const uint4 (&v)[NV], int K, floa
   return rsqrtf(s / static_cast<float>(K) + eps);
 }
 
-// Running |bf16(x * inv * gamma)| maximum (packed bf16x2) over the row held in v.  gamma stays packed
-// bf16 in shared memory: one conflict-free 16-byte read per vector (an fp32 copy would cost four times
-// the shared-memory bandwidth, which is what bounded this kernel before).
+// Running maximum of |(x * inv) * gamma| in fp32 over the row held in v.  Rounding to bf16 is
+// monotonic, so the tensor amax of the bf16 values is the bf16 rounding of this maximum: no
+// per-element conversion.  gamma is read as fp32 from two shared-memory tables (elements 0-3 and
+// 4-7 of every vector), each a conflict-free 16-byte read per lane.
 template <int NV>
-__device__ __forceinline__ uint32_t stats_row_amax(const uint4 (&v)[NV], const uint4* gamma_s, float inv, int K,
-                                                   int lane, uint32_t mx) {
+__device__ __forceinline__ float stats_row_amax(const uint4 (&v)[NV], const float4* gamma_lo, const float4* gamma_hi,
+                                                float inv, int K, int lane, float mx) {
   const float2 inv2 = make_float2(inv, inv);
   const int nvec_row = K >> 3;
 #pragma unroll
   for (int j = 0; j < NV; ++j) {
     const int q = lane + 32 * j;
     if (q < nvec_row) {
-      const uint4 g = gamma_s[q];
-      float2 t0 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2),
-                       make_float2(bf16lo_to_f32(g.x), bf16hi_to_f32(g.x)));
-      float2 t1 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2),
-                       make_float2(bf16lo_to_f32(g.y), bf16hi_to_f32(g.y)));
-      float2 t2 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2),
-                       make_float2(bf16lo_to_f32(g.z), bf16hi_to_f32(g.z)));
-      float2 t3 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2),
-                       make_float2(bf16lo_to_f32(g.w), bf16hi_to_f32(g.w)));
-      mx = absmax_xs(mx, f32x2_to_bf16x2(t0.x, t0.y));
-      mx = absmax_xs(mx, f32x2_to_bf16x2(t1.x, t1.y));
-      mx = absmax_xs(mx, f32x2_to_bf16x2(t2.x, t2.y));
-      mx = absmax_xs(mx, f32x2_to_bf16x2(t3.x, t3.y));
+      const float4 g01 = gamma_lo[q];
+      const float4 g23 = gamma_hi[q];
+      const float2 t0 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2), make_float2(g01.x, g01.y));
+      const float2 t1 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2), make_float2(g01.z, g01.w));
+      const float2 t2 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2), make_float2(g23.x, g23.y));
+      const float2 t3 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2), make_float2(g23.z, g23.w));
+      mx = absmax3(mx, t0.x, t0.y);
+      mx = absmax3(mx, t1.x, t1.y);
+      mx = absmax3(mx, t2.x, t2.y);
+      mx = absmax3(mx, t3.x, t3.y);
     }
   }
   return mx;
@@ -138,46 +164,59 @@ __device__ __forceinline__ uint32_t stats_row_amax(const uint4 (&v)[NV], const u
 // and the slot is refilled as soon as the row's sum of squares has been reduced (the reduction needs
 // every lane's values, so all reads of the slot are complete by then).  Bytes in flight per SM are
 // set by the slots (warps x 2 rows), not by registers, which is what a streaming reduction at HBM
-// speed needs; no CTA-wide barrier after start-up.
+// speed needs.  A CTA owns a contiguous band of rows; each warp starts on two fixed rows of the band
+// (their copies are issued before anything else happens) and then takes the band's next row from a
+// shared counter whenever a slot frees up, so the warps of a CTA finish within one row of each other.
 template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS>
 __global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
-                     float* __restrict__ inv_rms, float* __restrict__ amax, float eps, int M, int K,
+                     float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
                      int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t stats_smem[];
+  __shared__ int next_row;   // next unclaimed row of the band (band-relative)
+  __shared__ float warp_max_s[kStatsMaxWarps];
   pdl_launch_dependents();   // the quantiser launched behind this kernel may set up and prefetch meanwhile
   const int warps = blockDim.x >> 5;
   const uint32_t row_bytes = (uint32_t)K * 2u;
-  uint4* gamma_s = reinterpret_cast<uint4*>(stats_smem);                    // [K/8] gamma, packed bf16
-  uint8_t* slots = stats_smem + (size_t)K * 2;                              // [warps][kStatsDepth][row_bytes]
+  float4* gamma_lo = reinterpret_cast<float4*>(stats_smem);                 // [K/8] gamma of elements 0-3 of each vector
+  float4* gamma_hi = gamma_lo + (K >> 3);                                   // [K/8] gamma of elements 4-7
+  uint8_t* slots = stats_smem + (size_t)K * 4;                              // [warps][kStatsDepth][row_bytes]
   uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t)warps * kStatsDepth * row_bytes);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < warps * kStatsDepth; ++i) mbar_init(&bars[i], 1);
-    fence_mbar_init();
-  }
-  for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) gamma_s[q] = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
-  __syncthreads();
-
-  const int stride = gridDim.x * warps;
-  const int row0 = blockIdx.x * warps + warp;
+  const int band = (M + gridDim.x - 1) / gridDim.x;
+  const int band0 = blockIdx.x * band;
+  const int n_band = min(band, M - band0);    // rows of this CTA (<= 0: nothing to do)
   uint8_t* my_slots = slots + (size_t)warp * kStatsDepth * row_bytes;
   uint64_t* my_bars = bars + warp * kStatsDepth;
-  auto issue = [&](int row, int d) {
+  auto issue = [&](int r, int d) {            // r: band-relative row
     mbar_expect_tx(&my_bars[d], row_bytes);
-    bulk_load_1d(my_slots + (size_t)d * row_bytes, x + (size_t)row * K, row_bytes, &my_bars[d]);
+    bulk_load_1d(my_slots + (size_t)d * row_bytes, x + (size_t)(band0 + r) * K, row_bytes, &my_bars[d]);
   };
+  // the warp's own barriers and first two copies: nothing here depends on another warp
+  int cur0 = warp < n_band ? warp : -1;
+  int cur1 = warp + warps < n_band ? warp + warps : -1;
   if (lane == 0) {
-#pragma unroll
-    for (int d = 0; d < kStatsDepth; ++d)
-      if (row0 + d * stride < M) issue(row0 + d * stride, d);
+    mbar_init(&my_bars[0], 1);
+    mbar_init(&my_bars[1], 1);
+    fence_mbar_init();
+    if (cur0 >= 0) issue(cur0, 0);
+    if (cur1 >= 0) issue(cur1, 1);
   }
-  uint32_t mx = 0;
+  if (threadIdx.x == 0) next_row = kStatsDepth * warps;
+  for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) {
+    const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
+    gamma_lo[q] = make_float4(bf16lo_to_f32(g.x), bf16hi_to_f32(g.x), bf16lo_to_f32(g.y), bf16hi_to_f32(g.y));
+    gamma_hi[q] = make_float4(bf16lo_to_f32(g.z), bf16hi_to_f32(g.z), bf16lo_to_f32(g.w), bf16hi_to_f32(g.w));
+  }
+  __syncthreads();
+
+  float mx = 0.0f;
   const int nvec_row = K >> 3;
-  int it = 0;
-  for (int row = row0; row < M; row += stride, ++it) {
-    const int d = it % kStatsDepth;
-    if (!mbar_wait_bounded(&my_bars[d], (uint32_t)(it / kStatsDepth) & 1u)) {
+  for (int it = 0;; ++it) {
+    const int d = it & 1;
+    const int r = d ? cur1 : cur0;
+    if (r < 0) break;   // rows are claimed in increasing order: an empty slot means the band is exhausted
+    if (!mbar_wait_bounded(&my_bars[d], (uint32_t)(it >> 1) & 1u)) {
       if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
       break;
     }
@@ -188,33 +227,47 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       const int q = lane + 32 * j;
       v[j] = (q < nvec_row) ? src[q] : make_uint4(0, 0, 0, 0);
     }
-    const int next = row + kStatsDepth * stride;
+    const int row = band0 + r;
+    int claimed = -1;
     float inv;
     if constexpr (COMPUTE_INV_RMS) {
       inv = stats_inv_rms<NV>(v, K, eps);
       if (lane == 0) {
         inv_rms[row] = inv;
-        if (next < M) issue(next, d);
+        claimed = atomicAdd(&next_row, 1);
+        if (claimed < n_band) issue(claimed, d); else claimed = -1;
       }
-      mx = stats_row_amax<NV>(v, gamma_s, inv, K, lane, mx);
+      mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
     } else {
       inv = __ldg(inv_rms + row);
-      mx = stats_row_amax<NV>(v, gamma_s, inv, K, lane, mx);
+      mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
       // every lane's copy of the row has been consumed by the arithmetic above
       __syncwarp();
-      if (lane == 0 && next < M) issue(next, d);
+      if (lane == 0) {
+        claimed = atomicAdd(&next_row, 1);
+        if (claimed < n_band) issue(claimed, d); else claimed = -1;
+      }
     }
+    claimed = __shfl_sync(0xffffffffu, claimed, 0);
+    if (d) cur1 = claimed; else cur0 = claimed;
   }
-  float run_max = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
-  run_max = warp_max(run_max);
-  if (lane == 0 && run_max > 0.0f) atomic_max_nonneg(amax, run_max);
+  float run_max = warp_max(mx);
+  if (lane == 0) warp_max_s[warp] = run_max;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < warps; ++w) run_max = fmaxf(run_max, warp_max_s[w]);
+    // the one rounding to bf16 that the element-wise maximum would have applied to its winner
+    partials[blockIdx.x] = __bfloat162float(__float2bfloat16_rn(run_max));   // every CTA writes: nothing to clear
+  }
 }
 
 // Any-K variant: the row is read twice (second read hits L1/L2).
 template <bool COMPUTE_INV_RMS>
 __global__ void __launch_bounds__(256)
 rmsnorm_stats_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
-                             float* __restrict__ inv_rms, float* __restrict__ amax, float eps, int M, int K) {
+                             float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K) {
+  __shared__ float warp_max_s[8];
+  pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
   const int warp_global = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int n_warps = gridDim.x * (blockDim.x >> 5);
@@ -276,7 +329,12 @@ rmsnorm_stats_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
     run_max = fmaxf(run_max, bf16x2_hmax_to_f32(mx));
   }
   run_max = warp_max(run_max);
-  if (lane == 0 && run_max > 0.0f) atomic_max_nonneg(amax, run_max);
+  if (lane == 0) warp_max_s[threadIdx.x >> 5] = run_max;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < 8; ++w) run_max = fmaxf(run_max, warp_max_s[w]);
+    partials[blockIdx.x] = run_max;
+  }
 }
 
 // ---------------------------------------------------------------------------------------
@@ -317,6 +375,7 @@ struct QuantSmem {
   alignas(8) ScaleLut lut_row[128];
   alignas(8) ScaleLut lut_col[128];
   alignas(8) uint64_t full[kQStages];
+  float amax_slot;
 };
 
 struct QuantArgs {
@@ -329,6 +388,9 @@ struct QuantArgs {
   uint8_t* col_fp4;        // [K, M/2]      (may be null: row-wise only)
   uint8_t* col_sc;         // [K/128, M/64, 512]
   float* sg_out;           // optional: sg_out[0] = amax_row / 2688
+  const float* partials;   // n_partials > 0: the tensor amax (both orientations) is the maximum of these
+  int n_partials;          //   per-CTA maxima of the pass-1 kernel launched before; amax_row/amax_col unused
+  float* amax_out;         // with partials, optional: amax_out[0] = amax, amax_out[1] = amax / 2688
   int* status;
   int M, K;
   int chunks_m, chunks_k;
@@ -493,10 +555,21 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
   // The input is never written by the pass-1 kernel this one may have been launched behind, so the
   // first chunks are already on their way; amax / inv_rms are that kernel's results.
   pdl_wait();
-  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = *a.amax_row / 2688.0f;
+  float amax_r, amax_c;
+  if (a.n_partials > 0) {
+    amax_r = amax_c = amax_from_partials(a.partials, a.n_partials, &sm.amax_slot);
+    if (tid == 0 && blockIdx.x == 0 && a.amax_out != nullptr) {
+      a.amax_out[0] = amax_r;
+      a.amax_out[1] = amax_r / 2688.0f;
+    }
+  } else {
+    amax_r = *a.amax_row;
+    amax_c = *a.amax_col;
+  }
+  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = amax_r / 2688.0f;
 
-  const float s_enc_row = nvfp4_global_encode_scale(*a.amax_row);
-  const float s_enc_col = nvfp4_global_encode_scale(*a.amax_col);
+  const float s_enc_row = nvfp4_global_encode_scale(amax_r);
+  const float s_enc_col = nvfp4_global_encode_scale(amax_c);
   const bool want_col = a.col_fp4 != nullptr;
   if (tid < 128) sm.lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
   else sm.lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
@@ -786,7 +859,7 @@ constexpr int kStripStageBytes = 1024;  // per warp: row codes of one strip awai
 
 __host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm) {
   return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes) + 2 * 128 * sizeof(ScaleLut) +
-         (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + (size_t)k_norm * sizeof(float) + 1024;
+         (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + 16 + (size_t)k_norm * sizeof(float) + 1024;
 }
 
 template <bool ENCODE_CENTRIC, bool NORM>
@@ -801,7 +874,8 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   ScaleLut* lut_row = reinterpret_cast<ScaleLut*>(staging + (size_t)kStripWarps * kStripStageBytes);
   ScaleLut* lut_col = lut_row + 128;
   uint64_t* bars = reinterpret_cast<uint64_t*>(lut_col + 128);                 // [warp][depth]
-  float* gamma_f = reinterpret_cast<float*>(bars + kStripWarps * depth);       // [K] (NORM)
+  float* amax_slot = reinterpret_cast<float*>(bars + kStripWarps * depth);     // 16 bytes
+  float* gamma_f = amax_slot + 4;                                              // [K] (NORM)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int wv = warp & 3;          // which 32 rows of the chunk
@@ -841,9 +915,20 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   // The input is never written by the pass-1 kernel this one may have been launched behind, so the
   // first strips are already on their way; amax / inv_rms are that kernel's results.
   pdl_wait();
-  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = *a.amax_row / 2688.0f;
-  const float s_enc_row = nvfp4_global_encode_scale(*a.amax_row);
-  const float s_enc_col = nvfp4_global_encode_scale(*a.amax_col);
+  float amax_r, amax_c;
+  if (a.n_partials > 0) {
+    amax_r = amax_c = amax_from_partials(a.partials, a.n_partials, amax_slot);
+    if (tid == 0 && blockIdx.x == 0 && a.amax_out != nullptr) {
+      a.amax_out[0] = amax_r;
+      a.amax_out[1] = amax_r / 2688.0f;
+    }
+  } else {
+    amax_r = *a.amax_row;
+    amax_c = *a.amax_col;
+  }
+  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = amax_r / 2688.0f;
+  const float s_enc_row = nvfp4_global_encode_scale(amax_r);
+  const float s_enc_col = nvfp4_global_encode_scale(amax_c);
   const bool want_col = a.col_fp4 != nullptr;
   if (tid < 128) lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
   else if (tid < 256) lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
@@ -1053,19 +1138,47 @@ rht16_amax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 // Host launchers
 // ---------------------------------------------------------------------------------------
 
-int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st, bool finalize) {
-  FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
-  const size_t n_vec = (size_t)n_elems / 8;
-  if (n_vec > 0) {
-    int grid = (int)std::min<size_t>((n_vec + 255) / 256, (size_t)device_sm_count() * 8);
-    amax_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(x), n_vec, amax_sg);
-    FP4_CUDA_CHECK(cudaGetLastError());
+// Launch configuration with the programmatic-serialisation attribute (when pdl): the kernel may start
+// while the kernel before it on the stream still runs and must call pdl_wait() before touching that
+// kernel's results.
+struct PdlLaunch {
+  cudaLaunchConfig_t cfg{};
+  cudaLaunchAttribute attr[1];
+  PdlLaunch(dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl) {
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl ? 1 : 0;
   }
-  if (finalize) {
-    finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
-    FP4_CUDA_CHECK(cudaGetLastError());
-  }
+  PdlLaunch(const PdlLaunch&) = delete;
+};
+
+// Reduction of the per-CTA maxima into amax_sg[0..1], launched behind the kernel that produced them.
+static int launch_reduce_partials(const float* partials, int n, float* amax_sg, cudaStream_t st) {
+  PdlLaunch l(dim3(1), dim3(256), 0, st, true);
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, reduce_partials_kernel, partials, n, amax_sg));
   return 0;
+}
+
+int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st, float* scratch,
+                AmaxPartials* partials_out) {
+  if (scratch == nullptr) scratch = stream_scratch(st);
+  if (scratch == nullptr) return -1;
+  const size_t n_vec = (size_t)n_elems / 8;
+  int grid = (int)std::min<size_t>((n_vec + 255) / 256, std::min<size_t>((size_t)device_sm_count() * 8, kScratchFloats));
+  grid = std::max(grid, 1);   // an empty input still leaves one partial (0)
+  amax_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(x), n_vec, scratch);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  if (partials_out != nullptr) {
+    partials_out->ptr = scratch;
+    partials_out->count = grid;
+    return 0;
+  }
+  return launch_reduce_partials(scratch, grid, amax_sg, st);
 }
 
 template <bool EC, bool NORM, bool W2D = false, bool OPT = false>
@@ -1076,17 +1189,8 @@ static int launch_quantize_t(const CUtensorMap& tmap, const QuantArgs& args, cud
   const int n_chunks = args.chunks_m * args.chunks_k;
   const int grid = std::min(n_chunks, (OPT ? 1 : 2) * device_sm_count());
   if (grid == 0) return 0;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kQThreads);
-  cfg.dynamicSmemBytes = (size_t)smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, args));
+  PdlLaunch l(dim3((unsigned)grid), dim3(kQThreads), (size_t)smem, st, pdl);
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, tmap, args));
   return 0;
 }
 
@@ -1115,17 +1219,8 @@ static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStr
   const int n_chunks = args.chunks_m * args.chunks_k;
   const int grid = std::min((n_chunks + 1) / 2, device_sm_count());
   if (grid == 0) return 0;
-  cudaLaunchConfig_t cfg{};
-  cfg.gridDim = dim3((unsigned)grid);
-  cfg.blockDim = dim3(kStripWarps * 32);
-  cfg.dynamicSmemBytes = (size_t)smem;
-  cfg.stream = st;
-  cudaLaunchAttribute attr[1];
-  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  attr[0].val.programmaticStreamSerializationAllowed = 1;
-  cfg.attrs = attr;
-  cfg.numAttrs = pdl ? 1 : 0;
-  FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, kern, tmap, tmap_row, args));
+  PdlLaunch l(dim3((unsigned)grid), dim3(kStripWarps * 32), (size_t)smem, st, pdl);
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, tmap, tmap_row, args));
   return 0;
 }
 
@@ -1139,7 +1234,9 @@ static bool strip_kernel_applies(const QuantArgs& a, bool norm) {
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
-                           cudaStream_t st, bool weight_2d, const QuantOpt* opt, bool behind_pass1) {
+                           cudaStream_t st, bool weight_2d, const QuantOpt* opt, const AmaxPartials* partials,
+                           float* amax_out) {
+  const bool behind_pass1 = partials != nullptr;
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
                             (uint64_t)K * 2, 64, kChunk, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -1152,6 +1249,13 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc;
   a.col_fp4 = (uint8_t*)col_fp4; a.col_sc = (uint8_t*)col_sc;
   a.sg_out = sg_out;
+  if (partials != nullptr) {
+    if (partials->ptr == nullptr || partials->count <= 0 || partials->count > kScratchFloats)
+      return set_error("launch_quantize: bad partial-amax descriptor");
+    a.partials = partials->ptr;
+    a.n_partials = partials->count;
+    a.amax_out = amax_out;
+  }
   a.status = device_status_ptr();
   if (a.status == nullptr) return -1;
   a.M = (int)M; a.K = (int)K;
@@ -1180,56 +1284,64 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
 
 // Warps per CTA of the pipelined statistics kernel for rows of K elements (0: rows too long for it).
 static int stats_warps_for(int64_t K) {
-  const int64_t budget = 227 * 1024 - K * 2 - 512;
+  const int64_t budget = 227 * 1024 - K * 4 - 2048;
   const int64_t w = budget / (kStatsDepth * K * 2);
   const int64_t cap = K <= 4096 ? kStatsMaxWarps : 6;
   return (int)std::max<int64_t>(0, std::min<int64_t>(w, cap));
 }
 
 template <int NV, bool CI>
-static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* amax_sg, float eps,
-                          int64_t M, int64_t K, int warps, int* status, cudaStream_t st) {
+static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
+                          int64_t M, int64_t K, int warps, int* status, cudaStream_t st, int* grid_out) {
   auto kern = rmsnorm_stats_kernel<NV, CI>;
-  const size_t smem = (size_t)K * 2 + (size_t)warps * kStatsDepth * K * 2 + (size_t)warps * kStatsDepth * 8;
+  const size_t smem = (size_t)K * 4 + (size_t)warps * kStatsDepth * K * 2 + (size_t)warps * kStatsDepth * 8;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
-  kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K, status);
+  kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, partials, eps, (int)M, (int)K, status);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  *grid_out = grid;
   return 0;
 }
 
+// RMSNorm statistics of x [M, K]: inv_rms per row (computed, or read when !compute_inv) and the tensor
+// amax of bf16(x * inv_rms * gamma).  partials_out == nullptr: amax_sg[0..1] are written on the stream
+// (two launches).  Otherwise only the per-CTA maxima are produced, in `scratch`, for the quantiser
+// launched next.
 static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms, float* amax_sg, float eps,
-                                int64_t M, int64_t K, bool compute_inv, cudaStream_t st, bool finalize = true) {
+                                int64_t M, int64_t K, bool compute_inv, cudaStream_t st, float* scratch = nullptr,
+                                AmaxPartials* partials_out = nullptr) {
   if ((reinterpret_cast<uintptr_t>(gamma) & 15) != 0) return set_error("rmsnorm statistics: gamma must be 16-byte aligned");
-  FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
-  if (M > 0) {
-    auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
-    auto gb = reinterpret_cast<const __nv_bfloat16*>(gamma);
-    const int warps = stats_warps_for(K);
-    int rc = 0;
-    if (K <= 8192 && warps >= 2) {
-      int* status = device_status_ptr();
-      if (status == nullptr) return -1;
-      if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
-                                      : launch_stats_t<4, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
-      else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
-                                           : launch_stats_t<8, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
-      else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
-                                           : launch_stats_t<16, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
-      else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st)
-                            : launch_stats_t<32, false>(xb, gb, inv_rms, amax_sg, eps, M, K, warps, status, st);
-      if (rc) return rc;
-    } else {
-      const int grid = (int)std::min<int64_t>((M + 7) / 8, (int64_t)device_sm_count() * 8);
-      if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-      else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, amax_sg, eps, (int)M, (int)K);
-    }
+  if (scratch == nullptr) scratch = stream_scratch(st);
+  if (scratch == nullptr) return -1;
+  auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
+  auto gb = reinterpret_cast<const __nv_bfloat16*>(gamma);
+  const int warps = stats_warps_for(K);
+  int grid = 0;
+  if (K <= 8192 && warps >= 2) {
+    int* status = device_status_ptr();
+    if (status == nullptr) return -1;
+    int rc;
+    if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
+                                    : launch_stats_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
+    else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
+                                         : launch_stats_t<8, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
+    else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
+                                         : launch_stats_t<16, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
+    else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
+                          : launch_stats_t<32, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
+    if (rc) return rc;
+  } else {
+    grid = (int)std::min<int64_t>((M + 7) / 8, std::min<int64_t>((int64_t)device_sm_count() * 8, kScratchFloats));
+    if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K);
+    else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K);
     FP4_CUDA_CHECK(cudaGetLastError());
   }
-  if (finalize) {
-    finalize_sg_kernel<<<1, 1, 0, st>>>(amax_sg);
-    FP4_CUDA_CHECK(cudaGetLastError());
+  if (partials_out != nullptr) {
+    partials_out->ptr = scratch;
+    partials_out->count = grid;
+    return 0;
   }
-  return 0;
+  return launch_reduce_partials(scratch, grid, amax_sg, st);
 }
 
 }  // namespace fp4b200
@@ -1274,10 +1386,11 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
     return set_error("nvfp4_quantize_for_gemm: row_fp4, row_sc and amax_sg are required");
   if (return_transpose && (col_fp4 == nullptr || col_sc == nullptr))
     return set_error("nvfp4_quantize_for_gemm: return_transpose needs col_fp4 and col_sc");
-  if (int rc = launch_amax(x_bf16, M * K, amax_sg, (cudaStream_t)stream, false)) return rc;
-  return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
-                         return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, amax_sg + 1,
-                         true, (cudaStream_t)stream, false, nullptr, true);
+  AmaxPartials part;
+  if (int rc = launch_amax(x_bf16, M * K, amax_sg, (cudaStream_t)stream, nullptr, &part)) return rc;
+  return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
+                         return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr,
+                         true, (cudaStream_t)stream, false, nullptr, &part, amax_sg);
 }
 
 int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
@@ -1326,9 +1439,10 @@ int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
   if (int rc = check_quant_shapes(w_bf16, N, K, "nvfp4_quantize_weight_2d")) return rc;
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc || !amax_sg)
     return set_error("nvfp4_quantize_weight_2d: all outputs are required");
-  if (int rc = launch_amax(w_bf16, N * K, amax_sg, (cudaStream_t)stream, false)) return rc;
-  return launch_quantize(w_bf16, N, K, amax_sg, amax_sg, false, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc,
-                         amax_sg + 1, true, (cudaStream_t)stream, true, nullptr, true);
+  AmaxPartials part;
+  if (int rc = launch_amax(w_bf16, N * K, amax_sg, (cudaStream_t)stream, nullptr, &part)) return rc;
+  return launch_quantize(w_bf16, N, K, nullptr, nullptr, false, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc,
+                         nullptr, true, (cudaStream_t)stream, true, nullptr, &part, amax_sg);
 }
 
 int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
@@ -1352,11 +1466,12 @@ int fp4b200_nvfp4_fused_norm_quantize(const void* x_bf16, const void* gamma_bf16
     return set_error("nvfp4_fused_norm_quantize: col_fp4 and col_sc must both be given or both be null");
   if ((reinterpret_cast<uintptr_t>(gamma_bf16) & 15) != 0)
     return set_error("nvfp4_fused_norm_quantize: gamma must be 16-byte aligned");
+  AmaxPartials part;
   if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, compute_inv_rms != 0,
-                                    (cudaStream_t)stream, false))
+                                    (cudaStream_t)stream, nullptr, &part))
     return rc;
-  return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, encode_centric != 0, inv_rms, gamma_bf16, row_fp4,
-                         row_sc, col_fp4, col_sc, amax_sg + 1, true, (cudaStream_t)stream, false, nullptr, true);
+  return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, inv_rms, gamma_bf16, row_fp4,
+                         row_sc, col_fp4, col_sc, nullptr, true, (cudaStream_t)stream, false, nullptr, &part, amax_sg);
 }
 
 
@@ -1374,11 +1489,11 @@ int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
 
 
 // ---- variant that allocates nothing -------------------------------------------------------
-// Scratch of the fused producer (inverse RMS per row, tensor amax, sg) in a fixed device array
-// owned by the library, for callers that must not allocate.  Every device that loads the
-// library holds kNoAllocMaxRows * 4 + 256 bytes of it until the process exits.
+// Scratch of the fused producer (inverse RMS per row, per-CTA partial maxima of pass 1) in a fixed
+// device array owned by the library, for callers that must not allocate.  Every device that loads
+// the library holds (kNoAllocMaxRows + kScratchFloats) * 4 bytes of it until the process exits.
 constexpr int64_t kNoAllocMaxRows = 65536;
-static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxRows + 64];
+static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxRows + kScratchFloats];
 
 // Device address of the scratch array on the current device.  The array's name is only a
 // host-side handle, so the address is looked up once per device and cached.
@@ -1417,12 +1532,14 @@ int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* ga
     return set_error("nvfp4_fused_norm_quantize_noalloc: gamma must be 16-byte aligned");
   float* scratch = noalloc_scratch_ptr();
   if (scratch == nullptr) return -1;
-  float* amax_sg = scratch;        // [0] amax (cleared by the statistics launcher), [1] sg
-  float* inv_rms = scratch + 64;   // [M]
-  if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, true, (cudaStream_t)stream, false))
+  float* partials = scratch;                 // [kScratchFloats] per-CTA maxima of the statistics kernel
+  float* inv_rms = scratch + kScratchFloats;  // [M]
+  AmaxPartials part;
+  if (int rc = launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, nullptr, eps, M, K, true, (cudaStream_t)stream, partials,
+                                    &part))
     return rc;
-  return launch_quantize(x_bf16, M, K, amax_sg, amax_sg, true, inv_rms, gamma_bf16, row_fp4, row_sc, col_fp4,
-                         col_sc, sg_out, true, (cudaStream_t)stream, false, nullptr, true);
+  return launch_quantize(x_bf16, M, K, nullptr, nullptr, true, inv_rms, gamma_bf16, row_fp4, row_sc, col_fp4,
+                         col_sc, sg_out, true, (cudaStream_t)stream, false, nullptr, &part, nullptr);
 }
 
 }  // extern "C"
