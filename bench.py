@@ -396,7 +396,7 @@ def main():
     quant_bytes = M_ROWS * K_COLS * 3.125
     stats_bytes = M_ROWS * K_COLS * 2.0
     achieved = quant_bytes / (t_quant * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "nvfp4_quantize_kernel<encode_centric, norm> (pass 2)",
+    roofline = {"bound": "hbm", "kernel": "nvfp4_quantize_strip_kernel<encode_centric, norm> (pass 2)",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": TRAFFIC_PER_LAUNCH,
                 "algorithmic_bytes_per_launch": quant_bytes, "avg_launch_ms": t_quant,
@@ -455,7 +455,7 @@ def main():
                 "config": {"workload": WORKLOAD, "rows_per_gpu": M_ROWS, "cols": K_COLS,
                            "l2": "inputs rotate over 3 copies of X (402 MB > 126 MB L2) between steps",
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
-                "clocks": clocks, "e2e": e2e, "gpu_launches": 3 * args.steps, "roofline": roofline,
+                "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
                 "cpu_baseline": cpu, "ffn_forward": ffn}
         print(json.dumps(line), flush=True)
     if world > 1:
@@ -464,7 +464,7 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one pass-2 launch at the bench size, from the ncu
 # capture summarised under profiles/.
-TRAFFIC_PER_LAUNCH = 134324736 + 35709184  # profiles/fused_rmsnorm_nvfp4_quant_16384x4096.md (in-kernel DRAM bytes)
+TRAFFIC_PER_LAUNCH = 134743808 + 38977024  # profiles/fused_rmsnorm_nvfp4_quant_16384x4096.md (in-kernel DRAM bytes)
 
 if __name__ == "__main__":
     main()
