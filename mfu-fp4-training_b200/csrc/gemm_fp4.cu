@@ -270,6 +270,135 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMa
     }
 }
 
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
+
+// bf16 outputs without fp32 accumulation take this form of the epilogue.
+__device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
+  return !g.out_fp32 && g.accum_f32 == nullptr;
+}
+
+// Epilogue for bf16 outputs in two phases.  Phase 1 drains the warp's quadrant of the accumulator
+// (256 columns): the first 128 columns go straight into the warp's two staging buffers, the other
+// 128 into 64 registers of packed bf16 — the load of the next 16 columns is in flight while the
+// current 16 are scaled and rounded — and then release() is called, after which the MMA warp may
+// overwrite the accumulator.  Phase 2 (TMA stores of the staged half, then staging and stores of the
+// register half) runs while the next tile's MMAs are already issuing, which is what the single
+// accumulator (256 + scale columns fill tensor memory) would otherwise forbid.
+template <typename Release>
+__device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t tmem,
+                                                   uint8_t* epi, int row0, int tn, float a_sg, int quad, int lane,
+                                                   Release release) {
+  float gs = a_sg;
+  if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? tn : 0));
+  const int row = row0 + quad * 32 + lane;
+  const int col0 = tn * kGemmBN;
+  int oi = 0, col_start = 0;
+  while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
+  const int ocol = col0 - col_start;
+  const uint32_t tbase = tmem + ((uint32_t)(quad * 32) << 16);
+  const __nv_bfloat16* res_row = g.residual != nullptr ? g.residual + (size_t)row * g.residual_ld + col0 : nullptr;
+  uint8_t* rowp = epi + lane * 128;
+  const int sw = lane & 7;
+
+  // eight packed words (16 columns) + optional residual
+  auto add_residual = [&](uint32_t (&w)[8], int col) {
+    const uint4* rs = reinterpret_cast<const uint4*>(res_row + col);
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const uint4 rv = __ldg(rs + q);
+      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const uint32_t d = w[4 * q + e];
+        w[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]), bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
+      }
+    }
+  };
+
+  // the stores of the previous tile have finished reading both staging buffers (issued a tile ago)
+  if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+  __syncwarp();
+
+  uint32_t o[64];
+  uint32_t ra[16], rb[16];
+  tmem_ld16(tbase, ra);
+#pragma unroll
+  for (int c = 0; c < 16; ++c) {          // 16 columns each
+    tmem_ld_wait();
+    if (c + 1 < 16) {
+      if (c & 1) tmem_ld16(tbase + (uint32_t)(c + 1) * 16, ra);
+      else tmem_ld16(tbase + (uint32_t)(c + 1) * 16, rb);
+    }
+    uint32_t w[8];
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
+      const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
+      w[q] = f32x2_to_bf16x2(__uint_as_float(lo) * gs, __uint_as_float(hi) * gs);
+    }
+    if (c < 8) {
+      // slab c/4 (64 columns = 128 bytes per row), 16-byte pieces 2*(c%4) and 2*(c%4)+1 of the row
+      if (res_row != nullptr) add_residual(w, c * 16);
+      uint8_t* dst = rowp + (c >> 2) * 4096;
+      const int p0 = (c & 3) * 2;
+      *reinterpret_cast<uint4*>(dst + ((p0 ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(dst + (((p0 + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    } else {
+#pragma unroll
+      for (int q = 0; q < 8; ++q) o[(c - 8) * 8 + q] = w[q];
+    }
+  }
+  release();
+
+  // staged half: two TMA stores
+  fence_proxy_async_smem();
+  __syncwarp();
+  if (lane == 0) {
+    tma_store_2d(&tmap_d.m[oi], epi, ocol, row0 + quad * 32);
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    tma_store_2d(&tmap_d.m[oi], epi + 4096, ocol + 64, row0 + quad * 32);
+    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+  }
+  // register half: slabs 2 and 3 through the same two buffers
+#pragma unroll
+  for (int slab = 2; slab < 4; ++slab) {
+    uint8_t* dst = rowp + (slab & 1) * 4096;
+    if (res_row != nullptr) {
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) w[q] = o[(slab - 2) * 32 + cc * 8 + q];
+        add_residual(w, slab * 64 + cc * 16);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[(slab - 2) * 32 + cc * 8 + q] = w[q];
+      }
+    }
+    // the store issued from this buffer (slab - 2) must have finished reading it
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 8; ++q)
+      *reinterpret_cast<uint4*>(dst + ((q ^ sw) << 4)) =
+          make_uint4(o[(slab - 2) * 32 + 4 * q], o[(slab - 2) * 32 + 4 * q + 1], o[(slab - 2) * 32 + 4 * q + 2],
+                     o[(slab - 2) * 32 + 4 * q + 3]);
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(&tmap_d.m[oi], epi + (slab & 1) * 4096, ocol + slab * 64, row0 + quad * 32);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+}
+
 template <bool MX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
@@ -445,11 +574,18 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         break;
       }
       tc_fence_after();
-      epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
       // accumulator drained: let the MMA warp start the next tile
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&sm.acc_empty);
+      auto release = [&]() {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&sm.acc_empty);
+      };
+      if (epilogue_is_bf16_plain(g)) {
+        epilogue_tile_bf16(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+      } else {
+        epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
+        release();
+      }
       acc_phase ^= 1;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staged stores have left shared memory
