@@ -7,6 +7,8 @@ import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.path.join(HERE, "libfp4b200.so")
+if os.environ.get("FP4B200_LIB"):
+    LIB_PATH = os.environ["FP4B200_LIB"]   # another build of the same library (A/B timing)
 
 _c_void_p = ctypes.c_void_p
 _i64 = ctypes.c_int64

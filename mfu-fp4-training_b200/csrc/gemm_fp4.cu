@@ -287,8 +287,8 @@ __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
 
 // Epilogue for bf16 outputs in two phases.  Phase 1 drains the warp's quadrant of the accumulator
 // (256 columns): the first 128 columns go straight into the warp's two staging buffers, the other
-// 128 into 64 registers of packed bf16 — the load of the next 16 columns is in flight while the
-// current 16 are scaled and rounded — and then release() is called, after which the MMA warp may
+// 128 into 64 registers of packed bf16 — the load of the next 32 columns is in flight while the
+// current 32 are scaled and rounded — and then release() is called, after which the MMA warp may
 // overwrite the accumulator.  Phase 2 (TMA stores of the staged half, then staging and stores of the
 // register half) runs while the next tile's MMAs are already issuing, which is what the single
 // accumulator (256 + scale columns fill tensor memory) would otherwise forbid.
@@ -328,32 +328,41 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   __syncwarp();
 
   uint32_t o[64];
-  uint32_t ra[16], rb[16];
-  tmem_ld16(tbase, ra);
+  uint32_t ra[32], rb[32];
+  tmem_ld32(tbase, ra);
 #pragma unroll
-  for (int c = 0; c < 16; ++c) {          // 16 columns each
+  for (int c = 0; c < 8; ++c) {           // 32 columns each; the next load is in flight while these are converted
     tmem_ld_wait();
-    if (c + 1 < 16) {
-      if (c & 1) tmem_ld16(tbase + (uint32_t)(c + 1) * 16, ra);
-      else tmem_ld16(tbase + (uint32_t)(c + 1) * 16, rb);
+    if (c + 1 < 8) {
+      if (c & 1) tmem_ld32(tbase + (uint32_t)(c + 1) * 32, ra);
+      else tmem_ld32(tbase + (uint32_t)(c + 1) * 32, rb);
     }
-    uint32_t w[8];
+    uint32_t w[16];
 #pragma unroll
-    for (int q = 0; q < 8; ++q) {
+    for (int q = 0; q < 16; ++q) {
       const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
       const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
       w[q] = f32x2_to_bf16x2(__uint_as_float(lo) * gs, __uint_as_float(hi) * gs);
     }
-    if (c < 8) {
-      // slab c/4 (64 columns = 128 bytes per row), 16-byte pieces 2*(c%4) and 2*(c%4)+1 of the row
-      if (res_row != nullptr) add_residual(w, c * 16);
-      uint8_t* dst = rowp + (c >> 2) * 4096;
-      const int p0 = (c & 3) * 2;
-      *reinterpret_cast<uint4*>(dst + ((p0 ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
-      *reinterpret_cast<uint4*>(dst + (((p0 + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    if (c < 4) {
+      // slab c/2 (64 columns = 128 bytes per row), 16-byte pieces 4*(c%2) .. 4*(c%2)+3 of the row
+      if (res_row != nullptr) {
+        uint32_t w0[8], w1[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { w0[q] = w[q]; w1[q] = w[8 + q]; }
+        add_residual(w0, c * 32);
+        add_residual(w1, c * 32 + 16);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) { w[q] = w0[q]; w[8 + q] = w1[q]; }
+      }
+      uint8_t* dst = rowp + (c >> 1) * 4096;
+      const int p0 = (c & 1) * 4;
+#pragma unroll
+      for (int q = 0; q < 4; ++q)
+        *reinterpret_cast<uint4*>(dst + (((p0 + q) ^ sw) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
     } else {
 #pragma unroll
-      for (int q = 0; q < 8; ++q) o[(c - 8) * 8 + q] = w[q];
+      for (int q = 0; q < 16; ++q) o[(c - 4) * 16 + q] = w[q];
     }
   }
   release();

@@ -152,6 +152,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int stage = 0;
       uint32_t phase = 0, acc_phase = 0;
       bool ok = true;
+      const uint32_t acc_full_remote = map_to_cta(&sm.acc_full, 1);
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
         if (!mbar_wait_timed(&sm.acc_empty, acc_phase ^ 1)) {
           atomicExch(g.status, kStatusGemmEpilogueTimeout);
@@ -185,7 +186,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           tc_commit_pair(smem_u32(&sm.empty[stage]));   // the producer forwards it to the other CTA
           if (++stage == kPairStages) { stage = 0; phase ^= 1; }
         }
-        if (ok) tc_commit_pair(smem_u32(&sm.acc_full));   // an epilogue warp forwards it to the other CTA
+        if (ok) {
+          // once per tile: signal both CTAs' epilogues directly (a forwarded arrival would add a hop)
+          tc_commit_pair(smem_u32(&sm.acc_full));
+          tc_commit_pair(acc_full_remote);
+        }
         acc_phase ^= 1;
       }
     }
@@ -237,7 +242,6 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     float a_sg = g.fixed_scale;
     if (g.a_sg != nullptr) a_sg = __ldg(g.a_sg);
     const uint32_t acc_empty_leader = map_to_cta(&sm.acc_empty, 0);
-    const uint32_t acc_full_peer = map_to_cta(&sm.acc_full, 1);
     bool ok = true;
     for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
       int tm, tn;
@@ -247,7 +251,6 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         ok = false;
         break;
       }
-      if (rank == 0 && warp == 2 && lane == 0) mbar_arrive_cluster(acc_full_peer);
       tc_fence_after();
       // this CTA's half of the accumulator is drained: tell the leader's MMA thread
       auto release = [&]() {
