@@ -199,6 +199,35 @@ int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_s
 int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,
                        const void* residual_bf16, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* ---- helpers around the hot path -------------------------------------------------------- */
+
+/* mxfp4_quantize_weight_2d(input) (mxfp4_v4/tk_quantize.cu:2734-2737; kernel mx_weight_2d_quantize,
+ * mxfp4_v3_quantize.cuh:1797-1960): one E8M0 scale per 32x32 tile shared by both orientations = the
+ * ceil exponent of the tile amax, lowered by one when amax * 2^-(e-127) < 0.87; column codes are the
+ * transposed row codes. */
+int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
+                                     void* col_fp4, void* col_sc, void* stream);
+
+/* nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps) (nvfp4_b200_gemm.cu:1792-1803; kernel
+ * common/c1_rms_reduce.cuh:11-38), also the first step of tk_fused_norm_quantize_from_row_rms_partial
+ * (nvfp4_v5/tk_quantize.cu:8266-8308) and of mxfp4_fused_rmsnorm_quantize_row_and_col_from_row_rms_partial
+ * (mxfp4_v4/tk_quantize.cu:6960-7052): inv_rms[r] = rsqrtf(sum_c partial[r, c] / hidden_size + eps), the
+ * sum taken per lane over columns l, l+32, ... and then by a shuffle-down tree, as the reference. */
+int fp4b200_row_rms_reduce(const float* row_rms_partial, int64_t M, int64_t partial_cols, int64_t hidden_size,
+                           float eps, float* inv_rms, void* stream);
+
+/* fp32_to_fp4x2(A_fp32) / fp4x2_to_fp32(A_fp4x2) of the reference GEMM module (nvfp4_b200_gemm.cu:1480-1510;
+ * kernels nvfp4_quantize.cuh:293-308): element 2i in the low nibble, RN-even, saturating. */
+int fp4b200_fp32_to_fp4x2(const float* in_f32, int64_t n_pairs, void* out_fp4x2, void* stream);
+int fp4b200_fp4x2_to_fp32(const void* in_fp4x2, int64_t n_bytes, float* out_f32, void* stream);
+
+/* nvfp4_quantize(A_bf16, A_fp4x2, A_sc, A_sc_global, scale_2d) of the reference GEMM module
+ * (nvfp4_b200_gemm.cu:1443-1478; kernels nvfp4_quantize.cuh:57-255): A_sc_global = amax / (6*448);
+ * block scale e4m3(b / 6 * (1 / max(A_sc_global, 1e-12))); codes e2m1(x / max(float(scale) * A_sc_global, 1e-12));
+ * scale_2d shares one scale per 16x16 tile.  Scale tiles [M/128, N/64, 512]. */
+int fp4b200_tk_nvfp4_quantize(const void* A_bf16, int64_t M, int64_t N, void* A_fp4x2, void* A_sc,
+                              float* A_sc_global, int scale_2d, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

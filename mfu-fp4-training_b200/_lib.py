@@ -56,6 +56,11 @@ SIGNATURES = {
                                    ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _i64, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p, _i64, _i64,
                            _i64, _c_void_p],
+    "fp4b200_mxfp4_quantize_weight_2d": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_row_rms_reduce": [_c_void_p, _i64, _i64, _i64, _f32, _c_void_p, _c_void_p],
+    "fp4b200_fp32_to_fp4x2": [_c_void_p, _i64, _c_void_p, _c_void_p],
+    "fp4b200_fp4x2_to_fp32": [_c_void_p, _i64, _c_void_p, _c_void_p],
+    "fp4b200_tk_nvfp4_quantize": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p],
 }
 _RESTYPES = {"fp4b200_last_error": ctypes.c_char_p}
 

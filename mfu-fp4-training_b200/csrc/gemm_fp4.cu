@@ -338,11 +338,13 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
       else tmem_ld32(tbase + (uint32_t)(c + 1) * 32, rb);
     }
     uint32_t w[16];
+    const float2 gs2 = make_float2(gs, gs);
 #pragma unroll
     for (int q = 0; q < 16; ++q) {
       const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
       const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
-      w[q] = f32x2_to_bf16x2(__uint_as_float(lo) * gs, __uint_as_float(hi) * gs);
+      const float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+      w[q] = f32x2_to_bf16x2(v.x, v.y);
     }
     if (c < 4) {
       // slab c/2 (64 columns = 128 bytes per row), 16-byte pieces 4*(c%2) .. 4*(c%2)+3 of the row

@@ -5,6 +5,8 @@
 //   E8M0 of the block amax, modes RTE / ceil / floor            :1295-1342
 //   coefficient 6 * 2^(127-e), codes = e2m1_rn(x * coefficient) :1601-1603 (exp2f_rcp util/ptx.cuh:330-338)
 //   scale bytes in 512-byte tiles of 128 rows x 4 blocks        :5059-5086
+//   weights: one scale per 32x32 tile for both orientations, ceil exponent lowered by one when the
+//   tile amax sits in the lower part of its binade ("4 over 6")  :1797-1960
 // Pipeline and shared-memory geometry are those of the NVFP4 quantiser (quant_nvfp4.cu): persistent
 // CTAs, 128x128 chunks as two 128-byte-swizzled TMA boxes, three stages.
 #include "fp4_common.cuh"
@@ -26,6 +28,7 @@ struct MxSmem {
   alignas(16) float inv_rms[2][kMxChunk];
   alignas(16) float gamma[2][kMxChunk];
   alignas(8) uint64_t full[kMxStages];
+  uint8_t tile_e8[4][4];                      // W2D: scale byte of each 32x32 tile of the chunk
 };
 
 struct MxArgs {
@@ -59,7 +62,17 @@ __device__ __forceinline__ float mx_coeff(uint32_t e) {
   return 6.0f * rcp;
 }
 
-template <bool NORM>
+// Scale byte of a 32x32 weight tile: the ceil exponent of the tile amax, lowered by one (values up to
+// 2x the top code then saturate) when amax * 2^-(e-127) < 0.87, i.e. when most of the finer grid
+// would otherwise go unused (reference mx_weight_2d_quantize, mxfp4_v3_quantize.cuh:1864-1878).
+__device__ __forceinline__ uint32_t mx_weight_tile_e8m0(float tile_amax) {
+  const uint32_t safe = mx_e8m0(tile_amax, 1);
+  const float rcp = (safe == 254) ? __uint_as_float(0x00400000u) : __uint_as_float((254u - safe) << 23);
+  const float phase = tile_amax * rcp;
+  return (safe > 0 && phase < 0.87f) ? safe - 1 : safe;
+}
+
+template <bool NORM, bool W2D>
 __global__ void __launch_bounds__(kMxThreads, 2)
 mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -129,6 +142,21 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
       return;
     }
     uint8_t* tile = sm.in[s];
+    if constexpr (W2D) {
+      // tile amaxes in the column-pass geometry: this warp holds rows grp*32.., columns chalf*64..;
+      // 16 lanes (32 columns) make one tile
+      const uint8_t* base = tile + chalf * kMxHalfBytes + (grp * 32) * 128;
+      uint32_t mx = 0;
+#pragma unroll
+      for (int i = 0; i < 32; ++i) mx = absmax_xs(mx, *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]));
+      float b = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+      b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 1));
+      b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 2));
+      b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 4));
+      b = fmaxf(b, __shfl_xor_sync(0xffffffffu, b, 8));
+      if ((lane & 15) == 0) sm.tile_e8[grp][chalf * 2 + (lane >> 4)] = (uint8_t)mx_weight_tile_e8m0(b);
+      __syncthreads();
+    }
 #pragma unroll
     for (int rep = 0; rep < 2; ++rep) {
       const int r = warp * 16 + rep * 8 + r_lo;
@@ -159,7 +187,8 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
 #pragma unroll
       for (int q = 0; q < 16; ++q) mx = absmax_xs(mx, w[q]);
       const float b = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
-      const uint32_t e = mx_e8m0(b, a.mode);
+      uint32_t e = mx_e8m0(b, a.mode);
+      if constexpr (W2D) e = sm.tile_e8[r >> 5][unit];
       const float coeff = mx_coeff(e);
       uint4 codes;
       codes.x = quant8(w, coeff); codes.y = quant8(w + 4, coeff);
@@ -177,7 +206,8 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
         w[i] = *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]);
         mx = absmax_xs(mx, w[i]);
       }
-      const uint32_t e0 = mx_e8m0(fabsf(bf16lo_to_f32(mx)), a.mode), e1 = mx_e8m0(fabsf(bf16hi_to_f32(mx)), a.mode);
+      uint32_t e0 = mx_e8m0(fabsf(bf16lo_to_f32(mx)), a.mode), e1 = mx_e8m0(fabsf(bf16hi_to_f32(mx)), a.mode);
+      if constexpr (W2D) e0 = e1 = sm.tile_e8[grp][chalf * 2 + (lane >> 4)];
       const float2 cc = make_float2(mx_coeff(e0), mx_coeff(e1));
       uint32_t q0[4], q1[4];
 #pragma unroll
@@ -224,7 +254,7 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
 }
 
 static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float* inv_rms, const void* gamma,
-                     void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st) {
+                     void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st, bool weight_2d = false) {
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,
                             64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -238,12 +268,15 @@ static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float*
   const int smem = (int)sizeof(MxSmem) + 1024;
   const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
   if (grid == 0) return 0;
-  if (inv_rms) {
-    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    mxfp4_quantize_kernel<true><<<grid, kMxThreads, smem, st>>>(tmap, a);
+  if (weight_2d) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_quantize_kernel<false, true><<<grid, kMxThreads, smem, st>>>(tmap, a);
+  } else if (inv_rms) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_quantize_kernel<true, false><<<grid, kMxThreads, smem, st>>>(tmap, a);
   } else {
-    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    mxfp4_quantize_kernel<false><<<grid, kMxThreads, smem, st>>>(tmap, a);
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_quantize_kernel<false, false><<<grid, kMxThreads, smem, st>>>(tmap, a);
   }
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
@@ -282,6 +315,13 @@ int fp4b200_mxfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
   if ((col_fp4 == nullptr) != (col_sc == nullptr))
     return set_error("mxfp4_quantize_normed: col_fp4 and col_sc must both be given or both be null");
   return launch_mx(x_bf16, M, K, mode, inv_rms, gamma_bf16, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
+                                     void* col_fp4, void* col_sc, void* stream) {
+  if (int rc = check_mx(w_bf16, N, K, 1, "mxfp4_quantize_weight_2d")) return rc;
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_quantize_weight_2d: all outputs are required");
+  return launch_mx(w_bf16, N, K, 1, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, true);
 }
 
 }  // extern "C"

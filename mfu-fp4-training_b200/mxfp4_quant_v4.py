@@ -73,3 +73,38 @@ def mxfp4_fused_silu_mul_quantize_row_and_col(h1_raw, h3, mode=0):
         _lib.call("fp4b200_silu_mul_bf16", h1_raw.data_ptr(), h3.data_ptr(), h1_raw.numel(), h.data_ptr(),
                   amax_sg.data_ptr(), _stream(h1_raw))
     return mxfp4_quantize_row_and_col(h, mode)
+
+
+def mxfp4_quantize_weight_2d(input):
+    """tk_quantize.cu:2734-2737 — one E8M0 scale per 32x32 tile shared by both orientations;
+    (row_fp4, row_sc, col_fp4, col_sc)."""
+    N, K = _check_bf16_2d(input, "input")
+    with torch.cuda.device(input.device):
+        rf, rs, cf, cs = _alloc(N, K, input.device, True)
+        _lib.call("fp4b200_mxfp4_quantize_weight_2d", input.data_ptr(), N, K, rf.data_ptr(), rs.data_ptr(),
+                  cf.data_ptr(), cs.data_ptr(), _stream(input))
+    return rf.view(_FP4), rs, cf.view(_FP4), cs
+
+
+def mxfp4_fused_rmsnorm_quantize_row_and_col_from_row_rms_partial(input, norm_weight, row_rms_partial, epsilon, mode=1):
+    """tk_quantize.cu:6960-7052 — inverse RMS from GEMM-epilogue row partials [M, K/256], then the fused
+    RMSNorm + row/col quantiser; (row_fp4, row_sc, col_fp4, col_sc, inv_rms).  The reference accepts only
+    mode 1 ("encode"), K == 4096 and M % 256 == 0 here; so does this mirror."""
+    from .tk_quant_v5 import row_rms_reduce
+    M, K = _check_bf16_2d(input, "input")
+    if int(mode) != 1:
+        raise RuntimeError("MXFP4 exact C/D/E production path requires encode mode")
+    if M % 256 or K != 4096:
+        raise RuntimeError("MXFP4 exact C/D/E consumer requires [M,4096] with M divisible by 256")
+    if (not isinstance(norm_weight, torch.Tensor) or norm_weight.dtype != torch.bfloat16 or norm_weight.numel() != K
+            or not norm_weight.is_contiguous() or norm_weight.device != input.device):
+        raise RuntimeError("norm_weight must be contiguous CUDA bfloat16 [K] on the input device")
+    if tuple(row_rms_partial.shape) != (M, K // 256) or row_rms_partial.device != input.device:
+        raise RuntimeError("row_rms_partial shape must be [M,K/256]")
+    inv_rms = row_rms_reduce(row_rms_partial, K, epsilon)
+    with torch.cuda.device(input.device):
+        rf, rs, cf, cs = _alloc(M, K, input.device, True)
+        _lib.call("fp4b200_mxfp4_quantize_normed", input.data_ptr(), norm_weight.data_ptr(), inv_rms.data_ptr(), M, K,
+                  1, rf.data_ptr(), rs.data_ptr(), cf.data_ptr(), cs.data_ptr(), _stream(input))
+    return rf.view(_FP4), rs, cf.view(_FP4), cs, inv_rms
+

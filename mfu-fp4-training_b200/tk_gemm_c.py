@@ -173,3 +173,56 @@ def nvfp4_split_dgrad_sum(A_fp4_cat, A_sc_cat, A_sg_list, B_fp4_list, B_sc_list,
         B_sg_l.append(B_sg_cat.narrow(0, i, 1))
         offs += d
     nvfp4_batched_accum_gemm(A_list, A_sc_l, list(A_sg_list), list(B_fp4_list), list(B_sc_list), B_sg_l, D_out)
+
+
+def nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps):
+    """nvfp4_b200_gemm.cu:1792-1803 — coeff[r] = rsqrt(sum(row_rms_partial[r, :]) / hidden_size + eps), in place."""
+    if (not isinstance(coeff, torch.Tensor) or not coeff.is_cuda or coeff.dtype != torch.float32 or coeff.dim() != 1
+            or not coeff.is_contiguous() or coeff.shape[0] != row_rms_partial.shape[0]):
+        raise RuntimeError("coeff must be contiguous CUDA float32 [M]")
+    p = row_rms_partial
+    if not p.is_cuda or p.dtype != torch.float32 or p.dim() != 2 or not p.is_contiguous() or p.device != coeff.device:
+        raise RuntimeError("row_rms_partial must be contiguous CUDA float32 [M,P] on coeff's device")
+    with torch.cuda.device(p.device):
+        _lib.call("fp4b200_row_rms_reduce", p.data_ptr(), p.shape[0], p.shape[1], int(hidden_size), float(eps),
+                  coeff.data_ptr(), _stream(p))
+
+
+def fp32_to_fp4x2(A_fp32):
+    """nvfp4_b200_gemm.cu:1480-1494 — [R, C] float32 -> [R, C/2] float4_e2m1fn_x2 (RN-even, saturating)."""
+    if not A_fp32.is_cuda or A_fp32.dtype != torch.float32 or A_fp32.dim() != 2 or not A_fp32.is_contiguous() \
+            or A_fp32.shape[1] % 2:
+        raise RuntimeError("fp32_to_fp4x2 expects a contiguous CUDA float32 [R, C] with even C")
+    out = torch.empty((A_fp32.shape[0], A_fp32.shape[1] // 2), dtype=torch.uint8, device=A_fp32.device)
+    with torch.cuda.device(A_fp32.device):
+        _lib.call("fp4b200_fp32_to_fp4x2", A_fp32.data_ptr(), out.numel(), out.data_ptr(), _stream(A_fp32))
+    return out.view(torch.float4_e2m1fn_x2)
+
+
+def fp4x2_to_fp32(A_fp4x2):
+    """nvfp4_b200_gemm.cu:1496-1510 — [R, C/2] packed codes -> [R, C] float32."""
+    a = A_fp4x2.view(torch.uint8)
+    if not a.is_cuda or a.dim() != 2 or not a.is_contiguous():
+        raise RuntimeError("fp4x2_to_fp32 expects a contiguous CUDA [R, C/2] tensor of packed codes")
+    out = torch.empty((a.shape[0], a.shape[1] * 2), dtype=torch.float32, device=a.device)
+    with torch.cuda.device(a.device):
+        _lib.call("fp4b200_fp4x2_to_fp32", a.data_ptr(), a.numel(), out.data_ptr(), _stream(a))
+    return out
+
+
+def nvfp4_quantize(A_bf16, A_fp4x2, A_sc, A_sc_global, scale_2d):
+    """nvfp4_b200_gemm.cu:1443-1478 — the GEMM module's own operand producer (used by its tests): fills the
+    caller's A_fp4x2 [M, N/2], A_sc (512-byte scale tiles, [M/128, N/64, 512] bytes) and A_sc_global [1]."""
+    if not A_bf16.is_cuda or A_bf16.dtype != torch.bfloat16 or A_bf16.dim() != 2 or not A_bf16.is_contiguous():
+        raise RuntimeError("A_bf16 must be a contiguous CUDA bfloat16 [M, N]")
+    M, N = A_bf16.shape
+    fp4 = A_fp4x2.view(torch.uint8)
+    sc = A_sc.view(torch.uint8)
+    if tuple(fp4.shape) != (M, N // 2) or not fp4.is_contiguous() or sc.numel() != M * N // 16 or not sc.is_contiguous():
+        raise RuntimeError("A_fp4x2 must be [M, N/2] and A_sc must hold M*N/16 scale bytes, both contiguous")
+    if A_sc_global.dtype != torch.float32 or A_sc_global.numel() != 1:
+        raise RuntimeError("A_sc_global must be a float32 tensor with one element")
+    with torch.cuda.device(A_bf16.device):
+        _lib.call("fp4b200_tk_nvfp4_quantize", A_bf16.data_ptr(), M, N, fp4.data_ptr(), sc.data_ptr(),
+                  A_sc_global.data_ptr(), int(bool(scale_2d)), _stream(A_bf16))
+

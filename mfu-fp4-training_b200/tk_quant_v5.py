@@ -118,6 +118,39 @@ def tk_fused_norm_quantize_from_inv_rms(input, gamma, inv_rms, with_silu, return
     return _fused_norm_impl(input, gamma, 0.0, with_silu, return_transpose, inv_rms)
 
 
+def row_rms_reduce(row_rms_partial, hidden_size, epsilon):
+    """inv_rms [M] from GEMM-epilogue row partials [M, P] (kernel: common/c1_rms_reduce.cuh:11-38)."""
+    p = row_rms_partial
+    if (not isinstance(p, torch.Tensor) or not p.is_cuda or p.dtype != torch.float32 or p.dim() != 2
+            or not p.is_contiguous()):
+        raise RuntimeError("row_rms_partial must be contiguous CUDA float32 [M,P]")
+    inv_rms = torch.empty(p.shape[0], dtype=torch.float32, device=p.device)
+    with torch.cuda.device(p.device):
+        _lib.call("fp4b200_row_rms_reduce", p.data_ptr(), p.shape[0], p.shape[1], int(hidden_size), float(epsilon),
+                  inv_rms.data_ptr(), _stream(p))
+    return inv_rms
+
+
+def tk_fused_norm_quantize_from_row_rms_partial(input, gamma, row_rms_partial, epsilon, with_silu, return_transpose):
+    """tk_quantize.cu:8266-8308 — inverse RMS from per-32-column partial sums of squares [M, K/32] left by a
+    GEMM epilogue, then the fused producer with that inverse RMS."""
+    M, K = _check_bf16_2d(input, "input")
+    if K > 4096:
+        raise RuntimeError("row_rms_partial warp reducer supports K <= 4096")
+    if (not isinstance(row_rms_partial, torch.Tensor) or row_rms_partial.dim() != 2
+            or tuple(row_rms_partial.shape) != (M, K // 32) or row_rms_partial.device != input.device):
+        raise RuntimeError("row_rms_partial shape must be [M,K/32] on the input device")
+    inv_rms = row_rms_reduce(row_rms_partial, K, epsilon)
+    return _fused_norm_impl(input, gamma, 0.0, with_silu, return_transpose, inv_rms)
+
+
+def tk_batched_quantize_for_gemm(inputs, return_transpose, encode_centric=True):
+    """tk_quantize.cu:11117-11152 — tk_quantize_for_gemm over a list; returns eight lists
+    (row_fp4s, row_scs, col_fp4s, col_scs, sgs, sgs, amax_keepalive, sync_keepalive)."""
+    outs = [tk_quantize_for_gemm(x, return_transpose, encode_centric) for x in inputs]
+    return tuple([o[i] for o in outs] for i in range(8))
+
+
 def _same_shape_bf16(ref, *others):
     for t in others:
         if (not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.bfloat16 or not t.is_contiguous()

@@ -496,6 +496,71 @@ def mxfp4_quantize_row_and_col(x: np.ndarray, mode: int = 1):
                 col_fp4=c_fp4, col_sc=swizzle_scales(c_e), col_sc_logical=c_e)
 
 
+def _mx_rcp(e: np.ndarray) -> np.ndarray:
+    """exp2f_rcp (util/ptx.cuh:330-338): 2^(127-e) built from the exponent field; e = 254 -> 2^-127."""
+    rcp = ((254 - e.astype(np.int64)).clip(0, 254).astype(np.uint32) << 23).view(np.float32)
+    return np.where(e == 254, F32(2.0 ** -127), rcp).astype(F32)
+
+
+def mxfp4_quantize_weight_2d(w: np.ndarray):
+    """``mxfp4_quantize_weight_2d`` (mxfp4_v4/tk_quantize.cu:2734-2737; mx_weight_2d_quantize,
+    mxfp4_v3_quantize.cuh:1797-1960): one scale per 32x32 tile for both orientations — the ceil exponent
+    of the tile amax, minus one when ``amax * 2^-(e-127) < 0.87`` — and column codes = transposed row codes."""
+    w = np.asarray(w, dtype=F32)
+    N, K = w.shape
+    assert N % 32 == 0 and K % 32 == 0
+    t = np.abs(w).reshape(N // 32, 32, K // 32, 32).max(axis=(1, 3)).astype(F32)
+    safe = mx_e8m0(t, 1)
+    with np.errstate(over="ignore", invalid="ignore"):
+        phase = (t * _mx_rcp(safe)).astype(F32)
+        e = np.where((safe > 0) & (phase < F32(0.87)), safe - 1, safe).astype(np.uint8)
+        coeff = (F32(6.0) * _mx_rcp(e)).astype(F32)
+        scaled = (w * np.repeat(np.repeat(coeff, 32, axis=0), 32, axis=1)).astype(F32)
+    codes = e2m1_encode_rn(scaled)
+    r_e = np.repeat(e, 32, axis=0)                         # [N, K/32]
+    c_e = np.repeat(np.ascontiguousarray(e.T), 32, axis=0)   # [K, N/32]
+    return dict(row_fp4=pack_fp4(codes), row_sc=swizzle_scales(r_e), row_sc_logical=r_e,
+                col_fp4=pack_fp4(np.ascontiguousarray(codes.T)), col_sc=swizzle_scales(c_e), col_sc_logical=c_e)
+
+
+def row_rms_reduce(partial: np.ndarray, hidden_size: int, eps: float) -> np.ndarray:
+    """``row_rms_coeff_warp_kernel`` (ThunderKittens/kernels/gemm/common/c1_rms_reduce.cuh:11-38): lane l adds
+    columns l, l+32, ... in order, then a shuffle-down tree (16, 8, 4, 2, 1); inv = 1/sqrt(sum/hidden + eps).
+    The final rsqrt is taken in float64 and rounded (the GPU's rsqrtf is within 2 ulp of it)."""
+    p = np.asarray(partial, dtype=F32)
+    M, P = p.shape
+    lanes = np.zeros((M, 32), dtype=F32)
+    for c0 in range(0, P, 32):
+        blk = p[:, c0:c0 + 32]
+        lanes[:, :blk.shape[1]] = (lanes[:, :blk.shape[1]] + blk).astype(F32)
+    for off in (16, 8, 4, 2, 1):
+        nxt = lanes.copy()
+        nxt[:, :32 - off] = (lanes[:, :32 - off] + lanes[:, off:]).astype(F32)
+        lanes = nxt
+    s = lanes[:, 0]
+    mean = (s / F32(hidden_size)).astype(F32)
+    return (1.0 / np.sqrt((mean + F32(eps)).astype(F32).astype(np.float64))).astype(F32)
+
+
+def tk_nvfp4_quantize(a: np.ndarray, scale_2d: bool = False):
+    """The reference GEMM module's own operand producer (ThunderKittens/kernels/gemm/nvfp4_b200/
+    nvfp4_quantize.cuh:57-255): ``sg = amax/(6*448)``; block scale ``e4m3(b/6 * (1/max(sg,1e-12)))``; codes
+    ``e2m1(x * (1/max(float(scale)*sg, 1e-12)))``; ``scale_2d`` shares the amax of each 16x16 tile."""
+    a = np.asarray(a, dtype=F32)
+    M, N = a.shape
+    amax = F32(np.abs(a).max()) if a.size else F32(0)
+    sg = (amax / (F32(6.0) * F32(448.0))).astype(F32)
+    s_glob_enc = (F32(1.0) / np.maximum(sg, F32(1e-12))).astype(F32)
+    b = np.abs(a).reshape(M, N // 16, 16).max(axis=-1).astype(F32)
+    if scale_2d:
+        b = np.repeat(b.reshape(M // 16, 16, N // 16).max(axis=1), 16, axis=0)
+    s8 = e4m3_encode(((b / F32(6.0)).astype(F32) * s_glob_enc).astype(F32))
+    s_loc = e4m3_decode(s8)
+    s_enc = (F32(1.0) / np.maximum((s_loc * sg).astype(F32), F32(1e-12))).astype(F32)
+    scaled = (a.reshape(M, N // 16, 16) * s_enc[..., None]).astype(F32).reshape(M, N)
+    return dict(fp4=pack_fp4(e2m1_encode_rn(scaled)), sc=swizzle_scales(s8), sc_logical=s8, sg=sg)
+
+
 def mxfp4_gemm_fp32(a_fp4, a_e, b_fp4, b_e) -> np.ndarray:
     """``D = (sum code_a*2^(ea-127)*code_b*2^(eb-127)) / 36`` (mxfp4_gb200/mxfp4_gemm.cuh:557-558)."""
     sa = np.exp2(a_e.astype(np.float64) - 127.0)
