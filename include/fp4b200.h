@@ -199,6 +199,16 @@ int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_s
 int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,
                        const void* residual_bf16, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list,
+ * D_out, config_idx) (mxfp4_gb200/mxfp4_gb200_gemm.cu:2572-2596; kernel mxfp4_split2_accum_gemm.cuh):
+ * D = bf16((sum_s A_full[:, off_s : off_s + w_s] * B_s^T) / 36) with all terms accumulated in tensor memory
+ * before the one rounding.  A_full's codes are [M, a_width/2]; segment s has its own scale tiles
+ * A_sc_list[s] [M/128, w_s/128, 512], operand B_list[s] [N, w_s/2] and B_sc_list[s] [N/128, w_s/128, 512].
+ * Up to 4 segments, each a multiple of 256 elements wide. */
+int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,
+                              const int64_t* a_col_widths, const void* const* A_sc_list, const void* const* B_list,
+                              const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream);
+
 /* ---- helpers around the hot path -------------------------------------------------------- */
 
 /* mxfp4_quantize_weight_2d(input) (mxfp4_v4/tk_quantize.cu:2734-2737; kernel mx_weight_2d_quantize,

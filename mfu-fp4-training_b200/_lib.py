@@ -56,6 +56,9 @@ SIGNATURES = {
                                    ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _i64, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p, _i64, _i64,
                            _i64, _c_void_p],
+    "fp4b200_mxfp4_gemm_ksplit": [_c_void_p, _i64, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
+                                  ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
+                                  _c_void_p, _int, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_quantize_weight_2d": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_row_rms_reduce": [_c_void_p, _i64, _i64, _i64, _f32, _c_void_p, _c_void_p],
     "fp4b200_fp32_to_fp4x2": [_c_void_p, _i64, _c_void_p, _c_void_p],

@@ -56,9 +56,20 @@ struct GemmSmem {
   int abort_flag;
 };
 
+// The K dimension may be the concatenation of up to kMaxKSeg segments, each with its own B tensor,
+// its own scale tensors and its own column offset inside the rows of A (one segment = a plain GEMM).
+constexpr int kMaxKSeg = 4;
+struct GemmBMaps {
+  CUtensorMap m[kMaxKSeg];
+};
+
 struct GemmArgs {
-  const uint8_t* a_sc;      // [M/128, K/(4*block), 512]
-  const uint8_t* b_sc;      // [N/128, K/(4*block), 512]
+  int n_seg;
+  int seg_stage_end[kMaxKSeg];      // cumulative number of 256-deep K stages at the end of each segment
+  int seg_a_col_bytes[kMaxKSeg];    // byte offset of the segment inside a row of A's codes
+  const uint8_t* seg_a_sc[kMaxKSeg];   // [M/128, Kseg/(4*block), 512]
+  const uint8_t* seg_b_sc[kMaxKSeg];   // [N/128, Kseg/(4*block), 512]
+  int seg_sf_tiles_k[kMaxKSeg];     // scale tiles along K per row tile, per segment
   const float* a_sg;        // device scalar (NVFP4) or null
   const float* b_sg;        // device scalar, or per-256-column-tile array when b_sg_per_tile != 0
   int b_sg_per_tile;
@@ -71,8 +82,7 @@ struct GemmArgs {
   const __nv_bfloat16* residual;  // optional [M, N] bf16 added after the bf16 rounding
   int residual_ld;
   const float* accum_f32;   // optional [M, N] fp32 partial sum added to acc*scale before the output rounding
-  int M, N, K;
-  int sf_tiles_k;           // scale tiles along K per row tile
+  int M, N, K;              // K = sum of the segments
   int* status;
 };
 
@@ -412,7 +422,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
 
 template <bool MX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                 const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   GemmSmem& sm = *reinterpret_cast<GemmSmem*>(smem_align_1024(smem_raw));
@@ -445,17 +455,28 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     // ------------------------------ TMA producer ------------------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
-      tma_prefetch_desc(&tmap_b);
+      for (int s = 0; s < g.n_seg; ++s) tma_prefetch_desc(&tmap_b.m[s]);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         int tm, tn;
         raster_tile(t, tiles_m, tiles_n, tm, tn);
-        const uint8_t* sfa_src = g.a_sc + (size_t)tm * g.sf_tiles_k * 512;
-        const uint8_t* sfb_src0 = g.b_sc + (size_t)(2 * tn) * g.sf_tiles_k * 512;
-        const uint8_t* sfb_src1 = sfb_src0 + (size_t)g.sf_tiles_k * 512;
-        for (int ks = 0; ks < k_stages; ++ks) {
+        int seg = -1, seg_end = 0, kl = 0, a_col = 0;
+        const CUtensorMap* bmap = nullptr;
+        const uint8_t *sfa_src = nullptr, *sfb_src0 = nullptr, *sfb_src1 = nullptr;
+        for (int ks = 0; ks < k_stages; ++ks, ++kl) {
+          if (ks == seg_end) {   // first stage of the next K segment
+            ++seg;
+            seg_end = g.seg_stage_end[seg];
+            kl = 0;
+            a_col = g.seg_a_col_bytes[seg];
+            bmap = &tmap_b.m[seg];
+            const size_t tiles_k = (size_t)g.seg_sf_tiles_k[seg];
+            sfa_src = g.seg_a_sc[seg] + (size_t)tm * tiles_k * 512;
+            sfb_src0 = g.seg_b_sc[seg] + (size_t)(2 * tn) * tiles_k * 512;
+            sfb_src1 = sfb_src0 + tiles_k * 512;
+          }
           if (!mbar_wait_timed(&sm.empty[stage], phase ^ 1)) {
             atomicExch(g.status, kStatusGemmTmaTimeout);
             ok = false;
@@ -463,12 +484,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           }
           constexpr int kSfPerStage = MX ? 1024 : 2048;
           mbar_expect_tx(&sm.full[stage], kATileBytes + kBTileBytes + 3 * kSfPerStage);
-          tma_load_2d(sm.a[stage], &tmap_a, ks * kGemmBKBytes, tm * kGemmBM, &sm.full[stage]);
-          tma_load_2d(sm.b[stage], &tmap_b, ks * kGemmBKBytes, tn * kGemmBN, &sm.full[stage]);
+          tma_load_2d(sm.a[stage], &tmap_a, a_col + kl * kGemmBKBytes, tm * kGemmBM, &sm.full[stage]);
+          tma_load_2d(sm.b[stage], bmap, kl * kGemmBKBytes, tn * kGemmBN, &sm.full[stage]);
           // scale tiles of this stage: NVFP4 4 tiles (256/64), MXFP4 2 tiles (256/128) per row tile
-          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)ks * kSfPerStage, kSfPerStage,
+          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)kl * kSfPerStage, kSfPerStage,
                        &sm.full[stage]);
           if (++stage == kGemmStages) { stage = 0; phase ^= 1; }
         }
@@ -623,17 +644,44 @@ static bool gemm_pair_disabled() {
   return off;
 }
 
-static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
-                       const float* B_sg, int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld,
-                       int n_out, int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N,
-                       int64_t K, cudaStream_t st, const float* accum_f32 = nullptr) {
-  CUtensorMap tmap_a, tmap_b;
-  if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)M,
-                            (uint64_t)K / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
+// K segments of one GEMM launch on the host side: D = sum_s A[:, off_s : off_s + k_s] * B_s^T, all
+// accumulated in tensor memory before the one epilogue.  a_width = elements per row of A's code matrix.
+struct KSegments {
+  int n = 0;
+  int64_t a_width = 0;
+  int64_t a_col_off[kMaxKSeg] = {0, 0, 0, 0};   // elements
+  int64_t k[kMaxKSeg] = {0, 0, 0, 0};           // elements, multiples of 256
+  const void* a_sc[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+  const void* b[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+  const void* b_sc[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+};
+
+static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const float* A_sg, const float* B_sg,
+                            int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld, int n_out,
+                            int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N, cudaStream_t st,
+                            const float* accum_f32 = nullptr) {
+  const bool pair = (M % 256) == 0 && !gemm_pair_disabled();
+  CUtensorMap tmap_a;
+  GemmBMaps tmap_b;
+  memset(&tmap_b, 0, sizeof(tmap_b));
+  if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.a_width / 2, (uint64_t)M,
+                            (uint64_t)segs.a_width / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  if (int rc = make_tmap_2d(&tmap_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)N,
-                            (uint64_t)K / 2, kGemmBKBytes, kGemmBN, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
+  int64_t K = 0;
+  GemmArgs g{};
+  g.n_seg = segs.n;
+  for (int s = 0; s < segs.n; ++s) {
+    // the pair kernel loads B in halves of 128 rows per CTA
+    if (int rc = make_tmap_2d(&tmap_b.m[s], segs.b[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.k[s] / 2, (uint64_t)N,
+                              (uint64_t)segs.k[s] / 2, kGemmBKBytes, pair ? 128 : kGemmBN, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+    K += segs.k[s];
+    g.seg_stage_end[s] = (int)(K / 256);
+    g.seg_a_col_bytes[s] = (int)(segs.a_col_off[s] / 2);
+    g.seg_a_sc[s] = (const uint8_t*)segs.a_sc[s];
+    g.seg_b_sc[s] = (const uint8_t*)segs.b_sc[s];
+    g.seg_sf_tiles_k[s] = (int)(segs.k[s] / (mx ? 128 : 64));
+  }
   GemmOutMaps omaps;
   memset(&omaps, 0, sizeof(omaps));
   for (int i = 0; i < n_out; ++i) {
@@ -643,8 +691,6 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
                               CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   }
-  GemmArgs g{};
-  g.a_sc = (const uint8_t*)A_sc; g.b_sc = (const uint8_t*)B_sc;
   g.a_sg = A_sg; g.b_sg = B_sg; g.b_sg_per_tile = b_sg_per_tile;
   g.fixed_scale = mx ? (1.0f / 36.0f) : 1.0f;
   for (int i = 0; i < 3; ++i) { g.d[i] = i < n_out ? D[i] : nullptr; g.d_col_end[i] = i < n_out ? d_col_end[i] : 0; g.d_ld[i] = i < n_out ? d_ld[i] : 0; }
@@ -652,14 +698,10 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   g.residual = (const __nv_bfloat16*)residual; g.residual_ld = residual_ld;
   g.accum_f32 = accum_f32;
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
-  g.sf_tiles_k = (int)(K / (mx ? 128 : 64));
   g.status = device_status_ptr();
   if (g.status == nullptr) return -1;
-  if ((M % 256) == 0 && !gemm_pair_disabled()) {
+  if (pair) {
     // two-CTA clusters: one 256 x 256 tile per pair of SMs
-    if (int rc = make_tmap_2d(&tmap_b, B, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K / 2, (uint64_t)N,
-                              (uint64_t)K / 2, kGemmBKBytes, 128, CU_TENSOR_MAP_SWIZZLE_128B))
-      return rc;
     const int psmem = (int)sizeof(GemmPairSmem) + 1024;
     const int pair_tiles = (int)((M / 256) * (N / kGemmBN));
     const int clusters = std::min(pair_tiles, device_sm_count() / 2);
@@ -695,6 +737,22 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   }
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
+}
+
+// plain GEMM = one K segment covering all of A
+static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                       const float* B_sg, int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld,
+                       int n_out, int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N,
+                       int64_t K, cudaStream_t st, const float* accum_f32 = nullptr) {
+  KSegments segs;
+  segs.n = 1;
+  segs.a_width = K;
+  segs.k[0] = K;
+  segs.a_sc[0] = A_sc;
+  segs.b[0] = B;
+  segs.b_sc[0] = B_sc;
+  return launch_gemm_segs(mx, A, segs, A_sg, B_sg, b_sg_per_tile, D, d_col_end, d_ld, n_out, out_fp32, residual, residual_ld,
+                          M, N, st, accum_f32);
 }
 
 }  // namespace fp4b200
@@ -768,6 +826,33 @@ int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const voi
   int ce[1] = {(int)N}, ld[1] = {(int)N};
   return launch_gemm(true, A, A_sc, nullptr, B, B_sc, nullptr, 0, d, ce, ld, 1, out_fp32, residual_bf16, (int)N, M, N,
                      K, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,
+                              const int64_t* a_col_widths, const void* const* A_sc_list, const void* const* B_list,
+                              const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream) {
+  if (!A_full || !a_col_offsets || !a_col_widths || !A_sc_list || !B_list || !B_sc_list || !D)
+    return set_error("mxfp4_gemm_ksplit: null pointer");
+  if (n_seg < 1 || n_seg > kMaxKSeg) return set_error("mxfp4_gemm_ksplit: 1 to %d K segments are supported", kMaxKSeg);
+  if (a_width <= 0 || (a_width % 32)) return set_error("mxfp4_gemm_ksplit: the row width of A must be a positive multiple of 32");
+  KSegments segs;
+  segs.n = n_seg;
+  segs.a_width = a_width;
+  int64_t K = 0;
+  for (int s = 0; s < n_seg; ++s) {
+    const int64_t off = a_col_offsets[s], w = a_col_widths[s];
+    if (w <= 0 || (w % 256) || off < 0 || (off % 32) || off + w > a_width)
+      return set_error("mxfp4_gemm_ksplit: segment %d (offset %lld, width %lld) must be a multiple of 256 wide, start at a "
+                       "multiple of 32 and lie inside the %lld columns of A", s, (long long)off, (long long)w, (long long)a_width);
+    segs.a_col_off[s] = off; segs.k[s] = w;
+    segs.a_sc[s] = A_sc_list[s]; segs.b[s] = B_list[s]; segs.b_sc[s] = B_sc_list[s];
+    if (int rc = check_gemm(A_full, A_sc_list[s], B_list[s], B_sc_list[s], M, N, w, "mxfp4_gemm_ksplit")) return rc;
+    K += w;
+  }
+  void* d[1] = {D};
+  int ce[1] = {(int)N}, ld[1] = {(int)N};
+  return launch_gemm_segs(true, A_full, segs, nullptr, nullptr, 0, d, ce, ld, 1, out_fp32, nullptr, 0, M, N,
+                          (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -73,7 +73,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 
 template <bool MX>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                      const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   GemmPairSmem& sm = *reinterpret_cast<GemmPairSmem*>(smem_align_1024(smem_raw));
@@ -111,7 +111,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------ TMA producer (both CTAs) --------------------------------
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
-      tma_prefetch_desc(&tmap_b);
+      for (int s = 0; s < g.n_seg; ++s) tma_prefetch_desc(&tmap_b.m[s]);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -122,10 +122,21 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
         int tm, tn;
         raster_tile(t, tiles_m, tiles_n, tm, tn);
-        const uint8_t* sfa_src = g.a_sc + (size_t)(2 * tm + rank) * g.sf_tiles_k * 512;
-        const uint8_t* sfb_src0 = g.b_sc + (size_t)(2 * tn) * g.sf_tiles_k * 512;
-        const uint8_t* sfb_src1 = sfb_src0 + (size_t)g.sf_tiles_k * 512;
-        for (int ks = 0; ks < k_stages; ++ks) {
+        int seg = -1, seg_end = 0, kl = 0, a_col = 0;
+        const CUtensorMap* bmap = nullptr;
+        const uint8_t *sfa_src = nullptr, *sfb_src0 = nullptr, *sfb_src1 = nullptr;
+        for (int ks = 0; ks < k_stages; ++ks, ++kl) {
+          if (ks == seg_end) {   // first stage of the next K segment
+            ++seg;
+            seg_end = g.seg_stage_end[seg];
+            kl = 0;
+            a_col = g.seg_a_col_bytes[seg];
+            bmap = &tmap_b.m[seg];
+            const size_t tiles_k = (size_t)g.seg_sf_tiles_k[seg];
+            sfa_src = g.seg_a_sc[seg] + (size_t)(2 * tm + rank) * tiles_k * 512;
+            sfb_src0 = g.seg_b_sc[seg] + (size_t)(2 * tn) * tiles_k * 512;
+            sfb_src1 = sfb_src0 + tiles_k * 512;
+          }
           const bool first_fill = filled < kPairStages;   // the first use of a stage waits for nothing
           ++filled;
           if (!mbar_wait_timed(&sm.empty[stage], phase ^ 1)) {
@@ -137,11 +148,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           // (one commit per stage instead of two keeps the tensor pipe's queue short)
           if (rank == 0 && !first_fill) mbar_arrive_cluster(empty_peer[stage]);
           mbar_expect_tx(&sm.full[stage], kATileBytes + kPairBHalfBytes + 3 * kSfPerStage);
-          tma_load_2d(sm.a[stage], &tmap_a, ks * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
-          tma_load_2d(sm.b[stage], &tmap_b, ks * kGemmBKBytes, tn * kGemmBN + (int)rank * 128, &sm.full[stage]);
-          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)ks * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          tma_load_2d(sm.a[stage], &tmap_a, a_col + kl * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
+          tma_load_2d(sm.b[stage], bmap, kl * kGemmBKBytes, tn * kGemmBN + (int)rank * 128, &sm.full[stage]);
+          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
           if (++stage == kPairStages) { stage = 0; phase ^= 1; }
         }
       }

@@ -42,3 +42,36 @@ def mxfp4_batched_gemm(A_list, A_sc_list, B_list, B_sc_list, D_out_list):
 
 def mxfp4_batched_gemm_config(A_list, A_sc_list, B_list, B_sc_list, D_out_list, config_id):
     mxfp4_batched_gemm(A_list, A_sc_list, B_list, B_sc_list, D_out_list)
+
+
+def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list, D_out,
+                                            config_idx=-1):
+    """mxfp4_gb200_gemm.cu:2572-2596 — ``D_out = bf16((sum_s A_full[:, off_s:off_s+w_s] . B_s^T) / 36)``: the
+    row-quantised gradient of a fused projection is the column concatenation of the splits; every term is
+    accumulated in tensor memory before the one rounding.  ``config_idx`` is accepted and ignored."""
+    import ctypes
+    n = len(B_list)
+    if n != 2:
+        raise RuntimeError("split2 one-pass dgrad expects exactly 2 B tensors")
+    if not (len(A_sc_list) == len(A_col_offsets) == len(A_col_widths) == len(B_sc_list) == n):
+        raise RuntimeError("split2 one-pass dgrad: list lengths differ")
+    _chk_operand(A_full, "A_full")
+    for t in list(A_sc_list) + list(B_list) + list(B_sc_list):
+        _chk_operand(t, "operand")
+    a = A_full.view(torch.uint8)
+    M, a_width = a.shape[0], a.shape[1] * 2
+    N = B_list[0].view(torch.uint8).shape[0]
+    for B, w in zip(B_list, A_col_widths):
+        b = B.view(torch.uint8)
+        if b.shape[0] != N or b.shape[1] * 2 != int(w):
+            raise RuntimeError("split2 one-pass dgrad: each B must be [N, width/2]")
+    out_fp32 = 1 if D_out.dtype == torch.float32 else 0
+    _chk_out(D_out, M, N, D_out.dtype if out_fp32 else torch.bfloat16)
+    offs = (ctypes.c_int64 * n)(*[int(v) for v in A_col_offsets])
+    widths = (ctypes.c_int64 * n)(*[int(v) for v in A_col_widths])
+    a_sc = (ctypes.c_void_p * n)(*[t.data_ptr() for t in A_sc_list])
+    b_p = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B_list])
+    b_sc = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B_sc_list])
+    with torch.cuda.device(A_full.device):
+        _lib.call("fp4b200_mxfp4_gemm_ksplit", a.data_ptr(), a_width, n, offs, widths, a_sc, b_p, b_sc, D_out.data_ptr(),
+                  out_fp32, M, N, _stream(A_full))

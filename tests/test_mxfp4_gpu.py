@@ -73,3 +73,39 @@ def test_mxfp4_gemm(shape):
     full = x.astype(np.float64) @ w.astype(np.float64).T
     assert np.linalg.norm(got - full) / np.linalg.norm(full) < 0.25
     assert np.abs(d16.float().cpu().numpy() - o.bf16_round(ref)).max() <= np.abs(ref).max() * 2.0 ** -7
+
+
+@pytest.mark.parametrize("M", [128, 256])
+def test_mxfp4_split2_dgrad_onepass(M):
+    """D = (A[:, :H] . B1^T + A[:, H:] . B2^T) / 36 in one launch: K segments with their own scale tensors
+    and B operands; both GEMM kernels (M = 128 -> one-CTA kernel, M = 256 -> CTA pair)."""
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    H, N = 512, 256
+    rng = np.random.default_rng(M)
+    dh1 = o.bf16_round(rng.standard_normal((M, H)).astype(np.float32))
+    dh3 = o.bf16_round((2.0 * rng.standard_normal((M, H))).astype(np.float32))
+    w1 = o.bf16_round((0.02 * rng.standard_normal((N, H))).astype(np.float32))
+    w3 = o.bf16_round((0.03 * rng.standard_normal((N, H))).astype(np.float32))
+    q1, q3 = mxq.mxfp4_quantize_for_gemm(to_dev_bf16(dh1), 1), mxq.mxfp4_quantize_for_gemm(to_dev_bf16(dh3), 1)
+    qw1, qw3 = mxq.mxfp4_quantize_for_gemm(to_dev_bf16(w1), 1), mxq.mxfp4_quantize_for_gemm(to_dev_bf16(w3), 1)
+    a_full = torch.cat([q1[0].view(torch.uint8), q3[0].view(torch.uint8)], dim=1).contiguous()
+    d = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
+                                                 [qw1[0], qw3[0]], [qw1[1], qw3[1]], d, -1)
+    d16 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
+                                                 [qw1[0], qw3[0]], [qw1[1], qw3[1]], d16)
+    torch.cuda.synchronize()
+    r1, r3 = o.mxfp4_quantize_1d(dh1, 1), o.mxfp4_quantize_1d(dh3, 1)
+    rw1, rw3 = o.mxfp4_quantize_1d(w1, 1), o.mxfp4_quantize_1d(w3, 1)
+    # the oracle's product already carries the 1/36 of each term; the sum of the two is what one pass computes
+    ref = (o.mxfp4_gemm_fp32(r1[0], r1[1], rw1[0], rw1[1]).astype(np.float64)
+           + o.mxfp4_gemm_fp32(r3[0], r3[1], rw3[0], rw3[1]).astype(np.float64))
+    got = d.cpu().numpy()
+    rel = np.linalg.norm(got - ref) / np.linalg.norm(ref)
+    assert rel <= 1e-3 and rel < 1e-5, rel
+    assert np.abs(d16.float().cpu().numpy() - o.bf16_round(ref.astype(np.float32))).max() <= np.abs(ref).max() * 2.0 ** -7
+    with pytest.raises(RuntimeError):
+        gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
+                                                     [qw1[0]], [qw1[1]], d)
+    assert_status_ok()
