@@ -108,3 +108,23 @@ def mxfp4_fused_rmsnorm_quantize_row_and_col_from_row_rms_partial(input, norm_we
                   1, rf.data_ptr(), rs.data_ptr(), cf.data_ptr(), cs.data_ptr(), _stream(input))
     return rf.view(_FP4), rs, cf.view(_FP4), cs, inv_rms
 
+
+
+def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
+    """tk_quantize.cu:4513-4620 — ``dh1 = bf16(dh*h3*silu'(h1_raw))``, ``dh3 = bf16(dh*silu(h1_raw))``, each
+    quantised row- and column-wise; outputs stacked on a leading dimension of 2 (dh1 first):
+    (row_fp4 [2,M,H/2], row_sc [2,M/128,H/128,32,16], col_fp4 [2,H,M/2], col_sc [2,H/128,M/128,32,16])."""
+    from .tk_quant_v5 import tk_silu_deriv_split_bf16
+    M, H = _check_bf16_2d(dh, "dh")
+    _same_shape_bf16(dh, h3, h1_raw)
+    u8 = dict(dtype=torch.uint8, device=dh.device)
+    row_fp4 = torch.empty((2, M, H // 2), **u8)
+    row_sc = torch.empty((2, M // 128, H // 128, 32, 16), **u8)
+    col_fp4 = torch.empty((2, H, M // 2), **u8)
+    col_sc = torch.empty((2, H // 128, M // 128, 32, 16), **u8)
+    dh1, dh3 = tk_silu_deriv_split_bf16(dh, h3, h1_raw)
+    with torch.cuda.device(dh.device):
+        for i, t in enumerate((dh1, dh3)):
+            _lib.call("fp4b200_mxfp4_quantize", t.data_ptr(), M, H, int(mode), row_fp4[i].data_ptr(), row_sc[i].data_ptr(),
+                      col_fp4[i].data_ptr(), col_sc[i].data_ptr(), _stream(dh))
+    return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc

@@ -118,3 +118,22 @@ def test_batched_quantize_matches_single_calls():
             assert torch.equal(lists[j][i].view(torch.uint8), single[j].view(torch.uint8))
         assert torch.equal(lists[4][i], single[4])
     assert_status_ok()
+
+
+def test_mxfp4_silu_deriv_split2():
+    mxq, tkq = mod("mxfp4_quant_v4"), mod("tk_quant_v5")
+    M, H = 256, 384
+    rng = np.random.default_rng(21)
+    dh = o.bf16_round((1e-3 * rng.standard_normal((M, H))).astype(np.float32))
+    h3 = o.bf16_round(rng.standard_normal((M, H)).astype(np.float32))
+    h1 = o.bf16_round((2.0 * rng.standard_normal((M, H))).astype(np.float32))
+    out = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(to_dev_bf16(dh), to_dev_bf16(h3), to_dev_bf16(h1), 1)
+    assert tuple(out[0].shape) == (2, M, H // 2) and tuple(out[3].shape) == (2, H // 128, M // 128, 32, 16)
+    dh1, dh3 = tkq.tk_silu_deriv_split_bf16(to_dev_bf16(dh), to_dev_bf16(h3), to_dev_bf16(h1))
+    torch.cuda.synchronize()
+    # the derivative itself (hardware __expf) is checked against the oracle in the NVFP4 SwiGLU tests
+    for i, t in enumerate((dh1, dh3)):
+        ref = o.mxfp4_quantize_row_and_col(t.float().cpu().numpy(), 1)
+        for j, k in enumerate(["row_fp4", "row_sc", "col_fp4", "col_sc"]):
+            assert np.array_equal(u8(out[j][i]).reshape(ref[k].shape), ref[k]), (i, k)
+    assert_status_ok()
