@@ -243,7 +243,7 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
            "down_gemm_tflops": fl_down * world / (ms[3] * 1e-3) / 1e12,
            "step_tflops": (fl_up + fl_down) * world / (total * 1e-3) / 1e12,
            "swiglu_quant_gbs": M * H * 5.125 * world / (ms[2] * 1e-3) / 1e9,
-           "roofline": {"bound": "tensor", "kernel": "fp4_gemm_kernel<nvfp4> (gate/up, N=28672 K=4096)",
+           "roofline": {"bound": "tensor", "kernel": "fp4_gemm_pair_kernel<nvfp4> (gate/up, N=28672 K=4096)",
                         "achieved": fl_up / (ms[1] * 1e-3) / 1e12, "unit": "TFLOP/s",
                         "peak": fp4_nominal, "frac": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_nominal,
                         "peak_kind": "nominal dense FP4 (no measured FP4 peak exists)",
@@ -251,6 +251,143 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
     if gather is not None:
         out["weight_all_gather"] = gather
     return out
+
+
+def _timed_stages(torch, stages, iters=3, warm=3):
+    """Runs the stage callables in order `warm + iters` times; returns mean ms per stage and per pass.
+    Three untimed passes: the mirrors allocate their outputs, and a stage's previous outputs are still
+    referenced while the next pass runs, so the caching allocator needs two passes to own both sets."""
+    n = len(stages)
+    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n + 1)] for _ in range(iters)]
+    for i in range(warm + iters):
+        for j, fn in enumerate(stages):
+            if i >= warm:
+                ev[i - warm][j].record()
+            fn()
+        if i >= warm:
+            ev[i - warm][n].record()
+    torch.cuda.synchronize()
+    ms = [statistics.mean(e[j].elapsed_time(e[j + 1]) for e in ev) for j in range(n)]
+    return ms, statistics.mean(e[0].elapsed_time(e[n]) for e in ev)
+
+
+def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
+    """Llama-3-8B FFN backward in NVFP4 at M=16384 per rank (config 4), production flags of the reference's
+    v5 route: gradients quantised decode-centric with Philox stochastic rounding on the row operand,
+    weights pre-quantised (their column operands serve the dgrads).  Stages: quantise dY; W2 dgrad;
+    W2 wgrad; SiLU-derivative producer (dh1, dh3 quantised); W1/W3 dgrad (two accumulated GEMMs);
+    W1 and W3 wgrads."""
+    tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
+    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    H, K, M = 14336, K_COLS, M_ROWS
+    dev = x_dev.device
+    g = torch.Generator(device="cpu").manual_seed(11)
+    def rnd(n, k, s):
+        return (s * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(dev)
+    q1 = tkq.tk_quantize_for_gemm(rnd(H, K, 0.02), True, False)
+    q3 = tkq.tk_quantize_for_gemm(rnd(H, K, 0.02), True, False)
+    q2 = tkq.tk_quantize_for_gemm(rnd(K, H, 0.02), True, False)
+    qx = tkq.tk_fused_norm_quantize(x_dev, gamma, EPS, False, True)      # forward's operands (column side for wgrad)
+    h1, h3 = rnd(M, H, 1.0), rnd(M, H, 1.0)
+    qh = tkq.tk_silu_quantize_split_for_gemm(h1, h3)
+    dy = rnd(M, K, 1e-3)
+    dh = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    dw2 = torch.empty(K, H, dtype=torch.bfloat16, device=dev)
+    dx = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    dw1 = torch.empty(H, K, dtype=torch.bfloat16, device=dev)
+    dw3 = torch.empty(H, K, dtype=torch.bfloat16, device=dev)
+    st = {}
+    def s_quant_dy():
+        st["qdy"] = tkq.tk_quantize_for_gemm_opt(dy, True, False, True, False, "none", False, 1234, 0, 448.0, "row")
+    def s_w2_dgrad():     # dh [M,H] = dY . W2 : B = W2's column operand [H, K/2]
+        q = st["qdy"]; gemm.nvfp4_gemm(q[0], q[1], q[4], q2[2], q2[3], q2[4], dh)
+    def s_w2_wgrad():     # dW2 [K,H] = dY^T . h : both column operands, contraction over M
+        q = st["qdy"]; gemm.nvfp4_gemm(q[2], q[3], q[5], qh[2], qh[3], qh[4], dw2)
+    def s_silu_deriv():
+        st["qd"] = tkq.tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1, True, False, True, False, "none", False,
+                                                                  1234, 1, "row")
+    def s_w13_dgrad():    # dx [M,K] = dh1 . W1 + dh3 . W3, fp32 running sum, one rounding
+        d = st["qd"]
+        gemm.nvfp4_batched_accum_gemm([d[0], d[6]], [d[1], d[7]], [d[4], d[10]], [q1[2], q3[2]], [q1[3], q3[3]],
+                                      [q1[4], q3[4]], dx)
+    def s_w13_wgrad():    # dW1 [H,K] = dh1^T . x, dW3 likewise
+        d = st["qd"]
+        gemm.nvfp4_gemm(d[2], d[3], d[5], qx[2], qx[3], qx[4], dw1)
+        gemm.nvfp4_gemm(d[8], d[9], d[11], qx[2], qx[3], qx[4], dw3)
+    names = ["quant_dy_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_quant_sr", "w13_dgrad_gemms", "w13_wgrad_gemms"]
+    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_w13_dgrad, s_w13_wgrad])
+    t = torch.tensor(ms + [total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, total = t[:-1].tolist(), t[-1].item()
+    fl = {"w2_dgrad_gemm": 2.0 * M * H * K, "w2_wgrad_gemm": 2.0 * K * H * M, "w13_dgrad_gemms": 4.0 * M * K * H,
+          "w13_wgrad_gemms": 4.0 * H * K * M}
+    gemm_ms = sum(m for n_, m in zip(names, ms) if n_ in fl)
+    return {"workload": "config4: Llama-3-8B FFN backward in NVFP4, M=16384 tokens per GPU, decode-centric, row-axis SR",
+            "ms": dict(zip(names, ms)), "step_ms": total,
+            "gemm_tflops": {n_: fl[n_] * world / (m * 1e-3) / 1e12 for n_, m in zip(names, ms) if n_ in fl},
+            "all_gemms_tflops": sum(fl.values()) * world / (gemm_ms * 1e-3) / 1e12,
+            "step_tflops": sum(fl.values()) * world / (total * 1e-3) / 1e12,
+            "quant_dy_gbs": M * K * 3.125 * world / (ms[0] * 1e-3) / 1e9,
+            "silu_deriv_quant_gbs": M * H * 8.25 * world / (ms[3] * 1e-3) / 1e9,
+            "frac_of_nominal_fp4_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / 9000.0,
+            "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
+
+
+def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
+    """MXFP4 (E8M0 / 32-blocks, mode 1) forward GEMMs of one Llama-3-8B decoder layer's weights (config 5:
+    QKV [6144,4096], O [4096,4096], W1/W3 [14336,4096], W2 [4096,14336]) on this rank's share of
+    M = 65536 tokens, with the producers that feed them (fused RMSNorm+quant, plain quant, SwiGLU)."""
+    mxq = importlib.import_module("mfu-fp4-training_b200.mxfp4_quant_v4")
+    gmx = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c_mx")
+    K, H, NQKV = K_COLS, 14336, 6144
+    M = 65536 // world
+    dev = gamma.device
+    g = torch.Generator(device="cpu").manual_seed(13)
+    def rnd(n, k, s):
+        return (s * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(dev)
+    wq = {n_: mxq.mxfp4_quantize_for_gemm(rnd(*shape, 0.02), 1)
+          for n_, shape in (("qkv", (NQKV, K)), ("o", (K, K)), ("w1", (H, K)), ("w3", (H, K)), ("w2", (K, H)))}
+    x = rnd(M, K, 1.0)
+    attn = rnd(M, K, 1.0)
+    qkv = torch.empty(M, NQKV, dtype=torch.bfloat16, device=dev)
+    o_out = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    h1 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    h3 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    y = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    st = {}
+    def s_norm_quant():
+        st["qx"] = mxq.mxfp4_fused_rmsnorm_quantize_row_and_col(x, gamma, EPS, 1)
+    def s_qkv():
+        q = st["qx"]; gmx.mxfp4_gemm(q[0], q[1], wq["qkv"][0], wq["qkv"][1], qkv)
+    def s_quant_attn():
+        st["qa"] = mxq.mxfp4_quantize_row_and_col(attn, 1)
+    def s_o():
+        q = st["qa"]; gmx.mxfp4_gemm(q[0], q[1], wq["o"][0], wq["o"][1], o_out)
+    def s_gate_up():
+        q = st["qx"]
+        gmx.mxfp4_gemm(q[0], q[1], wq["w1"][0], wq["w1"][1], h1)
+        gmx.mxfp4_gemm(q[0], q[1], wq["w3"][0], wq["w3"][1], h3)
+    def s_swiglu():
+        st["qh"] = mxq.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, 1)
+    def s_down():
+        q = st["qh"]; gmx.mxfp4_gemm(q[0], q[1], wq["w2"][0], wq["w2"][1], y)
+    names = ["rmsnorm_quant", "qkv_gemm", "quant_attn_out", "o_gemm", "gate_up_gemms", "swiglu_quant", "down_gemm"]
+    ms, total = _timed_stages(torch, [s_norm_quant, s_qkv, s_quant_attn, s_o, s_gate_up, s_swiglu, s_down], iters=2)
+    t = torch.tensor(ms + [total], device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms, total = t[:-1].tolist(), t[-1].item()
+    fl = {"qkv_gemm": 2.0 * M * NQKV * K, "o_gemm": 2.0 * M * K * K, "gate_up_gemms": 4.0 * M * H * K, "down_gemm": 2.0 * M * K * H}
+    gemm_ms = sum(m for n_, m in zip(names, ms) if n_ in fl)
+    return {"workload": f"config5: MXFP4 mode 1, one decoder layer's weight GEMMs forward, M={M} tokens per GPU (65536 / {world})",
+            "ms": dict(zip(names, ms)), "step_ms": total,
+            "gemm_tflops": {n_: fl[n_] * world / (m * 1e-3) / 1e12 for n_, m in zip(names, ms) if n_ in fl},
+            "all_gemms_tflops": sum(fl.values()) * world / (gemm_ms * 1e-3) / 1e12,
+            "rmsnorm_quant_gbs": M * K * 3.0625 * world / (ms[0] * 1e-3) / 1e9,
+            "frac_of_nominal_fp4_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / 9000.0,
+            "swiglu_quant_gbs": M * H * (4 + 1.0625) * world / (ms[5] * 1e-3) / 1e9,
+            "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
 
 
 def gemm_only(args):
@@ -407,31 +544,56 @@ def main():
                 "fused_op_frac_of_peak": (alg / (ms_per_step * 1e-3) / 1e9) / peaks["hbm_gbs"]}
 
     # ---- end to end: pinned host X in, all operands + inv_rms + scales back to the host ----
-    outs_host = None
-    n_e2e = max(3, min(args.steps, 10))
+    # Every step copies its own X and gamma from pinned host memory, calls the public entry point and
+    # copies every result back to pinned host memory.  As a caller with a steady stream of batches
+    # would, the three stages run on three streams with two sets of buffers, so the copy-in of step
+    # i+1 and the copy-out of step i-1 overlap the kernels of step i (PCIe is full duplex); nothing is
+    # skipped and nothing is reused between steps.
+    n_e2e = max(4, min(args.steps, 12))
     h2d = x_pin.numel() * 2 + g_pin.numel() * 2
-    x_dev = torch.empty_like(xs[0]); g_dev = torch.empty_like(gamma)
+    cur = torch.cuda.current_stream()
+    s_in, s_out = torch.cuda.Stream(), torch.cuda.Stream()
+    x_dev = [torch.empty_like(xs[0]) for _ in range(2)]
+    g_dev = [torch.empty_like(gamma) for _ in range(2)]
+    outs_host = [None, None]
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_comp = [torch.cuda.Event() for _ in range(2)]
+    ev_out = [torch.cuda.Event() for _ in range(2)]
+    d2h = 0
 
-    def e2e_step():
-        nonlocal outs_host
-        x_dev.copy_(x_pin, non_blocking=True)
-        g_dev.copy_(g_pin, non_blocking=True)
-        o_ = tkq.tk_fused_norm_quantize(x_dev, g_dev, EPS, False, True)
+    def e2e_step(i):
+        nonlocal d2h
+        k = i & 1
+        with torch.cuda.stream(s_in):
+            s_in.wait_event(ev_comp[k])          # the kernels that read this input buffer two steps ago
+            x_dev[k].copy_(x_pin, non_blocking=True)
+            g_dev[k].copy_(g_pin, non_blocking=True)
+            ev_in[k].record(s_in)
+        cur.wait_event(ev_in[k])
+        o_ = tkq.tk_fused_norm_quantize(x_dev[k], g_dev[k], EPS, False, True)
+        ev_comp[k].record(cur)
         res = [o_[0].view(torch.uint8), o_[1].view(torch.uint8), o_[2].view(torch.uint8),
                o_[3].view(torch.uint8), o_[5], o_[7]]
-        if outs_host is None:
-            outs_host = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
-        for hbuf, r in zip(outs_host, res):
-            hbuf.copy_(r, non_blocking=True)
-        return sum(r.numel() * r.element_size() for r in res)
+        if outs_host[k] is None:
+            outs_host[k] = [torch.empty(r.shape, dtype=r.dtype).pin_memory() for r in res]
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(ev_comp[k])
+            s_out.wait_event(ev_out[k])          # the previous copy-out into this set of host buffers
+            for hbuf, r in zip(outs_host[k], res):
+                hbuf.copy_(r, non_blocking=True)
+                r.record_stream(s_out)
+            ev_out[k].record(s_out)
+        d2h = sum(r.numel() * r.element_size() for r in res)
 
-    d2h = 0
-    for _ in range(2):
-        d2h = e2e_step()
+    for i in range(2):
+        e2e_step(i)
+    cur.wait_stream(s_out)
     barrier()
     e0.record()
-    for _ in range(n_e2e):
-        e2e_step()
+    for i in range(n_e2e):
+        e2e_step(i)
+    cur.wait_stream(s_in)
+    cur.wait_stream(s_out)
     e1.record()
     barrier()
     t2 = torch.tensor([e0.elapsed_time(e1)], device="cuda")
@@ -439,10 +601,15 @@ def main():
         dist.all_reduce(t2, op=dist.ReduceOp.MAX)
     e2e_ms = t2.item() / n_e2e
     e2e = {"value": alg * world / (e2e_ms * 1e-3) / 1e9, "unit": UNIT, "h2d_bytes_per_step": h2d,
-           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e}
+           "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": n_e2e,
+           "pipeline": "copy-in, kernels and copy-out on three streams, two buffer sets"}
 
     del outs_host
     ffn = ffn_forward_leg(torch, dist, world, local_rank, xs[0], gamma, peaks)
+    torch.cuda.empty_cache()
+    ffn_bwd = ffn_backward_leg(torch, dist, world, xs[0], gamma, peaks)
+    torch.cuda.empty_cache()
+    mx_layer = mxfp4_layer_leg(torch, dist, world, gamma, peaks)
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -456,7 +623,7 @@ def main():
                            "l2": "inputs rotate over 3 copies of X (402 MB > 126 MB L2) between steps",
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
-                "cpu_baseline": cpu, "ffn_forward": ffn}
+                "cpu_baseline": cpu, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer_forward": mx_layer}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -101,29 +101,6 @@ __device__ __forceinline__ float nvfp4_global_encode_scale(float amax) {
   return (amax == 0.0f || s == 0.0f) ? 1.0f : s;
 }
 
-// Per-16 block: stored decode-scale byte and the fp32 coefficient applied before the cast.
-// ENCODE_CENTRIC: m8 = e4m3(6/(b*S_enc)) (448 for b <= 1e-9), coeff = float(m8)*S_enc,
-//                 stored = e4m3(1/float(m8)).
-// decode-centric: s8 = e4m3(b/6*S_enc), coeff = min(1/(float(s8)*(1/S_enc)), FLT_MAX).
-template <bool ENCODE_CENTRIC>
-__device__ __forceinline__ void nvfp4_block_scale(float b, float s_enc, uint8_t& stored, float& coeff) {
-  if constexpr (ENCODE_CENTRIC) {
-    uint8_t m8;
-    if (b <= 1.0e-9f) {
-      m8 = 0x7E;  // 448
-    } else {
-      m8 = f32_to_e4m3(fminf(6.0f / (b * s_enc), kFltMax));
-    }
-    const float mf = e4m3_to_f32(m8);
-    coeff = mf * s_enc;
-    stored = f32_to_e4m3(1.0f / mf);
-  } else {
-    stored = f32_to_e4m3(fminf(b / 6.0f * s_enc, kFltMax));
-    const float s_dec = 1.0f / s_enc;
-    coeff = fminf(1.0f / (e4m3_to_f32(stored) * s_dec), kFltMax);
-  }
-}
-
 // Byte offset of scale (row r, block kb) inside its 512-byte tile of 128 rows x 4 blocks.
 __device__ __forceinline__ int scale_tile_offset(int r_in_tile, int kb_in_tile) {
   return (r_in_tile & 31) * 16 + (r_in_tile >> 5) * 4 + kb_in_tile;
@@ -187,15 +164,6 @@ __device__ __forceinline__ void fence_mbar_init() {
   asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
 }
 
-// TMA prefetch of one box / one contiguous range into L2 (no shared memory, no completion signal):
-// keeps DRAM requests in flight beyond what the shared-memory slots can hold.
-__device__ __forceinline__ void tma_prefetch_l2_2d(const CUtensorMap* tmap, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(tmap), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void bulk_prefetch_l2(const void* gsrc, uint32_t bytes) {
-  asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(gsrc), "r"(bytes) : "memory");
-}
-
 // 2-D tiled TMA store shared -> global of one box; completion is tracked by the thread's bulk async-group.
 __device__ __forceinline__ void tma_store_2d(const CUtensorMap* tmap, const void* smem_src, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%1, %2}], [%3];"
@@ -231,14 +199,6 @@ __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* t
       : "memory");
 }
 
-__device__ __forceinline__ void tma_load_3d(void* smem_dst, const CUtensorMap* tmap, int x, int y, int z,
-                                            uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
-      ::"r"(smem_u32(smem_dst)), "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
-      : "memory");
-}
-
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(tmap) : "memory");
 }
@@ -254,10 +214,7 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
-// Streaming (evict-first) 8- and 16-byte stores for write-once outputs.
-__device__ __forceinline__ void st_cs_u2(void* p, uint2 v) {
-  asm volatile("st.global.cs.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(v.x), "r"(v.y) : "memory");
-}
+// Streaming (evict-first) stores for write-once outputs.
 __device__ __forceinline__ void st_cs_u16(void* p, uint16_t v) {
   asm volatile("st.global.cs.u16 [%0], %1;" ::"l"(p), "h"(v) : "memory");
 }

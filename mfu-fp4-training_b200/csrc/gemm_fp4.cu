@@ -110,12 +110,6 @@ __device__ __forceinline__ uint64_t smem_desc(uint32_t saddr, uint32_t lbo_bytes
          ((uint64_t)((sbo_bytes & 0x3FFFF) >> 4) << 32) | (1ull << 46) | ((uint64_t)layout << 61);
 }
 
-// 32 rows x 16 bytes in shared memory -> 128 lanes x 4 columns of tensor memory (replicated per quadrant)
-__device__ __forceinline__ void tc_copy_sf(uint32_t tmem_addr, uint32_t saddr) {
-  const uint64_t desc = smem_desc(saddr, 128, 128, 0);
-  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(tmem_addr), "l"(desc) : "memory");
-}
-
 template <bool MX>
 __device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                        uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
@@ -278,16 +272,6 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMa
         }
       }
     }
-}
-
-__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-      : "r"(taddr)
-      : "memory");
 }
 
 // bf16 outputs without fp32 accumulation take this form of the epilogue.

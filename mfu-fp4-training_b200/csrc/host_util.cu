@@ -113,22 +113,6 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
   return 0;
 }
 
-int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
-                 uint64_t dim1, uint64_t dim2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
-                 uint32_t box1, uint32_t box2, CUtensorMapSwizzle swizzle) {
-  (void)elem_bytes;
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return set_error("cuTensorMapEncodeTiled is not available from the CUDA driver");
-  cuuint64_t dims[3] = {dim0, dim1, dim2};
-  cuuint64_t strides[2] = {pitch1_bytes, pitch2_bytes};
-  cuuint32_t box[3] = {box0, box1, box2};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = fn(out, dtype, 3, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return set_error("cuTensorMapEncodeTiled(3d) failed with CUresult %d", (int)r);
-  return 0;
-}
-
 }  // namespace fp4b200
 
 using namespace fp4b200;

@@ -44,11 +44,6 @@ struct AmaxPartials {
 int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
                  uint64_t dim1, uint64_t pitch_bytes, uint32_t box0, uint32_t box1, CUtensorMapSwizzle swizzle);
 
-// 3-D variant (dim2 outermost with its own byte stride).
-int make_tmap_3d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, int elem_bytes, uint64_t dim0,
-                 uint64_t dim1, uint64_t dim2, uint64_t pitch1_bytes, uint64_t pitch2_bytes, uint32_t box0,
-                 uint32_t box1, uint32_t box2, CUtensorMapSwizzle swizzle);
-
 // Options of the stochastic-rounding / Hadamard variants of the NVFP4 quantiser (one launch).
 struct QuantOpt {
   int sr;                    // data stochastic rounding on every pass of this launch

@@ -382,21 +382,6 @@ def rht_fixed_signs() -> np.ndarray:
     return np.array([1.0 if (RHT_SIGN_LITERAL >> i) & 1 else -1.0 for i in range(16)], dtype=F32)
 
 
-def _splitmix32_sign(seed: int, subseq: int, c: np.ndarray) -> np.ndarray:
-    """+1/-1 per coordinate ``c`` along the transformed axis (nvfp4_v5/tk_quantize.cu:483-488,
-    613-633): 64-bit mix of seed ^ subseq*0xd1b54a32d192ed03 ^ c*0x9e3779b97f4a7c15, low bit."""
-    M64 = (1 << 64) - 1
-    out = np.empty(len(c), dtype=F32)
-    for i, ci in enumerate(c):
-        z = (seed ^ ((subseq * 0xD1B54A32D192ED03) & M64) ^ ((int(ci) * 0x9E3779B97F4A7C15) & M64)) & M64
-        z = (z + 0x9E3779B97F4A7C15) & M64
-        z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & M64
-        z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & M64
-        z = z ^ (z >> 31)
-        out[i] = 1.0 if (z & 1) else -1.0
-    return out
-
-
 def fwht16_bf16(x: np.ndarray, signs: np.ndarray | None = None) -> np.ndarray:
     """Per 16 contiguous elements of the last axis: optional sign flip, unnormalised
     Sylvester butterflies (step 1,2,4,8), x0.25, all fp32, rounded to bf16

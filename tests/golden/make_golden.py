@@ -2,7 +2,7 @@
 
 Run in the build container only (it needs the reference checkout):
 
-    python tests/golden/make_golden.py --reference /root/reference
+    python tests/golden/make_golden.py --reference <path of the reference checkout>
 
 It loads ``transformer_engine/pytorch/custom_recipes/quantization_nvfp4.py`` (and its two
 small helper modules) straight from the reference tree, with stub parents injected into
@@ -72,7 +72,7 @@ def make_inputs(M, K, N, seed):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
     args = ap.parse_args()
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

@@ -38,3 +38,33 @@ def test_shim_rejects_cpu_tensors(pkg):
         tkq.tk_quantize_for_gemm(torch.zeros(128, 128, dtype=torch.bfloat16), True)
     with pytest.raises(RuntimeError):
         tkq.tk_fused_norm_quantize(torch.zeros(128, 128, dtype=torch.bfloat16), torch.ones(128), 1e-5, False, True)
+
+
+def test_entry_points_validate_before_touching_the_device(pkg):
+    """Argument checks come first in every entry point, so bad calls fail with a message on a machine
+    without a GPU as well (no kernel is launched here)."""
+    lib = pkg._lib.load()
+    buf = ctypes.create_string_buffer(4096)
+    p = ctypes.cast(buf, ctypes.c_void_p)
+
+    def msg():
+        return lib.fp4b200_last_error().decode()
+
+    assert lib.fp4b200_row_rms_reduce(p, 128, 7, 4096, 1e-5, p, None) == -1 and "partition" in msg()
+    assert lib.fp4b200_row_rms_reduce(p, 128, 129, 8192, 1e-5, p, None) == -1
+    assert lib.fp4b200_row_rms_reduce(p, 128, 16, 4096, -1.0, p, None) == -1 and "eps" in msg()
+    assert lib.fp4b200_fp32_to_fp4x2(p, -1, p, None) == -1
+    assert lib.fp4b200_tk_nvfp4_quantize(p, 100, 128, p, p, p, 0, None) == -1 and "multiples of 128" in msg()
+    assert lib.fp4b200_mxfp4_quantize_weight_2d(p, 128, 100, p, p, p, p, None) == -1
+    assert lib.fp4b200_nvfp4_fused_norm_quantize_noalloc(p, p, 1e-5, 65536 + 128, 128, p, p, p, p, p, None) == -1
+    assert "65536" in msg()
+    # K-split GEMM: segment count, widths and offsets
+    offs = (ctypes.c_int64 * 2)(0, 512)
+    widths = (ctypes.c_int64 * 2)(512, 500)
+    ptrs = (ctypes.c_void_p * 2)(p, p)
+    assert lib.fp4b200_mxfp4_gemm_ksplit(p, 1024, 5, offs, widths, ptrs, ptrs, ptrs, p, 0, 128, 256, None) == -1
+    assert lib.fp4b200_mxfp4_gemm_ksplit(p, 1024, 2, offs, widths, ptrs, ptrs, ptrs, p, 0, 128, 256, None) == -1
+    assert "segment 1" in msg()
+    widths = (ctypes.c_int64 * 2)(512, 768)     # runs past the 1024 columns of A
+    assert lib.fp4b200_mxfp4_gemm_ksplit(p, 1024, 2, offs, widths, ptrs, ptrs, ptrs, p, 0, 128, 256, None) == -1
+    assert lib.fp4b200_nvfp4_gemm(p, p, p, p, p, p, p, 0, None, 128, 200, 256, None) == -1 and "N % 256" in msg()
