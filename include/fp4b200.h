@@ -63,9 +63,13 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
 /* One launch of the stochastic-rounding / Hadamard variant of the quantiser, the counterpart of
  * tk_quantize_transpose(input, amax_row, amax_col, return_transpose, stochastic_rounding, encode_centric,
  * scale_sr=false, row_rht, col_rht, return_row, rng_state) (tk_quantize.cu:3807-3926; kernel
- * quantize_transpose_tuned.cuh:256-528).  data_sr: Philox4x32-10 stochastic rounding of the codes on
- * every pass of this launch, key rng_seed, counter offset rng_offset (= the reference's rng_state[1]),
- * sequence and draw order those of the reference kernel, so equal (seed, offset) give equal bytes.
+ * quantize_transpose_tuned.cuh:256-528).  data_sr: Philox4x32-10 stochastic rounding of the codes,
+ * key rng_seed, counter offset rng_offset (= the reference's rng_state[1]), sequence and draw order
+ * those of the reference kernel, so equal (seed, offset) give equal bytes: 1 = on every pass of this
+ * launch; 2 = row pass only, the bytes of the reference's row-only launch at rng_offset (its stream
+ * has 8 words per stage), with the column pass rounded to nearest in the same launch; 3 = column pass
+ * only, at rng_offset_col (the offset of the reference's separate column launch).  With 2 and 3 the
+ * callers that the reference serves with two launches (one axis stochastic) read the input once.
  * rht_row / rht_col: per-16 Hadamard transform (x0.25, rounded to bf16) along K for the row operand /
  * along M for the column operand, optionally after a sign flip hashed from (sign_seed, sign_subseq,
  * coordinate) (tk_quantize.cu:483-488,620-627).  gamma/inv_rms non-NULL fuse RMSNorm.  return_row = 0
@@ -74,8 +78,8 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
-                               int return_row, uint64_t rng_seed, uint64_t rng_offset, void* row_fp4, void* row_sc,
-                               void* col_fp4, void* col_sc, void* stream);
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream);
 
 /* Tensor amax (and sg) of the per-16 Hadamard transform of x along K (along_k != 0) or along M,
  * measured on the fp32 transform output: rht16_bf16_amax_kernel (tk_quantize.cu:574-664).  gamma/inv_rms

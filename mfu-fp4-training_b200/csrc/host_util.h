@@ -46,11 +46,12 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 
 // Options of the stochastic-rounding / Hadamard variants of the NVFP4 quantiser (one launch).
 struct QuantOpt {
-  int sr;                    // data stochastic rounding on every pass of this launch
+  int sr_row, sr_col;        // data stochastic rounding of the row pass / of the column pass
+  int row_per_stage;         // 0: by the launch's shape; 8: the row pass follows a row-only launch's random stream
   int rht_row, rht_col;      // 16-point Hadamard transform along K (row operand) / along M (column operand)
   int sign;                  // seeded sign flip before the transform
   int return_row;            // 0: skip the row-wise outputs but keep their place in the random stream
-  unsigned long long rng_seed, rng_offset;
+  unsigned long long rng_seed, rng_offset, rng_offset_col;   // column pass may take its own counter offset
   unsigned long long sign_seed, sign_subseq;
 };
 

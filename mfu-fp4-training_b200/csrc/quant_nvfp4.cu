@@ -396,11 +396,12 @@ struct QuantArgs {
   int chunks_m, chunks_k;
   int reverse;             // walk chunks from the last row block to the first
   // ---- OPT instantiations only (stochastic rounding / 16-point Hadamard transform) ----
-  int opt_sr;              // data stochastic rounding in this launch (row and column passes)
+  int opt_sr_row, opt_sr_col;   // data stochastic rounding of the row pass / of the column pass
+  int opt_row_per_stage;   // random words per 64x64 stage in the row pass's stream: 16 (launch with a column pass) or 8
   int opt_rht_row, opt_rht_col;   // per-16 Hadamard transform along K (row operand) / along M (column operand)
   int opt_sign;            // seeded sign flip before the transform
   int opt_return_row;      // 0: row-wise outputs are not written (their random words are still skipped)
-  unsigned long long rng_seed, rng_offset;     // Philox key and counter offset
+  unsigned long long rng_seed, rng_offset, rng_offset_col;   // Philox key, counter offset of the row pass / column pass
   unsigned long long sign_seed, sign_subseq;   // sign-mask hash inputs
 };
 
@@ -673,7 +674,7 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
         // same (seed, offset) gives the same word to the same element: 128 threads per chunk, four
         // 64x64 stages, per stage a row pass (2 iterations x 4 words) then a column pass (2 x 4 words);
         // a 16-element block consumes exactly one Philox block (quantize_transpose_tuned.cuh:392-528).
-        const int per_stage = want_col ? 16 : 8;
+        const int per_stage = a.opt_row_per_stage;
         uint32_t st_b[2];
         uint2 cd[2];
 #pragma unroll
@@ -683,7 +684,7 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
           for (int q = 0; q < 8; ++q) { x[2 * q] = bf16lo_to_f32(w[8 * b + q]); x[2 * q + 1] = bf16hi_to_f32(w[8 * b + q]); }
           const int lc0 = unit * 32 + b * 16;           // first column of the block inside the chunk
           uint32_t wsel[4] = {0, 0, 0, 0};
-          if (a.opt_sr) {
+          if (a.opt_sr_row) {
             const int stage = (r >> 6) * 2 + (lc0 >> 6);
             const int lr = r & 63, it_ref = lr >> 5;
             const int tid_ref = (lr & 31) * 4 + ((lc0 & 63) >> 4);
@@ -697,7 +698,7 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
             for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
           }
           cd[b] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
-                                            (unsigned long long)(k0 + lc0), s_enc_row, sm.lut_row, a.opt_sr != 0, wsel,
+                                            (unsigned long long)(k0 + lc0), s_enc_row, sm.lut_row, a.opt_sr_row != 0, wsel,
                                             st_b[b]);
         }
         if (a.opt_return_row) {
@@ -754,17 +755,17 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = wq ? bf16hi_to_f32(w[i]) : bf16lo_to_f32(w[i]);
             uint32_t wsel[4] = {0, 0, 0, 0};
-            if (a.opt_sr) {
+            if (a.opt_sr_col) {
               const int stage = (warp >> 2) * 2 + h;
               const int tid_ref = (((warp & 3) - (lane & 3)) & 3) * 32 + lane;
               const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
-              const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
+              const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
               wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
             }
             cd[wq] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
                                                (unsigned long long)(m0 + warp * 16), s_enc_col, sm.lut_col,
-                                               a.opt_sr != 0, wsel, st_c[wq]);
+                                               a.opt_sr_col != 0, wsel, st_c[wq]);
           }
           q = make_uint4(cd[0].x, cd[0].y, cd[1].x, cd[1].y);
           st0 = st_c[0]; st1 = st_c[1];
@@ -1263,7 +1264,9 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.reverse = reverse ? 1 : 0;
   const bool norm = inv_rms != nullptr;
   if (opt != nullptr) {
-    a.opt_sr = opt->sr; a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
+    a.opt_sr_row = opt->sr_row; a.opt_sr_col = opt->sr_col; a.rng_offset_col = opt->rng_offset_col;
+    a.opt_row_per_stage = opt->row_per_stage ? opt->row_per_stage : (col_fp4 != nullptr ? 16 : 8);
+    a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
     a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
     if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st, behind_pass1)
@@ -1416,7 +1419,8 @@ int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const f
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
-                               int return_row, uint64_t rng_seed, uint64_t rng_offset, void* row_fp4, void* row_sc,
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, void* row_fp4,
+                               void* row_sc,
                                void* col_fp4, void* col_sc, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_quantize_opt")) return rc;
   if (!amax_row) return set_error("nvfp4_quantize_opt: amax_row is required");
@@ -1427,7 +1431,12 @@ int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const
     return set_error("nvfp4_quantize_opt: col_fp4 and col_sc must both be given or both be null");
   if (!return_row && !col_fp4) return set_error("nvfp4_quantize_opt: nothing to compute");
   QuantOpt o{};
-  o.sr = data_sr != 0; o.rht_row = rht_row != 0; o.rht_col = rht_col != 0; o.sign = with_sign != 0;
+  if (data_sr < 0 || data_sr > 3) return set_error("nvfp4_quantize_opt: data_sr must be 0 (off), 1 (both passes), 2 (row pass) or 3 (column pass)");
+  o.sr_row = data_sr == 1 || data_sr == 2; o.sr_col = data_sr == 1 || data_sr == 3;
+  // a row-only stochastic launch of the reference draws 8 words per stage, also when this launch adds the column pass
+  o.row_per_stage = data_sr == 2 ? 8 : 0;
+  o.rng_offset_col = data_sr == 1 ? rng_offset : rng_offset_col;
+  o.rht_row = rht_row != 0; o.rht_col = rht_col != 0; o.sign = with_sign != 0;
   o.return_row = return_row != 0; o.rng_seed = rng_seed; o.rng_offset = rng_offset;
   o.sign_seed = sign_seed; o.sign_subseq = sign_subseq;
   return launch_quantize(x_bf16, M, K, amax_row, amax_col, encode_centric != 0, inv_rms, gamma_bf16, row_fp4, row_sc,

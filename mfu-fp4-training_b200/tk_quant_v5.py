@@ -290,8 +290,10 @@ def _amax_rht(x, along_k, sign, seed, subseq, gamma=None, inv_rms=None):
 
 
 def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row_rht, col_rht, return_row, seed, offset,
-                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None):
-    """One launch, the counterpart of tk_quantize_transpose (tk_quantize.cu:3807-3926)."""
+                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None, sr_mode=None, offset_col=0):
+    """One launch, the counterpart of tk_quantize_transpose (tk_quantize.cu:3807-3926).  ``sr_mode`` 2 / 3:
+    stochastic rounding on the row pass only (the bytes of the reference's row-only launch at ``offset``) /
+    on the column pass only (at ``offset_col``), the other pass rounded to nearest in the same launch."""
     M, K = x.shape
     u8 = dict(dtype=torch.uint8, device=x.device)
     row_fp4 = torch.empty((M, K // 2), **u8) if return_row else None
@@ -299,9 +301,11 @@ def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row
     col_fp4 = torch.empty((K, M // 2), **u8) if return_transpose else None
     col_sc = torch.empty((K // 128, M // 64, 512), **u8) if return_transpose else None
     _lib.call("fp4b200_nvfp4_quantize_opt", x.data_ptr(), _p(gamma), _p(inv_rms), M, K, amax_row.data_ptr(),
-              amax_col.data_ptr(), int(bool(encode_centric)), int(bool(sr)), int(bool(row_rht)), int(bool(col_rht)),
+              amax_col.data_ptr(), int(bool(encode_centric)), int(bool(sr)) if sr_mode is None else int(sr_mode),
+              int(bool(row_rht)), int(bool(col_rht)),
               int(bool(sign)), int(sign_seed) & _U64, int(sign_subseq) & _U64, int(bool(return_row)),
-              int(seed) & _U64, int(offset) & _U64, _p(row_fp4), _p(row_sc), _p(col_fp4), _p(col_sc), _stream(x))
+              int(seed) & _U64, int(offset) & _U64, int(offset_col) & _U64, _p(row_fp4), _p(row_sc), _p(col_fp4),
+              _p(col_sc), _stream(x))
     return row_fp4, row_sc, col_fp4, col_sc
 
 
@@ -364,6 +368,14 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
             off = _next_offset(input, rng_subsequence, use_sr)
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr, encode_centric, row_rht, col_rht,
                                          True, rng_seed, off, sign, rng_seed, rng_subsequence)
+        elif return_transpose and not row_mat and not col_mat:
+            # the reference serves "one axis stochastic" with a row launch and a column launch, each taking
+            # an offset; here one launch reads the input once and produces the same bytes
+            off_r = _next_offset(input, rng_subsequence, use_sr)
+            off_c = _next_offset(input, rng_subsequence, use_sr)
+            rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, True, encode_centric, row_rht, col_rht, True,
+                                         rng_seed, off_r, sign, rng_seed, rng_subsequence, sr_mode=2 if row_sr else 3,
+                                         offset_col=off_c)
         else:
             off = _next_offset(input, rng_subsequence, use_sr)
             rf, rs, _, _ = _launch_opt(input, row_amax, row_amax, False, row_sr, encode_centric, row_rht, False, True,
@@ -441,11 +453,9 @@ def tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1_raw, return_transpose=T
                 q = _launch_opt(t, row_amax, orig, True, row_sr, encode_centric, row_rht, False, True, rng_seed, off,
                                 False, 0, 0)
             else:
-                rf, rs, _, _ = _launch_opt(t, row_amax, orig, False, row_sr, encode_centric, row_rht, False, True,
-                                           rng_seed, off, False, 0, 0)
-                _, _, cf, cs = _launch_opt(t, row_amax, orig, True, col_sr, encode_centric, row_rht, False, False,
-                                           rng_seed, off, False, 0, 0)
-                q = (rf, rs, cf, cs)
+                # one axis stochastic: the reference's row launch and column launch (same offset) as one
+                q = _launch_opt(t, row_amax, orig, True, True, encode_centric, row_rht, False, True, rng_seed, off,
+                                False, 0, 0, sr_mode=2 if row_sr else 3, offset_col=off)
             outs.append((q[0].view(_FP4), q[1].view(_E4M3), q[2].view(_FP4), q[3].view(_E4M3)))
             sgs.append((row_amax.narrow(0, 1, 1), orig.narrow(0, 1, 1)))
             amax_list += [row_amax[0], orig[0]]
