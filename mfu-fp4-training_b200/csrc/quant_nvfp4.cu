@@ -863,7 +863,7 @@ __host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm) {
          (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + 16 + (size_t)k_norm * sizeof(float) + 1024;
 }
 
-template <bool ENCODE_CENTRIC, bool NORM>
+template <bool ENCODE_CENTRIC, bool NORM, bool OPT>
 __global__ void __launch_bounds__(kStripWarps * 32, 1)
 nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_row,
                             const QuantArgs a) {
@@ -1009,25 +1009,65 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       }
       uint32_t codes[8];
       uint32_t sc_word = 0;
+      if constexpr (OPT) {
+        // Stochastic rounding follows the reference kernel's thread/draw order inside the 128x128 chunk
+        // (128 threads, four 64x64 stages, per stage a row pass of 2 iterations x 4 words and, when the
+        // launch has one, a column pass of 2 x 4 words; quantize_transpose_tuned.cuh:392-528): the word
+        // for an element depends only on its position, so any kernel shape reproduces it.
+        const int rc = wv * kStripRows + lane;        // row inside the chunk
+        if (a.opt_return_row) {
 #pragma unroll
-      for (int b = 0; b < 4; ++b) {
-        uint32_t mx = 0;
+          for (int b = 0; b < 4; ++b) {
+            float x[16];
 #pragma unroll
-        for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[8 * b + q]);
-        const float bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
-        const ScaleLut e = lut_row[block_code<ENCODE_CENTRIC>(bm, s_enc_row)];
-        codes[2 * b] = quant8(w + 8 * b, e.coeff);
-        codes[2 * b + 1] = quant8(w + 8 * b + 4, e.coeff);
-        sc_word |= e.stored << (8 * b);
+            for (int q = 0; q < 8; ++q) { x[2 * q] = bf16lo_to_f32(w[8 * b + q]); x[2 * q + 1] = bf16hi_to_f32(w[8 * b + q]); }
+            const int lc0 = wh * kStripCols + b * 16;   // first column of the block inside the chunk
+            uint32_t wsel[4] = {0, 0, 0, 0};
+            if (a.opt_sr_row) {
+              const int stage = (rc >> 6) * 2 + (lc0 >> 6);
+              const int lr = rc & 63, it_ref = lr >> 5;
+              const int tid_ref = (lr & 31) * 4 + ((lc0 & 63) >> 4);
+              const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
+                                             128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
+              const uint4 rw = philox4x32_10(a.rng_seed, seq,
+                                             a.rng_offset + (unsigned long long)((stage * a.opt_row_per_stage + it_ref * 4) >> 2));
+              const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
+              const int bg = (tid_ref & 31) >> 4;
+#pragma unroll
+              for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
+            }
+            uint32_t stored;
+            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
+                                                       (unsigned long long)(col0 + b * 16), s_enc_row, lut_row,
+                                                       a.opt_sr_row != 0, wsel, stored);
+            codes[2 * b] = cd.x;
+            codes[2 * b + 1] = cd.y;
+            sc_word |= stored << (8 * b);
+          }
+        }
+      } else {
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          uint32_t mx = 0;
+#pragma unroll
+          for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[8 * b + q]);
+          const float bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+          const ScaleLut e = lut_row[block_code<ENCODE_CENTRIC>(bm, s_enc_row)];
+          codes[2 * b] = quant8(w + 8 * b, e.coeff);
+          codes[2 * b + 1] = quant8(w + 8 * b + 4, e.coeff);
+          sc_word |= e.stored << (8 * b);
+        }
       }
       // codes leave through a TMA store (32 rows x 32 bytes): per-lane global stores of 32 different
       // lines each would cost the L1 as much as all the shared-memory traffic of the strip
-      if (lane == 0) bulk_wait_group_read0();   // the previous strip's stores have left the staging buffers
-      __syncwarp();
-      *reinterpret_cast<uint4*>(my_stage + lane * 32) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-      *reinterpret_cast<uint4*>(my_stage + lane * 32 + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
-      // 512-byte tile (128 rows x these 4 blocks): row wv*32 + lane, blocks 0..3 are 4 adjacent bytes
-      st_cs_u32(a.row_sc + ((size_t)cm * (a.K >> 6) + (size_t)(col0 >> 6)) * 512 + lane * 16 + wv * 4, sc_word);
+      if (!OPT || a.opt_return_row) {
+        if (lane == 0) bulk_wait_group_read0();   // the previous strip's stores have left the staging buffers
+        __syncwarp();
+        *reinterpret_cast<uint4*>(my_stage + lane * 32) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+        *reinterpret_cast<uint4*>(my_stage + lane * 32 + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+        // 512-byte tile (128 rows x these 4 blocks): row wv*32 + lane, blocks 0..3 are 4 adjacent bytes
+        st_cs_u32(a.row_sc + ((size_t)cm * (a.K >> 6) + (size_t)(col0 >> 6)) * 512 + lane * 16 + wv * 4, sc_word);
+      }
     }
 
     // ---- column pass: lane = column pair -----------------------------------------------
@@ -1045,19 +1085,44 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
           w[i] = *reinterpret_cast<const uint32_t*>(gbase + (i >> 3) * 1024 + col_off[i & 7]);
           mx = absmax_xs(mx, w[i]);
         }
-        const float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
-        const ScaleLut e0 = lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
-        const ScaleLut e1 = lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
-        const float2 cc = make_float2(e0.coeff, e1.coeff);
-        float2 v[16];
+        if constexpr (OPT) {
+          const int grp16 = wv * 2 + g;   // 16-row group inside the chunk (the reference kernel's warp role)
 #pragma unroll
-        for (int i = 0; i < 16; ++i) v[i] = mul2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), cc);
-        cc0[2 * g] = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
-        cc0[2 * g + 1] = f32x8_to_e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
-        cc1[2 * g] = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
-        cc1[2 * g + 1] = f32x8_to_e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
-        sc0 |= e0.stored << (8 * g);
-        sc1 |= e1.stored << (8 * g);
+          for (int wq = 0; wq < 2; ++wq) {
+            float x[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) x[i] = wq ? bf16hi_to_f32(w[i]) : bf16lo_to_f32(w[i]);
+            uint32_t wsel[4] = {0, 0, 0, 0};
+            if (a.opt_sr_col) {
+              const int stage = (grp16 >> 2) * 2 + wh;
+              const int tid_ref = (((grp16 & 3) - (lane & 3)) & 3) * 32 + lane;
+              const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
+                                             128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
+              const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
+              wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
+            }
+            uint32_t stored;
+            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
+                                                       (unsigned long long)(cm * kChunk + grp16 * 16), s_enc_col, lut_col,
+                                                       a.opt_sr_col != 0, wsel, stored);
+            if (wq == 0) { cc0[2 * g] = cd.x; cc0[2 * g + 1] = cd.y; sc0 |= stored << (8 * g); }
+            else { cc1[2 * g] = cd.x; cc1[2 * g + 1] = cd.y; sc1 |= stored << (8 * g); }
+          }
+        } else {
+          const float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
+          const ScaleLut e0 = lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
+          const ScaleLut e1 = lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
+          const float2 cc = make_float2(e0.coeff, e1.coeff);
+          float2 v[16];
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = mul2(make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i])), cc);
+          cc0[2 * g] = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+          cc0[2 * g + 1] = f32x8_to_e2m1x8(v[8].x, v[9].x, v[10].x, v[11].x, v[12].x, v[13].x, v[14].x, v[15].x);
+          cc1[2 * g] = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+          cc1[2 * g + 1] = f32x8_to_e2m1x8(v[8].y, v[9].y, v[10].y, v[11].y, v[12].y, v[13].y, v[14].y, v[15].y);
+          sc0 |= e0.stored << (8 * g);
+          sc1 |= e1.stored << (8 * g);
+        }
       }
       // 16 bytes per column straight to [K, M/2]: as a TMA store this would be 64 box rows of 16 bytes,
       // and the TMA unit's rate of box rows (not bytes) is what bounds the kernel once everything goes through it
@@ -1076,8 +1141,10 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     fence_proxy_async_smem();   // this lane's generic-proxy writes (staging, normalised rows) before the TMA engine's accesses
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(&tmap_row, my_stage, col0 >> 1, row0);
-      bulk_commit_group();
+      if (!OPT || a.opt_return_row) {
+        tma_store_2d(&tmap_row, my_stage, col0 >> 1, row0);
+        bulk_commit_group();
+      }
       if (it + depth < my_count) issue_load(it + depth, s);
     }
   }
@@ -1204,17 +1271,20 @@ static bool quant_strip_disabled() {
   return off;
 }
 
-template <bool EC, bool NORM>
+template <bool EC, bool NORM, bool OPT = false>
 static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
   CUtensorMap tmap, tmap_row;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)args.K, (uint64_t)args.M,
                             (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   // row-wise codes as a byte matrix [M, K/2], stored in boxes of 32 rows x 32 bytes
-  if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
-                            (uint64_t)args.K / 2, kStripCols / 2, kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
-    return rc;
-  auto kern = nvfp4_quantize_strip_kernel<EC, NORM>;
+  tmap_row = tmap;   // launches without row-wise outputs never use it
+  if (args.row_fp4 != nullptr) {
+    if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
+                              (uint64_t)args.K / 2, kStripCols / 2, kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+  }
+  auto kern = nvfp4_quantize_strip_kernel<EC, NORM, OPT>;
   const int smem = (int)strip_smem_bytes(NORM ? args.K : 0);
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_chunks = args.chunks_m * args.chunks_k;
@@ -1269,6 +1339,12 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
     a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
     a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
+    if (strip_kernel_applies(a, norm)) {
+      if (encode_centric) return norm ? launch_quantize_strip_t<true, true, true>(x, a, st, behind_pass1)
+                                      : launch_quantize_strip_t<true, false, true>(x, a, st, behind_pass1);
+      return norm ? launch_quantize_strip_t<false, true, true>(x, a, st, behind_pass1)
+                  : launch_quantize_strip_t<false, false, true>(x, a, st, behind_pass1);
+    }
     if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st, behind_pass1)
                                     : launch_quantize_t<true, false, false, true>(tmap, a, st, behind_pass1);
     return norm ? launch_quantize_t<false, true, false, true>(tmap, a, st, behind_pass1)
