@@ -95,8 +95,7 @@ __device__ __forceinline__ float amax_from_partials(const float* partials, int n
 // virtual lanes 4L+128i+q (i = 0,1; q = 0..3) in acc[i][q], so the butterfly levels map to
 // shuffles over lane masks 4,2,1, register adds over q, a register add over i, and
 // shuffles over lane masks 16,8.
-constexpr int kStatsMaxWarps = 12;   // warps per CTA, one CTA per SM
-constexpr int kStatsDepth = 2;       // row slots per warp
+constexpr int kStatsMaxWarps = 16;   // warps per CTA, one CTA per SM
 
 // Sum of squares of the row held in v -> 1/rms, identical on all lanes.
 template <int NV>
@@ -159,19 +158,19 @@ __device__ __forceinline__ float stats_row_amax(const uint4 (&v)[NV], const floa
   return mx;
 }
 
-// One CTA per SM; every warp is its own pipeline: rows arrive in the warp's two shared-memory slots
-// by bulk copies that its lane 0 issues (one row = one contiguous copy), are lifted into registers,
-// and the slot is refilled as soon as the row's sum of squares has been reduced (the reduction needs
-// every lane's values, so all reads of the slot are complete by then).  Bytes in flight per SM are
-// set by the slots (warps x 2 rows), not by registers, which is what a streaming reduction at HBM
-// speed needs.  A CTA owns a contiguous band of rows; each warp starts on two fixed rows of the band
-// (their copies are issued before anything else happens) and then takes the band's next row from a
-// shared counter whenever a slot frees up, so the warps of a CTA finish within one row of each other.
+// One CTA per SM.  The CTA owns a contiguous band of rows and a ring of row slots in shared memory
+// (as many as fit: 24 of 8 KB at K = 4096); row r of the band lives in slot r % slots and arrives by
+// one bulk copy (a row is contiguous).  A warp claims the band's next row from a shared counter, waits
+// for that slot's barrier, lifts the row into registers and, as soon as the row's sum of squares has
+// been reduced (the reduction needs every lane's values, so all reads of the slot are complete by
+// then), refills the slot with the row `slots` further on.  Bytes in flight per SM are set by the ring,
+// not by registers or by the number of warps, which is what a streaming reduction at HBM speed needs;
+// rows are handed out one at a time, so the warps of a CTA finish within one row of each other.
 template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS>
 __global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                      float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
-                     int* __restrict__ status) {
+                     int n_slots, int* __restrict__ status) {
   extern __shared__ __align__(128) uint8_t stats_smem[];
   __shared__ int next_row;   // next unclaimed row of the band (band-relative)
   __shared__ float warp_max_s[kStatsMaxWarps];
@@ -180,29 +179,31 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   const uint32_t row_bytes = (uint32_t)K * 2u;
   float4* gamma_lo = reinterpret_cast<float4*>(stats_smem);                 // [K/8] gamma of elements 0-3 of each vector
   float4* gamma_hi = gamma_lo + (K >> 3);                                   // [K/8] gamma of elements 4-7
-  uint8_t* slots = stats_smem + (size_t)K * 4;                              // [warps][kStatsDepth][row_bytes]
-  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t)warps * kStatsDepth * row_bytes);
+  uint8_t* slots = stats_smem + (size_t)K * 4;                              // [n_slots][row_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t)n_slots * row_bytes);
+  // uses[s] = number of copies issued into slot s so far.  A barrier's parity alone cannot tell "the
+  // copy of my row has landed" from "the copy two uses earlier has landed", so a warp first makes sure
+  // that its row's copy has been issued (which implies that the use before it was fully consumed).
+  volatile int* uses = reinterpret_cast<volatile int*>(bars + n_slots);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int band = (M + gridDim.x - 1) / gridDim.x;
   const int band0 = blockIdx.x * band;
   const int n_band = min(band, M - band0);    // rows of this CTA (<= 0: nothing to do)
-  uint8_t* my_slots = slots + (size_t)warp * kStatsDepth * row_bytes;
-  uint64_t* my_bars = bars + warp * kStatsDepth;
-  auto issue = [&](int r, int d) {            // r: band-relative row
-    mbar_expect_tx(&my_bars[d], row_bytes);
-    bulk_load_1d(my_slots + (size_t)d * row_bytes, x + (size_t)(band0 + r) * K, row_bytes, &my_bars[d]);
+  auto issue = [&](int r) {                   // r: band-relative row -> slot r % n_slots
+    const int s = r % n_slots;
+    mbar_expect_tx(&bars[s], row_bytes);
+    bulk_load_1d(slots + (size_t)s * row_bytes, x + (size_t)(band0 + r) * K, row_bytes, &bars[s]);
+    __threadfence_block();
+    uses[s] = r / n_slots + 1;
   };
-  // the warp's own barriers and first two copies: nothing here depends on another warp
-  int cur0 = warp < n_band ? warp : -1;
-  int cur1 = warp + warps < n_band ? warp + warps : -1;
-  if (lane == 0) {
-    mbar_init(&my_bars[0], 1);
-    mbar_init(&my_bars[1], 1);
+  // thread s owns slot s at start-up: barrier, first copy (the ring fills while gamma is staged)
+  if (threadIdx.x == 0) next_row = 0;
+  for (int s = threadIdx.x; s < n_slots; s += blockDim.x) {
+    mbar_init(&bars[s], 1);
+    uses[s] = 0;
     fence_mbar_init();
-    if (cur0 >= 0) issue(cur0, 0);
-    if (cur1 >= 0) issue(cur1, 1);
+    if (s < n_band) issue(s);
   }
-  if (threadIdx.x == 0) next_row = kStatsDepth * warps;
   for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) {
     const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
     gamma_lo[q] = make_float4(bf16lo_to_f32(g.x), bf16hi_to_f32(g.x), bf16lo_to_f32(g.y), bf16hi_to_f32(g.y));
@@ -212,15 +213,25 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
 
   float mx = 0.0f;
   const int nvec_row = K >> 3;
-  for (int it = 0;; ++it) {
-    const int d = it & 1;
-    const int r = d ? cur1 : cur0;
-    if (r < 0) break;   // rows are claimed in increasing order: an empty slot means the band is exhausted
-    if (!mbar_wait_bounded(&my_bars[d], (uint32_t)(it >> 1) & 1u)) {
+  while (true) {
+    int r = 0;
+    if (lane == 0) r = atomicAdd(&next_row, 1);
+    r = __shfl_sync(0xffffffffu, r, 0);
+    if (r >= n_band) break;
+    const int s = r % n_slots;
+    const int use = r / n_slots;
+    bool ok = true;
+    if (lane == 0) {
+      uint32_t spins = 0;
+      while (uses[s] <= use && ++spins < kSpinLimit) {}
+      ok = uses[s] > use;
+    }
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;
+    if (!ok || !mbar_wait_bounded(&bars[s], (uint32_t)use & 1u)) {
       if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
       break;
     }
-    const uint4* src = reinterpret_cast<const uint4*>(my_slots + (size_t)d * row_bytes);
+    const uint4* src = reinterpret_cast<const uint4*>(slots + (size_t)s * row_bytes);
     uint4 v[NV];
 #pragma unroll
     for (int j = 0; j < NV; ++j) {
@@ -228,14 +239,12 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       v[j] = (q < nvec_row) ? src[q] : make_uint4(0, 0, 0, 0);
     }
     const int row = band0 + r;
-    int claimed = -1;
     float inv;
     if constexpr (COMPUTE_INV_RMS) {
       inv = stats_inv_rms<NV>(v, K, eps);
       if (lane == 0) {
         inv_rms[row] = inv;
-        claimed = atomicAdd(&next_row, 1);
-        if (claimed < n_band) issue(claimed, d); else claimed = -1;
+        if (r + n_slots < n_band) issue(r + n_slots);
       }
       mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
     } else {
@@ -243,13 +252,8 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
       // every lane's copy of the row has been consumed by the arithmetic above
       __syncwarp();
-      if (lane == 0) {
-        claimed = atomicAdd(&next_row, 1);
-        if (claimed < n_band) issue(claimed, d); else claimed = -1;
-      }
+      if (lane == 0 && r + n_slots < n_band) issue(r + n_slots);
     }
-    claimed = __shfl_sync(0xffffffffu, claimed, 0);
-    if (d) cur1 = claimed; else cur0 = claimed;
   }
   float run_max = warp_max(mx);
   if (lane == 0) warp_max_s[warp] = run_max;
@@ -1361,22 +1365,21 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   return norm ? launch_quantize_t<false, true>(tmap, a, st, behind_pass1) : launch_quantize_t<false, false>(tmap, a, st, behind_pass1);
 }
 
-// Warps per CTA of the pipelined statistics kernel for rows of K elements (0: rows too long for it).
-static int stats_warps_for(int64_t K) {
-  const int64_t budget = 227 * 1024 - K * 4 - 2048;
-  const int64_t w = budget / (kStatsDepth * K * 2);
-  const int64_t cap = K <= 4096 ? kStatsMaxWarps : 6;
-  return (int)std::max<int64_t>(0, std::min<int64_t>(w, cap));
+// Row slots of the pipelined statistics kernel for rows of K elements (fewer than 4: rows too long for it).
+static int stats_slots_for(int64_t K) {
+  const int64_t budget = 227 * 1024 - K * 4 - 2048;   // gamma tables, barriers, static shared memory
+  return (int)std::max<int64_t>(0, std::min<int64_t>(budget / (K * 2), 64));
 }
 
 template <int NV, bool CI>
 static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
-                          int64_t M, int64_t K, int warps, int* status, cudaStream_t st, int* grid_out) {
+                          int64_t M, int64_t K, int slots, int* status, cudaStream_t st, int* grid_out) {
   auto kern = rmsnorm_stats_kernel<NV, CI>;
-  const size_t smem = (size_t)K * 4 + (size_t)warps * kStatsDepth * K * 2 + (size_t)warps * kStatsDepth * 8;
+  const int warps = std::min(NV <= 16 ? kStatsMaxWarps : 6, slots);
+  const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 + (size_t)slots * 12;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
-  kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, partials, eps, (int)M, (int)K, status);
+  kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, partials, eps, (int)M, (int)K, slots, status);
   FP4_CUDA_CHECK(cudaGetLastError());
   *grid_out = grid;
   return 0;
@@ -1394,20 +1397,20 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
   if (scratch == nullptr) return -1;
   auto xb = reinterpret_cast<const __nv_bfloat16*>(x);
   auto gb = reinterpret_cast<const __nv_bfloat16*>(gamma);
-  const int warps = stats_warps_for(K);
+  const int slots = stats_slots_for(K);
   int grid = 0;
-  if (K <= 8192 && warps >= 2) {
+  if (K <= 8192 && slots >= 4) {
     int* status = device_status_ptr();
     if (status == nullptr) return -1;
     int rc;
-    if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
-                                    : launch_stats_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
-    else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
-                                         : launch_stats_t<8, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
-    else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
-                                         : launch_stats_t<16, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
-    else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid)
-                          : launch_stats_t<32, false>(xb, gb, inv_rms, scratch, eps, M, K, warps, status, st, &grid);
+    if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
+                                    : launch_stats_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
+    else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
+                                         : launch_stats_t<8, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
+    else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
+                                         : launch_stats_t<16, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
+    else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
+                          : launch_stats_t<32, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
     if (rc) return rc;
   } else {
     grid = (int)std::min<int64_t>((M + 7) / 8, std::min<int64_t>((int64_t)device_sm_count() * 8, kScratchFloats));
