@@ -230,6 +230,30 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
 int fp4b200_row_rms_reduce(const float* row_rms_partial, int64_t M, int64_t partial_cols, int64_t hidden_size,
                            float eps, float* inv_rms, void* stream);
 
+/* ---- RMSNorm backward behind the dgrad GEMMs ----------------------------------------------- */
+
+/* sum3_rmsnorm_bwd_out(d0, d1, d2, input, norm_weight, inv_rms, d_sum, grad_input, dgamma_partials, dgamma)
+ * (nvfp4_b200_gemm.cu:432-562; kernels :196-323 and :382-430): all matrices [M, K] bf16 row-major.
+ *   d_sum      = bf16(bf16(d0 + d1) + d2)
+ *   grad_input = bf16(inv * (d_sum*gamma - x*inv*mean)),  mean = sum_c(d_sum * (x*inv*gamma)) / K per row, summed in
+ *                the order of the reference's 512-thread block (thread t: columns t, t+512, ...; cub block sum)
+ *   dgamma_partials [ceil(M/256), K] fp32: per 256-row tile, rows accumulated in turn; dgamma [K] (fp32, or bf16
+ *                when dgamma_is_bf16) = the tiles added in turn.  Deterministic: no atomics.
+ * K a multiple of 256, at most 4096 (the reference takes any K).  Outputs must not overlap inputs or each other. */
+int fp4b200_sum3_rmsnorm_bwd(const void* d0, const void* d1, const void* d2, const void* input, const void* norm_weight,
+                             const float* inv_rms, void* d_sum, void* grad_input, float* dgamma_partials, void* dgamma,
+                             int dgamma_is_bf16, int64_t M, int64_t K, void* stream);
+
+/* rmsnorm_bwd_residual_out(d_normed, input, norm_weight, inv_rms, residual_grad, grad_input, dgamma)
+ * (nvfp4_b200_gemm.cu:564-646; kernel :325-380): K = 4096 only, as the reference.
+ *   grad_input = bf16(bf16(dx) + residual_grad), dx as above with the reference's 256-thread block order.
+ *   dgamma [K] fp32 = sum over rows of d_normed * (x*inv).  The reference adds these with atomics in no fixed
+ *                order; here they go through the same 256-row tiles as above, which needs the scratch
+ *                dgamma_partials [ceil(M/256), K] fp32 from the caller and makes the result reproducible. */
+int fp4b200_rmsnorm_bwd_residual(const void* d_normed, const void* input, const void* norm_weight, const float* inv_rms,
+                                 const void* residual_grad, void* grad_input, float* dgamma_partials, float* dgamma,
+                                 int64_t M, int64_t K, void* stream);
+
 /* fp32_to_fp4x2(A_fp32) / fp4x2_to_fp32(A_fp4x2) of the reference GEMM module (nvfp4_b200_gemm.cu:1480-1510;
  * kernels nvfp4_quantize.cuh:293-308): element 2i in the low nibble, RN-even, saturating. */
 int fp4b200_fp32_to_fp4x2(const float* in_f32, int64_t n_pairs, void* out_fp4x2, void* stream);

@@ -190,6 +190,13 @@ __device__ __forceinline__ void bulk_load_1d(void* smem_dst, const void* gsrc, u
                : "memory");
 }
 
+// Contiguous bytes from shared memory to global memory as one bulk copy of the calling thread's
+// current bulk group (16-byte aligned addresses, size a multiple of 16).
+__device__ __forceinline__ void bulk_store_1d(void* gdst, const void* smem_src, uint32_t bytes) {
+  asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(gdst), "r"(smem_u32(smem_src)), "r"(bytes)
+               : "memory");
+}
+
 // 2-D tiled TMA load (no multicast): box at element coordinates (x = inner, y = outer).
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int x, int y,
                                             uint64_t* bar) {

@@ -188,6 +188,65 @@ def nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps):
                   coeff.data_ptr(), _stream(p))
 
 
+def _bf16_matrix(t, name, like=None):
+    if (not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous() or t.dtype != torch.bfloat16 or t.dim() != 2
+            or (like is not None and (t.shape != like.shape or t.device != like.device))):
+        raise RuntimeError(f"{name} must be contiguous CUDA bf16 [M,K]")
+
+
+def sum3_rmsnorm_bwd_out(d0, d1, d2, input, norm_weight, inv_rms, d_sum, grad_input, dgamma_partials, dgamma):
+    """nvfp4_b200_gemm.cu:432-562 — d_sum = d0 + d1 + d2 (bf16, left to right), RMSNorm backward dx into grad_input,
+    dgamma through fixed 256-row tiles (dgamma_partials [ceil(M/256), K] fp32) into dgamma [K] (fp32 or bf16);
+    everything into the caller's tensors."""
+    _bf16_matrix(d0, "d0")
+    for t, name in ((d1, "d1"), (d2, "d2"), (input, "input"), (d_sum, "d_sum"), (grad_input, "grad_input")):
+        _bf16_matrix(t, name, d0)
+    M, K = d0.shape
+    if M <= 0 or K <= 0:
+        raise RuntimeError("sum3_rmsnorm_bwd_out requires positive int32-indexable M*K")
+    if (not norm_weight.is_cuda or not norm_weight.is_contiguous() or norm_weight.dtype != torch.bfloat16
+            or norm_weight.dim() != 1 or norm_weight.numel() != K):
+        raise RuntimeError("norm_weight must be contiguous CUDA bf16 [K]")
+    if not inv_rms.is_cuda or not inv_rms.is_contiguous() or inv_rms.dtype != torch.float32 or inv_rms.numel() != M:
+        raise RuntimeError("inv_rms must be contiguous CUDA fp32 [M]")
+    tiles = (M + 255) // 256
+    if (not dgamma_partials.is_cuda or not dgamma_partials.is_contiguous() or dgamma_partials.dtype != torch.float32
+            or tuple(dgamma_partials.shape) != (tiles, K)):
+        raise RuntimeError("dgamma_partials must be contiguous CUDA fp32 [ceil(M/256),K]")
+    if (not dgamma.is_cuda or not dgamma.is_contiguous() or dgamma.dtype not in (torch.float32, torch.bfloat16)
+            or dgamma.dim() != 1 or dgamma.numel() != K):
+        raise RuntimeError("dgamma must be contiguous CUDA fp32 or bf16 [K]")
+    with torch.cuda.device(d0.device):
+        _lib.call("fp4b200_sum3_rmsnorm_bwd", d0.data_ptr(), d1.data_ptr(), d2.data_ptr(), input.data_ptr(),
+                  norm_weight.data_ptr(), inv_rms.data_ptr(), d_sum.data_ptr(), grad_input.data_ptr(),
+                  dgamma_partials.data_ptr(), dgamma.data_ptr(), int(dgamma.dtype == torch.bfloat16), M, K, _stream(d0))
+
+
+def rmsnorm_bwd_residual_out(d_normed, input, norm_weight, inv_rms, residual_grad, grad_input, dgamma):
+    """nvfp4_b200_gemm.cu:564-646 — grad_input = bf16(RMSNorm backward dx) + residual_grad, dgamma [4096] fp32; K = 4096.
+    dgamma is accumulated through fixed 256-row tiles (a scratch tensor from torch's allocator) instead of the
+    reference's atomics, so repeated calls give identical bits."""
+    _bf16_matrix(d_normed, "d_normed")
+    M, K = d_normed.shape
+    if M <= 0 or K != 4096:
+        raise RuntimeError("rmsnorm_bwd_residual_out requires [M,4096] with int32 M")
+    for t, name in ((input, "input"), (residual_grad, "residual_grad"), (grad_input, "grad_input")):
+        _bf16_matrix(t, name, d_normed)
+    if (not norm_weight.is_cuda or not norm_weight.is_contiguous() or norm_weight.dtype != torch.bfloat16
+            or norm_weight.dim() != 1 or norm_weight.numel() != K):
+        raise RuntimeError("norm_weight must be contiguous CUDA bf16 [4096]")
+    if (not inv_rms.is_cuda or not inv_rms.is_contiguous() or inv_rms.dtype != torch.float32 or inv_rms.dim() != 1
+            or inv_rms.numel() != M):
+        raise RuntimeError("inv_rms must be contiguous CUDA fp32 [M]")
+    if not dgamma.is_cuda or not dgamma.is_contiguous() or dgamma.dtype != torch.float32 or dgamma.dim() != 1 or dgamma.numel() != K:
+        raise RuntimeError("dgamma must be contiguous CUDA fp32 [4096]")
+    partials = torch.empty(((M + 255) // 256, K), dtype=torch.float32, device=d_normed.device)
+    with torch.cuda.device(d_normed.device):
+        _lib.call("fp4b200_rmsnorm_bwd_residual", d_normed.data_ptr(), input.data_ptr(), norm_weight.data_ptr(),
+                  inv_rms.data_ptr(), residual_grad.data_ptr(), grad_input.data_ptr(), partials.data_ptr(), dgamma.data_ptr(),
+                  M, K, _stream(d_normed))
+
+
 def fp32_to_fp4x2(A_fp32):
     """nvfp4_b200_gemm.cu:1480-1494 — [R, C] float32 -> [R, C/2] float4_e2m1fn_x2 (RN-even, saturating)."""
     if not A_fp32.is_cuda or A_fp32.dtype != torch.float32 or A_fp32.dim() != 2 or not A_fp32.is_contiguous() \

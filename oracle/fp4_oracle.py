@@ -527,6 +527,94 @@ def row_rms_reduce(partial: np.ndarray, hidden_size: int, eps: float) -> np.ndar
     return (1.0 / np.sqrt((mean + F32(eps)).astype(F32).astype(np.float64))).astype(F32)
 
 
+def _fma32(a: np.ndarray, b: np.ndarray, c: np.ndarray) -> np.ndarray:
+    """fp32 fused multiply-add: the exact product (<= 48 significant bits, exact in the 64-bit significand of
+    the x86 long double) plus c, rounded to the long double and then to fp32.  The double rounding can only
+    differ from the single one when the long-double sum lands exactly on an fp32 tie, ~2^-40 per operation."""
+    assert np.finfo(np.longdouble).nmant >= 63, "needs the x86 80-bit long double"
+    p = np.asarray(a, dtype=F32).astype(np.longdouble) * np.asarray(b, dtype=F32).astype(np.longdouble)
+    return (p + np.asarray(c, dtype=F32).astype(np.longdouble)).astype(F32)
+
+
+def _block_sum(local: np.ndarray) -> np.ndarray:
+    """Sum over the last axis (B threads, B a multiple of 32) in the order of ``cub::BlockReduce<float, B>::Sum``
+    with its default warp-reduction algorithm (CCCL, the CUDA toolkit's bundled copy; not part of the reference
+    tree): inside each warp a shuffle-down tree with offsets 1, 2, 4, 8, 16 (lane 0 ends with the balanced tree
+    over neighbouring lanes), then thread 0 adds the warp sums one after another in warp order."""
+    v = np.asarray(local, dtype=F32)
+    M, B = v.shape
+    v = v.reshape(M, B // 32, 32)
+    while v.shape[-1] > 1:
+        v = (v[..., 0::2] + v[..., 1::2]).astype(F32)
+    w = v[..., 0]
+    total = w[:, 0].copy()
+    for k in range(1, w.shape[1]):
+        total = (total + w[:, k]).astype(F32)
+    return total
+
+
+def _rmsnorm_bwd_core(dy, x, gamma, inv_rms, block: int):
+    """Row mean and dx (fp32, before the bf16 rounding) of the reference's RMSNorm backward kernels
+    (ThunderKittens/kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:254-323 with block = 512, :325-380 with block =
+    256): thread t walks columns t, t + block, ... with ``s = fma(dy, (x*inv)*gamma, s)``; mean = block sum / K;
+    ``dx = inv * fma(dy, gamma, -((x*inv)*mean))`` (the contraction nvcc applies to ``dy*gamma - x*inv*mean``)."""
+    dy = np.asarray(dy, dtype=F32)
+    x = np.asarray(x, dtype=F32)
+    g = np.asarray(gamma, dtype=F32)[None, :]
+    inv = np.asarray(inv_rms, dtype=F32)[:, None]
+    M, K = x.shape
+    xi = (x * inv).astype(F32)
+    normed = (xi * g).astype(F32)
+    local = np.zeros((M, block), dtype=F32)
+    for c0 in range(0, K, block):
+        n = min(block, K - c0)
+        local[:, :n] = _fma32(dy[:, c0:c0 + n], normed[:, c0:c0 + n], local[:, :n])
+    mean = (_block_sum(local) / F32(K)).astype(F32)
+    u = (xi * mean[:, None]).astype(F32)
+    v = ((dy * g).astype(F32) - u).astype(F32)       # dy*gamma is exact in fp32 (two bf16 factors)
+    return mean, (inv * v).astype(F32)
+
+
+def rmsnorm_bwd_dgamma_tiles(dy, x, inv_rms, row_tile: int = 256):
+    """``partials[tile, c] = fma(dy*x, inv, partial)`` over the tile's rows in turn (dy*x is exact in fp32), and
+    dgamma = the tiles added in turn (nvfp4_b200_gemm.cu:382-430)."""
+    dy = np.asarray(dy, dtype=F32)
+    x = np.asarray(x, dtype=F32)
+    inv = np.asarray(inv_rms, dtype=F32)
+    M, K = x.shape
+    tiles = (M + row_tile - 1) // row_tile
+    partials = np.zeros((tiles, K), dtype=F32)
+    prod = (dy * x).astype(F32)
+    for t in range(tiles):
+        for r in range(t * row_tile, min(M, (t + 1) * row_tile)):
+            partials[t] = _fma32(prod[r], np.full(K, inv[r], dtype=F32), partials[t])
+    dgamma = np.zeros(K, dtype=F32)
+    for t in range(tiles):
+        dgamma = (dgamma + partials[t]).astype(F32)
+    return partials, dgamma
+
+
+def sum3_rmsnorm_bwd(d0, d1, d2, x, gamma, inv_rms):
+    """``sum3_rmsnorm_bwd_out`` (nvfp4_b200_gemm.cu:432-562): d_sum = bf16(bf16(d0 + d1) + d2), dx of the
+    512-thread kernel, dgamma through 256-row tiles (fp32; its bf16 form is the RN rounding of it)."""
+    d_sum = bf16_round((bf16_round((np.asarray(d0, F32) + np.asarray(d1, F32)).astype(F32)) + np.asarray(d2, F32)).astype(F32))
+    _, dx = _rmsnorm_bwd_core(d_sum, x, gamma, inv_rms, 512)
+    partials, dgamma = rmsnorm_bwd_dgamma_tiles(d_sum, x, inv_rms)
+    return dict(d_sum=d_sum, grad_input=bf16_round(dx), dgamma_partials=partials, dgamma=dgamma)
+
+
+def rmsnorm_bwd_residual(d_normed, x, gamma, inv_rms, residual_grad):
+    """``rmsnorm_bwd_residual_out`` (nvfp4_b200_gemm.cu:564-646): dx of the 256-thread kernel, rounded to bf16,
+    plus the residual gradient in bf16.  The reference accumulates dgamma = sum over rows of dy*(x*inv) with
+    atomics in no fixed order; ``dgamma`` here is the float64 sum of those fp32 terms, to compare within a
+    tolerance."""
+    _, dx = _rmsnorm_bwd_core(d_normed, x, gamma, inv_rms, 256)
+    out = bf16_round((bf16_round(dx) + np.asarray(residual_grad, F32)).astype(F32))
+    xi = (np.asarray(x, F32) * np.asarray(inv_rms, F32)[:, None]).astype(F32)
+    terms = (np.asarray(d_normed, F32) * xi).astype(F32)
+    return dict(grad_input=out, dgamma=terms.astype(np.float64).sum(axis=0))
+
+
 def tk_nvfp4_quantize(a: np.ndarray, scale_2d: bool = False):
     """The reference GEMM module's own operand producer (ThunderKittens/kernels/gemm/nvfp4_b200/
     nvfp4_quantize.cuh:57-255): ``sg = amax/(6*448)``; block scale ``e4m3(b/6 * (1/max(sg,1e-12)))``; codes
