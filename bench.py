@@ -314,8 +314,22 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
         d = st["qd"]
         gemm.nvfp4_gemm(d[2], d[3], d[5], qx[2], qx[3], qx[4], dw1)
         gemm.nvfp4_gemm(d[8], d[9], d[11], qx[2], qx[3], qx[4], dw3)
-    names = ["quant_dy_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_quant_sr", "w13_dgrad_gemms", "w13_wgrad_gemms"]
-    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_w13_dgrad, s_w13_wgrad])
+    inv_rms = qx[5]
+    dx_in = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    dgamma = torch.empty(K, dtype=torch.float32, device=dev)
+    def s_rmsnorm_bwd():  # dx_in = RMSNorm backward of dx + the residual stream's gradient (dY), dgamma through row tiles
+        gemm.rmsnorm_bwd_residual_out(dx, x_dev, gamma, inv_rms, dy, dx_in, dgamma)
+    names = ["quant_dy_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_quant_sr", "w13_dgrad_gemms", "w13_wgrad_gemms",
+             "rmsnorm_bwd_residual"]
+    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_w13_dgrad, s_w13_wgrad,
+                                      s_rmsnorm_bwd])
+    # the attention side's form of the same step: three dgrad streams summed first (12 B per element)
+    d_sum = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    partials = torch.empty((M + 255) // 256, K, dtype=torch.float32, device=dev)
+    d3 = [dx, dy, rnd(M, K, 1e-3)]
+    def s_sum3():
+        gemm.sum3_rmsnorm_bwd_out(d3[0], d3[1], d3[2], x_dev, gamma, inv_rms, d_sum, dx_in, partials, dgamma)
+    sum3_ms = _timed_stages(torch, [s_sum3])[0][0]
     t = torch.tensor(ms + [total], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -330,6 +344,9 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
             "step_tflops": sum(fl.values()) * world / (total * 1e-3) / 1e12,
             "quant_dy_gbs": M * K * 3.125 * world / (ms[0] * 1e-3) / 1e9,
             "silu_deriv_quant_gbs": M * H * 8.25 * world / (ms[3] * 1e-3) / 1e9,
+            "rmsnorm_bwd_residual_gbs": M * K * 8.0 * world / (ms[6] * 1e-3) / 1e9,
+            "sum3_rmsnorm_bwd": {"ms": sum3_ms, "gbs": M * K * 12.0 / (sum3_ms * 1e-3) / 1e9,
+                                 "frac_of_measured_hbm": M * K * 12.0 / (sum3_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
             "frac_of_nominal_fp4_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / 9000.0,
             "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
 

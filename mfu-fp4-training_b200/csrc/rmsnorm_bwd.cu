@@ -20,6 +20,8 @@
 
 #include <cuda_bf16.h>
 
+#include <cstdlib>
+
 namespace fp4b200 {
 
 constexpr int kBwdRowTile = 256;      // rows per dgamma tile (fixed by the layout of dgamma_partials)
@@ -38,13 +40,69 @@ __device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
 // rows back with bulk copies before it refills the slot.  Lane L holds columns 8L + 256j + e
 // (j = vector index, e = 0..7), i.e. "threads" t = (8L + e) mod B: for B = 512 the vectors of even j
 // belong to t < 256 and those of odd j to t >= 256, and ascending j walks a thread's columns in order.
-template <bool SUM3>
-__global__ void __launch_bounds__(256, 1)
+//
+// FUSE_DGAMMA: the CTA's rows are interleaved over the grid (row = CTA + i * CTAs) so that all CTAs sweep
+// the matrix together, every finished row is counted on its 256-row tile, and kDgammaWarps extra warps per
+// CTA turn finished tiles into dgamma partials inside the same launch, filling the bandwidth the dx warps
+// leave (no second launch, no tail of its own).  The second pass over dy and x still mostly reaches HBM:
+// at this streaming rate a line stays in L2 for some ten microseconds, less than a 256-row column chain of
+// dependent round trips takes.  Those warps wait (bounded) on other CTAs' progress, so the grid must be
+// co-resident: the kernel is then launched cooperatively with at most one CTA per SM.  The dx warps never
+// wait on anything but their own copies.
+constexpr int kDgammaWarps = 4;
+constexpr int kDgammaRows = 16;     // rows requested ahead per column chain
+
+__device__ __forceinline__ uint2 ld_cg_u2(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.global.cg.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
+  return v;
+}
+
+__device__ __forceinline__ int ld_acquire_gpu(const int* p) {
+  int v;
+  asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// One dgamma chain segment: rows [row, row + n) of 4 columns, in turn.
+__device__ __forceinline__ void dgamma_rows(const uint2* dp, const uint2* xp, size_t pitch, const float* __restrict__ inv_rms,
+                                            int row, int n, float (&p)[4]) {
+  int i = 0;
+#pragma unroll 1
+  for (; i + kDgammaRows <= n; i += kDgammaRows) {
+    uint2 dv[kDgammaRows], xv[kDgammaRows];
+#pragma unroll
+    for (int u = 0; u < kDgammaRows; ++u) {
+      dv[u] = ld_cg_u2(dp + (size_t)(i + u) * pitch);
+      xv[u] = ld_cg_u2(xp + (size_t)(i + u) * pitch);
+    }
+#pragma unroll
+    for (int u = 0; u < kDgammaRows; ++u) {
+      const float iv = __ldg(inv_rms + row + i + u);
+      p[0] = fmaf(bf16lo_to_f32(dv[u].x) * bf16lo_to_f32(xv[u].x), iv, p[0]);
+      p[1] = fmaf(bf16hi_to_f32(dv[u].x) * bf16hi_to_f32(xv[u].x), iv, p[1]);
+      p[2] = fmaf(bf16lo_to_f32(dv[u].y) * bf16lo_to_f32(xv[u].y), iv, p[2]);
+      p[3] = fmaf(bf16hi_to_f32(dv[u].y) * bf16hi_to_f32(xv[u].y), iv, p[3]);
+    }
+  }
+  for (; i < n; ++i) {
+    const uint2 d = ld_cg_u2(dp + (size_t)i * pitch), xx = ld_cg_u2(xp + (size_t)i * pitch);
+    const float iv = __ldg(inv_rms + row + i);
+    p[0] = fmaf(bf16lo_to_f32(d.x) * bf16lo_to_f32(xx.x), iv, p[0]);
+    p[1] = fmaf(bf16hi_to_f32(d.x) * bf16hi_to_f32(xx.x), iv, p[1]);
+    p[2] = fmaf(bf16lo_to_f32(d.y) * bf16lo_to_f32(xx.y), iv, p[2]);
+    p[3] = fmaf(bf16hi_to_f32(d.y) * bf16hi_to_f32(xx.y), iv, p[3]);
+  }
+}
+
+template <bool SUM3, bool FUSE_DGAMMA>
+__global__ void __launch_bounds__((8 + kDgammaWarps) * 32, 1)
 rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16* __restrict__ in1,
                       const __nv_bfloat16* __restrict__ in2, const __nv_bfloat16* __restrict__ x,
                       const __nv_bfloat16* __restrict__ gamma, const float* __restrict__ inv_rms,
                       const __nv_bfloat16* __restrict__ residual, __nv_bfloat16* __restrict__ d_sum,
-                      __nv_bfloat16* __restrict__ dx_out, int M, int K, int n_slots, int* __restrict__ status) {
+                      __nv_bfloat16* __restrict__ dx_out, int M, int K, int n_slots, int n_dx_warps,
+                      int* __restrict__ tile_done, float* __restrict__ dgamma_partials, int* __restrict__ status) {
   constexpr int NT = SUM3 ? 4 : 3;      // streams per slot
   constexpr int H = SUM3 ? 2 : 1;       // halves of the virtual block held per lane
   extern __shared__ __align__(128) uint8_t bwd_smem[];
@@ -58,22 +116,27 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
   // uses[s]: copies issued into slot s so far (a barrier's one phase bit cannot tell two uses apart)
   volatile int* uses = reinterpret_cast<volatile int*>(bars + n_slots);
   const int lane = threadIdx.x & 31;
+  // rows of this CTA: a contiguous band, or (FUSE_DGAMMA) every gridDim.x-th row
   const int band = (M + gridDim.x - 1) / gridDim.x;
-  const int band0 = blockIdx.x * band;
-  const int n_band = min(band, M - band0);
+  const int n_band = FUSE_DGAMMA ? (M - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x
+                                 : min(band, M - (int)blockIdx.x * band);
+  auto global_row = [&](int r) { return FUSE_DGAMMA ? (int)blockIdx.x + r * (int)gridDim.x : (int)blockIdx.x * band + r; };
+  const uint64_t once = l2_policy_evict_first();
   auto issue = [&](int r) {
     const int s = r % n_slots;
     uint8_t* dst = slots + (size_t)s * slot_bytes;
-    const size_t off = (size_t)(band0 + r) * K;
+    const size_t off = (size_t)global_row(r) * K;
     mbar_expect_tx(&bars[s], slot_bytes);
-    bulk_load_1d(dst, in0 + off, row_bytes, &bars[s]);
+    // streams nobody reads again leave L2 first, so that the rows the dgamma warps come back for stay
     if constexpr (SUM3) {
-      bulk_load_1d(dst + row_bytes, in1 + off, row_bytes, &bars[s]);
-      bulk_load_1d(dst + 2 * row_bytes, in2 + off, row_bytes, &bars[s]);
+      bulk_load_1d_hint(dst, in0 + off, row_bytes, &bars[s], once);
+      bulk_load_1d_hint(dst + row_bytes, in1 + off, row_bytes, &bars[s], once);
+      bulk_load_1d_hint(dst + 2 * row_bytes, in2 + off, row_bytes, &bars[s], once);
       bulk_load_1d(dst + 3 * row_bytes, x + off, row_bytes, &bars[s]);
     } else {
+      bulk_load_1d(dst, in0 + off, row_bytes, &bars[s]);
       bulk_load_1d(dst + row_bytes, x + off, row_bytes, &bars[s]);
-      bulk_load_1d(dst + 2 * row_bytes, residual + off, row_bytes, &bars[s]);
+      bulk_load_1d_hint(dst + 2 * row_bytes, residual + off, row_bytes, &bars[s], once);
     }
     __threadfence_block();
     uses[s] = r / n_slots + 1;
@@ -92,9 +155,50 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
   }
   __syncthreads();
 
+  if constexpr (FUSE_DGAMMA) {
+    const int warp = threadIdx.x >> 5;
+    if (warp >= n_dx_warps) {
+      // ---- dgamma warps: items = (tile, slice of 128 columns), tile-major, dealt round-robin over all such warps
+      const int slices = K >> 7;
+      const int n_tiles = (M + kBwdRowTile - 1) / kBwdRowTile;
+      const int n_items = n_tiles * slices;
+      const int n_workers = kDgammaWarps * (int)gridDim.x;
+      const size_t pitch = (size_t)K >> 2;
+      const __nv_bfloat16* dy_src = SUM3 ? d_sum : in0;
+      for (int item = (warp - n_dx_warps) * (int)gridDim.x + (int)blockIdx.x; item < n_items; item += n_workers) {
+        const int t = item / slices, c4 = (item - t * slices) * 32 + lane;
+        const int row0 = t * kBwdRowTile, rows = min(kBwdRowTile, M - row0);
+        bool ok = true;
+        if (lane == 0) {
+          uint32_t spins = 0;
+          while (ld_acquire_gpu(tile_done + t) < rows && ++spins < kSpinLimit) __nanosleep(256);
+          ok = ld_acquire_gpu(tile_done + t) >= rows;
+        }
+        if (__shfl_sync(0xffffffffu, (int)ok, 0) == 0) {
+          if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
+          return;
+        }
+        float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        dgamma_rows(reinterpret_cast<const uint2*>(dy_src) + (size_t)row0 * pitch + c4,
+                    reinterpret_cast<const uint2*>(x) + (size_t)row0 * pitch + c4, pitch, inv_rms, row0, rows, p);
+        reinterpret_cast<float4*>(dgamma_partials + (size_t)t * K)[c4] = make_float4(p[0], p[1], p[2], p[3]);
+      }
+      return;
+    }
+  }
+
   const int nvec_row = K >> 3;
   const int nv = (nvec_row + 31) >> 5;     // vectors per lane (K is a multiple of 256: the same for all lanes)
   const float k_f = static_cast<float>(K);
+  int pending_row = -1;                    // lane 0: row whose stores are in flight and not yet counted on its tile
+  auto count_pending = [&]() {
+    if (pending_row >= 0) {
+      bulk_wait_group0();                  // the row's stores are complete ...
+      __threadfence();                     // ... and ordered before the count that publishes them
+      atomicAdd(tile_done + pending_row / kBwdRowTile, 1);
+      pending_row = -1;
+    }
+  };
   while (true) {
     int r = 0;
     if (lane == 0) r = atomicAdd(&next_row, 1);
@@ -113,7 +217,7 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
       if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
       break;
     }
-    const int row = band0 + r;
+    const int row = global_row(r);
     uint8_t* slot = slots + (size_t)s * slot_bytes;
     uint4* s_dy = reinterpret_cast<uint4*>(slot);                                   // d0 -> dy (sum3) | dy
     uint4* s_x = reinterpret_cast<uint4*>(slot + (SUM3 ? 3 : 1) * row_bytes);
@@ -214,8 +318,12 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
     __syncwarp();
     if (lane == 0) {
       const size_t off = (size_t)row * K;
+      if constexpr (FUSE_DGAMMA) {
+        count_pending();                   // stores committed a whole row ago: no wait in practice
+        pending_row = row;
+      }
       if constexpr (SUM3) bulk_store_1d(d_sum + off, s_dy, row_bytes);
-      bulk_store_1d(dx_out + off, s_out, row_bytes);
+      bulk_store_1d_hint(dx_out + off, s_out, row_bytes, once);
       bulk_commit_group();
       if (r + n_slots < n_band) {
         bulk_wait_group_read0();   // the stores have read the slot: it may be overwritten
@@ -223,63 +331,26 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
       }
     }
   }
-  if (lane == 0) bulk_wait_group0();
+  if (lane == 0) {
+    if constexpr (FUSE_DGAMMA) count_pending();
+    bulk_wait_group0();
+  }
 }
 
-__device__ __forceinline__ uint2 ld_stream_u2(const uint2* p) {
-  uint2 v;
-  asm volatile("ld.global.cs.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p));
-  return v;
-}
-
-// dgamma tiles: thread = 4 columns, rows of the tile in turn.  Sixteen rows of both streams are requested
-// before the first is used (the volatile loads keep their order), which is what keeps enough bytes in
-// flight per SM for a kernel whose arithmetic is one dependent chain per column.
-constexpr int kDgammaRows = 16;
+// dgamma tiles as a kernel of its own (grids that cannot be co-resident, A/B runs): thread = 4 columns, rows
+// of the tile in turn, sixteen rows of both streams requested before the first is used.
 __global__ void __launch_bounds__(128)
 rmsnorm_bwd_dgamma_tile_kernel(const __nv_bfloat16* __restrict__ dy, const __nv_bfloat16* __restrict__ x,
                                const float* __restrict__ inv_rms, float* __restrict__ partials, int M, int K) {
-  __shared__ float inv_s[kBwdRowTile];
   const int c4 = blockIdx.x * blockDim.x + threadIdx.x;   // group of 4 columns
-  const int row0 = blockIdx.y * kBwdRowTile;
-  const int row1 = min(row0 + kBwdRowTile, M);
-  for (int r = threadIdx.x; r < row1 - row0; r += blockDim.x) inv_s[r] = __ldg(inv_rms + row0 + r);
-  __syncthreads();
   if (c4 * 4 >= K) return;
+  const int row0 = blockIdx.y * kBwdRowTile;
+  const int rows = min(kBwdRowTile, M - row0);
   const size_t pitch = (size_t)K >> 2;                    // uint2 per row
-  const uint2* dp = reinterpret_cast<const uint2*>(dy) + (size_t)row0 * pitch + c4;
-  const uint2* xp = reinterpret_cast<const uint2*>(x) + (size_t)row0 * pitch + c4;
-  float p0 = 0.0f, p1 = 0.0f, p2 = 0.0f, p3 = 0.0f;
-  int row = row0;
-#pragma unroll 1
-  for (; row + kDgammaRows <= row1; row += kDgammaRows) {
-    uint2 dv[kDgammaRows], xv[kDgammaRows];
-#pragma unroll
-    for (int u = 0; u < kDgammaRows; ++u) {
-      dv[u] = ld_stream_u2(dp + (size_t)u * pitch);
-      xv[u] = ld_stream_u2(xp + (size_t)u * pitch);
-    }
-#pragma unroll
-    for (int u = 0; u < kDgammaRows; ++u) {
-      const float iv = inv_s[row - row0 + u];
-      p0 = fmaf(bf16lo_to_f32(dv[u].x) * bf16lo_to_f32(xv[u].x), iv, p0);
-      p1 = fmaf(bf16hi_to_f32(dv[u].x) * bf16hi_to_f32(xv[u].x), iv, p1);
-      p2 = fmaf(bf16lo_to_f32(dv[u].y) * bf16lo_to_f32(xv[u].y), iv, p2);
-      p3 = fmaf(bf16hi_to_f32(dv[u].y) * bf16hi_to_f32(xv[u].y), iv, p3);
-    }
-    dp += kDgammaRows * pitch;
-    xp += kDgammaRows * pitch;
-  }
-  for (; row < row1; ++row) {
-    const uint2 d = ld_stream_u2(dp), xx = ld_stream_u2(xp);
-    const float iv = inv_s[row - row0];
-    p0 = fmaf(bf16lo_to_f32(d.x) * bf16lo_to_f32(xx.x), iv, p0);
-    p1 = fmaf(bf16hi_to_f32(d.x) * bf16hi_to_f32(xx.x), iv, p1);
-    p2 = fmaf(bf16lo_to_f32(d.y) * bf16lo_to_f32(xx.y), iv, p2);
-    p3 = fmaf(bf16hi_to_f32(d.y) * bf16hi_to_f32(xx.y), iv, p3);
-    dp += pitch;
-    xp += pitch;
-  }
+  float p[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  dgamma_rows(reinterpret_cast<const uint2*>(dy) + (size_t)row0 * pitch + c4,
+              reinterpret_cast<const uint2*>(x) + (size_t)row0 * pitch + c4, pitch, inv_rms, row0, rows, p);
+  const float p0 = p[0], p1 = p[1], p2 = p[2], p3 = p[3];
   reinterpret_cast<float4*>(partials + (size_t)blockIdx.y * K)[c4] = make_float4(p0, p1, p2, p3);
 }
 
@@ -330,40 +401,82 @@ int bwd_slots_for(int64_t K, int streams) {
   return (int)std::min<int64_t>(16, budget / (K * 2 * streams));
 }
 
-template <bool SUM3>
-int launch_bwd_dx(const void* in0, const void* in1, const void* in2, const void* x, const void* gamma, const float* inv_rms,
-                  const void* residual, void* d_sum, void* dx, int64_t M, int64_t K, cudaStream_t st) {
-  int* status = device_status_ptr();
-  if (status == nullptr) return -1;
-  const int sms = device_sm_count();
-  if (sms <= 0) return -1;
-  const int slots = bwd_slots_for(K, SUM3 ? 4 : 3);
-  const int warps = std::min(8, slots);
-  const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 * (SUM3 ? 4 : 3) + (size_t)slots * 12 + 16;
-  auto kern = rmsnorm_bwd_dx_kernel<SUM3>;
-  FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-  const int grid = (int)std::min<int64_t>(sms, M);
-  kern<<<grid, warps * 32, smem, st>>>(static_cast<const __nv_bfloat16*>(in0), static_cast<const __nv_bfloat16*>(in1),
-                                       static_cast<const __nv_bfloat16*>(in2), static_cast<const __nv_bfloat16*>(x),
-                                       static_cast<const __nv_bfloat16*>(gamma), inv_rms,
-                                       static_cast<const __nv_bfloat16*>(residual), static_cast<__nv_bfloat16*>(d_sum),
-                                       static_cast<__nv_bfloat16*>(dx), (int)M, (int)K, slots, status);
-  FP4_CUDA_CHECK(cudaGetLastError());
-  return 0;
+bool fused_dgamma_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FP4B200_BWD_FUSED_DGAMMA");   // "0": dgamma tiles as a kernel of their own (A/B runs)
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
 }
 
-int launch_dgamma(const void* dy, const void* x, const float* inv_rms, float* partials, void* dgamma, bool out_bf16,
-                  int64_t M, int64_t K, cudaStream_t st) {
-  const int row_tiles = (int)((M + kBwdRowTile - 1) / kBwdRowTile);
-  const dim3 grid((unsigned)((K / 4 + 127) / 128), (unsigned)row_tiles);
-  rmsnorm_bwd_dgamma_tile_kernel<<<grid, 128, 0, st>>>(static_cast<const __nv_bfloat16*>(dy),
-                                                       static_cast<const __nv_bfloat16*>(x), inv_rms, partials, (int)M, (int)K);
-  FP4_CUDA_CHECK(cudaGetLastError());
+bool cooperative_launch_supported() {
+  int dev = 0, v = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess) return false;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) != cudaSuccess) return false;
+  return v != 0;
+}
+
+int launch_dgamma_reduce(const float* partials, void* dgamma, bool out_bf16, int row_tiles, int64_t K, cudaStream_t st) {
   const unsigned rgrid = (unsigned)((K + 63) / 64);
   if (out_bf16) rmsnorm_bwd_dgamma_reduce_kernel<true><<<rgrid, 64, 0, st>>>(partials, dgamma, row_tiles, (int)K);
   else rmsnorm_bwd_dgamma_reduce_kernel<false><<<rgrid, 64, 0, st>>>(partials, dgamma, row_tiles, (int)K);
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
+}
+
+// dx (+ d_sum), the dgamma tiles and their reduction.  dy_for_dgamma: the stream dgamma is taken from (d_sum, which
+// the dx kernel writes, or the caller's d_normed).
+template <bool SUM3>
+int launch_rmsnorm_bwd(const void* in0, const void* in1, const void* in2, const void* x, const void* gamma,
+                       const float* inv_rms, const void* residual, void* d_sum, void* dx, float* partials, void* dgamma,
+                       bool dgamma_bf16, int64_t M, int64_t K, cudaStream_t st) {
+  int* status = device_status_ptr();
+  if (status == nullptr) return -1;
+  const int sms = device_sm_count();
+  if (sms <= 0) return -1;
+  const int slots = bwd_slots_for(K, SUM3 ? 4 : 3);
+  int warps = std::min(8, slots);
+  const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 * (SUM3 ? 4 : 3) + (size_t)slots * 12 + 16;
+  const int grid = (int)std::min<int64_t>(sms, M);
+  const int row_tiles = (int)((M + kBwdRowTile - 1) / kBwdRowTile);
+  const __nv_bfloat16* p_in0 = static_cast<const __nv_bfloat16*>(in0);
+  const __nv_bfloat16* p_in1 = static_cast<const __nv_bfloat16*>(in1);
+  const __nv_bfloat16* p_in2 = static_cast<const __nv_bfloat16*>(in2);
+  const __nv_bfloat16* p_x = static_cast<const __nv_bfloat16*>(x);
+  const __nv_bfloat16* p_gamma = static_cast<const __nv_bfloat16*>(gamma);
+  const __nv_bfloat16* p_res = static_cast<const __nv_bfloat16*>(residual);
+  __nv_bfloat16* p_dsum = static_cast<__nv_bfloat16*>(d_sum);
+  __nv_bfloat16* p_dx = static_cast<__nv_bfloat16*>(dx);
+  int m_i = (int)M, k_i = (int)K, slots_i = slots;
+
+  bool fused = fused_dgamma_enabled() && row_tiles <= kScratchFloats && cooperative_launch_supported();
+  if (fused) {
+    auto kern = rmsnorm_bwd_dx_kernel<SUM3, true>;
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const int block = (warps + kDgammaWarps) * 32;
+    int per_sm = 0;
+    FP4_CUDA_CHECK(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, block, smem));
+    if (per_sm < 1) fused = false;
+    if (fused) {
+      float* scratch = stream_scratch(st);
+      if (scratch == nullptr) return -1;
+      int* tile_done = reinterpret_cast<int*>(scratch);
+      FP4_CUDA_CHECK(cudaMemsetAsync(tile_done, 0, (size_t)row_tiles * sizeof(int), st));
+      void* args[] = {&p_in0, &p_in1, &p_in2, &p_x, &p_gamma, &inv_rms, &p_res, &p_dsum, &p_dx, &m_i, &k_i,
+                      &slots_i, &warps, &tile_done, &partials, &status};
+      FP4_CUDA_CHECK(cudaLaunchCooperativeKernel(reinterpret_cast<void*>(kern), dim3(grid), dim3(block), args, smem, st));
+      return launch_dgamma_reduce(partials, dgamma, dgamma_bf16, row_tiles, K, st);
+    }
+  }
+  auto kern = rmsnorm_bwd_dx_kernel<SUM3, false>;
+  FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  kern<<<grid, warps * 32, smem, st>>>(p_in0, p_in1, p_in2, p_x, p_gamma, inv_rms, p_res, p_dsum, p_dx, m_i, k_i, slots_i,
+                                       warps, nullptr, nullptr, status);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  const dim3 tgrid((unsigned)((K / 4 + 127) / 128), (unsigned)row_tiles);
+  rmsnorm_bwd_dgamma_tile_kernel<<<tgrid, 128, 0, st>>>(SUM3 ? p_dsum : p_in0, p_x, inv_rms, partials, m_i, k_i);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return launch_dgamma_reduce(partials, dgamma, dgamma_bf16, row_tiles, K, st);
 }
 
 int check_shape(const char* fn, int64_t M, int64_t K) {
@@ -403,8 +516,8 @@ int fp4b200_sum3_rmsnorm_bwd(const void* d0, const void* d1, const void* d2, con
                        {norm_weight, (size_t)K * 2, "norm_weight"}, {inv_rms, (size_t)M * 4, "inv_rms"}};
   if (check_no_overlap(fn, outs, 4, ins, 6) != 0) return -1;
   cudaStream_t st = (cudaStream_t)stream;
-  if (launch_bwd_dx<true>(d0, d1, d2, input, norm_weight, inv_rms, nullptr, d_sum, grad_input, M, K, st) != 0) return -1;
-  return launch_dgamma(d_sum, input, inv_rms, dgamma_partials, dgamma, dgamma_is_bf16 != 0, M, K, st);
+  return launch_rmsnorm_bwd<true>(d0, d1, d2, input, norm_weight, inv_rms, nullptr, d_sum, grad_input, dgamma_partials, dgamma,
+                                  dgamma_is_bf16 != 0, M, K, st);
 }
 
 int fp4b200_rmsnorm_bwd_residual(const void* d_normed, const void* input, const void* norm_weight, const float* inv_rms,
@@ -427,10 +540,8 @@ int fp4b200_rmsnorm_bwd_residual(const void* d_normed, const void* input, const 
                        {inv_rms, (size_t)M * 4, "inv_rms"}, {residual_grad, mat, "residual_grad"}};
   if (check_no_overlap(fn, outs, 3, ins, 5) != 0) return -1;
   cudaStream_t st = (cudaStream_t)stream;
-  if (launch_bwd_dx<false>(d_normed, nullptr, nullptr, input, norm_weight, inv_rms, residual_grad, nullptr, grad_input, M, K,
-                           st) != 0)
-    return -1;
-  return launch_dgamma(d_normed, input, inv_rms, dgamma_partials, dgamma, false, M, K, st);
+  return launch_rmsnorm_bwd<false>(d_normed, nullptr, nullptr, input, norm_weight, inv_rms, residual_grad, nullptr, grad_input,
+                                   dgamma_partials, dgamma, false, M, K, st);
 }
 
 }  // extern "C"
