@@ -276,7 +276,8 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
     v5 route: gradients quantised decode-centric with Philox stochastic rounding on the row operand,
     weights pre-quantised (their column operands serve the dgrads).  Stages: quantise dY; W2 dgrad;
     W2 wgrad; SiLU-derivative producer (dh1, dh3 quantised); W1/W3 dgrad (two accumulated GEMMs);
-    W1 and W3 wgrads."""
+    W1 and W3 wgrads; RMSNorm backward of the block input with the residual stream's gradient added.  The
+    attention side's form of the last step (three gradient streams summed first) is timed beside them."""
     tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
     gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
     H, K, M = 14336, K_COLS, M_ROWS
@@ -407,6 +408,40 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
             "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
 
 
+def rmsnorm_bwd_only(args):
+    """sum3 + RMSNorm backward + tiled dgamma on [M, K] bf16 streams; two input sets alternate so that no step
+    finds its inputs in L2.  Prints time and algorithmic bandwidth (12 B per element)."""
+    import torch
+    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    M, K = (int(v) for v in args.rmsnorm_bwd_only.lower().split("x"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(5)
+    sets = [[(s * torch.randn(M, K, generator=g, device=dev)).to(torch.bfloat16) for s in (1e-3, 1e-3, 1e-3, 1.0)]
+            for _ in range(2)]
+    gamma = (1 + 0.1 * torch.randn(K, generator=g, device=dev)).to(torch.bfloat16)
+    inv = [torch.rsqrt(st[3].float().pow(2).mean(dim=1) + EPS) for st in sets]
+    d_sum, dx = torch.empty_like(sets[0][3]), torch.empty_like(sets[0][3])
+    partials = torch.empty((M + 255) // 256, K, dtype=torch.float32, device=dev)
+    dgamma = torch.empty(K, dtype=torch.float32, device=dev)
+    def step(i):
+        d0, d1, d2, x = sets[i % 2]
+        gemm.sum3_rmsnorm_bwd_out(d0, d1, d2, x, gamma, inv[i % 2], d_sum, dx, partials, dgamma)
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    steps = min(args.steps, 50)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    print(json.dumps({"rmsnorm_bwd_only": args.rmsnorm_bwd_only, "ms": ms, "algorithmic_gbs": 12.0 * M * K / (ms * 1e-3) / 1e9,
+                      "status": importlib.import_module("mfu-fp4-training_b200._lib").device_status()}))
+
+
 def gemm_only(args):
     """Times fp4b200_nvfp4_gemm alone at one shape on cuda:0 (random codes and scales)."""
     import torch
@@ -447,10 +482,15 @@ def main():
                     help="timed loop only (no per-kernel, end-to-end or CPU legs): the command ncu captures")
     ap.add_argument("--gemm-only", default=None, metavar="MxNxK",
                     help="time only the NVFP4 GEMM at this shape (tuning / ncu capture helper)")
+    ap.add_argument("--rmsnorm-bwd-only", default=None, metavar="MxK",
+                    help="time only the RMSNorm backward (sum3 form) at this shape (tuning / ncu capture helper)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.gemm_only:
         gemm_only(args)
+        return
+    if args.rmsnorm_bwd_only:
+        rmsnorm_bwd_only(args)
         return
 
     if args.impl == "reference":
@@ -554,7 +594,7 @@ def main():
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": TRAFFIC_PER_LAUNCH,
                 "algorithmic_bytes_per_launch": quant_bytes, "avg_launch_ms": t_quant,
-                "other_kernels": {"rmsnorm_stats_kernel (pass 1)": {
+                "other_kernels": {"rmsnorm_stats_kernel + partials reduction (pass 1 stand-alone, two launches)": {
                     "achieved": stats_bytes / (t_stats * 1e-3) / 1e9, "unit": "GB/s", "avg_launch_ms": t_stats,
                     "algorithmic_bytes_per_launch": stats_bytes,
                     "frac": stats_bytes / (t_stats * 1e-3) / 1e9 / peaks["hbm_gbs"]}},

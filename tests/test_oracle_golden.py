@@ -129,3 +129,43 @@ def test_fwht16_is_orthonormal_involution():
     y = o.fwht16_bf16(x)
     z = o.fwht16_bf16(y)
     assert np.abs(z - x).max() < 0.05
+
+
+def test_rmsnorm_backward_oracle_block_sum_order_and_float64_agreement():
+    """The restated block sum follows the tree it claims (checked on values whose fp32 sum depends on the order),
+    and the whole backward agrees with the float64 formulas to bf16 / fp32 accuracy; the fused multiply-add helper
+    is exact where a product-then-add is not."""
+    # 1 + 2^-24 + 2^-24: ((1 + e) + e) = 1 in fp32 (each add rounds to even), (1 + (e + e)) = 1 + 2^-23
+    e = np.float32(2.0 ** -24)
+    v = np.zeros((1, 64), dtype=np.float32)
+    v[0, 0], v[0, 1], v[0, 2] = 1.0, e, e                 # lanes 0..2 of warp 0: (v0 + v1) + (v2 + v3)
+    assert o._block_sum(v)[0] == np.float32(1.0)          # (1 + e) -> 1, (e + 0) = e, 1 + e -> 1
+    v[0, 1], v[0, 2], v[0, 3] = 0.0, e, e                 # (1 + 0) + (e + e) = 1 + 2^-23
+    assert o._block_sum(v)[0] == np.float32(1.0) + np.float32(2.0 ** -23)
+    w = np.zeros((1, 96), dtype=np.float32)               # warp sums are added one after another: (1 + e) + e = 1
+    w[0, 0], w[0, 32], w[0, 64] = 1.0, e, e
+    assert o._block_sum(w)[0] == np.float32(1.0)
+    # fma: 3 * (1/3 rounded) - 1 is not zero, and only the single rounding sees it
+    a, b = np.float32(3.0), np.float32(1.0) / np.float32(3.0)
+    assert o._fma32(a, b, np.float32(-1.0)) != 0 and np.float32(a * b) + np.float32(-1.0) == 0
+
+    rng = np.random.default_rng(4)
+    M, K = 300, 1024
+    d = [o.bf16_round((1e-3 * rng.standard_normal((M, K))).astype(np.float32)) for _ in range(3)]
+    x = o.make_activations(M, K, seed=5)
+    g = o.make_gamma(K, seed=6)
+    inv = o.rmsnorm_inv_rms(x, 1e-5)
+    r = o.sum3_rmsnorm_bwd(d[0], d[1], d[2], x, g, inv)
+    dy = r["d_sum"].astype(np.float64)
+    xh = x.astype(np.float64) * inv[:, None]
+    mean = (dy * xh * g).sum(axis=1, keepdims=True) / K
+    dx = inv[:, None] * (dy * g - xh * mean)
+    assert np.abs(r["grad_input"] - dx).max() <= 2.0 ** -8 * np.abs(dx).max()
+    assert r["dgamma_partials"].shape == (2, K)
+    assert np.abs(r["dgamma"] - (dy * xh).sum(axis=0)).max() <= 1e-5 * np.abs(dy * xh).sum(axis=0).max()
+    res = o.bf16_round((1e-2 * rng.standard_normal((M, K))).astype(np.float32))
+    r2 = o.rmsnorm_bwd_residual(d[0], x, g, inv, res)
+    xh = x.astype(np.float64) * inv[:, None]
+    mean = (d[0] * xh * g).sum(axis=1, keepdims=True) / K
+    want = inv[:, None] * (d[0] * g - xh * mean) + res
+    assert np.abs(r2["grad_input"] - want).max() <= 2.0 ** -7 * np.abs(want).max()
