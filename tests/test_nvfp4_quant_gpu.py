@@ -33,6 +33,32 @@ def test_quantize_for_gemm_bit_exact(shape, ec):
     assert_status_ok()
 
 
+@pytest.mark.parametrize("ec", [True, False])
+@pytest.mark.parametrize("amax_exp", [0, 7, -20, 100])
+def test_block_scale_for_every_bf16_block_maximum(amax_exp, ec):
+    """Every positive bf16 value of 24 binades below the tensor amax is the maximum of some 16-block: the scale
+    byte for all of them, normal and subnormal E4M3 results, saturation and the tiny-amax branch, in both passes."""
+    tkq = mod("tk_quant_v5")
+    top = 127 + amax_exp                                   # biased exponent of the tensor amax 2^amax_exp
+    expo = np.arange(top - 24, top, dtype=np.uint32)
+    expo = expo[(expo >= 1) & (expo <= 254)]
+    bits = ((expo[:, None] << 7) | np.arange(128, dtype=np.uint32)[None, :]).reshape(-1).astype(np.uint16)
+    vals = o.bf16_from_bits(bits)                          # ascending positive bf16 values
+    n_blocks = (-(-vals.size // 2048)) * 2048
+    v = np.resize(vals, n_blocks)
+    M, K = 128, n_blocks * 16 // 128
+    rng = np.random.default_rng(amax_exp + 1000)
+    x = (rng.uniform(-1, 1, size=(n_blocks, 16)).astype(np.float32) * v[:, None])
+    x[:, 3] = v * np.where(rng.integers(0, 2, size=n_blocks) == 0, 1.0, -1.0)   # the block maximum itself
+    x = o.bf16_round(x).reshape(M, K)
+    x[0, 0] = np.float32(2.0 ** amax_exp)
+    out = tkq.tk_quantize_for_gemm(to_dev_bf16(x), True, ec)
+    torch.cuda.synchronize()
+    ref = o.nvfp4_quantize_for_gemm(x, True, ec)
+    _check_operands(out, ref)
+    assert_status_ok()
+
+
 def test_quantize_row_only_and_golden_inputs(golden):
     tkq = mod("tk_quant_v5")
     x = o.bf16_from_bits(golden["mid_x_bits"])
