@@ -230,6 +230,14 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
 int fp4b200_row_rms_reduce(const float* row_rms_partial, int64_t M, int64_t partial_cols, int64_t hidden_size,
                            float eps, float* inv_rms, void* stream);
 
+/* tk_quantize_nhsd_wo_for_gemm(input, return_transpose, encode_centric) (nvfp4_v5/tk_quantize.cu:3006-3134):
+ * the attention output in its native [B, H, S, D = 64] layout, quantised as the matrix [M = B*S, K = H*D] the
+ * output projection consumes (element (b*S + s, h*64 + d) = input[b, h, s, d]) without a transposing copy.
+ * Same bytes as fp4b200_nvfp4_quantize_for_gemm on the permuted tensor.  S % 128 == 0; outputs 16-byte aligned. */
+int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int64_t S, int64_t D, int return_transpose,
+                                   int encode_centric, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                   float* amax_sg, void* stream);
+
 /* ---- RMSNorm backward behind the dgrad GEMMs ----------------------------------------------- */
 
 /* sum3_rmsnorm_bwd_out(d0, d1, d2, input, norm_weight, inv_rms, d_sum, grad_input, dgamma_partials, dgamma)

@@ -399,6 +399,7 @@ struct QuantArgs {
   int M, K;
   int chunks_m, chunks_k;
   int reverse;             // walk chunks from the last row block to the first
+  int nhsd_heads, nhsd_seq; // > 0: x is [B, heads, seq, 64] and the matrix is [B*seq, heads*64] (strip kernel only)
   // ---- OPT instantiations only (stochastic rounding / 16-point Hadamard transform) ----
   int opt_sr_row, opt_sr_col;   // data stochastic rounding of the row pass / of the column pass
   int opt_row_per_stage;   // random words per 64x64 stage in the row pass's stream: 16 (launch with a column pass) or 8
@@ -903,8 +904,15 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     int cm, ck;
     chunk_coords(it, cm, ck);
     mbar_expect_tx(&my_bars[s], kStripBytes);
-    tma_load_2d(my_slots + (size_t)s * kStripBytes, &tmap_x, ck * kChunk + wh * kStripCols, cm * kChunk + wv * kStripRows,
-                &my_bars[s]);
+    int x = ck * kChunk + wh * kStripCols, y = cm * kChunk + wv * kStripRows;
+    if (a.nhsd_seq > 0) {
+      // head-major input: the strip (32 tokens of one sequence x one 64-wide head) is a contiguous block of the
+      // [B * heads * seq, 64] matrix the tensor map describes (seq is a multiple of 128: no strip straddles two)
+      const int b = y / a.nhsd_seq;
+      y = (b * a.nhsd_heads + (x >> 6)) * a.nhsd_seq + (y - b * a.nhsd_seq);
+      x = 0;
+    }
+    tma_load_2d(my_slots + (size_t)s * kStripBytes, &tmap_x, x, y, &my_bars[s]);
   };
 
   if (tid == 0) {
@@ -1278,8 +1286,10 @@ static bool quant_strip_disabled() {
 template <bool EC, bool NORM, bool OPT = false>
 static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
   CUtensorMap tmap, tmap_row;
-  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)args.K, (uint64_t)args.M,
-                            (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
+  const bool nhsd = args.nhsd_seq > 0;   // [B * heads * seq, 64] instead of [M, K]
+  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, nhsd ? 64u : (uint64_t)args.K,
+                            nhsd ? (uint64_t)args.M * (uint64_t)args.nhsd_heads : (uint64_t)args.M,
+                            nhsd ? 128u : (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   // row-wise codes as a byte matrix [M, K/2], stored in boxes of 32 rows x 32 bytes
   tmap_row = tmap;   // launches without row-wise outputs never use it
@@ -1310,7 +1320,7 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
                            cudaStream_t st, bool weight_2d, const QuantOpt* opt, const AmaxPartials* partials,
-                           float* amax_out) {
+                           float* amax_out, int nhsd_heads, int nhsd_seq) {
   const bool behind_pass1 = partials != nullptr;
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
@@ -1336,7 +1346,10 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.M = (int)M; a.K = (int)K;
   a.chunks_m = (int)(M / kChunk); a.chunks_k = (int)(K / kChunk);
   a.reverse = reverse ? 1 : 0;
+  a.nhsd_heads = nhsd_heads; a.nhsd_seq = nhsd_seq;
   const bool norm = inv_rms != nullptr;
+  if (nhsd_seq > 0 && (opt != nullptr || weight_2d || norm || !strip_kernel_applies(a, false)))
+    return set_error("head-major input: plain quantisation into 16-byte aligned outputs only");
   if (opt != nullptr) {
     a.opt_sr_row = opt->sr_row; a.opt_sr_col = opt->sr_col; a.rng_offset_col = opt->rng_offset_col;
     a.opt_row_per_stage = opt->row_per_stage ? opt->row_per_stage : (col_fp4 != nullptr ? 16 : 8);
@@ -1473,6 +1486,27 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
   return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
                          return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr,
                          true, (cudaStream_t)stream, false, nullptr, &part, amax_sg);
+}
+
+int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int64_t S, int64_t D, int return_transpose,
+                                   int encode_centric, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                   float* amax_sg, void* stream) {
+  const char* fn = "nvfp4_quantize_nhsd_wo";
+  if (B <= 0 || H <= 0 || S <= 0) return set_error("%s: B, H and S must be positive", fn);
+  if (D != 64) return set_error("%s: head_dim must be 64 (got %lld)", fn, (long long)D);
+  if ((S % 128) != 0) return set_error("%s: the sequence length must be a multiple of 128 (got %lld)", fn, (long long)S);
+  if (B * S > INT32_MAX || H * D > INT32_MAX) return set_error("%s: matrix too large", fn);
+  const int64_t M = B * S, K = H * D;
+  if (int rc = check_quant_shapes(x_bf16, M, K, fn)) return rc;
+  if (row_fp4 == nullptr || row_sc == nullptr || amax_sg == nullptr)
+    return set_error("%s: row_fp4, row_sc and amax_sg are required", fn);
+  if (return_transpose && (col_fp4 == nullptr || col_sc == nullptr))
+    return set_error("%s: return_transpose needs col_fp4 and col_sc", fn);
+  AmaxPartials part;
+  if (int rc = launch_amax(x_bf16, M * K, amax_sg, (cudaStream_t)stream, nullptr, &part)) return rc;
+  return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
+                         return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr, true,
+                         (cudaStream_t)stream, false, nullptr, &part, amax_sg, (int)H, (int)S);
 }
 
 int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,

@@ -66,6 +66,34 @@ def tk_quantize_for_gemm(input, return_transpose, encode_centric=True):
             col_sc.view(_E4M3) if return_transpose else col_sc, sg, sg, amax_sg, sync_buf)
 
 
+def tk_quantize_nhsd_wo_for_gemm(input, return_transpose, encode_centric=True):
+    """tk_quantize.cu:3006-3134 — attention output bf16 [B, H, S, 64] quantised as the matrix [B*S, H*64] that the
+    output projection consumes, without a transposing copy; same 8-tuple as ``tk_quantize_for_gemm``."""
+    if not isinstance(input, torch.Tensor) or not input.is_cuda or not input.is_contiguous():
+        raise RuntimeError("input must be a contiguous CUDA tensor")
+    if input.dtype != torch.bfloat16 or input.dim() != 4:
+        raise RuntimeError("input must be bf16 [B, H, S, D]")
+    B, H, S, D = (int(v) for v in input.shape)
+    if D != 64:
+        raise RuntimeError("NHSD WO direct quantization currently requires head_dim == 64")
+    if S % 128:
+        raise RuntimeError("NHSD WO direct quantization requires sequence length to be a multiple of 128")
+    M, K = B * S, H * D
+    if M % 128 or K % 128:
+        raise RuntimeError("logical [B*S, H*D] dimensions must be multiples of 128")
+    with torch.cuda.device(input.device):
+        row_fp4, row_sc, col_fp4, col_sc = _alloc_operands(M, K, input.device, return_transpose)
+        amax_sg = torch.empty(2, dtype=torch.float32, device=input.device)
+        sync_buf = torch.zeros(4, dtype=torch.int32, device=input.device)
+        _lib.call("fp4b200_nvfp4_quantize_nhsd_wo", input.data_ptr(), B, H, S, D, int(bool(return_transpose)),
+                  int(bool(encode_centric)), row_fp4.data_ptr(), row_sc.data_ptr(),
+                  _p(col_fp4) if return_transpose else None, _p(col_sc) if return_transpose else None,
+                  amax_sg.data_ptr(), _stream(input))
+    sg = amax_sg.narrow(0, 1, 1)
+    return (row_fp4.view(_FP4), row_sc.view(_E4M3), col_fp4.view(_FP4) if return_transpose else col_fp4,
+            col_sc.view(_E4M3) if return_transpose else col_sc, sg, sg, amax_sg, sync_buf)
+
+
 def tk_quantize_weight_2d(input):
     """tk_quantize.cu:2445-2555 — 16x16-tile weight quantisation, returns
     (row_fp4, row_sc, col_fp4, col_sc, sg, sg)."""

@@ -175,3 +175,31 @@ def test_quantize_weight_2d(shape):
     assert np.array_equal(o.unpack_fp4(u8(out[2])), o.unpack_fp4(u8(out[0])).T)
     assert out[4].item() == o.nvfp4_global_decode_scale(amax)
     assert_status_ok()
+
+
+@pytest.mark.parametrize("ec", [True, False])
+@pytest.mark.parametrize("shape", [(1, 2, 128, 64), (3, 6, 256, 64), (2, 32, 1024, 64)])
+def test_quantize_nhsd_wo_equals_quantising_the_permuted_tensor(shape, ec):
+    """Attention output in [B, H, S, D] layout: same bytes as quantising its [B*S, H*D] permutation, and (for the
+    small shapes) as the oracle."""
+    tkq = mod("tk_quant_v5")
+    B, H, S, D = shape
+    M, K = B * S, H * D
+    x = o.make_activations(M, K, seed=B + H + S)                      # the logical matrix
+    x_nhsd = np.ascontiguousarray(x.reshape(B, S, H, D).transpose(0, 2, 1, 3))
+    out = tkq.tk_quantize_nhsd_wo_for_gemm(to_dev_bf16(x_nhsd), True, ec)
+    flat = tkq.tk_quantize_for_gemm(to_dev_bf16(x), True, ec)
+    torch.cuda.synchronize()
+    for i in range(4):
+        assert torch.equal(out[i].view(torch.uint8), flat[i].view(torch.uint8)), i
+    assert torch.equal(out[6], flat[6])
+    if M * K <= 1 << 20:
+        _check_operands(out, o.nvfp4_quantize_for_gemm(x, True, ec))
+    row_only = tkq.tk_quantize_nhsd_wo_for_gemm(to_dev_bf16(x_nhsd), False, ec)
+    torch.cuda.synchronize()
+    assert torch.equal(row_only[0].view(torch.uint8), flat[0].view(torch.uint8)) and row_only[2].numel() == 0
+    with pytest.raises(RuntimeError):
+        tkq.tk_quantize_nhsd_wo_for_gemm(to_dev_bf16(x_nhsd[:, :, :64]), True, ec)      # S not a multiple of 128
+    with pytest.raises(RuntimeError):
+        tkq.tk_quantize_nhsd_wo_for_gemm(to_dev_bf16(np.zeros((1, 2, 128, 32), np.float32)), True, ec)   # head_dim 32
+    assert_status_ok()
