@@ -259,6 +259,91 @@ def tk_silu_deriv_quantize_split_for_gemm(dh, h3, h1_raw):
     return (*q1, a1.narrow(0, 1, 1), zero, *q3, a3.narrow(0, 1, 1), zero.clone(), amax_buf, sync_buf, dh1, dh3)
 
 
+# ---- allocate-once / launch-many pairs (CUDA-graph capture) --------------------------------------
+# The *_launch functions run into buffers made by their *_alloc twin and allocate nothing, so they can be
+# captured into a CUDA graph.  The library keeps a few KB of device scratch per (device, stream), created on
+# a stream's first call: run one call on the capture stream before capturing.
+
+def tk_v4_quantize_for_gemm_alloc(M, K, return_transpose, device):
+    """tk_quantize.cu:3622-3641 — (row_fp4, row_sc, col_fp4, col_sc, amax_buf, sync_buf), codes and scales as uint8."""
+    if M % 128 or K % 128:
+        raise RuntimeError("M and K must be multiples of 128")
+    dev = torch.device(device)
+    row_fp4, row_sc, col_fp4, col_sc = _alloc_operands(int(M), int(K), dev, bool(return_transpose))
+    return (row_fp4, row_sc, col_fp4, col_sc, torch.empty(2, dtype=torch.float32, device=dev),
+            torch.empty(4, dtype=torch.int32, device=dev))
+
+
+def tk_v4_quantize_for_gemm_launch(input, return_transpose, encode_centric, row_fp4, row_sc, col_fp4, col_sc, amax_buf,
+                                   sync_buf):
+    """tk_quantize.cu:3646-3799 — amax + row/column quantisation into the caller's buffers; returns
+    (row_fp4, row_sc, col_fp4, col_sc, sg, sg) as views of them."""
+    M, K = _check_bf16_2d(input, "input")
+    if row_fp4.numel() != M * K // 2 or row_sc.numel() != M * K // 16 or amax_buf.numel() < 2:
+        raise RuntimeError("buffers do not match the input shape (use tk_v4_quantize_for_gemm_alloc)")
+    if return_transpose and (col_fp4.numel() != M * K // 2 or col_sc.numel() != M * K // 16):
+        raise RuntimeError("return_transpose needs the column buffers of tk_v4_quantize_for_gemm_alloc(..., True, ...)")
+    with torch.cuda.device(input.device):
+        _lib.call("fp4b200_nvfp4_quantize_for_gemm", input.data_ptr(), M, K, int(bool(return_transpose)),
+                  int(bool(encode_centric)), row_fp4.data_ptr(), row_sc.data_ptr(),
+                  col_fp4.data_ptr() if return_transpose else None, col_sc.data_ptr() if return_transpose else None,
+                  amax_buf.data_ptr(), _stream(input))
+    sg = amax_buf.narrow(0, 1, 1)
+    return (row_fp4.view(_FP4), row_sc.view(_E4M3), col_fp4.view(_FP4) if return_transpose else col_fp4,
+            col_sc.view(_E4M3) if return_transpose else col_sc, sg, sg)
+
+
+def tk_silu_deriv_quantize_split_for_gemm_alloc(M, H, device):
+    """tk_quantize.cu:9660-9690 — 14 buffers: operands of dh1 (4), of dh3 (4), sg_buf [2], zero_buf [1], amax_buf [2],
+    sync_buf [4], dh1, dh3 (bf16 [M, H])."""
+    if M % 128 or H % 128:
+        raise RuntimeError("M and H must be multiples of 128")
+    dev = torch.device(device)
+    o1 = _alloc_operands(int(M), int(H), dev, True)
+    o2 = _alloc_operands(int(M), int(H), dev, True)
+    f32 = dict(dtype=torch.float32, device=dev)
+    return (o1[0].view(_FP4), o1[1].view(_E4M3), o1[2].view(_FP4), o1[3].view(_E4M3),
+            o2[0].view(_FP4), o2[1].view(_E4M3), o2[2].view(_FP4), o2[3].view(_E4M3),
+            torch.empty(2, **f32), torch.zeros(1, **f32), torch.empty(2, **f32),
+            torch.empty(4, dtype=torch.int32, device=dev),
+            torch.empty((int(M), int(H)), dtype=torch.bfloat16, device=dev),
+            torch.empty((int(M), int(H)), dtype=torch.bfloat16, device=dev))
+
+
+def tk_silu_deriv_quantize_split_for_gemm_launch(dh, h3, h1_raw, out1_fp4, out1_sc, out1_fp4_t, out1_sc_t, out2_fp4,
+                                                 out2_sc, out2_fp4_t, out2_sc_t, sg_buf, zero_buf, amax_buf, sync_buf, dh1,
+                                                 dh3):
+    """tk_quantize.cu:9696-9887 — SiLU-derivative producer (encode-centric, round-to-nearest) into the caller's
+    buffers; returns the 12-tuple (dh1 operands, sg1, zero, dh3 operands, sg3, zero).  amax_buf receives the two
+    tensor maxima; sync_buf (unused by this implementation's kernels) carries them between the launches."""
+    M, H = _check_bf16_2d(dh, "dh")
+    _same_shape_bf16(dh, h3, h1_raw)
+    for t in (dh1, dh3):
+        if t.dtype != torch.bfloat16 or not t.is_contiguous() or tuple(t.shape) != (M, H):
+            raise RuntimeError("dh1 / dh3 must be contiguous bf16 [M, H]")
+    if sg_buf.numel() < 2 or amax_buf.numel() < 2 or sync_buf.numel() < 4 or sync_buf.dtype != torch.int32:
+        raise RuntimeError("sg_buf [2], amax_buf [2] and int32 sync_buf [4] are required")
+    for t in (out1_fp4, out1_fp4_t, out2_fp4, out2_fp4_t):
+        if t.numel() * t.element_size() != M * H // 2:
+            raise RuntimeError("code buffers do not match the input shape")
+    for t in (out1_sc, out1_sc_t, out2_sc, out2_sc_t):
+        if t.numel() != M * H // 16:
+            raise RuntimeError("scale buffers do not match the input shape")
+    with torch.cuda.device(dh.device):
+        st = _stream(dh)
+        pair = sync_buf.view(torch.float32)          # [amax1, sg1, amax3, sg3] between the launches
+        _lib.call("fp4b200_silu_deriv_bf16", dh.data_ptr(), h3.data_ptr(), h1_raw.data_ptr(), dh.numel(), dh1.data_ptr(),
+                  dh3.data_ptr(), pair.data_ptr(), pair.data_ptr() + 8, st)
+        for x, amax_ptr, slot, (c, s_, ct, st_) in ((dh1, pair.data_ptr(), 0, (out1_fp4, out1_sc, out1_fp4_t, out1_sc_t)),
+                                                     (dh3, pair.data_ptr() + 8, 1, (out2_fp4, out2_sc, out2_fp4_t, out2_sc_t))):
+            _lib.call("fp4b200_nvfp4_quantize", x.data_ptr(), M, H, amax_ptr, None, 1, c.data_ptr(), s_.data_ptr(),
+                      ct.data_ptr(), st_.data_ptr(), sg_buf.data_ptr() + 4 * slot, st)
+        amax_buf.narrow(0, 0, 1).copy_(pair.narrow(0, 0, 1))
+        amax_buf.narrow(0, 1, 1).copy_(pair.narrow(0, 2, 1))
+    return (out1_fp4, out1_sc, out1_fp4_t, out1_sc_t, sg_buf.narrow(0, 0, 1), zero_buf,
+            out2_fp4, out2_sc, out2_fp4_t, out2_sc_t, sg_buf.narrow(0, 1, 1), zero_buf)
+
+
 # ---- stochastic rounding / Hadamard ("opt") producers -----------------------------------------
 
 _U64 = (1 << 64) - 1

@@ -1,0 +1,112 @@
+"""The allocate-once / launch-many pairs and the other entry points inside CUDA graph capture: a captured call,
+replayed on new input data, gives the same bytes as an eager call on that data."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import fp4_oracle as o
+from tests.gpu_util import assert_status_ok, mod, to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+
+def _capture(fn, warm):
+    """Runs `warm` once on a side stream (the library creates its per-stream scratch on a stream's first call),
+    captures `fn` on that stream and returns the graph."""
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        warm()
+    torch.cuda.current_stream().wait_stream(s)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=s):
+        fn()
+    return g
+
+
+def test_v4_quantize_pair_in_a_graph():
+    tkq = mod("tk_quant_v5")
+    M, K = 512, 1024
+    x = to_dev_bf16(o.make_activations(M, K, seed=1))
+    bufs = tkq.tk_v4_quantize_for_gemm_alloc(M, K, True, x.device)
+    res = {}
+
+    def launch():
+        res["out"] = tkq.tk_v4_quantize_for_gemm_launch(x, True, True, *bufs)
+
+    g = _capture(launch, launch)
+    x2 = o.make_activations(M, K, seed=2)
+    x.copy_(to_dev_bf16(x2))
+    g.replay()
+    torch.cuda.synchronize()
+    ref = o.nvfp4_quantize_for_gemm(x2, True, True)
+    out = res["out"]
+    for i, k in enumerate(["row_fp4", "row_sc", "col_fp4", "col_sc"]):
+        assert np.array_equal(out[i].view(torch.uint8).cpu().numpy().reshape(ref[k].shape), ref[k]), k
+    assert out[4].item() == ref["sg"] and bufs[4][0].item() == ref["amax"]
+    assert_status_ok()
+
+
+def test_silu_deriv_split_pair_in_a_graph_equals_the_allocating_call():
+    tkq = mod("tk_quant_v5")
+    M, H = 256, 512
+    rng = np.random.default_rng(5)
+    mk = lambda s: to_dev_bf16(o.bf16_round((s * rng.standard_normal((M, H))).astype(np.float32)))
+    dh, h3, h1 = mk(1e-3), mk(1.0), mk(2.0)
+    bufs = tkq.tk_silu_deriv_quantize_split_for_gemm_alloc(M, H, dh.device)
+    res = {}
+
+    def launch():
+        res["out"] = tkq.tk_silu_deriv_quantize_split_for_gemm_launch(dh, h3, h1, *bufs)
+
+    g = _capture(launch, launch)
+    for t, s in ((dh, 2e-3), (h3, 0.5), (h1, 1.5)):
+        t.copy_(mk(s))
+    g.replay()
+    torch.cuda.synchronize()
+    eager = tkq.tk_silu_deriv_quantize_split_for_gemm(dh, h3, h1)
+    torch.cuda.synchronize()
+    out = res["out"]
+    assert len(out) == 12
+    for i in (0, 1, 2, 3, 6, 7, 8, 9):
+        assert torch.equal(out[i].view(torch.uint8), eager[i].view(torch.uint8)), i
+    assert torch.equal(out[4], eager[4]) and torch.equal(out[10], eager[10])          # sg of dh1 / dh3
+    assert torch.equal(bufs[10], eager[12])                                           # the two tensor maxima
+    assert torch.equal(bufs[12], eager[14]) and torch.equal(bufs[13], eager[15])     # dh1, dh3
+    assert out[5].item() == 0.0
+    assert_status_ok()
+
+
+def test_fused_norm_quantize_and_rmsnorm_backward_in_a_graph():
+    """The fused producer (two launches, the second programmatically dependent on the first) and the RMSNorm
+    backward (cooperative launch) are captured with their allocating mirrors: torch's graph pool serves them."""
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    M, K = 512, 1024
+    x = to_dev_bf16(o.make_activations(M, K, seed=3))
+    g_w = to_dev_bf16(o.make_gamma(K, seed=4))
+    d = [to_dev_bf16(o.bf16_round((1e-3 * np.random.default_rng(6 + i).standard_normal((M, K))).astype(np.float32)))
+         for i in range(3)]
+    d_sum, dx = torch.empty_like(x), torch.empty_like(x)
+    partials = torch.empty((M // 256, K), dtype=torch.float32, device="cuda")
+    dgamma = torch.empty(K, dtype=torch.float32, device="cuda")
+    res = {}
+
+    def step():
+        res["q"] = tkq.tk_fused_norm_quantize(x, g_w, 1e-5, False, True)
+        gemm.sum3_rmsnorm_bwd_out(d[0], d[1], d[2], x, g_w, res["q"][5], d_sum, dx, partials, dgamma)
+
+    g = _capture(step, step)
+    x2 = o.make_activations(M, K, seed=9)
+    x.copy_(to_dev_bf16(x2))
+    g.replay()
+    torch.cuda.synchronize()
+    q = [t.clone() for t in res["q"][:6]]
+    dx_g, dg_g = dx.clone(), dgamma.clone()
+    eager = tkq.tk_fused_norm_quantize(x, g_w, 1e-5, False, True)
+    gemm.sum3_rmsnorm_bwd_out(d[0], d[1], d[2], x, g_w, eager[5], d_sum, dx, partials, dgamma)
+    torch.cuda.synchronize()
+    for i in range(4):
+        assert torch.equal(q[i].view(torch.uint8), eager[i].view(torch.uint8)), i
+    assert torch.equal(q[5], eager[5]) and torch.equal(dx_g, dx) and torch.equal(dg_g, dgamma)
+    assert_status_ok()
