@@ -128,3 +128,60 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
             _lib.call("fp4b200_mxfp4_quantize", t.data_ptr(), M, H, int(mode), row_fp4[i].data_ptr(), row_sc[i].data_ptr(),
                       col_fp4[i].data_ptr(), col_sc[i].data_ptr(), _stream(dh))
     return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
+
+
+# ---- *_launch_inplace twins: the caller owns the outputs -----------------------------------------
+
+def _check_out(t, shape, fp4, name):
+    want = _FP4 if fp4 else torch.uint8
+    if (not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous() or t.dtype != want
+            or tuple(t.shape) != tuple(shape)):
+        raise RuntimeError(f"{name} must be a contiguous CUDA {'float4_e2m1fn_x2' if fp4 else 'uint8'} tensor of shape "
+                           f"{tuple(shape)}")
+
+
+def _check_operand_outs(row_fp4, row_sc, col_fp4, col_sc, M, K, lead=()):
+    _check_out(row_fp4, (*lead, M, K // 2), True, "row_fp4")
+    _check_out(row_sc, (*lead, M // 128, K // 128, 32, 16), False, "row_sc")
+    _check_out(col_fp4, (*lead, K, M // 2), True, "col_fp4")
+    _check_out(col_sc, (*lead, K // 128, M // 128, 32, 16), False, "col_sc")
+
+
+def mxfp4_quantize_row_and_col_launch_inplace(input, row_fp4, row_sc, col_fp4, col_sc, mode=0):
+    """tk_quantize.cu:3149-3229 — row and column quantisation into the caller's tensors; returns None."""
+    M, K = _check_bf16_2d(input, "input")
+    _check_operand_outs(row_fp4, row_sc, col_fp4, col_sc, M, K)
+    with torch.cuda.device(input.device):
+        _lib.call("fp4b200_mxfp4_quantize", input.data_ptr(), M, K, int(mode), row_fp4.data_ptr(), row_sc.data_ptr(),
+                  col_fp4.data_ptr(), col_sc.data_ptr(), _stream(input))
+
+
+def mxfp4_fused_silu_mul_quantize_row_and_col_launch_inplace(h1_raw, h3, row_fp4, row_sc, col_fp4, col_sc, mode=0):
+    """tk_quantize.cu:3231-3310 — operands of ``bf16(silu(h1_raw) * h3)`` into the caller's tensors; returns None.
+    The product itself is a temporary from torch's allocator (the reference keeps it in shared memory)."""
+    M, H = _check_bf16_2d(h1_raw, "h1_raw")
+    _same_shape_bf16(h1_raw, h3)
+    _check_operand_outs(row_fp4, row_sc, col_fp4, col_sc, M, H)
+    with torch.cuda.device(h1_raw.device):
+        h = torch.empty_like(h1_raw)
+        amax_sg = torch.empty(2, dtype=torch.float32, device=h1_raw.device)
+        st = _stream(h1_raw)
+        _lib.call("fp4b200_silu_mul_bf16", h1_raw.data_ptr(), h3.data_ptr(), h1_raw.numel(), h.data_ptr(),
+                  amax_sg.data_ptr(), st)
+        _lib.call("fp4b200_mxfp4_quantize", h.data_ptr(), M, H, int(mode), row_fp4.data_ptr(), row_sc.data_ptr(),
+                  col_fp4.data_ptr(), col_sc.data_ptr(), st)
+
+
+def mxfp4_fused_silu_deriv_quantize_split2_row_and_col_launch_inplace(dh, h3, h1_raw, row_fp4, row_sc, col_fp4, col_sc,
+                                                                      mode=0):
+    """tk_quantize.cu:4611-4700 — the stacked operands of dh1 and dh3 (leading dimension 2) into the caller's
+    tensors; returns None."""
+    from .tk_quant_v5 import tk_silu_deriv_split_bf16
+    M, H = _check_bf16_2d(dh, "dh")
+    _same_shape_bf16(dh, h3, h1_raw)
+    _check_operand_outs(row_fp4, row_sc, col_fp4, col_sc, M, H, lead=(2,))
+    dh1, dh3 = tk_silu_deriv_split_bf16(dh, h3, h1_raw)
+    with torch.cuda.device(dh.device):
+        for i, t in enumerate((dh1, dh3)):
+            _lib.call("fp4b200_mxfp4_quantize", t.data_ptr(), M, H, int(mode), row_fp4[i].data_ptr(), row_sc[i].data_ptr(),
+                      col_fp4[i].data_ptr(), col_sc[i].data_ptr(), _stream(dh))

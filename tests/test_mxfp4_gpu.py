@@ -109,3 +109,39 @@ def test_mxfp4_split2_dgrad_onepass(M):
         gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
                                                      [qw1[0]], [qw1[1]], d)
     assert_status_ok()
+
+
+def test_launch_inplace_twins_fill_the_callers_tensors():
+    """The *_launch_inplace functions write the same bytes into caller-owned tensors as their allocating twins
+    return, and reject tensors of the wrong shape or dtype."""
+    mxq = mod("mxfp4_quant_v4")
+    M, H = 256, 384
+    rng = np.random.default_rng(31)
+    mk = lambda s: to_dev_bf16(o.bf16_round((s * rng.standard_normal((M, H))).astype(np.float32)))
+    x, h3, dh = mk(1.0), mk(1.0), mk(1e-3)
+    u8 = dict(dtype=torch.uint8, device="cuda")
+
+    def outs(lead=()):
+        return (torch.empty((*lead, M, H // 2), **u8).view(torch.float4_e2m1fn_x2), torch.empty((*lead, M // 128, H // 128, 32, 16), **u8),
+                torch.empty((*lead, H, M // 2), **u8).view(torch.float4_e2m1fn_x2), torch.empty((*lead, H // 128, M // 128, 32, 16), **u8))
+
+    for mode in (0, 1, 2):
+        got = outs()
+        assert mxq.mxfp4_quantize_row_and_col_launch_inplace(x, *got, mode) is None
+        want = mxq.mxfp4_quantize_row_and_col(x, mode)
+        got2 = outs()
+        mxq.mxfp4_fused_silu_mul_quantize_row_and_col_launch_inplace(x, h3, *got2, mode)
+        want2 = mxq.mxfp4_fused_silu_mul_quantize_row_and_col(x, h3, mode)
+        got3 = outs((2,))
+        mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col_launch_inplace(dh, h3, x, *got3, mode)
+        want3 = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, x, mode)
+        torch.cuda.synchronize()
+        for g, w in ((got, want), (got2, want2), (got3, want3)):
+            for a, b in zip(g, w):
+                assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    bad = outs()
+    with pytest.raises(RuntimeError):
+        mxq.mxfp4_quantize_row_and_col_launch_inplace(x, bad[0], bad[1].view(M // 128, H // 128, 512), bad[2], bad[3], 1)
+    with pytest.raises(RuntimeError):
+        mxq.mxfp4_quantize_row_and_col_launch_inplace(x, bad[0].view(torch.uint8), bad[1], bad[2], bad[3], 1)
+    assert_status_ok()
