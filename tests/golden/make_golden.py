@@ -7,6 +7,8 @@ Run in the build container only (it needs the reference checkout):
 It loads ``transformer_engine/pytorch/custom_recipes/quantization_nvfp4.py`` (and its two
 small helper modules) straight from the reference tree, with stub parents injected into
 ``sys.modules`` because the compiled ``transformer_engine`` package is not installable here.
+A second fixture, ``rmsnorm_bwd_reference_golden.npz``, comes from the reference's PyTorch formula for the
+RMSNorm backward of the FFN block (one function executed out of ``fused_te_linear.py``).
 Nothing from the reference is copied into this repository: only seeded inputs (as bf16 bit
 patterns) and the bytes the reference produced for them are stored.
 """
@@ -70,10 +72,50 @@ def make_inputs(M, K, N, seed):
     return x.to(torch.bfloat16), w.to(torch.bfloat16)
 
 
+def load_function_source(path: str, name: str, namespace: dict):
+    """Executes one top-level function definition of a reference module (the module as a whole imports packages
+    that are not installed here) and returns it."""
+    import ast
+    with open(path) as f:
+        tree = ast.parse(f.read())
+    for node in tree.body:
+        if isinstance(node, ast.FunctionDef) and node.name == name:
+            mod = ast.Module(body=[node], type_ignores=[])
+            exec(compile(mod, path, "exec"), namespace)
+            return namespace[name]
+    raise RuntimeError(f"{name} not found in {path}")
+
+
+def make_rmsnorm_bwd_golden(root: str):
+    """RMSNorm backward of the FFN block through the reference's own PyTorch formula
+    (low_bits_training/quantization/fused_te_linear.py, _te_ffn_rmsnorm_backward_reference)."""
+    fn = load_function_source(os.path.join(root, "low_bits_training", "quantization", "fused_te_linear.py"),
+                              "_te_ffn_rmsnorm_backward_reference", {"torch": torch})
+    g = torch.Generator().manual_seed(77)
+    M, K = 160, 512
+    x = torch.randn(M, K, generator=g)
+    x[:, torch.randperm(K, generator=g)[:2]] *= 20.0
+    x = x.to(torch.bfloat16)
+    dy = (1e-3 * torch.randn(M, K, generator=g)).to(torch.bfloat16)
+    gamma = (1.0 + 0.1 * torch.randn(K, generator=g)).to(torch.bfloat16)
+    inv_rms = torch.rsqrt(x.float().pow(2).mean(dim=1) + 1e-5)
+    dx, dgamma = fn(dy, x, gamma, inv_rms)
+    out = {"x_bits": bf16_bits(x), "dy_bits": bf16_bits(dy), "gamma_bits": bf16_bits(gamma), "inv_rms": inv_rms.numpy(),
+           "dx_bits": bf16_bits(dx), "dgamma": dgamma.numpy()}
+    path = os.path.join(HERE, "rmsnorm_bwd_reference_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
+    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd"])
     args = ap.parse_args()
+    if args.which in ("all", "rmsnorm_bwd"):
+        make_rmsnorm_bwd_golden(args.reference)
+    if args.which == "rmsnorm_bwd":
+        return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]
 

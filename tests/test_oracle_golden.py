@@ -169,3 +169,23 @@ def test_rmsnorm_backward_oracle_block_sum_order_and_float64_agreement():
     mean = (d[0] * xh * g).sum(axis=1, keepdims=True) / K
     want = inv[:, None] * (d[0] * g - xh * mean) + res
     assert np.abs(r2["grad_input"] - want).max() <= 2.0 ** -7 * np.abs(want).max()
+
+
+def test_rmsnorm_backward_oracle_vs_the_references_pytorch_formula():
+    """The restated kernels against the reference's own PyTorch formula for the same step (fixture made by
+    tests/golden/make_golden.py from fused_te_linear.py): the formula orders its operations differently
+    (inv*proj - inv^3*x*dot, torch's summation), so dx agrees to one bf16 rounding step and dgamma to fp32 accuracy."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "rmsnorm_bwd_reference_golden.npz"))
+    x, dy, gamma = (o.bf16_from_bits(g[k]) for k in ("x_bits", "dy_bits", "gamma_bits"))
+    inv = g["inv_rms"]
+    want_dx = o.bf16_from_bits(g["dx_bits"])
+    zero = np.zeros_like(x)
+    got = o.rmsnorm_bwd_residual(dy, x, gamma, inv, zero)            # residual 0: dx itself
+    diff = np.abs(got["grad_input"] - want_dx)
+    ulp = np.maximum(np.abs(want_dx), 2.0 ** -126) * 2.0 ** -7        # one bf16 step at that magnitude
+    assert (diff <= ulp).all() and (diff == 0).mean() > 0.97
+    assert np.abs(got["dgamma"] - g["dgamma"]).max() <= 2e-5 * np.abs(g["dgamma"]).max()
+    s3 = o.sum3_rmsnorm_bwd(dy, zero, zero, x, gamma, inv)            # the 512-thread order, two zero streams
+    assert (np.abs(s3["grad_input"] - want_dx) <= ulp).all()
+    assert np.abs(s3["dgamma"] - g["dgamma"]).max() <= 2e-5 * np.abs(g["dgamma"]).max()
