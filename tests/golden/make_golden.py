@@ -8,7 +8,9 @@ It loads ``transformer_engine/pytorch/custom_recipes/quantization_nvfp4.py`` (an
 small helper modules) straight from the reference tree, with stub parents injected into
 ``sys.modules`` because the compiled ``transformer_engine`` package is not installable here.
 A second fixture, ``rmsnorm_bwd_reference_golden.npz``, comes from the reference's PyTorch formula for the
-RMSNorm backward of the FFN block (one function executed out of ``fused_te_linear.py``).
+RMSNorm backward of the FFN block (one function executed out of ``fused_te_linear.py``); a third,
+``scale_swizzle_reference_golden.npz``, from the torch helper of the reference's MXFP4 tests that lays scale
+bytes out in 512-byte tiles.
 Nothing from the reference is copied into this repository: only seeded inputs (as bf16 bit
 patterns) and the bytes the reference produced for them are stored.
 """
@@ -107,14 +109,29 @@ def make_rmsnorm_bwd_golden(root: str):
     print("wrote", path, {k: v.shape for k, v in out.items()})
 
 
+def make_scale_swizzle_golden(root: str):
+    """The 512-byte scale tile layout through the reference's own torch helper (scale_swizzle in
+    fp4_runtime/TK_quantisation/mxfp4_v1/test_mxfp4_quantize.py): distinct bytes in, swizzled tiles out."""
+    fn = load_function_source(os.path.join(root, "fp4_runtime", "TK_quantisation", "mxfp4_v1", "test_mxfp4_quantize.py"),
+                              "scale_swizzle", {"torch": torch})
+    g = torch.Generator().manual_seed(5)
+    logical = torch.randint(0, 256, (384, 12), generator=g, dtype=torch.int64).to(torch.uint8)   # 3 x 3 tiles
+    out = {"logical": logical.numpy(), "swizzled": fn(logical).numpy()}
+    path = os.path.join(HERE, "scale_swizzle_reference_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
-    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd"])
+    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle"])
     args = ap.parse_args()
     if args.which in ("all", "rmsnorm_bwd"):
         make_rmsnorm_bwd_golden(args.reference)
-    if args.which == "rmsnorm_bwd":
+    if args.which in ("all", "scale_swizzle"):
+        make_scale_swizzle_golden(args.reference)
+    if args.which in ("rmsnorm_bwd", "scale_swizzle"):
         return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

@@ -189,3 +189,12 @@ def test_rmsnorm_backward_oracle_vs_the_references_pytorch_formula():
     s3 = o.sum3_rmsnorm_bwd(dy, zero, zero, x, gamma, inv)            # the 512-thread order, two zero streams
     assert (np.abs(s3["grad_input"] - want_dx) <= ulp).all()
     assert np.abs(s3["dgamma"] - g["dgamma"]).max() <= 2e-5 * np.abs(g["dgamma"]).max()
+
+
+def test_scale_swizzle_matches_the_references_torch_helper():
+    """The 512-byte scale tile layout against the reference's own torch helper (scale_swizzle of its MXFP4 tests,
+    run by tests/golden/make_golden.py on random bytes of a 3 x 3 tile grid)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "scale_swizzle_reference_golden.npz"))
+    assert np.array_equal(o.swizzle_scales(g["logical"]).reshape(g["swizzled"].shape), g["swizzled"])
+    assert np.array_equal(o.unswizzle_scales(g["swizzled"].reshape(3, 3, 512), 384, 12), g["logical"])
