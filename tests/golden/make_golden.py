@@ -10,7 +10,8 @@ small helper modules) straight from the reference tree, with stub parents inject
 A second fixture, ``rmsnorm_bwd_reference_golden.npz``, comes from the reference's PyTorch formula for the
 RMSNorm backward of the FFN block (one function executed out of ``fused_te_linear.py``); a third,
 ``scale_swizzle_reference_golden.npz``, from the torch helper of the reference's MXFP4 tests that lays scale
-bytes out in 512-byte tiles.
+bytes out in 512-byte tiles; a fourth, ``mxfp4_reference_golden.npz``, from the MXFP4 emulation
+(``custom_recipes/quantization_mxfp4.py``).
 Nothing from the reference is copied into this repository: only seeded inputs (as bf16 bit
 patterns) and the bytes the reference produced for them are stored.
 """
@@ -50,7 +51,7 @@ def load_reference(root: str):
     qt.QuantizedTensorStorage = QuantizedTensorStorage
     qt.Quantizer = Quantizer
     mods = {}
-    for short in ("utils", "quantization", "quantization_nvfp4"):
+    for short in ("utils", "quantization", "quantization_nvfp4", "quantization_mxfp4"):
         full = f"transformer_engine.pytorch.custom_recipes.{short}"
         spec = importlib.util.spec_from_file_location(full, os.path.join(base, short + ".py"))
         mod = importlib.util.module_from_spec(spec)
@@ -122,16 +123,40 @@ def make_scale_swizzle_golden(root: str):
     print("wrote", path, {k: v.shape for k, v in out.items()})
 
 
+def make_mxfp4_golden(root: str):
+    """MXFP4 (32-element blocks, E8M0 scales, no tensor scale) through the reference's CPU emulation
+    MXFP4QuantizerRef (custom_recipes/quantization_mxfp4.py), decode-centric, and its block-wise qgemm with the
+    1/36 factor.  The emulation rounds the scale exponent in the log domain (round(log2(amax))); the CUDA kernels'
+    RTE mode rounds the mantissa: the two agree except for block maxima in [sqrt(2), 1.5) x 2^k."""
+    mods = load_reference(root)
+    qm, utils, quantization = mods["quantization_mxfp4"], mods["utils"], mods["quantization"]
+    M, K, N = 256, 512, 128
+    x, w = make_inputs(M, K, N, 4242)
+    q = qm.MXFP4QuantizerRef(dtype=utils.Fp4Formats.E2M1, rowwise=True, columnwise=True, quant_tile_shape=(1, 32),
+                             use_global_scale=False, encode_centric=False)
+    qx, qw = q.quantize(x), q.quantize(w)
+    y = q.qgemm(qx.data, qw.data, quantization.MMParams(), torch.float32, qx.scale, qw.scale)
+    out = {"x_bits": bf16_bits(x), "w_bits": bf16_bits(w),
+           "x_data": qx.data.numpy(), "x_scale": qx.scale.view(torch.uint8).numpy(),
+           "x_data_t": qx.data_t.numpy(), "x_scale_t": qx.scale_t.view(torch.uint8).numpy(),
+           "w_data": qw.data.numpy(), "w_scale": qw.scale.view(torch.uint8).numpy(), "qgemm_f32": y.numpy()}
+    path = os.path.join(HERE, "mxfp4_reference_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
-    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle"])
+    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4"])
     args = ap.parse_args()
     if args.which in ("all", "rmsnorm_bwd"):
         make_rmsnorm_bwd_golden(args.reference)
     if args.which in ("all", "scale_swizzle"):
         make_scale_swizzle_golden(args.reference)
-    if args.which in ("rmsnorm_bwd", "scale_swizzle"):
+    if args.which in ("all", "mxfp4"):
+        make_mxfp4_golden(args.reference)
+    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4"):
         return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

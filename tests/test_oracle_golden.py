@@ -198,3 +198,31 @@ def test_scale_swizzle_matches_the_references_torch_helper():
     g = np.load(os.path.join(os.path.dirname(__file__), "golden", "scale_swizzle_reference_golden.npz"))
     assert np.array_equal(o.swizzle_scales(g["logical"]).reshape(g["swizzled"].shape), g["swizzled"])
     assert np.array_equal(o.unswizzle_scales(g["swizzled"].reshape(3, 3, 512), 384, 12), g["logical"])
+
+
+def test_mxfp4_oracle_vs_the_references_cpu_emulation():
+    """MXFP4 against the reference's CPU emulation (MXFP4QuantizerRef, decode-centric, no tensor scale; fixture made
+    by tests/golden/make_golden.py).  The emulation rounds the scale exponent in the log domain, the CUDA kernels'
+    RTE mode (restated by the oracle's mode 0) rounds the mantissa: scale bytes and codes must be identical for every
+    block whose maximum is outside [sqrt(2), 1.5] x 2^k, in both orientations; the block-scaled product of the
+    emulation's own bytes (1/36 factor) must be reproduced exactly."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "mxfp4_reference_golden.npz"))
+    x = o.bf16_from_bits(g["x_bits"])
+    M, K = x.shape
+    ref = o.mxfp4_quantize_row_and_col(x, 0)
+    for mat, codes, sc, want_codes, want_sc in ((x, ref["row_fp4"], ref["row_sc_logical"], g["x_data"], g["x_scale"]),
+                                                (np.ascontiguousarray(x.T), ref["col_fp4"], ref["col_sc_logical"],
+                                                 g["x_data_t"], g["x_scale_t"])):
+        r, c = mat.shape
+        amax = np.abs(mat).reshape(r, c // 32, 32).max(axis=-1)
+        mant = amax / 2.0 ** np.floor(np.log2(amax))
+        safe = ~((mant >= np.sqrt(2.0) - 1e-6) & (mant <= 1.5))
+        assert safe.mean() > 0.9
+        assert np.array_equal(sc[safe], want_sc[safe])
+        assert (sc[~safe] <= want_sc[~safe]).all() and (want_sc[~safe] - sc[~safe] <= 1).all()   # log rounding goes up first
+        got = o.unpack_fp4(codes).reshape(r, c // 32, 32)
+        want = o.unpack_fp4(want_codes).reshape(r, c // 32, 32)
+        assert np.array_equal(got[safe], want[safe])
+    y = o.mxfp4_gemm_fp32(g["x_data"], g["x_scale"], g["w_data"], g["w_scale"])
+    assert np.array_equal(y, g["qgemm_f32"])
