@@ -11,7 +11,8 @@ A second fixture, ``rmsnorm_bwd_reference_golden.npz``, comes from the reference
 RMSNorm backward of the FFN block (one function executed out of ``fused_te_linear.py``); a third,
 ``scale_swizzle_reference_golden.npz``, from the torch helper of the reference's MXFP4 tests that lays scale
 bytes out in 512-byte tiles; a fourth, ``mxfp4_reference_golden.npz``, from the MXFP4 emulation
-(``custom_recipes/quantization_mxfp4.py``).
+(``custom_recipes/quantization_mxfp4.py``); a fifth, ``tk_gemm_quantize_reference_golden.npz``, from the torch
+reference of the GEMM module's own tile quantiser (its ``test_quantize.py``).
 Nothing from the reference is copied into this repository: only seeded inputs (as bf16 bit
 patterns) and the bytes the reference produced for them are stored.
 """
@@ -145,10 +146,35 @@ def make_mxfp4_golden(root: str):
     print("wrote", path, {k: v.shape for k, v in out.items()})
 
 
+def make_tk_gemm_quantize_golden(root: str):
+    """The GEMM module's own tile quantiser through the torch reference of its test script
+    (torch_nvfp4_quantize and scale_swizzle in ThunderKittens/kernels/gemm/nvfp4_b200/test_quantize.py).  That
+    reference calls the module's fp32 -> packed E2M1 cast for its last step; the reference's CPU emulation of the
+    same cast (cast_to_fp4x2 of custom_recipes/quantization_nvfp4.py) stands in for it here."""
+    mods = load_reference(root)
+    cast = mods["quantization_nvfp4"].cast_to_fp4x2
+    path = os.path.join(root, "fp4_runtime", "ThunderKittens", "kernels", "gemm", "nvfp4_b200", "test_quantize.py")
+    ns = {"torch": torch, "fp32_to_fp4x2": lambda v: cast(v.clamp(-6.0, 6.0))}
+    quant = load_function_source(path, "torch_nvfp4_quantize", ns)
+    swz = load_function_source(path, "scale_swizzle", ns)
+    x, _ = make_inputs(256, 512, 128, 99)
+    out = {"a_bits": bf16_bits(x)}
+    for scale_2d in (False, True):
+        fp4, sc, sg = quant(x, scale_2d)
+        tag = "2d" if scale_2d else "1d"
+        out[f"{tag}_fp4"] = fp4.numpy()
+        out[f"{tag}_sc"] = sc.view(torch.uint8).numpy()
+        out[f"{tag}_sc_swizzled"] = swz(sc).view(torch.uint8).numpy()
+        out[f"{tag}_sg"] = sg.numpy()
+    p = os.path.join(HERE, "tk_gemm_quantize_reference_golden.npz")
+    np.savez_compressed(p, **out)
+    print("wrote", p, {k: v.shape for k, v in out.items()})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
-    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4"])
+    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize"])
     args = ap.parse_args()
     if args.which in ("all", "rmsnorm_bwd"):
         make_rmsnorm_bwd_golden(args.reference)
@@ -156,7 +182,9 @@ def main():
         make_scale_swizzle_golden(args.reference)
     if args.which in ("all", "mxfp4"):
         make_mxfp4_golden(args.reference)
-    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4"):
+    if args.which in ("all", "tk_gemm_quantize"):
+        make_tk_gemm_quantize_golden(args.reference)
+    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize"):
         return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

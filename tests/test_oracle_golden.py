@@ -226,3 +226,27 @@ def test_mxfp4_oracle_vs_the_references_cpu_emulation():
         assert np.array_equal(got[safe], want[safe])
     y = o.mxfp4_gemm_fp32(g["x_data"], g["x_scale"], g["w_data"], g["w_scale"])
     assert np.array_equal(y, g["qgemm_f32"])
+
+
+def test_gemm_module_tile_quantiser_vs_the_references_torch_function():
+    """The GEMM module's own quantiser (restated from its CUDA source) against the torch reference of its test
+    script (fixture made by tests/golden/make_golden.py): scale bytes, their 512-byte tile layout and the tensor
+    scale are identical; that reference forms its multipliers as 1 / (scale * (1 / (2688 / amax))) where the kernel
+    uses 1 / (scale * (amax / 2688)), so a code next to a rounding boundary may land on the neighbouring value
+    (the reference's script prints such differences rather than asserting)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "tk_gemm_quantize_reference_golden.npz"))
+    a = o.bf16_from_bits(g["a_bits"])
+    M, N = a.shape
+    for tag, scale_2d in (("1d", False), ("2d", True)):
+        r = o.tk_nvfp4_quantize(a, scale_2d)
+        assert np.array_equal(r["sc_logical"], g[tag + "_sc"])
+        assert np.array_equal(r["sc"].reshape(g[tag + "_sc_swizzled"].shape), g[tag + "_sc_swizzled"])
+        assert abs(float(r["sg"]) - float(g[tag + "_sg"][0])) <= 2.0 ** -23 * float(r["sg"])
+        mine, ref = o.unpack_fp4(r["fp4"]), o.unpack_fp4(g[tag + "_fp4"])
+        same = mine == ref
+        assert same.mean() > 0.995
+        vm, vr = o.E2M1_TO_F32[mine[~same]], o.E2M1_TO_F32[ref[~same]]
+        order = np.array(sorted(set(np.abs(o.E2M1_TO_F32).tolist())))
+        step = np.abs(np.searchsorted(order, np.abs(vm)) - np.searchsorted(order, np.abs(vr)))
+        assert (np.sign(vm) * np.sign(vr) >= 0).all() and (step <= 1).all()
