@@ -12,7 +12,9 @@ RMSNorm backward of the FFN block (one function executed out of ``fused_te_linea
 ``scale_swizzle_reference_golden.npz``, from the torch helper of the reference's MXFP4 tests that lays scale
 bytes out in 512-byte tiles; a fourth, ``mxfp4_reference_golden.npz``, from the MXFP4 emulation
 (``custom_recipes/quantization_mxfp4.py``); a fifth, ``tk_gemm_quantize_reference_golden.npz``, from the torch
-reference of the GEMM module's own tile quantiser (its ``test_quantize.py``).
+reference of the GEMM module's own tile quantiser (its ``test_quantize.py``); a sixth,
+``rht_and_norm_reference_golden.npz``, from the emulation's Hadamard transform and the PyTorch formula of the
+forward RMSNorm.
 Nothing from the reference is copied into this repository: only seeded inputs (as bf16 bit
 patterns) and the bytes the reference produced for them are stored.
 """
@@ -171,10 +173,35 @@ def make_tk_gemm_quantize_golden(root: str):
     print("wrote", p, {k: v.shape for k, v in out.items()})
 
 
+def make_rht_and_norm_golden(root: str):
+    """The 16-point Hadamard transform of the reference's CPU emulation (NVFP4QuantizerRef._apply_rht, with and
+    without its fixed sign vector) and the forward RMSNorm of the FFN block in the reference's PyTorch formula
+    (_te_ffn_rmsnorm_forward_reference in fused_te_linear.py)."""
+    mods = load_reference(root)
+    qn, utils = mods["quantization_nvfp4"], mods["utils"]
+    x, _ = make_inputs(64, 256, 16, 31)
+    out = {"x_bits": bf16_bits(x)}
+    for sign in (False, True):
+        q = qn.NVFP4QuantizerRef(dtype=utils.Fp4Formats.E2M1, rowwise=True, columnwise=True, quant_tile_shape=(1, 16),
+                                 with_rht=True, with_random_sign_mask=sign)
+        out["rht_signed_bits" if sign else "rht_plain_bits"] = bf16_bits(q._apply_rht(x))
+    fwd = load_function_source(os.path.join(root, "low_bits_training", "quantization", "fused_te_linear.py"),
+                               "_te_ffn_rmsnorm_forward_reference", {"torch": torch})
+    g = torch.Generator().manual_seed(32)
+    gamma = (1.0 + 0.1 * torch.randn(256, generator=g)).to(torch.bfloat16)
+    normed, inv_rms = fwd(x, gamma, 1e-5)
+    out["gamma_bits"] = bf16_bits(gamma)
+    out["normed_bits"] = bf16_bits(normed)
+    out["inv_rms"] = inv_rms.squeeze(-1).numpy()
+    path = os.path.join(HERE, "rht_and_norm_reference_golden.npz")
+    np.savez_compressed(path, **out)
+    print("wrote", path, {k: v.shape for k, v in out.items()})
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
-    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize"])
+    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm"])
     args = ap.parse_args()
     if args.which in ("all", "rmsnorm_bwd"):
         make_rmsnorm_bwd_golden(args.reference)
@@ -184,7 +211,9 @@ def main():
         make_mxfp4_golden(args.reference)
     if args.which in ("all", "tk_gemm_quantize"):
         make_tk_gemm_quantize_golden(args.reference)
-    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize"):
+    if args.which in ("all", "rht_and_norm"):
+        make_rht_and_norm_golden(args.reference)
+    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm"):
         return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

@@ -250,3 +250,17 @@ def test_gemm_module_tile_quantiser_vs_the_references_torch_function():
         order = np.array(sorted(set(np.abs(o.E2M1_TO_F32).tolist())))
         step = np.abs(np.searchsorted(order, np.abs(vm)) - np.searchsorted(order, np.abs(vr)))
         assert (np.sign(vm) * np.sign(vr) >= 0).all() and (step <= 1).all()
+
+
+def test_hadamard_transform_and_forward_rmsnorm_vs_the_reference():
+    """The 16-point Hadamard transform (with and without the fixed sign vector) against the reference emulation's
+    _apply_rht, and the forward RMSNorm against the reference's PyTorch formula (fixture made by
+    tests/golden/make_golden.py): transform outputs and normalised values bit for bit, 1/rms to fp32 rounding."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(__file__), "golden", "rht_and_norm_reference_golden.npz"))
+    x = o.bf16_from_bits(g["x_bits"])
+    assert np.array_equal(o.fwht16_bf16(x), o.bf16_from_bits(g["rht_plain_bits"]))
+    assert np.array_equal(o.fwht16_bf16(x, o.rht_fixed_signs()), o.bf16_from_bits(g["rht_signed_bits"]))
+    gamma = o.bf16_from_bits(g["gamma_bits"])
+    assert np.abs(o.rmsnorm_inv_rms(x, 1e-5) / g["inv_rms"] - 1).max() <= 2.5e-7
+    assert np.array_equal(o.rmsnorm_apply(x, g["inv_rms"], gamma), o.bf16_from_bits(g["normed_bits"]))
