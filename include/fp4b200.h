@@ -230,6 +230,14 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
 int fp4b200_row_rms_reduce(const float* row_rms_partial, int64_t M, int64_t partial_cols, int64_t hidden_size,
                            float eps, float* inv_rms, void* stream);
 
+/* One group of tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, ...) (nvfp4_v5/tk_quantize.cu:6425-6835):
+ * amax + quantisation of one [M, K] input whose row-wise codes go into a column slice of a wider code matrix
+ * (row_fp4 points at the slice's first byte, row_pitch_bytes is the wide matrix's pitch); its column-wise codes are a
+ * contiguous row block of the transposed matrix.  Per-group tensor amax, as the reference. */
+int fp4b200_nvfp4_quantize_for_gemm_into(const void* x_bf16, int64_t M, int64_t K, int return_transpose, int encode_centric,
+                                         void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4, void* col_sc,
+                                         float* amax_sg, void* stream);
+
 /* tk_quantize_nhsd_wo_for_gemm(input, return_transpose, encode_centric) (nvfp4_v5/tk_quantize.cu:3006-3134):
  * the attention output in its native [B, H, S, D = 64] layout, quantised as the matrix [M = B*S, K = H*D] the
  * output projection consumes (element (b*S + s, h*64 + d) = input[b, h, s, d]) without a transposing copy.

@@ -70,11 +70,12 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st,
 // kernel (it fetches its first chunks while that kernel drains), reduces the partials itself and
 // writes amax_out[0] = amax, amax_out[1] = amax/2688 (when non-null).  sg_out (when non-null)
 // receives amax_row/2688 in both cases.  nhsd_seq > 0: x is laid out [B, nhsd_heads, nhsd_seq, 64] and
-// stands for the matrix [M = B * nhsd_seq, K = nhsd_heads * 64] (plain quantisation only).
+// stands for the matrix [M = B * nhsd_seq, K = nhsd_heads * 64]; row_pitch_bytes > 0: row_fp4 is a column slice
+// of a wider code matrix with that pitch (both: plain quantisation only).
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
                     bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4, void* row_sc,
                     void* col_fp4, void* col_sc, float* sg_out, bool reverse, cudaStream_t st, bool weight_2d = false,
                     const QuantOpt* opt = nullptr, const AmaxPartials* partials = nullptr, float* amax_out = nullptr,
-                    int nhsd_heads = 0, int nhsd_seq = 0);
+                    int nhsd_heads = 0, int nhsd_seq = 0, int64_t row_pitch_bytes = 0);
 
 }  // namespace fp4b200

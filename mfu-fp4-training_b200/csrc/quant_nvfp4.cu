@@ -400,6 +400,7 @@ struct QuantArgs {
   int chunks_m, chunks_k;
   int reverse;             // walk chunks from the last row block to the first
   int nhsd_heads, nhsd_seq; // > 0: x is [B, heads, seq, 64] and the matrix is [B*seq, heads*64] (strip kernel only)
+  int row_pitch_bytes;     // > 0: pitch of the row-wise code matrix (it is a column slice of a wider one; strip kernel only)
   // ---- OPT instantiations only (stochastic rounding / 16-point Hadamard transform) ----
   int opt_sr_row, opt_sr_col;   // data stochastic rounding of the row pass / of the column pass
   int opt_row_per_stage;   // random words per 64x64 stage in the row pass's stream: 16 (launch with a column pass) or 8
@@ -1295,7 +1296,8 @@ static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStr
   tmap_row = tmap;   // launches without row-wise outputs never use it
   if (args.row_fp4 != nullptr) {
     if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
-                              (uint64_t)args.K / 2, kStripCols / 2, kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+                              args.row_pitch_bytes > 0 ? (uint64_t)args.row_pitch_bytes : (uint64_t)args.K / 2, kStripCols / 2,
+                              kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
   }
   auto kern = nvfp4_quantize_strip_kernel<EC, NORM, OPT>;
@@ -1320,7 +1322,7 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
                            bool encode_centric, const float* inv_rms, const void* gamma, void* row_fp4,
                            void* row_sc, void* col_fp4, void* col_sc, float* sg_out, bool reverse,
                            cudaStream_t st, bool weight_2d, const QuantOpt* opt, const AmaxPartials* partials,
-                           float* amax_out, int nhsd_heads, int nhsd_seq) {
+                           float* amax_out, int nhsd_heads, int nhsd_seq, int64_t row_pitch_bytes) {
   const bool behind_pass1 = partials != nullptr;
   CUtensorMap tmap;
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
@@ -1347,7 +1349,10 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.chunks_m = (int)(M / kChunk); a.chunks_k = (int)(K / kChunk);
   a.reverse = reverse ? 1 : 0;
   a.nhsd_heads = nhsd_heads; a.nhsd_seq = nhsd_seq;
+  a.row_pitch_bytes = (int)row_pitch_bytes;
   const bool norm = inv_rms != nullptr;
+  if (row_pitch_bytes > 0 && (opt != nullptr || weight_2d || !strip_kernel_applies(a, norm)))
+    return set_error("row codes into a wider matrix: plain quantisation into 16-byte aligned outputs only");
   if (nhsd_seq > 0 && (opt != nullptr || weight_2d || norm || !strip_kernel_applies(a, false)))
     return set_error("head-major input: plain quantisation into 16-byte aligned outputs only");
   if (opt != nullptr) {
@@ -1486,6 +1491,24 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
   return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
                          return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr,
                          true, (cudaStream_t)stream, false, nullptr, &part, amax_sg);
+}
+
+int fp4b200_nvfp4_quantize_for_gemm_into(const void* x_bf16, int64_t M, int64_t K, int return_transpose, int encode_centric,
+                                         void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4, void* col_sc,
+                                         float* amax_sg, void* stream) {
+  const char* fn = "nvfp4_quantize_for_gemm_into";
+  if (int rc = check_quant_shapes(x_bf16, M, K, fn)) return rc;
+  if (row_fp4 == nullptr || row_sc == nullptr || amax_sg == nullptr)
+    return set_error("%s: row_fp4, row_sc and amax_sg are required", fn);
+  if (return_transpose && (col_fp4 == nullptr || col_sc == nullptr))
+    return set_error("%s: return_transpose needs col_fp4 and col_sc", fn);
+  if (row_pitch_bytes < K / 2 || (row_pitch_bytes % 16) != 0 || row_pitch_bytes > INT32_MAX)
+    return set_error("%s: the row pitch must be a multiple of 16 bytes and at least K/2 (got %lld)", fn, (long long)row_pitch_bytes);
+  AmaxPartials part;
+  if (int rc = launch_amax(x_bf16, M * K, amax_sg, (cudaStream_t)stream, nullptr, &part)) return rc;
+  return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
+                         return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr, true,
+                         (cudaStream_t)stream, false, nullptr, &part, amax_sg, 0, 0, row_pitch_bytes);
 }
 
 int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int64_t S, int64_t D, int return_transpose,

@@ -94,6 +94,63 @@ def tk_quantize_nhsd_wo_for_gemm(input, return_transpose, encode_centric=True):
             col_sc.view(_E4M3) if return_transpose else col_sc, sg, sg, amax_sg, sync_buf)
 
 
+def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochastic_rounding=False, rng_seed=0,
+                                           rng_subsequence=0, data_sr_axes="both"):
+    """tk_quantize.cu:6425-6835 — three gradient streams [M, n_g] (the attention side's dQ, dK, dV), each quantised
+    with its own tensor amax (encode-centric, round-to-nearest) straight into the column slices of one row-wise code
+    matrix [M, N/2] and the row blocks of one column-wise code matrix [N, M/2], N = n_0 + n_1 + n_2.  Returns the
+    reference's 15-tuple: (row code views, row scales, sg [3], column code views, column scales, full row codes,
+    row scales concatenated along the block dimension, full column codes, column scales concatenated, three empty
+    descriptor / barrier tensors' places, amax [3], ...).  Stochastic rounding of this producer is not built."""
+    if data_stochastic_rounding:
+        raise RuntimeError("tk_group_quantize_dim1_split3_for_gemm: data stochastic rounding is not built")
+    inputs = [input0, input1, input2]
+    for t in inputs:
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
+            raise RuntimeError("split3 inputs must be CUDA bf16 matrices contiguous along the inner dimension")
+        if t.device != input0.device:
+            raise RuntimeError("split3 inputs must be on the same CUDA device")
+    M = int(input0.shape[0])
+    if any(int(t.shape[0]) != M for t in inputs):
+        raise RuntimeError("split3 inputs must share the same row count")
+    splits = [int(t.shape[1]) for t in inputs]
+    n_total = sum(splits)
+    if M % 128 or any(n % 128 for n in splits):
+        raise RuntimeError("M and every split width must be multiples of 128")
+    dev = input0.device
+    u8 = dict(dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        fp4_row_full = torch.empty((M, n_total // 2), **u8)
+        fp4_col_full = torch.empty((n_total, M // 2), **u8)
+        amax_sg = torch.empty((3, 2), dtype=torch.float32, device=dev)
+        sc_row, sc_col = [], []
+        off = 0
+        for g, (t, n) in enumerate(zip(inputs, splits)):
+            x = t if t.is_contiguous() else t.contiguous()   # the amax pass reads a dense buffer
+            sc_row.append(torch.empty((M // 128, n // 64, 512), **u8))
+            sc_col.append(torch.empty((n // 128, M // 64, 512), **u8))
+            _lib.call("fp4b200_nvfp4_quantize_for_gemm_into", x.data_ptr(), M, n, 1, 1, fp4_row_full.data_ptr() + off // 2,
+                      n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2), sc_col[g].data_ptr(),
+                      amax_sg[g].data_ptr(), _stream(input0))
+            off += n
+        sg_per_group = amax_sg[:, 1].contiguous()
+        amax_tensor = amax_sg[:, 0].contiguous()
+        fp4_row_list, fp4_col_list = [], []
+        off = 0
+        for n in splits:
+            fp4_row_list.append(fp4_row_full.narrow(1, off // 2, n // 2))
+            fp4_col_list.append(fp4_col_full.narrow(0, off, n).view(_FP4))
+            off += n
+        sc_row_cat = torch.cat(sc_row, 1).view(_E4M3)
+        sc_col_cat = torch.cat(sc_col, 0).view(_E4M3)
+        empty_u8 = torch.empty(0, **u8)
+        empty_i32 = torch.empty(0, dtype=torch.int32, device=dev)
+    return ([t for t in fp4_row_list], [t.view(_E4M3) for t in sc_row], sg_per_group, fp4_col_list,
+            [t.view(_E4M3) for t in sc_col], fp4_row_full.view(_FP4), sc_row_cat, fp4_col_full.view(_FP4), sc_col_cat,
+            empty_u8, torch.empty(0, dtype=torch.uint8), torch.empty(0, dtype=torch.int64, device=dev), amax_tensor,
+            torch.zeros(6, dtype=torch.int32, device=dev), empty_i32)
+
+
 def tk_quantize_weight_2d(input):
     """tk_quantize.cu:2445-2555 — 16x16-tile weight quantisation, returns
     (row_fp4, row_sc, col_fp4, col_sc, sg, sg)."""

@@ -203,3 +203,38 @@ def test_quantize_nhsd_wo_equals_quantising_the_permuted_tensor(shape, ec):
     with pytest.raises(RuntimeError):
         tkq.tk_quantize_nhsd_wo_for_gemm(to_dev_bf16(np.zeros((1, 2, 128, 32), np.float32)), True, ec)   # head_dim 32
     assert_status_ok()
+
+
+def test_split3_group_quantiser_writes_slices_of_the_concatenated_operands():
+    """Three gradient streams of different widths (one of them a strided view), each with its own tensor amax: the
+    slices of the concatenated code matrices and the per-group scales equal the single-input quantiser's bytes,
+    which the oracle checks; the concatenated scale tensors are the per-group ones side by side."""
+    tkq = mod("tk_quant_v5")
+    M, splits = 256, (512, 128, 256)
+    xs = [o.make_activations(M, n, seed=60 + i, scale=10.0 ** (-i)) for i, n in enumerate(splits)]
+    wide = to_dev_bf16(np.concatenate([xs[1], xs[1]], axis=1))
+    devs = [to_dev_bf16(xs[0]), wide[:, :splits[1]], to_dev_bf16(xs[2])]        # the middle input has row stride 256
+    out = tkq.tk_group_quantize_dim1_split3_for_gemm(*devs)
+    torch.cuda.synchronize()
+    assert len(out) == 15
+    rows, row_sc, sg, cols, col_sc, row_full, row_sc_cat, col_full, col_sc_cat = out[:9]
+    n_total = sum(splits)
+    assert tuple(row_full.shape) == (M, n_total // 2) and tuple(col_full.shape) == (n_total, M // 2)
+    off = 0
+    for g, (x, n) in enumerate(zip(xs, splits)):
+        ref = o.nvfp4_quantize_for_gemm(x, True, True)
+        assert np.array_equal(u8(rows[g]), ref["row_fp4"]) and np.array_equal(u8(cols[g]), ref["col_fp4"])
+        assert np.array_equal(u8(row_sc[g]).reshape(ref["row_sc"].shape), ref["row_sc"])
+        assert np.array_equal(u8(col_sc[g]).reshape(ref["col_sc"].shape), ref["col_sc"])
+        assert sg[g].item() == ref["sg"] and out[12][g].item() == ref["amax"]
+        assert np.array_equal(u8(row_full)[:, off // 2:(off + n) // 2], ref["row_fp4"])
+        assert np.array_equal(u8(col_full)[off:off + n], ref["col_fp4"])
+        assert rows[g].data_ptr() == row_full.data_ptr() + off // 2                # views of the full buffers
+        off += n
+    assert np.array_equal(u8(row_sc_cat), np.concatenate([u8(t) for t in row_sc], axis=1))
+    assert np.array_equal(u8(col_sc_cat), np.concatenate([u8(t) for t in col_sc], axis=0))
+    with pytest.raises(RuntimeError):
+        tkq.tk_group_quantize_dim1_split3_for_gemm(*devs, True, 1, 0, "row")       # SR of this producer: not built
+    with pytest.raises(RuntimeError):
+        tkq.tk_group_quantize_dim1_split3_for_gemm(devs[0], devs[1], to_dev_bf16(xs[2][:128]))
+    assert_status_ok()
