@@ -246,6 +246,18 @@ int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int
                                    int encode_centric, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
                                    float* amax_sg, void* stream);
 
+/* nvfp4_grouped_gemm_rope_live64 / _rope_packed_cat / _rope_packed_split (nvfp4_b200_gemm.cu:1338-1441; epilogue
+ * nvfp4_rope_epilogue.cuh:104-161): the grouped GEMM of the fused QKV projection with the rotary embedding applied in
+ * the epilogue to the output columns [0, rope_cols) (Q and K): after the accumulator has been multiplied by the tensor
+ * scales (and, with round_input_bf16, rounded to bf16), neighbouring columns (2i, 2i+1) of token row r are rotated by
+ * rope_cs[r mod rope_seq_len, (col mod rope_head_dim) / 2] = (cos, sin), then rounded to bf16.  Outputs as in
+ * fp4b200_nvfp4_grouped_gemm (1 to 3 bf16 matrices split by column range, each a multiple of 256 wide);
+ * rope_seq_len and rope_head_dim powers of two, rope_cs fp32 [rope_seq_len, rope_head_dim/2, 2]. */
+int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                                    const float* B_sg_per_tile, int n_out, void* const* D, const int64_t* D_cols,
+                                    const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim, int64_t rope_cols,
+                                    int round_input_bf16, int64_t M, int64_t N, int64_t K, void* stream);
+
 /* ---- RMSNorm backward behind the dgrad GEMMs ----------------------------------------------- */
 
 /* sum3_rmsnorm_bwd_out(d0, d1, d2, input, norm_weight, inv_rms, d_sum, grad_input, dgamma_partials, dgamma)

@@ -82,6 +82,12 @@ struct GemmArgs {
   const __nv_bfloat16* residual;  // optional [M, N] bf16 added after the bf16 rounding
   int residual_ld;
   const float* accum_f32;   // optional [M, N] fp32 partial sum added to acc*scale before the output rounding
+  // optional rotary embedding of the column range [0, rope_col_end) (the Q and K parts of a fused QKV projection)
+  // in the bf16 epilogue: pairs of neighbouring columns rotated by the (cos, sin) entry of their token and
+  // position inside the head (reference: nvfp4_rope_epilogue.cuh:104-161)
+  const float2* rope_cs;    // [seq_len, head_dim/2] (cos, sin)
+  int rope_seq_mask, rope_pair_dim, rope_head_mask, rope_col_end;
+  int rope_round_bf16;      // round the scaled accumulator to bf16 before the rotation ("packed" forms)
   int M, N, K;              // K = sum of the segments
   int* status;
 };
@@ -239,9 +245,25 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMa
         }
       } else {
         uint32_t o[16];
+        if (g.rope_cs != nullptr && col0 + c < g.rope_col_end) {
+          // even' = fma(x, cos, -(y*sin)), odd' = fma(y, cos, x*sin): the contraction nvcc applies to the
+          // reference's x*cos - y*sin and y*cos + x*sin
+          const float2* cs_row = g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim;
 #pragma unroll
-        for (int q = 0; q < 16; ++q)
-          o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs_out, __uint_as_float(r[2 * q + 1]) * gs_out);
+          for (int q = 0; q < 16; ++q) {
+            float x = __fmul_rn(__uint_as_float(r[2 * q]), gs_out), y = __fmul_rn(__uint_as_float(r[2 * q + 1]), gs_out);
+            if (g.rope_round_bf16) {
+              x = __bfloat162float(__float2bfloat16_rn(x));
+              y = __bfloat162float(__float2bfloat16_rn(y));
+            }
+            const float2 cs = __ldg(cs_row + (((col0 + c + 2 * q) & g.rope_head_mask) >> 1));
+            o[q] = f32x2_to_bf16x2(__fmaf_rn(x, cs.x, -__fmul_rn(y, cs.y)), __fmaf_rn(y, cs.x, __fmul_rn(x, cs.y)));
+          }
+        } else {
+#pragma unroll
+          for (int q = 0; q < 16; ++q)
+            o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs_out, __uint_as_float(r[2 * q + 1]) * gs_out);
+        }
         if (g.residual != nullptr) {
           const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.residual_ld + col0 + c);
 #pragma unroll
@@ -276,7 +298,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMa
 
 // bf16 outputs without fp32 accumulation take this form of the epilogue.
 __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
-  return !g.out_fp32 && g.accum_f32 == nullptr;
+  return !g.out_fp32 && g.accum_f32 == nullptr && g.rope_cs == nullptr;
 }
 
 // Epilogue for bf16 outputs in two phases.  Phase 1 drains the warp's quadrant of the accumulator
@@ -640,10 +662,16 @@ struct KSegments {
   const void* b_sc[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
 };
 
+// Rotary embedding applied by the bf16 epilogue to the output columns [0, col_end).
+struct RopeDesc {
+  const float2* cs;   // [seq_len, head_dim/2] (cos, sin), seq_len and head_dim powers of two
+  int seq_len, head_dim, col_end, round_bf16;
+};
+
 static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const float* A_sg, const float* B_sg,
                             int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld, int n_out,
                             int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N, cudaStream_t st,
-                            const float* accum_f32 = nullptr) {
+                            const float* accum_f32 = nullptr, const RopeDesc* rope = nullptr) {
   const bool pair = (M % 256) == 0 && !gemm_pair_disabled();
   CUtensorMap tmap_a;
   GemmBMaps tmap_b;
@@ -681,6 +709,10 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   g.n_out = n_out; g.out_fp32 = out_fp32;
   g.residual = (const __nv_bfloat16*)residual; g.residual_ld = residual_ld;
   g.accum_f32 = accum_f32;
+  if (rope != nullptr) {
+    g.rope_cs = rope->cs; g.rope_seq_mask = rope->seq_len - 1; g.rope_pair_dim = rope->head_dim / 2;
+    g.rope_head_mask = rope->head_dim - 1; g.rope_col_end = rope->col_end; g.rope_round_bf16 = rope->round_bf16;
+  }
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.status = device_status_ptr();
   if (g.status == nullptr) return -1;
@@ -727,7 +759,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
 static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                        const float* B_sg, int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld,
                        int n_out, int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N,
-                       int64_t K, cudaStream_t st, const float* accum_f32 = nullptr) {
+                       int64_t K, cudaStream_t st, const float* accum_f32 = nullptr, const RopeDesc* rope = nullptr) {
   KSegments segs;
   segs.n = 1;
   segs.a_width = K;
@@ -736,7 +768,7 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
   segs.b[0] = B;
   segs.b_sc[0] = B_sc;
   return launch_gemm_segs(mx, A, segs, A_sg, B_sg, b_sg_per_tile, D, d_col_end, d_ld, n_out, out_fp32, residual, residual_ld,
-                          M, N, st, accum_f32);
+                          M, N, st, accum_f32, rope);
 }
 
 }  // namespace fp4b200
@@ -799,6 +831,38 @@ int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_s
   if (acc != N) return set_error("nvfp4_grouped_gemm: output columns must add up to N");
   return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg_per_tile, 1, D, ce, ld, n_out, 0, nullptr, 0, M, N, K,
                      (cudaStream_t)stream);
+}
+
+int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
+                                    const float* B_sg_per_tile, int n_out, void* const* D, const int64_t* D_cols,
+                                    const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim, int64_t rope_cols,
+                                    int round_input_bf16, int64_t M, int64_t N, int64_t K, void* stream) {
+  const char* fn = "nvfp4_grouped_gemm_rope";
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, fn)) return rc;
+  if (!A_sg || !B_sg_per_tile || !D || !D_cols || !rope_cs) return set_error("%s: null argument", fn);
+  if (n_out < 1 || n_out > 3) return set_error("%s: 1 to 3 outputs are supported", fn);
+  if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)) || (M % rope_seq_len))
+    return set_error("%s: rope_seq_len must be a power of two that divides M (got %lld)", fn, (long long)rope_seq_len);
+  if (rope_head_dim < 2 || (rope_head_dim & (rope_head_dim - 1)) || rope_head_dim > 256)
+    return set_error("%s: rope_head_dim must be a power of two between 2 and 256 (got %lld)", fn, (long long)rope_head_dim);
+  if (rope_cols <= 0 || rope_cols > N || (rope_cols % 32) || (rope_cols % rope_head_dim))
+    return set_error("%s: the rotated column range must be head-aligned, a multiple of 32 and at most N (got %lld)", fn,
+                     (long long)rope_cols);
+  if (reinterpret_cast<uintptr_t>(rope_cs) & 7) return set_error("%s: rope_cs must be 8-byte aligned", fn);
+  int ce[3] = {0, 0, 0}, ld[3] = {0, 0, 0};
+  int64_t acc = 0;
+  for (int i = 0; i < n_out; ++i) {
+    if (!D[i] || D_cols[i] <= 0 || (D_cols[i] % kGemmBN))
+      return set_error("%s: every output needs a column count that is a multiple of 256", fn);
+    acc += D_cols[i];
+    ce[i] = (int)acc;
+    ld[i] = (int)D_cols[i];
+  }
+  if (acc != N) return set_error("%s: output columns must add up to N", fn);
+  RopeDesc rope{reinterpret_cast<const float2*>(rope_cs), (int)rope_seq_len, (int)rope_head_dim, (int)rope_cols,
+                round_input_bf16 != 0};
+  return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg_per_tile, 1, D, ce, ld, n_out, 0, nullptr, 0, M, N, K,
+                     (cudaStream_t)stream, nullptr, &rope);
 }
 
 int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,

@@ -119,6 +119,67 @@ def nvfp4_grouped_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_
     nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt, D_V_opt, silu_dim)
 
 
+def _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, outs, rope_cs, seq_len, head_dim, rope_cols,
+                       round_input_bf16):
+    for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
+        _chk_operand(t, n)
+    M, N, K = _shapes(A, B)
+    _chk_sg(A_sc_global, "A_sc_global")
+    _chk_sg(B_sg_per_tile, "B_sg_per_tile", N // 256)
+    cols = []
+    for o in outs:
+        if not o.is_cuda or o.dtype != torch.bfloat16 or not o.is_contiguous() or o.dim() != 2 or o.shape[0] != M:
+            raise RuntimeError("Q/K/V outputs must be contiguous CUDA bfloat16 [M, n_i]")
+        cols.append(o.shape[1])
+    if sum(cols) != N:
+        raise RuntimeError("Q/K/V output columns must sum to B rows")
+    seq_len, head_dim = int(seq_len), int(head_dim)
+    if seq_len <= 0 or seq_len & (seq_len - 1):
+        raise RuntimeError("rope_seq_len must be a power of two")
+    if (not rope_cs.is_cuda or not rope_cs.is_contiguous() or rope_cs.dtype != torch.float32
+            or tuple(rope_cs.shape) != (seq_len, head_dim // 2, 2)):
+        raise RuntimeError("rope_cs must be contiguous CUDA float32 [seq_len,rotary_dim/2,2]")
+    ptrs = (ctypes.c_void_p * len(outs))(*[o.data_ptr() for o in outs])
+    ccols = (ctypes.c_int64 * len(outs))(*cols)
+    with torch.cuda.device(A.device):
+        _lib.call("fp4b200_nvfp4_grouped_gemm_rope", A.data_ptr(), A_sc.data_ptr(), A_sc_global.data_ptr(), B.data_ptr(),
+                  B_sc.data_ptr(), B_sg_per_tile.data_ptr(), len(outs), ptrs, ccols, rope_cs.data_ptr(), seq_len, head_dim,
+                  int(rope_cols), int(bool(round_input_bf16)), M, N, K, _stream(A))
+
+
+def nvfp4_grouped_gemm_rope_live64(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K, D_V, rope_cs, rope_seq_len,
+                                   silu_dim=0):
+    """nvfp4_b200_gemm.cu:1338-1368 — fused QKV projection, rotary embedding (heads of 64) on the Q and K outputs in
+    the epilogue, V untouched; rope_cs [seq_len, 32, 2]."""
+    if silu_dim:
+        raise RuntimeError("nvfp4_grouped_gemm_rope_live64: the SiLU epilogue (silu_dim > 0) is not built")
+    _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, [D, D_K, D_V], rope_cs, rope_seq_len, 64,
+                       D.shape[1] + D_K.shape[1], False)
+
+
+def nvfp4_grouped_gemm_rope_packed_split(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K, D_V, rope_cs, rope_seq_len,
+                                         rope_head_dim, rope_rotary_dim):
+    """nvfp4_b200_gemm.cu:1406-1441 — as above for any power-of-two head size, the scaled accumulator rounded to
+    bf16 before the rotation (the order of the unfused path: GEMM output in bf16, then RoPE)."""
+    if int(rope_rotary_dim) != int(rope_head_dim):
+        raise RuntimeError("packed RoPE requires rotary_dim == head_dim")
+    _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, [D, D_K, D_V], rope_cs, rope_seq_len, rope_head_dim,
+                       D.shape[1] + D_K.shape[1], True)
+
+
+def nvfp4_grouped_gemm_rope_packed_cat(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, rope_cs, rope_seq_len,
+                                       rope_head_dim, rope_rotary_dim, q_dim, k_dim):
+    """nvfp4_b200_gemm.cu:1370-1404 — single output [M, q_dim + k_dim + v_dim], rotation on the first q_dim + k_dim
+    columns."""
+    if int(rope_rotary_dim) != int(rope_head_dim):
+        raise RuntimeError("packed RoPE requires rotary_dim == head_dim")
+    q_dim, k_dim = int(q_dim), int(k_dim)
+    if q_dim <= 0 or k_dim <= 0 or q_dim + k_dim >= B.shape[0] or q_dim % 256 or k_dim % 256:
+        raise RuntimeError("Q/K dimensions must be positive multiples of 256 with a V suffix")
+    _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, [D], rope_cs, rope_seq_len, rope_head_dim,
+                       q_dim + k_dim, True)
+
+
 def nvfp4_batched_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_list, D_list):
     """nvfp4_b200_gemm.cu:1946-2010: independent GEMMs ``D_i = A_i . B_i^T`` (up to four)."""
     n = len(D_list)

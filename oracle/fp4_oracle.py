@@ -634,6 +634,29 @@ def tk_nvfp4_quantize(a: np.ndarray, scale_2d: bool = False):
     return dict(fp4=pack_fp4(e2m1_encode_rn(scaled)), sc=swizzle_scales(s8), sc_logical=s8, sg=sg)
 
 
+def rope_epilogue(v: np.ndarray, rope_cs: np.ndarray, head_dim: int, rope_cols: int, round_input_bf16: bool) -> np.ndarray:
+    """The rotary-embedding epilogue of the fused QKV projection (ThunderKittens/kernels/gemm/nvfp4_b200/
+    nvfp4_rope_epilogue.cuh:38-56,104-161): v [M, N] fp32 = accumulator x tensor scales; for the columns below
+    rope_cols every pair (2i, 2i+1) is rotated by (cos, sin) = rope_cs[row mod seq_len, (col mod head_dim) / 2]:
+    even' = fma(x, cos, -(y*sin)), odd' = fma(y, cos, x*sin) (the contraction nvcc applies to x*cos - y*sin and
+    y*cos + x*sin), x and y first rounded to bf16 in the "packed" forms; everything is then rounded to bf16."""
+    v = np.asarray(v, dtype=F32)
+    M, N = v.shape
+    seq_len = rope_cs.shape[0]
+    out = v.copy()
+    part = v[:, :rope_cols]
+    if round_input_bf16:
+        part = bf16_round(part)
+    x, y = part[:, 0::2], part[:, 1::2]
+    rows = np.arange(M) % seq_len
+    pos = (np.arange(0, rope_cols, 2) % head_dim) // 2
+    c = np.asarray(rope_cs, dtype=F32)[rows][:, pos, 0]
+    sn = np.asarray(rope_cs, dtype=F32)[rows][:, pos, 1]
+    out[:, 0:rope_cols:2] = _fma32(x, c, -(y * sn).astype(F32))
+    out[:, 1:rope_cols:2] = _fma32(y, c, (x * sn).astype(F32))
+    return bf16_round(out)
+
+
 def mxfp4_gemm_fp32(a_fp4, a_e, b_fp4, b_e) -> np.ndarray:
     """``D = (sum code_a*2^(ea-127)*code_b*2^(eb-127)) / 36`` (mxfp4_gb200/mxfp4_gemm.cuh:557-558)."""
     sa = np.exp2(a_e.astype(np.float64) - 127.0)

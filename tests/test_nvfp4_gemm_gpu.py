@@ -122,3 +122,52 @@ def test_grouped_residual_and_batched_accum():
     torch.cuda.synchronize()
     assert torch.equal(acc, (f1 + f3).to(torch.bfloat16))
     assert_status_ok()
+
+
+@pytest.mark.parametrize("M", [256, 384])       # the two-CTA kernel and the one-CTA kernel
+def test_grouped_gemm_with_rope_epilogue(M):
+    """Fused QKV projection with the rotary embedding in the epilogue: the fp32 epilogue of the same GEMM gives the
+    scaled accumulator the rotation starts from, so the three forms (heads of 64 without the intermediate bf16
+    rounding; packed split and packed single-output with it) can be checked bit for bit against the oracle's
+    rotation of that accumulator; V is the plain bf16 rounding."""
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    K, q_dim, k_dim, v_dim, seq = 512, 512, 256, 256, 128
+    N = q_dim + k_dim + v_dim
+    x, w, qx, qw = _quant_pair(M, N, K, seed=M + 17)
+    b_sg = qw[4].expand(N // 256).contiguous()
+    d32 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], qw[0], qw[1], qw[4], d32)
+    torch.cuda.synchronize()
+    v = d32.cpu().numpy()
+    rng = np.random.default_rng(3)
+    for head, form in ((64, "live64"), (128, "split"), (128, "cat")):
+        ang = rng.uniform(0, 2 * np.pi, size=(seq, head // 2)).astype(np.float32)
+        cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+        cs_d = torch.from_numpy(cs).cuda()
+        dq = torch.full((M, q_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dk = torch.full((M, k_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dv = torch.full((M, v_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        if form == "live64":
+            gemm.nvfp4_grouped_gemm_rope_live64(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, seq)
+            got = torch.cat([dq, dk, dv], dim=1)
+        elif form == "split":
+            gemm.nvfp4_grouped_gemm_rope_packed_split(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, seq, head, head)
+            got = torch.cat([dq, dk, dv], dim=1)
+        else:
+            got = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+            gemm.nvfp4_grouped_gemm_rope_packed_cat(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, got, cs_d, seq, head, head,
+                                                    q_dim, k_dim)
+        torch.cuda.synchronize()
+        assert_status_ok()
+        ref = o.rope_epilogue(v, cs, head, q_dim + k_dim, form != "live64")
+        assert np.array_equal(got.float().cpu().numpy(), ref), form
+        # and the rotation is a rotation: pair norms of Q are those of the un-rotated bf16 product (to rounding)
+        plain = o.bf16_round(v[:, :q_dim]).astype(np.float64)
+        rot = got[:, :q_dim].float().cpu().numpy().astype(np.float64)
+        n0 = np.hypot(plain[:, 0::2], plain[:, 1::2])
+        n1 = np.hypot(rot[:, 0::2], rot[:, 1::2])
+        assert np.abs(n1 - n0).max() <= 2.0 ** -6 * n0.max()
+    with pytest.raises(RuntimeError):
+        gemm.nvfp4_grouped_gemm_rope_packed_split(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, seq, 128, 64)
+    with pytest.raises(RuntimeError):
+        gemm.nvfp4_grouped_gemm_rope_live64(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, 96)
