@@ -258,6 +258,12 @@ int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float
                                     const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim, int64_t rope_cols,
                                     int round_input_bf16, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* nvfp4_forward_rope_packed_qk / nvfp4_inverse_rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out)
+ * (nvfp4_b200_gemm.cu:1083-1218): rotary embedding (inverse != 0: its inverse, the backward of the attention side) of
+ * contiguous bf16 Q [rows, q_dim] and K [rows, k_dim] in one launch; rope_cs fp32 [rope_seq_len, rope_head_dim/2, 2]. */
+int fp4b200_rope_packed_qk(const void* q, const void* k, const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim,
+                           void* q_out, void* k_out, int64_t rows, int64_t q_dim, int64_t k_dim, int inverse, void* stream);
+
 /* ---- RMSNorm backward behind the dgrad GEMMs ----------------------------------------------- */
 
 /* sum3_rmsnorm_bwd_out(d0, d1, d2, input, norm_weight, inv_rms, d_sum, grad_input, dgamma_partials, dgamma)

@@ -118,6 +118,38 @@ static int grid_for(size_t n, int threads) {
 
 using namespace fp4b200;
 
+// Rotary embedding (or its inverse) of contiguous bf16 Q [rows, q_dim] and K [rows, k_dim] in one launch:
+// pairs of neighbouring columns, (cos, sin) = cs[row mod seq_len, (pair index) mod (head_dim / 2)].
+// forward: even' = fma(-y, sin, x*cos), odd' = fma(x, sin, y*cos); inverse: even' = fma(y, sin, x*cos),
+// odd' = fma(-x, sin, y*cos)   (reference: nvfp4_b200_gemm.cu:1083-1131).  Thread = 8 elements (16 bytes).
+template <bool INVERSE>
+__global__ void __launch_bounds__(256)
+rope_packed_qk_kernel(const uint4* __restrict__ q, const uint4* __restrict__ k, uint4* __restrict__ q_out,
+                      uint4* __restrict__ k_out, const float2* __restrict__ cs, size_t q_vecs, size_t k_vecs, int q_vec_row,
+                      int k_vec_row, int pair_dim, int seq_mask) {
+  const int pair_mask = pair_dim - 1;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < q_vecs + k_vecs; i += (size_t)gridDim.x * blockDim.x) {
+    const bool is_q = i < q_vecs;
+    const size_t v = is_q ? i : i - q_vecs;
+    const int vec_row = is_q ? q_vec_row : k_vec_row;
+    const size_t row = v / (size_t)vec_row;
+    const int pair0 = (int)(v - row * (size_t)vec_row) * 4;        // first of this vector's four pairs inside the row
+    const float2* cs_row = cs + (size_t)((int)row & seq_mask) * pair_dim;
+    const uint4 in = __ldcs((is_q ? q : k) + v);
+    const uint32_t w[4] = {in.x, in.y, in.z, in.w};
+    uint32_t o[4];
+#pragma unroll
+    for (int p = 0; p < 4; ++p) {
+      const float x = bf16lo_to_f32(w[p]), y = bf16hi_to_f32(w[p]);
+      const float2 c = __ldg(cs_row + ((pair0 + p) & pair_mask));
+      const float e = INVERSE ? __fmaf_rn(y, c.y, __fmul_rn(x, c.x)) : __fmaf_rn(-y, c.y, __fmul_rn(x, c.x));
+      const float d = INVERSE ? __fmaf_rn(-x, c.y, __fmul_rn(y, c.x)) : __fmaf_rn(x, c.y, __fmul_rn(y, c.x));
+      o[p] = f32x2_to_bf16x2(e, d);
+    }
+    st_cs_u4((is_q ? q_out : k_out) + v, make_uint4(o[0], o[1], o[2], o[3]));
+  }
+}
+
 extern "C" {
 
 int fp4b200_fp32_to_fp4x2(const float* in_f32, int64_t n_pairs, void* out_fp4x2, void* stream) {
@@ -154,6 +186,38 @@ int fp4b200_row_rms_reduce(const float* row_rms_partial, int64_t M, int64_t part
   if (M == 0) return 0;
   row_rms_reduce_kernel<<<(unsigned)((M + 3) / 4), 128, 0, (cudaStream_t)stream>>>(row_rms_partial, inv_rms, M, partial_cols,
                                                                                     hidden_size, eps);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int fp4b200_rope_packed_qk(const void* q, const void* k, const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim,
+                           void* q_out, void* k_out, int64_t rows, int64_t q_dim, int64_t k_dim, int inverse, void* stream) {
+  const char* fn = "rope_packed_qk";
+  if (!q || !k || !rope_cs || !q_out || !k_out) return set_error("%s: null pointer", fn);
+  if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)))
+    return set_error("%s: rope_seq_len must be a positive power of two", fn);
+  if (rope_head_dim < 8 || (rope_head_dim & (rope_head_dim - 1)))
+    return set_error("%s: rope_head_dim must be a power of two, at least 8 (got %lld)", fn, (long long)rope_head_dim);
+  if (rows <= 0 || (rows % rope_seq_len)) return set_error("%s: rows must be a positive multiple of rope_seq_len", fn);
+  if (q_dim <= 0 || k_dim <= 0 || (q_dim % rope_head_dim) || (k_dim % rope_head_dim))
+    return set_error("%s: Q/K columns must be positive multiples of rope_head_dim", fn);
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(q_out) |
+       reinterpret_cast<uintptr_t>(k_out)) & 15)
+    return set_error("%s: Q/K inputs and outputs must be 16-byte aligned", fn);
+  if (reinterpret_cast<uintptr_t>(rope_cs) & 7) return set_error("%s: rope_cs must be 8-byte aligned", fn);
+  const size_t qv = (size_t)rows * (size_t)q_dim / 8, kv = (size_t)rows * (size_t)k_dim / 8;
+  const unsigned grid = grid_for(qv + kv, 256);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (inverse)
+    rope_packed_qk_kernel<true><<<grid, 256, 0, st>>>(static_cast<const uint4*>(q), static_cast<const uint4*>(k),
+                                                      static_cast<uint4*>(q_out), static_cast<uint4*>(k_out),
+                                                      reinterpret_cast<const float2*>(rope_cs), qv, kv, (int)(q_dim / 8),
+                                                      (int)(k_dim / 8), (int)(rope_head_dim / 2), (int)(rope_seq_len - 1));
+  else
+    rope_packed_qk_kernel<false><<<grid, 256, 0, st>>>(static_cast<const uint4*>(q), static_cast<const uint4*>(k),
+                                                       static_cast<uint4*>(q_out), static_cast<uint4*>(k_out),
+                                                       reinterpret_cast<const float2*>(rope_cs), qv, kv, (int)(q_dim / 8),
+                                                       (int)(k_dim / 8), (int)(rope_head_dim / 2), (int)(rope_seq_len - 1));
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

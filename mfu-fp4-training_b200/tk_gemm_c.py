@@ -180,6 +180,37 @@ def nvfp4_grouped_gemm_rope_packed_cat(A, A_sc, A_sc_global, B, B_sc, B_sg_per_t
                        q_dim + k_dim, True)
 
 
+def _rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out, inverse):
+    for t in (q, k, q_out, k_out):
+        if not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or not t.is_contiguous():
+            raise RuntimeError("Q/K inputs and outputs must be contiguous CUDA bf16 matrices")
+    if q.shape != q_out.shape or k.shape != k_out.shape:
+        raise RuntimeError("Q/K output shapes must match their inputs")
+    if q.shape[0] != k.shape[0]:
+        raise RuntimeError("Q/K rows must match")
+    seq_len, head = int(rope_seq_len), int(rope_head_dim)
+    if (not rope_cs.is_cuda or not rope_cs.is_contiguous() or rope_cs.dtype != torch.float32
+            or tuple(rope_cs.shape) != (seq_len, head // 2, 2)):
+        raise RuntimeError("rope_cs must be contiguous CUDA float32 [seq_len,head_dim/2,2]")
+    for out in (q_out, k_out):
+        for src in (q, k):
+            if out.data_ptr() < src.data_ptr() + src.numel() * 2 and src.data_ptr() < out.data_ptr() + out.numel() * 2:
+                raise RuntimeError("output must not overlap an input")
+    with torch.cuda.device(q.device):
+        _lib.call("fp4b200_rope_packed_qk", q.data_ptr(), k.data_ptr(), rope_cs.data_ptr(), seq_len, head, q_out.data_ptr(),
+                  k_out.data_ptr(), q.shape[0], q.shape[1], k.shape[1], int(inverse), _stream(q))
+
+
+def nvfp4_forward_rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out):
+    """nvfp4_b200_gemm.cu:1183-1194 — rotary embedding of contiguous bf16 Q and K in one launch."""
+    _rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out, False)
+
+
+def nvfp4_inverse_rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out):
+    """nvfp4_b200_gemm.cu:1205-1216 — the inverse rotation (gradients of Q and K on the way back to the QKV dgrad)."""
+    _rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out, True)
+
+
 def nvfp4_batched_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_list, D_list):
     """nvfp4_b200_gemm.cu:1946-2010: independent GEMMs ``D_i = A_i . B_i^T`` (up to four)."""
     n = len(D_list)

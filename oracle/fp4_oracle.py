@@ -657,6 +657,26 @@ def rope_epilogue(v: np.ndarray, rope_cs: np.ndarray, head_dim: int, rope_cols: 
     return bf16_round(out)
 
 
+def rope_packed(x: np.ndarray, rope_cs: np.ndarray, inverse: bool) -> np.ndarray:
+    """Rotary embedding of a bf16 matrix [rows, heads * head_dim] (ThunderKittens/kernels/gemm/nvfp4_b200/
+    nvfp4_b200_gemm.cu:1083-1131): pair p of a row uses (cos, sin) = rope_cs[row mod seq_len, p mod (head_dim/2)];
+    forward even' = fma(-y, sin, x*cos), odd' = fma(x, sin, y*cos); inverse even' = fma(y, sin, x*cos),
+    odd' = fma(-x, sin, y*cos); results rounded to bf16."""
+    x = np.asarray(x, dtype=F32)
+    rows, cols = x.shape
+    seq_len, pair_dim = rope_cs.shape[0], rope_cs.shape[1]
+    r = np.arange(rows) % seq_len
+    p = np.arange(cols // 2) % pair_dim
+    c = np.asarray(rope_cs, dtype=F32)[r][:, p, 0]
+    s = np.asarray(rope_cs, dtype=F32)[r][:, p, 1]
+    xe, xo = x[:, 0::2], x[:, 1::2]
+    out = np.empty_like(x)
+    sign = F32(1.0) if inverse else F32(-1.0)
+    out[:, 0::2] = _fma32((sign * xo).astype(F32), s, (xe * c).astype(F32))
+    out[:, 1::2] = _fma32((-sign * xe).astype(F32), s, (xo * c).astype(F32))
+    return bf16_round(out)
+
+
 def mxfp4_gemm_fp32(a_fp4, a_e, b_fp4, b_e) -> np.ndarray:
     """``D = (sum code_a*2^(ea-127)*code_b*2^(eb-127)) / 36`` (mxfp4_gb200/mxfp4_gemm.cuh:557-558)."""
     sa = np.exp2(a_e.astype(np.float64) - 127.0)

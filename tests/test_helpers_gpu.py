@@ -137,3 +137,32 @@ def test_mxfp4_silu_deriv_split2():
         for j, k in enumerate(["row_fp4", "row_sc", "col_fp4", "col_sc"]):
             assert np.array_equal(u8(out[j][i]).reshape(ref[k].shape), ref[k]), (i, k)
     assert_status_ok()
+
+
+@pytest.mark.parametrize("head", [64, 128])
+def test_rope_packed_qk_forward_and_inverse(head):
+    """Rotary embedding of Q and K in one launch, both directions bit-exact against the oracle; the inverse undoes
+    the forward up to the two bf16 roundings."""
+    gemm = mod("tk_gemm_c")
+    rows, seq, q_dim, k_dim = 512, 128, 4 * head, head
+    rng = np.random.default_rng(head)
+    q = o.bf16_round(rng.standard_normal((rows, q_dim)).astype(np.float32))
+    k = o.bf16_round(rng.standard_normal((rows, k_dim)).astype(np.float32))
+    ang = rng.uniform(0, 2 * np.pi, size=(seq, head // 2)).astype(np.float32)
+    cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+    qd, kd, csd = to_dev_bf16(q), to_dev_bf16(k), torch.from_numpy(cs).cuda()
+    qf, kf = torch.empty_like(qd), torch.empty_like(kd)
+    gemm.nvfp4_forward_rope_packed_qk(qd, kd, csd, seq, head, qf, kf)
+    qi, ki = torch.empty_like(qd), torch.empty_like(kd)
+    gemm.nvfp4_inverse_rope_packed_qk(qf, kf, csd, seq, head, qi, ki)
+    torch.cuda.synchronize()
+    ref_qf, ref_kf = o.rope_packed(q, cs, False), o.rope_packed(k, cs, False)
+    assert np.array_equal(qf.float().cpu().numpy(), ref_qf) and np.array_equal(kf.float().cpu().numpy(), ref_kf)
+    assert np.array_equal(qi.float().cpu().numpy(), o.rope_packed(ref_qf, cs, True))
+    assert np.array_equal(ki.float().cpu().numpy(), o.rope_packed(ref_kf, cs, True))
+    assert np.abs(qi.float().cpu().numpy() - q).max() <= 2.0 ** -6 * np.abs(q).max()
+    with pytest.raises(RuntimeError):
+        gemm.nvfp4_forward_rope_packed_qk(qd, kd, csd, seq, head, qd, kf)          # output aliases an input
+    with pytest.raises(RuntimeError):
+        gemm.nvfp4_forward_rope_packed_qk(qd, kd, csd[:96].contiguous(), 96, head, qf, kf)   # not a power of two
+    assert_status_ok()
