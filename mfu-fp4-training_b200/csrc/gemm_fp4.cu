@@ -298,7 +298,7 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMa
 
 // bf16 outputs without fp32 accumulation take this form of the epilogue.
 __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
-  return !g.out_fp32 && g.accum_f32 == nullptr && g.rope_cs == nullptr;
+  return !g.out_fp32 && g.accum_f32 == nullptr;
 }
 
 // Epilogue for bf16 outputs in two phases.  Phase 1 drains the warp's quadrant of the accumulator
@@ -308,7 +308,7 @@ __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
 // overwrite the accumulator.  Phase 2 (TMA stores of the staged half, then staging and stores of the
 // register half) runs while the next tile's MMAs are already issuing, which is what the single
 // accumulator (256 + scale columns fill tensor memory) would otherwise forbid.
-template <typename Release>
+template <bool ROPE, typename Release>
 __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t tmem,
                                                    uint8_t* epi, int row0, int tn, float a_sg, int quad, int lane,
                                                    Release release) {
@@ -339,6 +339,30 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
     }
   };
 
+  // Rotary embedding of 16 columns (eight pairs): (cos, sin) of this lane's token row and of the pairs' positions
+  // inside their head are 64 contiguous bytes of the table (head_dim >= 16).  even' = fma(x, cos, -(y*sin)),
+  // odd' = fma(y, cos, x*sin).
+  const bool rope_tile = ROPE && col0 < g.rope_col_end;   // ROPE: g.rope_cs is set
+  const float2* cs_row = rope_tile ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
+  auto load_cs = [&](float4 (&cs)[4], int col) {
+    const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
+#pragma unroll
+    for (int q = 0; q < 4; ++q) cs[q] = __ldg(p + q);
+  };
+  auto rotate_pair = [&](float x, float y, float c, float sn) {
+    return f32x2_to_bf16x2(__fmaf_rn(x, c, -__fmul_rn(y, sn)), __fmaf_rn(y, c, __fmul_rn(x, sn)));
+  };
+  // eight packed bf16 pairs, already rounded (the "packed" forms rotate the bf16 GEMM output)
+  auto rotate_packed = [&](uint32_t (&w)[8], int col) {
+    float4 cs[4];
+    load_cs(cs, col);
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      w[2 * q] = rotate_pair(bf16lo_to_f32(w[2 * q]), bf16hi_to_f32(w[2 * q]), cs[q].x, cs[q].y);
+      w[2 * q + 1] = rotate_pair(bf16lo_to_f32(w[2 * q + 1]), bf16hi_to_f32(w[2 * q + 1]), cs[q].z, cs[q].w);
+    }
+  };
+
   // the stores of the previous tile have finished reading both staging buffers (issued a tile ago)
   if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
   __syncwarp();
@@ -355,12 +379,30 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
     }
     uint32_t w[16];
     const float2 gs2 = make_float2(gs, gs);
+    if (rope_tile && !g.rope_round_bf16) {
+      // rotation of the unrounded scaled accumulator: has to happen here, where the fp32 values are
 #pragma unroll
-    for (int q = 0; q < 16; ++q) {
-      const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
-      const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
-      const float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
-      w[q] = f32x2_to_bf16x2(v.x, v.y);
+      for (int h = 0; h < 2; ++h) {
+        float4 cs[4];
+        load_cs(cs, c * 32 + h * 16);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint32_t lo = (c & 1) ? rb[16 * h + 2 * q] : ra[16 * h + 2 * q];
+          const uint32_t hi = (c & 1) ? rb[16 * h + 2 * q + 1] : ra[16 * h + 2 * q + 1];
+          const float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+          const float cc = (q & 1) ? cs[q >> 1].z : cs[q >> 1].x, sn = (q & 1) ? cs[q >> 1].w : cs[q >> 1].y;
+          w[8 * h + q] = rotate_pair(v.x, v.y, cc, sn);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int q = 0; q < 16; ++q) {
+        const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
+        const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
+        const float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+        w[q] = f32x2_to_bf16x2(v.x, v.y);
+      }
+      // packed forms: both halves are rotated after the accumulator's release (the staged half in place)
     }
     if (c < 4) {
       // slab c/2 (64 columns = 128 bytes per row), 16-byte pieces 4*(c%2) .. 4*(c%2)+3 of the row
@@ -385,6 +427,22 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   }
   release();
 
+  if (rope_tile && g.rope_round_bf16) {
+    // staged half: this lane's own row, 16 columns (two 16-byte pieces) at a time
+#pragma unroll
+    for (int slab = 0; slab < 2; ++slab) {
+#pragma unroll
+      for (int pp = 0; pp < 4; ++pp) {
+        uint4* p0 = reinterpret_cast<uint4*>(rowp + slab * 4096 + (((2 * pp) ^ sw) << 4));
+        uint4* p1 = reinterpret_cast<uint4*>(rowp + slab * 4096 + (((2 * pp + 1) ^ sw) << 4));
+        const uint4 a = *p0, b = *p1;
+        uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+        rotate_packed(w, slab * 64 + pp * 16);
+        *p0 = make_uint4(w[0], w[1], w[2], w[3]);
+        *p1 = make_uint4(w[4], w[5], w[6], w[7]);
+      }
+    }
+  }
   // staged half: two TMA stores
   fence_proxy_async_smem();
   __syncwarp();
@@ -398,6 +456,17 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
 #pragma unroll
   for (int slab = 2; slab < 4; ++slab) {
     uint8_t* dst = rowp + (slab & 1) * 4096;
+    if (rope_tile && g.rope_round_bf16) {
+#pragma unroll
+      for (int cc = 0; cc < 4; ++cc) {
+        uint32_t w[8];
+#pragma unroll
+        for (int q = 0; q < 8; ++q) w[q] = o[(slab - 2) * 32 + cc * 8 + q];
+        rotate_packed(w, slab * 64 + cc * 16);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) o[(slab - 2) * 32 + cc * 8 + q] = w[q];
+      }
+    }
     if (res_row != nullptr) {
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
@@ -619,7 +688,10 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (lane == 0) mbar_arrive(&sm.acc_empty);
       };
       if (epilogue_is_bf16_plain(g)) {
-        epilogue_tile_bf16(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+        if (g.rope_cs != nullptr)
+          epilogue_tile_bf16<true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+        else
+          epilogue_tile_bf16<false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
       } else {
         epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
         release();
@@ -843,8 +915,9 @@ int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float
   if (n_out < 1 || n_out > 3) return set_error("%s: 1 to 3 outputs are supported", fn);
   if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)) || (M % rope_seq_len))
     return set_error("%s: rope_seq_len must be a power of two that divides M (got %lld)", fn, (long long)rope_seq_len);
-  if (rope_head_dim < 2 || (rope_head_dim & (rope_head_dim - 1)) || rope_head_dim > 256)
-    return set_error("%s: rope_head_dim must be a power of two between 2 and 256 (got %lld)", fn, (long long)rope_head_dim);
+  if (rope_head_dim < 16 || (rope_head_dim & (rope_head_dim - 1)) || rope_head_dim > 256)
+    return set_error("%s: rope_head_dim must be a power of two between 16 and 256 (got %lld)", fn, (long long)rope_head_dim);
+  if (reinterpret_cast<uintptr_t>(rope_cs) & 15) return set_error("%s: rope_cs must be 16-byte aligned", fn);
   if (rope_cols <= 0 || rope_cols > N || (rope_cols % 32) || (rope_cols % rope_head_dim))
     return set_error("%s: the rotated column range must be head-aligned, a multiple of 32 and at most N (got %lld)", fn,
                      (long long)rope_cols);
