@@ -353,6 +353,13 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
     return f32x2_to_bf16x2(__fmaf_rn(x, c, -__fmul_rn(y, sn)), __fmaf_rn(y, c, __fmul_rn(x, sn)));
   };
   // eight packed bf16 pairs, already rounded (the "packed" forms rotate the bf16 GEMM output)
+  auto rotate_with = [&](uint32_t (&w)[8], const float4 (&cs)[4]) {
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      w[2 * q] = rotate_pair(bf16lo_to_f32(w[2 * q]), bf16hi_to_f32(w[2 * q]), cs[q].x, cs[q].y);
+      w[2 * q + 1] = rotate_pair(bf16lo_to_f32(w[2 * q + 1]), bf16hi_to_f32(w[2 * q + 1]), cs[q].z, cs[q].w);
+    }
+  };
   auto rotate_packed = [&](uint32_t (&w)[8], int col) {
     float4 cs[4];
     load_cs(cs, col);
@@ -427,6 +434,9 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   }
   release();
 
+  // Heads of at most 128 columns: the column 128 further on sits at the same position of its head, so one read of
+  // (cos, sin) serves a piece of the staged half and the piece of the register half 128 columns to its right.
+  const bool rope_shared = rope_tile && g.rope_round_bf16 && g.rope_head_mask < 128 && col0 + 128 < g.rope_col_end;
   if (rope_tile && g.rope_round_bf16) {
     // staged half: this lane's own row, 16 columns (two 16-byte pieces) at a time
 #pragma unroll
@@ -437,9 +447,19 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
         uint4* p1 = reinterpret_cast<uint4*>(rowp + slab * 4096 + (((2 * pp + 1) ^ sw) << 4));
         const uint4 a = *p0, b = *p1;
         uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        rotate_packed(w, slab * 64 + pp * 16);
+        float4 cs[4];
+        load_cs(cs, slab * 64 + pp * 16);
+        rotate_with(w, cs);
         *p0 = make_uint4(w[0], w[1], w[2], w[3]);
         *p1 = make_uint4(w[4], w[5], w[6], w[7]);
+        if (rope_shared) {
+          uint32_t v[8];
+#pragma unroll
+          for (int q = 0; q < 8; ++q) v[q] = o[slab * 32 + pp * 8 + q];
+          rotate_with(v, cs);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) o[slab * 32 + pp * 8 + q] = v[q];
+        }
       }
     }
   }
@@ -456,7 +476,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
 #pragma unroll
   for (int slab = 2; slab < 4; ++slab) {
     uint8_t* dst = rowp + (slab & 1) * 4096;
-    if (rope_tile && g.rope_round_bf16) {
+    if (rope_tile && g.rope_round_bf16 && !rope_shared) {
 #pragma unroll
       for (int cc = 0; cc < 4; ++cc) {
         uint32_t w[8];

@@ -140,7 +140,7 @@ def test_grouped_gemm_with_rope_epilogue(M):
     torch.cuda.synchronize()
     v = d32.cpu().numpy()
     rng = np.random.default_rng(3)
-    for head, form in ((64, "live64"), (128, "split"), (128, "cat")):
+    for head, form in ((64, "live64"), (128, "split"), (128, "cat"), (256, "split"), (32, "cat")):
         ang = rng.uniform(0, 2 * np.pi, size=(seq, head // 2)).astype(np.float32)
         cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
         cs_d = torch.from_numpy(cs).cuda()
