@@ -352,6 +352,57 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
             "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
 
 
+def attention_side_leg(torch, dist, world, peaks):
+    """Attention-side producers and epilogues of a Llama-3-8B layer in NVFP4 at M = 16384 tokens per rank (two
+    sequences of 8192): fused QKV projection with the rotary embedding in the GEMM epilogue (Q 4096, K 1024,
+    V 1024 columns, heads of 128), quantisation of the attention output from its [B, H, S, 64] layout for the
+    output projection, the inverse rotation of dQ / dK and the three-stream gradient quantiser in front of the
+    QKV dgrad."""
+    tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
+    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    M, K, q_dim, kv_dim, seq, head = M_ROWS, K_COLS, 4096, 1024, 8192, 128
+    N = q_dim + 2 * kv_dim
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(17)
+    def rnd(n, k, s):
+        return (s * torch.randn(n, k, generator=g, device=dev)).to(torch.bfloat16)
+    qx = tkq.tk_quantize_for_gemm(rnd(M, K, 1.0), False, True)
+    qw = tkq.tk_quantize_for_gemm(rnd(N, K, 0.02), False, True)
+    b_sg = qw[4].expand(N // 256).contiguous()
+    ang = torch.rand(seq, head // 2, generator=g, device=dev) * 6.2831853
+    cs = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+    dq = torch.empty(M, q_dim, dtype=torch.bfloat16, device=dev)
+    dk = torch.empty(M, kv_dim, dtype=torch.bfloat16, device=dev)
+    dv = torch.empty(M, kv_dim, dtype=torch.bfloat16, device=dev)
+    attn = rnd(M, K, 1.0).view(M // seq, K // 64, seq, 64)          # [B, H, S, 64]
+    gq, gk, gv = rnd(M, q_dim, 1e-3), rnd(M, kv_dim, 1e-3), rnd(M, kv_dim, 1e-3)
+    gq2, gk2 = torch.empty_like(gq), torch.empty_like(gk)
+    def s_qkv_rope():
+        gemm.nvfp4_grouped_gemm_rope_packed_split(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs, seq, head, head)
+    def s_qkv_plain():
+        gemm.nvfp4_grouped_gemm(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv)
+    def s_quant_attn():
+        tkq.tk_quantize_nhsd_wo_for_gemm(attn, True, True)
+    def s_inverse_rope():
+        gemm.nvfp4_inverse_rope_packed_qk(gq, gk, cs, seq, head, gq2, gk2)
+    def s_split3():
+        tkq.tk_group_quantize_dim1_split3_for_gemm(gq2, gk2, gv)
+    names = ["qkv_gemm_rope", "qkv_gemm_plain", "quant_attn_out_nhsd", "inverse_rope_dq_dk", "split3_quant"]
+    ms, _ = _timed_stages(torch, [s_qkv_rope, s_qkv_plain, s_quant_attn, s_inverse_rope, s_split3])
+    t = torch.tensor(ms, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = t.tolist()
+    fl = 2.0 * M * N * K
+    return {"workload": "Llama-3-8B attention side in NVFP4, M=16384 tokens per GPU, heads of 128, sequences of 8192",
+            "ms": dict(zip(names, ms)),
+            "qkv_gemm_rope_tflops": fl * world / (ms[0] * 1e-3) / 1e12,
+            "qkv_gemm_plain_tflops": fl * world / (ms[1] * 1e-3) / 1e12,
+            "quant_attn_out_gbs": M * K * 3.125 * world / (ms[2] * 1e-3) / 1e9,
+            "inverse_rope_gbs": M * (q_dim + kv_dim) * 4.0 * world / (ms[3] * 1e-3) / 1e9,
+            "split3_quant_gbs": M * N * 3.125 * world / (ms[4] * 1e-3) / 1e9}
+
+
 def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
     """MXFP4 (E8M0 / 32-blocks, mode 1) forward GEMMs of one Llama-3-8B decoder layer's weights (config 5:
     QKV [6144,4096], O [4096,4096], W1/W3 [14336,4096], W2 [4096,14336]) on this rank's share of
@@ -667,6 +718,8 @@ def main():
     ffn_bwd = ffn_backward_leg(torch, dist, world, xs[0], gamma, peaks)
     torch.cuda.empty_cache()
     mx_layer = mxfp4_layer_leg(torch, dist, world, gamma, peaks)
+    torch.cuda.empty_cache()
+    attn_side = attention_side_leg(torch, dist, world, peaks)
     clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
@@ -680,7 +733,8 @@ def main():
                            "l2": "inputs rotate over 3 copies of X (402 MB > 126 MB L2) between steps",
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
-                "cpu_baseline": cpu, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer_forward": mx_layer}
+                "cpu_baseline": cpu, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer_forward": mx_layer,
+                "attention_side": attn_side}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
