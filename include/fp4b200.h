@@ -273,7 +273,7 @@ int fp4b200_rope_packed_qk(const void* q, const void* k, const float* rope_cs, i
  *                the order of the reference's 512-thread block (thread t: columns t, t+512, ...; cub block sum)
  *   dgamma_partials [ceil(M/256), K] fp32: per 256-row tile, rows accumulated in turn; dgamma [K] (fp32, or bf16
  *                when dgamma_is_bf16) = the tiles added in turn.  Deterministic: no atomics.
- * K a multiple of 256, at most 4096 (the reference takes any K).  Outputs must not overlap inputs or each other. */
+ * K a multiple of 256, at most 8192 (the reference takes any K).  Outputs must not overlap inputs or each other. */
 int fp4b200_sum3_rmsnorm_bwd(const void* d0, const void* d1, const void* d2, const void* input, const void* norm_weight,
                              const float* inv_rms, void* d_sum, void* grad_input, float* dgamma_partials, void* dgamma,
                              int dgamma_is_bf16, int64_t M, int64_t K, void* stream);

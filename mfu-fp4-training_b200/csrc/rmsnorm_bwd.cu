@@ -25,7 +25,7 @@
 namespace fp4b200 {
 
 constexpr int kBwdRowTile = 256;      // rows per dgamma tile (fixed by the layout of dgamma_partials)
-constexpr int kBwdMaxVec = 16;        // 16-byte vectors per lane and row: K <= 4096
+constexpr int kBwdMaxVec = 32;        // 16-byte vectors per lane and row: K <= 8192 (kernels are built for 16 and 32)
 
 __device__ __forceinline__ uint32_t bf16x2_add(uint32_t a, uint32_t b) {
   uint32_t d;
@@ -95,7 +95,7 @@ __device__ __forceinline__ void dgamma_rows(const uint2* dp, const uint2* xp, si
   }
 }
 
-template <bool SUM3, bool FUSE_DGAMMA>
+template <bool SUM3, bool FUSE_DGAMMA, int MAXV /* vectors per lane the row loops are unrolled for */>
 __global__ void __launch_bounds__((8 + kDgammaWarps) * 32, 1)
 rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16* __restrict__ in1,
                       const __nv_bfloat16* __restrict__ in2, const __nv_bfloat16* __restrict__ x,
@@ -232,7 +232,7 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
 #pragma unroll
       for (int p = 0; p < 4; ++p) acc[h][p] = make_float2(0.0f, 0.0f);
 #pragma unroll
-    for (int j = 0; j < kBwdMaxVec; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       if (j < nv) {
         const int q = lane + 32 * j;
         uint4 dy = s_dy[q];
@@ -285,7 +285,7 @@ rmsnorm_bwd_dx_kernel(const __nv_bfloat16* __restrict__ in0, const __nv_bfloat16
 
     // ---- dx, written over a stream this lane has already consumed
 #pragma unroll
-    for (int j = 0; j < kBwdMaxVec; ++j) {
+    for (int j = 0; j < MAXV; ++j) {
       if (j < nv) {
         const int q = lane + 32 * j;
         const uint4 dy = s_dy[q];
@@ -451,7 +451,7 @@ int launch_rmsnorm_bwd(const void* in0, const void* in1, const void* in2, const 
 
   bool fused = fused_dgamma_enabled() && row_tiles <= kScratchFloats && cooperative_launch_supported();
   if (fused) {
-    auto kern = rmsnorm_bwd_dx_kernel<SUM3, true>;
+    auto kern = K <= 4096 ? rmsnorm_bwd_dx_kernel<SUM3, true, 16> : rmsnorm_bwd_dx_kernel<SUM3, true, 32>;
     FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int block = (warps + kDgammaWarps) * 32;
     int per_sm = 0;
@@ -468,7 +468,7 @@ int launch_rmsnorm_bwd(const void* in0, const void* in1, const void* in2, const 
       return launch_dgamma_reduce(partials, dgamma, dgamma_bf16, row_tiles, K, st);
     }
   }
-  auto kern = rmsnorm_bwd_dx_kernel<SUM3, false>;
+  auto kern = K <= 4096 ? rmsnorm_bwd_dx_kernel<SUM3, false, 16> : rmsnorm_bwd_dx_kernel<SUM3, false, 32>;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   kern<<<grid, warps * 32, smem, st>>>(p_in0, p_in1, p_in2, p_x, p_gamma, inv_rms, p_res, p_dsum, p_dx, m_i, k_i, slots_i,
                                        warps, nullptr, nullptr, status);

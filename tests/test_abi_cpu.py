@@ -70,6 +70,6 @@ def test_entry_points_validate_before_touching_the_device(pkg):
     assert lib.fp4b200_nvfp4_gemm(p, p, p, p, p, p, p, 0, None, 128, 200, 256, None) == -1 and "N % 256" in msg()
     # RMSNorm backward: shape limits, then aliasing of outputs with inputs
     assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 4, 384, None) == -1 and "multiple of 256" in msg()
-    assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 4, 8192, None) == -1
+    assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 4, 16384, None) == -1 and "8192" in msg()
     assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 1, 256, None) == -1 and "overlaps" in msg()
     assert lib.fp4b200_rmsnorm_bwd_residual(p, p, p, p, p, p, p, p, 4, 2048, None) == -1 and "4096" in msg()

@@ -30,7 +30,7 @@ def _f32(t):
 
 
 @pytest.mark.parametrize("dgamma_dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(1, 256), (300, 1024), (513, 4096), (1024, 768)])
+@pytest.mark.parametrize("shape", [(1, 256), (300, 1024), (513, 4096), (1024, 768), (260, 8192), (130, 6144)])
 def test_sum3_rmsnorm_bwd_bit_exact(shape, dgamma_dtype):
     gemm = mod("tk_gemm_c")
     M, K = shape
