@@ -252,11 +252,14 @@ int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int
  * scales (and, with round_input_bf16, rounded to bf16), neighbouring columns (2i, 2i+1) of token row r are rotated by
  * rope_cs[r mod rope_seq_len, (col mod rope_head_dim) / 2] = (cos, sin), then rounded to bf16.  Outputs as in
  * fp4b200_nvfp4_grouped_gemm (1 to 3 bf16 matrices split by column range, each a multiple of 256 wide);
- * rope_seq_len and rope_head_dim powers of two, rope_cs fp32 [rope_seq_len, rope_head_dim/2, 2]. */
+ * rope_seq_len and rope_head_dim powers of two, rope_cs fp32 [rope_seq_len, rope_head_dim/2, 2].
+ * silu_dim > 0 (the silu_dim argument of nvfp4_grouped_gemm and nvfp4_grouped_gemm_rope_live64, nvfp4_gemm.cuh:210-225):
+ * x / (1 + __expf(-x)) on the scaled accumulator of the columns [0, silu_dim) before any rotation; rope_cs may then be
+ * null (SiLU only). */
 int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                                     const float* B_sg_per_tile, int n_out, void* const* D, const int64_t* D_cols,
                                     const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim, int64_t rope_cols,
-                                    int round_input_bf16, int64_t M, int64_t N, int64_t K, void* stream);
+                                    int round_input_bf16, int64_t silu_dim, int64_t M, int64_t N, int64_t K, void* stream);
 
 /* nvfp4_forward_rope_packed_qk / nvfp4_inverse_rope_packed_qk(q, k, rope_cs, rope_seq_len, rope_head_dim, q_out, k_out)
  * (nvfp4_b200_gemm.cu:1083-1218): rotary embedding (inverse != 0: its inverse, the backward of the attention side) of

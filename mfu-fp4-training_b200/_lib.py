@@ -66,7 +66,7 @@ SIGNATURES = {
     "fp4b200_nvfp4_quantize_nhsd_wo": [_c_void_p, _i64, _i64, _i64, _i64, _int, _int, _c_void_p, _c_void_p, _c_void_p,
                                        _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_grouped_gemm_rope": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p,
-                                        _c_void_p, _c_void_p, _i64, _i64, _i64, _int, _i64, _i64, _i64, _c_void_p],
+                                        _c_void_p, _c_void_p, _i64, _i64, _i64, _int, _i64, _i64, _i64, _i64, _c_void_p],
     "fp4b200_rope_packed_qk": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _c_void_p, _c_void_p, _i64, _i64, _i64, _int,
                                _c_void_p],
     "fp4b200_sum3_rmsnorm_bwd": [_c_void_p] * 10 + [_int, _i64, _i64, _c_void_p],

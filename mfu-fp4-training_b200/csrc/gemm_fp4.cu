@@ -88,6 +88,7 @@ struct GemmArgs {
   const float2* rope_cs;    // [seq_len, head_dim/2] (cos, sin)
   int rope_seq_mask, rope_pair_dim, rope_head_mask, rope_col_end;
   int rope_round_bf16;      // round the scaled accumulator to bf16 before the rotation ("packed" forms)
+  int silu_col_end;         // > 0: x / (1 + __expf(-x)) on the scaled accumulator of the columns [0, silu_col_end), before any rotation
   int M, N, K;              // K = sum of the segments
   int* status;
 };
@@ -342,7 +343,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   // Rotary embedding of 16 columns (eight pairs): (cos, sin) of this lane's token row and of the pairs' positions
   // inside their head are 64 contiguous bytes of the table (head_dim >= 16).  even' = fma(x, cos, -(y*sin)),
   // odd' = fma(y, cos, x*sin).
-  const bool rope_tile = ROPE && col0 < g.rope_col_end;   // ROPE: g.rope_cs is set
+  const bool rope_tile = ROPE && g.rope_cs != nullptr && col0 < g.rope_col_end;   // ROPE: a rotation and / or SiLU is requested
   const float2* cs_row = rope_tile ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
   auto load_cs = [&](float4 (&cs)[4], int col) {
     const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
@@ -386,6 +387,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
     }
     uint32_t w[16];
     const float2 gs2 = make_float2(gs, gs);
+    const bool silu_chunk = ROPE && col0 + c * 32 < g.silu_col_end;
     if (rope_tile && !g.rope_round_bf16) {
       // rotation of the unrounded scaled accumulator: has to happen here, where the fp32 values are
 #pragma unroll
@@ -396,7 +398,8 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
         for (int q = 0; q < 8; ++q) {
           const uint32_t lo = (c & 1) ? rb[16 * h + 2 * q] : ra[16 * h + 2 * q];
           const uint32_t hi = (c & 1) ? rb[16 * h + 2 * q + 1] : ra[16 * h + 2 * q + 1];
-          const float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+          float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+          if (silu_chunk) v = make_float2(v.x / (1.0f + __expf(-v.x)), v.y / (1.0f + __expf(-v.y)));
           const float cc = (q & 1) ? cs[q >> 1].z : cs[q >> 1].x, sn = (q & 1) ? cs[q >> 1].w : cs[q >> 1].y;
           w[8 * h + q] = rotate_pair(v.x, v.y, cc, sn);
         }
@@ -406,7 +409,8 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
       for (int q = 0; q < 16; ++q) {
         const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
         const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
-        const float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+        float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
+        if (ROPE && silu_chunk) v = make_float2(v.x / (1.0f + __expf(-v.x)), v.y / (1.0f + __expf(-v.y)));
         w[q] = f32x2_to_bf16x2(v.x, v.y);
       }
       // packed forms: both halves are rotated after the accumulator's release (the staged half in place)
@@ -708,7 +712,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (lane == 0) mbar_arrive(&sm.acc_empty);
       };
       if (epilogue_is_bf16_plain(g)) {
-        if (g.rope_cs != nullptr)
+        if (g.rope_cs != nullptr || g.silu_col_end > 0)
           epilogue_tile_bf16<true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
         else
           epilogue_tile_bf16<false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
@@ -756,8 +760,9 @@ struct KSegments {
 
 // Rotary embedding applied by the bf16 epilogue to the output columns [0, col_end).
 struct RopeDesc {
-  const float2* cs;   // [seq_len, head_dim/2] (cos, sin), seq_len and head_dim powers of two
+  const float2* cs;   // [seq_len, head_dim/2] (cos, sin), seq_len and head_dim powers of two; null: no rotation
   int seq_len, head_dim, col_end, round_bf16;
+  int silu_col_end;   // SiLU on the columns [0, silu_col_end) before the rotation; 0: none
 };
 
 static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const float* A_sg, const float* B_sg,
@@ -803,7 +808,8 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   g.accum_f32 = accum_f32;
   if (rope != nullptr) {
     g.rope_cs = rope->cs; g.rope_seq_mask = rope->seq_len - 1; g.rope_pair_dim = rope->head_dim / 2;
-    g.rope_head_mask = rope->head_dim - 1; g.rope_col_end = rope->col_end; g.rope_round_bf16 = rope->round_bf16;
+    g.rope_head_mask = rope->head_dim - 1; g.rope_col_end = rope->cs != nullptr ? rope->col_end : 0;
+    g.rope_round_bf16 = rope->round_bf16; g.silu_col_end = rope->silu_col_end;
   }
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.status = device_status_ptr();
@@ -928,20 +934,24 @@ int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_s
 int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                                     const float* B_sg_per_tile, int n_out, void* const* D, const int64_t* D_cols,
                                     const float* rope_cs, int64_t rope_seq_len, int64_t rope_head_dim, int64_t rope_cols,
-                                    int round_input_bf16, int64_t M, int64_t N, int64_t K, void* stream) {
+                                    int round_input_bf16, int64_t silu_dim, int64_t M, int64_t N, int64_t K, void* stream) {
   const char* fn = "nvfp4_grouped_gemm_rope";
   if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, fn)) return rc;
-  if (!A_sg || !B_sg_per_tile || !D || !D_cols || !rope_cs) return set_error("%s: null argument", fn);
+  if (!A_sg || !B_sg_per_tile || !D || !D_cols) return set_error("%s: null argument", fn);
   if (n_out < 1 || n_out > 3) return set_error("%s: 1 to 3 outputs are supported", fn);
-  if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)) || (M % rope_seq_len))
-    return set_error("%s: rope_seq_len must be a power of two that divides M (got %lld)", fn, (long long)rope_seq_len);
-  if (rope_head_dim < 16 || (rope_head_dim & (rope_head_dim - 1)) || rope_head_dim > 256)
-    return set_error("%s: rope_head_dim must be a power of two between 16 and 256 (got %lld)", fn, (long long)rope_head_dim);
-  if (reinterpret_cast<uintptr_t>(rope_cs) & 15) return set_error("%s: rope_cs must be 16-byte aligned", fn);
-  if (rope_cols <= 0 || rope_cols > N || (rope_cols % 32) || (rope_cols % rope_head_dim))
-    return set_error("%s: the rotated column range must be head-aligned, a multiple of 32 and at most N (got %lld)", fn,
-                     (long long)rope_cols);
-  if (reinterpret_cast<uintptr_t>(rope_cs) & 7) return set_error("%s: rope_cs must be 8-byte aligned", fn);
+  if (rope_cs == nullptr && silu_dim <= 0) return set_error("%s: neither a rotation table nor a SiLU range was given", fn);
+  if (silu_dim < 0 || silu_dim > N || (silu_dim % 32))
+    return set_error("%s: silu_dim must be a multiple of 32 between 0 and N (got %lld)", fn, (long long)silu_dim);
+  if (rope_cs != nullptr) {
+    if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)) || (M % rope_seq_len))
+      return set_error("%s: rope_seq_len must be a power of two that divides M (got %lld)", fn, (long long)rope_seq_len);
+    if (rope_head_dim < 16 || (rope_head_dim & (rope_head_dim - 1)) || rope_head_dim > 256)
+      return set_error("%s: rope_head_dim must be a power of two between 16 and 256 (got %lld)", fn, (long long)rope_head_dim);
+    if (reinterpret_cast<uintptr_t>(rope_cs) & 15) return set_error("%s: rope_cs must be 16-byte aligned", fn);
+    if (rope_cols <= 0 || rope_cols > N || (rope_cols % 32) || (rope_cols % rope_head_dim))
+      return set_error("%s: the rotated column range must be head-aligned, a multiple of 32 and at most N (got %lld)", fn,
+                       (long long)rope_cols);
+  }
   int ce[3] = {0, 0, 0}, ld[3] = {0, 0, 0};
   int64_t acc = 0;
   for (int i = 0; i < n_out; ++i) {
@@ -952,8 +962,8 @@ int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float
     ld[i] = (int)D_cols[i];
   }
   if (acc != N) return set_error("%s: output columns must add up to N", fn);
-  RopeDesc rope{reinterpret_cast<const float2*>(rope_cs), (int)rope_seq_len, (int)rope_head_dim, (int)rope_cols,
-                round_input_bf16 != 0};
+  RopeDesc rope{reinterpret_cast<const float2*>(rope_cs), rope_cs ? (int)rope_seq_len : 1, rope_cs ? (int)rope_head_dim : 2,
+                (int)rope_cols, round_input_bf16 != 0, (int)silu_dim};
   return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg_per_tile, 1, D, ce, ld, n_out, 0, nullptr, 0, M, N, K,
                      (cudaStream_t)stream, nullptr, &rope);
 }

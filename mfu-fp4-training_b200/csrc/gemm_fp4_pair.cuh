@@ -270,7 +270,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       };
       if (epilogue_is_bf16_plain(g)) {
-        if (g.rope_cs != nullptr)
+        if (g.rope_cs != nullptr || g.silu_col_end > 0)
           epilogue_tile_bf16<true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
                                    lane, release);
         else

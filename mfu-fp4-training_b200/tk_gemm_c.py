@@ -91,9 +91,12 @@ def nvfp4_gemm_residual(A, A_sc, A_sc_global, B, B_sc, B_sc_global, R, D):
 
 def nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt=None, D_V_opt=None, silu_dim=0):
     """nvfp4_b200_gemm.cu:764-841: one GEMM over concatenated weights, per-256-row tensor scales,
-    outputs routed by column range to ``D`` (and ``D_K_opt``, ``D_V_opt``)."""
+    outputs routed by column range to ``D`` (and ``D_K_opt``, ``D_V_opt``); ``silu_dim`` > 0 applies
+    ``x / (1 + exp(-x))`` to the first ``silu_dim`` output columns."""
     if silu_dim:
-        raise RuntimeError("nvfp4_grouped_gemm: the SiLU epilogue (silu_dim > 0) is not built")
+        # SiLU of the columns [0, silu_dim) in the epilogue (nvfp4_gemm.cuh:210-225)
+        outs = [D] + [t for t in (D_K_opt, D_V_opt) if t is not None]
+        return _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, outs, None, 1, 2, 0, False, silu_dim)
     for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
         _chk_operand(t, n)
     M, N, K = _shapes(A, B)
@@ -120,7 +123,7 @@ def nvfp4_grouped_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_
 
 
 def _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, outs, rope_cs, seq_len, head_dim, rope_cols,
-                       round_input_bf16):
+                       round_input_bf16, silu_dim=0):
     for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
         _chk_operand(t, n)
     M, N, K = _shapes(A, B)
@@ -134,27 +137,27 @@ def _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, outs, rope_
     if sum(cols) != N:
         raise RuntimeError("Q/K/V output columns must sum to B rows")
     seq_len, head_dim = int(seq_len), int(head_dim)
-    if seq_len <= 0 or seq_len & (seq_len - 1):
-        raise RuntimeError("rope_seq_len must be a power of two")
-    if (not rope_cs.is_cuda or not rope_cs.is_contiguous() or rope_cs.dtype != torch.float32
-            or tuple(rope_cs.shape) != (seq_len, head_dim // 2, 2)):
-        raise RuntimeError("rope_cs must be contiguous CUDA float32 [seq_len,rotary_dim/2,2]")
+    if rope_cs is not None:
+        if seq_len <= 0 or seq_len & (seq_len - 1):
+            raise RuntimeError("rope_seq_len must be a power of two")
+        if (not rope_cs.is_cuda or not rope_cs.is_contiguous() or rope_cs.dtype != torch.float32
+                or tuple(rope_cs.shape) != (seq_len, head_dim // 2, 2)):
+            raise RuntimeError("rope_cs must be contiguous CUDA float32 [seq_len,rotary_dim/2,2]")
     ptrs = (ctypes.c_void_p * len(outs))(*[o.data_ptr() for o in outs])
     ccols = (ctypes.c_int64 * len(outs))(*cols)
     with torch.cuda.device(A.device):
         _lib.call("fp4b200_nvfp4_grouped_gemm_rope", A.data_ptr(), A_sc.data_ptr(), A_sc_global.data_ptr(), B.data_ptr(),
-                  B_sc.data_ptr(), B_sg_per_tile.data_ptr(), len(outs), ptrs, ccols, rope_cs.data_ptr(), seq_len, head_dim,
-                  int(rope_cols), int(bool(round_input_bf16)), M, N, K, _stream(A))
+                  B_sc.data_ptr(), B_sg_per_tile.data_ptr(), len(outs), ptrs, ccols,
+                  None if rope_cs is None else rope_cs.data_ptr(), seq_len, head_dim, int(rope_cols),
+                  int(bool(round_input_bf16)), int(silu_dim), M, N, K, _stream(A))
 
 
 def nvfp4_grouped_gemm_rope_live64(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K, D_V, rope_cs, rope_seq_len,
                                    silu_dim=0):
     """nvfp4_b200_gemm.cu:1338-1368 — fused QKV projection, rotary embedding (heads of 64) on the Q and K outputs in
     the epilogue, V untouched; rope_cs [seq_len, 32, 2]."""
-    if silu_dim:
-        raise RuntimeError("nvfp4_grouped_gemm_rope_live64: the SiLU epilogue (silu_dim > 0) is not built")
     _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, [D, D_K, D_V], rope_cs, rope_seq_len, 64,
-                       D.shape[1] + D_K.shape[1], False)
+                       D.shape[1] + D_K.shape[1], False, silu_dim)
 
 
 def nvfp4_grouped_gemm_rope_packed_split(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K, D_V, rope_cs, rope_seq_len,

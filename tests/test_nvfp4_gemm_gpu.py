@@ -171,3 +171,43 @@ def test_grouped_gemm_with_rope_epilogue(M):
         gemm.nvfp4_grouped_gemm_rope_packed_split(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, seq, 128, 64)
     with pytest.raises(RuntimeError):
         gemm.nvfp4_grouped_gemm_rope_live64(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, 96)
+
+
+@pytest.mark.parametrize("M", [256, 128])
+def test_grouped_gemm_silu_epilogue(M):
+    """silu_dim: x / (1 + exp(-x)) on the first output columns in the epilogue (hardware __expf: one bf16 step against
+    the oracle), the remaining columns the plain bf16 rounding; with the heads-of-64 rotation behind it."""
+    gemm = mod("tk_gemm_c")
+    K, N, silu_dim, seq = 512, 768, 256, 128
+    x, w, qx, qw = _quant_pair(M, N, K, seed=M + 23)
+    b_sg = qw[4].expand(N // 256).contiguous()
+    d32 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], qw[0], qw[1], qw[4], d32)
+    d = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gemm.nvfp4_grouped_gemm(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, d, None, None, silu_dim)
+    torch.cuda.synchronize()
+    assert_status_ok()
+    v = d32.cpu().numpy()
+    got = d.float().cpu().numpy()
+    assert np.array_equal(got[:, silu_dim:], o.bf16_round(v[:, silu_dim:]))
+    with np.errstate(over="ignore"):
+        act = (v[:, :silu_dim] / (np.float32(1.0) + np.exp(-v[:, :silu_dim]).astype(np.float32))).astype(np.float32)
+    ref = o.bf16_round(act)
+    step = np.maximum(np.abs(ref), 2.0 ** -100) * 2.0 ** -7
+    assert (np.abs(got[:, :silu_dim] - ref) <= step).all() and (got[:, :silu_dim] == ref).mean() > 0.99
+    # SiLU, then the rotation of Q and K (heads of 64)
+    rng = np.random.default_rng(5)
+    ang = rng.uniform(0, 2 * np.pi, size=(seq, 32)).astype(np.float32)
+    cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+    dq, dk, dv = (torch.empty((M, 256), dtype=torch.bfloat16, device="cuda") for _ in range(3))
+    gemm.nvfp4_grouped_gemm_rope_live64(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, torch.from_numpy(cs).cuda(),
+                                        seq, silu_dim)
+    torch.cuda.synchronize()
+    assert_status_ok()
+    v2 = v.copy()
+    v2[:, :silu_dim] = act
+    ref2 = o.rope_epilogue(v2, cs, 64, 512, False)
+    got2 = torch.cat([dq, dk, dv], dim=1).float().cpu().numpy()
+    assert np.array_equal(got2[:, 512:], ref2[:, 512:]) and np.array_equal(got2[:, 256:512], ref2[:, 256:512])
+    tol = np.maximum(np.abs(ref2[:, :256]), np.abs(act).max() * 2.0 ** -8) * 2.0 ** -6
+    assert (np.abs(got2[:, :256] - ref2[:, :256]) <= tol).all()
