@@ -73,12 +73,17 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
  * rht_row / rht_col: per-16 Hadamard transform (x0.25, rounded to bf16) along K for the row operand /
  * along M for the column operand, optionally after a sign flip hashed from (sign_seed, sign_subseq,
  * coordinate) (tk_quantize.cu:483-488,620-627).  gamma/inv_rms non-NULL fuse RMSNorm.  return_row = 0
- * writes no row-wise output but keeps its words in the random stream.  Scale stochastic rounding is
- * not built. */
+ * writes no row-wise output but keeps its words in the random stream.  scale_sr: the E4M3 scale byte of
+ * every block is rounded stochastically by one more word of the same stream, drawn before the block's data
+ * words (quantize_transpose_tuned.cuh:205-254); with data_sr 2 / 3 the row pass follows the row-only launch
+ * at rng_offset and the column pass the column launch at rng_offset_col, as above.  The reference draws no
+ * scale word for an encode-centric block whose maximum is <= 1e-9; here every block draws one, so streams
+ * differ from the reference's behind such a block of the same 128x128 chunk.  scale_sr needs 16-byte
+ * aligned outputs. */
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
-                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
                                void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream);
 
 /* Tensor amax (and sg) of the per-16 Hadamard transform of x along K (along_k != 0) or along M,

@@ -54,6 +54,14 @@ __device__ __forceinline__ uint8_t f32_to_e4m3(float v) {
   return (uint8_t)__nv_cvt_float_to_fp8(v, __NV_SATFINITE, __NV_E4M3);
 }
 
+// fp32 -> E4M3 with stochastic rounding by the low 16 bits of rbits (the hardware adds them to the 16 leading
+// discarded bits of the value's position between its two neighbours and rounds up on carry); saturating.
+__device__ __forceinline__ uint8_t f32_to_e4m3_sr(float v, uint32_t rbits) {
+  uint32_t p;
+  asm("cvt.rs.satfinite.e4m3x4.f32 %0, {%1, %1, %1, %1}, %2;" : "=r"(p) : "f"(v), "r"(rbits));
+  return (uint8_t)(p & 0xFFu);
+}
+
 __device__ __forceinline__ float e4m3_to_f32(uint8_t b) {
   __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)b, __NV_E4M3);
   return __half2float(__half(h));

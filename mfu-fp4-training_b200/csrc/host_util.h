@@ -47,6 +47,7 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dtype, 
 // Options of the stochastic-rounding / Hadamard variants of the NVFP4 quantiser (one launch).
 struct QuantOpt {
   int sr_row, sr_col;        // data stochastic rounding of the row pass / of the column pass
+  int scale_sr;              // stochastic rounding of the E4M3 scale byte (one more random word per block, drawn first)
   int row_per_stage;         // 0: by the launch's shape; 8: the row pass follows a row-only launch's random stream
   int rht_row, rht_col;      // 16-point Hadamard transform along K (row operand) / along M (column operand)
   int sign;                  // seeded sign flip before the transform

@@ -403,6 +403,7 @@ struct QuantArgs {
   int row_pitch_bytes;     // > 0: pitch of the row-wise code matrix (it is a column slice of a wider one; strip kernel only)
   // ---- OPT instantiations only (stochastic rounding / 16-point Hadamard transform) ----
   int opt_sr_row, opt_sr_col;   // data stochastic rounding of the row pass / of the column pass
+  int opt_scale_sr;             // stochastic rounding of the scale byte: every block draws one word before its data words
   int opt_row_per_stage;   // random words per 64x64 stage in the row pass's stream: 16 (launch with a column pass) or 8
   int opt_rht_row, opt_rht_col;   // per-16 Hadamard transform along K (row operand) / along M (column operand)
   int opt_sign;            // seeded sign flip before the transform
@@ -436,6 +437,16 @@ __device__ __forceinline__ uint32_t block_code(float b, float s_enc) {
   }
 }
 
+// The same value as block_code rounds, rounded stochastically by the block's first random word
+// (reference: quantize_transpose_tuned.cuh:205-254).
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ uint32_t block_code_sr(float b, float s_enc, uint32_t rbits) {
+  if constexpr (ENCODE_CENTRIC) {
+    return (b <= 1.0e-9f) ? 0x7Eu : (uint32_t)f32_to_e4m3_sr(fminf(6.0f / (b * s_enc), kFltMax), rbits);
+  } else {
+    return (uint32_t)f32_to_e4m3_sr(fminf(b / 6.0f * s_enc, kFltMax), rbits);
+  }
+}
 
 // ---- helpers of the OPT instantiations ------------------------------------------------------
 
@@ -454,6 +465,20 @@ __device__ __forceinline__ uint4 philox4x32_10(unsigned long long seed, unsigned
     kx += 0x9E3779B9u; ky += 0xBB67AE85u;
   }
   return make_uint4(c0, c1, c2, c3);
+}
+
+// Random words of the draws n0 .. n0 + count - 1 (count <= 5) of one thread's stream: draw n is component n & 3 of the
+// Philox block at counter offset + (n >> 2) (the reference refills its four words when the fourth has been used,
+// core.cuh:116-127).
+__device__ __forceinline__ void philox_draws(unsigned long long seed, unsigned long long seq, unsigned long long offset, int n0,
+                                             int count, uint32_t (&out)[5]) {
+  const uint4 b0 = philox4x32_10(seed, seq, offset + (unsigned long long)(n0 >> 2));
+  const bool two = ((n0 + count - 1) >> 2) != (n0 >> 2);
+  const uint4 b1 = two ? philox4x32_10(seed, seq, offset + (unsigned long long)((n0 >> 2) + 1)) : b0;
+  const uint32_t w[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+  const int sh = n0 & 3;
+#pragma unroll
+  for (int i = 0; i < 5; ++i) out[i] = sh == 0 ? w[i] : (sh == 1 ? w[i + 1] : (sh == 2 ? w[i + 2] : w[i + 3]));   // registers only
 }
 
 // +1 / -1 per coordinate along the transformed axis (reference: tk_quantize.cu:483-488,620-627)
@@ -505,7 +530,8 @@ __device__ __forceinline__ uint2 quant16_rn(const float (&x)[16], float coeff) {
 template <bool ENCODE_CENTRIC>
 __device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, bool sign, unsigned long long sign_seed,
                                            unsigned long long sign_subseq, unsigned long long coord0, float s_enc,
-                                           const ScaleLut* lut, bool sr, const uint32_t (&wsel)[4], uint32_t& stored) {
+                                           const ScaleLut* lut, bool sr, const uint32_t (&wsel)[4], uint32_t& stored,
+                                           bool scale_sr = false, uint32_t scale_rbits = 0) {
   if (rht) {
     if (sign) {
 #pragma unroll
@@ -518,7 +544,7 @@ __device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, bool sign, 
   float bm = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(x[i]));
-  const ScaleLut e = lut[block_code<ENCODE_CENTRIC>(bm, s_enc)];
+  const ScaleLut e = lut[scale_sr ? block_code_sr<ENCODE_CENTRIC>(bm, s_enc, scale_rbits) : block_code<ENCODE_CENTRIC>(bm, s_enc)];
   stored = e.stored;
   return sr ? quant16_sr(x, e.coeff, wsel) : quant16_rn(x, e.coeff);
 }
@@ -1036,23 +1062,34 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             for (int q = 0; q < 8; ++q) { x[2 * q] = bf16lo_to_f32(w[8 * b + q]); x[2 * q + 1] = bf16hi_to_f32(w[8 * b + q]); }
             const int lc0 = wh * kStripCols + b * 16;   // first column of the block inside the chunk
             uint32_t wsel[4] = {0, 0, 0, 0};
-            if (a.opt_sr_row) {
+            uint32_t scale_rbits = 0;
+            if (a.opt_sr_row || a.opt_scale_sr) {
               const int stage = (rc >> 6) * 2 + (lc0 >> 6);
               const int lr = rc & 63, it_ref = lr >> 5;
               const int tid_ref = (lr & 31) * 4 + ((lc0 & 63) >> 4);
               const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
-              const uint4 rw = philox4x32_10(a.rng_seed, seq,
-                                             a.rng_offset + (unsigned long long)((stage * a.opt_row_per_stage + it_ref * 4) >> 2));
-              const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
               const int bg = (tid_ref & 31) >> 4;
+              if (a.opt_scale_sr) {
+                // q words per block (scale first, then the data words); the stage holds 2 (row-only launch) or 4 blocks
+                const int q = 1 + (a.opt_sr_row ? 4 : 0);
+                uint32_t dr[5];
+                philox_draws(a.rng_seed, seq, a.rng_offset, stage * (a.opt_row_per_stage >> 2) * q + it_ref * q, q, dr);
+                scale_rbits = dr[0];
 #pragma unroll
-              for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
+                for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bg) & 1) ? dr[3 + (g & 1)] : dr[1 + (g & 1)];
+              } else {
+                const uint4 rw = philox4x32_10(a.rng_seed, seq,
+                                               a.rng_offset + (unsigned long long)((stage * a.opt_row_per_stage + it_ref * 4) >> 2));
+                const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
+#pragma unroll
+                for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
+              }
             }
             uint32_t stored;
             const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
                                                        (unsigned long long)(col0 + b * 16), s_enc_row, lut_row,
-                                                       a.opt_sr_row != 0, wsel, stored);
+                                                       a.opt_sr_row != 0, wsel, stored, a.opt_scale_sr != 0, scale_rbits);
             codes[2 * b] = cd.x;
             codes[2 * b + 1] = cd.y;
             sc_word |= stored << (8 * b);
@@ -1106,18 +1143,28 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
 #pragma unroll
             for (int i = 0; i < 16; ++i) x[i] = wq ? bf16hi_to_f32(w[i]) : bf16lo_to_f32(w[i]);
             uint32_t wsel[4] = {0, 0, 0, 0};
-            if (a.opt_sr_col) {
+            uint32_t scale_rbits = 0;
+            if (a.opt_sr_col || a.opt_scale_sr) {
               const int stage = (grp16 >> 2) * 2 + wh;
               const int tid_ref = (((grp16 & 3) - (lane & 3)) & 3) * 32 + lane;
               const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
-              const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
-              wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
+              if (a.opt_scale_sr) {
+                // the stage's two row blocks (drawn or skipped over by the launch this pass belongs to), then its two column blocks
+                const int q = 1 + (a.opt_sr_col ? 4 : 0);
+                uint32_t dr[5];
+                philox_draws(a.rng_seed, seq, a.rng_offset_col, stage * 4 * q + 2 * q + wq * q, q, dr);
+                scale_rbits = dr[0];
+                wsel[0] = dr[1]; wsel[1] = dr[2]; wsel[2] = dr[3]; wsel[3] = dr[4];
+              } else {
+                const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
+                wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
+              }
             }
             uint32_t stored;
             const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
                                                        (unsigned long long)(cm * kChunk + grp16 * 16), s_enc_col, lut_col,
-                                                       a.opt_sr_col != 0, wsel, stored);
+                                                       a.opt_sr_col != 0, wsel, stored, a.opt_scale_sr != 0, scale_rbits);
             if (wq == 0) { cc0[2 * g] = cd.x; cc0[2 * g + 1] = cd.y; sc0 |= stored << (8 * g); }
             else { cc1[2 * g] = cd.x; cc1[2 * g + 1] = cd.y; sc1 |= stored << (8 * g); }
           }
@@ -1357,6 +1404,7 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
     return set_error("head-major input: plain quantisation into 16-byte aligned outputs only");
   if (opt != nullptr) {
     a.opt_sr_row = opt->sr_row; a.opt_sr_col = opt->sr_col; a.rng_offset_col = opt->rng_offset_col;
+    a.opt_scale_sr = opt->scale_sr;
     a.opt_row_per_stage = opt->row_per_stage ? opt->row_per_stage : (col_fp4 != nullptr ? 16 : 8);
     a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
@@ -1367,6 +1415,7 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
       return norm ? launch_quantize_strip_t<false, true, true>(x, a, st, behind_pass1)
                   : launch_quantize_strip_t<false, false, true>(x, a, st, behind_pass1);
     }
+    if (a.opt_scale_sr) return set_error("scale stochastic rounding needs 16-byte aligned outputs (strip quantiser only)");
     if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st, behind_pass1)
                                     : launch_quantize_t<true, false, false, true>(tmap, a, st, behind_pass1);
     return norm ? launch_quantize_t<false, true, false, true>(tmap, a, st, behind_pass1)
@@ -1555,9 +1604,8 @@ int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const f
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
-                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, void* row_fp4,
-                               void* row_sc,
-                               void* col_fp4, void* col_sc, void* stream) {
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
+                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_quantize_opt")) return rc;
   if (!amax_row) return set_error("nvfp4_quantize_opt: amax_row is required");
   if ((gamma_bf16 == nullptr) != (inv_rms == nullptr))
@@ -1570,8 +1618,9 @@ int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const
   if (data_sr < 0 || data_sr > 3) return set_error("nvfp4_quantize_opt: data_sr must be 0 (off), 1 (both passes), 2 (row pass) or 3 (column pass)");
   o.sr_row = data_sr == 1 || data_sr == 2; o.sr_col = data_sr == 1 || data_sr == 3;
   // a row-only stochastic launch of the reference draws 8 words per stage, also when this launch adds the column pass
-  o.row_per_stage = data_sr == 2 ? 8 : 0;
-  o.rng_offset_col = data_sr == 1 ? rng_offset : rng_offset_col;
+  o.row_per_stage = (data_sr == 2 || data_sr == 3) ? 8 : 0;
+  o.scale_sr = scale_sr != 0;
+  o.rng_offset_col = (data_sr == 0 || data_sr == 1) ? rng_offset : rng_offset_col;   // one launch of the reference: one stream
   o.rht_row = rht_row != 0; o.rht_col = rht_col != 0; o.sign = with_sign != 0;
   o.return_row = return_row != 0; o.rng_seed = rng_seed; o.rng_offset = rng_offset;
   o.sign_seed = sign_seed; o.sign_subseq = sign_subseq;

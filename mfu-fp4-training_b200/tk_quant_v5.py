@@ -460,7 +460,7 @@ def _amax_rht(x, along_k, sign, seed, subseq, gamma=None, inv_rms=None):
 
 
 def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row_rht, col_rht, return_row, seed, offset,
-                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None, sr_mode=None, offset_col=0):
+                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None, sr_mode=None, offset_col=0, scale_sr=False):
     """One launch, the counterpart of tk_quantize_transpose (tk_quantize.cu:3807-3926).  ``sr_mode`` 2 / 3:
     stochastic rounding on the row pass only (the bytes of the reference's row-only launch at ``offset``) /
     on the column pass only (at ``offset_col``), the other pass rounded to nearest in the same launch."""
@@ -474,8 +474,8 @@ def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row
               amax_col.data_ptr(), int(bool(encode_centric)), int(bool(sr)) if sr_mode is None else int(sr_mode),
               int(bool(row_rht)), int(bool(col_rht)),
               int(bool(sign)), int(sign_seed) & _U64, int(sign_subseq) & _U64, int(bool(return_row)),
-              int(seed) & _U64, int(offset) & _U64, int(offset_col) & _U64, _p(row_fp4), _p(row_sc), _p(col_fp4),
-              _p(col_sc), _stream(x))
+              int(seed) & _U64, int(offset) & _U64, int(offset_col) & _U64, int(bool(scale_sr)), _p(row_fp4), _p(row_sc),
+              _p(col_fp4), _p(col_sc), _stream(x))
     return row_fp4, row_sc, col_fp4, col_sc
 
 
@@ -484,16 +484,14 @@ def tk_quantize_transpose(input, amax_row, amax_col, return_transpose, stochasti
     """tk_quantize.cu:3807-3926 — quantise with pre-computed device amaxes; ``rng_state`` = int64[2] tensor
     ``[seed, offset]``.  Returns (row_fp4, row_sc, col_fp4, col_sc) as uint8 tensors."""
     _check_bf16_2d(input, "input")
-    if scale_stochastic_rounding:
-        raise RuntimeError("tk_quantize_transpose: scale stochastic rounding is not built")
     seed = offset = 0
-    if stochastic_rounding:
+    if stochastic_rounding or scale_stochastic_rounding:
         if rng_state is None or rng_state.numel() < 2:
             raise RuntimeError("rng_state [seed, offset] is required with stochastic rounding")
         seed, offset = (int(v) & _U64 for v in rng_state.cpu().tolist()[:2])
     with torch.cuda.device(input.device):
         out = _launch_opt(input, amax_row, amax_col, return_transpose, stochastic_rounding, encode_centric, row_rht,
-                          col_rht, return_row, seed, offset, False, 0, 0)
+                          col_rht, return_row, seed, offset, False, 0, 0, scale_sr=scale_stochastic_rounding)
     empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
     return tuple(empty if t is None else t for t in out)
 
@@ -502,10 +500,9 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
                              scale_stochastic_rounding=False, rht_axes="none", with_random_sign_mask=False, rng_seed=0,
                              rng_subsequence=0, global_scale_target=448.0, data_sr_axes="both"):
     """tk_quantize.cu:4299-4540 — returns (row_fp4, row_sc, col_fp4, col_sc, row_sg, col_sg).  Same choice of
-    amaxes, number of launches and Philox offsets as the reference; scale stochastic rounding is not built."""
+    amaxes, number of launches and Philox offsets as the reference."""
     M, K = _check_bf16_2d(input, "input")
-    if scale_stochastic_rounding:
-        raise RuntimeError("tk_quantize_for_gemm_opt: scale stochastic rounding is not built")
+    scale_sr = bool(scale_stochastic_rounding)
     if not (0.0 < float(global_scale_target) <= 512.0):
         raise RuntimeError(f"global_scale_target must be finite and in (0, 512], got {global_scale_target}")
     row_rht, col_rht = _norm_axes(rht_axes)
@@ -514,10 +511,10 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
     axes = _norm_sr_axes(data_sr_axes)
     row_sr = bool(data_stochastic_rounding) and axes in ("row", "both")
     col_sr = bool(data_stochastic_rounding) and axes in ("col", "both")
-    if not (row_rht or col_rht or row_sr or col_sr) and float(global_scale_target) == 448.0:
+    if not (row_rht or col_rht or row_sr or col_sr or scale_sr) and float(global_scale_target) == 448.0:
         base = tk_quantize_for_gemm(input, return_transpose, encode_centric)
         return base[:6]
-    use_sr = row_sr or col_sr
+    use_sr = row_sr or col_sr or scale_sr
     sign = bool(with_random_sign_mask)
     with torch.cuda.device(input.device):
         plain = None
@@ -537,7 +534,7 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
         if return_transpose and not row_mat and row_sr == col_sr and not col_mat:
             off = _next_offset(input, rng_subsequence, use_sr)
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr, encode_centric, row_rht, col_rht,
-                                         True, rng_seed, off, sign, rng_seed, rng_subsequence)
+                                         True, rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)
         elif return_transpose and not row_mat and not col_mat:
             # the reference serves "one axis stochastic" with a row launch and a column launch, each taking
             # an offset; here one launch reads the input once and produces the same bytes
@@ -545,16 +542,16 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
             off_c = _next_offset(input, rng_subsequence, use_sr)
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, True, encode_centric, row_rht, col_rht, True,
                                          rng_seed, off_r, sign, rng_seed, rng_subsequence, sr_mode=2 if row_sr else 3,
-                                         offset_col=off_c)
+                                         offset_col=off_c, scale_sr=scale_sr)
         else:
             off = _next_offset(input, rng_subsequence, use_sr)
             rf, rs, _, _ = _launch_opt(input, row_amax, row_amax, False, row_sr, encode_centric, row_rht, False, True,
-                                       rng_seed, off, sign, rng_seed, rng_subsequence)
+                                       rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)
             cf = cs = None
             if return_transpose:
                 off = _next_offset(input, rng_subsequence, use_sr)
                 _, _, cf, cs = _launch_opt(input, col_amax, col_amax, True, col_sr, encode_centric, False, col_rht,
-                                           False, rng_seed, off, sign, rng_seed, rng_subsequence)
+                                           False, rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)
     empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
     row_sg = row_amax.narrow(0, 1, 1)
     col_sg = col_amax.narrow(0, 1, 1) if return_transpose else row_sg
@@ -574,20 +571,19 @@ def tk_fused_norm_quantize_opt(input, gamma, epsilon, return_transpose=True, enc
         raise RuntimeError("tk_fused_norm_quantize_opt currently supports the regular-TK QKV row-RHT contract only")
     if with_random_sign_mask:
         raise RuntimeError("tk_fused_norm_quantize_opt does not yet fuse random-sign RHT")
-    if scale_stochastic_rounding:
-        raise RuntimeError("tk_fused_norm_quantize_opt: scale stochastic rounding is not built")
     if gamma.dtype != torch.bfloat16 or gamma.numel() != K or not gamma.is_contiguous() or gamma.device != input.device:
         raise RuntimeError("gamma must be contiguous CUDA bfloat16 [K] on the input device")
     sr = bool(data_stochastic_rounding)
+    scale_sr = bool(scale_stochastic_rounding)
     with torch.cuda.device(input.device):
         inv_rms = torch.empty(M, dtype=torch.float32, device=input.device)
         col_amax = torch.empty(2, dtype=torch.float32, device=input.device)
         _lib.call("fp4b200_nvfp4_rmsnorm_stats", input.data_ptr(), gamma.data_ptr(), float(epsilon), M, K,
                   inv_rms.data_ptr(), 1, col_amax.data_ptr(), _stream(input))
         row_amax = _amax_rht(input, True, False, 0, 0, gamma, inv_rms)
-        off = _next_offset(input, rng_subsequence, sr)
+        off = _next_offset(input, rng_subsequence, sr or scale_sr)
         rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, sr, encode_centric, True, False, True, rng_seed,
-                                     off, False, 0, 0, gamma, inv_rms)
+                                     off, False, 0, 0, gamma, inv_rms, scale_sr=scale_sr)
     return (rf.view(_FP4), rs.view(_E4M3), cf.view(_FP4), cs.view(_E4M3), row_amax.narrow(0, 1, 1),
             col_amax.narrow(0, 1, 1), inv_rms)
 

@@ -173,7 +173,22 @@ def nvfp4_global_decode_scale(amax) -> np.float32:
     return np.float32(np.float32(amax) / np.float32(2688.0))
 
 
-def nvfp4_block_scale(block_amax: np.ndarray, s_enc, mode: str):
+def e4m3_encode_sr(v: np.ndarray, rbits: np.ndarray) -> np.ndarray:
+    """``cvt.rs.satfinite.e4m3x4.f32`` on non-negative inputs, first result byte: the value's position between its two
+    E4M3 neighbours, as a 16-bit fraction, plus the low 16 bits of the random word, rounds up on carry (model
+    measured on a B200: single-bit sweeps of all 32 random bits against all 20 discarded mantissa bits, then random
+    cases); 448 and above saturate."""
+    v = np.asarray(v, dtype=np.float64)
+    grid = e4m3_decode(np.arange(0x7F, dtype=np.uint8)).astype(np.float64)      # 0 .. 448, ascending
+    idx = np.clip(np.searchsorted(grid, v, side="right") - 1, 0, 0x7E - 1)
+    lo, hi = grid[idx], grid[idx + 1]
+    k = np.floor((v - lo) / (hi - lo) * 65536.0).astype(np.int64)
+    up = (k + (np.asarray(rbits).astype(np.int64) & 0xFFFF)) >= 65536
+    code = np.where(up, idx + 1, idx)
+    return np.where(v >= 448.0, 0x7E, code).astype(np.uint8)
+
+
+def nvfp4_block_scale(block_amax: np.ndarray, s_enc, mode: str, scale_rbits=None):
     """Per-16 block: returns (stored E4M3 byte, fp32 coefficient applied before the E2M1 cast).
 
     mode "encode": TK encode-centric (core.cuh:51-60, fused_amax_quantize.cuh:267-270):
@@ -184,6 +199,8 @@ def nvfp4_block_scale(block_amax: np.ndarray, s_enc, mode: str):
         coeff = min(1/(float(s8)*(1/S_enc)), FLT_MAX).
     mode "decode_te": the reference's CPU emulation (quantization_nvfp4.py:580-610):
         s8 = e4m3(clamp(b * (S_enc * (1/6)), 448)); same coefficient formula.
+    scale_rbits (one 32-bit word per block): the byte is rounded stochastically instead
+    (quantize_transpose_tuned.cuh:205-254).
     """
     b = np.asarray(block_amax, dtype=np.float32)
     s_enc = np.float32(s_enc)
@@ -191,7 +208,7 @@ def nvfp4_block_scale(block_amax: np.ndarray, s_enc, mode: str):
         if mode == "encode":
             m = (F32(6.0) / (b * s_enc).astype(F32)).astype(F32)
             m = np.minimum(m, FLT_MAX)
-            m8 = e4m3_encode(m)
+            m8 = e4m3_encode(m) if scale_rbits is None else e4m3_encode_sr(m, scale_rbits)
             m8 = np.where(b <= F32(1.0e-9), np.uint8(0x7E), m8).astype(np.uint8)
             mf = e4m3_decode(m8)
             coeff = (mf * s_enc).astype(F32)
@@ -204,7 +221,7 @@ def nvfp4_block_scale(block_amax: np.ndarray, s_enc, mode: str):
         else:
             raise ValueError(mode)
         s = np.minimum(s, FLT_MAX)
-        s8 = e4m3_encode(s)
+        s8 = e4m3_encode(s) if scale_rbits is None else e4m3_encode_sr(s, scale_rbits)
         s_dec = F32(F32(1.0) / s_enc)
         coeff = (F32(1.0) / (e4m3_decode(s8) * s_dec).astype(F32)).astype(F32)
         coeff = np.minimum(coeff, FLT_MAX)  # 1/0 = inf -> FLT_MAX
@@ -844,15 +861,65 @@ def _sr_words_col(M, K, seed, offset):
     return words.reshape(K, M // 4)
 
 
-def _quantize_axis_opt(x, amax, mode, rht, signs, sr_words):
-    """x [R, C] quantised along C with optional transform and stochastic rounding."""
+def _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks):
+    """The q consecutive random words every 16-element block draws when blocks draw q words each (scale word first,
+    then four data words): draw n of a thread's stream is component n & 3 of the Philox block at counter
+    offset + (n >> 2) (core.cuh:116-127).  A 64x64 stage holds ``stage_blocks`` blocks per thread before the next stage
+    starts (2 row blocks, + 2 column blocks when the launch has a column pass).  Returns uint32 [rows, blocks, q] for the
+    row operand [M, K/16] or the column operand [K, M/16]."""
+    if column_pass:
+        k = np.arange(K)[:, None]; m = np.arange(M // 16)[None, :] * 16
+        cy, cx, r, c = m // 128, k // 128, m % 128, k % 128
+        stage = (r // 64) * 2 + c // 64
+        lr, lc = r % 64, c % 64
+        lane, wq = lc // 2, lc % 2
+        tid = (((lr // 16) - lane % 4) & 3) * 32 + lane
+        n0 = stage * 4 * q + 2 * q + wq * q
+    else:
+        m = np.arange(M)[:, None]; k = np.arange(K // 16)[None, :] * 16
+        cy, cx, r, c = m // 128, k // 128, m % 128, k % 128
+        stage = (r // 64) * 2 + c // 64
+        lr, lc = r % 64, c % 64
+        tid = (lr % 32) * 4 + lc // 16
+        n0 = stage * stage_blocks * q + (lr // 32) * q
+    seq = (tid + 128 * cx + 128 * (K // 128) * cy).astype(np.uint64)
+    n0 = np.broadcast_to(n0, seq.shape)
+    out = np.empty(seq.shape + (q,), dtype=np.uint32)
+    for j in range(q):
+        n = n0 + j
+        blk = philox4x32_10(seed, seq, np.uint64(offset) + (n >> 2).astype(np.uint64))
+        out[..., j] = np.take_along_axis(blk, (n & 3)[..., None], axis=-1)[..., 0]
+    return out, tid
+
+
+def _scale_sr_words(M, K, seed, offset, column_pass, data_sr, stage_blocks):
+    """(scale word per block, data words per 4-element group or None) of a pass with scale stochastic rounding."""
+    q = 1 + (4 if data_sr else 0)
+    d, tid = _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks)
+    scale = d[..., 0]
+    if not data_sr:
+        return scale, None
+    data = d[..., 1:]
+    if column_pass:
+        return scale, data.reshape(K, M // 4)
+    bg = (tid % 32) // 16                       # which 8-element half the thread's first wave takes
+    sel = np.empty(data.shape, dtype=np.uint32)
+    for g in range(4):
+        first = (((g >> 1) - bg) & 1) == 0
+        sel[..., g] = np.where(first, data[..., g & 1], data[..., 2 + (g & 1)])
+    return scale, sel.reshape(M, K // 4)
+
+
+def _quantize_axis_opt(x, amax, mode, rht, signs, sr_words, scale_words=None):
+    """x [R, C] quantised along C with optional transform and stochastic rounding (of the codes by sr_words, of the
+    scale bytes by scale_words)."""
     x = np.asarray(x, dtype=F32)
     R, C = x.shape
     if rht:
         x = bf16_round(_fwht16_f32(x, signs))
     xb = x.reshape(R, C // 16, 16)
     b = np.abs(xb).max(axis=-1)
-    stored, coeff = nvfp4_block_scale(b, nvfp4_global_encode_scale(amax), mode)
+    stored, coeff = nvfp4_block_scale(b, nvfp4_global_encode_scale(amax), mode, scale_words)
     with np.errstate(over="ignore", invalid="ignore"):
         scaled = (xb * coeff[..., None]).astype(F32)
     if sr_words is None:
@@ -863,9 +930,11 @@ def _quantize_axis_opt(x, amax, mode, rht, signs, sr_words):
 
 
 def nvfp4_quantize_transpose_launch(x, amax_row, amax_col, return_transpose, sr, encode_centric, row_rht, col_rht,
-                                    return_row, seed=0, offset=0, sign=None):
+                                    return_row, seed=0, offset=0, sign=None, scale_sr=False):
     """One launch of the reference's tuned kernel (``tk_quantize_transpose``, tk_quantize.cu:3807-3926):
-    stochastic rounding applies to every pass of the launch; ``sign`` = (seed, subseq) or None."""
+    stochastic rounding (of the codes: ``sr``; of the scale bytes: ``scale_sr``) applies to every pass of the
+    launch; ``sign`` = (seed, subseq) or None.  An encode-centric block with maximum <= 1e-9 draws no scale word in
+    the reference; here it draws one like every other block."""
     x = np.asarray(x, dtype=F32)
     M, K = x.shape
     mode = "encode" if encode_centric else "decode"
@@ -873,21 +942,25 @@ def nvfp4_quantize_transpose_launch(x, amax_row, amax_col, return_transpose, sr,
     per_stage = 16 if return_transpose else 8
     if return_row:
         sg = rht_sign_vector(sign[0], sign[1], K) if (sign and row_rht) else None
-        words = _sr_words_row(M, K, seed, offset, per_stage) if sr else None
-        fp4, s = _quantize_axis_opt(x, amax_row, mode, row_rht, sg, words)
+        words, sw = (_sr_words_row(M, K, seed, offset, per_stage) if sr else None), None
+        if scale_sr:
+            sw, words = _scale_sr_words(M, K, seed, offset, False, sr, 4 if return_transpose else 2)
+        fp4, s = _quantize_axis_opt(x, amax_row, mode, row_rht, sg, words, sw)
         out.update(row_fp4=fp4, row_sc=swizzle_scales(s))
     if return_transpose:
         sg = rht_sign_vector(sign[0], sign[1], M) if (sign and col_rht) else None
-        words = _sr_words_col(M, K, seed, offset) if sr else None
-        fp4, s = _quantize_axis_opt(np.ascontiguousarray(x.T), amax_col, mode, col_rht, sg, words)
+        words, sw = (_sr_words_col(M, K, seed, offset) if sr else None), None
+        if scale_sr:
+            sw, words = _scale_sr_words(M, K, seed, offset, True, sr, 4)
+        fp4, s = _quantize_axis_opt(np.ascontiguousarray(x.T), amax_col, mode, col_rht, sg, words, sw)
         out.update(col_fp4=fp4, col_sc=swizzle_scales(s))
     return out
 
 
 def nvfp4_quantize_for_gemm_opt(x, return_transpose=True, encode_centric=True, data_sr=False, rht_axes="none",
                                 with_random_sign_mask=False, rng_seed=0, rng_subsequence=0, data_sr_axes="both",
-                                invocation=0):
-    """``tk_quantize_for_gemm_opt`` host logic (tk_quantize.cu:4299-4540) without scale stochastic rounding:
+                                invocation=0, scale_sr=False):
+    """``tk_quantize_for_gemm_opt`` host logic (tk_quantize.cu:4299-4540):
     which amax feeds which orientation, how many launches there are and which Philox offset each one
     gets (``rng_subsequence + n * 2**32`` with ``n`` the number of earlier SR launches on the device).
     Returns (dict of outputs incl. row_sg/col_sg, number of invocations consumed)."""
@@ -897,7 +970,7 @@ def nvfp4_quantize_for_gemm_opt(x, return_transpose=True, encode_centric=True, d
     col_rht = rht_axes in ("col", "both")
     row_sr = data_sr and data_sr_axes in ("row", "both")
     col_sr = data_sr and data_sr_axes in ("col", "both")
-    use_sr = row_sr or col_sr
+    use_sr = row_sr or col_sr or scale_sr
     sign = (rng_seed, rng_subsequence) if with_random_sign_mask else None
     sv_k = rht_sign_vector(*sign, K) if (sign and row_rht) else None
     sv_m = rht_sign_vector(*sign, M) if (sign and col_rht) else None
@@ -919,15 +992,15 @@ def nvfp4_quantize_for_gemm_opt(x, return_transpose=True, encode_centric=True, d
     out = {}
     if return_transpose and not row_materialised and row_sr == col_sr and not col_materialised:
         o = nvfp4_quantize_transpose_launch(x, row_amax, col_amax, True, row_sr, encode_centric, row_rht, col_rht, True,
-                                            rng_seed, next_offset(), sign)
+                                            rng_seed, next_offset(), sign, scale_sr)
         out.update(o)
     else:
         o = nvfp4_quantize_transpose_launch(x, row_amax, row_amax, False, row_sr, encode_centric, row_rht, False, True,
-                                            rng_seed, next_offset(), sign)
+                                            rng_seed, next_offset(), sign, scale_sr)
         out.update(o)
         if return_transpose:
             o = nvfp4_quantize_transpose_launch(x, col_amax, col_amax, True, col_sr, encode_centric, False, col_rht,
-                                                False, rng_seed, next_offset(), sign)
+                                                False, rng_seed, next_offset(), sign, scale_sr)
             out.update(o)
     out["row_sg"] = nvfp4_global_decode_scale(row_amax)
     out["col_sg"] = nvfp4_global_decode_scale(col_amax) if return_transpose else out["row_sg"]

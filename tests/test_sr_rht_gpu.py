@@ -81,20 +81,22 @@ def test_sr_large_tensor_statistics():
     assert_status_ok()
 
 
-def test_fused_norm_quantize_opt_row_rht_sr():
+@pytest.mark.parametrize("data_sr,scale_sr", [(True, False), (True, True), (False, True)])
+def test_fused_norm_quantize_opt_row_rht_sr(data_sr, scale_sr):
     tkq = mod("tk_quant_v5")
     M, K = 256, 512
     x = o.make_activations(M, K, seed=41)
     g = o.make_gamma(K, seed=42)
     tkq.tk_set_sr_invocation_count(0)
-    out = tkq.tk_fused_norm_quantize_opt(to_dev_bf16(x), to_dev_bf16(g), 1e-5, True, False, True, False, "row", False,
-                                         7, 9)
+    out = tkq.tk_fused_norm_quantize_opt(to_dev_bf16(x), to_dev_bf16(g), 1e-5, True, False, data_sr, scale_sr, "row",
+                                         False, 7, 9)
     torch.cuda.synchronize()
     inv = out[6].cpu().numpy()
     n = o.rmsnorm_apply(x, inv, g)
     row_amax = o.rht16_amax(n, True)
     col_amax = o.tensor_amax(n)
-    ref = o.nvfp4_quantize_transpose_launch(n, row_amax, col_amax, True, True, False, True, False, True, 7, 9)
+    ref = o.nvfp4_quantize_transpose_launch(n, row_amax, col_amax, True, data_sr, False, True, False, True, 7, 9,
+                                            scale_sr=scale_sr)
     _cmp(out, ref)
     assert out[4].item() == o.nvfp4_global_decode_scale(row_amax)
     assert out[5].item() == o.nvfp4_global_decode_scale(col_amax)
@@ -126,4 +128,59 @@ def test_silu_deriv_opt_row_rht_sr(axes):
         _cmp(out[base:base + 4], ref)
         assert out[base + 4].item() == o.nvfp4_global_decode_scale(row_amax)
         assert out[base + 5].item() == o.nvfp4_global_decode_scale(orig)
+    assert_status_ok()
+
+
+SCALE_SR_CASES = [
+    dict(data_sr=False, rht="none", sign=False, axes="both", rt=True),
+    dict(data_sr=True, rht="none", sign=False, axes="both", rt=True),
+    dict(data_sr=True, rht="none", sign=False, axes="row", rt=True),
+    dict(data_sr=True, rht="none", sign=False, axes="col", rt=True),
+    dict(data_sr=False, rht="none", sign=False, axes="both", rt=False),
+    dict(data_sr=True, rht="col", sign=True, axes="both", rt=True),
+]
+
+
+@pytest.mark.parametrize("case", SCALE_SR_CASES)
+@pytest.mark.parametrize("ec", [True, False])
+def test_scale_stochastic_rounding(case, ec):
+    """Stochastic rounding of the E4M3 scale bytes (one more random word per block, drawn before the block's data
+    words), alone and together with data SR on both axes or one: bytes identical to the oracle's replay of the
+    reference's stream with the measured model of ``cvt.rs.satfinite.e4m3x4.f32``.  No block of the input is all
+    zero (there the reference, encode-centric, would draw one word fewer)."""
+    tkq = mod("tk_quant_v5")
+    M, K = 256, 384
+    x = o.make_activations(M, K, seed=23)
+    seed, subseq = 0xFEDCBA987, 5
+    tkq.tk_set_sr_invocation_count(11)
+    out = tkq.tk_quantize_for_gemm_opt(to_dev_bf16(x), case["rt"], ec, case["data_sr"], True, case["rht"], case["sign"],
+                                       seed, subseq, 448.0, case["axes"])
+    torch.cuda.synchronize()
+    ref, used = o.nvfp4_quantize_for_gemm_opt(x, case["rt"], ec, case["data_sr"], case["rht"], case["sign"], seed, subseq,
+                                              case["axes"], invocation=11, scale_sr=True)
+    _cmp(out, ref)
+    assert tkq.tk_sr_invocation_count() == 11 + used
+    # the scale bytes do move: a good part of them differs from the round-to-nearest launch
+    plain, _ = o.nvfp4_quantize_for_gemm_opt(x, case["rt"], ec, case["data_sr"], case["rht"], case["sign"], seed, subseq,
+                                             case["axes"], invocation=11)
+    assert (ref["row_sc"] != plain["row_sc"]).mean() > 0.05
+    assert_status_ok()
+
+
+def test_scale_sr_is_unbiased_on_a_large_tensor():
+    """Decode-centric scale SR on 2 M blocks: the mean of the decoded scale bytes matches the mean of the unrounded
+    scales far better than round-to-nearest's systematic offset allows it to."""
+    tkq = mod("tk_quant_v5")
+    M, K = 2048, 16384
+    g = torch.Generator(device="cuda").manual_seed(2)
+    x = torch.randn((M, K), generator=g, device="cuda").to(torch.bfloat16)
+    out = tkq.tk_quantize_for_gemm_opt(x, False, False, False, True, "none", False, 99, 0, 448.0, "both")
+    torch.cuda.synchronize()
+    amax = x.float().abs().max().item()
+    s_enc = np.float32(2688.0) / np.float32(amax)
+    b = x.float().abs().view(M, K // 16, 16).amax(dim=-1).cpu().numpy()
+    exact = b.astype(np.float64) / 6.0 * float(s_enc)
+    sc = o.e4m3_decode(o.unswizzle_scales(u8(out[1]), M, K // 16)).astype(np.float64)
+    rel = abs(sc.mean() - exact.mean()) / exact.mean()
+    assert rel < 2e-4, rel
     assert_status_ok()
