@@ -302,6 +302,10 @@ __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
   return !g.out_fp32 && g.accum_f32 == nullptr;
 }
 
+// x / (1 + exp(-x)) with the hardware exponential and approximate division: no slow-path branch, so the 256
+// unrolled uses in the drain loops stay a few instructions each.
+__device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
+
 // Epilogue for bf16 outputs in two phases.  Phase 1 drains the warp's quadrant of the accumulator
 // (256 columns): the first 128 columns go straight into the warp's two staging buffers, the other
 // 128 into 64 registers of packed bf16 — the load of the next 32 columns is in flight while the
@@ -309,7 +313,7 @@ __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
 // overwrite the accumulator.  Phase 2 (TMA stores of the staged half, then staging and stores of the
 // register half) runs while the next tile's MMAs are already issuing, which is what the single
 // accumulator (256 + scale columns fill tensor memory) would otherwise forbid.
-template <bool ROPE, typename Release>
+template <bool ROPE, bool SILU, typename Release>
 __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t tmem,
                                                    uint8_t* epi, int row0, int tn, float a_sg, int quad, int lane,
                                                    Release release) {
@@ -343,7 +347,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   // Rotary embedding of 16 columns (eight pairs): (cos, sin) of this lane's token row and of the pairs' positions
   // inside their head are 64 contiguous bytes of the table (head_dim >= 16).  even' = fma(x, cos, -(y*sin)),
   // odd' = fma(y, cos, x*sin).
-  const bool rope_tile = ROPE && g.rope_cs != nullptr && col0 < g.rope_col_end;   // ROPE: a rotation and / or SiLU is requested
+  const bool rope_tile = ROPE && col0 < g.rope_col_end;   // rope_col_end is 0 when there is no table (SiLU alone)
   const float2* cs_row = rope_tile ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
   auto load_cs = [&](float4 (&cs)[4], int col) {
     const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
@@ -387,7 +391,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
     }
     uint32_t w[16];
     const float2 gs2 = make_float2(gs, gs);
-    const bool silu_chunk = ROPE && col0 + c * 32 < g.silu_col_end;
+    const bool silu_chunk = SILU && col0 + c * 32 < g.silu_col_end;
     if (rope_tile && !g.rope_round_bf16) {
       // rotation of the unrounded scaled accumulator: has to happen here, where the fp32 values are
 #pragma unroll
@@ -399,7 +403,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
           const uint32_t lo = (c & 1) ? rb[16 * h + 2 * q] : ra[16 * h + 2 * q];
           const uint32_t hi = (c & 1) ? rb[16 * h + 2 * q + 1] : ra[16 * h + 2 * q + 1];
           float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
-          if (silu_chunk) v = make_float2(v.x / (1.0f + __expf(-v.x)), v.y / (1.0f + __expf(-v.y)));
+          if constexpr (SILU) { if (silu_chunk) v = make_float2(silu_fast(v.x), silu_fast(v.y)); }
           const float cc = (q & 1) ? cs[q >> 1].z : cs[q >> 1].x, sn = (q & 1) ? cs[q >> 1].w : cs[q >> 1].y;
           w[8 * h + q] = rotate_pair(v.x, v.y, cc, sn);
         }
@@ -410,7 +414,7 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
         const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
         const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
         float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
-        if (ROPE && silu_chunk) v = make_float2(v.x / (1.0f + __expf(-v.x)), v.y / (1.0f + __expf(-v.y)));
+        if constexpr (SILU) { if (silu_chunk) v = make_float2(silu_fast(v.x), silu_fast(v.y)); }
         w[q] = f32x2_to_bf16x2(v.x, v.y);
       }
       // packed forms: both halves are rotated after the accumulator's release (the staged half in place)
@@ -712,10 +716,12 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (lane == 0) mbar_arrive(&sm.acc_empty);
       };
       if (epilogue_is_bf16_plain(g)) {
-        if (g.rope_cs != nullptr || g.silu_col_end > 0)
-          epilogue_tile_bf16<true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+        if (g.silu_col_end > 0)
+          epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+        else if (g.rope_cs != nullptr)
+          epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
         else
-          epilogue_tile_bf16<false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+          epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
       } else {
         epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
         release();

@@ -270,11 +270,14 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       };
       if (epilogue_is_bf16_plain(g)) {
-        if (g.rope_cs != nullptr || g.silu_col_end > 0)
-          epilogue_tile_bf16<true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
+        if (g.silu_col_end > 0)
+          epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
+                                   lane, release);
+        else if (g.rope_cs != nullptr)
+          epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
                                    lane, release);
         else
-          epilogue_tile_bf16<false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
+          epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
                                     lane, release);
       } else {
         epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad, lane);

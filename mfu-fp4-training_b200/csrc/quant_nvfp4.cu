@@ -890,36 +890,51 @@ constexpr int kStripWarps = 16;
 constexpr int kStripDepth = 2;          // input slots per warp: one being processed, one in flight
 constexpr int kStripStageBytes = 1024;  // per warp: row codes of one strip awaiting their TMA store
 
-__host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm) {
-  return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes) + 2 * 128 * sizeof(ScaleLut) +
-         (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + 16 + (size_t)k_norm * sizeof(float) + 1024;
+constexpr int kStripColStageBytes = 2048;   // per warp, paired form: column codes of two strips (64 columns x 32 B)
+
+__host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm, bool pair) {
+  return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes + (pair ? kStripColStageBytes : 0)) +
+         2 * 128 * sizeof(ScaleLut) + (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + 16 +
+         (size_t)k_norm * sizeof(float) + 1024;
 }
 
-template <bool ENCODE_CENTRIC, bool NORM, bool OPT>
+// OPT: 0 = round to nearest, no transform; 1 = the optional modes (stochastic rounding of the codes, Hadamard
+// transform, sign mask, row operand optional); 2 = those plus stochastic rounding of the scale bytes (a kernel
+// of its own, so that the extra random-word bookkeeping costs the usual modes no registers).
+template <bool ENCODE_CENTRIC, bool NORM, int OPT, bool PAIR>
 __global__ void __launch_bounds__(kStripWarps * 32, 1)
 nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_row,
                             const QuantArgs a) {
   constexpr int depth = kStripDepth;
+  constexpr bool kScaleSr = OPT == 2;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* base = smem_align_1024(smem_raw);
   uint8_t* slots = base;                                                       // [warp][depth][4 KiB]
   uint8_t* staging = base + (size_t)kStripWarps * depth * kStripBytes;         // [warp][2 KiB]
-  ScaleLut* lut_row = reinterpret_cast<ScaleLut*>(staging + (size_t)kStripWarps * kStripStageBytes);
+  uint8_t* col_staging = staging + (size_t)kStripWarps * kStripStageBytes;      // [warp][2 KiB] (PAIR)
+  ScaleLut* lut_row = reinterpret_cast<ScaleLut*>(col_staging + (PAIR ? (size_t)kStripWarps * kStripColStageBytes : 0));
   ScaleLut* lut_col = lut_row + 128;
   uint64_t* bars = reinterpret_cast<uint64_t*>(lut_col + 128);                 // [warp][depth]
   float* amax_slot = reinterpret_cast<float*>(bars + kStripWarps * depth);     // 16 bytes
   float* gamma_f = amax_slot + 4;                                              // [K] (NORM)
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int wv = warp & 3;          // which 32 rows of the chunk
-  const int wh = (warp >> 2) & 1;   // which 64 columns of the chunk
+  // Eight warps per chunk, one strip each (4 down x 2 across), or, paired, four warps per chunk with two
+  // vertically adjacent strips each (2 x 2 down, 2 across): a paired warp collects the column codes of both
+  // strips in shared memory and stores 32 contiguous bytes per column after the lower one.
+  constexpr int pair = PAIR ? 1 : 0;
+  const int wv_base = pair ? (warp & 1) * 2 : (warp & 3);   // first 32-row band of the chunk this warp works on
+  const int wh = pair ? (warp >> 1) & 1 : (warp >> 2) & 1;  // which 64 columns of the chunk
+  const int groups = pair ? 4 : 2;                           // chunks the CTA works on at a time
   const int n_chunks = a.chunks_m * a.chunks_k;
-  const int first = blockIdx.x * 2 + (warp >> 3);
-  const int step = gridDim.x * 2;
-  const int my_count = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
+  const int first = blockIdx.x * groups + (pair ? warp >> 2 : warp >> 3);
+  const int step = gridDim.x * groups;
+  const int my_chunks = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
+  const int my_count = my_chunks << pair;                    // strips
   uint8_t* my_slots = slots + (size_t)warp * depth * kStripBytes;
   uint64_t* my_bars = bars + warp * depth;
   uint8_t* my_stage = staging + (size_t)warp * kStripStageBytes;
+  uint8_t* my_col_stage = col_staging + (size_t)warp * kStripColStageBytes;
 
   auto chunk_coords = [&](int it, int& cm, int& ck) {
     int c = first + it * step;
@@ -927,11 +942,11 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     cm = c / a.chunks_k;
     ck = c - cm * a.chunks_k;
   };
-  auto issue_load = [&](int it, int s) {
+  auto issue_load = [&](int sit, int s) {
     int cm, ck;
-    chunk_coords(it, cm, ck);
+    chunk_coords(sit >> pair, cm, ck);
     mbar_expect_tx(&my_bars[s], kStripBytes);
-    int x = ck * kChunk + wh * kStripCols, y = cm * kChunk + wv * kStripRows;
+    int x = ck * kChunk + wh * kStripCols, y = cm * kChunk + (wv_base + (sit & pair)) * kStripRows;
     if (a.nhsd_seq > 0) {
       // head-major input: the strip (32 tokens of one sequence x one 64-wide head) is a contiguous block of the
       // [B * heads * seq, 64] matrix the tensor map describes (seq is a multiple of 128: no strip straddles two)
@@ -994,23 +1009,26 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     if (my_count > 0) {
       int cm, ck;
       chunk_coords(0, cm, ck);
-      inv_next = __ldg(a.inv_rms + cm * kChunk + wv * kStripRows + lane);
+      inv_next = __ldg(a.inv_rms + cm * kChunk + wv_base * kStripRows + lane);
     }
   }
+  uint32_t held_sc = 0;   // paired: the upper strip's column scale bytes (two per column)
 
   for (int it = 0; it < my_count; ++it) {
     const int s = it % depth;
     const uint32_t parity = (uint32_t)(it / depth) & 1u;
     int cm, ck;
-    chunk_coords(it, cm, ck);
+    chunk_coords(it >> pair, cm, ck);
+    const int half = it & pair;                          // paired: 0 = upper strip, 1 = lower strip
+    const int wv = wv_base + half;                       // which 32 rows of the chunk
     const int row0 = cm * kChunk + wv * kStripRows;      // first row of the strip
     const int col0 = ck * kChunk + wh * kStripCols;      // first column of the strip
     const float inv = inv_next;
     if constexpr (NORM) {
       if (it + 1 < my_count) {
         int ncm, nck;
-        chunk_coords(it + 1, ncm, nck);
-        inv_next = __ldg(a.inv_rms + ncm * kChunk + wv * kStripRows + lane);
+        chunk_coords((it + 1) >> pair, ncm, nck);
+        inv_next = __ldg(a.inv_rms + ncm * kChunk + (wv_base + ((it + 1) & pair)) * kStripRows + lane);
       }
     }
     if (!mbar_wait_bounded(&my_bars[s], parity)) {
@@ -1048,7 +1066,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       }
       uint32_t codes[8];
       uint32_t sc_word = 0;
-      if constexpr (OPT) {
+      if constexpr (OPT != 0) {
         // Stochastic rounding follows the reference kernel's thread/draw order inside the 128x128 chunk
         // (128 threads, four 64x64 stages, per stage a row pass of 2 iterations x 4 words and, when the
         // launch has one, a column pass of 2 x 4 words; quantize_transpose_tuned.cuh:392-528): the word
@@ -1063,14 +1081,14 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             const int lc0 = wh * kStripCols + b * 16;   // first column of the block inside the chunk
             uint32_t wsel[4] = {0, 0, 0, 0};
             uint32_t scale_rbits = 0;
-            if (a.opt_sr_row || a.opt_scale_sr) {
+            if (a.opt_sr_row || kScaleSr) {
               const int stage = (rc >> 6) * 2 + (lc0 >> 6);
               const int lr = rc & 63, it_ref = lr >> 5;
               const int tid_ref = (lr & 31) * 4 + ((lc0 & 63) >> 4);
               const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
               const int bg = (tid_ref & 31) >> 4;
-              if (a.opt_scale_sr) {
+              if constexpr (kScaleSr) {
                 // q words per block (scale first, then the data words); the stage holds 2 (row-only launch) or 4 blocks
                 const int q = 1 + (a.opt_sr_row ? 4 : 0);
                 uint32_t dr[5];
@@ -1089,7 +1107,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             uint32_t stored;
             const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
                                                        (unsigned long long)(col0 + b * 16), s_enc_row, lut_row,
-                                                       a.opt_sr_row != 0, wsel, stored, a.opt_scale_sr != 0, scale_rbits);
+                                                       a.opt_sr_row != 0, wsel, stored, kScaleSr, scale_rbits);
             codes[2 * b] = cd.x;
             codes[2 * b + 1] = cd.y;
             sc_word |= stored << (8 * b);
@@ -1135,7 +1153,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
           w[i] = *reinterpret_cast<const uint32_t*>(gbase + (i >> 3) * 1024 + col_off[i & 7]);
           mx = absmax_xs(mx, w[i]);
         }
-        if constexpr (OPT) {
+        if constexpr (OPT != 0) {
           const int grp16 = wv * 2 + g;   // 16-row group inside the chunk (the reference kernel's warp role)
 #pragma unroll
           for (int wq = 0; wq < 2; ++wq) {
@@ -1144,12 +1162,12 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             for (int i = 0; i < 16; ++i) x[i] = wq ? bf16hi_to_f32(w[i]) : bf16lo_to_f32(w[i]);
             uint32_t wsel[4] = {0, 0, 0, 0};
             uint32_t scale_rbits = 0;
-            if (a.opt_sr_col || a.opt_scale_sr) {
+            if (a.opt_sr_col || kScaleSr) {
               const int stage = (grp16 >> 2) * 2 + wh;
               const int tid_ref = (((grp16 & 3) - (lane & 3)) & 3) * 32 + lane;
               const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
-              if (a.opt_scale_sr) {
+              if constexpr (kScaleSr) {
                 // the stage's two row blocks (drawn or skipped over by the launch this pass belongs to), then its two column blocks
                 const int q = 1 + (a.opt_sr_col ? 4 : 0);
                 uint32_t dr[5];
@@ -1164,7 +1182,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             uint32_t stored;
             const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
                                                        (unsigned long long)(cm * kChunk + grp16 * 16), s_enc_col, lut_col,
-                                                       a.opt_sr_col != 0, wsel, stored, a.opt_scale_sr != 0, scale_rbits);
+                                                       a.opt_sr_col != 0, wsel, stored, kScaleSr, scale_rbits);
             if (wq == 0) { cc0[2 * g] = cd.x; cc0[2 * g + 1] = cd.y; sc0 |= stored << (8 * g); }
             else { cc1[2 * g] = cd.x; cc1[2 * g + 1] = cd.y; sc1 |= stored << (8 * g); }
           }
@@ -1186,15 +1204,39 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       }
       // 16 bytes per column straight to [K, M/2]: as a TMA store this would be 64 box rows of 16 bytes,
       // and the TMA unit's rate of box rows (not bytes) is what bounds the kernel once everything goes through it
-      uint8_t* cdst = a.col_fp4 + (size_t)(col0 + 2 * lane) * (a.M >> 1) + (row0 >> 1);
-      st_cs_u4(cdst, make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]));
-      st_cs_u4(cdst + (a.M >> 1), make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]));
-      // 512-byte tile (128 columns x four 16-row groups of a 64-row band): this strip holds groups
-      // (wv & 1) * 2 and (wv & 1) * 2 + 1 of band cm * 2 + (wv >> 1): two adjacent bytes per column
       const int cin = wh * kStripCols + 2 * lane;   // column inside the 128-column tile
-      uint8_t* sdst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)(cm * 2 + (wv >> 1))) * 512 + (wv & 1) * 2;
-      st_cs_u16(sdst + scale_tile_offset(cin, 0), (uint16_t)sc0);
-      st_cs_u16(sdst + scale_tile_offset(cin + 1, 0), (uint16_t)sc1);
+      if constexpr (!PAIR) {
+        uint8_t* cdst = a.col_fp4 + (size_t)(col0 + 2 * lane) * (a.M >> 1) + (row0 >> 1);
+        st_cs_u4(cdst, make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]));
+        st_cs_u4(cdst + (a.M >> 1), make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]));
+        // 512-byte tile (128 columns x four 16-row groups of a 64-row band): this strip holds groups
+        // (wv & 1) * 2 and (wv & 1) * 2 + 1 of band cm * 2 + (wv >> 1): two adjacent bytes per column
+        uint8_t* sdst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)(cm * 2 + (wv >> 1))) * 512 + (wv & 1) * 2;
+        st_cs_u16(sdst + scale_tile_offset(cin, 0), (uint16_t)sc0);
+        st_cs_u16(sdst + scale_tile_offset(cin + 1, 0), (uint16_t)sc1);
+      } else {
+        // 64 rows of a column are 32 contiguous bytes.  Both strips' codes go to a [64 columns][32 B] tile in
+        // shared memory (16-byte units, unit u at u ^ ((u >> 3) & 7): conflict-free both ways); after the lower
+        // strip, store k writes columns 16k .. 16k+15, lanes 2j and 2j+1 the two halves of one column, so a
+        // store touches 16 whole sectors instead of 32 half sectors.
+        auto unit = [](int u) { return (u ^ ((u >> 3) & 7)) << 4; };
+        *reinterpret_cast<uint4*>(my_col_stage + unit(4 * lane + half)) = make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]);
+        *reinterpret_cast<uint4*>(my_col_stage + unit(4 * lane + 2 + half)) = make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]);
+        if (half == 0) {
+          held_sc = (sc0 & 0xFFFFu) | (sc1 << 16);
+        } else {
+          __syncwarp();
+          const size_t pitch = (size_t)(a.M >> 1);
+          uint8_t* cdst = a.col_fp4 + (size_t)(col0 + (lane >> 1)) * pitch + ((row0 - kStripRows) >> 1) + (lane & 1) * 16;
+#pragma unroll
+          for (int k = 0; k < 4; ++k)
+            st_cs_u4(cdst + (size_t)(16 * k) * pitch, *reinterpret_cast<const uint4*>(my_col_stage + unit(32 * k + lane)));
+          // the four 16-row groups of the 64-row band cm * 2 + (wv >> 1): one 32-bit word per column
+          uint8_t* sdst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)(cm * 2 + (wv >> 1))) * 512;
+          st_cs_u32(sdst + scale_tile_offset(cin, 0), (held_sc & 0xFFFFu) | (sc0 << 16));
+          st_cs_u32(sdst + scale_tile_offset(cin + 1, 0), (held_sc >> 16) | (sc1 << 16));
+        }
+      }
     }
 
     // staged codes -> global memory; the slot is free again: refill it with the strip `depth` chunks ahead
@@ -1331,8 +1373,17 @@ static bool quant_strip_disabled() {
   return off;
 }
 
-template <bool EC, bool NORM, bool OPT = false>
-static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
+// FP4B200_QUANT_PAIR: "0" never pairs strips, "1" pairs them whenever there are column outputs; unset: by size.
+static int quant_pair_mode() {
+  static const int mode = [] {
+    const char* e = getenv("FP4B200_QUANT_PAIR");
+    return e == nullptr ? -1 : (e[0] == '0' ? 0 : 1);
+  }();
+  return mode;
+}
+
+template <bool EC, bool NORM, int OPT, bool PAIR>
+static int launch_quantize_strip_tp(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
   CUtensorMap tmap, tmap_row;
   const bool nhsd = args.nhsd_seq > 0;   // [B * heads * seq, 64] instead of [M, K]
   if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, nhsd ? 64u : (uint64_t)args.K,
@@ -1347,22 +1398,37 @@ static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStr
                               kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
   }
-  auto kern = nvfp4_quantize_strip_kernel<EC, NORM, OPT>;
-  const int smem = (int)strip_smem_bytes(NORM ? args.K : 0);
+  auto kern = nvfp4_quantize_strip_kernel<EC, NORM, OPT, PAIR>;
+  const int smem = (int)strip_smem_bytes(NORM ? args.K : 0, PAIR);
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   const int n_chunks = args.chunks_m * args.chunks_k;
-  const int grid = std::min((n_chunks + 1) / 2, device_sm_count());
+  constexpr int groups = PAIR ? 4 : 2;
+  const int grid = std::min((n_chunks + groups - 1) / groups, device_sm_count());
   if (grid == 0) return 0;
   PdlLaunch l(dim3((unsigned)grid), dim3(kStripWarps * 32), (size_t)smem, st, pdl);
   FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, tmap, tmap_row, args));
   return 0;
 }
 
+// Paired strips when there are column outputs, enough chunks to keep the four groups of every SM busy, and
+// room in shared memory for the column staging tiles.
+static bool strip_pairing_applies(const QuantArgs& a, bool norm) {
+  if (a.col_fp4 == nullptr || strip_smem_bytes(norm ? a.K : 0, true) > 227 * 1024) return false;
+  const int mode = quant_pair_mode();
+  return mode < 0 ? a.chunks_m * a.chunks_k >= 4 * device_sm_count() : mode == 1;
+}
+
+template <bool EC, bool NORM, int OPT = 0>
+static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
+  return strip_pairing_applies(args, NORM) ? launch_quantize_strip_tp<EC, NORM, OPT, true>(x, args, st, pdl)
+                                           : launch_quantize_strip_tp<EC, NORM, OPT, false>(x, args, st, pdl);
+}
+
 // The strip kernel stores codes by TMA (16-byte aligned outputs) and keeps gamma in shared memory.
 static bool strip_kernel_applies(const QuantArgs& a, bool norm) {
   if (quant_strip_disabled()) return false;
   if (((reinterpret_cast<uintptr_t>(a.row_fp4) | reinterpret_cast<uintptr_t>(a.col_fp4)) & 15) != 0) return false;   // TMA / 16-byte stores
-  return strip_smem_bytes(norm ? a.K : 0) <= 227 * 1024;
+  return strip_smem_bytes(norm ? a.K : 0, false) <= 227 * 1024;
 }
 
 int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, const float* amax_col,
@@ -1410,10 +1476,16 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
     a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
     if (strip_kernel_applies(a, norm)) {
-      if (encode_centric) return norm ? launch_quantize_strip_t<true, true, true>(x, a, st, behind_pass1)
-                                      : launch_quantize_strip_t<true, false, true>(x, a, st, behind_pass1);
-      return norm ? launch_quantize_strip_t<false, true, true>(x, a, st, behind_pass1)
-                  : launch_quantize_strip_t<false, false, true>(x, a, st, behind_pass1);
+      if (a.opt_scale_sr) {
+        if (encode_centric) return norm ? launch_quantize_strip_t<true, true, 2>(x, a, st, behind_pass1)
+                                        : launch_quantize_strip_t<true, false, 2>(x, a, st, behind_pass1);
+        return norm ? launch_quantize_strip_t<false, true, 2>(x, a, st, behind_pass1)
+                    : launch_quantize_strip_t<false, false, 2>(x, a, st, behind_pass1);
+      }
+      if (encode_centric) return norm ? launch_quantize_strip_t<true, true, 1>(x, a, st, behind_pass1)
+                                      : launch_quantize_strip_t<true, false, 1>(x, a, st, behind_pass1);
+      return norm ? launch_quantize_strip_t<false, true, 1>(x, a, st, behind_pass1)
+                  : launch_quantize_strip_t<false, false, 1>(x, a, st, behind_pass1);
     }
     if (a.opt_scale_sr) return set_error("scale stochastic rounding needs 16-byte aligned outputs (strip quantiser only)");
     if (encode_centric) return norm ? launch_quantize_t<true, true, false, true>(tmap, a, st, behind_pass1)
