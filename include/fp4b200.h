@@ -227,6 +227,17 @@ int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, co
 int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
                                      void* col_fp4, void* col_sc, void* stream);
 
+/* mxfp4_quantize_for_gemm_opt(input, mode, data_stochastic_rounding, scale_stochastic_rounding, rng_seed,
+ * rng_subsequence) (mxfp4_v4/tk_quantize.cu:1796-1881; kernel mxfp4_v3_fused_kernel_opt / mx_rowwise_quantize_opt,
+ * mxfp4_v3_quantize.cuh:1618-1790, 5270-5345): row operand only.  data_sr rounds the codes stochastically
+ * (cvt.rs.satfinite.e2m1x4.f32 with the words of the owning reference thread's Philox stream: subsequence
+ * rng_subsequence + ((chunk * 4 + tile) * 128 + thread), offset 0); scale_sr rounds the E8M0 byte up with
+ * probability mantissa / 2^23 (and replaces the mode's rule).  Each 16-element half of a 32-block rounds the
+ * scale with its own word: the stored byte is the first half's, the second half's codes use its own, as the
+ * reference does.  M, K multiples of 128; row_fp4 [M, K/2], row_sc [M/128, K/128, 512]. */
+int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
+                                  uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* stream);
+
 /* nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps) (nvfp4_b200_gemm.cu:1792-1803; kernel
  * common/c1_rms_reduce.cuh:11-38), also the first step of tk_fused_norm_quantize_from_row_rms_partial
  * (nvfp4_v5/tk_quantize.cu:8266-8308) and of mxfp4_fused_rmsnorm_quantize_row_and_col_from_row_rms_partial

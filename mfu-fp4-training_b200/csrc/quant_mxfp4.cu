@@ -253,6 +253,95 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
   }
 }
 
+// ---------------------------------------------------------------------------------------
+// Row quantiser with stochastic rounding (of the codes and / or of the E8M0 scale byte)
+// ---------------------------------------------------------------------------------------
+//
+// One thread per 16 contiguous elements, two adjacent threads per 32-block.  The random words follow the
+// reference kernel (mxfp4_v3_quantize.cuh:1618-1790, launched by tk_quantize.cu:1796-1846): its 128 threads
+// walk a 128x128 chunk as four 64x64 tiles, a thread (tid_Y = row % 32, tid_X = 16-column segment) owning the
+// rows tid_Y and tid_Y + 32 of a tile; its Philox stream (subsequence base + ((chunk * 4 + tile) * 128 + thread),
+// offset 0) yields, per row, one word for the scale byte (scale SR) and then four words for the codes (data
+// SR), the two 8-element halves taken in swapped order by the upper half-warp.  Every thread rounds the scale
+// of its block with its OWN word: the byte stored is the even segment's, while the odd segment's codes use the
+// odd thread's byte, as in the reference.
+struct MxSrArgs {
+  const __nv_bfloat16* x;
+  uint8_t* row_fp4;   // [M, K/2]
+  uint8_t* row_sc;    // [M/128, K/128, 512]
+  int64_t M, K;
+  int mode, data_sr, scale_sr;
+  unsigned long long seed, subseq;
+};
+
+__device__ __forceinline__ uint32_t mx_e8m0_sr(float b, uint32_t rbits) {
+  if (b <= 1e-38f) return 0;
+  const uint32_t u = __float_as_uint(b);
+  const uint32_t e = (u >> 23) & 0xFF, m = u & 0x7FFFFF;
+  if (m == 0 || e >= 0xFE) return e;
+  return ((unsigned long long)rbits < ((unsigned long long)m << 9)) ? e + 1 : e;
+}
+
+__global__ void __launch_bounds__(256) mxfp4_quantize_row_sr_kernel(const MxSrArgs a) {
+  const int64_t segs_per_row = a.K >> 4;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;   // segment index; whole warps are in range
+  if (idx >= a.M * segs_per_row) return;
+  const int64_t r = idx / segs_per_row;
+  const int c = (int)(idx - r * segs_per_row) << 4;
+  const uint4* src = reinterpret_cast<const uint4*>(a.x + r * a.K + c);
+  const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
+  const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  uint32_t mx = 0;
+#pragma unroll
+  for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[q]);
+  float bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+  bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
+
+  // the reference thread that owns this segment, and where this row sits in its draw order
+  const int rr = (int)(r & 127), cc = c & 127;
+  const int tile = (rr >> 6) * 2 + (cc >> 6);
+  const int it = (rr & 63) >> 5;
+  const int tid_ref = (rr & 31) * 4 + ((cc & 63) >> 4);
+  const int bank_group = (tid_ref & 31) >> 4;
+  const unsigned long long chunk = (unsigned long long)(r >> 7) * (unsigned long long)(a.K >> 7) + (unsigned long long)(c >> 7);
+  const unsigned long long seq = a.subseq + (chunk * 4ull + (unsigned long long)tile) * 128ull + (unsigned long long)tid_ref;
+  const int q = (a.scale_sr ? 1 : 0) + (a.data_sr ? 4 : 0);
+  uint32_t dr[5];
+  philox_draws(a.seed, seq, 0ull, it * q, q, dr);
+
+  const uint32_t e = a.scale_sr ? mx_e8m0_sr(bm, dr[0]) : mx_e8m0(bm, a.mode);
+  const float coeff = mx_coeff(e);   // 6 * 2^(127-e): exact in bf16, as the reference rounds it
+  uint32_t lo, hi;
+  if (a.data_sr) {
+    const int d0 = a.scale_sr ? 1 : 0;
+    uint32_t wsel[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bank_group) & 1) ? dr[d0 + 2 + (g & 1)] : dr[d0 + (g & 1)];
+    uint32_t h[4];
+#pragma unroll
+    for (int g = 0; g < 4; ++g)
+      h[g] = f32x4_to_e2m1x4_sr(bf16lo_to_f32(w[2 * g]) * coeff, bf16hi_to_f32(w[2 * g]) * coeff,
+                                bf16lo_to_f32(w[2 * g + 1]) * coeff, bf16hi_to_f32(w[2 * g + 1]) * coeff, wsel[g]);
+    lo = h[0] | (h[1] << 16);
+    hi = h[2] | (h[3] << 16);
+  } else {
+    lo = quant8(w, coeff);
+    hi = quant8(w + 4, coeff);
+  }
+  *reinterpret_cast<uint2*>(a.row_fp4 + r * (a.K >> 1) + (c >> 1)) = make_uint2(lo, hi);
+  if (((c >> 4) & 1) == 0)
+    a.row_sc[((size_t)(r >> 7) * (size_t)(a.K >> 7) + (size_t)(c >> 7)) * 512 + scale_tile_offset(rr, cc >> 5)] = (uint8_t)e;
+}
+
+static int launch_mx_row_sr(const MxSrArgs& a, cudaStream_t st) {
+  const int64_t segs = a.M * (a.K >> 4);
+  const int64_t blocks = (segs + 255) / 256;
+  if (blocks == 0) return 0;
+  mxfp4_quantize_row_sr_kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
 static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float* inv_rms, const void* gamma,
                      void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st, bool weight_2d = false) {
   CUtensorMap tmap;
@@ -322,6 +411,19 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
   if (int rc = check_mx(w_bf16, N, K, 1, "mxfp4_quantize_weight_2d")) return rc;
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_quantize_weight_2d: all outputs are required");
   return launch_mx(w_bf16, N, K, 1, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, true);
+}
+
+int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
+                                  uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* stream) {
+  if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize_row_sr")) return rc;
+  if (!row_fp4 || !row_sc) return set_error("mxfp4_quantize_row_sr: row_fp4 and row_sc are required");
+  if (reinterpret_cast<uintptr_t>(row_fp4) & 7) return set_error("mxfp4_quantize_row_sr: row_fp4 must be 8-byte aligned");
+  if (M * (K >> 4) > (int64_t)0x7fffffff * 256) return set_error("mxfp4_quantize_row_sr: tensor too large");
+  MxSrArgs a{};
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x_bf16); a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc;
+  a.M = M; a.K = K; a.mode = mode; a.data_sr = data_sr != 0; a.scale_sr = scale_sr != 0;
+  a.seed = rng_seed; a.subseq = rng_subsequence;
+  return launch_mx_row_sr(a, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -450,37 +450,6 @@ __device__ __forceinline__ uint32_t block_code_sr(float b, float s_enc, uint32_t
 
 // ---- helpers of the OPT instantiations ------------------------------------------------------
 
-// Philox4x32-10 block: key = seed, counter = {offset (64 bit), sequence (64 bit)}
-// (reference generator: nvfp4_v5/util/curanddx.hpp:20-103)
-__device__ __forceinline__ uint4 philox4x32_10(unsigned long long seed, unsigned long long sequence,
-                                               unsigned long long offset) {
-  uint32_t kx = (uint32_t)seed, ky = (uint32_t)(seed >> 32);
-  uint32_t c0 = (uint32_t)offset, c1 = (uint32_t)(offset >> 32), c2 = (uint32_t)sequence, c3 = (uint32_t)(sequence >> 32);
-#pragma unroll
-  for (int i = 0; i < 10; ++i) {
-    const uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
-    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
-    const uint32_t n0 = hi1 ^ c1 ^ kx, n2 = hi0 ^ c3 ^ ky;
-    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
-    kx += 0x9E3779B9u; ky += 0xBB67AE85u;
-  }
-  return make_uint4(c0, c1, c2, c3);
-}
-
-// Random words of the draws n0 .. n0 + count - 1 (count <= 5) of one thread's stream: draw n is component n & 3 of the
-// Philox block at counter offset + (n >> 2) (the reference refills its four words when the fourth has been used,
-// core.cuh:116-127).
-__device__ __forceinline__ void philox_draws(unsigned long long seed, unsigned long long seq, unsigned long long offset, int n0,
-                                             int count, uint32_t (&out)[5]) {
-  const uint4 b0 = philox4x32_10(seed, seq, offset + (unsigned long long)(n0 >> 2));
-  const bool two = ((n0 + count - 1) >> 2) != (n0 >> 2);
-  const uint4 b1 = two ? philox4x32_10(seed, seq, offset + (unsigned long long)((n0 >> 2) + 1)) : b0;
-  const uint32_t w[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
-  const int sh = n0 & 3;
-#pragma unroll
-  for (int i = 0; i < 5; ++i) out[i] = sh == 0 ? w[i] : (sh == 1 ? w[i + 1] : (sh == 2 ? w[i + 2] : w[i + 3]));   // registers only
-}
-
 // +1 / -1 per coordinate along the transformed axis (reference: tk_quantize.cu:483-488,620-627)
 __device__ __forceinline__ float rht_sign(unsigned long long seed, unsigned long long subseq, unsigned long long coord) {
   unsigned long long x = seed ^ (subseq * 0xd1b54a32d192ed03ull) ^ (coord * 0x9e3779b97f4a7c15ull);

@@ -39,6 +39,22 @@ def mxfp4_quantize_for_gemm(input, mode=0):
     return rf.view(_FP4), rs
 
 
+def mxfp4_quantize_for_gemm_opt(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
+                                rng_seed=0, rng_subsequence=0):
+    """tk_quantize.cu:1848-1881 (bound at 7285) — row-wise (fp4, scales) with stochastic rounding of the codes
+    and / or of the E8M0 scale bytes, on the reference's Philox stream for (rng_seed, rng_subsequence); with
+    neither flag it is ``mxfp4_quantize_for_gemm``."""
+    if not data_stochastic_rounding and not scale_stochastic_rounding:
+        return mxfp4_quantize_for_gemm(input, mode)
+    M, K = _check_bf16_2d(input, "input")
+    with torch.cuda.device(input.device):
+        rf, rs, _, _ = _alloc(M, K, input.device, False)
+        _lib.call("fp4b200_mxfp4_quantize_row_sr", input.data_ptr(), M, K, int(mode), int(bool(data_stochastic_rounding)),
+                  int(bool(scale_stochastic_rounding)), int(rng_seed) & 0xFFFFFFFFFFFFFFFF,
+                  int(rng_subsequence) & 0xFFFFFFFFFFFFFFFF, rf.data_ptr(), rs.data_ptr(), _stream(input))
+    return rf.view(_FP4), rs
+
+
 def mxfp4_quantize_row_and_col(input, mode=0):
     """tk_quantize.cu:7344 — (row_fp4, row_sc, col_fp4, col_sc)."""
     rf, rs, cf, cs = _quant(input, mode, True)

@@ -498,6 +498,63 @@ def mxfp4_quantize_row_and_col(x: np.ndarray, mode: int = 1):
                 col_fp4=c_fp4, col_sc=swizzle_scales(c_e), col_sc_logical=c_e)
 
 
+def mx_e8m0_sr(block_amax: np.ndarray, rbits: np.ndarray) -> np.ndarray:
+    """``float_to_e8m0_stochastic`` (mxfp4_v3_quantize.cuh:1449-1459): 0 if b <= 1e-38; the fp32 exponent, raised by one
+    when the mantissa is non-zero, the exponent below 0xFE and rbits < mantissa << 9."""
+    b = np.ascontiguousarray(block_amax, dtype=np.float32)
+    bits = b.view(np.uint32)
+    e = ((bits >> 23) & 0xFF).astype(np.int64)
+    m = (bits & 0x7FFFFF).astype(np.int64)
+    up = (m != 0) & (e < 0xFE) & (np.asarray(rbits).astype(np.int64) < (m << 9))
+    return np.where(b <= F32(1e-38), 0, e + up).astype(np.uint8)
+
+
+def mxfp4_quantize_for_gemm_opt(x: np.ndarray, mode: int, data_sr: bool, scale_sr: bool, seed: int, subseq: int):
+    """``mxfp4_quantize_for_gemm_opt`` (mxfp4_v4/tk_quantize.cu:1796-1881; mx_rowwise_quantize_opt,
+    mxfp4_v3_quantize.cuh:1618-1790).  A reference thread owns 16 contiguous elements of the rows tid_Y and tid_Y + 32
+    of a 64x64 tile; its Philox stream (subsequence subseq + ((chunk * 4 + tile) * 128 + thread), offset 0) gives per
+    row one word for the scale byte (scale_sr) and then four for the codes (data_sr; lanes 16..31 of a warp take the
+    two 8-element halves in swapped order).  Each half of a 32-block rounds the scale with its own word; the byte
+    stored is the first half's.  Returns (packed [M, K/2], swizzled scales, logical scale bytes [M, K/32])."""
+    x = np.asarray(x, dtype=F32)
+    M, K = x.shape
+    assert M % 128 == 0 and K % 128 == 0
+    r = np.arange(M)[:, None]
+    c = (np.arange(K // 16) * 16)[None, :]
+    rr, cc = r & 127, c & 127
+    tile = (rr >> 6) * 2 + (cc >> 6)
+    it = (rr & 63) >> 5
+    tid = (rr & 31) * 4 + ((cc & 63) >> 4)
+    bank = (tid & 31) >> 4
+    chunk = (r >> 7) * (K // 128) + (c >> 7)
+    seq = (np.uint64(subseq) + ((chunk * 4 + tile) * 128 + tid).astype(np.uint64)).astype(np.uint64)
+    q = (1 if scale_sr else 0) + (4 if data_sr else 0)
+    n0 = it * q + np.zeros_like(tid)
+
+    def draw(n):   # word of draw number n of each segment's thread
+        blk = philox4x32_10(seed, seq, (n >> 2).astype(np.uint64))
+        return np.take_along_axis(blk, (n & 3)[..., None], axis=-1)[..., 0]
+
+    seg = x.reshape(M, K // 16, 16)
+    seg_max = np.abs(seg).max(axis=-1)
+    bm = np.maximum(seg_max, seg_max.reshape(M, K // 32, 2)[:, :, ::-1].reshape(M, K // 16))   # the pair's maximum
+    e = mx_e8m0_sr(bm, draw(n0)) if scale_sr else mx_e8m0(bm, mode)
+    with np.errstate(over="ignore", invalid="ignore"):
+        coeff = (F32(6.0) * _mx_rcp(e)).astype(F32)
+        scaled = (seg * coeff[..., None]).astype(F32)
+    if data_sr:
+        d0 = 1 if scale_sr else 0
+        words = np.empty((M, K // 16, 4), dtype=np.uint32)
+        for g in range(4):
+            wave = ((g >> 1) - bank) & 1
+            words[..., g] = draw(n0 + d0 + 2 * wave + (g & 1))
+        codes = e2m1_encode_sr(scaled.reshape(M, K // 16, 4, 4), words).reshape(M, K)
+    else:
+        codes = e2m1_encode_rn(scaled).reshape(M, K)
+    e_logical = np.ascontiguousarray(e[:, 0::2])
+    return pack_fp4(codes), swizzle_scales(e_logical), e_logical
+
+
 def _mx_rcp(e: np.ndarray) -> np.ndarray:
     """exp2f_rcp (util/ptx.cuh:330-338): 2^(127-e) built from the exponent field; e = 254 -> 2^-127."""
     rcp = ((254 - e.astype(np.int64)).clip(0, 254).astype(np.uint32) << 23).view(np.float32)
@@ -780,7 +837,8 @@ def e2m1_encode_sr(v4: np.ndarray, rbits: np.ndarray) -> np.ndarray:
         a = np.abs(v4[..., p]).astype(np.float64)
         idx = np.clip(np.searchsorted(_E2M1_GRID, a, side="right") - 1, 0, 6)
         lo, hi = _E2M1_GRID[idx], _E2M1_GRID[idx + 1]
-        k = np.floor((a - lo) / (hi - lo) * 65536.0).astype(np.int64)
+        with np.errstate(invalid="ignore"):   # NaN (0 * inf under an overflowed coefficient) is handled below
+            k = np.floor(np.nan_to_num((a - lo) / (hi - lo), nan=0.0, posinf=0.0) * 65536.0).astype(np.int64)
         code = np.where((k + Vs[p]) >= 65536, idx + 1, idx)
         code = np.where(a >= 6, 7, code)
         code = code | (np.signbit(v4[..., p]).astype(np.int64) << 3)

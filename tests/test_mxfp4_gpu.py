@@ -145,3 +145,40 @@ def test_launch_inplace_twins_fill_the_callers_tensors():
     with pytest.raises(RuntimeError):
         mxq.mxfp4_quantize_row_and_col_launch_inplace(x, bad[0].view(torch.uint8), bad[1], bad[2], bad[3], 1)
     assert_status_ok()
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (512, 1024)])
+@pytest.mark.parametrize("data_sr,scale_sr", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_mxfp4_quantize_for_gemm_opt_stochastic(shape, data_sr, scale_sr, mode):
+    """Codes and scale bytes of the stochastic-rounding row quantiser, bit for bit on the reference's random stream."""
+    mxq = mod("mxfp4_quant_v4")
+    x = o.make_activations(*shape, seed=sum(shape) + 3 * mode)
+    x[1, 32:64] = 0.0
+    seed, subseq = 0x1234_5678_9ABC, 77 + mode
+    out = mxq.mxfp4_quantize_for_gemm_opt(to_dev_bf16(x), mode, data_sr, scale_sr, seed, subseq)
+    torch.cuda.synchronize()
+    fp4, sc, _ = o.mxfp4_quantize_for_gemm_opt(x, mode, data_sr, scale_sr, seed, subseq)
+    assert np.array_equal(u8(out[0]), fp4)
+    assert np.array_equal(u8(out[1]).reshape(sc.shape), sc)
+    assert_status_ok()
+
+
+def test_mxfp4_quantize_for_gemm_opt_without_flags_is_the_plain_quantiser_and_sr_is_unbiased():
+    mxq = mod("mxfp4_quant_v4")
+    M, K = 1024, 2048
+    x = o.make_activations(M, K, seed=9)
+    xd = to_dev_bf16(x)
+    plain = mxq.mxfp4_quantize_for_gemm(xd, 1)
+    same = mxq.mxfp4_quantize_for_gemm_opt(xd, 1, False, False, 1, 2)
+    assert torch.equal(plain[0].view(torch.uint8), same[0].view(torch.uint8)) and torch.equal(plain[1], same[1])
+    # data SR with the ceil scale of mode 1 never saturates: the dequantised tensor is unbiased
+    out = mxq.mxfp4_quantize_for_gemm_opt(xd, 1, True, False, 11, 5)
+    torch.cuda.synchronize()
+    fp4, sc, e = o.mxfp4_quantize_for_gemm_opt(x, 1, True, False, 11, 5)
+    assert np.array_equal(u8(out[0]), fp4)
+    deq = o.mxfp4_dequantize(fp4, e)
+    rn = o.mxfp4_dequantize(*o.mxfp4_quantize_1d(x, 1))
+    assert abs((deq - x).mean()) < 4.0 * np.linalg.norm(deq - x) / (M * K)   # four standard errors of the mean
+    assert np.linalg.norm(deq - x) < 1.7 * np.linalg.norm(rn - x)
+    assert_status_ok()
