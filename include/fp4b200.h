@@ -238,6 +238,18 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
 int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
                                   uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* stream);
 
+/* mxfp4_quantize_row_and_col_opt(input, mode, data_stochastic_rounding, scale_stochastic_rounding, rng_seed,
+ * rng_subsequence) without a Hadamard transform (mxfp4_v4/tk_quantize.cu:2820-2953; kernel
+ * mxfp4_v4_rowcol_fused_kernel_opt, mxfp4_v3_quantize.cuh:5443-5560).  rng_subsequence here is the base the launch
+ * ends up with: the caller's value plus the reference's per-call offset (2^40 times the number of earlier SR
+ * calls; the Python mirror keeps that counter).  data_sr is the reference's "correlated" rounding: the row and the
+ * column view round element (i, j) with the same 16-bit integer, derived from (rng_seed, base, chunk, i, j) by a
+ * GF(2^16) construction instead of the Philox stream; scale_sr draws from the reference threads' Philox streams
+ * as in fp4b200_mxfp4_quantize_row_sr (column view: its own subsequences). */
+int fp4b200_mxfp4_quantize_row_and_col_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
+                                          uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc,
+                                          void* col_fp4, void* col_sc, void* stream);
+
 /* nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps) (nvfp4_b200_gemm.cu:1792-1803; kernel
  * common/c1_rms_reduce.cuh:11-38), also the first step of tk_fused_norm_quantize_from_row_rms_partial
  * (nvfp4_v5/tk_quantize.cu:8266-8308) and of mxfp4_fused_rmsnorm_quantize_row_and_col_from_row_rms_partial

@@ -272,7 +272,58 @@ struct MxSrArgs {
   int64_t M, K;
   int mode, data_sr, scale_sr;
   unsigned long long seed, subseq;
+  int correlated;     // row + column launch: the codes round with the position's shared 16-bit integer (below)
+  uint8_t* col_fp4;   // [K, M/2]            (column kernel)
+  uint8_t* col_sc;    // [K/128, M/128, 512]
 };
+
+// Rounding words of 16 consecutive elements of a row (ROW_VECTOR) or column such that both views of element
+// (i, j) add the same 16-bit integer (reference: mxfp4_correlated_sr_rbits16, mxfp4_v3_quantize.cuh:1375-1432).
+// A hash of (base, i >> 4, j >> 4) gives two GF(2^16) elements (a, b) per 16x16 tile; the 2x2 cell (i >> 1, j >> 1)
+// rounds with the field b + a * p, p the polynomial with bits (j >> 1) | (i >> 1) << 3.  A word carries two fields in
+// the byte order cvt.rs.satfinite.e2m1x4.f32 reads them: elements 0 and 2 of its group of four add fields 2k and
+// 2k+1, elements 1 and 3 the same fields bit-reversed.
+__device__ __forceinline__ uint32_t gf16_times_x(uint32_t v) { return ((v << 1) & 0xFFFFu) ^ ((0u - (v >> 15)) & 0x100Bu); }
+
+template <bool ROW_VECTOR>
+__device__ __forceinline__ uint4 mx_correlated_words(unsigned long long base, uint32_t row, uint32_t col) {
+  uint32_t t = (uint32_t)base ^ (uint32_t)(base >> 32);
+  t ^= (row >> 4) * 0x9E3779B9u;
+  t ^= (col >> 4) * 0x85EBCA6Bu;
+  t ^= t >> 16; t *= 0x7FEB352Du;
+  t ^= t >> 15; t *= 0x846CA68Bu;
+  t ^= t >> 16;
+  uint32_t ap[6];
+  ap[0] = t & 0xFFFFu;
+#pragma unroll
+  for (int i = 1; i < 6; ++i) ap[i] = gf16_times_x(ap[i - 1]);
+  const uint32_t grp = ((ROW_VECTOR ? row : col) & 14u) >> 1;
+  constexpr int fixed = ROW_VECTOR ? 3 : 0, step = ROW_VECTOR ? 0 : 3;
+  uint32_t f0 = t >> 16;
+#pragma unroll
+  for (int b = 0; b < 3; ++b) f0 ^= ap[fixed + b] & (0u - ((grp >> b) & 1u));
+  uint32_t f[8];
+#pragma unroll
+  for (int m = 0; m < 8; ++m) f[m] = f0 ^ ((m & 1) ? ap[step] : 0u) ^ ((m & 2) ? ap[step + 1] : 0u) ^ ((m & 4) ? ap[step + 2] : 0u);
+  auto pack = [](uint32_t ef, uint32_t ab) { return ((ab & 0xFF00u) << 16) | ((ef & 0xFF00u) << 8) | ((ab & 0xFFu) << 8) | (ef & 0xFFu); };
+  return make_uint4(pack(f[0], f[1]), pack(f[2], f[3]), pack(f[4], f[5]), pack(f[6], f[7]));
+}
+
+// 16 bf16 values (eight packed words) times coeff -> 8 bytes of codes, stochastic rounding with one word per group
+// of four; swap: neighbours exchanged before the conversion and their codes exchanged back after it
+__device__ __forceinline__ uint2 mx_quant16_sr(const uint32_t (&w)[8], float coeff, const uint32_t (&wsel)[4], bool swap) {
+  uint32_t h[4];
+#pragma unroll
+  for (int g = 0; g < 4; ++g) {
+    const float v0 = bf16lo_to_f32(w[2 * g]) * coeff, v1 = bf16hi_to_f32(w[2 * g]) * coeff;
+    const float v2 = bf16lo_to_f32(w[2 * g + 1]) * coeff, v3 = bf16hi_to_f32(w[2 * g + 1]) * coeff;
+    const uint32_t c = swap ? f32x4_to_e2m1x4_sr(v1, v0, v3, v2, wsel[g]) : f32x4_to_e2m1x4_sr(v0, v1, v2, v3, wsel[g]);
+    h[g] = swap ? (((c & 0xF0F0u) >> 4) | ((c & 0x0F0Fu) << 4)) : c;
+  }
+  return make_uint2(h[0] | (h[1] << 16), h[2] | (h[3] << 16));
+}
+
+constexpr unsigned long long kMxCorrelatedSalt = 0xA0761D6478BD642Full;
 
 __device__ __forceinline__ uint32_t mx_e8m0_sr(float b, uint32_t rbits) {
   if (b <= 1e-38f) return 0;
@@ -305,7 +356,7 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_row_sr_kernel(const MxSrAr
   const int bank_group = (tid_ref & 31) >> 4;
   const unsigned long long chunk = (unsigned long long)(r >> 7) * (unsigned long long)(a.K >> 7) + (unsigned long long)(c >> 7);
   const unsigned long long seq = a.subseq + (chunk * 4ull + (unsigned long long)tile) * 128ull + (unsigned long long)tid_ref;
-  const int q = (a.scale_sr ? 1 : 0) + (a.data_sr ? 4 : 0);
+  const int q = (a.scale_sr ? 1 : 0) + ((a.data_sr && !a.correlated) ? 4 : 0);
   uint32_t dr[5];
   philox_draws(a.seed, seq, 0ull, it * q, q, dr);
 
@@ -313,17 +364,18 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_row_sr_kernel(const MxSrAr
   const float coeff = mx_coeff(e);   // 6 * 2^(127-e): exact in bf16, as the reference rounds it
   uint32_t lo, hi;
   if (a.data_sr) {
-    const int d0 = a.scale_sr ? 1 : 0;
     uint32_t wsel[4];
+    if (a.correlated) {
+      const uint4 cw = mx_correlated_words<true>((a.subseq + chunk * 512ull) ^ a.seed ^ kMxCorrelatedSalt, (uint32_t)r, (uint32_t)c);
+      wsel[0] = cw.x; wsel[1] = cw.y; wsel[2] = cw.z; wsel[3] = cw.w;
+    } else {
+      const int d0 = a.scale_sr ? 1 : 0;
 #pragma unroll
-    for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bank_group) & 1) ? dr[d0 + 2 + (g & 1)] : dr[d0 + (g & 1)];
-    uint32_t h[4];
-#pragma unroll
-    for (int g = 0; g < 4; ++g)
-      h[g] = f32x4_to_e2m1x4_sr(bf16lo_to_f32(w[2 * g]) * coeff, bf16hi_to_f32(w[2 * g]) * coeff,
-                                bf16lo_to_f32(w[2 * g + 1]) * coeff, bf16hi_to_f32(w[2 * g + 1]) * coeff, wsel[g]);
-    lo = h[0] | (h[1] << 16);
-    hi = h[2] | (h[3] << 16);
+      for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bank_group) & 1) ? dr[d0 + 2 + (g & 1)] : dr[d0 + (g & 1)];
+    }
+    const uint2 cd = mx_quant16_sr(w, coeff, wsel, a.correlated && (r & 1));
+    lo = cd.x;
+    hi = cd.y;
   } else {
     lo = quant8(w, coeff);
     hi = quant8(w + 4, coeff);
@@ -331,6 +383,84 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_row_sr_kernel(const MxSrAr
   *reinterpret_cast<uint2*>(a.row_fp4 + r * (a.K >> 1) + (c >> 1)) = make_uint2(lo, hi);
   if (((c >> 4) & 1) == 0)
     a.row_sc[((size_t)(r >> 7) * (size_t)(a.K >> 7) + (size_t)(c >> 7)) * 512 + scale_tile_offset(rr, cc >> 5)] = (uint8_t)e;
+}
+
+// Column view of the row + column launch (reference: mx_colwise_quantize_direct_opt, mxfp4_v3_quantize.cuh:4031-4230,
+// called by quantize_chunk_rowcol_pipelined_opt, 3321-3430).  One thread per (16 rows, two adjacent columns), as the
+// reference thread; it reads the partner's 16 rows as well for the 32-row block maximum.  Scale SR: draws 0 and 1 of
+// the thread's stream (subsequence base + ((column-view chunk * 4 + tile) * 128 + thread)) for its two columns.
+__global__ void __launch_bounds__(256) mxfp4_quantize_col_sr_kernel(const MxSrArgs a) {
+  const int64_t pairs = a.K >> 1;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (a.M >> 4) * pairs) return;
+  const int64_t g16 = idx / pairs;
+  const int j = (int)(idx - g16 * pairs) << 1;   // first of the two columns
+  const int64_t i0 = g16 << 4;
+  const uint32_t* own = reinterpret_cast<const uint32_t*>(a.x + i0 * a.K + j);
+  const uint32_t* other = reinterpret_cast<const uint32_t*>(a.x + (i0 ^ 16) * a.K + j);
+  const int64_t ld = a.K >> 1;   // row pitch in 32-bit words
+  uint32_t v[16];
+  uint32_t mx = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    v[i] = __ldg(own + i * ld);
+    mx = absmax_xs(mx, v[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 16; ++i) mx = absmax_xs(mx, __ldg(other + i * ld));
+  const float bm0 = fabsf(bf16lo_to_f32(mx)), bm1 = fabsf(bf16hi_to_f32(mx));
+
+  const int jj = j & 127, ii = (int)(i0 & 127);
+  const int tile = (jj >> 6) * 2 + (ii >> 6);
+  const int tx = (jj & 63) >> 1, ty = (ii & 63) >> 4;
+  const int tid_ref = ((tx >> 4) * 2 + (ty >> 1)) * 32 + (ty & 1) * 16 + (tx & 15);
+  const unsigned long long chunk_col = (unsigned long long)(j >> 7) * (unsigned long long)(a.M >> 7) + (unsigned long long)(i0 >> 7);
+  const unsigned long long chunk_in = (unsigned long long)(i0 >> 7) * (unsigned long long)(a.K >> 7) + (unsigned long long)(j >> 7);
+  uint32_t e0, e1;
+  if (a.scale_sr) {
+    const uint4 rw = philox4x32_10(a.seed, a.subseq + (chunk_col * 4ull + (unsigned long long)tile) * 128ull + (unsigned long long)tid_ref, 0ull);
+    e0 = mx_e8m0_sr(bm0, rw.x);
+    e1 = mx_e8m0_sr(bm1, rw.y);
+  } else {
+    e0 = mx_e8m0(bm0, a.mode);
+    e1 = mx_e8m0(bm1, a.mode);
+  }
+  // the two columns as packed pairs of consecutive rows
+  uint32_t c0[8], c1[8];
+#pragma unroll
+  for (int q = 0; q < 8; ++q) {
+    c0[q] = __byte_perm(v[2 * q], v[2 * q + 1], 0x5410);
+    c1[q] = __byte_perm(v[2 * q], v[2 * q + 1], 0x7632);
+  }
+  uint2 o0, o1;
+  if (a.data_sr) {
+    const unsigned long long base = (a.subseq + chunk_in * 512ull) ^ a.seed ^ kMxCorrelatedSalt;
+    const uint4 w0 = mx_correlated_words<false>(base, (uint32_t)i0, (uint32_t)j);
+    const uint4 w1 = mx_correlated_words<false>(base, (uint32_t)i0, (uint32_t)j + 1u);
+    const uint32_t ws0[4] = {w0.x, w0.y, w0.z, w0.w}, ws1[4] = {w1.x, w1.y, w1.z, w1.w};
+    o0 = mx_quant16_sr(c0, mx_coeff(e0), ws0, false);   // j is even
+    o1 = mx_quant16_sr(c1, mx_coeff(e1), ws1, true);
+  } else {
+    o0 = make_uint2(quant8(c0, mx_coeff(e0)), quant8(c0 + 4, mx_coeff(e0)));
+    o1 = make_uint2(quant8(c1, mx_coeff(e1)), quant8(c1 + 4, mx_coeff(e1)));
+  }
+  uint8_t* dst = a.col_fp4 + (size_t)j * (size_t)(a.M >> 1) + (size_t)(i0 >> 1);
+  *reinterpret_cast<uint2*>(dst) = o0;
+  *reinterpret_cast<uint2*>(dst + (a.M >> 1)) = o1;
+  if ((i0 & 16) == 0) {
+    uint8_t* sdst = a.col_sc + ((size_t)(j >> 7) * (size_t)(a.M >> 7) + (size_t)(i0 >> 7)) * 512;
+    sdst[scale_tile_offset(jj, ii >> 5)] = (uint8_t)e0;
+    sdst[scale_tile_offset(jj + 1, ii >> 5)] = (uint8_t)e1;
+  }
+}
+
+static int launch_mx_col_sr(const MxSrArgs& a, cudaStream_t st) {
+  const int64_t n = (a.M >> 4) * (a.K >> 1);
+  const int64_t blocks = (n + 255) / 256;
+  if (blocks == 0) return 0;
+  mxfp4_quantize_col_sr_kernel<<<(unsigned)blocks, 256, 0, st>>>(a);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
 }
 
 static int launch_mx_row_sr(const MxSrArgs& a, cudaStream_t st) {
@@ -424,6 +554,23 @@ int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int 
   a.M = M; a.K = K; a.mode = mode; a.data_sr = data_sr != 0; a.scale_sr = scale_sr != 0;
   a.seed = rng_seed; a.subseq = rng_subsequence;
   return launch_mx_row_sr(a, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_quantize_row_and_col_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
+                                          uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc,
+                                          void* col_fp4, void* col_sc, void* stream) {
+  if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize_row_and_col_sr")) return rc;
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_quantize_row_and_col_sr: all four outputs are required");
+  if ((reinterpret_cast<uintptr_t>(row_fp4) | reinterpret_cast<uintptr_t>(col_fp4)) & 7)
+    return set_error("mxfp4_quantize_row_and_col_sr: code outputs must be 8-byte aligned");
+  if (M * (K >> 4) > (int64_t)0x7fffffff * 128) return set_error("mxfp4_quantize_row_and_col_sr: tensor too large");
+  MxSrArgs a{};
+  a.x = reinterpret_cast<const __nv_bfloat16*>(x_bf16); a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc;
+  a.col_fp4 = (uint8_t*)col_fp4; a.col_sc = (uint8_t*)col_sc;
+  a.M = M; a.K = K; a.mode = mode; a.data_sr = data_sr != 0; a.scale_sr = scale_sr != 0; a.correlated = 1;
+  a.seed = rng_seed; a.subseq = rng_subsequence;
+  if (int rc = launch_mx_row_sr(a, (cudaStream_t)stream)) return rc;
+  return launch_mx_col_sr(a, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -55,6 +55,42 @@ def mxfp4_quantize_for_gemm_opt(input, mode=0, data_stochastic_rounding=False, s
     return rf.view(_FP4), rs
 
 
+# The reference advances a device-global offset by 2^40 per stochastic row + column launch
+# (mxfp4_forward_sr_invocation_offset, tk_quantize.cu:33-48) and adds it to the caller's subsequence; the mirror
+# keeps the count on the host, readable and settable so that a resumed run or a test can restore it.
+_SR_INVOCATION_STRIDE = 1 << 40
+_sr_invocations = 0
+
+
+def mxfp4_forward_sr_invocation_count():
+    return _sr_invocations
+
+
+def mxfp4_set_forward_sr_invocation_count(n):
+    global _sr_invocations
+    _sr_invocations = int(n)
+
+
+def mxfp4_quantize_row_and_col_opt(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
+                                   rng_seed=0, rng_subsequence=0):
+    """tk_quantize.cu:2920-2953 (bound at 7397) — (row_fp4, row_sc, col_fp4, col_sc) with stochastic rounding; the
+    codes of the two views agree element by element ("correlated" rounding).  With neither flag it is
+    ``mxfp4_quantize_row_and_col``."""
+    global _sr_invocations
+    if not data_stochastic_rounding and not scale_stochastic_rounding:
+        return mxfp4_quantize_row_and_col(input, mode)
+    M, K = _check_bf16_2d(input, "input")
+    base = (int(rng_subsequence) + _sr_invocations * _SR_INVOCATION_STRIDE) & 0xFFFFFFFFFFFFFFFF
+    _sr_invocations += 1
+    with torch.cuda.device(input.device):
+        rf, rs, cf, cs = _alloc(M, K, input.device, True)
+        _lib.call("fp4b200_mxfp4_quantize_row_and_col_sr", input.data_ptr(), M, K, int(mode),
+                  int(bool(data_stochastic_rounding)), int(bool(scale_stochastic_rounding)),
+                  int(rng_seed) & 0xFFFFFFFFFFFFFFFF, base, rf.data_ptr(), rs.data_ptr(), cf.data_ptr(), cs.data_ptr(),
+                  _stream(input))
+    return rf.view(_FP4), rs, cf.view(_FP4), cs
+
+
 def mxfp4_quantize_row_and_col(input, mode=0):
     """tk_quantize.cu:7344 — (row_fp4, row_sc, col_fp4, col_sc)."""
     rf, rs, cf, cs = _quant(input, mode, True)

@@ -555,6 +555,136 @@ def mxfp4_quantize_for_gemm_opt(x: np.ndarray, mode: int, data_sr: bool, scale_s
     return pack_fp4(codes), swizzle_scales(e_logical), e_logical
 
 
+def _gf16_xtime(v: np.ndarray) -> np.ndarray:
+    """Multiplication by x in GF(2^16) modulo x^16 + x^12 + x^3 + x + 1 (mxfp4_v3_quantize.cuh:1359-1362)."""
+    v = v.astype(np.uint32)
+    return (((v << np.uint32(1)) & np.uint32(0xFFFF)) ^ (np.where((v >> np.uint32(15)) != 0, 0x100B, 0).astype(np.uint32))).astype(np.uint32)
+
+
+def mxfp4_correlated_sr_words(base: np.ndarray, row: np.ndarray, col: np.ndarray, row_vector: bool) -> np.ndarray:
+    """``mxfp4_correlated_sr_rbits16`` (mxfp4_v3_quantize.cuh:1375-1432): the four rounding words of 16 consecutive
+    elements of a row (row_vector) or of a column, such that both views give an element the same 16-bit integer.
+    A hash of (base, row >> 4, col >> 4) yields a pair (a, b) of GF(2^16) elements per 16x16 tile; the 2x2 cell
+    (i >> 1, j >> 1) of the tile gets the field b + a * p with p the polynomial whose bits are (j >> 1) | (i >> 1) << 3.
+    A vector holds eight fields, packed two per word in the byte order the conversion instruction reads them (see
+    e2m1_encode_sr): its even elements round with the field, its odd ones with the field bit-reversed; the callers
+    exchange neighbours in odd rows / columns, so element (i, j) uses the plain field iff i + j is even in both
+    views.  Returns uint32 [..., 4]."""
+    base = np.asarray(base, dtype=np.uint64)
+    row = np.asarray(row).astype(np.uint32)
+    col = np.asarray(col).astype(np.uint32)
+    t = ((base & np.uint64(0xFFFFFFFF)) ^ (base >> np.uint64(32))).astype(np.uint32)
+    t = t ^ ((row >> np.uint32(4)) * np.uint32(0x9E3779B9))
+    t = t ^ ((col >> np.uint32(4)) * np.uint32(0x85EBCA6B))
+    t = t ^ (t >> np.uint32(16)); t = t * np.uint32(0x7FEB352D)
+    t = t ^ (t >> np.uint32(15)); t = t * np.uint32(0x846CA68B)
+    t = t ^ (t >> np.uint32(16))
+    a1 = t & np.uint32(0xFFFF)
+    b = t >> np.uint32(16)
+    a2 = _gf16_xtime(a1); a4 = _gf16_xtime(a2); a8 = _gf16_xtime(a4); a16 = _gf16_xtime(a8); a32 = _gf16_xtime(a16)
+    grp = ((row if row_vector else col) & np.uint32(14)) >> np.uint32(1)
+    sel = (a8, a16, a32) if row_vector else (a1, a2, a4)
+    prod = np.zeros_like(t)
+    for bit in range(3):
+        prod = prod ^ np.where(((grp >> np.uint32(bit)) & np.uint32(1)) != 0, sel[bit], 0).astype(np.uint32)
+    f0 = b ^ prod
+    s1, s2, s4 = (a1, a2, a4) if row_vector else (a8, a16, a32)
+    f = [f0, f0 ^ s1, f0 ^ s2, f0 ^ s1 ^ s2, f0 ^ s4, f0 ^ s4 ^ s1, f0 ^ s4 ^ s2, f0 ^ s4 ^ s1 ^ s2]
+
+    def pack(ef, ab):
+        return (((ab & 0xFF00) << 16) | ((ef & 0xFF00) << 8) | ((ab & 0xFF) << 8) | (ef & 0xFF)).astype(np.uint32)
+
+    return np.stack([pack(f[0], f[1]), pack(f[2], f[3]), pack(f[4], f[5]), pack(f[6], f[7])], axis=-1)
+
+
+_MX_CORRELATED_SALT = 0xA0761D6478BD642F
+_M64 = (1 << 64) - 1
+
+
+def _sr_swapped_pairs(scaled4: np.ndarray, words: np.ndarray, swap: np.ndarray) -> np.ndarray:
+    """e2m1_encode_sr of groups of four, with the elements of each adjacent pair exchanged before and the codes
+    exchanged back after the conversion where ``swap`` is set (mxfp4_swap_bf16_pair_lanes /
+    mxfp4_swap_fp4_pair_lanes, mxfp4_v3_quantize.cuh:1434-1447)."""
+    perm = [1, 0, 3, 2]
+    sw = swap[..., None, None]
+    codes = e2m1_encode_sr(np.where(sw, scaled4[..., perm], scaled4), words)
+    return np.where(sw, codes[..., perm], codes)
+
+
+def mxfp4_quantize_row_and_col_opt(x: np.ndarray, mode: int, data_sr: bool, scale_sr: bool, seed: int, subseq: int):
+    """``mxfp4_quantize_row_and_col_opt`` without a Hadamard transform (mxfp4_v4/tk_quantize.cu:2820-2953; kernel
+    mxfp4_v4_rowcol_fused_kernel_opt, quantize_chunk_rowcol_pipelined_opt, mx_rowwise_quantize_opt,
+    mx_colwise_quantize_direct_opt: mxfp4_v3_quantize.cuh:5443-5560, 3321-3430, 1618-1790, 4031-4230).
+    ``subseq`` is the subsequence base the launch ends up with (the caller's plus the invocation offset).
+    Codes: "correlated" stochastic rounding — both views round element (i, j) with the same 16-bit integer, from
+    mxfp4_correlated_sr_words with base = seed ^ (subseq + chunk * 512) ^ salt.  Scale bytes: each thread of the
+    reference rounds its block's exponent with a word of its own Philox stream (row view: draw number = the
+    iteration; column view: draws 0 and 1 for its two columns), the thread of the first 16 elements stores."""
+    x = np.asarray(x, dtype=F32)
+    M, K = x.shape
+    assert M % 128 == 0 and K % 128 == 0
+    gx, gy = K // 128, M // 128
+
+    def draw(seq, n):
+        blk = philox4x32_10(seed, seq, (n >> 2).astype(np.uint64))
+        return np.take_along_axis(blk, (n & 3)[..., None], axis=-1)[..., 0]
+
+    def base_of(chunk):
+        return ((np.uint64(subseq) + chunk.astype(np.uint64) * np.uint64(512)) ^ np.uint64(seed & _M64)
+                ^ np.uint64(_MX_CORRELATED_SALT)).astype(np.uint64)
+
+    # ---- row view: segment (r, c) = 16 elements of row r from column c
+    r = np.arange(M)[:, None]
+    c = (np.arange(K // 16) * 16)[None, :]
+    rr, cc = r & 127, c & 127
+    chunk = (r >> 7) * gx + (c >> 7)
+    tile = (rr >> 6) * 2 + (cc >> 6)
+    tid = (rr & 31) * 4 + ((cc & 63) >> 4)
+    it = ((rr & 63) >> 5) + np.zeros_like(tid)
+    seq = (np.uint64(subseq) + ((chunk * 4 + tile) * 128 + tid).astype(np.uint64)).astype(np.uint64)
+    seg = x.reshape(M, K // 16, 16)
+    smax = np.abs(seg).max(axis=-1)
+    bm = np.maximum(smax, smax.reshape(M, K // 32, 2)[:, :, ::-1].reshape(M, K // 16))
+    e = mx_e8m0_sr(bm, draw(seq, it)) if scale_sr else mx_e8m0(bm, mode)
+    with np.errstate(over="ignore", invalid="ignore"):
+        scaled = (seg * (F32(6.0) * _mx_rcp(e)).astype(F32)[..., None]).astype(F32)
+    if data_sr:
+        words = mxfp4_correlated_sr_words(base_of(chunk), r + np.zeros_like(c), c + np.zeros_like(r), True)
+        codes = _sr_swapped_pairs(scaled.reshape(M, K // 16, 4, 4), words, ((r & 1) == 1) | np.zeros_like(c, dtype=bool))
+        codes = codes.reshape(M, K)
+    else:
+        codes = e2m1_encode_rn(scaled).reshape(M, K)
+    row_e = np.ascontiguousarray(e[:, 0::2])
+    row_fp4 = pack_fp4(codes)
+
+    # ---- column view: segment (j, i0) = the 16 rows from i0 of column j
+    j = np.arange(K)[:, None]
+    i0 = (np.arange(M // 16) * 16)[None, :]
+    jj, ii = j & 127, i0 & 127
+    chunk_in = (i0 >> 7) * gx + (j >> 7)            # the chunk of the input both views belong to
+    chunk_col = (j >> 7) * gy + (i0 >> 7)           # its number in the column view's stream
+    tile = (jj >> 6) * 2 + (ii >> 6)
+    tx, ty = (jj & 63) >> 1, (ii & 63) >> 4
+    tid = ((tx >> 4) * 2 + (ty >> 1)) * 32 + (ty & 1) * 16 + (tx & 15)
+    seq = (np.uint64(subseq) + ((chunk_col * 4 + tile) * 128 + tid).astype(np.uint64)).astype(np.uint64)
+    xt = np.ascontiguousarray(x.T)
+    seg = xt.reshape(K, M // 16, 16)
+    smax = np.abs(seg).max(axis=-1)
+    bm = np.maximum(smax, smax.reshape(K, M // 32, 2)[:, :, ::-1].reshape(K, M // 16))
+    e = mx_e8m0_sr(bm, draw(seq, (j & 1) + np.zeros_like(tid))) if scale_sr else mx_e8m0(bm, mode)
+    with np.errstate(over="ignore", invalid="ignore"):
+        scaled = (seg * (F32(6.0) * _mx_rcp(e)).astype(F32)[..., None]).astype(F32)
+    if data_sr:
+        words = mxfp4_correlated_sr_words(base_of(chunk_in), i0 + np.zeros_like(j), j + np.zeros_like(i0), False)
+        codes = _sr_swapped_pairs(scaled.reshape(K, M // 16, 4, 4), words, ((j & 1) == 1) | np.zeros_like(i0, dtype=bool))
+        codes = codes.reshape(K, M)
+    else:
+        codes = e2m1_encode_rn(scaled).reshape(K, M)
+    col_e = np.ascontiguousarray(e[:, 0::2])
+    return dict(row_fp4=row_fp4, row_sc=swizzle_scales(row_e), row_sc_logical=row_e,
+                col_fp4=pack_fp4(codes), col_sc=swizzle_scales(col_e), col_sc_logical=col_e)
+
+
 def _mx_rcp(e: np.ndarray) -> np.ndarray:
     """exp2f_rcp (util/ptx.cuh:330-338): 2^(127-e) built from the exponent field; e = 254 -> 2^-127."""
     rcp = ((254 - e.astype(np.int64)).clip(0, 254).astype(np.uint32) << 23).view(np.float32)

@@ -182,3 +182,48 @@ def test_mxfp4_quantize_for_gemm_opt_without_flags_is_the_plain_quantiser_and_sr
     assert abs((deq - x).mean()) < 4.0 * np.linalg.norm(deq - x) / (M * K)   # four standard errors of the mean
     assert np.linalg.norm(deq - x) < 1.7 * np.linalg.norm(rn - x)
     assert_status_ok()
+
+
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (384, 256)])
+@pytest.mark.parametrize("data_sr,scale_sr", [(True, False), (False, True), (True, True)])
+@pytest.mark.parametrize("mode", [0, 1])
+def test_mxfp4_quantize_row_and_col_opt_stochastic(shape, data_sr, scale_sr, mode):
+    """Row + column launch with correlated rounding of the codes and Philox rounding of the scales, bit for bit,
+    on the second call of a run (the invocation offset of 2^40 is part of the stream's base)."""
+    mxq = mod("mxfp4_quant_v4")
+    x = o.make_activations(*shape, seed=sum(shape) + mode)
+    x[3, 64:96] = 0.0
+    seed, subseq = 0xC0FFEE, 456
+    mxq.mxfp4_set_forward_sr_invocation_count(1)
+    out = mxq.mxfp4_quantize_row_and_col_opt(to_dev_bf16(x), mode, data_sr, scale_sr, seed, subseq)
+    torch.cuda.synchronize()
+    assert mxq.mxfp4_forward_sr_invocation_count() == 2
+    _check(out, o.mxfp4_quantize_row_and_col_opt(x, mode, data_sr, scale_sr, seed, subseq + (1 << 40)))
+    assert_status_ok()
+
+
+def test_mxfp4_correlated_rounding_agrees_between_the_views_and_advances():
+    """The property the reference's own test of this launch asserts (mxfp4_v4/test_correlated_dual_sr.py): with the
+    same maximum in every row block and column block, the row codes equal the transposed column codes, and two
+    calls in a row round differently."""
+    mxq = mod("mxfp4_quant_v4")
+    n = 512
+    ri, ci = np.arange(n)[:, None], np.arange(n)[None, :]
+    peak = (ri % 32) == (ci % 32)
+    rng = np.random.default_rng(17)
+    x = (0.2 + 0.5 * rng.random((n, n))).astype(np.float32) * np.where(rng.random((n, n)) < 0.5, -1.0, 1.0)
+    x[peak] = 1.0
+    xd = to_dev_bf16(o.bf16_round(x.astype(np.float32)))
+    mxq.mxfp4_set_forward_sr_invocation_count(0)
+    prev = None
+    for _ in range(3):
+        out = mxq.mxfp4_quantize_row_and_col_opt(xd, 0, True, False, 123, 456)
+        row = o.unpack_fp4(u8(out[0]))
+        col = o.unpack_fp4(u8(out[2])).T
+        assert np.array_equal(row, col)
+        assert torch.equal(out[1], out[3])
+        if prev is not None:
+            assert (row != prev).mean() > 0.01
+        prev = row
+    assert mxq.mxfp4_forward_sr_invocation_count() == 3
+    assert_status_ok()
