@@ -234,9 +234,14 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
  * rng_subsequence + ((chunk * 4 + tile) * 128 + thread), offset 0); scale_sr rounds the E8M0 byte up with
  * probability mantissa / 2^23 (and replaces the mode's rule).  Each 16-element half of a 32-block rounds the
  * scale with its own word: the stored byte is the first half's, the second half's codes use its own, as the
- * reference does.  M, K multiples of 128; row_fp4 [M, K/2], row_sc [M/128, K/128, 512]. */
+ * reference does.  rht_block 16 or 32 (mxfp4_quantize_for_gemm_opt_rht, tk_quantize.cu:1883-2060): a Hadamard
+ * transform of that many consecutive elements of a row in front of the quantisation (fp32 butterflies, block
+ * maximum of the fp32 output, codes from its bf16 rounding), behind the reference's fixed sign diagonal when
+ * rht_sign is set; with a transform both SR flags may be 0.  M, K multiples of 128; row_fp4 [M, K/2],
+ * row_sc [M/128, K/128, 512]. */
 int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
-                                  uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* stream);
+                                  int rht_block, int rht_sign, uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4,
+                                  void* row_sc, void* stream);
 
 /* mxfp4_quantize_row_and_col_opt(input, mode, data_stochastic_rounding, scale_stochastic_rounding, rng_seed,
  * rng_subsequence) without a Hadamard transform (mxfp4_v4/tk_quantize.cu:2820-2953; kernel
@@ -245,10 +250,14 @@ int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int 
  * calls; the Python mirror keeps that counter).  data_sr is the reference's "correlated" rounding: the row and the
  * column view round element (i, j) with the same 16-bit integer, derived from (rng_seed, base, chunk, i, j) by a
  * GF(2^16) construction instead of the Philox stream; scale_sr draws from the reference threads' Philox streams
- * as in fp4b200_mxfp4_quantize_row_sr (column view: its own subsequences). */
+ * as in fp4b200_mxfp4_quantize_row_sr (column view: its own subsequences).  row_rht / col_rht with rht_block 16 or
+ * 32 (mxfp4_quantize_row_and_col_opt_rht: column view only, _rht_both, _rht_row_only; tk_quantize.cu:2955-3146)
+ * transform the row view along K and / or the column view along M; data_sr then draws from the Philox streams in
+ * both views instead of the correlated construction, as the reference does. */
 int fp4b200_mxfp4_quantize_row_and_col_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
-                                          uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc,
-                                          void* col_fp4, void* col_sc, void* stream);
+                                          int rht_block, int rht_sign, int row_rht, int col_rht, uint64_t rng_seed,
+                                          uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* col_fp4,
+                                          void* col_sc, void* stream);
 
 /* nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps) (nvfp4_b200_gemm.cu:1792-1803; kernel
  * common/c1_rms_reduce.cuh:11-38), also the first step of tk_fused_norm_quantize_from_row_rms_partial

@@ -60,8 +60,9 @@ SIGNATURES = {
                                   ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
                                   _c_void_p, _int, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_quantize_weight_2d": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
-    "fp4b200_mxfp4_quantize_row_sr": [_c_void_p, _i64, _i64, _int, _int, _int, ctypes.c_uint64, ctypes.c_uint64, _c_void_p, _c_void_p, _c_void_p],
-    "fp4b200_mxfp4_quantize_row_and_col_sr": [_c_void_p, _i64, _i64, _int, _int, _int, ctypes.c_uint64, ctypes.c_uint64, _c_void_p,
+    "fp4b200_mxfp4_quantize_row_sr": [_c_void_p, _i64, _i64, _int, _int, _int, _int, _int, ctypes.c_uint64, ctypes.c_uint64, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_mxfp4_quantize_row_and_col_sr": [_c_void_p, _i64, _i64, _int, _int, _int, _int, _int, _int, _int, ctypes.c_uint64,
+                                              ctypes.c_uint64, _c_void_p,
                                               _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_row_rms_reduce": [_c_void_p, _i64, _i64, _i64, _f32, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_for_gemm_into": [_c_void_p, _i64, _i64, _int, _int, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p,

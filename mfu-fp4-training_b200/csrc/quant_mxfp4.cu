@@ -273,6 +273,9 @@ struct MxSrArgs {
   int mode, data_sr, scale_sr;
   unsigned long long seed, subseq;
   int correlated;     // row + column launch: the codes round with the position's shared 16-bit integer (below)
+  int rht_block;      // 0, or 16 / 32: Hadamard transform of that many consecutive elements along the quantised axis
+  int rht_sign;       // the reference's fixed sign diagonal (bit i of 0x2817 set: +1) in front of the transform
+  int row_rht, col_rht;
   uint8_t* col_fp4;   // [K, M/2]            (column kernel)
   uint8_t* col_sc;    // [K/128, M/128, 512]
 };
@@ -324,6 +327,44 @@ __device__ __forceinline__ uint2 mx_quant16_sr(const uint32_t (&w)[8], float coe
 }
 
 constexpr unsigned long long kMxCorrelatedSalt = 0xA0761D6478BD642Full;
+constexpr uint32_t kMxRhtSignBits = 0x00002817u;   // make_rht_sign_bits, mxfp4_v3_quantize.cuh:1461-1476
+
+// Signs and the 16-point butterflies (steps 1, 2, 4, 8; sum to the low index, difference to the high one), not yet
+// normalised (reference: apply_block_rht_registers / fwht16_unnormalized, mxfp4_v3_quantize.cuh:1478-1530).
+__device__ __forceinline__ void mx_fwht16(float (&v)[16], bool sign) {
+  if (sign) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] *= ((kMxRhtSignBits >> i) & 1u) ? 1.0f : -1.0f;
+  }
+#pragma unroll
+  for (int step = 1; step < 16; step <<= 1) {
+#pragma unroll
+    for (int base = 0; base < 16; base += 2 * step) {
+#pragma unroll
+      for (int j = 0; j < step; ++j) {
+        const float p = v[base + j], q = v[base + j + step];
+        v[base + j] = p + q;
+        v[base + j + step] = p - q;
+      }
+    }
+  }
+}
+
+// Last stage of the 32-point transform (first half: own + peer, second half: peer - own) and the normalisation
+__device__ __forceinline__ void mx_rht_finish(float (&v)[16], const float (&peer)[16], int block, int rank) {
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    if (block == 32) v[i] = ((rank == 0) ? (v[i] + peer[i]) : (peer[i] - v[i])) * 0.1767766952966369f;
+    else v[i] *= 0.25f;
+  }
+}
+
+__device__ __forceinline__ float mx_amax16(const float (&v)[16]) {
+  float m = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(v[i]));
+  return m;
+}
 
 __device__ __forceinline__ uint32_t mx_e8m0_sr(float b, uint32_t rbits) {
   if (b <= 1e-38f) return 0;
@@ -341,11 +382,25 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_row_sr_kernel(const MxSrAr
   const int c = (int)(idx - r * segs_per_row) << 4;
   const uint4* src = reinterpret_cast<const uint4*>(a.x + r * a.K + c);
   const uint4 v0 = __ldg(src), v1 = __ldg(src + 1);
-  const uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
-  uint32_t mx = 0;
+  uint32_t w[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+  float bm;
+  if (a.row_rht) {
+    float t[16], peer[16];
 #pragma unroll
-  for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[q]);
-  float bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+    for (int q = 0; q < 8; ++q) { t[2 * q] = bf16lo_to_f32(w[q]); t[2 * q + 1] = bf16hi_to_f32(w[q]); }
+    mx_fwht16(t, a.rht_sign != 0);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) peer[i] = __shfl_xor_sync(0xffffffffu, t[i], 1);
+    mx_rht_finish(t, peer, a.rht_block, (c >> 4) & 1);
+    bm = mx_amax16(t);   // of the transform's fp32 output; the codes come from its bf16 rounding
+#pragma unroll
+    for (int q = 0; q < 8; ++q) w[q] = f32x2_to_bf16x2(t[2 * q], t[2 * q + 1]);
+  } else {
+    uint32_t mx = 0;
+#pragma unroll
+    for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[q]);
+    bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+  }
   bm = fmaxf(bm, __shfl_xor_sync(0xffffffffu, bm, 1));
 
   // the reference thread that owns this segment, and where this row sits in its draw order
@@ -400,15 +455,49 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_col_sr_kernel(const MxSrAr
   const uint32_t* other = reinterpret_cast<const uint32_t*>(a.x + (i0 ^ 16) * a.K + j);
   const int64_t ld = a.K >> 1;   // row pitch in 32-bit words
   uint32_t v[16];
-  uint32_t mx = 0;
+  float bm0, bm1;
+  if (a.col_rht) {
+    // both halves of the 32-row block are transformed here: the partner's output is needed for the block maximum
+    // (and, for 32-point blocks, its butterflies for this half's last stage)
+    const int rank = (int)(i0 >> 4) & 1;
+    float bm[2];
 #pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    v[i] = __ldg(own + i * ld);
-    mx = absmax_xs(mx, v[i]);
+    for (int cpar = 0; cpar < 2; ++cpar) {
+      float t[16], u[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t wo = __ldg(own + i * ld), wp = __ldg(other + i * ld);
+        t[i] = cpar ? bf16hi_to_f32(wo) : bf16lo_to_f32(wo);
+        u[i] = cpar ? bf16hi_to_f32(wp) : bf16lo_to_f32(wp);
+      }
+      mx_fwht16(t, a.rht_sign != 0);
+      mx_fwht16(u, a.rht_sign != 0);
+      float tt[16];
+#pragma unroll
+      for (int i = 0; i < 16; ++i) tt[i] = t[i];
+      mx_rht_finish(t, u, a.rht_block, rank);
+      mx_rht_finish(u, tt, a.rht_block, rank ^ 1);
+      bm[cpar] = fmaxf(mx_amax16(t), mx_amax16(u));
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        const uint32_t h = f32x2_to_bf16x2(t[i], 0.0f) & 0xFFFFu;
+        v[i] = cpar ? (v[i] | (h << 16)) : h;
+      }
+    }
+    bm0 = bm[0];
+    bm1 = bm[1];
+  } else {
+    uint32_t mx = 0;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      v[i] = __ldg(own + i * ld);
+      mx = absmax_xs(mx, v[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < 16; ++i) mx = absmax_xs(mx, __ldg(other + i * ld));
+    bm0 = fabsf(bf16lo_to_f32(mx));
+    bm1 = fabsf(bf16hi_to_f32(mx));
   }
-#pragma unroll
-  for (int i = 0; i < 16; ++i) mx = absmax_xs(mx, __ldg(other + i * ld));
-  const float bm0 = fabsf(bf16lo_to_f32(mx)), bm1 = fabsf(bf16hi_to_f32(mx));
 
   const int jj = j & 127, ii = (int)(i0 & 127);
   const int tile = (jj >> 6) * 2 + (ii >> 6);
@@ -417,8 +506,9 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_col_sr_kernel(const MxSrAr
   const unsigned long long chunk_col = (unsigned long long)(j >> 7) * (unsigned long long)(a.M >> 7) + (unsigned long long)(i0 >> 7);
   const unsigned long long chunk_in = (unsigned long long)(i0 >> 7) * (unsigned long long)(a.K >> 7) + (unsigned long long)(j >> 7);
   uint32_t e0, e1;
+  const unsigned long long seq = a.subseq + (chunk_col * 4ull + (unsigned long long)tile) * 128ull + (unsigned long long)tid_ref;
   if (a.scale_sr) {
-    const uint4 rw = philox4x32_10(a.seed, a.subseq + (chunk_col * 4ull + (unsigned long long)tile) * 128ull + (unsigned long long)tid_ref, 0ull);
+    const uint4 rw = philox4x32_10(a.seed, seq, 0ull);
     e0 = mx_e8m0_sr(bm0, rw.x);
     e1 = mx_e8m0_sr(bm1, rw.y);
   } else {
@@ -433,13 +523,22 @@ __global__ void __launch_bounds__(256) mxfp4_quantize_col_sr_kernel(const MxSrAr
     c1[q] = __byte_perm(v[2 * q], v[2 * q + 1], 0x7632);
   }
   uint2 o0, o1;
-  if (a.data_sr) {
+  if (a.data_sr && a.correlated) {
     const unsigned long long base = (a.subseq + chunk_in * 512ull) ^ a.seed ^ kMxCorrelatedSalt;
     const uint4 w0 = mx_correlated_words<false>(base, (uint32_t)i0, (uint32_t)j);
     const uint4 w1 = mx_correlated_words<false>(base, (uint32_t)i0, (uint32_t)j + 1u);
     const uint32_t ws0[4] = {w0.x, w0.y, w0.z, w0.w}, ws1[4] = {w1.x, w1.y, w1.z, w1.w};
     o0 = mx_quant16_sr(c0, mx_coeff(e0), ws0, false);   // j is even
     o1 = mx_quant16_sr(c1, mx_coeff(e1), ws1, true);
+  } else if (a.data_sr) {
+    // the thread's own stream: after the two scale words (scale SR), four words for each of its two columns
+    const int d0 = a.scale_sr ? 2 : 0;
+    uint32_t da[5], db[5];
+    philox_draws(a.seed, seq, 0ull, d0, 4, da);
+    philox_draws(a.seed, seq, 0ull, d0 + 4, 4, db);
+    const uint32_t ws0[4] = {da[0], da[1], da[2], da[3]}, ws1[4] = {db[0], db[1], db[2], db[3]};
+    o0 = mx_quant16_sr(c0, mx_coeff(e0), ws0, false);
+    o1 = mx_quant16_sr(c1, mx_coeff(e1), ws1, false);
   } else {
     o0 = make_uint2(quant8(c0, mx_coeff(e0)), quant8(c0 + 4, mx_coeff(e0)));
     o1 = make_uint2(quant8(c1, mx_coeff(e1)), quant8(c1 + 4, mx_coeff(e1)));
@@ -543,9 +642,16 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
   return launch_mx(w_bf16, N, K, 1, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, true);
 }
 
+static int check_mx_rht(int rht_block, const char* who) {
+  if (rht_block != 0 && rht_block != 16 && rht_block != 32) return set_error("%s: RHT block size must be 16 or 32 (0: no transform)", who);
+  return 0;
+}
+
 int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
-                                  uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* stream) {
+                                  int rht_block, int rht_sign, uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4,
+                                  void* row_sc, void* stream) {
   if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize_row_sr")) return rc;
+  if (int rc = check_mx_rht(rht_block, "mxfp4_quantize_row_sr")) return rc;
   if (!row_fp4 || !row_sc) return set_error("mxfp4_quantize_row_sr: row_fp4 and row_sc are required");
   if (reinterpret_cast<uintptr_t>(row_fp4) & 7) return set_error("mxfp4_quantize_row_sr: row_fp4 must be 8-byte aligned");
   if (M * (K >> 4) > (int64_t)0x7fffffff * 256) return set_error("mxfp4_quantize_row_sr: tensor too large");
@@ -553,13 +659,18 @@ int fp4b200_mxfp4_quantize_row_sr(const void* x_bf16, int64_t M, int64_t K, int 
   a.x = reinterpret_cast<const __nv_bfloat16*>(x_bf16); a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc;
   a.M = M; a.K = K; a.mode = mode; a.data_sr = data_sr != 0; a.scale_sr = scale_sr != 0;
   a.seed = rng_seed; a.subseq = rng_subsequence;
+  a.rht_block = rht_block; a.rht_sign = rht_sign != 0; a.row_rht = rht_block != 0;
   return launch_mx_row_sr(a, (cudaStream_t)stream);
 }
 
 int fp4b200_mxfp4_quantize_row_and_col_sr(const void* x_bf16, int64_t M, int64_t K, int mode, int data_sr, int scale_sr,
-                                          uint64_t rng_seed, uint64_t rng_subsequence, void* row_fp4, void* row_sc,
-                                          void* col_fp4, void* col_sc, void* stream) {
+                                          int rht_block, int rht_sign, int row_rht, int col_rht, uint64_t rng_seed,
+                                          uint64_t rng_subsequence, void* row_fp4, void* row_sc, void* col_fp4,
+                                          void* col_sc, void* stream) {
   if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize_row_and_col_sr")) return rc;
+  if (int rc = check_mx_rht(rht_block, "mxfp4_quantize_row_and_col_sr")) return rc;
+  if ((rht_block == 0) != (!row_rht && !col_rht))
+    return set_error("mxfp4_quantize_row_and_col_sr: a transform needs a block size and at least one axis");
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_quantize_row_and_col_sr: all four outputs are required");
   if ((reinterpret_cast<uintptr_t>(row_fp4) | reinterpret_cast<uintptr_t>(col_fp4)) & 7)
     return set_error("mxfp4_quantize_row_and_col_sr: code outputs must be 8-byte aligned");
@@ -567,7 +678,9 @@ int fp4b200_mxfp4_quantize_row_and_col_sr(const void* x_bf16, int64_t M, int64_t
   MxSrArgs a{};
   a.x = reinterpret_cast<const __nv_bfloat16*>(x_bf16); a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc;
   a.col_fp4 = (uint8_t*)col_fp4; a.col_sc = (uint8_t*)col_sc;
-  a.M = M; a.K = K; a.mode = mode; a.data_sr = data_sr != 0; a.scale_sr = scale_sr != 0; a.correlated = 1;
+  a.M = M; a.K = K; a.mode = mode; a.data_sr = data_sr != 0; a.scale_sr = scale_sr != 0;
+  a.rht_block = rht_block; a.rht_sign = rht_sign != 0; a.row_rht = row_rht != 0; a.col_rht = col_rht != 0;
+  a.correlated = a.data_sr && !a.row_rht && !a.col_rht;   // with a transform both views draw from their Philox streams
   a.seed = rng_seed; a.subseq = rng_subsequence;
   if (int rc = launch_mx_row_sr(a, (cudaStream_t)stream)) return rc;
   return launch_mx_col_sr(a, (cudaStream_t)stream);

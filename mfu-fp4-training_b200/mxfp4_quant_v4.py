@@ -39,23 +39,42 @@ def mxfp4_quantize_for_gemm(input, mode=0):
     return rf.view(_FP4), rs
 
 
+def _row_sr(input, mode, data_sr, scale_sr, rht_block, sign, rng_seed, rng_subsequence):
+    M, K = _check_bf16_2d(input, "input")
+    with torch.cuda.device(input.device):
+        rf, rs, _, _ = _alloc(M, K, input.device, False)
+        _lib.call("fp4b200_mxfp4_quantize_row_sr", input.data_ptr(), M, K, int(mode), int(bool(data_sr)), int(bool(scale_sr)),
+                  int(rht_block), int(bool(sign)), int(rng_seed) & 0xFFFFFFFFFFFFFFFF,
+                  int(rng_subsequence) & 0xFFFFFFFFFFFFFFFF, rf.data_ptr(), rs.data_ptr(), _stream(input))
+    return rf.view(_FP4), rs
+
+
 def mxfp4_quantize_for_gemm_opt(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
-                                rng_seed=0, rng_subsequence=0):
+                                rng_seed=1234, rng_subsequence=0):
     """tk_quantize.cu:1848-1881 (bound at 7285) — row-wise (fp4, scales) with stochastic rounding of the codes
     and / or of the E8M0 scale bytes, on the reference's Philox stream for (rng_seed, rng_subsequence); with
     neither flag it is ``mxfp4_quantize_for_gemm``."""
     if not data_stochastic_rounding and not scale_stochastic_rounding:
         return mxfp4_quantize_for_gemm(input, mode)
-    M, K = _check_bf16_2d(input, "input")
-    with torch.cuda.device(input.device):
-        rf, rs, _, _ = _alloc(M, K, input.device, False)
-        _lib.call("fp4b200_mxfp4_quantize_row_sr", input.data_ptr(), M, K, int(mode), int(bool(data_stochastic_rounding)),
-                  int(bool(scale_stochastic_rounding)), int(rng_seed) & 0xFFFFFFFFFFFFFFFF,
-                  int(rng_subsequence) & 0xFFFFFFFFFFFFFFFF, rf.data_ptr(), rs.data_ptr(), _stream(input))
-    return rf.view(_FP4), rs
+    return _row_sr(input, mode, data_stochastic_rounding, scale_stochastic_rounding, 0, False, rng_seed, rng_subsequence)
 
 
-# The reference advances a device-global offset by 2^40 per stochastic row + column launch
+def _check_rht_block(rht_block_size):
+    if int(rht_block_size) not in (16, 32):
+        raise RuntimeError("RHT block size must be 16 or 32")
+    return int(rht_block_size)
+
+
+def mxfp4_quantize_for_gemm_opt_rht(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
+                                    rht_block_size=16, with_random_sign_mask=True, rng_seed=1234, rng_subsequence=0):
+    """tk_quantize.cu:1883-2060 (bound at 7292) — as ``mxfp4_quantize_for_gemm_opt`` behind a Hadamard transform of
+    16 or 32 consecutive elements of each row (``with_random_sign_mask``: the reference's fixed sign diagonal in
+    front of it); both rounding flags may be off."""
+    return _row_sr(input, mode, data_stochastic_rounding, scale_stochastic_rounding, _check_rht_block(rht_block_size),
+                   with_random_sign_mask, rng_seed, rng_subsequence)
+
+
+# The reference advances a device-global offset by 2^40 per row + column launch that uses its generator
 # (mxfp4_forward_sr_invocation_offset, tk_quantize.cu:33-48) and adds it to the caller's subsequence; the mirror
 # keeps the count on the host, readable and settable so that a resumed run or a test can restore it.
 _SR_INVOCATION_STRIDE = 1 << 40
@@ -71,24 +90,54 @@ def mxfp4_set_forward_sr_invocation_count(n):
     _sr_invocations = int(n)
 
 
-def mxfp4_quantize_row_and_col_opt(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
-                                   rng_seed=0, rng_subsequence=0):
-    """tk_quantize.cu:2920-2953 (bound at 7397) — (row_fp4, row_sc, col_fp4, col_sc) with stochastic rounding; the
-    codes of the two views agree element by element ("correlated" rounding).  With neither flag it is
-    ``mxfp4_quantize_row_and_col``."""
+def _rowcol_sr(input, mode, data_sr, scale_sr, rht_block, sign, row_rht, col_rht, rng_seed, rng_subsequence):
     global _sr_invocations
-    if not data_stochastic_rounding and not scale_stochastic_rounding:
-        return mxfp4_quantize_row_and_col(input, mode)
     M, K = _check_bf16_2d(input, "input")
-    base = (int(rng_subsequence) + _sr_invocations * _SR_INVOCATION_STRIDE) & 0xFFFFFFFFFFFFFFFF
-    _sr_invocations += 1
+    base = int(rng_subsequence) & 0xFFFFFFFFFFFFFFFF
+    if data_sr or scale_sr or (rht_block and sign):   # the launches that prepare a generator state (tk_quantize.cu:2853-2860)
+        base = (base + _sr_invocations * _SR_INVOCATION_STRIDE) & 0xFFFFFFFFFFFFFFFF
+        _sr_invocations += 1
     with torch.cuda.device(input.device):
         rf, rs, cf, cs = _alloc(M, K, input.device, True)
-        _lib.call("fp4b200_mxfp4_quantize_row_and_col_sr", input.data_ptr(), M, K, int(mode),
-                  int(bool(data_stochastic_rounding)), int(bool(scale_stochastic_rounding)),
+        _lib.call("fp4b200_mxfp4_quantize_row_and_col_sr", input.data_ptr(), M, K, int(mode), int(bool(data_sr)),
+                  int(bool(scale_sr)), int(rht_block), int(bool(sign)), int(bool(row_rht)), int(bool(col_rht)),
                   int(rng_seed) & 0xFFFFFFFFFFFFFFFF, base, rf.data_ptr(), rs.data_ptr(), cf.data_ptr(), cs.data_ptr(),
                   _stream(input))
     return rf.view(_FP4), rs, cf.view(_FP4), cs
+
+
+def mxfp4_quantize_row_and_col_opt(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
+                                   rng_seed=1234, rng_subsequence=0):
+    """tk_quantize.cu:2920-2953 (bound at 7397) — (row_fp4, row_sc, col_fp4, col_sc) with stochastic rounding; the
+    codes of the two views agree element by element ("correlated" rounding).  With neither flag it is
+    ``mxfp4_quantize_row_and_col``."""
+    if not data_stochastic_rounding and not scale_stochastic_rounding:
+        return mxfp4_quantize_row_and_col(input, mode)
+    return _rowcol_sr(input, mode, data_stochastic_rounding, scale_stochastic_rounding, 0, False, False, False, rng_seed,
+                      rng_subsequence)
+
+
+def mxfp4_quantize_row_and_col_opt_rht(input, mode=0, data_stochastic_rounding=False, scale_stochastic_rounding=False,
+                                       rht_block_size=16, with_random_sign_mask=True, rng_seed=1234, rng_subsequence=0):
+    """tk_quantize.cu:3082-3102 (bound at 7404) — Hadamard transform along M on the column view only."""
+    return _rowcol_sr(input, mode, data_stochastic_rounding, scale_stochastic_rounding, _check_rht_block(rht_block_size),
+                      with_random_sign_mask, False, True, rng_seed, rng_subsequence)
+
+
+def mxfp4_quantize_row_and_col_opt_rht_both(input, mode=0, data_stochastic_rounding=False,
+                                            scale_stochastic_rounding=False, rht_block_size=16,
+                                            with_random_sign_mask=True, rng_seed=1234, rng_subsequence=0):
+    """tk_quantize.cu:3104-3124 (bound at 7413) — transform along K on the row view and along M on the column view."""
+    return _rowcol_sr(input, mode, data_stochastic_rounding, scale_stochastic_rounding, _check_rht_block(rht_block_size),
+                      with_random_sign_mask, True, True, rng_seed, rng_subsequence)
+
+
+def mxfp4_quantize_row_and_col_opt_rht_row_only(input, mode=0, data_stochastic_rounding=False,
+                                                scale_stochastic_rounding=False, rht_block_size=16,
+                                                with_random_sign_mask=True, rng_seed=1234, rng_subsequence=0):
+    """tk_quantize.cu:3126-3146 (bound at 7422) — transform along K on the row view only."""
+    return _rowcol_sr(input, mode, data_stochastic_rounding, scale_stochastic_rounding, _check_rht_block(rht_block_size),
+                      with_random_sign_mask, True, False, rng_seed, rng_subsequence)
 
 
 def mxfp4_quantize_row_and_col(input, mode=0):

@@ -509,13 +509,41 @@ def mx_e8m0_sr(block_amax: np.ndarray, rbits: np.ndarray) -> np.ndarray:
     return np.where(b <= F32(1e-38), 0, e + up).astype(np.uint8)
 
 
-def mxfp4_quantize_for_gemm_opt(x: np.ndarray, mode: int, data_sr: bool, scale_sr: bool, seed: int, subseq: int):
+_MX_RHT_SIGN_BITS = 0x2817
+
+
+def _mx_rht_segments(seg: np.ndarray, block: int, sign: bool) -> np.ndarray:
+    """Hadamard transform of 16 or 32 consecutive elements as the reference's threads compute it
+    (apply_block_rht_registers / fwht16_unnormalized, mxfp4_v3_quantize.cuh:1478-1530): seg [..., n, 16] holds the
+    16-element pieces, consecutive pieces forming the 32-blocks.  Fixed signs (bit i of 0x2817 set: +1), butterflies
+    of distance 1, 2, 4, 8 in fp32 (sum to the low index), for 32 the last stage across the two pieces (first: own +
+    peer, second: peer - own), then one multiplication by 0.25 or by float(1/sqrt(32))."""
+    v = np.array(seg, dtype=F32)
+    if sign:
+        v = v * np.array([1.0 if (_MX_RHT_SIGN_BITS >> i) & 1 else -1.0 for i in range(16)], dtype=F32)
+    lead = v.shape[:-1]
+    for step in (1, 2, 4, 8):
+        t = v.reshape(lead + (16 // (2 * step), 2, step))
+        p, q = t[..., 0, :], t[..., 1, :]
+        v = np.stack([(p + q).astype(F32), (p - q).astype(F32)], axis=-2).reshape(lead + (16,))
+    if block == 32:
+        t = v.reshape(lead[:-1] + (lead[-1] // 2, 2, 16))
+        p, q = t[..., 0, :], t[..., 1, :]
+        v = np.stack([(p + q).astype(F32), (p - q).astype(F32)], axis=-2).reshape(lead + (16,))
+        return (v * F32(0.1767766952966369)).astype(F32)
+    return (v * F32(0.25)).astype(F32)
+
+
+def mxfp4_quantize_for_gemm_opt(x: np.ndarray, mode: int, data_sr: bool, scale_sr: bool, seed: int, subseq: int,
+                                rht_block: int = 0, rht_sign: bool = False):
     """``mxfp4_quantize_for_gemm_opt`` (mxfp4_v4/tk_quantize.cu:1796-1881; mx_rowwise_quantize_opt,
     mxfp4_v3_quantize.cuh:1618-1790).  A reference thread owns 16 contiguous elements of the rows tid_Y and tid_Y + 32
     of a 64x64 tile; its Philox stream (subsequence subseq + ((chunk * 4 + tile) * 128 + thread), offset 0) gives per
     row one word for the scale byte (scale_sr) and then four for the codes (data_sr; lanes 16..31 of a warp take the
     two 8-element halves in swapped order).  Each half of a 32-block rounds the scale with its own word; the byte
-    stored is the first half's.  Returns (packed [M, K/2], swizzled scales, logical scale bytes [M, K/32])."""
+    stored is the first half's.  rht_block 16 / 32 (``mxfp4_quantize_for_gemm_opt_rht``, tk_quantize.cu:1883-2060):
+    the rows are transformed first (_mx_rht_segments), the block maximum is that of the fp32 output and the codes
+    come from its bf16 rounding.  Returns (packed [M, K/2], swizzled scales, logical scale bytes [M, K/32])."""
     x = np.asarray(x, dtype=F32)
     M, K = x.shape
     assert M % 128 == 0 and K % 128 == 0
@@ -536,7 +564,11 @@ def mxfp4_quantize_for_gemm_opt(x: np.ndarray, mode: int, data_sr: bool, scale_s
         return np.take_along_axis(blk, (n & 3)[..., None], axis=-1)[..., 0]
 
     seg = x.reshape(M, K // 16, 16)
-    seg_max = np.abs(seg).max(axis=-1)
+    if rht_block:
+        t = _mx_rht_segments(seg, rht_block, rht_sign)
+        seg_max, seg = np.abs(t).max(axis=-1), bf16_round(t)
+    else:
+        seg_max = np.abs(seg).max(axis=-1)
     bm = np.maximum(seg_max, seg_max.reshape(M, K // 32, 2)[:, :, ::-1].reshape(M, K // 16))   # the pair's maximum
     e = mx_e8m0_sr(bm, draw(n0)) if scale_sr else mx_e8m0(bm, mode)
     with np.errstate(over="ignore", invalid="ignore"):
@@ -611,7 +643,9 @@ def _sr_swapped_pairs(scaled4: np.ndarray, words: np.ndarray, swap: np.ndarray) 
     return np.where(sw, codes[..., perm], codes)
 
 
-def mxfp4_quantize_row_and_col_opt(x: np.ndarray, mode: int, data_sr: bool, scale_sr: bool, seed: int, subseq: int):
+def mxfp4_quantize_row_and_col_opt(x: np.ndarray, mode: int, data_sr: bool, scale_sr: bool, seed: int, subseq: int,
+                                   rht_block: int = 0, rht_sign: bool = False, row_rht: bool = False,
+                                   col_rht: bool = False):
     """``mxfp4_quantize_row_and_col_opt`` without a Hadamard transform (mxfp4_v4/tk_quantize.cu:2820-2953; kernel
     mxfp4_v4_rowcol_fused_kernel_opt, quantize_chunk_rowcol_pipelined_opt, mx_rowwise_quantize_opt,
     mx_colwise_quantize_direct_opt: mxfp4_v3_quantize.cuh:5443-5560, 3321-3430, 1618-1790, 4031-4230).
@@ -619,7 +653,10 @@ def mxfp4_quantize_row_and_col_opt(x: np.ndarray, mode: int, data_sr: bool, scal
     Codes: "correlated" stochastic rounding — both views round element (i, j) with the same 16-bit integer, from
     mxfp4_correlated_sr_words with base = seed ^ (subseq + chunk * 512) ^ salt.  Scale bytes: each thread of the
     reference rounds its block's exponent with a word of its own Philox stream (row view: draw number = the
-    iteration; column view: draws 0 and 1 for its two columns), the thread of the first 16 elements stores."""
+    iteration; column view: draws 0 and 1 for its two columns), the thread of the first 16 elements stores.
+    With a transform on either view (``..._opt_rht``: column view, ``_rht_both``, ``_rht_row_only``;
+    tk_quantize.cu:2955-3146) the codes of BOTH views round with Philox words instead: row view four words per
+    iteration after the scale word, column view four per column after the two scale words."""
     x = np.asarray(x, dtype=F32)
     M, K = x.shape
     assert M % 128 == 0 and K % 128 == 0
@@ -642,13 +679,25 @@ def mxfp4_quantize_row_and_col_opt(x: np.ndarray, mode: int, data_sr: bool, scal
     tid = (rr & 31) * 4 + ((cc & 63) >> 4)
     it = ((rr & 63) >> 5) + np.zeros_like(tid)
     seq = (np.uint64(subseq) + ((chunk * 4 + tile) * 128 + tid).astype(np.uint64)).astype(np.uint64)
+    correlated = data_sr and not (row_rht or col_rht)
     seg = x.reshape(M, K // 16, 16)
-    smax = np.abs(seg).max(axis=-1)
+    if row_rht:
+        t = _mx_rht_segments(seg, rht_block, rht_sign)
+        smax, seg = np.abs(t).max(axis=-1), bf16_round(t)
+    else:
+        smax = np.abs(seg).max(axis=-1)
     bm = np.maximum(smax, smax.reshape(M, K // 32, 2)[:, :, ::-1].reshape(M, K // 16))
-    e = mx_e8m0_sr(bm, draw(seq, it)) if scale_sr else mx_e8m0(bm, mode)
+    q = (1 if scale_sr else 0) + (4 if (data_sr and not correlated) else 0)
+    e = mx_e8m0_sr(bm, draw(seq, it * q)) if scale_sr else mx_e8m0(bm, mode)
     with np.errstate(over="ignore", invalid="ignore"):
         scaled = (seg * (F32(6.0) * _mx_rcp(e)).astype(F32)[..., None]).astype(F32)
-    if data_sr:
+    if data_sr and not correlated:
+        bank = (tid & 31) >> 4
+        words = np.empty((M, K // 16, 4), dtype=np.uint32)
+        for g in range(4):
+            words[..., g] = draw(seq, it * q + (1 if scale_sr else 0) + 2 * (((g >> 1) - bank) & 1) + (g & 1))
+        codes = e2m1_encode_sr(scaled.reshape(M, K // 16, 4, 4), words).reshape(M, K)
+    elif data_sr:
         words = mxfp4_correlated_sr_words(base_of(chunk), r + np.zeros_like(c), c + np.zeros_like(r), True)
         codes = _sr_swapped_pairs(scaled.reshape(M, K // 16, 4, 4), words, ((r & 1) == 1) | np.zeros_like(c, dtype=bool))
         codes = codes.reshape(M, K)
@@ -669,12 +718,21 @@ def mxfp4_quantize_row_and_col_opt(x: np.ndarray, mode: int, data_sr: bool, scal
     seq = (np.uint64(subseq) + ((chunk_col * 4 + tile) * 128 + tid).astype(np.uint64)).astype(np.uint64)
     xt = np.ascontiguousarray(x.T)
     seg = xt.reshape(K, M // 16, 16)
-    smax = np.abs(seg).max(axis=-1)
+    if col_rht:
+        t = _mx_rht_segments(seg, rht_block, rht_sign)
+        smax, seg = np.abs(t).max(axis=-1), bf16_round(t)
+    else:
+        smax = np.abs(seg).max(axis=-1)
     bm = np.maximum(smax, smax.reshape(K, M // 32, 2)[:, :, ::-1].reshape(K, M // 16))
     e = mx_e8m0_sr(bm, draw(seq, (j & 1) + np.zeros_like(tid))) if scale_sr else mx_e8m0(bm, mode)
     with np.errstate(over="ignore", invalid="ignore"):
         scaled = (seg * (F32(6.0) * _mx_rcp(e)).astype(F32)[..., None]).astype(F32)
-    if data_sr:
+    if data_sr and not correlated:
+        words = np.empty((K, M // 16, 4), dtype=np.uint32)
+        for g in range(4):
+            words[..., g] = draw(seq, (2 if scale_sr else 0) + 4 * (j & 1) + g + np.zeros_like(tid))
+        codes = e2m1_encode_sr(scaled.reshape(K, M // 16, 4, 4), words).reshape(K, M)
+    elif data_sr:
         words = mxfp4_correlated_sr_words(base_of(chunk_in), i0 + np.zeros_like(j), j + np.zeros_like(i0), False)
         codes = _sr_swapped_pairs(scaled.reshape(K, M // 16, 4, 4), words, ((j & 1) == 1) | np.zeros_like(i0, dtype=bool))
         codes = codes.reshape(K, M)

@@ -227,3 +227,55 @@ def test_mxfp4_correlated_rounding_agrees_between_the_views_and_advances():
         prev = row
     assert mxq.mxfp4_forward_sr_invocation_count() == 3
     assert_status_ok()
+
+
+@pytest.mark.parametrize("block", [16, 32])
+@pytest.mark.parametrize("sign", [False, True])
+@pytest.mark.parametrize("data_sr,scale_sr", [(False, False), (True, False), (True, True)])
+def test_mxfp4_quantize_for_gemm_opt_rht(block, sign, data_sr, scale_sr):
+    mxq = mod("mxfp4_quant_v4")
+    M, K = 256, 384
+    x = o.make_activations(M, K, seed=block + 2 * sign)
+    out = mxq.mxfp4_quantize_for_gemm_opt_rht(to_dev_bf16(x), 1, data_sr, scale_sr, block, sign, 99, 3)
+    torch.cuda.synchronize()
+    fp4, sc, _ = o.mxfp4_quantize_for_gemm_opt(x, 1, data_sr, scale_sr, 99, 3, block, sign)
+    assert np.array_equal(u8(out[0]), fp4)
+    assert np.array_equal(u8(out[1]).reshape(sc.shape), sc)
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("variant,row_rht,col_rht", [("mxfp4_quantize_row_and_col_opt_rht", False, True),
+                                                     ("mxfp4_quantize_row_and_col_opt_rht_both", True, True),
+                                                     ("mxfp4_quantize_row_and_col_opt_rht_row_only", True, False)])
+@pytest.mark.parametrize("block", [16, 32])
+@pytest.mark.parametrize("data_sr,scale_sr,sign", [(False, False, True), (True, False, False), (True, True, True),
+                                                   (False, False, False)])
+def test_mxfp4_quantize_row_and_col_opt_rht_variants(variant, row_rht, col_rht, block, data_sr, scale_sr, sign):
+    mxq = mod("mxfp4_quant_v4")
+    M, K = 256, 384
+    x = o.make_activations(M, K, seed=7 + block)
+    mxq.mxfp4_set_forward_sr_invocation_count(2)
+    out = getattr(mxq, variant)(to_dev_bf16(x), 0, data_sr, scale_sr, block, sign, 31, 5)
+    torch.cuda.synchronize()
+    advanced = data_sr or scale_sr or sign
+    assert mxq.mxfp4_forward_sr_invocation_count() == (3 if advanced else 2)
+    ref = o.mxfp4_quantize_row_and_col_opt(x, 0, data_sr, scale_sr, 31, 5 + ((2 << 40) if advanced else 0), block, sign,
+                                           row_rht, col_rht)
+    _check(out, ref)
+    assert_status_ok()
+
+
+def test_mxfp4_rht_is_orthogonal_on_the_dequantised_tensor():
+    """Round to nearest behind a 32-point transform along K: the inverse transform of the dequantised codes is as
+    close to the input as the plain quantiser's output (the transform spreads outliers, it loses nothing)."""
+    mxq = mod("mxfp4_quant_v4")
+    M, K = 512, 1024
+    x = o.make_activations(M, K, seed=4)
+    out = mxq.mxfp4_quantize_for_gemm_opt_rht(to_dev_bf16(x), 1, False, False, 32, True, 1, 1)
+    torch.cuda.synchronize()
+    e = o.unswizzle_scales(u8(out[1]).reshape(M // 128, K // 128, 512), M, K // 32)
+    deq_t = o.mxfp4_dequantize(u8(out[0]), e)
+    t = o._mx_rht_segments(x.reshape(M, K // 16, 16), 32, True).reshape(M, K)
+    plain = o.mxfp4_dequantize(*o.mxfp4_quantize_1d(x, 1))
+    assert np.linalg.norm(deq_t - t) / np.linalg.norm(t) < 1.05 * np.linalg.norm(plain - x) / np.linalg.norm(x)
+    assert_status_ok()
