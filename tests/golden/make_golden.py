@@ -198,10 +198,43 @@ def make_rht_and_norm_golden(root: str):
     print("wrote", path, {k: v.shape for k, v in out.items()})
 
 
+def make_sr_state_golden(root: str):
+    """A scripted life of the reference's MXFP4SRState (low_bits_training/quantization/mxfp4_sr_state.py) on one
+    rank of a world of one and as rank 1 of a declared world of two (no process group: local rows only): the pairs
+    handed out by reserve(), and the checkpoint of the single-rank run."""
+    import importlib.util
+    import json
+    path = os.path.join(root, "low_bits_training", "quantization", "mxfp4_sr_state.py")
+    spec = importlib.util.spec_from_file_location("ref_mxfp4_sr_state", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    names = ["layers.3.ffn", "layers.0.attn", "layers.0.ffn"]
+    keys = [ref.ffn_deriv_grad_key(names[0]), ref.qkv_grad_key(names[1]), ref.wo_grad_key(names[1]),
+            ref.ffn_w2_grad_key(names[2]), ref.linear_grad_key("head")]
+    script = [0, 1, 1, 4, 2, 0, 3, 1]   # indices into keys, in call order
+    seed, base = (1 << 64) - 3, 5 << 32
+    out = {"names": names, "keys": keys, "script": script, "seed": seed, "subsequence_base": base, "runs": {}}
+    for label, rank, world in (("single", 0, 1), ("rank1_of_2", 1, 2)):
+        st = ref.MXFP4SRState(keys, device="cpu", user_seed=seed, user_subsequence_base=base, training_steps=10,
+                              gradient_accumulation_steps=2, rank=rank, world_size=world)
+        pairs = [list(st.reserve(keys[i])) for i in script]
+        run = {"reserved": pairs, "peek": [list(st.peek(k)) for k in keys], "local_rows": st._local_state_matrix().tolist(),
+               "reservations_per_slot": st.reservations_per_slot, "sorted_keys": list(st.logical_keys)}
+        if world == 1:
+            sd = st.state_dict()
+            run["state_dict"] = {k: (v.tolist() if torch.is_tensor(v) else v) for k, v in sd.items()}
+        out["runs"][label] = run
+    dst = os.path.join(HERE, "mxfp4_sr_state_reference_golden.json")
+    with open(dst, "w") as f:
+        json.dump(out, f, indent=1)
+    print("wrote", dst)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
-    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm"])
+    ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm",
+                                                     "sr_state"])
     args = ap.parse_args()
     if args.which in ("all", "rmsnorm_bwd"):
         make_rmsnorm_bwd_golden(args.reference)
@@ -213,7 +246,9 @@ def main():
         make_tk_gemm_quantize_golden(args.reference)
     if args.which in ("all", "rht_and_norm"):
         make_rht_and_norm_golden(args.reference)
-    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm"):
+    if args.which in ("all", "sr_state"):
+        make_sr_state_golden(args.reference)
+    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm", "sr_state"):
         return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

@@ -279,3 +279,28 @@ def test_mxfp4_rht_is_orthogonal_on_the_dequantised_tensor():
     plain = o.mxfp4_dequantize(*o.mxfp4_quantize_1d(x, 1))
     assert np.linalg.norm(deq_t - t) / np.linalg.norm(t) < 1.05 * np.linalg.norm(plain - x) / np.linalg.norm(x)
     assert_status_ok()
+
+
+def test_reserved_coordinates_drive_the_stochastic_quantiser():
+    """mxfp4_sr_state.reserve() -> (seed, subsequence) -> quantiser: two reservations of one producer give two
+    different roundings, each reproduced by the oracle from the pair alone (what a resumed run relies on)."""
+    mxq, sr = mod("mxfp4_quant_v4"), mod("mxfp4_sr_state")
+    key = sr.ffn_w2_grad_key("layers.0.ffn")
+    st = sr.MXFP4SRState([key, sr.qkv_grad_key("layers.0.attn")], user_seed=2024, user_subsequence_base=0,
+                         training_steps=2, gradient_accumulation_steps=1)
+    x = o.make_activations(128, 256, seed=12)
+    xd = to_dev_bf16(x)
+    seen = []
+    for _ in range(2):
+        seed, sub = st.reserve(key)
+        out = mxq.mxfp4_quantize_for_gemm_opt(xd, 1, True, False, seed, sub)
+        torch.cuda.synchronize()
+        fp4, sc, _ = o.mxfp4_quantize_for_gemm_opt(x, 1, True, False, seed, sub)
+        assert np.array_equal(u8(out[0]), fp4)
+        seen.append(fp4)
+    assert (seen[0] != seen[1]).mean() > 0.01
+    resumed = sr.MXFP4SRState(st.logical_keys, user_seed=2024, user_subsequence_base=0, training_steps=2,
+                              gradient_accumulation_steps=1)
+    resumed.load_state_dict(st.state_dict())
+    assert resumed.reserve(key) == st.reserve(key)
+    assert_status_ok()
