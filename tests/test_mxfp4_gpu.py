@@ -226,6 +226,24 @@ def test_mxfp4_correlated_rounding_agrees_between_the_views_and_advances():
             assert (row != prev).mean() > 0.01
         prev = row
     assert mxq.mxfp4_forward_sr_invocation_count() == 3
+    # the same test's second bound: over 64 calls, whether an off-peak element rounds up to code 4 is uncorrelated
+    # (|r| < 0.02) with the same event 2, 4 or 8 elements further along either axis
+    xs = np.full((n, n), 0.3, dtype=np.float32)
+    xs[peak] = 1.0
+    xd = to_dev_bf16(o.bf16_round(xs))
+    ups = []
+    for _ in range(64):
+        out = mxq.mxfp4_quantize_row_and_col_opt(xd, 0, True, False, 123, 456)
+        ups.append((o.unpack_fp4(u8(out[0])) == 4) & ~peak)
+    ups = np.stack(ups).astype(np.float32)
+    worst = 0.0
+    for dr, dc in ((0, 2), (2, 0), (0, 4), (4, 0), (0, 8), (8, 0)):
+        valid = ~peak[: n - dr, : n - dc] & ~peak[dr:, dc:]
+        a = ups[:, : n - dr, : n - dc][:, valid].ravel()
+        b = ups[:, dr:, dc:][:, valid].ravel()
+        a, b = a - a.mean(), b - b.mean()
+        worst = max(worst, abs(float((a * b).mean() / (a.std() * b.std()))))
+    assert worst < 0.02, worst
     assert_status_ok()
 
 
