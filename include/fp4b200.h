@@ -86,6 +86,17 @@ int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const
                                int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
                                void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream);
 
+/* As fp4b200_nvfp4_quantize_opt, with the row-wise codes written into a column slice of a wider matrix:
+ * row_pitch_bytes is that matrix's row pitch (0: K/2, a dense [M, K/2]); 16-byte aligned outputs only.  Serves the
+ * stochastic-rounding route of tk_group_quantize_dim1_split3_for_gemm (nvfp4_v5/tk_quantize.cu:6485-6548: one
+ * launch of the tuned kernel per gradient stream into slices of one row-wise and one column-wise code matrix). */
+int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
+                                    const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
+                                    int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
+                                    int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                                    int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
+                                    void* col_sc, void* stream);
+
 /* Tensor amax (and sg) of the per-16 Hadamard transform of x along K (along_k != 0) or along M,
  * measured on the fp32 transform output: rht16_bf16_amax_kernel (tk_quantize.cu:574-664).  gamma/inv_rms
  * non-NULL (along K only) transform bf16(x*inv_rms*gamma): rmsnorm_rht16_amax_with_orig_kernel (:1113-1172). */

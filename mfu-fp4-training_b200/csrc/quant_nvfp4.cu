@@ -1433,8 +1433,8 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
   a.nhsd_heads = nhsd_heads; a.nhsd_seq = nhsd_seq;
   a.row_pitch_bytes = (int)row_pitch_bytes;
   const bool norm = inv_rms != nullptr;
-  if (row_pitch_bytes > 0 && (opt != nullptr || weight_2d || !strip_kernel_applies(a, norm)))
-    return set_error("row codes into a wider matrix: plain quantisation into 16-byte aligned outputs only");
+  if (row_pitch_bytes > 0 && (weight_2d || !strip_kernel_applies(a, norm)))
+    return set_error("row codes into a wider matrix: 1-D blocks into 16-byte aligned outputs only");
   if (nhsd_seq > 0 && (opt != nullptr || weight_2d || norm || !strip_kernel_applies(a, false)))
     return set_error("head-major input: plain quantisation into 16-byte aligned outputs only");
   if (opt != nullptr) {
@@ -1642,12 +1642,33 @@ int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const f
   return 0;
 }
 
+int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
+                                    const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
+                                    int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
+                                    int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                                    int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
+                                    void* col_sc, void* stream);
+
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
                                void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  return fp4b200_nvfp4_quantize_opt_into(x_bf16, gamma_bf16, inv_rms, M, K, amax_row, amax_col, encode_centric, data_sr, rht_row,
+                                         rht_col, with_sign, sign_seed, sign_subseq, return_row, rng_seed, rng_offset,
+                                         rng_offset_col, scale_sr, row_fp4, 0, row_sc, col_fp4, col_sc, stream);
+}
+
+int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
+                                    const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
+                                    int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
+                                    int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                                    int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
+                                    void* col_sc, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_quantize_opt")) return rc;
+  if (row_pitch_bytes != 0 && (row_pitch_bytes < K / 2 || (row_pitch_bytes % 16) != 0 || row_pitch_bytes > INT32_MAX))
+    return set_error("nvfp4_quantize_opt: the row pitch must be 0 or a multiple of 16 bytes and at least K/2 (got %lld)",
+                     (long long)row_pitch_bytes);
   if (!amax_row) return set_error("nvfp4_quantize_opt: amax_row is required");
   if ((gamma_bf16 == nullptr) != (inv_rms == nullptr))
     return set_error("nvfp4_quantize_opt: gamma and inv_rms must both be given (fused RMSNorm) or both be null");
@@ -1666,7 +1687,8 @@ int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const
   o.return_row = return_row != 0; o.rng_seed = rng_seed; o.rng_offset = rng_offset;
   o.sign_seed = sign_seed; o.sign_subseq = sign_subseq;
   return launch_quantize(x_bf16, M, K, amax_row, amax_col, encode_centric != 0, inv_rms, gamma_bf16, row_fp4, row_sc,
-                         col_fp4, col_sc, nullptr, false, (cudaStream_t)stream, false, &o);
+                         col_fp4, col_sc, nullptr, false, (cudaStream_t)stream, false, &o, nullptr, nullptr, 0, 0,
+                         row_pitch_bytes);
 }
 
 int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,

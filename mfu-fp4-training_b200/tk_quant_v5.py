@@ -101,9 +101,12 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
     matrix [M, N/2] and the row blocks of one column-wise code matrix [N, M/2], N = n_0 + n_1 + n_2.  Returns the
     reference's 15-tuple: (row code views, row scales, sg [3], column code views, column scales, full row codes,
     row scales concatenated along the block dimension, full column codes, column scales concatenated, three empty
-    descriptor / barrier tensors' places, amax [3], ...).  Stochastic rounding of this producer is not built."""
-    if data_stochastic_rounding:
-        raise RuntimeError("tk_group_quantize_dim1_split3_for_gemm: data stochastic rounding is not built")
+    descriptor / barrier tensors' places, amax [3], ...).  Stochastic rounding on both axes takes the reference's
+    default route (:6485-6548): one launch of the tuned kernel per stream, the streams at three consecutive
+    invocation offsets; rounding one axis only (the reference's grouped kernel) is not built."""
+    sr = bool(data_stochastic_rounding)
+    if sr and _norm_sr_axes(data_sr_axes) != "both":
+        raise RuntimeError("tk_group_quantize_dim1_split3_for_gemm: stochastic rounding of one axis only is not built")
     inputs = [input0, input1, input2]
     for t in inputs:
         if not isinstance(t, torch.Tensor) or not t.is_cuda or t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1:
@@ -129,9 +132,18 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
             x = t if t.is_contiguous() else t.contiguous()   # the amax pass reads a dense buffer
             sc_row.append(torch.empty((M // 128, n // 64, 512), **u8))
             sc_col.append(torch.empty((n // 128, M // 64, 512), **u8))
-            _lib.call("fp4b200_nvfp4_quantize_for_gemm_into", x.data_ptr(), M, n, 1, 1, fp4_row_full.data_ptr() + off // 2,
-                      n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2), sc_col[g].data_ptr(),
-                      amax_sg[g].data_ptr(), _stream(input0))
+            if sr:
+                _lib.call("fp4b200_nvfp4_amax", x.data_ptr(), M * n, amax_sg[g].data_ptr(), _stream(input0))
+                _lib.call("fp4b200_nvfp4_quantize_opt_into", x.data_ptr(), None, None, M, n, amax_sg[g].data_ptr(),
+                          amax_sg[g].data_ptr(), 1, 1, 0, 0, 0, 0, 0, 1, int(rng_seed) & _U64,
+                          _next_offset(input0, rng_subsequence, True), 0, 0, fp4_row_full.data_ptr() + off // 2,
+                          n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2),
+                          sc_col[g].data_ptr(), _stream(input0))
+            else:
+                _lib.call("fp4b200_nvfp4_quantize_for_gemm_into", x.data_ptr(), M, n, 1, 1,
+                          fp4_row_full.data_ptr() + off // 2, n_total // 2, sc_row[g].data_ptr(),
+                          fp4_col_full.data_ptr() + off * (M // 2), sc_col[g].data_ptr(), amax_sg[g].data_ptr(),
+                          _stream(input0))
             off += n
         sg_per_group = amax_sg[:, 1].contiguous()
         amax_tensor = amax_sg[:, 0].contiguous()

@@ -234,7 +234,22 @@ def test_split3_group_quantiser_writes_slices_of_the_concatenated_operands():
     assert np.array_equal(u8(row_sc_cat), np.concatenate([u8(t) for t in row_sc], axis=1))
     assert np.array_equal(u8(col_sc_cat), np.concatenate([u8(t) for t in col_sc], axis=0))
     with pytest.raises(RuntimeError):
-        tkq.tk_group_quantize_dim1_split3_for_gemm(*devs, True, 1, 0, "row")       # SR of this producer: not built
+        tkq.tk_group_quantize_dim1_split3_for_gemm(*devs, True, 1, 0, "row")       # SR of one axis only: not built
+    # stochastic rounding of both axes: one launch of the tuned kernel per stream, at consecutive invocation offsets
+    tkq.tk_set_sr_invocation_count(4)
+    out = tkq.tk_group_quantize_dim1_split3_for_gemm(*devs, True, 77, 3, "both")
+    torch.cuda.synchronize()
+    assert tkq.tk_sr_invocation_count() == 7
+    off = 0
+    for g, (x, n) in enumerate(zip(xs, splits)):
+        amax = o.tensor_amax(x)
+        ref = o.nvfp4_quantize_transpose_launch(x, amax, amax, True, True, True, False, False, True, 77, 3 + ((4 + g) << 32))
+        assert np.array_equal(u8(out[5])[:, off // 2:(off + n) // 2], ref["row_fp4"])
+        assert np.array_equal(u8(out[7])[off:off + n], ref["col_fp4"])
+        assert np.array_equal(u8(out[1][g]).reshape(ref["row_sc"].shape), ref["row_sc"])
+        assert np.array_equal(u8(out[4][g]).reshape(ref["col_sc"].shape), ref["col_sc"])
+        assert out[2][g].item() == o.nvfp4_global_decode_scale(amax)
+        off += n
     with pytest.raises(RuntimeError):
         tkq.tk_group_quantize_dim1_split3_for_gemm(devs[0], devs[1], to_dev_bf16(xs[2][:128]))
     assert_status_ok()
