@@ -1,0 +1,72 @@
+"""The reference's release gate for this path (tools/check_fp4_runtime_numerics.py), run through the mirrors: 512^3,
+inputs from the CUDA generator with the gate's seed, NVFP4 route (tk_quantize_for_gemm -> nvfp4_gemm) and MXFP4 route
+(signed 32-point Hadamard quantiser -> mxfp4_gemm) against the bf16 matmul.  The thresholds are the gate's; the
+values the reference recorded on its own kernels (release/gpu_gate_receipt.json:47-56) are compared as well."""
+import math
+
+import pytest
+import torch
+
+from tests.gpu_util import assert_status_ok, mod
+
+pytestmark = pytest.mark.gpu
+
+SHAPE, SEED = 512, 20260903
+RECEIPT = {"nvfp4_v5": (0.16246938705444336, 0.9868103265762329, 1.000624179840088),
+           "mxfp4_v4_signed_h32": (0.16712865233421326, 0.9859760403633118, 0.9949585199356079)}
+# The same generator and seed give the same inputs, and the recorded metrics come back to the last float32 digit or
+# two (measured differences: 1.5e-8 in rel_l2, 6e-8 in cosine, 0 to 6e-8 in the norm ratio).  One differing code in
+# 262144 outputs' worth of operands moves rel_l2 by more than this bound.
+RECEIPT_TOL = 1e-6
+
+
+def _inputs():
+    g = torch.Generator(device="cuda")
+    g.manual_seed(SEED)
+    scale = SHAPE ** -0.25
+    lhs = (torch.randn((SHAPE, SHAPE), device="cuda", dtype=torch.float32, generator=g) * scale).to(torch.bfloat16).contiguous()
+    rhs = (torch.randn((SHAPE, SHAPE), device="cuda", dtype=torch.float32, generator=g) * scale).to(torch.bfloat16).contiguous()
+    return lhs, rhs
+
+
+def _metrics(actual, reference):
+    a, r = actual.float(), reference.float()
+    rn = torch.linalg.vector_norm(r)
+    vals = (float(torch.linalg.vector_norm(a - r) / rn),
+            float(torch.nn.functional.cosine_similarity(a.flatten(), r.flatten(), dim=0)),
+            float(torch.linalg.vector_norm(a) / rn))
+    assert all(math.isfinite(v) for v in vals)
+    return vals
+
+
+def _gate(label, vals):
+    rel_l2, cosine, norm_ratio = vals
+    assert rel_l2 < 0.25 and cosine > 0.96 and 0.80 <= norm_ratio <= 1.20, (label, vals)
+    want = RECEIPT[label]
+    print(label, "measured", vals, "recorded", want)
+    assert all(abs(v - w) < RECEIPT_TOL for v, w in zip(vals, want)), (label, vals, want)
+
+
+def test_nvfp4_route_passes_the_release_gate():
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    lhs, rhs = _inputs()
+    reference = lhs @ rhs.t()
+    lq, rq = tkq.tk_quantize_for_gemm(lhs, True), tkq.tk_quantize_for_gemm(rhs, True)
+    actual = torch.empty_like(reference)
+    gemm.nvfp4_gemm(lq[0], lq[1], lq[4], rq[0], rq[1], rq[4], actual)
+    torch.cuda.synchronize()
+    _gate("nvfp4_v5", _metrics(actual, reference))
+    assert_status_ok()
+
+
+def test_mxfp4_signed_h32_route_passes_the_release_gate():
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    lhs, rhs = _inputs()
+    reference = lhs @ rhs.t()
+    lq = mxq.mxfp4_quantize_for_gemm_opt_rht(lhs, 1, False, False, 32, True, 1234, 0)
+    rq = mxq.mxfp4_quantize_for_gemm_opt_rht(rhs, 1, False, False, 32, True, 1234, 0)
+    actual = torch.empty_like(reference)
+    gemm.mxfp4_gemm(lq[0], lq[1], rq[0], rq[1], actual)
+    torch.cuda.synchronize()
+    _gate("mxfp4_v4_signed_h32", _metrics(actual, reference))
+    assert_status_ok()
