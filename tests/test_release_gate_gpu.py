@@ -70,3 +70,48 @@ def test_mxfp4_signed_h32_route_passes_the_release_gate():
     torch.cuda.synchronize()
     _gate("mxfp4_v4_signed_h32", _metrics(actual, reference))
     assert_status_ok()
+
+
+def test_correlated_rounding_reproduces_the_recorded_spatial_correlation():
+    """The behaviour gate next to the two routes (mxfp4_v4/test_correlated_dual_sr.py; recorded maximum spatial
+    correlation 0.001073, release/gpu_gate_receipt.json:59-62): 512 x 512 of 0.3 with 1.0 where row % 32 == col % 32,
+    64 stochastic row + column launches from a fresh invocation counter with seed 123 / subsequence 456.  The two
+    views agree, the rounding changes from call to call, and the correlation statistic equals the recorded one."""
+    mxq = mod("mxfp4_quant_v4")
+    n = 512
+    ri = torch.arange(n, device="cuda")[:, None]
+    ci = torch.arange(n, device="cuda")[None, :]
+    peak = (ri % 32) == (ci % 32)
+    values = torch.full((n, n), 0.3, device="cuda", dtype=torch.bfloat16)
+    values[peak] = 1.0
+
+    def unpack(t):
+        p = t.view(torch.uint8)
+        return torch.stack((p & 0x0F, p >> 4), dim=-1).reshape(p.shape[0], -1)
+
+    mxq.mxfp4_set_forward_sr_invocation_count(0)
+    samples, prev, change = [], None, []
+    for _ in range(64):
+        out = mxq.mxfp4_quantize_row_and_col_opt(values, 0, True, False, 123, 456)
+        row, col = unpack(out[0]), unpack(out[2]).T.contiguous()
+        assert torch.equal(row, col)
+        if prev is not None:
+            change.append(float((row != prev).float().mean()))
+        prev = row
+        samples.append((row == 4) & ~peak)
+    assert sum(change) / len(change) > 0.01
+    s = torch.stack(samples)
+
+    def corr(a, b):
+        a, b = a.float(), b.float()
+        a, b = a - a.mean(), b - b.mean()
+        return float((a * b).mean() / (a.std(unbiased=False) * b.std(unbiased=False)))
+
+    worst = 0.0
+    for dr, dc in ((0, 2), (2, 0), (0, 4), (4, 0), (0, 8), (8, 0)):
+        valid = ~peak[: n - dr, : n - dc] & ~peak[dr:, dc:]
+        worst = max(worst, abs(corr(s[:, : n - dr, : n - dc][:, valid], s[:, dr:, dc:][:, valid])))
+    print("max spatial correlation", worst, "recorded 0.001073")
+    assert worst < 0.02
+    assert abs(worst - 0.001073) < 1e-6
+    assert_status_ok()
