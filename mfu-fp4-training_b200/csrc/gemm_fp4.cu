@@ -523,7 +523,9 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   }
 }
 
-template <bool MX>
+// SILU: the instantiation for launches with a SiLU range (every bf16 tile takes the epilogue form that knows it);
+// the other instantiation carries the plain and the rotary forms only, as compact as before the option existed.
+template <bool MX, bool SILU = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                 const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
@@ -716,7 +718,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         if (lane == 0) mbar_arrive(&sm.acc_empty);
       };
       if (epilogue_is_bf16_plain(g)) {
-        if (g.silu_col_end > 0)
+        if constexpr (SILU)
           epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
         else if (g.rope_cs != nullptr)
           epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
@@ -838,6 +840,9 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     if (mx) {
       FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
       FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<true>, tmap_a, tmap_b, omaps, g));
+    } else if (g.silu_col_end > 0) {
+      FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
+      FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<false, true>, tmap_a, tmap_b, omaps, g));
     } else {
       FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
       FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<false>, tmap_a, tmap_b, omaps, g));
@@ -851,6 +856,9 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   if (mx) {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     fp4_gemm_kernel<true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
+  } else if (g.silu_col_end > 0) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    fp4_gemm_kernel<false, true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
   } else {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     fp4_gemm_kernel<false><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);

@@ -71,7 +71,9 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
   }
 }
 
-template <bool MX>
+// SILU: the instantiation for launches with a SiLU range (every bf16 tile takes the epilogue form that knows it);
+// the other instantiation carries the plain and the rotary forms only, as compact as before the option existed.
+template <bool MX, bool SILU = false>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                      const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
@@ -270,7 +272,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       };
       if (epilogue_is_bf16_plain(g)) {
-        if (g.silu_col_end > 0)
+        if constexpr (SILU)
           epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
                                    lane, release);
         else if (g.rope_cs != nullptr)
