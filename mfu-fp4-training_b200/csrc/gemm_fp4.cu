@@ -297,8 +297,10 @@ __device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMa
     }
 }
 
+constexpr int kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2, kEpiGeneral = 3;
+
 // bf16 outputs without fp32 accumulation take this form of the epilogue.
-__device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
+__host__ __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
   return !g.out_fp32 && g.accum_f32 == nullptr;
 }
 
@@ -523,9 +525,10 @@ __device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const Gemm
   }
 }
 
-// SILU: the instantiation for launches with a SiLU range (every bf16 tile takes the epilogue form that knows it);
-// the other instantiation carries the plain and the rotary forms only, as compact as before the option existed.
-template <bool MX, bool SILU = false>
+// EPI: one epilogue form per instantiation, chosen by the host (kEpiPlain: bf16 outputs, optional residual;
+// kEpiRope: with the rotary embedding; kEpiSilu: with a SiLU range, rotary or not; kEpiGeneral: fp32 outputs or
+// accumulation).  Several forms inside one kernel cost every one of them a few percent.
+template <bool MX, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                 const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
@@ -717,16 +720,15 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.acc_empty);
       };
-      if (epilogue_is_bf16_plain(g)) {
-        if constexpr (SILU)
-          epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
-        else if (g.rope_cs != nullptr)
-          epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
-        else
-          epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
-      } else {
+      if constexpr (EPI == kEpiGeneral) {
         epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
         release();
+      } else if constexpr (EPI == kEpiSilu) {
+        epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+      } else if constexpr (EPI == kEpiRope) {
+        epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
+      } else {
+        epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
       }
       acc_phase ^= 1;
     }
@@ -822,6 +824,8 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
   g.status = device_status_ptr();
   if (g.status == nullptr) return -1;
+  const int epi = (g.out_fp32 || g.accum_f32 != nullptr) ? kEpiGeneral
+                  : g.silu_col_end > 0 ? kEpiSilu : g.rope_cs != nullptr ? kEpiRope : kEpiPlain;
   if (pair) {
     // two-CTA clusters: one 256 x 256 tile per pair of SMs
     const int psmem = (int)sizeof(GemmPairSmem) + 1024;
@@ -837,32 +841,36 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
     cfg.attrs = attr;
     cfg.numAttrs = 1;
+#define FP4_LAUNCH_PAIR(MXF, EPI)                                                                                          \
+  do {                                                                                                                   \
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<MXF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem)); \
+    FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<MXF, EPI>, tmap_a, tmap_b, omaps, g));                   \
+  } while (0)
     if (mx) {
-      FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
-      FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<true>, tmap_a, tmap_b, omaps, g));
-    } else if (g.silu_col_end > 0) {
-      FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
-      FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<false, true>, tmap_a, tmap_b, omaps, g));
-    } else {
-      FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem));
-      FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<false>, tmap_a, tmap_b, omaps, g));
-    }
+      if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(true, kEpiGeneral); else FP4_LAUNCH_PAIR(true, kEpiPlain);
+    } else if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(false, kEpiGeneral);
+    else if (epi == kEpiSilu) FP4_LAUNCH_PAIR(false, kEpiSilu);
+    else if (epi == kEpiRope) FP4_LAUNCH_PAIR(false, kEpiRope);
+    else FP4_LAUNCH_PAIR(false, kEpiPlain);
+#undef FP4_LAUNCH_PAIR
     return 0;
   }
   const int smem = (int)sizeof(GemmSmem) + 1024;
   const int n_tiles = (int)((M / kGemmBM) * (N / kGemmBN));
   const int grid = std::min(n_tiles, device_sm_count());
   if (grid == 0) return 0;
+#define FP4_LAUNCH_ONE(MXF, EPI)                                                                                      \
+  do {                                                                                                               \
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<MXF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
+    fp4_gemm_kernel<MXF, EPI><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);                             \
+  } while (0)
   if (mx) {
-    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    fp4_gemm_kernel<true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
-  } else if (g.silu_col_end > 0) {
-    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    fp4_gemm_kernel<false, true><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
-  } else {
-    FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    fp4_gemm_kernel<false><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);
-  }
+    if (epi == kEpiGeneral) FP4_LAUNCH_ONE(true, kEpiGeneral); else FP4_LAUNCH_ONE(true, kEpiPlain);
+  } else if (epi == kEpiGeneral) FP4_LAUNCH_ONE(false, kEpiGeneral);
+  else if (epi == kEpiSilu) FP4_LAUNCH_ONE(false, kEpiSilu);
+  else if (epi == kEpiRope) FP4_LAUNCH_ONE(false, kEpiRope);
+  else FP4_LAUNCH_ONE(false, kEpiPlain);
+#undef FP4_LAUNCH_ONE
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -71,9 +71,10 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
   }
 }
 
-// SILU: the instantiation for launches with a SiLU range (every bf16 tile takes the epilogue form that knows it);
-// the other instantiation carries the plain and the rotary forms only, as compact as before the option existed.
-template <bool MX, bool SILU = false>
+// EPI: one epilogue form per instantiation, chosen by the host (kEpiPlain: bf16 outputs, optional residual;
+// kEpiRope: with the rotary embedding; kEpiSilu: with a SiLU range, rotary or not; kEpiGeneral: fp32 outputs or
+// accumulation).  Several forms inside one kernel cost every one of them a few percent.
+template <bool MX, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                      const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
@@ -271,19 +272,18 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       };
-      if (epilogue_is_bf16_plain(g)) {
-        if constexpr (SILU)
-          epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
-                                   lane, release);
-        else if (g.rope_cs != nullptr)
-          epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
-                                   lane, release);
-        else
-          epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
-                                    lane, release);
-      } else {
+      if constexpr (EPI == kEpiGeneral) {
         epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad, lane);
         release();
+      } else if constexpr (EPI == kEpiSilu) {
+        epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
+                                   lane, release);
+      } else if constexpr (EPI == kEpiRope) {
+        epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
+                                   lane, release);
+      } else {
+        epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
+                                   lane, release);
       }
       acc_phase ^= 1;
     }
