@@ -607,7 +607,8 @@ def tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1_raw, return_transpose=T
     """tk_quantize.cu:10063-10255 — 15-tuple: dh1 (row_fp4,row_sc,col_fp4,col_sc,row_sg,col_sg), dh3 likewise,
     amaxes[4], dh1 bf16, dh3 bf16.  As in the reference the row operand is Hadamard-transformed
     (``rht_axes="row"``), there is no sign mask, and each of dh1/dh3 takes one Philox offset shared by its
-    row and column launches; ``rht_axes="none"`` is accepted as an extension (no transform)."""
+    row and column launches (also when only the scale bytes round stochastically); ``rht_axes="none"`` is
+    accepted as an extension (no transform)."""
     if not return_transpose:
         raise RuntimeError("split2 opt producer currently requires return_transpose=True")
     row_rht, col_rht = _norm_axes(rht_axes)
@@ -615,12 +616,11 @@ def tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1_raw, return_transpose=T
         raise RuntimeError(f"split2 opt producer currently supports the row-RHT regular-TK contract only; got {rht_axes}")
     if with_random_sign_mask:
         raise RuntimeError("split2 opt producer does not support random RHT sign masks yet")
-    if scale_stochastic_rounding:
-        raise RuntimeError("split2 opt producer: scale stochastic rounding is not built")
+    scale_sr = bool(scale_stochastic_rounding)
     axes = _norm_sr_axes(data_sr_axes)
     row_sr = bool(data_stochastic_rounding) and axes in ("row", "both")
     col_sr = bool(data_stochastic_rounding) and axes in ("col", "both")
-    use_sr = row_sr or col_sr
+    use_sr = row_sr or col_sr or scale_sr
     with torch.cuda.device(dh.device):
         M, H, dh1, dh3, a1, a3 = _silu_deriv(dh, h3, h1_raw)
         outs, sgs, amax_list = [], [], []
@@ -629,11 +629,11 @@ def tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1_raw, return_transpose=T
             off = _next_offset(t, rng_subsequence, use_sr)
             if row_sr == col_sr:
                 q = _launch_opt(t, row_amax, orig, True, row_sr, encode_centric, row_rht, False, True, rng_seed, off,
-                                False, 0, 0)
+                                False, 0, 0, scale_sr=scale_sr)
             else:
                 # one axis stochastic: the reference's row launch and column launch (same offset) as one
                 q = _launch_opt(t, row_amax, orig, True, True, encode_centric, row_rht, False, True, rng_seed, off,
-                                False, 0, 0, sr_mode=2 if row_sr else 3, offset_col=off)
+                                False, 0, 0, sr_mode=2 if row_sr else 3, offset_col=off, scale_sr=scale_sr)
             outs.append((q[0].view(_FP4), q[1].view(_E4M3), q[2].view(_FP4), q[3].view(_E4M3)))
             sgs.append((row_amax.narrow(0, 1, 1), orig.narrow(0, 1, 1)))
             amax_list += [row_amax[0], orig[0]]

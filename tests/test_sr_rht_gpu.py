@@ -103,8 +103,9 @@ def test_fused_norm_quantize_opt_row_rht_sr(data_sr, scale_sr):
     assert_status_ok()
 
 
-@pytest.mark.parametrize("axes", ["both", "row"])
-def test_silu_deriv_opt_row_rht_sr(axes):
+@pytest.mark.parametrize("axes,data_sr,scale_sr", [("both", True, False), ("row", True, False), ("both", True, True),
+                                                   ("row", True, True), ("both", False, True)])
+def test_silu_deriv_opt_row_rht_sr(axes, data_sr, scale_sr):
     tkq = mod("tk_quant_v5")
     M, H = 256, 512
     rng = np.random.default_rng(8)
@@ -113,18 +114,21 @@ def test_silu_deriv_opt_row_rht_sr(axes):
     dh = o.bf16_round(rng.standard_normal((M, H)).astype(np.float32) * 1e-3)
     tkq.tk_set_sr_invocation_count(5)
     out = tkq.tk_silu_deriv_quantize_split_for_gemm_opt(to_dev_bf16(dh), to_dev_bf16(h3), to_dev_bf16(h1), True, False,
-                                                        True, False, "row", False, 21, 4, axes)
+                                                        data_sr, scale_sr, "row", False, 21, 4, axes)
     torch.cuda.synchronize()
     assert len(out) == 15 and tkq.tk_sr_invocation_count() == 7
     for base, idx, n in ((0, 13, 5), (6, 14, 6)):
         t = out[idx].float().cpu().numpy()
         row_amax, orig = o.rht16_amax(t, True), o.tensor_amax(t)
         off = 4 + n * (1 << 32)
-        if axes == "both":
-            ref = o.nvfp4_quantize_transpose_launch(t, row_amax, orig, True, True, False, True, False, True, 21, off)
+        if axes == "both" or not data_sr:
+            ref = o.nvfp4_quantize_transpose_launch(t, row_amax, orig, True, data_sr, False, True, False, True, 21, off,
+                                                    scale_sr=scale_sr)
         else:
-            ref = o.nvfp4_quantize_transpose_launch(t, row_amax, orig, False, True, False, True, False, True, 21, off)
-            ref.update(o.nvfp4_quantize_transpose_launch(t, row_amax, orig, True, False, False, True, False, False, 21, off))
+            ref = o.nvfp4_quantize_transpose_launch(t, row_amax, orig, False, True, False, True, False, True, 21, off,
+                                                    scale_sr=scale_sr)
+            ref.update(o.nvfp4_quantize_transpose_launch(t, row_amax, orig, True, False, False, True, False, False, 21, off,
+                                                         scale_sr=scale_sr))
         _cmp(out[base:base + 4], ref)
         assert out[base + 4].item() == o.nvfp4_global_decode_scale(row_amax)
         assert out[base + 5].item() == o.nvfp4_global_decode_scale(orig)
