@@ -73,3 +73,12 @@ def test_entry_points_validate_before_touching_the_device(pkg):
     assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 4, 16384, None) == -1 and "8192" in msg()
     assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 1, 256, None) == -1 and "overlaps" in msg()
     assert lib.fp4b200_rmsnorm_bwd_residual(p, p, p, p, p, p, p, p, 4, 2048, None) == -1 and "4096" in msg()
+    # stochastic MXFP4 quantisers: transform block size, axes, outputs
+    assert lib.fp4b200_mxfp4_quantize_row_sr(p, 128, 128, 1, 1, 0, 8, 0, 1, 2, p, p, None) == -1 and "16 or 32" in msg()
+    assert lib.fp4b200_mxfp4_quantize_row_sr(p, 128, 100, 1, 1, 0, 0, 0, 1, 2, p, p, None) == -1
+    assert lib.fp4b200_mxfp4_quantize_row_and_col_sr(p, 128, 128, 1, 1, 0, 16, 1, 0, 0, 1, 2, p, p, p, p, None) == -1
+    assert "at least one axis" in msg()
+    assert lib.fp4b200_mxfp4_quantize_row_and_col_sr(p, 128, 128, 1, 1, 0, 0, 0, 0, 0, 1, 2, p, p, p, None, None) == -1
+    # pitched opt quantiser: the pitch of the wider row-code matrix
+    assert lib.fp4b200_nvfp4_quantize_opt_into(p, None, None, 128, 256, p, p, 1, 1, 0, 0, 0, 0, 0, 1, 1, 0, 0, 0, p, 100, p, p, p,
+                                               None) == -1 and "row pitch" in msg()
