@@ -641,7 +641,7 @@ def main():
     quant_bytes = M_ROWS * K_COLS * 3.125
     stats_bytes = M_ROWS * K_COLS * 2.0
     achieved = quant_bytes / (t_quant * 1e-3) / 1e9
-    roofline = {"bound": "hbm", "kernel": "nvfp4_quantize_strip_kernel<encode_centric, norm> (pass 2)",
+    roofline = {"bound": "hbm", "kernel": "nvfp4_quantize_strip_kernel<encode_centric, norm, paired> (pass 2)",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                 "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": TRAFFIC_PER_LAUNCH,
                 "algorithmic_bytes_per_launch": quant_bytes, "avg_launch_ms": t_quant,
@@ -742,7 +742,7 @@ def main():
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one pass-2 launch at the bench size, from the ncu
 # capture summarised under profiles/.
-TRAFFIC_PER_LAUNCH = 134743808 + 38977024  # profiles/fused_rmsnorm_nvfp4_quant_16384x4096.md (in-kernel DRAM bytes)
+TRAFFIC_PER_LAUNCH = 134334208 + 38618624  # profiles/fused_rmsnorm_nvfp4_quant_16384x4096.md (in-kernel DRAM bytes)
 
 if __name__ == "__main__":
     main()
