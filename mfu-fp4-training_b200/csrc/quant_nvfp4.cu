@@ -210,6 +210,10 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     gamma_hi[q] = make_float4(bf16lo_to_f32(g.z), bf16hi_to_f32(g.z), bf16lo_to_f32(g.w), bf16hi_to_f32(g.w));
   }
   __syncthreads();
+  // Launched behind a kernel that lets its dependents start early (the strip quantiser of the previous call), this
+  // kernel has by now staged gamma and filled its ring from x, neither of which that kernel writes; inv_rms and the
+  // partial maxima may still be read by it, so nothing is written (and a caller's inv_rms not read) before it ends.
+  pdl_wait();
 
   float mx = 0.0f;
   const int nvec_row = K >> 3;
@@ -933,6 +937,9 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     fence_mbar_init();
   }
   __syncthreads();
+  // A statistics kernel launched behind this one (the next call of the fused producer) may set up and fill its ring
+  // as SMs free up; it writes nothing before this kernel has ended.
+  pdl_launch_dependents();
   if (lane == 0) {
     for (int s = 0; s < depth && s < my_count; ++s) issue_load(s, s);
   }
@@ -1479,6 +1486,15 @@ static int stats_slots_for(int64_t K) {
   return (int)std::max<int64_t>(0, std::min<int64_t>(budget / (K * 2), 64));
 }
 
+// FP4B200_PDL_CHAIN=0: the statistics kernel is launched the ordinary way (A/B runs).
+static bool stats_pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FP4B200_PDL_CHAIN");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
 template <int NV, bool CI>
 static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
                           int64_t M, int64_t K, int slots, int* status, cudaStream_t st, int* grid_out) {
@@ -1487,8 +1503,8 @@ static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, floa
   const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 + (size_t)slots * 12;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
-  kern<<<grid, warps * 32, smem, st>>>(xb, gb, inv_rms, partials, eps, (int)M, (int)K, slots, status);
-  FP4_CUDA_CHECK(cudaGetLastError());
+  PdlLaunch l(dim3((unsigned)grid), dim3((unsigned)warps * 32), smem, st, stats_pdl_enabled());
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, xb, gb, inv_rms, partials, eps, (int)M, (int)K, slots, status));
   *grid_out = grid;
   return 0;
 }
