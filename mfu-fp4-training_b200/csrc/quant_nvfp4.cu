@@ -46,6 +46,9 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
   if (threadIdx.x < 32) {
     v = threadIdx.x < 8 ? warp_part[threadIdx.x] : 0.0f;
     v = warp_max(v);
+    // Launched behind a quantiser that lets its dependents start early, this kernel has only read x so far; that
+    // quantiser may still be reading the partial maxima of ITS input from the same scratch, so the write waits.
+    pdl_wait();
     if (threadIdx.x == 0) partials[blockIdx.x] = v;
   }
 }
@@ -1303,6 +1306,15 @@ struct PdlLaunch {
   PdlLaunch(const PdlLaunch&) = delete;
 };
 
+// FP4B200_PDL_CHAIN=0: the statistics and amax kernels are launched the ordinary way (A/B runs).
+static bool stats_pdl_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FP4B200_PDL_CHAIN");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
 // Reduction of the per-CTA maxima into amax_sg[0..1], launched behind the kernel that produced them.
 static int launch_reduce_partials(const float* partials, int n, float* amax_sg, cudaStream_t st) {
   PdlLaunch l(dim3(1), dim3(256), 0, st, true);
@@ -1317,8 +1329,8 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st,
   const size_t n_vec = (size_t)n_elems / 8;
   int grid = (int)std::min<size_t>((n_vec + 255) / 256, std::min<size_t>((size_t)device_sm_count() * 8, kScratchFloats));
   grid = std::max(grid, 1);   // an empty input still leaves one partial (0)
-  amax_bf16_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const uint4*>(x), n_vec, scratch);
-  FP4_CUDA_CHECK(cudaGetLastError());
+  PdlLaunch l(dim3((unsigned)grid), dim3(256), 0, st, stats_pdl_enabled());
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, amax_bf16_kernel, reinterpret_cast<const uint4*>(x), n_vec, scratch));
   if (partials_out != nullptr) {
     partials_out->ptr = scratch;
     partials_out->count = grid;
@@ -1484,15 +1496,6 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
 static int stats_slots_for(int64_t K) {
   const int64_t budget = 227 * 1024 - K * 4 - 2048;   // gamma tables, barriers, static shared memory
   return (int)std::max<int64_t>(0, std::min<int64_t>(budget / (K * 2), 64));
-}
-
-// FP4B200_PDL_CHAIN=0: the statistics kernel is launched the ordinary way (A/B runs).
-static bool stats_pdl_enabled() {
-  static const bool on = [] {
-    const char* e = getenv("FP4B200_PDL_CHAIN");
-    return !(e != nullptr && e[0] == '0');
-  }();
-  return on;
 }
 
 template <int NV, bool CI>
