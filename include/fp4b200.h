@@ -186,10 +186,27 @@ int fp4b200_silu_deriv_bf16(const void* dh, const void* h3, const void* h1, int6
                             void* dh3_out, float* amax_sg1, float* amax_sg3, void* stream);
 
 /* ---- block-scaled FP4 GEMMs ------------------------------------------------------------ */
-/* Shapes: M % 128 == 0, N % 256 == 0, K % 256 == 0.  A [M,K/2] and B [N,K/2] packed codes,
- * scales in the 512-byte tile layout above, D row-major [M,N] written in place.
+/* Shapes: M % 128 == 0, N % 128 == 0, K % 256 == 0 (NVFP4) or K % 128 == 0 (MXFP4).  A [M,K/2] and
+ * B [N,K/2] packed codes, scales in the 512-byte tile layout above, D row-major [M,N] written in place.
  * out_fp32 = 0: D is bf16, = 1: D is fp32 (the accumulator times the tensor scales, unrounded).
- * residual_bf16 (optional, bf16 [M,N]): D = bf16(bf16(acc*scale) + R). */
+ * residual_bf16 (optional, bf16 [M,N]): D = bf16(bf16(acc*scale) + R).
+ * The kernels are launched as programmatic dependents of the previous kernel in the stream (their set-up
+ * overlaps its tail; they touch no global memory before its writes are visible). */
+
+/* The first-pass kernels of the quantisers (tensor maximum, RMSNorm statistics) are launched as programmatic
+ * dependents too.  By default they read nothing before the previous kernel on the stream has ended, because their
+ * input is usually what that kernel produced.  enabled = 1 is the caller's promise that no input of a call (x, gamma)
+ * is written by the kernel launched immediately before it on the same stream — true of back-to-back calls on
+ * independent inputs — and lets those kernels fill their shared-memory rings while the previous kernel drains
+ * (-5 us per fused call at [16384 x 4096]).  Process-wide; returns the previous setting; FP4B200_PDL_EARLY_READS=1
+ * sets it at load.  No counterpart in the reference. */
+int fp4b200_set_pdl_early_reads(int enabled);
+
+/* Switches that launch attribute for the GEMM calls of the calling thread (1 = on, the default; 0 = ordinary
+ * launches) and returns the previous setting: what the reference's *_nopdl entry points select
+ * (nvfp4_b200_gemm.cu:1702-1735; kernel nvfp4_gemm.cuh:577,596,1002).  FP4B200_GEMM_PDL=0 in the environment
+ * switches it off for the whole process. */
+int fp4b200_set_gemm_pdl(int enabled);
 
 /* D = bf16((A.B^T) * A_sg * B_sg): nvfp4_gemm / nvfp4_gemm_config / nvfp4_gemm_nopdl /
  * nvfp4_gemm_residual (fp4_runtime/ThunderKittens/kernels/gemm/nvfp4_b200/nvfp4_b200_gemm.cu:648-761,

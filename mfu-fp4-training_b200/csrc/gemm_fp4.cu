@@ -11,12 +11,15 @@
 //  fp4_runtime/ThunderKittens/kernels/gemm/mxfp4_gb200/mxfp4_gemm.cuh).  Unlike the reference
 // there is no cluster-multicast TMA load: every CTA fetches its own operand tiles.
 //
-// One persistent CTA per SM works through 128 x 256 output tiles.  Warp roles:
+// One persistent CTA per SM works through 128 x 256 output tiles (this file), or a pair of CTAs through
+// 256 x 256 tiles (gemm_fp4_pair.cuh, the default when M is a multiple of 256).  Warp roles:
 //   warp 0      TMA producer: per 256-deep K stage one A box (128 rows x 128 B), one B box
 //               (256 rows x 128 B), both 128-byte swizzled, and three bulk copies of scale tiles
 //   warp 1      owns tensor memory; one lane issues tcgen05.mma
 //   warps 2..5  epilogue: tcgen05.ld the accumulator, scale, (residual), convert, store
 //   warps 6..9  scale movers: shared memory -> registers -> tcgen05.st into this quadrant's scale columns
+// Both kernels run setup (barriers, tensor-memory allocation, descriptor prefetch) ahead of griddepcontrol.wait,
+// so that, launched as a programmatic dependent, it overlaps the previous kernel's tail.
 // Every wait on an mbarrier is bounded in time; a wait that runs out records a status code,
 // and the CTA drains to the common exit where tensor memory is released.
 #include "fp4_common.cuh"
@@ -53,7 +56,6 @@ struct GemmSmem {
   alignas(8) uint64_t acc_full;
   alignas(8) uint64_t acc_empty;
   uint32_t tmem_base;
-  int abort_flag;
 };
 
 // The K dimension may be the concatenation of up to kMaxKSeg segments, each with its own B tensor,
@@ -65,11 +67,12 @@ struct GemmBMaps {
 
 struct GemmArgs {
   int n_seg;
-  int seg_stage_end[kMaxKSeg];      // cumulative number of 256-deep K stages at the end of each segment
+  int seg_stage_end[kMaxKSeg];      // cumulative number of K stages (256 deep; a tail may be 128) at the end of each segment
   int seg_a_col_bytes[kMaxKSeg];    // byte offset of the segment inside a row of A's codes
   const uint8_t* seg_a_sc[kMaxKSeg];   // [M/128, Kseg/(4*block), 512]
   const uint8_t* seg_b_sc[kMaxKSeg];   // [N/128, Kseg/(4*block), 512]
   int seg_sf_tiles_k[kMaxKSeg];     // scale tiles along K per row tile, per segment
+  int seg_tail_half[kMaxKSeg];      // 1: the segment's last stage holds 128 elements only (MXFP4, K an odd multiple of 128)
   const float* a_sg;        // device scalar (NVFP4) or null
   const float* b_sg;        // device scalar, or per-256-column-tile array when b_sg_per_tile != 0
   int b_sg_per_tile;
@@ -194,340 +197,198 @@ struct GemmOutMaps {
   CUtensorMap m[3];
 };
 
-// Epilogue of one 128 x 256 accumulator tile by one warp (its 32-lane quadrant): tensor memory ->
-// registers -> scale / accumulate / residual -> swizzled staging -> TMA store.  row0 = first global
-// row of the tile, tn = column-tile index, epi = this warp's two 4 KiB staging buffers.
-__device__ __forceinline__ void epilogue_tile(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t tmem, uint8_t* epi,
-                                              int row0, int tn, float a_sg, int quad, int lane) {
-    float gs = a_sg;
-    if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? tn : 0));
-    const int row = row0 + quad * 32 + lane;
-    int col0 = tn * kGemmBN;
-    // which output receives this column tile
-    int oi = 0, col_start = 0;
-    while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
-    const int ocol = col0 - col_start;
-    // 32 columns per tensor-memory load; a slab of 128 bytes per row (64 bf16 or 32 fp32 columns) is
-    // staged in the 128-byte-swizzled layout and written with one TMA store per slab
-    const int chunks_per_slab = g.out_fp32 ? 1 : 2;
-#pragma unroll 1
-    for (int c = 0; c < kGemmBN; c += 32) {
-      const int chunk = c >> 5;
-      const int slab = chunk / chunks_per_slab;
-      uint8_t* buf = epi + (slab & 1) * 4096;
-      uint32_t r[32];
-      tmem_ld32(tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)c, r);
-      if ((chunk % chunks_per_slab) == 0) {
-        // the store issued from this buffer two slabs ago must have finished reading it
-        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-        __syncwarp();
-      }
-      tmem_ld_wait();
-      uint8_t* rowp = buf + lane * 128;
-      if (g.accum_f32 != nullptr) {
-        // running fp32 sum over a batch of GEMMs: partial + acc*scale (multiply, then add)
-        const float4* ps = reinterpret_cast<const float4*>(g.accum_f32 + (size_t)row * g.N + col0 + c);
+// One lane's share of a stage's scale tiles, shared memory -> registers, in the column order of the stage's scale
+// slot in tensor memory: 16 columns of A scales (4 per K step of 64), then 32 of B scales (4 + 4 per K step, the
+// two 128-row groups of the tile).  Lane l holds the 16 bytes of tile row l, i.e. the scales of rows l, 32+l,
+// 64+l, 96+l.  MXFP4 stages hold two tiles per group; the other columns are zeroed.
+template <int kTiles>
+__device__ __forceinline__ void load_stage_scales(const uint8_t* sfa, const uint8_t* sfb, int lane, uint32_t (&ra)[16],
+                                                  uint32_t (&rb)[32]) {
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 pv = __ldg(ps + q);
-          r[4 * q] = __float_as_uint(__fadd_rn(pv.x, __fmul_rn(__uint_as_float(r[4 * q]), gs)));
-          r[4 * q + 1] = __float_as_uint(__fadd_rn(pv.y, __fmul_rn(__uint_as_float(r[4 * q + 1]), gs)));
-          r[4 * q + 2] = __float_as_uint(__fadd_rn(pv.z, __fmul_rn(__uint_as_float(r[4 * q + 2]), gs)));
-          r[4 * q + 3] = __float_as_uint(__fadd_rn(pv.w, __fmul_rn(__uint_as_float(r[4 * q + 3]), gs)));
-        }
-      }
-      const float gs_out = g.accum_f32 != nullptr ? 1.0f : gs;
-      if (g.out_fp32) {
+  for (int j = 0; j < kTiles; ++j) {
+    const uint4 va = *reinterpret_cast<const uint4*>(sfa + j * 512 + lane * 16);
+    ra[4 * j] = va.x; ra[4 * j + 1] = va.y; ra[4 * j + 2] = va.z; ra[4 * j + 3] = va.w;
+    const uint4 v0 = *reinterpret_cast<const uint4*>(sfb + j * 512 + lane * 16);
+    const uint4 v1 = *reinterpret_cast<const uint4*>(sfb + kTiles * 512 + j * 512 + lane * 16);
+    rb[8 * j] = v0.x; rb[8 * j + 1] = v0.y; rb[8 * j + 2] = v0.z; rb[8 * j + 3] = v0.w;
+    rb[8 * j + 4] = v1.x; rb[8 * j + 5] = v1.y; rb[8 * j + 6] = v1.z; rb[8 * j + 7] = v1.w;
+  }
 #pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const float4 v = make_float4(__uint_as_float(r[4 * q]) * gs_out, __uint_as_float(r[4 * q + 1]) * gs_out,
-                                       __uint_as_float(r[4 * q + 2]) * gs_out, __uint_as_float(r[4 * q + 3]) * gs_out);
-          *reinterpret_cast<float4*>(rowp + ((q ^ (lane & 7)) << 4)) = v;
-        }
-      } else {
-        uint32_t o[16];
-        if (g.rope_cs != nullptr && col0 + c < g.rope_col_end) {
-          // even' = fma(x, cos, -(y*sin)), odd' = fma(y, cos, x*sin): the contraction nvcc applies to the
-          // reference's x*cos - y*sin and y*cos + x*sin
-          const float2* cs_row = g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim;
+  for (int j = kTiles; j < 4; ++j) {
+    ra[4 * j] = ra[4 * j + 1] = ra[4 * j + 2] = ra[4 * j + 3] = 0;
 #pragma unroll
-          for (int q = 0; q < 16; ++q) {
-            float x = __fmul_rn(__uint_as_float(r[2 * q]), gs_out), y = __fmul_rn(__uint_as_float(r[2 * q + 1]), gs_out);
-            if (g.rope_round_bf16) {
-              x = __bfloat162float(__float2bfloat16_rn(x));
-              y = __bfloat162float(__float2bfloat16_rn(y));
-            }
-            const float2 cs = __ldg(cs_row + (((col0 + c + 2 * q) & g.rope_head_mask) >> 1));
-            o[q] = f32x2_to_bf16x2(__fmaf_rn(x, cs.x, -__fmul_rn(y, cs.y)), __fmaf_rn(y, cs.x, __fmul_rn(x, cs.y)));
-          }
-        } else {
-#pragma unroll
-          for (int q = 0; q < 16; ++q)
-            o[q] = f32x2_to_bf16x2(__uint_as_float(r[2 * q]) * gs_out, __uint_as_float(r[2 * q + 1]) * gs_out);
-        }
-        if (g.residual != nullptr) {
-          const uint4* rs = reinterpret_cast<const uint4*>(g.residual + (size_t)row * g.residual_ld + col0 + c);
-#pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            const uint4 rv = __ldg(rs + q);
-            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              const uint32_t d = o[4 * q + e];
-              o[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]),
-                                             bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
-            }
-          }
-        }
-        const int piece0 = (chunk & 1) * 4;
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          *reinterpret_cast<uint4*>(rowp + (((piece0 + q) ^ (lane & 7)) << 4)) =
-              make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
-      }
-      if ((chunk % chunks_per_slab) == chunks_per_slab - 1) {
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          const int slab_cols = g.out_fp32 ? 32 : 64;
-          tma_store_2d(&tmap_d.m[oi], buf, ocol + slab * slab_cols, row0 + quad * 32);
-          asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-        }
-      }
-    }
+    for (int e = 0; e < 8; ++e) rb[8 * j + e] = 0;
+  }
 }
+
 
 constexpr int kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2, kEpiGeneral = 3;
 
-// bf16 outputs without fp32 accumulation take this form of the epilogue.
-__host__ __device__ __forceinline__ bool epilogue_is_bf16_plain(const GemmArgs& g) {
-  return !g.out_fp32 && g.accum_f32 == nullptr;
-}
-
-// x / (1 + exp(-x)) with the hardware exponential and approximate division: no slow-path branch, so the 256
-// unrolled uses in the drain loops stay a few instructions each.
+// x / (1 + exp(-x)) with the hardware exponential and approximate division: no slow-path branch, so the
+// unrolled uses in the epilogue stay a few instructions each.
 __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f + __expf(-x)); }
 
-// Epilogue for bf16 outputs in two phases.  Phase 1 drains the warp's quadrant of the accumulator
-// (256 columns): the first 128 columns go straight into the warp's two staging buffers, the other
-// 128 into 64 registers of packed bf16 — the load of the next 32 columns is in flight while the
-// current 32 are scaled and rounded — and then release() is called, after which the MMA warp may
-// overwrite the accumulator.  Phase 2 (TMA stores of the staged half, then staging and stores of the
-// register half) runs while the next tile's MMAs are already issuing, which is what the single
-// accumulator (256 + scale columns fill tensor memory) would otherwise forbid.
-template <bool ROPE, bool SILU, typename Release>
-__device__ __forceinline__ void epilogue_tile_bf16(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t tmem,
-                                                   uint8_t* epi, int row0, int tn, float a_sg, int quad, int lane,
-                                                   Release release) {
+// Epilogue of NCOLS (64 or 128) accumulator columns by one warp (its 32-lane quadrant of tensor memory).
+// The columns are lifted into registers by loads issued back to back (128 columns, 64 KB per SM, leave tensor
+// memory in ~300 cycles this way) and release() is called at once: from then on the MMA thread may overwrite
+// them, and scaling, rounding, staging and the TMA stores run beside the next tile's MMAs.
+//   taddr  tensor-memory address of the first column in this warp's lane quadrant
+//   row0   first global row of this warp's 32 rows;  col0  first global column
+//   epi    this warp's NCOLS / 64 staging buffers of 4 KiB (32 rows x 128 bytes, 128-byte swizzle)
+// EPI selects the form: kEpiPlain bf16 (optional residual), kEpiRope with the rotary embedding, kEpiSilu with a
+// SiLU range (rotary or not), kEpiGeneral fp32 outputs or fp32 accumulation.
+// (Storing the rounded values straight from registers, 32 bytes per lane and store, instead of through the staging
+// buffers and TMA stores was measured: 8 % slower at N 28672, K 4096.)
+template <int EPI, int NCOLS, typename Release>
+__device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
+                                                int row0, int col0, float a_sg, int lane, Release release) {
+  static_assert(NCOLS == 64 || NCOLS == 128, "one or two slabs of 64 columns");
+  constexpr int kBufs = NCOLS / 64;
+  uint32_t r[NCOLS];
+#pragma unroll
+  for (int k = 0; k < NCOLS / 32; ++k) tmem_ld32(taddr + (uint32_t)(32 * k), *reinterpret_cast<uint32_t(*)[32]>(&r[32 * k]));
+  tmem_ld_wait();
+  release();
+  if (col0 >= g.N) return;   // second half of the last column tile when N is an odd multiple of 128
+
   float gs = a_sg;
-  if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? tn : 0));
-  const int row = row0 + quad * 32 + lane;
-  const int col0 = tn * kGemmBN;
-  int oi = 0, col_start = 0;
+  if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? (col0 >> 8) : 0));
+  const int row = row0 + lane;
+  int oi = 0, col_start = 0;   // which output receives this column range
   while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
   const int ocol = col0 - col_start;
-  const uint32_t tbase = tmem + ((uint32_t)(quad * 32) << 16);
-  const __nv_bfloat16* res_row = g.residual != nullptr ? g.residual + (size_t)row * g.residual_ld + col0 : nullptr;
   uint8_t* rowp = epi + lane * 128;
   const int sw = lane & 7;
-
-  // eight packed words (16 columns) + optional residual
-  auto add_residual = [&](uint32_t (&w)[8], int col) {
-    const uint4* rs = reinterpret_cast<const uint4*>(res_row + col);
-#pragma unroll
-    for (int q = 0; q < 2; ++q) {
-      const uint4 rv = __ldg(rs + q);
-      const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const uint32_t d = w[4 * q + e];
-        w[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]), bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
-      }
+  // a staging buffer may be rewritten once the store issued from it (kBufs slabs ago) has read it
+  auto buffer_free = [&]() {
+    if (lane == 0) {
+      if constexpr (kBufs == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+      else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
     }
-  };
-
-  // Rotary embedding of 16 columns (eight pairs): (cos, sin) of this lane's token row and of the pairs' positions
-  // inside their head are 64 contiguous bytes of the table (head_dim >= 16).  even' = fma(x, cos, -(y*sin)),
-  // odd' = fma(y, cos, x*sin).
-  const bool rope_tile = ROPE && col0 < g.rope_col_end;   // rope_col_end is 0 when there is no table (SiLU alone)
-  const float2* cs_row = rope_tile ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
-  auto load_cs = [&](float4 (&cs)[4], int col) {
-    const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
-#pragma unroll
-    for (int q = 0; q < 4; ++q) cs[q] = __ldg(p + q);
-  };
-  auto rotate_pair = [&](float x, float y, float c, float sn) {
-    return f32x2_to_bf16x2(__fmaf_rn(x, c, -__fmul_rn(y, sn)), __fmaf_rn(y, c, __fmul_rn(x, sn)));
-  };
-  // eight packed bf16 pairs, already rounded (the "packed" forms rotate the bf16 GEMM output)
-  auto rotate_with = [&](uint32_t (&w)[8], const float4 (&cs)[4]) {
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      w[2 * q] = rotate_pair(bf16lo_to_f32(w[2 * q]), bf16hi_to_f32(w[2 * q]), cs[q].x, cs[q].y);
-      w[2 * q + 1] = rotate_pair(bf16lo_to_f32(w[2 * q + 1]), bf16hi_to_f32(w[2 * q + 1]), cs[q].z, cs[q].w);
-    }
-  };
-  auto rotate_packed = [&](uint32_t (&w)[8], int col) {
-    float4 cs[4];
-    load_cs(cs, col);
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      w[2 * q] = rotate_pair(bf16lo_to_f32(w[2 * q]), bf16hi_to_f32(w[2 * q]), cs[q].x, cs[q].y);
-      w[2 * q + 1] = rotate_pair(bf16lo_to_f32(w[2 * q + 1]), bf16hi_to_f32(w[2 * q + 1]), cs[q].z, cs[q].w);
-    }
-  };
-
-  // the stores of the previous tile have finished reading both staging buffers (issued a tile ago)
-  if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-  __syncwarp();
-
-  uint32_t o[64];
-  uint32_t ra[32], rb[32];
-  tmem_ld32(tbase, ra);
-#pragma unroll
-  for (int c = 0; c < 8; ++c) {           // 32 columns each; the next load is in flight while these are converted
-    tmem_ld_wait();
-    if (c + 1 < 8) {
-      if (c & 1) tmem_ld32(tbase + (uint32_t)(c + 1) * 32, ra);
-      else tmem_ld32(tbase + (uint32_t)(c + 1) * 32, rb);
-    }
-    uint32_t w[16];
-    const float2 gs2 = make_float2(gs, gs);
-    const bool silu_chunk = SILU && col0 + c * 32 < g.silu_col_end;
-    if (rope_tile && !g.rope_round_bf16) {
-      // rotation of the unrounded scaled accumulator: has to happen here, where the fp32 values are
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        float4 cs[4];
-        load_cs(cs, c * 32 + h * 16);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) {
-          const uint32_t lo = (c & 1) ? rb[16 * h + 2 * q] : ra[16 * h + 2 * q];
-          const uint32_t hi = (c & 1) ? rb[16 * h + 2 * q + 1] : ra[16 * h + 2 * q + 1];
-          float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
-          if constexpr (SILU) { if (silu_chunk) v = make_float2(silu_fast(v.x), silu_fast(v.y)); }
-          const float cc = (q & 1) ? cs[q >> 1].z : cs[q >> 1].x, sn = (q & 1) ? cs[q >> 1].w : cs[q >> 1].y;
-          w[8 * h + q] = rotate_pair(v.x, v.y, cc, sn);
-        }
-      }
-    } else {
-#pragma unroll
-      for (int q = 0; q < 16; ++q) {
-        const uint32_t lo = (c & 1) ? rb[2 * q] : ra[2 * q];
-        const uint32_t hi = (c & 1) ? rb[2 * q + 1] : ra[2 * q + 1];
-        float2 v = mul2(make_float2(__uint_as_float(lo), __uint_as_float(hi)), gs2);
-        if constexpr (SILU) { if (silu_chunk) v = make_float2(silu_fast(v.x), silu_fast(v.y)); }
-        w[q] = f32x2_to_bf16x2(v.x, v.y);
-      }
-      // packed forms: both halves are rotated after the accumulator's release (the staged half in place)
-    }
-    if (c < 4) {
-      // slab c/2 (64 columns = 128 bytes per row), 16-byte pieces 4*(c%2) .. 4*(c%2)+3 of the row
-      if (res_row != nullptr) {
-        uint32_t w0[8], w1[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) { w0[q] = w[q]; w1[q] = w[8 + q]; }
-        add_residual(w0, c * 32);
-        add_residual(w1, c * 32 + 16);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) { w[q] = w0[q]; w[8 + q] = w1[q]; }
-      }
-      uint8_t* dst = rowp + (c >> 1) * 4096;
-      const int p0 = (c & 1) * 4;
-#pragma unroll
-      for (int q = 0; q < 4; ++q)
-        *reinterpret_cast<uint4*>(dst + (((p0 + q) ^ sw) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-    } else {
-#pragma unroll
-      for (int q = 0; q < 16; ++q) o[(c - 4) * 16 + q] = w[q];
-    }
-  }
-  release();
-
-  // Heads of at most 128 columns: the column 128 further on sits at the same position of its head, so one read of
-  // (cos, sin) serves a piece of the staged half and the piece of the register half 128 columns to its right.
-  const bool rope_shared = rope_tile && g.rope_round_bf16 && g.rope_head_mask < 128 && col0 + 128 < g.rope_col_end;
-  if (rope_tile && g.rope_round_bf16) {
-    // staged half: this lane's own row, 16 columns (two 16-byte pieces) at a time
-#pragma unroll
-    for (int slab = 0; slab < 2; ++slab) {
-#pragma unroll
-      for (int pp = 0; pp < 4; ++pp) {
-        uint4* p0 = reinterpret_cast<uint4*>(rowp + slab * 4096 + (((2 * pp) ^ sw) << 4));
-        uint4* p1 = reinterpret_cast<uint4*>(rowp + slab * 4096 + (((2 * pp + 1) ^ sw) << 4));
-        const uint4 a = *p0, b = *p1;
-        uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
-        float4 cs[4];
-        load_cs(cs, slab * 64 + pp * 16);
-        rotate_with(w, cs);
-        *p0 = make_uint4(w[0], w[1], w[2], w[3]);
-        *p1 = make_uint4(w[4], w[5], w[6], w[7]);
-        if (rope_shared) {
-          uint32_t v[8];
-#pragma unroll
-          for (int q = 0; q < 8; ++q) v[q] = o[slab * 32 + pp * 8 + q];
-          rotate_with(v, cs);
-#pragma unroll
-          for (int q = 0; q < 8; ++q) o[slab * 32 + pp * 8 + q] = v[q];
-        }
-      }
-    }
-  }
-  // staged half: two TMA stores
-  fence_proxy_async_smem();
-  __syncwarp();
-  if (lane == 0) {
-    tma_store_2d(&tmap_d.m[oi], epi, ocol, row0 + quad * 32);
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-    tma_store_2d(&tmap_d.m[oi], epi + 4096, ocol + 64, row0 + quad * 32);
-    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
-  }
-  // register half: slabs 2 and 3 through the same two buffers
-#pragma unroll
-  for (int slab = 2; slab < 4; ++slab) {
-    uint8_t* dst = rowp + (slab & 1) * 4096;
-    if (rope_tile && g.rope_round_bf16 && !rope_shared) {
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t w[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) w[q] = o[(slab - 2) * 32 + cc * 8 + q];
-        rotate_packed(w, slab * 64 + cc * 16);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) o[(slab - 2) * 32 + cc * 8 + q] = w[q];
-      }
-    }
-    if (res_row != nullptr) {
-#pragma unroll
-      for (int cc = 0; cc < 4; ++cc) {
-        uint32_t w[8];
-#pragma unroll
-        for (int q = 0; q < 8; ++q) w[q] = o[(slab - 2) * 32 + cc * 8 + q];
-        add_residual(w, slab * 64 + cc * 16);
-#pragma unroll
-        for (int q = 0; q < 8; ++q) o[(slab - 2) * 32 + cc * 8 + q] = w[q];
-      }
-    }
-    // the store issued from this buffer (slab - 2) must have finished reading it
-    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
     __syncwarp();
-#pragma unroll
-    for (int q = 0; q < 8; ++q)
-      *reinterpret_cast<uint4*>(dst + ((q ^ sw) << 4)) =
-          make_uint4(o[(slab - 2) * 32 + 4 * q], o[(slab - 2) * 32 + 4 * q + 1], o[(slab - 2) * 32 + 4 * q + 2],
-                     o[(slab - 2) * 32 + 4 * q + 3]);
+  };
+  auto store_slab = [&](const uint8_t* buf, int x) {
     fence_proxy_async_smem();
     __syncwarp();
     if (lane == 0) {
-      tma_store_2d(&tmap_d.m[oi], epi + (slab & 1) * 4096, ocol + slab * 64, row0 + quad * 32);
+      tma_store_2d(&tmap_d.m[oi], buf, x, row0);
       asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  };
+
+  if constexpr (EPI == kEpiGeneral) {
+    // slabs of 128 bytes per row: 32 fp32 columns, or 64 bf16 columns from two 32-column chunks
+#pragma unroll
+    for (int c = 0; c < NCOLS / 32; ++c) {
+      float v[32];
+      if (g.accum_f32 != nullptr) {
+        // running fp32 sum over a batch of GEMMs: partial + acc*scale (multiply, then add)
+        const float4* ps = reinterpret_cast<const float4*>(g.accum_f32 + (size_t)row * g.N + col0 + 32 * c);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const float4 pv = __ldg(ps + q);
+          v[4 * q] = __fadd_rn(pv.x, __fmul_rn(__uint_as_float(r[32 * c + 4 * q]), gs));
+          v[4 * q + 1] = __fadd_rn(pv.y, __fmul_rn(__uint_as_float(r[32 * c + 4 * q + 1]), gs));
+          v[4 * q + 2] = __fadd_rn(pv.z, __fmul_rn(__uint_as_float(r[32 * c + 4 * q + 2]), gs));
+          v[4 * q + 3] = __fadd_rn(pv.w, __fmul_rn(__uint_as_float(r[32 * c + 4 * q + 3]), gs));
+        }
+      } else {
+#pragma unroll
+        for (int q = 0; q < 32; ++q) v[q] = __fmul_rn(__uint_as_float(r[32 * c + q]), gs);
+      }
+      if (g.out_fp32) {
+        uint8_t* buf = rowp + (c & (kBufs - 1)) * 4096;
+        buffer_free();
+#pragma unroll
+        for (int q = 0; q < 8; ++q)
+          *reinterpret_cast<float4*>(buf + ((q ^ sw) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+        store_slab(epi + (c & (kBufs - 1)) * 4096, ocol + 32 * c);
+      } else {
+        uint8_t* buf = rowp + (c >> 1) * 4096;
+        if ((c & 1) == 0) buffer_free();
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          *reinterpret_cast<uint4*>(buf + ((((c & 1) * 4 + q) ^ sw) << 4)) =
+              make_uint4(f32x2_to_bf16x2(v[8 * q], v[8 * q + 1]), f32x2_to_bf16x2(v[8 * q + 2], v[8 * q + 3]),
+                         f32x2_to_bf16x2(v[8 * q + 4], v[8 * q + 5]), f32x2_to_bf16x2(v[8 * q + 6], v[8 * q + 7]));
+        if (c & 1) store_slab(epi + (c >> 1) * 4096, ocol + 64 * (c >> 1));
+      }
+    }
+  } else {
+    constexpr bool ROPE = EPI == kEpiRope || EPI == kEpiSilu;
+    constexpr bool SILU = EPI == kEpiSilu;
+    const float2 gs2 = make_float2(gs, gs);
+    const __nv_bfloat16* res_row = g.residual != nullptr ? g.residual + (size_t)row * g.residual_ld + col0 : nullptr;
+    // rope_col_end is 0 when there is no table (SiLU alone)
+    const float2* cs_row = (ROPE && col0 < g.rope_col_end) ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
+#pragma unroll
+    for (int slab = 0; slab < kBufs; ++slab) {      // 64 columns = 128 bytes per row
+      uint32_t w[32];
+#pragma unroll
+      for (int h = 0; h < 4; ++h) {                 // 16 columns = eight pairs
+        const int col = slab * 64 + h * 16;
+        const bool silu_here = SILU && col0 + col < g.silu_col_end;
+        const bool rope_here = ROPE && cs_row != nullptr && col0 + col < g.rope_col_end;
+        float4 cs[4];
+        if (rope_here) {
+          // (cos, sin) of this lane's token and of the pairs' positions inside their head: 64 contiguous bytes
+          const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) cs[q] = __ldg(p + q);
+        }
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          float2 v = mul2(make_float2(__uint_as_float(r[col + 2 * q]), __uint_as_float(r[col + 2 * q + 1])), gs2);
+          if constexpr (SILU) { if (silu_here) v = make_float2(silu_fast(v.x), silu_fast(v.y)); }
+          uint32_t o = f32x2_to_bf16x2(v.x, v.y);
+          if constexpr (ROPE) {
+            if (rope_here) {
+              // even' = fma(x, cos, -(y*sin)), odd' = fma(y, cos, x*sin); the packed forms rotate the rounded output
+              const float x = g.rope_round_bf16 ? bf16lo_to_f32(o) : v.x, y = g.rope_round_bf16 ? bf16hi_to_f32(o) : v.y;
+              const float cc = (q & 1) ? cs[q >> 1].z : cs[q >> 1].x, sn = (q & 1) ? cs[q >> 1].w : cs[q >> 1].y;
+              o = f32x2_to_bf16x2(__fmaf_rn(x, cc, -__fmul_rn(y, sn)), __fmaf_rn(y, cc, __fmul_rn(x, sn)));
+            }
+          }
+          w[h * 8 + q] = o;
+        }
+      }
+      if (res_row != nullptr) {
+        const uint4* rs = reinterpret_cast<const uint4*>(res_row + slab * 64);
+#pragma unroll
+        for (int q = 0; q < 8; ++q) {
+          const uint4 rv = __ldg(rs + q);
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t d = w[4 * q + e];
+            w[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]), bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
+          }
+        }
+      }
+      uint8_t* buf = rowp + slab * 4096;
+      buffer_free();
+#pragma unroll
+      for (int q = 0; q < 8; ++q)
+        *reinterpret_cast<uint4*>(buf + ((q ^ sw) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
+      store_slab(epi + slab * 4096, ocol + slab * 64);
     }
   }
 }
 
-// EPI: one epilogue form per instantiation, chosen by the host (kEpiPlain: bf16 outputs, optional residual;
-// kEpiRope: with the rotary embedding; kEpiSilu: with a SiLU range, rotary or not; kEpiGeneral: fp32 outputs or
-// accumulation).  Several forms inside one kernel cost every one of them a few percent.
+// K-segment bookkeeping of the producer: which segment a K stage belongs to and its index inside the segment.
+struct SegCursor {
+  int seg = -1, seg_end = 0, kl = 0;
+  __device__ __forceinline__ bool enter(const GemmArgs& g, int ks) {   // true at a segment's first stage
+    if (ks != seg_end) { ++kl; return false; }
+    ++seg;
+    seg_end = g.seg_stage_end[seg];
+    kl = 0;
+    return true;
+  }
+};
+
+// EPI: one epilogue form per instantiation, chosen by the host.  Several forms inside one kernel cost every one of
+// them a few percent.
 template <bool MX, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
@@ -537,16 +398,18 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
 
   const int tid = threadIdx.x;
   const int warp = tid >> 5, lane = tid & 31;
-  const int tiles_m = g.M / kGemmBM, tiles_n = g.N / kGemmBN;
+  const int tiles_m = g.M / kGemmBM, tiles_n = (g.N + kGemmBN - 1) / kGemmBN;
   const int n_tiles = tiles_m * tiles_n;
-  const int k_stages = g.K / (2 * kGemmBKBytes);     // stages of 256 elements
+  const int k_stages = g.seg_stage_end[g.n_seg - 1];   // stages of 256 elements (the very last may hold 128)
+  const bool k_tail_half = g.seg_tail_half[g.n_seg - 1] != 0;   // only a plain MXFP4 GEMM (one segment) can have one
 
   if (tid == 0) {
     for (int s = 0; s < kGemmStages; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); mbar_init(&sm.sf_ready[s], 4); }
     mbar_init(&sm.acc_full, 1);
     mbar_init(&sm.acc_empty, 4);   // one arrival per epilogue warp
-    sm.abort_flag = 0;
     fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    for (int s = 0; s < g.n_seg; ++s) tma_prefetch_desc(&tmap_b.m[s]);
   }
   if (warp == 1) {   // tensor-memory allocation is a warp-wide operation
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
@@ -558,32 +421,33 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  // Launched as a programmatic dependent, everything above ran beside the previous kernel's tail; nothing below
+  // touches global memory before that kernel's writes are visible.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_a);
-      for (int s = 0; s < g.n_seg; ++s) tma_prefetch_desc(&tmap_b.m[s]);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
         int tm, tn;
         raster_tile(t, tiles_m, tiles_n, tm, tn);
-        int seg = -1, seg_end = 0, kl = 0, a_col = 0;
+        SegCursor cur;
+        int a_col = 0;
         const CUtensorMap* bmap = nullptr;
         const uint8_t *sfa_src = nullptr, *sfb_src0 = nullptr, *sfb_src1 = nullptr;
-        for (int ks = 0; ks < k_stages; ++ks, ++kl) {
-          if (ks == seg_end) {   // first stage of the next K segment
-            ++seg;
-            seg_end = g.seg_stage_end[seg];
-            kl = 0;
-            a_col = g.seg_a_col_bytes[seg];
-            bmap = &tmap_b.m[seg];
-            const size_t tiles_k = (size_t)g.seg_sf_tiles_k[seg];
-            sfa_src = g.seg_a_sc[seg] + (size_t)tm * tiles_k * 512;
-            sfb_src0 = g.seg_b_sc[seg] + (size_t)(2 * tn) * tiles_k * 512;
-            sfb_src1 = sfb_src0 + tiles_k * 512;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (cur.enter(g, ks)) {   // first stage of the next K segment
+            a_col = g.seg_a_col_bytes[cur.seg];
+            bmap = &tmap_b.m[cur.seg];
+            const size_t tiles_k = (size_t)g.seg_sf_tiles_k[cur.seg];
+            sfa_src = g.seg_a_sc[cur.seg] + (size_t)tm * tiles_k * 512;
+            sfb_src0 = g.seg_b_sc[cur.seg] + (size_t)(2 * tn) * tiles_k * 512;
+            // the last column tile of an N that is an odd multiple of 128 has no second group of B rows
+            sfb_src1 = (2 * tn + 1) * 128 < g.N ? sfb_src0 + tiles_k * 512 : sfb_src0;
           }
           if (!mbar_wait_timed(&sm.empty[stage], phase ^ 1)) {
             atomicExch(g.status, kStatusGemmTmaTimeout);
@@ -591,14 +455,14 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             break;
           }
           constexpr int kSfPerStage = MX ? 1024 : 2048;
-          mbar_expect_tx(&sm.full[stage], kATileBytes + kBTileBytes + 3 * kSfPerStage);
-          tma_load_2d(sm.a[stage], &tmap_a, a_col + kl * kGemmBKBytes, tm * kGemmBM, &sm.full[stage]);
-          tma_load_2d(sm.b[stage], bmap, kl * kGemmBKBytes, tn * kGemmBN, &sm.full[stage]);
+          const uint32_t sf_bytes = (MX && k_tail_half && ks + 1 == k_stages) ? kSfPerStage / 2 : kSfPerStage;
+          mbar_expect_tx(&sm.full[stage], kATileBytes + kBTileBytes + 3 * sf_bytes);
+          tma_load_2d(sm.a[stage], &tmap_a, a_col + cur.kl * kGemmBKBytes, tm * kGemmBM, &sm.full[stage]);
+          tma_load_2d(sm.b[stage], bmap, cur.kl * kGemmBKBytes, tn * kGemmBN, &sm.full[stage]);
           // scale tiles of this stage: NVFP4 4 tiles (256/64), MXFP4 2 tiles (256/128) per row tile
-          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)kl * kSfPerStage, kSfPerStage,
-                       &sm.full[stage]);
+          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
           if (++stage == kGemmStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -611,7 +475,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       uint32_t acc_phase = 0;
       bool ok = true;
       for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
-        // the epilogue must have drained the accumulator of the previous tile
+        // the epilogue must have lifted the previous tile's accumulator out of tensor memory
         if (!mbar_wait_timed(&sm.acc_empty, acc_phase ^ 1)) {
           atomicExch(g.status, kStatusGemmEpilogueTimeout);
           ok = false;
@@ -619,13 +483,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         tc_fence_after();
         for (int ks = 0; ks < k_stages; ++ks) {
-          if (!mbar_wait_timed(&sm.full[stage], phase)) {
-            atomicExch(g.status, kStatusGemmMmaTimeout);
-            ok = false;
-            break;
-          }
-          tc_fence_after();
-          if (!mbar_wait_timed(&sm.sf_ready[stage], phase)) {   // scales of this stage are in tensor memory
+          if (!mbar_wait_timed(&sm.sf_ready[stage], phase)) {   // operands landed and scales are in tensor memory
             atomicExch(g.status, kStatusGemmMmaTimeout);
             ok = false;
             break;
@@ -634,17 +492,26 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
           const uint32_t sf_cols = tmem + kSfTmemBase + stage * kSfSlotCols;
           const uint32_t a_base = smem_u32(sm.a[stage]);
           const uint32_t b_base = smem_u32(sm.b[stage]);
+          // MXFP4 with K an odd multiple of 128: the very last stage holds 128 elements, two MMAs instead of four
+          // (a branch of its own: a run-time MMA count in the unrolled loop cost every stage of every shape ~4 %)
+          if (MX && k_tail_half && ks + 1 == k_stages) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
-            const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
-            if constexpr (!MX) {
-              tc_mma<false>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 0, 0), sf_cols + j * 4,
-                            sf_cols + 16 + j * 8, (ks | j) != 0);
-            } else {
-              const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
-              tc_mma<true>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 1, sf_id),
-                           sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
+            for (int j = 0; j < 2; ++j)
+              tc_mma<true>(tmem, smem_desc(a_base + j * 32, 16, 1024, 2), smem_desc(b_base + j * 32, 16, 1024, 2),
+                          block_scaled_idesc(kGemmBM, kGemmBN, 1, j * 2), sf_cols, sf_cols + 16, (ks | j) != 0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
+              const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+              if constexpr (!MX) {
+                tc_mma<false>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 0, 0), sf_cols + j * 4,
+                             sf_cols + 16 + j * 8, (ks | j) != 0);
+              } else {
+                const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
+                tc_mma<true>(tmem, adesc, bdesc, block_scaled_idesc(kGemmBM, kGemmBN, 1, sf_id),
+                            sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
+              }
             }
           }
           tc_commit(&sm.empty[stage]);   // frees the shared-memory stage once these MMAs have read it
@@ -674,21 +541,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
         }
         const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + kSfTmemBase + stage * kSfSlotCols;
         uint32_t ra[16], rb[32];
-#pragma unroll
-        for (int j = 0; j < kTiles; ++j) {
-          const uint4 va = *reinterpret_cast<const uint4*>(&sm.sfa[stage][j * 512 + lane * 16]);
-          ra[4 * j] = va.x; ra[4 * j + 1] = va.y; ra[4 * j + 2] = va.z; ra[4 * j + 3] = va.w;
-          const uint4 v0 = *reinterpret_cast<const uint4*>(&sm.sfb[stage][j * 512 + lane * 16]);
-          const uint4 v1 = *reinterpret_cast<const uint4*>(&sm.sfb[stage][kTiles * 512 + j * 512 + lane * 16]);
-          rb[8 * j] = v0.x; rb[8 * j + 1] = v0.y; rb[8 * j + 2] = v0.z; rb[8 * j + 3] = v0.w;
-          rb[8 * j + 4] = v1.x; rb[8 * j + 5] = v1.y; rb[8 * j + 6] = v1.z; rb[8 * j + 7] = v1.w;
-        }
-#pragma unroll
-        for (int j = kTiles; j < 4; ++j) {
-          ra[4 * j] = ra[4 * j + 1] = ra[4 * j + 2] = ra[4 * j + 3] = 0;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) rb[8 * j + e] = 0;
-        }
+        load_stage_scales<kTiles>(sm.sfa[stage], sm.sfb[stage], lane, ra, rb);
         tmem_st16(taddr, ra);
         tmem_st32(taddr + 16, rb);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
@@ -707,29 +560,23 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
     bool ok = true;
     for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
       int tm, tn;
-        raster_tile(t, tiles_m, tiles_n, tm, tn);
+      raster_tile(t, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;
         break;
       }
       tc_fence_after();
-      // accumulator drained: let the MMA warp start the next tile
-      auto release = [&]() {
+      const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
+      uint8_t* epi = &sm.epi[warp - 2][0][0];
+      const int row0 = tm * kGemmBM + quad * 32;
+      epilogue_region<EPI, 128>(g, tmap_d, tq, epi, row0, tn * kGemmBN, a_sg, lane, [] {});
+      // both halves are out of tensor memory: let the MMA warp start the next tile
+      epilogue_region<EPI, 128>(g, tmap_d, tq + 128, epi, row0, tn * kGemmBN + 128, a_sg, lane, [&] {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.acc_empty);
-      };
-      if constexpr (EPI == kEpiGeneral) {
-        epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane);
-        release();
-      } else if constexpr (EPI == kEpiSilu) {
-        epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
-      } else if constexpr (EPI == kEpiRope) {
-        epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
-      } else {
-        epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * kGemmBM, tn, a_sg, quad, lane, release);
-      }
+      });
       acc_phase ^= 1;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staged stores have left shared memory
@@ -754,6 +601,14 @@ namespace fp4b200 {
 static bool gemm_pair_disabled() {
   static const bool off = [] { const char* e = getenv("FP4B200_GEMM_PAIR"); return e != nullptr && e[0] == '0'; }();
   return off;
+}
+
+// Programmatic dependent launch of the GEMM kernels: on unless FP4B200_GEMM_PDL=0 or the calling thread has switched
+// it off with fp4b200_set_gemm_pdl(0) (the mirrors' *_nopdl entry points do, around their one call).
+static thread_local int t_gemm_pdl = 1;
+static bool gemm_pdl_enabled() {
+  static const bool env_off = [] { const char* e = getenv("FP4B200_GEMM_PDL"); return e != nullptr && e[0] == '0'; }();
+  return !env_off && t_gemm_pdl != 0;
 }
 
 // K segments of one GEMM launch on the host side: D = sum_s A[:, off_s : off_s + k_s] * B_s^T, all
@@ -786,7 +641,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.a_width / 2, (uint64_t)M,
                             (uint64_t)segs.a_width / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  int64_t K = 0;
+  int64_t K = 0, stages = 0;
   GemmArgs g{};
   g.n_seg = segs.n;
   for (int s = 0; s < segs.n; ++s) {
@@ -795,7 +650,9 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
                               (uint64_t)segs.k[s] / 2, kGemmBKBytes, pair ? 128 : kGemmBN, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
     K += segs.k[s];
-    g.seg_stage_end[s] = (int)(K / 256);
+    stages += (segs.k[s] + 255) / 256;
+    g.seg_stage_end[s] = (int)stages;
+    g.seg_tail_half[s] = (segs.k[s] % 256) != 0;
     g.seg_a_col_bytes[s] = (int)(segs.a_col_off[s] / 2);
     g.seg_a_sc[s] = (const uint8_t*)segs.a_sc[s];
     g.seg_b_sc[s] = (const uint8_t*)segs.b_sc[s];
@@ -829,18 +686,20 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   if (pair) {
     // two-CTA clusters: one 256 x 256 tile per pair of SMs
     const int psmem = (int)sizeof(GemmPairSmem) + 1024;
-    const int pair_tiles = (int)((M / 256) * (N / kGemmBN));
+    const int pair_tiles = (int)((M / 256) * ((N + kGemmBN - 1) / kGemmBN));
     const int clusters = std::min(pair_tiles, device_sm_count() / 2);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * clusters, 1, 1);
-    cfg.blockDim = dim3(kGemmThreads, 1, 1);
+    cfg.blockDim = dim3(kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = psmem;
     cfg.stream = st;
-    cudaLaunchAttribute attr[1];
+    cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = 1;
+    cfg.numAttrs = gemm_pdl_enabled() ? 2 : 1;
 #define FP4_LAUNCH_PAIR(MXF, EPI)                                                                                          \
   do {                                                                                                                   \
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<MXF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem)); \
@@ -856,13 +715,23 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     return 0;
   }
   const int smem = (int)sizeof(GemmSmem) + 1024;
-  const int n_tiles = (int)((M / kGemmBM) * (N / kGemmBN));
+  const int n_tiles = (int)((M / kGemmBM) * ((N + kGemmBN - 1) / kGemmBN));
   const int grid = std::min(n_tiles, device_sm_count());
   if (grid == 0) return 0;
+  cudaLaunchConfig_t cfg1{};
+  cfg1.gridDim = dim3(grid, 1, 1);
+  cfg1.blockDim = dim3(kGemmThreads, 1, 1);
+  cfg1.dynamicSmemBytes = smem;
+  cfg1.stream = st;
+  cudaLaunchAttribute attr1[1];
+  attr1[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr1[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg1.attrs = attr1;
+  cfg1.numAttrs = gemm_pdl_enabled() ? 1 : 0;
 #define FP4_LAUNCH_ONE(MXF, EPI)                                                                                      \
   do {                                                                                                               \
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_kernel<MXF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem)); \
-    fp4_gemm_kernel<MXF, EPI><<<grid, kGemmThreads, smem, st>>>(tmap_a, tmap_b, omaps, g);                             \
+    FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg1, fp4_gemm_kernel<MXF, EPI>, tmap_a, tmap_b, omaps, g));                   \
   } while (0)
   if (mx) {
     if (epi == kEpiGeneral) FP4_LAUNCH_ONE(true, kEpiGeneral); else FP4_LAUNCH_ONE(true, kEpiPlain);
@@ -895,11 +764,12 @@ static int launch_gemm(bool mx, const void* A, const void* A_sc, const float* A_
 
 using namespace fp4b200;
 
+// k_mult: 256 (NVFP4: a K stage is four scale tiles of 64 elements) or 128 (MXFP4: a half-depth last stage)
 static int check_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, int64_t M, int64_t N,
-                      int64_t K, const char* who) {
+                      int64_t K, const char* who, int k_mult = 256) {
   if (!A || !A_sc || !B || !B_sc) return set_error("%s: operand pointer is null", who);
-  if (M <= 0 || N <= 0 || K <= 0 || (M % kGemmBM) || (N % kGemmBN) || (K % 256))
-    return set_error("%s: needs M %% 128 == 0, N %% 256 == 0, K %% 256 == 0 (got M=%lld N=%lld K=%lld)", who,
+  if (M <= 0 || N <= 0 || K <= 0 || (M % kGemmBM) || (N % 128) || (K % k_mult))
+    return set_error("%s: needs M %% 128 == 0, N %% 128 == 0, K %% %d == 0 (got M=%lld N=%lld K=%lld)", who, k_mult,
                      (long long)M, (long long)N, (long long)K);
   if (M > (1 << 30) || N > (1 << 30) || K > (1 << 30)) return set_error("%s: dimension too large", who);
   if ((reinterpret_cast<uintptr_t>(A) | reinterpret_cast<uintptr_t>(B) | reinterpret_cast<uintptr_t>(A_sc) |
@@ -909,6 +779,12 @@ static int check_gemm(const void* A, const void* A_sc, const void* B, const void
 }
 
 extern "C" {
+
+int fp4b200_set_gemm_pdl(int enabled) {
+  const int before = t_gemm_pdl;
+  t_gemm_pdl = enabled != 0;
+  return before;
+}
 
 int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                        const float* B_sg, void* D, int out_fp32, const void* residual_bf16, int64_t M, int64_t N,
@@ -992,7 +868,7 @@ int fp4b200_nvfp4_grouped_gemm_rope(const void* A, const void* A_sc, const float
 
 int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,
                        const void* residual_bf16, int64_t M, int64_t N, int64_t K, void* stream) {
-  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, "mxfp4_gemm")) return rc;
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, "mxfp4_gemm", 128)) return rc;
   if (!D) return set_error("mxfp4_gemm: D is required");
   if (residual_bf16 && out_fp32) return set_error("mxfp4_gemm: the residual epilogue writes bf16 only");
   void* d[1] = {D};

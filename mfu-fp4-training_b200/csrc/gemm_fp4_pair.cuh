@@ -2,27 +2,43 @@
 // computes one 256 x 256 output tile with tcgen05.mma.cta_group::2.  Each CTA loads its own 128 rows
 // of A and its own half (128 rows) of the B tile, so a K stage costs 38 KB of L2 -> SM traffic per SM
 // instead of 54 KB for the same MMA work — operand delivery, not the tensor pipe, bounds the
-// one-CTA kernel.  No multicast loads: the second CTA's data arrives through its own TMA and its
-// readiness is forwarded with remote mbarrier arrivals; the leader's tcgen05.commit signals the
-// barriers of both CTAs one by one.  Included by gemm_fp4.cu after the shared helpers.
+// one-CTA kernel.  No multicast loads: the second CTA's data arrives through its own TMA.
+//
+// Tensor-memory plan (512 columns per SM): consecutive tiles of a pair alternate between the accumulator
+// columns [0, 256) and [128, 384), so that only the middle 128 columns are shared between a tile and the next.
+// The epilogue lifts that shared half into registers first (~300 cycles) and releases it; the MMA thread then
+// starts the next tile while the private half is drained, scaled, rounded and stored.  The block scales of two
+// K stages (2 x 48 columns from column 384) fit beside the accumulators.
+//
+// What bounds this kernel is shared-memory bandwidth (128 B per clock and SM for reads and writes together): at
+// the tensor pipe's full rate the operands alone need 64 B per clock to arrive and 64 B per clock to be read;
+// scale tiles (written once, read by four mover warps) and staged outputs come on top.  Measured per 256-deep
+// stage: ~760 cycles where the MMAs alone take 512.  Moving the scales with tcgen05.cp (one read per tile,
+// replicated to the four lane quadrants by the copy) was measured too and is slower: twelve copies per stage
+// cost ~1100 cycles of the tensor pipe when the MMA thread issues them and ~600 when a thread of their own does.
+// Included by gemm_fp4.cu after the shared helpers.
 #pragma once
 
 namespace fp4b200 {
 
 constexpr int kPairStages = 5;
 constexpr int kPairBHalfBytes = 128 * kGemmBKBytes;   // this CTA's half of the B tile: 16 KiB
+constexpr int kPairSfSlots = 2;                       // K stages whose scales are resident in tensor memory
+constexpr int kPairSfBase = 384;                      // accumulators occupy columns [0, 384)
+constexpr int kPairThreads = kGemmThreads;            // producer, MMA thread, four epilogue warps, four scale movers
 
 struct GemmPairSmem {
   alignas(1024) uint8_t a[kPairStages][kATileBytes];
   alignas(1024) uint8_t b[kPairStages][kPairBHalfBytes];
-  alignas(1024) uint8_t epi[4][2][4096];
+  alignas(1024) uint8_t epi[4][2][4096];       // per epilogue warp: two slabs of 32 rows x 128 bytes
   alignas(128) uint8_t sfa[kPairStages][kASfBytes];
   alignas(128) uint8_t sfb[kPairStages][kBSfBytes];
   alignas(8) uint64_t full[kPairStages];       // this CTA's TMA data of the stage has landed
-  alignas(8) uint64_t empty[kPairStages];      // the pair's MMAs have finished reading the stage
-  alignas(8) uint64_t sf_ready[kPairStages];   // leader only: operands + scales of BOTH CTAs are in place
+  alignas(8) uint64_t empty[kPairStages];      // the pair's MMAs have finished reading the stage (and its scale slot)
+  alignas(8) uint64_t sf_ready[kPairSfSlots];  // leader only: operands + scales of BOTH CTAs are in place
   alignas(8) uint64_t acc_full;                // accumulator of the tile is complete
-  alignas(8) uint64_t acc_empty;               // leader only: both CTAs' epilogues have drained it
+  alignas(8) uint64_t acc_empty_shared;        // leader only: both CTAs have lifted columns [128, 256) out
+  alignas(8) uint64_t acc_empty_priv[2];       // leader only: columns [0, 128) / [256, 384)
   uint32_t tmem_base;
 };
 
@@ -41,15 +57,17 @@ __device__ __forceinline__ uint32_t map_to_cta(const void* p, uint32_t rank) {
   return r;
 }
 // Arrival on a barrier of any CTA of the pair.  Relaxed: the arriving threads publish no generic-proxy
-// writes (tensor-memory stores are ordered by tcgen05.wait::st + tcgen05.fence, operand tiles by the
+// writes (tensor-memory stores and loads are ordered by tcgen05.wait + tcgen05.fence, operand tiles by the
 // TMA's own mbarrier), and a cluster-scope release was measured at ~1200 cycles per arrival while TMA
 // traffic is in flight.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
-// completion of all earlier tcgen05 operations of this thread -> one arrival on a barrier of any CTA of the pair
-__device__ __forceinline__ void tc_commit_pair(uint32_t cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr)
+// completion of all earlier tcgen05 operations of this thread -> one arrival on the barrier at this offset in
+// BOTH CTAs of the pair (one instruction in the tensor pipe's queue, no forwarding hop)
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"((uint16_t)3)
                : "memory");
 }
 
@@ -71,11 +89,9 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
   }
 }
 
-// EPI: one epilogue form per instantiation, chosen by the host (kEpiPlain: bf16 outputs, optional residual;
-// kEpiRope: with the rotary embedding; kEpiSilu: with a SiLU range, rotary or not; kEpiGeneral: fp32 outputs or
-// accumulation).  Several forms inside one kernel cost every one of them a few percent.
+// EPI: one epilogue form per instantiation, chosen by the host (see epilogue_region).
 template <bool MX, int EPI = kEpiPlain>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kPairThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                      const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -83,20 +99,25 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs)
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
-  const int tiles_m = g.M / 256, tiles_n = g.N / kGemmBN;
+  const int tiles_m = g.M / 256, tiles_n = (g.N + kGemmBN - 1) / kGemmBN;
   const int n_tiles = tiles_m * tiles_n;
-  const int k_stages = g.K / (2 * kGemmBKBytes);
+  const int k_stages = g.seg_stage_end[g.n_seg - 1];
+  const bool k_tail_half = g.seg_tail_half[g.n_seg - 1] != 0;   // only a plain MXFP4 GEMM (one segment) can have one
   constexpr int kSfPerStage = MX ? 1024 : 2048;
 
   if (tid == 0) {
     for (int s = 0; s < kPairStages; ++s) {
       mbar_init(&sm.full[s], 1);
       mbar_init(&sm.empty[s], 1);
-      mbar_init(&sm.sf_ready[s], 8);   // four mover warps of each CTA
     }
+    for (int s = 0; s < kPairSfSlots; ++s) mbar_init(&sm.sf_ready[s], 8);   // four mover warps of each CTA
     mbar_init(&sm.acc_full, 1);
-    mbar_init(&sm.acc_empty, 8);       // four epilogue warps of each CTA
+    mbar_init(&sm.acc_empty_shared, 8);                                      // four epilogue warps of each CTA
+    mbar_init(&sm.acc_empty_priv[0], 8);
+    mbar_init(&sm.acc_empty_priv[1], 8);
     fence_mbar_init();
+    tma_prefetch_desc(&tmap_a);
+    for (int s = 0; s < g.n_seg; ++s) tma_prefetch_desc(&tmap_b.m[s]);
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&sm.tmem_base)),
@@ -109,53 +130,46 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   cluster_sync_all();                 // both CTAs' barriers exist before any remote arrival
   tc_fence_after();
   const uint32_t tmem = sm.tmem_base;
+  // Launched as a programmatic dependent, everything above ran beside the previous kernel's tail; nothing below
+  // touches global memory before that kernel's writes are visible.
+  pdl_launch_dependents();
+  pdl_wait();
 
   if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) --------------------------------
     if (lane == 0) {
-      tma_prefetch_desc(&tmap_a);
-      for (int s = 0; s < g.n_seg; ++s) tma_prefetch_desc(&tmap_b.m[s]);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      uint32_t empty_peer[kPairStages];
-#pragma unroll
-      for (int s = 0; s < kPairStages; ++s) empty_peer[s] = map_to_cta(&sm.empty[s], 1);
-      int filled = 0;
       for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
         int tm, tn;
         raster_tile(t, tiles_m, tiles_n, tm, tn);
-        int seg = -1, seg_end = 0, kl = 0, a_col = 0;
+        SegCursor cur;
+        int a_col = 0;
         const CUtensorMap* bmap = nullptr;
         const uint8_t *sfa_src = nullptr, *sfb_src0 = nullptr, *sfb_src1 = nullptr;
-        for (int ks = 0; ks < k_stages; ++ks, ++kl) {
-          if (ks == seg_end) {   // first stage of the next K segment
-            ++seg;
-            seg_end = g.seg_stage_end[seg];
-            kl = 0;
-            a_col = g.seg_a_col_bytes[seg];
-            bmap = &tmap_b.m[seg];
-            const size_t tiles_k = (size_t)g.seg_sf_tiles_k[seg];
-            sfa_src = g.seg_a_sc[seg] + (size_t)(2 * tm + rank) * tiles_k * 512;
-            sfb_src0 = g.seg_b_sc[seg] + (size_t)(2 * tn) * tiles_k * 512;
-            sfb_src1 = sfb_src0 + tiles_k * 512;
+        for (int ks = 0; ks < k_stages; ++ks) {
+          if (cur.enter(g, ks)) {   // first stage of the next K segment
+            a_col = g.seg_a_col_bytes[cur.seg];
+            bmap = &tmap_b.m[cur.seg];
+            const size_t tiles_k = (size_t)g.seg_sf_tiles_k[cur.seg];
+            sfa_src = g.seg_a_sc[cur.seg] + (size_t)(2 * tm + rank) * tiles_k * 512;
+            sfb_src0 = g.seg_b_sc[cur.seg] + (size_t)(2 * tn) * tiles_k * 512;
+            // the last column tile of an N that is an odd multiple of 128 has no second group of B rows
+            sfb_src1 = (2 * tn + 1) * 128 < g.N ? sfb_src0 + tiles_k * 512 : sfb_src0;
           }
-          const bool first_fill = filled < kPairStages;   // the first use of a stage waits for nothing
-          ++filled;
           if (!mbar_wait_timed(&sm.empty[stage], phase ^ 1)) {
             atomicExch(g.status, kStatusGemmTmaTimeout);
             ok = false;
             break;
           }
-          // the leader's barrier is signalled by tcgen05.commit; it passes the news on to the other CTA
-          // (one commit per stage instead of two keeps the tensor pipe's queue short)
-          if (rank == 0 && !first_fill) mbar_arrive_cluster(empty_peer[stage]);
-          mbar_expect_tx(&sm.full[stage], kATileBytes + kPairBHalfBytes + 3 * kSfPerStage);
-          tma_load_2d(sm.a[stage], &tmap_a, a_col + kl * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
-          tma_load_2d(sm.b[stage], bmap, kl * kGemmBKBytes, tn * kGemmBN + (int)rank * 128, &sm.full[stage]);
-          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
-          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)kl * kSfPerStage, kSfPerStage, &sm.full[stage]);
+          const uint32_t sf_bytes = (MX && k_tail_half && ks + 1 == k_stages) ? kSfPerStage / 2 : kSfPerStage;
+          mbar_expect_tx(&sm.full[stage], kATileBytes + kPairBHalfBytes + 3 * sf_bytes);
+          tma_load_2d(sm.a[stage], &tmap_a, a_col + cur.kl * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
+          tma_load_2d(sm.b[stage], bmap, cur.kl * kGemmBKBytes, tn * kGemmBN + (int)rank * 128, &sm.full[stage]);
+          bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
+          bulk_load_1d(sm.sfb[stage] + kSfPerStage, sfb_src1 + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
           if (++stage == kPairStages) { stage = 0; phase ^= 1; }
         }
       }
@@ -164,88 +178,101 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------ MMA issuer (leader CTA only) ----------------------------
     if (lane == 0 && rank == 0) {
       int stage = 0;
-      uint32_t phase = 0, acc_phase = 0;
+      uint32_t gk = 0;                       // K stages issued so far, over all tiles
+      uint32_t shared_phase = 0, priv_phase = 0;   // priv_phase: bit `kind`
+      int kind = 0;                          // 0: accumulator at columns [0, 256), 1: at [128, 384)
       bool ok = true;
-      const uint32_t acc_full_remote = map_to_cta(&sm.acc_full, 1);
-      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-        if (!mbar_wait_timed(&sm.acc_empty, acc_phase ^ 1)) {
+      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters, kind ^= 1) {
+        // the private half was released two tiles ago, the shared half by the previous tile's epilogue
+        if (!mbar_wait_timed(&sm.acc_empty_priv[kind], ((priv_phase >> kind) & 1u) ^ 1u) ||
+            !mbar_wait_timed(&sm.acc_empty_shared, shared_phase ^ 1)) {
           atomicExch(g.status, kStatusGemmEpilogueTimeout);
           ok = false;
           break;
         }
+        priv_phase ^= 1u << kind;
+        shared_phase ^= 1;
         tc_fence_after();
-        for (int ks = 0; ks < k_stages; ++ks) {
-          if (!mbar_wait_timed(&sm.sf_ready[stage], phase)) {
+        const uint32_t d_tmem = tmem + (uint32_t)kind * 128;
+        for (int ks = 0; ks < k_stages; ++ks, ++gk) {
+          // operands of both CTAs have landed and the movers have put the stage's scales into tensor memory
+          const uint32_t slot = gk % kPairSfSlots;
+          if (!mbar_wait_timed(&sm.sf_ready[slot], (gk / kPairSfSlots) & 1u)) {
             atomicExch(g.status, kStatusGemmMmaTimeout);
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint32_t sf_cols = tmem + kSfTmemBase + stage * kSfSlotCols;
+          const uint32_t sf_cols = tmem + kPairSfBase + slot * kSfSlotCols;
           const uint32_t a_base = smem_u32(sm.a[stage]);
           const uint32_t b_base = smem_u32(sm.b[stage]);
+          // MXFP4 with K an odd multiple of 128: the very last stage holds 128 elements, two MMAs instead of four
+          // (a branch of its own: a run-time MMA count in the unrolled loop cost every stage of every shape ~4 %)
+          if (MX && k_tail_half && ks + 1 == k_stages) {
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
-            const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
-            if constexpr (!MX) {
-              tc_mma_pair<false>(tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 0, 0), sf_cols + j * 4,
-                                 sf_cols + 16 + j * 8, (ks | j) != 0);
-            } else {
-              const int sf_id = (j & 1) * 2;
-              tc_mma_pair<true>(tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 1, sf_id),
-                                sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
+            for (int j = 0; j < 2; ++j)
+              tc_mma_pair<true>(d_tmem, smem_desc(a_base + j * 32, 16, 1024, 2), smem_desc(b_base + j * 32, 16, 1024, 2),
+                          block_scaled_idesc(256, kGemmBN, 1, j * 2), sf_cols, sf_cols + 16, (ks | j) != 0);
+          } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint64_t adesc = smem_desc(a_base + j * 32, 16, 1024, 2);
+              const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
+              if constexpr (!MX) {
+                tc_mma_pair<false>(d_tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 0, 0), sf_cols + j * 4,
+                             sf_cols + 16 + j * 8, (ks | j) != 0);
+              } else {
+                const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
+                tc_mma_pair<true>(d_tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 1, sf_id),
+                            sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
+              }
             }
           }
-          tc_commit_pair(smem_u32(&sm.empty[stage]));   // the producer forwards it to the other CTA
-          if (++stage == kPairStages) { stage = 0; phase ^= 1; }
+          tc_commit_pair(&sm.empty[stage]);   // both CTAs: the stage may be refilled
+          if (++stage == kPairStages) stage = 0;
         }
-        if (ok) {
-          // once per tile: signal both CTAs' epilogues directly (a forwarded arrival would add a hop)
-          tc_commit_pair(smem_u32(&sm.acc_full));
-          tc_commit_pair(acc_full_remote);
-        }
-        acc_phase ^= 1;
+        if (ok) tc_commit_pair(&sm.acc_full);   // both CTAs' epilogues
       }
     }
   } else if (warp >= 6) {
     // ------------------------------ scale movers (both CTAs) --------------------------------
+    // A scale slot is rewritten as soon as the MMAs of the stage two steps back have completed, which the
+    // leader's tcgen05.commit announces to both CTAs at once (multicast arrival on that stage's `empty` barrier).
     const int quad = warp & 3;
     int stage = 0;
     uint32_t phase = 0;
+    uint32_t gk = 0;
     bool ok = true;
     constexpr int kTiles = MX ? 2 : 4;
+    static_assert(kPairSfSlots == 2, "the movers keep one leader address per slot");
+    const uint32_t sf_ready_leader0 = map_to_cta(&sm.sf_ready[0], 0), sf_ready_leader1 = map_to_cta(&sm.sf_ready[1], 0);
     for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
-      for (int ks = 0; ks < k_stages; ++ks) {
+      for (int ks = 0; ks < k_stages; ++ks, ++gk) {
         if (!mbar_wait_timed(&sm.full[stage], phase)) {
           if (lane == 0) atomicExch(g.status, kStatusGemmMmaTimeout);
           ok = false;
           break;
         }
-        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + kSfTmemBase + stage * kSfSlotCols;
         uint32_t ra[16], rb[32];
-#pragma unroll
-        for (int j = 0; j < kTiles; ++j) {
-          const uint4 va = *reinterpret_cast<const uint4*>(&sm.sfa[stage][j * 512 + lane * 16]);
-          ra[4 * j] = va.x; ra[4 * j + 1] = va.y; ra[4 * j + 2] = va.z; ra[4 * j + 3] = va.w;
-          const uint4 v0 = *reinterpret_cast<const uint4*>(&sm.sfb[stage][j * 512 + lane * 16]);
-          const uint4 v1 = *reinterpret_cast<const uint4*>(&sm.sfb[stage][kTiles * 512 + j * 512 + lane * 16]);
-          rb[8 * j] = v0.x; rb[8 * j + 1] = v0.y; rb[8 * j + 2] = v0.z; rb[8 * j + 3] = v0.w;
-          rb[8 * j + 4] = v1.x; rb[8 * j + 5] = v1.y; rb[8 * j + 6] = v1.z; rb[8 * j + 7] = v1.w;
+        load_stage_scales<kTiles>(sm.sfa[stage], sm.sfb[stage], lane, ra, rb);
+        const uint32_t slot = gk % kPairSfSlots;
+        if (gk >= kPairSfSlots) {
+          const uint32_t pg = gk - kPairSfSlots;
+          if (!mbar_wait_timed(&sm.empty[pg % kPairStages], (pg / kPairStages) & 1u)) {
+            if (lane == 0) atomicExch(g.status, kStatusGemmMmaTimeout);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
         }
-#pragma unroll
-        for (int j = kTiles; j < 4; ++j) {
-          ra[4 * j] = ra[4 * j + 1] = ra[4 * j + 2] = ra[4 * j + 3] = 0;
-#pragma unroll
-          for (int e = 0; e < 8; ++e) rb[8 * j + e] = 0;
-        }
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + kPairSfBase + slot * kSfSlotCols;
         tmem_st16(taddr, ra);
         tmem_st32(taddr + 16, rb);
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
         // tell the leader: this CTA's operands have landed and this quadrant's scales are in place
-        if (lane == 0) mbar_arrive_cluster(map_to_cta(&sm.sf_ready[stage], 0));
+        if (lane == 0) mbar_arrive_cluster(slot ? sf_ready_leader1 : sf_ready_leader0);
         if (++stage == kPairStages) { stage = 0; phase ^= 1; }
       }
     }
@@ -253,38 +280,37 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     // ------------------------------ epilogue (both CTAs) -------------------------------------
     const int quad = warp & 3;
     uint32_t acc_phase = 0;
+    int kind = 0;
     float a_sg = g.fixed_scale;
     if (g.a_sg != nullptr) a_sg = __ldg(g.a_sg);
-    const uint32_t acc_empty_leader = map_to_cta(&sm.acc_empty, 0);
+    const uint32_t empty_shared_leader = map_to_cta(&sm.acc_empty_shared, 0);
+    const uint32_t empty_priv_leader0 = map_to_cta(&sm.acc_empty_priv[0], 0), empty_priv_leader1 = map_to_cta(&sm.acc_empty_priv[1], 0);
     bool ok = true;
-    for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+    for (int t = cluster_id; t < n_tiles && ok; t += n_clusters, kind ^= 1) {
       int tm, tn;
-        raster_tile(t, tiles_m, tiles_n, tm, tn);
+      raster_tile(t, tiles_m, tiles_n, tm, tn);
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;
         break;
       }
       tc_fence_after();
-      // this CTA's half of the accumulator is drained: tell the leader's MMA thread
-      auto release = [&]() {
+      const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
+      uint8_t* epi = &sm.epi[warp - 2][0][0];
+      const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
+      const int col0 = tn * kGemmBN;
+      // tensor-memory columns [128, 256) hold output columns [128, 256) of a tile at [0, 256) and output
+      // columns [0, 128) of a tile at [128, 384): lift them out first, the next tile needs them
+      epilogue_region<EPI, 128>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane, [&] {
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-      };
-      if constexpr (EPI == kEpiGeneral) {
-        epilogue_tile(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad, lane);
-        release();
-      } else if constexpr (EPI == kEpiSilu) {
-        epilogue_tile_bf16<true, true>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
-                                   lane, release);
-      } else if constexpr (EPI == kEpiRope) {
-        epilogue_tile_bf16<true, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
-                                   lane, release);
-      } else {
-        epilogue_tile_bf16<false, false>(g, tmap_d, tmem, &sm.epi[warp - 2][0][0], tm * 256 + (int)rank * 128, tn, a_sg, quad,
-                                   lane, release);
-      }
+        if (lane == 0) mbar_arrive_cluster(empty_shared_leader);
+      });
+      epilogue_region<EPI, 128>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane, [&] {
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(kind ? empty_priv_leader1 : empty_priv_leader0);
+      });
       acc_phase ^= 1;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

@@ -18,9 +18,13 @@ namespace fp4b200 {
 // ---------------------------------------------------------------------------------------
 
 // partials[blockIdx.x] = max|x| over this CTA's share (every CTA writes, so nothing needs clearing)
+// early_reads: the caller has promised that x was not written by the kernel launched just before this one (see
+// fp4b200_set_pdl_early_reads), so x may be read while that kernel still runs; otherwise nothing is read before
+// that kernel's writes are visible.
 __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, size_t n_vec,
-                                                        float* __restrict__ partials) {
+                                                        float* __restrict__ partials, int early_reads) {
   pdl_launch_dependents();   // a quantiser launched behind this kernel may set up and prefetch meanwhile
+  if (!early_reads) pdl_wait();
   uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
   const size_t stride = (size_t)gridDim.x * blockDim.x;
   size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -46,8 +50,8 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
   if (threadIdx.x < 32) {
     v = threadIdx.x < 8 ? warp_part[threadIdx.x] : 0.0f;
     v = warp_max(v);
-    // Launched behind a quantiser that lets its dependents start early, this kernel has only read x so far; that
-    // quantiser may still be reading the partial maxima of ITS input from the same scratch, so the write waits.
+    // Launched behind a quantiser that lets its dependents start early, this kernel may have only read x so far;
+    // that quantiser may still be reading the partial maxima of ITS input from the same scratch, so the write waits.
     pdl_wait();
     if (threadIdx.x == 0) partials[blockIdx.x] = v;
   }
@@ -173,7 +177,7 @@ template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_
 __global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                      float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
-                     int n_slots, int* __restrict__ status) {
+                     int n_slots, int* __restrict__ status, int early_reads) {
   extern __shared__ __align__(128) uint8_t stats_smem[];
   __shared__ int next_row;   // next unclaimed row of the band (band-relative)
   __shared__ float warp_max_s[kStatsMaxWarps];
@@ -205,17 +209,22 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     mbar_init(&bars[s], 1);
     uses[s] = 0;
     fence_mbar_init();
-    if (s < n_band) issue(s);
   }
+  // Launched as a programmatic dependent, this kernel may have started while the kernel before it still runs.  By
+  // default it reads nothing of the caller's before that kernel's writes are visible: x is usually what that kernel
+  // just produced.  With early_reads (the caller's promise that x and gamma were written earlier than that) the
+  // ring fills and gamma is staged meanwhile, and only the writes below wait.
+  if (!early_reads) pdl_wait();
+  for (int s = threadIdx.x; s < n_slots; s += blockDim.x)
+    if (s < n_band) issue(s);
   for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) {
     const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
     gamma_lo[q] = make_float4(bf16lo_to_f32(g.x), bf16hi_to_f32(g.x), bf16lo_to_f32(g.y), bf16hi_to_f32(g.y));
     gamma_hi[q] = make_float4(bf16lo_to_f32(g.z), bf16hi_to_f32(g.z), bf16lo_to_f32(g.w), bf16hi_to_f32(g.w));
   }
   __syncthreads();
-  // Launched behind a kernel that lets its dependents start early (the strip quantiser of the previous call), this
-  // kernel has by now staged gamma and filled its ring from x, neither of which that kernel writes; inv_rms and the
-  // partial maxima may still be read by it, so nothing is written (and a caller's inv_rms not read) before it ends.
+  // inv_rms and the partial maxima may still be read by the strip quantiser of the previous call, so nothing is
+  // written (and a caller's inv_rms not read) before that kernel has ended.
   pdl_wait();
 
   float mx = 0.0f;
@@ -1315,6 +1324,15 @@ static bool stats_pdl_enabled() {
   return on;
 }
 
+// Whether the pass-1 kernels may read their input before the previous kernel on the stream has ended: off unless
+// the caller promises (fp4b200_set_pdl_early_reads, or FP4B200_PDL_EARLY_READS=1) that no input of a call is
+// written by the kernel launched immediately before it.
+static int g_pdl_early_reads = [] {
+  const char* e = getenv("FP4B200_PDL_EARLY_READS");
+  return (e != nullptr && e[0] == '1') ? 1 : 0;
+}();
+static int pdl_early_reads() { return g_pdl_early_reads; }
+
 // Reduction of the per-CTA maxima into amax_sg[0..1], launched behind the kernel that produced them.
 static int launch_reduce_partials(const float* partials, int n, float* amax_sg, cudaStream_t st) {
   PdlLaunch l(dim3(1), dim3(256), 0, st, true);
@@ -1330,7 +1348,8 @@ int launch_amax(const void* x, int64_t n_elems, float* amax_sg, cudaStream_t st,
   int grid = (int)std::min<size_t>((n_vec + 255) / 256, std::min<size_t>((size_t)device_sm_count() * 8, kScratchFloats));
   grid = std::max(grid, 1);   // an empty input still leaves one partial (0)
   PdlLaunch l(dim3((unsigned)grid), dim3(256), 0, st, stats_pdl_enabled());
-  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, amax_bf16_kernel, reinterpret_cast<const uint4*>(x), n_vec, scratch));
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, amax_bf16_kernel, reinterpret_cast<const uint4*>(x), n_vec, scratch,
+                                    pdl_early_reads()));
   if (partials_out != nullptr) {
     partials_out->ptr = scratch;
     partials_out->count = grid;
@@ -1507,7 +1526,8 @@ static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, floa
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
   const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
   PdlLaunch l(dim3((unsigned)grid), dim3((unsigned)warps * 32), smem, st, stats_pdl_enabled());
-  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, xb, gb, inv_rms, partials, eps, (int)M, (int)K, slots, status));
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, xb, gb, inv_rms, partials, eps, (int)M, (int)K, slots, status,
+                                    pdl_early_reads()));
   *grid_out = grid;
   return 0;
 }
@@ -1568,6 +1588,12 @@ static int check_quant_shapes(const void* x, int64_t M, int64_t K, const char* w
 }
 
 extern "C" {
+
+int fp4b200_set_pdl_early_reads(int enabled) {
+  const int before = g_pdl_early_reads;
+  g_pdl_early_reads = enabled != 0;
+  return before;
+}
 
 int fp4b200_nvfp4_amax(const void* x_bf16, int64_t n_elems, float* amax_sg, void* stream) {
   if (x_bf16 == nullptr || amax_sg == nullptr) return set_error("nvfp4_amax: null pointer");

@@ -48,6 +48,18 @@ def _stream(t):
     return torch.cuda.current_stream(t.device).cuda_stream
 
 
+class _NoPdl:
+    """The GEMM launches inside the block are ordinary launches, not programmatic dependents (the reference's
+    ``*_nopdl`` entry points, nvfp4_b200_gemm.cu:1702-1735); the calling thread's setting is restored afterwards."""
+
+    def __enter__(self):
+        self._before = _lib.load().fp4b200_set_gemm_pdl(0)
+
+    def __exit__(self, *exc):
+        _lib.load().fp4b200_set_gemm_pdl(self._before)
+        return False
+
+
 def _gemm(A, A_sc, A_sg, B, B_sc, B_sg, D, residual=None):
     for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
         _chk_operand(t, n)
@@ -77,11 +89,13 @@ def nvfp4_gemm_config(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D, config_id):
 
 
 def nvfp4_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D):
-    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
+    with _NoPdl():
+        _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
 
 
 def nvfp4_gemm_config_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D, config_id):
-    _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
+    with _NoPdl():
+        _gemm(A, A_sc, A_sc_global, B, B_sc, B_sc_global, D)
 
 
 def nvfp4_gemm_residual(A, A_sc, A_sc_global, B, B_sc, B_sc_global, R, D):
@@ -119,7 +133,8 @@ def nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt=
 
 def nvfp4_grouped_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt=None, D_V_opt=None,
                              silu_dim=0):
-    nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt, D_V_opt, silu_dim)
+    with _NoPdl():
+        nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt, D_V_opt, silu_dim)
 
 
 def _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, outs, rope_cs, seq_len, head_dim, rope_cols,

@@ -67,7 +67,7 @@ def test_entry_points_validate_before_touching_the_device(pkg):
     assert "segment 1" in msg()
     widths = (ctypes.c_int64 * 2)(512, 768)     # runs past the 1024 columns of A
     assert lib.fp4b200_mxfp4_gemm_ksplit(p, 1024, 2, offs, widths, ptrs, ptrs, ptrs, p, 0, 128, 256, None) == -1
-    assert lib.fp4b200_nvfp4_gemm(p, p, p, p, p, p, p, 0, None, 128, 200, 256, None) == -1 and "N % 256" in msg()
+    assert lib.fp4b200_nvfp4_gemm(p, p, p, p, p, p, p, 0, None, 128, 200, 256, None) == -1 and "N % 128" in msg()
     # RMSNorm backward: shape limits, then aliasing of outputs with inputs
     assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 4, 384, None) == -1 and "multiple of 256" in msg()
     assert lib.fp4b200_sum3_rmsnorm_bwd(p, p, p, p, p, p, p, p, p, p, 0, 4, 16384, None) == -1 and "8192" in msg()

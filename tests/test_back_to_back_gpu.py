@@ -15,8 +15,18 @@ from tests.gpu_util import assert_status_ok, to_dev_bf16
 pytestmark = pytest.mark.gpu
 
 
+@pytest.fixture
+def early_reads(request):
+    """Sets the library's early-reads switch for one test and restores it."""
+    lib = importlib.import_module("mfu-fp4-training_b200._lib").load()
+    before = lib.fp4b200_set_pdl_early_reads(int(request.param))
+    yield bool(request.param)
+    lib.fp4b200_set_pdl_early_reads(before)
+
+
+@pytest.mark.parametrize("early_reads", [0, 1], indirect=True)
 @pytest.mark.parametrize("shape", [(16384, 4096), (2048, 1024)])
-def test_back_to_back_calls_sharing_inv_rms_do_not_disturb_each_other(shape):
+def test_back_to_back_calls_sharing_inv_rms_do_not_disturb_each_other(shape, early_reads):
     lib = importlib.import_module("mfu-fp4-training_b200._lib")
     M, K = shape
     dev = torch.device("cuda")
@@ -52,4 +62,58 @@ def test_back_to_back_calls_sharing_inv_rms_do_not_disturb_each_other(shape):
         ref = o.nvfp4_quantize_for_gemm(o.rmsnorm_apply(x, inv_rms.cpu().numpy(), gamma.float().cpu().numpy()), True, True)
         assert np.array_equal(outs[1][0].cpu().numpy(), ref["row_fp4"]) and np.array_equal(outs[1][2].cpu().numpy(), ref["col_fp4"])
         assert np.abs(inv_rms.cpu().numpy() / inv - 1).max() < 2e-6
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("shape", [(16384, 4096), (512, 1024)])
+def test_input_rewritten_by_the_previous_kernel_is_read_after_it(shape):
+    """The usual call pattern of a training step: the kernel launched just before the producer (here a torch copy,
+    in a model the residual add or a GEMM epilogue) writes the very buffer the producer reads.  The first-pass
+    kernels are programmatic dependents, so they must not read x or gamma before that kernel's writes are visible
+    (the library's default).  Every call is compared with the same call made alone on settled memory; both the fused
+    RMSNorm producer and the plain quantiser (tensor-maximum kernel in front) are covered."""
+    lib = importlib.import_module("mfu-fp4-training_b200._lib")
+    M, K = shape
+    dev = torch.device("cuda")
+    g = torch.Generator(device="cuda").manual_seed(11)
+    srcs = [(torch.randn((M, K), generator=g, device=dev) * s).to(torch.bfloat16) for s in (1.0, 5.0, 0.25)]
+    gammas = [to_dev_bf16(o.make_gamma(K, seed=s)) for s in (3, 4, 5)]
+    x = torch.empty((M, K), dtype=torch.bfloat16, device=dev)        # the one buffer every call reads
+    gamma = torch.empty(K, dtype=torch.bfloat16, device=dev)
+    inv_rms = torch.empty(M, dtype=torch.float32, device=dev)
+    amax_sg = torch.empty(2, dtype=torch.float32, device=dev)
+    u8 = dict(dtype=torch.uint8, device=dev)
+    stream = torch.cuda.current_stream().cuda_stream
+
+    def outs():
+        return (torch.empty((M, K // 2), **u8), torch.empty((M // 128, K // 64, 512), **u8),
+                torch.empty((K, M // 2), **u8), torch.empty((K // 128, M // 64, 512), **u8))
+
+    def fused(o4):
+        lib.call("fp4b200_nvfp4_fused_norm_quantize", x.data_ptr(), gamma.data_ptr(), 1e-5, M, K, inv_rms.data_ptr(), 1, 1,
+                 o4[0].data_ptr(), o4[1].data_ptr(), o4[2].data_ptr(), o4[3].data_ptr(), amax_sg.data_ptr(), stream)
+
+    def plain(o4):
+        lib.call("fp4b200_nvfp4_quantize_for_gemm", x.data_ptr(), M, K, 1, 1, o4[0].data_ptr(), o4[1].data_ptr(),
+                 o4[2].data_ptr(), o4[3].data_ptr(), amax_sg.data_ptr(), stream)
+
+    for call in (fused, plain):
+        n_calls = 9
+        got = [outs() for _ in range(n_calls)]
+        torch.cuda.synchronize()
+        for i in range(n_calls):
+            x.copy_(srcs[i % 3])            # the kernel right in front of the producer writes its input ...
+            gamma.copy_(gammas[i % 3])      # ... and its weight
+            call(got[i])
+        torch.cuda.synchronize()
+        for k in range(3):
+            x.copy_(srcs[k])
+            gamma.copy_(gammas[k])
+            torch.cuda.synchronize()
+            alone = outs()
+            call(alone)
+            torch.cuda.synchronize()
+            for i in range(k, n_calls, 3):
+                for a, b in zip(got[i], alone):
+                    assert torch.equal(a, b), f"{call.__name__}: call {i} read its input before the copy in front of it had landed"
     assert_status_ok()

@@ -51,7 +51,9 @@ def test_mxfp4_fused_rmsnorm_and_silu():
     assert_status_ok()
 
 
-@pytest.mark.parametrize("shape", [(128, 256, 256), (256, 512, 1024), (512, 768, 2304)])
+# K = 384, 1152: an odd multiple of 128 (half-depth last K stage); N = 384: half-empty last column tile
+@pytest.mark.parametrize("shape", [(128, 256, 256), (256, 512, 1024), (512, 768, 2304), (256, 384, 384), (128, 256, 1152),
+                                   (2048, 4096, 640)])
 def test_mxfp4_gemm(shape):
     mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
     M, N, K = shape

@@ -29,8 +29,12 @@ def _oracle_product(qx, qw, M, N, K):
     return o.nvfp4_gemm_fp32(u8(qx[0]), a_sc, qx[4].item(), u8(qw[0]), b_sc, qw[4].item())
 
 
+# (256, 384, 512) and (128, 128, 256): N an odd multiple of 128 (half-empty last column tile) on both kernels;
+# (2048, 9472, 512) and (4096, 4096, 256): several tiles per CTA pair, so that the accumulator alternates between its
+# two tensor-memory positions and, with one K stage per tile, the epilogue is what the MMA thread waits for
 @pytest.mark.parametrize("shape", [(128, 256, 256), (128, 256, 1024), (256, 512, 512), (384, 768, 2304),
-                                   (1024, 1024, 4096)])
+                                   (1024, 1024, 4096), (256, 384, 512), (128, 128, 256), (2048, 9472, 512),
+                                   (4096, 4096, 256)])
 def test_nvfp4_gemm_fp32_and_bf16(shape):
     gemm = mod("tk_gemm_c")
     M, N, K = shape

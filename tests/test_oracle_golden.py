@@ -1,5 +1,7 @@
 """CPU: the oracle against the golden vectors produced by the reference's own CPU emulation
 (tests/golden/make_golden.py), plus internal consistency of the oracle."""
+import os
+
 import numpy as np
 import pytest
 
@@ -264,3 +266,36 @@ def test_hadamard_transform_and_forward_rmsnorm_vs_the_reference():
     gamma = o.bf16_from_bits(g["gamma_bits"])
     assert np.abs(o.rmsnorm_inv_rms(x, 1e-5) / g["inv_rms"] - 1).max() <= 2.5e-7
     assert np.array_equal(o.rmsnorm_apply(x, g["inv_rms"], gamma), o.bf16_from_bits(g["normed_bits"]))
+
+
+def _sr_cases():
+    from tests.golden import make_sr_golden as G
+    return G
+
+
+@pytest.mark.parametrize("idx", range(16))
+def test_oracle_stochastic_and_hadamard_quantiser_vs_the_references_own_kernels(idx):
+    """The numpy oracle against bytes recorded from the reference's compiled sm_100a kernels
+    (tests/golden/nvfp4_sr_reference_golden.npz): the Philox draw order, the model of the stochastic conversion
+    instructions, the sign hash and the launch numbering are pinned by the reference itself, not by a reading of it."""
+    G = _sr_cases()
+    name, shape, kind, kw = G.CASES[idx]
+    if "target" in kw:
+        pytest.skip("the oracle's opt quantiser has no tensor-scale target argument; the CUDA path is held to this case")
+    if name.endswith("zero_blocks"):
+        pytest.skip("all-zero encode-centric blocks under scale SR shift the reference thread's later draws: see the GPU test")
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "nvfp4_sr_reference_golden.npz"))
+    x = G.make_input(kind, shape, 100 + idx)
+    ref, used = o.nvfp4_quantize_for_gemm_opt(x, kw["return_transpose"], kw["encode_centric"], kw["data_sr"], kw["rht"], kw["sign"],
+                                              G.SEED, G.SUBSEQ, kw["sr_axes"], invocation=int(gold[f"{name}.first_launch"]),
+                                              scale_sr=kw["scale_sr"])
+    assert used == int(gold[f"{name}.launches"])
+    M, K = shape
+    assert np.array_equal(ref["row_fp4"], gold[f"{name}.row_fp4"])
+    assert np.array_equal(o.swizzle_scales(ref["row_sc_logical"]).reshape(-1), gold[f"{name}.row_sc"]) if "row_sc_logical" in ref \
+        else np.array_equal(np.asarray(ref["row_sc"]).reshape(-1), gold[f"{name}.row_sc"])
+    if kw["return_transpose"]:
+        assert np.array_equal(ref["col_fp4"], gold[f"{name}.col_fp4"])
+        assert np.array_equal(np.asarray(ref["col_sc"]).reshape(-1), gold[f"{name}.col_sc"]) if "col_sc" in ref \
+            else np.array_equal(o.swizzle_scales(ref["col_sc_logical"]).reshape(-1), gold[f"{name}.col_sc"])
+    assert np.float32(ref["row_sg"]) == gold[f"{name}.sg_row"][0] and np.float32(ref["col_sg"]) == gold[f"{name}.sg_col"][0]
