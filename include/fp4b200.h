@@ -77,14 +77,16 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
  * every block is rounded stochastically by one more word of the same stream, drawn before the block's data
  * words (quantize_transpose_tuned.cuh:205-254); with data_sr 2 / 3 the row pass follows the row-only launch
  * at rng_offset and the column pass the column launch at rng_offset_col, as above.  The reference draws no
- * scale word for an encode-centric block whose maximum is <= 1e-9; here every block draws one, so streams
- * differ from the reference's behind such a block of the same 128x128 chunk.  scale_sr needs 16-byte
+ * scale word for an encode-centric block whose maximum is <= 1e-9 (quantize_transpose_tuned.cuh:244-254), which
+ * moves every later draw of the reference thread that owns the block: with ec_zero_scratch (device memory,
+ * M*K/32 bytes, 2-byte aligned; used only when encode_centric and scale_sr) a first kernel maps those blocks and
+ * the draws follow the reference's; with NULL every block is taken to draw a scale word.  scale_sr needs 16-byte
  * aligned outputs. */
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
-                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream);
+                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* ec_zero_scratch, void* stream);
 
 /* As fp4b200_nvfp4_quantize_opt, with the row-wise codes written into a column slice of a wider matrix:
  * row_pitch_bytes is that matrix's row pitch (0: K/2, a dense [M, K/2]); 16-byte aligned outputs only.  Serves the
@@ -95,7 +97,7 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
                                     int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                     int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
                                     int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
-                                    void* col_sc, void* stream);
+                                    void* col_sc, void* ec_zero_scratch, void* stream);
 
 /* Tensor amax (and sg) of the per-16 Hadamard transform of x along K (along_k != 0) or along M,
  * measured on the fp32 transform output: rht16_bf16_amax_kernel (tk_quantize.cu:574-664).  gamma/inv_rms

@@ -54,6 +54,9 @@ struct QuantOpt {
   int return_row;            // 0: skip the row-wise outputs but keep their place in the random stream
   unsigned long long rng_seed, rng_offset, rng_offset_col;   // column pass may take its own counter offset
   unsigned long long sign_seed, sign_subseq;
+  // encode-centric scale_sr: 2 * (M/128) * (K/128) * 128 uint16 of device scratch for the map of blocks that draw no
+  // scale word (null: every block is taken to draw one)
+  void* ec_zero_scratch;
 };
 
 // Launchers defined in quant_nvfp4.cu and shared with the other producers.

@@ -426,6 +426,11 @@ struct QuantArgs {
   int opt_return_row;      // 0: row-wise outputs are not written (their random words are still skipped)
   unsigned long long rng_seed, rng_offset, rng_offset_col;   // Philox key, counter offset of the row pass / column pass
   unsigned long long sign_seed, sign_subseq;   // sign-mask hash inputs
+  // Encode-centric scale SR only: per (128x128 chunk, reference thread) the blocks that draw no scale word, bit p =
+  // the block at position p of that thread's order in the row pass's stream / in the column pass's stream
+  // (ec_zero_block_mask_kernel); null: every block is taken to draw one.
+  const uint16_t* ec_zero_row_stream;
+  const uint16_t* ec_zero_col_stream;
 };
 
 template <bool ENCODE_CENTRIC>
@@ -868,6 +873,61 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
 // CTA-synchronous kernel above, so neighbouring pieces of the outputs are written within a few
 // microseconds of each other.  Warps drift freely: nothing waits at a barrier.
 
+// Which 16-element blocks of x draw no scale word under encode-centric scale stochastic rounding: the reference
+// stores the largest multiplier for a block whose maximum is <= 1e-9 before it would have drawn
+// (quantize_transpose_tuned.cuh:244-254), and since a thread of its tuned kernel draws its words one after another,
+// every later draw of that thread inside the 128x128 chunk moves up by one.  One CTA per chunk, one thread per
+// reference thread t: its row blocks are rows 64*sy + (t >> 2) + 32*it, columns 16*(4*sx + (t & 3)) .. +15 of stage
+// (sy, sx), its column blocks rows 64*sy + 16*g .. +15 of column 64*sx + 2*(t & 31) + wq with
+// g = ((t >> 5) + (t & 3)) & 3.  Bit p of a mask = the block at position p of the thread's order in that stream:
+// stage * sb + it for row blocks (sb = blocks per stage of the stream: 2 in a row-only launch, else 4) and
+// stage * 4 + 2 + wq for column blocks.  The maxima are those of the raw input (exact for the plain quantiser; with a
+// Hadamard transform or RMSNorm in front a block is taken to be zero when its input is).
+__global__ void __launch_bounds__(128)
+ec_zero_block_mask_kernel(const __nv_bfloat16* __restrict__ x, int K, int chunks_k, int sb_row_stream,
+                          int rows_in_row_stream, int cols_in_row_stream, int rows_in_col_stream,
+                          uint16_t* __restrict__ mask_row_stream, uint16_t* __restrict__ mask_col_stream) {
+  const int chunk = blockIdx.x, t = threadIdx.x;
+  const int cm = chunk / chunks_k, ck = chunk - cm * chunks_k;
+  const __nv_bfloat16* base = x + (size_t)cm * 128 * K + (size_t)ck * 128;
+  uint32_t zr = 0, zc = 0;   // bit stage*2 + it / stage*2 + wq
+#pragma unroll
+  for (int stage = 0; stage < 4; ++stage) {
+    const int sy = stage >> 1, sx = stage & 1;
+#pragma unroll
+    for (int it = 0; it < 2; ++it) {
+      const uint4* p = reinterpret_cast<const uint4*>(base + (size_t)(64 * sy + (t >> 2) + 32 * it) * K + 16 * (4 * sx + (t & 3)));
+      const uint4 a = __ldg(p), b = __ldg(p + 1);
+      uint32_t m = bf16x2_absmax(bf16x2_absmax(bf16x2_absmax(0u, a.x), a.y), bf16x2_absmax(bf16x2_absmax(0u, a.z), a.w));
+      m = bf16x2_absmax(m, bf16x2_absmax(bf16x2_absmax(bf16x2_absmax(0u, b.x), b.y), bf16x2_absmax(bf16x2_absmax(0u, b.z), b.w)));
+      if (bf16x2_hmax_to_f32(m) <= 1.0e-9f) zr |= 1u << (stage * 2 + it);
+    }
+    const int g = ((t >> 5) + (t & 3)) & 3;
+#pragma unroll
+    for (int wq = 0; wq < 2; ++wq) {
+      const __nv_bfloat16* p = base + (size_t)(64 * sy + 16 * g) * K + 64 * sx + 2 * (t & 31) + wq;
+      float m = 0.0f;
+#pragma unroll
+      for (int r = 0; r < 16; ++r) m = fmaxf(m, fabsf(__bfloat162float(p[(size_t)r * K])));
+      if (m <= 1.0e-9f) zc |= 1u << (stage * 2 + wq);
+    }
+  }
+  uint32_t mr = 0, mc = 0;
+#pragma unroll
+  for (int stage = 0; stage < 4; ++stage) {
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const uint32_t r = (zr >> (stage * 2 + i)) & 1u, c = (zc >> (stage * 2 + i)) & 1u;
+      if (rows_in_row_stream) mr |= r << (stage * sb_row_stream + i);
+      if (cols_in_row_stream) mr |= c << (stage * 4 + 2 + i);
+      if (rows_in_col_stream) mc |= r << (stage * 4 + i);
+      mc |= c << (stage * 4 + 2 + i);
+    }
+  }
+  mask_row_stream[(size_t)chunk * 128 + t] = (uint16_t)mr;
+  mask_col_stream[(size_t)chunk * 128 + t] = (uint16_t)mc;
+}
+
 constexpr int kStripRows = 32;
 constexpr int kStripCols = 64;
 constexpr int kStripBytes = kStripRows * kStripCols * 2;
@@ -1077,13 +1137,21 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
               const int bg = (tid_ref & 31) >> 4;
               if constexpr (kScaleSr) {
-                // q words per block (scale first, then the data words); the stage holds 2 (row-only launch) or 4 blocks
+                // q words per block (scale first, then the data words); the stage holds 2 (row-only launch) or 4 blocks.
+                // Earlier blocks of the reference thread that drew no scale word move this block's draws up; a block
+                // that draws none itself takes its data words from its first draw on.
                 const int q = 1 + (a.opt_sr_row ? 4 : 0);
+                const int pos = stage * (a.opt_row_per_stage >> 2) + it_ref;
+                uint32_t zm = 0;
+                if (ENCODE_CENTRIC && a.ec_zero_row_stream != nullptr) zm = __ldg(a.ec_zero_row_stream + seq);
+                const bool own_zero = (zm >> pos) & 1u;
                 uint32_t dr[5];
-                philox_draws(a.rng_seed, seq, a.rng_offset, stage * (a.opt_row_per_stage >> 2) * q + it_ref * q, q, dr);
+                philox_draws(a.rng_seed, seq, a.rng_offset, pos * q - __popc(zm & ((1u << pos) - 1u)), q, dr);
                 scale_rbits = dr[0];
+                const uint32_t d0 = own_zero ? dr[0] : dr[1], d1 = own_zero ? dr[1] : dr[2], d2 = own_zero ? dr[2] : dr[3],
+                               d3 = own_zero ? dr[3] : dr[4];
 #pragma unroll
-                for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bg) & 1) ? dr[3 + (g & 1)] : dr[1 + (g & 1)];
+                for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bg) & 1) ? ((g & 1) ? d3 : d2) : ((g & 1) ? d1 : d0);
               } else {
                 const uint4 rw = philox4x32_10(a.rng_seed, seq,
                                                a.rng_offset + (unsigned long long)((stage * a.opt_row_per_stage + it_ref * 4) >> 2));
@@ -1158,10 +1226,15 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
               if constexpr (kScaleSr) {
                 // the stage's two row blocks (drawn or skipped over by the launch this pass belongs to), then its two column blocks
                 const int q = 1 + (a.opt_sr_col ? 4 : 0);
+                const int pos = stage * 4 + 2 + wq;
+                uint32_t zm = 0;
+                if (ENCODE_CENTRIC && a.ec_zero_col_stream != nullptr) zm = __ldg(a.ec_zero_col_stream + seq);
+                const bool own_zero = (zm >> pos) & 1u;
                 uint32_t dr[5];
-                philox_draws(a.rng_seed, seq, a.rng_offset_col, stage * 4 * q + 2 * q + wq * q, q, dr);
+                philox_draws(a.rng_seed, seq, a.rng_offset_col, pos * q - __popc(zm & ((1u << pos) - 1u)), q, dr);
                 scale_rbits = dr[0];
-                wsel[0] = dr[1]; wsel[1] = dr[2]; wsel[2] = dr[3]; wsel[3] = dr[4];
+                wsel[0] = own_zero ? dr[0] : dr[1]; wsel[1] = own_zero ? dr[1] : dr[2];
+                wsel[2] = own_zero ? dr[2] : dr[3]; wsel[3] = own_zero ? dr[3] : dr[4];
               } else {
                 const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
                 wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
@@ -1483,6 +1556,20 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
     a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
     if (strip_kernel_applies(a, norm)) {
+      if (a.opt_scale_sr && encode_centric && opt->ec_zero_scratch != nullptr) {
+        // which blocks draw no scale word, per stream: one launch of the reference (both passes in one stream), or,
+        // when one axis only rounds its codes stochastically, its row-only launch and its column launch
+        const bool split = opt->row_per_stage == 8 && col_fp4 != nullptr;
+        const int n_chunks = a.chunks_m * a.chunks_k;
+        uint16_t* masks = reinterpret_cast<uint16_t*>(opt->ec_zero_scratch);
+        ec_zero_block_mask_kernel<<<n_chunks, 128, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x), (int)K, a.chunks_k,
+                                                           a.opt_row_per_stage >> 2, opt->return_row != 0,
+                                                           col_fp4 != nullptr && !split, !split && opt->return_row != 0,
+                                                           masks, masks + (size_t)n_chunks * 128);
+        FP4_CUDA_CHECK(cudaGetLastError());
+        a.ec_zero_row_stream = masks;
+        a.ec_zero_col_stream = masks + (size_t)n_chunks * 128;
+      }
       if (a.opt_scale_sr) {
         if (encode_centric) return norm ? launch_quantize_strip_t<true, true, 2>(x, a, st, behind_pass1)
                                         : launch_quantize_strip_t<true, false, 2>(x, a, st, behind_pass1);
@@ -1692,16 +1779,16 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
                                     int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                     int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
                                     int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
-                                    void* col_sc, void* stream);
+                                    void* col_sc, void* ec_zero_scratch, void* stream);
 
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
-                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* ec_zero_scratch, void* stream) {
   return fp4b200_nvfp4_quantize_opt_into(x_bf16, gamma_bf16, inv_rms, M, K, amax_row, amax_col, encode_centric, data_sr, rht_row,
                                          rht_col, with_sign, sign_seed, sign_subseq, return_row, rng_seed, rng_offset,
-                                         rng_offset_col, scale_sr, row_fp4, 0, row_sc, col_fp4, col_sc, stream);
+                                         rng_offset_col, scale_sr, row_fp4, 0, row_sc, col_fp4, col_sc, ec_zero_scratch, stream);
 }
 
 int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
@@ -1709,8 +1796,9 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
                                     int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                     int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
                                     int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
-                                    void* col_sc, void* stream) {
+                                    void* col_sc, void* ec_zero_scratch, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_quantize_opt")) return rc;
+  if (reinterpret_cast<uintptr_t>(ec_zero_scratch) & 1) return set_error("nvfp4_quantize_opt: ec_zero_scratch must be 2-byte aligned");
   if (row_pitch_bytes != 0 && (row_pitch_bytes < K / 2 || (row_pitch_bytes % 16) != 0 || row_pitch_bytes > INT32_MAX))
     return set_error("nvfp4_quantize_opt: the row pitch must be 0 or a multiple of 16 bytes and at least K/2 (got %lld)",
                      (long long)row_pitch_bytes);
@@ -1731,6 +1819,7 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
   o.rht_row = rht_row != 0; o.rht_col = rht_col != 0; o.sign = with_sign != 0;
   o.return_row = return_row != 0; o.rng_seed = rng_seed; o.rng_offset = rng_offset;
   o.sign_seed = sign_seed; o.sign_subseq = sign_subseq;
+  o.ec_zero_scratch = ec_zero_scratch;
   return launch_quantize(x_bf16, M, K, amax_row, amax_col, encode_centric != 0, inv_rms, gamma_bf16, row_fp4, row_sc,
                          col_fp4, col_sc, nullptr, false, (cudaStream_t)stream, false, &o, nullptr, nullptr, 0, 0,
                          row_pitch_bytes);

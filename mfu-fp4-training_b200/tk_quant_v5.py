@@ -138,7 +138,7 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
                           amax_sg[g].data_ptr(), 1, 1, 0, 0, 0, 0, 0, 1, int(rng_seed) & _U64,
                           _next_offset(input0, rng_subsequence, True), 0, 0, fp4_row_full.data_ptr() + off // 2,
                           n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2),
-                          sc_col[g].data_ptr(), _stream(input0))
+                          sc_col[g].data_ptr(), None, _stream(input0))
             else:
                 _lib.call("fp4b200_nvfp4_quantize_for_gemm_into", x.data_ptr(), M, n, 1, 1,
                           fp4_row_full.data_ptr() + off // 2, n_total // 2, sc_row[g].data_ptr(),
@@ -482,12 +482,15 @@ def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row
     row_sc = torch.empty((M // 128, K // 64, 512), **u8) if return_row else None
     col_fp4 = torch.empty((K, M // 2), **u8) if return_transpose else None
     col_sc = torch.empty((K // 128, M // 64, 512), **u8) if return_transpose else None
+    # encode-centric scale SR: scratch for the map of blocks that draw no scale word (the reference thread's later
+    # draws move up behind such a block, quantize_transpose_tuned.cuh:244-254)
+    zero_map = torch.empty(M * K // 32, **u8) if (scale_sr and encode_centric) else None
     _lib.call("fp4b200_nvfp4_quantize_opt", x.data_ptr(), _p(gamma), _p(inv_rms), M, K, amax_row.data_ptr(),
               amax_col.data_ptr(), int(bool(encode_centric)), int(bool(sr)) if sr_mode is None else int(sr_mode),
               int(bool(row_rht)), int(bool(col_rht)),
               int(bool(sign)), int(sign_seed) & _U64, int(sign_subseq) & _U64, int(bool(return_row)),
               int(seed) & _U64, int(offset) & _U64, int(offset_col) & _U64, int(bool(scale_sr)), _p(row_fp4), _p(row_sc),
-              _p(col_fp4), _p(col_sc), _stream(x))
+              _p(col_fp4), _p(col_sc), _p(zero_map), _stream(x))
     return row_fp4, row_sc, col_fp4, col_sc
 
 

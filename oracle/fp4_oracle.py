@@ -1107,12 +1107,10 @@ def _sr_words_col(M, K, seed, offset):
     return words.reshape(K, M // 4)
 
 
-def _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks):
-    """The q consecutive random words every 16-element block draws when blocks draw q words each (scale word first,
-    then four data words): draw n of a thread's stream is component n & 3 of the Philox block at counter
-    offset + (n >> 2) (core.cuh:116-127).  A 64x64 stage holds ``stage_blocks`` blocks per thread before the next stage
-    starts (2 row blocks, + 2 column blocks when the launch has a column pass).  Returns uint32 [rows, blocks, q] for the
-    row operand [M, K/16] or the column operand [K, M/16]."""
+def _sr_block_positions(M, K, column_pass, stage_blocks):
+    """Where the reference's tuned kernel handles each 16-element block: (chunk row, chunk column, thread, position in
+    that thread's order of blocks) — a 64x64 stage holds ``stage_blocks`` blocks per thread (2 row blocks, + 2 column
+    blocks when the launch has a column pass); quantize_transpose_tuned.cuh:392-528, 600-830."""
     if column_pass:
         k = np.arange(K)[:, None]; m = np.arange(M // 16)[None, :] * 16
         cy, cx, r, c = m // 128, k // 128, m % 128, k % 128
@@ -1120,28 +1118,64 @@ def _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks):
         lr, lc = r % 64, c % 64
         lane, wq = lc // 2, lc % 2
         tid = (((lr // 16) - lane % 4) & 3) * 32 + lane
-        n0 = stage * 4 * q + 2 * q + wq * q
+        pos = stage * 4 + 2 + wq
     else:
         m = np.arange(M)[:, None]; k = np.arange(K // 16)[None, :] * 16
         cy, cx, r, c = m // 128, k // 128, m % 128, k % 128
         stage = (r // 64) * 2 + c // 64
         lr, lc = r % 64, c % 64
         tid = (lr % 32) * 4 + lc // 16
-        n0 = stage * stage_blocks * q + (lr // 32) * q
+        pos = stage * stage_blocks + lr // 32
+    shape = np.broadcast(cy, cx).shape
+    return tuple(np.broadcast_to(a, shape) for a in (cy, cx, tid, pos))
+
+
+def _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks, skipped=None, own_zero=None):
+    """The random words every 16-element block draws when blocks draw q words each (scale word first, then four data
+    words): draw n of a thread's stream is component n & 3 of the Philox block at counter offset + (n >> 2)
+    (core.cuh:116-127), and a block at position p of its thread starts at n = p * q - skipped, where ``skipped`` counts
+    the earlier blocks of that thread that drew no scale word.  A block that draws no scale word itself (``own_zero``)
+    takes its data words one draw earlier.  Returns uint32 [rows, blocks, q] (component 0 = scale word, unused when
+    own_zero) for the row operand [M, K/16] or the column operand [K, M/16], and the thread index."""
+    cy, cx, tid, pos = _sr_block_positions(M, K, column_pass, stage_blocks)
     seq = (tid + 128 * cx + 128 * (K // 128) * cy).astype(np.uint64)
-    n0 = np.broadcast_to(n0, seq.shape)
+    n0 = pos * q
+    if skipped is not None:
+        n0 = n0 - skipped
     out = np.empty(seq.shape + (q,), dtype=np.uint32)
     for j in range(q):
         n = n0 + j
+        if own_zero is not None and j >= 1:
+            n = n - own_zero.astype(n.dtype)
         blk = philox4x32_10(seed, seq, np.uint64(offset) + (n >> 2).astype(np.uint64))
         out[..., j] = np.take_along_axis(blk, (n & 3)[..., None], axis=-1)[..., 0]
     return out, tid
 
 
-def _scale_sr_words(M, K, seed, offset, column_pass, data_sr, stage_blocks):
+def _zero_block_skips(M, K, zero_row, zero_col, stage_blocks):
+    """For every row block [M, K/16] and column block [K, M/16]: how many earlier blocks of the same reference thread
+    drew no scale word (all-zero encode-centric blocks, compute_encoding_scaling_factor_nv_maybe_sr returns before
+    its draw, quantize_transpose_tuned.cuh:244-254).  zero_row / zero_col: the blocks' flags, None for a pass the
+    launch does not have or that advances the stream without looking at the data."""
+    table = np.zeros((M // 128, K // 128, 128, 16), dtype=np.int64)
+    if zero_row is not None:
+        cy, cx, tid, pos = _sr_block_positions(M, K, False, stage_blocks)
+        table[cy, cx, tid, pos] = zero_row
+    if zero_col is not None:
+        cy, cx, tid, pos = _sr_block_positions(M, K, True, stage_blocks)
+        table[cy, cx, tid, pos] = zero_col
+    before = np.cumsum(table, axis=-1) - table
+    cy, cx, tid, pos = _sr_block_positions(M, K, False, stage_blocks)
+    skip_row = before[cy, cx, tid, pos]
+    cy, cx, tid, pos = _sr_block_positions(M, K, True, stage_blocks)
+    skip_col = before[cy, cx, tid, pos]
+    return skip_row, skip_col
+
+
+def _scale_sr_words(M, K, seed, offset, column_pass, data_sr, stage_blocks, skipped=None, own_zero=None):
     """(scale word per block, data words per 4-element group or None) of a pass with scale stochastic rounding."""
     q = 1 + (4 if data_sr else 0)
-    d, tid = _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks)
+    d, tid = _sr_block_draws(M, K, seed, offset, column_pass, q, stage_blocks, skipped, own_zero)
     scale = d[..., 0]
     if not data_sr:
         return scale, None
@@ -1156,14 +1190,20 @@ def _scale_sr_words(M, K, seed, offset, column_pass, data_sr, stage_blocks):
     return scale, sel.reshape(M, K // 4)
 
 
-def _quantize_axis_opt(x, amax, mode, rht, signs, sr_words, scale_words=None):
-    """x [R, C] quantised along C with optional transform and stochastic rounding (of the codes by sr_words, of the
-    scale bytes by scale_words)."""
+def _axis_blocks(x, rht, signs):
+    """x [R, C] as the 16-element blocks a pass quantises: transformed (and rounded to bf16) when rht."""
     x = np.asarray(x, dtype=F32)
     R, C = x.shape
     if rht:
         x = bf16_round(_fwht16_f32(x, signs))
-    xb = x.reshape(R, C // 16, 16)
+    return x.reshape(R, C // 16, 16)
+
+
+def _quantize_axis_opt(x, amax, mode, rht, signs, sr_words, scale_words=None):
+    """x [R, C] quantised along C with optional transform and stochastic rounding (of the codes by sr_words, of the
+    scale bytes by scale_words)."""
+    R, C = np.asarray(x).shape
+    xb = _axis_blocks(x, rht, signs)
     b = np.abs(xb).max(axis=-1)
     stored, coeff = nvfp4_block_scale(b, nvfp4_global_encode_scale(amax), mode, scale_words)
     with np.errstate(over="ignore", invalid="ignore"):
@@ -1179,26 +1219,34 @@ def nvfp4_quantize_transpose_launch(x, amax_row, amax_col, return_transpose, sr,
                                     return_row, seed=0, offset=0, sign=None, scale_sr=False):
     """One launch of the reference's tuned kernel (``tk_quantize_transpose``, tk_quantize.cu:3807-3926):
     stochastic rounding (of the codes: ``sr``; of the scale bytes: ``scale_sr``) applies to every pass of the
-    launch; ``sign`` = (seed, subseq) or None.  An encode-centric block with maximum <= 1e-9 draws no scale word in
-    the reference; here it draws one like every other block."""
+    launch; ``sign`` = (seed, subseq) or None.  An encode-centric block with maximum <= 1e-9 draws no scale word
+    (it stores the largest multiplier at once), so every later draw of the reference thread that owns it moves up."""
     x = np.asarray(x, dtype=F32)
     M, K = x.shape
     mode = "encode" if encode_centric else "decode"
     out = {}
     per_stage = 16 if return_transpose else 8
+    stage_blocks = 4 if return_transpose else 2
+    sg_row = rht_sign_vector(sign[0], sign[1], K) if (sign and row_rht) else None
+    sg_col = rht_sign_vector(sign[0], sign[1], M) if (sign and col_rht) else None
+    xt = np.ascontiguousarray(x.T)
+    skip_row = skip_col = zero_row = zero_col = None
+    if scale_sr and encode_centric:
+        # a pass that only advances the stream (row operand not returned) draws for every block without looking at it
+        zero_row = (np.abs(_axis_blocks(x, row_rht, sg_row)).max(axis=-1) <= F32(1e-9)) if return_row else None
+        zero_col = (np.abs(_axis_blocks(xt, col_rht, sg_col)).max(axis=-1) <= F32(1e-9)) if return_transpose else None
+        skip_row, skip_col = _zero_block_skips(M, K, zero_row, zero_col, stage_blocks)
     if return_row:
-        sg = rht_sign_vector(sign[0], sign[1], K) if (sign and row_rht) else None
         words, sw = (_sr_words_row(M, K, seed, offset, per_stage) if sr else None), None
         if scale_sr:
-            sw, words = _scale_sr_words(M, K, seed, offset, False, sr, 4 if return_transpose else 2)
-        fp4, s = _quantize_axis_opt(x, amax_row, mode, row_rht, sg, words, sw)
+            sw, words = _scale_sr_words(M, K, seed, offset, False, sr, stage_blocks, skip_row, zero_row)
+        fp4, s = _quantize_axis_opt(x, amax_row, mode, row_rht, sg_row, words, sw)
         out.update(row_fp4=fp4, row_sc=swizzle_scales(s))
     if return_transpose:
-        sg = rht_sign_vector(sign[0], sign[1], M) if (sign and col_rht) else None
         words, sw = (_sr_words_col(M, K, seed, offset) if sr else None), None
         if scale_sr:
-            sw, words = _scale_sr_words(M, K, seed, offset, True, sr, 4)
-        fp4, s = _quantize_axis_opt(np.ascontiguousarray(x.T), amax_col, mode, col_rht, sg, words, sw)
+            sw, words = _scale_sr_words(M, K, seed, offset, True, sr, 4, skip_col, zero_col)
+        fp4, s = _quantize_axis_opt(xt, amax_col, mode, col_rht, sg_col, words, sw)
         out.update(col_fp4=fp4, col_sc=swizzle_scales(s))
     return out
 

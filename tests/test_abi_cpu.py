@@ -81,4 +81,4 @@ def test_entry_points_validate_before_touching_the_device(pkg):
     assert lib.fp4b200_mxfp4_quantize_row_and_col_sr(p, 128, 128, 1, 1, 0, 0, 0, 0, 0, 1, 2, p, p, p, None, None) == -1
     # pitched opt quantiser: the pitch of the wider row-code matrix
     assert lib.fp4b200_nvfp4_quantize_opt_into(p, None, None, 128, 256, p, p, 1, 1, 0, 0, 0, 0, 0, 1, 1, 0, 0, 0, p, 100, p, p, p,
-                                               None) == -1 and "row pitch" in msg()
+                                               None, None) == -1 and "row pitch" in msg()

@@ -282,8 +282,6 @@ def test_oracle_stochastic_and_hadamard_quantiser_vs_the_references_own_kernels(
     name, shape, kind, kw = G.CASES[idx]
     if "target" in kw:
         pytest.skip("the oracle's opt quantiser has no tensor-scale target argument; the CUDA path is held to this case")
-    if name.endswith("zero_blocks"):
-        pytest.skip("all-zero encode-centric blocks under scale SR shift the reference thread's later draws: see the GPU test")
     gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "nvfp4_sr_reference_golden.npz"))
     x = G.make_input(kind, shape, 100 + idx)
     ref, used = o.nvfp4_quantize_for_gemm_opt(x, kw["return_transpose"], kw["encode_centric"], kw["data_sr"], kw["rht"], kw["sign"],
