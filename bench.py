@@ -165,12 +165,174 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
-def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5):
+def _mod(name):
+    return importlib.import_module("mfu-fp4-training_b200." + name)
+
+
+def load_reference_kernels():
+    """The reference's own extension modules compiled by oracle/build_ref.sh (oracle/_ref/), or {} when absent.
+    Used only to time the reference's kernels beside this library's on one GPU; nothing else touches them."""
+    import glob
+    import importlib.util
+    out = {}
+    for name in ("_tk_quant_v5", "_C"):
+        paths = glob.glob(os.path.join(ROOT, "oracle", "_ref", name + ".*.so")) + glob.glob(os.path.join(ROOT, "oracle", "_ref", name + ".so"))
+        if not paths:
+            continue
+        try:
+            spec = importlib.util.spec_from_file_location(name, paths[0])
+            mod = importlib.util.module_from_spec(spec)
+            spec.loader.exec_module(mod)
+            out[name] = mod
+        except Exception as e:                       # a module that does not load is reported, not fatal
+            out[name + "_error"] = str(e)[:200]
+    return out
+
+
+def _time_loop(torch, fn, iters, warm=3):
+    """Mean ms of `iters` back-to-back calls of fn(i) after `warm` untimed ones (CUDA events on the current stream)."""
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(warm + i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters
+
+
+def _sustained(torch, fn, seconds, iters):
+    """Keeps fn running back to back for `seconds` (the part settles under its power limit), then times `iters` calls."""
+    t0 = time.perf_counter()
+    i = 0
+    while time.perf_counter() - t0 < seconds:
+        for _ in range(32):
+            fn(i)
+            i += 1
+        torch.cuda.synchronize()
+    return _time_loop(torch, fn, iters, warm=0)
+
+
+def gemm_roofline_leg(torch, peaks, local_rank, world, refs, traffic):
+    """The two FFN GEMM shapes of config 3 alone (gate/up: N 28672, K 4096; down: N 4096, K 14336; M 16384), random
+    codes and scales, three operand sets in rotation (>= 3 x the 126 MB L2 together with the output), 20 timed
+    launches after warm-up ("burst": the part still at its boost clock) and 20 more after ~1.2 s of back-to-back
+    launches ("sustained": at the 1000 W limit the SM clock settles near 1.3-1.45 GHz).  Beside them, at N = 1 and
+    when present, the reference's own nvfp4_gemm kernel and cuBLASLt's NVFP4 GEMM (torch._scaled_mm) on the same
+    operands: the ceiling a library reaches on this box."""
+    gemm = _mod("tk_gemm_c")
+    dev = torch.device("cuda", local_rank)
+    g = torch.Generator(device=dev).manual_seed(23)
+    out = {}
+    for name, (M, N, K) in (("gate_up", (M_ROWS, 28672, K_COLS)), ("down", (M_ROWS, K_COLS, 14336))):
+        sets = []
+        for _ in range(3):
+            sets.append((torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev, generator=g),
+                         torch.randint(40, 64, (M // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g),
+                         torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g),
+                         torch.randint(40, 64, (N // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g)))
+        sg = torch.full((1,), 1e-3, dtype=torch.float32, device=dev)
+        d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+        fl = 2.0 * M * N * K
+
+        def ours(i):
+            a, a_sc, b, b_sc = sets[i % 3]
+            gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
+        arms = {"ours": ours}
+        if world == 1 and "_C" in refs:
+            def ref_kernel(i):
+                a, a_sc, b, b_sc = sets[i % 3]
+                refs["_C"].nvfp4_gemm(a.view(torch.float4_e2m1fn_x2), a_sc.view(torch.float8_e4m3fn), sg,
+                                      b.view(torch.float4_e2m1fn_x2), b_sc.view(torch.float8_e4m3fn), sg, d)
+            arms["reference_kernel"] = ref_kernel
+        if world == 1 and hasattr(torch, "_scaled_mm") and hasattr(torch, "float4_e2m1fn_x2"):
+            def cublaslt(i):
+                a, a_sc, b, b_sc = sets[i % 3]
+                torch._scaled_mm(a.view(torch.float4_e2m1fn_x2), b.view(torch.float4_e2m1fn_x2).t(),
+                                 a_sc.view(torch.float8_e4m3fn).reshape(-1), b_sc.view(torch.float8_e4m3fn).reshape(-1),
+                                 out_dtype=torch.bfloat16)
+            arms["cublaslt"] = cublaslt
+        res = {}
+        for arm, fn in arms.items():
+            try:
+                burst = _time_loop(torch, fn, 20)
+                sampler = ClockSampler(local_rank)
+                sampler.start()
+                sus = _sustained(torch, fn, 1.2, 20)
+                clk = sampler.stop()
+            except Exception as e:       # a comparison arm that cannot run here is reported, the bench goes on
+                if arm == "ours":
+                    raise
+                res[arm] = {"unavailable": str(e)[:160]}
+                continue
+            res[arm] = {"burst_ms": burst, "burst_tflops": fl / burst / 1e9, "sustained_ms": sus,
+                        "sustained_tflops": fl / sus / 1e9, "sm_mhz_sustained": clk["sm_mhz"], "reasons": clk["reasons"]}
+            time.sleep(1.0)              # let the part recover its boost clock before the next arm's burst figure
+        out[name] = {"shape": f"{M}x{N}x{K}", **res}
+        del sets, d
+        torch.cuda.empty_cache()
+    o_ = out["gate_up"]["ours"]
+    mhz = o_["sm_mhz_sustained"] or 1965.0
+    roof = {"bound": "tensor", "kernel": "fp4_gemm_pair_kernel<nvfp4, plain> (gate/up: M 16384, N 28672, K 4096)",
+            "achieved": o_["burst_tflops"], "unit": "TFLOP/s", "peak": 9000.0, "frac": o_["burst_tflops"] / 9000.0,
+            "peak_kind": "nominal dense FP4 at 1965 MHz (no measured FP4 peak exists); 4 x measured bf16 burst beside it",
+            "frac_of_4x_measured_bf16": o_["burst_tflops"] / (4.0 * peaks["bf16_tflops"]),
+            "sustained": {"achieved": o_["sustained_tflops"], "sm_mhz": mhz,
+                          "frac_of_nominal_at_sampled_clock": o_["sustained_tflops"] / (9000.0 * mhz / 1965.0),
+                          "frac_of_4x_measured_bf16_sustained": o_["sustained_tflops"] / (4.0 * peaks.get("bf16_tflops_sustained", peaks["bf16_tflops"]))},
+            "traffic": traffic.get("fp4_gemm_pair_kernel", {}).get("dram_bytes_per_launch_16384x28672x4096"),
+            "l2": "three operand sets in rotation; the 940 MB output alone exceeds L2"}
+    return out, roof
+
+
+def config1_leg(torch, dev):
+    """BASELINE config 1: X bf16 [2048 x 4096] (outlier channels) and W bf16 [4096 x 4096] ~ N(0, 0.02) quantised to
+    NVFP4 (1-D blocks, round to nearest, decode-centric as the reference's CPU emulation) and multiplied; beside it the
+    numpy oracle's quantise -> dequantise -> float64 product on the host cores, and the relative Frobenius distance of
+    the GPU's fp32 epilogue from that product."""
+    import numpy as np
+    from oracle import fp4_oracle as o
+    tkq, gemm = _mod("tk_quant_v5"), _mod("tk_gemm_c")
+    M, K, N = 2048, 4096, 4096
+    x = o.make_activations(M, K, seed=1)
+    w = o.bf16_round((0.02 * np.random.default_rng(2).standard_normal((N, K))).astype(np.float32))
+    xd = torch.from_numpy(x).to(torch.bfloat16).to(dev)
+    wd = torch.from_numpy(w).to(torch.bfloat16).to(dev)
+    qw = tkq.tk_quantize_for_gemm(wd, False, False)
+    d16 = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    d32 = torch.empty(M, N, dtype=torch.float32, device=dev)
+    st = {}
+
+    def step(i):
+        st["qx"] = tkq.tk_quantize_for_gemm(xd, False, False)
+        q = st["qx"]
+        gemm.nvfp4_gemm(q[0], q[1], q[4], qw[0], qw[1], qw[4], d16)
+    ms = _time_loop(torch, step, 20)
+    q = st["qx"]
+    gemm.nvfp4_gemm(q[0], q[1], q[4], qw[0], qw[1], qw[4], d32)
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    rx, rw = o.nvfp4_quantize_for_gemm(x, False, False), o.nvfp4_quantize_for_gemm(w, False, False)
+    ref = o.nvfp4_gemm_fp32(rx["row_fp4"], rx["row_sc_logical"], rx["sg"], rw["row_fp4"], rw["row_sc_logical"], rw["sg"])
+    cpu_s = time.perf_counter() - t0
+    got = d32.cpu().numpy()
+    rel = float(np.linalg.norm(got - ref) / np.linalg.norm(ref))
+    same_codes = bool(np.array_equal(q[0].view(torch.uint8).cpu().numpy(), rx["row_fp4"]))
+    fl = 2.0 * M * N * K
+    return {"workload": "config1: NVFP4 quantise X[2048x4096] -> GEMM with quantised W[4096x4096], RTN, decode-centric",
+            "gpu_ms_quantise_x_plus_gemm": ms, "gpu_tflops": fl / ms / 1e9,
+            "cpu_seconds_quantise_both_plus_qgemm": cpu_s, "cpu_tflops": fl / cpu_s / 1e12, "cpu_kind": "numpy oracle (port)",
+            "cpu_cores": os.cpu_count(), "rel_frobenius_fp32_epilogue_vs_oracle": rel, "codes_equal_oracle": same_codes,
+            "tolerance": 1e-3}
+
+
+def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=20):
     """Llama-3-8B FFN forward in NVFP4 at M=16384 per rank (config 3): fused RMSNorm+quant, grouped
-    gate/up GEMM (N=28672, K=4096), SwiGLU producer, down GEMM (N=4096, K=14336).  Weights are
-    quantised once outside the timed region.  Returns per-kernel and whole-step figures."""
-    tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
-    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    gate/up GEMM (N=28672, K=4096), SwiGLU producer, down GEMM (N=4096, K=14336), chained on real data.  Weights
+    are quantised once outside the timed region.  Returns per-kernel and whole-step figures."""
+    tkq, gemm = _mod("tk_quant_v5"), _mod("tk_gemm_c")
     H, K, M = 14336, K_COLS, M_ROWS
     dev = x_dev.device
     g = torch.Generator(device="cpu").manual_seed(7)
@@ -185,7 +347,7 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
     else:
         # weights are FSDP-sharded along their rows; every rank quantises its shard and the ranks
         # all-gather packed codes + scale tiles (plus one float amax all-reduce per weight)
-        fsdp = importlib.import_module("mfu-fp4-training_b200.fsdp_weights")
+        fsdp = _mod("fsdp_weights")
         rank = dist.get_rank()
         shards = []
         for n, k in ((H, K), (H, K), (K, H)):
@@ -194,16 +356,18 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
             del w
         ops = []
         g0, g1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        for rep in range(3):
-            if rep == 2:
+        n_rep = 10
+        for rep in range(3 + n_rep):
+            if rep == 3:
                 dist.barrier(); torch.cuda.synchronize(); g0.record()
-            ops = [fsdp.all_gather_nvfp4_weight(sh, None, False, True) for sh in shards]
+            ops = fsdp.all_gather_nvfp4_weights(shards, None, False, True, reuse_buffers=True)
         g1.record(); torch.cuda.synchronize()
-        ag = torch.tensor([g0.elapsed_time(g1)], device=dev)
+        ag = torch.tensor([g0.elapsed_time(g1) / n_rep], device=dev)
         dist.all_reduce(ag, op=dist.ReduceOp.MAX)
         nbytes = sum(fsdp.gathered_bytes(n, k, "nvfp4", False) for n, k in ((H, K), (H, K), (K, H)))
         gather = {"ms": ag.item(), "bytes_received_per_rank": nbytes, "bf16_equivalent_bytes": 3 * H * K * 2,
-                  "note": "quantise own shard + amax all-reduce + all-gather of row-wise codes and scale tiles, 3 FFN weights"}
+                  "note": "quantise own shards, ONE amax all-reduce and ONE group of all-gathers for the three FFN weights "
+                          "(row-wise codes and scale tiles), send / receive buffers kept between steps; mean of 10"}
         ops = [(o_[0], o_[1], o_[4]) for o_ in ops]
     (w1c, w1s, w1g), (w3c, w3s, w3g), (w2c, w2s, w2g) = ops
     b13 = torch.cat([w1c, w3c], 0)
@@ -212,42 +376,34 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=5
     h1 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     h3 = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     y = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    st = {}
+    def s_norm_quant():
+        st["qx"] = tkq.tk_fused_norm_quantize(x_dev, gamma, EPS, False, True)
+    def s_gate_up():
+        q = st["qx"]; gemm.nvfp4_grouped_gemm(q[0], q[1], q[4], b13, b13_sc, b13_sg, h1, h3)
+    def s_swiglu():
+        st["qh"] = tkq.tk_silu_quantize_split_for_gemm(h1, h3)
+    def s_down():
+        q = st["qh"]; gemm.nvfp4_gemm(q[0], q[1], q[4], w2c, w2s, w2g, y)
     names = ["rmsnorm_quant", "gate_up_gemm", "swiglu_quant", "down_gemm"]
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(5)] for _ in range(iters)]
-    for i in range(2 + iters):
-        rec = (lambda j: ev[i - 2][j].record()) if i >= 2 else (lambda j: None)
-        rec(0)
-        qx = tkq.tk_fused_norm_quantize(x_dev, gamma, EPS, False, True)
-        rec(1)
-        gemm.nvfp4_grouped_gemm(qx[0], qx[1], qx[4], b13, b13_sc, b13_sg, h1, h3)
-        rec(2)
-        qh = tkq.tk_silu_quantize_split_for_gemm(h1, h3)
-        rec(3)
-        gemm.nvfp4_gemm(qh[0], qh[1], qh[4], w2c, w2s, w2g, y)
-        rec(4)
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    ms, total = _timed_stages(torch, [s_norm_quant, s_gate_up, s_swiglu, s_down], iters=iters)
+    clk = sampler.stop()
     if world > 1:
         dist.barrier()
-    torch.cuda.synchronize()
-    ms = [statistics.mean(e[j].elapsed_time(e[j + 1]) for e in ev) for j in range(4)]
-    total = statistics.mean(e[0].elapsed_time(e[4]) for e in ev)
     t = torch.tensor(ms + [total], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, total = t[:4].tolist(), t[4].item()
     fl_up, fl_down = 2.0 * M * 2 * H * K, 2.0 * M * K * H
-    fp4_nominal = 9000.0
-    fp4_box = 4.0 * peaks["bf16_tflops"]
     out = {"workload": "config3: Llama-3-8B FFN forward in NVFP4, M=16384 tokens per GPU", "ms": dict(zip(names, ms)),
-           "step_ms": total,
+           "step_ms": total, "iterations": iters, "clocks": clk,
            "gate_up_gemm_tflops": fl_up * world / (ms[1] * 1e-3) / 1e12,
            "down_gemm_tflops": fl_down * world / (ms[3] * 1e-3) / 1e12,
            "step_tflops": (fl_up + fl_down) * world / (total * 1e-3) / 1e12,
            "swiglu_quant_gbs": M * H * 5.125 * world / (ms[2] * 1e-3) / 1e9,
-           "roofline": {"bound": "tensor", "kernel": "fp4_gemm_pair_kernel<nvfp4> (gate/up, N=28672 K=4096)",
-                        "achieved": fl_up / (ms[1] * 1e-3) / 1e12, "unit": "TFLOP/s",
-                        "peak": fp4_nominal, "frac": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_nominal,
-                        "peak_kind": "nominal dense FP4 (no measured FP4 peak exists)",
-                        "frac_of_4x_measured_bf16": fl_up / (ms[1] * 1e-3) / 1e12 / fp4_box, "traffic": None}}
+           "swiglu_quant_frac_of_measured_hbm": M * H * 5.125 / (ms[2] * 1e-3) / 1e9 / peaks["hbm_gbs"]}
     if gather is not None:
         out["weight_all_gather"] = gather
     return out
@@ -271,26 +427,38 @@ def _timed_stages(torch, stages, iters=3, warm=3):
     return ms, statistics.mean(e[0].elapsed_time(e[n]) for e in ev)
 
 
-def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
-    """Llama-3-8B FFN backward in NVFP4 at M=16384 per rank (config 4), production flags of the reference's
-    v5 route: gradients quantised decode-centric with Philox stochastic rounding on the row operand,
-    weights pre-quantised (their column operands serve the dgrads).  Stages: quantise dY; W2 dgrad;
-    W2 wgrad; SiLU-derivative producer (dh1, dh3 quantised); W1/W3 dgrad (two accumulated GEMMs);
-    W1 and W3 wgrads; RMSNorm backward of the block input with the residual stream's gradient added.  The
-    attention side's form of the last step (three gradient streams summed first) is timed beside them."""
-    tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
-    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks, iters=10):
+    """Llama-3-8B FFN backward in NVFP4 at M=16384 per rank (config 4, as BASELINE.json words it): dgrad GEMMs from
+    round-to-nearest operands; wgrad GEMMs from operands with the 16-point Hadamard transform along the token
+    dimension on BOTH sides (seeded sign vector) and Philox stochastic rounding (fixed seed / subsequence) of the
+    gradient side.  Stages: quantise dY (row operand RTN, column operand transformed + SR; the transform's tensor
+    maximum scan is part of the stage); W2 dgrad; W2 wgrad; SiLU-derivative producer (dh1, dh3 and their RTN
+    operands); wgrad operands of dh1 and dh3 (transformed + SR); W1/W3 dgrad (two accumulated GEMMs); W1 and W3
+    wgrads; RMSNorm backward with the residual gradient.  The transformed column operands of the forward's
+    activations (x normalised, h) are made once outside the timed passes and timed on their own beside them."""
+    tkq, gemm = _mod("tk_quant_v5"), _mod("tk_gemm_c")
     H, K, M = 14336, K_COLS, M_ROWS
     dev = x_dev.device
+    SEED, SUBSEQ = 20261125, 3
     g = torch.Generator(device="cpu").manual_seed(11)
     def rnd(n, k, s):
         return (s * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(dev)
     q1 = tkq.tk_quantize_for_gemm(rnd(H, K, 0.02), True, False)
     q3 = tkq.tk_quantize_for_gemm(rnd(H, K, 0.02), True, False)
     q2 = tkq.tk_quantize_for_gemm(rnd(K, H, 0.02), True, False)
-    qx = tkq.tk_fused_norm_quantize(x_dev, gamma, EPS, False, True)      # forward's operands (column side for wgrad)
+    qx = tkq.tk_fused_norm_quantize(x_dev, gamma, EPS, False, True)
+    inv_rms = qx[5]
     h1, h3 = rnd(M, H, 1.0), rnd(M, H, 1.0)
-    qh = tkq.tk_silu_quantize_split_for_gemm(h1, h3)
+    # forward-side wgrad operands: column operands with the transform along M and the same sign vector, no SR
+    xn = (x_dev.float() * inv_rms[:, None] * gamma.float()[None, :]).to(torch.bfloat16)
+    hh = (torch.nn.functional.silu(h1.float()) * h3.float()).to(torch.bfloat16)
+    fw = {}
+    def s_fw_x():
+        fw["x"] = tkq.tk_quantize_for_gemm_opt(xn, True, True, False, False, "col", True, SEED, SUBSEQ, 448.0, "both")
+    def s_fw_h():
+        fw["h"] = tkq.tk_quantize_for_gemm_opt(hh, True, True, False, False, "col", True, SEED, SUBSEQ, 448.0, "both")
+    fw_ms, _ = _timed_stages(torch, [s_fw_x, s_fw_h], iters=5)
+    del xn, hh
     dy = rnd(M, K, 1e-3)
     dh = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     dw2 = torch.empty(K, H, dtype=torch.bfloat16, device=dev)
@@ -298,39 +466,43 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
     dw1 = torch.empty(H, K, dtype=torch.bfloat16, device=dev)
     dw3 = torch.empty(H, K, dtype=torch.bfloat16, device=dev)
     st = {}
+    tkq.tk_set_sr_invocation_count(0)
+    def grad_operands(t):   # row: RTN; column: Hadamard along M with the sign vector + stochastic rounding
+        return tkq.tk_quantize_for_gemm_opt(t, True, False, True, False, "col", True, SEED, SUBSEQ, 448.0, "col")
     def s_quant_dy():
-        st["qdy"] = tkq.tk_quantize_for_gemm_opt(dy, True, False, True, False, "none", False, 1234, 0, 448.0, "row")
+        st["qdy"] = grad_operands(dy)
     def s_w2_dgrad():     # dh [M,H] = dY . W2 : B = W2's column operand [H, K/2]
         q = st["qdy"]; gemm.nvfp4_gemm(q[0], q[1], q[4], q2[2], q2[3], q2[4], dh)
-    def s_w2_wgrad():     # dW2 [K,H] = dY^T . h : both column operands, contraction over M
-        q = st["qdy"]; gemm.nvfp4_gemm(q[2], q[3], q[5], qh[2], qh[3], qh[4], dw2)
+    def s_w2_wgrad():     # dW2 [K,H] = dY^T . h : transformed column operands of both, contraction over M
+        q, f = st["qdy"], fw["h"]; gemm.nvfp4_gemm(q[2], q[3], q[5], f[2], f[3], f[5], dw2)
     def s_silu_deriv():
-        st["qd"] = tkq.tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1, True, False, True, False, "none", False,
-                                                                  1234, 1, "row")
+        st["qd"] = tkq.tk_silu_deriv_quantize_split_for_gemm(dh, h3, h1)
+    def s_wgrad_operands():
+        d = st["qd"]
+        st["g1"], st["g3"] = grad_operands(d[14]), grad_operands(d[15])
     def s_w13_dgrad():    # dx [M,K] = dh1 . W1 + dh3 . W3, fp32 running sum, one rounding
         d = st["qd"]
         gemm.nvfp4_batched_accum_gemm([d[0], d[6]], [d[1], d[7]], [d[4], d[10]], [q1[2], q3[2]], [q1[3], q3[3]],
                                       [q1[4], q3[4]], dx)
     def s_w13_wgrad():    # dW1 [H,K] = dh1^T . x, dW3 likewise
-        d = st["qd"]
-        gemm.nvfp4_gemm(d[2], d[3], d[5], qx[2], qx[3], qx[4], dw1)
-        gemm.nvfp4_gemm(d[8], d[9], d[11], qx[2], qx[3], qx[4], dw3)
-    inv_rms = qx[5]
+        f = fw["x"]
+        gemm.nvfp4_gemm(st["g1"][2], st["g1"][3], st["g1"][5], f[2], f[3], f[5], dw1)
+        gemm.nvfp4_gemm(st["g3"][2], st["g3"][3], st["g3"][5], f[2], f[3], f[5], dw3)
     dx_in = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
     dgamma = torch.empty(K, dtype=torch.float32, device=dev)
     def s_rmsnorm_bwd():  # dx_in = RMSNorm backward of dx + the residual stream's gradient (dY), dgamma through row tiles
         gemm.rmsnorm_bwd_residual_out(dx, x_dev, gamma, inv_rms, dy, dx_in, dgamma)
-    names = ["quant_dy_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_quant_sr", "w13_dgrad_gemms", "w13_wgrad_gemms",
-             "rmsnorm_bwd_residual"]
-    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_w13_dgrad, s_w13_wgrad,
-                                      s_rmsnorm_bwd])
-    # the attention side's form of the same step: three dgrad streams summed first (12 B per element)
+    names = ["quant_dy_rht_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_quant", "dh_wgrad_operands_rht_sr",
+             "w13_dgrad_gemms", "w13_wgrad_gemms", "rmsnorm_bwd_residual"]
+    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_wgrad_operands, s_w13_dgrad,
+                                      s_w13_wgrad, s_rmsnorm_bwd], iters=iters)
+    # the attention side's form of the last step: three dgrad streams summed first (12 B per element)
     d_sum = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
     partials = torch.empty((M + 255) // 256, K, dtype=torch.float32, device=dev)
     d3 = [dx, dy, rnd(M, K, 1e-3)]
     def s_sum3():
         gemm.sum3_rmsnorm_bwd_out(d3[0], d3[1], d3[2], x_dev, gamma, inv_rms, d_sum, dx_in, partials, dgamma)
-    sum3_ms = _timed_stages(torch, [s_sum3])[0][0]
+    sum3_ms = _timed_stages(torch, [s_sum3], iters=10)[0][0]
     t = torch.tensor(ms + [total], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -338,14 +510,17 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks):
     fl = {"w2_dgrad_gemm": 2.0 * M * H * K, "w2_wgrad_gemm": 2.0 * K * H * M, "w13_dgrad_gemms": 4.0 * M * K * H,
           "w13_wgrad_gemms": 4.0 * H * K * M}
     gemm_ms = sum(m for n_, m in zip(names, ms) if n_ in fl)
-    return {"workload": "config4: Llama-3-8B FFN backward in NVFP4, M=16384 tokens per GPU, decode-centric, row-axis SR",
-            "ms": dict(zip(names, ms)), "step_ms": total,
+    return {"workload": "config4: Llama-3-8B FFN backward in NVFP4, M=16384 tokens per GPU; dgrad operands RTN, wgrad "
+                        "operands Hadamard-16 along tokens with a seeded sign vector on both sides, gradients' column "
+                        "operands with Philox SR (seed 20261125, subsequence 3, launch counter from 0)",
+            "ms": dict(zip(names, ms)), "step_ms": total, "iterations": iters,
+            "forward_side_wgrad_operands_ms": {"x_normalised_rht_col": fw_ms[0], "h_rht_col": fw_ms[1]},
             "gemm_tflops": {n_: fl[n_] * world / (m * 1e-3) / 1e12 for n_, m in zip(names, ms) if n_ in fl},
             "all_gemms_tflops": sum(fl.values()) * world / (gemm_ms * 1e-3) / 1e12,
             "step_tflops": sum(fl.values()) * world / (total * 1e-3) / 1e12,
             "quant_dy_gbs": M * K * 3.125 * world / (ms[0] * 1e-3) / 1e9,
             "silu_deriv_quant_gbs": M * H * 8.25 * world / (ms[3] * 1e-3) / 1e9,
-            "rmsnorm_bwd_residual_gbs": M * K * 8.0 * world / (ms[6] * 1e-3) / 1e9,
+            "rmsnorm_bwd_residual_gbs": M * K * 8.0 * world / (ms[7] * 1e-3) / 1e9,
             "sum3_rmsnorm_bwd": {"ms": sum3_ms, "gbs": M * K * 12.0 / (sum3_ms * 1e-3) / 1e9,
                                  "frac_of_measured_hbm": M * K * 12.0 / (sum3_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},
             "frac_of_nominal_fp4_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / 9000.0,
@@ -358,8 +533,7 @@ def attention_side_leg(torch, dist, world, peaks):
     V 1024 columns, heads of 128), quantisation of the attention output from its [B, H, S, 64] layout for the
     output projection, the inverse rotation of dQ / dK and the three-stream gradient quantiser in front of the
     QKV dgrad."""
-    tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
-    gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
+    tkq, gemm = _mod("tk_quant_v5"), _mod("tk_gemm_c")
     M, K, q_dim, kv_dim, seq, head = M_ROWS, K_COLS, 4096, 1024, 8192, 128
     N = q_dim + 2 * kv_dim
     dev = torch.device("cuda", torch.cuda.current_device())
@@ -388,7 +562,7 @@ def attention_side_leg(torch, dist, world, peaks):
     def s_split3():
         tkq.tk_group_quantize_dim1_split3_for_gemm(gq2, gk2, gv)
     names = ["qkv_gemm_rope", "qkv_gemm_plain", "quant_attn_out_nhsd", "inverse_rope_dq_dk", "split3_quant"]
-    ms, _ = _timed_stages(torch, [s_qkv_rope, s_qkv_plain, s_quant_attn, s_inverse_rope, s_split3])
+    ms, _ = _timed_stages(torch, [s_qkv_rope, s_qkv_plain, s_quant_attn, s_inverse_rope, s_split3], iters=20)
     t = torch.tensor(ms, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -398,25 +572,44 @@ def attention_side_leg(torch, dist, world, peaks):
             "ms": dict(zip(names, ms)),
             "qkv_gemm_rope_tflops": fl * world / (ms[0] * 1e-3) / 1e12,
             "qkv_gemm_plain_tflops": fl * world / (ms[1] * 1e-3) / 1e12,
+            "rope_epilogue_cost": ms[0] / ms[1] - 1.0,
             "quant_attn_out_gbs": M * K * 3.125 * world / (ms[2] * 1e-3) / 1e9,
             "inverse_rope_gbs": M * (q_dim + kv_dim) * 4.0 * world / (ms[3] * 1e-3) / 1e9,
             "split3_quant_gbs": M * N * 3.125 * world / (ms[4] * 1e-3) / 1e9}
 
 
 def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
-    """MXFP4 (E8M0 / 32-blocks, mode 1) forward GEMMs of one Llama-3-8B decoder layer's weights (config 5:
-    QKV [6144,4096], O [4096,4096], W1/W3 [14336,4096], W2 [4096,14336]) on this rank's share of
-    M = 65536 tokens, with the producers that feed them (fused RMSNorm+quant, plain quant, SwiGLU)."""
-    mxq = importlib.import_module("mfu-fp4-training_b200.mxfp4_quant_v4")
-    gmx = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c_mx")
+    """Config 5: MXFP4 (E8M0 / 32-blocks, mode 1) forward AND backward GEMM set of one Llama-3-8B decoder layer
+    (QKV [6144,4096], O [4096,4096], W1/W3 [14336,4096], W2 [4096,14336]) on this rank's share of M = 65536 tokens,
+    with the producers that feed them.  With N > 1 the layer's weights are FSDP-sharded along their rows and fetched,
+    as packed codes + scale tiles in both orientations, by ONE all-gather inside a timed stage of every pass."""
+    mxq, gmx = _mod("mxfp4_quant_v4"), _mod("tk_gemm_c_mx")
     K, H, NQKV = K_COLS, 14336, 6144
     M = 65536 // world
     dev = gamma.device
     g = torch.Generator(device="cpu").manual_seed(13)
     def rnd(n, k, s):
         return (s * torch.randn(n, k, generator=g)).to(torch.bfloat16).to(dev)
-    wq = {n_: mxq.mxfp4_quantize_for_gemm(rnd(*shape, 0.02), 1)
-          for n_, shape in (("qkv", (NQKV, K)), ("o", (K, K)), ("w1", (H, K)), ("w3", (H, K)), ("w2", (K, H)))}
+    wnames = ("qkv", "o", "w1", "w3", "w2")
+    wshapes = {"qkv": (NQKV, K), "o": (K, K), "w1": (H, K), "w3": (H, K), "w2": (K, H)}
+    wq = {}
+    gather_stage = None
+    if world == 1:
+        wq = {n_: mxq.mxfp4_quantize_row_and_col(rnd(*wshapes[n_], 0.02), 1) for n_ in wnames}
+    else:
+        fsdp = _mod("fsdp_weights")
+        rank = dist.get_rank()
+        shards = []
+        for n_ in wnames:
+            n, k = wshapes[n_]
+            w = rnd(n, k, 0.02)
+            shards.append(w[rank * n // world:(rank + 1) * n // world].contiguous())
+            del w
+        def gather_stage():
+            got = fsdp.all_gather_mxfp4_weights(shards, None, True, 1, reuse_buffers=True)
+            for n_, o_ in zip(wnames, got):
+                wq[n_] = o_
+        gather_stage()
     x = rnd(M, K, 1.0)
     attn = rnd(M, K, 1.0)
     qkv = torch.empty(M, NQKV, dtype=torch.bfloat16, device=dev)
@@ -433,30 +626,85 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
         st["qa"] = mxq.mxfp4_quantize_row_and_col(attn, 1)
     def s_o():
         q = st["qa"]; gmx.mxfp4_gemm(q[0], q[1], wq["o"][0], wq["o"][1], o_out)
-    def s_gate_up():
+    def s_gate_up():      # the reference runs the two projections as one batched launch (mxfp4_fused_linear.py:9494)
         q = st["qx"]
-        gmx.mxfp4_gemm(q[0], q[1], wq["w1"][0], wq["w1"][1], h1)
-        gmx.mxfp4_gemm(q[0], q[1], wq["w3"][0], wq["w3"][1], h3)
+        gmx.mxfp4_batched_gemm([q[0], q[0]], [q[1], q[1]], [wq["w1"][0], wq["w3"][0]], [wq["w1"][1], wq["w3"][1]], [h1, h3])
     def s_swiglu():
         st["qh"] = mxq.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, 1)
     def s_down():
         q = st["qh"]; gmx.mxfp4_gemm(q[0], q[1], wq["w2"][0], wq["w2"][1], y)
-    names = ["rmsnorm_quant", "qkv_gemm", "quant_attn_out", "o_gemm", "gate_up_gemms", "swiglu_quant", "down_gemm"]
-    ms, total = _timed_stages(torch, [s_norm_quant, s_qkv, s_quant_attn, s_o, s_gate_up, s_swiglu, s_down], iters=2)
+    fwd = [("rmsnorm_quant", s_norm_quant), ("qkv_gemm", s_qkv), ("quant_attn_out", s_quant_attn), ("o_gemm", s_o),
+           ("gate_up_gemms", s_gate_up), ("swiglu_quant", s_swiglu), ("down_gemm", s_down)]
+    # ---- backward: gradient quantisers, dgrads (weights' column operands), wgrads (column operands of both sides)
+    dy = rnd(M, K, 1e-3)
+    dh = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+    dxf = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    dattn = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    dqkv = rnd(M, NQKV, 1e-3)
+    dxa = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+    dw = {n_: torch.empty(*wshapes[n_], dtype=torch.bfloat16, device=dev) for n_ in wnames}
+    def s_q_dy():
+        st["gdy"] = mxq.mxfp4_quantize_row_and_col(dy, 1)
+    def s_w2_dgrad():
+        q = st["gdy"]; gmx.mxfp4_gemm(q[0], q[1], wq["w2"][2], wq["w2"][3], dh)
+    def s_w2_wgrad():
+        q, f = st["gdy"], st["qh"]; gmx.mxfp4_gemm(q[2], q[3], f[2], f[3], dw["w2"])
+    def s_silu_deriv():
+        st["gd"] = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, 1)
+    def s_w13_dgrad():   # dgrad of the fused gate/up projection from the concatenated [dh1 | dh3] operand, one launch
+        d = st["gd"]
+        # the producer stacks dh1 and dh3 on a leading dimension; the one-pass GEMM reads them side by side
+        a_full = torch.cat([d[0][0].view(torch.uint8), d[0][1].view(torch.uint8)], dim=1).view(torch.float4_e2m1fn_x2)
+        gmx.mxfp4_split2_dgrad_strided_onepass_gemm(a_full, [d[1][0], d[1][1]], [0, H], [H, H], [wq["w1"][2], wq["w3"][2]],
+                                                    [wq["w1"][3], wq["w3"][3]], dxf, -1)
+    def s_w13_wgrad():
+        d, f = st["gd"], st["qx"]
+        gmx.mxfp4_gemm(d[2][0], d[3][0], f[2], f[3], dw["w1"])
+        gmx.mxfp4_gemm(d[2][1], d[3][1], f[2], f[3], dw["w3"])
+    def s_q_do():
+        st["gdo"] = mxq.mxfp4_quantize_row_and_col(dxf, 1)
+    def s_o_dgrad():
+        q = st["gdo"]; gmx.mxfp4_gemm(q[0], q[1], wq["o"][2], wq["o"][3], dattn)
+    def s_o_wgrad():
+        q, f = st["gdo"], st["qa"]; gmx.mxfp4_gemm(q[2], q[3], f[2], f[3], dw["o"])
+    def s_q_dqkv():
+        st["gq"] = mxq.mxfp4_quantize_row_and_col(dqkv, 1)
+    def s_qkv_dgrad():
+        q = st["gq"]; gmx.mxfp4_gemm(q[0], q[1], wq["qkv"][2], wq["qkv"][3], dxa)
+    def s_qkv_wgrad():
+        q, f = st["gq"], st["qx"]; gmx.mxfp4_gemm(q[2], q[3], f[2], f[3], dw["qkv"])
+    bwd = [("quant_dy", s_q_dy), ("w2_dgrad_gemm", s_w2_dgrad), ("w2_wgrad_gemm", s_w2_wgrad),
+           ("silu_deriv_quant_split2", s_silu_deriv), ("w13_dgrad_onepass_gemm", s_w13_dgrad), ("w13_wgrad_gemms", s_w13_wgrad),
+           ("quant_d_o", s_q_do), ("o_dgrad_gemm", s_o_dgrad), ("o_wgrad_gemm", s_o_wgrad), ("quant_d_qkv", s_q_dqkv),
+           ("qkv_dgrad_gemm", s_qkv_dgrad), ("qkv_wgrad_gemm", s_qkv_wgrad)]
+    stages = ([("weight_all_gather", gather_stage)] if gather_stage is not None else []) + fwd + bwd
+    names = [n_ for n_, _ in stages]
+    ms, total = _timed_stages(torch, [f for _, f in stages], iters=3)
     t = torch.tensor(ms + [total], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms, total = t[:-1].tolist(), t[-1].item()
-    fl = {"qkv_gemm": 2.0 * M * NQKV * K, "o_gemm": 2.0 * M * K * K, "gate_up_gemms": 4.0 * M * H * K, "down_gemm": 2.0 * M * K * H}
-    gemm_ms = sum(m for n_, m in zip(names, ms) if n_ in fl)
-    return {"workload": f"config5: MXFP4 mode 1, one decoder layer's weight GEMMs forward, M={M} tokens per GPU (65536 / {world})",
-            "ms": dict(zip(names, ms)), "step_ms": total,
-            "gemm_tflops": {n_: fl[n_] * world / (m * 1e-3) / 1e12 for n_, m in zip(names, ms) if n_ in fl},
-            "all_gemms_tflops": sum(fl.values()) * world / (gemm_ms * 1e-3) / 1e12,
-            "rmsnorm_quant_gbs": M * K * 3.0625 * world / (ms[0] * 1e-3) / 1e9,
-            "frac_of_nominal_fp4_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / 9000.0,
-            "swiglu_quant_gbs": M * H * (4 + 1.0625) * world / (ms[5] * 1e-3) / 1e9,
-            "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
+    by = dict(zip(names, ms))
+    fl = {"qkv_gemm": 2.0 * M * NQKV * K, "o_gemm": 2.0 * M * K * K, "gate_up_gemms": 4.0 * M * H * K, "down_gemm": 2.0 * M * K * H,
+          "w2_dgrad_gemm": 2.0 * M * H * K, "w2_wgrad_gemm": 2.0 * M * H * K, "w13_dgrad_onepass_gemm": 4.0 * M * H * K,
+          "w13_wgrad_gemms": 4.0 * M * H * K, "o_dgrad_gemm": 2.0 * M * K * K, "o_wgrad_gemm": 2.0 * M * K * K,
+          "qkv_dgrad_gemm": 2.0 * M * NQKV * K, "qkv_wgrad_gemm": 2.0 * M * NQKV * K}
+    gemm_ms = sum(by[n_] for n_ in fl)
+    out = {"workload": f"config5: MXFP4 mode 1, one decoder layer's GEMM set forward + backward, M={M} tokens per GPU "
+                       f"(65536 / {world})" + (", weights FSDP-sharded and all-gathered as packed FP4 + scales" if world > 1 else ""),
+           "ms": by, "step_ms": total,
+           "gemm_tflops": {n_: fl[n_] * world / (by[n_] * 1e-3) / 1e12 for n_ in fl},
+           "all_gemms_tflops": sum(fl.values()) * world / (gemm_ms * 1e-3) / 1e12,
+           "rmsnorm_quant_gbs": M * K * 3.0625 * world / (by["rmsnorm_quant"] * 1e-3) / 1e9,
+           "swiglu_quant_gbs": M * H * (4 + 1.0625) * world / (by["swiglu_quant"] * 1e-3) / 1e9,
+           "frac_of_nominal_fp4_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / 9000.0,
+           "frac_of_4x_measured_bf16_all_gemms": sum(fl.values()) / (gemm_ms * 1e-3) / 1e12 / (4.0 * peaks["bf16_tflops"])}
+    if world > 1:
+        fsdp = _mod("fsdp_weights")
+        nbytes = sum(fsdp.gathered_bytes(*wshapes[n_], "mxfp4", True) for n_ in wnames)
+        out["weight_all_gather"] = {"ms": by["weight_all_gather"], "bytes_received_per_rank": nbytes,
+                                    "bf16_equivalent_bytes": 2 * sum(a * b for a, b in wshapes.values())}
+    return out
 
 
 def rmsnorm_bwd_only(args):
@@ -641,9 +889,11 @@ def main():
     quant_bytes = M_ROWS * K_COLS * 3.125
     stats_bytes = M_ROWS * K_COLS * 2.0
     achieved = quant_bytes / (t_quant * 1e-3) / 1e9
+    traffic = load_traffic()
     roofline = {"bound": "hbm", "kernel": "nvfp4_quantize_strip_kernel<encode_centric, norm, paired> (pass 2)",
                 "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
-                "peak_kind": f"of {peak_kind} copy bandwidth", "traffic": TRAFFIC_PER_LAUNCH,
+                "peak_kind": f"of {peak_kind} copy bandwidth",
+                "traffic": traffic.get("nvfp4_quantize_strip_kernel", {}).get("dram_bytes_per_launch_16384x4096"),
                 "algorithmic_bytes_per_launch": quant_bytes, "avg_launch_ms": t_quant,
                 "other_kernels": {"rmsnorm_stats_kernel + partials reduction (pass 1 stand-alone, two launches)": {
                     "achieved": stats_bytes / (t_stats * 1e-3) / 1e9, "unit": "GB/s", "avg_launch_ms": t_stats,
@@ -713,6 +963,50 @@ def main():
            "pipeline": "copy-in, kernels and copy-out on three streams, two buffer sets"}
 
     del outs_host
+    clocks = sampler.stop() if rank == 0 else None      # clocks of the headline's timed region and its end-to-end leg
+
+    # ---- the shape an 8-way split of config 2's tokens gives each GPU: 2048 rows, X (16.8 MB) stays in L2 ----
+    # Twenty calls through the C ABI captured in one CUDA graph: at 10 us per call the host's launch path would
+    # otherwise be what is timed.
+    rows_s = 2048
+    x_small = xs[0][:rows_s].contiguous()
+    o_small = (torch.empty((rows_s, K_COLS // 2), **u8), torch.empty((rows_s * K_COLS // 16,), **u8),
+               torch.empty((K_COLS, rows_s // 2), **u8), torch.empty((rows_s * K_COLS // 16,), **u8))
+    side = torch.cuda.Stream()
+
+    def small_call(st):
+        lib.call("fp4b200_nvfp4_fused_norm_quantize", x_small.data_ptr(), gamma.data_ptr(), EPS, rows_s, K_COLS, inv_rms.data_ptr(),
+                 1, 1, o_small[0].data_ptr(), o_small[1].data_ptr(), o_small[2].data_ptr(), o_small[3].data_ptr(),
+                 amax_sg.data_ptr(), st)
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        small_call(side.cuda_stream)          # the stream's first call creates the library's per-stream scratch
+    side.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph, stream=side):
+        for _ in range(20):
+            small_call(torch.cuda.current_stream().cuda_stream)
+    small_ms = _time_loop(torch, lambda i: graph.replay(), 20, warm=3) / 20
+    small = {"rows": rows_s, "ms": small_ms, "value": algorithmic_bytes(rows_s, K_COLS) / (small_ms * 1e-3) / 1e9, "unit": UNIT,
+             "frac_of_measured_hbm": algorithmic_bytes(rows_s, K_COLS) / (small_ms * 1e-3) / 1e9 / peaks["hbm_gbs"],
+             "note": "strong-scaling point: 16384 / 8 tokens per GPU; the input (16.8 MB) and the outputs stay in L2, so the "
+                     "figure is a rate against the HBM copy bandwidth, not HBM traffic; 20 calls per CUDA-graph replay"}
+    del graph
+
+    # ---- the reference's own kernels on this box (one GPU only; present when oracle/build_ref.sh was run) ----
+    refs = load_reference_kernels() if world == 1 else {}
+    ref_quant = None
+    if "_tk_quant_v5" in refs:
+        rq = refs["_tk_quant_v5"]
+        ref_ms = _time_loop(torch, lambda i: rq.tk_fused_norm_quantize(xs[i % n_rot], gamma, EPS, False, True), 50, warm=5)
+        ours_ms = _time_loop(torch, lambda i: tkq.tk_fused_norm_quantize(xs[i % n_rot], gamma, EPS, False, True), 50, warm=5)
+        ref_quant = {"kernel": "reference tk_fused_norm_quantize (barrier-free branch, tk_quantize.cu:8048-8108), compiled "
+                               "from the reference's sources for sm_100a", "ms": ref_ms,
+                     "value": alg / (ref_ms * 1e-3) / 1e9, "unit": UNIT, "ours_ms_same_loop": ours_ms,
+                     "ours_over_reference": ref_ms / ours_ms}
+    gemm_shapes, roofline_gemm = gemm_roofline_leg(torch, peaks, local_rank, world, refs, traffic)
+    torch.cuda.empty_cache()
+    cfg1 = config1_leg(torch, dev) if rank == 0 else None
     ffn = ffn_forward_leg(torch, dist, world, local_rank, xs[0], gamma, peaks)
     torch.cuda.empty_cache()
     ffn_bwd = ffn_backward_leg(torch, dist, world, xs[0], gamma, peaks)
@@ -720,7 +1014,6 @@ def main():
     mx_layer = mxfp4_layer_leg(torch, dist, world, gamma, peaks)
     torch.cuda.empty_cache()
     attn_side = attention_side_leg(torch, dist, world, peaks)
-    clocks = sampler.stop() if rank == 0 else None
 
     if rank == 0:
         cpu = None
@@ -733,16 +1026,26 @@ def main():
                            "l2": "inputs rotate over 3 copies of X (402 MB > 126 MB L2) between steps",
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
-                "cpu_baseline": cpu, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer_forward": mx_layer,
+                "cpu_baseline": cpu, "strong_scaling_point": small, "roofline_gemm": roofline_gemm,
+                "gemm_shapes": gemm_shapes, "reference_kernels_same_box": {"fused_rmsnorm_nvfp4_quant": ref_quant,
+                                                                            "load_errors": {k: v for k, v in refs.items() if k.endswith("_error")}},
+                "config1_quantize_gemm": cfg1, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer": mx_layer,
                 "attention_side": attn_side}
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one pass-2 launch at the bench size, from the ncu
-# capture summarised under profiles/.
-TRAFFIC_PER_LAUNCH = 134334208 + 38618624  # profiles/fused_rmsnorm_nvfp4_quant_16384x4096.md (in-kernel DRAM bytes)
+def load_traffic():
+    """DRAM bytes per launch (dram__bytes_read.sum + dram__bytes_write.sum) of the kernels the roofline blocks name,
+    from the ncu captures: a small JSON kept beside the profile summaries, {} when it is missing."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as f:
+            return json.load(f)
+    except (OSError, ValueError):
+        return {}
+
 
 if __name__ == "__main__":
     main()

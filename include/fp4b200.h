@@ -68,8 +68,9 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
  * those of the reference kernel, so equal (seed, offset) give equal bytes: 1 = on every pass of this
  * launch; 2 = row pass only, the bytes of the reference's row-only launch at rng_offset (its stream
  * has 8 words per stage), with the column pass rounded to nearest in the same launch; 3 = column pass
- * only, at rng_offset_col (the offset of the reference's separate column launch).  With 2 and 3 the
- * callers that the reference serves with two launches (one axis stochastic) read the input once.
+ * only, at rng_offset_col (the offset of the reference's separate column launch); 4 = both passes, the row pass
+ * as with 2 and the column pass as with 3.  With 2, 3 and 4 the callers that the reference serves with two
+ * launches (one axis stochastic, or a sign-masked transform) read the input once.
  * rht_row / rht_col: per-16 Hadamard transform (x0.25, rounded to bf16) along K for the row operand /
  * along M for the column operand, optionally after a sign flip hashed from (sign_seed, sign_subseq,
  * coordinate) (tk_quantize.cu:483-488,620-627).  gamma/inv_rms non-NULL fuse RMSNorm.  return_row = 0

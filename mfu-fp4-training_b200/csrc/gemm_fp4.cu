@@ -234,16 +234,16 @@ __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f 
 // them, and scaling, rounding, staging and the TMA stores run beside the next tile's MMAs.
 //   taddr  tensor-memory address of the first column in this warp's lane quadrant
 //   row0   first global row of this warp's 32 rows;  col0  first global column
-//   epi    this warp's NCOLS / 64 staging buffers of 4 KiB (32 rows x 128 bytes, 128-byte swizzle)
+//   epi    this warp's two staging buffers of 4 KiB (32 rows x 128 bytes, 128-byte swizzle); slab0 = which of them
+//          the call's first 128-byte slab goes to (consecutive slabs of consecutive calls alternate)
 // EPI selects the form: kEpiPlain bf16 (optional residual), kEpiRope with the rotary embedding, kEpiSilu with a
 // SiLU range (rotary or not), kEpiGeneral fp32 outputs or fp32 accumulation.
 // (Storing the rounded values straight from registers, 32 bytes per lane and store, instead of through the staging
 // buffers and TMA stores was measured: 8 % slower at N 28672, K 4096.)
 template <int EPI, int NCOLS, typename Release>
 __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
-                                                int row0, int col0, float a_sg, int lane, Release release) {
+                                                int row0, int col0, float a_sg, int lane, Release release, int slab0 = 0) {
   static_assert(NCOLS == 64 || NCOLS == 128, "one or two slabs of 64 columns");
-  constexpr int kBufs = NCOLS / 64;
   uint32_t r[NCOLS];
 #pragma unroll
   for (int k = 0; k < NCOLS / 32; ++k) tmem_ld32(taddr + (uint32_t)(32 * k), *reinterpret_cast<uint32_t(*)[32]>(&r[32 * k]));
@@ -259,12 +259,9 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
   const int ocol = col0 - col_start;
   uint8_t* rowp = epi + lane * 128;
   const int sw = lane & 7;
-  // a staging buffer may be rewritten once the store issued from it (kBufs slabs ago) has read it
+  // a staging buffer may be rewritten once the store issued from it two slabs ago has read it
   auto buffer_free = [&]() {
-    if (lane == 0) {
-      if constexpr (kBufs == 2) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
-      else asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-    }
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
     __syncwarp();
   };
   auto store_slab = [&](const uint8_t* buf, int x) {
@@ -297,21 +294,21 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
         for (int q = 0; q < 32; ++q) v[q] = __fmul_rn(__uint_as_float(r[32 * c + q]), gs);
       }
       if (g.out_fp32) {
-        uint8_t* buf = rowp + (c & (kBufs - 1)) * 4096;
+        uint8_t* buf = rowp + ((c + slab0) & 1) * 4096;
         buffer_free();
 #pragma unroll
         for (int q = 0; q < 8; ++q)
           *reinterpret_cast<float4*>(buf + ((q ^ sw) << 4)) = make_float4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
-        store_slab(epi + (c & (kBufs - 1)) * 4096, ocol + 32 * c);
+        store_slab(epi + ((c + slab0) & 1) * 4096, ocol + 32 * c);
       } else {
-        uint8_t* buf = rowp + (c >> 1) * 4096;
+        uint8_t* buf = rowp + (((c >> 1) + slab0) & 1) * 4096;
         if ((c & 1) == 0) buffer_free();
 #pragma unroll
         for (int q = 0; q < 4; ++q)
           *reinterpret_cast<uint4*>(buf + ((((c & 1) * 4 + q) ^ sw) << 4)) =
               make_uint4(f32x2_to_bf16x2(v[8 * q], v[8 * q + 1]), f32x2_to_bf16x2(v[8 * q + 2], v[8 * q + 3]),
                          f32x2_to_bf16x2(v[8 * q + 4], v[8 * q + 5]), f32x2_to_bf16x2(v[8 * q + 6], v[8 * q + 7]));
-        if (c & 1) store_slab(epi + (c >> 1) * 4096, ocol + 64 * (c >> 1));
+        if (c & 1) store_slab(epi + (((c >> 1) + slab0) & 1) * 4096, ocol + 64 * (c >> 1));
       }
     }
   } else {
@@ -322,7 +319,7 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
     // rope_col_end is 0 when there is no table (SiLU alone)
     const float2* cs_row = (ROPE && col0 < g.rope_col_end) ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
 #pragma unroll
-    for (int slab = 0; slab < kBufs; ++slab) {      // 64 columns = 128 bytes per row
+    for (int slab = 0; slab < NCOLS / 64; ++slab) { // 64 columns = 128 bytes per row
       uint32_t w[32];
 #pragma unroll
       for (int h = 0; h < 4; ++h) {                 // 16 columns = eight pairs
@@ -365,13 +362,28 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
           }
         }
       }
-      uint8_t* buf = rowp + slab * 4096;
+      uint8_t* buf = rowp + ((slab + slab0) & 1) * 4096;
       buffer_free();
 #pragma unroll
       for (int q = 0; q < 8; ++q)
         *reinterpret_cast<uint4*>(buf + ((q ^ sw) << 4)) = make_uint4(w[4 * q], w[4 * q + 1], w[4 * q + 2], w[4 * q + 3]);
-      store_slab(epi + slab * 4096, ocol + slab * 64);
+      store_slab(epi + ((slab + slab0) & 1) * 4096, ocol + slab * 64);
     }
+  }
+}
+
+// A region of 128 accumulator columns in the width the epilogue form's register budget affords: the plain and
+// general forms lift all 128 columns at once; the rotary and SiLU forms work on 64 at a time (with 128 raw values
+// live they spill, and with ~5 KB of L1 beside 222 KB of shared memory every spill is an L2 round trip), so their
+// release comes after the second half's loads.
+template <int EPI, typename Release>
+__device__ __forceinline__ void epilogue_region128(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
+                                                   int row0, int col0, float a_sg, int lane, Release release) {
+  if constexpr (EPI == kEpiRope || EPI == kEpiSilu) {
+    epilogue_region<EPI, 64>(g, tmap_d, taddr, epi, row0, col0, a_sg, lane, [] {}, 0);
+    epilogue_region<EPI, 64>(g, tmap_d, taddr + 64, epi, row0, col0 + 64, a_sg, lane, release, 1);
+  } else {
+    epilogue_region<EPI, 128>(g, tmap_d, taddr, epi, row0, col0, a_sg, lane, release, 0);
   }
 }
 
@@ -570,9 +582,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
       uint8_t* epi = &sm.epi[warp - 2][0][0];
       const int row0 = tm * kGemmBM + quad * 32;
-      epilogue_region<EPI, 128>(g, tmap_d, tq, epi, row0, tn * kGemmBN, a_sg, lane, [] {});
+      epilogue_region128<EPI>(g, tmap_d, tq, epi, row0, tn * kGemmBN, a_sg, lane, [] {});
       // both halves are out of tensor memory: let the MMA warp start the next tile
-      epilogue_region<EPI, 128>(g, tmap_d, tq + 128, epi, row0, tn * kGemmBN + 128, a_sg, lane, [&] {
+      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, tn * kGemmBN + 128, a_sg, lane, [&] {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(&sm.acc_empty);

@@ -301,12 +301,12 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int col0 = tn * kGemmBN;
       // tensor-memory columns [128, 256) hold output columns [128, 256) of a tile at [0, 256) and output
       // columns [0, 128) of a tile at [128, 384): lift them out first, the next tile needs them
-      epilogue_region<EPI, 128>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane, [&] {
+      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane, [&] {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(empty_shared_leader);
       });
-      epilogue_region<EPI, 128>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane, [&] {
+      epilogue_region128<EPI>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane, [&] {
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(kind ? empty_priv_leader1 : empty_priv_leader0);

@@ -480,6 +480,20 @@ __device__ __forceinline__ float rht_sign(unsigned long long seed, unsigned long
   const uint32_t h = (uint32_t)((x ^ (x >> 31)) >> 32);
   return (h & 1u) ? 1.0f : -1.0f;
 }
+// 1 where the sign of that coordinate is -1
+__device__ __forceinline__ uint32_t rht_sign_is_negative(unsigned long long seed, unsigned long long subseq,
+                                                         unsigned long long coord) {
+  return rht_sign(seed, subseq, coord) < 0.0f ? 1u : 0u;
+}
+// bit i = sign of coordinate coord0 + i is -1 (one thread, sixteen hashes: the slow form, for the kernels that are not
+// on the fast path; the strip quantiser shares one hash per lane through a ballot instead)
+__device__ __forceinline__ uint32_t rht_sign_mask16(unsigned long long seed, unsigned long long subseq,
+                                                    unsigned long long coord0) {
+  uint32_t m = 0;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) m |= rht_sign_is_negative(seed, subseq, coord0 + (unsigned long long)i) << i;
+  return m;
+}
 
 // unnormalised Sylvester butterflies (steps 1,2,4,8), then x0.25 (quantize_transpose_tuned.cuh:161-179)
 __device__ __forceinline__ void fwht16(float (&v)[16]) {
@@ -517,15 +531,15 @@ __device__ __forceinline__ uint2 quant16_rn(const float (&x)[16], float coeff) {
 }
 
 // transform (optional sign flip, Hadamard, bf16 rounding), block scale, codes of one 16-element block
+// neg_mask: bit i = element i is negated before the transform (the sign vector of the block's 16 coordinates; 0: none)
 template <bool ENCODE_CENTRIC>
-__device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, bool sign, unsigned long long sign_seed,
-                                           unsigned long long sign_subseq, unsigned long long coord0, float s_enc,
+__device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, uint32_t neg_mask, float s_enc,
                                            const ScaleLut* lut, bool sr, const uint32_t (&wsel)[4], uint32_t& stored,
                                            bool scale_sr = false, uint32_t scale_rbits = 0) {
   if (rht) {
-    if (sign) {
+    if (neg_mask != 0) {
 #pragma unroll
-      for (int i = 0; i < 16; ++i) x[i] *= rht_sign(sign_seed, sign_subseq, coord0 + (unsigned long long)i);
+      for (int i = 0; i < 16; ++i) x[i] = ((neg_mask >> i) & 1u) ? -x[i] : x[i];
     }
     fwht16(x);
 #pragma unroll
@@ -719,9 +733,8 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
 #pragma unroll
             for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
           }
-          cd[b] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
-                                            (unsigned long long)(k0 + lc0), s_enc_row, sm.lut_row, a.opt_sr_row != 0, wsel,
-                                            st_b[b]);
+          const uint32_t neg = (a.opt_sign && a.opt_rht_row) ? rht_sign_mask16(a.sign_seed, a.sign_subseq, (unsigned long long)(k0 + lc0)) : 0u;
+          cd[b] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, neg, s_enc_row, sm.lut_row, a.opt_sr_row != 0, wsel, st_b[b]);
         }
         if (a.opt_return_row) {
           st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1),
@@ -785,9 +798,8 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
               const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
               wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
             }
-            cd[wq] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
-                                               (unsigned long long)(m0 + warp * 16), s_enc_col, sm.lut_col,
-                                               a.opt_sr_col != 0, wsel, st_c[wq]);
+            const uint32_t neg = (a.opt_sign && a.opt_rht_col) ? rht_sign_mask16(a.sign_seed, a.sign_subseq, (unsigned long long)(m0 + warp * 16)) : 0u;
+            cd[wq] = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, neg, s_enc_col, sm.lut_col, a.opt_sr_col != 0, wsel, st_c[wq]);
           }
           q = make_uint4(cd[0].x, cd[0].y, cd[1].x, cd[1].y);
           st0 = st_c[0]; st1 = st_c[1];
@@ -1120,6 +1132,12 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         // launch has one, a column pass of 2 x 4 words; quantize_transpose_tuned.cuh:392-528): the word
         // for an element depends only on its position, so any kernel shape reproduces it.
         const int rc = wv * kStripRows + lane;        // row inside the chunk
+        // sign vector of the strip's 64 columns: one hash per lane and half, shared through a ballot
+        uint32_t row_neg_lo = 0, row_neg_hi = 0;
+        if (a.opt_sign && a.opt_rht_row && a.opt_return_row) {
+          row_neg_lo = __ballot_sync(0xffffffffu, rht_sign_is_negative(a.sign_seed, a.sign_subseq, (unsigned long long)(col0 + lane)) != 0);
+          row_neg_hi = __ballot_sync(0xffffffffu, rht_sign_is_negative(a.sign_seed, a.sign_subseq, (unsigned long long)(col0 + 32 + lane)) != 0);
+        }
         if (a.opt_return_row) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
@@ -1161,9 +1179,9 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
               }
             }
             uint32_t stored;
-            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
-                                                       (unsigned long long)(col0 + b * 16), s_enc_row, lut_row,
-                                                       a.opt_sr_row != 0, wsel, stored, kScaleSr, scale_rbits);
+            const uint32_t neg = ((b < 2 ? row_neg_lo : row_neg_hi) >> (16 * (b & 1))) & 0xFFFFu;
+            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, neg, s_enc_row, lut_row, a.opt_sr_row != 0, wsel,
+                                                       stored, kScaleSr, scale_rbits);
             codes[2 * b] = cd.x;
             codes[2 * b + 1] = cd.y;
             sc_word |= stored << (8 * b);
@@ -1199,6 +1217,11 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       if constexpr (NORM) __syncwarp();   // the normalised rows of all lanes are in the slot
       uint32_t cc0[4], cc1[4];            // codes of columns c and c+1: rows 0..7, 8..15, 16..23, 24..31
       uint32_t sc0 = 0, sc1 = 0;
+      uint32_t col_neg = 0;               // sign vector of the strip's 32 rows: one hash per lane, shared through a ballot
+      if constexpr (OPT != 0) {
+        if (a.opt_sign && a.opt_rht_col)
+          col_neg = __ballot_sync(0xffffffffu, rht_sign_is_negative(a.sign_seed, a.sign_subseq, (unsigned long long)(row0 + lane)) != 0);
+      }
 #pragma unroll
       for (int g = 0; g < 2; ++g) {
         const uint8_t* gbase = tile + g * 16 * 128;
@@ -1241,8 +1264,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
               }
             }
             uint32_t stored;
-            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, a.opt_sign != 0, a.sign_seed, a.sign_subseq,
-                                                       (unsigned long long)(cm * kChunk + grp16 * 16), s_enc_col, lut_col,
+            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, (col_neg >> (16 * g)) & 0xFFFFu, s_enc_col, lut_col,
                                                        a.opt_sr_col != 0, wsel, stored, kScaleSr, scale_rbits);
             if (wq == 0) { cc0[2 * g] = cd.x; cc0[2 * g + 1] = cd.y; sc0 |= stored << (8 * g); }
             else { cc1[2 * g] = cd.x; cc1[2 * g + 1] = cd.y; sc1 |= stored << (8 * g); }
@@ -1347,8 +1369,13 @@ rht16_amax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
       coord0 = rb * 16;
     }
     if (sign) {
+      // scan along M: the 32 lanes of a warp hold 32 columns of ONE 16-row group (K is a multiple of 128 and the
+      // grid stride a multiple of 32), so sixteen lanes hash one row each and share the mask
+      const uint32_t neg = along_k ? rht_sign_mask16(sign_seed, sign_subseq, (unsigned long long)coord0)
+                                   : (__ballot_sync(0xffffffffu, (threadIdx.x & 31) < 16 &&
+                                          rht_sign_is_negative(sign_seed, sign_subseq, (unsigned long long)(coord0 + (threadIdx.x & 15))) != 0) & 0xFFFFu);
 #pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] *= rht_sign(sign_seed, sign_subseq, (unsigned long long)(coord0 + i));
+      for (int i = 0; i < 16; ++i) v[i] = ((neg >> i) & 1u) ? -v[i] : v[i];
     }
     fwht16(v);
 #pragma unroll
@@ -1810,10 +1837,12 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
     return set_error("nvfp4_quantize_opt: col_fp4 and col_sc must both be given or both be null");
   if (!return_row && !col_fp4) return set_error("nvfp4_quantize_opt: nothing to compute");
   QuantOpt o{};
-  if (data_sr < 0 || data_sr > 3) return set_error("nvfp4_quantize_opt: data_sr must be 0 (off), 1 (both passes), 2 (row pass) or 3 (column pass)");
-  o.sr_row = data_sr == 1 || data_sr == 2; o.sr_col = data_sr == 1 || data_sr == 3;
+  if (data_sr < 0 || data_sr > 4)
+    return set_error("nvfp4_quantize_opt: data_sr must be 0 (off), 1 (both passes, one stream), 2 (row pass), 3 (column pass) or "
+                     "4 (both passes, a stream each)");
+  o.sr_row = data_sr == 1 || data_sr == 2 || data_sr == 4; o.sr_col = data_sr == 1 || data_sr == 3 || data_sr == 4;
   // a row-only stochastic launch of the reference draws 8 words per stage, also when this launch adds the column pass
-  o.row_per_stage = (data_sr == 2 || data_sr == 3) ? 8 : 0;
+  o.row_per_stage = (data_sr >= 2) ? 8 : 0;
   o.scale_sr = scale_sr != 0;
   o.rng_offset_col = (data_sr == 0 || data_sr == 1) ? rng_offset : rng_offset_col;   // one launch of the reference: one stream
   o.rht_row = rht_row != 0; o.rht_col = rht_col != 0; o.sign = with_sign != 0;

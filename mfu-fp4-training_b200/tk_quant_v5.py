@@ -546,7 +546,17 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
         else:
             col_amax = row_amax
         row_mat, col_mat = row_rht and sign, col_rht and sign     # the reference materialises these
-        if return_transpose and not row_mat and row_sr == col_sr and not col_mat:
+        if return_transpose and (row_mat or col_mat) and not (scale_sr and not (row_sr or col_sr)):
+            # the reference runs a row launch and a column launch over a sign-flipped, transformed copy; the sign
+            # flip happens inside this library's transform, so one launch reads the input once and gives each pass
+            # the stream of its reference launch
+            off_r = _next_offset(input, rng_subsequence, use_sr)
+            off_c = _next_offset(input, rng_subsequence, use_sr)
+            mode = 0 if not (row_sr or col_sr) else (4 if (row_sr and col_sr) else (2 if row_sr else 3))
+            rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr or col_sr, encode_centric, row_rht, col_rht,
+                                         True, rng_seed, off_r, sign, rng_seed, rng_subsequence, sr_mode=mode,
+                                         offset_col=off_c, scale_sr=scale_sr)
+        elif return_transpose and not row_mat and row_sr == col_sr and not col_mat:
             off = _next_offset(input, rng_subsequence, use_sr)
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr, encode_centric, row_rht, col_rht,
                                          True, rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)

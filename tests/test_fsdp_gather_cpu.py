@@ -56,6 +56,23 @@ def _worker(rank, world, port, q):
         ref = o.mxfp4_quantize_row_and_col(w, 1)
         ok = ok and all(np.array_equal(out[i].numpy().reshape(ref[k].shape), ref[k])
                         for i, k in enumerate(["row_fp4", "row_sc", "col_fp4", "col_sc"]))
+        # a layer's weights at once: one amax all-reduce over the stacked maxima, one group of all-gathers
+        w2 = o.bf16_round((0.03 * np.random.default_rng(6).standard_normal((256, 384))).astype(np.float32))
+        w2[5, 5] = -0.75      # this one's tensor amax lives in rank 0's shard
+        w2 = o.bf16_round(w2)
+        shard2 = torch.from_numpy(w2[rank * 256 // world:(rank + 1) * 256 // world]).to(torch.bfloat16).contiguous()
+        for want_col in (True, False):
+            outs = fsdp.all_gather_nvfp4_weights([shard, shard2], None, want_col, True, quantize_shard=_oracle_nvfp4)
+            for got, full in zip(outs, (w, w2)):
+                ref = o.nvfp4_quantize_for_gemm(full, True, True)
+                keys = ["row_fp4", "row_sc"] + (["col_fp4", "col_sc"] if want_col else [])
+                ok = ok and all(np.array_equal(got[i].numpy().reshape(ref[k].shape), ref[k]) for i, k in enumerate(keys))
+                ok = ok and got[4].item() == ref["sg"] and (want_col or got[2] is None)
+        outs = fsdp.all_gather_mxfp4_weights([shard, shard2], None, True, 1, quantize_shard=_oracle_mxfp4)
+        for got, full in zip(outs, (w, w2)):
+            ref = o.mxfp4_quantize_row_and_col(full, 1)
+            ok = ok and all(np.array_equal(got[i].numpy().reshape(ref[k].shape), ref[k])
+                            for i, k in enumerate(["row_fp4", "row_sc", "col_fp4", "col_sc"]))
         bad = False
         try:
             fsdp.all_gather_nvfp4_weight(shard[:100].contiguous(), None)

@@ -36,6 +36,26 @@ def _worker(rank, world, port, q):
         out = fsdp.all_gather_mxfp4_weight(shard, None, True, 1)
         ref = mxq.mxfp4_quantize_row_and_col(wd, 1)
         ok = ok and all(torch.equal(out[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
+        # a layer's weights at once (one amax all-reduce, one group of all-gathers)
+        w2 = (0.03 * torch.randn(512, 768, generator=g)).to(torch.bfloat16)
+        w2[9, 9] = -0.9
+        w2d = w2.cuda()
+        shard2 = w2d[rank * 512 // world:(rank + 1) * 512 // world].contiguous()
+        for want_col in (True, False):
+            outs = fsdp.all_gather_nvfp4_weights([shard, shard2], None, want_col, True)
+            for got, full in zip(outs, (wd, w2d)):
+                ref = tkq.tk_quantize_for_gemm(full, True, True)
+                ok = ok and all(torch.equal(got[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4 if want_col else 2))
+                ok = ok and got[4].item() == ref[4].item()
+        for _ in range(2):   # the kept send / receive buffers give the same bytes on every call
+            outs = fsdp.all_gather_nvfp4_weights([shard, shard2], None, True, True, reuse_buffers=True)
+            for got, full in zip(outs, (wd, w2d)):
+                ref = tkq.tk_quantize_for_gemm(full, True, True)
+                ok = ok and all(torch.equal(got[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
+        outs = fsdp.all_gather_mxfp4_weights([shard, shard2], None, True, 1)
+        for got, full in zip(outs, (wd, w2d)):
+            ref = mxq.mxfp4_quantize_row_and_col(full, 1)
+            ok = ok and all(torch.equal(got[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
         torch.cuda.synchronize()
         q.put((rank, bool(ok)))
     finally:
