@@ -193,13 +193,17 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   // that its row's copy has been issued (which implies that the use before it was fully consumed).
   volatile int* uses = reinterpret_cast<volatile int*>(bars + n_slots);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int band = (M + gridDim.x - 1) / gridDim.x;
-  const int band0 = blockIdx.x * band;
-  const int n_band = min(band, M - band0);    // rows of this CTA (<= 0: nothing to do)
-  auto issue = [&](int r) {                   // r: band-relative row -> slot r % n_slots
+  // Rows are dealt round-robin: CTA b takes rows b, b + grid, b + 2*grid, ...  All CTAs so sweep x from its first
+  // row to its last together, and what the L2 still holds when the kernel ends is the END of x — which the
+  // quantiser launched next walks first (it goes through the row blocks backwards).  The copies carry an
+  // evict-last hint for the same reason: the quantiser's own output must not push x out.
+  const int n_band = (int)blockIdx.x < M ? (M - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;   // rows of this CTA
+  const uint64_t keep = l2_policy_evict_last();
+  auto row_of = [&](int r) { return (size_t)r * gridDim.x + blockIdx.x; };
+  auto issue = [&](int r) {                   // r: this CTA's r-th row -> slot r % n_slots
     const int s = r % n_slots;
     mbar_expect_tx(&bars[s], row_bytes);
-    bulk_load_1d(slots + (size_t)s * row_bytes, x + (size_t)(band0 + r) * K, row_bytes, &bars[s]);
+    bulk_load_1d_hint(slots + (size_t)s * row_bytes, x + row_of(r) * K, row_bytes, &bars[s], keep);
     __threadfence_block();
     uses[s] = r / n_slots + 1;
   };
@@ -254,7 +258,7 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       const int q = lane + 32 * j;
       v[j] = (q < nvec_row) ? src[q] : make_uint4(0, 0, 0, 0);
     }
-    const int row = band0 + r;
+    const size_t row = row_of(r);
     float inv;
     if constexpr (COMPUTE_INV_RMS) {
       inv = stats_inv_rms<NV>(v, K, eps);
@@ -999,6 +1003,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     cm = c / a.chunks_k;
     ck = c - cm * a.chunks_k;
   };
+  const uint64_t use_once = l2_policy_evict_first();   // the input's last use and the outputs: nothing to keep in L2
   auto issue_load = [&](int sit, int s) {
     int cm, ck;
     chunk_coords(sit >> pair, cm, ck);
@@ -1011,7 +1016,8 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       y = (b * a.nhsd_heads + (x >> 6)) * a.nhsd_seq + (y - b * a.nhsd_seq);
       x = 0;
     }
-    tma_load_2d(my_slots + (size_t)s * kStripBytes, &tmap_x, x, y, &my_bars[s]);
+    // read once here: the lines (kept in L2 by the statistics pass for this kernel) become the first to go
+    tma_load_2d_hint(my_slots + (size_t)s * kStripBytes, &tmap_x, x, y, &my_bars[s], use_once);
   };
 
   if (tid == 0) {
@@ -1327,7 +1333,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     __syncwarp();
     if (lane == 0) {
       if (!OPT || a.opt_return_row) {
-        tma_store_2d(&tmap_row, my_stage, col0 >> 1, row0);
+        tma_store_2d_hint(&tmap_row, my_stage, col0 >> 1, row0, use_once);
         bulk_commit_group();
       }
       if (it + depth < my_count) issue_load(it + depth, s);
