@@ -205,6 +205,12 @@ int fp4b200_silu_deriv_bf16(const void* dh, const void* h3, const void* h1, int6
  * sets it at load.  No counterpart in the reference. */
 int fp4b200_set_pdl_early_reads(int enabled);
 
+/* No counterpart in the reference.  Launches a one-warp kernel that waits, with the same bounded wait every kernel
+ * of this library uses, on a barrier nothing will arrive on: after limit_cycles (1 .. 1e8) clock cycles it gives
+ * up, stores status code 6 and returns.  fp4b200_device_status() then reports 6 once and 0 afterwards.  For tests of
+ * the failure-reporting path; no copy is in flight and nothing is left waiting. */
+int fp4b200_selftest_bounded_wait(int64_t limit_cycles, void* stream);
+
 /* Switches that launch attribute for the GEMM calls of the calling thread (1 = on, the default; 0 = ordinary
  * launches) and returns the previous setting: what the reference's *_nopdl entry points select
  * (nvfp4_b200_gemm.cu:1702-1735; kernel nvfp4_gemm.cuh:577,596,1002).  FP4B200_GEMM_PDL=0 in the environment

@@ -54,6 +54,7 @@ SIGNATURES = {
     "fp4b200_silu_deriv_bf16": [_c_void_p, _c_void_p, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                 _c_void_p],
     "fp4b200_set_gemm_pdl": [_int],
+    "fp4b200_selftest_bounded_wait": [_i64, _c_void_p],
     "fp4b200_set_pdl_early_reads": [_int],
     "fp4b200_nvfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int,
                            _c_void_p, _i64, _i64, _i64, _c_void_p],

@@ -22,6 +22,7 @@ enum StatusCode : int {
   kStatusGemmMmaTimeout = 3,
   kStatusGemmEpilogueTimeout = 4,
   kStatusGemmTmemTimeout = 5,
+  kStatusSelfTestTimeout = 6,
 };
 
 // ---------------------------------------------------------------------------------------

@@ -96,13 +96,25 @@ struct GemmArgs {
   int* status;
 };
 
-__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity, long long limit_cycles = kWaitLimitCycles) {
   if (mbar_try_wait(bar, parity)) return true;
   const long long t0 = clock64();
   while (!mbar_try_wait(bar, parity)) {
-    if (clock64() - t0 > kWaitLimitCycles) return false;
+    if (clock64() - t0 > limit_cycles) return false;
   }
   return true;
+}
+
+// Exercises the give-up path of mbar_wait_timed in the safe form: one warp, a barrier that nothing will ever arrive
+// on, no copy in flight, a limit of the caller's choosing.  The wait runs out, the status word gets its code and the
+// kernel returns like any other.
+__global__ void bounded_wait_selftest_kernel(int* status, long long limit_cycles) {
+  __shared__ alignas(8) uint64_t bar;
+  if (threadIdx.x == 0) {
+    mbar_init(&bar, 1);
+    fence_mbar_init();
+    if (!mbar_wait_timed(&bar, 0, limit_cycles)) atomicExch(status, kStatusSelfTestTimeout);
+  }
 }
 
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -791,6 +803,15 @@ static int check_gemm(const void* A, const void* A_sc, const void* B, const void
 }
 
 extern "C" {
+
+int fp4b200_selftest_bounded_wait(int64_t limit_cycles, void* stream) {
+  if (limit_cycles < 1 || limit_cycles > 100000000) return set_error("selftest_bounded_wait: the limit must be 1 to 1e8 cycles");
+  int* status = device_status_ptr();
+  if (status == nullptr) return -1;
+  bounded_wait_selftest_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(status, (long long)limit_cycles);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 int fp4b200_set_gemm_pdl(int enabled) {
   const int before = t_gemm_pdl;

@@ -95,6 +95,10 @@ def _rowcol_sr(input, mode, data_sr, scale_sr, rht_block, sign, row_rht, col_rht
     M, K = _check_bf16_2d(input, "input")
     base = int(rng_subsequence) & 0xFFFFFFFFFFFFFFFF
     if data_sr or scale_sr or (rht_block and sign):   # the launches that prepare a generator state (tk_quantize.cu:2853-2860)
+        if torch.cuda.is_current_stream_capturing():
+            # host-side launch number: a captured graph would replay one offset on every launch
+            raise RuntimeError("stochastic rounding inside CUDA-graph capture would replay one Philox offset on every "
+                               "graph launch: run the stochastic quantisers outside the captured region")
         base = (base + _sr_invocations * _SR_INVOCATION_STRIDE) & 0xFFFFFFFFFFFFFFFF
         _sr_invocations += 1
     with torch.cuda.device(input.device):

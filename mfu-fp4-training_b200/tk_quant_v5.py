@@ -437,6 +437,12 @@ def _next_offset(t, rng_subsequence, use_sr):
     idx = t.device.index
     n = _sr_invocations.get(idx, 0)
     if use_sr:
+        # The launch number is host state: a CUDA graph would bake this launch's offset in and replay the same
+        # random words on every step (the reference numbers its launches on the device, tk_quantize.cu:443-481).
+        # Refuse rather than round with correlated noise.
+        if torch.cuda.is_current_stream_capturing():
+            raise RuntimeError("stochastic rounding inside CUDA-graph capture would replay one Philox offset on every "
+                               "graph launch: run the stochastic quantisers outside the captured region")
         _sr_invocations[idx] = n + 1
     return (int(rng_subsequence) + n * (1 << 32)) & _U64
 

@@ -10,13 +10,19 @@ import pytest
 REQUIRED = {
     "_tk_quant_v5": ["tk_quantize_for_gemm", "tk_quantize_weight_2d", "tk_fused_norm_quantize",
                      "tk_fused_norm_quantize_from_inv_rms", "tk_silu_quantize_split_for_gemm",
-                     "tk_silu_deriv_quantize_split_for_gemm", "tk_silu_deriv_quantize_split_for_gemm_opt"],
+                     "tk_silu_deriv_quantize_split_for_gemm", "tk_silu_deriv_quantize_split_for_gemm_opt",
+                     "tk_quantize_for_gemm_opt", "tk_quantize_transpose", "tk_fused_norm_quantize_opt",
+                     "tk_quantize_nhsd_wo_for_gemm", "tk_group_quantize_dim1_split3_for_gemm"],
+    # tk_gemm.py:3454-3461 dereferences nvfp4_split_dgrad_sum and nvfp4_batched_accum_gemm unconditionally
     "_C": ["nvfp4_gemm", "nvfp4_gemm_config", "nvfp4_gemm_nopdl", "nvfp4_grouped_gemm", "nvfp4_gemm_residual",
-           "nvfp4_batched_gemm"],
+           "nvfp4_batched_gemm", "nvfp4_split_dgrad_sum", "nvfp4_batched_accum_gemm", "nvfp4_forward_rope_packed_qk",
+           "nvfp4_inverse_rope_packed_qk", "nvfp4_grouped_gemm_rope_packed_split", "sum3_rmsnorm_bwd_out",
+           "rmsnorm_bwd_residual_out"],
     "mxfp4_quant_v4": ["mxfp4_quantize_for_gemm", "mxfp4_quantize_row_and_col",
-                       "mxfp4_fused_rmsnorm_quantize_row_and_col", "mxfp4_fused_silu_mul_quantize_row_and_col"],
+                       "mxfp4_fused_rmsnorm_quantize_row_and_col", "mxfp4_fused_silu_mul_quantize_row_and_col",
+                       "mxfp4_quantize_for_gemm_opt_rht", "mxfp4_quantize_weight_2d", "mxfp4_quantize_row_and_col_opt"],
     "_C_mx": ["mxfp4_gemm", "mxfp4_gemm_config", "mxfp4_batched_gemm", "mxfp4_batched_gemm_config",
-              "mxfp4_gemm_residual"],
+              "mxfp4_gemm_residual", "mxfp4_split2_dgrad_strided_onepass_gemm"],
 }
 
 

@@ -110,3 +110,30 @@ def test_fused_norm_quantize_and_rmsnorm_backward_in_a_graph():
         assert torch.equal(q[i].view(torch.uint8), eager[i].view(torch.uint8)), i
     assert torch.equal(q[5], eager[5]) and torch.equal(dx_g, dx) and torch.equal(dg_g, dgamma)
     assert_status_ok()
+
+
+def test_stochastic_rounding_is_refused_inside_capture():
+    """The stochastic quantisers number their launches on the host, so a captured launch would replay one Philox
+    offset on every graph launch (correlated rounding noise step after step).  They raise instead, without having
+    advanced the launch counter, and the capture itself survives."""
+    tkq, mxq = mod("tk_quant_v5"), mod("mxfp4_quant_v4")
+    x = (1e-3 * torch.randn(256, 256, device="cuda")).to(torch.bfloat16)
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        tkq.tk_quantize_for_gemm(x, True, False)          # the stream's first call (per-stream scratch) outside capture
+    side.synchronize()
+    before = tkq.tk_sr_invocation_count()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        with pytest.raises(RuntimeError, match="graph"):
+            tkq.tk_quantize_for_gemm_opt(x, True, False, True, False, "none", False, 1, 0, 448.0, "row")
+        with pytest.raises(RuntimeError, match="graph"):
+            mxq.mxfp4_quantize_row_and_col_opt(x, 1, True, False, 1, 0)
+        out = tkq.tk_quantize_for_gemm(x, True, False)     # round to nearest captures as before
+    assert tkq.tk_sr_invocation_count() == before
+    g.replay()
+    torch.cuda.synchronize()
+    ref = tkq.tk_quantize_for_gemm(x, True, False)
+    assert torch.equal(out[0].view(torch.uint8), ref[0].view(torch.uint8))
+    assert_status_ok()

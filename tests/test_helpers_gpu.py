@@ -166,3 +166,19 @@ def test_rope_packed_qk_forward_and_inverse(head):
     with pytest.raises(RuntimeError):
         gemm.nvfp4_forward_rope_packed_qk(qd, kd, csd[:96].contiguous(), 96, head, qf, kf)   # not a power of two
     assert_status_ok()
+
+
+def test_a_bounded_wait_that_runs_out_reports_through_the_status_word():
+    """No kernel of the library spins without a limit: a wait that runs out stores a code in the device's status
+    word and the kernel returns.  The self-test kernel makes that happen harmlessly (a barrier nobody arrives on,
+    ~50 us limit); the host then reads the code once, and 0 afterwards, and the context stays usable."""
+    lib = mod("_lib")
+    assert lib.device_status() == 0
+    lib.call("fp4b200_selftest_bounded_wait", 100000, torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    assert lib.device_status() == 6          # kStatusSelfTestTimeout; reading clears the word
+    assert lib.device_status() == 0
+    x = torch.ones(8, device="cuda")
+    assert (x + 1).sum().item() == 16.0      # the context is alive
+    with pytest.raises(RuntimeError, match="1 to 1e8"):
+        lib.call("fp4b200_selftest_bounded_wait", 0, None)

@@ -56,6 +56,36 @@ def test_noalloc_matches_allocating_entry_point_twice():
     assert_status_ok()
 
 
+def test_noalloc_against_the_oracle():
+    """The same entry point against the CPU oracle alone, so that its check does not lean on another entry point of
+    this library.  The oracle's inverse RMS comes from a float32 tree and a correctly rounded reciprocal square root,
+    the GPU's from its own `rsqrtf` (<= 2e-6 relative apart), and this entry point does not hand its inverse RMS out;
+    a normalised value that sits on a bf16 rounding boundary may therefore land one code apart: at most 1 byte in
+    1000 may differ, and the tensor scale to 1 part in 1e5."""
+    lib = mod("_lib")
+    M, K = 256, 512
+    x = o.make_activations(M, K, seed=211)
+    gamma = o.make_gamma(K, seed=212)
+    xd, gd = to_dev_bf16(x), to_dev_bf16(gamma)
+    u8 = dict(dtype=torch.uint8, device="cuda")
+    out = (torch.empty((M, K // 2), **u8), torch.empty((M * K // 16,), **u8), torch.empty((K, M // 2), **u8),
+           torch.empty((M * K // 16,), **u8))
+    sg = torch.zeros(1, dtype=torch.float32, device="cuda")
+    for _ in range(2):
+        lib.call("fp4b200_nvfp4_fused_norm_quantize_noalloc", xd.data_ptr(), gd.data_ptr(), 1e-5, M, K, out[0].data_ptr(),
+                 out[1].data_ptr(), out[2].data_ptr(), out[3].data_ptr(), sg.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    inv = o.rmsnorm_inv_rms(x, 1e-5)
+    ref = o.nvfp4_quantize_for_gemm(o.rmsnorm_apply(x, inv, o.bf16_round(gamma)), True, True)
+    assert abs(sg.item() / ref["sg"] - 1.0) < 1e-5
+    for got, key in zip(out, ("row_fp4", "row_sc", "col_fp4", "col_sc")):
+        got = got.cpu().numpy().reshape(-1)
+        want = np.asarray(ref[key]).reshape(-1)
+        assert got.size == want.size
+        assert (got != want).mean() <= 1e-3, f"{key}: {(got != want).mean():.5f} of the bytes differ from the oracle"
+    assert_status_ok()
+
+
 def test_noalloc_rejects_too_many_rows():
     lib = mod("_lib")
     x = torch.zeros(128, 128, dtype=torch.bfloat16, device="cuda")
