@@ -92,6 +92,7 @@ struct GemmArgs {
   int rope_seq_mask, rope_pair_dim, rope_head_mask, rope_col_end;
   int rope_round_bf16;      // round the scaled accumulator to bf16 before the rotation ("packed" forms)
   int silu_col_end;         // > 0: x / (1 + __expf(-x)) on the scaled accumulator of the columns [0, silu_col_end), before any rotation
+  int rope_in_tmem;         // pair kernel, heads of 64 or 128: each row's (cos, sin) table row lives in tensor memory
   int M, N, K;              // K = sum of the segments
   int* status;
 };
@@ -183,6 +184,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+      : "r"(taddr)
+      : "memory");
+}
 
 // registers -> 32 lanes x 16 / 32 columns of tensor memory (this warp's lane quadrant)
 __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&r)[16]) {
@@ -252,15 +262,35 @@ __device__ __forceinline__ float silu_fast(float x) { return __fdividef(x, 1.0f 
 // SiLU range (rotary or not), kEpiGeneral fp32 outputs or fp32 accumulation.
 // (Storing the rounded values straight from registers, 32 bytes per lane and store, instead of through the staging
 // buffers and TMA stores was measured: 8 % slower at N 28672, K 4096.)
-template <int EPI, int NCOLS, typename Release>
-__device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
-                                                int row0, int col0, float a_sg, int lane, Release release, int slab0 = 0) {
+// What an epilogue warp does once a range of accumulator columns is in its registers: one arrival on the barrier the
+// MMA thread waits on (a barrier of this CTA, or of the leader CTA of a pair), or nothing.
+struct AccRelease {
+  uint64_t* local = nullptr;        // barrier in this CTA's shared memory
+  uint32_t cluster_addr = 0;        // or: shared::cluster address of a barrier of another CTA
+  __device__ __forceinline__ void operator()(int lane) const {
+    if (local == nullptr && cluster_addr == 0) return;
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      if (cluster_addr != 0) asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+      else mbar_arrive(local);
+    }
+  }
+};
+
+// CS_TMEM: the rotary table's rows come from tensor memory (cs_taddr) instead of global memory.
+// Not inlined: with the forms' bodies inlined at every call site the register allocation of the whole kernel suffers
+// (the rotary forms spilled a kilobyte per thread).
+template <int EPI, int NCOLS, bool CS_TMEM = false>
+__device__ __noinline__ void epilogue_region(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
+                                                int row0, int col0, float a_sg, int lane, AccRelease release, int slab0 = 0,
+                                                uint32_t cs_taddr = 0) {
   static_assert(NCOLS == 64 || NCOLS == 128, "one or two slabs of 64 columns");
   uint32_t r[NCOLS];
 #pragma unroll
   for (int k = 0; k < NCOLS / 32; ++k) tmem_ld32(taddr + (uint32_t)(32 * k), *reinterpret_cast<uint32_t(*)[32]>(&r[32 * k]));
   tmem_ld_wait();
-  release();
+  release(lane);
   if (col0 >= g.N) return;   // second half of the last column tile when N is an odd multiple of 128
 
   float gs = a_sg;
@@ -329,7 +359,8 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
     const float2 gs2 = make_float2(gs, gs);
     const __nv_bfloat16* res_row = g.residual != nullptr ? g.residual + (size_t)row * g.residual_ld + col0 : nullptr;
     // rope_col_end is 0 when there is no table (SiLU alone)
-    const float2* cs_row = (ROPE && col0 < g.rope_col_end) ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
+    const bool rope_region = ROPE && g.rope_cs != nullptr && col0 < g.rope_col_end;
+    const float2* cs_row = (rope_region && !CS_TMEM) ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
 #pragma unroll
     for (int slab = 0; slab < NCOLS / 64; ++slab) { // 64 columns = 128 bytes per row
       uint32_t w[32];
@@ -337,13 +368,24 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
       for (int h = 0; h < 4; ++h) {                 // 16 columns = eight pairs
         const int col = slab * 64 + h * 16;
         const bool silu_here = SILU && col0 + col < g.silu_col_end;
-        const bool rope_here = ROPE && cs_row != nullptr && col0 + col < g.rope_col_end;
+        const bool rope_here = rope_region && col0 + col < g.rope_col_end;
         float4 cs[4];
         if (rope_here) {
-          // (cos, sin) of this lane's token and of the pairs' positions inside their head: 64 contiguous bytes
-          const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
+          // (cos, sin) of this lane's token and of the pairs' positions inside their head: 64 contiguous bytes of
+          // the table — or sixteen columns of this lane's copy of its table row in tensor memory (pair kernel)
+          if constexpr (CS_TMEM) {
+            uint32_t t[16];
+            tmem_ld16(cs_taddr + (uint32_t)((col0 + col) & g.rope_head_mask), t);
+            tmem_ld_wait();
 #pragma unroll
-          for (int q = 0; q < 4; ++q) cs[q] = __ldg(p + q);
+            for (int q = 0; q < 4; ++q)
+              cs[q] = make_float4(__uint_as_float(t[4 * q]), __uint_as_float(t[4 * q + 1]), __uint_as_float(t[4 * q + 2]),
+                                  __uint_as_float(t[4 * q + 3]));
+          } else {
+            const float4* p = reinterpret_cast<const float4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
+#pragma unroll
+            for (int q = 0; q < 4; ++q) cs[q] = __ldg(p + q);
+          }
         }
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
@@ -388,12 +430,18 @@ __device__ __forceinline__ void epilogue_region(const GemmArgs& g, const GemmOut
 // general forms lift all 128 columns at once; the rotary and SiLU forms work on 64 at a time (with 128 raw values
 // live they spill, and with ~5 KB of L1 beside 222 KB of shared memory every spill is an L2 round trip), so their
 // release comes after the second half's loads.
-template <int EPI, typename Release>
+template <int EPI>
 __device__ __forceinline__ void epilogue_region128(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
-                                                   int row0, int col0, float a_sg, int lane, Release release) {
+                                                   int row0, int col0, float a_sg, int lane, AccRelease release,
+                                                   uint32_t cs_taddr = 0) {
   if constexpr (EPI == kEpiRope || EPI == kEpiSilu) {
-    epilogue_region<EPI, 64>(g, tmap_d, taddr, epi, row0, col0, a_sg, lane, [] {}, 0);
-    epilogue_region<EPI, 64>(g, tmap_d, taddr + 64, epi, row0, col0 + 64, a_sg, lane, release, 1);
+    if (cs_taddr != 0) {
+      epilogue_region<EPI, 64, true>(g, tmap_d, taddr, epi, row0, col0, a_sg, lane, AccRelease{}, 0, cs_taddr);
+      epilogue_region<EPI, 64, true>(g, tmap_d, taddr + 64, epi, row0, col0 + 64, a_sg, lane, release, 1, cs_taddr);
+    } else {
+      epilogue_region<EPI, 64>(g, tmap_d, taddr, epi, row0, col0, a_sg, lane, AccRelease{}, 0);
+      epilogue_region<EPI, 64>(g, tmap_d, taddr + 64, epi, row0, col0 + 64, a_sg, lane, release, 1);
+    }
   } else {
     epilogue_region<EPI, 128>(g, tmap_d, taddr, epi, row0, col0, a_sg, lane, release, 0);
   }
@@ -594,13 +642,9 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
       const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
       uint8_t* epi = &sm.epi[warp - 2][0][0];
       const int row0 = tm * kGemmBM + quad * 32;
-      epilogue_region128<EPI>(g, tmap_d, tq, epi, row0, tn * kGemmBN, a_sg, lane, [] {});
+      epilogue_region128<EPI>(g, tmap_d, tq, epi, row0, tn * kGemmBN, a_sg, lane, AccRelease{});
       // both halves are out of tensor memory: let the MMA warp start the next tile
-      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, tn * kGemmBN + 128, a_sg, lane, [&] {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&sm.acc_empty);
-      });
+      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, tn * kGemmBN + 128, a_sg, lane, AccRelease{&sm.acc_empty, 0});
       acc_phase ^= 1;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // staged stores have left shared memory
@@ -703,6 +747,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     g.rope_round_bf16 = rope->round_bf16; g.silu_col_end = rope->silu_col_end;
   }
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
+  g.rope_in_tmem = pair && g.rope_cs != nullptr && (rope->head_dim == 64 || rope->head_dim == 128);
   g.status = device_status_ptr();
   if (g.status == nullptr) return -1;
   const int epi = (g.out_fp32 || g.accum_f32 != nullptr) ? kEpiGeneral

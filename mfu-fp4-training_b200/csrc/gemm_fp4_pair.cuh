@@ -71,6 +71,34 @@ __device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
                : "memory");
 }
 
+// Which tiles a CTA pair works through, and in which order.  Default: tile t = pair + i * pairs in the grouped
+// raster order (compact blocks of the output in flight at a time).  With the rotary table in tensor memory
+// (rope_in_tmem): a contiguous run of tiles in row-major order, so that a pair stays on one row block of the output
+// for many tiles in a row and re-fills its (cos, sin) rows once or twice per launch; the accumulator then does not
+// alternate (columns [256, 384) hold the table rows).
+struct PairTiles {
+  int first, step, count, tiles_m, tiles_n;
+  bool row_major;
+  __device__ __forceinline__ PairTiles(const GemmArgs& g, int pair, int pairs, int tiles_m_, int tiles_n_)
+      : tiles_m(tiles_m_), tiles_n(tiles_n_), row_major(g.rope_in_tmem != 0) {
+    const int n = tiles_m * tiles_n;
+    if (row_major) {
+      first = (int)((long long)pair * n / pairs);
+      step = 1;
+      count = (int)((long long)(pair + 1) * n / pairs) - first;
+    } else {
+      first = pair;
+      step = pairs;
+      count = pair < n ? (n - pair + pairs - 1) / pairs : 0;
+    }
+  }
+  __device__ __forceinline__ void get(int i, int& tm, int& tn) const {
+    const int t = first + i * step;
+    if (row_major) { tm = t / tiles_n; tn = t - tm * tiles_n; }
+    else raster_tile(t, tiles_m, tiles_n, tm, tn);
+  }
+};
+
 template <bool MX>
 __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                             uint32_t sfa_tmem, uint32_t sfb_tmem, uint32_t accumulate) {
@@ -100,7 +128,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const uint32_t rank = cluster_ctarank();          // 0 = leader (issues the MMAs)
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int tiles_m = g.M / 256, tiles_n = (g.N + kGemmBN - 1) / kGemmBN;
-  const int n_tiles = tiles_m * tiles_n;
+  const PairTiles tiles(g, cluster_id, n_clusters, tiles_m, tiles_n);
+  const int kind_toggle = g.rope_in_tmem ? 0 : 1;      // 0: the accumulator stays at columns [0, 256)
   const int k_stages = g.seg_stage_end[g.n_seg - 1];
   const bool k_tail_half = g.seg_tail_half[g.n_seg - 1] != 0;   // only a plain MXFP4 GEMM (one segment) can have one
   constexpr int kSfPerStage = MX ? 1024 : 2048;
@@ -141,9 +170,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+      for (int ti = 0; ti < tiles.count && ok; ++ti) {
         int tm, tn;
-        raster_tile(t, tiles_m, tiles_n, tm, tn);
+        tiles.get(ti, tm, tn);
         SegCursor cur;
         int a_col = 0;
         const CUtensorMap* bmap = nullptr;
@@ -182,7 +211,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       uint32_t shared_phase = 0, priv_phase = 0;   // priv_phase: bit `kind`
       int kind = 0;                          // 0: accumulator at columns [0, 256), 1: at [128, 384)
       bool ok = true;
-      for (int t = cluster_id; t < n_tiles && ok; t += n_clusters, kind ^= 1) {
+      for (int ti = 0; ti < tiles.count && ok; ++ti, kind ^= kind_toggle) {
         // the private half was released two tiles ago, the shared half by the previous tile's epilogue
         if (!mbar_wait_timed(&sm.acc_empty_priv[kind], ((priv_phase >> kind) & 1u) ^ 1u) ||
             !mbar_wait_timed(&sm.acc_empty_shared, shared_phase ^ 1)) {
@@ -246,7 +275,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     constexpr int kTiles = MX ? 2 : 4;
     static_assert(kPairSfSlots == 2, "the movers keep one leader address per slot");
     const uint32_t sf_ready_leader0 = map_to_cta(&sm.sf_ready[0], 0), sf_ready_leader1 = map_to_cta(&sm.sf_ready[1], 0);
-    for (int t = cluster_id; t < n_tiles && ok; t += n_clusters) {
+    for (int ti = 0; ti < tiles.count && ok; ++ti) {
       for (int ks = 0; ks < k_stages; ++ks, ++gk) {
         if (!mbar_wait_timed(&sm.full[stage], phase)) {
           if (lane == 0) atomicExch(g.status, kStatusGemmMmaTimeout);
@@ -286,9 +315,32 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     const uint32_t empty_shared_leader = map_to_cta(&sm.acc_empty_shared, 0);
     const uint32_t empty_priv_leader0 = map_to_cta(&sm.acc_empty_priv[0], 0), empty_priv_leader1 = map_to_cta(&sm.acc_empty_priv[1], 0);
     bool ok = true;
-    for (int t = cluster_id; t < n_tiles && ok; t += n_clusters, kind ^= 1) {
+    int cs_tm = -1;                                   // row block whose table rows are in tensor memory
+    const uint32_t cs_taddr = g.rope_in_tmem ? tmem + ((uint32_t)(quad * 32) << 16) + 256u : 0u;
+    for (int ti = 0; ti < tiles.count && ok; ++ti, kind ^= kind_toggle) {
       int tm, tn;
-      raster_tile(t, tiles_m, tiles_n, tm, tn);
+      tiles.get(ti, tm, tn);
+      if constexpr (EPI == kEpiRope || EPI == kEpiSilu) {
+        if (g.rope_in_tmem && tm != cs_tm) {
+          // This lane's row of the (cos, sin) table, 2 * pair_dim floats, into columns [256, 256 + 2 * pair_dim) of
+          // its tensor-memory lane: once per row block, while the tile's MMAs run.  Every later tile of the row
+          // block reads the sixteen columns it needs from there instead of 64 scattered bytes per lane from L2.
+          const int row = tm * 256 + (int)rank * 128 + quad * 32 + lane;
+          const float4* src = reinterpret_cast<const float4*>(g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim);
+          for (int c = 0; c < (g.rope_pair_dim >> 4); ++c) {      // 32 floats = 16 pairs per store
+            uint32_t v[32];
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 f = __ldg(src + c * 8 + q);
+              v[4 * q] = __float_as_uint(f.x); v[4 * q + 1] = __float_as_uint(f.y);
+              v[4 * q + 2] = __float_as_uint(f.z); v[4 * q + 3] = __float_as_uint(f.w);
+            }
+            tmem_st32(cs_taddr + (uint32_t)(32 * c), v);
+          }
+          asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          cs_tm = tm;
+        }
+      }
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;
@@ -301,16 +353,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       const int col0 = tn * kGemmBN;
       // tensor-memory columns [128, 256) hold output columns [128, 256) of a tile at [0, 256) and output
       // columns [0, 128) of a tile at [128, 384): lift them out first, the next tile needs them
-      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane, [&] {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(empty_shared_leader);
-      });
-      epilogue_region128<EPI>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane, [&] {
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive_cluster(kind ? empty_priv_leader1 : empty_priv_leader0);
-      });
+      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane,
+                              AccRelease{nullptr, empty_shared_leader}, cs_taddr);
+      epilogue_region128<EPI>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane,
+                              AccRelease{nullptr, kind ? empty_priv_leader1 : empty_priv_leader0}, cs_taddr);
       acc_phase ^= 1;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
