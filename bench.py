@@ -993,6 +993,15 @@ def main():
                      "figure is a rate against the HBM copy bandwidth, not HBM traffic; 20 calls per CUDA-graph replay"}
     del graph
 
+    # ---- the same loop with the caller's promise that no input is produced by the kernel launched just before its call
+    # (true of this loop): the statistics kernel of call i+1 then fills its ring while the quantiser of call i drains
+    before = lib.load().fp4b200_set_pdl_early_reads(1)
+    early_ms = _time_loop(torch, step, min(args.steps, 200), warm=5)
+    lib.load().fp4b200_set_pdl_early_reads(before)
+    early = {"ms_per_step": early_ms, "value": alg / (early_ms * 1e-3) / 1e9, "unit": UNIT,
+             "note": "fp4b200_set_pdl_early_reads(1): not the default, because in a training step the producer's input is "
+                     "what the previous kernel wrote"}
+
     # ---- the reference's own kernels on this box (one GPU only; present when oracle/build_ref.sh was run) ----
     refs = load_reference_kernels() if world == 1 else {}
     ref_quant = None
@@ -1026,7 +1035,7 @@ def main():
                            "l2": "inputs rotate over 3 copies of X (402 MB > 126 MB L2) between steps",
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
-                "cpu_baseline": cpu, "strong_scaling_point": small, "roofline_gemm": roofline_gemm,
+                "cpu_baseline": cpu, "strong_scaling_point": small, "with_early_reads_promise": early, "roofline_gemm": roofline_gemm,
                 "gemm_shapes": gemm_shapes, "reference_kernels_same_box": {"fused_rmsnorm_nvfp4_quant": ref_quant,
                                                                             "load_errors": {k: v for k, v in refs.items() if k.endswith("_error")}},
                 "config1_quantize_gemm": cfg1, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer": mx_layer,
