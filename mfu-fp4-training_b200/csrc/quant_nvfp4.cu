@@ -473,6 +473,57 @@ __device__ __forceinline__ uint32_t block_code_sr(float b, float s_enc, uint32_t
   }
 }
 
+// Table form of block_code for the large launches: a block maximum is a bf16 value, so for one S_enc the code is a
+// function of 15 bits, and it is constant below and above a window of 24 binades (below: the multiplier saturates
+// at 448 / the decode scale rounds to 0; above: the multiplier rounds to 0 / the decode scale saturates).  The window
+// is placed by S_enc's exponent; entry i belongs to the bf16 value with bits base + i and is evaluated with the same
+// instructions as the direct form, so the two agree bit for bit.  Encode-centric entries hold everything a block
+// needs in one word — the multiplier f as bf16 (it has four significant bits) in the upper half, so that the
+// coefficient f * S_enc is one multiplication away, and the stored byte in the lowest byte — because a second,
+// dependent table read costs the shared-memory pipe more than the first; decode-centric entries hold the code
+// (= the stored byte), whose coefficient 1 / (f * S_dec) comes from the 128-entry table.
+constexpr int kCodeLutSize = 24 * 128;
+
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ int code_lut_base_bits(float s_enc) {
+  const int es = (int)((__float_as_uint(s_enc) >> 23) & 0xFFu) - 127;   // S_enc in [2^es, 2^(es+1))
+  int e_hi = 13 - es;                                    // last binade of the window
+  if (ENCODE_CENTRIC) e_hi = max(e_hi, -29);             // keeps the 1e-9 rule's values inside or below the window
+  return (e_hi - 23 + 127) * 128;
+}
+
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ void code_lut_fill(uint32_t* lut, int base_bits, float s_enc, int tid, int n_threads) {
+  for (int i = tid; i < kCodeLutSize; i += n_threads) {
+    const int bits = base_bits + i;
+    // bit patterns outside the finite non-negative bf16 values are never looked up
+    const float b = (bits >= 0 && bits < 0x7F80) ? __uint_as_float((uint32_t)bits << 16) : 0.0f;
+    const uint32_t code = block_code<ENCODE_CENTRIC>(b, s_enc);
+    if constexpr (ENCODE_CENTRIC) {
+      const float f = e4m3_to_f32((uint8_t)code);
+      lut[i] = (__float_as_uint(f) & 0xFFFF0000u) | (uint32_t)f32_to_e4m3(1.0f / f);
+    } else {
+      lut[i] = code;
+    }
+  }
+}
+
+// (coefficient, stored byte) of the block whose maximum has these 15 bits
+template <bool ENCODE_CENTRIC>
+__device__ __forceinline__ ScaleLut code_lut_lookup(const uint32_t* lut, const ScaleLut* lut128, int base_bits, float s_enc,
+                                                    uint32_t abs_bits) {
+  const int idx = min(max((int)abs_bits - base_bits, 0), kCodeLutSize - 1);
+  const uint32_t v = lut[idx];
+  if constexpr (ENCODE_CENTRIC) {
+    ScaleLut e;
+    e.coeff = __uint_as_float(v & 0xFFFF0000u) * s_enc;
+    e.stored = v & 0xFFu;
+    return e;
+  } else {
+    return lut128[v];
+  }
+}
+
 // ---- helpers of the OPT instantiations ------------------------------------------------------
 
 // +1 / -1 per coordinate along the transformed axis (reference: tk_quantize.cu:483-488,620-627)
@@ -954,9 +1005,9 @@ constexpr int kStripStageBytes = 1024;  // per warp: row codes of one strip awai
 constexpr int kStripColStageBytes = 2048;   // per warp, paired form: column codes of two strips (64 columns x 32 B)
 
 __host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm, bool pair) {
-  return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes + (pair ? kStripColStageBytes : 0)) +
+  return (size_t)kStripWarps * (kStripDepth * kStripBytes + kStripStageBytes * (pair ? 2 : 1) + (pair ? kStripColStageBytes : 0)) +
          2 * 128 * sizeof(ScaleLut) + (size_t)kStripWarps * kStripDepth * sizeof(uint64_t) + 16 +
-         (size_t)k_norm * sizeof(float) + 1024;
+         (size_t)k_norm * sizeof(float) + (pair ? (k_norm > 0 ? 1 : 2) * kCodeLutSize * sizeof(uint32_t) : 0) + 1024;
 }
 
 // OPT: 0 = round to nearest, no transform; 1 = the optional modes (stochastic rounding of the codes, Hadamard
@@ -972,43 +1023,59 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   uint8_t* base = smem_align_1024(smem_raw);
   uint8_t* slots = base;                                                       // [warp][depth][4 KiB]
   uint8_t* staging = base + (size_t)kStripWarps * depth * kStripBytes;         // [warp][2 KiB]
-  uint8_t* col_staging = staging + (size_t)kStripWarps * kStripStageBytes;      // [warp][2 KiB] (PAIR)
+  uint8_t* col_staging = staging + (size_t)kStripWarps * kStripStageBytes * (PAIR ? 2 : 1);   // [warp][2 KiB] (PAIR)
   ScaleLut* lut_row = reinterpret_cast<ScaleLut*>(col_staging + (PAIR ? (size_t)kStripWarps * kStripColStageBytes : 0));
   ScaleLut* lut_col = lut_row + 128;
   uint64_t* bars = reinterpret_cast<uint64_t*>(lut_col + 128);                 // [warp][depth]
   float* amax_slot = reinterpret_cast<float*>(bars + kStripWarps * depth);     // 16 bytes
   float* gamma_f = amax_slot + 4;                                              // [K] (NORM)
+  constexpr bool kCodeLut = PAIR && OPT == 0;    // the large round-to-nearest launches look block codes up
+  // [kCodeLutSize], and a second one for the column operand unless NORM (one tensor maximum for both operands)
+  uint32_t* code_lut_row = reinterpret_cast<uint32_t*>(gamma_f + (NORM ? a.K : 0));
+  uint32_t* code_lut_col = NORM ? code_lut_row : code_lut_row + kCodeLutSize;
 
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const int warp = __shfl_sync(0xffffffffu, tid >> 5, 0);   // the same value, known to be uniform across the warp
   // Eight warps per chunk, one strip each (4 down x 2 across), or, paired, four warps per chunk with two
   // vertically adjacent strips each (2 x 2 down, 2 across): a paired warp collects the column codes of both
   // strips in shared memory and stores 32 contiguous bytes per column after the lower one.
+  // A warp's unit of work is its share of one chunk: one strip, or, paired, the two strips (64 rows x 64 columns).
   constexpr int pair = PAIR ? 1 : 0;
+  constexpr int halves = PAIR ? 2 : 1;
   const int wv_base = pair ? (warp & 1) * 2 : (warp & 3);   // first 32-row band of the chunk this warp works on
   const int wh = pair ? (warp >> 1) & 1 : (warp >> 2) & 1;  // which 64 columns of the chunk
   const int groups = pair ? 4 : 2;                           // chunks the CTA works on at a time
   const int n_chunks = a.chunks_m * a.chunks_k;
   const int first = blockIdx.x * groups + (pair ? warp >> 2 : warp >> 3);
   const int step = gridDim.x * groups;
-  const int my_chunks = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
-  const int my_count = my_chunks << pair;                    // strips
+  const int my_units = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
   uint8_t* my_slots = slots + (size_t)warp * depth * kStripBytes;
   uint64_t* my_bars = bars + warp * depth;
-  uint8_t* my_stage = staging + (size_t)warp * kStripStageBytes;
+  uint8_t* my_stage = staging + (size_t)warp * (kStripStageBytes * halves);
   uint8_t* my_col_stage = col_staging + (size_t)warp * kStripColStageBytes;
 
-  auto chunk_coords = [&](int it, int& cm, int& ck) {
-    int c = first + it * step;
-    if (a.reverse) c = n_chunks - 1 - c;
+  // The warp's chunks are first, first + step, ... (counted from the last chunk backwards when a.reverse): the
+  // (row block, column block) pair of the next one follows from the current one by two additions and a wrap.
+  const int step_m = step / a.chunks_k, step_k = step - step_m * a.chunks_k;
+  auto advance = [&](int& m, int& k) {
+    if (!a.reverse) {
+      k += step_k; m += step_m;
+      if (k >= a.chunks_k) { k -= a.chunks_k; ++m; }
+    } else {
+      k -= step_k; m -= step_m;
+      if (k < 0) { k += a.chunks_k; --m; }
+    }
+  };
+  int cm = 0, ck = 0;   // the unit being worked on
+  if (my_units > 0) {
+    const int c = a.reverse ? n_chunks - 1 - first : first;
     cm = c / a.chunks_k;
     ck = c - cm * a.chunks_k;
-  };
+  }
   const uint64_t use_once = l2_policy_evict_first();   // the input's last use and the outputs: nothing to keep in L2
-  auto issue_load = [&](int sit, int s) {
-    int cm, ck;
-    chunk_coords(sit >> pair, cm, ck);
+  auto issue_load = [&](int m, int k, int h, int s) {
     mbar_expect_tx(&my_bars[s], kStripBytes);
-    int x = ck * kChunk + wh * kStripCols, y = cm * kChunk + (wv_base + (sit & pair)) * kStripRows;
+    int x = k * kChunk + wh * kStripCols, y = m * kChunk + (wv_base + h) * kStripRows;
     if (a.nhsd_seq > 0) {
       // head-major input: the strip (32 tokens of one sequence x one 64-wide head) is a contiguous block of the
       // [B * heads * seq, 64] matrix the tensor map describes (seq is a multiple of 128: no strip straddles two)
@@ -1030,8 +1097,23 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   // A statistics kernel launched behind this one (the next call of the fused producer) may set up and fill its ring
   // as SMs free up; it writes nothing before this kernel has ended.
   pdl_launch_dependents();
-  if (lane == 0) {
-    for (int s = 0; s < depth && s < my_count; ++s) issue_load(s, s);
+  // Both slots are filled before the loop: paired, with the two strips of the first unit (slot = half, and a slot
+  // is refilled with the same half of the next unit); else with the first two units (slot = unit & 1).
+  int lm = cm, lk = ck, l_idx = 0;   // the next unit to request
+  if (my_units > 0) {
+    if (lane == 0) issue_load(lm, lk, 0, 0);
+    if constexpr (PAIR) {
+      if (lane == 0) issue_load(lm, lk, 1, 1);
+    }
+    advance(lm, lk);
+    l_idx = 1;
+    if constexpr (!PAIR) {
+      if (my_units > 1) {
+        if (lane == 0) issue_load(lm, lk, 0, 1);
+        advance(lm, lk);
+        l_idx = 2;
+      }
+    }
   }
   // The input is never written by the pass-1 kernel this one may have been launched behind, so the
   // first strips are already on their way; amax / inv_rms are that kernel's results.
@@ -1053,6 +1135,14 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   const bool want_col = a.col_fp4 != nullptr;
   if (tid < 128) lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
   else if (tid < 256) lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
+  int code_base_row = 0, code_base_col = 0;
+  if constexpr (kCodeLut) {
+    code_base_row = code_lut_base_bits<ENCODE_CENTRIC>(s_enc_row);
+    code_base_col = code_lut_base_bits<ENCODE_CENTRIC>(s_enc_col);
+    code_lut_fill<ENCODE_CENTRIC>(code_lut_row, code_base_row, s_enc_row, tid, kStripWarps * 32);
+    if (NORM || s_enc_col == s_enc_row) code_lut_col = code_lut_row;
+    else if (want_col) code_lut_fill<ENCODE_CENTRIC>(code_lut_col, code_base_col, s_enc_col, tid, kStripWarps * 32);
+  }
   if constexpr (NORM) {
     for (int q = tid; q < (a.K >> 1); q += kStripWarps * 32) {
       const uint32_t g = __ldg(reinterpret_cast<const uint32_t*>(a.gamma) + q);
@@ -1070,35 +1160,50 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
 #pragma unroll
   for (int j = 0; j < 8; ++j) col_off[j] = j * 128 + ((((lane >> 2) ^ j) << 4) | ((lane & 3) << 2));
 
-  float inv_next = 0.0f;
+  // lane-constant parts of the output addresses
+  const int cin = wh * kStripCols + 2 * lane;   // this lane's first column inside the 128-column tile
+  const int col_sc_lane0 = scale_tile_offset(cin, 0), col_sc_lane1 = scale_tile_offset(cin + 1, 0);
+  const size_t col_pitch = (size_t)(a.M >> 1);
+  const size_t row_sc_tiles_per_row_block = (size_t)(a.K >> 6);
+  const size_t col_sc_tiles_per_col_block = (size_t)(a.M >> 6);
+
+  float inv_next[halves];
+#pragma unroll
+  for (int h = 0; h < halves; ++h) inv_next[h] = 0.0f;
   if constexpr (NORM) {
-    if (my_count > 0) {
-      int cm, ck;
-      chunk_coords(0, cm, ck);
-      inv_next = __ldg(a.inv_rms + cm * kChunk + wv_base * kStripRows + lane);
+    if (my_units > 0) {
+#pragma unroll
+      for (int h = 0; h < halves; ++h) inv_next[h] = __ldg(a.inv_rms + cm * kChunk + (wv_base + h) * kStripRows + lane);
     }
   }
   uint32_t held_sc = 0;   // paired: the upper strip's column scale bytes (two per column)
+  bool ok = true;
 
-  for (int it = 0; it < my_count; ++it) {
-    const int s = it % depth;
-    const uint32_t parity = (uint32_t)(it / depth) & 1u;
-    int cm, ck;
-    chunk_coords(it >> pair, cm, ck);
-    const int half = it & pair;                          // paired: 0 = upper strip, 1 = lower strip
-    const int wv = wv_base + half;                       // which 32 rows of the chunk
-    const int row0 = cm * kChunk + wv * kStripRows;      // first row of the strip
-    const int col0 = ck * kChunk + wh * kStripCols;      // first column of the strip
-    const float inv = inv_next;
+  for (int u = 0; u < my_units && ok; ++u) {
+    int nm = cm, nk = ck;
+    advance(nm, nk);
+    float inv_unit[halves];
+#pragma unroll
+    for (int h = 0; h < halves; ++h) inv_unit[h] = inv_next[h];
     if constexpr (NORM) {
-      if (it + 1 < my_count) {
-        int ncm, nck;
-        chunk_coords((it + 1) >> pair, ncm, nck);
-        inv_next = __ldg(a.inv_rms + ncm * kChunk + (wv_base + ((it + 1) & pair)) * kStripRows + lane);
+      if (u + 1 < my_units) {
+#pragma unroll
+        for (int h = 0; h < halves; ++h) inv_next[h] = __ldg(a.inv_rms + nm * kChunk + (wv_base + h) * kStripRows + lane);
       }
     }
+    const int col0 = ck * kChunk + wh * kStripCols;      // first column of the unit
+    uint8_t* const row_sc_unit = a.row_sc + (((size_t)cm * row_sc_tiles_per_row_block + (size_t)(col0 >> 6)) << 9) + lane * 16;
+
+#pragma unroll
+    for (int half = 0; half < halves; ++half) {
+    const int s = PAIR ? half : (u & 1);
+    const uint32_t parity = PAIR ? ((uint32_t)u & 1u) : (((uint32_t)u >> 1) & 1u);
+    const int wv = wv_base + half;                       // which 32 rows of the chunk
+    const int row0 = cm * kChunk + wv * kStripRows;      // first row of the strip
+    const float inv = inv_unit[half];
     if (!mbar_wait_bounded(&my_bars[s], parity)) {
       if (lane == 0) atomicExch(a.status, kStatusQuantTmaTimeout);
+      ok = false;
       break;
     }
     uint8_t* tile = my_slots + (size_t)s * kStripBytes;
@@ -1199,22 +1304,30 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
           uint32_t mx = 0;
 #pragma unroll
           for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[8 * b + q]);
-          const float bm = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
-          const ScaleLut e = lut_row[block_code<ENCODE_CENTRIC>(bm, s_enc_row)];
+          ScaleLut e;
+          if constexpr (kCodeLut) {
+            const uint32_t am = mx & 0x7FFF7FFFu;
+            e = code_lut_lookup<ENCODE_CENTRIC>(code_lut_row, lut_row, code_base_row, s_enc_row, max(am >> 16, am & 0xFFFFu));
+          } else {
+            e = lut_row[block_code<ENCODE_CENTRIC>(fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx))), s_enc_row)];
+          }
           codes[2 * b] = quant8(w + 8 * b, e.coeff);
           codes[2 * b + 1] = quant8(w + 8 * b + 4, e.coeff);
           sc_word |= e.stored << (8 * b);
         }
       }
-      // codes leave through a TMA store (32 rows x 32 bytes): per-lane global stores of 32 different
-      // lines each would cost the L1 as much as all the shared-memory traffic of the strip
+      // codes leave through a TMA store (32 bytes per row; one store per unit): per-lane global stores of 32
+      // different lines each would cost the L1 as much as all the shared-memory traffic of the strip
       if (!OPT || a.opt_return_row) {
-        if (lane == 0) bulk_wait_group_read0();   // the previous strip's stores have left the staging buffers
-        __syncwarp();
-        *reinterpret_cast<uint4*>(my_stage + lane * 32) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
-        *reinterpret_cast<uint4*>(my_stage + lane * 32 + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
+        if (half == 0) {
+          if (lane == 0) bulk_wait_group_read0();   // the previous unit's store has left the staging buffer
+          __syncwarp();
+        }
+        uint8_t* stage_row = my_stage + half * kStripStageBytes + lane * 32;
+        *reinterpret_cast<uint4*>(stage_row) = make_uint4(codes[0], codes[1], codes[2], codes[3]);
+        *reinterpret_cast<uint4*>(stage_row + 16) = make_uint4(codes[4], codes[5], codes[6], codes[7]);
         // 512-byte tile (128 rows x these 4 blocks): row wv*32 + lane, blocks 0..3 are 4 adjacent bytes
-        st_cs_u32(a.row_sc + ((size_t)cm * (a.K >> 6) + (size_t)(col0 >> 6)) * 512 + lane * 16 + wv * 4, sc_word);
+        st_cs_u32(row_sc_unit + wv * 4, sc_word);
       }
     }
 
@@ -1276,9 +1389,14 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             else { cc1[2 * g] = cd.x; cc1[2 * g + 1] = cd.y; sc1 |= stored << (8 * g); }
           }
         } else {
-          const float b0 = fabsf(bf16lo_to_f32(mx)), b1 = fabsf(bf16hi_to_f32(mx));
-          const ScaleLut e0 = lut_col[block_code<ENCODE_CENTRIC>(b0, s_enc_col)];
-          const ScaleLut e1 = lut_col[block_code<ENCODE_CENTRIC>(b1, s_enc_col)];
+          ScaleLut e0, e1;
+          if constexpr (kCodeLut) {
+            e0 = code_lut_lookup<ENCODE_CENTRIC>(code_lut_col, lut_col, code_base_col, s_enc_col, mx & 0x7FFFu);
+            e1 = code_lut_lookup<ENCODE_CENTRIC>(code_lut_col, lut_col, code_base_col, s_enc_col, (mx >> 16) & 0x7FFFu);
+          } else {
+            e0 = lut_col[block_code<ENCODE_CENTRIC>(fabsf(bf16lo_to_f32(mx)), s_enc_col)];
+            e1 = lut_col[block_code<ENCODE_CENTRIC>(fabsf(bf16hi_to_f32(mx)), s_enc_col)];
+          }
           const float2 cc = make_float2(e0.coeff, e1.coeff);
           float2 v[16];
 #pragma unroll
@@ -1293,51 +1411,55 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
       }
       // 16 bytes per column straight to [K, M/2]: as a TMA store this would be 64 box rows of 16 bytes,
       // and the TMA unit's rate of box rows (not bytes) is what bounds the kernel once everything goes through it
-      const int cin = wh * kStripCols + 2 * lane;   // column inside the 128-column tile
       if constexpr (!PAIR) {
-        uint8_t* cdst = a.col_fp4 + (size_t)(col0 + 2 * lane) * (a.M >> 1) + (row0 >> 1);
+        uint8_t* cdst = a.col_fp4 + (size_t)(col0 + 2 * lane) * col_pitch + (row0 >> 1);
         st_cs_u4(cdst, make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]));
-        st_cs_u4(cdst + (a.M >> 1), make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]));
+        st_cs_u4(cdst + col_pitch, make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]));
         // 512-byte tile (128 columns x four 16-row groups of a 64-row band): this strip holds groups
         // (wv & 1) * 2 and (wv & 1) * 2 + 1 of band cm * 2 + (wv >> 1): two adjacent bytes per column
-        uint8_t* sdst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)(cm * 2 + (wv >> 1))) * 512 + (wv & 1) * 2;
-        st_cs_u16(sdst + scale_tile_offset(cin, 0), (uint16_t)sc0);
-        st_cs_u16(sdst + scale_tile_offset(cin + 1, 0), (uint16_t)sc1);
+        uint8_t* sdst = a.col_sc + (((size_t)ck * col_sc_tiles_per_col_block + (size_t)(cm * 2 + (wv >> 1))) << 9) + (wv & 1) * 2;
+        st_cs_u16(sdst + col_sc_lane0, (uint16_t)sc0);
+        st_cs_u16(sdst + col_sc_lane1, (uint16_t)sc1);
       } else {
         // 64 rows of a column are 32 contiguous bytes.  Both strips' codes go to a [64 columns][32 B] tile in
         // shared memory (16-byte units, unit u at u ^ ((u >> 3) & 7): conflict-free both ways); after the lower
         // strip, store k writes columns 16k .. 16k+15, lanes 2j and 2j+1 the two halves of one column, so a
         // store touches 16 whole sectors instead of 32 half sectors.
-        auto unit = [](int u) { return (u ^ ((u >> 3) & 7)) << 4; };
+        auto unit = [](int q) { return (q ^ ((q >> 3) & 7)) << 4; };
         *reinterpret_cast<uint4*>(my_col_stage + unit(4 * lane + half)) = make_uint4(cc0[0], cc0[1], cc0[2], cc0[3]);
         *reinterpret_cast<uint4*>(my_col_stage + unit(4 * lane + 2 + half)) = make_uint4(cc1[0], cc1[1], cc1[2], cc1[3]);
         if (half == 0) {
           held_sc = (sc0 & 0xFFFFu) | (sc1 << 16);
         } else {
           __syncwarp();
-          const size_t pitch = (size_t)(a.M >> 1);
-          uint8_t* cdst = a.col_fp4 + (size_t)(col0 + (lane >> 1)) * pitch + ((row0 - kStripRows) >> 1) + (lane & 1) * 16;
+          uint8_t* cdst = a.col_fp4 + (size_t)(col0 + (lane >> 1)) * col_pitch + ((row0 - kStripRows) >> 1) + (lane & 1) * 16;
 #pragma unroll
           for (int k = 0; k < 4; ++k)
-            st_cs_u4(cdst + (size_t)(16 * k) * pitch, *reinterpret_cast<const uint4*>(my_col_stage + unit(32 * k + lane)));
+            st_cs_u4(cdst + (size_t)(16 * k) * col_pitch, *reinterpret_cast<const uint4*>(my_col_stage + unit(32 * k + lane)));
           // the four 16-row groups of the 64-row band cm * 2 + (wv >> 1): one 32-bit word per column
-          uint8_t* sdst = a.col_sc + ((size_t)ck * (a.M >> 6) + (size_t)(cm * 2 + (wv >> 1))) * 512;
-          st_cs_u32(sdst + scale_tile_offset(cin, 0), (held_sc & 0xFFFFu) | (sc0 << 16));
-          st_cs_u32(sdst + scale_tile_offset(cin + 1, 0), (held_sc >> 16) | (sc1 << 16));
+          uint8_t* sdst = a.col_sc + (((size_t)ck * col_sc_tiles_per_col_block + (size_t)(cm * 2 + (wv >> 1))) << 9);
+          st_cs_u32(sdst + col_sc_lane0, (held_sc & 0xFFFFu) | (sc0 << 16));
+          st_cs_u32(sdst + col_sc_lane1, (held_sc >> 16) | (sc1 << 16));
         }
       }
     }
 
-    // staged codes -> global memory; the slot is free again: refill it with the strip `depth` chunks ahead
+    // the slot is free again: refill it with this half of the next unit to request; after the unit's last strip the
+    // staged row codes leave for global memory
     fence_proxy_async_smem();   // this lane's generic-proxy writes (staging, normalised rows) before the TMA engine's accesses
     __syncwarp();
     if (lane == 0) {
-      if (!OPT || a.opt_return_row) {
-        tma_store_2d_hint(&tmap_row, my_stage, col0 >> 1, row0, use_once);
+      if (half == halves - 1 && (!OPT || a.opt_return_row)) {
+        tma_store_2d_hint(&tmap_row, my_stage, col0 >> 1, cm * kChunk + wv_base * kStripRows, use_once);
         bulk_commit_group();
       }
-      if (it + depth < my_count) issue_load(it + depth, s);
+      if (l_idx < my_units) issue_load(lm, lk, half, s);
     }
+    }   // halves
+    advance(lm, lk);
+    ++l_idx;
+    cm = nm;
+    ck = nk;
   }
   if (lane == 0) bulk_wait_group0();
 }
@@ -1503,12 +1625,12 @@ static int launch_quantize_strip_tp(const void* x, const QuantArgs& args, cudaSt
                             nhsd ? (uint64_t)args.M * (uint64_t)args.nhsd_heads : (uint64_t)args.M,
                             nhsd ? 128u : (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  // row-wise codes as a byte matrix [M, K/2], stored in boxes of 32 rows x 32 bytes
+  // row-wise codes as a byte matrix [M, K/2], stored in boxes of 32 (paired: 64) rows x 32 bytes
   tmap_row = tmap;   // launches without row-wise outputs never use it
   if (args.row_fp4 != nullptr) {
     if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
                               args.row_pitch_bytes > 0 ? (uint64_t)args.row_pitch_bytes : (uint64_t)args.K / 2, kStripCols / 2,
-                              kStripRows, CU_TENSOR_MAP_SWIZZLE_NONE))
+                              kStripRows * (PAIR ? 2 : 1), CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
   }
   auto kern = nvfp4_quantize_strip_kernel<EC, NORM, OPT, PAIR>;
@@ -1527,6 +1649,7 @@ static int launch_quantize_strip_tp(const void* x, const QuantArgs& args, cudaSt
 // room in shared memory for the column staging tiles.
 static bool strip_pairing_applies(const QuantArgs& a, bool norm) {
   if (a.col_fp4 == nullptr || strip_smem_bytes(norm ? a.K : 0, true) > 227 * 1024) return false;
+  if (norm && a.n_partials == 0 && a.amax_row != a.amax_col) return false;   // the paired NORM form keeps one code table
   const int mode = quant_pair_mode();
   return mode < 0 ? a.chunks_m * a.chunks_k >= 4 * device_sm_count() : mode == 1;
 }
