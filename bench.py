@@ -410,9 +410,11 @@ def ffn_forward_leg(torch, dist, world, local_rank, x_dev, gamma, peaks, iters=2
 
 
 def _timed_stages(torch, stages, iters=3, warm=3):
-    """Runs the stage callables in order `warm + iters` times; returns mean ms per stage and per pass.
+    """Runs the stage callables in order `warm + iters` times; returns the median ms per stage and per pass.
     Three untimed passes: the mirrors allocate their outputs, and a stage's previous outputs are still
-    referenced while the next pass runs, so the caching allocator needs two passes to own both sets."""
+    referenced while the next pass runs, so the caching allocator needs two passes to own both sets.  Medians:
+    with tens of GB cached, one pass in ten can still stall for milliseconds inside the allocator (a cudaMalloc or
+    a cudaFree of cached blocks behind a 470 MB request), which is the mirrors' cost, not the kernels'."""
     n = len(stages)
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(n + 1)] for _ in range(iters)]
     for i in range(warm + iters):
@@ -423,8 +425,8 @@ def _timed_stages(torch, stages, iters=3, warm=3):
         if i >= warm:
             ev[i - warm][n].record()
     torch.cuda.synchronize()
-    ms = [statistics.mean(e[j].elapsed_time(e[j + 1]) for e in ev) for j in range(n)]
-    return ms, statistics.mean(e[0].elapsed_time(e[n]) for e in ev)
+    ms = [statistics.median(e[j].elapsed_time(e[j + 1]) for e in ev) for j in range(n)]
+    return ms, statistics.median(e[0].elapsed_time(e[n]) for e in ev)
 
 
 def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks, iters=10):
@@ -679,7 +681,7 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
            ("qkv_dgrad_gemm", s_qkv_dgrad), ("qkv_wgrad_gemm", s_qkv_wgrad)]
     stages = ([("weight_all_gather", gather_stage)] if gather_stage is not None else []) + fwd + bwd
     names = [n_ for n_, _ in stages]
-    ms, total = _timed_stages(torch, [f for _, f in stages], iters=3)
+    ms, total = _timed_stages(torch, [f for _, f in stages], iters=5)
     t = torch.tensor(ms + [total], device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -807,6 +809,9 @@ def main():
         raise RuntimeError("bench.py needs a CUDA device: the FP4 hot path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     if world > 1:
+        # NCCL writes its version banner to stdout at the VERSION level; stdout carries the one JSON line
+        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
+            os.environ["NCCL_DEBUG"] = "WARN"
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")
