@@ -82,12 +82,31 @@ int fp4b200_nvfp4_quantize_for_gemm(const void* x_bf16, int64_t M, int64_t K, in
  * moves every later draw of the reference thread that owns the block: with ec_zero_scratch (device memory,
  * M*K/32 bytes, 2-byte aligned; used only when encode_centric and scale_sr) a first kernel maps those blocks and
  * the draws follow the reference's; with NULL every block is taken to draw a scale word.  scale_sr needs 16-byte
- * aligned outputs. */
+ * aligned outputs.
+ * rng_state: NULL, or two 64-bit device words {key, base} (8-byte aligned) that fp4b200_sr_prepare_state wrote
+ * earlier on the stream: the kernel then takes its key from rng_state[0] (rng_seed is ignored) and adds
+ * rng_state[1] to rng_offset and rng_offset_col, which become the launch's place among the launches that were
+ * reserved together (0, 2^32, ...).  This is the reference's rng_state tensor (tk_quantize.cu:3807-3926 reads it in
+ * the kernel), and what makes the call safe to capture in a CUDA graph. */
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
-                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                               const uint64_t* rng_state, int scale_sr,
                                void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* ec_zero_scratch, void* stream);
+
+/* Numbering of stochastic launches on the device (tk_quantize.cu:443-481: tk_sr_invocation_offset,
+ * tk_prepare_advancing_rng_state_kernel).  The library keeps one 64-bit counter per device.
+ * fp4b200_sr_prepare_state launches one thread that adds launches * 2^32 to the counter and writes
+ * rng_state[0] = rng_seed, rng_state[1] = rng_subsequence + (the counter before the addition); rng_state is device
+ * memory for two 64-bit words.  Because the addition happens on the device, a replayed CUDA graph that holds this
+ * launch reserves new numbers on every replay.  fp4b200_sr_set_invocation_offset stores a value into the counter
+ * (stream-ordered; checkpoint resume and tests: the reference's counter cannot be set) and
+ * fp4b200_sr_get_invocation_offset copies it into out_dev (device memory, stream-ordered). */
+int fp4b200_sr_prepare_state(uint64_t* rng_state, uint64_t rng_seed, uint64_t rng_subsequence, uint64_t launches,
+                             void* stream);
+int fp4b200_sr_set_invocation_offset(uint64_t value, void* stream);
+int fp4b200_sr_get_invocation_offset(uint64_t* out_dev, void* stream);
 
 /* As fp4b200_nvfp4_quantize_opt, with the row-wise codes written into a column slice of a wider matrix:
  * row_pitch_bytes is that matrix's row pitch (0: K/2, a dense [M, K/2]); 16-byte aligned outputs only.  Serves the
@@ -97,7 +116,7 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
                                     const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                     int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                     int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
-                                    int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
+                                    const uint64_t* rng_state, int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
                                     void* col_sc, void* ec_zero_scratch, void* stream);
 
 /* Tensor amax (and sg) of the per-16 Hadamard transform of x along K (along_k != 0) or along M,

@@ -53,6 +53,7 @@ struct QuantOpt {
   int sign;                  // seeded sign flip before the transform
   int return_row;            // 0: skip the row-wise outputs but keep their place in the random stream
   unsigned long long rng_seed, rng_offset, rng_offset_col;   // column pass may take its own counter offset
+  const void* rng_state;     // device words {key, base} (8-byte aligned) or null: the key replaces rng_seed, base is added to both offsets
   unsigned long long sign_seed, sign_subseq;
   // encode-centric scale_sr: 2 * (M/128) * (K/128) * 128 uint16 of device scratch for the map of blocks that draw no
   // scale word (null: every block is taken to draw one)

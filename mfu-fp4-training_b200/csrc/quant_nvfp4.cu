@@ -429,6 +429,9 @@ struct QuantArgs {
   int opt_sign;            // seeded sign flip before the transform
   int opt_return_row;      // 0: row-wise outputs are not written (their random words are still skipped)
   unsigned long long rng_seed, rng_offset, rng_offset_col;   // Philox key, counter offset of the row pass / column pass
+  // non-null: device words {key, base} written by an earlier kernel on the stream (sr_prepare_state_kernel): the key
+  // replaces rng_seed and base is added to both offsets, so a replayed CUDA graph draws from a new place every time
+  const unsigned long long* rng_state;
   unsigned long long sign_seed, sign_subseq;   // sign-mask hash inputs
   // Encode-centric scale SR only: per (128x128 chunk, reference thread) the blocks that draw no scale word, bit p =
   // the block at position p of that thread's order in the row pass's stream / in the column pass's stream
@@ -665,6 +668,15 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
   const bool want_col = a.col_fp4 != nullptr;
   if (tid < 128) sm.lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
   else sm.lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
+  // Philox key and the two counter offsets of this launch (OPT): from the arguments, or from the device words an
+  // earlier kernel on the stream prepared (a.rng_state)
+  __shared__ volatile unsigned long long rng_s[3];   // volatile: read where used, not held in registers across the loop
+  if (OPT && tid == 0) {
+    const unsigned long long base = a.rng_state != nullptr ? a.rng_state[1] : 0ull;
+    rng_s[0] = a.rng_state != nullptr ? a.rng_state[0] : a.rng_seed;
+    rng_s[1] = a.rng_offset + base;
+    rng_s[2] = a.rng_offset_col + base;
+  }
   if constexpr (NORM) {
     if (my_count > 0) {
       int cm, ck;
@@ -781,8 +793,8 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
             const int tid_ref = (lr & 31) * 4 + ((lc0 & 63) >> 4);
             const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                            128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
-            const uint4 rw = philox4x32_10(a.rng_seed, seq,
-                                           a.rng_offset + (unsigned long long)((stage * per_stage + it_ref * 4) >> 2));
+            const uint4 rw = philox4x32_10(rng_s[0], seq,
+                                           rng_s[1] + (unsigned long long)((stage * per_stage + it_ref * 4) >> 2));
             const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
             const int bg = (tid_ref & 31) >> 4;
 #pragma unroll
@@ -850,7 +862,7 @@ nvfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const QuantArg
               const int tid_ref = (((warp & 3) - (lane & 3)) & 3) * 32 + lane;
               const unsigned long long seq = (unsigned long long)tid_ref + 128ull * (unsigned long long)ck +
                                              128ull * (unsigned long long)a.chunks_k * (unsigned long long)cm;
-              const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
+              const uint4 rw = philox4x32_10(rng_s[0], seq, rng_s[2] + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
               wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
             }
             const uint32_t neg = (a.opt_sign && a.opt_rht_col) ? rht_sign_mask16(a.sign_seed, a.sign_subseq, (unsigned long long)(m0 + warp * 16)) : 0u;
@@ -1135,6 +1147,15 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   const bool want_col = a.col_fp4 != nullptr;
   if (tid < 128) lut_row[tid] = lut_entry<ENCODE_CENTRIC>(tid, s_enc_row);
   else if (tid < 256) lut_col[tid - 128] = lut_entry<ENCODE_CENTRIC>(tid - 128, s_enc_col);
+  // Philox key and the two counter offsets of this launch (OPT): from the arguments, or from the device words an
+  // earlier kernel on the stream prepared (a.rng_state)
+  __shared__ volatile unsigned long long rng_s[3];   // volatile: read where used, not held in registers across the loop
+  if (OPT != 0 && tid == 0) {
+    const unsigned long long base = a.rng_state != nullptr ? a.rng_state[1] : 0ull;
+    rng_s[0] = a.rng_state != nullptr ? a.rng_state[0] : a.rng_seed;
+    rng_s[1] = a.rng_offset + base;
+    rng_s[2] = a.rng_offset_col + base;
+  }
   int code_base_row = 0, code_base_col = 0;
   if constexpr (kCodeLut) {
     code_base_row = code_lut_base_bits<ENCODE_CENTRIC>(s_enc_row);
@@ -1275,15 +1296,15 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
                 if (ENCODE_CENTRIC && a.ec_zero_row_stream != nullptr) zm = __ldg(a.ec_zero_row_stream + seq);
                 const bool own_zero = (zm >> pos) & 1u;
                 uint32_t dr[5];
-                philox_draws(a.rng_seed, seq, a.rng_offset, pos * q - __popc(zm & ((1u << pos) - 1u)), q, dr);
+                philox_draws(rng_s[0], seq, rng_s[1], pos * q - __popc(zm & ((1u << pos) - 1u)), q, dr);
                 scale_rbits = dr[0];
                 const uint32_t d0 = own_zero ? dr[0] : dr[1], d1 = own_zero ? dr[1] : dr[2], d2 = own_zero ? dr[2] : dr[3],
                                d3 = own_zero ? dr[3] : dr[4];
 #pragma unroll
                 for (int g = 0; g < 4; ++g) wsel[g] = (((g >> 1) - bg) & 1) ? ((g & 1) ? d3 : d2) : ((g & 1) ? d1 : d0);
               } else {
-                const uint4 rw = philox4x32_10(a.rng_seed, seq,
-                                               a.rng_offset + (unsigned long long)((stage * a.opt_row_per_stage + it_ref * 4) >> 2));
+                const uint4 rw = philox4x32_10(rng_s[0], seq,
+                                               rng_s[1] + (unsigned long long)((stage * a.opt_row_per_stage + it_ref * 4) >> 2));
                 const uint32_t words[4] = {rw.x, rw.y, rw.z, rw.w};
 #pragma unroll
                 for (int g = 0; g < 4; ++g) wsel[g] = words[2 * (((g >> 1) - bg) & 1) + (g & 1)];
@@ -1373,12 +1394,12 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
                 if (ENCODE_CENTRIC && a.ec_zero_col_stream != nullptr) zm = __ldg(a.ec_zero_col_stream + seq);
                 const bool own_zero = (zm >> pos) & 1u;
                 uint32_t dr[5];
-                philox_draws(a.rng_seed, seq, a.rng_offset_col, pos * q - __popc(zm & ((1u << pos) - 1u)), q, dr);
+                philox_draws(rng_s[0], seq, rng_s[2], pos * q - __popc(zm & ((1u << pos) - 1u)), q, dr);
                 scale_rbits = dr[0];
                 wsel[0] = own_zero ? dr[0] : dr[1]; wsel[1] = own_zero ? dr[1] : dr[2];
                 wsel[2] = own_zero ? dr[2] : dr[3]; wsel[3] = own_zero ? dr[3] : dr[4];
               } else {
-                const uint4 rw = philox4x32_10(a.rng_seed, seq, a.rng_offset_col + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
+                const uint4 rw = philox4x32_10(rng_s[0], seq, rng_s[2] + (unsigned long long)((stage * 16 + 8 + wq * 4) >> 2));
                 wsel[0] = rw.x; wsel[1] = rw.y; wsel[2] = rw.z; wsel[3] = rw.w;
               }
             }
@@ -1521,6 +1542,34 @@ rht16_amax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
 }
 
 // ---------------------------------------------------------------------------------------
+// Numbering of stochastic launches on the device
+// ---------------------------------------------------------------------------------------
+//
+// The reference numbers its stochastic launches with a device word that a one-thread kernel advances by 2^32 per
+// reserved launch, and hands the launch its {key, base} through device memory (tk_quantize.cu:443-481:
+// tk_sr_invocation_offset, tk_prepare_advancing_rng_state_kernel), so that a captured CUDA graph draws from a new
+// place on every replay.  Same here: one counter per device (a module-scope device word), same stride.
+constexpr unsigned long long kSrInvocationStride = 1ull << 32;
+__device__ unsigned long long g_sr_invocation_offset = 0;
+
+__global__ void sr_prepare_state_kernel(unsigned long long* __restrict__ rng_state, unsigned long long seed,
+                                        unsigned long long subsequence, unsigned long long launches) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const unsigned long long offset = atomicAdd(&g_sr_invocation_offset, kSrInvocationStride * launches);
+    rng_state[0] = seed;
+    rng_state[1] = subsequence + offset;
+  }
+}
+
+__global__ void sr_set_offset_kernel(unsigned long long value) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) g_sr_invocation_offset = value;
+}
+
+__global__ void sr_get_offset_kernel(unsigned long long* __restrict__ out) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) *out = g_sr_invocation_offset;
+}
+
+// ---------------------------------------------------------------------------------------
 // Host launchers
 // ---------------------------------------------------------------------------------------
 
@@ -1656,8 +1705,13 @@ static bool strip_pairing_applies(const QuantArgs& a, bool norm) {
 
 template <bool EC, bool NORM, int OPT = 0>
 static int launch_quantize_strip_t(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
-  return strip_pairing_applies(args, NORM) ? launch_quantize_strip_tp<EC, NORM, OPT, true>(x, args, st, pdl)
-                                           : launch_quantize_strip_tp<EC, NORM, OPT, false>(x, args, st, pdl);
+  // The paired form of the fused-RMSNorm kernel with stochastic data rounding needs more than 128 registers: unpaired.
+  if constexpr (NORM && OPT == 1) {
+    return launch_quantize_strip_tp<EC, NORM, OPT, false>(x, args, st, pdl);
+  } else {
+    return strip_pairing_applies(args, NORM) ? launch_quantize_strip_tp<EC, NORM, OPT, true>(x, args, st, pdl)
+                                             : launch_quantize_strip_tp<EC, NORM, OPT, false>(x, args, st, pdl);
+  }
 }
 
 // The strip kernel stores codes by TMA (16-byte aligned outputs) and keeps gamma in shared memory.
@@ -1710,6 +1764,7 @@ int launch_quantize(const void* x, int64_t M, int64_t K, const float* amax_row, 
     a.opt_row_per_stage = opt->row_per_stage ? opt->row_per_stage : (col_fp4 != nullptr ? 16 : 8);
     a.opt_rht_row = opt->rht_row; a.opt_rht_col = opt->rht_col; a.opt_sign = opt->sign;
     a.opt_return_row = opt->return_row; a.rng_seed = opt->rng_seed; a.rng_offset = opt->rng_offset;
+    a.rng_state = reinterpret_cast<const unsigned long long*>(opt->rng_state);
     a.sign_seed = opt->sign_seed; a.sign_subseq = opt->sign_subseq;
     if (strip_kernel_applies(a, norm)) {
       if (a.opt_scale_sr && encode_centric && opt->ec_zero_scratch != nullptr) {
@@ -1934,26 +1989,29 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
                                     const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                     int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                     int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
-                                    int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
-                                    void* col_sc, void* ec_zero_scratch, void* stream);
+                                    const uint64_t* rng_state, int scale_sr, void* row_fp4, int64_t row_pitch_bytes,
+                                    void* row_sc, void* col_fp4, void* col_sc, void* ec_zero_scratch, void* stream);
 
 int fp4b200_nvfp4_quantize_opt(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
-                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col, int scale_sr,
+                               int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
+                               const uint64_t* rng_state, int scale_sr,
                                void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* ec_zero_scratch, void* stream) {
   return fp4b200_nvfp4_quantize_opt_into(x_bf16, gamma_bf16, inv_rms, M, K, amax_row, amax_col, encode_centric, data_sr, rht_row,
                                          rht_col, with_sign, sign_seed, sign_subseq, return_row, rng_seed, rng_offset,
-                                         rng_offset_col, scale_sr, row_fp4, 0, row_sc, col_fp4, col_sc, ec_zero_scratch, stream);
+                                         rng_offset_col, rng_state, scale_sr, row_fp4, 0, row_sc, col_fp4, col_sc,
+                                         ec_zero_scratch, stream);
 }
 
 int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                                     const float* amax_row, const float* amax_col, int encode_centric, int data_sr,
                                     int rht_row, int rht_col, int with_sign, uint64_t sign_seed, uint64_t sign_subseq,
                                     int return_row, uint64_t rng_seed, uint64_t rng_offset, uint64_t rng_offset_col,
-                                    int scale_sr, void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4,
-                                    void* col_sc, void* ec_zero_scratch, void* stream) {
+                                    const uint64_t* rng_state, int scale_sr, void* row_fp4, int64_t row_pitch_bytes,
+                                    void* row_sc, void* col_fp4, void* col_sc, void* ec_zero_scratch, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_quantize_opt")) return rc;
+  if (reinterpret_cast<uintptr_t>(rng_state) & 7) return set_error("nvfp4_quantize_opt: rng_state must be 8-byte aligned");
   if (reinterpret_cast<uintptr_t>(ec_zero_scratch) & 1) return set_error("nvfp4_quantize_opt: ec_zero_scratch must be 2-byte aligned");
   if (row_pitch_bytes != 0 && (row_pitch_bytes < K / 2 || (row_pitch_bytes % 16) != 0 || row_pitch_bytes > INT32_MAX))
     return set_error("nvfp4_quantize_opt: the row pitch must be 0 or a multiple of 16 bytes and at least K/2 (got %lld)",
@@ -1978,6 +2036,7 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
   o.return_row = return_row != 0; o.rng_seed = rng_seed; o.rng_offset = rng_offset;
   o.sign_seed = sign_seed; o.sign_subseq = sign_subseq;
   o.ec_zero_scratch = ec_zero_scratch;
+  o.rng_state = rng_state;
   return launch_quantize(x_bf16, M, K, amax_row, amax_col, encode_centric != 0, inv_rms, gamma_bf16, row_fp4, row_sc,
                          col_fp4, col_sc, nullptr, false, (cudaStream_t)stream, false, &o, nullptr, nullptr, 0, 0,
                          row_pitch_bytes);
@@ -2036,6 +2095,33 @@ int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
                          col_fp4, col_sc, nullptr, true, (cudaStream_t)stream);
 }
 
+
+// ---- device-side numbering of stochastic launches ---------------------------------------------
+
+int fp4b200_sr_prepare_state(uint64_t* rng_state, uint64_t rng_seed, uint64_t rng_subsequence, uint64_t launches,
+                             void* stream) {
+  if (rng_state == nullptr || (reinterpret_cast<uintptr_t>(rng_state) & 7))
+    return set_error("sr_prepare_state: rng_state must be 8-byte aligned device memory for two 64-bit words");
+  if (launches == 0) return set_error("sr_prepare_state: the number of launches to reserve must be positive");
+  sr_prepare_state_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long*>(rng_state), rng_seed,
+                                                            rng_subsequence, launches);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int fp4b200_sr_set_invocation_offset(uint64_t value, void* stream) {
+  sr_set_offset_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(value);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int fp4b200_sr_get_invocation_offset(uint64_t* out_dev, void* stream) {
+  if (out_dev == nullptr || (reinterpret_cast<uintptr_t>(out_dev) & 7))
+    return set_error("sr_get_invocation_offset: out must be 8-byte aligned device memory");
+  sr_get_offset_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long*>(out_dev));
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 // ---- variant that allocates nothing -------------------------------------------------------
 // Scratch of the fused producer (inverse RMS per row, per-CTA partial maxima of pass 1) in a fixed

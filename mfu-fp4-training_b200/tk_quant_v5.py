@@ -134,9 +134,10 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
             sc_col.append(torch.empty((n // 128, M // 64, 512), **u8))
             if sr:
                 _lib.call("fp4b200_nvfp4_amax", x.data_ptr(), M * n, amax_sg[g].data_ptr(), _stream(input0))
+                state = _reserve_sr(input0, rng_seed, rng_subsequence, True)
                 _lib.call("fp4b200_nvfp4_quantize_opt_into", x.data_ptr(), None, None, M, n, amax_sg[g].data_ptr(),
-                          amax_sg[g].data_ptr(), 1, 1, 0, 0, 0, 0, 0, 1, int(rng_seed) & _U64,
-                          _next_offset(input0, rng_subsequence, True), 0, 0, fp4_row_full.data_ptr() + off // 2,
+                          amax_sg[g].data_ptr(), 1, 1, 0, 0, 0, 0, 0, 1, 0, 0, 0, state.data_ptr(), 0,
+                          fp4_row_full.data_ptr() + off // 2,
                           n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2),
                           sc_col[g].data_ptr(), None, _stream(input0))
             else:
@@ -416,35 +417,40 @@ def tk_silu_deriv_quantize_split_for_gemm_launch(dh, h3, h1_raw, out1_fp4, out1_
 # ---- stochastic rounding / Hadamard ("opt") producers -----------------------------------------
 
 _U64 = (1 << 64) - 1
-_sr_invocations = {}   # device index -> number of SR launches so far (the reference's device-global counter)
+_SR_STRIDE = 1 << 32   # counter distance between two stochastic launches (tk_quantize.cu:443)
 
 
 def tk_sr_invocation_count(device=None) -> int:
-    """Number of stochastic-rounding launches issued so far on ``device`` in this process: the Philox offset
-    of launch n is ``rng_subsequence + n * 2**32`` (reference: tk_sr_invocation_offset, tk_quantize.cu:443-481)."""
-    idx = torch.cuda.current_device() if device is None else torch.device(device).index
-    return _sr_invocations.get(idx, 0)
+    """Number of stochastic-rounding launches reserved so far on ``device`` in this process: launch n draws at the
+    Philox offset ``rng_subsequence + n * 2**32``.  The counter lives on the device, as the reference's
+    (tk_sr_invocation_offset, tk_quantize.cu:443-481); reading it waits for the current stream."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        out = torch.empty(1, dtype=torch.int64, device=dev)
+        _lib.call("fp4b200_sr_get_invocation_offset", out.data_ptr(), torch.cuda.current_stream(dev).cuda_stream)
+        return (int(out.item()) & _U64) >> 32
 
 
 def tk_set_sr_invocation_count(n: int, device=None) -> None:
-    """Restores the counter (checkpoint resume, tests); no counterpart in the reference, whose counter
-    cannot be set."""
-    idx = torch.cuda.current_device() if device is None else torch.device(device).index
-    _sr_invocations[idx] = int(n)
+    """Restores the counter (checkpoint resume, tests) in stream order; no counterpart in the reference, whose
+    counter cannot be set."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    with torch.cuda.device(dev):
+        _lib.call("fp4b200_sr_set_invocation_offset", (int(n) * _SR_STRIDE) & _U64,
+                  torch.cuda.current_stream(dev).cuda_stream)
 
 
-def _next_offset(t, rng_subsequence, use_sr):
-    idx = t.device.index
-    n = _sr_invocations.get(idx, 0)
-    if use_sr:
-        # The launch number is host state: a CUDA graph would bake this launch's offset in and replay the same
-        # random words on every step (the reference numbers its launches on the device, tk_quantize.cu:443-481).
-        # Refuse rather than round with correlated noise.
-        if torch.cuda.is_current_stream_capturing():
-            raise RuntimeError("stochastic rounding inside CUDA-graph capture would replay one Philox offset on every "
-                               "graph launch: run the stochastic quantisers outside the captured region")
-        _sr_invocations[idx] = n + 1
-    return (int(rng_subsequence) + n * (1 << 32)) & _U64
+def _reserve_sr(t, rng_seed, rng_subsequence, use_sr, launches=1):
+    """Device words {key, base} for the next ``launches`` stochastic launches on t's device (None without
+    stochastic rounding): a one-thread kernel advances the device counter, so a captured graph reserves new
+    numbers on every replay (tk_make_advancing_rng_state, tk_quantize.cu:469-481).  Launch k of the group passes
+    the relative offset ``k * 2**32``."""
+    if not use_sr:
+        return None
+    state = torch.empty(2, dtype=torch.int64, device=t.device)
+    _lib.call("fp4b200_sr_prepare_state", state.data_ptr(), int(rng_seed) & _U64, int(rng_subsequence) & _U64,
+              int(launches), _stream(t))
+    return state
 
 
 def _norm_axes(rht_axes):
@@ -478,16 +484,20 @@ def _amax_rht(x, along_k, sign, seed, subseq, gamma=None, inv_rms=None):
 
 
 def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row_rht, col_rht, return_row, seed, offset,
-                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None, sr_mode=None, offset_col=0, scale_sr=False):
+                sign, sign_seed, sign_subseq, gamma=None, inv_rms=None, sr_mode=None, offset_col=0, scale_sr=False,
+                rng_state=None, out=None):
     """One launch, the counterpart of tk_quantize_transpose (tk_quantize.cu:3807-3926).  ``sr_mode`` 2 / 3:
     stochastic rounding on the row pass only (the bytes of the reference's row-only launch at ``offset``) /
     on the column pass only (at ``offset_col``), the other pass rounded to nearest in the same launch."""
     M, K = x.shape
     u8 = dict(dtype=torch.uint8, device=x.device)
-    row_fp4 = torch.empty((M, K // 2), **u8) if return_row else None
-    row_sc = torch.empty((M // 128, K // 64, 512), **u8) if return_row else None
-    col_fp4 = torch.empty((K, M // 2), **u8) if return_transpose else None
-    col_sc = torch.empty((K // 128, M // 64, 512), **u8) if return_transpose else None
+    if out is not None:      # the caller's buffers (alloc / launch pairs)
+        row_fp4, row_sc, col_fp4, col_sc = out
+    else:
+        row_fp4 = torch.empty((M, K // 2), **u8) if return_row else None
+        row_sc = torch.empty((M // 128, K // 64, 512), **u8) if return_row else None
+        col_fp4 = torch.empty((K, M // 2), **u8) if return_transpose else None
+        col_sc = torch.empty((K // 128, M // 64, 512), **u8) if return_transpose else None
     # encode-centric scale SR: scratch for the map of blocks that draw no scale word (the reference thread's later
     # draws move up behind such a block, quantize_transpose_tuned.cuh:244-254)
     zero_map = torch.empty(M * K // 32, **u8) if (scale_sr and encode_centric) else None
@@ -495,7 +505,7 @@ def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row
               amax_col.data_ptr(), int(bool(encode_centric)), int(bool(sr)) if sr_mode is None else int(sr_mode),
               int(bool(row_rht)), int(bool(col_rht)),
               int(bool(sign)), int(sign_seed) & _U64, int(sign_subseq) & _U64, int(bool(return_row)),
-              int(seed) & _U64, int(offset) & _U64, int(offset_col) & _U64, int(bool(scale_sr)), _p(row_fp4), _p(row_sc),
+              int(seed) & _U64, int(offset) & _U64, int(offset_col) & _U64, _p(rng_state), int(bool(scale_sr)), _p(row_fp4), _p(row_sc),
               _p(col_fp4), _p(col_sc), _p(zero_map), _stream(x))
     return row_fp4, row_sc, col_fp4, col_sc
 
@@ -505,14 +515,16 @@ def tk_quantize_transpose(input, amax_row, amax_col, return_transpose, stochasti
     """tk_quantize.cu:3807-3926 — quantise with pre-computed device amaxes; ``rng_state`` = int64[2] tensor
     ``[seed, offset]``.  Returns (row_fp4, row_sc, col_fp4, col_sc) as uint8 tensors."""
     _check_bf16_2d(input, "input")
-    seed = offset = 0
+    state = None
     if stochastic_rounding or scale_stochastic_rounding:
-        if rng_state is None or rng_state.numel() < 2:
-            raise RuntimeError("rng_state [seed, offset] is required with stochastic rounding")
-        seed, offset = (int(v) & _U64 for v in rng_state.cpu().tolist()[:2])
+        if (rng_state is None or rng_state.numel() < 2 or rng_state.dtype != torch.int64 or not rng_state.is_contiguous()
+                or rng_state.device != input.device):
+            raise RuntimeError("rng_state must be a contiguous int64[2] tensor [seed, offset] on the input's device "
+                               "with stochastic rounding")
+        state = rng_state   # read by the kernel, as in the reference: no host round trip
     with torch.cuda.device(input.device):
         out = _launch_opt(input, amax_row, amax_col, return_transpose, stochastic_rounding, encode_centric, row_rht,
-                          col_rht, return_row, seed, offset, False, 0, 0, scale_sr=scale_stochastic_rounding)
+                          col_rht, return_row, 0, 0, False, 0, 0, scale_sr=scale_stochastic_rounding, rng_state=state)
     empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
     return tuple(empty if t is None else t for t in out)
 
@@ -556,33 +568,33 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
             # the reference runs a row launch and a column launch over a sign-flipped, transformed copy; the sign
             # flip happens inside this library's transform, so one launch reads the input once and gives each pass
             # the stream of its reference launch
-            off_r = _next_offset(input, rng_subsequence, use_sr)
-            off_c = _next_offset(input, rng_subsequence, use_sr)
+            state = _reserve_sr(input, rng_seed, rng_subsequence, use_sr, 2)
             mode = 0 if not (row_sr or col_sr) else (4 if (row_sr and col_sr) else (2 if row_sr else 3))
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr or col_sr, encode_centric, row_rht, col_rht,
-                                         True, rng_seed, off_r, sign, rng_seed, rng_subsequence, sr_mode=mode,
-                                         offset_col=off_c, scale_sr=scale_sr)
+                                         True, rng_seed, 0, sign, rng_seed, rng_subsequence, sr_mode=mode,
+                                         offset_col=_SR_STRIDE, scale_sr=scale_sr, rng_state=state)
         elif return_transpose and not row_mat and row_sr == col_sr and not col_mat:
-            off = _next_offset(input, rng_subsequence, use_sr)
+            state = _reserve_sr(input, rng_seed, rng_subsequence, use_sr)
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, row_sr, encode_centric, row_rht, col_rht,
-                                         True, rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)
+                                         True, rng_seed, 0, sign, rng_seed, rng_subsequence, scale_sr=scale_sr,
+                                         rng_state=state)
         elif return_transpose and not row_mat and not col_mat:
             # the reference serves "one axis stochastic" with a row launch and a column launch, each taking
             # an offset; here one launch reads the input once and produces the same bytes
-            off_r = _next_offset(input, rng_subsequence, use_sr)
-            off_c = _next_offset(input, rng_subsequence, use_sr)
+            state = _reserve_sr(input, rng_seed, rng_subsequence, use_sr, 2)
             rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, True, encode_centric, row_rht, col_rht, True,
-                                         rng_seed, off_r, sign, rng_seed, rng_subsequence, sr_mode=2 if row_sr else 3,
-                                         offset_col=off_c, scale_sr=scale_sr)
+                                         rng_seed, 0, sign, rng_seed, rng_subsequence, sr_mode=2 if row_sr else 3,
+                                         offset_col=_SR_STRIDE, scale_sr=scale_sr, rng_state=state)
         else:
-            off = _next_offset(input, rng_subsequence, use_sr)
+            state = _reserve_sr(input, rng_seed, rng_subsequence, use_sr)
             rf, rs, _, _ = _launch_opt(input, row_amax, row_amax, False, row_sr, encode_centric, row_rht, False, True,
-                                       rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)
+                                       rng_seed, 0, sign, rng_seed, rng_subsequence, scale_sr=scale_sr, rng_state=state)
             cf = cs = None
             if return_transpose:
-                off = _next_offset(input, rng_subsequence, use_sr)
+                state = _reserve_sr(input, rng_seed, rng_subsequence, use_sr)
                 _, _, cf, cs = _launch_opt(input, col_amax, col_amax, True, col_sr, encode_centric, False, col_rht,
-                                           False, rng_seed, off, sign, rng_seed, rng_subsequence, scale_sr=scale_sr)
+                                           False, rng_seed, 0, sign, rng_seed, rng_subsequence, scale_sr=scale_sr,
+                                           rng_state=state)
     empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
     row_sg = row_amax.narrow(0, 1, 1)
     col_sg = col_amax.narrow(0, 1, 1) if return_transpose else row_sg
@@ -612,9 +624,9 @@ def tk_fused_norm_quantize_opt(input, gamma, epsilon, return_transpose=True, enc
         _lib.call("fp4b200_nvfp4_rmsnorm_stats", input.data_ptr(), gamma.data_ptr(), float(epsilon), M, K,
                   inv_rms.data_ptr(), 1, col_amax.data_ptr(), _stream(input))
         row_amax = _amax_rht(input, True, False, 0, 0, gamma, inv_rms)
-        off = _next_offset(input, rng_subsequence, sr or scale_sr)
+        state = _reserve_sr(input, rng_seed, rng_subsequence, sr or scale_sr)
         rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, sr, encode_centric, True, False, True, rng_seed,
-                                     off, False, 0, 0, gamma, inv_rms, scale_sr=scale_sr)
+                                     0, False, 0, 0, gamma, inv_rms, scale_sr=scale_sr, rng_state=state)
     return (rf.view(_FP4), rs.view(_E4M3), cf.view(_FP4), cs.view(_E4M3), row_amax.narrow(0, 1, 1),
             col_amax.narrow(0, 1, 1), inv_rms)
 
@@ -645,16 +657,86 @@ def tk_silu_deriv_quantize_split_for_gemm_opt(dh, h3, h1_raw, return_transpose=T
         outs, sgs, amax_list = [], [], []
         for t, orig in ((dh1, a1), (dh3, a3)):
             row_amax = _amax_rht(t, True, False, 0, 0) if row_rht else orig
-            off = _next_offset(t, rng_subsequence, use_sr)
+            state = _reserve_sr(t, rng_seed, rng_subsequence, use_sr)
             if row_sr == col_sr:
-                q = _launch_opt(t, row_amax, orig, True, row_sr, encode_centric, row_rht, False, True, rng_seed, off,
-                                False, 0, 0, scale_sr=scale_sr)
+                q = _launch_opt(t, row_amax, orig, True, row_sr, encode_centric, row_rht, False, True, rng_seed, 0,
+                                False, 0, 0, scale_sr=scale_sr, rng_state=state)
             else:
                 # one axis stochastic: the reference's row launch and column launch (same offset) as one
-                q = _launch_opt(t, row_amax, orig, True, True, encode_centric, row_rht, False, True, rng_seed, off,
-                                False, 0, 0, sr_mode=2 if row_sr else 3, offset_col=off, scale_sr=scale_sr)
+                q = _launch_opt(t, row_amax, orig, True, True, encode_centric, row_rht, False, True, rng_seed, 0,
+                                False, 0, 0, sr_mode=2 if row_sr else 3, offset_col=0, scale_sr=scale_sr,
+                                rng_state=state)
             outs.append((q[0].view(_FP4), q[1].view(_E4M3), q[2].view(_FP4), q[3].view(_E4M3)))
             sgs.append((row_amax.narrow(0, 1, 1), orig.narrow(0, 1, 1)))
             amax_list += [row_amax[0], orig[0]]
         amaxes = torch.stack(amax_list)
     return (*outs[0], *sgs[0], *outs[1], *sgs[1], amaxes, dh1, dh3)
+
+
+def tk_silu_deriv_quantize_split_for_gemm_opt_alloc(M, H, device):
+    """tk_quantize.cu:10259-10290 — the 11 buffers of the pair: operands of dh1 (4) and of dh3 (4) as uint8, sgs [4],
+    amaxes [4], sync_buf [4].  Call outside graph capture."""
+    if M % 128 or H % 128:
+        raise RuntimeError("M and H must be multiples of 128")
+    dev = torch.device(device)
+    o1 = _alloc_operands(int(M), int(H), dev, True)
+    o2 = _alloc_operands(int(M), int(H), dev, True)
+    f32 = dict(dtype=torch.float32, device=dev)
+    return (*o1, *o2, torch.empty(4, **f32), torch.empty(4, **f32), torch.empty(4, dtype=torch.int32, device=dev))
+
+
+def tk_silu_deriv_quantize_split_for_gemm_opt_launch(dh, h3, h1_raw, return_transpose, encode_centric,
+                                                     data_stochastic_rounding, scale_stochastic_rounding, rht_axes,
+                                                     with_random_sign_mask, rng_seed, rng_subsequence, out1_fp4, out1_sc,
+                                                     out1_fp4_t, out1_sc_t, out2_fp4, out2_sc, out2_fp4_t, out2_sc_t, sgs,
+                                                     amaxes, sync_buf, data_sr_axes="both"):
+    """tk_quantize.cu:10292-10388 — the SiLU-derivative producer with the row operand Hadamard-transformed and
+    optional stochastic rounding, into the caller's buffers; safe to capture in a CUDA graph (the launch number
+    comes from the device counter).  Returns the 12-tuple (dh1 operands, row sg, column sg, dh3 operands, row sg,
+    column sg); amaxes receives [row amax 1, column amax 1, row amax 3, column amax 3].
+
+    Random stream, as in the reference's kernel for this pair (persistent_silu_deriv_quantize.cuh:64-74,150-176): ONE
+    reserved launch number; dh1 and dh3 each draw from that same offset, in the order of a single launch of the
+    tuned quantiser with both passes (row blocks, then column blocks of each 64 x 64 stage).  That order exists here
+    for rounding both axes, or neither, stochastically; one axis alone is not built for this pair.  dh1 and dh3 in
+    bf16 are temporaries from torch's allocator (the reference keeps them in shared memory)."""
+    M, H = _check_bf16_2d(dh, "dh")
+    _same_shape_bf16(dh, h3, h1_raw)
+    if not return_transpose:
+        raise RuntimeError("split2 opt prealloc producer currently requires return_transpose=True")
+    row_rht, col_rht = _norm_axes(rht_axes)
+    if not row_rht or col_rht:
+        raise RuntimeError(f"split2 opt prealloc producer currently supports the row-RHT regular-TK contract only; got {rht_axes}")
+    if with_random_sign_mask:
+        raise RuntimeError("split2 opt prealloc producer does not support random RHT sign masks yet")
+    axes = _norm_sr_axes(data_sr_axes)
+    row_sr = bool(data_stochastic_rounding) and axes in ("row", "both")
+    col_sr = bool(data_stochastic_rounding) and axes in ("col", "both")
+    if row_sr != col_sr:
+        raise RuntimeError("split2 opt prealloc producer: stochastic rounding of one axis only is not built")
+    scale_sr = bool(scale_stochastic_rounding)
+    if sgs.numel() < 4 or amaxes.numel() < 4 or sgs.dtype != torch.float32 or amaxes.dtype != torch.float32:
+        raise RuntimeError("sgs [4] and amaxes [4] (float32) are required")
+    if sync_buf.numel() < 4 or sync_buf.dtype != torch.int32:
+        raise RuntimeError("int32 sync_buf [4] is required")
+    outs = ((out1_fp4, out1_sc, out1_fp4_t, out1_sc_t), (out2_fp4, out2_sc, out2_fp4_t, out2_sc_t))
+    for c, s_, ct, st_ in outs:
+        if c.numel() * c.element_size() != M * H // 2 or ct.numel() * ct.element_size() != M * H // 2:
+            raise RuntimeError("code buffers do not match the input shape")
+        if s_.numel() != M * H // 16 or st_.numel() != M * H // 16:
+            raise RuntimeError("scale buffers do not match the input shape")
+    with torch.cuda.device(dh.device):
+        _, _, dh1, dh3, a1, a3 = _silu_deriv(dh, h3, h1_raw)
+        state = _reserve_sr(dh, rng_seed, rng_subsequence, row_sr or scale_sr)
+        for g, (t, orig, out) in enumerate(((dh1, a1, outs[0]), (dh3, a3, outs[1]))):
+            row_amax = _amax_rht(t, True, False, 0, 0)
+            _launch_opt(t, row_amax, orig, True, row_sr, encode_centric, True, False, True, rng_seed, 0, False, 0, 0,
+                        scale_sr=scale_sr, rng_state=state, out=out)
+            amaxes.narrow(0, 2 * g, 1).copy_(row_amax.narrow(0, 0, 1))
+            amaxes.narrow(0, 2 * g + 1, 1).copy_(orig.narrow(0, 0, 1))
+            sgs.narrow(0, 2 * g, 1).copy_(row_amax.narrow(0, 1, 1))
+            sgs.narrow(0, 2 * g + 1, 1).copy_(orig.narrow(0, 1, 1))
+    return (out1_fp4.view(_FP4), out1_sc.view(_E4M3), out1_fp4_t.view(_FP4), out1_sc_t.view(_E4M3),
+            sgs.narrow(0, 0, 1), sgs.narrow(0, 1, 1),
+            out2_fp4.view(_FP4), out2_sc.view(_E4M3), out2_fp4_t.view(_FP4), out2_sc_t.view(_E4M3),
+            sgs.narrow(0, 2, 1), sgs.narrow(0, 3, 1))

@@ -80,5 +80,9 @@ def test_entry_points_validate_before_touching_the_device(pkg):
     assert "at least one axis" in msg()
     assert lib.fp4b200_mxfp4_quantize_row_and_col_sr(p, 128, 128, 1, 1, 0, 0, 0, 0, 0, 1, 2, p, p, p, None, None) == -1
     # pitched opt quantiser: the pitch of the wider row-code matrix
-    assert lib.fp4b200_nvfp4_quantize_opt_into(p, None, None, 128, 256, p, p, 1, 1, 0, 0, 0, 0, 0, 1, 1, 0, 0, 0, p, 100, p, p, p,
-                                               None, None) == -1 and "row pitch" in msg()
+    assert lib.fp4b200_nvfp4_quantize_opt_into(p, None, None, 128, 256, p, p, 1, 1, 0, 0, 0, 0, 0, 1, 1, 0, 0, None, 0, p, 100, p, p,
+                                               p, None, None) == -1 and "row pitch" in msg()
+    # device-side numbering of stochastic launches: argument checks come before any launch
+    assert lib.fp4b200_sr_prepare_state(None, 1, 2, 1, None) == -1 and "rng_state" in msg()
+    assert lib.fp4b200_sr_prepare_state(p, 1, 2, 0, None) == -1 and "positive" in msg()
+    assert lib.fp4b200_sr_get_invocation_offset(None, None) == -1

@@ -112,28 +112,84 @@ def test_fused_norm_quantize_and_rmsnorm_backward_in_a_graph():
     assert_status_ok()
 
 
-def test_stochastic_rounding_is_refused_inside_capture():
-    """The stochastic quantisers number their launches on the host, so a captured launch would replay one Philox
-    offset on every graph launch (correlated rounding noise step after step).  They raise instead, without having
-    advanced the launch counter, and the capture itself survives."""
+def test_captured_stochastic_rounding_draws_anew_on_every_replay():
+    """The NVFP4 stochastic quantisers number their launches on the device (a one-thread kernel advances the counter
+    and hands the launch its key and offset through device memory, as the reference does), so a captured call
+    reserves a new launch number on every replay: replay k gives the bytes of the eager call made with the counter
+    at the value replay k found.  The MXFP4 forms still count on the host and refuse to be captured."""
     tkq, mxq = mod("tk_quant_v5"), mod("mxfp4_quant_v4")
     x = (1e-3 * torch.randn(256, 256, device="cuda")).to(torch.bfloat16)
+    args = (x, True, False, True, False, "none", False, 77, 5, 448.0, "both")
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
-        tkq.tk_quantize_for_gemm(x, True, False)          # the stream's first call (per-stream scratch) outside capture
+        tkq.tk_quantize_for_gemm_opt(*args)                 # the stream's first call (per-stream scratch) outside capture
     side.synchronize()
-    before = tkq.tk_sr_invocation_count()
+    tkq.tk_set_sr_invocation_count(40)
+    torch.cuda.synchronize()
     g = torch.cuda.CUDAGraph()
     with torch.cuda.graph(g, stream=side):
         with pytest.raises(RuntimeError, match="graph"):
-            tkq.tk_quantize_for_gemm_opt(x, True, False, True, False, "none", False, 1, 0, 448.0, "row")
-        with pytest.raises(RuntimeError, match="graph"):
             mxq.mxfp4_quantize_row_and_col_opt(x, 1, True, False, 1, 0)
-        out = tkq.tk_quantize_for_gemm(x, True, False)     # round to nearest captures as before
-    assert tkq.tk_sr_invocation_count() == before
-    g.replay()
-    torch.cuda.synchronize()
-    ref = tkq.tk_quantize_for_gemm(x, True, False)
-    assert torch.equal(out[0].view(torch.uint8), ref[0].view(torch.uint8))
+        out = tkq.tk_quantize_for_gemm_opt(*args)
+    assert tkq.tk_sr_invocation_count() == 40               # capturing launches nothing
+    replays = []
+    for _ in range(3):
+        g.replay()
+        torch.cuda.synchronize()
+        replays.append([t.view(torch.uint8).clone() for t in out[:4]])
+    assert tkq.tk_sr_invocation_count() == 43
+    assert not torch.equal(replays[0][0], replays[1][0]) and not torch.equal(replays[1][2], replays[2][2])
+    for k in range(3):
+        tkq.tk_set_sr_invocation_count(40 + k)
+        eager = tkq.tk_quantize_for_gemm_opt(*args)
+        for a, b in zip(replays[k], eager[:4]):
+            assert torch.equal(a, b.view(torch.uint8))
+    assert_status_ok()
+
+
+def test_split2_opt_pair_captures_and_equals_its_parts():
+    """tk_silu_deriv_quantize_split_for_gemm_opt_alloc / _launch: buffers once, launch captured, replayed on new data.
+    Each of dh1 / dh3 equals the single-launch quantiser (row operand transformed, both passes one random stream) on
+    the bf16 intermediate at the launch number the pair reserved: one number for both, as in the reference's kernel
+    for this pair."""
+    tkq = mod("tk_quant_v5")
+    M, H = 256, 384
+    def inputs(seed):
+        g = torch.Generator(device="cuda").manual_seed(seed)
+        return ((1e-3 * torch.randn(M, H, device="cuda", generator=g)).to(torch.bfloat16),
+                torch.randn(M, H, device="cuda", generator=g).to(torch.bfloat16),
+                torch.randn(M, H, device="cuda", generator=g).to(torch.bfloat16))
+    dh, h3, h1 = inputs(1)
+    bufs = tkq.tk_silu_deriv_quantize_split_for_gemm_opt_alloc(M, H, dh.device)
+    def launch():
+        return tkq.tk_silu_deriv_quantize_split_for_gemm_opt_launch(dh, h3, h1, True, False, True, True, "row", False, 9, 2,
+                                                                    *bufs, "both")
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        launch()
+    side.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        out = launch()
+    for seed, count in ((2, 11), (3, 12)):
+        a, b, c = inputs(seed)
+        dh.copy_(a); h3.copy_(b); h1.copy_(c)
+        tkq.tk_set_sr_invocation_count(count)
+        torch.cuda.synchronize()
+        g.replay()
+        torch.cuda.synchronize()
+        assert tkq.tk_sr_invocation_count() == count + 1    # one number for the whole pair
+        d1, d3 = tkq.tk_silu_deriv_split_bf16(dh, h3, h1)
+        for t, o in ((d1, out[0:6]), (d3, out[6:12])):
+            row_amax = tkq._amax_rht(t, True, False, 0, 0)
+            plain = tkq._amax_plain(t)
+            state = torch.tensor([9, 2 + (count << 32)], dtype=torch.int64, device=t.device)
+            ref = tkq.tk_quantize_transpose(t, row_amax, plain, True, True, False, True, True, False, True, state)
+            for got, want in zip(o[:4], ref):
+                assert torch.equal(got.view(torch.uint8).reshape(-1), want.view(torch.uint8).reshape(-1))
+            assert float(o[4]) == float(row_amax[1]) and float(o[5]) == float(plain[1])
+    with pytest.raises(RuntimeError, match="one axis"):
+        tkq.tk_silu_deriv_quantize_split_for_gemm_opt_launch(dh, h3, h1, True, False, True, False, "row", False, 9, 2, *bufs, "row")
     assert_status_ok()
