@@ -447,6 +447,100 @@ __device__ __forceinline__ void epilogue_region128(const GemmArgs& g, const Gemm
   }
 }
 
+// Rotary / SiLU epilogue of the pair kernel's wide form: eight epilogue warps per CTA, two per lane quadrant, each
+// owning 128 of the tile's 256 columns.  A warp lifts all its 128 accumulator columns into registers at once and
+// releases them; the MMA thread then starts the next tile while the rotation (about 1400 instructions per lane and
+// 256 columns: too many to sit between two tiles on one warp per scheduler) runs beside that tile's MMAs.  The
+// registers for this come from the other warps of the CTA (setmaxnreg in the kernel).  Sixteen columns at a time:
+// table values from this lane's copy of its table row in tensor memory (cs_taddr != 0) or from global memory, scale,
+// SiLU, rotate, round, stage (one buffer of 32 rows x 128 bytes per warp, 128-byte swizzle), TMA store per 64 columns.
+template <int EPI>
+__device__ __forceinline__ void epilogue_wide(const GemmArgs& g, const GemmOutMaps& tmap_d, uint32_t taddr, uint8_t* epi,
+                                              int row0, int col0, float a_sg, int lane, uint32_t release_cluster_addr,
+                                              uint32_t cs_taddr) {
+  constexpr bool SILU = EPI == kEpiSilu;
+  uint32_t r[128];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) tmem_ld32(taddr + (uint32_t)(32 * k), *reinterpret_cast<uint32_t(*)[32]>(&r[32 * k]));
+  tmem_ld_wait();
+  AccRelease{nullptr, release_cluster_addr}(lane);
+  if (col0 >= g.N) return;   // second half of the last column tile when N is an odd multiple of 128
+
+  float gs = a_sg;
+  if (g.b_sg != nullptr) gs = a_sg * __ldg(g.b_sg + (g.b_sg_per_tile ? (col0 >> 8) : 0));
+  const float2 gs2 = make_float2(gs, gs);
+  const int row = row0 + lane;
+  int oi = 0, col_start = 0;   // which output receives this column range
+  while (oi + 1 < g.n_out && col0 >= g.d_col_end[oi]) { col_start = g.d_col_end[oi]; ++oi; }
+  const int ocol = col0 - col_start;
+  uint8_t* rowp = epi + lane * 128;
+  const int sw = lane & 7;
+  const __nv_bfloat16* res_row = g.residual != nullptr ? g.residual + (size_t)row * g.residual_ld + col0 : nullptr;
+  const bool rope_region = g.rope_cs != nullptr && col0 < g.rope_col_end;
+  const float2* cs_row = (rope_region && cs_taddr == 0) ? g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim : nullptr;
+#pragma unroll
+  for (int slab = 0; slab < 2; ++slab) {          // 64 columns = 128 bytes per row
+    // the staging buffer may be rewritten once the previous slab's store has read it
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int h = 0; h < 4; ++h) {                 // 16 columns = eight pairs
+      const int col = slab * 64 + h * 16;
+      const bool silu_here = SILU && col0 + col < g.silu_col_end;
+      const bool rope_here = rope_region && col0 + col < g.rope_col_end;
+      uint32_t t[16];
+      if (rope_here) {
+        if (cs_taddr != 0) {
+          tmem_ld16(cs_taddr + (uint32_t)((col0 + col) & g.rope_head_mask), t);
+          tmem_ld_wait();
+        } else {
+          const uint4* p = reinterpret_cast<const uint4*>(cs_row + (((col0 + col) & g.rope_head_mask) >> 1));
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 f = __ldg(p + q);
+            t[4 * q] = f.x; t[4 * q + 1] = f.y; t[4 * q + 2] = f.z; t[4 * q + 3] = f.w;
+          }
+        }
+      }
+      uint32_t w[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float2 v = mul2(make_float2(__uint_as_float(r[col + 2 * q]), __uint_as_float(r[col + 2 * q + 1])), gs2);
+        if constexpr (SILU) { if (silu_here) v = make_float2(silu_fast(v.x), silu_fast(v.y)); }
+        uint32_t o = f32x2_to_bf16x2(v.x, v.y);
+        if (rope_here) {
+          // even' = fma(x, cos, -(y*sin)), odd' = fma(y, cos, x*sin); the packed forms rotate the rounded output
+          const float x = g.rope_round_bf16 ? bf16lo_to_f32(o) : v.x, y = g.rope_round_bf16 ? bf16hi_to_f32(o) : v.y;
+          const float cc = __uint_as_float(t[2 * q]), sn = __uint_as_float(t[2 * q + 1]);
+          o = f32x2_to_bf16x2(__fmaf_rn(x, cc, -__fmul_rn(y, sn)), __fmaf_rn(y, cc, __fmul_rn(x, sn)));
+        }
+        w[q] = o;
+      }
+      if (res_row != nullptr) {
+        const uint4* rs = reinterpret_cast<const uint4*>(res_row + col);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+          const uint4 rv = __ldg(rs + q);
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const uint32_t d = w[4 * q + e];
+            w[4 * q + e] = f32x2_to_bf16x2(bf16lo_to_f32(d) + bf16lo_to_f32(rw[e]), bf16hi_to_f32(d) + bf16hi_to_f32(rw[e]));
+          }
+        }
+      }
+      *reinterpret_cast<uint4*>(rowp + (((2 * h) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(rowp + (((2 * h + 1) ^ sw) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(&tmap_d.m[oi], epi, ocol + slab * 64, row0);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+}
+
 // K-segment bookkeeping of the producer: which segment a K stage belongs to and its index inside the segment.
 struct SegCursor {
   int seg = -1, seg_end = 0, kl = 0;
@@ -759,7 +853,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     const int clusters = std::min(pair_tiles, device_sm_count() / 2);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * clusters, 1, 1);
-    cfg.blockDim = dim3(kPairThreads, 1, 1);
+    cfg.blockDim = dim3(pair_form_is_wide(epi) && !mx ? kPairWideThreads : kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = psmem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];

@@ -26,6 +26,12 @@ constexpr int kPairBHalfBytes = 128 * kGemmBKBytes;   // this CTA's half of the 
 constexpr int kPairSfSlots = 2;                       // K stages whose scales are resident in tensor memory
 constexpr int kPairSfBase = 384;                      // accumulators occupy columns [0, 384)
 constexpr int kPairThreads = kGemmThreads;            // producer, MMA thread, four epilogue warps, four scale movers
+// The rotary / SiLU forms ("wide"): four warpgroups — {producer, MMA thread, two idle warps}, four scale movers, and two
+// groups of four epilogue warps — with the register file re-divided between them (setmaxnreg), because an epilogue
+// warp there holds 128 raw accumulator columns while it rotates them.  56 + 88 + 2 x 184 = 512 = 4 x 128.
+constexpr int kPairWideThreads = 512;
+constexpr int kWideRegsControl = 56, kWideRegsMovers = 88, kWideRegsEpilogue = 184;
+__host__ __device__ constexpr bool pair_form_is_wide(int epi) { return epi == kEpiRope || epi == kEpiSilu; }
 
 struct GemmPairSmem {
   alignas(1024) uint8_t a[kPairStages][kATileBytes];
@@ -119,7 +125,7 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 
 // EPI: one epilogue form per instantiation, chosen by the host (see epilogue_region).
 template <bool MX, int EPI = kEpiPlain>
-__global__ void __launch_bounds__(kPairThreads, 1)
+__global__ void __launch_bounds__(pair_form_is_wide(EPI) ? kPairWideThreads : kPairThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
                      const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -129,7 +135,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int cluster_id = blockIdx.x >> 1, n_clusters = gridDim.x >> 1;
   const int tiles_m = g.M / 256, tiles_n = (g.N + kGemmBN - 1) / kGemmBN;
   const PairTiles tiles(g, cluster_id, n_clusters, tiles_m, tiles_n);
-  const int kind_toggle = g.rope_in_tmem ? 0 : 1;      // 0: the accumulator stays at columns [0, 256)
+  constexpr bool kWide = pair_form_is_wide(EPI);
+  // roles by warp: 0 producer, 1 MMA thread; scale movers and epilogue warps in lane-quadrant order (warp & 3)
+  constexpr int kMoverWarp0 = kWide ? 4 : 6, kEpiWarp0 = kWide ? 8 : 2, kEpiWarps = kWide ? 8 : 4;
+  const int kind_toggle = (kWide || g.rope_in_tmem) ? 0 : 1;      // 0: the accumulator stays at columns [0, 256)
   const int k_stages = g.seg_stage_end[g.n_seg - 1];
   const bool k_tail_half = g.seg_tail_half[g.n_seg - 1] != 0;   // only a plain MXFP4 GEMM (one segment) can have one
   constexpr int kSfPerStage = MX ? 1024 : 2048;
@@ -141,7 +150,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
     for (int s = 0; s < kPairSfSlots; ++s) mbar_init(&sm.sf_ready[s], 8);   // four mover warps of each CTA
     mbar_init(&sm.acc_full, 1);
-    mbar_init(&sm.acc_empty_shared, 8);                                      // four epilogue warps of each CTA
+    mbar_init(&sm.acc_empty_shared, 2 * kEpiWarps);                          // the epilogue warps of each CTA
     mbar_init(&sm.acc_empty_priv[0], 8);
     mbar_init(&sm.acc_empty_priv[1], 8);
     fence_mbar_init();
@@ -164,8 +173,12 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   pdl_launch_dependents();
   pdl_wait();
 
-  if (warp == 0) {
+  if (kWide && warp >= 2 && warp < 4) {
+    // idle warps of the first warpgroup: they only hand their registers over
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsControl));
+  } else if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) --------------------------------
+    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsControl));
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -205,6 +218,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ----------------------------
+    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsControl));
     if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t gk = 0;                       // K stages issued so far, over all tiles
@@ -213,7 +227,8 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       bool ok = true;
       for (int ti = 0; ti < tiles.count && ok; ++ti, kind ^= kind_toggle) {
         // the private half was released two tiles ago, the shared half by the previous tile's epilogue
-        if (!mbar_wait_timed(&sm.acc_empty_priv[kind], ((priv_phase >> kind) & 1u) ^ 1u) ||
+        // (wide forms: one accumulator, every epilogue warp arrives on the one barrier)
+        if ((!kWide && !mbar_wait_timed(&sm.acc_empty_priv[kind], ((priv_phase >> kind) & 1u) ^ 1u)) ||
             !mbar_wait_timed(&sm.acc_empty_shared, shared_phase ^ 1)) {
           atomicExch(g.status, kStatusGemmEpilogueTimeout);
           ok = false;
@@ -263,8 +278,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (ok) tc_commit_pair(&sm.acc_full);   // both CTAs' epilogues
       }
     }
-  } else if (warp >= 6) {
+  } else if (warp >= kMoverWarp0 && warp < kMoverWarp0 + 4) {
     // ------------------------------ scale movers (both CTAs) --------------------------------
+    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsMovers));
     // A scale slot is rewritten as soon as the MMAs of the stage two steps back have completed, which the
     // leader's tcgen05.commit announces to both CTAs at once (multicast arrival on that stage's `empty` barrier).
     const int quad = warp & 3;
@@ -305,8 +321,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         if (++stage == kPairStages) { stage = 0; phase ^= 1; }
       }
     }
-  } else {
+  } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {
     // ------------------------------ epilogue (both CTAs) -------------------------------------
+    if constexpr (kWide) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWideRegsEpilogue));
     const int quad = warp & 3;
     uint32_t acc_phase = 0;
     int kind = 0;
@@ -317,17 +334,22 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     bool ok = true;
     int cs_tm = -1;                                   // row block whose table rows are in tensor memory
     const uint32_t cs_taddr = g.rope_in_tmem ? tmem + ((uint32_t)(quad * 32) << 16) + 256u : 0u;
+    const int half = kWide ? (warp - kEpiWarp0) >> 2 : 0;   // wide: which 128 of the tile's 256 columns
     for (int ti = 0; ti < tiles.count && ok; ++ti, kind ^= kind_toggle) {
       int tm, tn;
       tiles.get(ti, tm, tn);
-      if constexpr (EPI == kEpiRope || EPI == kEpiSilu) {
+      if constexpr (kWide) {
         if (g.rope_in_tmem && tm != cs_tm) {
           // This lane's row of the (cos, sin) table, 2 * pair_dim floats, into columns [256, 256 + 2 * pair_dim) of
           // its tensor-memory lane: once per row block, while the tile's MMAs run.  Every later tile of the row
           // block reads the sixteen columns it needs from there instead of 64 scattered bytes per lane from L2.
+          // The quadrant's two warps write half of the row each, after both have finished with the previous row
+          // block's values and before either reads the new ones (named barrier 1 + quad, 64 threads).
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
           const int row = tm * 256 + (int)rank * 128 + quad * 32 + lane;
           const float4* src = reinterpret_cast<const float4*>(g.rope_cs + (size_t)(row & g.rope_seq_mask) * g.rope_pair_dim);
-          for (int c = 0; c < (g.rope_pair_dim >> 4); ++c) {      // 32 floats = 16 pairs per store
+          const int chunks = g.rope_pair_dim >> 4;            // stores of 32 floats = 16 pairs: 2 (heads of 64) or 4
+          for (int c = half * (chunks >> 1); c < (half + 1) * (chunks >> 1); ++c) {
             uint32_t v[32];
 #pragma unroll
             for (int q = 0; q < 8; ++q) {
@@ -338,6 +360,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             tmem_st32(cs_taddr + (uint32_t)(32 * c), v);
           }
           asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+          tc_fence_before();
+          asm volatile("bar.sync %0, 64;" ::"r"(1 + quad) : "memory");
+          tc_fence_after();
           cs_tm = tm;
         }
       }
@@ -348,15 +373,21 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       }
       tc_fence_after();
       const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
-      uint8_t* epi = &sm.epi[warp - 2][0][0];
       const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
       const int col0 = tn * kGemmBN;
-      // tensor-memory columns [128, 256) hold output columns [128, 256) of a tile at [0, 256) and output
-      // columns [0, 128) of a tile at [128, 384): lift them out first, the next tile needs them
-      epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane,
-                              AccRelease{nullptr, empty_shared_leader}, cs_taddr);
-      epilogue_region128<EPI>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane,
-                              AccRelease{nullptr, kind ? empty_priv_leader1 : empty_priv_leader0}, cs_taddr);
+      if constexpr (kWide) {
+        uint8_t* epi = &sm.epi[0][0][0] + (size_t)(warp - kEpiWarp0) * 4096;   // one staging buffer per warp
+        epilogue_wide<EPI>(g, tmap_d, tq + (uint32_t)(half * 128), epi, row0, col0 + half * 128, a_sg, lane,
+                           empty_shared_leader, cs_taddr);
+      } else {
+        uint8_t* epi = &sm.epi[warp - kEpiWarp0][0][0];
+        // tensor-memory columns [128, 256) hold output columns [128, 256) of a tile at [0, 256) and output
+        // columns [0, 128) of a tile at [128, 384): lift them out first, the next tile needs them
+        epilogue_region128<EPI>(g, tmap_d, tq + 128, epi, row0, col0 + (kind ? 0 : 128), a_sg, lane,
+                                AccRelease{nullptr, empty_shared_leader}, cs_taddr);
+        epilogue_region128<EPI>(g, tmap_d, tq + (kind ? 256 : 0), epi, row0, col0 + (kind ? 128 : 0), a_sg, lane,
+                                AccRelease{nullptr, kind ? empty_priv_leader1 : empty_priv_leader0}, cs_taddr);
+      }
       acc_phase ^= 1;
     }
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");

@@ -177,6 +177,39 @@ def test_grouped_gemm_with_rope_epilogue(M):
         gemm.nvfp4_grouped_gemm_rope_live64(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, 96)
 
 
+def test_rope_epilogue_over_many_row_blocks():
+    """More tiles than CTA pairs (16 x 12 tiles of 256 x 256): every pair works through a run of tiles that crosses
+    from one row block into the next, so the per-row-block refill of the rotation table (and the hand-over between
+    the two epilogue warps of a lane quadrant) is exercised; every output element is checked against the oracle's
+    rotation of the fp32 epilogue of the same GEMM."""
+    gemm = mod("tk_gemm_c")
+    M, K, q_dim, k_dim, v_dim, seq = 4096, 256, 2048, 512, 512, 1024
+    N = q_dim + k_dim + v_dim
+    x, w, qx, qw = _quant_pair(M, N, K, seed=91)
+    b_sg = qw[4].expand(N // 256).contiguous()
+    d32 = torch.empty((M, N), dtype=torch.float32, device="cuda")
+    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], qw[0], qw[1], qw[4], d32)
+    torch.cuda.synchronize()
+    v = d32.cpu().numpy()
+    rng = np.random.default_rng(8)
+    for head, form in ((128, "split"), (64, "live64")):
+        ang = rng.uniform(0, 2 * np.pi, size=(seq, head // 2)).astype(np.float32)
+        cs = np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+        cs_d = torch.from_numpy(cs).cuda()
+        dq = torch.full((M, q_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dk = torch.full((M, k_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        dv = torch.full((M, v_dim), float("nan"), dtype=torch.bfloat16, device="cuda")
+        if form == "live64":
+            gemm.nvfp4_grouped_gemm_rope_live64(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, seq)
+        else:
+            gemm.nvfp4_grouped_gemm_rope_packed_split(qx[0], qx[1], qx[4], qw[0], qw[1], b_sg, dq, dk, dv, cs_d, seq, head, head)
+        torch.cuda.synchronize()
+        assert_status_ok()
+        got = torch.cat([dq, dk, dv], dim=1).float().cpu().numpy()
+        ref = o.rope_epilogue(v, cs, head, q_dim + k_dim, form != "live64")
+        assert np.array_equal(got, ref), form
+
+
 @pytest.mark.parametrize("M", [256, 128])
 def test_grouped_gemm_silu_epilogue(M):
     """silu_dim: x / (1 + exp(-x)) on the first output columns in the epilogue (hardware __expf: one bf16 step against
