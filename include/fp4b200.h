@@ -244,9 +244,10 @@ int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const
                        int64_t K, void* stream);
 
 /* One term of nvfp4_batched_accum_gemm (nvfp4_b200_gemm.cu:2567-2635; kernel nvfp4_batched_accum_gemm.cuh):
- * D = round(partial_f32 + acc * A_sg * B_sg), partial_f32 a caller buffer [M,N] holding the fp32 sum of the
- * earlier terms (written by this entry point or by fp4b200_nvfp4_gemm with out_fp32 = 1).  D may alias
- * partial_f32 when out_fp32 = 1. */
+ * D = round(fma(acc, A_sg * B_sg, partial_f32)), partial_f32 a caller buffer [M,N] holding the fp32 sum of the
+ * earlier terms (written by this entry point or by fp4b200_nvfp4_gemm with out_fp32 = 1).  One rounding per term
+ * after the first, as the reference's kernel does (nvfp4_batched_accum_gemm.cuh:293-310: its multiply and add are
+ * compiled to a fused multiply-add).  D may alias partial_f32 when out_fp32 = 1. */
 int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                              const float* B_sg, const float* partial_f32, void* D, int out_fp32, int64_t M, int64_t N,
                              int64_t K, void* stream);

@@ -84,7 +84,7 @@ struct GemmArgs {
   int out_fp32;             // 0: bf16 output, 1: fp32 output
   const __nv_bfloat16* residual;  // optional [M, N] bf16 added after the bf16 rounding
   int residual_ld;
-  const float* accum_f32;   // optional [M, N] fp32 partial sum added to acc*scale before the output rounding
+  const float* accum_f32;   // optional [M, N] fp32 partial sum: fma(acc, scale, partial) before the output rounding
   // optional rotary embedding of the column range [0, rope_col_end) (the Q and K parts of a fused QKV projection)
   // in the bf16 epilogue: pairs of neighbouring columns rotated by the (cos, sin) entry of their token and
   // position inside the head (reference: nvfp4_rope_epilogue.cuh:104-161)
@@ -321,15 +321,17 @@ __device__ __noinline__ void epilogue_region(const GemmArgs& g, const GemmOutMap
     for (int c = 0; c < NCOLS / 32; ++c) {
       float v[32];
       if (g.accum_f32 != nullptr) {
-        // running fp32 sum over a batch of GEMMs: partial + acc*scale (multiply, then add)
+        // running fp32 sum over a batch of GEMMs: fma(acc, scale, partial), one rounding per term — what the
+        // reference's kernel does for every term after the first (its multiply and add contract to a fused
+        // multiply-add; checked against its compiled kernel's output bytes)
         const float4* ps = reinterpret_cast<const float4*>(g.accum_f32 + (size_t)row * g.N + col0 + 32 * c);
 #pragma unroll
         for (int q = 0; q < 8; ++q) {
           const float4 pv = __ldg(ps + q);
-          v[4 * q] = __fadd_rn(pv.x, __fmul_rn(__uint_as_float(r[32 * c + 4 * q]), gs));
-          v[4 * q + 1] = __fadd_rn(pv.y, __fmul_rn(__uint_as_float(r[32 * c + 4 * q + 1]), gs));
-          v[4 * q + 2] = __fadd_rn(pv.z, __fmul_rn(__uint_as_float(r[32 * c + 4 * q + 2]), gs));
-          v[4 * q + 3] = __fadd_rn(pv.w, __fmul_rn(__uint_as_float(r[32 * c + 4 * q + 3]), gs));
+          v[4 * q] = __fmaf_rn(__uint_as_float(r[32 * c + 4 * q]), gs, pv.x);
+          v[4 * q + 1] = __fmaf_rn(__uint_as_float(r[32 * c + 4 * q + 1]), gs, pv.y);
+          v[4 * q + 2] = __fmaf_rn(__uint_as_float(r[32 * c + 4 * q + 2]), gs, pv.z);
+          v[4 * q + 3] = __fmaf_rn(__uint_as_float(r[32 * c + 4 * q + 3]), gs, pv.w);
         }
       } else {
 #pragma unroll

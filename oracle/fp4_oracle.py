@@ -443,6 +443,39 @@ def nvfp4_gemm_fp32(a_fp4, a_sc_logical, a_sg, b_fp4, b_sc_logical, b_sg) -> np.
     return (acc.astype(F32) * gs).astype(F32)
 
 
+def fma_f32(a: np.ndarray, b, c: np.ndarray) -> np.ndarray:
+    """Element-wise fused multiply-add ``round_fp32(a * b + c)`` of fp32 arrays with ONE rounding.  The product of
+    two fp32 numbers is exact in float64; the sum with c is formed in float64 together with its exact rounding error
+    (two-sum), and the error decides the direction where the float64 sum sits exactly half way between two fp32
+    values — the only case in which rounding twice could differ from rounding once."""
+    p = np.asarray(a, dtype=np.float32).astype(np.float64) * np.asarray(b, dtype=np.float32).astype(np.float64)
+    c64 = np.asarray(c, dtype=np.float32).astype(np.float64)
+    s = p + c64
+    bb = s - p
+    err = (p - (s - bb)) + (c64 - bb)
+    r = s.astype(np.float32)
+    tie = (np.ascontiguousarray(s).view(np.int64) & 0x1FFFFFFF) == 0x10000000     # low 29 mantissa bits: exactly one half
+    fix = tie & (err != 0) & np.isfinite(s)
+    if fix.any():
+        lo = np.minimum(np.nextafter(r, np.float32(-np.inf)), r)
+        hi = np.maximum(np.nextafter(r, np.float32(np.inf)), r)
+        down = np.where(r.astype(np.float64) > s, lo, r)      # the fp32 neighbour below / above the half-way point
+        up = np.where(r.astype(np.float64) < s, hi, r)
+        r = np.where(fix, np.where(err > 0, up, down), r)
+    return r.astype(np.float32)
+
+
+def nvfp4_batched_accum_f32(raw_accs, scales) -> np.ndarray:
+    """fp32 running sum of nvfp4_batched_accum_gemm before its one bf16 rounding: term 0 is ``acc_0 * s_0``
+    (rounded), every later term ``fma(acc_i, s_i, sum)`` — the reference's source multiplies and adds
+    (nvfp4_batched_accum_gemm.cuh:293-310) and its compiled kernel fuses the two, which its output bytes show.
+    raw_accs: unscaled fp32 accumulators [M, N]; scales: fp32 ``A_sg_i * B_sg_i``."""
+    acc = (np.asarray(raw_accs[0], dtype=np.float32) * F32(scales[0])).astype(np.float32)
+    for a, s_ in zip(raw_accs[1:], scales[1:]):
+        acc = fma_f32(a, F32(s_), acc)
+    return acc
+
+
 # ----------------------------------------------------------------------------------------
 # MXFP4 (32-blocks, E8M0 scales)
 # ----------------------------------------------------------------------------------------

@@ -2,6 +2,9 @@
 high-precision product of dequantised operands.  Tolerance (stated by the benchmark spec): relative
 Frobenius error <= 1e-3 for the fp32 epilogue; the bf16 output is compared with the bf16-rounded
 oracle (bf16 rounding alone is ~1.7e-3 relative, above that bound)."""
+import hashlib
+import os
+
 import numpy as np
 import pytest
 import torch
@@ -120,11 +123,37 @@ def test_grouped_residual_and_batched_accum():
     acc = torch.empty_like(h1)
     gemm.nvfp4_batched_accum_gemm([qx[0], qx[0]], [qx[1], qx[1]], [qx[4], qx[4]], [q1[0], q3[0]], [q1[1], q3[1]],
                                   [q1[4], q3[4]], acc)
-    f1 = torch.empty((M, H), dtype=torch.float32, device="cuda"); f3 = torch.empty_like(f1)
-    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], q1[0], q1[1], q1[4], f1)
-    gemm.nvfp4_gemm(qx[0], qx[1], qx[4], q3[0], q3[1], q3[4], f3)
+    # the oracle's summation order on the raw accumulators (fp32 epilogue with unit tensor scales): first term
+    # multiplied, the second joined by one fused multiply-add, one bf16 rounding at the end
+    one = torch.ones(1, device="cuda")
+    r1 = torch.empty((M, H), dtype=torch.float32, device="cuda"); r3 = torch.empty_like(r1)
+    gemm.nvfp4_gemm(qx[0], qx[1], one, q1[0], q1[1], one, r1)
+    gemm.nvfp4_gemm(qx[0], qx[1], one, q3[0], q3[1], one, r3)
     torch.cuda.synchronize()
-    assert torch.equal(acc, (f1 + f3).to(torch.bfloat16))
+    scales = [np.float32(qx[4].item()) * np.float32(q1[4].item()), np.float32(qx[4].item()) * np.float32(q3[4].item())]
+    want = o.bf16_round(o.nvfp4_batched_accum_f32([r1.cpu().numpy(), r3.cpu().numpy()], scales))
+    assert np.array_equal(acc.float().cpu().numpy(), want)
+    assert_status_ok()
+
+
+def test_batched_accum_equals_the_reference_kernels_bytes():
+    """nvfp4_batched_accum_gemm with 2, 3 and 4 terms against the output bytes of the reference's own kernel on the
+    same operands (tests/golden/make_accum_golden.py recorded them on a B200): pins the fp32 summation order."""
+    gold = np.load(os.path.join(os.path.dirname(__file__), "golden", "nvfp4_accum_reference_golden.npz"))
+    import importlib.util
+    spec = importlib.util.spec_from_file_location("make_accum_golden",
+                                                  os.path.join(os.path.dirname(__file__), "golden", "make_accum_golden.py"))
+    mk = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mk)
+    gemm = mod("tk_gemm_c")
+    terms = mk.make_terms(4)
+    for n in (2, 3, 4):
+        d = torch.empty(mk.M, mk.N, dtype=torch.bfloat16, device="cuda")
+        gemm.nvfp4_batched_accum_gemm(*mk.split(terms[:n]), d)
+        torch.cuda.synchronize()
+        bits = d.view(torch.int16).cpu().numpy()
+        assert np.array_equal(bits[::8], gold[f"rows_{n}"]), n
+        assert hashlib.sha256(bits.tobytes()).digest() == gold[f"sha256_{n}"].tobytes(), n
     assert_status_ok()
 
 
