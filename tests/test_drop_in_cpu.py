@@ -12,7 +12,8 @@ REQUIRED = {
                      "tk_fused_norm_quantize_from_inv_rms", "tk_silu_quantize_split_for_gemm",
                      "tk_silu_deriv_quantize_split_for_gemm", "tk_silu_deriv_quantize_split_for_gemm_opt",
                      "tk_quantize_for_gemm_opt", "tk_quantize_transpose", "tk_fused_norm_quantize_opt",
-                     "tk_quantize_nhsd_wo_for_gemm", "tk_group_quantize_dim1_split3_for_gemm"],
+                     "tk_quantize_nhsd_wo_for_gemm", "tk_group_quantize_dim1_split3_for_gemm",
+                     "tk_silu_deriv_quantize_split_for_gemm_opt_alloc", "tk_silu_deriv_quantize_split_for_gemm_opt_launch"],
     # tk_gemm.py:3454-3461 dereferences nvfp4_split_dgrad_sum and nvfp4_batched_accum_gemm unconditionally
     "_C": ["nvfp4_gemm", "nvfp4_gemm_config", "nvfp4_gemm_nopdl", "nvfp4_grouped_gemm", "nvfp4_gemm_residual",
            "nvfp4_batched_gemm", "nvfp4_split_dgrad_sum", "nvfp4_batched_accum_gemm", "nvfp4_forward_rope_packed_qk",
