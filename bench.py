@@ -809,9 +809,8 @@ def main():
         raise RuntimeError("bench.py needs a CUDA device: the FP4 hot path has no CPU fallback")
     torch.cuda.set_device(local_rank)
     if world > 1:
-        # NCCL writes its version banner to stdout at the VERSION level; stdout carries the one JSON line
-        if os.environ.get("NCCL_DEBUG", "VERSION").upper() == "VERSION":
-            os.environ["NCCL_DEBUG"] = "WARN"
+        # NCCL writes its version banner and debug lines to stdout; stdout carries the one JSON line
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
     tkq = importlib.import_module("mfu-fp4-training_b200.tk_quant_v5")

@@ -156,14 +156,14 @@ int fp4b200_nvfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
                                   void* row_sc, void* col_fp4, void* col_sc, void* stream);
 
 /* Fused RMSNorm + NVFP4 quantisation (encode-centric, as fp4b200_nvfp4_fused_norm_quantize with
- * compute_inv_rms = 1) for callers that cannot allocate device memory: code running inside a CUDA
- * graph capture, under a memory pool that is already full by design, or in a host thread that
- * is not allowed to touch the allocator.  It has no counterpart in the reference, whose producers
+ * compute_inv_rms = 1) for callers that cannot allocate device memory: code running under a memory pool
+ * that is already full by design, or in a host thread that is not allowed to touch the allocator.
+ * It has no counterpart in the reference, whose producers
  * always allocate their scratch through torch.  The caller passes inputs and outputs only (sg_out
  * receives amax/2688); the per-row inverse RMS and the first pass's per-CTA partial maxima live
  * in a fixed array inside the library (264 KiB per device, held until the process exits), so M is
  * limited to 65536 rows and larger calls are rejected with an error.  The first call on a device
- * looks up the array's device address; make that call before any stream capture starts.  All calls
+ * looks up the array's device address (cached afterwards; host threads may race to cache the same value).  All calls
  * share the array, which keeps the previous call's contents (every call overwrites the part it
  * reads): two calls that overlap on the GPU, e.g. on different streams, race. */
 int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,
@@ -251,6 +251,16 @@ int fp4b200_nvfp4_gemm(const void* A, const void* A_sc, const float* A_sg, const
 int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,
                              const float* B_sg, const float* partial_f32, void* D, int out_fp32, int64_t M, int64_t N,
                              int64_t K, void* stream);
+
+/* nvfp4_batched_accum_gemm in one launch (nvfp4_b200_gemm.cu:2567-2635; kernel nvfp4_batched_accum_gemm.cuh):
+ * D = bf16(sum_i (A_i . B_i^T) * A_sg_i * B_sg_i) for 1 to 4 terms, each with its own operands, scale tensors,
+ * tensor scales and reduction width K[i].  The terms' accumulators are handed to the epilogue one after the other
+ * and summed there in fp32 registers in the reference's order (term 0 multiplied, every later term by one fused
+ * multiply-add), one rounding to bf16, one store.  Needs M % 256 == 0 (two-CTA kernel); otherwise chain
+ * fp4b200_nvfp4_gemm (fp32 output) and fp4b200_nvfp4_gemm_accum. */
+int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const void* const* A_sc, const float* const* A_sg,
+                                     const void* const* B, const void* const* B_sc, const float* const* B_sg,
+                                     const int64_t* K, void* D, int64_t M, int64_t N, void* stream);
 
 /* nvfp4_grouped_gemm (nvfp4_b200_gemm.cu:764-841): B is the row concatenation of n_out weights,
  * B_sg_per_tile holds one tensor scale per 256 rows of B, output i receives D_cols[i] columns

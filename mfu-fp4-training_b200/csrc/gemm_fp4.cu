@@ -73,6 +73,11 @@ struct GemmArgs {
   const uint8_t* seg_b_sc[kMaxKSeg];   // [N/128, Kseg/(4*block), 512]
   int seg_sf_tiles_k[kMaxKSeg];     // scale tiles along K per row tile, per segment
   int seg_tail_half[kMaxKSeg];      // 1: the segment's last stage holds 128 elements only (MXFP4, K an odd multiple of 128)
+  // Batched accumulation (kEpiBatchSum): every segment is a GEMM term of its own — its own A tensor (tensor map
+  // tmap_a_seg.m[s]) and its own tensor scales; the terms' scaled accumulators are summed in fp32 by the epilogue.
+  int a_per_seg;
+  const float* seg_a_sg[kMaxKSeg];
+  const float* seg_b_sg[kMaxKSeg];
   const float* a_sg;        // device scalar (NVFP4) or null
   const float* b_sg;        // device scalar, or per-256-column-tile array when b_sg_per_tile != 0
   int b_sg_per_tile;
@@ -244,7 +249,7 @@ __device__ __forceinline__ void load_stage_scales(const uint8_t* sfa, const uint
 }
 
 
-constexpr int kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2, kEpiGeneral = 3;
+constexpr int kEpiPlain = 0, kEpiRope = 1, kEpiSilu = 2, kEpiGeneral = 3, kEpiBatchSum = 4;
 
 // x / (1 + exp(-x)) with the hardware exponential and approximate division: no slow-path branch, so the
 // unrolled uses in the epilogue stay a few instructions each.
@@ -543,6 +548,61 @@ __device__ __forceinline__ void epilogue_wide(const GemmArgs& g, const GemmOutMa
   }
 }
 
+// Batched accumulation in the pair kernel's wide structure (eight epilogue warps, 128 columns each): the MMA thread
+// hands over one accumulator per term; a warp folds it into a register sum — term 0: acc * scale (rounded), later
+// terms: fma(acc, scale, sum), the reference's order (nvfp4_batched_accum_gemm.cuh:293-310 as compiled) — 16 columns
+// at a time, releases the accumulator, and after the last term rounds the sum to bf16 and stores it.
+// acc_phase: the parity the warp waits for next; returns false when a wait ran out.
+__device__ __forceinline__ bool epilogue_batch_sum(const GemmArgs& g, const GemmOutMaps& tmap_d, uint64_t* acc_full, uint32_t& acc_phase,
+                                                   uint32_t taddr, uint8_t* epi, int row0, int col0, int lane,
+                                                   uint32_t release_cluster_addr) {
+  float sum[128];
+  for (int term = 0; term < g.n_seg; ++term) {
+    if (!mbar_wait_timed(acc_full, acc_phase)) {
+      if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
+      return false;
+    }
+    acc_phase ^= 1;
+    tc_fence_after();
+    const float gs = __ldg(g.seg_a_sg[term]) * __ldg(g.seg_b_sg[term]);
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {          // sixteen columns at a time: the sum already holds 128 registers
+      uint32_t r[16];
+      tmem_ld16(taddr + (uint32_t)(16 * c), r);
+      tmem_ld_wait();
+      if (term == 0) {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) sum[16 * c + q] = __fmul_rn(__uint_as_float(r[q]), gs);
+      } else {
+#pragma unroll
+        for (int q = 0; q < 16; ++q) sum[16 * c + q] = __fmaf_rn(__uint_as_float(r[q]), gs, sum[16 * c + q]);
+      }
+    }
+    AccRelease{nullptr, release_cluster_addr}(lane);
+  }
+  if (col0 >= g.N) return true;   // second half of the last column tile when N is an odd multiple of 128
+  uint8_t* rowp = epi + lane * 128;
+  const int sw = lane & 7;
+#pragma unroll
+  for (int slab = 0; slab < 2; ++slab) {          // 64 columns = 128 bytes per row
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+    __syncwarp();
+#pragma unroll
+    for (int q = 0; q < 8; ++q) {
+      const float* v = sum + slab * 64 + 8 * q;
+      *reinterpret_cast<uint4*>(rowp + ((q ^ sw) << 4)) =
+          make_uint4(f32x2_to_bf16x2(v[0], v[1]), f32x2_to_bf16x2(v[2], v[3]), f32x2_to_bf16x2(v[4], v[5]), f32x2_to_bf16x2(v[6], v[7]));
+    }
+    fence_proxy_async_smem();
+    __syncwarp();
+    if (lane == 0) {
+      tma_store_2d(&tmap_d.m[0], epi, col0 + slab * 64, row0);
+      asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+    }
+  }
+  return true;
+}
+
 // K-segment bookkeeping of the producer: which segment a K stage belongs to and its index inside the segment.
 struct SegCursor {
   int seg = -1, seg_end = 0, kl = 0;
@@ -785,6 +845,12 @@ struct KSegments {
   const void* a_sc[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
   const void* b[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
   const void* b_sc[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+  // batched accumulation (two-CTA kernel only): every segment is a term with its own A tensor [M, k/2] and tensor scales,
+  // summed in fp32 by the epilogue instead of in tensor memory
+  bool batch_sum = false;
+  const void* a[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+  const float* a_sg[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+  const float* b_sg[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
 };
 
 // Rotary embedding applied by the bf16 epilogue to the output columns [0, col_end).
@@ -800,10 +866,19 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
                             const float* accum_f32 = nullptr, const RopeDesc* rope = nullptr) {
   const bool pair = (M % 256) == 0 && !gemm_pair_disabled();
   CUtensorMap tmap_a;
-  GemmBMaps tmap_b;
+  GemmBMaps tmap_b, tmap_a_seg;
   memset(&tmap_b, 0, sizeof(tmap_b));
-  if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.a_width / 2, (uint64_t)M,
-                            (uint64_t)segs.a_width / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
+  memset(&tmap_a_seg, 0, sizeof(tmap_a_seg));
+  if (segs.batch_sum && (!pair || mx || out_fp32 || residual != nullptr || accum_f32 != nullptr || rope != nullptr || n_out != 1))
+    return set_error("batched accumulation in one kernel: NVFP4, M a multiple of 256, one bf16 output");
+  if (segs.batch_sum) {
+    for (int s = 0; s < segs.n; ++s)
+      if (int rc = make_tmap_2d(&tmap_a_seg.m[s], segs.a[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.k[s] / 2, (uint64_t)M,
+                                (uint64_t)segs.k[s] / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
+        return rc;
+    tmap_a = tmap_a_seg.m[0];
+  } else if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.a_width / 2, (uint64_t)M,
+                                   (uint64_t)segs.a_width / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   int64_t K = 0, stages = 0;
   GemmArgs g{};
@@ -821,7 +896,10 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     g.seg_a_sc[s] = (const uint8_t*)segs.a_sc[s];
     g.seg_b_sc[s] = (const uint8_t*)segs.b_sc[s];
     g.seg_sf_tiles_k[s] = (int)(segs.k[s] / (mx ? 128 : 64));
+    g.seg_a_sg[s] = segs.a_sg[s];
+    g.seg_b_sg[s] = segs.b_sg[s];
   }
+  g.a_per_seg = segs.batch_sum ? 1 : 0;
   GemmOutMaps omaps;
   memset(&omaps, 0, sizeof(omaps));
   for (int i = 0; i < n_out; ++i) {
@@ -846,7 +924,8 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   g.rope_in_tmem = pair && g.rope_cs != nullptr && (rope->head_dim == 64 || rope->head_dim == 128);
   g.status = device_status_ptr();
   if (g.status == nullptr) return -1;
-  const int epi = (g.out_fp32 || g.accum_f32 != nullptr) ? kEpiGeneral
+  const int epi = segs.batch_sum ? kEpiBatchSum
+                  : (g.out_fp32 || g.accum_f32 != nullptr) ? kEpiGeneral
                   : g.silu_col_end > 0 ? kEpiSilu : g.rope_cs != nullptr ? kEpiRope : kEpiPlain;
   if (pair) {
     // two-CTA clusters: one 256 x 256 tile per pair of SMs
@@ -868,11 +947,12 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
 #define FP4_LAUNCH_PAIR(MXF, EPI)                                                                                          \
   do {                                                                                                                   \
     FP4_CUDA_CHECK(cudaFuncSetAttribute(fp4_gemm_pair_kernel<MXF, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, psmem)); \
-    FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<MXF, EPI>, tmap_a, tmap_b, omaps, g));                   \
+    FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<MXF, EPI>, tmap_a, tmap_b, omaps, g, tmap_a_seg));       \
   } while (0)
     if (mx) {
       if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(true, kEpiGeneral); else FP4_LAUNCH_PAIR(true, kEpiPlain);
     } else if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(false, kEpiGeneral);
+    else if (epi == kEpiBatchSum) FP4_LAUNCH_PAIR(false, kEpiBatchSum);
     else if (epi == kEpiSilu) FP4_LAUNCH_PAIR(false, kEpiSilu);
     else if (epi == kEpiRope) FP4_LAUNCH_PAIR(false, kEpiRope);
     else FP4_LAUNCH_PAIR(false, kEpiPlain);
@@ -981,6 +1061,31 @@ int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg,
   int ce[1] = {(int)N}, ld[1] = {(int)N};
   return launch_gemm(false, A, A_sc, A_sg, B, B_sc, B_sg, 0, d, ce, ld, 1, out_fp32, nullptr, 0, M, N, K,
                      (cudaStream_t)stream, partial_f32);
+}
+
+int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const void* const* A_sc, const float* const* A_sg,
+                                     const void* const* B, const void* const* B_sc, const float* const* B_sg,
+                                     const int64_t* K, void* D, int64_t M, int64_t N, void* stream) {
+  const char* fn = "nvfp4_batched_accum_gemm";
+  if (n_terms < 1 || n_terms > kMaxKSeg) return set_error("%s: 1 to %d terms (got %d)", fn, kMaxKSeg, n_terms);
+  if (!A || !A_sc || !A_sg || !B || !B_sc || !B_sg || !K || !D) return set_error("%s: null argument", fn);
+  if ((M % 256) != 0 || gemm_pair_disabled())
+    return set_error("%s: the one-kernel form needs M to be a multiple of 256 (two-CTA kernel); use the chain of "
+                     "fp4b200_nvfp4_gemm_accum launches otherwise", fn);
+  KSegments segs;
+  segs.n = n_terms;
+  segs.batch_sum = true;
+  for (int i = 0; i < n_terms; ++i) {
+    if (int rc = check_gemm(A[i], A_sc[i], B[i], B_sc[i], M, N, K[i], fn)) return rc;
+    if (!A_sg[i] || !B_sg[i]) return set_error("%s: every term needs its tensor scales", fn);
+    segs.k[i] = K[i];
+    segs.a[i] = A[i]; segs.a_sc[i] = A_sc[i]; segs.a_sg[i] = A_sg[i];
+    segs.b[i] = B[i]; segs.b_sc[i] = B_sc[i]; segs.b_sg[i] = B_sg[i];
+  }
+  segs.a_width = K[0];
+  void* d[1] = {D};
+  int ce[1] = {(int)N}, ld[1] = {(int)N};
+  return launch_gemm_segs(false, A[0], segs, nullptr, nullptr, 0, d, ce, ld, 1, 0, nullptr, 0, M, N, (cudaStream_t)stream);
 }
 
 int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_sg, const void* B, const void* B_sc,

@@ -31,7 +31,9 @@ constexpr int kPairThreads = kGemmThreads;            // producer, MMA thread, f
 // warp there holds 128 raw accumulator columns while it rotates them.  56 + 88 + 2 x 184 = 512 = 4 x 128.
 constexpr int kPairWideThreads = 512;
 constexpr int kWideRegsControl = 56, kWideRegsMovers = 88, kWideRegsEpilogue = 184;
-__host__ __device__ constexpr bool pair_form_is_wide(int epi) { return epi == kEpiRope || epi == kEpiSilu; }
+// batched accumulation: the producer and the MMA thread track segments as well (56 + 72 + 2 x 192 = 512)
+constexpr int kSumRegsControl = 56, kSumRegsMovers = 72, kSumRegsEpilogue = 192;
+__host__ __device__ constexpr bool pair_form_is_wide(int epi) { return epi == kEpiRope || epi == kEpiSilu || epi == kEpiBatchSum; }
 
 struct GemmPairSmem {
   alignas(1024) uint8_t a[kPairStages][kATileBytes];
@@ -127,7 +129,8 @@ __device__ __forceinline__ void tc_mma_pair(uint32_t d_tmem, uint64_t adesc, uin
 template <bool MX, int EPI = kEpiPlain>
 __global__ void __launch_bounds__(pair_form_is_wide(EPI) ? kPairWideThreads : kPairThreads, 1)
 fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ GemmBMaps tmap_b,
-                     const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g) {
+                     const __grid_constant__ GemmOutMaps tmap_d, const GemmArgs g,
+                     const __grid_constant__ GemmBMaps tmap_a_seg) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   GemmPairSmem& sm = *reinterpret_cast<GemmPairSmem*>(smem_align_1024(smem_raw));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -136,6 +139,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int tiles_m = g.M / 256, tiles_n = (g.N + kGemmBN - 1) / kGemmBN;
   const PairTiles tiles(g, cluster_id, n_clusters, tiles_m, tiles_n);
   constexpr bool kWide = pair_form_is_wide(EPI);
+  constexpr bool kBatchSum = EPI == kEpiBatchSum;   // every K segment is a term with an accumulator hand-over of its own
+  constexpr int kRegsControl = kBatchSum ? kSumRegsControl : kWideRegsControl, kRegsMovers = kBatchSum ? kSumRegsMovers : kWideRegsMovers,
+                kRegsEpilogue = kBatchSum ? kSumRegsEpilogue : kWideRegsEpilogue;
   // roles by warp: 0 producer, 1 MMA thread; scale movers and epilogue warps in lane-quadrant order (warp & 3)
   constexpr int kMoverWarp0 = kWide ? 4 : 6, kEpiWarp0 = kWide ? 8 : 2, kEpiWarps = kWide ? 8 : 4;
   const int kind_toggle = (kWide || g.rope_in_tmem) ? 0 : 1;      // 0: the accumulator stays at columns [0, 256)
@@ -175,10 +181,10 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 
   if (kWide && warp >= 2 && warp < 4) {
     // idle warps of the first warpgroup: they only hand their registers over
-    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsControl));
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
   } else if (warp == 0) {
     // ------------------------------ TMA producer (both CTAs) --------------------------------
-    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsControl));
+    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
     if (lane == 0) {
       int stage = 0;
       uint32_t phase = 0;
@@ -189,11 +195,13 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         SegCursor cur;
         int a_col = 0;
         const CUtensorMap* bmap = nullptr;
+        const CUtensorMap* amap = &tmap_a;
         const uint8_t *sfa_src = nullptr, *sfb_src0 = nullptr, *sfb_src1 = nullptr;
         for (int ks = 0; ks < k_stages; ++ks) {
           if (cur.enter(g, ks)) {   // first stage of the next K segment
             a_col = g.seg_a_col_bytes[cur.seg];
             bmap = &tmap_b.m[cur.seg];
+            if (g.a_per_seg) amap = &tmap_a_seg.m[cur.seg];
             const size_t tiles_k = (size_t)g.seg_sf_tiles_k[cur.seg];
             sfa_src = g.seg_a_sc[cur.seg] + (size_t)(2 * tm + rank) * tiles_k * 512;
             sfb_src0 = g.seg_b_sc[cur.seg] + (size_t)(2 * tn) * tiles_k * 512;
@@ -207,7 +215,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
           const uint32_t sf_bytes = (MX && k_tail_half && ks + 1 == k_stages) ? kSfPerStage / 2 : kSfPerStage;
           mbar_expect_tx(&sm.full[stage], kATileBytes + kPairBHalfBytes + 3 * sf_bytes);
-          tma_load_2d(sm.a[stage], &tmap_a, a_col + cur.kl * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
+          tma_load_2d(sm.a[stage], amap, a_col + cur.kl * kGemmBKBytes, tm * 256 + (int)rank * 128, &sm.full[stage]);
           tma_load_2d(sm.b[stage], bmap, cur.kl * kGemmBKBytes, tn * kGemmBN + (int)rank * 128, &sm.full[stage]);
           bulk_load_1d(sm.sfa[stage], sfa_src + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
           bulk_load_1d(sm.sfb[stage], sfb_src0 + (size_t)cur.kl * kSfPerStage, sf_bytes, &sm.full[stage]);
@@ -218,7 +226,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer (leader CTA only) ----------------------------
-    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsControl));
+    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsControl));
     if (lane == 0 && rank == 0) {
       int stage = 0;
       uint32_t gk = 0;                       // K stages issued so far, over all tiles
@@ -226,6 +234,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
       int kind = 0;                          // 0: accumulator at columns [0, 256), 1: at [128, 384)
       bool ok = true;
       for (int ti = 0; ti < tiles.count && ok; ++ti, kind ^= kind_toggle) {
+       // One accumulator hand-over per tile — or, batched accumulation, per term (= K segment) of the tile.
+       const int n_groups = kBatchSum ? g.n_seg : 1;
+       for (int grp = 0; grp < n_groups && ok; ++grp) {
+        const int ks_begin = (kBatchSum && grp > 0) ? g.seg_stage_end[grp - 1] : 0;
+        const int ks_end = kBatchSum ? g.seg_stage_end[grp] : k_stages;
         // the private half was released two tiles ago, the shared half by the previous tile's epilogue
         // (wide forms: one accumulator, every epilogue warp arrives on the one barrier)
         if ((!kWide && !mbar_wait_timed(&sm.acc_empty_priv[kind], ((priv_phase >> kind) & 1u) ^ 1u)) ||
@@ -238,7 +251,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
         shared_phase ^= 1;
         tc_fence_after();
         const uint32_t d_tmem = tmem + (uint32_t)kind * 128;
-        for (int ks = 0; ks < k_stages; ++ks, ++gk) {
+        for (int ks = ks_begin; ks < ks_end; ++ks, ++gk) {
           // operands of both CTAs have landed and the movers have put the stage's scales into tensor memory
           const uint32_t slot = gk % kPairSfSlots;
           if (!mbar_wait_timed(&sm.sf_ready[slot], (gk / kPairSfSlots) & 1u)) {
@@ -250,13 +263,14 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           const uint32_t sf_cols = tmem + kPairSfBase + slot * kSfSlotCols;
           const uint32_t a_base = smem_u32(sm.a[stage]);
           const uint32_t b_base = smem_u32(sm.b[stage]);
+          const int ka = ks - ks_begin;          // 0 at the first stage of this accumulator
           // MXFP4 with K an odd multiple of 128: the very last stage holds 128 elements, two MMAs instead of four
           // (a branch of its own: a run-time MMA count in the unrolled loop cost every stage of every shape ~4 %)
           if (MX && k_tail_half && ks + 1 == k_stages) {
 #pragma unroll
             for (int j = 0; j < 2; ++j)
               tc_mma_pair<true>(d_tmem, smem_desc(a_base + j * 32, 16, 1024, 2), smem_desc(b_base + j * 32, 16, 1024, 2),
-                          block_scaled_idesc(256, kGemmBN, 1, j * 2), sf_cols, sf_cols + 16, (ks | j) != 0);
+                          block_scaled_idesc(256, kGemmBN, 1, j * 2), sf_cols, sf_cols + 16, (ka | j) != 0);
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -264,11 +278,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               const uint64_t bdesc = smem_desc(b_base + j * 32, 16, 1024, 2);
               if constexpr (!MX) {
                 tc_mma_pair<false>(d_tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 0, 0), sf_cols + j * 4,
-                             sf_cols + 16 + j * 8, (ks | j) != 0);
+                             sf_cols + 16 + j * 8, (ka | j) != 0);
               } else {
                 const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
                 tc_mma_pair<true>(d_tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 1, sf_id),
-                            sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ks | j) != 0);
+                            sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ka | j) != 0);
               }
             }
           }
@@ -276,11 +290,12 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           if (++stage == kPairStages) stage = 0;
         }
         if (ok) tc_commit_pair(&sm.acc_full);   // both CTAs' epilogues
+       }
       }
     }
   } else if (warp >= kMoverWarp0 && warp < kMoverWarp0 + 4) {
     // ------------------------------ scale movers (both CTAs) --------------------------------
-    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kWideRegsMovers));
+    if constexpr (kWide) asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(kRegsMovers));
     // A scale slot is rewritten as soon as the MMAs of the stage two steps back have completed, which the
     // leader's tcgen05.commit announces to both CTAs at once (multicast arrival on that stage's `empty` barrier).
     const int quad = warp & 3;
@@ -323,7 +338,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     }
   } else if (warp >= kEpiWarp0 && warp < kEpiWarp0 + kEpiWarps) {
     // ------------------------------ epilogue (both CTAs) -------------------------------------
-    if constexpr (kWide) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kWideRegsEpilogue));
+    if constexpr (kWide) asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(kRegsEpilogue));
     const int quad = warp & 3;
     uint32_t acc_phase = 0;
     int kind = 0;
@@ -366,15 +381,21 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           cs_tm = tm;
         }
       }
+      const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
+      const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
+      const int col0 = tn * kGemmBN;
+      if constexpr (kBatchSum) {
+        uint8_t* epi = &sm.epi[0][0][0] + (size_t)(warp - kEpiWarp0) * 4096;   // one staging buffer per warp
+        ok = epilogue_batch_sum(g, tmap_d, &sm.acc_full, acc_phase, tq + (uint32_t)(half * 128), epi, row0, col0 + half * 128,
+                                lane, empty_shared_leader);
+        continue;
+      }
       if (!mbar_wait_timed(&sm.acc_full, acc_phase)) {
         if (lane == 0) atomicExch(g.status, kStatusGemmTmemTimeout);
         ok = false;
         break;
       }
       tc_fence_after();
-      const uint32_t tq = tmem + ((uint32_t)(quad * 32) << 16);
-      const int row0 = tm * 256 + (int)rank * 128 + quad * 32;
-      const int col0 = tn * kGemmBN;
       if constexpr (kWide) {
         uint8_t* epi = &sm.epi[0][0][0] + (size_t)(warp - kEpiWarp0) * 4096;   // one staging buffer per warp
         epilogue_wide<EPI>(g, tmap_d, tq + (uint32_t)(half * 128), epi, row0, col0 + half * 128, a_sg, lane,

@@ -8,6 +8,8 @@
 //   row / column math  fp4_runtime/TK_quantisation/nvfp4_v5/fused_amax_quantize.cuh:216-381
 //   scale tile layout  fp4_runtime/TK_quantisation/nvfp4_v5/persistent_quantize.cuh:33-36
 //   RMSNorm pass       fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:1025-1111
+#include <atomic>
+
 #include "fp4_common.cuh"
 #include "host_util.h"
 
@@ -2131,24 +2133,27 @@ constexpr int64_t kNoAllocMaxRows = 65536;
 static __device__ __align__(256) float g_noalloc_scratch[kNoAllocMaxRows + kScratchFloats];
 
 // Device address of the scratch array on the current device.  The array's name is only a
-// host-side handle, so the address is looked up once per device and cached.
+// host-side handle, so the address is looked up once per device and cached (host threads that race
+// here store the same value).
 static float* noalloc_scratch_ptr() {
-  static float* cached[64] = {nullptr};
+  static std::atomic<float*> cached[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
     set_error("nvfp4_fused_norm_quantize_noalloc: cudaGetDevice failed");
     return nullptr;
   }
-  if (cached[dev] == nullptr) {
+  float* have = cached[dev].load(std::memory_order_acquire);
+  if (have == nullptr) {
     void* p = nullptr;
     const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
     if (e != cudaSuccess || p == nullptr) {
       set_error("nvfp4_fused_norm_quantize_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e));
       return nullptr;
     }
-    cached[dev] = static_cast<float*>(p);
+    have = static_cast<float*>(p);
+    cached[dev].store(have, std::memory_order_release);
   }
-  return cached[dev];
+  return have;
 }
 
 int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,

@@ -9,6 +9,7 @@ in place; every function returns ``None``.  Kernels go to torch's current stream
 from __future__ import annotations
 
 import ctypes
+import os
 
 import torch
 
@@ -240,7 +241,9 @@ def nvfp4_batched_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_lis
 
 def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_sg_list, D_out):
     """nvfp4_b200_gemm.cu:2567-2635: ``D_out = bf16(sum_i (A_i . B_i^T) * A_sg_i * B_sg_i)`` with the sum kept in
-    fp32 in batch order (at most four terms in the reference; any number here)."""
+    fp32 in batch order — term 0 multiplied, every later term joined by one fused multiply-add, as the reference's
+    kernel does.  Up to four terms with M a multiple of 256 run as ONE launch (the terms' accumulators are summed in
+    the epilogue's registers); anything else as a chain of launches through an fp32 partial sum."""
     n = len(A_list)
     if n == 0 or not (len(A_sc_list) == len(A_sg_list) == len(B_list) == len(B_sc_list) == len(B_sg_list) == n):
         raise RuntimeError("nvfp4_batched_accum_gemm: all lists must have the same non-zero length")
@@ -248,23 +251,31 @@ def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_
         return _gemm(A_list[0], A_sc_list[0], A_sg_list[0], B_list[0], B_sc_list[0], B_sg_list[0], D_out)
     M, N, _ = _shapes(A_list[0], B_list[0])
     _chk_out(D_out, M, N)
+    Ks = []
+    for i in range(n):
+        for t, nm in ((A_list[i], "A"), (A_sc_list[i], "A_sc"), (B_list[i], "B"), (B_sc_list[i], "B_sc")):
+            _chk_operand(t, nm)
+        _chk_sg(A_sg_list[i], "A_sc_global")
+        _chk_sg(B_sg_list[i], "B_sc_global")
+        Mi, Ni, Ki = _shapes(A_list[i], B_list[i])
+        if (Mi, Ni) != (M, N):
+            raise RuntimeError("nvfp4_batched_accum_gemm: every term must produce the same [M, N]")
+        Ks.append(Ki)
     with torch.cuda.device(D_out.device):
+        if n <= 4 and M % 256 == 0 and os.environ.get("FP4B200_GEMM_PAIR", "1") != "0":
+            def arr(ts):
+                return (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
+            _lib.call("fp4b200_nvfp4_batched_accum_gemm", n, arr(A_list), arr(A_sc_list), arr(A_sg_list), arr(B_list),
+                      arr(B_sc_list), arr(B_sg_list), (ctypes.c_int64 * n)(*Ks), D_out.data_ptr(), M, N, _stream(A_list[0]))
+            return
         partial = torch.empty((M, N), dtype=torch.float32, device=D_out.device)
         _gemm(A_list[0], A_sc_list[0], A_sg_list[0], B_list[0], B_sc_list[0], B_sg_list[0], partial)
         for i in range(1, n):
-            A, B = A_list[i], B_list[i]
-            for t, nm in ((A, "A"), (A_sc_list[i], "A_sc"), (B, "B"), (B_sc_list[i], "B_sc")):
-                _chk_operand(t, nm)
-            _chk_sg(A_sg_list[i], "A_sc_global")
-            _chk_sg(B_sg_list[i], "B_sc_global")
-            Mi, Ni, Ki = _shapes(A, B)
-            if (Mi, Ni) != (M, N):
-                raise RuntimeError("nvfp4_batched_accum_gemm: every term must produce the same [M, N]")
             last = i == n - 1
             dst = D_out if last else partial
-            _lib.call("fp4b200_nvfp4_gemm_accum", A.data_ptr(), A_sc_list[i].data_ptr(), A_sg_list[i].data_ptr(),
-                      B.data_ptr(), B_sc_list[i].data_ptr(), B_sg_list[i].data_ptr(), partial.data_ptr(),
-                      dst.data_ptr(), 0 if last else 1, M, N, Ki, _stream(A))
+            _lib.call("fp4b200_nvfp4_gemm_accum", A_list[i].data_ptr(), A_sc_list[i].data_ptr(), A_sg_list[i].data_ptr(),
+                      B_list[i].data_ptr(), B_sc_list[i].data_ptr(), B_sg_list[i].data_ptr(), partial.data_ptr(),
+                      dst.data_ptr(), 0 if last else 1, M, N, Ks[i], _stream(A_list[i]))
 
 
 def nvfp4_split_dgrad_sum(A_fp4_cat, A_sc_cat, A_sg_list, B_fp4_list, B_sc_list, B_sg_cat, split_dims, D_out):

@@ -1,8 +1,8 @@
 """GPU: the entry point that allocates nothing (fp4b200_nvfp4_fused_norm_quantize_noalloc).
 
 Some callers of this library cannot allocate device memory when they need the fused producer:
-code that runs while a stream is being captured, or under a memory budget that is already fully
-handed out.  For them the library keeps the producer's scratch (inverse RMS per row, tensor amax)
+code that runs under a memory budget that is already fully handed out, or in a thread that must
+not touch the allocator.  For them the library keeps the producer's scratch (inverse RMS per row, tensor amax)
 in a fixed device array of its own.  This test calls that entry point through the C ABI twice in a
 row, with different inputs, and checks every output byte against the ordinary entry point, which
 uses caller-provided buffers: the second call must not see anything left over from the first.
