@@ -256,11 +256,15 @@ int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg,
  * D = bf16(sum_i (A_i . B_i^T) * A_sg_i * B_sg_i) for 1 to 4 terms, each with its own operands, scale tensors,
  * tensor scales and reduction width K[i].  The terms' accumulators are handed to the epilogue one after the other
  * and summed there in fp32 registers in the reference's order (term 0 multiplied, every later term by one fused
- * multiply-add), one rounding to bf16, one store.  Needs M % 256 == 0 (two-CTA kernel); otherwise chain
- * fp4b200_nvfp4_gemm (fp32 output) and fp4b200_nvfp4_gemm_accum. */
+ * multiply-add), one rounding to bf16, one store.  A term's A may be a column slice of a wider matrix, which is what
+ * nvfp4_split_dgrad_sum (nvfp4_b200_gemm.cu:2424-2565) needs: A_pitch_bytes[i] is then the row pitch of its codes
+ * (NULL or 0: K[i]/2) and A_sc_row_tiles[i] the number of 512-byte scale tiles between consecutive 128-row blocks of
+ * its scale tensor (NULL or 0: K[i]/64).  Needs M % 256 == 0 (two-CTA kernel); otherwise chain fp4b200_nvfp4_gemm
+ * (fp32 output) and fp4b200_nvfp4_gemm_accum. */
 int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const void* const* A_sc, const float* const* A_sg,
                                      const void* const* B, const void* const* B_sc, const float* const* B_sg,
-                                     const int64_t* K, void* D, int64_t M, int64_t N, void* stream);
+                                     const int64_t* K, const int64_t* A_pitch_bytes, const int64_t* A_sc_row_tiles, void* D,
+                                     int64_t M, int64_t N, void* stream);
 
 /* nvfp4_grouped_gemm (nvfp4_b200_gemm.cu:764-841): B is the row concatenation of n_out weights,
  * B_sg_per_tile holds one tensor scale per 256 rows of B, output i receives D_cols[i] columns

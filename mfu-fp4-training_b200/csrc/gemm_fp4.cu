@@ -72,6 +72,7 @@ struct GemmArgs {
   const uint8_t* seg_a_sc[kMaxKSeg];   // [M/128, Kseg/(4*block), 512]
   const uint8_t* seg_b_sc[kMaxKSeg];   // [N/128, Kseg/(4*block), 512]
   int seg_sf_tiles_k[kMaxKSeg];     // scale tiles along K per row tile, per segment
+  int seg_a_sf_row_tiles[kMaxKSeg]; // scale tiles from one 128-row block of A's scales to the next (= seg_sf_tiles_k unless A is a column slice)
   int seg_tail_half[kMaxKSeg];      // 1: the segment's last stage holds 128 elements only (MXFP4, K an odd multiple of 128)
   // Batched accumulation (kEpiBatchSum): every segment is a GEMM term of its own — its own A tensor (tensor map
   // tmap_a_seg.m[s]) and its own tensor scales; the terms' scaled accumulators are summed in fp32 by the epilogue.
@@ -672,7 +673,7 @@ fp4_gemm_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constan
             a_col = g.seg_a_col_bytes[cur.seg];
             bmap = &tmap_b.m[cur.seg];
             const size_t tiles_k = (size_t)g.seg_sf_tiles_k[cur.seg];
-            sfa_src = g.seg_a_sc[cur.seg] + (size_t)tm * tiles_k * 512;
+            sfa_src = g.seg_a_sc[cur.seg] + (size_t)tm * (size_t)g.seg_a_sf_row_tiles[cur.seg] * 512;
             sfb_src0 = g.seg_b_sc[cur.seg] + (size_t)(2 * tn) * tiles_k * 512;
             // the last column tile of an N that is an odd multiple of 128 has no second group of B rows
             sfb_src1 = (2 * tn + 1) * 128 < g.N ? sfb_src0 + tiles_k * 512 : sfb_src0;
@@ -851,6 +852,10 @@ struct KSegments {
   const void* a[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
   const float* a_sg[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
   const float* b_sg[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
+  // a term's A may be a column slice of a wider code matrix: row pitch of its codes in bytes (0: k/2) and scale tiles
+  // from one 128-row block of its scale tensor to the next (0: k/64)
+  int64_t a_pitch_bytes[kMaxKSeg] = {0, 0, 0, 0};
+  int64_t a_sc_row_tiles[kMaxKSeg] = {0, 0, 0, 0};
 };
 
 // Rotary embedding applied by the bf16 epilogue to the output columns [0, col_end).
@@ -874,7 +879,8 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
   if (segs.batch_sum) {
     for (int s = 0; s < segs.n; ++s)
       if (int rc = make_tmap_2d(&tmap_a_seg.m[s], segs.a[s], CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.k[s] / 2, (uint64_t)M,
-                                (uint64_t)segs.k[s] / 2, kGemmBKBytes, kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
+                                segs.a_pitch_bytes[s] > 0 ? (uint64_t)segs.a_pitch_bytes[s] : (uint64_t)segs.k[s] / 2, kGemmBKBytes,
+                                kGemmBM, CU_TENSOR_MAP_SWIZZLE_128B))
         return rc;
     tmap_a = tmap_a_seg.m[0];
   } else if (int rc = make_tmap_2d(&tmap_a, A, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)segs.a_width / 2, (uint64_t)M,
@@ -896,6 +902,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     g.seg_a_sc[s] = (const uint8_t*)segs.a_sc[s];
     g.seg_b_sc[s] = (const uint8_t*)segs.b_sc[s];
     g.seg_sf_tiles_k[s] = (int)(segs.k[s] / (mx ? 128 : 64));
+    g.seg_a_sf_row_tiles[s] = segs.a_sc_row_tiles[s] > 0 ? (int)segs.a_sc_row_tiles[s] : g.seg_sf_tiles_k[s];
     g.seg_a_sg[s] = segs.a_sg[s];
     g.seg_b_sg[s] = segs.b_sg[s];
   }
@@ -1065,7 +1072,8 @@ int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg,
 
 int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const void* const* A_sc, const float* const* A_sg,
                                      const void* const* B, const void* const* B_sc, const float* const* B_sg,
-                                     const int64_t* K, void* D, int64_t M, int64_t N, void* stream) {
+                                     const int64_t* K, const int64_t* A_pitch_bytes, const int64_t* A_sc_row_tiles, void* D,
+                                     int64_t M, int64_t N, void* stream) {
   const char* fn = "nvfp4_batched_accum_gemm";
   if (n_terms < 1 || n_terms > kMaxKSeg) return set_error("%s: 1 to %d terms (got %d)", fn, kMaxKSeg, n_terms);
   if (!A || !A_sc || !A_sg || !B || !B_sc || !B_sg || !K || !D) return set_error("%s: null argument", fn);
@@ -1079,6 +1087,16 @@ int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const vo
     if (int rc = check_gemm(A[i], A_sc[i], B[i], B_sc[i], M, N, K[i], fn)) return rc;
     if (!A_sg[i] || !B_sg[i]) return set_error("%s: every term needs its tensor scales", fn);
     segs.k[i] = K[i];
+    if (A_pitch_bytes != nullptr) {
+      if (A_pitch_bytes[i] != 0 && (A_pitch_bytes[i] < K[i] / 2 || (A_pitch_bytes[i] % 16)))
+        return set_error("%s: a row pitch of A must be 0 or a multiple of 16 bytes and at least K/2", fn);
+      segs.a_pitch_bytes[i] = A_pitch_bytes[i];
+    }
+    if (A_sc_row_tiles != nullptr) {
+      if (A_sc_row_tiles[i] != 0 && A_sc_row_tiles[i] < K[i] / 64)
+        return set_error("%s: the scale tiles per row block of A must be 0 or at least K/64", fn);
+      segs.a_sc_row_tiles[i] = A_sc_row_tiles[i];
+    }
     segs.a[i] = A[i]; segs.a_sc[i] = A_sc[i]; segs.a_sg[i] = A_sg[i];
     segs.b[i] = B[i]; segs.b_sc[i] = B_sc[i]; segs.b_sg[i] = B_sg[i];
   }

@@ -203,7 +203,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             bmap = &tmap_b.m[cur.seg];
             if (g.a_per_seg) amap = &tmap_a_seg.m[cur.seg];
             const size_t tiles_k = (size_t)g.seg_sf_tiles_k[cur.seg];
-            sfa_src = g.seg_a_sc[cur.seg] + (size_t)(2 * tm + rank) * tiles_k * 512;
+            sfa_src = g.seg_a_sc[cur.seg] + (size_t)(2 * tm + rank) * (size_t)g.seg_a_sf_row_tiles[cur.seg] * 512;
             sfb_src0 = g.seg_b_sc[cur.seg] + (size_t)(2 * tn) * tiles_k * 512;
             // the last column tile of an N that is an odd multiple of 128 has no second group of B rows
             sfb_src1 = (2 * tn + 1) * 128 < g.N ? sfb_src0 + tiles_k * 512 : sfb_src0;

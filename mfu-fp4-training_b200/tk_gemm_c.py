@@ -266,7 +266,8 @@ def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_
             def arr(ts):
                 return (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
             _lib.call("fp4b200_nvfp4_batched_accum_gemm", n, arr(A_list), arr(A_sc_list), arr(A_sg_list), arr(B_list),
-                      arr(B_sc_list), arr(B_sg_list), (ctypes.c_int64 * n)(*Ks), D_out.data_ptr(), M, N, _stream(A_list[0]))
+                      arr(B_sc_list), arr(B_sg_list), (ctypes.c_int64 * n)(*Ks), None, None, D_out.data_ptr(), M, N,
+                      _stream(A_list[0]))
             return
         partial = torch.empty((M, N), dtype=torch.float32, device=D_out.device)
         _gemm(A_list[0], A_sc_list[0], A_sg_list[0], B_list[0], B_sc_list[0], B_sg_list[0], partial)
@@ -281,14 +282,43 @@ def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_
 def nvfp4_split_dgrad_sum(A_fp4_cat, A_sc_cat, A_sg_list, B_fp4_list, B_sc_list, B_sg_cat, split_dims, D_out):
     """nvfp4_b200_gemm.cu:2424-2565: dgrad of a fused projection — the row-quantised gradient is the column
     concatenation of the splits; term i multiplies columns of split i by the column-quantised weight i.
-    The slices are made contiguous here (a copy the reference avoids with strided descriptors)."""
-    offs = 0
-    A_list, A_sc_l, B_sg_l = [], [], []
+    One launch over the column slices where they are (M a multiple of 256, up to four splits); otherwise the slices
+    are made contiguous and the terms are chained."""
+    n = len(split_dims)
+    if any(d % 128 for d in split_dims):
+        raise RuntimeError("nvfp4_split_dgrad_sum: split sizes must be multiples of 128")
     a_u8 = A_fp4_cat.view(torch.uint8)
     sc_u8 = A_sc_cat.view(torch.uint8)
+    M, k_total = a_u8.shape[0], a_u8.shape[1] * 2
+    one_launch = (n <= 4 and M % 256 == 0 and os.environ.get("FP4B200_GEMM_PAIR", "1") != "0" and a_u8.is_contiguous()
+                  and sc_u8.is_contiguous() and all(d % 256 == 0 for d in split_dims)
+                  and sum(split_dims) == k_total and len(B_fp4_list) == n and len(B_sc_list) == n and len(A_sg_list) == n)
+    if one_launch:
+        N = B_fp4_list[0].shape[0]
+        _chk_out(D_out, M, N)
+        for i in range(n):
+            for t, nm in ((B_fp4_list[i], "B"), (B_sc_list[i], "B_sc")):
+                _chk_operand(t, nm)
+            _chk_sg(A_sg_list[i], "A_sc_global")
+            if B_fp4_list[i].shape != (N, split_dims[i] // 2):
+                raise RuntimeError("nvfp4_split_dgrad_sum: weight i must be [N, split_i / 2] codes")
+        _chk_sg(B_sg_cat, "B_sg_cat", n)
+        offs, a_ptrs, sc_ptrs = 0, [], []
+        for d in split_dims:
+            a_ptrs.append(a_u8.data_ptr() + offs // 2)
+            sc_ptrs.append(sc_u8.data_ptr() + (offs // 64) * 512)
+            offs += d
+        vp = ctypes.c_void_p * n
+        i64 = ctypes.c_int64 * n
+        with torch.cuda.device(D_out.device):
+            _lib.call("fp4b200_nvfp4_batched_accum_gemm", n, vp(*a_ptrs), vp(*sc_ptrs), vp(*[t.data_ptr() for t in A_sg_list]),
+                      vp(*[t.data_ptr() for t in B_fp4_list]), vp(*[t.data_ptr() for t in B_sc_list]),
+                      vp(*[B_sg_cat.data_ptr() + 4 * i for i in range(n)]), i64(*split_dims), i64(*([k_total // 2] * n)),
+                      i64(*([k_total // 64] * n)), D_out.data_ptr(), M, N, _stream(A_fp4_cat))
+        return
+    offs = 0
+    A_list, A_sc_l, B_sg_l = [], [], []
     for i, d in enumerate(split_dims):
-        if d % 128:
-            raise RuntimeError("nvfp4_split_dgrad_sum: split sizes must be multiples of 128")
         A_list.append(a_u8[:, offs // 2:(offs + d) // 2].contiguous())
         A_sc_l.append(sc_u8[:, offs // 64:(offs + d) // 64, :].contiguous())
         B_sg_l.append(B_sg_cat.narrow(0, i, 1))

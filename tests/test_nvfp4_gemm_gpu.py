@@ -136,6 +136,59 @@ def test_grouped_residual_and_batched_accum():
     assert_status_ok()
 
 
+@pytest.mark.parametrize("M,Ks", [(384, (512, 512)), (512, (256, 768, 512)), (256, (512, 256, 256, 512))])
+def test_batched_accum_forms_against_the_oracle_order(M, Ks):
+    """The chain of launches (M not a multiple of 256: one-CTA kernel, fp32 partial between launches) and the one-launch
+    form (terms of different reduction widths, three and four terms) against the oracle's summation order applied to
+    the raw accumulators of the single GEMMs."""
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    N = 512
+    A, Asc, Asg, B, Bsc, Bsg, raws, scales = [], [], [], [], [], [], [], []
+    one = torch.ones(1, device="cuda")
+    for i, K in enumerate(Ks):
+        x, w, qx, qw = _quant_pair(M, N, K, seed=300 + 7 * i + M)
+        A.append(qx[0]); Asc.append(qx[1]); Asg.append(qx[4]); B.append(qw[0]); Bsc.append(qw[1]); Bsg.append(qw[4])
+        r = torch.empty((M, N), dtype=torch.float32, device="cuda")
+        gemm.nvfp4_gemm(qx[0], qx[1], one, qw[0], qw[1], one, r)
+        raws.append(r)
+        scales.append(np.float32(qx[4].item()) * np.float32(qw[4].item()))
+    d = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gemm.nvfp4_batched_accum_gemm(A, Asc, Asg, B, Bsc, Bsg, d)
+    torch.cuda.synchronize()
+    want = o.bf16_round(o.nvfp4_batched_accum_f32([r.cpu().numpy() for r in raws], scales))
+    assert np.array_equal(d.float().cpu().numpy(), want)
+    assert_status_ok()
+
+
+@pytest.mark.parametrize("M", [256, 384])       # one launch over the column slices / chained launches over copies
+def test_split_dgrad_sum_reads_the_slices_where_they_are(M):
+    """nvfp4_split_dgrad_sum on the column concatenation that the three-stream gradient quantiser produces (own tensor
+    scale per stream) against nvfp4_batched_accum_gemm on contiguous copies of the slices."""
+    tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
+    splits, n_out = [512, 256, 256], 512
+    rng = np.random.default_rng(M)
+    grads = [to_dev_bf16(o.bf16_round((s_ * rng.standard_normal((M, d))).astype(np.float32))) for d, s_ in zip(splits, (1e-3, 3e-3, 5e-4))]
+    q = tkq.tk_group_quantize_dim1_split3_for_gemm(*grads)
+    a_cat, a_sc_cat, sg = q[5], q[6], q[2]
+    ws = [tkq.tk_quantize_for_gemm(to_dev_bf16(o.bf16_round((0.02 * rng.standard_normal((n_out, d))).astype(np.float32))), False, True)
+          for d in splits]
+    b_sg_cat = torch.cat([w[4] for w in ws]).contiguous()
+    a_sg_list = [sg.narrow(0, i, 1) for i in range(3)]
+    d = torch.full((M, n_out), float("nan"), dtype=torch.bfloat16, device="cuda")
+    gemm.nvfp4_split_dgrad_sum(a_cat, a_sc_cat, a_sg_list, [w[0] for w in ws], [w[1] for w in ws], b_sg_cat, splits, d)
+    a_u8, sc_u8 = a_cat.view(torch.uint8), a_sc_cat.view(torch.uint8)
+    A, Asc, off = [], [], 0
+    for dd in splits:
+        A.append(a_u8[:, off // 2:(off + dd) // 2].contiguous())
+        Asc.append(sc_u8[:, off // 64:(off + dd) // 64, :].contiguous())
+        off += dd
+    want = torch.empty_like(d)
+    gemm.nvfp4_batched_accum_gemm(A, Asc, a_sg_list, [w[0] for w in ws], [w[1] for w in ws], [w[4] for w in ws], want)
+    torch.cuda.synchronize()
+    assert torch.equal(d, want)
+    assert_status_ok()
+
+
 def test_batched_accum_equals_the_reference_kernels_bytes():
     """nvfp4_batched_accum_gemm with 2, 3 and 4 terms against the output bytes of the reference's own kernel on the
     same operands (tests/golden/make_accum_golden.py recorded them on a B200): pins the fp32 summation order."""
