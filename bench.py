@@ -744,7 +744,9 @@ def rmsnorm_bwd_only(args):
 
 
 def gemm_only(args):
-    """Times fp4b200_nvfp4_gemm alone at one shape on cuda:0 (random codes and scales)."""
+    """Times one NVFP4 GEMM form alone at one shape on cuda:0 (random codes and scales): the plain GEMM, the fused QKV
+    projection with the rotary embedding in its epilogue (--gemm-form rope: heads of 128, sequences of 4096, the last
+    sixth of the columns not rotated), or two accumulated terms in one launch (--gemm-form accum2)."""
     import torch
     gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
     lib = importlib.import_module("mfu-fp4-training_b200._lib")
@@ -752,23 +754,43 @@ def gemm_only(args):
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     g = torch.Generator(device=dev).manual_seed(1)
-    a = torch.randint(0, 256, (M, K // 2), dtype=torch.uint8, device=dev, generator=g)
-    b = torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, device=dev, generator=g)
-    a_sc = torch.randint(40, 64, (M // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g)
-    b_sc = torch.randint(40, 64, (N // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g)
+    def operand(rows):
+        return (torch.randint(0, 256, (rows, K // 2), dtype=torch.uint8, device=dev, generator=g),
+                torch.randint(40, 64, (rows // 128, K // 64, 512), dtype=torch.uint8, device=dev, generator=g))
+    a, a_sc = operand(M)
+    b, b_sc = operand(N)
     sg = torch.full((1,), 1e-3, dtype=torch.float32, device=dev)
     d = torch.empty(M, N, dtype=torch.bfloat16, device=dev)
+    flops = 2.0 * M * N * K
+    if args.gemm_form == "rope":
+        seq, head = 4096, 128
+        kv = N // 6
+        dq, dk, dv = (torch.empty(M, n, dtype=torch.bfloat16, device=dev) for n in (N - 2 * kv, kv, kv))
+        ang = torch.rand(seq, head // 2, generator=g, device=dev) * 6.2831853
+        cs = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+        b_sg = sg.expand(N // 256).contiguous()
+        def run():
+            gemm.nvfp4_grouped_gemm_rope_packed_split(a, a_sc, sg, b, b_sc, b_sg, dq, dk, dv, cs, seq, head, head)
+    elif args.gemm_form == "accum2":
+        a2, a2_sc = operand(M)
+        b2, b2_sc = operand(N)
+        flops *= 2
+        def run():
+            gemm.nvfp4_batched_accum_gemm([a, a2], [a_sc, a2_sc], [sg, sg], [b, b2], [b_sc, b2_sc], [sg, sg], d)
+    else:
+        def run():
+            gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
     for _ in range(args.warmup):
-        gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
+        run()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(args.steps):
-        gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
+        run()
     e1.record()
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / args.steps
-    print(json.dumps({"gemm_only": args.gemm_only, "ms": ms, "tflops": 2.0 * M * N * K / (ms * 1e-3) / 1e12,
+    print(json.dumps({"gemm_only": args.gemm_only, "form": args.gemm_form, "ms": ms, "tflops": flops / (ms * 1e-3) / 1e12,
                       "status": lib.device_status()}), flush=True)
 
 
@@ -783,6 +805,8 @@ def main():
                     help="timed loop only (no per-kernel, end-to-end or CPU legs): the command ncu captures")
     ap.add_argument("--gemm-only", default=None, metavar="MxNxK",
                     help="time only the NVFP4 GEMM at this shape (tuning / ncu capture helper)")
+    ap.add_argument("--gemm-form", default="plain", choices=["plain", "rope", "accum2"],
+                    help="with --gemm-only: which epilogue form to time")
     ap.add_argument("--rmsnorm-bwd-only", default=None, metavar="MxK",
                     help="time only the RMSNorm backward (sum3 form) at this shape (tuning / ncu capture helper)")
     args = ap.parse_args()
