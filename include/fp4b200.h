@@ -121,10 +121,12 @@ int fp4b200_nvfp4_quantize_opt_into(const void* x_bf16, const void* gamma_bf16, 
 
 /* Tensor amax (and sg) of the per-16 Hadamard transform of x along K (along_k != 0) or along M,
  * measured on the fp32 transform output: rht16_bf16_amax_kernel (tk_quantize.cu:574-664).  gamma/inv_rms
- * non-NULL (along K only) transform bf16(x*inv_rms*gamma): rmsnorm_rht16_amax_with_orig_kernel (:1113-1172). */
+ * non-NULL (along K only) transform bf16(x*inv_rms*gamma): rmsnorm_rht16_amax_with_orig_kernel (:1113-1172).
+ * plain_amax_sg (NULL or two floats; scan along M only): the tensor amax and sg of x itself from the same read — the
+ * row operand's scale when only the column operand is transformed (the reference runs a second scan for it). */
 int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                              int along_k, int with_sign, uint64_t sign_seed, uint64_t sign_subseq, float* amax_sg,
-                             void* stream);
+                             float* plain_amax_sg, void* stream);
 
 /* tk_quantize_weight_2d(input) (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:2445-2555): one
  * decode-centric scale per 16x16 tile shared by both orientations, so that the column-wise codes

@@ -37,7 +37,7 @@ SIGNATURES = {
                                         ctypes.c_uint64, ctypes.c_uint64, _c_void_p, _int, _c_void_p, _i64, _c_void_p, _c_void_p,
                                         _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_rht16_amax": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _int, ctypes.c_uint64, ctypes.c_uint64, _c_void_p,
-                                 _c_void_p],
+                                 _c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_weight_2d": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                          _c_void_p],
     "fp4b200_nvfp4_rmsnorm_stats": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _int, _c_void_p,

@@ -1543,6 +1543,67 @@ rht16_amax_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __re
   }
 }
 
+// Column scan of the transform's tensor maximum, two columns per thread: a lane reads 32 bits of sixteen consecutive
+// rows (a warp covers 128 contiguous bytes of every row), transforms both columns and, when plain_amax is given,
+// also takes the maximum of the untransformed values — the row operand's tensor scale when only the column operand is
+// transformed, from the same read.  Same arithmetic as rht16_amax_kernel with along_k = 0.
+__global__ void __launch_bounds__(256)
+rht16_col_amax_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ amax, float* __restrict__ plain_amax,
+                      int64_t M, int64_t K, int sign, unsigned long long sign_seed, unsigned long long sign_subseq) {
+  const int64_t pairs = K >> 1, groups = (M / 16) * pairs;
+  float local = 0.0f;
+  uint32_t plain = 0;
+  for (int64_t gidx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; gidx < groups; gidx += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t rb = gidx / pairs, cp = gidx - rb * pairs;
+    const uint32_t* p = reinterpret_cast<const uint32_t*>(x + rb * 16 * K) + cp;
+    uint32_t w[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) w[i] = __ldg(p + (size_t)i * pairs);
+    float v0[16], v1[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      plain = absmax_xs(plain, w[i]);
+      v0[i] = bf16lo_to_f32(w[i]);
+      v1[i] = bf16hi_to_f32(w[i]);
+    }
+    if (sign) {
+      // the 32 lanes of a warp hold 64 columns of ONE 16-row group (K is a multiple of 128 and the grid stride a
+      // multiple of 32), so sixteen lanes hash one row each and share the mask
+      const uint32_t neg = __ballot_sync(0xffffffffu, (threadIdx.x & 31) < 16 &&
+                               rht_sign_is_negative(sign_seed, sign_subseq, (unsigned long long)(rb * 16 + (threadIdx.x & 15))) != 0) & 0xFFFFu;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        if ((neg >> i) & 1u) { v0[i] = -v0[i]; v1[i] = -v1[i]; }
+      }
+    }
+    fwht16(v0);
+    fwht16(v1);
+#pragma unroll
+    for (int i = 0; i < 16; ++i) local = fmaxf(local, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
+  }
+  float plain_f = fmaxf(fabsf(bf16lo_to_f32(plain)), fabsf(bf16hi_to_f32(plain)));
+  local = warp_max(local);
+  plain_f = warp_max(plain_f);
+  __shared__ float part[2][8];
+  if ((threadIdx.x & 31) == 0) { part[0][threadIdx.x >> 5] = local; part[1][threadIdx.x >> 5] = plain_f; }
+  __syncthreads();
+  if (threadIdx.x < 32) {
+    local = threadIdx.x < 8 ? part[0][threadIdx.x] : 0.0f;
+    plain_f = threadIdx.x < 8 ? part[1][threadIdx.x] : 0.0f;
+    local = warp_max(local);
+    plain_f = warp_max(plain_f);
+    if (threadIdx.x == 0) {
+      if (local > 0.0f) atomic_max_nonneg(amax, local);
+      if (plain_amax != nullptr && plain_f > 0.0f) atomic_max_nonneg(plain_amax, plain_f);
+    }
+  }
+}
+
+__global__ void finalize_sg_pair_kernel(float* __restrict__ a, float* __restrict__ b) {
+  a[1] = a[0] / 2688.0f;
+  if (b != nullptr) b[1] = b[0] / 2688.0f;
+}
+
 // ---------------------------------------------------------------------------------------
 // Numbering of stochastic launches on the device
 // ---------------------------------------------------------------------------------------
@@ -1969,13 +2030,26 @@ int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int
 
 int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M, int64_t K,
                              int along_k, int with_sign, uint64_t sign_seed, uint64_t sign_subseq, float* amax_sg,
-                             void* stream) {
+                             float* plain_amax_sg, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_rht16_amax")) return rc;
   if (!amax_sg) return set_error("nvfp4_rht16_amax: amax_sg is required");
   if ((gamma_bf16 == nullptr) != (inv_rms == nullptr) || (gamma_bf16 != nullptr && !along_k))
     return set_error("nvfp4_rht16_amax: fused RMSNorm needs gamma and inv_rms and the transform along K");
+  if (plain_amax_sg != nullptr && along_k)
+    return set_error("nvfp4_rht16_amax: the untransformed maximum comes with the scan along M only");
   cudaStream_t st = (cudaStream_t)stream;
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
+  if (!along_k) {
+    if (plain_amax_sg != nullptr) FP4_CUDA_CHECK(cudaMemsetAsync(plain_amax_sg, 0, 2 * sizeof(float), st));
+    const int64_t groups = M * K / 32;
+    const int grid = (int)std::min<int64_t>((groups + 255) / 256, (int64_t)device_sm_count() * 8);
+    rht16_col_amax_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x_bf16), amax_sg, plain_amax_sg, M, K,
+                                                with_sign != 0, sign_seed, sign_subseq);
+    FP4_CUDA_CHECK(cudaGetLastError());
+    finalize_sg_pair_kernel<<<1, 1, 0, st>>>(amax_sg, plain_amax_sg);
+    FP4_CUDA_CHECK(cudaGetLastError());
+    return 0;
+  }
   const int64_t groups = M * K / 16;
   const int grid = (int)std::min<int64_t>((groups + 255) / 256, (int64_t)device_sm_count() * 8);
   rht16_amax_kernel<<<grid, 256, 0, st>>>(reinterpret_cast<const __nv_bfloat16*>(x_bf16),

@@ -475,12 +475,15 @@ def _amax_plain(x):
     return amax_sg
 
 
-def _amax_rht(x, along_k, sign, seed, subseq, gamma=None, inv_rms=None):
+def _amax_rht(x, along_k, sign, seed, subseq, gamma=None, inv_rms=None, with_plain=False):
+    """Tensor amax / sg of the 16-point transform of x; ``with_plain`` (scan along M only): also x's own amax / sg
+    from the same read, returned second."""
     M, K = x.shape
     amax_sg = torch.empty(2, dtype=torch.float32, device=x.device)
+    plain = torch.empty(2, dtype=torch.float32, device=x.device) if with_plain else None
     _lib.call("fp4b200_nvfp4_rht16_amax", x.data_ptr(), _p(gamma), _p(inv_rms), M, K, int(along_k), int(sign),
-              int(seed) & _U64, int(subseq) & _U64, amax_sg.data_ptr(), _stream(x))
-    return amax_sg
+              int(seed) & _U64, int(subseq) & _U64, amax_sg.data_ptr(), _p(plain), _stream(x))
+    return (amax_sg, plain) if with_plain else amax_sg
 
 
 def _launch_opt(x, amax_row, amax_col, return_transpose, sr, encode_centric, row_rht, col_rht, return_row, seed, offset,
@@ -550,19 +553,16 @@ def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, 
     use_sr = row_sr or col_sr or scale_sr
     sign = bool(with_random_sign_mask)
     with torch.cuda.device(input.device):
-        plain = None
         if row_rht:
             row_amax = _amax_rht(input, True, sign, rng_seed, rng_subsequence)
+            col_amax = _amax_rht(input, False, sign, rng_seed, rng_subsequence) if col_rht else _amax_plain(input)
+        elif col_rht:
+            # the column operand's scan yields the untransformed maximum for the row operand from the same read
+            col_amax, row_amax = _amax_rht(input, False, sign, rng_seed, rng_subsequence, with_plain=True)
         else:
-            plain = row_amax = _amax_plain(input)
+            col_amax = row_amax = _amax_plain(input)
             if float(global_scale_target) != 448.0:
                 row_amax.mul_(448.0 / float(global_scale_target))
-        if col_rht:
-            col_amax = _amax_rht(input, False, sign, rng_seed, rng_subsequence)
-        elif row_rht:
-            col_amax = _amax_plain(input)
-        else:
-            col_amax = row_amax
         row_mat, col_mat = row_rht and sign, col_rht and sign     # the reference materialises these
         if return_transpose and (row_mat or col_mat) and not (scale_sr and not (row_sr or col_sr)):
             # the reference runs a row launch and a column launch over a sign-flipped, transformed copy; the sign
