@@ -135,7 +135,8 @@ int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
                                      void* col_fp4, void* col_sc, float* amax_sg, void* stream);
 
 /* RMSNorm statistics: inv_rms[M] = rsqrt(mean(x^2)+eps) (computed when compute_inv_rms != 0,
- * else read) and amax of bf16(x*inv_rms*gamma).
+ * else read) and amax of bf16(x*inv_rms*gamma); amax_sg may be NULL when only inv_rms is wanted (the MXFP4
+ * producers: no tensor scale), which skips the second sweep over each row.
  * Replaces rmsnorm_bf16_amax_kernel (fp4_runtime/TK_quantisation/nvfp4_v5/tk_quantize.cu:1025-1111). */
 int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
                                 float* inv_rms, int compute_inv_rms, float* amax_sg, void* stream);

@@ -179,7 +179,7 @@ template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_
 __global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                      float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
-                     int n_slots, int* __restrict__ status, int early_reads) {
+                     int n_slots, int* __restrict__ status, int early_reads, int want_amax) {
   extern __shared__ __align__(128) uint8_t stats_smem[];
   __shared__ int next_row;   // next unclaimed row of the band (band-relative)
   __shared__ float warp_max_s[kStatsMaxWarps];
@@ -268,7 +268,8 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
         inv_rms[row] = inv;
         if (r + n_slots < n_band) issue(r + n_slots);
       }
-      mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
+      // want_amax == 0: the caller needs the inverse RMS only (a format without a tensor scale)
+      if (want_amax) mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
     } else {
       inv = __ldg(inv_rms + row);
       mx = stats_row_amax<NV>(v, gamma_lo, gamma_hi, inv, K, lane, mx);
@@ -1880,7 +1881,7 @@ static int stats_slots_for(int64_t K) {
 
 template <int NV, bool CI>
 static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
-                          int64_t M, int64_t K, int slots, int* status, cudaStream_t st, int* grid_out) {
+                          int64_t M, int64_t K, int slots, int* status, cudaStream_t st, int* grid_out, int want_amax) {
   auto kern = rmsnorm_stats_kernel<NV, CI>;
   const int warps = std::min(NV <= 16 ? kStatsMaxWarps : 6, slots);
   const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 + (size_t)slots * 12;
@@ -1888,7 +1889,7 @@ static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, floa
   const int grid = (int)std::min<int64_t>((M + warps - 1) / warps, (int64_t)device_sm_count());
   PdlLaunch l(dim3((unsigned)grid), dim3((unsigned)warps * 32), smem, st, stats_pdl_enabled());
   FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, xb, gb, inv_rms, partials, eps, (int)M, (int)K, slots, status,
-                                    pdl_early_reads()));
+                                    pdl_early_reads(), want_amax));
   *grid_out = grid;
   return 0;
 }
@@ -1907,18 +1908,20 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
   auto gb = reinterpret_cast<const __nv_bfloat16*>(gamma);
   const int slots = stats_slots_for(K);
   int grid = 0;
+  // neither a tensor amax nor partial maxima wanted: inverse RMS only (the pipelined kernel skips the second sweep)
+  const int want_amax = (amax_sg != nullptr || partials_out != nullptr) ? 1 : 0;
   if (K <= 8192 && slots >= 4) {
     int* status = device_status_ptr();
     if (status == nullptr) return -1;
     int rc;
-    if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
-                                    : launch_stats_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
-    else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
-                                         : launch_stats_t<8, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
-    else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
-                                         : launch_stats_t<16, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
-    else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid)
-                          : launch_stats_t<32, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid);
+    if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax)
+                                    : launch_stats_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax);
+    else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax)
+                                         : launch_stats_t<8, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax);
+    else if (K <= 4096) rc = compute_inv ? launch_stats_t<16, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax)
+                                         : launch_stats_t<16, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax);
+    else rc = compute_inv ? launch_stats_t<32, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax)
+                          : launch_stats_t<32, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax);
     if (rc) return rc;
   } else {
     grid = (int)std::min<int64_t>((M + 7) / 8, std::min<int64_t>((int64_t)device_sm_count() * 8, kScratchFloats));
@@ -1931,6 +1934,7 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
     partials_out->count = grid;
     return 0;
   }
+  if (!want_amax) return 0;
   return launch_reduce_partials(scratch, grid, amax_sg, st);
 }
 
@@ -2132,8 +2136,9 @@ int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
 int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
                                 float* inv_rms, int compute_inv_rms, float* amax_sg, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_rmsnorm_stats")) return rc;
-  if (gamma_bf16 == nullptr || inv_rms == nullptr || amax_sg == nullptr)
-    return set_error("nvfp4_rmsnorm_stats: gamma, inv_rms and amax_sg are required");
+  if (gamma_bf16 == nullptr || inv_rms == nullptr)
+    return set_error("nvfp4_rmsnorm_stats: gamma and inv_rms are required");
+  if (amax_sg == nullptr && !compute_inv_rms) return set_error("nvfp4_rmsnorm_stats: nothing to compute");
   return launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, compute_inv_rms != 0,
                               (cudaStream_t)stream);
 }
