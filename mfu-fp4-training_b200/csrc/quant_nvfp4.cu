@@ -288,6 +288,148 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
   }
 }
 
+// The same statistics with TWO warps per row: warp `half` of a pair takes the row's vectors of parity `half`, which is
+// exactly the i = half accumulators of the summation tree above, so the pair's two partial sums are part[0] and
+// part[1] of stats_inv_rms, exchanged through shared memory at a 64-thread named barrier and added in that order.
+// A row then takes half as long and holds half the registers, so 24 warps (12 pairs) fit beside a ring of two row
+// slots per pair: more warps to hide the reduction's latency, and a shorter tail when the CTA's rows run out.
+// Rows are dealt to pairs round-robin (pair p: the CTA's rows p, p + pairs, ...) and a pair refills its own slots, so
+// no counter and no cross-warp claim protocol is needed.
+constexpr int kStatsPairSlots = 2;   // row slots per pair
+
+template <int NVH /* 16-byte vectors per lane and warp: K <= NVH*512 */, bool COMPUTE_INV_RMS>
+__global__ void __launch_bounds__(NVH <= 8 ? 768 : 384, 1)
+rmsnorm_stats_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
+                          float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
+                          int* __restrict__ status, int early_reads, int want_amax) {
+  extern __shared__ __align__(128) uint8_t stats_smem[];
+  __shared__ float warp_max_s[24];
+  pdl_launch_dependents();   // the quantiser launched behind this kernel may set up and prefetch meanwhile
+  const int warps = blockDim.x >> 5, pairs = warps >> 1;
+  const uint32_t row_bytes = (uint32_t)K * 2u;
+  float4* gamma_lo = reinterpret_cast<float4*>(stats_smem);                 // [K/8] gamma of elements 0-3 of each vector
+  float4* gamma_hi = gamma_lo + (K >> 3);                                   // [K/8] gamma of elements 4-7
+  uint8_t* slots = stats_smem + (size_t)K * 4;                              // [pairs][kStatsPairSlots][row_bytes]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(slots + (size_t)pairs * kStatsPairSlots * row_bytes);
+  float* xchg = reinterpret_cast<float*>(bars + pairs * kStatsPairSlots);   // [2 buffers][pairs][2 halves][32 lanes]
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int pair = warp >> 1, half = warp & 1;
+  // Rows r = blockIdx.x, blockIdx.x + grid, ... belong to this CTA (all CTAs sweep x front to back together, so that
+  // the END of x is what L2 holds when the quantiser starts there); the CTA's k-th row goes to pair k % pairs.
+  const int n_band = (int)blockIdx.x < M ? (M - (int)blockIdx.x + (int)gridDim.x - 1) / (int)gridDim.x : 0;
+  const int my_rows = pair < n_band ? (n_band - pair + pairs - 1) / pairs : 0;
+  const uint64_t keep = l2_policy_evict_last();
+  uint8_t* my_slots = slots + (size_t)pair * kStatsPairSlots * row_bytes;
+  uint64_t* my_bars = bars + pair * kStatsPairSlots;
+  auto row_of = [&](int k) { return (size_t)(pair + k * pairs) * gridDim.x + blockIdx.x; };
+  auto issue = [&](int k) {                   // the pair's k-th row -> its slot k % kStatsPairSlots
+    const int sl = k % kStatsPairSlots;
+    mbar_expect_tx(&my_bars[sl], row_bytes);
+    bulk_load_1d_hint(my_slots + (size_t)sl * row_bytes, x + row_of(k) * K, row_bytes, &my_bars[sl], keep);
+  };
+  if (half == 0 && lane == 0) {
+    for (int sl = 0; sl < kStatsPairSlots; ++sl) mbar_init(&my_bars[sl], 1);
+    fence_mbar_init();
+  }
+  // By default nothing of the caller's is read before the previous kernel's writes are visible (x is usually what that
+  // kernel just produced); with early_reads the ring fills and gamma is staged meanwhile.
+  if (!early_reads) pdl_wait();
+  if (half == 0 && lane == 0)
+    for (int k = 0; k < kStatsPairSlots && k < my_rows; ++k) issue(k);
+  if (want_amax) {
+    for (int q = threadIdx.x; q < (K >> 3); q += blockDim.x) {
+      const uint4 g = __ldg(reinterpret_cast<const uint4*>(gamma) + q);
+      gamma_lo[q] = make_float4(bf16lo_to_f32(g.x), bf16hi_to_f32(g.x), bf16lo_to_f32(g.y), bf16hi_to_f32(g.y));
+      gamma_hi[q] = make_float4(bf16lo_to_f32(g.z), bf16hi_to_f32(g.z), bf16lo_to_f32(g.w), bf16hi_to_f32(g.w));
+    }
+  }
+  __syncthreads();
+  // inv_rms and the partial maxima may still be read by the strip quantiser of the previous call
+  pdl_wait();
+
+  float mx = 0.0f;
+  const int nvec_row = K >> 3;
+  const float2 zero2 = make_float2(0.0f, 0.0f);
+  (void)zero2;
+  for (int k = 0; k < my_rows; ++k) {
+    const int sl = k % kStatsPairSlots;
+    if (!mbar_wait_bounded(&my_bars[sl], (uint32_t)(k / kStatsPairSlots) & 1u)) {
+      if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
+      break;   // both warps of the pair wait on the same barrier and give up together
+    }
+    const uint4* src = reinterpret_cast<const uint4*>(my_slots + (size_t)sl * row_bytes);
+    uint4 v[NVH];
+#pragma unroll
+    for (int j = 0; j < NVH; ++j) {
+      const int q = lane + 32 * (2 * j + half);
+      v[j] = (q < nvec_row) ? src[q] : make_uint4(0, 0, 0, 0);
+    }
+    const size_t row = row_of(k);
+    float inv;
+    if constexpr (COMPUTE_INV_RMS) {
+      // acc[q]: virtual lane 4*lane + 128*half + q of the reference's 256-thread tree
+      float a4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int j = 0; j < NVH; ++j) {
+        a4[0] = fma_sq_bf16x2(v[j].x, a4[0]);
+        a4[1] = fma_sq_bf16x2(v[j].y, a4[1]);
+        a4[2] = fma_sq_bf16x2(v[j].z, a4[2]);
+        a4[3] = fma_sq_bf16x2(v[j].w, a4[3]);
+      }
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 4);
+        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 2);
+        a4[q] += __shfl_xor_sync(0xffffffffu, a4[q], 1);
+      }
+      const float part = (a4[0] + a4[2]) + (a4[1] + a4[3]);
+      float* xb = xchg + (size_t)(((k & 1) * pairs + pair) * 2) * 32;
+      xb[half * 32 + lane] = part;
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");   // both halves of the row are in registers, both sums written
+      const float other = xb[(half ^ 1) * 32 + lane];
+      float s_ = half == 0 ? part + other : other + part;             // part[0] + part[1]
+      s_ += __shfl_xor_sync(0xffffffffu, s_, 16);
+      s_ += __shfl_xor_sync(0xffffffffu, s_, 8);
+      inv = rsqrtf(s_ / static_cast<float>(K) + eps);
+      if (half == 0 && lane == 0) {
+        inv_rms[row] = inv;
+        if (k + kStatsPairSlots < my_rows) issue(k + kStatsPairSlots);
+      }
+    } else {
+      inv = __ldg(inv_rms + row);
+      asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");   // both warps hold their halves: the slot may be refilled
+      if (half == 0 && lane == 0 && k + kStatsPairSlots < my_rows) issue(k + kStatsPairSlots);
+    }
+    if (want_amax) {
+      const float2 inv2 = make_float2(inv, inv);
+#pragma unroll
+      for (int j = 0; j < NVH; ++j) {
+        const int q = lane + 32 * (2 * j + half);
+        if (q < nvec_row) {
+          const float4 g01 = gamma_lo[q];
+          const float4 g23 = gamma_hi[q];
+          const float2 t0 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].x), bf16hi_to_f32(v[j].x)), inv2), make_float2(g01.x, g01.y));
+          const float2 t1 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].y), bf16hi_to_f32(v[j].y)), inv2), make_float2(g01.z, g01.w));
+          const float2 t2 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].z), bf16hi_to_f32(v[j].z)), inv2), make_float2(g23.x, g23.y));
+          const float2 t3 = mul2(mul2(make_float2(bf16lo_to_f32(v[j].w), bf16hi_to_f32(v[j].w)), inv2), make_float2(g23.z, g23.w));
+          mx = absmax3(mx, t0.x, t0.y);
+          mx = absmax3(mx, t1.x, t1.y);
+          mx = absmax3(mx, t2.x, t2.y);
+          mx = absmax3(mx, t3.x, t3.y);
+        }
+      }
+    }
+  }
+  float run_max = warp_max(mx);
+  if (lane == 0) warp_max_s[warp] = run_max;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < warps; ++w) run_max = fmaxf(run_max, warp_max_s[w]);
+    // the one rounding to bf16 that the element-wise maximum would have applied to its winner
+    partials[blockIdx.x] = __bfloat162float(__float2bfloat16_rn(run_max));   // every CTA writes: nothing to clear
+  }
+}
+
 // Any-K variant: the row is read twice (second read hits L1/L2).
 template <bool COMPUTE_INV_RMS>
 __global__ void __launch_bounds__(256)
@@ -1894,6 +2036,33 @@ static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, floa
   return 0;
 }
 
+// FP4B200_STATS_PAIR=0: one warp per row (the earlier form of the statistics kernel), for A/B runs.
+static bool stats_pair_enabled() {
+  static const bool on = [] {
+    const char* e = getenv("FP4B200_STATS_PAIR");
+    return !(e != nullptr && e[0] == '0');
+  }();
+  return on;
+}
+
+template <int NVH, bool CI>
+static int launch_stats_pair_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
+                               int64_t M, int64_t K, int* status, cudaStream_t st, int* grid_out, int want_amax) {
+  auto kern = rmsnorm_stats_pair_kernel<NVH, CI>;
+  const int max_pairs = NVH <= 8 ? 12 : 6;
+  const int64_t per_pair = (int64_t)kStatsPairSlots * K * 2 + kStatsPairSlots * 8 + 2 * 2 * 32 * 4;
+  const int pairs = (int)std::min<int64_t>(max_pairs, (227 * 1024 - K * 4 - 1024) / per_pair);
+  if (pairs < 1) return set_error("rmsnorm statistics: rows of %lld elements do not fit the pipelined kernel", (long long)K);
+  const size_t smem = (size_t)K * 4 + (size_t)pairs * per_pair;
+  FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  const int grid = (int)std::min<int64_t>((M + pairs - 1) / pairs, (int64_t)device_sm_count());
+  PdlLaunch l(dim3((unsigned)grid), dim3((unsigned)pairs * 64), smem, st, stats_pdl_enabled());
+  FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, kern, xb, gb, inv_rms, partials, eps, (int)M, (int)K, status, pdl_early_reads(),
+                                    want_amax));
+  *grid_out = grid;
+  return 0;
+}
+
 // RMSNorm statistics of x [M, K]: inv_rms per row (computed, or read when !compute_inv) and the tensor
 // amax of bf16(x * inv_rms * gamma).  partials_out == nullptr: amax_sg[0..1] are written on the stream
 // (two launches).  Otherwise only the per-CTA maxima are produced, in `scratch`, for the quantiser
@@ -1914,6 +2083,16 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
     int* status = device_status_ptr();
     if (status == nullptr) return -1;
     int rc;
+    if (stats_pair_enabled()) {
+      if (K <= 1024) rc = compute_inv ? launch_stats_pair_t<2, true>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax)
+                                      : launch_stats_pair_t<2, false>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax);
+      else if (K <= 2048) rc = compute_inv ? launch_stats_pair_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax)
+                                           : launch_stats_pair_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax);
+      else if (K <= 4096) rc = compute_inv ? launch_stats_pair_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax)
+                                           : launch_stats_pair_t<8, false>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax);
+      else rc = compute_inv ? launch_stats_pair_t<16, true>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax)
+                            : launch_stats_pair_t<16, false>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax);
+    } else
     if (K <= 1024) rc = compute_inv ? launch_stats_t<4, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax)
                                     : launch_stats_t<4, false>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax);
     else if (K <= 2048) rc = compute_inv ? launch_stats_t<8, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, want_amax)
