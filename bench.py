@@ -288,7 +288,7 @@ def gemm_roofline_leg(torch, peaks, local_rank, world, refs, traffic):
 
 
 def config1_leg(torch, dev):
-    """BASELINE config 1: X bf16 [2048 x 4096] (outlier channels) and W bf16 [4096 x 4096] ~ N(0, 0.02) quantised to
+    """Benchmark configuration 1: X bf16 [2048 x 4096] (outlier channels) and W bf16 [4096 x 4096] ~ N(0, 0.02) quantised to
     NVFP4 (1-D blocks, round to nearest, decode-centric as the reference's CPU emulation) and multiplied; beside it the
     numpy oracle's quantise -> dequantise -> float64 product on the host cores, and the relative Frobenius distance of
     the GPU's fp32 epilogue from that product."""
@@ -430,7 +430,7 @@ def _timed_stages(torch, stages, iters=3, warm=3):
 
 
 def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks, iters=10):
-    """Llama-3-8B FFN backward in NVFP4 at M=16384 per rank (config 4, as BASELINE.json words it): dgrad GEMMs from
+    """Llama-3-8B FFN backward in NVFP4 at M=16384 per rank (benchmark configuration 4 as it is worded): dgrad GEMMs from
     round-to-nearest operands; wgrad GEMMs from operands with the 16-point Hadamard transform along the token
     dimension on BOTH sides (seeded sign vector) and Philox stochastic rounding (fixed seed / subsequence) of the
     gradient side.  Stages: quantise dY (row operand RTN, column operand transformed + SR; the transform's tensor
