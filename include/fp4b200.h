@@ -134,6 +134,13 @@ int fp4b200_nvfp4_rht16_amax(const void* x_bf16, const void* gamma_bf16, const f
 int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
                                      void* col_fp4, void* col_sc, float* amax_sg, void* stream);
 
+/* The same 16x16-tile quantisation with the tensor amax given (a device scalar) instead of computed: a row shard of a
+ * weight quantised with the amax of the whole weight gives the whole weight's bytes for its rows, which is what a
+ * packed all-gather of 2-D quantised weight shards needs.  No counterpart in the reference, which quantises the
+ * gathered weight. */
+int fp4b200_nvfp4_quantize_weight_2d_with_amax(const void* w_bf16, int64_t N, int64_t K, const float* amax, void* row_fp4,
+                                               void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
 /* RMSNorm statistics: inv_rms[M] = rsqrt(mean(x^2)+eps) (computed when compute_inv_rms != 0,
  * else read) and amax of bf16(x*inv_rms*gamma); amax_sg may be NULL when only inv_rms is wanted (the MXFP4
  * producers: no tensor scale), which skips the second sweep over each row.

@@ -40,6 +40,8 @@ SIGNATURES = {
                                  _c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_weight_2d": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                          _c_void_p],
+    "fp4b200_nvfp4_quantize_weight_2d_with_amax": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                                   _c_void_p],
     "fp4b200_nvfp4_rmsnorm_stats": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _int, _c_void_p,
                                     _c_void_p],
     "fp4b200_nvfp4_fused_norm_quantize": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _int, _int,

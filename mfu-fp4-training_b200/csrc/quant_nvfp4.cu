@@ -2312,6 +2312,15 @@ int fp4b200_nvfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
                          nullptr, true, (cudaStream_t)stream, true, nullptr, &part, amax_sg);
 }
 
+int fp4b200_nvfp4_quantize_weight_2d_with_amax(const void* w_bf16, int64_t N, int64_t K, const float* amax, void* row_fp4,
+                                               void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  if (int rc = check_quant_shapes(w_bf16, N, K, "nvfp4_quantize_weight_2d_with_amax")) return rc;
+  if (!amax || !row_fp4 || !row_sc || !col_fp4 || !col_sc)
+    return set_error("nvfp4_quantize_weight_2d_with_amax: amax and all outputs are required");
+  return launch_quantize(w_bf16, N, K, amax, amax, false, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc,
+                         nullptr, true, (cudaStream_t)stream, true);
+}
+
 int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
                                 float* inv_rms, int compute_inv_rms, float* amax_sg, void* stream) {
   if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_rmsnorm_stats")) return rc;

@@ -42,9 +42,11 @@ def _part_shapes(N: int, K: int, fmt: str, want_col: bool):
     return shapes
 
 
-def _cuda_quantize_nvfp4(w_shard: torch.Tensor, amax: torch.Tensor, encode_centric: bool, want_col: bool, out=None):
+def _cuda_quantize_nvfp4(w_shard: torch.Tensor, amax: torch.Tensor, encode_centric: bool, want_col: bool, out=None,
+                         weight_2d: bool = False):
     """Row (+column) NVFP4 quantisation of a shard with a given device-resident tensor amax; into `out`
-    (row_fp4, row_sc[, col_fp4, col_sc]) when given."""
+    (row_fp4, row_sc[, col_fp4, col_sc]) when given.  ``weight_2d``: one decode-centric scale per 16 x 16 tile for both
+    orientations (tk_quantize_weight_2d's blocks; needs both orientations)."""
     from . import _lib
     N, K = w_shard.shape
     u8 = dict(dtype=torch.uint8, device=w_shard.device)
@@ -52,6 +54,14 @@ def _cuda_quantize_nvfp4(w_shard: torch.Tensor, amax: torch.Tensor, encode_centr
         out = [torch.empty(sh, **u8) for sh in _part_shapes(N, K, "nvfp4", want_col)]
     row_fp4, row_sc = out[0], out[1]
     col_fp4, col_sc = (out[2], out[3]) if want_col else (None, None)
+    if weight_2d:
+        if not want_col:
+            raise RuntimeError("2-D weight blocks are quantised in both orientations at once")
+        with torch.cuda.device(w_shard.device):
+            _lib.call("fp4b200_nvfp4_quantize_weight_2d_with_amax", w_shard.data_ptr(), N, K, amax.data_ptr(),
+                      row_fp4.data_ptr(), row_sc.data_ptr(), col_fp4.data_ptr(), col_sc.data_ptr(),
+                      torch.cuda.current_stream(w_shard.device).cuda_stream)
+        return row_fp4, row_sc, col_fp4, col_sc
     with torch.cuda.device(w_shard.device):
         _lib.call("fp4b200_nvfp4_quantize", w_shard.data_ptr(), N, K, amax.data_ptr(), None, int(encode_centric),
                   row_fp4.data_ptr(), row_sc.data_ptr(), None if col_fp4 is None else col_fp4.data_ptr(),
@@ -197,17 +207,26 @@ def _assemble(gathered, want_col):
 
 
 def all_gather_nvfp4_weights(w_shards, group=None, want_col: bool = True, encode_centric: bool = True,
-                             quantize_shard: Optional[Callable] = None, reuse_buffers: bool = False):
+                             quantize_shard: Optional[Callable] = None, reuse_buffers: bool = False,
+                             weight_2d: bool = False):
     """``all_gather_nvfp4_weight`` for a list of weights with one amax all-reduce and one group of all-gathers.
     Returns a list of ``(row_fp4, row_sc, col_fp4, col_sc, sg [1])``, byte-identical to the per-weight function's.
     ``reuse_buffers``: the results live in a workspace kept for these shapes and are overwritten by the next call
-    with the same shapes (what a layer's per-step gather wants); off, every call returns fresh tensors."""
+    with the same shapes (what a layer's per-step gather wants); off, every call returns fresh tensors.
+    ``weight_2d``: the weights' 16 x 16 block form (tk_quantize_weight_2d, fused_te_linear.py:4716-4748: decode-centric,
+    one scale per tile for both orientations); shards of a multiple of 128 rows hold whole tiles, so the gathered
+    bytes are those of quantising the gathered weight."""
+    if weight_2d and quantize_shard is None:
+        def quantize_shard_2d(w, amax, ec, wc, out=None):
+            return _cuda_quantize_nvfp4(w, amax, ec, wc, out=out, weight_2d=True)
+    else:
+        quantize_shard_2d = None
     for w in w_shards:
         _check_shard(w)
     world = dist.get_world_size(group)
     amaxes = _local_amaxes(w_shards)
     dist.all_reduce(amaxes, op=dist.ReduceOp.MAX, group=group)
-    q = quantize_shard or _cuda_quantize_nvfp4
+    q = quantize_shard or quantize_shard_2d or _cuda_quantize_nvfp4
     n_parts = 4 if want_col else 2
     send, recv = (_workspace("nvfp4", w_shards, want_col, world) if (reuse_buffers and quantize_shard is None)
                   else ([None] * len(w_shards), None))

@@ -52,6 +52,12 @@ def _worker(rank, world, port, q):
             for got, full in zip(outs, (wd, w2d)):
                 ref = tkq.tk_quantize_for_gemm(full, True, True)
                 ok = ok and all(torch.equal(got[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
+        # the weights' 16 x 16 block form: shards hold whole tiles, so the gather equals tk_quantize_weight_2d of the weight
+        outs = fsdp.all_gather_nvfp4_weights([shard, shard2], None, True, False, weight_2d=True)
+        for got, full in zip(outs, (wd, w2d)):
+            ref = tkq.tk_quantize_weight_2d(full)
+            ok = ok and all(torch.equal(got[i].reshape(-1), ref[i].view(torch.uint8).reshape(-1)) for i in range(4))
+            ok = ok and got[4].item() == ref[4].item()
         outs = fsdp.all_gather_mxfp4_weights([shard, shard2], None, True, 1)
         for got, full in zip(outs, (wd, w2d)):
             ref = mxq.mxfp4_quantize_row_and_col(full, 1)
