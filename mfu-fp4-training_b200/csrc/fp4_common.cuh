@@ -297,6 +297,20 @@ __device__ __forceinline__ float2 mul2(float2 a, float2 b) {
   return d;
 }
 
+// {a.x + b.x, a.y + b.y} and {a.x - b.x, a.y - b.y}: two IEEE additions per instruction
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; add.rn.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+__device__ __forceinline__ float2 sub2(float2 a, float2 b) {
+  float2 d;
+  asm("{.reg .b64 x, y, z; mov.b64 x, {%2, %3}; mov.b64 y, {%4, %5}; sub.rn.f32x2 z, x, y; mov.b64 {%0, %1}, z;}"
+      : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+  return d;
+}
+
 // {a.x*b.x + c.x, a.y*b.y + c.y}, each a fused multiply-add (same rounding as fmaf)
 __device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
   float2 d;

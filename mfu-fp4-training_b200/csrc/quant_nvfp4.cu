@@ -716,6 +716,26 @@ __device__ __forceinline__ void fwht16(float (&v)[16]) {
   for (int i = 0; i < 16; ++i) v[i] *= 0.25f;
 }
 
+// the same transform of two independent 16-vectors at once (.x and .y), in packed fp32x2 arithmetic: the same IEEE
+// additions in the same order, half the instructions
+__device__ __forceinline__ void fwht16x2(float2 (&v)[16]) {
+#pragma unroll
+  for (int step = 1; step < 16; step <<= 1) {
+#pragma unroll
+    for (int base = 0; base < 16; base += 2 * step) {
+#pragma unroll
+      for (int j = 0; j < step; ++j) {
+        const float2 x = v[base + j], y = v[base + j + step];
+        v[base + j] = add2(x, y);
+        v[base + j + step] = sub2(x, y);
+      }
+    }
+  }
+  const float2 q = make_float2(0.25f, 0.25f);
+#pragma unroll
+  for (int i = 0; i < 16; ++i) v[i] = mul2(v[i], q);
+}
+
 // 16 values times coeff -> 8 bytes of codes, stochastic rounding with words wsel[0..3] for the
 // four groups of four elements
 __device__ __forceinline__ uint2 quant16_sr(const float (&x)[16], float coeff, const uint32_t (&wsel)[4]) {
@@ -738,7 +758,8 @@ __device__ __forceinline__ uint2 quant16_rn(const float (&x)[16], float coeff) {
 template <bool ENCODE_CENTRIC>
 __device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, uint32_t neg_mask, float s_enc,
                                            const ScaleLut* lut, bool sr, const uint32_t (&wsel)[4], uint32_t& stored,
-                                           bool scale_sr = false, uint32_t scale_rbits = 0) {
+                                           bool scale_sr = false, uint32_t scale_rbits = 0,
+                                           const uint32_t* code_lut = nullptr, int code_base = 0) {
   if (rht) {
     if (neg_mask != 0) {
 #pragma unroll
@@ -751,7 +772,11 @@ __device__ __forceinline__ uint2 opt_block(float (&x)[16], bool rht, uint32_t ne
   float bm = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) bm = fmaxf(bm, fabsf(x[i]));
-  const ScaleLut e = lut[scale_sr ? block_code_sr<ENCODE_CENTRIC>(bm, s_enc, scale_rbits) : block_code<ENCODE_CENTRIC>(bm, s_enc)];
+  // the block's values are bf16 values (inputs, or rounded after the transform), so its maximum's upper 16 bits index
+  // the code table of the large launches
+  const ScaleLut e = (code_lut != nullptr && !scale_sr)
+                         ? code_lut_lookup<ENCODE_CENTRIC>(code_lut, lut, code_base, s_enc, __float_as_uint(bm) >> 16)
+                         : lut[scale_sr ? block_code_sr<ENCODE_CENTRIC>(bm, s_enc, scale_rbits) : block_code<ENCODE_CENTRIC>(bm, s_enc)];
   stored = e.stored;
   return sr ? quant16_sr(x, e.coeff, wsel) : quant16_rn(x, e.coeff);
 }
@@ -1186,7 +1211,9 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   uint64_t* bars = reinterpret_cast<uint64_t*>(lut_col + 128);                 // [warp][depth]
   float* amax_slot = reinterpret_cast<float*>(bars + kStripWarps * depth);     // 16 bytes
   float* gamma_f = amax_slot + 4;                                              // [K] (NORM)
-  constexpr bool kCodeLut = PAIR && OPT == 0;    // the large round-to-nearest launches look block codes up
+  // the large launches look block codes up (not with scale SR: its codes are drawn; not RMSNorm + modes: the two
+  // operands' tensor scales differ there and the paired RMSNorm form keeps one table)
+  constexpr bool kCodeLut = PAIR && (OPT == 0 || (OPT == 1 && !NORM));
   // [kCodeLutSize], and a second one for the column operand unless NORM (one tensor maximum for both operands)
   uint32_t* code_lut_row = reinterpret_cast<uint32_t*>(gamma_f + (NORM ? a.K : 0));
   uint32_t* code_lut_col = NORM ? code_lut_row : code_lut_row + kCodeLutSize;
@@ -1415,7 +1442,26 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
           row_neg_lo = __ballot_sync(0xffffffffu, rht_sign_is_negative(a.sign_seed, a.sign_subseq, (unsigned long long)(col0 + lane)) != 0);
           row_neg_hi = __ballot_sync(0xffffffffu, rht_sign_is_negative(a.sign_seed, a.sign_subseq, (unsigned long long)(col0 + 32 + lane)) != 0);
         }
-        if (a.opt_return_row) {
+        if (a.opt_return_row && !kScaleSr && !a.opt_rht_row && !a.opt_sr_row) {
+          // a row operand without any of the modes (only the column operand is transformed or rounded
+          // stochastically): the round-to-nearest kernel's row arithmetic
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            uint32_t mx = 0;
+#pragma unroll
+            for (int q = 0; q < 8; ++q) mx = absmax_xs(mx, w[8 * b + q]);
+            ScaleLut e;
+            if constexpr (kCodeLut) {
+              const uint32_t am = mx & 0x7FFF7FFFu;
+              e = code_lut_lookup<ENCODE_CENTRIC>(code_lut_row, lut_row, code_base_row, s_enc_row, max(am >> 16, am & 0xFFFFu));
+            } else {
+              e = lut_row[block_code<ENCODE_CENTRIC>(fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx))), s_enc_row)];
+            }
+            codes[2 * b] = quant8(w + 8 * b, e.coeff);
+            codes[2 * b + 1] = quant8(w + 8 * b + 4, e.coeff);
+            sc_word |= e.stored << (8 * b);
+          }
+        } else if (a.opt_return_row) {
 #pragma unroll
           for (int b = 0; b < 4; ++b) {
             float x[16];
@@ -1458,7 +1504,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
             uint32_t stored;
             const uint32_t neg = ((b < 2 ? row_neg_lo : row_neg_hi) >> (16 * (b & 1))) & 0xFFFFu;
             const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_row != 0, neg, s_enc_row, lut_row, a.opt_sr_row != 0, wsel,
-                                                       stored, kScaleSr, scale_rbits);
+                                                       stored, kScaleSr, scale_rbits, kCodeLut ? code_lut_row : nullptr, code_base_row);
             codes[2 * b] = cd.x;
             codes[2 * b + 1] = cd.y;
             sc_word |= stored << (8 * b);
@@ -1519,6 +1565,19 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
         }
         if constexpr (OPT != 0) {
           const int grp16 = wv * 2 + g;   // 16-row group inside the chunk (the reference kernel's warp role)
+          if (a.opt_rht_col) {
+            // the transform of both columns of the pair at once, in packed fp32x2 arithmetic, rounded back to bf16x2
+            const uint32_t neg = (col_neg >> (16 * g)) & 0xFFFFu;
+            float2 v[16];
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+              v[i] = make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i]));
+              if ((neg >> i) & 1u) v[i] = make_float2(-v[i].x, -v[i].y);
+            }
+            fwht16x2(v);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) w[i] = f32x2_to_bf16x2(v[i].x, v[i].y);
+          }
 #pragma unroll
           for (int wq = 0; wq < 2; ++wq) {
             float x[16];
@@ -1549,8 +1608,9 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
               }
             }
             uint32_t stored;
-            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, a.opt_rht_col != 0, (col_neg >> (16 * g)) & 0xFFFFu, s_enc_col, lut_col,
-                                                       a.opt_sr_col != 0, wsel, stored, kScaleSr, scale_rbits);
+            const uint2 cd = opt_block<ENCODE_CENTRIC>(x, false, 0u, s_enc_col, lut_col,   // (already transformed above)
+                                                       a.opt_sr_col != 0, wsel, stored, kScaleSr, scale_rbits,
+                                                       kCodeLut ? code_lut_col : nullptr, code_base_col);
             if (wq == 0) { cc0[2 * g] = cd.x; cc0[2 * g + 1] = cd.y; sc0 |= stored << (8 * g); }
             else { cc1[2 * g] = cd.x; cc1[2 * g + 1] = cd.y; sc1 |= stored << (8 * g); }
           }
@@ -1702,12 +1762,11 @@ rht16_col_amax_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ a
     uint32_t w[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) w[i] = __ldg(p + (size_t)i * pairs);
-    float v0[16], v1[16];
+    float2 v[16];
 #pragma unroll
     for (int i = 0; i < 16; ++i) {
       plain = absmax_xs(plain, w[i]);
-      v0[i] = bf16lo_to_f32(w[i]);
-      v1[i] = bf16hi_to_f32(w[i]);
+      v[i] = make_float2(bf16lo_to_f32(w[i]), bf16hi_to_f32(w[i]));
     }
     if (sign) {
       // the 32 lanes of a warp hold 64 columns of ONE 16-row group (K is a multiple of 128 and the grid stride a
@@ -1716,13 +1775,12 @@ rht16_col_amax_kernel(const __nv_bfloat16* __restrict__ x, float* __restrict__ a
                                rht_sign_is_negative(sign_seed, sign_subseq, (unsigned long long)(rb * 16 + (threadIdx.x & 15))) != 0) & 0xFFFFu;
 #pragma unroll
       for (int i = 0; i < 16; ++i) {
-        if ((neg >> i) & 1u) { v0[i] = -v0[i]; v1[i] = -v1[i]; }
+        if ((neg >> i) & 1u) v[i] = make_float2(-v[i].x, -v[i].y);
       }
     }
-    fwht16(v0);
-    fwht16(v1);
+    fwht16x2(v);
 #pragma unroll
-    for (int i = 0; i < 16; ++i) local = fmaxf(local, fmaxf(fabsf(v0[i]), fabsf(v1[i])));
+    for (int i = 0; i < 16; ++i) local = fmaxf(local, fmaxf(fabsf(v[i].x), fabsf(v[i].y)));
   }
   float plain_f = fmaxf(fabsf(bf16lo_to_f32(plain)), fabsf(bf16hi_to_f32(plain)));
   local = warp_max(local);
