@@ -28,55 +28,80 @@ __device__ __forceinline__ void block_amax_commit(float v, float* amax) {
 __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__ h1, const uint4* __restrict__ h3,
                                                        uint4* __restrict__ out, size_t n_vec,
                                                        float* __restrict__ amax) {
+  constexpr int kU = 4;   // vectors per stream and thread in flight (see silu_deriv_kernel)
   uint32_t mx = 0;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    const uint4 a = __ldg(h1 + i), b = __ldg(h3 + i);
-    const uint32_t aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-    uint32_t o[4];
+  const size_t tile = (size_t)blockDim.x * kU;
+  for (size_t base = (size_t)blockIdx.x * tile; base < n_vec; base += (size_t)gridDim.x * tile) {
+    uint4 a[kU], b[kU];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const float lo = silu_f(bf16lo_to_f32(aw[q])) * bf16lo_to_f32(bw[q]);
-      const float hi = silu_f(bf16hi_to_f32(aw[q])) * bf16hi_to_f32(bw[q]);
-      o[q] = f32x2_to_bf16x2(lo, hi);
-      mx = bf16x2_absmax(mx, o[q]);
+    for (int u = 0; u < kU; ++u) {
+      const size_t i = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (i < n_vec) { a[u] = __ldg(h1 + i); b[u] = __ldg(h3 + i); }
     }
-    out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const size_t i = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (i >= n_vec) continue;
+      const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+      uint32_t o[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float lo = silu_f(bf16lo_to_f32(aw[q])) * bf16lo_to_f32(bw[q]);
+        const float hi = silu_f(bf16hi_to_f32(aw[q])) * bf16hi_to_f32(bw[q]);
+        o[q] = f32x2_to_bf16x2(lo, hi);
+        mx = bf16x2_absmax(mx, o[q]);
+      }
+      out[i] = make_uint4(o[0], o[1], o[2], o[3]);
+    }
   }
   block_amax_commit(bf16x2_hmax_to_f32(mx), amax);
 }
 
+// Four vectors per stream and thread in flight (a block works on tiles of 1024 vectors = 16 KB per stream): five
+// streams at once leave each one short runs between DRAM page switches otherwise (0.45 -> 0.38 ms at 16384 x 14336).
 __global__ void __launch_bounds__(256)
 silu_deriv_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ h3, const uint4* __restrict__ h1,
                   uint4* __restrict__ dh1, uint4* __restrict__ dh3, size_t n_vec, float* __restrict__ amax1,
                   float* __restrict__ amax3) {
+  constexpr int kU = 4;
   uint32_t mx1 = 0, mx3 = 0;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_vec; i += stride) {
-    const uint4 d = __ldg(dh + i), a = __ldg(h3 + i), b = __ldg(h1 + i);
-    const uint32_t dw[4] = {d.x, d.y, d.z, d.w}, aw[4] = {a.x, a.y, a.z, a.w}, bw[4] = {b.x, b.y, b.z, b.w};
-    uint32_t o1[4], o3[4];
+  const size_t tile = (size_t)blockDim.x * kU;
+  for (size_t base = (size_t)blockIdx.x * tile; base < n_vec; base += (size_t)gridDim.x * tile) {
+    uint4 d[kU], a[kU], b[kU];
 #pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      float c[2], e[2];
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const float df = k ? bf16hi_to_f32(dw[q]) : bf16lo_to_f32(dw[q]);
-        const float af = k ? bf16hi_to_f32(aw[q]) : bf16lo_to_f32(aw[q]);
-        const float x = k ? bf16hi_to_f32(bw[q]) : bf16lo_to_f32(bw[q]);
-        const float sig = 1.0f / (1.0f + __expf(-x));
-        const float sl = x * sig;
-        const float slp = sig * (1.0f + x - sl);
-        c[k] = df * af * slp;
-        e[k] = df * sl;
-      }
-      o1[q] = f32x2_to_bf16x2(c[0], c[1]);
-      o3[q] = f32x2_to_bf16x2(e[0], e[1]);
-      mx1 = bf16x2_absmax(mx1, o1[q]);
-      mx3 = bf16x2_absmax(mx3, o3[q]);
+    for (int u = 0; u < kU; ++u) {
+      const size_t i = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (i < n_vec) { d[u] = __ldg(dh + i); a[u] = __ldg(h3 + i); b[u] = __ldg(h1 + i); }
     }
-    dh1[i] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
-    dh3[i] = make_uint4(o3[0], o3[1], o3[2], o3[3]);
+#pragma unroll
+    for (int u = 0; u < kU; ++u) {
+      const size_t i = base + (size_t)u * blockDim.x + threadIdx.x;
+      if (i >= n_vec) continue;
+      const uint32_t dw[4] = {d[u].x, d[u].y, d[u].z, d[u].w}, aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w},
+                     bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
+      uint32_t o1[4], o3[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float c[2], e[2];
+#pragma unroll
+        for (int k = 0; k < 2; ++k) {
+          const float df = k ? bf16hi_to_f32(dw[q]) : bf16lo_to_f32(dw[q]);
+          const float af = k ? bf16hi_to_f32(aw[q]) : bf16lo_to_f32(aw[q]);
+          const float x = k ? bf16hi_to_f32(bw[q]) : bf16lo_to_f32(bw[q]);
+          const float sig = 1.0f / (1.0f + __expf(-x));
+          const float sl = x * sig;
+          const float slp = sig * (1.0f + x - sl);
+          c[k] = df * af * slp;
+          e[k] = df * sl;
+        }
+        o1[q] = f32x2_to_bf16x2(c[0], c[1]);
+        o3[q] = f32x2_to_bf16x2(e[0], e[1]);
+        mx1 = bf16x2_absmax(mx1, o1[q]);
+        mx3 = bf16x2_absmax(mx3, o3[q]);
+      }
+      dh1[i] = make_uint4(o1[0], o1[1], o1[2], o1[3]);
+      dh3[i] = make_uint4(o3[0], o3[1], o3[2], o3[3]);
+    }
   }
   block_amax_commit(bf16x2_hmax_to_f32(mx1), amax1);
   __syncthreads();
@@ -110,7 +135,7 @@ int fp4b200_silu_mul_bf16(const void* h1, const void* h3, int64_t n_elems, void*
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg, 0, 2 * sizeof(float), st));
   const size_t n_vec = (size_t)n_elems / 8;
   if (n_vec) {
-    const int grid = (int)std::min<size_t>((n_vec + 255) / 256, (size_t)device_sm_count() * 8);
+    const int grid = (int)std::min<size_t>((n_vec + 1023) / 1024, (size_t)device_sm_count() * 8);
     silu_mul_kernel<<<grid, 256, 0, st>>>((const uint4*)h1, (const uint4*)h3, (uint4*)h_out, n_vec, amax_sg);
     FP4_CUDA_CHECK(cudaGetLastError());
   }
@@ -142,7 +167,7 @@ int fp4b200_silu_deriv_bf16(const void* dh, const void* h3, const void* h1, int6
   FP4_CUDA_CHECK(cudaMemsetAsync(amax_sg3, 0, 2 * sizeof(float), st));
   const size_t n_vec = (size_t)n_elems / 8;
   if (n_vec) {
-    const int grid = (int)std::min<size_t>((n_vec + 255) / 256, (size_t)device_sm_count() * 8);
+    const int grid = (int)std::min<size_t>((n_vec + 1023) / 1024, (size_t)device_sm_count() * 8);
     silu_deriv_kernel<<<grid, 256, 0, st>>>((const uint4*)dh, (const uint4*)h3, (const uint4*)h1, (uint4*)dh1_out,
                                             (uint4*)dh3_out, n_vec, amax_sg1, amax_sg3);
     FP4_CUDA_CHECK(cudaGetLastError());
