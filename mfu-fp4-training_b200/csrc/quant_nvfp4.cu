@@ -304,6 +304,8 @@ rmsnorm_stats_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
                           int* __restrict__ status, int early_reads, int want_amax) {
   extern __shared__ __align__(128) uint8_t stats_smem[];
   __shared__ float warp_max_s[24];
+  __shared__ volatile int pair_abort[12];   // set when a wait of the pair ran out
+  if (threadIdx.x < 12) pair_abort[threadIdx.x] = 0;
   pdl_launch_dependents();   // the quantiser launched behind this kernel may set up and prefetch meanwhile
   const int warps = blockDim.x >> 5, pairs = warps >> 1;
   const uint32_t row_bytes = (uint32_t)K * 2u;
@@ -353,9 +355,13 @@ rmsnorm_stats_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
   (void)zero2;
   for (int k = 0; k < my_rows; ++k) {
     const int sl = k % kStatsPairSlots;
+    // A wait that runs out is reported and both warps of the pair leave together AFTER the row's named barrier: a
+    // warp must never wait there for a partner that has already left.
     if (!mbar_wait_bounded(&my_bars[sl], (uint32_t)(k / kStatsPairSlots) & 1u)) {
-      if (lane == 0) atomicExch(status, kStatusQuantTmaTimeout);
-      break;   // both warps of the pair wait on the same barrier and give up together
+      if (lane == 0) {
+        atomicExch(status, kStatusQuantTmaTimeout);
+        pair_abort[pair] = 1;
+      }
     }
     const uint4* src = reinterpret_cast<const uint4*>(my_slots + (size_t)sl * row_bytes);
     uint4 v[NVH];
@@ -386,6 +392,7 @@ rmsnorm_stats_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
       float* xb = xchg + (size_t)(((k & 1) * pairs + pair) * 2) * 32;
       xb[half * 32 + lane] = part;
       asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");   // both halves of the row are in registers, both sums written
+      if (pair_abort[pair] != 0) break;
       const float other = xb[(half ^ 1) * 32 + lane];
       float s_ = half == 0 ? part + other : other + part;             // part[0] + part[1]
       s_ += __shfl_xor_sync(0xffffffffu, s_, 16);
@@ -398,6 +405,7 @@ rmsnorm_stats_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
     } else {
       inv = __ldg(inv_rms + row);
       asm volatile("bar.sync %0, 64;" ::"r"(1 + pair) : "memory");   // both warps hold their halves: the slot may be refilled
+      if (pair_abort[pair] != 0) break;
       if (half == 0 && lane == 0 && k + kStatsPairSlots < my_rows) issue(k + kStatsPairSlots);
     }
     if (want_amax) {
