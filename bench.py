@@ -923,7 +923,7 @@ def main():
                 "peak_kind": f"of {peak_kind} copy bandwidth",
                 "traffic": traffic.get("nvfp4_quantize_strip_kernel", {}).get("dram_bytes_per_launch_16384x4096"),
                 "algorithmic_bytes_per_launch": quant_bytes, "avg_launch_ms": t_quant,
-                "other_kernels": {"rmsnorm_stats_kernel + partials reduction (pass 1 stand-alone, two launches)": {
+                "other_kernels": {"rmsnorm_stats_pair_kernel + partials reduction (pass 1 stand-alone, two launches)": {
                     "achieved": stats_bytes / (t_stats * 1e-3) / 1e9, "unit": "GB/s", "avg_launch_ms": t_stats,
                     "algorithmic_bytes_per_launch": stats_bytes,
                     "frac": stats_bytes / (t_stats * 1e-3) / 1e9 / peaks["hbm_gbs"]}},
