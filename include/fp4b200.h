@@ -107,6 +107,12 @@ int fp4b200_sr_prepare_state(uint64_t* rng_state, uint64_t rng_seed, uint64_t rn
                              void* stream);
 int fp4b200_sr_set_invocation_offset(uint64_t value, void* stream);
 int fp4b200_sr_get_invocation_offset(uint64_t* out_dev, void* stream);
+/* The per-producer numbering (low_bits_training/quantization/localcta_sr_state.py:1-11: one persistent int64[2]
+ * {seed, next subsequence} per producer, advanced by the extension on the producer's stream right before its
+ * quantiser).  One thread copies producer_state[0..1] into rng_state[0..1] and adds launches * 2^32 to
+ * producer_state[1]; rng_state then serves fp4b200_nvfp4_quantize_opt exactly as after fp4b200_sr_prepare_state.
+ * Both are device memory, 8-byte aligned.  The library's per-device counter is not touched. */
+int fp4b200_sr_reserve_from_state(int64_t* producer_state, uint64_t* rng_state, uint64_t launches, void* stream);
 
 /* As fp4b200_nvfp4_quantize_opt, with the row-wise codes written into a column slice of a wider matrix:
  * row_pitch_bytes is that matrix's row pitch (0: K/2, a dense [M, K/2]); 16-byte aligned outputs only.  Serves the

@@ -30,6 +30,7 @@ SIGNATURES = {
                                    ctypes.c_uint64, ctypes.c_uint64, _c_void_p, _int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                    _c_void_p, _c_void_p],
     "fp4b200_sr_prepare_state": [_c_void_p, ctypes.c_uint64, ctypes.c_uint64, ctypes.c_uint64, _c_void_p],
+    "fp4b200_sr_reserve_from_state": [_c_void_p, _c_void_p, ctypes.c_uint64, _c_void_p],
     "fp4b200_sr_set_invocation_offset": [ctypes.c_uint64, _c_void_p],
     "fp4b200_sr_get_invocation_offset": [_c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_opt_into": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _c_void_p, _c_void_p, _int, _int, _int,

@@ -1833,6 +1833,19 @@ __global__ void sr_prepare_state_kernel(unsigned long long* __restrict__ rng_sta
   }
 }
 
+// The other numbering: a PRODUCER's own persistent pair {seed, next subsequence} (one row of a checkpointed table),
+// advanced by the stride per reserved launch right before the launch it feeds, on that launch's stream; independent
+// of the order in which different producers are launched (low_bits_training/quantization/localcta_sr_state.py:1-11).
+__global__ void sr_reserve_from_state_kernel(unsigned long long* __restrict__ producer_state,
+                                             unsigned long long* __restrict__ rng_state, unsigned long long launches) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const unsigned long long next = producer_state[1];
+    rng_state[0] = producer_state[0];
+    rng_state[1] = next;
+    producer_state[1] = next + kSrInvocationStride * launches;
+  }
+}
+
 __global__ void sr_set_offset_kernel(unsigned long long value) {
   if (threadIdx.x == 0 && blockIdx.x == 0) g_sr_invocation_offset = value;
 }
@@ -2440,6 +2453,18 @@ int fp4b200_sr_prepare_state(uint64_t* rng_state, uint64_t rng_seed, uint64_t rn
   if (launches == 0) return set_error("sr_prepare_state: the number of launches to reserve must be positive");
   sr_prepare_state_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long*>(rng_state), rng_seed,
                                                             rng_subsequence, launches);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int fp4b200_sr_reserve_from_state(int64_t* producer_state, uint64_t* rng_state, uint64_t launches, void* stream) {
+  if (producer_state == nullptr || (reinterpret_cast<uintptr_t>(producer_state) & 7))
+    return set_error("sr_reserve_from_state: producer_state must be 8-byte aligned device memory for two 64-bit words");
+  if (rng_state == nullptr || (reinterpret_cast<uintptr_t>(rng_state) & 7))
+    return set_error("sr_reserve_from_state: rng_state must be 8-byte aligned device memory for two 64-bit words");
+  if (launches == 0) return set_error("sr_reserve_from_state: the number of launches to reserve must be positive");
+  sr_reserve_from_state_kernel<<<1, 1, 0, (cudaStream_t)stream>>>(reinterpret_cast<unsigned long long*>(producer_state),
+                                                                 reinterpret_cast<unsigned long long*>(rng_state), launches);
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
 }

@@ -8,6 +8,9 @@ through the C ABI in ``include/fp4b200.h``.  There is no fallback path.
 """
 from __future__ import annotations
 
+import contextlib
+import threading
+
 import torch
 
 from . import _lib
@@ -440,14 +443,42 @@ def tk_set_sr_invocation_count(n: int, device=None) -> None:
                   torch.cuda.current_stream(dev).cuda_stream)
 
 
+_PRODUCER_STATE = threading.local()
+
+
+@contextlib.contextmanager
+def producer_sr_state(state):
+    """Inside the block, the stochastic quantisers of this module called from this thread number their launches from
+    ``state`` — a producer's persistent int64[2] {seed, next subsequence} on its device, e.g. a row of
+    ``localcta_sr_state.LocalCTASRState`` — instead of the device-wide counter: each call takes the pair as its Philox
+    key and base and advances ``state[1]`` by 2**32 per launch it makes, on its own stream; the ``rng_seed`` /
+    ``rng_subsequence`` arguments are ignored.  ``None`` leaves the device-wide numbering in force (the calling
+    convention of get_localcta_sr_state, which returns None without an installed table)."""
+    if state is not None and (not isinstance(state, torch.Tensor) or not state.is_cuda or state.dtype != torch.int64
+                              or state.numel() != 2 or not state.is_contiguous()):
+        raise RuntimeError("producer_sr_state: the state must be a contiguous CUDA int64 tensor with two elements")
+    before = getattr(_PRODUCER_STATE, "state", None)
+    _PRODUCER_STATE.state = state
+    try:
+        yield
+    finally:
+        _PRODUCER_STATE.state = before
+
+
 def _reserve_sr(t, rng_seed, rng_subsequence, use_sr, launches=1):
     """Device words {key, base} for the next ``launches`` stochastic launches on t's device (None without
     stochastic rounding): a one-thread kernel advances the device counter, so a captured graph reserves new
     numbers on every replay (tk_make_advancing_rng_state, tk_quantize.cu:469-481).  Launch k of the group passes
-    the relative offset ``k * 2**32``."""
+    the relative offset ``k * 2**32``.  Under producer_sr_state the numbers come from that producer's own pair."""
     if not use_sr:
         return None
     state = torch.empty(2, dtype=torch.int64, device=t.device)
+    own = getattr(_PRODUCER_STATE, "state", None)
+    if own is not None:
+        if own.device != t.device:
+            raise RuntimeError(f"producer_sr_state: the state is on {own.device}, its producer's input on {t.device}")
+        _lib.call("fp4b200_sr_reserve_from_state", own.data_ptr(), state.data_ptr(), int(launches), _stream(t))
+        return state
     _lib.call("fp4b200_sr_prepare_state", state.data_ptr(), int(rng_seed) & _U64, int(rng_subsequence) & _U64,
               int(launches), _stream(t))
     return state

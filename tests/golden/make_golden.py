@@ -230,11 +230,107 @@ def make_sr_state_golden(root: str):
     print("wrote", dst)
 
 
+def make_localcta_sr_state_golden(root: str):
+    """A scripted life of the reference's LocalCTASRState (low_bits_training/quantization/localcta_sr_state.py) on
+    CPU tensors: rows after a list of advances (the consumer's ``state[1] += 2**32``, done by hand), the checkpoint of
+    the single-rank run, the rows after a v1 migration as rank 0 and rank 1 of two, the enable policy over a list of
+    environments, and the keys discovered on stand-in modules."""
+    import importlib.util
+    import json
+    path = os.path.join(root, "low_bits_training", "quantization", "localcta_sr_state.py")
+    spec = importlib.util.spec_from_file_location("ref_localcta_sr_state", path)
+    ref = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(ref)
+    names = ["layers.3.ffn", "layers.0.attn", "layers.0.ffn"]
+    keys = [ref.ffn_deriv_grad_key(names[0]), ref.qkv_grad_key(names[1]), ref.wo_grad_key(names[1]),
+            ref.ffn_w2_grad_key(names[2])]
+    script = [[0, 1], [1, 2], [1, 1], [3, 1], [2, 3], [0, 1]]   # (index into keys, launches reserved)
+    seed, base = (1 << 64) - 2, 7 << 32
+    out = {"names": names, "keys": keys, "script": script, "seed": seed, "subsequence_base": base, "runs": {}}
+    for label, rank, world in (("single", 0, 1), ("rank1_of_2", 1, 2)):
+        st = ref.LocalCTASRState(keys, device="cpu", user_seed=seed, user_subsequence_base=base, training_steps=10,
+                                 gradient_accumulation_steps=2, rank=rank, world_size=world)
+        run = {"initial_rows": st._local_state_matrix().tolist(), "reservations_per_slot": st.reservations_per_slot,
+               "sorted_keys": list(st.logical_keys)}
+        for i, n in script:
+            st.get(keys[i])[1] += n * ref.SUBSEQUENCE_STRIDE
+        run["rows_after_script"] = st._local_state_matrix().tolist()
+        if world == 1:
+            sd = st.state_dict()
+            run["state_dict"] = {k: (v.tolist() if torch.is_tensor(v) else v) for k, v in sd.items()}
+        out["runs"][label] = run
+    # a v1 table (one per checkpoint, seeds base + slot + 1) taken in by rank 0 and rank 1 of a world of two
+    n = len(keys)
+    v1_seed_base = 1000
+    v1 = {"version": [1], "subsequence_stride": [ref.SUBSEQUENCE_STRIDE], "logical_keys": sorted(keys),
+          "states": [[v1_seed_base + s + 1, (3 + s) << 32] for s in range(n)]}
+    out["v1"] = {"state_dict": v1, "rows": {}}
+    for rank in (0, 1):
+        st = ref.LocalCTASRState(keys, device="cpu", user_seed=seed, user_subsequence_base=base, training_steps=10,
+                                 gradient_accumulation_steps=2, rank=rank, world_size=2)
+        st.migrate_from_v1_state_dict({"version": torch.tensor(v1["version"]), "logical_keys": v1["logical_keys"],
+                                       "subsequence_stride": torch.tensor(v1["subsequence_stride"]),
+                                       "states": torch.tensor(v1["states"], dtype=torch.int64)})
+        out["v1"]["rows"][str(rank)] = st._local_state_matrix().tolist()
+    # enable policy
+    names_env = ["USE_TK_LOCALCTA", "USE_TK_LOCALCTA_VARIANT", "NVFP4_USE_STOCHASTIC_ROUNDING", "NVFP4_SR_GRAD",
+                 "NVFP4_GRAD_SR_AXES", "NVFP4_USE_SCALE_STOCHASTIC_ROUNDING", "NVFP4_SCALE_SR_GRAD", "NVFP4_SR_ACTIVATION",
+                 "NVFP4_SCALE_SR_ACTIVATION"]
+    envs = [{}, {"USE_TK_LOCALCTA": "1"}, {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "V4"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_USE_STOCHASTIC_ROUNDING": "1"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_USE_STOCHASTIC_ROUNDING": "1",
+             "NVFP4_GRAD_SR_AXES": "none"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_USE_STOCHASTIC_ROUNDING": "1",
+             "NVFP4_SR_GRAD": "0"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_SR_GRAD": "true", "NVFP4_GRAD_SR_AXES": "col"},
+            {"USE_TK_LOCALCTA": "yes", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_USE_SCALE_STOCHASTIC_ROUNDING": "1"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_USE_SCALE_STOCHASTIC_ROUNDING": "1",
+             "NVFP4_SR_GRAD": "0"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_USE_SCALE_STOCHASTIC_ROUNDING": "1",
+             "NVFP4_SR_GRAD": "1", "NVFP4_GRAD_SR_AXES": "off"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_SCALE_SR_GRAD": "1"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_SCALE_SR_GRAD": "off",
+             "NVFP4_USE_SCALE_STOCHASTIC_ROUNDING": "1"},
+            {"USE_TK_LOCALCTA": "off", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_SR_GRAD": "1"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_SR_ACTIVATION": "1"},
+            {"USE_TK_LOCALCTA": "1", "USE_TK_LOCALCTA_VARIANT": "v4", "NVFP4_SCALE_SR_ACTIVATION": "1", "NVFP4_SR_GRAD": "1"}]
+    saved = {k: os.environ.pop(k, None) for k in names_env}
+    policy = []
+    try:
+        for env in envs:
+            for k in names_env:
+                os.environ.pop(k, None)
+            os.environ.update(env)
+            policy.append({"env": env, "grad_sr": ref.localcta_v4_grad_sr_enabled(),
+                           "role": {r: [ref._role_sr_enabled(r), ref._role_scale_sr_enabled(r)]
+                                    for r in ("grad", "activation", "weight")}})
+    finally:
+        for k in names_env:
+            os.environ.pop(k, None)
+        os.environ.update({k: v for k, v in saved.items() if v is not None})
+    out["policy"] = policy
+    # discovery on stand-ins that carry the reference's class names
+    def stand_in(kind, name):
+        m = type(kind, (torch.nn.Module,), {})()
+        m._lbt_debug_name = name
+        return m
+    root_mod = torch.nn.Module()
+    root_mod.a = stand_in("FusedAttentionFP4_TK", "layers.0.attention")
+    root_mod.b = stand_in("FusedFeedForwardFP4_TK", "layers.0.feed_forward")
+    root_mod.c = stand_in("FusedSquaredReLUFeedForwardFP4_TK", "layers.1.feed_forward")
+    root_mod.d = torch.nn.Linear(2, 2)
+    out["discovered"] = list(ref.discover_logical_keys([root_mod]))
+    dst = os.path.join(HERE, "localcta_sr_state_reference_golden.json")
+    with open(dst, "w") as f:
+        json.dump(out, f, indent=1)
+    print("wrote", dst)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the mfu-fp4-training checkout")
     ap.add_argument("--which", default="all", choices=["all", "nvfp4", "rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm",
-                                                     "sr_state"])
+                                                     "sr_state", "localcta_sr_state"])
     args = ap.parse_args()
     if args.which in ("all", "rmsnorm_bwd"):
         make_rmsnorm_bwd_golden(args.reference)
@@ -248,7 +344,10 @@ def main():
         make_rht_and_norm_golden(args.reference)
     if args.which in ("all", "sr_state"):
         make_sr_state_golden(args.reference)
-    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm", "sr_state"):
+    if args.which in ("all", "localcta_sr_state"):
+        make_localcta_sr_state_golden(args.reference)
+    if args.which in ("rmsnorm_bwd", "scale_swizzle", "mxfp4", "tk_gemm_quantize", "rht_and_norm", "sr_state",
+                      "localcta_sr_state"):
         return
     mods = load_reference(args.reference)
     qn, utils, quantization = mods["quantization_nvfp4"], mods["utils"], mods["quantization"]

@@ -148,6 +148,72 @@ def test_captured_stochastic_rounding_draws_anew_on_every_replay():
     assert_status_ok()
 
 
+def test_a_producers_own_counter_feeds_the_quantiser_and_advances_in_captured_replays():
+    """producer_sr_state: the stochastic quantisers take key and base from a producer's persistent {seed, next
+    subsequence} row (a LocalCTASRState table on the device) and advance the row by 2**32 per launch on their own
+    stream; the device-wide counter is not touched.  The bytes are those of the explicit call with that seed and
+    subsequence at launch number 0.  Captured, every replay advances the live row; what warm-up and capture reserved
+    is rolled back by preserve_during_cuda_graph_capture."""
+    tkq, srs = mod("tk_quant_v5"), mod("localcta_sr_state")
+    keys = [srs.ffn_w2_grad_key("layers.0.ffn"), srs.qkv_grad_key("layers.0.attn:qkv")]
+    table = srs.LocalCTASRState(keys, device="cuda", user_seed=(1 << 64) - 2, user_subsequence_base=9 << 32,
+                                training_steps=4, gradient_accumulation_steps=1)
+    x = (1e-3 * torch.randn(256, 256, device="cuda")).to(torch.bfloat16)
+    U64 = (1 << 64) - 1
+
+    def call(seed=0, sub=0):
+        return tkq.tk_quantize_for_gemm_opt(x, True, False, True, False, "none", False, seed, sub, 448.0, "both")
+
+    def explicit(row):
+        tkq.tk_set_sr_invocation_count(0)
+        return [t.view(torch.uint8).clone() for t in call(int(row[0]) & U64, int(row[1]) & U64)[:4]]
+
+    tkq.tk_set_sr_invocation_count(11)
+    row = table.get(keys[1], x.device)
+    other = table.get(keys[0]).clone()
+    before = row.clone()
+    with tkq.producer_sr_state(row):
+        got = [t.view(torch.uint8).clone() for t in call(123, 456)]     # seed / subsequence arguments are ignored
+        launches = (int(row[1]) - int(before[1])) >> 32
+        assert launches >= 1 and int(row[0]) == int(before[0])
+        with tkq.producer_sr_state(None):                               # None: the device-wide numbering again
+            call()
+    assert tkq.tk_sr_invocation_count() == 11 + launches                # only the inner, unbound call counted there
+    assert torch.equal(table.get(keys[0]), other)
+    for a, b in zip(got, explicit(before)):
+        assert torch.equal(a, b)
+    with pytest.raises(RuntimeError, match="contiguous CUDA int64 tensor with two elements"):
+        with tkq.producer_sr_state(torch.zeros(2, dtype=torch.int64)):
+            pass
+
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    g = torch.cuda.CUDAGraph()
+    start = row.clone()
+    with table.preserve_during_cuda_graph_capture([keys[1]]):
+        with torch.cuda.stream(side), tkq.producer_sr_state(row):
+            call()                                                       # warm-up on the capture stream
+        side.synchronize()
+        with torch.cuda.graph(g, stream=side), tkq.producer_sr_state(row):
+            out = call()
+    assert torch.equal(row, start)                                       # warm-up and capture left no trace
+    replays = []
+    for _ in range(2):
+        g.replay()
+        torch.cuda.synchronize()
+        replays.append([t.view(torch.uint8).clone() for t in out[:4]])
+    assert (int(row[1]) - int(start[1])) >> 32 == 2 * launches
+    assert not torch.equal(replays[0][0], replays[1][0])
+    for k in range(2):
+        at = start.clone()
+        at[1] += k * launches * (1 << 32)
+        for a, b in zip(replays[k], explicit(at)):
+            assert torch.equal(a, b)
+    sd = table.state_dict()
+    assert sd["states"][0, table.logical_keys.index(keys[1])].tolist() == row.tolist()
+    assert_status_ok()
+
+
 def test_split2_opt_pair_captures_and_equals_its_parts():
     """tk_silu_deriv_quantize_split_for_gemm_opt_alloc / _launch: buffers once, launch captured, replayed on new data.
     Each of dh1 / dh3 equals the single-launch quantiser (row operand transformed, both passes one random stream) on
