@@ -477,14 +477,13 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks, iters=10):
         q = st["qdy"]; gemm.nvfp4_gemm(q[0], q[1], q[4], q2[2], q2[3], q2[4], dh)
     def s_w2_wgrad():     # dW2 [K,H] = dY^T . h : transformed column operands of both, contraction over M
         q, f = st["qdy"], fw["h"]; gemm.nvfp4_gemm(q[2], q[3], q[5], f[2], f[3], f[5], dw2)
-    def s_silu_deriv():
-        st["qd"] = tkq.tk_silu_deriv_quantize_split_for_gemm(dh, h3, h1)
-    def s_wgrad_operands():
-        d = st["qd"]
-        st["g1"], st["g3"] = grad_operands(d[14]), grad_operands(d[15])
+    def s_silu_deriv():   # dh1 = dh * h3 * silu'(h1), dh3 = dh * silu(h1), both bf16 (the activations' backward)
+        st["dh13"] = tkq.tk_silu_deriv_split_bf16(dh, h3, h1)
+    def s_dh_operands():  # each gradient quantised once: row operand for the dgrad, transformed SR column operand for the wgrad
+        st["g1"], st["g3"] = grad_operands(st["dh13"][0]), grad_operands(st["dh13"][1])
     def s_w13_dgrad():    # dx [M,K] = dh1 . W1 + dh3 . W3, fp32 running sum, one rounding
-        d = st["qd"]
-        gemm.nvfp4_batched_accum_gemm([d[0], d[6]], [d[1], d[7]], [d[4], d[10]], [q1[2], q3[2]], [q1[3], q3[3]],
+        a, b = st["g1"], st["g3"]
+        gemm.nvfp4_batched_accum_gemm([a[0], b[0]], [a[1], b[1]], [a[4], b[4]], [q1[2], q3[2]], [q1[3], q3[3]],
                                       [q1[4], q3[4]], dx)
     def s_w13_wgrad():    # dW1 [H,K] = dh1^T . x, dW3 likewise
         f = fw["x"]
@@ -494,9 +493,9 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks, iters=10):
     dgamma = torch.empty(K, dtype=torch.float32, device=dev)
     def s_rmsnorm_bwd():  # dx_in = RMSNorm backward of dx + the residual stream's gradient (dY), dgamma through row tiles
         gemm.rmsnorm_bwd_residual_out(dx, x_dev, gamma, inv_rms, dy, dx_in, dgamma)
-    names = ["quant_dy_rht_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_quant", "dh_wgrad_operands_rht_sr",
+    names = ["quant_dy_rht_sr", "w2_dgrad_gemm", "w2_wgrad_gemm", "silu_deriv_split_bf16", "dh_operands_rht_sr",
              "w13_dgrad_gemms", "w13_wgrad_gemms", "rmsnorm_bwd_residual"]
-    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_wgrad_operands, s_w13_dgrad,
+    ms, total = _timed_stages(torch, [s_quant_dy, s_w2_dgrad, s_w2_wgrad, s_silu_deriv, s_dh_operands, s_w13_dgrad,
                                       s_w13_wgrad, s_rmsnorm_bwd], iters=iters)
     # the attention side's form of the last step: three dgrad streams summed first (12 B per element)
     d_sum = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
@@ -521,7 +520,8 @@ def ffn_backward_leg(torch, dist, world, x_dev, gamma, peaks, iters=10):
             "all_gemms_tflops": sum(fl.values()) * world / (gemm_ms * 1e-3) / 1e12,
             "step_tflops": sum(fl.values()) * world / (total * 1e-3) / 1e12,
             "quant_dy_gbs": M * K * 3.125 * world / (ms[0] * 1e-3) / 1e9,
-            "silu_deriv_quant_gbs": M * H * 8.25 * world / (ms[3] * 1e-3) / 1e9,
+            "silu_deriv_split_gbs": M * H * 10.0 * world / (ms[3] * 1e-3) / 1e9,
+            "dh_operands_gbs": 2 * M * H * 3.125 * world / (ms[4] * 1e-3) / 1e9,
             "rmsnorm_bwd_residual_gbs": M * K * 8.0 * world / (ms[7] * 1e-3) / 1e9,
             "sum3_rmsnorm_bwd": {"ms": sum3_ms, "gbs": M * K * 12.0 / (sum3_ms * 1e-3) / 1e9,
                                  "frac_of_measured_hbm": M * K * 12.0 / (sum3_ms * 1e-3) / 1e9 / peaks["hbm_gbs"]},

@@ -314,6 +314,22 @@ int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, co
 int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
                                      void* col_fp4, void* col_sc, void* stream);
 
+/* One-pass MXFP4 SwiGLU producers: the activation is computed on the chunk in shared memory and only codes and
+ * scales are written (no tensor-level scale exists, so nothing has to be known about the whole tensor first).
+ * fp4b200_mxfp4_silu_mul_quantize: operands of bf16(silu(h1_raw) * h3)
+ * (mxfp4_fused_silu_mul_quantize_row_and_col[_launch_inplace], mxfp4_v4/tk_quantize.cu:3231-3310).
+ * fp4b200_mxfp4_silu_deriv_quantize_split2: operands of dh1 = bf16(dh * h3 * silu'(h1_raw)) and dh3 =
+ * bf16(dh * silu(h1_raw)), dh3's stacked behind dh1's in every output array: row_fp4 [2, M, H/2], row_sc
+ * [2, M/128, H/128, 512], col_fp4 [2, H, M/2], col_sc [2, H/128, M/128, 512]
+ * (mxfp4_fused_silu_deriv_quantize_split2_row_and_col[_launch_inplace], mxfp4_v4/tk_quantize.cu:4513-4700).
+ * Same bytes as the element kernels (fp4b200_silu_mul_bf16 / fp4b200_silu_deriv_bf16) followed by
+ * fp4b200_mxfp4_quantize.  M % 128 == 0, H % 128 == 0, 16-byte aligned inputs; all outputs required. */
+int fp4b200_mxfp4_silu_mul_quantize(const void* h1_raw, const void* h3, int64_t M, int64_t H, int mode, void* row_fp4,
+                                    void* row_sc, void* col_fp4, void* col_sc, void* stream);
+int fp4b200_mxfp4_silu_deriv_quantize_split2(const void* dh, const void* h3, const void* h1_raw, int64_t M, int64_t H,
+                                             int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                             void* stream);
+
 /* mxfp4_quantize_for_gemm_opt(input, mode, data_stochastic_rounding, scale_stochastic_rounding, rng_seed,
  * rng_subsequence) (mxfp4_v4/tk_quantize.cu:1796-1881; kernel mxfp4_v3_fused_kernel_opt / mx_rowwise_quantize_opt,
  * mxfp4_v3_quantize.cuh:1618-1790, 5270-5345): row operand only.  data_sr rounds the codes stochastically

@@ -11,6 +11,7 @@
 // CTAs, 128x128 chunks as two 128-byte-swizzled TMA boxes, three stages.
 #include "fp4_common.cuh"
 #include "host_util.h"
+#include "swiglu_math.cuh"
 
 namespace fp4b200 {
 
@@ -249,6 +250,235 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
         const int c = idx >> 2, g = idx & 3;
         st_cs_u4(a.col_fp4 + (size_t)(k0 + c) * (a.M >> 1) + (m0 >> 1) + g * 16, sm.col_codes[g][c]);
       }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// One-pass SwiGLU producers: the activation is computed on the chunk in shared memory
+// ---------------------------------------------------------------------------------------
+//
+// MXFP4 has no tensor-level scale, so bf16(silu(h1) * h3) (ACT 1) or the pair dh1 = bf16(dh * h3 * silu'(h1)),
+// dh3 = bf16(dh * silu(h1)) (ACT 2) never has to exist in HBM: the inputs' chunks arrive by TMA, the row pass
+// computes the product(s) on its way through the chunk (the thread that quantises a 32-element row block computes
+// it, and writes the bf16 values back IN PLACE for the column pass), and only codes and scales are written:
+// 5.06 instead of 9.06 bytes per element (ACT 1), 8.1 instead of 16.1 (ACT 2).  As the reference's fused producers
+// (mxfp4_v4/tk_quantize.cu:3231-3310, 4513-4700), which keep the product in shared memory too.  Geometry of the
+// passes as in mxfp4_quantize_kernel; three chunk buffers per CTA, two CTAs per SM:
+//   ACT 1: h1 of chunk i alternates between buffers 0 / 1 and becomes h; h3 always sits in buffer 2, which is free
+//          again after the row pass (h3 of chunk i+1 is then requested) while h1 of chunk i+1 was requested a chunk
+//          earlier;
+//   ACT 2: dh -> buffer 0 (becomes dh1), h3 -> buffer 1 (becomes dh3), h1 -> buffer 2; each buffer is refilled for the
+//          next chunk as soon as its last reader is past it (the other CTA of the SM covers the rest of the latency).
+struct MxActSmem {
+  alignas(1024) uint8_t buf[3][kMxTileBytes];
+  alignas(16) uint4 col_codes[4][kMxChunk];
+  alignas(16) uint8_t row_sc[2][2][512];   // [output][parity of the chunk]
+  alignas(16) uint8_t col_sc[512];
+  alignas(8) uint64_t full[3];
+};
+
+struct MxActArgs {
+  uint8_t* row_fp4[2];   // [M, H/2] per output (ACT 1: one output)
+  uint8_t* row_sc[2];    // [M/128, H/128, 512]
+  uint8_t* col_fp4[2];   // [H, M/2]
+  uint8_t* col_sc[2];    // [H/128, M/128, 512]
+  int* status;
+  int M, K, chunks_m, chunks_k;
+  int mode;
+};
+
+// one 32-element row block held as sixteen bf16x2 words: scale byte and 16 bytes of codes
+__device__ __forceinline__ uint4 mx_row_block(const uint32_t (&w)[16], int mode, uint32_t& e) {
+  uint32_t mx = 0;
+#pragma unroll
+  for (int q = 0; q < 16; ++q) mx = absmax_xs(mx, w[q]);
+  const float b = fmaxf(fabsf(bf16lo_to_f32(mx)), fabsf(bf16hi_to_f32(mx)));
+  e = mx_e8m0(b, mode);
+  const float coeff = mx_coeff(e);
+  uint4 codes;
+  codes.x = quant8(w, coeff); codes.y = quant8(w + 4, coeff);
+  codes.z = quant8(w + 8, coeff); codes.w = quant8(w + 12, coeff);
+  return codes;
+}
+
+// column pass of one warp over its 32 rows x 64 columns of a chunk (lane = two adjacent columns)
+__device__ __forceinline__ void mx_col_pass(const uint8_t* tile, int grp, int chalf, int lane, const int (&col_off)[8],
+                                            int mode, uint4 (*col_codes)[kMxChunk], uint8_t* col_sc) {
+  const uint8_t* base = tile + chalf * kMxHalfBytes + (grp * 32) * 128;
+  uint32_t w[32];
+  uint32_t mx = 0;
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    w[i] = *reinterpret_cast<const uint32_t*>(base + i * 128 + col_off[i & 7]);
+    mx = absmax_xs(mx, w[i]);
+  }
+  const uint32_t e0 = mx_e8m0(fabsf(bf16lo_to_f32(mx)), mode), e1 = mx_e8m0(fabsf(bf16hi_to_f32(mx)), mode);
+  const float2 cc = make_float2(mx_coeff(e0), mx_coeff(e1));
+  uint32_t q0[4], q1[4];
+#pragma unroll
+  for (int p = 0; p < 4; ++p) {
+    float2 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      v[i] = mul2(make_float2(bf16lo_to_f32(w[8 * p + i]), bf16hi_to_f32(w[8 * p + i])), cc);
+    q0[p] = f32x8_to_e2m1x8(v[0].x, v[1].x, v[2].x, v[3].x, v[4].x, v[5].x, v[6].x, v[7].x);
+    q1[p] = f32x8_to_e2m1x8(v[0].y, v[1].y, v[2].y, v[3].y, v[4].y, v[5].y, v[6].y, v[7].y);
+  }
+  const int c = 2 * lane + 64 * chalf;
+  col_codes[grp][c] = make_uint4(q0[0], q0[1], q0[2], q0[3]);
+  col_codes[grp][c + 1] = make_uint4(q1[0], q1[1], q1[2], q1[3]);
+  col_sc[scale_tile_offset(c, grp)] = (uint8_t)e0;
+  col_sc[scale_tile_offset(c + 1, grp)] = (uint8_t)e1;
+}
+
+template <int ACT>
+__global__ void __launch_bounds__(kMxThreads, 2)
+mxfp4_act_quantize_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                          const __grid_constant__ CUtensorMap tmap_c, const MxActArgs a) {
+  static_assert(ACT == 1 || ACT == 2, "ACT 1: silu(h1) * h3 from (a = h1, b = h3); ACT 2: dh1, dh3 from (a = dh, b = h3, c = h1)");
+  constexpr int kOut = ACT;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  MxActSmem& sm = *reinterpret_cast<MxActSmem*>(smem_align_1024(smem_raw));
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int n_chunks = a.chunks_m * a.chunks_k;
+  const int first = blockIdx.x, step = gridDim.x;
+  const int my_count = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
+  auto chunk_coords = [&](int it, int& cm, int& ck) {
+    const int c = first + it * step;
+    cm = c / a.chunks_k;
+    ck = c - cm * a.chunks_k;
+  };
+  auto issue_load = [&](int it, int b, const CUtensorMap* map) {
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    mbar_expect_tx(&sm.full[b], kMxTileBytes);
+    tma_load_2d(sm.buf[b], map, ck * kMxChunk, cm * kMxChunk, &sm.full[b]);
+    tma_load_2d(sm.buf[b] + kMxHalfBytes, map, ck * kMxChunk + 64, cm * kMxChunk, &sm.full[b]);
+  };
+  if (tid == 0) {
+    tma_prefetch_desc(&tmap_a);
+    tma_prefetch_desc(&tmap_b);
+    if (ACT == 2) tma_prefetch_desc(&tmap_c);
+    for (int b = 0; b < 3; ++b) mbar_init(&sm.full[b], 1);
+    fence_mbar_init();
+  }
+  __syncthreads();
+  if (tid == 0 && my_count > 0) {
+    if (ACT == 1) {
+      issue_load(0, 0, &tmap_a);
+      issue_load(0, 2, &tmap_b);
+      if (my_count > 1) issue_load(1, 1, &tmap_a);
+    } else {
+      issue_load(0, 0, &tmap_a);
+      issue_load(0, 1, &tmap_b);
+      issue_load(0, 2, &tmap_c);
+    }
+  }
+  const int unit = lane >> 3, r_lo = lane & 7;
+  const int half_off = (unit >> 1) * kMxHalfBytes, cb = (unit & 1) * 4;
+  int row_off[4];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) row_off[j] = ((cb + j) ^ r_lo) << 4;
+  int col_off[8];
+#pragma unroll
+  for (int j = 0; j < 8; ++j) col_off[j] = (((lane >> 2) ^ j) << 4) + (lane & 3) * 4;
+  const int grp = warp >> 1, chalf = warp & 1;
+  uint32_t phase[3] = {0, 0, 0};
+
+  // scale tiles and column codes of one output, from shared memory to their places
+  auto store_col = [&](int o, int cm, int ck, int m0, int k0) {
+    if (tid >= 128) {
+      uint8_t* dst = a.col_sc[o] + ((size_t)ck * a.chunks_m + cm) * 512;
+      const int t = tid - 128;
+      st_cs_u32(dst + t * 4, *reinterpret_cast<const uint32_t*>(&sm.col_sc[t * 4]));
+    }
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      const int idx = rep * kMxThreads + tid;
+      const int c = idx >> 2, g = idx & 3;
+      st_cs_u4(a.col_fp4[o] + (size_t)(k0 + c) * (a.M >> 1) + (m0 >> 1) + g * 16, sm.col_codes[g][c]);
+    }
+  };
+
+  for (int it = 0; it < my_count; ++it) {
+    int cm, ck;
+    chunk_coords(it, cm, ck);
+    const int m0 = cm * kMxChunk, k0 = ck * kMxChunk, pp = it & 1;
+    const int bx = ACT == 1 ? (it & 1) : 0;       // buffer whose contents become the (first) output
+    const int by = ACT == 1 ? 2 : 1;              // h3; ACT 2: becomes the second output
+    bool ok = mbar_wait_bounded(&sm.full[bx], phase[bx]) && mbar_wait_bounded(&sm.full[by], phase[by]);
+    if (ACT == 2) ok = ok && mbar_wait_bounded(&sm.full[2], phase[2]);
+    if (!ok) {
+      if (tid == 0) atomicExch(a.status, kStatusQuantTmaTimeout);
+      return;
+    }
+    phase[bx] ^= 1; phase[by] ^= 1;
+    if (ACT == 2) phase[2] ^= 1;
+    uint8_t* tx = sm.buf[bx];
+    uint8_t* ty = sm.buf[by];
+    // ---- activation + row pass
+#pragma unroll
+    for (int rep = 0; rep < 2; ++rep) {
+      const int r = warp * 16 + rep * 8 + r_lo;
+      const int ro = half_off + r * 128;
+      uint32_t w0[16], w1[kOut == 2 ? 16 : 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const uint4 va = *reinterpret_cast<const uint4*>(tx + ro + row_off[j]);
+        const uint4 vb = *reinterpret_cast<const uint4*>(ty + ro + row_off[j]);
+        const uint32_t aw[4] = {va.x, va.y, va.z, va.w}, bw[4] = {vb.x, vb.y, vb.z, vb.w};
+        if constexpr (ACT == 1) {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) w0[4 * j + q] = silu_mul_bf16x2(aw[q], bw[q]);
+        } else {
+          const uint4 vc = *reinterpret_cast<const uint4*>(sm.buf[2] + ro + row_off[j]);
+          const uint32_t cw[4] = {vc.x, vc.y, vc.z, vc.w};
+#pragma unroll
+          for (int q = 0; q < 4; ++q) silu_deriv_bf16x2(aw[q], bw[q], cw[q], w0[4 * j + q], w1[4 * j + q]);
+          *reinterpret_cast<uint4*>(ty + ro + row_off[j]) = make_uint4(w1[4 * j], w1[4 * j + 1], w1[4 * j + 2], w1[4 * j + 3]);
+        }
+        *reinterpret_cast<uint4*>(tx + ro + row_off[j]) = make_uint4(w0[4 * j], w0[4 * j + 1], w0[4 * j + 2], w0[4 * j + 3]);
+      }
+      uint32_t e;
+      const size_t at = (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1);
+      st_cs_u4(a.row_fp4[0] + at, mx_row_block(w0, a.mode, e));
+      sm.row_sc[0][pp][scale_tile_offset(r, unit)] = (uint8_t)e;
+      if constexpr (ACT == 2) {
+        st_cs_u4(a.row_fp4[1] + at, mx_row_block(w1, a.mode, e));
+        sm.row_sc[1][pp][scale_tile_offset(r, unit)] = (uint8_t)e;
+      }
+    }
+    __syncthreads();
+    if (tid == 0 && it + 1 < my_count) {
+      fence_proxy_async_smem();
+      if (ACT == 1) issue_load(it + 1, 2, &tmap_b);    // h3 is consumed
+      else issue_load(it + 1, 2, &tmap_c);             // h1 is consumed
+    }
+    if (tid < 128) {
+#pragma unroll
+      for (int o = 0; o < kOut; ++o)
+        st_cs_u32(a.row_sc[o] + ((size_t)cm * a.chunks_k + ck) * 512 + tid * 4,
+                  *reinterpret_cast<const uint32_t*>(&sm.row_sc[o][pp][tid * 4]));
+    }
+    // ---- column pass(es)
+    mx_col_pass(tx, grp, chalf, lane, col_off, a.mode, sm.col_codes, sm.col_sc);
+    __syncthreads();
+    if (tid == 0) {
+      fence_proxy_async_smem();
+      if (ACT == 1) { if (it + 2 < my_count) issue_load(it + 2, bx, &tmap_a); }
+      else if (it + 1 < my_count) issue_load(it + 1, 0, &tmap_a);
+    }
+    store_col(0, cm, ck, m0, k0);
+    if constexpr (ACT == 2) {
+      __syncthreads();   // the first output's column codes have left shared memory
+      mx_col_pass(ty, grp, chalf, lane, col_off, a.mode, sm.col_codes, sm.col_sc);
+      __syncthreads();
+      if (tid == 0 && it + 1 < my_count) {
+        fence_proxy_async_smem();
+        issue_load(it + 1, 1, &tmap_b);
+      }
+      store_col(1, cm, ck, m0, k0);
     }
   }
 }
@@ -600,6 +830,37 @@ static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float*
   return 0;
 }
 
+static int launch_mx_act(int act, const void* in_a, const void* in_b, const void* in_c, int64_t M, int64_t K, int mode,
+                         uint8_t* row_fp4, uint8_t* row_sc, uint8_t* col_fp4, uint8_t* col_sc, cudaStream_t st) {
+  CUtensorMap tm[3];
+  const void* src[3] = {in_a, in_b, act == 2 ? in_c : in_a};
+  for (int i = 0; i < 3; ++i)
+    if (int rc = make_tmap_2d(&tm[i], src[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
+                              (uint64_t)K * 2, 64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  MxActArgs a{};
+  const size_t codes = (size_t)M * K / 2, scales = (size_t)(M / 128) * (K / 128) * 512;
+  for (int o = 0; o < 2; ++o) {   // the second output (ACT 2) is stacked behind the first in every array
+    a.row_fp4[o] = row_fp4 + o * codes; a.row_sc[o] = row_sc + o * scales;
+    a.col_fp4[o] = col_fp4 + o * codes; a.col_sc[o] = col_sc + o * scales;
+  }
+  a.status = device_status_ptr();
+  if (!a.status) return -1;
+  a.M = (int)M; a.K = (int)K; a.chunks_m = (int)(M / kMxChunk); a.chunks_k = (int)(K / kMxChunk); a.mode = mode;
+  const int smem = (int)sizeof(MxActSmem) + 1024;
+  const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
+  if (grid == 0) return 0;
+  if (act == 1) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_act_quantize_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_act_quantize_kernel<1><<<grid, kMxThreads, smem, st>>>(tm[0], tm[1], tm[2], a);
+  } else {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_act_quantize_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_act_quantize_kernel<2><<<grid, kMxThreads, smem, st>>>(tm[0], tm[1], tm[2], a);
+  }
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace fp4b200
 
 using namespace fp4b200;
@@ -640,6 +901,27 @@ int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, v
   if (int rc = check_mx(w_bf16, N, K, 1, "mxfp4_quantize_weight_2d")) return rc;
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_quantize_weight_2d: all outputs are required");
   return launch_mx(w_bf16, N, K, 1, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, true);
+}
+
+int fp4b200_mxfp4_silu_mul_quantize(const void* h1_raw, const void* h3, int64_t M, int64_t H, int mode, void* row_fp4,
+                                    void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  if (int rc = check_mx(h1_raw, M, H, mode, "mxfp4_silu_mul_quantize")) return rc;
+  if (int rc = check_mx(h3, M, H, mode, "mxfp4_silu_mul_quantize")) return rc;
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_silu_mul_quantize: all outputs are required");
+  return launch_mx_act(1, h1_raw, h3, nullptr, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4,
+                       (uint8_t*)col_sc, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_silu_deriv_quantize_split2(const void* dh, const void* h3, const void* h1_raw, int64_t M, int64_t H,
+                                             int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
+                                             void* stream) {
+  if (int rc = check_mx(dh, M, H, mode, "mxfp4_silu_deriv_quantize_split2")) return rc;
+  if (int rc = check_mx(h3, M, H, mode, "mxfp4_silu_deriv_quantize_split2")) return rc;
+  if (int rc = check_mx(h1_raw, M, H, mode, "mxfp4_silu_deriv_quantize_split2")) return rc;
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc)
+    return set_error("mxfp4_silu_deriv_quantize_split2: all outputs are required");
+  return launch_mx_act(2, dh, h3, h1_raw, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4,
+                       (uint8_t*)col_sc, (cudaStream_t)stream);
 }
 
 static int check_mx_rht(int rht_block, const char* who) {

@@ -8,10 +8,9 @@
 // evaluated left to right in fp32 and rounded to bf16 once, as in the reference kernels.
 #include "fp4_common.cuh"
 #include "host_util.h"
+#include "swiglu_math.cuh"
 
 namespace fp4b200 {
-
-__device__ __forceinline__ float silu_f(float x) { return x / (1.0f + __expf(-x)); }
 
 __device__ __forceinline__ void block_amax_commit(float v, float* amax) {
   v = warp_max(v);
@@ -46,9 +45,7 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
       uint32_t o[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        const float lo = silu_f(bf16lo_to_f32(aw[q])) * bf16lo_to_f32(bw[q]);
-        const float hi = silu_f(bf16hi_to_f32(aw[q])) * bf16hi_to_f32(bw[q]);
-        o[q] = f32x2_to_bf16x2(lo, hi);
+        o[q] = silu_mul_bf16x2(aw[q], bw[q]);
         mx = bf16x2_absmax(mx, o[q]);
       }
       out[i] = make_uint4(o[0], o[1], o[2], o[3]);
@@ -82,20 +79,7 @@ silu_deriv_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ h3, co
       uint32_t o1[4], o3[4];
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        float c[2], e[2];
-#pragma unroll
-        for (int k = 0; k < 2; ++k) {
-          const float df = k ? bf16hi_to_f32(dw[q]) : bf16lo_to_f32(dw[q]);
-          const float af = k ? bf16hi_to_f32(aw[q]) : bf16lo_to_f32(aw[q]);
-          const float x = k ? bf16hi_to_f32(bw[q]) : bf16lo_to_f32(bw[q]);
-          const float sig = 1.0f / (1.0f + __expf(-x));
-          const float sl = x * sig;
-          const float slp = sig * (1.0f + x - sl);
-          c[k] = df * af * slp;
-          e[k] = df * sl;
-        }
-        o1[q] = f32x2_to_bf16x2(c[0], c[1]);
-        o3[q] = f32x2_to_bf16x2(e[0], e[1]);
+        silu_deriv_bf16x2(dw[q], aw[q], bw[q], o1[q], o3[q]);
         mx1 = bf16x2_absmax(mx1, o1[q]);
         mx3 = bf16x2_absmax(mx3, o3[q]);
       }

@@ -7,12 +7,20 @@ fp4_runtime/TK_quantisation/mxfp4_v4/tk_quantize.cu:7281-7724: codes ``[rows, co
 """
 from __future__ import annotations
 
+import os
+
 import torch
 
 from . import _lib
 from .tk_quant_v5 import _check_bf16_2d, _same_shape_bf16, _stream
 
 _FP4 = torch.float4_e2m1fn_x2
+
+
+def _one_pass_act():
+    """FP4B200_MX_ONE_PASS=0 routes the SwiGLU producers through the element kernel and a bf16 intermediate again
+    (A/B runs; the bytes are the same)."""
+    return os.environ.get("FP4B200_MX_ONE_PASS", "1") != "0"
 
 
 def _alloc(M, K, device, want_col):
@@ -172,6 +180,11 @@ def mxfp4_fused_silu_mul_quantize_row_and_col(h1_raw, h3, mode=0):
     M, H = _check_bf16_2d(h1_raw, "h1_raw")
     _same_shape_bf16(h1_raw, h3)
     with torch.cuda.device(h1_raw.device):
+        if _one_pass_act():
+            rf, rs, cf, cs = _alloc(M, H, h1_raw.device, True)
+            _lib.call("fp4b200_mxfp4_silu_mul_quantize", h1_raw.data_ptr(), h3.data_ptr(), M, H, int(mode), rf.data_ptr(),
+                      rs.data_ptr(), cf.data_ptr(), cs.data_ptr(), _stream(h1_raw))
+            return rf.view(_FP4), rs, cf.view(_FP4), cs
         h = torch.empty_like(h1_raw)
         amax_sg = torch.empty(2, dtype=torch.float32, device=h1_raw.device)
         _lib.call("fp4b200_silu_mul_bf16", h1_raw.data_ptr(), h3.data_ptr(), h1_raw.numel(), h.data_ptr(),
@@ -226,6 +239,11 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
     row_sc = torch.empty((2, M // 128, H // 128, 32, 16), **u8)
     col_fp4 = torch.empty((2, H, M // 2), **u8)
     col_sc = torch.empty((2, H // 128, M // 128, 32, 16), **u8)
+    if _one_pass_act():
+        with torch.cuda.device(dh.device):
+            _lib.call("fp4b200_mxfp4_silu_deriv_quantize_split2", dh.data_ptr(), h3.data_ptr(), h1_raw.data_ptr(), M, H,
+                      int(mode), row_fp4.data_ptr(), row_sc.data_ptr(), col_fp4.data_ptr(), col_sc.data_ptr(), _stream(dh))
+        return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
     dh1, dh3 = tk_silu_deriv_split_bf16(dh, h3, h1_raw)
     with torch.cuda.device(dh.device):
         for i, t in enumerate((dh1, dh3)):
@@ -262,11 +280,15 @@ def mxfp4_quantize_row_and_col_launch_inplace(input, row_fp4, row_sc, col_fp4, c
 
 def mxfp4_fused_silu_mul_quantize_row_and_col_launch_inplace(h1_raw, h3, row_fp4, row_sc, col_fp4, col_sc, mode=0):
     """tk_quantize.cu:3231-3310 — operands of ``bf16(silu(h1_raw) * h3)`` into the caller's tensors; returns None.
-    The product itself is a temporary from torch's allocator (the reference keeps it in shared memory)."""
+    One pass: the product lives in shared memory only, as in the reference."""
     M, H = _check_bf16_2d(h1_raw, "h1_raw")
     _same_shape_bf16(h1_raw, h3)
     _check_operand_outs(row_fp4, row_sc, col_fp4, col_sc, M, H)
     with torch.cuda.device(h1_raw.device):
+        if _one_pass_act():
+            _lib.call("fp4b200_mxfp4_silu_mul_quantize", h1_raw.data_ptr(), h3.data_ptr(), M, H, int(mode),
+                      row_fp4.data_ptr(), row_sc.data_ptr(), col_fp4.data_ptr(), col_sc.data_ptr(), _stream(h1_raw))
+            return
         h = torch.empty_like(h1_raw)
         amax_sg = torch.empty(2, dtype=torch.float32, device=h1_raw.device)
         st = _stream(h1_raw)
@@ -284,6 +306,11 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col_launch_inplace(dh, h3, h1
     M, H = _check_bf16_2d(dh, "dh")
     _same_shape_bf16(dh, h3, h1_raw)
     _check_operand_outs(row_fp4, row_sc, col_fp4, col_sc, M, H, lead=(2,))
+    if _one_pass_act():
+        with torch.cuda.device(dh.device):
+            _lib.call("fp4b200_mxfp4_silu_deriv_quantize_split2", dh.data_ptr(), h3.data_ptr(), h1_raw.data_ptr(), M, H,
+                      int(mode), row_fp4.data_ptr(), row_sc.data_ptr(), col_fp4.data_ptr(), col_sc.data_ptr(), _stream(dh))
+        return
     dh1, dh3 = tk_silu_deriv_split_bf16(dh, h3, h1_raw)
     with torch.cuda.device(dh.device):
         for i, t in enumerate((dh1, dh3)):

@@ -51,6 +51,37 @@ def test_mxfp4_fused_rmsnorm_and_silu():
     assert_status_ok()
 
 
+# (4096, 4096): 1024 chunks over 296 CTAs, so a CTA walks three or four chunks and every buffer of its ring is reused
+@pytest.mark.parametrize("shape", [(128, 128), (256, 384), (384, 1280), (4096, 4096)])
+@pytest.mark.parametrize("mode", [0, 1, 2])
+def test_one_pass_swiglu_producers_equal_element_kernel_plus_quantiser(shape, mode, monkeypatch):
+    """The one-pass producers (activation computed on the chunk in shared memory, no bf16 intermediate in HBM) give
+    the bytes of the oracle's quantiser applied to the element kernels' bf16 outputs, and the bytes of the two-pass
+    route of the same mirrors."""
+    mxq, tkq = mod("mxfp4_quant_v4"), mod("tk_quant_v5")
+    M, H = shape
+    g = torch.Generator(device="cuda").manual_seed(M + H + mode)
+    mk = lambda s: (s * torch.randn(M, H, device="cuda", generator=g)).to(torch.bfloat16)
+    h1, h3, dh = mk(1.5), mk(1.0), mk(1e-3)
+    h1[0, :32] = 0.0                                     # an all-zero block of h and of dh3
+    dh[-1, -32:] = 0.0
+    monkeypatch.setenv("FP4B200_MX_ONE_PASS", "1")
+    fwd = mxq.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, mode)
+    bwd = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, mode)
+    monkeypatch.setenv("FP4B200_MX_ONE_PASS", "0")
+    fwd2 = mxq.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, mode)
+    bwd2 = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, mode)
+    torch.cuda.synchronize()
+    for a, b in zip(fwd + bwd, fwd2 + bwd2):
+        assert a.shape == b.shape and torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    if M * H <= 1 << 20:
+        h = tkq.tk_silu_mul_split_bf16(h1, h3).float().cpu().numpy()
+        _check(fwd, o.mxfp4_quantize_row_and_col(h, mode))
+        for i, t in enumerate(tkq.tk_silu_deriv_split_bf16(dh, h3, h1)):
+            _check([x[i] for x in bwd], o.mxfp4_quantize_row_and_col(t.float().cpu().numpy(), mode))
+    assert_status_ok()
+
+
 # K = 384, 1152: an odd multiple of 128 (half-depth last K stage); N = 384: half-empty last column tile
 @pytest.mark.parametrize("shape", [(128, 256, 256), (256, 512, 1024), (512, 768, 2304), (256, 384, 384), (128, 256, 1152),
                                    (2048, 4096, 640)])
