@@ -245,6 +245,11 @@ int fp4b200_set_pdl_early_reads(int enabled);
  * up, stores status code 6 and returns.  fp4b200_device_status() then reports 6 once and 0 afterwards.  For tests of
  * the failure-reporting path; no copy is in flight and nothing is left waiting. */
 int fp4b200_selftest_bounded_wait(int64_t limit_cycles, void* stream);
+/* Self-test of the SwiGLU producers' division: for every bf16 pattern x with |x| < 64 compares, on the device, the
+ * short sequence they use for x / d and 1 / d (d = 1 + __expf(-x): reciprocal estimate, one Newton step, one corrected
+ * product) with the general IEEE division; mismatches_dev[0], [1] receive the number of patterns that differ (0, 0
+ * on a correct build).  No counterpart in the reference, whose element kernels use the general division. */
+int fp4b200_selftest_silu_division(uint32_t* mismatches_dev, void* stream);
 
 /* Switches that launch attribute for the GEMM calls of the calling thread (1 = on, the default; 0 = ordinary
  * launches) and returns the previous setting: what the reference's *_nopdl entry points select

@@ -58,6 +58,7 @@ SIGNATURES = {
                                         _c_void_p],
     "fp4b200_mxfp4_silu_deriv_quantize_split2": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p, _c_void_p,
                                                  _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_selftest_silu_division": [_c_void_p, _c_void_p],
     "fp4b200_silu_mul_bf16": [_c_void_p, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_silu_quantize": [_c_void_p, _c_void_p, _i64, _i64, _c_void_p, _int, _c_void_p, _c_void_p,
                                     _c_void_p, _c_void_p, _c_void_p, _c_void_p],

@@ -429,13 +429,17 @@ mxfp4_act_quantize_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         const uint4 vb = *reinterpret_cast<const uint4*>(ty + ro + row_off[j]);
         const uint32_t aw[4] = {va.x, va.y, va.z, va.w}, bw[4] = {vb.x, vb.y, vb.z, vb.w};
         if constexpr (ACT == 1) {
+          uint32_t o[4];
+          silu_mul_bf16x8(aw, bw, o);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) w0[4 * j + q] = silu_mul_bf16x2(aw[q], bw[q]);
+          for (int q = 0; q < 4; ++q) w0[4 * j + q] = o[q];
         } else {
           const uint4 vc = *reinterpret_cast<const uint4*>(sm.buf[2] + ro + row_off[j]);
           const uint32_t cw[4] = {vc.x, vc.y, vc.z, vc.w};
+          uint32_t o1[4], o3[4];
+          silu_deriv_bf16x8(aw, bw, cw, o1, o3);
 #pragma unroll
-          for (int q = 0; q < 4; ++q) silu_deriv_bf16x2(aw[q], bw[q], cw[q], w0[4 * j + q], w1[4 * j + q]);
+          for (int q = 0; q < 4; ++q) { w0[4 * j + q] = o1[q]; w1[4 * j + q] = o3[q]; }
           *reinterpret_cast<uint4*>(ty + ro + row_off[j]) = make_uint4(w1[4 * j], w1[4 * j + 1], w1[4 * j + 2], w1[4 * j + 3]);
         }
         *reinterpret_cast<uint4*>(tx + ro + row_off[j]) = make_uint4(w0[4 * j], w0[4 * j + 1], w0[4 * j + 2], w0[4 * j + 3]);

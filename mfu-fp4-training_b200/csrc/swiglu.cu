@@ -43,11 +43,9 @@ __global__ void __launch_bounds__(256) silu_mul_kernel(const uint4* __restrict__
       if (i >= n_vec) continue;
       const uint32_t aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w}, bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
       uint32_t o[4];
+      silu_mul_bf16x8(aw, bw, o);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        o[q] = silu_mul_bf16x2(aw[q], bw[q]);
-        mx = bf16x2_absmax(mx, o[q]);
-      }
+      for (int q = 0; q < 4; ++q) mx = bf16x2_absmax(mx, o[q]);
       out[i] = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
@@ -77,9 +75,9 @@ silu_deriv_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ h3, co
       const uint32_t dw[4] = {d[u].x, d[u].y, d[u].z, d[u].w}, aw[4] = {a[u].x, a[u].y, a[u].z, a[u].w},
                      bw[4] = {b[u].x, b[u].y, b[u].z, b[u].w};
       uint32_t o1[4], o3[4];
+      silu_deriv_bf16x8(dw, aw, bw, o1, o3);
 #pragma unroll
       for (int q = 0; q < 4; ++q) {
-        silu_deriv_bf16x2(dw[q], aw[q], bw[q], o1[q], o3[q]);
         mx1 = bf16x2_absmax(mx1, o1[q]);
         mx3 = bf16x2_absmax(mx3, o3[q]);
       }
@@ -90,6 +88,18 @@ silu_deriv_kernel(const uint4* __restrict__ dh, const uint4* __restrict__ h3, co
   block_amax_commit(bf16x2_hmax_to_f32(mx1), amax1);
   __syncthreads();
   block_amax_commit(bf16x2_hmax_to_f32(mx3), amax3);
+}
+
+// Every bf16 pattern x with |x| < 64: the short division sequence against the general division, for x / d and 1 / d
+// with d = 1 + __expf(-x).  out[0], out[1]: patterns that differ (must both be 0).
+__global__ void __launch_bounds__(256) silu_division_selftest_kernel(unsigned int* __restrict__ out) {
+  const uint32_t pattern = blockIdx.x * blockDim.x + threadIdx.x;
+  const float x = __uint_as_float(pattern << 16);
+  if (!(fabsf(x) < 64.0f)) return;
+  const float d = 1.0f + __expf(-x);
+  const float r1 = rcp_refined(d);
+  if (__float_as_uint(quotient_given_rcp(x, d, r1)) != __float_as_uint(x / d)) atomicAdd(out, 1u);
+  if (__float_as_uint(sigmoid_given_rcp(d, r1)) != __float_as_uint(1.0f / d)) atomicAdd(out + 1, 1u);
 }
 
 __global__ void finalize_sg2_kernel(float* a, float* b) {
@@ -110,6 +120,16 @@ static int check_mh(const void* p, int64_t M, int64_t H, const char* who) {
 }
 
 extern "C" {
+
+int fp4b200_selftest_silu_division(uint32_t* mismatches_dev, void* stream) {
+  if (!mismatches_dev || (reinterpret_cast<uintptr_t>(mismatches_dev) & 3))
+    return set_error("selftest_silu_division: two 32-bit words of device memory are required");
+  cudaStream_t st = (cudaStream_t)stream;
+  FP4_CUDA_CHECK(cudaMemsetAsync(mismatches_dev, 0, 2 * sizeof(uint32_t), st));
+  silu_division_selftest_kernel<<<256, 256, 0, st>>>(mismatches_dev);
+  FP4_CUDA_CHECK(cudaGetLastError());
+  return 0;
+}
 
 int fp4b200_silu_mul_bf16(const void* h1, const void* h3, int64_t n_elems, void* h_out, float* amax_sg,
                           void* stream) {
