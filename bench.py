@@ -743,6 +743,36 @@ def rmsnorm_bwd_only(args):
                       "status": importlib.import_module("mfu-fp4-training_b200._lib").device_status()}))
 
 
+def mx_swiglu_only(args):
+    """The one-pass MXFP4 SwiGLU producers at [M, H]: operands of silu(h1) * h3 (5.0625 algorithmic bytes per
+    element) and of the dh1 / dh3 pair (8.125).  Prints both times and algorithmic bandwidths."""
+    import torch
+    mxq = importlib.import_module("mfu-fp4-training_b200.mxfp4_quant_v4")
+    M, H = (int(v) for v in args.mx_swiglu_only.lower().split("x"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    g = torch.Generator(device=dev).manual_seed(7)
+    h1, h3, dh = ((s * torch.randn(M, H, generator=g, device=dev)).to(torch.bfloat16) for s in (1.0, 1.0, 1e-3))
+    out = {}
+    for name, fn, bytes_per in (("silu_mul", lambda: mxq.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, 1), 5.0625),
+                                ("silu_deriv_split2",
+                                 lambda: mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, 1), 8.125)):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        steps = min(args.steps, 20)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / steps
+        out[name] = {"ms": ms, "algorithmic_gbs": bytes_per * M * H / (ms * 1e-3) / 1e9}
+    out["status"] = importlib.import_module("mfu-fp4-training_b200._lib").device_status()
+    print(json.dumps({"mx_swiglu_only": args.mx_swiglu_only, **out}))
+
+
 def gemm_only(args):
     """Times one NVFP4 GEMM form alone at one shape on cuda:0 (random codes and scales): the plain GEMM, the fused QKV
     projection with the rotary embedding in its epilogue (--gemm-form rope: heads of 128, sequences of 4096, the last
@@ -809,8 +839,13 @@ def main():
                     help="with --gemm-only: which epilogue form to time")
     ap.add_argument("--rmsnorm-bwd-only", default=None, metavar="MxK",
                     help="time only the RMSNorm backward (sum3 form) at this shape (tuning / ncu capture helper)")
+    ap.add_argument("--mx-swiglu-only", default=None, metavar="MxH",
+                    help="time only the one-pass MXFP4 SwiGLU producers at this shape (tuning / ncu capture helper)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.mx_swiglu_only:
+        mx_swiglu_only(args)
+        return
     if args.gemm_only:
         gemm_only(args)
         return
