@@ -175,7 +175,7 @@ def load_reference_kernels():
     import glob
     import importlib.util
     out = {}
-    for name in ("_tk_quant_v5", "_C"):
+    for name in ("_tk_quant_v5", "_C", "mxfp4_quant_v4", "_C_mx"):
         paths = glob.glob(os.path.join(ROOT, "oracle", "_ref", name + ".*.so")) + glob.glob(os.path.join(ROOT, "oracle", "_ref", name + ".so"))
         if not paths:
             continue
@@ -578,6 +578,53 @@ def attention_side_leg(torch, dist, world, peaks):
             "quant_attn_out_gbs": M * K * 3.125 * world / (ms[2] * 1e-3) / 1e9,
             "inverse_rope_gbs": M * (q_dim + kv_dim) * 4.0 * world / (ms[3] * 1e-3) / 1e9,
             "split3_quant_gbs": M * N * 3.125 * world / (ms[4] * 1e-3) / 1e9}
+
+
+def mxfp4_reference_producers_leg(torch, ref, ref_gemm=None):
+    """The MXFP4 producers of config 5 (65536 tokens, mode 1), the reference's compiled kernels and this library's in
+    the same loop on the same tensors: fused RMSNorm + quantiser [65536 x 4096], SwiGLU producer and SiLU-derivative
+    pair [65536 x 14336], plain row + column quantiser [65536 x 4096]; with the reference's GEMM module also the gate
+    (or up) and down GEMMs of that layer."""
+    mxq = _mod("mxfp4_quant_v4")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(23)
+    rnd = lambda m, k, s: (s * torch.randn(m, k, generator=g, device=dev)).to(torch.bfloat16)
+    M, K, H = 65536, K_COLS, 14336
+    x, gam = rnd(M, K, 1.0), (1 + 0.1 * torch.randn(K, generator=g, device=dev)).to(torch.bfloat16)
+    out = {}
+    def both(name, ref_fn, our_fn, iters):
+        r = _time_loop(torch, lambda i: ref_fn(), iters)
+        u = _time_loop(torch, lambda i: our_fn(), iters)
+        out[name] = {"reference_ms": r, "ours_ms": u, "ours_over_reference": r / u}
+    both("rmsnorm_quant_65536x4096", lambda: ref.mxfp4_fused_rmsnorm_quantize_row_and_col(x, gam, EPS, 1),
+         lambda: mxq.mxfp4_fused_rmsnorm_quantize_row_and_col(x, gam, EPS, 1), 10)
+    both("quantize_row_and_col_65536x4096", lambda: ref.mxfp4_quantize_row_and_col(x, 1),
+         lambda: mxq.mxfp4_quantize_row_and_col(x, 1), 10)
+    del x
+    h1, h3, dh = rnd(M, H, 1.0), rnd(M, H, 1.0), rnd(M, H, 1e-3)
+    both("silu_mul_quant_65536x14336", lambda: ref.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, 1),
+         lambda: mxq.mxfp4_fused_silu_mul_quantize_row_and_col(h1, h3, 1), 5)
+    both("silu_deriv_quant_split2_65536x14336", lambda: ref.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, 1),
+         lambda: mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, 1), 5)
+    out["kernels"] = "reference mxfp4_quant_v4 (mxfp4_v4/tk_quantize.cu), compiled from the reference's sources for sm_100a"
+    if ref_gemm is not None:
+        del dh
+        gemm = _mod("tk_gemm_c_mx")
+        qh = mxq.mxfp4_quantize_for_gemm(h1, 1)                                   # [M, H] row operand
+        del h1, h3
+        qx = mxq.mxfp4_quantize_for_gemm(rnd(M, K, 1.0), 1)                       # [M, K]
+        qw1 = mxq.mxfp4_quantize_for_gemm(rnd(H, K, 0.02), 1)                     # W1 [H, K]
+        qw2 = mxq.mxfp4_quantize_for_gemm(rnd(K, H, 0.02), 1)                     # W2 [K, H]
+        d_up = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
+        d_dn = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        for name, a, b, d, fl in (("gemm_65536x14336x4096", qx, qw1, d_up, 2.0 * M * H * K),
+                                  ("gemm_65536x4096x14336", qh, qw2, d_dn, 2.0 * M * K * H)):
+            both(name, lambda: ref_gemm.mxfp4_gemm(a[0], a[1], b[0], b[1], d),
+                 lambda: gemm.mxfp4_gemm(a[0], a[1], b[0], b[1], d), 10)
+            out[name]["ours_tflops"] = fl / (out[name]["ours_ms"] * 1e-3) / 1e12
+            out[name]["reference_tflops"] = fl / (out[name]["reference_ms"] * 1e-3) / 1e12
+        out["gemm_kernels"] = "reference _C_mx.mxfp4_gemm (mxfp4_gb200/mxfp4_gb200_gemm.cu), compiled from the reference's sources"
+    return out
 
 
 def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
@@ -1076,6 +1123,13 @@ def main():
                                "from the reference's sources for sm_100a", "ms": ref_ms,
                      "value": alg / (ref_ms * 1e-3) / 1e9, "unit": UNIT, "ours_ms_same_loop": ours_ms,
                      "ours_over_reference": ref_ms / ours_ms}
+    ref_mx = None
+    if "mxfp4_quant_v4" in refs:
+        try:
+            ref_mx = mxfp4_reference_producers_leg(torch, refs["mxfp4_quant_v4"], refs.get("_C_mx"))
+        except Exception as e:                       # the reference's kernels are evidence beside the line, never fatal
+            ref_mx = {"error": str(e)[:300]}
+        torch.cuda.empty_cache()
     gemm_shapes, roofline_gemm = gemm_roofline_leg(torch, peaks, local_rank, world, refs, traffic)
     torch.cuda.empty_cache()
     cfg1 = config1_leg(torch, dev) if rank == 0 else None
@@ -1099,7 +1153,7 @@ def main():
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
                 "cpu_baseline": cpu, "strong_scaling_point": small, "with_early_reads_promise": early, "roofline_gemm": roofline_gemm,
-                "gemm_shapes": gemm_shapes, "reference_kernels_same_box": {"fused_rmsnorm_nvfp4_quant": ref_quant,
+                "gemm_shapes": gemm_shapes, "reference_kernels_same_box": {"fused_rmsnorm_nvfp4_quant": ref_quant, "mxfp4_producers": ref_mx,
                                                                             "load_errors": {k: v for k, v in refs.items() if k.endswith("_error")}},
                 "config1_quantize_gemm": cfg1, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer": mx_layer,
                 "attention_side": attn_side}

@@ -9,9 +9,9 @@
 #   * by bench.py's --reference-kernels leg, to time the reference's kernels beside this library's.
 # Nothing under mfu-fp4-training_b200/ loads them.
 #
-#   oracle/build_ref.sh <reference checkout> [quant|gemm|all]
+#   oracle/build_ref.sh <reference checkout> [quant|gemm|mxquant|mxgemm|all]
 set -euo pipefail
-REF=${1:?usage: build_ref.sh <reference checkout> [quant|gemm|all]}
+REF=${1:?usage: build_ref.sh <reference checkout> [quant|gemm|mxquant|mxgemm|all]}
 WHAT=${2:-all}
 HERE=$(cd "$(dirname "$0")" && pwd)
 OUT=$HERE/_ref
@@ -42,5 +42,21 @@ if [ "$WHAT" = gemm ] || [ "$WHAT" = all ]; then
      -D__CUDA_NO_HALF_OPERATORS__ -D__CUDA_NO_HALF_CONVERSIONS__ -D__CUDA_NO_BFLOAT16_CONVERSIONS__ \
      -D__CUDA_NO_HALF2_OPERATORS__ -L"${CUDA_HOME:-/usr/local/cuda}/lib64/stubs" -lcuda \
      nvfp4_b200_gemm.cu -o "$OUT/_C$SUFFIX")
+fi
+if [ "$WHAT" = mxquant ] || [ "$WHAT" = all ]; then
+  # mxfp4_quant_v4: MXFP4 quantisers (tk_quantize.cu + mxfp4_v3_quantize.cuh; flags of mxfp4_v4/Makefile:32-49)
+  (cd "$REF/fp4_runtime/TK_quantisation/mxfp4_v4" &&
+   $NVCC $COMMON -diag-suppress 177 -I../nvfp4_v5 -DTORCH_EXTENSION_NAME=mxfp4_quant_v4 \
+     -D__CUDA_NO_HALF_OPERATORS__ -D__CUDA_NO_HALF_CONVERSIONS__ -D__CUDA_NO_BFLOAT16_CONVERSIONS__ \
+     -D__CUDA_NO_HALF2_OPERATORS__ -L"${CUDA_HOME:-/usr/local/cuda}/lib64/stubs" -lcuda \
+     tk_quantize.cu -o "$OUT/mxfp4_quant_v4$SUFFIX")
+fi
+if [ "$WHAT" = mxgemm ] || [ "$WHAT" = all ]; then
+  # _C_mx: MXFP4 tcgen05 GEMMs (mxfp4_gb200_gemm.cu; mxfp4_gb200/Makefile + kernels/common.mk)
+  (cd "$REF/fp4_runtime/ThunderKittens/kernels/gemm/mxfp4_gb200" &&
+   $NVCC $COMMON -I../../../include -I../../../prototype -DTORCH_COMPILE -DTORCH_EXTENSION_NAME=_C_mx \
+     -D__CUDA_NO_HALF_OPERATORS__ -D__CUDA_NO_HALF_CONVERSIONS__ -D__CUDA_NO_BFLOAT16_CONVERSIONS__ \
+     -D__CUDA_NO_HALF2_OPERATORS__ -L"${CUDA_HOME:-/usr/local/cuda}/lib64/stubs" -lcuda \
+     mxfp4_gb200_gemm.cu -o "$OUT/_C_mx$SUFFIX")
 fi
 ls -la "$OUT"

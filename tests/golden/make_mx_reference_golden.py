@@ -1,0 +1,106 @@
+"""Records the output bytes of the reference's OWN sm_100a MXFP4 quantiser kernels on seeded inputs.
+
+Test infrastructure.  Needs one B200 and the reference's ``mxfp4_quant_v4`` extension module compiled by
+``oracle/build_ref.sh <checkout> mxquant`` into ``oracle/_ref/`` (the reference's sources are not needed at run time):
+
+    python tests/golden/make_mx_reference_golden.py     # writes tests/golden/mxfp4_reference_kernels_golden.npz
+
+No kernel of that module waits on another CTA (read in mxfp4_v4/tk_quantize.cu and mxfp4_v3_quantize.cuh: no
+grid-wide counter or flag), so every entry point listed in CASES is called.  Inputs are regenerated from their seeds
+by the tests (``make_inputs`` below), so the fixture holds outputs only.  Calls run in the order of CASES in ONE fresh
+process.
+"""
+import glob
+import importlib.util
+import os
+import sys
+
+import numpy as np
+import torch
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+ROOT = os.path.dirname(os.path.dirname(HERE))
+sys.path.insert(0, ROOT)
+from oracle import fp4_oracle as o  # noqa: E402
+
+SEED, SUBSEQ = 20261126, 5 << 32
+SHAPE = (256, 384)
+
+# name -> (function, positional arguments after the tensors)
+CASES = [
+    ("rowcol_m0", "mxfp4_quantize_row_and_col", "x", (0,)),
+    ("rowcol_m1", "mxfp4_quantize_row_and_col", "x", (1,)),
+    ("rowcol_m2", "mxfp4_quantize_row_and_col", "x", (2,)),
+    ("row_only_m1", "mxfp4_quantize_for_gemm", "x", (1,)),
+    ("weight_2d", "mxfp4_quantize_weight_2d", "w", ()),
+    ("rmsnorm_m1", "mxfp4_fused_rmsnorm_quantize_row_and_col", "x_gamma", (1e-5, 1)),
+    ("silu_mul_m1", "mxfp4_fused_silu_mul_quantize_row_and_col", "h1_h3", (1,)),
+    ("silu_mul_m0", "mxfp4_fused_silu_mul_quantize_row_and_col", "h1_h3", (0,)),
+    ("silu_deriv_m1", "mxfp4_fused_silu_deriv_quantize_split2_row_and_col", "dh_h3_h1", (1,)),
+    ("row_sr_data", "mxfp4_quantize_for_gemm_opt", "g", (1, True, False, SEED, SUBSEQ)),
+    ("row_sr_scale", "mxfp4_quantize_for_gemm_opt", "g", (1, False, True, SEED, SUBSEQ)),
+    ("row_sr_both", "mxfp4_quantize_for_gemm_opt", "g", (0, True, True, SEED, SUBSEQ)),
+    ("rowcol_sr_data", "mxfp4_quantize_row_and_col_opt", "g", (1, True, False, SEED, SUBSEQ)),
+    ("rowcol_sr_both", "mxfp4_quantize_row_and_col_opt", "g", (1, True, True, SEED, SUBSEQ)),
+    ("row_rht16_sign", "mxfp4_quantize_for_gemm_opt_rht", "g", (1, False, False, 16, True, SEED, SUBSEQ)),
+    ("row_rht32_sr", "mxfp4_quantize_for_gemm_opt_rht", "g", (1, True, False, 32, True, SEED, SUBSEQ)),
+    ("rowcol_rht_col16", "mxfp4_quantize_row_and_col_opt_rht", "g", (1, False, False, 16, True, SEED, SUBSEQ)),
+    ("rowcol_rht_col32_sr", "mxfp4_quantize_row_and_col_opt_rht", "g", (1, True, False, 32, True, SEED, SUBSEQ)),
+    ("rowcol_rht_both16", "mxfp4_quantize_row_and_col_opt_rht_both", "g", (1, False, False, 16, True, SEED, SUBSEQ)),
+    ("rowcol_rht_row_only16", "mxfp4_quantize_row_and_col_opt_rht_row_only", "g", (1, False, False, 16, True, SEED, SUBSEQ)),
+]
+
+
+def make_inputs(kind, seed):
+    """The seeded inputs of a case as float32 arrays of bf16 values; the tests call this too."""
+    M, K = SHAPE
+    rng = np.random.default_rng(seed)
+    r = lambda s: o.bf16_round((s * rng.standard_normal((M, K))).astype(np.float32))
+    if kind == "x":
+        x = o.make_activations(M, K, seed=seed).copy()
+        x[3, 32:64] = 0.0                      # an all-zero row block
+        x[64:96, 7] = 0.0                      # an all-zero column block
+        return (x,)
+    if kind == "w":
+        return (r(0.02),)
+    if kind == "x_gamma":
+        return (o.make_activations(M, K, seed=seed), o.make_gamma(K, seed=seed + 1))
+    if kind == "h1_h3":
+        return (r(2.0), r(1.0))
+    if kind == "dh_h3_h1":
+        return (r(1e-3), r(1.0), r(2.0))
+    if kind == "g":
+        return (r(1e-3),)
+    raise ValueError(kind)
+
+
+def load_reference_module():
+    paths = glob.glob(os.path.join(ROOT, "oracle", "_ref", "mxfp4_quant_v4*.so"))
+    if not paths:
+        raise SystemExit("oracle/_ref/mxfp4_quant_v4*.so is missing: run oracle/build_ref.sh <reference checkout> mxquant")
+    spec = importlib.util.spec_from_file_location("mxfp4_quant_v4", paths[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
+def main():
+    ref = load_reference_module()
+    dev = torch.device("cuda", 0)
+    out = {}
+    for i, (name, fn, kind, extra) in enumerate(CASES):
+        tensors = [torch.from_numpy(a).to(torch.bfloat16).to(dev) for a in make_inputs(kind, 300 + i)]
+        r = getattr(ref, fn)(*tensors, *extra)
+        torch.cuda.synchronize()
+        for j, t in enumerate(r):
+            if not torch.is_tensor(t):
+                continue
+            a = t.view(torch.uint8) if t.dtype not in (torch.float32, torch.uint8) else t
+            out[f"{name}.{j}"] = a.cpu().numpy()
+    dst = os.environ.get("MX_GOLDEN_OUT", os.path.join(HERE, "mxfp4_reference_kernels_golden.npz"))
+    np.savez_compressed(dst, **out)
+    print(f"wrote {dst}: {len(out)} arrays, {os.path.getsize(dst)} bytes")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,57 @@
+"""GPU parity against bytes the reference's OWN sm_100a MXFP4 kernels produced
+(tests/golden/mxfp4_reference_kernels_golden.npz, recorded by tests/golden/make_mx_reference_golden.py from the
+reference's compiled ``mxfp4_quant_v4`` module on a B200): round-to-nearest row / column quantisers in the three
+exponent modes, the 32 x 32 weight form, the fused RMSNorm, SwiGLU and SiLU-derivative producers (whose element
+arithmetic — ``__expf``, the division — is the reference kernel's, not a CPU restatement's), and the stochastic /
+Hadamard forms with their Philox streams and launch numbering.  Bit-exact, no tolerance."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests.golden import make_mx_reference_golden as G
+from tests.gpu_util import assert_status_ok, mod, to_dev_bf16
+
+pytestmark = pytest.mark.gpu
+
+_PATH = os.path.join(os.path.dirname(__file__), "golden", "mxfp4_reference_kernels_golden.npz")
+GOLD = np.load(_PATH) if os.path.exists(_PATH) else None
+
+
+def _numbered(case):
+    """Does this call take a launch number of the row + column stochastic quantiser (mxfp4_v4/tk_quantize.cu:2853-2860)?"""
+    _, fn, _, extra = case
+    if not fn.startswith("mxfp4_quantize_row_and_col_opt"):
+        return False
+    data_sr, scale_sr = extra[1], extra[2]
+    with_sign = len(extra) == 7 and extra[4]
+    return bool(data_sr or scale_sr or with_sign)
+
+
+@pytest.mark.skipif(GOLD is None, reason="fixture not recorded")
+@pytest.mark.parametrize("idx", range(len(G.CASES)), ids=[c[0] for c in G.CASES])
+def test_mxfp4_producers_reproduce_the_reference_kernels_bytes(idx):
+    name, fn, kind, extra = G.CASES[idx]
+    mxq = mod("mxfp4_quant_v4")
+    tensors = [to_dev_bf16(a) for a in G.make_inputs(kind, 300 + idx)]
+    mxq.mxfp4_set_forward_sr_invocation_count(sum(_numbered(c) for c in G.CASES[:idx]))
+    r = getattr(mxq, fn)(*tensors, *extra)
+    torch.cuda.synchronize()
+    checked = 0
+    for j, t in enumerate(r):
+        key = f"{name}.{j}"
+        if key not in GOLD.files:
+            continue
+        want = GOLD[key]
+        got = t if t.dtype in (torch.float32, torch.uint8) else t.view(torch.uint8)
+        got = got.cpu().numpy()
+        assert got.size == want.size, key
+        if got.dtype == np.float32:
+            assert np.array_equal(got.reshape(-1), want.reshape(-1)), key
+        else:
+            bad = int((got.reshape(-1) != want.reshape(-1)).sum())
+            assert bad == 0, f"{key}: {bad} of {got.size} bytes differ from the reference kernel's"
+        checked += 1
+    assert checked >= 2
+    assert_status_ok()
