@@ -201,6 +201,13 @@ int fp4b200_mxfp4_quantize(const void* x_bf16, int64_t M, int64_t K, int mode, v
 int fp4b200_mxfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, const float* inv_rms, int64_t M,
                                   int64_t K, int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
                                   void* stream);
+/* inv_rms[r] = rsqrtf(sum_k x[r,k]^2 / K + eps) in the summation order of the reference's MXFP4 producer
+ * (mxfp4_v4/mxfp4_v3_quantize.cuh:109-172, compute_inv_rms_kernel: 256 threads, thread t takes the 8-element vectors
+ * t, t + 256, ... in sequence, xor butterflies inside and across its warps), which differs from the NVFP4 producer's
+ * tree in the last bit of some rows.  gamma (16-byte aligned, [K]) is only staged, not used.  Feeds
+ * fp4b200_mxfp4_quantize_normed for mxfp4_fused_rmsnorm_quantize_row_and_col. */
+int fp4b200_mxfp4_rmsnorm_inv_rms(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
+                                  float* inv_rms, void* stream);
 
 /* ---- SwiGLU producers ------------------------------------------------------------------ */
 

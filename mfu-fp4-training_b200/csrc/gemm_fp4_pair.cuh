@@ -23,7 +23,17 @@ namespace fp4b200 {
 
 constexpr int kPairStages = 5;
 constexpr int kPairBHalfBytes = 128 * kGemmBKBytes;   // this CTA's half of the B tile: 16 KiB
-constexpr int kPairSfSlots = 2;                       // K stages whose scales are resident in tensor memory
+// K stages whose scales are resident in tensor memory, and the columns of one such slot.  NVFP4: 16 columns of A
+// scales + 32 of B scales per stage, two slots in the 128 columns beside the accumulators.  MXFP4 has half the scale
+// bytes: 8 + 16 columns, one slot per shared-memory stage, so its movers may run as far ahead of the MMA thread as the
+// TMA producer does instead of one stage.  With two slots the hand-over of a stage — scales written, waited for,
+// announced across the cluster, MMAs issued — has to fit inside one stage's MMA time, and it does not quite: five slots
+// took the MXFP4 GEMM at K = 14336 from 5.34 to 5.80 PFLOP/s.  NVFP4 in five HALF-stage slots of the same 24 columns
+// (two MMAs each, a completion barrier per half) was built and measured as well: correct, and 8 % slower — the
+// hand-over's fixed cost is paid twice per stage then.
+constexpr int kPairSfSlotsNv = 2, kPairSfSlotsMx = 5;
+constexpr int kPairSfSlotsMax = 5;
+constexpr int kPairSfSlotColsMx = 24;
 constexpr int kPairSfBase = 384;                      // accumulators occupy columns [0, 384)
 constexpr int kPairThreads = kGemmThreads;            // producer, MMA thread, four epilogue warps, four scale movers
 // The rotary / SiLU forms ("wide"): four warpgroups — {producer, MMA thread, two idle warps}, four scale movers, and two
@@ -43,7 +53,7 @@ struct GemmPairSmem {
   alignas(128) uint8_t sfb[kPairStages][kBSfBytes];
   alignas(8) uint64_t full[kPairStages];       // this CTA's TMA data of the stage has landed
   alignas(8) uint64_t empty[kPairStages];      // the pair's MMAs have finished reading the stage (and its scale slot)
-  alignas(8) uint64_t sf_ready[kPairSfSlots];  // leader only: operands + scales of BOTH CTAs are in place
+  alignas(8) uint64_t sf_ready[kPairSfSlotsMax];  // leader only: operands + scales of BOTH CTAs are in place
   alignas(8) uint64_t acc_full;                // accumulator of the tile is complete
   alignas(8) uint64_t acc_empty_shared;        // leader only: both CTAs have lifted columns [128, 256) out
   alignas(8) uint64_t acc_empty_priv[2];       // leader only: columns [0, 128) / [256, 384)
@@ -148,6 +158,11 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
   const int k_stages = g.seg_stage_end[g.n_seg - 1];
   const bool k_tail_half = g.seg_tail_half[g.n_seg - 1] != 0;   // only a plain MXFP4 GEMM (one segment) can have one
   constexpr int kSfPerStage = MX ? 1024 : 2048;
+  constexpr int kPairSfSlots = MX ? kPairSfSlotsMx : kPairSfSlotsNv;
+  constexpr int kSlotCols = MX ? kPairSfSlotColsMx : kSfSlotCols;
+  constexpr int kSfbOff = MX ? 8 : 16;          // B scales behind the A scales of the slot
+  static_assert(kPairSfBase + kPairSfSlots * kSlotCols <= 512, "scale slots must fit beside the accumulators");
+  static_assert(!MX || kPairSfSlots == kPairStages, "MXFP4: the scale slot of a stage is the stage");
 
   if (tid == 0) {
     for (int s = 0; s < kPairStages; ++s) {
@@ -260,7 +275,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
             break;
           }
           tc_fence_after();
-          const uint32_t sf_cols = tmem + kPairSfBase + slot * kSfSlotCols;
+          const uint32_t sf_cols = tmem + kPairSfBase + slot * kSlotCols;
           const uint32_t a_base = smem_u32(sm.a[stage]);
           const uint32_t b_base = smem_u32(sm.b[stage]);
           const int ka = ks - ks_begin;          // 0 at the first stage of this accumulator
@@ -270,7 +285,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
 #pragma unroll
             for (int j = 0; j < 2; ++j)
               tc_mma_pair<true>(d_tmem, smem_desc(a_base + j * 32, 16, 1024, 2), smem_desc(b_base + j * 32, 16, 1024, 2),
-                          block_scaled_idesc(256, kGemmBN, 1, j * 2), sf_cols, sf_cols + 16, (ka | j) != 0);
+                          block_scaled_idesc(256, kGemmBN, 1, j * 2), sf_cols, sf_cols + kSfbOff, (ka | j) != 0);
           } else {
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -282,7 +297,7 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
               } else {
                 const int sf_id = (j & 1) * 2;   // bytes 0..1 or 2..3 of the scale column
                 tc_mma_pair<true>(d_tmem, adesc, bdesc, block_scaled_idesc(256, kGemmBN, 1, sf_id),
-                            sf_cols + (j >> 1) * 4, sf_cols + 16 + (j >> 1) * 8, (ka | j) != 0);
+                            sf_cols + (j >> 1) * 4, sf_cols + kSfbOff + (j >> 1) * 8, (ka | j) != 0);
               }
             }
           }
@@ -304,8 +319,9 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
     uint32_t gk = 0;
     bool ok = true;
     constexpr int kTiles = MX ? 2 : 4;
-    static_assert(kPairSfSlots == 2, "the movers keep one leader address per slot");
-    const uint32_t sf_ready_leader0 = map_to_cta(&sm.sf_ready[0], 0), sf_ready_leader1 = map_to_cta(&sm.sf_ready[1], 0);
+    uint32_t sf_ready_leader[kPairSfSlots];       // the leader's barrier of each slot
+#pragma unroll
+    for (int s = 0; s < kPairSfSlots; ++s) sf_ready_leader[s] = map_to_cta(&sm.sf_ready[s], 0);
     for (int ti = 0; ti < tiles.count && ok; ++ti) {
       for (int ks = 0; ks < k_stages; ++ks, ++gk) {
         if (!mbar_wait_timed(&sm.full[stage], phase)) {
@@ -325,14 +341,25 @@ fp4_gemm_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_co
           }
           tc_fence_after();
         }
-        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + kPairSfBase + slot * kSfSlotCols;
-        tmem_st16(taddr, ra);
-        tmem_st32(taddr + 16, rb);
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + kPairSfBase + slot * kSlotCols;
+        if constexpr (MX) {
+          tmem_st8(taddr, ra);
+          tmem_st8(taddr + 8, rb);
+          tmem_st8(taddr + 16, rb + 8);
+        } else {
+          tmem_st16(taddr, ra);
+          tmem_st32(taddr + 16, rb);
+        }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         tc_fence_before();
         __syncwarp();
         // tell the leader: this CTA's operands have landed and this quadrant's scales are in place
-        if (lane == 0) mbar_arrive_cluster(slot ? sf_ready_leader1 : sf_ready_leader0);
+        if (lane == 0) {
+          uint32_t leader = sf_ready_leader[0];
+#pragma unroll
+          for (int s = 1; s < kPairSfSlots; ++s) leader = slot == (uint32_t)s ? sf_ready_leader[s] : leader;
+          mbar_arrive_cluster(leader);
+        }
         if (++stage == kPairStages) { stage = 0; phase ^= 1; }
       }
     }

@@ -139,6 +139,34 @@ __device__ __forceinline__ float stats_inv_rms(const uint4 (&v)[NV], int K, floa
   return rsqrtf(s / static_cast<float>(K) + eps);
 }
 
+// The same for the summation tree of the reference's MXFP4 producer (mxfp4_v4/mxfp4_v3_quantize.cuh:109-172,
+// compute_inv_rms_kernel): thread t of its 256 accumulates the eight elements of vector t, then of vector t + 256,
+// ... in sequence; xor butterflies over 16,8,4,2,1 inside each of its eight warps, then over the eight warp sums
+// (the same butterfly on a warp whose lanes 8-31 hold zeros).  Lane L here holds that kernel's threads
+// 32*w + L (w = 0..7) in acc[w].
+template <int NV>
+__device__ __forceinline__ float stats_inv_rms_mx(const uint4 (&v)[NV], int K, float eps) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    float a = acc[j & 7];
+    a = fma_sq_bf16x2(v[j].x, a);
+    a = fma_sq_bf16x2(v[j].y, a);
+    a = fma_sq_bf16x2(v[j].z, a);
+    a = fma_sq_bf16x2(v[j].w, a);
+    acc[j & 7] = a;
+  }
+#pragma unroll
+  for (int w = 0; w < 8; ++w) {
+    if (w < NV) {
+#pragma unroll
+      for (int m = 16; m > 0; m >>= 1) acc[w] += __shfl_xor_sync(0xffffffffu, acc[w], m);
+    }
+  }
+  const float s = ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
+  return rsqrtf(s / static_cast<float>(K) + eps);
+}
+
 // Running maximum of |(x * inv) * gamma| in fp32 over the row held in v.  Rounding to bf16 is
 // monotonic, so the tensor amax of the bf16 values is the bf16 rounding of this maximum: no
 // per-element conversion.  gamma is read as fp32 from two shared-memory tables (elements 0-3 and
@@ -175,7 +203,7 @@ __device__ __forceinline__ float stats_row_amax(const uint4 (&v)[NV], const floa
 // then), refills the slot with the row `slots` further on.  Bytes in flight per SM are set by the ring,
 // not by registers or by the number of warps, which is what a streaming reduction at HBM speed needs;
 // rows are handed out one at a time, so the warps of a CTA finish within one row of each other.
-template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS>
+template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS, bool MX_TREE = false>
 __global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                      float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
@@ -263,7 +291,8 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     const size_t row = row_of(r);
     float inv;
     if constexpr (COMPUTE_INV_RMS) {
-      inv = stats_inv_rms<NV>(v, K, eps);
+      if constexpr (MX_TREE) inv = stats_inv_rms_mx<NV>(v, K, eps);
+      else inv = stats_inv_rms<NV>(v, K, eps);
       if (lane == 0) {
         inv_rms[row] = inv;
         if (r + n_slots < n_band) issue(r + n_slots);
@@ -442,7 +471,8 @@ rmsnorm_stats_pair_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat
 template <bool COMPUTE_INV_RMS>
 __global__ void __launch_bounds__(256)
 rmsnorm_stats_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
-                             float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K) {
+                             float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
+                             int mx_tree) {
   __shared__ float warp_max_s[8];
   pdl_launch_dependents();
   const int lane = threadIdx.x & 31;
@@ -453,6 +483,31 @@ rmsnorm_stats_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
   for (int row = warp_global; row < M; row += n_warps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
     float inv;
+    if (COMPUTE_INV_RMS && mx_tree) {
+      // the MXFP4 producer's tree (see stats_inv_rms_mx); inverse RMS only
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int q0 = 0; q0 < nvec_row; q0 += 256) {
+#pragma unroll
+        for (int w = 0; w < 8; ++w) {
+          const int q = q0 + 32 * w + lane;
+          if (q < nvec_row) {
+            const uint4 vv = __ldg(xr + q);
+            float a = acc[w];
+            a = fma_sq_bf16x2(vv.x, a); a = fma_sq_bf16x2(vv.y, a);
+            a = fma_sq_bf16x2(vv.z, a); a = fma_sq_bf16x2(vv.w, a);
+            acc[w] = a;
+          }
+        }
+      }
+#pragma unroll
+      for (int w = 0; w < 8; ++w) {
+#pragma unroll
+        for (int m = 16; m > 0; m >>= 1) acc[w] += __shfl_xor_sync(0xffffffffu, acc[w], m);
+      }
+      const float s = ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
+      if (lane == 0) inv_rms[row] = rsqrtf(s / static_cast<float>(K) + eps);
+      continue;
+    }
     if constexpr (COMPUTE_INV_RMS) {
       float acc[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
       for (int q0 = 0; q0 < nvec_row; q0 += 64) {
@@ -2100,10 +2155,10 @@ static int stats_slots_for(int64_t K) {
   return (int)std::max<int64_t>(0, std::min<int64_t>(budget / (K * 2), 64));
 }
 
-template <int NV, bool CI>
+template <int NV, bool CI, bool MX_TREE = false>
 static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
                           int64_t M, int64_t K, int slots, int* status, cudaStream_t st, int* grid_out, int want_amax) {
-  auto kern = rmsnorm_stats_kernel<NV, CI>;
+  auto kern = rmsnorm_stats_kernel<NV, CI, MX_TREE>;
   const int warps = std::min(NV <= 16 ? kStatsMaxWarps : 6, slots);
   const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 + (size_t)slots * 12;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -2148,7 +2203,7 @@ static int launch_stats_pair_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb,
 // launched next.
 static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms, float* amax_sg, float eps,
                                 int64_t M, int64_t K, bool compute_inv, cudaStream_t st, float* scratch = nullptr,
-                                AmaxPartials* partials_out = nullptr) {
+                                AmaxPartials* partials_out = nullptr, bool mx_tree = false) {
   if ((reinterpret_cast<uintptr_t>(gamma) & 15) != 0) return set_error("rmsnorm statistics: gamma must be 16-byte aligned");
   if (scratch == nullptr) scratch = stream_scratch(st);
   if (scratch == nullptr) return -1;
@@ -2162,6 +2217,12 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
     int* status = device_status_ptr();
     if (status == nullptr) return -1;
     int rc;
+    if (mx_tree) {   // inverse RMS only, in the MXFP4 producer's summation order: one warp per row
+      if (K <= 1024) rc = launch_stats_t<4, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else if (K <= 2048) rc = launch_stats_t<8, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else if (K <= 4096) rc = launch_stats_t<16, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else rc = launch_stats_t<32, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+    } else
     if (stats_pair_enabled()) {
       if (K <= 1024) rc = compute_inv ? launch_stats_pair_t<2, true>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax)
                                       : launch_stats_pair_t<2, false>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax);
@@ -2183,8 +2244,8 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
     if (rc) return rc;
   } else {
     grid = (int)std::min<int64_t>((M + 7) / 8, std::min<int64_t>((int64_t)device_sm_count() * 8, kScratchFloats));
-    if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K);
-    else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K);
+    if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K, mx_tree ? 1 : 0);
+    else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K, 0);
     FP4_CUDA_CHECK(cudaGetLastError());
   }
   if (partials_out != nullptr) {
@@ -2408,6 +2469,14 @@ int fp4b200_nvfp4_rmsnorm_stats(const void* x_bf16, const void* gamma_bf16, floa
   if (amax_sg == nullptr && !compute_inv_rms) return set_error("nvfp4_rmsnorm_stats: nothing to compute");
   return launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, amax_sg, eps, M, K, compute_inv_rms != 0,
                               (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_rmsnorm_inv_rms(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
+                                  float* inv_rms, void* stream) {
+  if (int rc = check_quant_shapes(x_bf16, M, K, "mxfp4_rmsnorm_inv_rms")) return rc;
+  if (gamma_bf16 == nullptr || inv_rms == nullptr) return set_error("mxfp4_rmsnorm_inv_rms: gamma and inv_rms are required");
+  return launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, nullptr, eps, M, K, true, (cudaStream_t)stream, nullptr, nullptr,
+                              true);
 }
 
 int fp4b200_nvfp4_fused_norm_quantize(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,

@@ -168,8 +168,9 @@ def mxfp4_fused_rmsnorm_quantize_row_and_col(input, norm_weight, epsilon, mode=0
         rf, rs, cf, cs = _alloc(M, K, input.device, True)
         inv_rms = torch.empty(M, dtype=torch.float32, device=input.device)
         st = _stream(input)
-        _lib.call("fp4b200_nvfp4_rmsnorm_stats", input.data_ptr(), norm_weight.data_ptr(), float(epsilon), M, K,
-                  inv_rms.data_ptr(), 1, None, st)   # inverse RMS only: MXFP4 has no tensor scale
+        # inverse RMS only (MXFP4 has no tensor scale), in this producer's own summation order
+        _lib.call("fp4b200_mxfp4_rmsnorm_inv_rms", input.data_ptr(), norm_weight.data_ptr(), float(epsilon), M, K,
+                  inv_rms.data_ptr(), st)
         _lib.call("fp4b200_mxfp4_quantize_normed", input.data_ptr(), norm_weight.data_ptr(), inv_rms.data_ptr(), M, K,
                   int(mode), rf.data_ptr(), rs.data_ptr(), cf.data_ptr(), cs.data_ptr(), st)
     return rf.view(_FP4), rs, cf.view(_FP4), cs, inv_rms
