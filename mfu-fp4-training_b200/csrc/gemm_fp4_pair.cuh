@@ -30,7 +30,8 @@ constexpr int kPairBHalfBytes = 128 * kGemmBKBytes;   // this CTA's half of the 
 // announced across the cluster, MMAs issued — has to fit inside one stage's MMA time, and it does not quite: five slots
 // took the MXFP4 GEMM at K = 14336 from 5.34 to 5.80 PFLOP/s.  NVFP4 in five HALF-stage slots of the same 24 columns
 // (two MMAs each, a completion barrier per half) was built and measured as well: correct, and 8 % slower — the
-// hand-over's fixed cost is paid twice per stage then.
+// hand-over's fixed cost is paid twice per stage then; five whole-stage NVFP4 slots behind the single accumulator of the
+// batched-accumulation form: 1 % slower (with twice the scale bytes the shared-memory port binds first).
 constexpr int kPairSfSlotsNv = 2, kPairSfSlotsMx = 5;
 constexpr int kPairSfSlotsMax = 5;
 constexpr int kPairSfSlotColsMx = 24;
