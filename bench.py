@@ -580,6 +580,43 @@ def attention_side_leg(torch, dist, world, peaks):
             "split3_quant_gbs": M * N * 3.125 * world / (ms[4] * 1e-3) / 1e9}
 
 
+def nvfp4_reference_producers_leg(torch, ref, ref_gemm=None):
+    """Producers of config 4 (16384 tokens), the reference's compiled kernels and this library's in the same loop on
+    the same tensors.  Only entry points whose launch path has no grid-wide software barrier: the optional-mode
+    quantiser (tuned TMA kernel behind its scans) in the gradient form of config 4 — row operand round-to-nearest,
+    column operand through the Hadamard transform along tokens with the sign vector and Philox SR — the SwiGLU element
+    kernels, and the batched-accumulation GEMM."""
+    tkq = _mod("tk_quant_v5")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    g = torch.Generator(device=dev).manual_seed(29)
+    rnd = lambda m, k, s: (s * torch.randn(m, k, generator=g, device=dev)).to(torch.bfloat16)
+    M, K, H = M_ROWS, K_COLS, 14336
+    out = {}
+    def both(name, ref_fn, our_fn, iters):
+        r = _time_loop(torch, lambda i: ref_fn(), iters)
+        u = _time_loop(torch, lambda i: our_fn(), iters)
+        out[name] = {"reference_ms": r, "ours_ms": u, "ours_over_reference": r / u}
+    args = (True, False, True, False, "col", True, 20261125, 3, 448.0, "col")
+    dy, dh1 = rnd(M, K, 1e-3), rnd(M, H, 1e-3)
+    both("grad_operands_16384x4096", lambda: ref.tk_quantize_for_gemm_opt(dy, *args), lambda: tkq.tk_quantize_for_gemm_opt(dy, *args), 20)
+    both("grad_operands_16384x14336", lambda: ref.tk_quantize_for_gemm_opt(dh1, *args), lambda: tkq.tk_quantize_for_gemm_opt(dh1, *args), 10)
+    h1, h3 = rnd(M, H, 1.0), rnd(M, H, 1.0)
+    both("silu_deriv_split_bf16_16384x14336", lambda: ref.tk_silu_deriv_split_bf16(dh1, h3, h1),
+         lambda: tkq.tk_silu_deriv_split_bf16(dh1, h3, h1), 10)
+    both("silu_mul_split_bf16_16384x14336", lambda: ref.tk_silu_mul_split_bf16(h1, h3), lambda: tkq.tk_silu_mul_split_bf16(h1, h3), 10)
+    out["kernels"] = "reference _tk_quant_v5 (nvfp4_v5/tk_quantize.cu), compiled from the reference's sources for sm_100a"
+    if ref_gemm is not None and hasattr(ref_gemm, "nvfp4_batched_accum_gemm"):
+        gemm = _mod("tk_gemm_c")
+        qa = [tkq.tk_quantize_for_gemm(t, False, False) for t in (dh1, h3)]
+        del dy, dh1, h1, h3
+        qb = [tkq.tk_quantize_for_gemm(rnd(K, H, 0.02), False, False) for _ in range(2)]
+        d = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
+        lists = ([q[0] for q in qa], [q[1] for q in qa], [q[4] for q in qa], [q[0] for q in qb], [q[1] for q in qb], [q[4] for q in qb])
+        both("batched_accum_gemm_2x16384x4096x14336", lambda: ref_gemm.nvfp4_batched_accum_gemm(*lists, d),
+             lambda: gemm.nvfp4_batched_accum_gemm(*lists, d), 10)
+    return out
+
+
 def mxfp4_reference_producers_leg(torch, ref, ref_gemm=None):
     """The MXFP4 producers of config 5 (65536 tokens, mode 1), the reference's compiled kernels and this library's in
     the same loop on the same tensors: fused RMSNorm + quantiser [65536 x 4096], SwiGLU producer and SiLU-derivative
@@ -1123,6 +1160,13 @@ def main():
                                "from the reference's sources for sm_100a", "ms": ref_ms,
                      "value": alg / (ref_ms * 1e-3) / 1e9, "unit": UNIT, "ours_ms_same_loop": ours_ms,
                      "ours_over_reference": ref_ms / ours_ms}
+    ref_nv = None
+    if "_tk_quant_v5" in refs:
+        try:
+            ref_nv = nvfp4_reference_producers_leg(torch, refs["_tk_quant_v5"], refs.get("_C"))
+        except Exception as e:                       # the reference's kernels are evidence beside the line, never fatal
+            ref_nv = {"error": str(e)[:300]}
+        torch.cuda.empty_cache()
     ref_mx = None
     if "mxfp4_quant_v4" in refs:
         try:
@@ -1153,7 +1197,8 @@ def main():
                            "sharding": f"token dimension, {world} x [{M_ROWS}x{K_COLS}] per-rank batches, no collective"},
                 "clocks": clocks, "e2e": e2e, "gpu_launches": 2 * args.steps, "roofline": roofline,
                 "cpu_baseline": cpu, "strong_scaling_point": small, "with_early_reads_promise": early, "roofline_gemm": roofline_gemm,
-                "gemm_shapes": gemm_shapes, "reference_kernels_same_box": {"fused_rmsnorm_nvfp4_quant": ref_quant, "mxfp4_producers": ref_mx,
+                "gemm_shapes": gemm_shapes, "reference_kernels_same_box": {"fused_rmsnorm_nvfp4_quant": ref_quant, "nvfp4_producers": ref_nv,
+                                                                            "mxfp4_producers": ref_mx,
                                                                             "load_errors": {k: v for k, v in refs.items() if k.endswith("_error")}},
                 "config1_quantize_gemm": cfg1, "ffn_forward": ffn, "ffn_backward": ffn_bwd, "mxfp4_layer": mx_layer,
                 "attention_side": attn_side}
