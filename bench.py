@@ -614,6 +614,10 @@ def nvfp4_reference_producers_leg(torch, ref, ref_gemm=None):
         lists = ([q[0] for q in qa], [q[1] for q in qa], [q[4] for q in qa], [q[0] for q in qb], [q[1] for q in qb], [q[4] for q in qb])
         both("batched_accum_gemm_2x16384x4096x14336", lambda: ref_gemm.nvfp4_batched_accum_gemm(*lists, d),
              lambda: gemm.nvfp4_batched_accum_gemm(*lists, d), 10)
+        ref_gemm.nvfp4_batched_accum_gemm(*lists, d)
+        d_ref = d.clone()
+        gemm.nvfp4_batched_accum_gemm(*lists, d)
+        out["batched_accum_gemm_2x16384x4096x14336"]["outputs_bit_identical"] = bool(torch.equal(d, d_ref))
     return out
 
 
@@ -658,6 +662,11 @@ def mxfp4_reference_producers_leg(torch, ref, ref_gemm=None):
                                   ("gemm_65536x4096x14336", qh, qw2, d_dn, 2.0 * M * K * H)):
             both(name, lambda: ref_gemm.mxfp4_gemm(a[0], a[1], b[0], b[1], d),
                  lambda: gemm.mxfp4_gemm(a[0], a[1], b[0], b[1], d), 10)
+            ref_gemm.mxfp4_gemm(a[0], a[1], b[0], b[1], d)
+            d_ref = d.clone()
+            gemm.mxfp4_gemm(a[0], a[1], b[0], b[1], d)
+            out[name]["outputs_bit_identical"] = bool(torch.equal(d, d_ref))
+            del d_ref
             out[name]["ours_tflops"] = fl / (out[name]["ours_ms"] * 1e-3) / 1e12
             out[name]["reference_tflops"] = fl / (out[name]["reference_ms"] * 1e-3) / 1e12
         out["gemm_kernels"] = "reference _C_mx.mxfp4_gemm (mxfp4_gb200/mxfp4_gb200_gemm.cu), compiled from the reference's sources"

@@ -84,6 +84,27 @@ def load_reference_module():
     return mod
 
 
+GEMM_SHAPES = [(256, 256, 512), (256, 512, 1280)]   # M, N, K
+
+
+def gemm_operands(shape, seed):
+    """bf16-valued float32 A [M, K] and B [N, K] of a GEMM case; the tests call this too."""
+    M, N, K = shape
+    rng = np.random.default_rng(seed)
+    return (o.bf16_round(rng.standard_normal((M, K)).astype(np.float32)),
+            o.bf16_round((0.02 * rng.standard_normal((N, K))).astype(np.float32)))
+
+
+def load_reference_gemm_module():
+    paths = glob.glob(os.path.join(ROOT, "oracle", "_ref", "_C_mx*.so"))
+    if not paths:
+        return None
+    spec = importlib.util.spec_from_file_location("_C_mx", paths[0])
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    return mod
+
+
 def main():
     ref = load_reference_module()
     dev = torch.device("cuda", 0)
@@ -97,6 +118,20 @@ def main():
                 continue
             a = t.view(torch.uint8) if t.dtype not in (torch.float32, torch.uint8) else t
             out[f"{name}.{j}"] = a.cpu().numpy()
+    ref_gemm = load_reference_gemm_module()
+    if ref_gemm is not None:
+        # quantised by the reference's quantiser (mode 1), multiplied by the reference's GEMM: D bf16, and D + R
+        for i, shape in enumerate(GEMM_SHAPES):
+            a, b = (torch.from_numpy(t).to(torch.bfloat16).to(dev) for t in gemm_operands(shape, 700 + i))
+            qa, qb = ref.mxfp4_quantize_for_gemm(a, 1), ref.mxfp4_quantize_for_gemm(b, 1)
+            d = torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device=dev)
+            ref_gemm.mxfp4_gemm(qa[0], qa[1], qb[0], qb[1], d)
+            torch.cuda.synchronize()
+            out[f"gemm_{i}.d"] = d.view(torch.int16).cpu().numpy()
+            r = (0.5 * torch.randn(shape[0], shape[1], generator=torch.Generator().manual_seed(800 + i))).to(torch.bfloat16).to(dev)
+            ref_gemm.mxfp4_gemm_residual(qa[0], qa[1], qb[0], qb[1], r, d)
+            torch.cuda.synchronize()
+            out[f"gemm_{i}.d_residual"] = d.view(torch.int16).cpu().numpy()
     dst = os.environ.get("MX_GOLDEN_OUT", os.path.join(HERE, "mxfp4_reference_kernels_golden.npz"))
     np.savez_compressed(dst, **out)
     print(f"wrote {dst}: {len(out)} arrays, {os.path.getsize(dst)} bytes")

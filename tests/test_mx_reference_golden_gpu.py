@@ -55,3 +55,23 @@ def test_mxfp4_producers_reproduce_the_reference_kernels_bytes(idx):
         checked += 1
     assert checked >= 2
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "gemm_0.d" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+@pytest.mark.parametrize("idx", range(len(G.GEMM_SHAPES)))
+def test_mxfp4_gemm_reproduces_the_reference_kernels_bytes(idx):
+    """mxfp4_gemm and mxfp4_gemm_residual on operands quantised in mode 1: the bf16 outputs of the reference's compiled
+    `_C_mx` kernels, bit for bit (same tcgen05 instruction, same 1/36 epilogue, one rounding)."""
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    shape = G.GEMM_SHAPES[idx]
+    a, b = (to_dev_bf16(t) for t in G.gemm_operands(shape, 700 + idx))
+    qa, qb = mxq.mxfp4_quantize_for_gemm(a, 1), mxq.mxfp4_quantize_for_gemm(b, 1)
+    d = torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device="cuda")
+    gemm.mxfp4_gemm(qa[0], qa[1], qb[0], qb[1], d)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD[f"gemm_{idx}.d"])
+    r = (0.5 * torch.randn(shape[0], shape[1], generator=torch.Generator().manual_seed(800 + idx))).to(torch.bfloat16).cuda()
+    gemm.mxfp4_gemm_residual(qa[0], qa[1], qb[0], qb[1], r, d)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD[f"gemm_{idx}.d_residual"])
+    assert_status_ok()
