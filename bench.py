@@ -750,7 +750,7 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
         d = st["gd"]
         # the producer stacks dh1 and dh3 on a leading dimension; the one-pass GEMM reads them side by side
         a_full = torch.cat([d[0][0].view(torch.uint8), d[0][1].view(torch.uint8)], dim=1).view(torch.float4_e2m1fn_x2)
-        gmx.mxfp4_split2_dgrad_strided_onepass_gemm(a_full, [d[1][0], d[1][1]], [0, H], [H, H], [wq["w1"][2], wq["w3"][2]],
+        gmx.mxfp4_split2_dgrad_strided_onepass_gemm(a_full, [d[1][0], d[1][1]], [0, H // 2], [H // 2, H // 2], [wq["w1"][2], wq["w3"][2]],
                                                     [wq["w1"][3], wq["w3"][3]], dxf, -1)
     def s_w13_wgrad():
         d, f = st["gd"], st["qx"]

@@ -287,12 +287,15 @@ int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg,
  * multiply-add), one rounding to bf16, one store.  A term's A may be a column slice of a wider matrix, which is what
  * nvfp4_split_dgrad_sum (nvfp4_b200_gemm.cu:2424-2565) needs: A_pitch_bytes[i] is then the row pitch of its codes
  * (NULL or 0: K[i]/2) and A_sc_row_tiles[i] the number of 512-byte scale tiles between consecutive 128-row blocks of
- * its scale tensor (NULL or 0: K[i]/64).  Needs M % 256 == 0 (two-CTA kernel); otherwise chain fp4b200_nvfp4_gemm
+ * its scale tensor (NULL or 0: K[i]/64).  round_each_term = 1 gives nvfp4_split_dgrad_sum's arithmetic instead of
+ * nvfp4_batched_accum_gemm's: the reference runs a batched GEMM into one bf16 matrix per split and adds those with
+ * Tensor.add_ (nvfp4_b200_gemm.cu:2466-2487), so every term is rounded to bf16 and the running sum is rounded to bf16
+ * after every addition, left to right.  Needs M % 256 == 0 (two-CTA kernel); otherwise chain fp4b200_nvfp4_gemm
  * (fp32 output) and fp4b200_nvfp4_gemm_accum. */
 int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const void* const* A_sc, const float* const* A_sg,
                                      const void* const* B, const void* const* B_sc, const float* const* B_sg,
                                      const int64_t* K, const int64_t* A_pitch_bytes, const int64_t* A_sc_row_tiles, void* D,
-                                     int64_t M, int64_t N, void* stream);
+                                     int64_t M, int64_t N, int round_each_term, void* stream);
 
 /* nvfp4_grouped_gemm (nvfp4_b200_gemm.cu:764-841): B is the row concatenation of n_out weights,
  * B_sg_per_tile holds one tensor scale per 256 rows of B, output i receives D_cols[i] columns

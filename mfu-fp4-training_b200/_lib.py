@@ -75,7 +75,7 @@ SIGNATURES = {
     "fp4b200_nvfp4_batched_accum_gemm": [_int, ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
                                          ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
                                          ctypes.POINTER(_i64), ctypes.POINTER(_i64), ctypes.POINTER(_i64), _c_void_p, _i64, _i64,
-                                         _c_void_p],
+                                         _int, _c_void_p],
     "fp4b200_nvfp4_grouped_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int,
                                    ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _i64, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p, _i64, _i64,

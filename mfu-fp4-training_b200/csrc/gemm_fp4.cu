@@ -77,6 +77,7 @@ struct GemmArgs {
   // Batched accumulation (kEpiBatchSum): every segment is a GEMM term of its own — its own A tensor (tensor map
   // tmap_a_seg.m[s]) and its own tensor scales; the terms' scaled accumulators are summed in fp32 by the epilogue.
   int a_per_seg;
+  int round_terms;          // batched accumulation: every term rounded to bf16, terms added in bf16 left to right
   const float* seg_a_sg[kMaxKSeg];
   const float* seg_b_sg[kMaxKSeg];
   const float* a_sg;        // device scalar (NVFP4) or null
@@ -560,6 +561,8 @@ __device__ __forceinline__ void epilogue_wide(const GemmArgs& g, const GemmOutMa
 // terms: fma(acc, scale, sum), the reference's order (nvfp4_batched_accum_gemm.cuh:293-310 as compiled) — 16 columns
 // at a time, releases the accumulator, and after the last term rounds the sum to bf16 and stores it.
 // acc_phase: the parity the warp waits for next; returns false when a wait ran out.
+__device__ __forceinline__ float bf16_round_f32(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
+
 __device__ __forceinline__ bool epilogue_batch_sum(const GemmArgs& g, const GemmOutMaps& tmap_d, uint64_t* acc_full, uint32_t& acc_phase,
                                                    uint32_t taddr, uint8_t* epi, int row0, int col0, int lane,
                                                    uint32_t release_cluster_addr) {
@@ -577,7 +580,14 @@ __device__ __forceinline__ bool epilogue_batch_sum(const GemmArgs& g, const Gemm
       uint32_t r[16];
       tmem_ld16(taddr + (uint32_t)(16 * c), r);
       tmem_ld_wait();
-      if (term == 0) {
+      if (g.round_terms) {
+        // every term as the bf16 matrix a GEMM of its own would have written, added to the bf16 sum so far
+#pragma unroll
+        for (int q = 0; q < 16; ++q) {
+          const float t = bf16_round_f32(__fmul_rn(__uint_as_float(r[q]), gs));
+          sum[16 * c + q] = term == 0 ? t : bf16_round_f32(__fadd_rn(sum[16 * c + q], t));
+        }
+      } else if (term == 0) {
 #pragma unroll
         for (int q = 0; q < 16; ++q) sum[16 * c + q] = __fmul_rn(__uint_as_float(r[q]), gs);
       } else {
@@ -855,6 +865,7 @@ struct KSegments {
   // batched accumulation (two-CTA kernel only): every segment is a term with its own A tensor [M, k/2] and tensor scales,
   // summed in fp32 by the epilogue instead of in tensor memory
   bool batch_sum = false;
+  bool round_terms = false;   // with batch_sum: bf16(term) summed in bf16, left to right, instead of one fp32 sum
   const void* a[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
   const float* a_sg[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
   const float* b_sg[kMaxKSeg] = {nullptr, nullptr, nullptr, nullptr};
@@ -913,6 +924,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     g.seg_b_sg[s] = segs.b_sg[s];
   }
   g.a_per_seg = segs.batch_sum ? 1 : 0;
+  g.round_terms = (segs.batch_sum && segs.round_terms) ? 1 : 0;
   GemmOutMaps omaps;
   memset(&omaps, 0, sizeof(omaps));
   for (int i = 0; i < n_out; ++i) {
@@ -1079,7 +1091,7 @@ int fp4b200_nvfp4_gemm_accum(const void* A, const void* A_sc, const float* A_sg,
 int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const void* const* A_sc, const float* const* A_sg,
                                      const void* const* B, const void* const* B_sc, const float* const* B_sg,
                                      const int64_t* K, const int64_t* A_pitch_bytes, const int64_t* A_sc_row_tiles, void* D,
-                                     int64_t M, int64_t N, void* stream) {
+                                     int64_t M, int64_t N, int round_each_term, void* stream) {
   const char* fn = "nvfp4_batched_accum_gemm";
   if (n_terms < 1 || n_terms > kMaxKSeg) return set_error("%s: 1 to %d terms (got %d)", fn, kMaxKSeg, n_terms);
   if (!A || !A_sc || !A_sg || !B || !B_sc || !B_sg || !K || !D) return set_error("%s: null argument", fn);
@@ -1089,6 +1101,7 @@ int fp4b200_nvfp4_batched_accum_gemm(int n_terms, const void* const* A, const vo
   KSegments segs;
   segs.n = n_terms;
   segs.batch_sum = true;
+  segs.round_terms = round_each_term != 0;
   for (int i = 0; i < n_terms; ++i) {
     if (int rc = check_gemm(A[i], A_sc[i], B[i], B_sc[i], M, N, K[i], fn)) return rc;
     if (!A_sg[i] || !B_sg[i]) return set_error("%s: every term needs its tensor scales", fn);

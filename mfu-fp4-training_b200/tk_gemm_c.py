@@ -266,7 +266,7 @@ def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_
             def arr(ts):
                 return (ctypes.c_void_p * n)(*[t.data_ptr() for t in ts])
             _lib.call("fp4b200_nvfp4_batched_accum_gemm", n, arr(A_list), arr(A_sc_list), arr(A_sg_list), arr(B_list),
-                      arr(B_sc_list), arr(B_sg_list), (ctypes.c_int64 * n)(*Ks), None, None, D_out.data_ptr(), M, N,
+                      arr(B_sc_list), arr(B_sg_list), (ctypes.c_int64 * n)(*Ks), None, None, D_out.data_ptr(), M, N, 0,
                       _stream(A_list[0]))
             return
         partial = torch.empty((M, N), dtype=torch.float32, device=D_out.device)
@@ -281,9 +281,10 @@ def nvfp4_batched_accum_gemm(A_list, A_sc_list, A_sg_list, B_list, B_sc_list, B_
 
 def nvfp4_split_dgrad_sum(A_fp4_cat, A_sc_cat, A_sg_list, B_fp4_list, B_sc_list, B_sg_cat, split_dims, D_out):
     """nvfp4_b200_gemm.cu:2424-2565: dgrad of a fused projection — the row-quantised gradient is the column
-    concatenation of the splits; term i multiplies columns of split i by the column-quantised weight i.
-    One launch over the column slices where they are (M a multiple of 256, up to four splits); otherwise the slices
-    are made contiguous and the terms are chained."""
+    concatenation of the splits; term i multiplies columns of split i by the column-quantised weight i.  The
+    reference multiplies every split into a bf16 matrix of its own and adds those with ``Tensor.add_``, so every term
+    and every partial sum is rounded to bf16; so here.  One launch over the column slices where they are (M a multiple
+    of 256, up to four splits; the epilogue rounds as described); otherwise one GEMM per split and ``add_``."""
     n = len(split_dims)
     if any(d % 128 for d in split_dims):
         raise RuntimeError("nvfp4_split_dgrad_sum: split sizes must be multiples of 128")
@@ -314,16 +315,20 @@ def nvfp4_split_dgrad_sum(A_fp4_cat, A_sc_cat, A_sg_list, B_fp4_list, B_sc_list,
             _lib.call("fp4b200_nvfp4_batched_accum_gemm", n, vp(*a_ptrs), vp(*sc_ptrs), vp(*[t.data_ptr() for t in A_sg_list]),
                       vp(*[t.data_ptr() for t in B_fp4_list]), vp(*[t.data_ptr() for t in B_sc_list]),
                       vp(*[B_sg_cat.data_ptr() + 4 * i for i in range(n)]), i64(*split_dims), i64(*([k_total // 2] * n)),
-                      i64(*([k_total // 64] * n)), D_out.data_ptr(), M, N, _stream(A_fp4_cat))
+                      i64(*([k_total // 64] * n)), D_out.data_ptr(), M, N, 1, _stream(A_fp4_cat))
         return
+    # as the reference: one GEMM per split into a bf16 matrix of its own, then Tensor.add_ left to right
     offs = 0
-    A_list, A_sc_l, B_sg_l = [], [], []
     for i, d in enumerate(split_dims):
-        A_list.append(a_u8[:, offs // 2:(offs + d) // 2].contiguous())
-        A_sc_l.append(sc_u8[:, offs // 64:(offs + d) // 64, :].contiguous())
-        B_sg_l.append(B_sg_cat.narrow(0, i, 1))
+        a_i = a_u8[:, offs // 2:(offs + d) // 2].contiguous()
+        sc_i = sc_u8[:, offs // 64:(offs + d) // 64, :].contiguous()
+        if i == 0:
+            _gemm(a_i, sc_i, A_sg_list[i], B_fp4_list[i], B_sc_list[i], B_sg_cat.narrow(0, i, 1), D_out)
+        else:
+            term = torch.empty_like(D_out)
+            _gemm(a_i, sc_i, A_sg_list[i], B_fp4_list[i], B_sc_list[i], B_sg_cat.narrow(0, i, 1), term)
+            D_out.add_(term)
         offs += d
-    nvfp4_batched_accum_gemm(A_list, A_sc_l, list(A_sg_list), list(B_fp4_list), list(B_sc_list), B_sg_l, D_out)
 
 
 def nvfp4_row_rms_reduce(row_rms_partial, coeff, hidden_size, eps):

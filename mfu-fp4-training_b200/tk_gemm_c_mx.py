@@ -48,7 +48,9 @@ def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_
                                             config_idx=-1):
     """mxfp4_gb200_gemm.cu:2572-2596 — ``D_out = bf16((sum_s A_full[:, off_s:off_s+w_s] . B_s^T) / 36)``: the
     row-quantised gradient of a fused projection is the column concatenation of the splits; every term is
-    accumulated in tensor memory before the one rounding.  ``config_idx`` is accepted and ignored."""
+    accumulated in tensor memory before the one rounding.  ``A_col_offsets`` / ``A_col_widths`` count PACKED columns
+    (bytes of ``A_full``, two elements each), as the reference's do (checks at :430-467).  ``config_idx`` is accepted
+    and ignored."""
     import ctypes
     n = len(B_list)
     if n != 2:
@@ -63,12 +65,17 @@ def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_
     N = B_list[0].view(torch.uint8).shape[0]
     for B, w in zip(B_list, A_col_widths):
         b = B.view(torch.uint8)
-        if b.shape[0] != N or b.shape[1] * 2 != int(w):
-            raise RuntimeError("split2 one-pass dgrad: each B must be [N, width/2]")
+        if b.shape[0] != N or b.shape[1] != int(w):
+            raise RuntimeError("B_list packed K must match A_col_widths")
+    for off, w in zip(A_col_offsets, A_col_widths):
+        if int(off) < 0 or int(w) <= 0 or int(off) + int(w) > a.shape[1]:
+            raise RuntimeError("A_full slice exceeds packed width")
+        if (int(w) * 2) % 128:
+            raise RuntimeError("split widths must be multiples of 128")
     out_fp32 = 1 if D_out.dtype == torch.float32 else 0
     _chk_out(D_out, M, N, D_out.dtype if out_fp32 else torch.bfloat16)
-    offs = (ctypes.c_int64 * n)(*[int(v) for v in A_col_offsets])
-    widths = (ctypes.c_int64 * n)(*[int(v) for v in A_col_widths])
+    offs = (ctypes.c_int64 * n)(*[2 * int(v) for v in A_col_offsets])      # the library counts elements
+    widths = (ctypes.c_int64 * n)(*[2 * int(v) for v in A_col_widths])
     a_sc = (ctypes.c_void_p * n)(*[t.data_ptr() for t in A_sc_list])
     b_p = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B_list])
     b_sc = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B_sc_list])

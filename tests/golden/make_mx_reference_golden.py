@@ -85,6 +85,7 @@ def load_reference_module():
 
 
 GEMM_SHAPES = [(256, 256, 512), (256, 512, 1280)]   # M, N, K
+ONEPASS = (256, 256, 512)                           # M, N, width of each of the two splits
 
 
 def gemm_operands(shape, seed):
@@ -132,6 +133,24 @@ def main():
             ref_gemm.mxfp4_gemm_residual(qa[0], qa[1], qb[0], qb[1], r, d)
             torch.cuda.synchronize()
             out[f"gemm_{i}.d_residual"] = d.view(torch.int16).cpu().numpy()
+    if ref_gemm is not None:
+        # the one-pass split2 dgrad (A = column concatenation of two row-quantised gradients, one weight per split,
+        # all terms accumulated before the one rounding) and two batched products
+        Mo, No, w = ONEPASS
+        g1, g2 = (torch.from_numpy(gemm_operands((Mo, 1, w), 720 + i)[0] * 1e-3).to(torch.bfloat16).to(dev) for i in range(2))
+        q1, q2 = ref.mxfp4_quantize_for_gemm(g1, 1), ref.mxfp4_quantize_for_gemm(g2, 1)
+        a_full = torch.cat([q1[0].view(torch.uint8), q2[0].view(torch.uint8)], dim=1).contiguous()
+        ws = [ref.mxfp4_quantize_for_gemm(torch.from_numpy(gemm_operands((1, No, w), 730 + i)[1]).to(torch.bfloat16).to(dev), 1)
+              for i in range(2)]
+        d = torch.empty(Mo, No, dtype=torch.bfloat16, device=dev)
+        ref_gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q2[1]], [0, w // 2], [w // 2, w // 2],
+                                                         [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], d, -1)
+        torch.cuda.synchronize()
+        out["onepass.d"] = d.view(torch.int16).cpu().numpy()
+        d1, d2 = torch.empty_like(d), torch.empty_like(d)
+        ref_gemm.mxfp4_batched_gemm([q1[0], q2[0]], [q1[1], q2[1]], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], [d1, d2])
+        torch.cuda.synchronize()
+        out["batched.0"], out["batched.1"] = d1.view(torch.int16).cpu().numpy(), d2.view(torch.int16).cpu().numpy()
     dst = os.environ.get("MX_GOLDEN_OUT", os.path.join(HERE, "mxfp4_reference_kernels_golden.npz"))
     np.savez_compressed(dst, **out)
     print(f"wrote {dst}: {len(out)} arrays, {os.path.getsize(dst)} bytes")

@@ -75,3 +75,24 @@ def test_mxfp4_gemm_reproduces_the_reference_kernels_bytes(idx):
     torch.cuda.synchronize()
     assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD[f"gemm_{idx}.d_residual"])
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "onepass.d" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+def test_mxfp4_onepass_split2_dgrad_and_batched_gemm_reproduce_the_reference_kernels_bytes():
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    Mo, No, w = G.ONEPASS
+    g1, g2 = ((torch.from_numpy(G.gemm_operands((Mo, 1, w), 720 + i)[0] * 1e-3).to(torch.bfloat16).cuda()) for i in range(2))
+    q1, q2 = mxq.mxfp4_quantize_for_gemm(g1, 1), mxq.mxfp4_quantize_for_gemm(g2, 1)
+    a_full = torch.cat([q1[0].view(torch.uint8), q2[0].view(torch.uint8)], dim=1).contiguous()
+    ws = [mxq.mxfp4_quantize_for_gemm(to_dev_bf16(G.gemm_operands((1, No, w), 730 + i)[1]), 1) for i in range(2)]
+    d = torch.empty(Mo, No, dtype=torch.bfloat16, device="cuda")
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q2[1]], [0, w // 2], [w // 2, w // 2],
+                                                 [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], d, -1)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD["onepass.d"])
+    d1, d2 = torch.empty_like(d), torch.empty_like(d)
+    gemm.mxfp4_batched_gemm([q1[0], q2[0]], [q1[1], q2[1]], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], [d1, d2])
+    torch.cuda.synchronize()
+    assert np.array_equal(d1.view(torch.int16).cpu().numpy(), GOLD["batched.0"])
+    assert np.array_equal(d2.view(torch.int16).cpu().numpy(), GOLD["batched.1"])
+    assert_status_ok()

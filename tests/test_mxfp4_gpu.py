@@ -123,10 +123,10 @@ def test_mxfp4_split2_dgrad_onepass(M):
     qw1, qw3 = mxq.mxfp4_quantize_for_gemm(to_dev_bf16(w1), 1), mxq.mxfp4_quantize_for_gemm(to_dev_bf16(w3), 1)
     a_full = torch.cat([q1[0].view(torch.uint8), q3[0].view(torch.uint8)], dim=1).contiguous()
     d = torch.empty((M, N), dtype=torch.float32, device="cuda")
-    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H // 2], [H // 2, H // 2],
                                                  [qw1[0], qw3[0]], [qw1[1], qw3[1]], d, -1)
     d16 = torch.empty((M, N), dtype=torch.bfloat16, device="cuda")
-    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H // 2], [H // 2, H // 2],
                                                  [qw1[0], qw3[0]], [qw1[1], qw3[1]], d16)
     torch.cuda.synchronize()
     r1, r3 = o.mxfp4_quantize_1d(dh1, 1), o.mxfp4_quantize_1d(dh3, 1)
@@ -139,7 +139,7 @@ def test_mxfp4_split2_dgrad_onepass(M):
     assert rel <= 1e-3 and rel < 1e-5, rel
     assert np.abs(d16.float().cpu().numpy() - o.bf16_round(ref.astype(np.float32))).max() <= np.abs(ref).max() * 2.0 ** -7
     with pytest.raises(RuntimeError):
-        gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H], [H, H],
+        gemm.mxfp4_split2_dgrad_strided_onepass_gemm(a_full.view(torch.float4_e2m1fn_x2), [q1[1], q3[1]], [0, H // 2], [H // 2, H // 2],
                                                      [qw1[0]], [qw1[1]], d)
     assert_status_ok()
 

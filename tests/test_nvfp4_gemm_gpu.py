@@ -163,7 +163,8 @@ def test_batched_accum_forms_against_the_oracle_order(M, Ks):
 @pytest.mark.parametrize("M", [256, 384])       # one launch over the column slices / chained launches over copies
 def test_split_dgrad_sum_reads_the_slices_where_they_are(M):
     """nvfp4_split_dgrad_sum on the column concatenation that the three-stream gradient quantiser produces (own tensor
-    scale per stream) against nvfp4_batched_accum_gemm on contiguous copies of the slices."""
+    scale per stream) against the reference's arithmetic for it (nvfp4_b200_gemm.cu:2466-2487): one GEMM per split on
+    a contiguous copy of its slice into a bf16 matrix of its own, then Tensor.add_ left to right."""
     tkq, gemm = mod("tk_quant_v5"), mod("tk_gemm_c")
     splits, n_out = [512, 256, 256], 512
     rng = np.random.default_rng(M)
@@ -183,7 +184,11 @@ def test_split_dgrad_sum_reads_the_slices_where_they_are(M):
         Asc.append(sc_u8[:, off // 64:(off + dd) // 64, :].contiguous())
         off += dd
     want = torch.empty_like(d)
-    gemm.nvfp4_batched_accum_gemm(A, Asc, a_sg_list, [w[0] for w in ws], [w[1] for w in ws], [w[4] for w in ws], want)
+    for i in range(3):
+        term = want if i == 0 else torch.empty_like(d)
+        gemm.nvfp4_gemm(A[i], Asc[i], a_sg_list[i], ws[i][0], ws[i][1], ws[i][4], term)
+        if i:
+            want.add_(term)
     torch.cuda.synchronize()
     assert torch.equal(d, want)
     assert_status_ok()
