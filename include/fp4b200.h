@@ -208,6 +208,12 @@ int fp4b200_mxfp4_quantize_normed(const void* x_bf16, const void* gamma_bf16, co
  * fp4b200_mxfp4_quantize_normed for mxfp4_fused_rmsnorm_quantize_row_and_col. */
 int fp4b200_mxfp4_rmsnorm_inv_rms(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
                                   float* inv_rms, void* stream);
+/* The same in the order of the inverse-RMS kernel that runs in front of tk_fused_norm_quantize_opt's stochastic forms
+ * (nvfp4_v5/fused_norm_quantize.cuh:391-434: 256 threads, thread t takes the single elements t, t + 256, ...; xor
+ * butterflies inside the warps, then over the eight warp sums) — a third tree, again different in the last bit of
+ * some rows from the one tk_fused_norm_quantize uses. */
+int fp4b200_nvfp4_rmsnorm_inv_rms_opt(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
+                                      float* inv_rms, void* stream);
 
 /* ---- SwiGLU producers ------------------------------------------------------------------ */
 

@@ -167,6 +167,37 @@ __device__ __forceinline__ float stats_inv_rms_mx(const uint4 (&v)[NV], int K, f
   return rsqrtf(s / static_cast<float>(K) + eps);
 }
 
+// And for the tree of the inverse-RMS kernel in front of the reference's optional-mode fused producer
+// (nvfp4_v5/fused_norm_quantize.cuh:391-434, inv_rms_kernel_ns::compute_inv_rms_kernel<256>): thread t accumulates the
+// single elements t, t + 256, ...; xor butterflies over 16,8,4,2,1 inside a warp, then 4,2,1 over the eight warp sums.
+// Element e of lane L's vector j is element 256 j + 8 L + e of the row: that kernel's thread 8 L + e, i.e. warp L / 4,
+// lane 8 (L % 4) + e — so its masks 16 and 8 are shuffles over this warp's lane masks 2 and 1, its masks 4,2,1 register
+// adds over e, and the warp sums meet by shuffles over lane masks 16, 8, 4.
+template <int NV>
+__device__ __forceinline__ float stats_inv_rms_strided(const uint4 (&v)[NV], int K, float eps) {
+  float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+  for (int j = 0; j < NV; ++j) {
+    const uint32_t w[4] = {v[j].x, v[j].y, v[j].z, v[j].w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float lo = bf16lo_to_f32(w[q]), hi = bf16hi_to_f32(w[q]);
+      acc[2 * q] = fmaf(lo, lo, acc[2 * q]);
+      acc[2 * q + 1] = fmaf(hi, hi, acc[2 * q + 1]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) {
+    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+    acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+  }
+  float s = ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
+  s += __shfl_xor_sync(0xffffffffu, s, 16);
+  s += __shfl_xor_sync(0xffffffffu, s, 8);
+  s += __shfl_xor_sync(0xffffffffu, s, 4);
+  return rsqrtf(s / static_cast<float>(K) + eps);
+}
+
 // Running maximum of |(x * inv) * gamma| in fp32 over the row held in v.  Rounding to bf16 is
 // monotonic, so the tensor amax of the bf16 values is the bf16 rounding of this maximum: no
 // per-element conversion.  gamma is read as fp32 from two shared-memory tables (elements 0-3 and
@@ -203,7 +234,7 @@ __device__ __forceinline__ float stats_row_amax(const uint4 (&v)[NV], const floa
 // then), refills the slot with the row `slots` further on.  Bytes in flight per SM are set by the ring,
 // not by registers or by the number of warps, which is what a streaming reduction at HBM speed needs;
 // rows are handed out one at a time, so the warps of a CTA finish within one row of each other.
-template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS, bool MX_TREE = false>
+template <int NV /* 16-byte vectors held per lane; K <= NV*256 */, bool COMPUTE_INV_RMS, int TREE = 0 /* 1: the MXFP4 producer's summation tree, 2: the optional-mode NVFP4 producer's */>
 __global__ void __launch_bounds__(NV <= 16 ? kStatsMaxWarps * 32 : 192, 1)
 rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ gamma,
                      float* __restrict__ inv_rms, float* __restrict__ partials, float eps, int M, int K,
@@ -291,7 +322,8 @@ rmsnorm_stats_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
     const size_t row = row_of(r);
     float inv;
     if constexpr (COMPUTE_INV_RMS) {
-      if constexpr (MX_TREE) inv = stats_inv_rms_mx<NV>(v, K, eps);
+      if constexpr (TREE == 1) inv = stats_inv_rms_mx<NV>(v, K, eps);
+      else if constexpr (TREE == 2) inv = stats_inv_rms_strided<NV>(v, K, eps);
       else inv = stats_inv_rms<NV>(v, K, eps);
       if (lane == 0) {
         inv_rms[row] = inv;
@@ -483,7 +515,32 @@ rmsnorm_stats_generic_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfl
   for (int row = warp_global; row < M; row += n_warps) {
     const uint4* xr = reinterpret_cast<const uint4*>(x + (size_t)row * K);
     float inv;
-    if (COMPUTE_INV_RMS && mx_tree) {
+    if (COMPUTE_INV_RMS && mx_tree == 2) {
+      // the optional-mode NVFP4 producer's tree (see stats_inv_rms_strided); inverse RMS only
+      float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+      for (int q = lane; q < nvec_row; q += 32) {
+        const uint4 vv = __ldg(xr + q);
+        const uint32_t w[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float lo = bf16lo_to_f32(w[e]), hi = bf16hi_to_f32(w[e]);
+          acc[2 * e] = fmaf(lo, lo, acc[2 * e]);
+          acc[2 * e + 1] = fmaf(hi, hi, acc[2 * e + 1]);
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 2);
+        acc[e] += __shfl_xor_sync(0xffffffffu, acc[e], 1);
+      }
+      float s = ((acc[0] + acc[4]) + (acc[2] + acc[6])) + ((acc[1] + acc[5]) + (acc[3] + acc[7]));
+      s += __shfl_xor_sync(0xffffffffu, s, 16);
+      s += __shfl_xor_sync(0xffffffffu, s, 8);
+      s += __shfl_xor_sync(0xffffffffu, s, 4);
+      if (lane == 0) inv_rms[row] = rsqrtf(s / static_cast<float>(K) + eps);
+      continue;
+    }
+    if (COMPUTE_INV_RMS && mx_tree == 1) {
       // the MXFP4 producer's tree (see stats_inv_rms_mx); inverse RMS only
       float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
       for (int q0 = 0; q0 < nvec_row; q0 += 256) {
@@ -2155,10 +2212,10 @@ static int stats_slots_for(int64_t K) {
   return (int)std::max<int64_t>(0, std::min<int64_t>(budget / (K * 2), 64));
 }
 
-template <int NV, bool CI, bool MX_TREE = false>
+template <int NV, bool CI, int TREE = 0>
 static int launch_stats_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb, float* inv_rms, float* partials, float eps,
                           int64_t M, int64_t K, int slots, int* status, cudaStream_t st, int* grid_out, int want_amax) {
-  auto kern = rmsnorm_stats_kernel<NV, CI, MX_TREE>;
+  auto kern = rmsnorm_stats_kernel<NV, CI, TREE>;
   const int warps = std::min(NV <= 16 ? kStatsMaxWarps : 6, slots);
   const size_t smem = (size_t)K * 4 + (size_t)slots * K * 2 + (size_t)slots * 12;
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
@@ -2203,7 +2260,7 @@ static int launch_stats_pair_t(const __nv_bfloat16* xb, const __nv_bfloat16* gb,
 // launched next.
 static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms, float* amax_sg, float eps,
                                 int64_t M, int64_t K, bool compute_inv, cudaStream_t st, float* scratch = nullptr,
-                                AmaxPartials* partials_out = nullptr, bool mx_tree = false) {
+                                AmaxPartials* partials_out = nullptr, int tree = 0) {
   if ((reinterpret_cast<uintptr_t>(gamma) & 15) != 0) return set_error("rmsnorm statistics: gamma must be 16-byte aligned");
   if (scratch == nullptr) scratch = stream_scratch(st);
   if (scratch == nullptr) return -1;
@@ -2217,11 +2274,16 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
     int* status = device_status_ptr();
     if (status == nullptr) return -1;
     int rc;
-    if (mx_tree) {   // inverse RMS only, in the MXFP4 producer's summation order: one warp per row
-      if (K <= 1024) rc = launch_stats_t<4, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
-      else if (K <= 2048) rc = launch_stats_t<8, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
-      else if (K <= 4096) rc = launch_stats_t<16, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
-      else rc = launch_stats_t<32, true, true>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+    if (tree == 1) {   // inverse RMS only, in the MXFP4 producer's summation order: one warp per row
+      if (K <= 1024) rc = launch_stats_t<4, true, 1>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else if (K <= 2048) rc = launch_stats_t<8, true, 1>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else if (K <= 4096) rc = launch_stats_t<16, true, 1>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else rc = launch_stats_t<32, true, 1>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+    } else if (tree == 2) {   // the same for the optional-mode NVFP4 producer's
+      if (K <= 1024) rc = launch_stats_t<4, true, 2>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else if (K <= 2048) rc = launch_stats_t<8, true, 2>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else if (K <= 4096) rc = launch_stats_t<16, true, 2>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
+      else rc = launch_stats_t<32, true, 2>(xb, gb, inv_rms, scratch, eps, M, K, slots, status, st, &grid, 0);
     } else
     if (stats_pair_enabled()) {
       if (K <= 1024) rc = compute_inv ? launch_stats_pair_t<2, true>(xb, gb, inv_rms, scratch, eps, M, K, status, st, &grid, want_amax)
@@ -2244,7 +2306,7 @@ static int launch_rmsnorm_stats(const void* x, const void* gamma, float* inv_rms
     if (rc) return rc;
   } else {
     grid = (int)std::min<int64_t>((M + 7) / 8, std::min<int64_t>((int64_t)device_sm_count() * 8, kScratchFloats));
-    if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K, mx_tree ? 1 : 0);
+    if (compute_inv) rmsnorm_stats_generic_kernel<true><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K, tree);
     else rmsnorm_stats_generic_kernel<false><<<grid, 256, 0, st>>>(xb, gb, inv_rms, scratch, eps, (int)M, (int)K, 0);
     FP4_CUDA_CHECK(cudaGetLastError());
   }
@@ -2476,7 +2538,15 @@ int fp4b200_mxfp4_rmsnorm_inv_rms(const void* x_bf16, const void* gamma_bf16, fl
   if (int rc = check_quant_shapes(x_bf16, M, K, "mxfp4_rmsnorm_inv_rms")) return rc;
   if (gamma_bf16 == nullptr || inv_rms == nullptr) return set_error("mxfp4_rmsnorm_inv_rms: gamma and inv_rms are required");
   return launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, nullptr, eps, M, K, true, (cudaStream_t)stream, nullptr, nullptr,
-                              true);
+                              1);
+}
+
+int fp4b200_nvfp4_rmsnorm_inv_rms_opt(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M, int64_t K,
+                                      float* inv_rms, void* stream) {
+  if (int rc = check_quant_shapes(x_bf16, M, K, "nvfp4_rmsnorm_inv_rms_opt")) return rc;
+  if (gamma_bf16 == nullptr || inv_rms == nullptr) return set_error("nvfp4_rmsnorm_inv_rms_opt: gamma and inv_rms are required");
+  return launch_rmsnorm_stats(x_bf16, gamma_bf16, inv_rms, nullptr, eps, M, K, true, (cudaStream_t)stream, nullptr, nullptr,
+                              2);
 }
 
 int fp4b200_nvfp4_fused_norm_quantize(const void* x_bf16, const void* gamma_bf16, float eps, int64_t M,

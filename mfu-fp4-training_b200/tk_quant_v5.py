@@ -559,8 +559,13 @@ def tk_quantize_transpose(input, amax_row, amax_col, return_transpose, stochasti
     with torch.cuda.device(input.device):
         out = _launch_opt(input, amax_row, amax_col, return_transpose, stochastic_rounding, encode_centric, row_rht,
                           col_rht, return_row, 0, 0, False, 0, 0, scale_sr=scale_stochastic_rounding, rng_state=state)
-    empty = torch.empty((0,), dtype=torch.uint8, device=input.device)
-    return tuple(empty if t is None else t for t in out)
+    # shapes as the reference returns them: scale bytes as [rows, blocks per row] (the bytes are in the GEMM's tile order)
+    M, K = input.shape
+    # With return_row = False the reference still returns row tensors of full shape that nothing has written; so here.
+    u8 = dict(dtype=torch.uint8, device=input.device)
+    rf, rs, cf, cs = out
+    return (torch.empty((M, K // 2), **u8) if rf is None else rf, torch.empty((M, K // 16), **u8) if rs is None else rs.view(M, K // 16),
+            torch.empty((0,), **u8) if cf is None else cf, torch.empty((0,), **u8) if cs is None else cs.view(K, M // 16))
 
 
 def tk_quantize_for_gemm_opt(input, return_transpose=True, encode_centric=True, data_stochastic_rounding=False,
@@ -652,8 +657,11 @@ def tk_fused_norm_quantize_opt(input, gamma, epsilon, return_transpose=True, enc
     with torch.cuda.device(input.device):
         inv_rms = torch.empty(M, dtype=torch.float32, device=input.device)
         col_amax = torch.empty(2, dtype=torch.float32, device=input.device)
+        # inverse RMS in the summation order of this producer's own kernel, then the tensor maximum with it
+        _lib.call("fp4b200_nvfp4_rmsnorm_inv_rms_opt", input.data_ptr(), gamma.data_ptr(), float(epsilon), M, K,
+                  inv_rms.data_ptr(), _stream(input))
         _lib.call("fp4b200_nvfp4_rmsnorm_stats", input.data_ptr(), gamma.data_ptr(), float(epsilon), M, K,
-                  inv_rms.data_ptr(), 1, col_amax.data_ptr(), _stream(input))
+                  inv_rms.data_ptr(), 0, col_amax.data_ptr(), _stream(input))
         row_amax = _amax_rht(input, True, False, 0, 0, gamma, inv_rms)
         state = _reserve_sr(input, rng_seed, rng_subsequence, sr or scale_sr)
         rf, rs, cf, cs = _launch_opt(input, row_amax, col_amax, True, sr, encode_centric, True, False, True, rng_seed,
