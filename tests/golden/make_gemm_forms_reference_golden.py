@@ -11,6 +11,7 @@ grid-wide barrier) and STORED in the fixture, so that the tests feed the same pa
   nvfp4_batched_gemm                                       two independent products
   nvfp4_split_dgrad_sum                                    two column slices of one A, summed in fp32
   nvfp4_row_rms_reduce                                     inverse RMS from row partials
+  nvfp4_quantize, fp32_to_fp4x2, fp4x2_to_fp32             the module's own tile quantiser and code conversions
 
     python tests/golden/make_gemm_forms_reference_golden.py   # writes tests/golden/nvfp4_gemm_forms_reference_golden.npz
 """
@@ -81,6 +82,19 @@ def main():
     inv = torch.empty(M, dtype=torch.float32, device=dev)
     c.nvfp4_row_rms_reduce(part, inv, 4096, 1e-5)
     out["row_rms_reduce"] = inv.cpu().numpy()
+    # the module's own tile quantiser (1 x 16 and 16 x 16 blocks) and the code conversions
+    src = t(normal(256, 384, 660))
+    for tag, two_d in (("tkq_1d", False), ("tkq_2d", True)):
+        fp4 = torch.empty(256, 192, dtype=torch.uint8, device=dev).view(torch.float4_e2m1fn_x2)
+        sc = torch.empty(256 // 128, 384 // 64, 512, dtype=torch.uint8, device=dev).view(torch.float8_e4m3fn)
+        sg = torch.empty(1, dtype=torch.float32, device=dev)
+        c.nvfp4_quantize(src, fp4, sc, sg, two_d)
+        torch.cuda.synchronize()
+        out[f"{tag}.fp4"], out[f"{tag}.sc"], out[f"{tag}.sg"] = u8(fp4), u8(sc), sg.cpu().numpy()
+    f32 = torch.from_numpy((np.random.default_rng(661).standard_normal((64, 128)) * 3.0).astype(np.float32)).to(dev)
+    codes = c.fp32_to_fp4x2(f32)
+    out["fp32_to_fp4x2"] = u8(codes)
+    out["fp4x2_to_fp32"] = c.fp4x2_to_fp32(codes).cpu().numpy()
     torch.cuda.synchronize()
     dst = os.environ.get("GEMM_FORMS_GOLDEN_OUT", os.path.join(HERE, "nvfp4_gemm_forms_reference_golden.npz"))
     np.savez_compressed(dst, **out)

@@ -71,3 +71,25 @@ def test_gemm_forms_reproduce_the_reference_kernels_outputs():
     torch.cuda.synchronize()
     assert np.array_equal(inv.cpu().numpy(), GOLD["row_rms_reduce"])
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "tkq_1d.fp4" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+def test_tile_quantiser_and_code_conversions_reproduce_the_reference_kernels_bytes():
+    gemm = mod("tk_gemm_c")
+    src = to_dev_bf16(normal(256, 384, 660))
+    for tag, two_d in (("tkq_1d", False), ("tkq_2d", True)):
+        fp4 = torch.empty(256, 192, dtype=torch.uint8, device="cuda").view(torch.float4_e2m1fn_x2)
+        sc = torch.empty(2, 6, 512, dtype=torch.uint8, device="cuda").view(torch.float8_e4m3fn)
+        sg = torch.empty(1, dtype=torch.float32, device="cuda")
+        gemm.nvfp4_quantize(src, fp4, sc, sg, two_d)
+        torch.cuda.synchronize()
+        for key, got in ((f"{tag}.fp4", fp4), (f"{tag}.sc", sc)):
+            got = got.view(torch.uint8).cpu().numpy().reshape(-1)
+            bad = int((got != GOLD[key].reshape(-1)).sum())
+            assert bad == 0, f"{key}: {bad} of {got.size} bytes differ from the reference kernel's"
+        assert sg.item() == GOLD[f"{tag}.sg"].reshape(-1)[0]
+    f32 = torch.from_numpy((np.random.default_rng(661).standard_normal((64, 128)) * 3.0).astype(np.float32)).cuda()
+    codes = gemm.fp32_to_fp4x2(f32)
+    assert np.array_equal(codes.view(torch.uint8).cpu().numpy(), GOLD["fp32_to_fp4x2"])
+    assert np.array_equal(gemm.fp4x2_to_fp32(codes).cpu().numpy(), GOLD["fp4x2_to_fp32"])
+    assert_status_ok()
