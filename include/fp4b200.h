@@ -399,6 +399,17 @@ int fp4b200_nvfp4_quantize_for_gemm_into(const void* x_bf16, int64_t M, int64_t 
                                          void* row_fp4, int64_t row_pitch_bytes, void* row_sc, void* col_fp4, void* col_sc,
                                          float* amax_sg, void* stream);
 
+/* tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2) with round-to-nearest codes
+ * (nvfp4_v5/tk_quantize.cu:6425-6835) in two launches: the three tensor maxima, then all three [M, n_g] inputs
+ * quantised (encode-centric, each with its own amax) into the column slices of row_fp4_full [M, N/2] and the row blocks
+ * of col_fp4_full [N, M/2], N = n0 + n1 + n2.  Row-wise scales go to one swizzled tensor per input
+ * ([M/128, n_g/64, 512]); column-wise scales to the row blocks of col_sc_cat [N/128, M/64, 512], which is their
+ * concatenation.  amax3[g] = tensor amax of input g, sg3[g] = amax3[g] / 2688.  Same bytes as one
+ * fp4b200_nvfp4_quantize_for_gemm_into call per input. */
+int fp4b200_nvfp4_quantize_split3_into(const void* x0, const void* x1, const void* x2, int64_t M, int64_t n0, int64_t n1,
+                                       int64_t n2, void* row_fp4_full, void* row_sc0, void* row_sc1, void* row_sc2,
+                                       void* col_fp4_full, void* col_sc_cat, float* amax3, float* sg3, void* stream);
+
 /* tk_quantize_nhsd_wo_for_gemm(input, return_transpose, encode_centric) (nvfp4_v5/tk_quantize.cu:3006-3134):
  * the attention output in its native [B, H, S, D = 64] layout, quantised as the matrix [M = B*S, K = H*D] the
  * output projection consumes (element (b*S + s, h*64 + d) = input[b, h, s, d]) without a transposing copy.

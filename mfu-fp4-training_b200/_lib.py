@@ -92,6 +92,8 @@ SIGNATURES = {
     "fp4b200_row_rms_reduce": [_c_void_p, _i64, _i64, _i64, _f32, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_for_gemm_into": [_c_void_p, _i64, _i64, _int, _int, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p,
                                              _c_void_p, _c_void_p],
+    "fp4b200_nvfp4_quantize_split3_into": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _i64, _i64, _c_void_p, _c_void_p,
+                                           _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_quantize_nhsd_wo": [_c_void_p, _i64, _i64, _i64, _i64, _int, _int, _c_void_p, _c_void_p, _c_void_p,
                                        _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_grouped_gemm_rope": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p,

@@ -19,17 +19,12 @@ namespace fp4b200 {
 // Tensor amax of a bf16 buffer (pass 1 of the plain quantiser)
 // ---------------------------------------------------------------------------------------
 
-// partials[blockIdx.x] = max|x| over this CTA's share (every CTA writes, so nothing needs clearing)
-// early_reads: the caller has promised that x was not written by the kernel launched just before this one (see
-// fp4b200_set_pdl_early_reads), so x may be read while that kernel still runs; otherwise nothing is read before
-// that kernel's writes are visible.
-__global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, size_t n_vec,
-                                                        float* __restrict__ partials, int early_reads) {
-  pdl_launch_dependents();   // a quantiser launched behind this kernel may set up and prefetch meanwhile
-  if (!early_reads) pdl_wait();
+// Maximum |x| over the share CTA `cta` of `n_ctas` takes of n_vec 16-byte vectors; the result is in thread 0 (the
+// first warp holds it), and ends with a CTA barrier.
+__device__ __forceinline__ float cta_share_absmax(const uint4* __restrict__ x, size_t n_vec, int cta, int n_ctas) {
   uint32_t m0 = 0, m1 = 0, m2 = 0, m3 = 0;
-  const size_t stride = (size_t)gridDim.x * blockDim.x;
-  size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const size_t stride = (size_t)n_ctas * blockDim.x;
+  size_t i = (size_t)cta * blockDim.x + threadIdx.x;
   // four independent 16-byte loads in flight per thread
   for (; i + 3 * stride < n_vec; i += 4 * stride) {
     const uint4 a = __ldg(x + i), b = __ldg(x + i + stride), c = __ldg(x + i + 2 * stride),
@@ -52,10 +47,46 @@ __global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict_
   if (threadIdx.x < 32) {
     v = threadIdx.x < 8 ? warp_part[threadIdx.x] : 0.0f;
     v = warp_max(v);
+  }
+  return v;
+}
+
+// partials[blockIdx.x] = max|x| over this CTA's share (every CTA writes, so nothing needs clearing)
+// early_reads: the caller has promised that x was not written by the kernel launched just before this one (see
+// fp4b200_set_pdl_early_reads), so x may be read while that kernel still runs; otherwise nothing is read before
+// that kernel's writes are visible.
+__global__ void __launch_bounds__(256) amax_bf16_kernel(const uint4* __restrict__ x, size_t n_vec,
+                                                        float* __restrict__ partials, int early_reads) {
+  pdl_launch_dependents();   // a quantiser launched behind this kernel may set up and prefetch meanwhile
+  if (!early_reads) pdl_wait();
+  const float v = cta_share_absmax(x, n_vec, (int)blockIdx.x, (int)gridDim.x);
+  if (threadIdx.x < 32) {
     // Launched behind a quantiser that lets its dependents start early, this kernel may have only read x so far;
     // that quantiser may still be reading the partial maxima of ITS input from the same scratch, so the write waits.
     pdl_wait();
     if (threadIdx.x == 0) partials[blockIdx.x] = v;
+  }
+}
+
+// The same over three tensors in one launch: CTAs [0, cta_end[0]) take the first, [cta_end[0], cta_end[1]) the second,
+// the rest the third; partials[b] is CTA b's maximum, so each tensor's partial maxima are contiguous.
+struct AmaxGroup3 {
+  const uint4* x[3];
+  size_t n_vec[3];
+  int cta_end[2];
+};
+
+__global__ void __launch_bounds__(256) amax3_bf16_kernel(const AmaxGroup3 g, float* __restrict__ partials, int early_reads) {
+  pdl_launch_dependents();
+  if (!early_reads) pdl_wait();
+  const int b = (int)blockIdx.x;
+  float v;
+  if (b < g.cta_end[0]) v = cta_share_absmax(g.x[0], g.n_vec[0], b, g.cta_end[0]);
+  else if (b < g.cta_end[1]) v = cta_share_absmax(g.x[1], g.n_vec[1], b - g.cta_end[0], g.cta_end[1] - g.cta_end[0]);
+  else v = cta_share_absmax(g.x[2], g.n_vec[2], b - g.cta_end[1], (int)gridDim.x - g.cta_end[1]);
+  if (threadIdx.x < 32) {
+    pdl_wait();   // as in amax_bf16_kernel: the scratch may still be read by the kernel before
+    if (threadIdx.x == 0) partials[b] = v;
   }
 }
 
@@ -680,6 +711,7 @@ struct QuantArgs {
   const float* partials;   // n_partials > 0: the tensor amax (both orientations) is the maximum of these
   int n_partials;          //   per-CTA maxima of the pass-1 kernel launched before; amax_row/amax_col unused
   float* amax_out;         // with partials, optional: amax_out[0] = amax, amax_out[1] = amax / 2688
+  float* amax_scalar_out;  // optional: amax_scalar_out[0] = amax_row (strip kernel only)
   int* status;
   int M, K;
   int chunks_m, chunks_k;
@@ -1315,10 +1347,11 @@ __host__ __device__ constexpr size_t strip_smem_bytes(int64_t k_norm, bool pair)
 // OPT: 0 = round to nearest, no transform; 1 = the optional modes (stochastic rounding of the codes, Hadamard
 // transform, sign mask, row operand optional); 2 = those plus stochastic rounding of the scale bytes (a kernel
 // of its own, so that the extra random-word bookkeeping costs the usual modes no registers).
+// The work of CTA `cta` of the `n_ctas` that share one matrix (the whole grid, or one problem's range of a grouped
+// launch); tmap_x, tmap_row and a name kernel parameters.
 template <bool ENCODE_CENTRIC, bool NORM, int OPT, bool PAIR>
-__global__ void __launch_bounds__(kStripWarps * 32, 1)
-nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_row,
-                            const QuantArgs a) {
+__device__ __forceinline__ void quantize_strip_cta(const CUtensorMap& tmap_x, const CUtensorMap& tmap_row, const QuantArgs& a,
+                                                   const int cta, const int n_ctas) {
   constexpr int depth = kStripDepth;
   constexpr bool kScaleSr = OPT == 2;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -1350,8 +1383,8 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   const int wh = pair ? (warp >> 1) & 1 : (warp >> 2) & 1;  // which 64 columns of the chunk
   const int groups = pair ? 4 : 2;                           // chunks the CTA works on at a time
   const int n_chunks = a.chunks_m * a.chunks_k;
-  const int first = blockIdx.x * groups + (pair ? warp >> 2 : warp >> 3);
-  const int step = gridDim.x * groups;
+  const int first = cta * groups + (pair ? warp >> 2 : warp >> 3);
+  const int step = n_ctas * groups;
   const int my_units = first < n_chunks ? (n_chunks - first + step - 1) / step : 0;
   uint8_t* my_slots = slots + (size_t)warp * depth * kStripBytes;
   uint64_t* my_bars = bars + warp * depth;
@@ -1425,7 +1458,7 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   float amax_r, amax_c;
   if (a.n_partials > 0) {
     amax_r = amax_c = amax_from_partials(a.partials, a.n_partials, amax_slot);
-    if (tid == 0 && blockIdx.x == 0 && a.amax_out != nullptr) {
+    if (tid == 0 && cta == 0 && a.amax_out != nullptr) {
       a.amax_out[0] = amax_r;
       a.amax_out[1] = amax_r / 2688.0f;
     }
@@ -1433,7 +1466,8 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
     amax_r = *a.amax_row;
     amax_c = *a.amax_col;
   }
-  if (tid == 0 && blockIdx.x == 0 && a.sg_out != nullptr) a.sg_out[0] = amax_r / 2688.0f;
+  if (tid == 0 && cta == 0 && a.sg_out != nullptr) a.sg_out[0] = amax_r / 2688.0f;
+  if (tid == 0 && cta == 0 && a.amax_scalar_out != nullptr) a.amax_scalar_out[0] = amax_r;
   const float s_enc_row = nvfp4_global_encode_scale(amax_r);
   const float s_enc_col = nvfp4_global_encode_scale(amax_c);
   const bool want_col = a.col_fp4 != nullptr;
@@ -1810,6 +1844,39 @@ nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __
   if (lane == 0) bulk_wait_group0();
 }
 
+template <bool ENCODE_CENTRIC, bool NORM, int OPT, bool PAIR>
+__global__ void __launch_bounds__(kStripWarps * 32, 1)
+nvfp4_quantize_strip_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_row,
+                            const QuantArgs a) {
+  quantize_strip_cta<ENCODE_CENTRIC, NORM, OPT, PAIR>(tmap_x, tmap_row, a, (int)blockIdx.x, (int)gridDim.x);
+}
+
+// Three matrices with the same row count in ONE launch (the attention side's dQ, dK, dV): CTAs [0, cta_end[0]) work
+// on the first, [cta_end[0], cta_end[1]) on the second, the rest on the third, each range as a launch of its own would.
+struct StripProblem {
+  CUtensorMap tmap_x, tmap_row;
+  QuantArgs a;
+};
+struct StripGroup3 {
+  StripProblem p[3];
+  int cta_end[2];
+};
+
+template <bool PAIR>
+__global__ void __launch_bounds__(kStripWarps * 32, 1)
+nvfp4_quantize_strip3_kernel(const __grid_constant__ StripGroup3 g) {
+  const int b = (int)blockIdx.x;
+  if (b < g.cta_end[0]) {
+    quantize_strip_cta<true, false, 0, PAIR>(g.p[0].tmap_x, g.p[0].tmap_row, g.p[0].a, b, g.cta_end[0]);
+  } else if (b < g.cta_end[1]) {
+    quantize_strip_cta<true, false, 0, PAIR>(g.p[1].tmap_x, g.p[1].tmap_row, g.p[1].a, b - g.cta_end[0],
+                                             g.cta_end[1] - g.cta_end[0]);
+  } else {
+    quantize_strip_cta<true, false, 0, PAIR>(g.p[2].tmap_x, g.p[2].tmap_row, g.p[2].a, b - g.cta_end[1],
+                                             (int)gridDim.x - g.cta_end[1]);
+  }
+}
+
 // Tensor amax of the 16-point Hadamard transform of x (per 16 contiguous elements along K when
 // along_k, else per 16 consecutive rows), taken on the fp32 transform output before its bf16
 // rounding, as the reference's scan does (tk_quantize.cu:574-664).
@@ -2063,22 +2130,28 @@ static int quant_pair_mode() {
   return mode;
 }
 
-template <bool EC, bool NORM, int OPT, bool PAIR>
-static int launch_quantize_strip_tp(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
-  CUtensorMap tmap, tmap_row;
+// The strip kernel's two tensor maps: the input in strips of 32 rows x 64 columns, and the row-wise codes.
+static int make_strip_tmaps(const void* x, const QuantArgs& args, bool pair, CUtensorMap* tmap, CUtensorMap* tmap_row) {
   const bool nhsd = args.nhsd_seq > 0;   // [B * heads * seq, 64] instead of [M, K]
-  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, nhsd ? 64u : (uint64_t)args.K,
+  if (int rc = make_tmap_2d(tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, nhsd ? 64u : (uint64_t)args.K,
                             nhsd ? (uint64_t)args.M * (uint64_t)args.nhsd_heads : (uint64_t)args.M,
                             nhsd ? 128u : (uint64_t)args.K * 2, kStripCols, kStripRows, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   // row-wise codes as a byte matrix [M, K/2], stored in boxes of 32 (paired: 64) rows x 32 bytes
-  tmap_row = tmap;   // launches without row-wise outputs never use it
+  *tmap_row = *tmap;   // launches without row-wise outputs never use it
   if (args.row_fp4 != nullptr) {
-    if (int rc = make_tmap_2d(&tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
+    if (int rc = make_tmap_2d(tmap_row, args.row_fp4, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)args.K / 2, (uint64_t)args.M,
                               args.row_pitch_bytes > 0 ? (uint64_t)args.row_pitch_bytes : (uint64_t)args.K / 2, kStripCols / 2,
-                              kStripRows * (PAIR ? 2 : 1), CU_TENSOR_MAP_SWIZZLE_NONE))
+                              kStripRows * (pair ? 2 : 1), CU_TENSOR_MAP_SWIZZLE_NONE))
       return rc;
   }
+  return 0;
+}
+
+template <bool EC, bool NORM, int OPT, bool PAIR>
+static int launch_quantize_strip_tp(const void* x, const QuantArgs& args, cudaStream_t st, bool pdl) {
+  CUtensorMap tmap, tmap_row;
+  if (int rc = make_strip_tmaps(x, args, PAIR, &tmap, &tmap_row)) return rc;
   auto kern = nvfp4_quantize_strip_kernel<EC, NORM, OPT, PAIR>;
   const int smem = (int)strip_smem_bytes(NORM ? args.K : 0, PAIR);
   FP4_CUDA_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
@@ -2390,6 +2463,116 @@ int fp4b200_nvfp4_quantize_for_gemm_into(const void* x_bf16, int64_t M, int64_t 
   return launch_quantize(x_bf16, M, K, nullptr, nullptr, encode_centric != 0, nullptr, nullptr, row_fp4, row_sc,
                          return_transpose ? col_fp4 : nullptr, return_transpose ? col_sc : nullptr, nullptr, true,
                          (cudaStream_t)stream, false, nullptr, &part, amax_sg, 0, 0, row_pitch_bytes);
+}
+
+// Shares of `total` for three weights, each between 1 and cap[i] and as near its exact share as that allows.
+static void split_three(const int64_t w[3], const int64_t cap[3], int64_t total, int out[3]) {
+  const double sum = (double)(w[0] + w[1] + w[2]);
+  double ideal[3];
+  int64_t given = 0;
+  for (int i = 0; i < 3; ++i) {
+    ideal[i] = (double)total * (double)w[i] / sum;
+    out[i] = (int)std::max<int64_t>(1, std::min<int64_t>((int64_t)ideal[i], cap[i]));
+    given += out[i];
+  }
+  for (; given < total; ++given) {   // hand the rest to whichever is furthest below its share
+    int best = -1;
+    for (int i = 0; i < 3; ++i)
+      if (out[i] < cap[i] && (best < 0 || ideal[i] - out[i] > ideal[best] - out[best])) best = i;
+    if (best < 0) break;
+    ++out[best];
+  }
+  for (; given > total; --given) {   // the minimum of 1 overshot: take from whichever is furthest above
+    int best = -1;
+    for (int i = 0; i < 3; ++i)
+      if (out[i] > 1 && (best < 0 || out[i] - ideal[i] > out[best] - ideal[best])) best = i;
+    if (best < 0) break;
+    --out[best];
+  }
+}
+
+int fp4b200_nvfp4_quantize_split3_into(const void* x0, const void* x1, const void* x2, int64_t M, int64_t n0, int64_t n1,
+                                       int64_t n2, void* row_fp4_full, void* row_sc0, void* row_sc1, void* row_sc2,
+                                       void* col_fp4_full, void* col_sc_cat, float* amax3, float* sg3, void* stream) {
+  const char* fn = "nvfp4_quantize_split3_into";
+  const void* xs[3] = {x0, x1, x2};
+  const int64_t ns[3] = {n0, n1, n2};
+  void* row_scs[3] = {row_sc0, row_sc1, row_sc2};
+  for (int g = 0; g < 3; ++g)
+    if (int rc = check_quant_shapes(xs[g], M, ns[g], fn)) return rc;
+  if (!row_fp4_full || !row_sc0 || !row_sc1 || !row_sc2 || !col_fp4_full || !col_sc_cat || !amax3 || !sg3)
+    return set_error("%s: every output is required", fn);
+  const int64_t n_total = n0 + n1 + n2;
+  if (M * n_total / 2 > INT32_MAX) return set_error("%s: outputs of more than 2 GiB are not supported", fn);
+  if (((reinterpret_cast<uintptr_t>(row_fp4_full) | reinterpret_cast<uintptr_t>(col_fp4_full)) & 15) != 0)
+    return set_error("%s: the code matrices must be 16-byte aligned", fn);
+  cudaStream_t st = (cudaStream_t)stream;
+  float* scratch = stream_scratch(st);
+  int* status = device_status_ptr();
+  if (scratch == nullptr || status == nullptr) return -1;
+  const int sms = device_sm_count();
+
+  // pass 1: the three tensor maxima as per-CTA partial maxima, one launch
+  AmaxGroup3 ag{};
+  int64_t w[3], cap[3];
+  int amax_ctas[3];
+  for (int g = 0; g < 3; ++g) {
+    ag.x[g] = reinterpret_cast<const uint4*>(xs[g]);
+    ag.n_vec[g] = (size_t)(M * ns[g] / 8);
+    w[g] = M * ns[g];
+    cap[g] = (int64_t)((ag.n_vec[g] + 255) / 256);
+  }
+  split_three(w, cap, std::min<int64_t>((int64_t)sms * 8, kScratchFloats), amax_ctas);
+  ag.cta_end[0] = amax_ctas[0];
+  ag.cta_end[1] = amax_ctas[0] + amax_ctas[1];
+  {
+    PdlLaunch l(dim3((unsigned)(ag.cta_end[1] + amax_ctas[2])), dim3(256), 0, st, stats_pdl_enabled());
+    FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, amax3_bf16_kernel, ag, scratch, pdl_early_reads()));
+  }
+
+  // pass 2: one launch, the SMs shared out by the matrices' sizes
+  int64_t total_chunks = 0;
+  for (int g = 0; g < 3; ++g) total_chunks += (M / kChunk) * (ns[g] / kChunk);
+  const int mode = quant_pair_mode();
+  const bool pair = strip_smem_bytes(0, true) <= 227 * 1024 && (mode < 0 ? total_chunks >= 4 * (int64_t)sms : mode == 1);
+  const int groups = pair ? 4 : 2;
+  StripGroup3 sg{};
+  int64_t off = 0, partial0 = 0;
+  for (int g = 0; g < 3; ++g) {
+    QuantArgs& a = sg.p[g].a;
+    a.row_fp4 = (uint8_t*)row_fp4_full + off / 2;
+    a.row_pitch_bytes = (int)(n_total / 2);
+    a.row_sc = (uint8_t*)row_scs[g];
+    a.col_fp4 = (uint8_t*)col_fp4_full + off * (M / 2);
+    a.col_sc = (uint8_t*)col_sc_cat + (off / 128) * (M / 64) * 512;
+    a.partials = scratch + partial0;
+    a.n_partials = amax_ctas[g];
+    a.amax_scalar_out = amax3 + g;
+    a.sg_out = sg3 + g;
+    a.status = status;
+    a.M = (int)M; a.K = (int)ns[g];
+    a.chunks_m = (int)(M / kChunk); a.chunks_k = (int)(ns[g] / kChunk);
+    a.reverse = 1;   // pass 1 read each matrix front to back: its tail is what the L2 still holds
+    if (int rc = make_strip_tmaps(xs[g], a, pair, &sg.p[g].tmap_x, &sg.p[g].tmap_row)) return rc;
+    w[g] = (int64_t)a.chunks_m * a.chunks_k;
+    cap[g] = (w[g] + groups - 1) / groups;
+    off += ns[g];
+    partial0 += amax_ctas[g];
+  }
+  int ctas[3];
+  split_three(w, cap, std::min<int64_t>(cap[0] + cap[1] + cap[2], sms), ctas);
+  sg.cta_end[0] = ctas[0];
+  sg.cta_end[1] = ctas[0] + ctas[1];
+  const int smem = (int)strip_smem_bytes(0, pair);
+  PdlLaunch l(dim3((unsigned)(sg.cta_end[1] + ctas[2])), dim3(kStripWarps * 32), (size_t)smem, st, true);
+  if (pair) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(nvfp4_quantize_strip3_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, nvfp4_quantize_strip3_kernel<true>, sg));
+  } else {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(nvfp4_quantize_strip3_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    FP4_CUDA_CHECK(cudaLaunchKernelEx(&l.cfg, nvfp4_quantize_strip3_kernel<false>, sg));
+  }
+  return 0;
 }
 
 int fp4b200_nvfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int64_t S, int64_t D, int return_transpose,

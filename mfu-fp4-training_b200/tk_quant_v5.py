@@ -128,14 +128,13 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
     with torch.cuda.device(dev):
         fp4_row_full = torch.empty((M, n_total // 2), **u8)
         fp4_col_full = torch.empty((n_total, M // 2), **u8)
-        amax_sg = torch.empty((3, 2), dtype=torch.float32, device=dev)
-        sc_row, sc_col = [], []
-        off = 0
-        for g, (t, n) in enumerate(zip(inputs, splits)):
-            x = t if t.is_contiguous() else t.contiguous()   # the amax pass reads a dense buffer
-            sc_row.append(torch.empty((M // 128, n // 64, 512), **u8))
-            sc_col.append(torch.empty((n // 128, M // 64, 512), **u8))
-            if sr:
+        xs = [t if t.is_contiguous() else t.contiguous() for t in inputs]   # the amax pass reads dense buffers
+        sc_row = [torch.empty((M // 128, n // 64, 512), **u8) for n in splits]
+        if sr:
+            amax_sg = torch.empty((3, 2), dtype=torch.float32, device=dev)
+            sc_col = [torch.empty((n // 128, M // 64, 512), **u8) for n in splits]
+            off = 0
+            for g, (x, n) in enumerate(zip(xs, splits)):
                 _lib.call("fp4b200_nvfp4_amax", x.data_ptr(), M * n, amax_sg[g].data_ptr(), _stream(input0))
                 state = _reserve_sr(input0, rng_seed, rng_subsequence, True)
                 _lib.call("fp4b200_nvfp4_quantize_opt_into", x.data_ptr(), None, None, M, n, amax_sg[g].data_ptr(),
@@ -143,14 +142,24 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
                           fp4_row_full.data_ptr() + off // 2,
                           n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2),
                           sc_col[g].data_ptr(), None, _stream(input0))
-            else:
-                _lib.call("fp4b200_nvfp4_quantize_for_gemm_into", x.data_ptr(), M, n, 1, 1,
-                          fp4_row_full.data_ptr() + off // 2, n_total // 2, sc_row[g].data_ptr(),
-                          fp4_col_full.data_ptr() + off * (M // 2), sc_col[g].data_ptr(), amax_sg[g].data_ptr(),
-                          _stream(input0))
-            off += n
-        sg_per_group = amax_sg[:, 1].contiguous()
-        amax_tensor = amax_sg[:, 0].contiguous()
+                off += n
+            sg_per_group = amax_sg[:, 1].contiguous()
+            amax_tensor = amax_sg[:, 0].contiguous()
+            sc_col_cat = torch.cat(sc_col, 0)
+        else:
+            # one amax launch and one quantiser launch for the three streams; the column-wise scales are written
+            # where their concatenation holds them, so the per-stream tensors are its row blocks
+            amax_pair = torch.empty((2, 3), dtype=torch.float32, device=dev)
+            amax_tensor, sg_per_group = amax_pair[0], amax_pair[1]
+            sc_col_cat = torch.empty((n_total // 128, M // 64, 512), **u8)
+            _lib.call("fp4b200_nvfp4_quantize_split3_into", xs[0].data_ptr(), xs[1].data_ptr(), xs[2].data_ptr(), M,
+                      splits[0], splits[1], splits[2], fp4_row_full.data_ptr(), sc_row[0].data_ptr(),
+                      sc_row[1].data_ptr(), sc_row[2].data_ptr(), fp4_col_full.data_ptr(), sc_col_cat.data_ptr(),
+                      amax_tensor.data_ptr(), sg_per_group.data_ptr(), _stream(input0))
+            sc_col, off = [], 0
+            for n in splits:
+                sc_col.append(sc_col_cat.narrow(0, off // 128, n // 128))
+                off += n
         fp4_row_list, fp4_col_list = [], []
         off = 0
         for n in splits:
@@ -158,7 +167,7 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
             fp4_col_list.append(fp4_col_full.narrow(0, off, n).view(_FP4))
             off += n
         sc_row_cat = torch.cat(sc_row, 1).view(_E4M3)
-        sc_col_cat = torch.cat(sc_col, 0).view(_E4M3)
+        sc_col_cat = sc_col_cat.view(_E4M3)
         empty_u8 = torch.empty(0, **u8)
         empty_i32 = torch.empty(0, dtype=torch.int32, device=dev)
     return ([t for t in fp4_row_list], [t.view(_E4M3) for t in sc_row], sg_per_group, fp4_col_list,

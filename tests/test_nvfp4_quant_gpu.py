@@ -205,6 +205,29 @@ def test_quantize_nhsd_wo_equals_quantising_the_permuted_tensor(shape, ec):
     assert_status_ok()
 
 
+@pytest.mark.parametrize("M", [1024, 4096])
+def test_split3_one_launch_equals_the_single_input_quantiser(M):
+    """The grouped launch (CTAs shared out among the three matrices; at M = 4096 each warp takes strip pairs) writes
+    the bytes of one single-input quantiser call per stream, at attention-gradient widths."""
+    tkq = mod("tk_quant_v5")
+    splits = (2048, 512, 512)
+    g = torch.Generator(device="cuda").manual_seed(M)
+    xs = [(10.0 ** (-i) * torch.randn(M, n, device="cuda", generator=g)).to(torch.bfloat16) for i, n in enumerate(splits)]
+    out = tkq.tk_group_quantize_dim1_split3_for_gemm(*xs)
+    off = 0
+    for i, (x, n) in enumerate(zip(xs, splits)):
+        one = tkq.tk_quantize_for_gemm(x, True, True)
+        assert torch.equal(out[0][i].contiguous().view(torch.uint8), one[0].view(torch.uint8))
+        assert torch.equal(out[1][i].view(torch.uint8).flatten(), one[1].view(torch.uint8).flatten())
+        assert torch.equal(out[3][i].view(torch.uint8), one[2].view(torch.uint8))
+        assert torch.equal(out[4][i].view(torch.uint8).flatten(), one[3].view(torch.uint8).flatten())
+        assert out[2][i].item() == one[4].item() and out[12][i].item() == x.float().abs().max().item()
+        off += n
+    assert out[6].is_contiguous() and out[8].is_contiguous()
+    assert torch.equal(out[8].view(torch.uint8), torch.cat([t.view(torch.uint8) for t in out[4]], 0))
+    assert_status_ok()
+
+
 def test_split3_group_quantiser_writes_slices_of_the_concatenated_operands():
     """Three gradient streams of different widths (one of them a strided view), each with its own tensor amax: the
     slices of the concatenated code matrices and the per-group scales equal the single-input quantiser's bytes,
