@@ -744,18 +744,18 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
         q = st["gdy"]; gmx.mxfp4_gemm(q[0], q[1], wq["w2"][2], wq["w2"][3], dh)
     def s_w2_wgrad():
         q, f = st["gdy"], st["qh"]; gmx.mxfp4_gemm(q[2], q[3], f[2], f[3], dw["w2"])
-    def s_silu_deriv():
-        st["gd"] = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1, 1)
-    def s_w13_dgrad():   # dgrad of the fused gate/up projection from the concatenated [dh1 | dh3] operand, one launch
+    def s_silu_deriv():   # the reference's default producer for the one-pass dgrad (mxfp4_fused_linear.py:10415-10431)
+        st["gd"] = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols(dh, h3, h1, 1)
+    def s_w13_dgrad():   # dgrad of the fused gate/up projection from the side-by-side [dh1 | dh3] row operand, one launch
         d = st["gd"]
-        # the producer stacks dh1 and dh3 on a leading dimension; the one-pass GEMM reads them side by side
-        a_full = torch.cat([d[0][0].view(torch.uint8), d[0][1].view(torch.uint8)], dim=1).view(torch.float4_e2m1fn_x2)
-        gmx.mxfp4_split2_dgrad_strided_onepass_gemm(a_full, [d[1][0], d[1][1]], [0, H // 2], [H // 2, H // 2], [wq["w1"][2], wq["w3"][2]],
+        hs = H // 128
+        gmx.mxfp4_split2_dgrad_strided_onepass_gemm(d[0], [d[1].narrow(1, 0, hs), d[1].narrow(1, hs, hs)], [0, H // 2],
+                                                    [H // 2, H // 2], [wq["w1"][2], wq["w3"][2]],
                                                     [wq["w1"][3], wq["w3"][3]], dxf, -1)
     def s_w13_wgrad():
         d, f = st["gd"], st["qx"]
-        gmx.mxfp4_gemm(d[2][0], d[3][0], f[2], f[3], dw["w1"])
-        gmx.mxfp4_gemm(d[2][1], d[3][1], f[2], f[3], dw["w3"])
+        gmx.mxfp4_gemm(d[2], d[3], f[2], f[3], dw["w1"])
+        gmx.mxfp4_gemm(d[4], d[5], f[2], f[3], dw["w3"])
     def s_q_do():
         st["gdo"] = mxq.mxfp4_quantize_row_and_col(dxf, 1)
     def s_o_dgrad():
@@ -769,7 +769,7 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
     def s_qkv_wgrad():
         q, f = st["gq"], st["qx"]; gmx.mxfp4_gemm(q[2], q[3], f[2], f[3], dw["qkv"])
     bwd = [("quant_dy", s_q_dy), ("w2_dgrad_gemm", s_w2_dgrad), ("w2_wgrad_gemm", s_w2_wgrad),
-           ("silu_deriv_quant_split2", s_silu_deriv), ("w13_dgrad_onepass_gemm", s_w13_dgrad), ("w13_wgrad_gemms", s_w13_wgrad),
+           ("silu_deriv_quant_splitcols", s_silu_deriv), ("w13_dgrad_onepass_gemm", s_w13_dgrad), ("w13_wgrad_gemms", s_w13_wgrad),
            ("quant_d_o", s_q_do), ("o_dgrad_gemm", s_o_dgrad), ("o_wgrad_gemm", s_o_wgrad), ("quant_d_qkv", s_q_dqkv),
            ("qkv_dgrad_gemm", s_qkv_dgrad), ("qkv_wgrad_gemm", s_qkv_wgrad)]
     stages = ([("weight_all_gather", gather_stage)] if gather_stage is not None else []) + fwd + bwd

@@ -326,6 +326,14 @@ int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, co
                               const int64_t* a_col_widths, const void* const* A_sc_list, const void* const* B_list,
                               const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream);
 
+/* The same with A_sc_list[s] a column slice of a wider scale tensor, as the reference's caller passes it
+ * (row_sc.narrow(1, ...) of the combined producer's [M/128, 2H/128, 512] tensor, mxfp4_fused_linear.py:10803-10829):
+ * a_sc_row_tiles[s] = 512-byte tiles from one 128-row block of that tensor to the next (0 or a null array: w_s/128). */
+int fp4b200_mxfp4_gemm_ksplit_strided(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,
+                                      const int64_t* a_col_widths, const void* const* A_sc_list,
+                                      const int64_t* a_sc_row_tiles, const void* const* B_list,
+                                      const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream);
+
 /* ---- helpers around the hot path -------------------------------------------------------- */
 
 /* mxfp4_quantize_weight_2d(input) (mxfp4_v4/tk_quantize.cu:2734-2737; kernel mx_weight_2d_quantize,
@@ -350,6 +358,25 @@ int fp4b200_mxfp4_silu_mul_quantize(const void* h1_raw, const void* h3, int64_t 
 int fp4b200_mxfp4_silu_deriv_quantize_split2(const void* dh, const void* h3, const void* h1_raw, int64_t M, int64_t H,
                                              int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
                                              void* stream);
+
+/* mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined(dh, h13, H, h3_offset, mode)
+ * (mxfp4_v4/tk_quantize.cu:5015-5099; kernel mxfp4_v3_quantize.cuh:8559): the same two gradients from dh [M, dh_stride]
+ * and a packed gate|up activation h13 [M, h13_stride] (h1 in columns [0, H), h3 in [h3_offset, h3_offset + H)), laid
+ * out for the one-pass split dgrad GEMM: row_fp4 [M, H] bytes = dh1's codes | dh3's codes, row_sc
+ * [M/128, 2H/128, 512] = dh1's scale tiles | dh3's per row block, col_fp4 [2H, M/2] and col_sc [2H/128, M/128, 512]
+ * = dh1's over dh3's. */
+int fp4b200_mxfp4_silu_deriv_quantize_split2_combined(const void* dh, int64_t dh_stride, const void* h13, int64_t h13_stride,
+                                                      int64_t h3_offset, int64_t M, int64_t H, int mode, void* row_fp4,
+                                                      void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
+/* mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols[_launch_inplace](dh, h3, h1_raw, ...)
+ * (mxfp4_v4/tk_quantize.cu:4708-4905), the producer the reference's default gate/up backward feeds its one-pass split
+ * dgrad GEMM from (mxfp4_fused_linear.py:10415-10431): the row-wise operand in the combined layout above (row_fp4
+ * [M, H] bytes, row_sc [M/128, 2H/128, 512]), the column-wise operands of dh1 and dh3 in tensors of their own
+ * (col*_fp4 [H, M/2], col*_sc [H/128, M/128, 512]). */
+int fp4b200_mxfp4_silu_deriv_quantize_split2_splitcols(const void* dh, const void* h3, const void* h1_raw, int64_t M,
+                                                       int64_t H, int mode, void* row_fp4, void* row_sc, void* col0_fp4,
+                                                       void* col0_sc, void* col1_fp4, void* col1_sc, void* stream);
 
 /* mxfp4_quantize_for_gemm_opt(input, mode, data_stochastic_rounding, scale_stochastic_rounding, rng_seed,
  * rng_subsequence) (mxfp4_v4/tk_quantize.cu:1796-1881; kernel mxfp4_v3_fused_kernel_opt / mx_rowwise_quantize_opt,

@@ -60,6 +60,10 @@ SIGNATURES = {
                                         _c_void_p],
     "fp4b200_mxfp4_silu_deriv_quantize_split2": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p, _c_void_p,
                                                  _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_mxfp4_silu_deriv_quantize_split2_combined": [_c_void_p, _i64, _c_void_p, _i64, _i64, _i64, _i64, _int,
+                                                          _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_mxfp4_silu_deriv_quantize_split2_splitcols": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p,
+                                                           _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_selftest_silu_division": [_c_void_p, _c_void_p],
     "fp4b200_silu_mul_bf16": [_c_void_p, _c_void_p, _i64, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_nvfp4_silu_quantize": [_c_void_p, _c_void_p, _i64, _i64, _c_void_p, _int, _c_void_p, _c_void_p,
@@ -84,6 +88,9 @@ SIGNATURES = {
     "fp4b200_mxfp4_gemm_ksplit": [_c_void_p, _i64, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                   ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
                                   _c_void_p, _int, _i64, _i64, _c_void_p],
+    "fp4b200_mxfp4_gemm_ksplit_strided": [_c_void_p, _i64, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
+                                          ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), ctypes.POINTER(_c_void_p),
+                                          ctypes.POINTER(_c_void_p), _c_void_p, _int, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_quantize_weight_2d": [_c_void_p, _i64, _i64, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_mxfp4_quantize_row_sr": [_c_void_p, _i64, _i64, _int, _int, _int, _int, _int, ctypes.c_uint64, ctypes.c_uint64, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_mxfp4_quantize_row_and_col_sr": [_c_void_p, _i64, _i64, _int, _int, _int, _int, _int, _int, _int, ctypes.c_uint64,

@@ -1193,9 +1193,10 @@ int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const voi
                      K, (cudaStream_t)stream);
 }
 
-int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,
-                              const int64_t* a_col_widths, const void* const* A_sc_list, const void* const* B_list,
-                              const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream) {
+int fp4b200_mxfp4_gemm_ksplit_strided(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,
+                                      const int64_t* a_col_widths, const void* const* A_sc_list,
+                                      const int64_t* a_sc_row_tiles, const void* const* B_list,
+                                      const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream) {
   if (!A_full || !a_col_offsets || !a_col_widths || !A_sc_list || !B_list || !B_sc_list || !D)
     return set_error("mxfp4_gemm_ksplit: null pointer");
   if (n_seg < 1 || n_seg > kMaxKSeg) return set_error("mxfp4_gemm_ksplit: 1 to %d K segments are supported", kMaxKSeg);
@@ -1212,12 +1213,25 @@ int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, co
     segs.a_col_off[s] = off; segs.k[s] = w;
     segs.a_sc[s] = A_sc_list[s]; segs.b[s] = B_list[s]; segs.b_sc[s] = B_sc_list[s];
     if (int rc = check_gemm(A_full, A_sc_list[s], B_list[s], B_sc_list[s], M, N, w, "mxfp4_gemm_ksplit")) return rc;
+    if (a_sc_row_tiles != nullptr && a_sc_row_tiles[s] != 0) {
+      if (a_sc_row_tiles[s] < w / 128 || a_sc_row_tiles[s] > INT32_MAX)
+        return set_error("mxfp4_gemm_ksplit: segment %d: %lld scale tiles per row block cannot hold its %lld", s,
+                         (long long)a_sc_row_tiles[s], (long long)(w / 128));
+      segs.a_sc_row_tiles[s] = a_sc_row_tiles[s];
+    }
     K += w;
   }
   void* d[1] = {D};
   int ce[1] = {(int)N}, ld[1] = {(int)N};
   return launch_gemm_segs(true, A_full, segs, nullptr, nullptr, 0, d, ce, ld, 1, out_fp32, nullptr, 0, M, N,
                           (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_gemm_ksplit(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,
+                              const int64_t* a_col_widths, const void* const* A_sc_list, const void* const* B_list,
+                              const void* const* B_sc_list, void* D, int out_fp32, int64_t M, int64_t N, void* stream) {
+  return fp4b200_mxfp4_gemm_ksplit_strided(A_full, a_width, n_seg, a_col_offsets, a_col_widths, A_sc_list, nullptr, B_list,
+                                           B_sc_list, D, out_fp32, M, N, stream);
 }
 
 }  // extern "C"

@@ -286,6 +286,8 @@ struct MxActArgs {
   int* status;
   int M, K, chunks_m, chunks_k;
   int mode;
+  int row_pitch_bytes;   // pitch of the row-wise code matrices (K/2, or the width of the matrix they are column slices of)
+  int row_sc_row_tiles;  // 512-byte scale tiles from one 128-row block of row_sc to the next (K/128, or the wider tensor's)
 };
 
 // one 32-element row block held as sixteen bf16x2 words: scale byte and 16 bytes of codes
@@ -445,7 +447,7 @@ mxfp4_act_quantize_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
         *reinterpret_cast<uint4*>(tx + ro + row_off[j]) = make_uint4(w0[4 * j], w0[4 * j + 1], w0[4 * j + 2], w0[4 * j + 3]);
       }
       uint32_t e;
-      const size_t at = (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1);
+      const size_t at = (size_t)(m0 + r) * a.row_pitch_bytes + ((k0 + unit * 32) >> 1);
       st_cs_u4(a.row_fp4[0] + at, mx_row_block(w0, a.mode, e));
       sm.row_sc[0][pp][scale_tile_offset(r, unit)] = (uint8_t)e;
       if constexpr (ACT == 2) {
@@ -462,7 +464,7 @@ mxfp4_act_quantize_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gr
     if (tid < 128) {
 #pragma unroll
       for (int o = 0; o < kOut; ++o)
-        st_cs_u32(a.row_sc[o] + ((size_t)cm * a.chunks_k + ck) * 512 + tid * 4,
+        st_cs_u32(a.row_sc[o] + ((size_t)cm * a.row_sc_row_tiles + ck) * 512 + tid * 4,
                   *reinterpret_cast<const uint32_t*>(&sm.row_sc[o][pp][tid * 4]));
     }
     // ---- column pass(es)
@@ -834,23 +836,34 @@ static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float*
   return 0;
 }
 
+// pitch_*: row pitch of each input in elements (0: K).  combined (ACT 2): the two row-wise code matrices are the left and
+// right halves of one [M, K] byte matrix and their scale tiles the left and right halves of one [M/128, 2K/128, 512]
+// tensor; else the second output is stacked behind the first in every array.  col_fp4_1 / col_sc_1: the second
+// output's column operand, when it is not stacked behind the first's.
 static int launch_mx_act(int act, const void* in_a, const void* in_b, const void* in_c, int64_t M, int64_t K, int mode,
-                         uint8_t* row_fp4, uint8_t* row_sc, uint8_t* col_fp4, uint8_t* col_sc, cudaStream_t st) {
+                         uint8_t* row_fp4, uint8_t* row_sc, uint8_t* col_fp4, uint8_t* col_sc, cudaStream_t st,
+                         int64_t pitch_a = 0, int64_t pitch_b = 0, int64_t pitch_c = 0, bool combined = false,
+                         uint8_t* col_fp4_1 = nullptr, uint8_t* col_sc_1 = nullptr) {
   CUtensorMap tm[3];
   const void* src[3] = {in_a, in_b, act == 2 ? in_c : in_a};
+  const int64_t pitch[3] = {pitch_a ? pitch_a : K, pitch_b ? pitch_b : K, act == 2 ? (pitch_c ? pitch_c : K) : (pitch_a ? pitch_a : K)};
   for (int i = 0; i < 3; ++i)
     if (int rc = make_tmap_2d(&tm[i], src[i], CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M,
-                              (uint64_t)K * 2, 64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
+                              (uint64_t)pitch[i] * 2, 64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
   MxActArgs a{};
   const size_t codes = (size_t)M * K / 2, scales = (size_t)(M / 128) * (K / 128) * 512;
-  for (int o = 0; o < 2; ++o) {   // the second output (ACT 2) is stacked behind the first in every array
-    a.row_fp4[o] = row_fp4 + o * codes; a.row_sc[o] = row_sc + o * scales;
+  for (int o = 0; o < 2; ++o) {
+    a.row_fp4[o] = row_fp4 + o * (combined ? (size_t)K / 2 : codes);
+    a.row_sc[o] = row_sc + o * (combined ? (size_t)(K / 128) * 512 : scales);
     a.col_fp4[o] = col_fp4 + o * codes; a.col_sc[o] = col_sc + o * scales;
   }
+  if (col_fp4_1 != nullptr) { a.col_fp4[1] = col_fp4_1; a.col_sc[1] = col_sc_1; }   // column operands in tensors of their own
   a.status = device_status_ptr();
   if (!a.status) return -1;
   a.M = (int)M; a.K = (int)K; a.chunks_m = (int)(M / kMxChunk); a.chunks_k = (int)(K / kMxChunk); a.mode = mode;
+  a.row_pitch_bytes = (int)(combined ? K : K / 2);
+  a.row_sc_row_tiles = (int)(combined ? 2 * (K / 128) : K / 128);
   const int smem = (int)sizeof(MxActSmem) + 1024;
   const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
   if (grid == 0) return 0;
@@ -926,6 +939,33 @@ int fp4b200_mxfp4_silu_deriv_quantize_split2(const void* dh, const void* h3, con
     return set_error("mxfp4_silu_deriv_quantize_split2: all outputs are required");
   return launch_mx_act(2, dh, h3, h1_raw, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4,
                        (uint8_t*)col_sc, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_silu_deriv_quantize_split2_combined(const void* dh, int64_t dh_stride, const void* h13, int64_t h13_stride,
+                                                      int64_t h3_offset, int64_t M, int64_t H, int mode, void* row_fp4,
+                                                      void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  const char* fn = "mxfp4_silu_deriv_quantize_split2_combined";
+  if (int rc = check_mx(dh, M, H, mode, fn)) return rc;
+  if (int rc = check_mx(h13, M, H, mode, fn)) return rc;
+  if (dh_stride < H || (dh_stride % 8)) return set_error("%s: the row stride of dh must cover H and be a multiple of 8", fn);
+  if (h3_offset < H || h3_offset + H > h13_stride || (h3_offset % 8) || (h13_stride % 8))
+    return set_error("%s: h13 must hold h1 in columns [0, H) and h3 in [h3_offset, h3_offset + H), both 16-byte aligned", fn);
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("%s: all outputs are required", fn);
+  const auto* h3 = reinterpret_cast<const uint8_t*>(h13) + (size_t)h3_offset * 2;
+  return launch_mx_act(2, dh, h3, h13, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4, (uint8_t*)col_sc,
+                       (cudaStream_t)stream, dh_stride, h13_stride, h13_stride, true);
+}
+
+int fp4b200_mxfp4_silu_deriv_quantize_split2_splitcols(const void* dh, const void* h3, const void* h1_raw, int64_t M,
+                                                       int64_t H, int mode, void* row_fp4, void* row_sc, void* col0_fp4,
+                                                       void* col0_sc, void* col1_fp4, void* col1_sc, void* stream) {
+  const char* fn = "mxfp4_silu_deriv_quantize_split2_splitcols";
+  if (int rc = check_mx(dh, M, H, mode, fn)) return rc;
+  if (int rc = check_mx(h3, M, H, mode, fn)) return rc;
+  if (int rc = check_mx(h1_raw, M, H, mode, fn)) return rc;
+  if (!row_fp4 || !row_sc || !col0_fp4 || !col0_sc || !col1_fp4 || !col1_sc) return set_error("%s: all outputs are required", fn);
+  return launch_mx_act(2, dh, h3, h1_raw, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col0_fp4,
+                       (uint8_t*)col0_sc, (cudaStream_t)stream, 0, 0, 0, true, (uint8_t*)col1_fp4, (uint8_t*)col1_sc);
 }
 
 static int check_mx_rht(int rht_block, const char* who) {

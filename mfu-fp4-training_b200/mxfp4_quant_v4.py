@@ -253,6 +253,68 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
     return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
 
 
+def mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined(dh, h13, H, h3_offset, mode=0):
+    """tk_quantize.cu:5015-5099 — the two gradients of the packed gate|up activation ``h13`` [M, stride] (h1 in columns
+    [0, H), h3 in [h3_offset, h3_offset + H)) laid out for the one-pass split dgrad GEMM: (row_fp4 [M, H] = dh1's
+    codes | dh3's, row_sc [M/128, 2H/128, 32, 16] = dh1's tiles | dh3's per row block, col_fp4 [2H, M/2] and col_sc
+    [2H/128, M/128, 32, 16] = dh1's over dh3's).  ``dh`` may be wider than H (its first H columns are read)."""
+    for t, n in ((dh, "dh"), (h13, "h13")):
+        if not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous() or t.dtype != torch.bfloat16 or t.dim() != 2:
+            raise RuntimeError(f"{n} must be a contiguous 2-D CUDA bf16 tensor")
+    M, H, h3_offset = int(dh.shape[0]), int(H), int(h3_offset)
+    if int(h13.shape[0]) != M:
+        raise RuntimeError("dh and h13 row count mismatch")
+    if M % 128 or H % 128:
+        raise RuntimeError("M and H must be divisible by 128")
+    if int(dh.shape[1]) < H:
+        raise RuntimeError("dh stride must cover H")
+    if h3_offset < H or h3_offset + H > int(h13.shape[1]):
+        raise RuntimeError("h13 must contain packed h1 and h3 slices")
+    u8 = dict(dtype=torch.uint8, device=dh.device)
+    row_fp4 = torch.empty((M, H), **u8)
+    row_sc = torch.empty((M // 128, 2 * H // 128, 32, 16), **u8)
+    col_fp4 = torch.empty((2 * H, M // 2), **u8)
+    col_sc = torch.empty((2 * H // 128, M // 128, 32, 16), **u8)
+    with torch.cuda.device(dh.device):
+        _lib.call("fp4b200_mxfp4_silu_deriv_quantize_split2_combined", dh.data_ptr(), int(dh.shape[1]), h13.data_ptr(),
+                  int(h13.shape[1]), h3_offset, M, H, int(mode), row_fp4.data_ptr(), row_sc.data_ptr(), col_fp4.data_ptr(),
+                  col_sc.data_ptr(), _stream(dh))
+    return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
+
+
+def mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols(dh, h3, h1_raw, mode=0):
+    """tk_quantize.cu:4708-4810 — dh1 and dh3 with the row-wise operand in the one-pass split dgrad GEMM's layout and
+    the column-wise operands apart: (row_fp4 [M, H] = dh1's codes | dh3's, row_sc [M/128, 2H/128, 32, 16],
+    col0_fp4 [H, M/2], col0_sc [H/128, M/128, 32, 16], col1_fp4, col1_sc)."""
+    M, H = _check_bf16_2d(dh, "dh")
+    _same_shape_bf16(dh, h3, h1_raw)
+    u8 = dict(dtype=torch.uint8, device=dh.device)
+    row_fp4 = torch.empty((M, H), **u8).view(_FP4)
+    row_sc = torch.empty((M // 128, 2 * H // 128, 32, 16), **u8)
+    cols = [torch.empty((H, M // 2), **u8).view(_FP4) for _ in range(2)]
+    col_scs = [torch.empty((H // 128, M // 128, 32, 16), **u8) for _ in range(2)]
+    mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols_launch_inplace(dh, h3, h1_raw, row_fp4, row_sc, cols[0],
+                                                                                col_scs[0], cols[1], col_scs[1], mode)
+    return row_fp4, row_sc, cols[0], col_scs[0], cols[1], col_scs[1]
+
+
+def mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols_launch_inplace(dh, h3, h1_raw, row_fp4, row_sc, col0_fp4,
+                                                                                col0_sc, col1_fp4, col1_sc, mode=0):
+    """tk_quantize.cu:4813-4905 — the same into the caller's tensors; returns None."""
+    M, H = _check_bf16_2d(dh, "dh")
+    _same_shape_bf16(dh, h3, h1_raw)
+    _check_out(row_fp4, (M, H), True, "row_fp4")
+    _check_out(row_sc, (M // 128, 2 * H // 128, 32, 16), False, "row_sc")
+    for t, n in ((col0_fp4, "col0_fp4"), (col1_fp4, "col1_fp4")):
+        _check_out(t, (H, M // 2), True, n)
+    for t, n in ((col0_sc, "col0_sc"), (col1_sc, "col1_sc")):
+        _check_out(t, (H // 128, M // 128, 32, 16), False, n)
+    with torch.cuda.device(dh.device):
+        _lib.call("fp4b200_mxfp4_silu_deriv_quantize_split2_splitcols", dh.data_ptr(), h3.data_ptr(), h1_raw.data_ptr(), M, H,
+                  int(mode), row_fp4.data_ptr(), row_sc.data_ptr(), col0_fp4.data_ptr(), col0_sc.data_ptr(),
+                  col1_fp4.data_ptr(), col1_sc.data_ptr(), _stream(dh))
+
+
 # ---- *_launch_inplace twins: the caller owns the outputs -----------------------------------------
 
 def _check_out(t, shape, fp4, name):

@@ -58,8 +58,19 @@ def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_
     if not (len(A_sc_list) == len(A_col_offsets) == len(A_col_widths) == len(B_sc_list) == n):
         raise RuntimeError("split2 one-pass dgrad: list lengths differ")
     _chk_operand(A_full, "A_full")
-    for t in list(A_sc_list) + list(B_list) + list(B_sc_list):
+    for t in list(B_list) + list(B_sc_list):
         _chk_operand(t, "operand")
+    # a segment's scales may be a column slice (narrow(1, ...)) of the combined producer's [M/128, tiles, 32, 16] tensor
+    row_tiles = []
+    for t in A_sc_list:
+        if not isinstance(t, torch.Tensor) or not t.is_cuda:
+            raise RuntimeError("A_sc_list must hold CUDA tensors")
+        if t.is_contiguous():
+            row_tiles.append(0)
+        elif t.dim() == 4 and tuple(t.shape[2:]) == (32, 16) and tuple(t.stride()[1:]) == (512, 16, 1) and t.stride(0) % 512 == 0:
+            row_tiles.append(t.stride(0) // 512)
+        else:
+            raise RuntimeError("A_sc_list entries must be contiguous or column slices of a [M/128, tiles, 32, 16] tensor")
     a = A_full.view(torch.uint8)
     M, a_width = a.shape[0], a.shape[1] * 2
     N = B_list[0].view(torch.uint8).shape[0]
@@ -80,5 +91,5 @@ def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_
     b_p = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B_list])
     b_sc = (ctypes.c_void_p * n)(*[t.data_ptr() for t in B_sc_list])
     with torch.cuda.device(A_full.device):
-        _lib.call("fp4b200_mxfp4_gemm_ksplit", a.data_ptr(), a_width, n, offs, widths, a_sc, b_p, b_sc, D_out.data_ptr(),
-                  out_fp32, M, N, _stream(A_full))
+        _lib.call("fp4b200_mxfp4_gemm_ksplit_strided", a.data_ptr(), a_width, n, offs, widths, a_sc,
+                  (ctypes.c_int64 * n)(*row_tiles), b_p, b_sc, D_out.data_ptr(), out_fp32, M, N, _stream(A_full))

@@ -48,6 +48,9 @@ CASES = [
     ("rowcol_rht_col32_sr", "mxfp4_quantize_row_and_col_opt_rht", "g", (1, True, False, 32, True, SEED, SUBSEQ)),
     ("rowcol_rht_both16", "mxfp4_quantize_row_and_col_opt_rht_both", "g", (1, False, False, 16, True, SEED, SUBSEQ)),
     ("rowcol_rht_row_only16", "mxfp4_quantize_row_and_col_opt_rht_row_only", "g", (1, False, False, 16, True, SEED, SUBSEQ)),
+    ("silu_deriv_combined_m1", "mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined", "dh_h13",
+     (SHAPE[1], SHAPE[1], 1)),
+    ("silu_deriv_splitcols_m1", "mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols", "dh_h3_h1", (1,)),
 ]
 
 
@@ -71,6 +74,8 @@ def make_inputs(kind, seed):
         return (r(1e-3), r(1.0), r(2.0))
     if kind == "g":
         return (r(1e-3),)
+    if kind == "dh_h13":       # the packed gate|up activation: h1 in the left half, h3 in the right
+        return (r(1e-3), np.concatenate([r(2.0), r(1.0)], axis=1))
     raise ValueError(kind)
 
 
@@ -94,6 +99,14 @@ def gemm_operands(shape, seed):
     rng = np.random.default_rng(seed)
     return (o.bf16_round(rng.standard_normal((M, K)).astype(np.float32)),
             o.bf16_round((0.02 * rng.standard_normal((N, K))).astype(np.float32)))
+
+
+def combined_inputs():
+    """dh [M, w] and the packed gate|up activation [M, 2w] of the combined-producer GEMM case; the tests call this too."""
+    Mo, _, w = ONEPASS
+    rng = np.random.default_rng(740)
+    r = lambda s, n: o.bf16_round((s * rng.standard_normal((Mo, n))).astype(np.float32))
+    return r(1e-3, w), np.concatenate([r(2.0, w), r(1.0, w)], axis=1)
 
 
 def load_reference_gemm_module():
@@ -151,6 +164,21 @@ def main():
         ref_gemm.mxfp4_batched_gemm([q1[0], q2[0]], [q1[1], q2[1]], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], [d1, d2])
         torch.cuda.synchronize()
         out["batched.0"], out["batched.1"] = d1.view(torch.int16).cpu().numpy(), d2.view(torch.int16).cpu().numpy()
+    if ref_gemm is not None:
+        # the reference's own call pattern (mxfp4_fused_linear.py:10390-10398, 10803-10829): the combined producer's
+        # side-by-side row operand and column slices of its scale tensor into the one-pass split dgrad GEMM
+        Mo, No, w = ONEPASS
+        dh, h13 = combined_inputs()
+        q = ref.mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined(
+            torch.from_numpy(dh).to(torch.bfloat16).to(dev), torch.from_numpy(h13).to(torch.bfloat16).to(dev), w, w, 1)
+        ws = [ref.mxfp4_quantize_for_gemm(torch.from_numpy(gemm_operands((1, No, w), 730 + i)[1]).to(torch.bfloat16).to(dev), 1)
+              for i in range(2)]
+        d = torch.empty(Mo, No, dtype=torch.bfloat16, device=dev)
+        ref_gemm.mxfp4_split2_dgrad_strided_onepass_gemm(q[0], [q[1].narrow(1, 0, w // 128), q[1].narrow(1, w // 128, w // 128)],
+                                                         [0, w // 2], [w // 2, w // 2], [ws[0][0], ws[1][0]],
+                                                         [ws[0][1], ws[1][1]], d, -1)
+        torch.cuda.synchronize()
+        out["onepass_combined.d"] = d.view(torch.int16).cpu().numpy()
     dst = os.environ.get("MX_GOLDEN_OUT", os.path.join(HERE, "mxfp4_reference_kernels_golden.npz"))
     np.savez_compressed(dst, **out)
     print(f"wrote {dst}: {len(out)} arrays, {os.path.getsize(dst)} bytes")

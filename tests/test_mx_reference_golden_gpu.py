@@ -96,3 +96,39 @@ def test_mxfp4_onepass_split2_dgrad_and_batched_gemm_reproduce_the_reference_ker
     assert np.array_equal(d1.view(torch.int16).cpu().numpy(), GOLD["batched.0"])
     assert np.array_equal(d2.view(torch.int16).cpu().numpy(), GOLD["batched.1"])
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "onepass_combined.d" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+def test_combined_producer_into_onepass_dgrad_reproduces_the_reference_kernels_bytes():
+    """The reference's call pattern for the gate/up dgrad: the combined SiLU-derivative producer's side-by-side row
+    operand, and column slices (non-contiguous views) of its scale tensor, into the one-pass split GEMM."""
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    Mo, No, w = G.ONEPASS
+    dh, h13 = (to_dev_bf16(t) for t in G.combined_inputs())
+    q = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined(dh, h13, w, w, 1)
+    ws = [mxq.mxfp4_quantize_for_gemm(to_dev_bf16(G.gemm_operands((1, No, w), 730 + i)[1]), 1) for i in range(2)]
+    d = torch.empty(Mo, No, dtype=torch.bfloat16, device="cuda")
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(q[0], [q[1].narrow(1, 0, w // 128), q[1].narrow(1, w // 128, w // 128)],
+                                                 [0, w // 2], [w // 2, w // 2], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], d, -1)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD["onepass_combined.d"])
+    # and the combined layout holds exactly the stacked producer's operands
+    st = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h13[:, w:].contiguous(), h13[:, :w].contiguous(), 1)
+    row = q[0].view(torch.uint8)
+    assert torch.equal(row[:, :w // 2], st[0].view(torch.uint8)[0]) and torch.equal(row[:, w // 2:], st[0].view(torch.uint8)[1])
+    assert torch.equal(q[1][:, :w // 128], st[1][0]) and torch.equal(q[1][:, w // 128:], st[1][1])
+    assert torch.equal(q[2].view(torch.uint8), st[2].view(torch.uint8).reshape(2 * w, Mo // 2))
+    assert torch.equal(q[3], st[3].reshape(2 * w // 128, Mo // 128, 32, 16))
+    # the default producer of that GEMM: the same row operand, column operands in tensors of their own
+    sp = mxq.mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols(dh, h13[:, w:].contiguous(), h13[:, :w].contiguous(), 1)
+    assert torch.equal(sp[0].view(torch.uint8), row) and torch.equal(sp[1], q[1])
+    for i in range(2):
+        assert torch.equal(sp[2 + 2 * i].view(torch.uint8), st[2].view(torch.uint8)[i]) and torch.equal(sp[3 + 2 * i], st[3][i])
+    d2 = torch.empty_like(d)
+    gemm.mxfp4_split2_dgrad_strided_onepass_gemm(sp[0], [sp[1].narrow(1, 0, w // 128), sp[1].narrow(1, w // 128, w // 128)],
+                                                 [0, w // 2], [w // 2, w // 2], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], d2, -1)
+    assert torch.equal(d2, d)
+    with pytest.raises(RuntimeError):
+        gemm.mxfp4_split2_dgrad_strided_onepass_gemm(sp[0], [sp[1][:, :, :16], sp[1].narrow(1, w // 128, w // 128)],
+                                                     [0, w // 2], [w // 2, w // 2], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], d2, -1)
+    assert_status_ok()
