@@ -343,6 +343,12 @@ int fp4b200_mxfp4_gemm_ksplit_strided(const void* A_full, int64_t a_width, int n
 int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
                                      void* col_fp4, void* col_sc, void* stream);
 
+/* mxfp4_fused_silu_mul_quantize_row_and_col_strided(h13, H, h3_offset, mode) (mxfp4_v4/tk_quantize.cu:4105-4132): the
+ * SwiGLU producer reading h1 and h3 out of one packed gate|up activation h13 [M, h13_stride] (h1 in columns [0, H), h3
+ * in [h3_offset, h3_offset + H)); outputs as fp4b200_mxfp4_silu_mul_quantize. */
+int fp4b200_mxfp4_silu_mul_quantize_strided(const void* h13, int64_t h13_stride, int64_t h3_offset, int64_t M, int64_t H,
+                                            int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
 /* One-pass MXFP4 SwiGLU producers: the activation is computed on the chunk in shared memory and only codes and
  * scales are written (no tensor-level scale exists, so nothing has to be known about the whole tensor first).
  * fp4b200_mxfp4_silu_mul_quantize: operands of bf16(silu(h1_raw) * h3)

@@ -929,6 +929,18 @@ int fp4b200_mxfp4_silu_mul_quantize(const void* h1_raw, const void* h3, int64_t 
                        (uint8_t*)col_sc, (cudaStream_t)stream);
 }
 
+int fp4b200_mxfp4_silu_mul_quantize_strided(const void* h13, int64_t h13_stride, int64_t h3_offset, int64_t M, int64_t H,
+                                            int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  const char* fn = "mxfp4_silu_mul_quantize_strided";
+  if (int rc = check_mx(h13, M, H, mode, fn)) return rc;
+  if (h3_offset < H || h3_offset + H > h13_stride || (h3_offset % 8) || (h13_stride % 8))
+    return set_error("%s: h13 must hold h1 in columns [0, H) and h3 in [h3_offset, h3_offset + H), both 16-byte aligned", fn);
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("%s: all outputs are required", fn);
+  const auto* h3 = reinterpret_cast<const uint8_t*>(h13) + (size_t)h3_offset * 2;
+  return launch_mx_act(1, h13, h3, nullptr, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4,
+                       (uint8_t*)col_sc, (cudaStream_t)stream, h13_stride, h13_stride);
+}
+
 int fp4b200_mxfp4_silu_deriv_quantize_split2(const void* dh, const void* h3, const void* h1_raw, int64_t M, int64_t H,
                                              int mode, void* row_fp4, void* row_sc, void* col_fp4, void* col_sc,
                                              void* stream) {

@@ -253,6 +253,26 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
     return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
 
 
+def mxfp4_fused_silu_mul_quantize_row_and_col_strided(h13, H, h3_offset, mode=0):
+    """tk_quantize.cu:4105-4132 — ``bf16(silu(h1) * h3)`` quantised row- and column-wise, h1 and h3 read out of the
+    packed gate|up activation ``h13`` [M, stride] (h1 in columns [0, H), h3 in [h3_offset, h3_offset + H)); returns
+    (row_fp4 [M, H/2], row_sc [M/128, H/128, 32, 16], col_fp4 [H, M/2], col_sc [H/128, M/128, 32, 16])."""
+    if not isinstance(h13, torch.Tensor) or not h13.is_cuda or not h13.is_contiguous() or h13.dtype != torch.bfloat16 or h13.dim() != 2:
+        raise RuntimeError("h13 must be a contiguous 2-D CUDA bf16 tensor")
+    M, H, h3_offset = int(h13.shape[0]), int(H), int(h3_offset)
+    if M % 128 or H % 128:
+        raise RuntimeError("M and H must be multiples of 128")
+    if h3_offset < H or h3_offset + H > int(h13.shape[1]):
+        raise RuntimeError("h13 must contain packed h1 and h3 slices")
+    u8 = dict(dtype=torch.uint8, device=h13.device)
+    row_fp4, row_sc = torch.empty((M, H // 2), **u8), torch.empty((M // 128, H // 128, 32, 16), **u8)
+    col_fp4, col_sc = torch.empty((H, M // 2), **u8), torch.empty((H // 128, M // 128, 32, 16), **u8)
+    with torch.cuda.device(h13.device):
+        _lib.call("fp4b200_mxfp4_silu_mul_quantize_strided", h13.data_ptr(), int(h13.shape[1]), h3_offset, M, H, int(mode),
+                  row_fp4.data_ptr(), row_sc.data_ptr(), col_fp4.data_ptr(), col_sc.data_ptr(), _stream(h13))
+    return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
+
+
 def mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined(dh, h13, H, h3_offset, mode=0):
     """tk_quantize.cu:5015-5099 — the two gradients of the packed gate|up activation ``h13`` [M, stride] (h1 in columns
     [0, H), h3 in [h3_offset, h3_offset + H)) laid out for the one-pass split dgrad GEMM: (row_fp4 [M, H] = dh1's

@@ -51,6 +51,7 @@ CASES = [
     ("silu_deriv_combined_m1", "mxfp4_fused_silu_deriv_quantize_split2_row_and_col_strided_combined", "dh_h13",
      (SHAPE[1], SHAPE[1], 1)),
     ("silu_deriv_splitcols_m1", "mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols", "dh_h3_h1", (1,)),
+    ("silu_mul_strided_m1", "mxfp4_fused_silu_mul_quantize_row_and_col_strided", "h13", (SHAPE[1], SHAPE[1], 1)),
 ]
 
 
@@ -74,6 +75,8 @@ def make_inputs(kind, seed):
         return (r(1e-3), r(1.0), r(2.0))
     if kind == "g":
         return (r(1e-3),)
+    if kind == "h13":
+        return (np.concatenate([r(2.0), r(1.0)], axis=1),)
     if kind == "dh_h13":       # the packed gate|up activation: h1 in the left half, h3 in the right
         return (r(1e-3), np.concatenate([r(2.0), r(1.0)], axis=1))
     raise ValueError(kind)
