@@ -169,6 +169,35 @@ def _mod(name):
     return importlib.import_module("mfu-fp4-training_b200." + name)
 
 
+def split3_only(args):
+    """One kernel family alone: the three-stream gradient quantiser of the attention backward (dQ | dK | dV with the
+    8B model's widths 4096 / 1024 / 1024, each with its own tensor amax): the grouped amax kernel, the grouped strip
+    quantiser and the concatenation of the row-wise scale tensors per call."""
+    import torch
+    M = int(args.split3_only)
+    tkq = _mod("tk_quant_v5")
+    peaks, _ = measured_peaks()
+    g = torch.Generator(device="cuda").manual_seed(11)
+    widths = (4096, 1024, 1024)
+    grads = [(1e-3 * torch.randn(M, n, device="cuda", generator=g)).to(torch.bfloat16) for n in widths]
+    steps, warm = min(args.steps, 50), max(args.warmup, 3)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    for _ in range(warm):
+        tkq.tk_group_quantize_dim1_split3_for_gemm(*grads)
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(steps):
+        tkq.tk_group_quantize_dim1_split3_for_gemm(*grads)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    # per element: 2 B read by the amax pass, 2 B read again, 0.5 + 0.0625 B written per operand
+    by = M * sum(widths) * (4.0 + 2 * 0.5625)
+    print(json.dumps({"split3_only": {"M": M, "widths": list(widths), "ms_per_call": ms, "launches_per_call": 3,
+                                      "algorithmic_GBps": by / (ms * 1e-3) / 1e9,
+                                      "frac_of_measured_hbm": by / (ms * 1e-3) / 1e9 / peaks["hbm_gbs"]}}))
+
+
 def load_reference_kernels():
     """The reference's own extension modules compiled by oracle/build_ref.sh (oracle/_ref/), or {} when absent.
     Used only to time the reference's kernels beside this library's on one GPU; nothing else touches them."""
@@ -942,10 +971,15 @@ def main():
                     help="time only the RMSNorm backward (sum3 form) at this shape (tuning / ncu capture helper)")
     ap.add_argument("--mx-swiglu-only", default=None, metavar="MxH",
                     help="time only the one-pass MXFP4 SwiGLU producers at this shape (tuning / ncu capture helper)")
+    ap.add_argument("--split3-only", default=None, metavar="M",
+                    help="time only the three-stream gradient quantiser (widths 4096/1024/1024) on M rows (ncu capture helper)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.mx_swiglu_only:
         mx_swiglu_only(args)
+        return
+    if args.split3_only:
+        split3_only(args)
         return
     if args.gemm_only:
         gemm_only(args)
