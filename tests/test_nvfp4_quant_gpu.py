@@ -205,12 +205,13 @@ def test_quantize_nhsd_wo_equals_quantising_the_permuted_tensor(shape, ec):
     assert_status_ok()
 
 
-@pytest.mark.parametrize("M", [1024, 4096])
-def test_split3_one_launch_equals_the_single_input_quantiser(M):
+@pytest.mark.parametrize("M,splits", [(1024, (2048, 512, 512)), (4096, (2048, 512, 512)), (128, (128, 128, 128)),
+                                      (256, (4096, 128, 128)), (384, (128, 2560, 384))])
+def test_split3_one_launch_equals_the_single_input_quantiser(M, splits):
     """The grouped launch (CTAs shared out among the three matrices; at M = 4096 each warp takes strip pairs) writes
-    the bytes of one single-input quantiser call per stream, at attention-gradient widths."""
+    the bytes of one single-input quantiser call per stream: attention-gradient widths, one chunk per matrix, and
+    very unequal widths (a matrix's share of the CTAs is never less than one)."""
     tkq = mod("tk_quant_v5")
-    splits = (2048, 512, 512)
     g = torch.Generator(device="cuda").manual_seed(M)
     xs = [(10.0 ** (-i) * torch.randn(M, n, device="cuda", generator=g)).to(torch.bfloat16) for i, n in enumerate(splits)]
     out = tkq.tk_group_quantize_dim1_split3_for_gemm(*xs)
