@@ -764,7 +764,7 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
     dh = torch.empty(M, H, dtype=torch.bfloat16, device=dev)
     dxf = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
     dattn = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
-    dqkv = rnd(M, NQKV, 1e-3)
+    dq, dk, dv = rnd(M, K, 1e-3), rnd(M, (NQKV - K) // 2, 1e-3), rnd(M, (NQKV - K) // 2, 1e-3)   # as attention's backward leaves them
     dxa = torch.empty(M, K, dtype=torch.bfloat16, device=dev)
     dw = {n_: torch.empty(*wshapes[n_], dtype=torch.bfloat16, device=dev) for n_ in wnames}
     def s_q_dy():
@@ -792,7 +792,7 @@ def mxfp4_layer_leg(torch, dist, world, gamma, peaks):
     def s_o_wgrad():
         q, f = st["gdo"], st["qa"]; gmx.mxfp4_gemm(q[2], q[3], f[2], f[3], dw["o"])
     def s_q_dqkv():
-        st["gq"] = mxq.mxfp4_quantize_row_and_col(dqkv, 1)
+        st["gq"] = mxq.mxfp4_quantize_split3_row_and_col(dq, dk, dv, 1)     # no bf16 concatenation (mxfp4_fused_linear.py:3748)
     def s_qkv_dgrad():
         q = st["gq"]; gmx.mxfp4_gemm(q[0], q[1], wq["qkv"][2], wq["qkv"][3], dxa)
     def s_qkv_wgrad():

@@ -343,6 +343,14 @@ int fp4b200_mxfp4_gemm_ksplit_strided(const void* A_full, int64_t a_width, int n
 int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
                                      void* col_fp4, void* col_sc, void* stream);
 
+/* mxfp4_quantize_split2_row_and_col(input0, input1, mode) / mxfp4_quantize_split3_row_and_col(input0, input1, input2,
+ * mode) and their _launch_inplace twins (mxfp4_v4/tk_quantize.cu:5375-5470, 6254-6440): the operands of the column
+ * concatenation [M, sum widths] of n = 2 or 3 bf16 matrices with the same row count (the gradients of a fused
+ * projection's outputs) without concatenating them: row_fp4 [M, K/2], row_sc [M/128, K/128, 512], col_fp4 [K, M/2],
+ * col_sc [K/128, M/128, 512], K = sum of widths. */
+int fp4b200_mxfp4_quantize_split(const void* const* xs, const int64_t* widths, int n, int64_t M, int mode, void* row_fp4,
+                                 void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
 /* mxfp4_fused_silu_mul_quantize_row_and_col_strided(h13, H, h3_offset, mode) (mxfp4_v4/tk_quantize.cu:4105-4132): the
  * SwiGLU producer reading h1 and h3 out of one packed gate|up activation h13 [M, h13_stride] (h1 in columns [0, H), h3
  * in [h3_offset, h3_offset + H)); outputs as fp4b200_mxfp4_silu_mul_quantize. */

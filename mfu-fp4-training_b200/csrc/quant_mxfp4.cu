@@ -42,6 +42,10 @@ struct MxArgs {
   int* status;
   int M, K, chunks_m, chunks_k;
   int mode;                    // 0 RTE, 1 ceil ("encode"), 2 floor ("decode")
+  // the matrix may be the column concatenation of up to three inputs that are never concatenated in memory: column
+  // chunks [0, split_chunk[0]) come from the first tensor map, [split_chunk[0], split_chunk[1]) from the second, the
+  // rest from the third (one input: both = chunks_k)
+  int split_chunk[2];
 };
 
 __device__ __forceinline__ uint32_t mx_e8m0(float b, int mode) {
@@ -75,7 +79,8 @@ __device__ __forceinline__ uint32_t mx_weight_tile_e8m0(float tile_amax) {
 
 template <bool NORM, bool W2D>
 __global__ void __launch_bounds__(kMxThreads, 2)
-mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a) {
+mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x1,
+                      const __grid_constant__ CUtensorMap tmap_x2, const MxArgs a) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   MxSmem& sm = *reinterpret_cast<MxSmem*>(smem_align_1024(smem_raw));
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -91,11 +96,16 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const MxArgs a
     int cm, ck;
     chunk_coords(it, cm, ck);
     mbar_expect_tx(&sm.full[s], kMxTileBytes);
-    tma_load_2d(sm.in[s], &tmap_x, ck * kMxChunk, cm * kMxChunk, &sm.full[s]);
-    tma_load_2d(sm.in[s] + kMxHalfBytes, &tmap_x, ck * kMxChunk + 64, cm * kMxChunk, &sm.full[s]);
+    const CUtensorMap* src = &tmap_x;
+    if (ck >= a.split_chunk[1]) { src = &tmap_x2; ck -= a.split_chunk[1]; }
+    else if (ck >= a.split_chunk[0]) { src = &tmap_x1; ck -= a.split_chunk[0]; }
+    tma_load_2d(sm.in[s], src, ck * kMxChunk, cm * kMxChunk, &sm.full[s]);
+    tma_load_2d(sm.in[s] + kMxHalfBytes, src, ck * kMxChunk + 64, cm * kMxChunk, &sm.full[s]);
   };
   if (tid == 0) {
     tma_prefetch_desc(&tmap_x);
+    if (a.split_chunk[0] < a.chunks_k) tma_prefetch_desc(&tmap_x1);
+    if (a.split_chunk[1] < a.chunks_k) tma_prefetch_desc(&tmap_x2);
     for (int s = 0; s < kMxStages; ++s) mbar_init(&sm.full[s], 1);
     fence_mbar_init();
   }
@@ -807,30 +817,44 @@ static int launch_mx_row_sr(const MxSrArgs& a, cudaStream_t st) {
   return 0;
 }
 
+// x1 / x2 with their widths k1 / k2 (elements): further inputs whose columns follow x's (K is the total width).
 static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float* inv_rms, const void* gamma,
-                     void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st, bool weight_2d = false) {
-  CUtensorMap tmap;
-  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)M, (uint64_t)K * 2,
+                     void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st, bool weight_2d = false,
+                     const void* x1 = nullptr, int64_t k1 = 0, const void* x2 = nullptr, int64_t k2 = 0) {
+  const int64_t k0 = K - k1 - k2;
+  CUtensorMap tmap, tmap1, tmap2;
+  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k0, (uint64_t)M, (uint64_t)k0 * 2,
                             64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
+  tmap1 = tmap2 = tmap;
+  if (x1 != nullptr)
+    if (int rc = make_tmap_2d(&tmap1, x1, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k1, (uint64_t)M, (uint64_t)k1 * 2,
+                              64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  if (x2 != nullptr)
+    if (int rc = make_tmap_2d(&tmap2, x2, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k2, (uint64_t)M, (uint64_t)k2 * 2,
+                              64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
   MxArgs a{};
   a.inv_rms = inv_rms; a.gamma = (const __nv_bfloat16*)gamma;
   a.row_fp4 = (uint8_t*)row_fp4; a.row_sc = (uint8_t*)row_sc; a.col_fp4 = (uint8_t*)col_fp4; a.col_sc = (uint8_t*)col_sc;
   a.status = device_status_ptr();
   if (!a.status) return -1;
   a.M = (int)M; a.K = (int)K; a.chunks_m = (int)(M / kMxChunk); a.chunks_k = (int)(K / kMxChunk); a.mode = mode;
+  a.split_chunk[0] = (int)(k0 / kMxChunk);
+  a.split_chunk[1] = (int)((k0 + k1) / kMxChunk);
   const int smem = (int)sizeof(MxSmem) + 1024;
   const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
   if (grid == 0) return 0;
   if (weight_2d) {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    mxfp4_quantize_kernel<false, true><<<grid, kMxThreads, smem, st>>>(tmap, a);
+    mxfp4_quantize_kernel<false, true><<<grid, kMxThreads, smem, st>>>(tmap, tmap1, tmap2, a);
   } else if (inv_rms) {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    mxfp4_quantize_kernel<true, false><<<grid, kMxThreads, smem, st>>>(tmap, a);
+    mxfp4_quantize_kernel<true, false><<<grid, kMxThreads, smem, st>>>(tmap, tmap1, tmap2, a);
   } else {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    mxfp4_quantize_kernel<false, false><<<grid, kMxThreads, smem, st>>>(tmap, a);
+    mxfp4_quantize_kernel<false, false><<<grid, kMxThreads, smem, st>>>(tmap, tmap1, tmap2, a);
   }
   FP4_CUDA_CHECK(cudaGetLastError());
   return 0;
@@ -927,6 +951,20 @@ int fp4b200_mxfp4_silu_mul_quantize(const void* h1_raw, const void* h3, int64_t 
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_silu_mul_quantize: all outputs are required");
   return launch_mx_act(1, h1_raw, h3, nullptr, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4,
                        (uint8_t*)col_sc, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_quantize_split(const void* const* xs, const int64_t* widths, int n, int64_t M, int mode, void* row_fp4,
+                                 void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  const char* fn = "mxfp4_quantize_split";
+  if (!xs || !widths || n < 2 || n > 3) return set_error("%s: two or three inputs are supported", fn);
+  int64_t K = 0;
+  for (int i = 0; i < n; ++i) {
+    if (int rc = check_mx(xs[i], M, widths[i], mode, fn)) return rc;
+    K += widths[i];
+  }
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("%s: all four outputs are required", fn);
+  return launch_mx(xs[0], M, K, mode, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, false,
+                   xs[1], widths[1], n == 3 ? xs[2] : nullptr, n == 3 ? widths[2] : 0);
 }
 
 int fp4b200_mxfp4_silu_mul_quantize_strided(const void* h13, int64_t h13_stride, int64_t h3_offset, int64_t M, int64_t H,

@@ -253,6 +253,55 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
     return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
 
 
+def _quantize_split(inputs, outs, mode):
+    import ctypes
+    M = None
+    for t in inputs:
+        if (not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous() or t.dtype != torch.bfloat16
+                or t.dim() != 2 or t.shape[0] % 128 or t.shape[1] % 128):
+            raise RuntimeError("split inputs must be contiguous bf16 matrices with dims divisible by 128")
+        if M is not None and int(t.shape[0]) != M:
+            raise RuntimeError("split inputs must have the same M dimension")
+        M = int(t.shape[0])
+    K = sum(int(t.shape[1]) for t in inputs)
+    if outs is None:
+        u8 = dict(dtype=torch.uint8, device=inputs[0].device)
+        outs = (torch.empty((M, K // 2), **u8).view(_FP4), torch.empty((M // 128, K // 128, 32, 16), **u8),
+                torch.empty((K, M // 2), **u8).view(_FP4), torch.empty((K // 128, M // 128, 32, 16), **u8))
+    else:
+        _check_operand_outs(*outs, M, K)
+    n = len(inputs)
+    xs = (ctypes.c_void_p * n)(*[t.data_ptr() for t in inputs])
+    widths = (ctypes.c_int64 * n)(*[int(t.shape[1]) for t in inputs])
+    with torch.cuda.device(inputs[0].device):
+        _lib.call("fp4b200_mxfp4_quantize_split", xs, widths, n, M, int(mode), outs[0].data_ptr(), outs[1].data_ptr(),
+                  outs[2].data_ptr(), outs[3].data_ptr(), _stream(inputs[0]))
+    return outs
+
+
+def mxfp4_quantize_split2_row_and_col(input0, input1, mode=0):
+    """tk_quantize.cu:5375-5440 — the operands of ``cat([input0, input1], dim=1)`` without the bf16 concatenation
+    (dh1 | dh3 of a fused gate/up projection): (row_fp4 [M, K/2], row_sc [M/128, K/128, 32, 16], col_fp4 [K, M/2],
+    col_sc [K/128, M/128, 32, 16]), K = K0 + K1."""
+    return _quantize_split((input0, input1), None, mode)
+
+
+def mxfp4_quantize_split2_row_and_col_launch_inplace(input0, input1, row_fp4, row_sc, col_fp4, col_sc, mode=0):
+    """tk_quantize.cu:5443-5470 — the same into the caller's tensors; returns None."""
+    _quantize_split((input0, input1), (row_fp4, row_sc, col_fp4, col_sc), mode)
+
+
+def mxfp4_quantize_split3_row_and_col(input0, input1, input2, mode=0):
+    """tk_quantize.cu:6254-6345 — the operands of ``cat([input0, input1, input2], dim=1)`` without the concatenation
+    (dQ | dK | dV on the way to the QKV dgrad and wgrad); shapes as the two-input form with K = K0 + K1 + K2."""
+    return _quantize_split((input0, input1, input2), None, mode)
+
+
+def mxfp4_quantize_split3_row_and_col_launch_inplace(input0, input1, input2, row_fp4, row_sc, col_fp4, col_sc, mode=0):
+    """tk_quantize.cu:6348-6440 — the same into the caller's tensors; returns None."""
+    _quantize_split((input0, input1, input2), (row_fp4, row_sc, col_fp4, col_sc), mode)
+
+
 def mxfp4_fused_silu_mul_quantize_row_and_col_strided(h13, H, h3_offset, mode=0):
     """tk_quantize.cu:4105-4132 — ``bf16(silu(h1) * h3)`` quantised row- and column-wise, h1 and h3 read out of the
     packed gate|up activation ``h13`` [M, stride] (h1 in columns [0, H), h3 in [h3_offset, h3_offset + H)); returns

@@ -44,6 +44,13 @@ def mxfp4_batched_gemm_config(A_list, A_sc_list, B_list, B_sc_list, D_out_list, 
     mxfp4_batched_gemm(A_list, A_sc_list, B_list, B_sc_list, D_out_list)
 
 
+def mxfp4_split3_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list, D_out,
+                                            config_idx=-1):
+    """mxfp4_gb200_gemm.cu:2677-2700 — the three-split form (dQ | dK | dV against the three row blocks of the QKV
+    weight's column operand): ``D_out = bf16((sum_s A_full[:, off_s:off_s+w_s] . B_s^T) / 36)``, one launch."""
+    _split_dgrad_onepass(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list, D_out, 3)
+
+
 def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list, D_out,
                                             config_idx=-1):
     """mxfp4_gb200_gemm.cu:2572-2596 — ``D_out = bf16((sum_s A_full[:, off_s:off_s+w_s] . B_s^T) / 36)``: the
@@ -51,12 +58,16 @@ def mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_
     accumulated in tensor memory before the one rounding.  ``A_col_offsets`` / ``A_col_widths`` count PACKED columns
     (bytes of ``A_full``, two elements each), as the reference's do (checks at :430-467).  ``config_idx`` is accepted
     and ignored."""
+    _split_dgrad_onepass(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list, D_out, 2)
+
+
+def _split_dgrad_onepass(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list, D_out, want):
     import ctypes
     n = len(B_list)
-    if n != 2:
-        raise RuntimeError("split2 one-pass dgrad expects exactly 2 B tensors")
+    if n != want:
+        raise RuntimeError(f"split{want} one-pass dgrad expects exactly {want} B tensors")
     if not (len(A_sc_list) == len(A_col_offsets) == len(A_col_widths) == len(B_sc_list) == n):
-        raise RuntimeError("split2 one-pass dgrad: list lengths differ")
+        raise RuntimeError(f"split{want} one-pass dgrad: list lengths differ")
     _chk_operand(A_full, "A_full")
     for t in list(B_list) + list(B_sc_list):
         _chk_operand(t, "operand")

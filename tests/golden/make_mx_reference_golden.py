@@ -52,6 +52,9 @@ CASES = [
      (SHAPE[1], SHAPE[1], 1)),
     ("silu_deriv_splitcols_m1", "mxfp4_fused_silu_deriv_quantize_split2_row_and_col_splitcols", "dh_h3_h1", (1,)),
     ("silu_mul_strided_m1", "mxfp4_fused_silu_mul_quantize_row_and_col_strided", "h13", (SHAPE[1], SHAPE[1], 1)),
+    ("split2_m1", "mxfp4_quantize_split2_row_and_col", "g2", (1,)),
+    ("split3_m1", "mxfp4_quantize_split3_row_and_col", "g3", (1,)),
+    ("split3_m0", "mxfp4_quantize_split3_row_and_col", "g3", (0,)),
 ]
 
 
@@ -75,6 +78,9 @@ def make_inputs(kind, seed):
         return (r(1e-3), r(1.0), r(2.0))
     if kind == "g":
         return (r(1e-3),)
+    if kind in ("g2", "g3"):      # gradients of a fused projection's outputs: different widths, the same rows
+        widths = (K, 128) if kind == "g2" else (256, 128, K)
+        return tuple(o.bf16_round((1e-3 * 4.0 ** i * rng.standard_normal((M, w))).astype(np.float32)) for i, w in enumerate(widths))
     if kind == "h13":
         return (np.concatenate([r(2.0), r(1.0)], axis=1),)
     if kind == "dh_h13":       # the packed gate|up activation: h1 in the left half, h3 in the right
@@ -110,6 +116,13 @@ def combined_inputs():
     rng = np.random.default_rng(740)
     r = lambda s, n: o.bf16_round((s * rng.standard_normal((Mo, n))).astype(np.float32))
     return r(1e-3, w), np.concatenate([r(2.0, w), r(1.0, w)], axis=1)
+
+
+def split3_inputs():
+    """Three gradients [M, 512 | 256 | 256] of the three-split GEMM case; the tests call this too."""
+    Mo = ONEPASS[0]
+    rng = np.random.default_rng(760)
+    return tuple(o.bf16_round((1e-3 * rng.standard_normal((Mo, w))).astype(np.float32)) for w in (512, 256, 256))
 
 
 def load_reference_gemm_module():
@@ -182,6 +195,23 @@ def main():
                                                          [ws[0][1], ws[1][1]], d, -1)
         torch.cuda.synchronize()
         out["onepass_combined.d"] = d.view(torch.int16).cpu().numpy()
+    if ref_gemm is not None:
+        # QKV dgrad as the reference runs it: split3 quantiser (no concatenation), then the three-split one-pass GEMM
+        Mo, No, w = ONEPASS
+        gs = split3_inputs()
+        q = ref.mxfp4_quantize_split3_row_and_col(*(torch.from_numpy(t).to(torch.bfloat16).to(dev) for t in gs), 1)
+        ws = [ref.mxfp4_quantize_for_gemm(torch.from_numpy(gemm_operands((1, No, t.shape[1]), 750 + i)[1]).to(torch.bfloat16).to(dev), 1)
+              for i, t in enumerate(gs)]
+        offs, a_scs, off = [], [], 0
+        for t in gs:
+            offs.append(off // 2)
+            a_scs.append(q[1].narrow(1, off // 128, t.shape[1] // 128))
+            off += t.shape[1]
+        d = torch.empty(Mo, No, dtype=torch.bfloat16, device=dev)
+        ref_gemm.mxfp4_split3_dgrad_strided_onepass_gemm(q[0], a_scs, offs, [t.shape[1] // 2 for t in gs], [x[0] for x in ws],
+                                                         [x[1] for x in ws], d, -1)
+        torch.cuda.synchronize()
+        out["onepass_split3.d"] = d.view(torch.int16).cpu().numpy()
     dst = os.environ.get("MX_GOLDEN_OUT", os.path.join(HERE, "mxfp4_reference_kernels_golden.npz"))
     np.savez_compressed(dst, **out)
     print(f"wrote {dst}: {len(out)} arrays, {os.path.getsize(dst)} bytes")

@@ -132,3 +132,39 @@ def test_combined_producer_into_onepass_dgrad_reproduces_the_reference_kernels_b
         gemm.mxfp4_split2_dgrad_strided_onepass_gemm(sp[0], [sp[1][:, :, :16], sp[1].narrow(1, w // 128, w // 128)],
                                                      [0, w // 2], [w // 2, w // 2], [ws[0][0], ws[1][0]], [ws[0][1], ws[1][1]], d2, -1)
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "onepass_split3.d" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+def test_split3_quantiser_into_three_split_onepass_dgrad_reproduces_the_reference_kernels_bytes():
+    """QKV dgrad as the reference runs it: dQ | dK | dV quantised without a concatenation, then one GEMM over the three
+    column slices, each against its own weight operand; and the split quantisers equal the quantiser of the
+    concatenation."""
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    Mo, No, _ = G.ONEPASS
+    gs = [to_dev_bf16(t) for t in G.split3_inputs()]
+    q = mxq.mxfp4_quantize_split3_row_and_col(*gs, 1)
+    ws = [mxq.mxfp4_quantize_for_gemm(to_dev_bf16(G.gemm_operands((1, No, t.shape[1]), 750 + i)[1]), 1) for i, t in enumerate(gs)]
+    offs, a_scs, off = [], [], 0
+    for t in gs:
+        offs.append(off // 2)
+        a_scs.append(q[1].narrow(1, off // 128, t.shape[1] // 128))
+        off += t.shape[1]
+    d = torch.empty(Mo, No, dtype=torch.bfloat16, device="cuda")
+    gemm.mxfp4_split3_dgrad_strided_onepass_gemm(q[0], a_scs, offs, [t.shape[1] // 2 for t in gs], [x[0] for x in ws],
+                                                 [x[1] for x in ws], d, -1)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD["onepass_split3.d"])
+    whole = mxq.mxfp4_quantize_row_and_col(torch.cat(gs, 1).contiguous(), 1)
+    for a, b in zip(q, whole):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    two = mxq.mxfp4_quantize_split2_row_and_col(gs[0], gs[1], 1)
+    whole2 = mxq.mxfp4_quantize_row_and_col(torch.cat(gs[:2], 1).contiguous(), 1)
+    for a, b in zip(two, whole2):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    outs = [torch.empty_like(t) for t in q]
+    assert mxq.mxfp4_quantize_split3_row_and_col_launch_inplace(*gs, *outs, 1) is None
+    for a, b in zip(outs, q):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    with pytest.raises(RuntimeError):
+        mxq.mxfp4_quantize_split3_row_and_col(gs[0], gs[1], gs[2][:128], 1)
+    assert_status_ok()
