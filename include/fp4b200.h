@@ -343,6 +343,13 @@ int fp4b200_mxfp4_gemm_ksplit_strided(const void* A_full, int64_t a_width, int n
 int fp4b200_mxfp4_quantize_weight_2d(const void* w_bf16, int64_t N, int64_t K, void* row_fp4, void* row_sc,
                                      void* col_fp4, void* col_sc, void* stream);
 
+/* mxfp4_quantize_nhsd_wo_row_and_col(input, mode) (mxfp4_v4/tk_quantize.cu:2739-2830): the attention output in its
+ * native [B, H, S, D] layout (D a multiple of 64, S of 128) quantised as the matrix [M = B*S, K = H*D] the output
+ * projection consumes (element (b*S + s, h*D + d) = input[b, h, s, d]) without a transposing copy; outputs as
+ * fp4b200_mxfp4_quantize. */
+int fp4b200_mxfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int64_t S, int64_t D, int mode, void* row_fp4,
+                                   void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
 /* mxfp4_quantize_split2_row_and_col(input0, input1, mode) / mxfp4_quantize_split3_row_and_col(input0, input1, input2,
  * mode) and their _launch_inplace twins (mxfp4_v4/tk_quantize.cu:5375-5470, 6254-6440): the operands of the column
  * concatenation [M, sum widths] of n = 2 or 3 bf16 matrices with the same row count (the gradients of a fused

@@ -58,6 +58,8 @@ SIGNATURES = {
     "fp4b200_nvfp4_rmsnorm_inv_rms_opt": [_c_void_p, _c_void_p, _f32, _i64, _i64, _c_void_p, _c_void_p],
     "fp4b200_mxfp4_silu_mul_quantize": [_c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
                                         _c_void_p],
+    "fp4b200_mxfp4_quantize_nhsd_wo": [_c_void_p, _i64, _i64, _i64, _i64, _int, _c_void_p, _c_void_p, _c_void_p, _c_void_p,
+                                       _c_void_p],
     "fp4b200_mxfp4_quantize_split": [ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _int, _i64, _int, _c_void_p, _c_void_p,
                                      _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_mxfp4_silu_mul_quantize_strided": [_c_void_p, _i64, _i64, _i64, _i64, _int, _c_void_p, _c_void_p, _c_void_p,

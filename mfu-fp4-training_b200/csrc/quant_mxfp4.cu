@@ -46,6 +46,9 @@ struct MxArgs {
   // chunks [0, split_chunk[0]) come from the first tensor map, [split_chunk[0], split_chunk[1]) from the second, the
   // rest from the third (one input: both = chunks_k)
   int split_chunk[2];
+  // > 0: the input is [B, heads, seq, dim] (dim a multiple of 64, seq of 128) and the matrix [B*seq, heads*dim] with
+  // element (b*seq + s, h*dim + d) = input[b, h, s, d]; tmap_x then describes [B*heads*seq, dim]
+  int nhsd_heads, nhsd_seq, nhsd_dim;
 };
 
 __device__ __forceinline__ uint32_t mx_e8m0(float b, int mode) {
@@ -99,6 +102,17 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
     const CUtensorMap* src = &tmap_x;
     if (ck >= a.split_chunk[1]) { src = &tmap_x2; ck -= a.split_chunk[1]; }
     else if (ck >= a.split_chunk[0]) { src = &tmap_x1; ck -= a.split_chunk[0]; }
+    if (a.nhsd_seq > 0) {
+      // a half tile (128 tokens of one sequence x 64 columns of one head) is a contiguous block of rows of [B*heads*seq, dim]
+      const int b = (cm * kMxChunk) / a.nhsd_seq, s0 = cm * kMxChunk - b * a.nhsd_seq;
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        const int col = ck * kMxChunk + h2 * 64, head = col / a.nhsd_dim;
+        tma_load_2d(sm.in[s] + h2 * kMxHalfBytes, src, col - head * a.nhsd_dim, (b * a.nhsd_heads + head) * a.nhsd_seq + s0,
+                    &sm.full[s]);
+      }
+      return;
+    }
     tma_load_2d(sm.in[s], src, ck * kMxChunk, cm * kMxChunk, &sm.full[s]);
     tma_load_2d(sm.in[s] + kMxHalfBytes, src, ck * kMxChunk + 64, cm * kMxChunk, &sm.full[s]);
   };
@@ -820,11 +834,15 @@ static int launch_mx_row_sr(const MxSrArgs& a, cudaStream_t st) {
 // x1 / x2 with their widths k1 / k2 (elements): further inputs whose columns follow x's (K is the total width).
 static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float* inv_rms, const void* gamma,
                      void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st, bool weight_2d = false,
-                     const void* x1 = nullptr, int64_t k1 = 0, const void* x2 = nullptr, int64_t k2 = 0) {
+                     const void* x1 = nullptr, int64_t k1 = 0, const void* x2 = nullptr, int64_t k2 = 0,
+                     int nhsd_heads = 0, int nhsd_seq = 0, int nhsd_dim = 0) {
   const int64_t k0 = K - k1 - k2;
   CUtensorMap tmap, tmap1, tmap2;
-  if (int rc = make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k0, (uint64_t)M, (uint64_t)k0 * 2,
-                            64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
+  if (int rc = nhsd_seq > 0
+                   ? make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)nhsd_dim, (uint64_t)M * nhsd_heads,
+                                  (uint64_t)nhsd_dim * 2, 64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B)
+                   : make_tmap_2d(&tmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)k0, (uint64_t)M, (uint64_t)k0 * 2,
+                                  64, kMxChunk, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   tmap1 = tmap2 = tmap;
   if (x1 != nullptr)
@@ -843,6 +861,7 @@ static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float*
   a.M = (int)M; a.K = (int)K; a.chunks_m = (int)(M / kMxChunk); a.chunks_k = (int)(K / kMxChunk); a.mode = mode;
   a.split_chunk[0] = (int)(k0 / kMxChunk);
   a.split_chunk[1] = (int)((k0 + k1) / kMxChunk);
+  a.nhsd_heads = nhsd_heads; a.nhsd_seq = nhsd_seq; a.nhsd_dim = nhsd_dim;
   const int smem = (int)sizeof(MxSmem) + 1024;
   const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
   if (grid == 0) return 0;
@@ -951,6 +970,19 @@ int fp4b200_mxfp4_silu_mul_quantize(const void* h1_raw, const void* h3, int64_t 
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("mxfp4_silu_mul_quantize: all outputs are required");
   return launch_mx_act(1, h1_raw, h3, nullptr, M, H, mode, (uint8_t*)row_fp4, (uint8_t*)row_sc, (uint8_t*)col_fp4,
                        (uint8_t*)col_sc, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int64_t S, int64_t D, int mode, void* row_fp4,
+                                   void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  const char* fn = "mxfp4_quantize_nhsd_wo";
+  if (B <= 0 || H <= 0 || S <= 0 || D <= 0) return set_error("%s: B, H, S and D must be positive", fn);
+  if (D % 64) return set_error("%s: head_dim must be a multiple of 64 (got %lld)", fn, (long long)D);
+  if (S % 128) return set_error("%s: the sequence length must be a multiple of 128 (got %lld)", fn, (long long)S);
+  if (B * S > INT32_MAX || H * D > INT32_MAX || B * H * S > INT32_MAX) return set_error("%s: dimension too large", fn);
+  if (int rc = check_mx(x_bf16, B * S, H * D, mode, fn)) return rc;
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("%s: all four outputs are required", fn);
+  return launch_mx(x_bf16, B * S, H * D, mode, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, false,
+                   nullptr, 0, nullptr, 0, (int)H, (int)S, (int)D);
 }
 
 int fp4b200_mxfp4_quantize_split(const void* const* xs, const int64_t* widths, int n, int64_t M, int mode, void* row_fp4,

@@ -253,6 +253,31 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
     return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
 
 
+def mxfp4_quantize_nhsd_wo_row_and_col(input, mode=0):
+    """tk_quantize.cu:2739-2830 — the attention output ``input`` [B, H, S, D] quantised as the [B*S, H*D] matrix the
+    output projection consumes, without the transposing copy; returns (row_fp4 [M, K/2], row_sc [M/128, K/128, 32, 16],
+    col_fp4 [K, M/2], col_sc [K/128, M/128, 32, 16])."""
+    if not isinstance(input, torch.Tensor) or not input.is_cuda or not input.is_contiguous():
+        raise RuntimeError("NHSD WO MXFP4 quantize expects a contiguous CUDA tensor")
+    if input.dtype != torch.bfloat16 or input.dim() != 4:
+        raise RuntimeError("NHSD WO MXFP4 quantize expects bf16 [B,H,S,D]")
+    B, H, S, D = (int(v) for v in input.shape)
+    if D % 64:
+        raise RuntimeError("NHSD WO MXFP4 quantize requires head_dim to be a multiple of 64")
+    if S % 128:
+        raise RuntimeError("NHSD WO MXFP4 quantize requires sequence length to be a multiple of 128")
+    M, K = B * S, H * D
+    if M % 128 or K % 128:
+        raise RuntimeError("logical [B*S,H*D] dimensions must be multiples of 128")
+    u8 = dict(dtype=torch.uint8, device=input.device)
+    row_fp4, row_sc = torch.empty((M, K // 2), **u8), torch.empty((M // 128, K // 128, 32, 16), **u8)
+    col_fp4, col_sc = torch.empty((K, M // 2), **u8), torch.empty((K // 128, M // 128, 32, 16), **u8)
+    with torch.cuda.device(input.device):
+        _lib.call("fp4b200_mxfp4_quantize_nhsd_wo", input.data_ptr(), B, H, S, D, int(mode), row_fp4.data_ptr(),
+                  row_sc.data_ptr(), col_fp4.data_ptr(), col_sc.data_ptr(), _stream(input))
+    return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
+
+
 def _quantize_split(inputs, outs, mode):
     import ctypes
     M = None

@@ -55,6 +55,8 @@ CASES = [
     ("split2_m1", "mxfp4_quantize_split2_row_and_col", "g2", (1,)),
     ("split3_m1", "mxfp4_quantize_split3_row_and_col", "g3", (1,)),
     ("split3_m0", "mxfp4_quantize_split3_row_and_col", "g3", (0,)),
+    ("nhsd_d64_m1", "mxfp4_quantize_nhsd_wo_row_and_col", "nhsd64", (1,)),
+    ("nhsd_d128_m1", "mxfp4_quantize_nhsd_wo_row_and_col", "nhsd128", (1,)),
 ]
 
 
@@ -81,6 +83,9 @@ def make_inputs(kind, seed):
     if kind in ("g2", "g3"):      # gradients of a fused projection's outputs: different widths, the same rows
         widths = (K, 128) if kind == "g2" else (256, 128, K)
         return tuple(o.bf16_round((1e-3 * 4.0 ** i * rng.standard_normal((M, w))).astype(np.float32)) for i, w in enumerate(widths))
+    if kind in ("nhsd64", "nhsd128"):   # attention output [B, H, S, D]
+        shape = (2, 4, 128, 64) if kind == "nhsd64" else (1, 3, 256, 128)
+        return (o.bf16_round(rng.standard_normal(shape).astype(np.float32)),)
     if kind == "h13":
         return (np.concatenate([r(2.0), r(1.0)], axis=1),)
     if kind == "dh_h13":       # the packed gate|up activation: h1 in the left half, h3 in the right

@@ -168,3 +168,19 @@ def test_split3_quantiser_into_three_split_onepass_dgrad_reproduces_the_referenc
     with pytest.raises(RuntimeError):
         mxq.mxfp4_quantize_split3_row_and_col(gs[0], gs[1], gs[2][:128], 1)
     assert_status_ok()
+
+
+def test_nhsd_attention_output_quantiser_equals_the_quantiser_of_the_transposed_copy():
+    mxq = mod("mxfp4_quant_v4")
+    g = torch.Generator(device="cuda").manual_seed(5)
+    for shape in ((2, 8, 256, 64), (1, 4, 384, 128)):
+        x = torch.randn(*shape, device="cuda", generator=g).to(torch.bfloat16)
+        B, H, S, D = shape
+        flat = x.permute(0, 2, 1, 3).reshape(B * S, H * D).contiguous()
+        for a, b in zip(mxq.mxfp4_quantize_nhsd_wo_row_and_col(x, 1), mxq.mxfp4_quantize_row_and_col(flat, 1)):
+            assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    with pytest.raises(RuntimeError):
+        mxq.mxfp4_quantize_nhsd_wo_row_and_col(x[:, :, :64].contiguous(), 1)      # S not a multiple of 128
+    with pytest.raises(RuntimeError):
+        mxq.mxfp4_quantize_nhsd_wo_row_and_col(torch.zeros(1, 4, 128, 32, dtype=torch.bfloat16, device="cuda"), 1)
+    assert_status_ok()
