@@ -191,7 +191,8 @@ int fp4b200_nvfp4_fused_norm_quantize_noalloc(const void* x_bf16, const void* ga
 /* Row (+column when col_* non-NULL) MXFP4 quantisation of bf16 [M,K]: 32-element blocks, E8M0
  * scale = exponent of the block amax rounded by mode (0 RTE, 1 ceil, 2 floor), codes =
  * e2m1(x * 6 * 2^(127-e)).  Replaces mxfp4_quantize_row_and_col / mxfp4_quantize_for_gemm
- * (fp4_runtime/TK_quantisation/mxfp4_v4/tk_quantize.cu:1883-2060; kernels mxfp4_v3_quantize.cuh:1540-1790). */
+ * (fp4_runtime/TK_quantisation/mxfp4_v4/tk_quantize.cu:1883-2060; kernels mxfp4_v3_quantize.cuh:1540-1790) and, with
+ * row_fp4 = row_sc = NULL, mxfp4_quantize_col_only (tk_quantize.cu:2404-2470): the column operand alone. */
 int fp4b200_mxfp4_quantize(const void* x_bf16, int64_t M, int64_t K, int mode, void* row_fp4, void* row_sc,
                            void* col_fp4, void* col_sc, void* stream);
 

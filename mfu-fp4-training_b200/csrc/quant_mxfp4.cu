@@ -182,8 +182,10 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       if ((lane & 15) == 0) sm.tile_e8[grp][chalf * 2 + (lane >> 4)] = (uint8_t)mx_weight_tile_e8m0(b);
       __syncthreads();
     }
+    // the row pass also normalises the tile in place for the column pass (NORM); without row outputs it is skipped otherwise
+    const bool row_pass = NORM || a.row_fp4 != nullptr;
 #pragma unroll
-    for (int rep = 0; rep < 2; ++rep) {
+    for (int rep = 0; rep < 2 && row_pass; ++rep) {
       const int r = warp * 16 + rep * 8 + r_lo;
       uint8_t* rowp = tile + half_off + r * 128;
       uint32_t w[16];
@@ -218,7 +220,7 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       uint4 codes;
       codes.x = quant8(w, coeff); codes.y = quant8(w + 4, coeff);
       codes.z = quant8(w + 8, coeff); codes.w = quant8(w + 12, coeff);
-      st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1), codes);
+      if (a.row_fp4 != nullptr) st_cs_u4(a.row_fp4 + (size_t)(m0 + r) * (a.K >> 1) + ((k0 + unit * 32) >> 1), codes);
       sm.row_sc[pp][scale_tile_offset(r, unit)] = (uint8_t)e;
     }
     __syncthreads();
@@ -260,8 +262,10 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       issue_load(it + kMxStages, s);
     }
     if (tid < 128) {
-      uint8_t* dst = a.row_sc + ((size_t)cm * a.chunks_k + ck) * 512;
-      st_cs_u32(dst + tid * 4, *reinterpret_cast<const uint32_t*>(&sm.row_sc[pp][tid * 4]));
+      if (a.row_fp4 != nullptr) {
+        uint8_t* dst = a.row_sc + ((size_t)cm * a.chunks_k + ck) * 512;
+        st_cs_u32(dst + tid * 4, *reinterpret_cast<const uint32_t*>(&sm.row_sc[pp][tid * 4]));
+      }
     } else if (want_col) {
       uint8_t* dst = a.col_sc + ((size_t)ck * a.chunks_m + cm) * 512;
       const int t = tid - 128;
@@ -939,7 +943,9 @@ extern "C" {
 int fp4b200_mxfp4_quantize(const void* x_bf16, int64_t M, int64_t K, int mode, void* row_fp4, void* row_sc,
                            void* col_fp4, void* col_sc, void* stream) {
   if (int rc = check_mx(x_bf16, M, K, mode, "mxfp4_quantize")) return rc;
-  if (!row_fp4 || !row_sc) return set_error("mxfp4_quantize: row_fp4 and row_sc are required");
+  if ((row_fp4 == nullptr) != (row_sc == nullptr))
+    return set_error("mxfp4_quantize: row_fp4 and row_sc must both be given or both be null");
+  if (!row_fp4 && !col_fp4) return set_error("mxfp4_quantize: no output was given");
   if ((col_fp4 == nullptr) != (col_sc == nullptr))
     return set_error("mxfp4_quantize: col_fp4 and col_sc must both be given or both be null");
   return launch_mx(x_bf16, M, K, mode, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream);

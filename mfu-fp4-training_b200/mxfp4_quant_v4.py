@@ -253,6 +253,18 @@ def mxfp4_fused_silu_deriv_quantize_split2_row_and_col(dh, h3, h1_raw, mode=0):
     return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
 
 
+def mxfp4_quantize_col_only(input, mode=0):
+    """tk_quantize.cu:2404-2470 — the column-wise operand alone (the wgrad's view of a tensor whose row-wise operand
+    nobody reads): (col_fp4 [K, M/2], col_sc [K/128, M/128, 32, 16])."""
+    M, K = _check_bf16_2d(input, "input")
+    u8 = dict(dtype=torch.uint8, device=input.device)
+    col_fp4, col_sc = torch.empty((K, M // 2), **u8), torch.empty((K // 128, M // 128, 32, 16), **u8)
+    with torch.cuda.device(input.device):
+        _lib.call("fp4b200_mxfp4_quantize", input.data_ptr(), M, K, int(mode), None, None, col_fp4.data_ptr(),
+                  col_sc.data_ptr(), _stream(input))
+    return col_fp4.view(_FP4), col_sc
+
+
 def mxfp4_quantize_nhsd_wo_row_and_col(input, mode=0):
     """tk_quantize.cu:2739-2830 — the attention output ``input`` [B, H, S, D] quantised as the [B*S, H*D] matrix the
     output projection consumes, without the transposing copy; returns (row_fp4 [M, K/2], row_sc [M/128, K/128, 32, 16],

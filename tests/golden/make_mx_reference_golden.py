@@ -57,6 +57,7 @@ CASES = [
     ("split3_m0", "mxfp4_quantize_split3_row_and_col", "g3", (0,)),
     ("nhsd_d64_m1", "mxfp4_quantize_nhsd_wo_row_and_col", "nhsd64", (1,)),
     ("nhsd_d128_m1", "mxfp4_quantize_nhsd_wo_row_and_col", "nhsd128", (1,)),
+    ("col_only_m1", "mxfp4_quantize_col_only", "x", (1,)),
 ]
 
 
