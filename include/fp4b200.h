@@ -359,6 +359,15 @@ int fp4b200_mxfp4_quantize_nhsd_wo(const void* x_bf16, int64_t B, int64_t H, int
 int fp4b200_mxfp4_quantize_split(const void* const* xs, const int64_t* widths, int n, int64_t M, int mode, void* row_fp4,
                                  void* row_sc, void* col_fp4, void* col_sc, void* stream);
 
+/* mxfp4_quantize_split3_row_and_col_inverse_rope_live64(input0, input1, input2, rope_cs, rope_seq_len, mode)
+ * (mxfp4_v4/tk_quantize.cu:6551-6644; kernel mxfp4_v3_quantize.cuh:6165, rotation :251-285): the three-input split
+ * quantiser with the inverse rotary embedding of dQ and dK folded into the load (heads of 64, neighbouring columns
+ * (2i, 2i+1) of token row r rotated back by rope_cs[r mod rope_seq_len, i mod 32] = (cos, sin), rounded to bf16, then
+ * quantised); dV is quantised as it is.  rope_cs fp32 [rope_seq_len, 32, 2], rope_seq_len a power of two. */
+int fp4b200_mxfp4_quantize_split3_inverse_rope(const void* dq, const void* dk, const void* dv, int64_t M, int64_t kq,
+                                               int64_t kk, int64_t kv, const float* rope_cs, int64_t rope_seq_len, int mode,
+                                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream);
+
 /* mxfp4_fused_silu_mul_quantize_row_and_col_strided(h13, H, h3_offset, mode) (mxfp4_v4/tk_quantize.cu:4105-4132): the
  * SwiGLU producer reading h1 and h3 out of one packed gate|up activation h13 [M, h13_stride] (h1 in columns [0, H), h3
  * in [h3_offset, h3_offset + H)); outputs as fp4b200_mxfp4_silu_mul_quantize. */

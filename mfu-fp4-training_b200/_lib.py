@@ -62,6 +62,8 @@ SIGNATURES = {
                                        _c_void_p],
     "fp4b200_mxfp4_quantize_split": [ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _int, _i64, _int, _c_void_p, _c_void_p,
                                      _c_void_p, _c_void_p, _c_void_p],
+    "fp4b200_mxfp4_quantize_split3_inverse_rope": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _i64, _i64, _c_void_p, _i64,
+                                                   _int, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p],
     "fp4b200_mxfp4_silu_mul_quantize_strided": [_c_void_p, _i64, _i64, _i64, _i64, _int, _c_void_p, _c_void_p, _c_void_p,
                                                 _c_void_p, _c_void_p],
     "fp4b200_mxfp4_silu_deriv_quantize_split2": [_c_void_p, _c_void_p, _c_void_p, _i64, _i64, _int, _c_void_p, _c_void_p,

@@ -49,6 +49,8 @@ struct MxArgs {
   // > 0: the input is [B, heads, seq, dim] (dim a multiple of 64, seq of 128) and the matrix [B*seq, heads*dim] with
   // element (b*seq + s, h*dim + d) = input[b, h, s, d]; tmap_x then describes [B*heads*seq, dim]
   int nhsd_heads, nhsd_seq, nhsd_dim;
+  const float2* rope_cs;       // ROPE: [seq_len, 32] (cos, sin) per token position and column pair of a 64-wide head
+  int rope_seq_mask;
 };
 
 __device__ __forceinline__ uint32_t mx_e8m0(float b, int mode) {
@@ -80,7 +82,9 @@ __device__ __forceinline__ uint32_t mx_weight_tile_e8m0(float tile_amax) {
   return (safe > 0 && phase < 0.87f) ? safe - 1 : safe;
 }
 
-template <bool NORM, bool W2D>
+// ROPE: the inverse rotary embedding (heads of 64, neighbouring columns paired) of the first two split inputs on the
+// way in: the row pass rotates the tile in place, as it normalises it with NORM.
+template <bool NORM, bool W2D, bool ROPE = false>
 __global__ void __launch_bounds__(kMxThreads, 2)
 mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_constant__ CUtensorMap tmap_x1,
                       const __grid_constant__ CUtensorMap tmap_x2, const MxArgs a) {
@@ -183,7 +187,8 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
       __syncthreads();
     }
     // the row pass also normalises the tile in place for the column pass (NORM); without row outputs it is skipped otherwise
-    const bool row_pass = NORM || a.row_fp4 != nullptr;
+    const bool rope_here = ROPE && ck < a.split_chunk[1];
+    const bool row_pass = NORM || rope_here || a.row_fp4 != nullptr;
 #pragma unroll
     for (int rep = 0; rep < 2 && row_pass; ++rep) {
       const int r = warp * 16 + rep * 8 + r_lo;
@@ -208,6 +213,26 @@ mxfp4_quantize_kernel(const __grid_constant__ CUtensorMap tmap_x, const __grid_c
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             *reinterpret_cast<uint4*>(rowp + row_off[j]) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+        }
+      }
+      if constexpr (ROPE) {
+        if (rope_here) {
+          // even' = x cos + y sin, odd' = y cos - x sin, each as one product and one fused multiply-add, rounded to bf16
+          // (reference apply_inverse_rope_tile_inplace_live64, mxfp4_v3_quantize.cuh:251-285)
+          const float4* cs4 = reinterpret_cast<const float4*>(a.rope_cs + (size_t)((m0 + r) & a.rope_seq_mask) * 32 + (unit & 1) * 16);
+#pragma unroll
+          for (int q = 0; q < 8; ++q) {
+            const float4 cs = __ldg(cs4 + q);
+            const float x0 = bf16lo_to_f32(w[2 * q]), y0 = bf16hi_to_f32(w[2 * q]);
+            const float x1 = bf16lo_to_f32(w[2 * q + 1]), y1 = bf16hi_to_f32(w[2 * q + 1]);
+            w[2 * q] = f32x2_to_bf16x2(__fmaf_rn(y0, cs.y, __fmul_rn(x0, cs.x)), __fmaf_rn(-x0, cs.y, __fmul_rn(y0, cs.x)));
+            w[2 * q + 1] = f32x2_to_bf16x2(__fmaf_rn(y1, cs.w, __fmul_rn(x1, cs.z)), __fmaf_rn(-x1, cs.w, __fmul_rn(y1, cs.z)));
+          }
+          if (want_col) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j)
+              *reinterpret_cast<uint4*>(rowp + row_off[j]) = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+          }
         }
       }
       uint32_t mx = 0;
@@ -839,7 +864,8 @@ static int launch_mx_row_sr(const MxSrArgs& a, cudaStream_t st) {
 static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float* inv_rms, const void* gamma,
                      void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, cudaStream_t st, bool weight_2d = false,
                      const void* x1 = nullptr, int64_t k1 = 0, const void* x2 = nullptr, int64_t k2 = 0,
-                     int nhsd_heads = 0, int nhsd_seq = 0, int nhsd_dim = 0) {
+                     int nhsd_heads = 0, int nhsd_seq = 0, int nhsd_dim = 0, const float* rope_cs = nullptr,
+                     int64_t rope_seq_len = 0) {
   const int64_t k0 = K - k1 - k2;
   CUtensorMap tmap, tmap1, tmap2;
   if (int rc = nhsd_seq > 0
@@ -866,10 +892,14 @@ static int launch_mx(const void* x, int64_t M, int64_t K, int mode, const float*
   a.split_chunk[0] = (int)(k0 / kMxChunk);
   a.split_chunk[1] = (int)((k0 + k1) / kMxChunk);
   a.nhsd_heads = nhsd_heads; a.nhsd_seq = nhsd_seq; a.nhsd_dim = nhsd_dim;
+  a.rope_cs = reinterpret_cast<const float2*>(rope_cs); a.rope_seq_mask = (int)(rope_seq_len - 1);
   const int smem = (int)sizeof(MxSmem) + 1024;
   const int grid = std::min(a.chunks_m * a.chunks_k, 2 * device_sm_count());
   if (grid == 0) return 0;
-  if (weight_2d) {
+  if (rope_cs != nullptr) {
+    FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false, false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    mxfp4_quantize_kernel<false, false, true><<<grid, kMxThreads, smem, st>>>(tmap, tmap1, tmap2, a);
+  } else if (weight_2d) {
     FP4_CUDA_CHECK(cudaFuncSetAttribute(mxfp4_quantize_kernel<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     mxfp4_quantize_kernel<false, true><<<grid, kMxThreads, smem, st>>>(tmap, tmap1, tmap2, a);
   } else if (inv_rms) {
@@ -1003,6 +1033,21 @@ int fp4b200_mxfp4_quantize_split(const void* const* xs, const int64_t* widths, i
   if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("%s: all four outputs are required", fn);
   return launch_mx(xs[0], M, K, mode, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, false,
                    xs[1], widths[1], n == 3 ? xs[2] : nullptr, n == 3 ? widths[2] : 0);
+}
+
+int fp4b200_mxfp4_quantize_split3_inverse_rope(const void* dq, const void* dk, const void* dv, int64_t M, int64_t kq,
+                                               int64_t kk, int64_t kv, const float* rope_cs, int64_t rope_seq_len, int mode,
+                                               void* row_fp4, void* row_sc, void* col_fp4, void* col_sc, void* stream) {
+  const char* fn = "mxfp4_quantize_split3_inverse_rope";
+  if (int rc = check_mx(dq, M, kq, mode, fn)) return rc;
+  if (int rc = check_mx(dk, M, kk, mode, fn)) return rc;
+  if (int rc = check_mx(dv, M, kv, mode, fn)) return rc;
+  if (!rope_cs || (reinterpret_cast<uintptr_t>(rope_cs) & 15)) return set_error("%s: rope_cs must be a 16-byte aligned table", fn);
+  if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)))
+    return set_error("%s: rope_seq_len must be a positive power of two (got %lld)", fn, (long long)rope_seq_len);
+  if (!row_fp4 || !row_sc || !col_fp4 || !col_sc) return set_error("%s: all four outputs are required", fn);
+  return launch_mx(dq, M, kq + kk + kv, mode, nullptr, nullptr, row_fp4, row_sc, col_fp4, col_sc, (cudaStream_t)stream, false,
+                   dk, kk, dv, kv, 0, 0, 0, rope_cs, rope_seq_len);
 }
 
 int fp4b200_mxfp4_silu_mul_quantize_strided(const void* h13, int64_t h13_stride, int64_t h3_offset, int64_t M, int64_t H,

@@ -339,6 +339,37 @@ def mxfp4_quantize_split3_row_and_col_launch_inplace(input0, input1, input2, row
     _quantize_split((input0, input1, input2), (row_fp4, row_sc, col_fp4, col_sc), mode)
 
 
+def mxfp4_quantize_split3_row_and_col_inverse_rope_live64(input0, input1, input2, rope_cs, rope_seq_len, mode=0):
+    """tk_quantize.cu:6551-6644 — ``mxfp4_quantize_split3_row_and_col`` with the inverse rotary embedding of the first two
+    inputs (dQ, dK; heads of 64, neighbouring columns paired) folded into the load; ``rope_cs`` fp32
+    [rope_seq_len, 32, 2], ``rope_seq_len`` a power of two."""
+    inputs = (input0, input1, input2)
+    M = None
+    for t in inputs:
+        if (not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous() or t.dtype != torch.bfloat16
+                or t.dim() != 2 or t.shape[0] % 128 or t.shape[1] % 128):
+            raise RuntimeError("split inputs must be contiguous bf16 matrices with dims divisible by 128")
+        if M is not None and int(t.shape[0]) != M:
+            raise RuntimeError("split inputs must have the same M dimension")
+        M = int(t.shape[0])
+    seq = int(rope_seq_len)
+    if seq <= 0 or seq & (seq - 1):
+        raise RuntimeError("rope_seq_len must be a positive power of two")
+    if (not isinstance(rope_cs, torch.Tensor) or not rope_cs.is_cuda or not rope_cs.is_contiguous()
+            or rope_cs.dtype != torch.float32 or tuple(rope_cs.shape) != (seq, 32, 2)):
+        raise RuntimeError("rope_cs must have shape (rope_seq_len, 32, 2)")
+    ks = [int(t.shape[1]) for t in inputs]
+    K = sum(ks)
+    u8 = dict(dtype=torch.uint8, device=input0.device)
+    row_fp4, row_sc = torch.empty((M, K // 2), **u8), torch.empty((M // 128, K // 128, 32, 16), **u8)
+    col_fp4, col_sc = torch.empty((K, M // 2), **u8), torch.empty((K // 128, M // 128, 32, 16), **u8)
+    with torch.cuda.device(input0.device):
+        _lib.call("fp4b200_mxfp4_quantize_split3_inverse_rope", input0.data_ptr(), input1.data_ptr(), input2.data_ptr(), M,
+                  ks[0], ks[1], ks[2], rope_cs.data_ptr(), seq, int(mode), row_fp4.data_ptr(), row_sc.data_ptr(),
+                  col_fp4.data_ptr(), col_sc.data_ptr(), _stream(input0))
+    return row_fp4.view(_FP4), row_sc, col_fp4.view(_FP4), col_sc
+
+
 def mxfp4_fused_silu_mul_quantize_row_and_col_strided(h13, H, h3_offset, mode=0):
     """tk_quantize.cu:4105-4132 — ``bf16(silu(h1) * h3)`` quantised row- and column-wise, h1 and h3 read out of the
     packed gate|up activation ``h13`` [M, stride] (h1 in columns [0, H), h3 in [h3_offset, h3_offset + H)); returns

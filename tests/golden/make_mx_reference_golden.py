@@ -131,6 +131,14 @@ def split3_inputs():
     return tuple(o.bf16_round((1e-3 * rng.standard_normal((Mo, w))).astype(np.float32)) for w in (512, 256, 256))
 
 
+def inverse_rope_inputs():
+    """dQ [256, 256], dK [256, 128], dV [256, 128] and a (cos, sin) table [128, 32, 2]; the tests call this too."""
+    rng = np.random.default_rng(770)
+    gs = tuple(o.bf16_round(rng.standard_normal((256, w)).astype(np.float32)) for w in (256, 128, 128))
+    ang = rng.uniform(-np.pi, np.pi, size=(128, 32)).astype(np.float32)
+    return gs, np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
 def load_reference_gemm_module():
     paths = glob.glob(os.path.join(ROOT, "oracle", "_ref", "_C_mx*.so"))
     if not paths:
@@ -218,6 +226,13 @@ def main():
                                                          [x[1] for x in ws], d, -1)
         torch.cuda.synchronize()
         out["onepass_split3.d"] = d.view(torch.int16).cpu().numpy()
+    # split3 with the inverse rotary embedding of the first two inputs folded in (sequence of 128 tokens, two per batch)
+    gs, cs = inverse_rope_inputs()
+    r = ref.mxfp4_quantize_split3_row_and_col_inverse_rope_live64(
+        *(torch.from_numpy(t).to(torch.bfloat16).to(dev) for t in gs), torch.from_numpy(cs).to(dev), cs.shape[0], 1)
+    torch.cuda.synchronize()
+    for j, t in enumerate(r):
+        out[f"split3_inverse_rope.{j}"] = (t.view(torch.uint8) if t.dtype != torch.uint8 else t).cpu().numpy()
     dst = os.environ.get("MX_GOLDEN_OUT", os.path.join(HERE, "mxfp4_reference_kernels_golden.npz"))
     np.savez_compressed(dst, **out)
     print(f"wrote {dst}: {len(out)} arrays, {os.path.getsize(dst)} bytes")

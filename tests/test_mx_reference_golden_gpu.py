@@ -184,3 +184,25 @@ def test_nhsd_attention_output_quantiser_equals_the_quantiser_of_the_transposed_
     with pytest.raises(RuntimeError):
         mxq.mxfp4_quantize_nhsd_wo_row_and_col(torch.zeros(1, 4, 128, 32, dtype=torch.bfloat16, device="cuda"), 1)
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "split3_inverse_rope.0" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+def test_split3_quantiser_with_the_inverse_rotation_folded_in_reproduces_the_reference_kernels_bytes():
+    """dQ and dK rotated back on the way into the quantiser (heads of 64), dV as it is: the reference kernel's bytes, and
+    the same bytes as the separate inverse-rotation kernel followed by the split quantiser."""
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c")
+    gs, cs = G.inverse_rope_inputs()
+    dev = [to_dev_bf16(t) for t in gs]
+    cs_dev = torch.from_numpy(cs).cuda()
+    r = mxq.mxfp4_quantize_split3_row_and_col_inverse_rope_live64(*dev, cs_dev, cs.shape[0], 1)
+    torch.cuda.synchronize()
+    for j, t in enumerate(r):
+        bad = int((t.view(torch.uint8).cpu().numpy().reshape(-1) != GOLD[f"split3_inverse_rope.{j}"].reshape(-1)).sum())
+        assert bad == 0, f"output {j}: {bad} bytes differ from the reference kernel's"
+    q_rot, k_rot = torch.empty_like(dev[0]), torch.empty_like(dev[1])
+    gemm.nvfp4_inverse_rope_packed_qk(dev[0], dev[1], cs_dev, cs.shape[0], 64, q_rot, k_rot)
+    for a, b in zip(r, mxq.mxfp4_quantize_split3_row_and_col(q_rot, k_rot, dev[2], 1)):
+        assert torch.equal(a.view(torch.uint8), b.view(torch.uint8))
+    with pytest.raises(RuntimeError):
+        mxq.mxfp4_quantize_split3_row_and_col_inverse_rope_live64(*dev, cs_dev[:, :16].contiguous(), cs.shape[0], 1)
+    assert_status_ok()
