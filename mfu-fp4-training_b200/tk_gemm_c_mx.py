@@ -35,6 +35,12 @@ def mxfp4_gemm_residual(A, A_sc, B, B_sc, R, D):
     _gemm(A, A_sc, B, B_sc, D, residual=R)
 
 
+def mxfp4_gemm_residual_config(A, A_sc, B, B_sc, R, D, config_id):
+    """mxfp4_gb200_gemm.cu:2742-2747 — the residual form with the reference's tile-configuration index, which is
+    accepted and ignored (one tile configuration here)."""
+    _gemm(A, A_sc, B, B_sc, D, residual=R)
+
+
 def mxfp4_batched_gemm(A_list, A_sc_list, B_list, B_sc_list, D_out_list):
     for A, A_sc, B, B_sc, D in zip(A_list, A_sc_list, B_list, B_sc_list, D_out_list, strict=True):
         _gemm(A, A_sc, B, B_sc, D)
