@@ -317,6 +317,14 @@ int fp4b200_nvfp4_grouped_gemm(const void* A, const void* A_sc, const float* A_s
 int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, int out_fp32,
                        const void* residual_bf16, int64_t M, int64_t N, int64_t K, void* stream);
 
+/* mxfp4_gemm_rope_live64[_config] / mxfp4_gemm_rope_live[_config](A, A_sc, B, B_sc, D, rope_cs, rope_seq_len)
+ * (mxfp4_gb200/mxfp4_gb200_gemm.cu:1777-1812; epilogue mxfp4_rope_epilogue.cuh:263-308): D = bf16(rotate((A.B^T) / 36)),
+ * every neighbouring column pair (2i, 2i+1) of token row r rotated by rope_cs[r mod rope_seq_len, i mod
+ * (rope_head_dim / 2)] = (cos, sin) in fp32 before the one rounding.  rope_cs fp32 [rope_seq_len, rope_head_dim/2, 2];
+ * rope_seq_len and rope_head_dim powers of two.  Runs on the one-CTA GEMM kernel. */
+int fp4b200_mxfp4_gemm_rope(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, const float* rope_cs,
+                            int64_t rope_seq_len, int64_t rope_head_dim, int64_t M, int64_t N, int64_t K, void* stream);
+
 /* mxfp4_split2_dgrad_strided_onepass_gemm(A_full, A_sc_list, A_col_offsets, A_col_widths, B_list, B_sc_list,
  * D_out, config_idx) (mxfp4_gb200/mxfp4_gb200_gemm.cu:2572-2596; kernel mxfp4_split2_accum_gemm.cuh):
  * D = bf16((sum_s A_full[:, off_s : off_s + w_s] * B_s^T) / 36) with all terms accumulated in tensor memory

@@ -93,6 +93,8 @@ SIGNATURES = {
                                    ctypes.POINTER(_c_void_p), ctypes.POINTER(_i64), _i64, _i64, _i64, _c_void_p],
     "fp4b200_mxfp4_gemm": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _int, _c_void_p, _i64, _i64,
                            _i64, _c_void_p],
+    "fp4b200_mxfp4_gemm_rope": [_c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _c_void_p, _i64, _i64, _i64, _i64, _i64,
+                                _c_void_p],
     "fp4b200_mxfp4_gemm_ksplit": [_c_void_p, _i64, _int, ctypes.POINTER(_i64), ctypes.POINTER(_i64),
                                   ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p), ctypes.POINTER(_c_void_p),
                                   _c_void_p, _int, _i64, _i64, _c_void_p],

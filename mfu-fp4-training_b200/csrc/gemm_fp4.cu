@@ -886,7 +886,9 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
                             int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld, int n_out,
                             int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N, cudaStream_t st,
                             const float* accum_f32 = nullptr, const RopeDesc* rope = nullptr) {
-  const bool pair = (M % 256) == 0 && !gemm_pair_disabled();
+  // MXFP4 with a rotary epilogue runs on the one-CTA kernel: the two-CTA kernel's rotary form keeps its table rows in
+  // tensor-memory columns that the MXFP4 scale slots use
+  const bool pair = (M % 256) == 0 && !gemm_pair_disabled() && !(mx && rope != nullptr);
   CUtensorMap tmap_a;
   GemmBMaps tmap_b, tmap_a_seg;
   memset(&tmap_b, 0, sizeof(tmap_b));
@@ -1004,7 +1006,9 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg1, fp4_gemm_kernel<MXF, EPI>, tmap_a, tmap_b, omaps, g));                   \
   } while (0)
   if (mx) {
-    if (epi == kEpiGeneral) FP4_LAUNCH_ONE(true, kEpiGeneral); else FP4_LAUNCH_ONE(true, kEpiPlain);
+    if (epi == kEpiGeneral) FP4_LAUNCH_ONE(true, kEpiGeneral);
+    else if (epi == kEpiRope) FP4_LAUNCH_ONE(true, kEpiRope);
+    else FP4_LAUNCH_ONE(true, kEpiPlain);
   } else if (epi == kEpiGeneral) FP4_LAUNCH_ONE(false, kEpiGeneral);
   else if (epi == kEpiSilu) FP4_LAUNCH_ONE(false, kEpiSilu);
   else if (epi == kEpiRope) FP4_LAUNCH_ONE(false, kEpiRope);
@@ -1191,6 +1195,24 @@ int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const voi
   int ce[1] = {(int)N}, ld[1] = {(int)N};
   return launch_gemm(true, A, A_sc, nullptr, B, B_sc, nullptr, 0, d, ce, ld, 1, out_fp32, residual_bf16, (int)N, M, N,
                      K, (cudaStream_t)stream);
+}
+
+int fp4b200_mxfp4_gemm_rope(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, const float* rope_cs,
+                            int64_t rope_seq_len, int64_t rope_head_dim, int64_t M, int64_t N, int64_t K, void* stream) {
+  const char* fn = "mxfp4_gemm_rope";
+  if (int rc = check_gemm(A, A_sc, B, B_sc, M, N, K, fn, 128)) return rc;
+  if (!D || !rope_cs) return set_error("%s: D and rope_cs are required", fn);
+  if (rope_seq_len <= 0 || (rope_seq_len & (rope_seq_len - 1)) || (M % rope_seq_len))
+    return set_error("%s: rope_seq_len must be a power of two that divides M (got %lld)", fn, (long long)rope_seq_len);
+  if (rope_head_dim < 16 || (rope_head_dim & (rope_head_dim - 1)) || rope_head_dim > 256 || (N % rope_head_dim))
+    return set_error("%s: rope_head_dim must be a power of two between 16 and 256 that divides N (got %lld)", fn,
+                     (long long)rope_head_dim);
+  if (reinterpret_cast<uintptr_t>(rope_cs) & 15) return set_error("%s: rope_cs must be 16-byte aligned", fn);
+  void* d[1] = {D};
+  int ce[1] = {(int)N}, ld[1] = {(int)N};
+  RopeDesc rope{reinterpret_cast<const float2*>(rope_cs), (int)rope_seq_len, (int)rope_head_dim, (int)N, false, 0};
+  return launch_gemm(true, A, A_sc, nullptr, B, B_sc, nullptr, 0, d, ce, ld, 1, 0, nullptr, 0, M, N, K, (cudaStream_t)stream,
+                     nullptr, &rope);
 }
 
 int fp4b200_mxfp4_gemm_ksplit_strided(const void* A_full, int64_t a_width, int n_seg, const int64_t* a_col_offsets,

@@ -35,6 +35,39 @@ def mxfp4_gemm_residual(A, A_sc, B, B_sc, R, D):
     _gemm(A, A_sc, B, B_sc, D, residual=R)
 
 
+def mxfp4_gemm_rope_live64(A, A_sc, B, B_sc, D, rope_cs, rope_seq_len):
+    """mxfp4_gb200_gemm.cu:1777-1787 — ``D = bf16(rope((A . B^T) / 36))``: every neighbouring column pair of the output
+    rotated in fp32 before the one rounding; ``rope_cs`` fp32 [rope_seq_len, head_dim/2, 2], the head size (a power
+    of two) read off its shape."""
+    for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
+        _chk_operand(t, n)
+    M, N, K = _shapes(A, B)
+    _chk_out(D, M, N)
+    seq = int(rope_seq_len)
+    if seq <= 0 or seq & (seq - 1):
+        raise RuntimeError("rope_seq_len must be a power of two")
+    if M % seq:
+        raise RuntimeError("output rows must be divisible by rope_seq_len")
+    if (not isinstance(rope_cs, torch.Tensor) or not rope_cs.is_cuda or not rope_cs.is_contiguous()
+            or rope_cs.dtype != torch.float32 or rope_cs.dim() != 3 or rope_cs.shape[0] != seq or rope_cs.shape[2] != 2):
+        raise RuntimeError("rope_cs must be contiguous CUDA float32 [rope_seq_len, head_dim/2, 2]")
+    head = 2 * int(rope_cs.shape[1])
+    if head & (head - 1) or N % head:
+        raise RuntimeError("output cols must be divisible by the RoPE head dimension")
+    with torch.cuda.device(A.device):
+        _lib.call("fp4b200_mxfp4_gemm_rope", A.data_ptr(), A_sc.data_ptr(), B.data_ptr(), B_sc.data_ptr(), D.data_ptr(),
+                  rope_cs.data_ptr(), seq, head, M, N, K, _stream(A))
+
+
+def mxfp4_gemm_rope_live64_config(A, A_sc, B, B_sc, D, rope_cs, rope_seq_len, config_id):
+    """mxfp4_gb200_gemm.cu:1789-1812 — the same; the tile-configuration index is accepted and ignored."""
+    mxfp4_gemm_rope_live64(A, A_sc, B, B_sc, D, rope_cs, rope_seq_len)
+
+
+mxfp4_gemm_rope_live = mxfp4_gemm_rope_live64                  # mxfp4_gb200_gemm.cu:2824: the same entry point
+mxfp4_gemm_rope_live_config = mxfp4_gemm_rope_live64_config    # :2831
+
+
 def mxfp4_gemm_residual_config(A, A_sc, B, B_sc, R, D, config_id):
     """mxfp4_gb200_gemm.cu:2742-2747 — the residual form with the reference's tile-configuration index, which is
     accepted and ignored (one tile configuration here)."""

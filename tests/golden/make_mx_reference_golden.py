@@ -131,6 +131,12 @@ def split3_inputs():
     return tuple(o.bf16_round((1e-3 * rng.standard_normal((Mo, w))).astype(np.float32)) for w in (512, 256, 256))
 
 
+def rope_table(seq_len, pair_dim):
+    """(cos, sin) fp32 [seq_len, pair_dim, 2] of seeded angles; the tests call this too."""
+    ang = np.random.default_rng(790 + pair_dim).uniform(-np.pi, np.pi, size=(seq_len, pair_dim)).astype(np.float32)
+    return np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
 def inverse_rope_inputs():
     """dQ [256, 256], dK [256, 128], dV [256, 128] and a (cos, sin) table [128, 32, 2]; the tests call this too."""
     rng = np.random.default_rng(770)
@@ -226,6 +232,16 @@ def main():
                                                          [x[1] for x in ws], d, -1)
         torch.cuda.synchronize()
         out["onepass_split3.d"] = d.view(torch.int16).cpu().numpy()
+    if ref_gemm is not None:
+        # GEMM with the rotary epilogue: heads of 64 (the 128-token table of the inverse-rotation case) and of 128
+        for tag, shape, pair_dim in (("rope64", GEMM_SHAPES[0], 32), ("rope128", GEMM_SHAPES[1], 64)):
+            a, b = (torch.from_numpy(t).to(torch.bfloat16).to(dev) for t in gemm_operands(shape, 780))
+            qa, qb = ref.mxfp4_quantize_for_gemm(a, 1), ref.mxfp4_quantize_for_gemm(b, 1)
+            cs = torch.from_numpy(rope_table(128, pair_dim)).to(dev)
+            d = torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device=dev)
+            ref_gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 128)
+            torch.cuda.synchronize()
+            out[f"gemm_{tag}.d"] = d.view(torch.int16).cpu().numpy()
     # split3 with the inverse rotary embedding of the first two inputs folded in (sequence of 128 tokens, two per batch)
     gs, cs = inverse_rope_inputs()
     r = ref.mxfp4_quantize_split3_row_and_col_inverse_rope_live64(

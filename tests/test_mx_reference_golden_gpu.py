@@ -206,3 +206,23 @@ def test_split3_quantiser_with_the_inverse_rotation_folded_in_reproduces_the_ref
     with pytest.raises(RuntimeError):
         mxq.mxfp4_quantize_split3_row_and_col_inverse_rope_live64(*dev, cs_dev[:, :16].contiguous(), cs.shape[0], 1)
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "gemm_rope64.d" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+@pytest.mark.parametrize("tag,idx,pair_dim", [("rope64", 0, 32), ("rope128", 1, 64)])
+def test_mxfp4_gemm_with_rotary_epilogue_reproduces_the_reference_kernels_bytes(tag, idx, pair_dim):
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    shape = G.GEMM_SHAPES[idx]
+    a, b = (to_dev_bf16(t) for t in G.gemm_operands(shape, 780))
+    qa, qb = mxq.mxfp4_quantize_for_gemm(a, 1), mxq.mxfp4_quantize_for_gemm(b, 1)
+    cs = torch.from_numpy(G.rope_table(128, pair_dim)).cuda()
+    d = torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device="cuda")
+    gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 128)
+    torch.cuda.synchronize()
+    assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD[f"gemm_{tag}.d"])
+    d2 = torch.empty_like(d)
+    gemm.mxfp4_gemm_rope_live_config(qa[0], qa[1], qb[0], qb[1], d2, cs, 128, 3)
+    assert torch.equal(d2, d)
+    with pytest.raises(RuntimeError):
+        gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 96)
+    assert_status_ok()
