@@ -68,6 +68,28 @@ mxfp4_gemm_rope_live = mxfp4_gemm_rope_live64                  # mxfp4_gb200_gem
 mxfp4_gemm_rope_live_config = mxfp4_gemm_rope_live64_config    # :2831
 
 
+def mxfp4_batched_gemm_rope_live64(A_list, A_sc_list, B_list, B_sc_list, D_out_list, rope_cs_list, rope_seq_len_list):
+    """mxfp4_gb200_gemm.cu:2958-2964 — independent GEMMs ``D_i = A_i . B_i^T``, each with the rotary epilogue of its own
+    table, or plain where its table is empty (the fused QKV projection: Q and K rotated, V not;
+    mxfp4_backend.py:3153-3175).  One launch per entry here."""
+    for A, A_sc, B, B_sc, D, cs, seq in zip(A_list, A_sc_list, B_list, B_sc_list, D_out_list, rope_cs_list,
+                                            rope_seq_len_list, strict=True):
+        if cs is None or cs.numel() == 0:
+            _gemm(A, A_sc, B, B_sc, D)
+        else:
+            mxfp4_gemm_rope_live64(A, A_sc, B, B_sc, D, cs, seq)
+
+
+def mxfp4_batched_gemm_rope_live64_config(A_list, A_sc_list, B_list, B_sc_list, D_out_list, rope_cs_list, rope_seq_len_list,
+                                          config_id):
+    """mxfp4_gb200_gemm.cu:2965-2972 — the same; the tile-configuration index is accepted and ignored."""
+    mxfp4_batched_gemm_rope_live64(A_list, A_sc_list, B_list, B_sc_list, D_out_list, rope_cs_list, rope_seq_len_list)
+
+
+mxfp4_batched_gemm_rope_live = mxfp4_batched_gemm_rope_live64                  # mxfp4_gb200_gemm.cu:2973
+mxfp4_batched_gemm_rope_live_config = mxfp4_batched_gemm_rope_live64_config    # :2980
+
+
 def mxfp4_gemm_residual_config(A, A_sc, B, B_sc, R, D, config_id):
     """mxfp4_gb200_gemm.cu:2742-2747 — the residual form with the reference's tile-configuration index, which is
     accepted and ignored (one tile configuration here)."""

@@ -242,6 +242,21 @@ def main():
             ref_gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 128)
             torch.cuda.synchronize()
             out[f"gemm_{tag}.d"] = d.view(torch.int16).cpu().numpy()
+    if ref_gemm is not None:
+        # the fused QKV projection as the reference's backend calls it (mxfp4_backend.py:3153-3175): one activation,
+        # three weights, Q and K with the rotary epilogue, V without (an empty table)
+        shape = GEMM_SHAPES[0]
+        a = torch.from_numpy(gemm_operands(shape, 781)[0]).to(torch.bfloat16).to(dev)
+        qa = ref.mxfp4_quantize_for_gemm(a, 1)
+        ws = [ref.mxfp4_quantize_for_gemm(torch.from_numpy(gemm_operands(shape, 782 + i)[1]).to(torch.bfloat16).to(dev), 1)
+              for i in range(3)]
+        cs = torch.from_numpy(rope_table(128, 32)).to(dev)
+        ds = [torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device=dev) for _ in range(3)]
+        ref_gemm.mxfp4_batched_gemm_rope_live64([qa[0]] * 3, [qa[1]] * 3, [w[0] for w in ws], [w[1] for w in ws], ds,
+                                                [cs, cs, torch.empty(0, dtype=torch.float32, device=dev)], [128, 128, 0])
+        torch.cuda.synchronize()
+        for i, d in enumerate(ds):
+            out[f"batched_rope.{i}"] = d.view(torch.int16).cpu().numpy()
     # split3 with the inverse rotary embedding of the first two inputs folded in (sequence of 128 tokens, two per batch)
     gs, cs = inverse_rope_inputs()
     r = ref.mxfp4_quantize_split3_row_and_col_inverse_rope_live64(

@@ -226,3 +226,20 @@ def test_mxfp4_gemm_with_rotary_epilogue_reproduces_the_reference_kernels_bytes(
     with pytest.raises(RuntimeError):
         gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 96)
     assert_status_ok()
+
+
+@pytest.mark.skipif(GOLD is None or "batched_rope.0" not in (GOLD.files if GOLD is not None else ()), reason="fixture not recorded")
+def test_mxfp4_batched_qkv_projection_with_rotary_epilogue_reproduces_the_reference_kernels_bytes():
+    """One activation against three weights, Q and K rotated in the epilogue, V not (its table is empty)."""
+    mxq, gemm = mod("mxfp4_quant_v4"), mod("tk_gemm_c_mx")
+    shape = G.GEMM_SHAPES[0]
+    qa = mxq.mxfp4_quantize_for_gemm(to_dev_bf16(G.gemm_operands(shape, 781)[0]), 1)
+    ws = [mxq.mxfp4_quantize_for_gemm(to_dev_bf16(G.gemm_operands(shape, 782 + i)[1]), 1) for i in range(3)]
+    cs = torch.from_numpy(G.rope_table(128, 32)).cuda()
+    ds = [torch.empty(shape[0], shape[1], dtype=torch.bfloat16, device="cuda") for _ in range(3)]
+    gemm.mxfp4_batched_gemm_rope_live64([qa[0]] * 3, [qa[1]] * 3, [w[0] for w in ws], [w[1] for w in ws], ds,
+                                        [cs, cs, torch.empty(0, dtype=torch.float32, device="cuda")], [128, 128, 0])
+    torch.cuda.synchronize()
+    for i, d in enumerate(ds):
+        assert np.array_equal(d.view(torch.int16).cpu().numpy(), GOLD[f"batched_rope.{i}"]), i
+    assert_status_ok()
