@@ -321,7 +321,8 @@ int fp4b200_mxfp4_gemm(const void* A, const void* A_sc, const void* B, const voi
  * (mxfp4_gb200/mxfp4_gb200_gemm.cu:1777-1812; epilogue mxfp4_rope_epilogue.cuh:263-308): D = bf16(rotate((A.B^T) / 36)),
  * every neighbouring column pair (2i, 2i+1) of token row r rotated by rope_cs[r mod rope_seq_len, i mod
  * (rope_head_dim / 2)] = (cos, sin) in fp32 before the one rounding.  rope_cs fp32 [rope_seq_len, rope_head_dim/2, 2];
- * rope_seq_len and rope_head_dim powers of two.  Runs on the one-CTA GEMM kernel. */
+ * rope_seq_len and rope_head_dim powers of two.  Same kernels as the NVFP4 rotary forms (two-CTA kernel with eight
+ * epilogue warps when M is a multiple of 256). */
 int fp4b200_mxfp4_gemm_rope(const void* A, const void* A_sc, const void* B, const void* B_sc, void* D, const float* rope_cs,
                             int64_t rope_seq_len, int64_t rope_head_dim, int64_t M, int64_t N, int64_t K, void* stream);
 

@@ -886,9 +886,7 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
                             int b_sg_per_tile, void* const* D, const int* d_col_end, const int* d_ld, int n_out,
                             int out_fp32, const void* residual, int residual_ld, int64_t M, int64_t N, cudaStream_t st,
                             const float* accum_f32 = nullptr, const RopeDesc* rope = nullptr) {
-  // MXFP4 with a rotary epilogue runs on the one-CTA kernel: the two-CTA kernel's rotary form keeps its table rows in
-  // tensor-memory columns that the MXFP4 scale slots use
-  const bool pair = (M % 256) == 0 && !gemm_pair_disabled() && !(mx && rope != nullptr);
+  const bool pair = (M % 256) == 0 && !gemm_pair_disabled();
   CUtensorMap tmap_a;
   GemmBMaps tmap_b, tmap_a_seg;
   memset(&tmap_b, 0, sizeof(tmap_b));
@@ -961,7 +959,8 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     const int clusters = std::min(pair_tiles, device_sm_count() / 2);
     cudaLaunchConfig_t cfg{};
     cfg.gridDim = dim3(2 * clusters, 1, 1);
-    cfg.blockDim = dim3(pair_form_is_wide(epi) && !mx ? kPairWideThreads : kPairThreads, 1, 1);
+    // the MXFP4 kernels with another epilogue form than the rotary one are instantiated as kEpiPlain / kEpiGeneral
+    cfg.blockDim = dim3(pair_form_is_wide(epi) && (!mx || epi == kEpiRope) ? kPairWideThreads : kPairThreads, 1, 1);
     cfg.dynamicSmemBytes = psmem;
     cfg.stream = st;
     cudaLaunchAttribute attr[2];
@@ -977,7 +976,9 @@ static int launch_gemm_segs(bool mx, const void* A, const KSegments& segs, const
     FP4_CUDA_CHECK(cudaLaunchKernelEx(&cfg, fp4_gemm_pair_kernel<MXF, EPI>, tmap_a, tmap_b, omaps, g, tmap_a_seg));       \
   } while (0)
     if (mx) {
-      if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(true, kEpiGeneral); else FP4_LAUNCH_PAIR(true, kEpiPlain);
+      if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(true, kEpiGeneral);
+      else if (epi == kEpiRope) FP4_LAUNCH_PAIR(true, kEpiRope);
+      else FP4_LAUNCH_PAIR(true, kEpiPlain);
     } else if (epi == kEpiGeneral) FP4_LAUNCH_PAIR(false, kEpiGeneral);
     else if (epi == kEpiBatchSum) FP4_LAUNCH_PAIR(false, kEpiBatchSum);
     else if (epi == kEpiSilu) FP4_LAUNCH_PAIR(false, kEpiSilu);
