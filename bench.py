@@ -898,8 +898,8 @@ def mx_swiglu_only(args):
 def gemm_only(args):
     """Times one GEMM form alone at one shape on cuda:0 (random codes and scales): the plain NVFP4 GEMM, the fused QKV
     projection with the rotary embedding in its epilogue (--gemm-form rope: heads of 128, sequences of 4096, the last
-    sixth of the columns not rotated), two accumulated terms in one launch (--gemm-form accum2), or the MXFP4 GEMM
-    (--gemm-form mx)."""
+    sixth of the columns not rotated), two accumulated terms in one launch (--gemm-form accum2), the MXFP4 GEMM
+    (--gemm-form mx), or the MXFP4 GEMM with the rotary epilogue on every column pair (--gemm-form mxrope)."""
     import torch
     gemm = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c")
     lib = importlib.import_module("mfu-fp4-training_b200._lib")
@@ -930,13 +930,19 @@ def gemm_only(args):
         flops *= 2
         def run():
             gemm.nvfp4_batched_accum_gemm([a, a2], [a_sc, a2_sc], [sg, sg], [b, b2], [b_sc, b2_sc], [sg, sg], d)
-    elif args.gemm_form == "mx":
+    elif args.gemm_form in ("mx", "mxrope"):
         gmx = importlib.import_module("mfu-fp4-training_b200.tk_gemm_c_mx")
         def mx_scales(rows):    # E8M0 bytes near 127: one per 32 elements, [rows/128, K/128, 32, 16]
             return torch.randint(120, 132, (rows // 128, K // 128, 32, 16), dtype=torch.uint8, device=dev, generator=g)
         a_e, b_e = mx_scales(M), mx_scales(N)
-        def run():
-            gmx.mxfp4_gemm(a, a_e, b, b_e, d)
+        if args.gemm_form == "mxrope":     # every column pair rotated, heads of 128, sequences of 4096
+            ang = torch.rand(4096, 64, device=dev, generator=g) * 6.2831853
+            cs = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+            def run():
+                gmx.mxfp4_gemm_rope_live64(a, a_e, b, b_e, d, cs, 4096)
+        else:
+            def run():
+                gmx.mxfp4_gemm(a, a_e, b, b_e, d)
     else:
         def run():
             gemm.nvfp4_gemm(a, a_sc, sg, b, b_sc, sg, d)
@@ -965,7 +971,7 @@ def main():
                     help="timed loop only (no per-kernel, end-to-end or CPU legs): the command ncu captures")
     ap.add_argument("--gemm-only", default=None, metavar="MxNxK",
                     help="time only the NVFP4 GEMM at this shape (tuning / ncu capture helper)")
-    ap.add_argument("--gemm-form", default="plain", choices=["plain", "rope", "accum2", "mx"],
+    ap.add_argument("--gemm-form", default="plain", choices=["plain", "rope", "accum2", "mx", "mxrope"],
                     help="with --gemm-only: which epilogue form to time")
     ap.add_argument("--rmsnorm-bwd-only", default=None, metavar="MxK",
                     help="time only the RMSNorm backward (sum3 form) at this shape (tuning / ncu capture helper)")
