@@ -698,7 +698,19 @@ def mxfp4_reference_producers_leg(torch, ref, ref_gemm=None):
             del d_ref
             out[name]["ours_tflops"] = fl / (out[name]["ours_ms"] * 1e-3) / 1e12
             out[name]["reference_tflops"] = fl / (out[name]["reference_ms"] * 1e-3) / 1e12
-        out["gemm_kernels"] = "reference _C_mx.mxfp4_gemm (mxfp4_gb200/mxfp4_gb200_gemm.cu), compiled from the reference's sources"
+        # the Q projection with the rotary epilogue (heads of 128, sequences of 8192): [M, 4096] = X . Wq^T, every pair rotated
+        del d_up, qh, qw2
+        qwq = mxq.mxfp4_quantize_for_gemm(rnd(K, K, 0.02), 1)
+        ang = torch.rand(8192, 64, generator=g, device=dev) * 6.2831853
+        cs = torch.stack([torch.cos(ang), torch.sin(ang)], dim=-1).contiguous()
+        name = "gemm_rope_65536x4096x4096"
+        both(name, lambda: ref_gemm.mxfp4_gemm_rope_live64(qx[0], qx[1], qwq[0], qwq[1], d_dn, cs, 8192),
+             lambda: gemm.mxfp4_gemm_rope_live64(qx[0], qx[1], qwq[0], qwq[1], d_dn, cs, 8192), 10)
+        ref_gemm.mxfp4_gemm_rope_live64(qx[0], qx[1], qwq[0], qwq[1], d_dn, cs, 8192)
+        d_ref = d_dn.clone()
+        gemm.mxfp4_gemm_rope_live64(qx[0], qx[1], qwq[0], qwq[1], d_dn, cs, 8192)
+        out[name]["outputs_bit_identical"] = bool(torch.equal(d_dn, d_ref))
+        out["gemm_kernels"] = "reference _C_mx.mxfp4_gemm / mxfp4_gemm_rope_live64 (mxfp4_gb200/mxfp4_gb200_gemm.cu), compiled from the reference's sources"
     return out
 
 
