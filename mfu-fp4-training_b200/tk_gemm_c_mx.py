@@ -59,6 +59,29 @@ def mxfp4_gemm_rope_live64(A, A_sc, B, B_sc, D, rope_cs, rope_seq_len):
                   rope_cs.data_ptr(), seq, head, M, N, K, _stream(A))
 
 
+def mxfp4_gemm_rope(A, A_sc, B, B_sc, D, rope_cos, rope_sin, rope_seq_len, rope_head_dim, rope_rotary_dim):
+    """mxfp4_gb200_gemm.cu:1814-1827 — the rotary epilogue with separate fp32 tables ``rope_cos`` / ``rope_sin``
+    [rope_seq_len, rope_rotary_dim/2].  Built for the full rotation (rotary_dim == head_dim) with power-of-two sequence
+    length and head size: the two tables are interleaved into the (cos, sin) table of ``mxfp4_gemm_rope_live64`` (one
+    small copy per call); a partial rotary dimension raises."""
+    seq, head, rot = int(rope_seq_len), int(rope_head_dim), int(rope_rotary_dim)
+    if rot != head:
+        raise RuntimeError("mxfp4_gemm_rope: a rotary dimension smaller than the head size is not built")
+    if head <= 0 or head & (head - 1) or seq <= 0 or seq & (seq - 1):
+        raise RuntimeError("mxfp4_gemm_rope: rope_seq_len and rope_head_dim must be powers of two")
+    for t, n in ((rope_cos, "rope_cos"), (rope_sin, "rope_sin")):
+        if (not isinstance(t, torch.Tensor) or not t.is_cuda or not t.is_contiguous() or t.dtype != torch.float32
+                or t.numel() != seq * (rot // 2)):
+            raise RuntimeError(f"{n} must be contiguous CUDA float32 with rope_seq_len * rope_rotary_dim / 2 elements")
+    cs = torch.stack([rope_cos.reshape(seq, rot // 2), rope_sin.reshape(seq, rot // 2)], dim=-1).contiguous()
+    mxfp4_gemm_rope_live64(A, A_sc, B, B_sc, D, cs, seq)
+
+
+def mxfp4_gemm_rope_config(A, A_sc, B, B_sc, D, rope_cos, rope_sin, rope_seq_len, rope_head_dim, rope_rotary_dim, config_id):
+    """mxfp4_gb200_gemm.cu:1829-1855 — the same; the tile-configuration index is accepted and ignored."""
+    mxfp4_gemm_rope(A, A_sc, B, B_sc, D, rope_cos, rope_sin, rope_seq_len, rope_head_dim, rope_rotary_dim)
+
+
 def mxfp4_gemm_rope_live64_config(A, A_sc, B, B_sc, D, rope_cs, rope_seq_len, config_id):
     """mxfp4_gb200_gemm.cu:1789-1812 — the same; the tile-configuration index is accepted and ignored."""
     mxfp4_gemm_rope_live64(A, A_sc, B, B_sc, D, rope_cs, rope_seq_len)

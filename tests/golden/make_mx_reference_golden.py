@@ -242,6 +242,11 @@ def main():
             ref_gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 128)
             torch.cuda.synchronize()
             out[f"gemm_{tag}.d"] = d.view(torch.int16).cpu().numpy()
+            # the same rotation from separate cos / sin tables [seq_len, rotary_dim / 2]
+            ref_gemm.mxfp4_gemm_rope(qa[0], qa[1], qb[0], qb[1], d, cs[..., 0].contiguous(), cs[..., 1].contiguous(), 128,
+                                     2 * pair_dim, 2 * pair_dim)
+            torch.cuda.synchronize()
+            out[f"gemm_{tag}.d_tables"] = d.view(torch.int16).cpu().numpy()
     if ref_gemm is not None:
         # the fused QKV projection as the reference's backend calls it (mxfp4_backend.py:3153-3175): one activation,
         # three weights, Q and K with the rotary epilogue, V without (an empty table)

@@ -223,6 +223,14 @@ def test_mxfp4_gemm_with_rotary_epilogue_reproduces_the_reference_kernels_bytes(
     d2 = torch.empty_like(d)
     gemm.mxfp4_gemm_rope_live_config(qa[0], qa[1], qb[0], qb[1], d2, cs, 128, 3)
     assert torch.equal(d2, d)
+    if f"gemm_{tag}.d_tables" in GOLD.files:      # separate cos / sin tables, full rotation
+        gemm.mxfp4_gemm_rope(qa[0], qa[1], qb[0], qb[1], d2, cs[..., 0].contiguous(), cs[..., 1].contiguous(), 128,
+                             2 * pair_dim, 2 * pair_dim)
+        torch.cuda.synchronize()
+        assert np.array_equal(d2.view(torch.int16).cpu().numpy(), GOLD[f"gemm_{tag}.d_tables"])
+        with pytest.raises(RuntimeError):
+            gemm.mxfp4_gemm_rope(qa[0], qa[1], qb[0], qb[1], d2, cs[..., 0].contiguous(), cs[..., 1].contiguous(), 128,
+                                 2 * pair_dim, pair_dim)
     with pytest.raises(RuntimeError):
         gemm.mxfp4_gemm_rope_live64(qa[0], qa[1], qb[0], qb[1], d, cs, 96)
     assert_status_ok()
