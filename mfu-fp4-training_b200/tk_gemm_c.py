@@ -138,6 +138,13 @@ def nvfp4_grouped_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_
         nvfp4_grouped_gemm(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt, D_V_opt, silu_dim)
 
 
+def nvfp4_grouped_gemm_config_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt=None, D_V_opt=None,
+                                    silu_dim=0, config_id=5):
+    """nvfp4_b200_gemm.cu:2922-2927 — the non-PDL grouped GEMM with the reference's tile-configuration index, which is
+    accepted and ignored (one tile configuration here)."""
+    nvfp4_grouped_gemm_nopdl(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, D, D_K_opt, D_V_opt, silu_dim)
+
+
 def _grouped_gemm_rope(A, A_sc, A_sc_global, B, B_sc, B_sg_per_tile, outs, rope_cs, seq_len, head_dim, rope_cols,
                        round_input_bf16, silu_dim=0):
     for t, n in ((A, "A"), (A_sc, "A_sc"), (B, "B"), (B_sc, "B_sc")):
