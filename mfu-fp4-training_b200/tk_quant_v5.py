@@ -176,6 +176,48 @@ def tk_group_quantize_dim1_split3_for_gemm(input0, input1, input2, data_stochast
             torch.zeros(6, dtype=torch.int32, device=dev), empty_i32)
 
 
+def tk_group_quantize_dim1_for_gemm(input, col_split_sections):
+    """tk_quantize.cu:6192-6416 — the column groups of ONE matrix [M, sum(sections)] (the concatenated dQ | dK | dV the
+    reference falls back to when its split3 entry point is absent, tk_gemm.py:6020-6024), each quantised with its own
+    tensor amax (encode-centric, round to nearest) into the column slices / row blocks of one pair of code matrices.
+    Returns the reference's 9-tuple: (row code views, row scales, sg [G], column code views, column scales, full row
+    codes, row scales concatenated, full column codes, column scales concatenated).  Three groups take the grouped
+    launch of the split3 quantiser; other counts one quantiser call per group."""
+    M, n_total = _check_bf16_2d(input, "input")
+    sections = [int(v) for v in col_split_sections]
+    if not sections or any(v <= 0 or v % 128 for v in sections) or sum(sections) != n_total:
+        raise RuntimeError("column sections must be positive multiples of 128 that add up to the input's width")
+    if len(sections) > 8:
+        raise RuntimeError("Max 8 groups")
+    parts, off = [], 0
+    for n in sections:
+        parts.append(input.narrow(1, off, n))
+        off += n
+    if len(sections) == 3:
+        return tk_group_quantize_dim1_split3_for_gemm(*parts)[:9]
+    dev = input.device
+    u8 = dict(dtype=torch.uint8, device=dev)
+    with torch.cuda.device(dev):
+        fp4_row_full = torch.empty((M, n_total // 2), **u8)
+        fp4_col_full = torch.empty((n_total, M // 2), **u8)
+        sc_col_cat = torch.empty((n_total // 128, M // 64, 512), **u8)
+        amax_sg = torch.empty((len(sections), 2), dtype=torch.float32, device=dev)
+        sc_row, sc_col, rows, cols, off = [], [], [], [], 0
+        for g, (t, n) in enumerate(zip(parts, sections)):
+            x = t.contiguous()                                   # the amax pass reads a dense buffer
+            sc_row.append(torch.empty((M // 128, n // 64, 512), **u8))
+            sc_col.append(sc_col_cat.narrow(0, off // 128, n // 128))
+            _lib.call("fp4b200_nvfp4_quantize_for_gemm_into", x.data_ptr(), M, n, 1, 1, fp4_row_full.data_ptr() + off // 2,
+                      n_total // 2, sc_row[g].data_ptr(), fp4_col_full.data_ptr() + off * (M // 2), sc_col[g].data_ptr(),
+                      amax_sg[g].data_ptr(), _stream(input))
+            rows.append(fp4_row_full.narrow(1, off // 2, n // 2))
+            cols.append(fp4_col_full.narrow(0, off, n).view(_FP4))
+            off += n
+        sc_row_cat = torch.cat(sc_row, 1).view(_E4M3)
+    return (rows, [t.view(_E4M3) for t in sc_row], amax_sg[:, 1].contiguous(), cols, [t.view(_E4M3) for t in sc_col],
+            fp4_row_full.view(_FP4), sc_row_cat, fp4_col_full.view(_FP4), sc_col_cat.view(_E4M3))
+
+
 def tk_quantize_weight_2d(input):
     """tk_quantize.cu:2445-2555 — 16x16-tile weight quantisation, returns
     (row_fp4, row_sc, col_fp4, col_sc, sg, sg)."""

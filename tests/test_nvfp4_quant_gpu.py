@@ -229,6 +229,30 @@ def test_split3_one_launch_equals_the_single_input_quantiser(M, splits):
     assert_status_ok()
 
 
+@pytest.mark.parametrize("sections", [(512, 128, 256), (256, 384), (128, 128, 256, 128)])
+def test_group_quantiser_of_one_matrix_equals_the_single_input_quantiser_per_group(sections):
+    """tk_group_quantize_dim1_for_gemm: the column groups of a concatenated matrix, three groups through the grouped
+    launch, other counts one call per group."""
+    tkq = mod("tk_quant_v5")
+    M = 256
+    g = torch.Generator(device="cuda").manual_seed(sum(sections))
+    parts = [(10.0 ** (-i) * torch.randn(M, n, device="cuda", generator=g)).to(torch.bfloat16) for i, n in enumerate(sections)]
+    out = tkq.tk_group_quantize_dim1_for_gemm(torch.cat(parts, 1).contiguous(), list(sections))
+    assert len(out) == 9
+    for i, x in enumerate(parts):
+        one = tkq.tk_quantize_for_gemm(x, True, True)
+        assert torch.equal(out[0][i].contiguous().view(torch.uint8), one[0].view(torch.uint8))
+        assert torch.equal(out[1][i].view(torch.uint8).flatten(), one[1].view(torch.uint8).flatten())
+        assert torch.equal(out[3][i].view(torch.uint8), one[2].view(torch.uint8))
+        assert torch.equal(out[4][i].view(torch.uint8).flatten(), one[3].view(torch.uint8).flatten())
+        assert out[2][i].item() == one[4].item()
+    assert torch.equal(out[6].view(torch.uint8), torch.cat([t.view(torch.uint8) for t in out[1]], 1))
+    assert torch.equal(out[8].view(torch.uint8), torch.cat([t.view(torch.uint8) for t in out[4]], 0))
+    with pytest.raises(RuntimeError):
+        tkq.tk_group_quantize_dim1_for_gemm(torch.cat(parts, 1).contiguous(), [128])
+    assert_status_ok()
+
+
 def test_split3_group_quantiser_writes_slices_of_the_concatenated_operands():
     """Three gradient streams of different widths (one of them a strided view), each with its own tensor amax: the
     slices of the concatenated code matrices and the per-group scales equal the single-input quantiser's bytes,
